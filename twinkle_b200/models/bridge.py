@@ -1,0 +1,170 @@
+"""HF ↔ internal-layout weight bridge.
+
+The reference reaches Hugging Face checkpoints through ``save_pretrained``
+(transformers backend) or the external ``mcore_bridge`` package (Megatron
+backend, ``src/twinkle/model/megatron/megatron.py:874-945``).  This bridge is
+the single converter for every parallel layout of the owned decoder:
+
+* fused ``qkv_proj`` / ``gate_up_proj`` ⇄ separate HF ``q/k/v_proj`` and
+  ``gate/up_proj`` (row concatenation, so splitting is bit-exact);
+* fused expert tensors ``[E, …]`` ⇄ per-expert HF tensors;
+* tensor-parallel shards ⇄ full tensors (column-parallel: rows; row-parallel:
+  columns; fused projections are sharded per logical part so every rank holds
+  whole heads);
+* pipeline stages own disjoint layer ranges;
+* PEFT adapter key names ``base_model.model.<module>.lora_A.weight``.
+
+All conversions are pure slicing / concatenation — no arithmetic — hence a
+save → load round trip is bitwise.
+"""
+from __future__ import annotations
+
+import re
+from typing import Callable, Dict, Iterable, Iterator, List, Optional, Tuple
+
+import torch
+
+from .config import DecoderConfig
+
+_LAYER = re.compile(r'^layers\.(\d+)\.(.+)$')
+
+
+def _hf_layer(i: int, rest: str) -> str:
+    return f'model.layers.{i}.{rest}'
+
+
+def internal_to_hf(name: str, tensor: torch.Tensor, cfg: DecoderConfig) -> List[Tuple[str, torch.Tensor]]:
+    """One internal (full, un-sharded) tensor → one or more HF tensors."""
+    if name == 'embed_tokens.weight':
+        return [('model.embed_tokens.weight', tensor)]
+    if name == 'norm.weight':
+        return [('model.norm.weight', tensor)]
+    if name == 'lm_head.weight':
+        return [('lm_head.weight', tensor)]
+    m = _LAYER.match(name)
+    if not m:
+        raise KeyError(f'no HF mapping for {name}')
+    i, rest = int(m.group(1)), m.group(2)
+    if rest in ('self_attn.qkv_proj.weight', 'self_attn.qkv_proj.bias'):
+        kind = rest.rsplit('.', 1)[1]
+        q, k, v = tensor.split([cfg.q_size, cfg.kv_size, cfg.kv_size], dim=0)
+        return [(_hf_layer(i, f'self_attn.q_proj.{kind}'), q), (_hf_layer(i, f'self_attn.k_proj.{kind}'), k),
+                (_hf_layer(i, f'self_attn.v_proj.{kind}'), v)]
+    if rest == 'mlp.gate_up_proj.weight':
+        g, u = tensor.chunk(2, dim=0)
+        return [(_hf_layer(i, 'mlp.gate_proj.weight'), g), (_hf_layer(i, 'mlp.up_proj.weight'), u)]
+    if rest == 'mlp.experts.gate_up_proj':
+        out = []
+        for e in range(tensor.shape[0]):
+            g, u = tensor[e].chunk(2, dim=0)
+            out += [(_hf_layer(i, f'mlp.experts.{e}.gate_proj.weight'), g), (_hf_layer(i, f'mlp.experts.{e}.up_proj.weight'), u)]
+        return out
+    if rest == 'mlp.experts.down_proj':
+        return [(_hf_layer(i, f'mlp.experts.{e}.down_proj.weight'), tensor[e]) for e in range(tensor.shape[0])]
+    return [(_hf_layer(i, rest), tensor)]
+
+
+def hf_names_for(name: str, cfg: DecoderConfig) -> List[str]:
+    """HF tensor names that make up one internal tensor (in concat order)."""
+    meta = torch.empty(0)
+    if name == 'embed_tokens.weight':
+        return ['model.embed_tokens.weight']
+    if name == 'norm.weight':
+        return ['model.norm.weight']
+    if name == 'lm_head.weight':
+        return ['lm_head.weight']
+    m = _LAYER.match(name)
+    i, rest = int(m.group(1)), m.group(2)
+    if rest.startswith('self_attn.qkv_proj.'):
+        kind = rest.rsplit('.', 1)[1]
+        return [_hf_layer(i, f'self_attn.{p}_proj.{kind}') for p in 'qkv']
+    if rest == 'mlp.gate_up_proj.weight':
+        return [_hf_layer(i, 'mlp.gate_proj.weight'), _hf_layer(i, 'mlp.up_proj.weight')]
+    if rest == 'mlp.experts.gate_up_proj':
+        return [_hf_layer(i, f'mlp.experts.{e}.{p}_proj.weight') for e in range(cfg.num_experts) for p in ('gate', 'up')]
+    if rest == 'mlp.experts.down_proj':
+        return [_hf_layer(i, f'mlp.experts.{e}.down_proj.weight') for e in range(cfg.num_experts)]
+    return [_hf_layer(i, rest)]
+
+
+def hf_to_internal(name: str, cfg: DecoderConfig, get: Callable[[str], torch.Tensor],
+                   expert_range: Optional[Tuple[int, int]] = None) -> torch.Tensor:
+    """Assemble one internal tensor from HF tensors fetched by ``get``."""
+    m = _LAYER.match(name)
+    rest = m.group(2) if m else ''
+    i = int(m.group(1)) if m else -1
+    if rest == 'mlp.experts.gate_up_proj':
+        lo, hi = expert_range or (0, cfg.num_experts)
+        return torch.stack([torch.cat([get(_hf_layer(i, f'mlp.experts.{e}.gate_proj.weight')),
+                                       get(_hf_layer(i, f'mlp.experts.{e}.up_proj.weight'))], 0) for e in range(lo, hi)])
+    if rest == 'mlp.experts.down_proj':
+        lo, hi = expert_range or (0, cfg.num_experts)
+        return torch.stack([get(_hf_layer(i, f'mlp.experts.{e}.down_proj.weight')) for e in range(lo, hi)])
+    parts = [get(n) for n in hf_names_for(name, cfg)]
+    return parts[0] if len(parts) == 1 else torch.cat(parts, 0)
+
+
+# ------------------------------------------------------ tensor-parallel layout
+def tp_rule(name: str, cfg: DecoderConfig):
+    """How an internal tensor is split over a tensor-parallel group:
+    ``('col', parts)`` rows sharded per logical part, ``('row', None)`` columns
+    sharded, ``('vocab', None)`` rows sharded (embedding / head), or ``None`` = replicated."""
+    if name in ('embed_tokens.weight', 'lm_head.weight'):
+        return ('vocab', None)
+    m = _LAYER.match(name)
+    if not m:
+        return None
+    rest = m.group(2)
+    if rest.startswith('self_attn.qkv_proj.'):
+        return ('col', [cfg.q_size, cfg.kv_size, cfg.kv_size])
+    if rest == 'mlp.gate_up_proj.weight':
+        half = cfg.intermediate_size
+        return ('col', [half, half])
+    if rest in ('self_attn.o_proj.weight', 'mlp.down_proj.weight'):
+        return ('row', None)
+    return None
+
+
+def tp_shard(name: str, full: torch.Tensor, cfg: DecoderConfig, tp_rank: int, tp_size: int) -> torch.Tensor:
+    rule = tp_rule(name, cfg)
+    if rule is None or tp_size == 1:
+        return full
+    kind, parts = rule
+    if kind == 'col':
+        pieces = full.split(parts, dim=0)
+        return torch.cat([p.chunk(tp_size, dim=0)[tp_rank] for p in pieces], 0)
+    if kind == 'row':
+        return full.chunk(tp_size, dim=1)[tp_rank]
+    return full.chunk(tp_size, dim=0)[tp_rank]  # vocab
+
+
+def tp_unshard(name: str, shards: List[torch.Tensor], cfg: DecoderConfig) -> torch.Tensor:
+    rule = tp_rule(name, cfg)
+    if rule is None or len(shards) == 1:
+        return shards[0]
+    kind, parts = rule
+    tp = len(shards)
+    if kind == 'col':
+        per = [p // tp for p in parts]
+        split = [s.split(per, dim=0) for s in shards]
+        return torch.cat([torch.cat([split[r][j] for r in range(tp)], 0) for j in range(len(parts))], 0)
+    if kind == 'row':
+        return torch.cat(shards, 1)
+    return torch.cat(shards, 0)
+
+
+# --------------------------------------------------------------------- PEFT
+def lora_internal_to_peft(module_name: str, part: str, which: str) -> str:
+    """``layers.3.self_attn.qkv_proj`` + ``q_proj`` + ``A`` →
+    ``base_model.model.model.layers.3.self_attn.q_proj.lora_A.weight``."""
+    prefix = module_name.rsplit('.', 1)[0] if '.' in module_name else ''
+    hf_mod = f'{prefix}.{part}' if prefix else part
+    if not hf_mod.startswith('lm_head'):
+        hf_mod = 'model.' + hf_mod
+    return f'base_model.model.{hf_mod}.lora_{which}.weight'
+
+
+def lora_expert_to_peft(module_name: str, which_proj: str, which: str) -> str:
+    """Expert (target-parameter) LoRA keys: ``…mlp.experts.lora_A.gate_up_proj``-style
+    names collapse to ``base_model.model.model.layers.N.mlp.experts.<proj>.lora_A.weight``."""
+    return f'base_model.model.model.{module_name}.{which_proj}_proj.lora_{which}.weight'

@@ -1,0 +1,154 @@
+"""Architecture description of the owned decoder family.
+
+One config class covers Qwen3 dense, Qwen3-MoE and Llama/Qwen2-style decoders
+(q/k-norm optional, attention bias optional).  ``from_hf`` reads a Hugging Face
+``config.json`` dict; ``to_hf`` writes one back, so checkpoints stay loadable by
+``transformers``.  Presets are the BASELINE architectures with random init.
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import asdict, dataclass, field
+from typing import Any, Dict, Optional
+
+
+@dataclass
+class DecoderConfig:
+    vocab_size: int = 151936
+    hidden_size: int = 4096
+    intermediate_size: int = 12288
+    num_hidden_layers: int = 36
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 8
+    head_dim: int = 128
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1e6
+    tie_word_embeddings: bool = False
+    qk_norm: bool = True
+    attention_bias: bool = False
+    rms_norm_offset: float = 0.0  # 1.0 for gemma-style "1 + w"
+    # MoE (num_experts == 0 → dense)
+    num_experts: int = 0
+    num_experts_per_tok: int = 8
+    moe_intermediate_size: int = 768
+    norm_topk_prob: bool = True
+    router_aux_loss_coef: float = 0.0
+    shared_expert_intermediate_size: int = 0
+    initializer_range: float = 0.02
+    model_type: str = 'qwen3'
+    torch_dtype: str = 'bfloat16'
+    max_position_embeddings: int = 40960
+    pad_token_id: Optional[int] = None
+    eos_token_id: Optional[int] = None
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    @property
+    def q_size(self) -> int:
+        return self.num_attention_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+    def num_params(self) -> int:
+        h, L = self.hidden_size, self.num_hidden_layers
+        attn = h * (self.q_size + 2 * self.kv_size) + self.q_size * h + (2 * self.head_dim if self.qk_norm else 0)
+        if self.is_moe:
+            ffn = self.num_experts * 3 * h * self.moe_intermediate_size + h * self.num_experts
+        else:
+            ffn = 3 * h * self.intermediate_size
+        per_layer = attn + ffn + 2 * h
+        emb = self.vocab_size * h * (1 if self.tie_word_embeddings else 2)
+        return L * per_layer + emb + h
+
+    def flops_per_token(self, avg_context: float = 0.0) -> float:
+        """Forward+backward matmul FLOPs per token (6·N_active + attention)."""
+        h, L = self.hidden_size, self.num_hidden_layers
+        attn_w = h * (self.q_size + 2 * self.kv_size) + self.q_size * h
+        ffn_w = (self.num_experts_per_tok * 3 * h * self.moe_intermediate_size + h * self.num_experts) if self.is_moe \
+            else 3 * h * self.intermediate_size
+        dense = L * (attn_w + ffn_w) + self.vocab_size * h
+        attn = L * 2 * self.q_size * avg_context  # QKᵀ and PV, causal average context
+        return 6.0 * dense + 6.0 * attn
+
+    # ---------------------------------------------------------------- HF I/O
+    @classmethod
+    def from_hf(cls, cfg: Dict[str, Any]) -> 'DecoderConfig':
+        cfg = dict(cfg)
+        if 'text_config' in cfg:
+            cfg = dict(cfg['text_config'])
+        mt = cfg.get('model_type', 'qwen3')
+        heads = cfg.get('num_attention_heads', 32)
+        out = cls(
+            vocab_size=cfg.get('vocab_size', 151936), hidden_size=cfg.get('hidden_size', 4096),
+            intermediate_size=cfg.get('intermediate_size', 12288), num_hidden_layers=cfg.get('num_hidden_layers', 36),
+            num_attention_heads=heads, num_key_value_heads=cfg.get('num_key_value_heads', heads),
+            head_dim=cfg.get('head_dim') or cfg.get('hidden_size', 4096) // heads, rms_norm_eps=cfg.get('rms_norm_eps', 1e-6),
+            rope_theta=float(cfg.get('rope_theta', (cfg.get('rope_parameters') or {}).get('rope_theta', 1e6))),
+            tie_word_embeddings=bool(cfg.get('tie_word_embeddings', False)),
+            qk_norm=mt.startswith('qwen3'), attention_bias=bool(cfg.get('attention_bias', mt == 'qwen2')),
+            num_experts=cfg.get('num_experts', cfg.get('num_local_experts', 0)) or 0,
+            num_experts_per_tok=cfg.get('num_experts_per_tok', 8), moe_intermediate_size=cfg.get('moe_intermediate_size', 768),
+            norm_topk_prob=bool(cfg.get('norm_topk_prob', True)), router_aux_loss_coef=float(cfg.get('router_aux_loss_coef', 0.0)),
+            initializer_range=cfg.get('initializer_range', 0.02), model_type=mt,
+            torch_dtype=str(cfg.get('torch_dtype', cfg.get('dtype', 'bfloat16'))),
+            max_position_embeddings=cfg.get('max_position_embeddings', 40960), pad_token_id=cfg.get('pad_token_id'),
+            eos_token_id=cfg.get('eos_token_id') if not isinstance(cfg.get('eos_token_id'), list) else cfg['eos_token_id'][0])
+        return out
+
+    @classmethod
+    def from_pretrained(cls, path: str) -> 'DecoderConfig':
+        with open(os.path.join(path, 'config.json')) as f:
+            return cls.from_hf(json.load(f))
+
+    def to_hf(self) -> Dict[str, Any]:
+        arch = 'Qwen3MoeForCausalLM' if self.is_moe else ('Qwen3ForCausalLM' if self.qk_norm else 'LlamaForCausalLM')
+        d = {
+            'architectures': [arch], 'model_type': 'qwen3_moe' if self.is_moe else self.model_type,
+            'vocab_size': self.vocab_size, 'hidden_size': self.hidden_size, 'intermediate_size': self.intermediate_size,
+            'num_hidden_layers': self.num_hidden_layers, 'num_attention_heads': self.num_attention_heads,
+            'num_key_value_heads': self.num_key_value_heads, 'head_dim': self.head_dim, 'rms_norm_eps': self.rms_norm_eps,
+            'rope_theta': self.rope_theta, 'tie_word_embeddings': self.tie_word_embeddings, 'attention_bias': self.attention_bias,
+            'hidden_act': 'silu', 'initializer_range': self.initializer_range, 'torch_dtype': self.torch_dtype,
+            'max_position_embeddings': self.max_position_embeddings,
+        }
+        if self.is_moe:
+            d.update(num_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
+                     moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob,
+                     router_aux_loss_coef=self.router_aux_loss_coef, decoder_sparse_step=1, mlp_only_layers=[])
+        return d
+
+    def save_pretrained(self, path: str) -> None:
+        os.makedirs(path, exist_ok=True)
+        with open(os.path.join(path, 'config.json'), 'w') as f:
+            json.dump(self.to_hf(), f, indent=2)
+
+
+PRESETS: Dict[str, Dict[str, Any]] = {
+    # BASELINE config 1
+    'tiny-dense': dict(vocab_size=1024, hidden_size=256, intermediate_size=688, num_hidden_layers=2, num_attention_heads=4,
+                       num_key_value_heads=2, head_dim=64, rope_theta=1e4, tie_word_embeddings=True, qk_norm=True,
+                       torch_dtype='float32'),
+    'tiny-moe': dict(vocab_size=1024, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                     head_dim=64, rope_theta=1e4, tie_word_embeddings=True, num_experts=8, num_experts_per_tok=2,
+                     moe_intermediate_size=128, router_aux_loss_coef=1e-3, torch_dtype='float32'),
+    'qwen3-0.6b': dict(hidden_size=1024, intermediate_size=3072, num_hidden_layers=28, num_attention_heads=16,
+                       num_key_value_heads=8, head_dim=128, tie_word_embeddings=True),
+    'qwen3-8b': dict(hidden_size=4096, intermediate_size=12288, num_hidden_layers=36, num_attention_heads=32,
+                     num_key_value_heads=8, head_dim=128),
+    'qwen3-32b': dict(hidden_size=5120, intermediate_size=25600, num_hidden_layers=64, num_attention_heads=64,
+                      num_key_value_heads=8, head_dim=128),
+    'qwen3-30b-a3b': dict(hidden_size=2048, intermediate_size=6144, num_hidden_layers=48, num_attention_heads=32,
+                          num_key_value_heads=4, head_dim=128, num_experts=128, num_experts_per_tok=8,
+                          moe_intermediate_size=768, router_aux_loss_coef=1e-3),
+}
+
+
+def preset(name: str, **overrides) -> DecoderConfig:
+    kw = dict(PRESETS[name.lower()])
+    kw.update(overrides)
+    return DecoderConfig(**kw)

@@ -1,0 +1,330 @@
+"""The owned decoder-only transformer (Qwen3 dense / Qwen3-MoE / Llama-style).
+
+The reference wraps Hugging Face modules (``src/twinkle/model/transformers/
+transformers.py:203-233``); here the network is written once against the
+``ops`` layer so that every hot op is our own kernel on B200 and the same code
+runs in fp32 on CPU for the gloo tests.  Tensors are always *packed*:
+``[T, hidden]`` rows of all sequences back to back, with ``cu_seqlens``
+delimiting them (padding-free; reference ``processor/base.py:501-524``).
+
+Parallel behaviour is injected, not hard-coded: ``attn_parallel`` (Ulysses
+head↔sequence exchange), ``moe_parallel`` (expert-parallel dispatch/combine) and
+``tp`` (tensor-parallel linears) are small strategy objects set by the engine.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from .config import DecoderConfig
+from .layers import Embedding, Linear, RMSNorm
+
+
+@dataclass
+class PackedBatch:
+    """What one forward consumes (already on the right device)."""
+    input_ids: torch.Tensor  # [T] int64
+    position_ids: torch.Tensor  # [T] int64
+    cu_seqlens: torch.Tensor  # [n+1] int32 — boundaries of the *full* (un-split) sequences
+    max_seqlen: int
+    labels: Optional[torch.Tensor] = None  # [T] int64, pre-shifted, −100 = ignore
+    # router replay: per layer [T, k] expert ids to force (reference moe/router_replay.py)
+    routed_experts: Optional[List[torch.Tensor]] = None
+    inputs_embeds: Optional[torch.Tensor] = None
+
+
+class Attention(nn.Module):
+
+    def __init__(self, cfg: DecoderConfig, layer_idx: int):
+        super().__init__()
+        self.cfg, self.layer_idx = cfg, layer_idx
+        h, d = cfg.hidden_size, cfg.head_dim
+        self.hq, self.hkv, self.d = cfg.num_attention_heads, cfg.num_key_value_heads, d
+        self.qkv_proj = Linear(h, cfg.q_size + 2 * cfg.kv_size, bias=cfg.attention_bias,
+                               parts=[('q_proj', cfg.q_size), ('k_proj', cfg.kv_size), ('v_proj', cfg.kv_size)])
+        self.o_proj = Linear(cfg.q_size, h, bias=False, name='o_proj')
+        if cfg.qk_norm:
+            self.q_norm = RMSNorm(d, cfg.rms_norm_eps)
+            self.k_norm = RMSNorm(d, cfg.rms_norm_eps)
+        else:
+            self.q_norm = self.k_norm = None
+        self.attn_parallel = None  # Ulysses strategy or None
+
+    def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, batch: PackedBatch,
+                kv_sink=None) -> torch.Tensor:
+        qkv = self.qkv_proj(x)
+        qw = self.q_norm.weight if self.q_norm is not None else None
+        kw = self.k_norm.weight if self.k_norm is not None else None
+        q, k, v = ops.qkv_norm_rope(qkv, qw, kw, cos, sin, self.hq, self.hkv, self.d, self.cfg.rms_norm_eps)
+        if kv_sink is not None:  # sampler prefill: keep K/V for the paged cache
+            kv_sink(self.layer_idx, k, v)
+        ap = self.attn_parallel
+        if ap is not None:
+            q, k, v = ap.scatter_heads(q, k, v)  # [T_local,H,D] → [T_full,H/sp,D]
+        o = ops.flash_attn_varlen(q, k, v, batch.cu_seqlens, batch.max_seqlen, True, 1.0 / math.sqrt(self.d))
+        if ap is not None:
+            o = ap.gather_heads(o)  # back to [T_local, Hq, D]
+        return self.o_proj(o.reshape(o.shape[0], -1))
+
+
+class MLP(nn.Module):
+
+    def __init__(self, cfg: DecoderConfig, intermediate: Optional[int] = None):
+        super().__init__()
+        i = intermediate or cfg.intermediate_size
+        self.gate_up_proj = Linear(cfg.hidden_size, 2 * i, parts=[('gate_proj', i), ('up_proj', i)])
+        self.down_proj = Linear(i, cfg.hidden_size, name='down_proj')
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.down_proj(ops.swiglu(self.gate_up_proj(x)))
+
+
+class Experts(nn.Module):
+    """Fused expert weights ``gate_up_proj [E, 2I, H]`` and ``down_proj [E, H, I]``
+    (local experts only under expert parallelism), with an optional per-expert
+    LoRA pool ``A [S, E, R, in]`` / ``B [S, E, out, R]`` (reference
+    ``model/multi_lora_target_parameters.py:38-118``)."""
+
+    def __init__(self, cfg: DecoderConfig, num_local: Optional[int] = None):
+        super().__init__()
+        e = num_local if num_local is not None else cfg.num_experts
+        self.num_local, self.first_expert = e, 0
+        self.gate_up_proj = nn.Parameter(torch.empty(e, 2 * cfg.moe_intermediate_size, cfg.hidden_size))
+        self.down_proj = nn.Parameter(torch.empty(e, cfg.hidden_size, cfg.moe_intermediate_size))
+        self.lora = nn.ParameterDict()
+        self.max_loras = 0
+
+    def add_lora_pool(self, max_loras: int, max_r: int) -> None:
+        e, two_i, h = self.gate_up_proj.shape
+        i = two_i // 2
+        dev, dt = self.gate_up_proj.device, self.gate_up_proj.dtype
+        self.max_loras, self.max_r = max_loras, max_r
+
+        def mk_a(inp):
+            a = torch.empty(max_loras, e, max_r, inp, device=dev, dtype=dt)
+            nn.init.kaiming_uniform_(a.view(-1, inp), a=math.sqrt(5))
+            return nn.Parameter(a)
+
+        self.lora['gate_up_A'] = mk_a(h)
+        self.lora['gate_up_B'] = nn.Parameter(torch.zeros(max_loras, e, two_i, max_r, device=dev, dtype=dt))
+        self.lora['down_A'] = mk_a(i)
+        self.lora['down_B'] = nn.Parameter(torch.zeros(max_loras, e, h, max_r, device=dev, dtype=dt))
+
+    def _expert_lora(self, x, offsets, which: str):
+        from .layers import current_lora_batch
+        lb = current_lora_batch()
+        if lb is None or self.max_loras == 0:
+            return None
+        slots = [int(s) for s in lb.seg_slots.tolist() if int(s) >= 0]
+        if not slots:
+            return None
+        if len(set(slots)) > 1:
+            raise NotImplementedError('expert LoRA serves one tenant per forward; token-level tenants mix only in dense linears')
+        slot = slots[0]
+        i = lb.seg_slots.tolist().index(slot)
+        t = lb.targets[i] if lb.targets else None
+        if t is not None and not t.matches('mlp.experts.' + which, which):
+            return None
+        r, scale = int(lb.seg_ranks[i]), float(lb.seg_scales[i])
+        a = self.lora[which + '_A'][slot, :, :r]  # [E, r, in]
+        b = self.lora[which + '_B'][slot, :, :, :r]  # [E, out, r]
+        h = ops.grouped_gemm(x, a, offsets)
+        return ops.grouped_gemm(h, b, offsets) * scale
+
+    def forward(self, x_sorted: torch.Tensor, offsets: torch.Tensor) -> torch.Tensor:
+        """``x_sorted`` rows grouped by local expert; ``offsets [E_local+1]``."""
+        gu = ops.grouped_gemm(x_sorted, self.gate_up_proj, offsets)
+        d = self._expert_lora(x_sorted, offsets, 'gate_up')
+        if d is not None:
+            gu = gu + d
+        act = ops.swiglu(gu)
+        y = ops.grouped_gemm(act, self.down_proj, offsets)
+        d = self._expert_lora(act, offsets, 'down')
+        if d is not None:
+            y = y + d
+        return y
+
+
+class MoEBlock(nn.Module):
+    """Router → top-k → (dispatch) → grouped experts → (combine) → weighted sum."""
+
+    def __init__(self, cfg: DecoderConfig, layer_idx: int):
+        super().__init__()
+        self.cfg, self.layer_idx = cfg, layer_idx
+        self.gate = Linear(cfg.hidden_size, cfg.num_experts, name='gate')
+        self.experts = Experts(cfg)
+        self.moe_parallel = None  # expert-parallel strategy or None
+        self.last_routed: Optional[torch.Tensor] = None
+        self.last_aux: Optional[torch.Tensor] = None
+        self.record_routing = False
+
+    def route(self, x: torch.Tensor, forced: Optional[torch.Tensor]):
+        logits = self.gate(x)
+        probs = torch.softmax(logits.float(), -1)
+        if forced is not None:
+            idx = forced.to(probs.device).long()
+            w = probs.gather(-1, idx)
+        else:
+            w, idx = probs.topk(self.cfg.num_experts_per_tok, -1)
+        if self.cfg.norm_topk_prob:
+            w = w / w.sum(-1, keepdim=True)
+        return w, idx, probs
+
+    def forward(self, x: torch.Tensor, forced: Optional[torch.Tensor] = None) -> torch.Tensor:
+        T, H = x.shape
+        k, E = self.cfg.num_experts_per_tok, self.cfg.num_experts
+        w, idx, probs = self.route(x, forced)
+        if self.record_routing:
+            self.last_routed = idx.detach()
+        if self.cfg.router_aux_loss_coef > 0 and torch.is_grad_enabled():
+            self.last_aux = ops.ref.moe_aux_loss(probs, idx, E)
+        mp = self.moe_parallel
+        if mp is not None:
+            return mp.forward(self, x, w, idx)
+        # local: sort (token, slot) pairs by expert
+        flat = idx.reshape(-1)
+        order = torch.argsort(flat, stable=True)
+        counts = torch.bincount(flat, minlength=E)
+        offsets = torch.zeros(E + 1, dtype=torch.int32, device=x.device)
+        offsets[1:] = counts.cumsum(0)
+        tok = order // k
+        y = self.experts(x.index_select(0, tok), offsets)
+        y = y * w.reshape(-1)[order].to(y.dtype).unsqueeze(-1)
+        out = torch.zeros(T, H, dtype=y.dtype, device=x.device)
+        out.index_add_(0, tok, y)
+        return out
+
+
+class DecoderLayer(nn.Module):
+
+    def __init__(self, cfg: DecoderConfig, layer_idx: int):
+        super().__init__()
+        self.layer_idx = layer_idx
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.rms_norm_offset)
+        self.self_attn = Attention(cfg, layer_idx)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.rms_norm_offset)
+        self.mlp = MoEBlock(cfg, layer_idx) if cfg.is_moe else MLP(cfg)
+        self.is_moe = cfg.is_moe
+
+    def forward(self, x: torch.Tensor, cos, sin, batch: PackedBatch, kv_sink=None) -> torch.Tensor:
+        h = x + self.self_attn(self.input_layernorm(x), cos, sin, batch, kv_sink)
+        n = self.post_attention_layernorm(h)
+        if self.is_moe:
+            forced = batch.routed_experts[self.layer_idx] if batch.routed_experts is not None else None
+            return h + self.mlp(n, forced)
+        return h + self.mlp(n)
+
+
+class DecoderModel(nn.Module):
+    """Embedding → N layers → final norm → (lm_head).  ``forward`` returns the
+    final hidden states; log-probs are formed by ``token_logprobs`` through the
+    fused lm_head + log-softmax kernel so logits are only built on request."""
+
+    def __init__(self, cfg: DecoderConfig, layer_range: Optional[Tuple[int, int]] = None, has_embed: bool = True,
+                 has_head: bool = True):
+        super().__init__()
+        self.cfg = cfg
+        lo, hi = layer_range or (0, cfg.num_hidden_layers)
+        self.layer_range = (lo, hi)
+        self.embed_tokens = Embedding(cfg.vocab_size, cfg.hidden_size) if has_embed else None
+        self.layers = nn.ModuleList([DecoderLayer(cfg, i) for i in range(lo, hi)])
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.rms_norm_offset) if has_head else None
+        if has_head and not cfg.tie_word_embeddings:
+            self.lm_head = Linear(cfg.hidden_size, cfg.vocab_size, name='lm_head')
+        else:
+            self.lm_head = None
+        self.has_head = has_head
+        for name, m in self.named_modules():
+            if isinstance(m, Linear):
+                m.full_name = name
+        self.layer_runner = None  # engine hook: runs one layer (checkpoint / FSDP unshard)
+
+    # --------------------------------------------------------------- init
+    @torch.no_grad()
+    def init_weights(self, seed: int = 0, std: Optional[float] = None) -> None:
+        """N(0, initializer_range) for matrices, ones for norms; the generator is
+        per-parameter-name so any sharding of the same model yields identical values."""
+        std = std or self.cfg.initializer_range
+        from ..utils.seed import stable_seed
+        for name, p in self.named_parameters():
+            if 'lora_' in name or name.startswith('lora'):
+                continue
+            if p.dim() == 1:
+                if name.endswith('bias'):
+                    p.zero_()
+                else:
+                    p.fill_(1.0 if self.cfg.rms_norm_offset == 0.0 else 0.0)
+                continue
+            g = torch.Generator(device='cpu').manual_seed(stable_seed(seed, name))
+            if p.numel() <= 2**24 or p.device.type == 'cpu':
+                p.copy_(torch.randn(p.shape, generator=g, dtype=torch.float32).mul_(std))
+            else:  # large matrices: draw on the device, still deterministic per name
+                gd = torch.Generator(device=p.device).manual_seed(stable_seed(seed, name))
+                p.normal_(0.0, std, generator=gd)
+
+    def head_weight(self) -> torch.Tensor:
+        return self.lm_head.weight if self.lm_head is not None else self.embed_tokens.weight
+
+    # ------------------------------------------------------------ forward
+    def embed(self, batch: PackedBatch) -> torch.Tensor:
+        if batch.inputs_embeds is not None:
+            return batch.inputs_embeds
+        return self.embed_tokens(batch.input_ids)
+
+    def forward(self, batch: PackedBatch, hidden: Optional[torch.Tensor] = None, kv_sink=None) -> torch.Tensor:
+        x = self.embed(batch) if hidden is None else hidden
+        cos, sin = ops.rope_tables(batch.position_ids, self.cfg.head_dim, self.cfg.rope_theta)
+        run = self.layer_runner
+        for layer in self.layers:
+            if run is not None:
+                x = run(layer, x, cos, sin, batch)
+            else:
+                x = layer(x, cos, sin, batch, kv_sink)
+        if self.norm is not None:
+            x = self.norm(x)
+        return x
+
+    def logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        return ops.linear(hidden, self.head_weight())
+
+    def token_logprobs(self, hidden: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0,
+                       with_entropy: bool = False):
+        """(logps [T] fp32, entropies|None) with ignored labels (−100) read as id 0."""
+        safe = labels.clamp_min(0)
+        return ops.fused_linear_logprob(hidden, self.head_weight(), safe, temperature, with_entropy)
+
+    def aux_loss(self) -> Optional[torch.Tensor]:
+        terms = [l.mlp.last_aux for l in self.layers if getattr(l, 'is_moe', False) and l.mlp.last_aux is not None]
+        if not terms:
+            return None
+        for l in self.layers:
+            if getattr(l, 'is_moe', False):
+                l.mlp.last_aux = None
+        return torch.stack(terms).mean() * self.cfg.router_aux_loss_coef
+
+    def collect_routed_experts(self) -> Optional[List[torch.Tensor]]:
+        out = [l.mlp.last_routed for l in self.layers if getattr(l, 'is_moe', False)]
+        return out if out and all(o is not None for o in out) else None
+
+    def set_record_routing(self, on: bool) -> None:
+        for l in self.layers:
+            if getattr(l, 'is_moe', False):
+                l.mlp.record_routing = on
+
+    def lora_modules(self) -> List[Tuple[str, nn.Module]]:
+        return [(n, m) for n, m in self.named_modules() if isinstance(m, (Linear, Experts))]
+
+
+def build_model(cfg: DecoderConfig, device='cpu', dtype=torch.float32, seed: int = 0, init: bool = True,
+                **kw) -> DecoderModel:
+    with torch.device(device):
+        model = DecoderModel(cfg, **kw)
+    model.to(dtype)
+    if init:
+        model.init_weights(seed)
+    return model

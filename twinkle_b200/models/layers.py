@@ -1,0 +1,170 @@
+"""Building blocks of the owned decoder: LoRA-capable linears, norms, embedding.
+
+The LoRA slot pool follows the contract of the reference's
+``src/twinkle/model/multi_lora.py:209-330``: ``max_loras`` physical adapters
+of rank ``max_r`` exist on every target linear from start-up; a tenant bound to
+a slot uses only the first ``r`` rows of ``A`` / columns of ``B`` and its own
+``alpha/r`` (or ``alpha/√r``) scale; modules not matched by the tenant's
+``target_modules`` skip the delta.  Unlike the reference (one tenant per
+forward) a batch may carry several tenants: ``LoraBatch`` names, per token
+segment, which slot applies, and the segmented kernel (``ops.sgmv``) serves
+them in one launch.
+"""
+from __future__ import annotations
+
+import math
+import re
+from contextlib import contextmanager
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+
+
+@dataclass
+class LoraBatch:
+    """Per-forward LoRA routing: segment ``i`` covers token rows
+    ``seg_starts[i]:seg_starts[i+1]`` and uses ``seg_slots[i]`` (−1 = base only)."""
+    seg_starts: torch.Tensor  # int32 [n+1]
+    seg_slots: torch.Tensor  # int32 [n]
+    seg_ranks: torch.Tensor  # int32 [n]
+    seg_scales: torch.Tensor  # fp32 [n]
+    targets: List[Optional[object]] = field(default_factory=list)  # per segment: compiled target filter
+
+    @staticmethod
+    def single(num_tokens: int, slot: int, rank: int, scale: float, device, target=None) -> 'LoraBatch':
+        return LoraBatch(torch.tensor([0, num_tokens], dtype=torch.int32, device=device),
+                         torch.tensor([slot], dtype=torch.int32, device=device),
+                         torch.tensor([rank], dtype=torch.int32, device=device),
+                         torch.tensor([scale], dtype=torch.float32, device=device), [target])
+
+
+class _LoraContext:
+    batch: Optional[LoraBatch] = None
+
+
+_CTX = _LoraContext()
+
+
+@contextmanager
+def lora_batch(batch: Optional[LoraBatch]):
+    prev = _CTX.batch
+    _CTX.batch = batch
+    try:
+        yield
+    finally:
+        _CTX.batch = prev
+
+
+def current_lora_batch() -> Optional[LoraBatch]:
+    return _CTX.batch
+
+
+class TargetFilter:
+    """``'all-linear'``, a list of module-name suffixes, or a full-match regex."""
+
+    def __init__(self, spec):
+        self.spec = spec
+        self._re = None
+        if isinstance(spec, str) and spec not in ('all-linear', 'all'):
+            self._re = re.compile(spec)
+
+    def matches(self, full_name: str, short_name: str) -> bool:
+        s = self.spec
+        if s is None or s in ('all-linear', 'all'):
+            return short_name not in ('lm_head', 'gate')  # PEFT's all-linear excludes the output head; router kept off
+        if self._re is not None:
+            return self._re.fullmatch(full_name) is not None
+        return any(full_name == t or full_name.endswith('.' + t) or short_name == t for t in s)
+
+
+class Linear(nn.Module):
+    """``y = x Wᵀ (+ b)`` with an optional LoRA slot pool.
+
+    ``parts`` names the logical HF projections fused along the output dim, e.g.
+    ``[('q_proj', 4096), ('k_proj', 1024), ('v_proj', 1024)]``; each part owns its
+    own ``A``/``B`` so adapters stay PEFT-compatible per projection.
+    """
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = False,
+                 parts: Optional[Sequence[Tuple[str, int]]] = None, name: str = ''):
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.weight = nn.Parameter(torch.empty(out_features, in_features))
+        self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
+        self.parts = list(parts) if parts else [(name or 'linear', out_features)]
+        assert sum(n for _, n in self.parts) == out_features
+        self.full_name = ''  # set by the model after construction
+        self.lora_A = nn.ParameterDict()
+        self.lora_B = nn.ParameterDict()
+        self.max_loras = 0
+        self.max_r = 0
+        self.wgrad_out: Optional[torch.Tensor] = None  # flat-bucket view to accumulate dW into
+
+    # ------------------------------------------------------------- LoRA pool
+    def add_lora_pool(self, max_loras: int, max_r: int, dtype=None, device=None) -> None:
+        dtype = dtype or self.weight.dtype
+        device = device or self.weight.device
+        self.max_loras, self.max_r = max_loras, max_r
+        for pname, n in self.parts:
+            a = torch.empty(max_loras, max_r, self.in_features, dtype=dtype, device=device)
+            for s in range(max_loras):
+                nn.init.kaiming_uniform_(a[s], a=math.sqrt(5))
+            self.lora_A[pname] = nn.Parameter(a)
+            self.lora_B[pname] = nn.Parameter(torch.zeros(max_loras, n, max_r, dtype=dtype, device=device))
+
+    def has_lora(self) -> bool:
+        return self.max_loras > 0
+
+    def _lora_delta(self, x2: torch.Tensor, lb: LoraBatch) -> Optional[torch.Tensor]:
+        prefix = self.full_name.rsplit('.', 1)[0] if '.' in self.full_name else ''
+        outs: List[Optional[torch.Tensor]] = []
+        for pname, n in self.parts:
+            slots = lb.seg_slots
+            if lb.targets and any(t is not None for t in lb.targets):
+                keep = [t is None or t.matches(f'{prefix}.{pname}' if prefix else pname, pname) for t in lb.targets]
+                if not any(keep):
+                    outs.append(None)
+                    continue
+                if not all(keep):
+                    slots = torch.where(torch.tensor(keep, device=slots.device), slots, torch.full_like(slots, -1))
+            outs.append(ops.sgmv(x2, self.lora_A[pname], self.lora_B[pname], lb.seg_starts, slots, lb.seg_ranks,
+                                 lb.seg_scales))
+        if all(o is None for o in outs):
+            return None
+        outs = [o if o is not None else x2.new_zeros(x2.shape[0], n) for o, (_, n) in zip(outs, self.parts)]
+        return outs[0] if len(outs) == 1 else torch.cat(outs, -1)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = ops.linear(x, self.weight, self.bias, self.wgrad_out if self.weight.requires_grad else None)
+        lb = _CTX.batch
+        if lb is not None and self.max_loras > 0:
+            x2 = x.reshape(-1, x.shape[-1])
+            d = self._lora_delta(x2, lb)
+            if d is not None:
+                y = y + d.view(y.shape)
+        return y
+
+
+class RMSNorm(nn.Module):
+
+    def __init__(self, dim: int, eps: float = 1e-6, offset: float = 0.0):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim) if offset == 0.0 else torch.zeros(dim))
+        self.eps, self.offset = eps, offset
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.rmsnorm(x, self.weight, self.eps, self.offset)
+
+
+class Embedding(nn.Module):
+
+    def __init__(self, num: int, dim: int):
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(num, dim))
+
+    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        return torch.nn.functional.embedding(ids, self.weight)

@@ -1,0 +1,422 @@
+"""Operator layer: autograd-aware entry points for every hot op.
+
+On CUDA tensors each op launches a hand-written sm_100a kernel from the
+in-tree extension ``twinkle_b200/ops/_C*.so`` (sources in ``ops/csrc``); if the
+extension cannot be loaded on a machine that has a GPU the import fails loudly
+instead of falling back.  On CPU tensors the fp32 formulas of
+``ops.reference`` run (used by gloo tests and as oracles).
+
+Kernel ↔ reference-site map (what each op replaces in the reference project):
+``linear`` → ``F.linear`` everywhere; ``flash_attn_varlen`` → flash-attn varlen
+(``model/transformers/strategy/sequence_parallel/__init__.py:230-337``);
+``rmsnorm``/``swiglu``/``qk_norm_rope`` → Liger kernels (``kernel/liger.py``);
+``fused_linear_logprob`` → ``utils/torch_utils.py:61-137`` +
+``loss/liger_fused_linear_cross_entropy.py``; ``adamw_step`` → ``torch.optim.AdamW``;
+``sgmv`` → ``model/multi_lora.py:320-326``; ``moe_*`` →
+``model/transformers/moe/expert_parallel.py``.
+"""
+from __future__ import annotations
+
+import math
+import os
+from typing import Optional, Tuple
+
+import torch
+
+from . import reference as ref
+
+_EXT = None
+
+
+def ext():
+    """The compiled extension; loaded on first use."""
+    global _EXT
+    if _EXT is None:
+        from .build import load_extension
+        _EXT = load_extension()
+    return _EXT
+
+
+def has_ext() -> bool:
+    try:
+        return ext() is not None
+    except Exception:
+        return False
+
+
+def _cuda(t: torch.Tensor) -> bool:
+    return t.is_cuda
+
+
+# ------------------------------------------------------------------ linear
+class _Linear(torch.autograd.Function):
+    """y = x @ Wᵀ with three tcgen05 GEMM layouts: NT forward, NN for dX, TN for dW."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, wgrad_out):
+        ctx.save_for_backward(x, weight)
+        ctx.has_bias = bias is not None
+        ctx.wgrad_out = wgrad_out
+        x2 = x.reshape(-1, x.shape[-1])
+        y = gemm(x2, weight, 'nt')
+        if bias is not None:
+            y = y + bias
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, weight = ctx.saved_tensors
+        g2 = gy.reshape(-1, gy.shape[-1])
+        if not g2.is_contiguous():
+            g2 = g2.contiguous()
+        x2 = x.reshape(-1, x.shape[-1])
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gx = gemm(g2, weight, 'nn').view(x.shape)
+        if ctx.needs_input_grad[1]:
+            if ctx.wgrad_out is not None:
+                # accumulate straight into the flat gradient bucket (fp32 or bf16)
+                gemm(g2, x2, 'tn', out=ctx.wgrad_out, accumulate=True)
+                gw = None
+            else:
+                gw = gemm(g2, x2, 'tn')
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            gb = g2.float().sum(0).to(gy.dtype)
+        return gx, gw, gb, None
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, layout: str = 'nt', out: Optional[torch.Tensor] = None,
+         accumulate: bool = False, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``nt``: a[M,K]·b[N,K]ᵀ; ``nn``: a[M,K]·b[K,N]; ``tn``: a[K,M]ᵀ·b[K,N].  bf16
+    operands, fp32 accumulation in tensor memory, bf16 or fp32 output."""
+    if _cuda(a) and a.dtype == torch.bfloat16:
+        return ext().gemm(a, b, layout, out, accumulate, out_dtype)
+    af, bf = a.float(), b.float()
+    r = af @ bf.t() if layout == 'nt' else (af @ bf if layout == 'nn' else af.t() @ bf)
+    if out is not None:
+        if accumulate:
+            out.add_(r.to(out.dtype))
+        else:
+            out.copy_(r)
+        return out
+    return r.to(out_dtype or a.dtype)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, wgrad_out: Optional[torch.Tensor] = None):
+    if _cuda(x) and x.dtype == torch.bfloat16:
+        return _Linear.apply(x, weight, bias, wgrad_out)
+    return torch.nn.functional.linear(x, weight, bias)
+
+
+# ------------------------------------------------------------------- norms
+class _RMSNorm(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, x, weight, eps, offset):
+        x2 = x.reshape(-1, x.shape[-1])
+        y, rstd = ext().rmsnorm_fwd(x2, weight, eps, offset)
+        ctx.save_for_backward(x2, weight, rstd)
+        ctx.offset = offset
+        ctx.shape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, weight, rstd = ctx.saved_tensors
+        gx, gw = ext().rmsnorm_bwd(gy.reshape(x2.shape).contiguous(), x2, weight, rstd, ctx.offset)
+        return gx.view(ctx.shape), gw.to(weight.dtype), None, None
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, offset: float = 0.0) -> torch.Tensor:
+    if _cuda(x) and x.dtype == torch.bfloat16:
+        return _RMSNorm.apply(x, weight, eps, offset)
+    return ref.rmsnorm(x, weight, eps, offset)
+
+
+def add_rmsnorm(x, residual, weight, eps: float = 1e-6, offset: float = 0.0):
+    """Returns (normed, new_residual).  The add is a separate (cheap, fused by
+    the caching allocator-friendly kernel) step on CUDA so autograd sees two
+    differentiable ops."""
+    if _cuda(x) and x.dtype == torch.bfloat16:
+        new_res = x + residual
+        return rmsnorm(new_res, weight, eps, offset), new_res
+    return ref.add_rmsnorm(x, residual, weight, eps, offset)
+
+
+# -------------------------------------------------------------------- rope
+class _QKNormRope(torch.autograd.Function):
+    """In: fused qkv ``[T, (Hq+2Hkv)·D]``; out: q ``[T,Hq,D]``, k ``[T,Hkv,D]``,
+    v ``[T,Hkv,D]`` — per-head RMSNorm on q,k then rotate-half RoPE, one pass."""
+
+    @staticmethod
+    def forward(ctx, qkv, q_weight, k_weight, cos, sin, hq, hkv, d, eps):
+        q, k, v, rstd = ext().qk_norm_rope_fwd(qkv, q_weight, k_weight, cos, sin, hq, hkv, d, eps)
+        ctx.save_for_backward(qkv, q_weight, k_weight, cos, sin, rstd)
+        ctx.dims = (hq, hkv, d, eps)
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, gq, gk, gv):
+        qkv, qw, kw, cos, sin, rstd = ctx.saved_tensors
+        hq, hkv, d, eps = ctx.dims
+        gqkv, gqw, gkw = ext().qk_norm_rope_bwd(gq.contiguous(), gk.contiguous(), gv.contiguous(), qkv, qw, kw, cos, sin,
+                                                rstd, hq, hkv, d)
+        return gqkv, gqw.to(qw.dtype), gkw.to(kw.dtype), None, None, None, None, None, None
+
+
+def qkv_norm_rope(qkv: torch.Tensor, q_weight, k_weight, cos, sin, hq: int, hkv: int, d: int, eps: float = 1e-6):
+    """Split fused qkv, apply q/k RMSNorm (if weights given) and RoPE."""
+    if _cuda(qkv) and qkv.dtype == torch.bfloat16 and q_weight is not None:
+        return _QKNormRope.apply(qkv, q_weight, k_weight, cos, sin, hq, hkv, d, eps)
+    T = qkv.shape[0]
+    q, k, v = qkv.split([hq * d, hkv * d, hkv * d], dim=-1)
+    q, k, v = q.reshape(T, hq, d), k.reshape(T, hkv, d), v.reshape(T, hkv, d)
+    q, k = ref.qk_norm_rope(q, k, q_weight, k_weight, cos, sin, eps)
+    return q, k, v
+
+
+def rope_tables(positions: torch.Tensor, head_dim: int, theta: float = 1e6):
+    return ref.rope_tables(positions, head_dim, theta)
+
+
+# ------------------------------------------------------------------ swiglu
+class _SwiGLU(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, gate_up):
+        ctx.save_for_backward(gate_up)
+        return ext().swiglu_fwd(gate_up)
+
+    @staticmethod
+    def backward(ctx, gy):
+        (gate_up, ) = ctx.saved_tensors
+        return ext().swiglu_bwd(gy.contiguous(), gate_up)
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    if _cuda(gate_up) and gate_up.dtype == torch.bfloat16:
+        return _SwiGLU.apply(gate_up)
+    return ref.swiglu(gate_up)
+
+
+# --------------------------------------------------------------- attention
+class _FlashAttnVarlen(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu_seqlens, max_seqlen, causal, scale):
+        out, lse = ext().flash_attn_fwd(q, k, v, cu_seqlens, max_seqlen, causal, scale)
+        ctx.save_for_backward(q, k, v, out, lse, cu_seqlens)
+        ctx.args = (max_seqlen, causal, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, gout):
+        q, k, v, out, lse, cu = ctx.saved_tensors
+        max_seqlen, causal, scale = ctx.args
+        dq, dk, dv = ext().flash_attn_bwd(gout.contiguous(), q, k, v, out, lse, cu, max_seqlen, causal, scale)
+        return dq, dk, dv, None, None, None, None
+
+
+def flash_attn_varlen(q, k, v, cu_seqlens, max_seqlen: int, causal: bool = True, scale: Optional[float] = None):
+    """Packed causal attention with GQA.  ``q [T,Hq,D]``, ``k,v [T,Hkv,D]``."""
+    scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
+    if _cuda(q) and q.dtype == torch.bfloat16:
+        return _FlashAttnVarlen.apply(q.contiguous(), k.contiguous(), v.contiguous(), cu_seqlens.to(torch.int32),
+                                      int(max_seqlen), causal, scale)
+    return ref.attention_varlen(q, k, v, cu_seqlens, causal, scale)
+
+
+def paged_attention_decode(q, k_cache, v_cache, block_tables, seq_lens, scale: Optional[float] = None):
+    scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
+    if _cuda(q) and q.dtype == torch.bfloat16:
+        return ext().paged_attn_decode(q.contiguous(), k_cache, v_cache, block_tables.to(torch.int32),
+                                       seq_lens.to(torch.int32), scale)
+    return ref.paged_attention_decode(q, k_cache, v_cache, block_tables, seq_lens, scale)
+
+
+# ------------------------------------------------------------- logprob / CE
+class _LogprobFromLogits(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, logits, labels, temperature, with_entropy):
+        x = logits.reshape(-1, logits.shape[-1])
+        lp, lse, ent = ext().logprob_fwd(x, labels.reshape(-1).to(torch.int64), temperature, with_entropy)
+        ctx.save_for_backward(x, labels.reshape(-1).to(torch.int64), lse, ent if with_entropy else lse)
+        ctx.temperature, ctx.with_entropy, ctx.shape = temperature, with_entropy, logits.shape
+        out_shape = labels.shape
+        return lp.view(out_shape), (ent.view(out_shape) if with_entropy else lp.new_zeros(()))
+
+    @staticmethod
+    def backward(ctx, glp, gent):
+        x, labels, lse, ent = ctx.saved_tensors
+        gent_flat = gent.reshape(-1).contiguous().float() if ctx.with_entropy else None
+        gx = ext().logprob_bwd(x, labels, lse, ent if ctx.with_entropy else None, glp.reshape(-1).contiguous().float(), gent_flat,
+                               ctx.temperature)
+        return gx.view(ctx.shape), None, None, None
+
+
+def logprob_from_logits(logits, labels, temperature: float = 1.0, with_entropy: bool = False):
+    """(logps, entropy|None); differentiable w.r.t. logits."""
+    if _cuda(logits) and logits.dtype in (torch.bfloat16, torch.float32):
+        lp, ent = _LogprobFromLogits.apply(logits.contiguous(), labels, temperature, with_entropy)
+        return lp, (ent if with_entropy else None)
+    return ref.logprob_from_logits(logits, labels, temperature, with_entropy)
+
+
+class _FusedLinearLogprob(torch.autograd.Function):
+    """lm_head GEMM + online-softmax statistics, chunked over tokens so the
+    ``[T, V]`` logits never exist; backward re-forms each chunk's logits,
+    converts them in place to dlogits and feeds the two gradient GEMMs."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, labels, temperature, with_entropy, chunk, wgrad_out):
+        T = hidden.shape[0]
+        lp = torch.empty(T, dtype=torch.float32, device=hidden.device)
+        lse = torch.empty_like(lp)
+        ent = torch.empty_like(lp) if with_entropy else None
+        labels = labels.to(torch.int64)
+        for s in range(0, T, chunk):
+            e = min(s + chunk, T)
+            logits = gemm(hidden[s:e], weight, 'nt')
+            a, b, c = ext().logprob_fwd(logits, labels[s:e], temperature, with_entropy)
+            lp[s:e], lse[s:e] = a, b
+            if with_entropy:
+                ent[s:e] = c
+        ctx.save_for_backward(hidden, weight, labels, lse, ent if with_entropy else lse)
+        ctx.cfg = (temperature, with_entropy, chunk)
+        ctx.wgrad_out = wgrad_out
+        return lp, (ent if with_entropy else lp.new_zeros(()))
+
+    @staticmethod
+    def backward(ctx, glp, gent):
+        hidden, weight, labels, lse, ent = ctx.saved_tensors
+        temperature, with_entropy, chunk = ctx.cfg
+        T = hidden.shape[0]
+        glp = glp.contiguous().float()
+        gent = gent.contiguous().float() if with_entropy else None
+        gh = torch.empty_like(hidden) if ctx.needs_input_grad[0] else None
+        need_w = ctx.needs_input_grad[1]
+        gw = ctx.wgrad_out
+        if need_w and gw is None:
+            gw = torch.zeros(weight.shape, dtype=torch.float32, device=weight.device)
+        for s in range(0, T, chunk):
+            e = min(s + chunk, T)
+            logits = gemm(hidden[s:e], weight, 'nt')
+            dlogits = ext().logprob_bwd(logits, labels[s:e], lse[s:e], ent[s:e] if with_entropy else None, glp[s:e],
+                                        gent[s:e] if with_entropy else None, temperature)
+            if gh is not None:
+                gemm(dlogits, weight, 'nn', out=gh[s:e])
+            if need_w:
+                gemm(dlogits, hidden[s:e], 'tn', out=gw, accumulate=True)
+        gw_ret = None
+        if need_w and ctx.wgrad_out is None:
+            gw_ret = gw.to(weight.dtype)
+        return gh, gw_ret, None, None, None, None, None
+
+
+def fused_linear_logprob(hidden, weight, labels, temperature: float = 1.0, with_entropy: bool = False, chunk: int = 4096,
+                         wgrad_out: Optional[torch.Tensor] = None):
+    """(logps [T] fp32, entropy|None) of ``labels`` under ``softmax(hidden·Wᵀ/T)``."""
+    if _cuda(hidden) and hidden.dtype == torch.bfloat16:
+        lp, ent = _FusedLinearLogprob.apply(hidden, weight, labels, temperature, with_entropy, chunk, wgrad_out)
+        return lp, (ent if with_entropy else None)
+    return ref.fused_linear_logprob(hidden, weight, labels, temperature, with_entropy)
+
+
+# ------------------------------------------------------------------- adamw
+def adamw_step(master, exp_avg, exp_avg_sq, grad, param_out, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0):
+    if _cuda(master):
+        ext().adamw_step(master, exp_avg, exp_avg_sq, grad, param_out, float(lr), float(beta1), float(beta2), float(eps),
+                         float(weight_decay), int(step), float(grad_scale))
+    else:
+        ref.adamw_step(master, exp_avg, exp_avg_sq, grad, param_out, lr, beta1, beta2, eps, weight_decay, step, grad_scale)
+
+
+def sumsq(t: torch.Tensor) -> torch.Tensor:
+    """Σ t² in fp32 as a 0-d tensor (partial of an L2 grad norm)."""
+    if _cuda(t) and t.dtype in (torch.bfloat16, torch.float32) and t.is_contiguous():
+        return ext().sumsq(t)
+    return t.float().pow(2).sum()
+
+
+# -------------------------------------------------------------------- lora
+class _SGMV(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, x, lora_a, lora_b, seg_starts, seg_slots, seg_ranks, seg_scales):
+        h = ext().sgmv_shrink(x, lora_a, seg_starts, seg_slots, seg_ranks)  # [T, R] fp32→bf16
+        y = ext().sgmv_expand(h, lora_b, seg_starts, seg_slots, seg_ranks, seg_scales)
+        ctx.save_for_backward(x, lora_a, lora_b, h, seg_starts, seg_slots, seg_ranks, seg_scales)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, a, b, h, st, sl, rk, sc = ctx.saved_tensors
+        gy = gy.contiguous()
+        gx, ga, gb = ext().sgmv_bwd(gy, x, a, b, h, st, sl, rk, sc, ctx.needs_input_grad[0])
+        return gx, ga.to(a.dtype), gb.to(b.dtype), None, None, None, None
+
+
+def sgmv(x, lora_a, lora_b, seg_starts, seg_slots, seg_ranks, seg_scales):
+    """Multi-tenant LoRA delta for a token-segmented batch (see ``reference.sgmv``)."""
+    if _cuda(x) and x.dtype == torch.bfloat16:
+        return _SGMV.apply(x, lora_a, lora_b, seg_starts.to(torch.int32), seg_slots.to(torch.int32),
+                           seg_ranks.to(torch.int32), seg_scales.float())
+    return _sgmv_autograd_cpu(x, lora_a, lora_b, seg_starts, seg_slots, seg_ranks, seg_scales)
+
+
+def _sgmv_autograd_cpu(x, lora_a, lora_b, seg_starts, seg_slots, seg_ranks, seg_scales):
+    outs = []
+    starts = seg_starts.tolist()
+    for i in range(len(starts) - 1):
+        xs = x[starts[i]:starts[i + 1]]
+        slot, r = int(seg_slots[i]), int(seg_ranks[i])
+        if slot < 0 or r == 0:
+            outs.append(xs.new_zeros(xs.shape[0], lora_b.shape[1]))
+        else:
+            outs.append((xs @ lora_a[slot, :r].t().to(xs.dtype)) @ lora_b[slot, :, :r].t().to(xs.dtype) * float(seg_scales[i]))
+    return torch.cat(outs, 0) if outs else x.new_zeros(0, lora_b.shape[1])
+
+
+# --------------------------------------------------------------------- moe
+def moe_router(logits, top_k: int, renormalize: bool = True):
+    """(weights [T,k] fp32, indices [T,k] int64, probs [T,E] fp32); differentiable
+    through ``weights``/``probs`` on the PyTorch path; the CUDA kernel also returns
+    the per-expert histogram used by dispatch."""
+    return ref.moe_router(logits, top_k, renormalize)
+
+
+class _GroupedGemm(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, x, weight, offsets):
+        ctx.save_for_backward(x, weight, offsets)
+        return ext().grouped_gemm(x, weight, offsets, 'nt')
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, weight, offsets = ctx.saved_tensors
+        gy = gy.contiguous()
+        gx = ext().grouped_gemm(gy, weight, offsets, 'nn') if ctx.needs_input_grad[0] else None
+        gw = ext().grouped_gemm_wgrad(gy, x, offsets, weight.shape[0]).to(weight.dtype) if ctx.needs_input_grad[1] else None
+        return gx, gw, None
+
+
+def grouped_gemm(x, weight, offsets):
+    """Per-expert GEMM over expert-sorted rows (``offsets [E+1]`` int32 on device)."""
+    if _cuda(x) and x.dtype == torch.bfloat16:
+        return _GroupedGemm.apply(x, weight, offsets.to(torch.int32))
+    outs = []
+    off = offsets.tolist()
+    for e in range(weight.shape[0]):
+        outs.append(x[off[e]:off[e + 1]] @ weight[e].t().to(x.dtype))
+    return torch.cat(outs, 0)
+
+
+def sample_tokens(logits, temperature=1.0, top_k=-1, top_p=1.0, generator=None, seeds=None):
+    if _cuda(logits) and seeds is not None:
+        return ext().sample_tokens(logits.contiguous(), float(temperature), int(top_k), float(top_p), seeds)
+    return ref.sample_tokens(logits, temperature, top_k, top_p, generator)
+
+
+__all__ = [n for n in dir() if not n.startswith('_')]

@@ -1,0 +1,254 @@
+"""Plain-PyTorch fp32 restatement of every hand-written kernel.
+
+These functions are (a) the oracle the CUDA kernels are tested against and
+(b) the path taken on CPU tensors (gloo tests).  They favour clarity over
+speed and never call a fused library kernel.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+
+# --------------------------------------------------------------------- norms
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, offset: float = 0.0) -> torch.Tensor:
+    xf = x.float()
+    inv = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return (xf * inv * (weight.float() + offset)).to(x.dtype)
+
+
+def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6,
+                offset: float = 0.0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``res' = x + residual`` (rounded to the storage dtype), ``y = rmsnorm(res')``."""
+    new_res = (x.float() + residual.float()).to(x.dtype)
+    return rmsnorm(new_res, weight, eps, offset), new_res
+
+
+# ---------------------------------------------------------------------- rope
+def rope_tables(positions: torch.Tensor, head_dim: int, theta: float = 1e6) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin ``[T, head_dim/2]`` in fp32 for integer ``positions [T]``."""
+    inv_freq = 1.0 / (theta**(torch.arange(0, head_dim, 2, dtype=torch.float32, device=positions.device) / head_dim))
+    ang = positions.float()[:, None] * inv_freq[None, :]
+    return ang.cos(), ang.sin()
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotate-half convention (HF Llama/Qwen): pairs are (i, i + D/2).  ``x [T, H, D]``."""
+    d2 = x.shape[-1] // 2
+    xf = x.float()
+    x1, x2 = xf[..., :d2], xf[..., d2:]
+    c, s = cos[:, None, :], sin[:, None, :]
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], -1).to(x.dtype)
+
+
+def qk_norm_rope(q: torch.Tensor, k: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+                 cos: torch.Tensor, sin: torch.Tensor, eps: float = 1e-6) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-head RMSNorm on q and k (Qwen3) followed by RoPE.  ``q [T,Hq,D]``, ``k [T,Hkv,D]``."""
+    if q_weight is not None:
+        q = rmsnorm(q, q_weight, eps)
+        k = rmsnorm(k, k_weight, eps)
+    return apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+
+
+# -------------------------------------------------------------------- swiglu
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """``[T, 2I]`` laid out as ``[gate | up]`` → ``silu(gate) * up`` ``[T, I]``."""
+    g, u = gate_up.float().chunk(2, dim=-1)
+    return (F.silu(g) * u).to(gate_up.dtype)
+
+
+def geglu(gate_up: torch.Tensor) -> torch.Tensor:
+    g, u = gate_up.float().chunk(2, dim=-1)
+    return (F.gelu(g, approximate='tanh') * u).to(gate_up.dtype)
+
+
+# ----------------------------------------------------------------- attention
+def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor, causal: bool = True,
+                     scale: Optional[float] = None, return_lse: bool = False):
+    """Packed attention.  ``q [T,Hq,D]``, ``k,v [T,Hkv,D]``, ``cu_seqlens`` int
+    ``[n+1]``; tokens of different segments never attend to each other; GQA by
+    repeating each kv head ``Hq/Hkv`` times."""
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    rep = Hq // Hkv
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+    out = torch.empty_like(q)
+    lse = torch.empty(Hq, T, dtype=torch.float32, device=q.device)
+    bounds = cu_seqlens.tolist()
+    for a, b in zip(bounds[:-1], bounds[1:]):
+        if b <= a:
+            continue
+        qs = q[a:b].float().transpose(0, 1)  # [Hq, L, D]
+        ks = k[a:b].float().transpose(0, 1).repeat_interleave(rep, 0)
+        vs = v[a:b].float().transpose(0, 1).repeat_interleave(rep, 0)
+        s = qs @ ks.transpose(1, 2) * scale
+        if causal:
+            L = b - a
+            s = s.masked_fill(torch.ones(L, L, dtype=torch.bool, device=q.device).triu(1), float('-inf'))
+        l = torch.logsumexp(s, -1)
+        p = torch.exp(s - l[..., None])
+        out[a:b] = (p @ vs).transpose(0, 1).to(q.dtype)
+        lse[:, a:b] = l
+    return (out, lse) if return_lse else out
+
+
+def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
+                           seq_lens: torch.Tensor, scale: Optional[float] = None) -> torch.Tensor:
+    """One query token per sequence against a paged KV cache.
+    ``q [B,Hq,D]``; caches ``[num_blocks, block_size, Hkv, D]``; ``block_tables
+    [B, max_blocks]`` int; ``seq_lens [B]`` (including the current token)."""
+    B, Hq, D = q.shape
+    bs, Hkv = k_cache.shape[1], k_cache.shape[2]
+    rep = Hq // Hkv
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+    out = torch.empty_like(q)
+    for b in range(B):
+        n = int(seq_lens[b])
+        nb = (n + bs - 1) // bs
+        blocks = block_tables[b, :nb].long()
+        kk = k_cache[blocks].reshape(-1, Hkv, D)[:n].float().repeat_interleave(rep, 1)
+        vv = v_cache[blocks].reshape(-1, Hkv, D)[:n].float().repeat_interleave(rep, 1)
+        s = torch.einsum('hd,nhd->hn', q[b].float(), kk) * scale
+        out[b] = torch.einsum('hn,nhd->hd', torch.softmax(s, -1), vv).to(q.dtype)
+    return out
+
+
+# ------------------------------------------------------------ logprob / loss
+def logprob_from_logits(logits: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0,
+                        with_entropy: bool = False) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    x = logits.float() / temperature
+    lse = torch.logsumexp(x, -1)
+    lp = x.gather(-1, labels.long().unsqueeze(-1)).squeeze(-1) - lse
+    ent = None
+    if with_entropy:
+        ent = lse - (torch.softmax(x, -1) * x).sum(-1)
+    return lp, ent
+
+
+def fused_linear_logprob(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0,
+                         with_entropy: bool = False, chunk: int = 2048) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """``log softmax(hidden @ weightᵀ / temperature)[labels]`` without keeping
+    the ``[T, V]`` matrix (chunks over T).  Differentiable via autograd."""
+    lps, ents = [], []
+    for s in range(0, hidden.shape[0], chunk):
+        logits = hidden[s:s + chunk].float() @ weight.float().t()
+        lp, ent = logprob_from_logits(logits, labels[s:s + chunk], temperature, with_entropy)
+        lps.append(lp)
+        if with_entropy:
+            ents.append(ent)
+    return torch.cat(lps), (torch.cat(ents) if with_entropy else None)
+
+
+# -------------------------------------------------------------------- adamw
+def adamw_step(master: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor, grad: torch.Tensor,
+               param_out: Optional[torch.Tensor], lr: float, beta1: float, beta2: float, eps: float, weight_decay: float,
+               step: int, grad_scale: float = 1.0) -> None:
+    """Decoupled weight decay Adam on fp32 master weights; ``grad_scale``
+    multiplies the gradient first (1/num_tokens × clip coefficient);
+    ``param_out`` (bf16 working copy) receives the rounded result."""
+    g = grad.float() * grad_scale
+    master.mul_(1.0 - lr * weight_decay)
+    exp_avg.mul_(beta1).add_(g, alpha=1.0 - beta1)
+    exp_avg_sq.mul_(beta2).addcmul_(g, g, value=1.0 - beta2)
+    bc1 = 1.0 - beta1**step
+    bc2 = 1.0 - beta2**step
+    denom = (exp_avg_sq / bc2).sqrt_().add_(eps)
+    master.addcdiv_(exp_avg / bc1, denom, value=-lr)
+    if param_out is not None:
+        param_out.copy_(master)
+
+
+# --------------------------------------------------------------------- lora
+def sgmv(x: torch.Tensor, lora_a: torch.Tensor, lora_b: torch.Tensor, seg_starts: torch.Tensor, seg_slots: torch.Tensor,
+         seg_ranks: torch.Tensor, seg_scales: torch.Tensor) -> torch.Tensor:
+    """Segmented multi-LoRA: rows ``seg_starts[i]:seg_starts[i+1]`` of ``x [T,K]``
+    use slot ``seg_slots[i]`` (−1 = no adapter) with rank ``seg_ranks[i]`` and
+    scale ``seg_scales[i]``.  ``lora_a [S, R, K]``, ``lora_b [S, N, R]``.
+    Returns the delta ``[T, N]`` in x's dtype."""
+    T = x.shape[0]
+    out = torch.zeros(T, lora_b.shape[1], dtype=x.dtype, device=x.device)
+    starts = seg_starts.tolist()
+    for i in range(len(starts) - 1):
+        slot, r = int(seg_slots[i]), int(seg_ranks[i])
+        if slot < 0 or r == 0 or starts[i + 1] <= starts[i]:
+            continue
+        a = lora_a[slot, :r].float()
+        b = lora_b[slot, :, :r].float()
+        xs = x[starts[i]:starts[i + 1]].float()
+        out[starts[i]:starts[i + 1]] = ((xs @ a.t()) @ b.t() * float(seg_scales[i])).to(x.dtype)
+    return out
+
+
+# ---------------------------------------------------------------------- moe
+def moe_router(logits: torch.Tensor, top_k: int, renormalize: bool = True) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """fp32 softmax → top-k → optional renormalisation.  Returns (weights [T,k]
+    fp32, indices [T,k] int64, full probabilities [T,E] fp32)."""
+    probs = torch.softmax(logits.float(), -1)
+    w, idx = probs.topk(top_k, -1)
+    if renormalize:
+        w = w / w.sum(-1, keepdim=True)
+    return w, idx, probs
+
+
+def moe_aux_loss(probs: torch.Tensor, indices: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """Switch-style load-balance loss: ``E · Σ_e f_e · P_e`` with ``f_e`` the
+    fraction of routed slots and ``P_e`` the mean router probability."""
+    T, k = indices.shape
+    f = torch.zeros(num_experts, dtype=torch.float32, device=probs.device)
+    f.scatter_add_(0, indices.reshape(-1), torch.ones(T * k, device=probs.device))
+    f = f / (T * k)
+    return num_experts * (f * probs.mean(0)).sum()
+
+
+def grouped_gemm(x: torch.Tensor, weight: torch.Tensor, offsets: torch.Tensor) -> torch.Tensor:
+    """Rows ``offsets[e]:offsets[e+1]`` of ``x [R, K]`` times ``weight[e]ᵀ`` with
+    ``weight [E, N, K]`` → ``[R, N]``."""
+    out = torch.zeros(x.shape[0], weight.shape[1], dtype=x.dtype, device=x.device)
+    off = offsets.tolist()
+    for e in range(weight.shape[0]):
+        a, b = off[e], off[e + 1]
+        if b > a:
+            out[a:b] = (x[a:b].float() @ weight[e].float().t()).to(x.dtype)
+    return out
+
+
+def moe_experts(x: torch.Tensor, weights: torch.Tensor, indices: torch.Tensor, w_gate_up: torch.Tensor,
+                w_down: torch.Tensor) -> torch.Tensor:
+    """Dense-math MoE FFN: ``Σ_k weights[t,k] · down_e(swiglu(gate_up_e(x_t)))``."""
+    T, k = indices.shape
+    out = torch.zeros(T, x.shape[1], dtype=torch.float32, device=x.device)
+    for e in range(w_gate_up.shape[0]):
+        tok, slot = (indices == e).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        h = swiglu((x[tok].float() @ w_gate_up[e].float().t()).to(x.dtype))
+        y = h.float() @ w_down[e].float().t()
+        out.index_add_(0, tok, y * weights[tok, slot, None].float())
+    return out.to(x.dtype)
+
+
+# ----------------------------------------------------------------- sampling
+def sample_tokens(logits: torch.Tensor, temperature: float = 1.0, top_k: int = -1, top_p: float = 1.0,
+                  generator: Optional[torch.Generator] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Returns (token ids [B], logprob of the chosen token under the *processed*
+    distribution [B])."""
+    x = logits.float()
+    if temperature <= 0:
+        tok = x.argmax(-1)
+        return tok, torch.zeros(x.shape[0], device=x.device)
+    x = x / temperature
+    if top_k and top_k > 0:
+        kth = x.topk(min(top_k, x.shape[-1]), -1).values[..., -1:]
+        x = x.masked_fill(x < kth, float('-inf'))
+    if top_p < 1.0:
+        sorted_x, order = x.sort(-1, descending=True)
+        cum = torch.softmax(sorted_x, -1).cumsum(-1)
+        drop = cum - torch.softmax(sorted_x, -1) >= top_p
+        sorted_x = sorted_x.masked_fill(drop, float('-inf'))
+        x = torch.full_like(x, float('-inf')).scatter(-1, order, sorted_x)
+    logp = torch.log_softmax(x, -1)
+    tok = torch.multinomial(logp.exp(), 1, generator=generator).squeeze(-1)
+    return tok, logp.gather(-1, tok[:, None]).squeeze(-1)

@@ -1,0 +1,151 @@
+"""Ulysses sequence parallelism: head ↔ sequence exchange around attention.
+
+Parity: reference ``src/twinkle/model/transformers/strategy/sequence_parallel/
+utils.py:269-401`` (``_SeqAllToAll`` / ``DistributedAttention``) and
+``__init__.py:597-671`` (``GatherLoss``).  Each rank holds a contiguous chunk of
+the packed row; before attention q/k/v go from ``[T/sp, H, D]`` to
+``[T, H/sp, D]`` (all-to-all), after attention the output goes back.  Ranks of
+one SP group are consecutive in the flattened (dp, fsdp) order, as in the
+reference (``data_rank = flat_index // ulysses_size``).
+
+Two data planes implement the exchange: ``torch.distributed.all_to_all_single``
+(baseline; gloo on CPU) and the peer-memory kernel of ``parallel.symm`` that
+writes each head slice straight into the destination rank's buffer.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .comm import Communicator
+
+_SP_GROUPS = {}
+
+
+def sp_group_for(mesh):
+    """Process group of this rank's Ulysses peers (created collectively once)."""
+    sp = mesh.ulysses_size or 1
+    if sp <= 1 or not (dist.is_available() and dist.is_initialized()):
+        return None
+    key = (id(mesh), sp)
+    if key in _SP_GROUPS:
+        return _SP_GROUPS[key]
+    # order ranks by their flat data index so that consecutive ``sp`` of them share a data rank
+    ranks = sorted(mesh._coord_of, key=lambda r: (mesh._flat_data_index(r), r))
+    by_other = {}
+    for r in ranks:
+        c = mesh.coord_of(r)
+        other = tuple(v for i, v in enumerate(c) if mesh.mesh_dim_names[i] not in ('dp', 'fsdp'))
+        by_other.setdefault(other, []).append(r)
+    mine = None
+    me = dist.get_rank()
+    for other, rs in sorted(by_other.items()):
+        for i in range(0, len(rs), sp):
+            grp_ranks = rs[i:i + sp]
+            g = dist.new_group(ranks=grp_ranks)
+            if me in grp_ranks:
+                mine = g
+    _SP_GROUPS[key] = mine
+    return mine
+
+
+class _HeadScatter(torch.autograd.Function):
+    """``[T_local, H, D]`` → ``[T_local·sp, H/sp, D]`` (forward) and the inverse (backward)."""
+
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, comm: Communicator):
+        ctx.comm = comm
+        return _seq_to_head(x, comm)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _head_to_seq(g.contiguous(), ctx.comm), None
+
+
+class _HeadGather(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, comm: Communicator):
+        ctx.comm = comm
+        return _head_to_seq(x, comm)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _seq_to_head(g.contiguous(), ctx.comm), None
+
+
+def _seq_to_head(x: torch.Tensor, comm: Communicator) -> torch.Tensor:
+    sp = comm.world_size
+    t, h, d = x.shape
+    assert h % sp == 0, f'{h} heads do not divide over sp={sp}'
+    send = x.view(t, sp, h // sp, d).transpose(0, 1).contiguous()  # [sp, t, h/sp, d] : block j goes to rank j
+    recv = torch.empty_like(send)
+    comm.all_to_all_single(recv, send)
+    return recv.view(sp * t, h // sp, d)  # blocks arrive in rank order = sequence order
+
+
+def _head_to_seq(x: torch.Tensor, comm: Communicator) -> torch.Tensor:
+    sp = comm.world_size
+    tt, hl, d = x.shape
+    t = tt // sp
+    send = x.view(sp, t, hl, d).contiguous()  # block j (token chunk j) returns to rank j
+    recv = torch.empty_like(send)
+    comm.all_to_all_single(recv, send)
+    return recv.transpose(0, 1).reshape(t, sp * hl, d)  # [t, sp, hl, d] → heads back in order
+
+
+class UlyssesAttention:
+    """Strategy object plugged into ``Attention.attn_parallel``."""
+
+    def __init__(self, comm: Communicator, num_kv_heads: int):
+        self.comm = comm
+        self.sp = comm.world_size
+        self.kv_rep = 1
+        if num_kv_heads % self.sp != 0:
+            # fewer kv heads than ranks: replicate kv heads so every rank gets one
+            if self.sp % num_kv_heads != 0:
+                raise ValueError(f'kv heads {num_kv_heads} incompatible with sp={self.sp}; use ring attention')
+            self.kv_rep = self.sp // num_kv_heads
+
+    def scatter_heads(self, q, k, v):
+        if self.kv_rep > 1:
+            k = k.repeat_interleave(self.kv_rep, dim=1)
+            v = v.repeat_interleave(self.kv_rep, dim=1)
+        return (_HeadScatter.apply(q.contiguous(), self.comm), _HeadScatter.apply(k.contiguous(), self.comm),
+                _HeadScatter.apply(v.contiguous(), self.comm))
+
+    def gather_heads(self, o):
+        return _HeadGather.apply(o.contiguous(), self.comm)
+
+
+class _GatherTokens(torch.autograd.Function):
+    """All-gather along dim 0; backward keeps this rank's slice of the gradient.
+    Every SP peer computes the same loss from the gathered values, and each
+    back-propagates only into its own chunk, so the loss is counted once."""
+
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, comm: Communicator):
+        ctx.comm, ctx.n = comm, x.shape[0]
+        return comm.all_gather_tensor(x.contiguous())
+
+    @staticmethod
+    def backward(ctx, g):
+        r = ctx.comm.rank
+        return g[r * ctx.n:(r + 1) * ctx.n].contiguous(), None
+
+
+def gather_tokens(x: torch.Tensor, comm: Communicator) -> torch.Tensor:
+    if comm.world_size == 1:
+        return x
+    return _GatherTokens.apply(x, comm)
+
+
+def apply_ulysses(model, mesh, cfg) -> None:
+    comm = Communicator(sp_group_for(mesh), next(model.parameters()).device)
+    if comm.world_size <= 1:
+        return
+    strat = UlyssesAttention(comm, cfg.num_key_value_heads)
+    for layer in model.layers:
+        layer.self_attn.attn_parallel = strat

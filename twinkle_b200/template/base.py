@@ -1,0 +1,325 @@
+"""Messages → tokens.
+
+Parity: reference ``src/twinkle/template/base.py:28-859`` — pre-pipeline
+(default system prompt, reasoning-content normalisation, standard message
+shape), chat-template rendering with labels on assistant turns only
+(round-by-round prefix tokenisation), post-pipeline (``max_length`` strategies
+raise / left / right / split / delete, attention fields, **labels rolled left by
+one** so that ``labels[t]`` is the target of ``logits[t]``),
+``concat_input_feature`` for RL (prompt ⊕ sampled tokens with labels only on
+the sampled part), ``decode``.
+
+The tokenizer is a Hugging Face tokenizer when ``model_id`` points at one; a
+self-contained byte-level ChatML tokenizer otherwise (used by tests and by
+random-init benchmarks, where no tokenizer files exist).
+"""
+from __future__ import annotations
+
+import copy
+import json
+import os
+from typing import Any, Dict, Iterable, List, Optional, Sequence, Tuple, Union
+
+import numpy as np
+
+from ..data_format import InputFeature, Message, Trajectory
+
+IGNORE = -100
+
+
+class ByteChatTokenizer:
+    """UTF-8 bytes + a few ChatML control tokens.  ids 0..255 are bytes."""
+    SPECIAL = ['<|pad|>', '<|im_start|>', '<|im_end|>', '<|endoftext|>', '<tool_call>', '</tool_call>', '<think>', '</think>']
+
+    def __init__(self, vocab_size: int = 1024):
+        self.special = {t: 256 + i for i, t in enumerate(self.SPECIAL)}
+        self.inv = {v: k for k, v in self.special.items()}
+        self.vocab_size = max(vocab_size, 256 + len(self.SPECIAL))
+        self.pad_token_id = self.special['<|pad|>']
+        self.eos_token_id = self.special['<|im_end|>']
+        self.eos_token = '<|im_end|>'
+        self.pad_token = '<|pad|>'
+
+    def __len__(self):
+        return self.vocab_size
+
+    def encode(self, text: str, add_special_tokens: bool = False) -> List[int]:
+        out: List[int] = []
+        i = 0
+        while i < len(text):
+            hit = None
+            if text[i] == '<':
+                for tok, tid in self.special.items():
+                    if text.startswith(tok, i):
+                        hit = (tok, tid)
+                        break
+            if hit:
+                out.append(hit[1])
+                i += len(hit[0])
+            else:
+                out.extend(text[i].encode('utf-8'))
+                i += 1
+        return out
+
+    def __call__(self, text, add_special_tokens=False, **kw):
+        if isinstance(text, str):
+            return {'input_ids': self.encode(text)}
+        return {'input_ids': [self.encode(t) for t in text]}
+
+    def decode(self, ids: Iterable[int], skip_special_tokens: bool = False) -> str:
+        buf, parts = bytearray(), []
+        for t in ids:
+            t = int(t)
+            if t < 256:
+                buf.append(t)
+            else:
+                if buf:
+                    parts.append(buf.decode('utf-8', errors='replace'))
+                    buf = bytearray()
+                if not skip_special_tokens and t in self.inv:
+                    parts.append(self.inv[t])
+        if buf:
+            parts.append(buf.decode('utf-8', errors='replace'))
+        return ''.join(parts)
+
+    def convert_tokens_to_ids(self, tok: str) -> int:
+        return self.special.get(tok, -1)
+
+    def apply_chat_template(self, messages: List[Dict[str, Any]], tools=None, tokenize: bool = False,
+                            add_generation_prompt: bool = False, **kw) -> str:
+        s = ''
+        if tools:
+            s += '<|im_start|>system\n# Tools\n' + '\n'.join(json.dumps(t, ensure_ascii=False) for t in tools) + '<|im_end|>\n'
+        for m in messages:
+            content = m.get('content') or ''
+            if not isinstance(content, str):
+                content = ''.join(p.get('text', '') for p in content if isinstance(p, dict))
+            if m.get('reasoning_content'):
+                content = f"<think>\n{m['reasoning_content']}\n</think>\n\n{content}"
+            for tc in m.get('tool_calls') or []:
+                args = tc.get('arguments')
+                args = args if isinstance(args, str) else json.dumps(args, ensure_ascii=False)
+                content += f'\n<tool_call>\n{{"name": "{tc.get("tool_name")}", "arguments": {args}}}\n</tool_call>'
+            s += f"<|im_start|>{m['role']}\n{content}<|im_end|>\n"
+        if add_generation_prompt:
+            s += '<|im_start|>assistant\n'
+        return s if not tokenize else self.encode(s)
+
+    def save_pretrained(self, path: str) -> None:
+        os.makedirs(path, exist_ok=True)
+        with open(os.path.join(path, 'byte_chat_tokenizer.json'), 'w') as f:
+            json.dump({'type': 'ByteChatTokenizer', 'vocab_size': self.vocab_size}, f)
+
+
+def load_tokenizer(model_id: Optional[str], vocab_size: int = 1024):
+    if model_id and os.path.isdir(str(model_id)) and any(
+            os.path.isfile(os.path.join(model_id, f)) for f in ('tokenizer.json', 'tokenizer_config.json', 'vocab.json')):
+        from transformers import AutoTokenizer
+        return AutoTokenizer.from_pretrained(model_id, trust_remote_code=False)
+    return ByteChatTokenizer(vocab_size)
+
+
+class Template:
+    """``truncation_strategy``: ``raise`` | ``left`` | ``right`` | ``split`` | ``delete``."""
+
+    def __init__(self, model_id: Optional[str] = None, tokenizer=None, max_length: Optional[int] = 8192,
+                 truncation_strategy: str = 'raise', default_system: Optional[str] = None, enable_thinking: bool = True,
+                 use_chat_template: bool = True, agent_template: Optional[str] = None, **kwargs):
+        self.model_id = model_id
+        self.tokenizer = tokenizer if tokenizer is not None else load_tokenizer(model_id, kwargs.get('vocab_size', 1024))
+        self.max_length = max_length
+        self.truncation_strategy = truncation_strategy
+        self.default_system = default_system
+        self.enable_thinking = enable_thinking
+        self.use_chat_template = use_chat_template
+        self.agent_template = agent_template
+        self.pre_pipeline = [self._add_default_system, self._to_standard_reasoning_content, self._build_standard_messages]
+        self.post_pipeline = [self._check_max_length, self._add_attention_fields, self._roll_labels]
+
+    # -------------------------------------------------------- pre-pipeline
+    def _add_default_system(self, traj: Trajectory) -> Trajectory:
+        msgs = traj.get('messages') or []
+        if self.default_system and (not msgs or msgs[0].get('role') != 'system'):
+            traj['messages'] = [{'role': 'system', 'content': self.default_system}] + list(msgs)
+        return traj
+
+    def _to_standard_reasoning_content(self, traj: Trajectory) -> Trajectory:
+        """``<think>…</think>`` inside assistant content moves to ``reasoning_content``."""
+        for m in traj.get('messages') or []:
+            c = m.get('content')
+            if m.get('role') == 'assistant' and isinstance(c, str) and '</think>' in c and not m.get('reasoning_content'):
+                head, tail = c.split('</think>', 1)
+                m['reasoning_content'] = head.replace('<think>', '').strip()
+                m['content'] = tail.lstrip('\n')
+        return traj
+
+    def _build_standard_messages(self, traj: Trajectory) -> Trajectory:
+        if not traj.get('messages') and traj.get('prompt'):
+            traj['messages'] = [{'role': 'user', 'content': traj['prompt']}]
+        for m in traj.get('messages') or []:
+            if m.get('content') is None:
+                m['content'] = ''
+        return traj
+
+    # ------------------------------------------------------------ rendering
+    def _render(self, messages: List[Message], tools=None, add_generation_prompt: bool = False) -> List[int]:
+        kw = {}
+        try:
+            text = self.tokenizer.apply_chat_template(messages, tools=tools or None, tokenize=False,
+                                                      add_generation_prompt=add_generation_prompt,
+                                                      enable_thinking=self.enable_thinking)
+        except TypeError:
+            text = self.tokenizer.apply_chat_template(messages, tokenize=False, add_generation_prompt=add_generation_prompt)
+        enc = self.tokenizer(text, add_special_tokens=False)
+        return list(enc['input_ids'])
+
+    def _encode_rounds(self, messages: List[Message], tools=None) -> Tuple[List[int], List[int]]:
+        """Token ids and un-rolled labels: tokenise growing prefixes; tokens added
+        by an assistant message (minus the generation prompt) carry labels."""
+        ids: List[int] = []
+        labels: List[int] = []
+        prev: List[int] = []
+        for i, m in enumerate(messages):
+            if m.get('role') == 'assistant':
+                with_prompt = self._render(messages[:i], tools, add_generation_prompt=True) if i > 0 else []
+                cur = self._render(messages[:i + 1], tools)
+                # common-prefix guard: some chat templates rewrite earlier turns
+                k = 0
+                while k < min(len(prev), len(cur)) and prev[k] == cur[k]:
+                    k += 1
+                if k < len(prev):
+                    ids, labels = ids[:k], labels[:k]
+                new = cur[len(ids):]
+                n_prompt = max(0, min(len(with_prompt), len(cur)) - len(ids))
+                train = m.get('loss', True) is not False
+                ids += new
+                labels += [IGNORE] * n_prompt + (list(new[n_prompt:]) if train else [IGNORE] * (len(new) - n_prompt))
+                prev = cur
+            elif i == len(messages) - 1 or messages[i + 1].get('role') == 'assistant':
+                cur = self._render(messages[:i + 1], tools)
+                k = 0
+                while k < min(len(prev), len(cur)) and prev[k] == cur[k]:
+                    k += 1
+                if k < len(prev):
+                    ids, labels = ids[:k], labels[:k]
+                new = cur[len(ids):]
+                ids += new
+                labels += [IGNORE] * len(new)
+                prev = cur
+        return ids, labels
+
+    # -------------------------------------------------------- post-pipeline
+    def _check_max_length(self, feats: List[InputFeature]) -> List[InputFeature]:
+        if not self.max_length:
+            return feats
+        out = []
+        for f in feats:
+            n = len(f['input_ids'])
+            if n <= self.max_length:
+                out.append(f)
+                continue
+            s = self.truncation_strategy
+            if s == 'raise':
+                raise ValueError(f'sequence of {n} tokens exceeds max_length={self.max_length}')
+            if s == 'delete':
+                continue
+            if s == 'left':
+                out.append({**f, 'input_ids': f['input_ids'][-self.max_length:], 'labels': f['labels'][-self.max_length:]})
+            elif s == 'right':
+                out.append({**f, 'input_ids': f['input_ids'][:self.max_length], 'labels': f['labels'][:self.max_length]})
+            elif s == 'split':
+                for a in range(0, n, self.max_length):
+                    out.append({**f, 'input_ids': f['input_ids'][a:a + self.max_length], 'labels': f['labels'][a:a + self.max_length]})
+            else:
+                raise ValueError(f'unknown truncation_strategy {s}')
+        return out
+
+    def _add_attention_fields(self, feats: List[InputFeature]) -> List[InputFeature]:
+        for f in feats:
+            n = len(f['input_ids'])
+            f['attention_mask'] = [1] * n
+            f['position_ids'] = list(range(n))
+            f['length'] = n
+        return feats
+
+    @staticmethod
+    def _roll_labels(feats: List[InputFeature]) -> List[InputFeature]:
+        for f in feats:
+            lab = list(f['labels'])
+            f['labels'] = lab[1:] + [IGNORE]
+        return feats
+
+    # ---------------------------------------------------------------- API
+    def encode(self, trajectory: Trajectory, add_generation_prompt: bool = False) -> Union[InputFeature, List[InputFeature]]:
+        traj = copy.deepcopy(dict(trajectory))
+        for fn in self.pre_pipeline:
+            traj = fn(traj)
+        msgs = traj.get('messages') or []
+        if add_generation_prompt or not any(m.get('role') == 'assistant' for m in msgs):
+            ids = self._render(msgs, traj.get('tools'), add_generation_prompt=True)
+            labels = [IGNORE] * len(ids)
+        else:
+            ids, labels = self._encode_rounds(msgs, traj.get('tools'))
+        feats: List[InputFeature] = [{'input_ids': ids, 'labels': labels}]
+        for fn in self.post_pipeline:
+            feats = fn(feats)
+        for f in feats:
+            if traj.get('user_data') is not None:
+                f['user_data'] = traj['user_data']  # type: ignore[typeddict-unknown-key]
+        if not feats:
+            return []
+        return feats[0] if len(feats) == 1 else feats
+
+    def batch_encode(self, trajectories: Sequence[Trajectory], add_generation_prompt: bool = False) -> List[InputFeature]:
+        out: List[InputFeature] = []
+        for t in trajectories:
+            r = self.encode(t, add_generation_prompt)
+            out.extend(r if isinstance(r, list) else [r])
+        return out
+
+    def decode(self, token_ids: Sequence[int], skip_special_tokens: bool = True) -> str:
+        return self.tokenizer.decode(list(token_ids), skip_special_tokens=skip_special_tokens)
+
+    def batch_decode(self, batch: Sequence[Sequence[int]], skip_special_tokens: bool = True) -> List[str]:
+        return [self.decode(x, skip_special_tokens) for x in batch]
+
+    @staticmethod
+    def concat_input_feature(prompt: InputFeature, new_tokens: Sequence[int]) -> InputFeature:
+        """Prompt ⊕ sampled tokens; (rolled) labels only on the sampled part:
+        ``labels[t] = input_ids[t+1]`` for positions whose next token was sampled."""
+        p = list(prompt['input_ids'])
+        new = [int(t) for t in new_tokens]
+        ids = p + new
+        labels = [IGNORE] * len(ids)
+        for t in range(len(p) - 1, len(ids) - 1):
+            labels[t] = ids[t + 1]
+        n = len(ids)
+        return {'input_ids': ids, 'labels': labels, 'attention_mask': [1] * n, 'position_ids': list(range(n)), 'length': n}
+
+    def pre_forward_hook(self, inputs: Dict[str, Any]) -> Dict[str, Any]:
+        """Multimodal templates merge vision embeddings here; text models pass through."""
+        return inputs
+
+    @property
+    def eos_token_id(self) -> Optional[int]:
+        return getattr(self.tokenizer, 'eos_token_id', None)
+
+
+class Qwen3Template(Template):
+    pass
+
+
+class Qwen3_5Template(Template):
+    """Hybrid-thinking chat format: an empty ``<think>`` block is emitted when
+    thinking is disabled so that the label mask matches generation."""
+
+    def __init__(self, *a, enable_thinking: bool = True, **kw):
+        super().__init__(*a, enable_thinking=enable_thinking, **kw)
+
+
+class DeepseekV4Template(Template):
+    pass
+
+
+template_mapping = {'Template': Template, 'default': Template, 'Qwen3Template': Qwen3Template, 'qwen3': Qwen3Template,
+                    'Qwen3_5Template': Qwen3_5Template, 'qwen3_5': Qwen3_5Template, 'DeepseekV4Template': DeepseekV4Template}
