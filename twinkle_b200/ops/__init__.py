@@ -250,7 +250,7 @@ class _LogprobFromLogits(torch.autograd.Function):
     def backward(ctx, glp, gent):
         x, labels, lse, ent = ctx.saved_tensors
         gent_flat = gent.reshape(-1).contiguous().float() if ctx.with_entropy else None
-        gx = ext().logprob_bwd(x, labels, lse, ent if ctx.with_entropy else None, glp.reshape(-1).contiguous().float(), gent_flat,
+        gx = ext().logprob_bwd(x.clone(), labels, lse, ent if ctx.with_entropy else None, glp.reshape(-1).contiguous().float(), gent_flat,
                                ctx.temperature)
         return gx.view(ctx.shape), None, None, None
 

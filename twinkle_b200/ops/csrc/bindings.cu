@@ -1,0 +1,52 @@
+// Python bindings of the sm_100a extension.
+#include <torch/extension.h>
+
+#include "host.h"
+
+namespace tk {
+torch::Tensor gemm(const torch::Tensor&, const torch::Tensor&, const std::string&, const c10::optional<torch::Tensor>&, bool,
+                   c10::optional<torch::ScalarType>);
+torch::Tensor grouped_gemm(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const std::string&);
+torch::Tensor grouped_gemm_wgrad(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, int64_t);
+std::vector<torch::Tensor> rmsnorm_fwd(const torch::Tensor&, const torch::Tensor&, double, double);
+std::vector<torch::Tensor> rmsnorm_bwd(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, double);
+std::vector<torch::Tensor> qk_norm_rope_fwd(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&,
+                                            const torch::Tensor&, int64_t, int64_t, int64_t, double);
+std::vector<torch::Tensor> qk_norm_rope_bwd(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&,
+                                            const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&,
+                                            const torch::Tensor&, int64_t, int64_t, int64_t);
+torch::Tensor swiglu_fwd(const torch::Tensor&);
+torch::Tensor swiglu_bwd(const torch::Tensor&, const torch::Tensor&);
+void adamw_step(torch::Tensor, torch::Tensor, torch::Tensor, const torch::Tensor&, const c10::optional<torch::Tensor>&, double, double,
+                double, double, double, int64_t, double);
+torch::Tensor sumsq(const torch::Tensor&);
+std::vector<torch::Tensor> logprob_fwd(const torch::Tensor&, const torch::Tensor&, double, bool);
+torch::Tensor logprob_bwd(torch::Tensor, const torch::Tensor&, const torch::Tensor&, const c10::optional<torch::Tensor>&,
+                          const torch::Tensor&, const c10::optional<torch::Tensor>&, double);
+std::vector<torch::Tensor> flash_attn_fwd(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, int64_t,
+                                          bool, double);
+std::vector<torch::Tensor> flash_attn_bwd(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&,
+                                          const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, int64_t, bool, double);
+}  // namespace tk
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &tk::gemm, py::arg("a"), py::arg("b"), py::arg("layout") = "nt", py::arg("out") = py::none(),
+        py::arg("accumulate") = false, py::arg("out_dtype") = py::none());
+  m.def("grouped_gemm", &tk::grouped_gemm);
+  m.def("grouped_gemm_wgrad", &tk::grouped_gemm_wgrad);
+  m.def("rmsnorm_fwd", &tk::rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &tk::rmsnorm_bwd);
+  m.def("qk_norm_rope_fwd", &tk::qk_norm_rope_fwd);
+  m.def("qk_norm_rope_bwd", &tk::qk_norm_rope_bwd);
+  m.def("swiglu_fwd", &tk::swiglu_fwd);
+  m.def("swiglu_bwd", &tk::swiglu_bwd);
+  m.def("adamw_step", &tk::adamw_step);
+  m.def("sumsq", &tk::sumsq);
+  m.def("logprob_fwd", &tk::logprob_fwd);
+  m.def("logprob_bwd", &tk::logprob_bwd);
+  m.def("flash_attn_fwd", &tk::flash_attn_fwd);
+  m.def("flash_attn_bwd", &tk::flash_attn_bwd);
+  m.def("read_and_clear_error", &tk::read_and_clear_error, "Value of the device error word (0 = healthy); clears it.");
+  m.def("num_sms", &tk::num_sms);
+  m.def("launch_count", &tk::launch_count, "Number of kernels launched by this extension so far.");
+}
