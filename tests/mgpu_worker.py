@@ -1,0 +1,116 @@
+"""Multi-GPU checks, run under torchrun (one rank per GPU).  Prints one JSON line per check on rank 0 and
+exits non-zero on the first failure.  Launched by tests/test_multigpu.py."""
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+import torch.distributed as dist
+
+
+def main():
+    rank, world, local = int(os.environ['RANK']), int(os.environ['WORLD_SIZE']), int(os.environ['LOCAL_RANK'])
+    torch.cuda.set_device(local)
+    dist.init_process_group('nccl', device_id=torch.device('cuda', local))
+    from twinkle_b200 import ops
+    from twinkle_b200.parallel.comm import Communicator
+    from twinkle_b200.parallel.symm import SymmCommunicator
+    E = ops.ext()
+    dev = torch.device('cuda', local)
+    results = {}
+
+    def report(name, ok, **kw):
+        t = torch.tensor([1 if ok else 0], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        if rank == 0:
+            print(json.dumps({'check': name, 'ok': bool(t.item()), **kw}), flush=True)
+        if not t.item():
+            dist.destroy_process_group()
+            sys.exit(1)
+
+    # ---- 1. peer all-gather / reduce-scatter kernels against NCCL
+    sc = SymmCommunicator(None, dev)
+    n = 1 << 20
+    shard = sc.alloc(n, torch.bfloat16)
+    shard.copy_(torch.randn(n, device=dev).bfloat16() + rank)
+    full = torch.empty(n * world, dtype=torch.bfloat16, device=dev)
+    dist.barrier()
+    sc.wait(sc.all_gather_async(full, shard))
+    want = torch.empty_like(full)
+    dist.all_gather_into_tensor(want, shard)
+    torch.cuda.synchronize()
+    report('peer_all_gather', bool(torch.equal(full, want)))
+    fg = sc.alloc(n * world, torch.bfloat16)
+    fg.copy_(torch.randn(n * world, device=dev).bfloat16())
+    gs = torch.ones(n, dtype=torch.float32, device=dev)
+    sc.reduce_scatter_accumulate(gs, fg, 0.5)
+    tmp = fg.float()
+    dist.all_reduce(tmp)
+    wantg = 1 + 0.5 * tmp[rank * n:(rank + 1) * n]
+    torch.cuda.synchronize()
+    err = float((gs - wantg).abs().max())
+    report('peer_reduce_scatter', err < 0.05 * world, max_err=err)
+    # ---- 2. Ulysses exchange against all_to_all
+    from twinkle_b200.parallel import ulysses as U
+    t, H, D = 256, 8, 128
+    x = torch.randn(t, H, D, device=dev).bfloat16()
+    plain = Communicator(None, dev)
+    a = U._seq_to_head(x, plain)
+    b = U._seq_to_head(x, sc)
+    c = U._head_to_seq(a, plain)
+    d = U._head_to_seq(a, sc)
+    torch.cuda.synchronize()
+    report('ulysses_push', bool(torch.equal(a, b) and torch.equal(c, d) and torch.equal(c, x)))
+    report('error_word', E.read_and_clear_error() == 0)
+
+    # ---- 3. training parity: FSDP(+Ulysses) on W GPUs vs the single-GPU curve of the same global batch
+    from twinkle_b200.model import TransformersModel
+    from twinkle_b200.models.config import preset
+    from twinkle_b200.utils.device_mesh import DeviceMesh
+    cfg = preset('qwen3-8b', num_hidden_layers=2, hidden_size=512, intermediate_size=1024, num_attention_heads=8,
+                 num_key_value_heads=2, vocab_size=4096)
+    g = torch.Generator().manual_seed(7)
+    feats = []
+    for _ in range(4):
+        ids = torch.randint(0, cfg.vocab_size, (257, ), generator=g)
+        feats.append({'input_ids': ids[:-1], 'labels': ids[1:]})
+
+    def curve(mesh, backend, my_feats, group_all=True):
+        m = TransformersModel(config=cfg, device_mesh=mesh, seed=0, comm_backend=backend, device=dev)
+        m.set_optimizer('AdamW', lr=1e-3)
+        out = []
+        for _ in range(4):
+            o = m.forward_backward(inputs=my_feats, micro_batch_size=2)
+            m.clip_grad_and_step(max_grad_norm=1.0)
+            t = torch.tensor([o['loss'] * o['num_tokens'], o['num_tokens']], device=dev, dtype=torch.float64)
+            if mesh.world_size > 1:
+                dist.all_reduce(t)
+                t = t / (mesh.ulysses_size or 1)
+            out.append(float(t[0] / t[1]))
+        return out
+
+    single = None
+    if rank == 0:
+        single = curve(DeviceMesh.from_sizes(dp_size=1), 'nccl', feats)
+    single = [single]
+    dist.broadcast_object_list(single, src=0)
+    single = single[0]
+    for backend in ('nccl', 'symm'):
+        mesh = DeviceMesh.from_sizes(fsdp_size=world, dp_size=None)
+        sl = mesh.get_slice(len(feats), mesh.get_data_rank_from_global_rank(rank))
+        c = curve(mesh, backend, feats[sl])
+        diff = max(abs(a - b) for a, b in zip(single, c))
+        report(f'fsdp{world}_{backend}_matches_single', diff < 3e-2, single=single, multi=c)
+        mesh = DeviceMesh.from_sizes(fsdp_size=world, dp_size=None, ulysses_size=world)
+        c = curve(mesh, backend, feats)
+        diff = max(abs(a - b) for a, b in zip(single, c))
+        report(f'ulysses{world}_{backend}_matches_single', diff < 3e-2, single=single, multi=c)
+    report('error_word_end', E.read_and_clear_error() == 0)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()

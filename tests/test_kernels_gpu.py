@@ -1,0 +1,211 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 restatement of the same op.
+Tolerances follow the reference's distributed tests (logits 1e-2 / 5e-3, grads 2e-2 / 1e-2) expressed
+as relative Frobenius error, which for bf16 outputs sits near 2e-3."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope='module')
+def E():
+    from twinkle_b200 import ops
+    e = ops.ext()
+    e.read_and_clear_error()
+    yield e
+    assert e.read_and_clear_error() == 0
+
+
+def rel(a, b):
+    a, b = a.float(), b.float()
+    return float((a - b).norm() / (b.norm() + 1e-12))
+
+
+@pytest.mark.parametrize('layout', ['nt', 'nn', 'tn'])
+@pytest.mark.parametrize('shape', [(128, 256, 64), (304, 520, 200), (1024, 4096, 4096), (4096, 1024, 2048), (72, 8, 64)])
+def test_gemm(E, layout, shape):
+    M, N, K = shape
+    torch.manual_seed(0)
+    if layout == 'nt':
+        a, b = torch.randn(M, K, device='cuda').bfloat16(), torch.randn(N, K, device='cuda').bfloat16()
+        r = a.float() @ b.float().t()
+    elif layout == 'nn':
+        a, b = torch.randn(M, K, device='cuda').bfloat16(), torch.randn(K, N, device='cuda').bfloat16()
+        r = a.float() @ b.float()
+    else:
+        a, b = torch.randn(K, M, device='cuda').bfloat16(), torch.randn(K, N, device='cuda').bfloat16()
+        r = a.float().t() @ b.float()
+    assert rel(E.gemm(a, b, layout), r) < 4e-3
+    assert rel(E.gemm(a, b, layout, None, False, torch.float32), r) < 1e-5
+    acc = torch.ones(M, N, device='cuda')
+    E.gemm(a, b, layout, acc, True)
+    assert rel(acc - 1, r) < 1e-5
+    assert E.read_and_clear_error() == 0
+
+
+def test_grouped_gemm(E):
+    from twinkle_b200.ops import reference as ref
+    torch.manual_seed(0)
+    Eg, K, N = 4, 256, 512
+    counts = [100, 0, 300, 128]
+    offs = [0]
+    for c in counts:
+        offs.append(offs[-1] + (c + 127) // 128 * 128)
+    x = torch.zeros(offs[-1], K, device='cuda').bfloat16()
+    for e, c in enumerate(counts):
+        x[offs[e]:offs[e] + c] = torch.randn(c, K, device='cuda').bfloat16()
+    w = torch.randn(Eg, N, K, device='cuda').bfloat16()
+    off = torch.tensor(offs, device='cuda', dtype=torch.int32)
+    want = ref.grouped_gemm(x, w, off)
+    assert rel(E.grouped_gemm(x, w, off, 'nt'), want) < 4e-3
+    assert rel(E.grouped_gemm(x, w.transpose(1, 2).contiguous(), off, 'nn'), want) < 4e-3
+    dy = torch.randn(offs[-1], N, device='cuda').bfloat16()
+    gw = E.grouped_gemm_wgrad(dy, x, off, Eg)
+    gr = torch.stack([dy[offs[e]:offs[e + 1]].float().t() @ x[offs[e]:offs[e + 1]].float() for e in range(Eg)])
+    assert rel(gw, gr) < 1e-5 and float(gw[1].abs().max()) == 0.0
+
+
+def test_rmsnorm(E):
+    from twinkle_b200 import ops
+    from twinkle_b200.ops import reference as ref
+    torch.manual_seed(0)
+    x = torch.randn(1000, 4096, device='cuda').bfloat16().requires_grad_(True)
+    w = (torch.randn(4096, device='cuda') * 0.1 + 1).bfloat16().requires_grad_(True)
+    y = ops.rmsnorm(x, w, 1e-6)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yr = ref.rmsnorm(xr, wr, 1e-6)
+    yr.backward(g.float())
+    assert rel(y, yr) < 4e-3 and rel(x.grad, xr.grad) < 4e-3 and rel(w.grad, wr.grad) < 4e-3
+
+
+def test_qk_norm_rope(E):
+    from twinkle_b200 import ops
+    from twinkle_b200.ops import reference as ref
+    torch.manual_seed(0)
+    T, hq, hkv, d = 777, 8, 2, 128
+    qkv = torch.randn(T, (hq + 2 * hkv) * d, device='cuda').bfloat16().requires_grad_(True)
+    qw = (torch.randn(d, device='cuda') * 0.1 + 1).bfloat16().requires_grad_(True)
+    kw = (torch.randn(d, device='cuda') * 0.1 + 1).bfloat16().requires_grad_(True)
+    cos, sin = ops.rope_tables(torch.arange(T, device='cuda'), d, 1e6)
+    q, k, v = ops.qkv_norm_rope(qkv, qw, kw, cos, sin, hq, hkv, d)
+    gq, gk, gv = torch.randn_like(q), torch.randn_like(k), torch.randn_like(v)
+    torch.autograd.backward([q, k, v], [gq, gk, gv])
+    qkvr, qwr, kwr = (t.detach().float().requires_grad_(True) for t in (qkv, qw, kw))
+    q_, k_, v_ = qkvr.split([hq * d, hkv * d, hkv * d], -1)
+    q_, k_, v_ = q_.reshape(T, hq, d), k_.reshape(T, hkv, d), v_.reshape(T, hkv, d)
+    q2, k2 = ref.qk_norm_rope(q_, k_, qwr, kwr, cos, sin)
+    torch.autograd.backward([q2, k2, v_], [gq.float(), gk.float(), gv.float()])
+    assert rel(q, q2) < 5e-3 and rel(k, k2) < 5e-3 and rel(v, v_) == 0
+    assert rel(qkv.grad, qkvr.grad) < 5e-3 and rel(qw.grad, qwr.grad) < 5e-3 and rel(kw.grad, kwr.grad) < 5e-3
+
+
+def test_swiglu_adamw_sumsq(E):
+    from twinkle_b200 import ops
+    from twinkle_b200.ops import reference as ref
+    torch.manual_seed(0)
+    gu = torch.randn(513, 2 * 1536, device='cuda').bfloat16().requires_grad_(True)
+    y = ops.swiglu(gu)
+    g = torch.randn_like(y)
+    y.backward(g)
+    gur = gu.detach().float().requires_grad_(True)
+    yr = ref.swiglu(gur)
+    yr.backward(g.float())
+    assert rel(y, yr) < 4e-3 and rel(gu.grad, gur.grad) < 4e-3
+    n = 1 << 20
+    m0 = torch.randn(n, device='cuda')
+    m, ea, es = m0.clone(), torch.zeros(n, device='cuda'), torch.zeros(n, device='cuda')
+    mr, ear, esr = m0.clone(), torch.zeros(n, device='cuda'), torch.zeros(n, device='cuda')
+    gr = torch.randn(n, device='cuda').bfloat16()
+    out = torch.empty(n, device='cuda', dtype=torch.bfloat16)
+    for step in (1, 2, 3):
+        ops.adamw_step(m, ea, es, gr, out, 1e-3, 0.9, 0.999, 1e-8, 0.01, step, 0.5)
+        ref.adamw_step(mr, ear, esr, gr, None, 1e-3, 0.9, 0.999, 1e-8, 0.01, step, 0.5)
+    assert rel(m, mr) < 1e-5 and rel(out, mr) < 4e-3
+    assert abs(float(ops.sumsq(gr)) / float(gr.float().pow(2).sum()) - 1) < 1e-4
+
+
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32])
+def test_logprob(E, dtype):
+    from twinkle_b200 import ops
+    from twinkle_b200.ops import reference as ref
+    torch.manual_seed(0)
+    x = (torch.randn(200, 151936, device='cuda') * 2).to(dtype).requires_grad_(True)
+    y = torch.randint(0, 151936, (200, ), device='cuda')
+    lp, ent = ops.logprob_from_logits(x, y, 0.7, True)
+    glp, ge = torch.randn_like(lp), torch.randn_like(lp)
+    torch.autograd.backward([lp, ent], [glp, ge])
+    xr = x.detach().float().requires_grad_(True)
+    lpr, entr = ref.logprob_from_logits(xr, y, 0.7, True)
+    torch.autograd.backward([lpr, entr], [glp, ge])
+    assert rel(lp, lpr) < 1e-5 and rel(ent, entr) < 1e-5 and rel(x.grad, xr.grad) < (4e-3 if dtype == torch.bfloat16 else 1e-5)
+
+
+def test_fused_linear_logprob(E):
+    from twinkle_b200 import ops
+    from twinkle_b200.ops import reference as ref
+    torch.manual_seed(0)
+    h = (torch.randn(1000, 512, device='cuda') * 0.5).bfloat16().requires_grad_(True)
+    w = (torch.randn(3000, 512, device='cuda') * 0.05).bfloat16().requires_grad_(True)
+    y = torch.randint(0, 3000, (1000, ), device='cuda')
+    lp, _ = ops.fused_linear_logprob(h, w, y, chunk=256)
+    (-lp.sum()).backward()
+    hr, wr = h.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    lpr, _ = ref.fused_linear_logprob(hr, wr, y)
+    (-lpr.sum()).backward()
+    assert rel(lp, lpr) < 1e-3 and rel(h.grad, hr.grad) < 5e-3 and rel(w.grad, wr.grad) < 5e-3
+
+
+@pytest.mark.parametrize('case', [([128], 1, 1), ([256], 2, 1), ([100, 300, 77], 4, 2), ([1024, 512, 1], 8, 2), ([2048], 32, 8)])
+def test_flash_attention(E, case):
+    from twinkle_b200 import ops
+    from twinkle_b200.ops import reference as ref
+    lens, hq, hkv = case
+    torch.manual_seed(0)
+    T, d = sum(lens), 128
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device='cuda', dtype=torch.int32)
+    q, k, v = (torch.randn(T, h, d, device='cuda').bfloat16().requires_grad_(True) for h in (hq, hkv, hkv))
+    o = ops.flash_attn_varlen(q, k, v, cu, max(lens))
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    orf = ref.attention_varlen(qr, kr, vr, cu)
+    assert rel(o, orf) < 5e-3
+    g = torch.randn_like(o)
+    o.backward(g)
+    orf.backward(g.float())
+    assert rel(q.grad, qr.grad) < 8e-3 and rel(k.grad, kr.grad) < 8e-3 and rel(v.grad, vr.grad) < 8e-3
+    assert E.read_and_clear_error() == 0
+
+
+def test_tiny_model_matches_cpu_reference(E):
+    """Whole decoder layer stack on the GPU kernels vs the same weights in fp32 on CPU."""
+    from twinkle_b200.models import PackedBatch, build_model, preset
+    cfg = preset('qwen3-8b', num_hidden_layers=2, hidden_size=512, intermediate_size=1024, num_attention_heads=4,
+                 num_key_value_heads=2, vocab_size=2048)
+    ref_model = build_model(cfg, device='cpu', dtype=torch.float32, seed=3)
+    gpu_model = build_model(cfg, device='cuda', dtype=torch.bfloat16, seed=3)
+    with torch.no_grad():
+        for (n, p), (_, pc) in zip(gpu_model.named_parameters(), ref_model.named_parameters()):
+            p.copy_(pc)
+            pc.copy_(p.float().cpu())
+    g = torch.Generator().manual_seed(0)
+    lens = [200, 120]
+    ids = torch.randint(0, cfg.vocab_size, (sum(lens), ), generator=g)
+    pos = torch.cat([torch.arange(n) for n in lens])
+    cu = torch.tensor([0, 200, 320], dtype=torch.int32)
+    labels = torch.randint(0, cfg.vocab_size, (sum(lens), ), generator=g)
+
+    def run(m, dev):
+        b = PackedBatch(ids.to(dev), pos.to(dev), cu.to(dev), 200, labels.to(dev))
+        h = m(b)
+        lp, _ = m.token_logprobs(h, b.labels)
+        loss = -lp.mean()
+        loss.backward()
+        return loss.detach().float().cpu(), m.layers[0].mlp.down_proj.weight.grad.float().cpu()
+
+    lc, gc = run(ref_model, 'cpu')
+    lg, gg = run(gpu_model, 'cuda')
+    assert abs(float(lc) - float(lg)) < 2e-2, (lc, lg)
+    assert rel(gg, gc) < 3e-2

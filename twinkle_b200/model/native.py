@@ -176,7 +176,7 @@ class TransformersModel(TwinkleModel):
             apply_expert_parallel(self.model, self.device_mesh, self.config)
         if self.sp_size > 1:
             from ..parallel.ulysses import apply_ulysses
-            apply_ulysses(self.model, self.device_mesh, self.config)
+            apply_ulysses(self.model, self.device_mesh, self.config, self.comm_backend)
         if comm.world_size > 1 and self.comm_backend in ('auto', 'symm') and self.device.type == 'cuda':
             try:
                 from ..parallel.symm import SymmCommunicator
@@ -513,6 +513,9 @@ class TransformersModel(TwinkleModel):
                     g['weight_decay'] = optim_params['weight_decay']
         og.optim_steps += 1
         scale = self._pending_scale.pop(og.adapter_name, 1.0)
+        fence = getattr(self._dp_comm(), 'step_barrier', None)
+        if fence is not None:
+            fence()  # peers have finished reading my parameter shards and gradient buffers
         gd, gn = opt.param_groups[0], opt.param_groups[1]
         lr, betas, eps = gd['lr'], gd['betas'], gd['eps']
         wd_for = lambda name: 0.0 if _no_decay(name) else gd['weight_decay']
@@ -544,6 +547,8 @@ class TransformersModel(TwinkleModel):
                     ops.adamw_step(s['master'].view(-1), s['exp_avg'].view(-1), s['exp_avg_sq'].view(-1),
                                    p.grad.contiguous().view(-1), p.data.view(-1), lr, betas[0], betas[1], eps,
                                    wd_for(name), og.optim_steps, scale)
+        if fence is not None:
+            fence()  # nobody gathers the shards before every rank has updated its own
         og.grad_ready = False
 
     @remote_function()

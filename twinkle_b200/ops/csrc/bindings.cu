@@ -27,6 +27,14 @@ std::vector<torch::Tensor> flash_attn_fwd(const torch::Tensor&, const torch::Ten
                                           bool, double);
 std::vector<torch::Tensor> flash_attn_bwd(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&,
                                           const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, int64_t, bool, double);
+std::pair<torch::Tensor, py::bytes> symm_alloc(int64_t);
+int64_t symm_open(const py::bytes&);
+void symm_close(int64_t);
+void symm_barrier(const std::vector<int64_t>&, int64_t, int64_t);
+void peer_all_gather(torch::Tensor, const std::vector<int64_t>&, int64_t, int64_t, int64_t);
+void peer_reduce_scatter_acc(torch::Tensor, const std::vector<int64_t>&, int64_t, double, const c10::optional<torch::Tensor>&, int64_t);
+void ulysses_exchange(const torch::Tensor&, const std::vector<int64_t>&, int64_t, bool, int64_t);
+void peer_copy_cast(const torch::Tensor&, const std::vector<int64_t>&, int64_t);
 }  // namespace tk
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -46,6 +54,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("logprob_bwd", &tk::logprob_bwd);
   m.def("flash_attn_fwd", &tk::flash_attn_fwd);
   m.def("flash_attn_bwd", &tk::flash_attn_bwd);
+  m.def("symm_alloc", &tk::symm_alloc, "cudaMalloc'ed uint8 tensor + its CUDA IPC handle");
+  m.def("symm_open", &tk::symm_open);
+  m.def("symm_close", &tk::symm_close);
+  m.def("symm_barrier", &tk::symm_barrier);
+  m.def("peer_all_gather", &tk::peer_all_gather);
+  m.def("peer_reduce_scatter_acc", &tk::peer_reduce_scatter_acc);
+  m.def("ulysses_exchange", &tk::ulysses_exchange);
+  m.def("peer_copy_cast", &tk::peer_copy_cast);
   m.def("read_and_clear_error", &tk::read_and_clear_error, "Value of the device error word (0 = healthy); clears it.");
   m.def("num_sms", &tk::num_sms);
   m.def("launch_count", &tk::launch_count, "Number of kernels launched by this extension so far.");

@@ -66,7 +66,10 @@ class FlatBucket:
         self.shard_numel = self.numel // self.world
         # --- persistent state -------------------------------------------------
         lo = self.rank * self.shard_numel
-        self.shard = torch.zeros(self.shard_numel, dtype=compute_dtype, device=device)
+        if self.world > 1 and hasattr(comm, 'alloc') and torch.device(device).type == 'cuda':
+            self.shard = comm.alloc(self.shard_numel, compute_dtype)  # peers pull this shard over NVLink
+        else:
+            self.shard = torch.zeros(self.shard_numel, dtype=compute_dtype, device=device)
         for p, o in zip(self.params, self.offsets):
             a, b = max(o, lo), min(o + p.numel(), lo + self.shard_numel)
             if b > a:
@@ -144,7 +147,7 @@ class FlatBucket:
                 self._bind_grads(self.grad_shard)
                 self.full_grad = None
                 return
-        self.full_grad = pool.take(self.numel, self.compute_dtype)
+        self.full_grad = pool.take_grad(self.numel, self.compute_dtype, self.comm)
         self.full_grad.zero_()
         self._bind_grads(self.full_grad)
 
@@ -161,7 +164,7 @@ class FlatBucket:
         self.comm.reduce_scatter_accumulate(self.grad_shard, self.full_grad)
         for p in self.params:
             p.grad = None
-        pool.give(self.full_grad)
+        pool.give_grad(self.full_grad)
         self.full_grad = None
 
     def zero_grad(self) -> None:
@@ -260,6 +263,26 @@ class BufferPool:
 
     def give(self, t: torch.Tensor) -> None:
         self.free.setdefault((t.numel(), t.dtype), []).append(t)
+
+    # Flat gradient buffers.  With a peer-memory communicator they live in symmetric memory (peers pull
+    # their slice) and rotate through a ring of two per size: a buffer is rewritten only after the next
+    # unit's barrier, by which time every peer has finished reading it.
+    def take_grad(self, numel: int, dtype: torch.dtype, comm) -> torch.Tensor:
+        if not hasattr(comm, 'alloc') or comm.world_size == 1 or torch.device(self.device).type != 'cuda':
+            return self.take(numel, dtype)
+        ring = self.__dict__.setdefault('_rings', {}).setdefault((numel, dtype), {'bufs': [], 'next': 0})
+        if len(ring['bufs']) < 2:
+            ring['bufs'].append(comm.alloc(numel, dtype))
+            ring['next'] = 0
+            return ring['bufs'][-1]
+        t = ring['bufs'][ring['next']]
+        ring['next'] ^= 1
+        return t
+
+    def give_grad(self, t: torch.Tensor) -> None:
+        if any(t is b for r in self.__dict__.get('_rings', {}).values() for b in r['bufs']):
+            return
+        self.give(t)
 
 
 class FSDPUnit:

@@ -76,9 +76,32 @@ class _HeadGather(torch.autograd.Function):
         return _seq_to_head(g.contiguous(), ctx.comm), None
 
 
+_SYMM_OUT = {}
+
+
+def _symm_out(comm, shape, dtype, tag):
+    """Destination buffers in symmetric memory, two per (shape, direction) used alternately so a
+    consumer of the previous exchange never races with the next push."""
+    key = (id(comm), tuple(shape), dtype, tag)
+    ent = _SYMM_OUT.get(key)
+    if ent is None:
+        n = 1
+        for v in shape:
+            n *= v
+        ent = {'bufs': [comm.alloc(n, dtype).view(shape) for _ in range(2)], 'next': 0}
+        _SYMM_OUT[key] = ent
+    t = ent['bufs'][ent['next']]
+    ent['next'] ^= 1
+    return t
+
+
 def _seq_to_head(x: torch.Tensor, comm: Communicator) -> torch.Tensor:
     sp = comm.world_size
     t, h, d = x.shape
+    if hasattr(comm, 'ulysses_exchange') and x.is_cuda:
+        out = _symm_out(comm, (sp * t, h // sp, d), x.dtype, 's2h')
+        comm.ulysses_exchange(x.contiguous(), out, True, h)
+        return out.clone()
     assert h % sp == 0, f'{h} heads do not divide over sp={sp}'
     send = x.view(t, sp, h // sp, d).transpose(0, 1).contiguous()  # [sp, t, h/sp, d] : block j goes to rank j
     recv = torch.empty_like(send)
@@ -90,6 +113,10 @@ def _head_to_seq(x: torch.Tensor, comm: Communicator) -> torch.Tensor:
     sp = comm.world_size
     tt, hl, d = x.shape
     t = tt // sp
+    if hasattr(comm, 'ulysses_exchange') and x.is_cuda:
+        out = _symm_out(comm, (t, sp * hl, d), x.dtype, 'h2s')
+        comm.ulysses_exchange(x.contiguous(), out, False, sp * hl)
+        return out.clone()
     send = x.view(sp, t, hl, d).contiguous()  # block j (token chunk j) returns to rank j
     recv = torch.empty_like(send)
     comm.all_to_all_single(recv, send)
@@ -142,10 +169,18 @@ def gather_tokens(x: torch.Tensor, comm: Communicator) -> torch.Tensor:
     return _GatherTokens.apply(x, comm)
 
 
-def apply_ulysses(model, mesh, cfg) -> None:
-    comm = Communicator(sp_group_for(mesh), next(model.parameters()).device)
+def apply_ulysses(model, mesh, cfg, backend: str = 'auto') -> None:
+    dev = next(model.parameters()).device
+    comm = Communicator(sp_group_for(mesh), dev)
     if comm.world_size <= 1:
         return
+    if backend in ('auto', 'symm') and dev.type == 'cuda':
+        try:
+            from .symm import SymmCommunicator
+            comm = SymmCommunicator(comm.group, dev)
+        except Exception:
+            if backend == 'symm':
+                raise
     strat = UlyssesAttention(comm, cfg.num_key_value_heads)
     for layer in model.layers:
         layer.self_attn.attn_parallel = strat

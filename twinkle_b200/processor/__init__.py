@@ -63,7 +63,13 @@ class MicroBatch:
     extras: Optional[Dict[str, Any]] = None
 
     def to(self, device) -> 'MicroBatch':
-        mv = lambda t: None if t is None else t.to(device, non_blocking=True)
+        def mv(t):
+            if t is None:
+                return None
+            if t.device.type == 'cpu' and torch.device(device).type == 'cuda' and not t.is_pinned():
+                t = t.pin_memory()  # staged through pinned memory so the copy is asynchronous
+            return t.to(device, non_blocking=True)
+
         return MicroBatch(mv(self.input_ids), mv(self.position_ids), mv(self.labels), mv(self.cu_seqlens), self.max_seqlen,
                           self.seq_lens, mv(self.local_index), self.extras)
 
