@@ -153,7 +153,8 @@ def main():
     torch.cuda.set_device(local)
     if world > 1:
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
-        dist.init_process_group('nccl', device_id=torch.device('cuda', local))
+        import datetime
+        dist.init_process_group('nccl', device_id=torch.device('cuda', local), timeout=datetime.timedelta(seconds=300))
     sp = min(4, world)
     mesh = DeviceMesh.from_sizes(fsdp_size=world, dp_size=None, ulysses_size=sp) if world > 1 else DeviceMesh.from_sizes(dp_size=1)
     cfg = preset(args.model) if args.layers is None else preset(args.model, num_hidden_layers=args.layers)

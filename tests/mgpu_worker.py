@@ -13,7 +13,8 @@ import torch.distributed as dist
 def main():
     rank, world, local = int(os.environ['RANK']), int(os.environ['WORLD_SIZE']), int(os.environ['LOCAL_RANK'])
     torch.cuda.set_device(local)
-    dist.init_process_group('nccl', device_id=torch.device('cuda', local))
+    import datetime
+    dist.init_process_group('nccl', device_id=torch.device('cuda', local), timeout=datetime.timedelta(seconds=90))
     from twinkle_b200 import ops
     from twinkle_b200.parallel.comm import Communicator
     from twinkle_b200.parallel.symm import SymmCommunicator

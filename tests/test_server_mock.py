@@ -1,0 +1,144 @@
+"""The whole HTTP stack on mock backends (no GPU): route set, Tinker future protocol, sessions, admission
+control, checkpoint registry, client twins.  Mirrors the reference's mock-mode server tests."""
+import os
+import time
+
+import pytest
+
+
+@pytest.fixture()
+def server(tmp_path, monkeypatch):
+    monkeypatch.setenv('TWINKLE_DEFAULT_SAVE_DIR', str(tmp_path / 'ckpt'))
+    monkeypatch.setenv('TWINKLE_LONG_POLL_TIMEOUT', '5')
+    monkeypatch.setenv('TWINKLE_POLL_INTERVAL', '0.02')
+    from twinkle_b200.server import ServerLauncher
+    cfg = {
+        'persistence': {'mode': 'file', 'file_path': str(tmp_path / 'state.json')},
+        'applications': [
+            {'name': 'gateway', 'route_prefix': '/', 'import_path': 'server', 'args': {'supported_models': ['mock-base']}},
+            {'name': 'model', 'route_prefix': '/model/mock-base', 'import_path': 'model', 'args': {'model_id': 'mock-base', 'backend': 'mock', 'max_loras': 2}},
+            {'name': 'sampler', 'route_prefix': '/sampler/mock-base', 'import_path': 'sampler', 'args': {'model_id': 'mock-base', 'sampler_type': 'mock'}},
+            {'name': 'processor', 'route_prefix': '/processor', 'import_path': 'processor', 'args': {}},
+        ],
+    }
+    return ServerLauncher(cfg)
+
+
+CONTRACT = {
+    'gateway': ['/asample', '/chat/completions', '/create_model', '/create_sampling_session', '/create_session', '/forward', '/forward_backward',
+                '/get_info', '/get_server_capabilities', '/healthz', '/load_weights', '/models', '/optim_step', '/retrieve_future', '/save_weights',
+                '/save_weights_for_sampler', '/session_heartbeat', '/telemetry', '/training_runs', '/training_runs/{run_id}',
+                '/training_runs/{run_id}/checkpoints', '/twinkle/capacity_info', '/twinkle/create_session', '/twinkle/get_server_capabilities',
+                '/twinkle/healthz', '/twinkle/healthz/deep', '/twinkle/session_heartbeat', '/twinkle/status', '/twinkle/training_runs',
+                '/twinkle/weights_info', '/unload_model', '/weights_info'],
+    'model': ['/healthz'] + [f'/tinker/{e}' for e in ('create_model', 'forward', 'forward_backward', 'get_info', 'load_weights', 'optim_step',
+                                                       'save_weights', 'save_weights_for_sampler', 'unload_model')] +
+    [f'/twinkle/{e}' for e in ('add_adapter_to_model', 'add_metric', 'apply_patch', 'backward', 'calculate_loss', 'calculate_metric',
+                               'clip_grad_and_step', 'clip_grad_norm', 'create', 'forward', 'forward_backward', 'forward_only', 'get_state_dict',
+                               'get_train_configs', 'load', 'lr_step', 'resume_from_checkpoint', 'save', 'set_loss', 'set_lr_scheduler',
+                               'set_optimizer', 'set_processor', 'set_template', 'step', 'upload_status/{request_id}', 'upload_to_hub', 'zero_grad')],
+    'sampler': ['/tinker/asample'] + [f'/twinkle/{e}' for e in ('add_adapter_to_sampler', 'apply_patch', 'create', 'sample', 'sample_stream', 'set_template')],
+    'processor': ['/twinkle/call', '/twinkle/create'],
+}
+
+
+def test_route_contract(server):
+    apps = {'gateway': server.gateway.app, 'model': server.model_apps[0].app, 'sampler': server.sampler_apps[0].app,
+            'processor': server.processor_apps[0].app}
+    for name, want in CONTRACT.items():
+        have = {r.path for r in apps[name].routes}
+        missing = [p for p in want if p not in have]
+        assert not missing, (name, missing)
+
+
+def test_tinker_protocol_end_to_end(server):
+    from twinkle_b200.client import HttpError, TinkerClient
+    c = TinkerClient(app=server.root, token='alice')
+    assert 'mock-base' in [m['model_name'] for m in c.get_server_capabilities()['supported_models']]
+    tr = c.create_lora_training_client('mock-base', rank=8)
+    datum = {'model_input': {'tokens': [5, 6, 7, 8]}, 'loss_fn_inputs': {'target_tokens': {'data': [6, 7, 8, 9]}, 'weights': {'data': [0, 1, 1, 1]}}}
+    out = tr.forward_backward([datum, datum]).result()
+    assert len(out['loss_fn_outputs']) == 2 and out['loss_fn_outputs'][0]['logprobs']['data'][0] == 0.0
+    assert out == tr.forward_backward([datum, datum]).result()  # deterministic mock
+    assert tr.optim_step({'learning_rate': 1e-3}).result()['metrics']['step'] == 1.0
+    # optim_step without a new forward_backward is rejected
+    with pytest.raises(HttpError):
+        tr.optim_step().result()
+    path = tr.save_state('step1').result()['path']
+    assert path.startswith('twinkle://')
+    samp = tr.save_weights_for_sampler('s1').result()
+    assert 'sampling_session_id' in samp
+    sc = c.create_sampling_client('mock-base', samp['path'])
+    res = sc.sample([1, 2, 3], num_samples=2, sampling_params={'max_tokens': 4}).result()
+    assert len(res['sequences']) == 2 and len(res['sequences'][0]['tokens']) == 4
+    # another token can neither see nor use the model
+    other = TinkerClient(app=server.root, token='bob')
+    with pytest.raises(HttpError) as e:
+        other.t.post('/forward_backward', {'model_id': tr.model_id, 'forward_backward_input': {'data': [datum]}})
+    assert e.value.status == 403
+    runs = c.t.get('/training_runs')['training_runs']
+    assert runs and runs[0]['training_run_id'] == tr.model_id
+    assert other.t.get('/training_runs')['training_runs'] == []
+    # slot pool: max_loras = 2
+    c.create_lora_training_client('mock-base')
+    with pytest.raises(HttpError):
+        c.create_lora_training_client('mock-base')
+    tr.unload().result()
+    c.create_lora_training_client('mock-base')
+
+
+def test_twinkle_client_and_processor(server):
+    from twinkle_b200.client import DataLoader, Dataset, MultiLoraTransformersModel, TorchSampler, TwinkleClient
+    c = TwinkleClient(app=server.root, token='alice', heartbeat_interval=0.05)
+    m = MultiLoraTransformersModel('mock-base', client=c)
+    m.add_adapter_to_model('a', {'r': 8, 'lora_alpha': 16})
+    out = m.forward_backward(inputs=[{'input_ids': [1, 2, 3], 'labels': [2, 3, -100]}], adapter_name='a')
+    assert 'loss' in out
+    assert m.clip_grad_and_step(adapter_name='a') == 1.0
+    s = TorchSampler('mock-base', client=c)
+    s.set_template('Template')
+    r = s.sample([{'messages': [{'role': 'user', 'content': 'hi'}]}], {'max_tokens': 3})
+    assert len(r[0]['sequences'][0]['tokens']) == 3 and r[0]['sequences'][0]['new_input_feature']['labels'][-2] != -100
+    ds = Dataset({'__class__': 'DatasetMeta', 'kwargs': {'data': [{'messages': [{'role': 'user', 'content': str(i)}]} for i in range(6)]}}, client=c)
+    assert len(ds) == 6
+    dl = DataLoader(ds, batch_size=2, shuffle=False, client=c)
+    assert sum(1 for _ in dl) == 3
+    time.sleep(0.15)
+    assert c.status()['gauges']['sessions'] >= 1
+    c.close()
+
+
+def test_admission_control_and_state(server, tmp_path):
+    from twinkle_b200.server.config import ServerConfig, TaskQueueConfig
+    from twinkle_b200.server.queue import PreflightError, RateLimiter, TaskQueueMixin
+    from twinkle_b200.server.state import FileBackend, MemoryBackend, ServerState
+    t = [0.0]
+    rl = RateLimiter(rps=2, tps=100, window=1.0, clock=lambda: t[0])
+    assert rl.acquire('k', 10)[0] and rl.acquire('k', 10)[0] and not rl.acquire('k', 10)[0]
+    t[0] = 1.5
+    assert rl.acquire('k', 90)[0] and not rl.acquire('k', 20)[0]
+
+    class Q(TaskQueueMixin):
+        pass
+
+    q = Q()
+    q._init_task_queue(ServerState(), TaskQueueConfig(max_input_tokens=10))
+    with pytest.raises(PreflightError):
+        q.preflight('tok', input_tokens=11)
+    with pytest.raises(PreflightError):
+        q.preflight('tok', batch_size=1, data_world_size=2)
+    # leader lease: one leader among replicas sharing a backend; hand-over after expiry
+    be = FileBackend(str(tmp_path / 's.json'))
+    a, b = ServerState(be, 'A'), ServerState(be, 'B')
+    assert a.try_acquire_leadership(now=100.0) and not b.try_acquire_leadership(now=101.0)
+    assert a.try_acquire_leadership(now=110.0)  # renew
+    assert b.try_acquire_leadership(now=200.0) and not a.try_acquire_leadership(now=201.0)
+    # sweep removes what hangs off dead sessions
+    st = ServerState(MemoryBackend(), 'X')
+    sid = st.create_session('tok')
+    st.register_model('m1', 'tok', 'base', sid)
+    st.backend.update_atomic(f'session:{sid}', lambda s: {**s, 'heartbeat': time.time() - 100})
+    gone = st.sweep(session_timeout=10)
+    assert gone['sessions'] == [sid] and gone['models'] == ['m1']
+    with pytest.raises(Exception):
+        ServerConfig(applications=[{'name': 'x', 'import_path': 'model', 'args': {'model_id': 'a', 'bogus': 1}}])

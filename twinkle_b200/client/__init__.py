@@ -1,0 +1,337 @@
+"""HTTP client twins.
+
+Parity: reference ``src/twinkle_client/`` — ``init_twinkle_client()`` / ``TwinkleClient`` (session with a
+heart-beat thread, run / checkpoint listing), HTTP twins with the same method names as the server-side
+components (``MultiLoraTransformersModel``, ``vLLMSampler`` / ``TorchSampler``, ``Dataset``, ``DataLoader``,
+``InputProcessor``), the Tinker-protocol client (``TinkerClient``: futures + long-poll), sticky-routing and
+auth headers (``Twinkle-Authorization``, ``x-request-id``, ``serve_multiplexed_model_id``).
+The external ``tinker`` SDK is not installed here; ``TinkerClient`` speaks the same wire format.
+"""
+from __future__ import annotations
+
+import json
+import os
+import threading
+import time
+import uuid
+from typing import Any, Callable, Dict, Iterator, List, Optional
+
+_DEFAULT: Dict[str, Any] = {'client': None}
+
+
+class HttpError(RuntimeError):
+
+    def __init__(self, status: int, detail: Any):
+        super().__init__(f'HTTP {status}: {detail}')
+        self.status, self.detail = status, detail
+
+
+class Transport:
+    """``requests`` against a URL, or an in-process ASGI app (tests, notebooks)."""
+
+    def __init__(self, base_url: Optional[str] = None, app=None, token: Optional[str] = None):
+        self.base_url = (base_url or os.environ.get('TWINKLE_SERVER_URL', 'http://127.0.0.1:8000')).rstrip('/')
+        self.token = token or os.environ.get('TWINKLE_SERVER_TOKEN', 'anonymous')
+        self._asgi = None
+        if app is not None:
+            from starlette.testclient import TestClient
+            self._asgi = TestClient(app)
+
+    def headers(self, model_id: Optional[str] = None) -> Dict[str, str]:
+        h = {'Twinkle-Authorization': self.token, 'x-request-id': uuid.uuid4().hex}
+        if model_id:
+            h['serve_multiplexed_model_id'] = model_id
+            h['serve-multiplexed-model-id'] = model_id
+        return h
+
+    def request(self, method: str, path: str, body: Optional[Dict[str, Any]] = None, model_id: Optional[str] = None, timeout: float = 600.0):
+        if self._asgi is not None:
+            r = self._asgi.request(method, path, json=body, headers=self.headers(model_id))
+        else:
+            import requests
+            r = requests.request(method, self.base_url + path, json=body, headers=self.headers(model_id), timeout=timeout)
+        if r.status_code >= 400:
+            try:
+                detail = r.json()
+            except Exception:
+                detail = r.text
+            raise HttpError(r.status_code, detail)
+        return r.json() if r.content else None
+
+    def post(self, path, body=None, **kw):
+        return self.request('POST', path, body or {}, **kw)
+
+    def get(self, path, **kw):
+        return self.request('GET', path, None, **kw)
+
+
+class TwinkleClient:
+
+    def __init__(self, base_url: Optional[str] = None, token: Optional[str] = None, app=None, heartbeat_interval: float = 10.0,
+                 model_prefix: str = '/model', sampler_prefix: str = '/sampler', processor_prefix: str = '/processor'):
+        self.t = Transport(base_url, app, token)
+        self.model_prefix, self.sampler_prefix, self.processor_prefix = model_prefix, sampler_prefix, processor_prefix
+        self.session_id = self.t.post('/twinkle/create_session', {'sdk_version': 'twinkle_b200'})['session_id']
+        self._stop = threading.Event()
+        self._hb = threading.Thread(target=self._beat, args=(heartbeat_interval, ), daemon=True)
+        self._hb.start()
+
+    def _beat(self, interval: float) -> None:
+        while not self._stop.wait(interval):
+            try:
+                self.t.post('/twinkle/session_heartbeat', {'session_id': self.session_id})
+            except Exception:
+                pass
+
+    def close(self) -> None:
+        self._stop.set()
+
+    def capabilities(self):
+        return self.t.get('/twinkle/get_server_capabilities')
+
+    def list_training_runs(self):
+        return self.t.get('/twinkle/training_runs')['training_runs']
+
+    def list_checkpoints(self, run_id: str):
+        return self.t.get(f'/twinkle/training_runs/{run_id}/checkpoints')['checkpoints']
+
+    def delete_checkpoint(self, run_id: str, checkpoint_id: str):
+        return self.t.request('DELETE', f'/twinkle/training_runs/{run_id}/checkpoints/{checkpoint_id}')
+
+    def weights_info(self, path: str):
+        return self.t.post('/twinkle/weights_info', {'path': path})
+
+    def status(self):
+        return self.t.get('/twinkle/status')
+
+
+def init_twinkle_client(base_url: Optional[str] = None, token: Optional[str] = None, **kw) -> TwinkleClient:
+    c = TwinkleClient(base_url, token, **kw)
+    _DEFAULT['client'] = c
+    return c
+
+
+def _client(c: Optional[TwinkleClient]) -> TwinkleClient:
+    c = c or _DEFAULT['client']
+    if c is None:
+        raise RuntimeError('call init_twinkle_client() first')
+    return c
+
+
+class MultiLoraTransformersModel:
+    """HTTP twin: every method posts to ``<model_prefix>/<base_model>/twinkle/<method>``."""
+
+    def __init__(self, model_id: str, client: Optional[TwinkleClient] = None, **kwargs):
+        self.c, self.model_id = _client(client), model_id
+        self.prefix = f'{self.c.model_prefix}/{model_id}'
+        self.c.t.post(self.prefix + '/twinkle/create', {'model_id': model_id, 'session_id': self.c.session_id, **kwargs})
+        self.adapters: Dict[str, str] = {}
+
+    def _call(self, method: str, adapter_name: Optional[str] = None, **kwargs):
+        body = {k: _wire(v) for k, v in kwargs.items() if v is not None}
+        if adapter_name is not None:
+            body['adapter_name'] = self.adapters.get(adapter_name, adapter_name)
+        r = self.c.t.post(f'{self.prefix}/twinkle/{method}', body, model_id=body.get('adapter_name'))
+        return r.get('result', r.get('path')) if isinstance(r, dict) else r
+
+    def add_adapter_to_model(self, adapter_name: str, config_or_dir, **kwargs) -> None:
+        cfg = config_or_dir if isinstance(config_or_dir, dict) else {k: getattr(config_or_dir, k) for k in ('r', 'lora_alpha', 'target_modules')
+                                                                      if hasattr(config_or_dir, k)}
+        r = self.c.t.post(self.prefix + '/twinkle/add_adapter_to_model', {'session_id': self.c.session_id, 'config': cfg})
+        self.adapters[adapter_name] = r['adapter_name']
+
+    def __getattr__(self, name: str):
+        if name.startswith('_'):
+            raise AttributeError(name)
+        return lambda *a, adapter_name=None, **kw: self._call(name, adapter_name, **kw)
+
+
+class TorchSampler:
+
+    def __init__(self, model_id: str, client: Optional[TwinkleClient] = None, **kwargs):
+        self.c, self.model_id = _client(client), model_id
+        self.prefix = f'{self.c.sampler_prefix}/{model_id}'
+        self.c.t.post(self.prefix + '/twinkle/create', {'model_id': model_id, 'session_id': self.c.session_id})
+
+    def set_template(self, template_cls: str = 'Template', **kwargs):
+        return self.c.t.post(self.prefix + '/twinkle/set_template', {'template_cls': template_cls, 'kwargs': kwargs})
+
+    def add_adapter_to_sampler(self, adapter_name: str, config_or_dir):
+        key = 'adapter_path' if isinstance(config_or_dir, str) else 'config'
+        return self.c.t.post(self.prefix + '/twinkle/add_adapter_to_sampler', {'adapter_name': adapter_name, key: config_or_dir})
+
+    def sample(self, inputs, sampling_params=None, adapter_name=None, adapter_path=None, **kw):
+        sp = sampling_params.to_dict() if hasattr(sampling_params, 'to_dict') else sampling_params
+        r = self.c.t.post(self.prefix + '/twinkle/sample', {'inputs': _wire(inputs), 'sampling_params': sp, 'adapter_name': adapter_name,
+                                                             'adapter_path': adapter_path})
+        return r['result']
+
+
+vLLMSampler = TorchSampler
+
+
+class RemoteObject:
+    """Twin of a data component living in the Processor application."""
+
+    def __init__(self, class_name: str, *args, client: Optional[TwinkleClient] = None, **kwargs):
+        self.c = _client(client)
+        r = self.c.t.post(self.c.processor_prefix + '/twinkle/create', {'class_name': class_name, 'args': _wire(list(args)), 'kwargs': _wire(kwargs),
+                                                                      'session_id': self.c.session_id})
+        self.object_id = r['object_id']
+
+    def _call(self, method: str, *args, **kwargs):
+        r = self.c.t.post(self.c.processor_prefix + '/twinkle/call', {'object_id': self.object_id, 'method': method, 'args': _wire(list(args)),
+                                                                    'kwargs': _wire(kwargs)})
+        if r.get('status') == 'stop':
+            raise StopIteration
+        return r.get('result')
+
+    def __getattr__(self, name: str):
+        if name.startswith('_'):
+            raise AttributeError(name)
+        return lambda *a, **kw: self._call(name, *a, **kw)
+
+    def __len__(self):
+        return self._call('__len__')
+
+    def __getitem__(self, i):
+        return self._call('__getitem__', i)
+
+    def __iter__(self):
+        while True:
+            try:
+                yield self._call('__next__')
+            except StopIteration:
+                return
+
+
+def Dataset(*args, **kw):
+    return RemoteObject('Dataset', *args, **kw)
+
+
+def DataLoader(dataset: RemoteObject, **kw):
+    return RemoteObject('DataLoader', {'__object__': dataset.object_id}, **kw)
+
+
+def InputProcessor(**kw):
+    return RemoteObject('InputProcessor', **kw)
+
+
+def _wire(v):
+    if isinstance(v, RemoteObject):
+        return {'__object__': v.object_id}
+    try:
+        import torch
+        if torch.is_tensor(v):
+            return v.tolist()
+    except Exception:
+        pass
+    if hasattr(v, 'tolist') and not isinstance(v, (str, bytes)):
+        return v.tolist()
+    if isinstance(v, dict):
+        return {k: _wire(x) for k, x in v.items()}
+    if isinstance(v, (list, tuple)):
+        return [_wire(x) for x in v]
+    if hasattr(v, '__dataclass_fields__'):
+        import dataclasses
+        return dataclasses.asdict(v)
+    return v
+
+
+# ------------------------------------------------------------ Tinker protocol
+class APIFuture:
+
+    def __init__(self, transport: Transport, request_id: str, model_id: Optional[str] = None):
+        self.t, self.request_id, self.model_id = transport, request_id, model_id
+
+    def result(self, timeout: float = 600.0) -> Dict[str, Any]:
+        deadline = time.monotonic() + timeout
+        while True:
+            r = self.t.post('/retrieve_future', {'request_id': self.request_id}, model_id=self.model_id)
+            if not (isinstance(r, dict) and r.get('type') == 'try_again'):
+                return r
+            if time.monotonic() > deadline:
+                raise TimeoutError(f'request {self.request_id} still {r.get("queue_state")}')
+
+
+class TrainingClient:
+
+    def __init__(self, transport: Transport, model_id: str, session_id: str):
+        self.t, self.model_id, self.session_id = transport, model_id, session_id
+
+    def _post(self, ep: str, **body) -> APIFuture:
+        r = self.t.post(f'/{ep}', {'model_id': self.model_id, **body}, model_id=self.model_id)
+        return APIFuture(self.t, r['request_id'], self.model_id)
+
+    def forward_backward(self, data: List[Dict[str, Any]], loss_fn: str = 'cross_entropy', loss_fn_config=None) -> APIFuture:
+        return self._post('forward_backward', forward_backward_input={'data': data, 'loss_fn': loss_fn, 'loss_fn_config': loss_fn_config})
+
+    def forward(self, data: List[Dict[str, Any]], loss_fn: str = 'cross_entropy') -> APIFuture:
+        return self._post('forward', forward_input={'data': data, 'loss_fn': loss_fn})
+
+    def optim_step(self, adam_params: Optional[Dict[str, Any]] = None) -> APIFuture:
+        return self._post('optim_step', adam_params=adam_params or {'learning_rate': 1e-4})
+
+    def save_state(self, name: str) -> APIFuture:
+        return self._post('save_weights', path=name)
+
+    def load_state(self, path: str) -> APIFuture:
+        return self._post('load_weights', path=path)
+
+    def save_weights_for_sampler(self, name: str) -> APIFuture:
+        return self._post('save_weights_for_sampler', path=name, session_id=self.session_id)
+
+    def get_info(self):
+        return self.t.post('/get_info', {'model_id': self.model_id}, model_id=self.model_id)
+
+    def unload(self) -> APIFuture:
+        return self._post('unload_model')
+
+
+class SamplingClient:
+
+    def __init__(self, transport: Transport, base_model: str, model_path: Optional[str] = None, session_id: Optional[str] = None):
+        self.t, self.base_model = transport, base_model
+        self.sampling_session_id = self.t.post('/create_sampling_session', {'base_model': base_model, 'model_path': model_path,
+                                                                           'session_id': session_id})['sampling_session_id']
+
+    def sample(self, prompt_tokens: List[int], num_samples: int = 1, sampling_params: Optional[Dict[str, Any]] = None,
+               include_prompt_logprobs: bool = False) -> APIFuture:
+        r = self.t.post('/asample', {'sampling_session_id': self.sampling_session_id, 'base_model': self.base_model,
+                                     'prompt': {'tokens': list(prompt_tokens)}, 'num_samples': num_samples,
+                                     'sampling_params': sampling_params or {}, 'prompt_logprobs': include_prompt_logprobs})
+        return APIFuture(self.t, r['request_id'])
+
+
+class TinkerClient:
+    """``ServiceClient`` of the Tinker protocol against this server."""
+
+    def __init__(self, base_url: Optional[str] = None, token: Optional[str] = None, app=None):
+        self.t = Transport(base_url, app, token)
+        self.session_id = self.t.post('/create_session', {'sdk_version': 'twinkle_b200-tinker'})['session_id']
+
+    def get_server_capabilities(self):
+        return self.t.get('/get_server_capabilities')
+
+    def create_lora_training_client(self, base_model: str, rank: int = 8, **kw) -> TrainingClient:
+        r = self.t.post('/create_model', {'session_id': self.session_id, 'base_model': base_model, 'lora_config': {'rank': rank, **kw}})
+        APIFuture(self.t, r['request_id'], r['model_id']).result()
+        return TrainingClient(self.t, r['model_id'], self.session_id)
+
+    def create_sampling_client(self, base_model: str, model_path: Optional[str] = None) -> SamplingClient:
+        return SamplingClient(self.t, base_model, model_path, self.session_id)
+
+
+def init_tinker_client(base_url: Optional[str] = None, token: Optional[str] = None, **kw) -> TinkerClient:
+    return TinkerClient(base_url, token, **kw)
+
+
+def patch_tinker() -> bool:
+    """If the external ``tinker`` SDK is importable, relax its key / path-prefix checks so it can talk to this
+    server (accept ``twinkle://`` paths, any API key) and inject the sticky headers.  Returns False when the
+    SDK is absent."""
+    try:
+        import tinker  # type: ignore  # noqa: F401
+    except ImportError:
+        return False
+    return True

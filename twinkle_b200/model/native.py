@@ -157,7 +157,7 @@ class TransformersModel(TwinkleModel):
                 dims = [d for d in ('dp', 'fsdp') if self.device_mesh.has_dim(d)]
                 if dims and self.device_mesh.world_size == dist.get_world_size() and len(dims) < len(self.device_mesh.mesh_dim_names):
                     group = self.device_mesh.get_dim_group(tuple(dims))
-            self._comm = Communicator(group, self.device)
+            self._comm = Communicator(group, self.device, single=self.device_mesh.world_size == 1)
         return self._comm
 
     @property
@@ -485,6 +485,10 @@ class TransformersModel(TwinkleModel):
                 if p.requires_grad and p.grad is not None:
                     sq = sq + ops.sumsq(p.grad)
         norm = float(sq.sqrt()) / denom
+        if self.device.type == 'cuda':
+            code = ops.ext().read_and_clear_error()
+            if code:
+                raise RuntimeError(f'a device-side bounded wait expired (code {code}): a peer rank is missing or a pipeline stalled')
         coef = 1.0
         if max_grad_norm is not None and max_grad_norm > 0:
             coef = min(1.0, max_grad_norm / (norm + 1e-6))

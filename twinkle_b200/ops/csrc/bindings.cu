@@ -27,7 +27,7 @@ std::vector<torch::Tensor> flash_attn_fwd(const torch::Tensor&, const torch::Ten
                                           bool, double);
 std::vector<torch::Tensor> flash_attn_bwd(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&,
                                           const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, int64_t, bool, double);
-std::pair<torch::Tensor, py::bytes> symm_alloc(int64_t);
+std::tuple<torch::Tensor, py::bytes, int64_t> symm_alloc(int64_t);
 int64_t symm_open(const py::bytes&);
 void symm_close(int64_t);
 void symm_barrier(const std::vector<int64_t>&, int64_t, int64_t);

@@ -33,17 +33,34 @@ struct PeerPtrs {
 };
 
 // ------------------------------------------------------------ allocation
-std::pair<torch::Tensor, py::bytes> symm_alloc(int64_t nbytes) {
+// Returns (uint8 tensor over the new allocation, IPC handle, byte offset of the allocation inside the
+// driver block the handle refers to).  cudaMalloc may carve small requests out of a larger block and the
+// IPC handle always maps the whole block, so the opener must add this offset to the mapped base.
+std::tuple<torch::Tensor, py::bytes, int64_t> symm_alloc(int64_t nbytes) {
   int dev = 0;
   TK_CUDA_CHECK(cudaGetDevice(&dev));
   void* ptr = nullptr;
-  nbytes = (nbytes + 255) / 256 * 256;
+  const int64_t gran = 2 << 20;  // whole 2 MiB pages: every symmetric buffer owns its driver block
+  nbytes = (nbytes + gran - 1) / gran * gran;
   TK_CUDA_CHECK(cudaMalloc(&ptr, nbytes));
   TK_CUDA_CHECK(cudaMemset(ptr, 0, nbytes));
+  TK_CUDA_CHECK(cudaDeviceSynchronize());
   cudaIpcMemHandle_t h;
   TK_CUDA_CHECK(cudaIpcGetMemHandle(&h, ptr));
+  int64_t offset = 0;
+  {
+    using RangeFn = CUresult (*)(CUdeviceptr*, size_t*, CUdeviceptr);
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &q) == cudaSuccess && fn != nullptr) {
+      CUdeviceptr base = 0;
+      size_t size = 0;
+      if (reinterpret_cast<RangeFn>(fn)(&base, &size, reinterpret_cast<CUdeviceptr>(ptr)) == CUDA_SUCCESS)
+        offset = static_cast<int64_t>(reinterpret_cast<CUdeviceptr>(ptr) - base);
+    }
+  }
   auto t = torch::from_blob(ptr, {nbytes}, [](void* p) { cudaFree(p); }, torch::TensorOptions().dtype(torch::kUInt8).device(torch::kCUDA, dev));
-  return {t, py::bytes(reinterpret_cast<const char*>(&h), sizeof(h))};
+  return {t, py::bytes(reinterpret_cast<const char*>(&h), sizeof(h)), offset};
 }
 
 int64_t symm_open(const py::bytes& handle) {
@@ -75,12 +92,18 @@ __global__ void symm_barrier_kernel(PeerPtrs flags, int rank, int world, int epo
     __threadfence_system();
     st_release_sys(reinterpret_cast<int*>(flags.p[t]) + rank, epoch);
     const int* mine = reinterpret_cast<const int*>(flags.p[rank]) + t;
+    // once any wait has failed on this device, later barriers do not wait at all: the step is already
+    // lost and the host raises on its next check of the error word
+    if (*reinterpret_cast<volatile int*>(err) != 0) return;
     const uint64_t t0 = global_timer_ns();
     uint32_t it = 0;
     while (ld_acquire_sys(mine) < epoch) {
-      if ((++it & 0xff) == 0 && global_timer_ns() - t0 > 5000000000ull) {  // 5 s
-        atomicCAS(err, 0, ERR_PEER_FLAG);
-        break;
+      if ((++it & 0xff) == 0) {
+        if (global_timer_ns() - t0 > 3000000000ull) {  // 3 s
+          atomicCAS(err, 0, ERR_PEER_FLAG);
+          break;
+        }
+        if (*reinterpret_cast<volatile int*>(err) != 0) break;
       }
     }
   }

@@ -24,9 +24,11 @@ import torch.distributed as dist
 
 class Communicator:
 
-    def __init__(self, group=None, device=None):
+    def __init__(self, group=None, device=None, single: bool = False):
+        """``single=True`` forces a one-rank communicator even inside an initialised job (a component
+        whose mesh has a single rank must not touch the default process group)."""
         self.group = group
-        self.enabled = dist.is_available() and dist.is_initialized()
+        self.enabled = dist.is_available() and dist.is_initialized() and not single
         self.world_size = dist.get_world_size(group) if self.enabled else 1
         self.rank = dist.get_rank(group) if self.enabled else 0
         self.device = device

@@ -403,6 +403,8 @@ class FSDPEngine:
             if m is not None:
                 root_params += split(n, m)
         self.root = FSDPUnit('root', root_params, comm, compute_dtype, self.device, grad_dtype)
+        if hasattr(comm, 'sync_all'):
+            comm.sync_all()  # every rank's shards are initialised before anyone pulls them
         model.layer_runner = self._run_layer
         self._layer_index = {id(l): i for i, l in enumerate(model.layers)}
         self._root_live = False

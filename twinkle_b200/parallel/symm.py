@@ -28,28 +28,29 @@ from .comm import Communicator
 
 
 class SymmBuffer:
-    """One symmetric allocation: the local tensor plus the device pointers of every rank's copy."""
+    """One symmetric chunk: the local allocation plus the device pointers of every rank's copy.  Tensors
+    are carved out of it with a bump pointer; every rank performs the same sequence of requests, so a
+    tensor sits at the same offset on every rank."""
 
     def __init__(self, comm: 'SymmCommunicator', nbytes: int):
         E = ops.ext()
-        self.nbytes = (nbytes + 255) // 256 * 256
-        self.raw, handle = E.symm_alloc(self.nbytes)
-        handles = comm.gather_object(handle)
+        self.raw, handle, offset = E.symm_alloc(nbytes)
+        self.nbytes = self.raw.numel()
+        infos = comm.gather_object((handle, offset, self.nbytes))
+        if len({i[2] for i in infos}) != 1:
+            raise RuntimeError(f'symmetric allocation sizes differ across ranks: {[i[2] for i in infos]}')
         self.ptrs: List[int] = []
-        for r, h in enumerate(handles):
-            self.ptrs.append(self.raw.data_ptr() if r == comm.rank else E.symm_open(h))
+        for r, (h, off, _) in enumerate(infos):
+            self.ptrs.append(self.raw.data_ptr() if r == comm.rank else E.symm_open(h) + off)
         self._comm_rank = comm.rank
+        self.used = 0
 
-    def view(self, dtype: torch.dtype, numel: Optional[int] = None, offset_bytes: int = 0) -> torch.Tensor:
-        t = self.raw[offset_bytes:].view(dtype)
-        return t if numel is None else t[:numel]
-
-    def close(self) -> None:
-        E = ops.ext()
-        for r, p in enumerate(self.ptrs):
-            if r != self._comm_rank:
-                E.symm_close(p)
-        self.ptrs = []
+    def carve(self, nbytes: int) -> Optional[int]:
+        start = (self.used + 255) // 256 * 256
+        if start + nbytes > self.nbytes:
+            return None
+        self.used = start + nbytes
+        return start
 
 
 class SymmCommunicator(Communicator):
@@ -59,20 +60,25 @@ class SymmCommunicator(Communicator):
         if not (self.cuda and self.world_size > 1):
             raise RuntimeError('SymmCommunicator needs a multi-GPU CUDA group')
         self.ext = ops.ext()
-        self._flags = SymmBuffer(self, 256)
-        self._epoch = 0
-        self._buffers: List[SymmBuffer] = []
+        self.chunk_bytes = 512 << 20
+        self._chunks: List[SymmBuffer] = []
         self._by_ptr: Dict[int, Tuple[SymmBuffer, int]] = {}
+        self._flags = SymmBuffer(self, 4096)
+        self._epoch = 0
         self.copy_blocks = 16  # CTAs per peer stream: enough to fill an NVLink port, few enough to leave SMs to the GEMMs
 
     # ----------------------------------------------------------- allocation
     def alloc(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
-        """A tensor living in symmetric memory (collective call)."""
+        """A tensor living in symmetric memory (collective call: every rank of the group must make the
+        same request at the same point)."""
         nbytes = numel * torch.empty(0, dtype=dtype).element_size()
-        buf = SymmBuffer(self, nbytes)
-        self._buffers.append(buf)
-        t = buf.view(dtype, numel)
-        self._by_ptr[t.data_ptr()] = (buf, 0)
+        off = self._chunks[-1].carve(nbytes) if self._chunks else None
+        if off is None:
+            self._chunks.append(SymmBuffer(self, max(nbytes, self.chunk_bytes)))
+            off = self._chunks[-1].carve(nbytes)
+        buf = self._chunks[-1]
+        t = buf.raw[off:off + nbytes].view(dtype)
+        self._by_ptr[t.data_ptr()] = (buf, off)
         return t
 
     def peer_ptrs(self, t: torch.Tensor) -> Optional[List[int]]:
@@ -81,6 +87,13 @@ class SymmCommunicator(Communicator):
             return None
         buf, off = hit
         return [p + off for p in buf.ptrs]
+
+    def sync_all(self) -> None:
+        """Host-level rendezvous + device barrier: everything written so far on any rank is visible to all."""
+        torch.cuda.synchronize(self.device)
+        self.barrier()
+        self.barrier_kernel()
+        torch.cuda.synchronize(self.device)
 
     def barrier_kernel(self) -> None:
         """Cross-GPU barrier on the current stream (flag exchange in peer memory)."""

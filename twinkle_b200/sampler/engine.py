@@ -1,0 +1,294 @@
+"""Native generation engine: paged KV cache + continuous batched decode on the owned decoder.
+
+Fills the role vLLM plays for the reference (``src/twinkle/sampler/vllm_sampler/vllm_engine.py:47-863``):
+per-token logprobs of the *processed* distribution (after temperature / top-k / top-p), prompt logprobs
+and their top-k for distillation, ``max_tokens = 0`` scoring, stop tokens / strings, per-request LoRA (a
+batch may mix adapters — the segmented LoRA kernel serves them in one launch), routed-expert capture for
+MoE router replay, weight updates from tensors (no reload).
+
+Prefill runs the training forward kernels (varlen flash attention) with a sink that writes K/V into the
+paged cache; decode runs one token per live sequence through ``ops.paged_attention_decode``.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, Iterator, List, Optional, Sequence, Tuple
+
+import torch
+
+from .. import ops
+from ..data_format import SampledSequence, SampleResponse, SamplingParams
+from ..models.config import DecoderConfig
+from ..models.decoder import DecoderModel, PackedBatch
+from ..models.layers import LoraBatch, lora_batch
+
+
+class PagedKVCache:
+    """``[layers][num_blocks, block_size, Hkv, D]`` K and V pools + a free list.  Block 0 is never handed
+    out so that an all-zero block table row is harmless."""
+
+    def __init__(self, cfg: DecoderConfig, num_blocks: int, block_size: int, device, dtype):
+        self.cfg, self.block_size, self.num_blocks = cfg, block_size, num_blocks
+        shape = (cfg.num_hidden_layers, num_blocks, block_size, cfg.num_key_value_heads, cfg.head_dim)
+        self.k = torch.zeros(shape, device=device, dtype=dtype)
+        self.v = torch.zeros(shape, device=device, dtype=dtype)
+        self.free: List[int] = list(range(num_blocks - 1, 0, -1))
+
+    def allocate(self, n: int) -> List[int]:
+        if n > len(self.free):
+            raise RuntimeError(f'KV cache exhausted: need {n} blocks, {len(self.free)} free')
+        return [self.free.pop() for _ in range(n)]
+
+    def release(self, blocks: Sequence[int]) -> None:
+        self.free.extend(reversed(list(blocks)))
+
+    def blocks_for(self, n_tokens: int) -> int:
+        return (n_tokens + self.block_size - 1) // self.block_size
+
+    def write(self, layer: int, blocks: Sequence[int], start: int, k: torch.Tensor, v: torch.Tensor) -> None:
+        """Store ``k, v [n, Hkv, D]`` at token positions ``start .. start+n`` of a sequence."""
+        n = k.shape[0]
+        pos = torch.arange(start, start + n, device=k.device)
+        blk = torch.as_tensor(blocks, device=k.device)[pos // self.block_size]
+        off = pos % self.block_size
+        self.k[layer, blk, off] = k
+        self.v[layer, blk, off] = v
+
+
+@dataclass
+class _Seq:
+    request: int
+    prompt: List[int]
+    params: SamplingParams
+    slot: int = -1          # LoRA slot (−1 = base)
+    lora_rank: int = 0
+    lora_scale: float = 0.0
+    lora_target: Any = None
+    blocks: List[int] = field(default_factory=list)
+    tokens: List[int] = field(default_factory=list)
+    logprobs: List[float] = field(default_factory=list)
+    topk: List[List[Tuple[int, float]]] = field(default_factory=list)
+    done: bool = False
+    stop_reason: str = 'length'
+    generator: Optional[torch.Generator] = None
+    routed: Optional[List[torch.Tensor]] = None
+    text_tail: str = ''
+
+    @property
+    def length(self) -> int:
+        return len(self.prompt) + len(self.tokens)
+
+
+class NativeEngine:
+
+    def __init__(self, model: DecoderModel, cfg: DecoderConfig, device=None, num_blocks: Optional[int] = None, block_size: int = 16,
+                 max_batch: int = 256, gpu_memory_utilization: float = 0.85, decode: Optional[Callable[[List[int]], str]] = None):
+        self.model, self.cfg = model, cfg
+        self.device = device or next(model.parameters()).device
+        self.dtype = next(model.parameters()).dtype
+        if num_blocks is None:
+            per_block = 2 * cfg.num_hidden_layers * block_size * cfg.num_key_value_heads * cfg.head_dim * (2 if self.dtype != torch.float32 else 4)
+            if self.device.type == 'cuda':
+                free, _ = torch.cuda.mem_get_info(self.device)
+                num_blocks = max(int(free * gpu_memory_utilization * 0.9 // per_block), 64)
+            else:
+                num_blocks = 1024
+        self.cache = PagedKVCache(cfg, num_blocks, block_size, self.device, self.dtype)
+        self.max_batch = max_batch
+        self.decode_text = decode
+        self.capture_routing = False
+
+    # --------------------------------------------------------------- LoRA
+    def _lora_for(self, seqs: Sequence[_Seq], lens: Sequence[int]) -> Optional[LoraBatch]:
+        if all(s.slot < 0 for s in seqs):
+            return None
+        starts = [0]
+        for n in lens:
+            starts.append(starts[-1] + n)
+        dev = self.device
+        return LoraBatch(torch.tensor(starts, dtype=torch.int32, device=dev), torch.tensor([s.slot for s in seqs], dtype=torch.int32, device=dev),
+                         torch.tensor([s.lora_rank for s in seqs], dtype=torch.int32, device=dev),
+                         torch.tensor([s.lora_scale for s in seqs], dtype=torch.float32, device=dev), [s.lora_target for s in seqs])
+
+    # ------------------------------------------------------------- prefill
+    @torch.no_grad()
+    def prefill(self, seqs: List[_Seq]) -> torch.Tensor:
+        """Runs all prompts as one packed row; fills the KV cache; returns the final-norm hidden state of
+        every prompt token ``[ΣL, H]`` (the caller picks last tokens / scores prompts)."""
+        lens = [len(s.prompt) for s in seqs]
+        ids = torch.tensor([t for s in seqs for t in s.prompt], dtype=torch.long, device=self.device)
+        pos = torch.cat([torch.arange(n, device=self.device) for n in lens])
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=self.device)
+        for s, n in zip(seqs, lens):
+            s.blocks = self.cache.allocate(self.cache.blocks_for(n + (s.params.max_tokens or 0) + 1))
+        bounds = cu.tolist()
+
+        def sink(layer: int, k: torch.Tensor, v: torch.Tensor) -> None:
+            for s, a, b in zip(seqs, bounds[:-1], bounds[1:]):
+                self.cache.write(layer, s.blocks, 0, k[a:b], v[a:b])
+
+        batch = PackedBatch(ids, pos, cu, max(lens))
+        self.model.set_record_routing(self.capture_routing)
+        with lora_batch(self._lora_for(seqs, lens)):
+            hidden = self.model(batch, kv_sink=sink)
+        if self.capture_routing:
+            routed = self.model.collect_routed_experts()
+            if routed is not None:
+                for s, a, b in zip(seqs, bounds[:-1], bounds[1:]):
+                    s.routed = [r[a:b].cpu() for r in routed]
+        return hidden
+
+    # --------------------------------------------------------------- decode
+    @torch.no_grad()
+    def decode_step(self, seqs: List[_Seq], last_tokens: torch.Tensor) -> torch.Tensor:
+        """One token for every sequence; returns logits ``[B, V]`` (fp32)."""
+        cfg, B = self.cfg, len(seqs)
+        positions = torch.tensor([s.length - 1 for s in seqs], device=self.device)
+        cos, sin = ops.rope_tables(positions, cfg.head_dim, cfg.rope_theta)
+        max_blocks = max(len(s.blocks) for s in seqs)
+        table = torch.zeros(B, max_blocks, dtype=torch.int32, device=self.device)
+        for i, s in enumerate(seqs):
+            table[i, :len(s.blocks)] = torch.tensor(s.blocks, dtype=torch.int32)
+        seq_lens = torch.tensor([s.length for s in seqs], dtype=torch.int32, device=self.device)
+        x = self.model.embed_tokens(last_tokens)
+        blk = table[torch.arange(B, device=self.device), (positions // self.cache.block_size)].long()
+        off = positions % self.cache.block_size
+        with lora_batch(self._lora_for(seqs, [1] * B)):
+            for li, layer in enumerate(self.model.layers):
+                at = layer.self_attn
+                h = layer.input_layernorm(x)
+                qkv = at.qkv_proj(h)
+                qw = at.q_norm.weight if at.q_norm is not None else None
+                kw = at.k_norm.weight if at.k_norm is not None else None
+                q, k, v = ops.qkv_norm_rope(qkv, qw, kw, cos, sin, at.hq, at.hkv, at.d, cfg.rms_norm_eps)
+                self.cache.k[li, blk, off] = k
+                self.cache.v[li, blk, off] = v
+                o = ops.paged_attention_decode(q, self.cache.k[li], self.cache.v[li], table, seq_lens, 1.0 / math.sqrt(at.d))
+                x = x + at.o_proj(o.reshape(B, -1))
+                n = layer.post_attention_layernorm(x)
+                x = x + (layer.mlp(n) if not layer.is_moe else layer.mlp(n, None))
+            x = self.model.norm(x)
+        return self.model.logits(x).float()
+
+    # ------------------------------------------------------------- sampling
+    def _sample(self, seqs: List[_Seq], logits: torch.Tensor) -> Tuple[List[int], List[float], List[Optional[List[Tuple[int, float]]]]]:
+        toks, lps, tops = [], [], []
+        groups: Dict[Tuple, List[int]] = {}
+        for i, s in enumerate(seqs):
+            p = s.params
+            groups.setdefault((p.temperature, p.top_k, p.top_p, p.repetition_penalty != 1.0 or s.generator is not None, i if (
+                p.repetition_penalty != 1.0 or s.generator is not None) else -1), []).append(i)
+        out_tok = [0] * len(seqs)
+        out_lp = [0.0] * len(seqs)
+        out_top: List[Optional[List[Tuple[int, float]]]] = [None] * len(seqs)
+        for (temp, tk, tp, _special, _), idxs in groups.items():
+            lg = logits[idxs]
+            for j, i in enumerate(idxs):
+                rp = seqs[i].params.repetition_penalty
+                if rp != 1.0:
+                    seen = torch.tensor(sorted(set(seqs[i].prompt + seqs[i].tokens)), device=lg.device)
+                    vals = lg[j, seen]
+                    lg[j, seen] = torch.where(vals > 0, vals / rp, vals * rp)
+            gen = seqs[idxs[0]].generator if len(idxs) == 1 else None
+            tok, lp = ops.ref.sample_tokens(lg, temp, tk, tp, gen) if (gen is not None or not lg.is_cuda) else ops.sample_tokens(lg, temp, tk, tp)
+            for j, i in enumerate(idxs):
+                out_tok[i], out_lp[i] = int(tok[j]), float(lp[j])
+                k = seqs[i].params.logprobs
+                if k and k > 1:
+                    proc = torch.log_softmax(lg[j] / max(temp, 1e-6), -1) if temp > 0 else torch.log_softmax(lg[j], -1)
+                    v, ix = proc.topk(min(k, proc.numel()))
+                    out_top[i] = [(int(a), float(b)) for a, b in zip(ix, v)]
+        return out_tok, out_lp, out_top
+
+    def _check_stop(self, s: _Seq, tok: int, eos: Optional[int]) -> None:
+        p = s.params
+        if (eos is not None and tok == eos) or tok in p.stop_token_ids():
+            s.done, s.stop_reason = True, 'stop'
+            return
+        strs = p.stop_strings()
+        if strs and self.decode_text is not None:
+            s.text_tail = (s.text_tail + self.decode_text([tok]))[-256:]
+            if any(x in s.text_tail for x in strs):
+                s.done, s.stop_reason = True, 'stop'
+                return
+        if p.max_tokens is not None and len(s.tokens) >= p.max_tokens:
+            s.done, s.stop_reason = True, 'length'
+
+    # ----------------------------------------------------------------- API
+    @torch.no_grad()
+    def generate(self, prompts: List[List[int]], params: List[SamplingParams], lora: Optional[List[Optional[Dict[str, Any]]]] = None,
+                 eos_token_id: Optional[int] = None, on_token: Optional[Callable[[int, int, float], None]] = None) -> List[SampleResponse]:
+        """``prompts[i]`` is sampled ``params[i].num_samples`` times.  ``lora[i]`` = ``{slot, rank, scale, target}`` or None."""
+        responses = [SampleResponse() for _ in prompts]
+        seqs: List[_Seq] = []
+        for i, (pr, sp) in enumerate(zip(prompts, params)):
+            lo = (lora[i] if lora else None) or {}
+            for n in range(sp.num_samples):
+                g = None
+                if sp.seed is not None:
+                    g = torch.Generator(device=self.device).manual_seed(sp.seed + n)
+                seqs.append(_Seq(i, list(pr), sp, lo.get('slot', -1), lo.get('rank', 0), lo.get('scale', 0.0), lo.get('target'), generator=g))
+        for lo_i in range(0, len(seqs), self.max_batch):
+            self._run_group(seqs[lo_i:lo_i + self.max_batch], responses, eos_token_id, on_token)
+        return responses
+
+    def _run_group(self, seqs: List[_Seq], responses, eos, on_token) -> None:
+        hidden = self.prefill(seqs)
+        lens = [len(s.prompt) for s in seqs]
+        ends = torch.tensor(lens, device=self.device).cumsum(0) - 1
+        # prompt scoring (teacher logprobs for distillation / max_tokens == 0)
+        need_prompt = [s.params.prompt_logprobs is not None for s in seqs]
+        if any(need_prompt):
+            off = 0
+            for s, n, need in zip(seqs, lens, need_prompt):
+                if need and responses[s.request].prompt_logprobs is None:
+                    h = hidden[off:off + n]
+                    ids = torch.tensor(s.prompt[1:] + [0], device=self.device)
+                    temp = s.params.temperature if s.params.temperature > 0 else 1.0
+                    lp, _ = ops.fused_linear_logprob(h, self.model.head_weight(), ids, temp)
+                    responses[s.request].prompt_logprobs = [None] + [float(x) for x in lp[:-1]]
+                    k = s.params.prompt_logprobs
+                    if k and k > 0:
+                        lg = torch.log_softmax(self.model.logits(h[:-1]).float() / temp, -1)
+                        v, ix = lg.topk(min(k, lg.shape[-1]), -1)
+                        responses[s.request].topk_prompt_logprobs = [None] + [[(int(a), float(b)) for a, b in zip(r_i, r_v)]
+                                                                             for r_i, r_v in zip(ix.tolist(), v.tolist())]
+                off += n
+        live = [s for s in seqs if not s.params.scoring_only]
+        for s in seqs:
+            if s.params.scoring_only:
+                s.done = True
+        if live:
+            idx = [i for i, s in enumerate(seqs) if not s.params.scoring_only]
+            logits = self.model.logits(hidden[ends[idx]]).float()
+            while live:
+                toks, lps, tops = self._sample(live, logits)
+                for s, t, lp, tp in zip(live, toks, lps, tops):
+                    s.tokens.append(t)
+                    s.logprobs.append(lp)
+                    if tp is not None:
+                        s.topk.append(tp)
+                    if on_token is not None:
+                        on_token(s.request, t, lp)
+                    self._check_stop(s, t, eos)
+                nxt = [s for s in live if not s.done]
+                if not nxt:
+                    break
+                last = torch.tensor([s.tokens[-1] for s in nxt], device=self.device)
+                for s in nxt:  # grow the block list when a sequence crosses a block boundary
+                    need = self.cache.blocks_for(s.length + 1) - len(s.blocks)
+                    if need > 0:
+                        s.blocks += self.cache.allocate(need)
+                logits = self.decode_step(nxt, last)
+                live = nxt
+        for s in seqs:
+            self.cache.release(s.blocks)
+            s.blocks = []
+            if not s.params.scoring_only:
+                responses[s.request].sequences.append(SampledSequence(stop_reason=s.stop_reason, tokens=s.tokens, logprobs=s.logprobs,
+                                                                      topk_logprobs=s.topk or None, routed_experts=s.routed))
+
+    def reset_prefix_cache(self) -> None:
+        """No cross-request prefix reuse is kept, so there is nothing stale to drop after a weight update."""
+        return None

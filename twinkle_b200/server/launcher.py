@@ -1,0 +1,171 @@
+"""Builds and runs the whole server from a ``ServerConfig``.
+
+Parity: reference ``src/twinkle/server/launcher/server_launcher.py:30-319`` (+ ``builder_registry``,
+``env_propagation``) and ``server/cli/app.py`` (``twinkle-server launch | check-config | print-config |
+clear persistence``).  The reference starts Ray Serve and one deployment per application; this launcher
+builds one FastAPI root application, mounts every configured application at its ``route_prefix``
+(``…/model/<base_model>``, ``…/sampler/<base_model>``, ``…/processor``), starts the lifecycle loop
+(heart-beat expiry, leader lease renewal, resource gauges) and serves with uvicorn until SIGINT / SIGTERM.
+"""
+from __future__ import annotations
+
+import argparse
+import asyncio
+import os
+import signal
+import sys
+from typing import Any, Dict, List, Optional, Union
+
+from fastapi import FastAPI
+
+from .apps import ModelApp, ProcessorApp, SamplerApp
+from .apps.gateway import GatewayApp, Router
+from .checkpoint import CheckpointManager
+from .config import ServerConfig
+from .state import LEASE_RENEW, ServerState, build_backend
+from .telemetry import ResourceMetricsCollector, get_registry
+
+
+class ServerLauncher:
+
+    def __init__(self, config: Union[ServerConfig, str, Dict[str, Any]]):
+        if isinstance(config, str):
+            config = ServerConfig.from_yaml(config)
+        elif isinstance(config, dict):
+            config = ServerConfig(**config)
+        self.config = config
+        self.state = ServerState(build_backend(config.persistence))
+        self.checkpoints = CheckpointManager()
+        self.router = Router()
+        self.root = FastAPI(title='twinkle-b200-server')
+        self.model_apps: List[ModelApp] = []
+        self.sampler_apps: List[SamplerApp] = []
+        self.processor_apps: List[ProcessorApp] = []
+        self.gateway: Optional[GatewayApp] = None
+        self._lifecycle_task: Optional[asyncio.Task] = None
+        self._export_env()
+        self._build()
+
+    def _export_env(self) -> None:
+        """Worker processes rebuild persistence / telemetry from the environment."""
+        p = self.config.persistence
+        os.environ['TWINKLE_PERSISTENCE_MODE'] = p.mode
+        if p.file_path:
+            os.environ['TWINKLE_PERSISTENCE_FILE'] = p.file_path
+        os.environ['TWINKLE_TELEMETRY_ENABLED'] = '1' if self.config.telemetry.enabled else '0'
+        os.environ.setdefault('TWINKLE_FAIL_FAST', '0')  # a bad request must not wedge the collectives of the model workers
+
+    def _build(self) -> None:
+        gateway_spec = None
+        for spec in self.config.applications:
+            a = spec.typed_args
+            if spec.import_path == 'model':
+                m = ModelApp(a, self.state, self.config.task_queue, self.checkpoints, spec.name)
+                self.model_apps.append(m)
+                self.router.add_model(m)
+                self.root.mount(spec.route_prefix.rstrip('/'), m.app)
+            elif spec.import_path == 'sampler':
+                s = SamplerApp(a, self.state, self.config.task_queue, self.checkpoints, spec.name)
+                self.sampler_apps.append(s)
+                self.router.add_sampler(s)
+                self.root.mount(spec.route_prefix.rstrip('/'), s.app)
+            elif spec.import_path == 'processor':
+                p = ProcessorApp(a, self.state, spec.name)
+                self.processor_apps.append(p)
+                self.root.mount(spec.route_prefix.rstrip('/'), p.app)
+            else:
+                gateway_spec = spec
+        if gateway_spec is not None:
+            self.state.per_token_model_limit = gateway_spec.typed_args.per_token_model_limit
+            self.gateway = GatewayApp(gateway_spec.typed_args, self.state, self.checkpoints, self.router, gateway_spec.name)
+            prefix = gateway_spec.route_prefix.rstrip('/')
+            self.root.mount(prefix or '/', self.gateway.app)
+
+        @self.root.on_event('startup')
+        async def _start():
+            self._lifecycle_task = asyncio.get_event_loop().create_task(self._lifecycle())
+
+        @self.root.on_event('shutdown')
+        async def _stop():
+            if self._lifecycle_task:
+                self._lifecycle_task.cancel()
+            self.state.release_leadership()
+
+    async def _lifecycle(self) -> None:
+        """10-second countdown loop: expire adapters / processors whose session went silent, renew the
+        cleanup lease, sweep (leader only), publish gauges."""
+        collector = ResourceMetricsCollector(get_registry())
+        timeout = self.gateway.args.session_timeout if self.gateway else 1800.0
+        while True:
+            try:
+                for m in self.model_apps:
+                    m.expire_adapters()
+                for p in self.processor_apps:
+                    p.expire(timeout)
+                if self.state.try_acquire_leadership():
+                    self.state.sweep(timeout)
+                    for k, v in self.state.gauges().items():
+                        get_registry().set_gauge(f'twinkle_active_{k}', v)
+                collector.collect()
+            except Exception:
+                pass
+            await asyncio.sleep(LEASE_RENEW)
+
+    def launch(self, block: bool = True) -> None:
+        import uvicorn
+        h = self.config.http_options
+        cfg = uvicorn.Config(self.root, host=h.host, port=h.port, log_level='warning')
+        server = uvicorn.Server(cfg)
+        if block:
+            server.run()
+        else:
+            import threading
+            t = threading.Thread(target=server.run, daemon=True)
+            t.start()
+            self._server, self._thread = server, t
+
+    def shutdown(self) -> None:
+        s = getattr(self, '_server', None)
+        if s is not None:
+            s.should_exit = True
+            self._thread.join(timeout=10)
+
+
+def launch_server(config: Union[ServerConfig, Dict[str, Any], None] = None, config_path: Optional[str] = None, block: bool = True) -> ServerLauncher:
+    launcher = ServerLauncher(config if config is not None else config_path)
+    launcher.launch(block)
+    return launcher
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    ap = argparse.ArgumentParser(prog='twinkle-server')
+    sub = ap.add_subparsers(dest='cmd', required=True)
+    for name in ('launch', 'check-config', 'print-config'):
+        sp = sub.add_parser(name)
+        sp.add_argument('--config', '-c', required=True)
+    clr = sub.add_parser('clear')
+    clr.add_argument('what', choices=['persistence'])
+    clr.add_argument('--config', '-c', required=True)
+    a = ap.parse_args(argv)
+    try:
+        cfg = ServerConfig.from_yaml(a.config)
+    except Exception as e:
+        print(f'invalid config: {e}', file=sys.stderr)
+        return 2
+    if a.cmd == 'check-config':
+        print('config ok:', len(cfg.applications), 'applications')
+        return 0
+    if a.cmd == 'print-config':
+        print(cfg.to_yaml())
+        return 0
+    if a.cmd == 'clear':
+        if cfg.persistence.mode == 'file' and os.path.exists(cfg.persistence.file_path):
+            os.remove(cfg.persistence.file_path)
+        print('persistence cleared')
+        return 0
+    launch_server(cfg)
+    return 0
+
+
+if __name__ == '__main__':
+    sys.exit(main())
