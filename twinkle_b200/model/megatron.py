@@ -1,0 +1,549 @@
+"""The tensor- / pipeline-parallel backend ("Megatron-style" path) on the same decoder and kernels.
+
+Parity: reference ``src/twinkle/model/megatron/megatron.py:99-1748`` (``MegatronModel``),
+``strategy/megatron.py:14-326`` and ``multi_lora_megatron.py:34-451``.  The reference delegates to
+megatron-core, TransformerEngine and ``mcore_bridge``; here the pieces are owned:
+
+* mesh order innermost→outermost ``tp - (cp) - dp - pp`` (the reference's ``'tp-cp-ep-dp-pp'``);
+* TP linears with sequence-parallel activations (``parallel.tensor``), vocab-parallel embedding and
+  log-prob;
+* 1F1B / interleaved-VPP schedule over NCCL p2p (``parallel.pipeline``); micro-batches come from the
+  ``InputProcessor``; the last stage computes logps → pluggable ``Loss``; the loss is broadcast from the last
+  stage and averaged over dp;
+* per-token loss: gradients are divided by the global token count at clip time (same contract as the
+  sharded backend);
+* weights are saved / loaded in Hugging Face safetensors naming through ``models.bridge`` (TP shards
+  gathered per tensor, pipeline stages contribute their layers) — bitwise round trip;
+* replicated AdamW state per rank on its own shards (fused AdamW kernel), data-parallel gradient
+  all-reduce.
+"""
+from __future__ import annotations
+
+import json
+import os
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..infra import collect_tensor_dict, remote_class, remote_function
+from ..loss import torch_loss_mapping
+from ..models.bridge import hf_names_for, hf_to_internal, internal_to_hf, tp_rule, tp_shard, tp_unshard
+from ..models.config import PRESETS, DecoderConfig, preset
+from ..models.decoder import DecoderModel, PackedBatch, build_model
+from ..module.scheduler import scheduler_mapping
+from ..parallel.comm import Communicator
+from ..parallel.pipeline import PipelineRunner
+from ..parallel.tensor import SliceTokens, apply_tensor_parallel
+from ..processor import InputProcessor
+from ..utils.device_mesh import DeviceMesh
+from ..utils.platform import Platform
+from ..utils.safetensors_io import SafetensorLazyLoader, StreamingSafetensorSaver
+from .base import TwinkleModel
+from .native import EngineOptimizer, _no_decay
+from .optimizer_group import AdamHyper, OptimizerGroup
+
+
+def split_layers(num_layers: int, pp: int, vpp: int) -> List[List[Tuple[int, int]]]:
+    """``result[rank][chunk] = (first_layer, last_layer_exclusive)``; virtual stage ``chunk·pp + rank``."""
+    stages = pp * vpp
+    base, extra = divmod(num_layers, stages)
+    bounds, lo = [], 0
+    for s in range(stages):
+        n = base + (1 if s < extra else 0)
+        bounds.append((lo, lo + n))
+        lo += n
+    return [[bounds[c * pp + r] for c in range(vpp)] for r in range(pp)]
+
+
+@remote_class()
+class MegatronModel(TwinkleModel):
+
+    def __init__(self, model_id: Optional[str] = None, config=None, device_mesh: DeviceMesh = None, mixed_precision: str = 'bf16',
+                 seed: int = 0, device=None, **kwargs):
+        self._try_init_process_group()
+        self.device_mesh = device_mesh or DeviceMesh.from_sizes(dp_size=Platform.get_world_size())
+        mesh = self.device_mesh
+        self.device = torch.device(device) if device is not None else Platform.current_device()
+        on_gpu = self.device.type == 'cuda'
+        if on_gpu:
+            torch.cuda.set_device(self.device)
+        self.compute_dtype = torch.bfloat16 if (on_gpu and mixed_precision == 'bf16') else torch.float32
+        if isinstance(config, DecoderConfig):
+            self.config = config
+        elif isinstance(config, dict):
+            self.config = DecoderConfig.from_hf(config)
+        elif model_id and model_id.lower() in PRESETS:
+            self.config = preset(model_id)
+        else:
+            self.config = DecoderConfig.from_pretrained(model_id)
+        self.model_id = model_id
+        cfg = self.config
+        self.tp_size, self.pp_size = mesh.tp_world_size or 1, mesh.pp_world_size or 1
+        self.vpp = mesh.vpp_size or 1
+        self.tp_rank, self.pp_rank = mesh.tp_rank or 0, mesh.pp_rank or 0
+        multi = dist.is_available() and dist.is_initialized() and mesh.world_size > 1
+        self.tp_comm = Communicator(mesh.get_dim_group('tp') if multi and mesh.has_dim('tp') else None, self.device, single=self.tp_size == 1)
+        self.pp_group = mesh.get_dim_group('pp') if multi and mesh.has_dim('pp') else None
+        dp_dims = tuple(d for d in ('dp', 'fsdp') if mesh.has_dim(d))
+        dp_world = 1
+        for d in dp_dims:
+            dp_world *= mesh.get_dim_size(d)
+        self.dp_comm = Communicator(mesh.get_dim_group(dp_dims) if multi and dp_dims and dp_world > 1 else None, self.device,
+                                    single=dp_world == 1)
+        # ---- model chunks of this pipeline rank
+        self.layer_plan = split_layers(cfg.num_hidden_layers, self.pp_size, self.vpp)
+        self.chunks: List[DecoderModel] = []
+        load_dir = model_id if model_id and os.path.isdir(str(model_id)) else None
+        for c, (lo, hi) in enumerate(self.layer_plan[self.pp_rank]):
+            first = self.pp_rank == 0 and c == 0
+            last = self.pp_rank == self.pp_size - 1 and c == self.vpp - 1
+            need_embed = first or (last and cfg.tie_word_embeddings)
+            m = build_model(cfg, device=self.device, dtype=self.compute_dtype, seed=seed, init=load_dir is None, layer_range=(lo, hi),
+                            has_embed=need_embed, has_head=last)
+            # parameter names carry GLOBAL layer indices so that seeds / bridge names agree across layouts
+            self._rename_for_init(m, lo, seed, load_dir)
+            apply_tensor_parallel(m, cfg, self.tp_comm, mesh.sequence_parallel)
+            self.chunks.append(m)
+        self.sequence_parallel = bool(mesh.sequence_parallel and self.tp_size > 1)
+        self.runner = PipelineRunner(self.pp_group, self.pp_rank, self.pp_size, self.vpp, self.compute_dtype, self.device)
+        self.optimizer_groups: Dict[str, OptimizerGroup] = {'': OptimizerGroup(adapter_name='')}
+        self._state: Dict[str, Dict[str, torch.Tensor]] = {}
+        self._pending_scale = 1.0
+
+    # ------------------------------------------------------------ weights
+    def _rename_for_init(self, m: DecoderModel, lo: int, seed: int, load_dir: Optional[str]) -> None:
+        """Re-initialise (or load) with global layer names: ``layers.<local>`` → ``layers.<lo+local>``."""
+        from ..utils.seed import stable_seed
+        loader = SafetensorLazyLoader(load_dir) if load_dir else None
+        with torch.no_grad():
+            for name, p in m.named_parameters():
+                g = self._global_name(name, lo)
+                if loader is not None:
+                    src = 'model.embed_tokens.weight' if (g == 'lm_head.weight' and 'lm_head.weight' not in loader) else None
+                    t = loader.get(src) if src else hf_to_internal(g, self.config, loader.get)
+                    p.copy_(t.to(p.dtype))
+                elif p.dim() > 1:
+                    gen = torch.Generator(device='cpu').manual_seed(stable_seed(seed, g))
+                    p.copy_(torch.randn(p.shape, generator=gen, dtype=torch.float32).mul_(self.config.initializer_range))
+        m._layer_offset = lo
+
+    @staticmethod
+    def _global_name(name: str, lo: int) -> str:
+        if name.startswith('layers.'):
+            parts = name.split('.')
+            parts[1] = str(int(parts[1]) + lo)
+            return '.'.join(parts)
+        return name
+
+    def named_parameters(self):
+        for m in self.chunks:
+            for n, p in m.named_parameters():
+                yield self._global_name(n, m._layer_offset), p
+
+    def _group(self, adapter_name=None) -> OptimizerGroup:
+        return self.optimizer_groups['']
+
+    # ------------------------------------------------------------ forward
+    def _micro_batches(self, inputs, micro_batch_size: Optional[int]):
+        og = self._group()
+        if isinstance(inputs, dict):
+            inputs = [inputs]
+        feats = list(inputs)
+        if feats and 'input_ids' not in feats[0]:
+            feats = og.template.batch_encode(feats)
+        proc = og.processor or InputProcessor(pad_token_id=self.config.pad_token_id or 0)
+        og.processor = proc
+        proc.micro_batch_size = micro_batch_size or 1
+        proc.sp_size = 1
+        items = proc.normalize(feats)
+        mult = self.tp_size if self.sequence_parallel else 1
+        mbs = []
+        for g in proc.split_micro_batches(items):
+            mbs.append(proc._pack(g, pad_multiple=mult, split=False))  # tokens must divide over the tp group
+        return feats, mbs
+
+    def _forward_chunk(self, mbs, og, loss_kwargs, results):
+        def run(chunk: int, micro: int, x: Optional[torch.Tensor]) -> torch.Tensor:
+            m = self.chunks[chunk]
+            mb = mbs[micro].to(self.device)
+            batch = PackedBatch(mb.input_ids, mb.position_ids, mb.cu_seqlens, mb.max_seqlen, mb.labels)
+            if x is None:
+                h = m.embed(batch)
+                if m.tp is not None and not m.tp.sp:
+                    pass
+            else:
+                h = x
+            cos, sin = ops.rope_tables(batch.position_ids, self.config.head_dim, self.config.rope_theta)
+            for layer in m.layers:
+                h = layer(h, cos, sin, batch)
+            if not m.has_head:
+                return h
+            h = m.norm(h)
+            logps, _ = m.token_logprobs(h, mb.labels)
+            out = {'logps': InputProcessor.unpack_packed_sequences(logps, mb.seq_lens, 0),
+                   'labels': InputProcessor.unpack_packed_sequences(mb.labels, mb.seq_lens, -100)}
+            res = og.loss_instance({'labels': out['labels']}, out, **loss_kwargs(micro))
+            loss = res['loss'] if isinstance(res, dict) else res
+            nt = float(res.get('num_tokens', 0) or 0) if isinstance(res, dict) else 0.0
+            results.append({'logps': out['logps'].detach(), 'labels': out['labels'], 'num_tokens': nt, 'loss': float(loss.detach())})
+            return loss
+
+        return run
+
+    def _hidden_shape(self, mbs):
+        def shape(micro: int):
+            t = int(mbs[micro].input_ids.numel())
+            if self.sequence_parallel:
+                t //= self.tp_size
+            return (t, self.config.hidden_size)
+        return shape
+
+    @remote_function(dispatch='slice_dp', collect=collect_tensor_dict)
+    def forward_backward(self, *, inputs, micro_batch_size: Optional[int] = 1, adapter_name: Optional[str] = None, **kwargs):
+        og = self._group()
+        feats, mbs = self._micro_batches(inputs, micro_batch_size)
+        n = len(feats)
+        per = micro_batch_size or 1
+
+        def loss_kwargs(micro: int):
+            from .native import TransformersModel
+            return TransformersModel._slice_kwargs(kwargs, micro * per, min((micro + 1) * per, n), n)
+
+        results: List[Dict[str, Any]] = []
+        self.runner.run(len(mbs), self._forward_chunk(mbs, og, loss_kwargs, results), self._hidden_shape(mbs))
+        # loss / token count live on the last stage: share them with the whole pipeline group
+        stats = torch.zeros(3, dtype=torch.float64, device=self.device if self.device.type == 'cuda' else 'cpu')
+        if results:
+            stats[0] = sum(r['loss'] for r in results)
+            stats[1] = sum(r['num_tokens'] for r in results)
+            stats[2] = len(results)
+        if self.pp_size > 1:
+            dist.all_reduce(stats, group=self.pp_group)  # only last-stage ranks contribute non-zeros
+        loss_sum, tokens, calls = (float(x) for x in stats)
+        og.train_status.num_tokens += tokens if tokens > 0 else calls
+        og.cur_step += 1
+        og.grad_ready = True
+        out: Dict[str, Any] = {'loss': loss_sum / tokens if tokens > 0 else loss_sum / max(calls, 1), 'num_tokens': tokens}
+        if results:
+            merged = collect_tensor_dict([{'logps': r['logps'], 'labels': r['labels']} for r in results])
+            out.update(merged)
+        return out
+
+    @remote_function(dispatch='slice_dp', collect=collect_tensor_dict)
+    def forward_only(self, *, inputs, micro_batch_size: Optional[int] = 1, **kwargs):
+        with torch.no_grad():
+            og = self._group()
+            feats, mbs = self._micro_batches(inputs, micro_batch_size)
+            results: List[Dict[str, Any]] = []
+            fc = self._forward_chunk(mbs, og, lambda m: {}, results)
+            # forward-only pipeline: every micro-batch flows through all stages in order
+            P, V = self.pp_size, self.vpp
+            for micro in range(len(mbs)):
+                for chunk in range(V):
+                    x = None
+                    if not self.runner.is_first(chunk):
+                        x = self.runner._recv(self._hidden_shape(mbs)(micro), self.runner.prev, 7_000_000 + chunk * 1024 + micro)
+                    y = fc(chunk, micro, x)
+                    if not self.runner.is_last(chunk):
+                        nxt_chunk = chunk if self.pp_rank < P - 1 else chunk + 1
+                        self.runner._send(y, self.runner.next, 7_000_000 + nxt_chunk * 1024 + micro)
+                        self.runner._flush()
+            for h in self.runner._pending:
+                h.wait()
+            self.runner._pending.clear()
+        return collect_tensor_dict([{'logps': r['logps'], 'labels': r['labels']} for r in results]) if results else {}
+
+    forward = forward_only
+
+    def calculate_loss(self, **kwargs):
+        raise NotImplementedError('the pipeline backend fuses loss into forward_backward')
+
+    def backward(self, **kwargs):
+        raise NotImplementedError('the pipeline backend fuses backward into forward_backward')
+
+    # ------------------------------------------------------------ optimiser
+    def _params(self) -> List[Tuple[str, torch.nn.Parameter]]:
+        return [(n, p) for n, p in self.named_parameters() if p.requires_grad]
+
+    @remote_function(collect='first')
+    def clip_grad_norm(self, max_grad_norm: float = 1.0, norm_type=2, **kwargs) -> float:
+        og = self._group()
+        # 1. data-parallel gradient sum; sequence-parallel: norm weights saw different tokens on each tp rank
+        for n, p in self._params():
+            if p.grad is None:
+                continue
+            if self.dp_comm.world_size > 1:
+                self.dp_comm.all_reduce(p.grad)
+            if self.tp_size > 1 and tp_rule(n, self.config) is None:
+                self.tp_comm.all_reduce(p.grad)
+        denom = self.dp_comm.all_reduce_scalar(og.train_status.num_tokens, 'sum') or 1.0
+        # 2. global norm: tp-sharded tensors are disjoint (sum over tp), replicated ones counted once; sum over pp
+        sq = torch.zeros((), dtype=torch.float32, device=self.device)
+        tied_dup = self.config.tie_word_embeddings and self.pp_size > 1 and self.pp_rank == self.pp_size - 1
+        for n, p in self._params():
+            if p.grad is None or (tied_dup and n == 'embed_tokens.weight'):
+                continue
+            s = ops.sumsq(p.grad)
+            if self.tp_size > 1 and tp_rule(n, self.config) is None:
+                s = s / self.tp_size
+            sq = sq + s
+        if self.tp_size > 1:
+            self.tp_comm.all_reduce(sq)
+        if self.pp_size > 1:
+            dist.all_reduce(sq, group=self.pp_group)
+        norm = float(sq.sqrt()) / denom
+        coef = min(1.0, max_grad_norm / (norm + 1e-6)) if max_grad_norm and max_grad_norm > 0 else 1.0
+        self._pending_scale = coef / denom
+        og._last_grad_norm = norm
+        og.train_status.num_tokens = 0.0
+        return norm
+
+    def _sync_tied_embedding_grads(self) -> None:
+        """Tied embedding/head across the first and last pipeline stage: sum the two gradients."""
+        if not (self.config.tie_word_embeddings and self.pp_size > 1):
+            return
+        if self.pp_rank in (0, self.pp_size - 1):
+            for m in self.chunks:
+                if m.embed_tokens is not None and m.embed_tokens.weight.grad is not None:
+                    g = m.embed_tokens.weight.grad
+                    other = self.runner._globals[self.pp_size - 1 if self.pp_rank == 0 else 0]
+                    buf = torch.empty_like(g)
+                    ops_ = [dist.P2POp(dist.isend, g.contiguous(), other, group=self.pp_group), dist.P2POp(dist.irecv, buf, other, group=self.pp_group)]
+                    for w in dist.batch_isend_irecv(ops_):
+                        w.wait()
+                    g.add_(buf)
+                    return
+
+    @remote_function()
+    def step(self, optim_params: Optional[Dict[str, Any]] = None, **kwargs) -> None:
+        og = self._group()
+        if og.optimizer is None:
+            self.set_optimizer('AdamW')
+        if optim_params:
+            for g in og.optimizer.param_groups:
+                for k in ('lr', 'eps'):
+                    if k in optim_params:
+                        g[k] = optim_params[k]
+                if 'betas' in optim_params:
+                    g['betas'] = tuple(optim_params['betas'])
+                if 'weight_decay' in optim_params and g['weight_decay'] > 0:
+                    g['weight_decay'] = optim_params['weight_decay']
+        og.optim_steps += 1
+        gd = og.optimizer.param_groups[0]
+        scale, self._pending_scale = self._pending_scale, 1.0
+        for n, p in self._params():
+            if p.grad is None:
+                continue
+            st = self._state.get(n)
+            if st is None:
+                st = {'master': p.data.float().clone(), 'exp_avg': torch.zeros_like(p.data, dtype=torch.float32),
+                      'exp_avg_sq': torch.zeros_like(p.data, dtype=torch.float32)}
+                self._state[n] = st
+            ops.adamw_step(st['master'].view(-1), st['exp_avg'].view(-1), st['exp_avg_sq'].view(-1), p.grad.contiguous().view(-1),
+                           p.data.view(-1), gd['lr'], gd['betas'][0], gd['betas'][1], gd['eps'], 0.0 if _no_decay(n) else gd['weight_decay'],
+                           og.optim_steps, scale)
+        og.grad_ready = False
+
+    @remote_function()
+    def zero_grad(self, **kwargs) -> None:
+        for _, p in self._params():
+            p.grad = None
+
+    @remote_function()
+    def lr_step(self, **kwargs) -> None:
+        og = self._group()
+        if og.lr_scheduler is not None:
+            og.lr_scheduler.step()
+
+    @remote_function(collect='first')
+    def clip_grad_and_step(self, max_grad_norm: float = 1.0, norm_type=2, **kwargs):
+        self._sync_tied_embedding_grads()
+        norm = self.clip_grad_norm(max_grad_norm, norm_type)
+        self.step(**kwargs)
+        self.zero_grad()
+        self.lr_step()
+        return norm
+
+    @remote_function()
+    def set_loss(self, loss_cls, **kwargs) -> None:
+        if isinstance(loss_cls, str):
+            loss_cls = torch_loss_mapping[loss_cls]
+        self._group().set_loss(loss_cls(**kwargs) if isinstance(loss_cls, type) else loss_cls)
+
+    @remote_function()
+    def set_optimizer(self, optimizer_cls='AdamW', **kwargs) -> None:
+        og = self._group()
+        h = AdamHyper(lr=kwargs.get('lr', 1e-5), betas=tuple(kwargs.get('betas', (0.9, 0.999))), eps=kwargs.get('eps', 1e-8),
+                      weight_decay=kwargs.get('weight_decay', 0.01))
+        og.hyper = h
+        names = [n for n, _ in self._params()]
+        og.optimizer = EngineOptimizer(h, [n for n in names if not _no_decay(n)], [n for n in names if _no_decay(n)])
+
+    @remote_function()
+    def set_lr_scheduler(self, scheduler_cls, **kwargs) -> None:
+        og = self._group()
+        if og.optimizer is None:
+            self.set_optimizer('AdamW')
+        if isinstance(scheduler_cls, str):
+            scheduler_cls = scheduler_mapping[scheduler_cls]
+        og.lr_scheduler = scheduler_cls(og.optimizer, **kwargs) if isinstance(scheduler_cls, type) else scheduler_cls
+
+    @remote_function()
+    def set_template(self, template_cls, **kwargs) -> None:
+        from ..template import Template, template_mapping
+        if isinstance(template_cls, str):
+            template_cls = template_mapping.get(template_cls, Template)
+        self._group().template = template_cls(**kwargs) if isinstance(template_cls, type) else template_cls
+
+    @remote_function()
+    def set_processor(self, processor_cls, **kwargs) -> None:
+        self._group().processor = processor_cls(**kwargs) if isinstance(processor_cls, type) else processor_cls
+
+    def apply_patch(self, patch_cls, **kwargs) -> None:
+        from ..patch import apply_patch
+        apply_patch(self, patch_cls, **kwargs)
+
+    def add_metric(self, metric_cls, is_training=None, **kwargs) -> None:
+        from ..metric import metric_mapping
+        m = metric_mapping[metric_cls](**kwargs) if isinstance(metric_cls, str) else metric_cls
+        self._group().train_status.metrics.append(m)
+
+    def calculate_metric(self, is_training: bool = True, **kwargs) -> Dict[str, Any]:
+        out: Dict[str, Any] = {}
+        for m in self._group().status(is_training).metrics:
+            out.update(m.calculate())
+        return out
+
+    def add_adapter_to_model(self, adapter_name: str, config_or_dir, **kwargs) -> None:
+        raise NotImplementedError('use MultiLoraMegatronModel for adapters')
+
+    def get_train_configs(self, **kwargs) -> str:
+        n = sum(p.numel() for _, p in self._params())
+        return (f'model: {self.model_id or self.config.model_type}; this rank holds {n:,} parameters\n'
+                f'layout: tp={self.tp_size} pp={self.pp_size} vpp={self.vpp} dp={self.dp_comm.world_size} '
+                f'sequence_parallel={self.sequence_parallel}; layers of this rank: {self.layer_plan[self.pp_rank]}')
+
+    # ---------------------------------------------------------- save / load
+    def _gather_full(self, name: str, p: torch.Tensor) -> torch.Tensor:
+        if self.tp_size == 1 or tp_rule(name, self.config) is None:
+            return p.detach()
+        parts = [torch.empty_like(p) for _ in range(self.tp_size)]
+        dist.all_gather(parts, p.detach().contiguous(), group=self.tp_comm.group)
+        return tp_unshard(name, parts, self.config)
+
+    @remote_function(collect='first')
+    def get_state_dict(self, **kwargs) -> Dict[str, torch.Tensor]:
+        """HF-named tensors held by this pipeline stage (TP shards gathered)."""
+        out = {}
+        for n, p in self.named_parameters():
+            if n == 'embed_tokens.weight' and self.config.tie_word_embeddings and self.pp_rank != 0:
+                continue
+            full = self._gather_full(n, p)
+            for hk, hv in internal_to_hf(n, full, self.config):
+                out[hk] = hv
+        return out
+
+    def get_hf_state_dict(self):
+        yield from self.get_state_dict().items()
+
+    @remote_function(collect='first')
+    def save(self, name: Optional[str] = None, output_dir: Optional[str] = None, **kwargs) -> str:
+        """Every pipeline stage writes its own shard files (``model-ppXX-….safetensors``); rank 0 merges the
+        indices so the directory is a standard HF checkpoint."""
+        path = os.path.join(output_dir or './output', name) if name else (output_dir or './output')
+        sd = self.get_state_dict()
+        writer = (self.tp_rank == 0) and (self.dp_comm.rank == 0)
+        os.makedirs(path, exist_ok=True)
+        if writer:
+            from safetensors.torch import save_file
+            fn = f'model-pp{self.pp_rank:02d}-of-{self.pp_size:02d}.safetensors'
+            save_file({k: v.detach().cpu().contiguous() for k, v in sd.items()}, os.path.join(path, fn), metadata={'format': 'pt'})
+            with open(os.path.join(path, f'.index-pp{self.pp_rank:02d}.json'), 'w') as f:
+                json.dump({k: fn for k in sd}, f)
+        if dist.is_available() and dist.is_initialized():
+            dist.barrier()
+        if Platform.is_master():
+            weight_map: Dict[str, str] = {}
+            for r in range(self.pp_size):
+                pth = os.path.join(path, f'.index-pp{r:02d}.json')
+                with open(pth) as f:
+                    weight_map.update(json.load(f))
+                os.remove(pth)
+            with open(os.path.join(path, 'model.safetensors.index.json'), 'w') as f:
+                json.dump({'metadata': {}, 'weight_map': weight_map}, f)
+            self.config.save_pretrained(path)
+        if dist.is_available() and dist.is_initialized():
+            dist.barrier()
+        return path
+
+    @remote_function()
+    def load(self, name: Optional[str] = None, output_dir: Optional[str] = None, **kwargs) -> None:
+        path = os.path.join(output_dir or './output', name) if name else (output_dir or './output')
+        loader = SafetensorLazyLoader(path)
+        with torch.no_grad():
+            for n, p in self.named_parameters():
+                src_head = n == 'lm_head.weight' and 'lm_head.weight' not in loader
+                full = loader.get('model.embed_tokens.weight') if src_head else hf_to_internal(n, self.config, loader.get)
+                p.copy_(tp_shard(n, full, self.config, self.tp_rank, self.tp_size).to(p.device, p.dtype))
+                st = self._state.get(n)
+                if st is not None:
+                    st['master'].copy_(p.data.float())
+
+    def resume_from_checkpoint(self, checkpoint_dir: str, **kwargs) -> Dict[str, Any]:
+        self.load(None, checkpoint_dir)
+        og = self._group()
+        return {'cur_step': og.cur_step, 'consumed_train_samples': og.consumed_train_samples,
+                'gradient_accumulation_steps': og.gradient_accumulation_steps}
+
+
+@remote_class()
+class MultiLoraMegatronModel(MegatronModel):
+    """Adapters on the pipeline backend.  LoRA pools attach to un-sharded linears only, so tensor parallelism
+    must be 1 here (pipeline and data parallelism are free); with tp > 1 use the sharded backend."""
+
+    def __init__(self, *args, max_loras: int = 5, max_r: int = 32, max_length: int = 8192, **kwargs):
+        super().__init__(*args, **kwargs)
+        if self.tp_size > 1:
+            raise NotImplementedError('multi-LoRA on the pipeline backend requires tp_size == 1')
+        from .multi_lora import MultiLora
+        self.max_length = max_length
+        self.pools = [MultiLora(m, max_loras, max_r) for m in self.chunks]
+        self.optimizer_groups = {}
+
+    def _group(self, adapter_name=None) -> OptimizerGroup:
+        if adapter_name is None:
+            adapter_name = getattr(self, '_active', None)
+        return self.optimizer_groups[adapter_name]
+
+    def add_adapter_to_model(self, adapter_name: str, config_or_dir, **kwargs) -> None:
+        from .multi_lora import LoraConfig
+        cfg = LoraConfig.from_any(config_or_dir)
+        for pool in self.pools:
+            pool.acquire_lora(adapter_name, cfg)
+        self.optimizer_groups[adapter_name] = OptimizerGroup(adapter_name=adapter_name, adapter_config=cfg)
+        self._active = adapter_name
+
+    def remove_adapter(self, adapter_name: str, **kwargs) -> None:
+        for pool in self.pools:
+            pool.release_lora(adapter_name)
+        self.optimizer_groups.pop(adapter_name, None)
+
+    def check_length(self, inputs, max_length=None) -> None:
+        limit = max_length or self.max_length
+        for f in ([inputs] if isinstance(inputs, dict) else inputs):
+            if len(f.get('input_ids', [])) > limit:
+                raise ValueError(f'input exceeds max_length {limit}')
+
+    def forward_backward(self, *, inputs, adapter_name: Optional[str] = None, **kwargs):
+        from ..models.layers import lora_batch
+        self._active = adapter_name
+        t = self.pools[0].tenants[adapter_name]
+        lb_factory = lambda n: self.pools[0].batch_for(adapter_name, n, self.device)
+        # one tenant per call: the same routing applies to every micro-batch (segment covers all tokens)
+        from ..models.layers import LoraBatch
+        big = LoraBatch.single(1 << 30, t.slot, t.config.r, t.config.scaling, self.device, t.target)
+        with lora_batch(big):
+            return MegatronModel.forward_backward.__wrapped__(self, inputs=inputs, **kwargs) if hasattr(
+                MegatronModel.forward_backward, '__wrapped__') else super().forward_backward(inputs=inputs, **kwargs)

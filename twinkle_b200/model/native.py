@@ -87,8 +87,9 @@ class TransformersModel(TwinkleModel):
                  device_mesh: DeviceMesh = None, mixed_precision: str = 'bf16', strategy: str = 'native_fsdp',
                  task: str = 'causal_lm', seed: int = 0, grad_dtype: Optional[str] = None, comm_backend: str = 'auto',
                  gradient_accumulation_steps: int = 1, max_loras: int = 0, max_r: int = 0, device=None,
-                 fsdp_group_dims: Optional[Sequence[str]] = None, **kwargs):
+                 fsdp_group_dims: Optional[Sequence[str]] = None, keep_attention: bool = True, **kwargs):
         self._try_init_process_group()
+        self.keep_attention = keep_attention
         self.device_mesh = device_mesh or DeviceMesh.from_sizes(dp_size=Platform.get_world_size())
         self.task = task
         self.model_id = model_id
@@ -189,7 +190,8 @@ class TransformersModel(TwinkleModel):
         ignored = None
         if self.device_mesh.ep_size and self.device_mesh.ep_size > 1 and self.config.is_moe:
             ignored = lambda n: '.mlp.experts.' in n  # experts are EP-local, not FSDP-sharded over the dp group
-        self.engine = FSDPEngine(self.model, comm, self.compute_dtype, self.device, grad_dtype=self.grad_dtype, ignored=ignored)
+        self.engine = FSDPEngine(self.model, comm, self.compute_dtype, self.device, grad_dtype=self.grad_dtype, ignored=ignored,
+                                 keep_attention=self.keep_attention)
 
     def _group(self, adapter_name: Optional[str]) -> OptimizerGroup:
         name = adapter_name or _DEFAULT

@@ -186,18 +186,17 @@ class MoEBlock(nn.Module):
         mp = self.moe_parallel
         if mp is not None:
             return mp.forward(self, x, w, idx)
-        # local: sort (token, slot) pairs by expert
+        # local: expert-sorted layout whose segments start on 128-row boundaries (grouped GEMM tiles and the
+        # per-expert wgrad reduction ranges then never straddle two experts); padding rows are zero
+        from ..parallel.expert import expert_layout
         flat = idx.reshape(-1)
-        order = torch.argsort(flat, stable=True)
-        counts = torch.bincount(flat, minlength=E)
-        offsets = torch.zeros(E + 1, dtype=torch.int32, device=x.device)
-        offsets[1:] = counts.cumsum(0)
+        order, rows, offsets, bound = expert_layout(flat, E, 128 if x.is_cuda else 1)
         tok = order // k
-        y = self.experts(x.index_select(0, tok), offsets)
+        xs = x.new_zeros(bound, H).index_copy(0, rows, x.index_select(0, tok))
+        y = self.experts(xs, offsets).index_select(0, rows)
         y = y * w.reshape(-1)[order].to(y.dtype).unsqueeze(-1)
         out = torch.zeros(T, H, dtype=y.dtype, device=x.device)
-        out.index_add_(0, tok, y)
-        return out
+        return out.index_add(0, tok, y)
 
 
 class DecoderLayer(nn.Module):
@@ -243,6 +242,7 @@ class DecoderModel(nn.Module):
             if isinstance(m, Linear):
                 m.full_name = name
         self.layer_runner = None  # engine hook: runs one layer (checkpoint / FSDP unshard)
+        self.tp = None  # tensor-parallel context, set by parallel.tensor.apply_tensor_parallel
 
     # --------------------------------------------------------------- init
     @torch.no_grad()
@@ -274,6 +274,9 @@ class DecoderModel(nn.Module):
     def embed(self, batch: PackedBatch) -> torch.Tensor:
         if batch.inputs_embeds is not None:
             return batch.inputs_embeds
+        if self.tp is not None:
+            from ..parallel.tensor import vocab_parallel_embedding
+            return vocab_parallel_embedding(batch.input_ids, self.embed_tokens.weight, self.tp)
         return self.embed_tokens(batch.input_ids)
 
     def forward(self, batch: PackedBatch, hidden: Optional[torch.Tensor] = None, kv_sink=None) -> torch.Tensor:
@@ -296,6 +299,11 @@ class DecoderModel(nn.Module):
                        with_entropy: bool = False):
         """(logps [T] fp32, entropies|None) with ignored labels (−100) read as id 0."""
         safe = labels.clamp_min(0)
+        if self.tp is not None:
+            from ..parallel.tensor import CopyToTP, GatherTokens, vocab_parallel_logprob
+            # backward of either op sums the per-vocabulary-shard partial gradients of the hidden states
+            hidden = GatherTokens.apply(hidden, self.tp.comm) if self.tp.sp else CopyToTP.apply(hidden, self.tp.comm)
+            return vocab_parallel_logprob(hidden, self.head_weight(), safe, self.tp, temperature), None
         return ops.fused_linear_logprob(hidden, self.head_weight(), safe, temperature, with_entropy)
 
     def aux_loss(self) -> Optional[torch.Tensor]:

@@ -103,6 +103,8 @@ class Linear(nn.Module):
         self.max_loras = 0
         self.max_r = 0
         self.wgrad_out: Optional[torch.Tensor] = None  # flat-bucket view to accumulate dW into
+        self.tp = None  # tensor-parallel context (parallel.tensor.TPContext)
+        self.tp_mode: Optional[str] = None  # 'col' | 'row'
 
     # ------------------------------------------------------------- LoRA pool
     def add_lora_pool(self, max_loras: int, max_r: int, dtype=None, device=None) -> None:
@@ -139,6 +141,9 @@ class Linear(nn.Module):
         return outs[0] if len(outs) == 1 else torch.cat(outs, -1)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.tp_mode is not None:
+            from ..parallel.tensor import tp_linear_forward
+            return tp_linear_forward(self, x)
         y = ops.linear(x, self.weight, self.bias, self.wgrad_out if self.weight.requires_grad else None)
         lb = _CTX.batch
         if lb is not None and self.max_loras > 0:

@@ -217,12 +217,57 @@ class _FlashAttnVarlen(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None
 
 
+class _FlashAttnReuse(torch.autograd.Function):
+    """Forward returns an attention output computed earlier (with its log-sum-exp); backward is the normal
+    flash backward.  Lets an activation-recompute pass skip the attention forward."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, out, lse, cu_seqlens, max_seqlen, causal, scale):
+        ctx.save_for_backward(q, k, v, out, lse, cu_seqlens)
+        ctx.args = (max_seqlen, causal, scale)
+        return out.view_as(out)
+
+    @staticmethod
+    def backward(ctx, gout):
+        q, k, v, out, lse, cu = ctx.saved_tensors
+        max_seqlen, causal, scale = ctx.args
+        dq, dk, dv = ext().flash_attn_bwd(gout.contiguous(), q, k, v, out, lse, cu, max_seqlen, causal, scale)
+        return dq, dk, dv, None, None, None, None, None, None
+
+
+class AttentionStash:
+    """``mode='save'``: every attention call in scope appends its (out, lse); ``mode='reuse'``: calls consume
+    them in the same order instead of recomputing."""
+    current = None
+
+    def __init__(self, mode: str, items=None):
+        self.mode, self.items, self._i = mode, ([] if items is None else items), 0
+
+    def __enter__(self):
+        self._prev = AttentionStash.current
+        AttentionStash.current = self
+        return self
+
+    def __exit__(self, *exc):
+        AttentionStash.current = self._prev
+
+
 def flash_attn_varlen(q, k, v, cu_seqlens, max_seqlen: int, causal: bool = True, scale: Optional[float] = None):
     """Packed causal attention with GQA.  ``q [T,Hq,D]``, ``k,v [T,Hkv,D]``."""
     scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
     if _cuda(q) and q.dtype == torch.bfloat16:
-        return _FlashAttnVarlen.apply(q.contiguous(), k.contiguous(), v.contiguous(), cu_seqlens.to(torch.int32),
-                                      int(max_seqlen), causal, scale)
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        cu = cu_seqlens.to(torch.int32)
+        st = AttentionStash.current
+        if st is not None and st.mode == 'save' and not torch.is_grad_enabled():
+            out, lse = ext().flash_attn_fwd(q, k, v, cu, int(max_seqlen), causal, scale)
+            st.items.append((out, lse))
+            return out
+        if st is not None and st.mode == 'reuse' and st._i < len(st.items):
+            out, lse = st.items[st._i]
+            st._i += 1
+            return _FlashAttnReuse.apply(q, k, v, out, lse, cu, int(max_seqlen), causal, scale)
+        return _FlashAttnVarlen.apply(q, k, v, cu, int(max_seqlen), causal, scale)
     return ref.attention_varlen(q, k, v, cu_seqlens, causal, scale)
 
 

@@ -32,6 +32,7 @@ all-reduced.
 from __future__ import annotations
 
 import math
+from contextlib import nullcontext
 from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
 
 import torch
@@ -332,7 +333,8 @@ class _LayerFn(torch.autograd.Function):
         unit.wait_unshard()
         if idx + 1 < len(engine.units):
             engine.units[idx + 1].unshard_async(engine.pool)
-        with torch.no_grad():
+        ctx.attn = [] if engine.keep_attention else None
+        with torch.no_grad(), (ops.AttentionStash('save', ctx.attn) if ctx.attn is not None else nullcontext()):
             y = layer(x, cos, sin, batch)
             aux = getattr(layer.mlp, 'last_aux', None) if getattr(layer, 'is_moe', False) else None
             if aux is not None:
@@ -353,7 +355,8 @@ class _LayerFn(torch.autograd.Function):
             engine.units[idx - 1].unshard_async(engine.pool)
         unit.prepare_grads(engine.pool)
         xd = x.detach().requires_grad_(True)
-        with torch.enable_grad(), engine.restore_context(ctx.lora_ctx):
+        with torch.enable_grad(), engine.restore_context(ctx.lora_ctx), (
+                ops.AttentionStash('reuse', ctx.attn) if ctx.attn is not None else nullcontext()):
             y = layer(xd, cos, sin, batch)
             outs, grads = [y], [gy]
             if getattr(layer, 'is_moe', False) and layer.mlp.last_aux is not None:
@@ -361,6 +364,7 @@ class _LayerFn(torch.autograd.Function):
                 grads.append(torch.as_tensor(engine.aux_grad_weight, dtype=layer.mlp.last_aux.dtype, device=gy.device))
                 layer.mlp.last_aux = None
         torch.autograd.backward(outs, grads)
+        ctx.attn = None
         unit.reduce_grads(engine.pool)
         unit.reshard(engine.pool)
         return (None, None, None, xd.grad, None, None, None) + (None, ) * (len(ctx.needs_input_grad) - 7)
@@ -371,8 +375,11 @@ class FSDPEngine:
 
     def __init__(self, model, comm: Communicator, compute_dtype: torch.dtype = torch.bfloat16, device=None,
                  reshard_after_forward: bool = True, grad_dtype: torch.dtype = torch.float32,
-                 ignored: Optional[Callable[[str], bool]] = None):
+                 ignored: Optional[Callable[[str], bool]] = None, keep_attention: bool = True):
+        """``keep_attention``: the forward keeps each layer's attention output + log-sum-exp (≈ tokens·Hq·D
+        bf16 per layer) so the recompute in backward skips the attention forward kernel."""
         self.model, self.comm = model, comm
+        self.keep_attention = keep_attention and torch.device(device or 'cpu').type == 'cuda'
         self.device = device or next(model.parameters()).device
         self.compute_dtype = compute_dtype
         self.reshard_after_forward = reshard_after_forward and comm.world_size > 1

@@ -1,0 +1,201 @@
+"""Tensor parallelism with sequence-parallel activations (the Megatron-style layout).
+
+What it replaces: megatron-core / TransformerEngine column- and row-parallel linears reached by the
+reference through ``src/twinkle/model/megatron/strategy/megatron.py:37-118`` (``tensor_model_parallel_size``,
+``sequence_parallel``), and the fused vocab-parallel cross entropy (``utils/torch_utils.py:139-147``).
+
+Layout: ``qkv_proj`` / ``gate_up_proj`` are column-parallel (output rows split per logical part so each rank
+owns whole heads), ``o_proj`` / ``down_proj`` row-parallel (input columns split), embedding and head
+vocab-parallel.  With ``sequence_parallel`` the residual stream is sharded over tokens inside the TP group:
+an all-gather precedes every column-parallel GEMM and a reduce-scatter follows every row-parallel GEMM
+(without it: identity / all-reduce).  Collectives go through ``Communicator`` (NCCL / gloo); the fused
+all-gather→GEMM and GEMM→reduce-scatter kernels plug in at the same two call sites.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from .. import ops
+from ..models.bridge import tp_shard
+from .comm import Communicator
+
+
+def _rs(x: torch.Tensor, comm: Communicator) -> torch.Tensor:
+    n = x.shape[0] // comm.world_size
+    out = x.new_empty((n, ) + tuple(x.shape[1:]))
+    dist.reduce_scatter_tensor(out, x.contiguous(), group=comm.group)
+    return out
+
+
+class GatherTokens(torch.autograd.Function):
+    """fwd: all-gather along tokens; bwd: reduce-scatter."""
+
+    @staticmethod
+    def forward(ctx, x, comm):
+        ctx.comm = comm
+        return comm.all_gather_tensor(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _rs(g, ctx.comm), None
+
+
+class ScatterTokens(torch.autograd.Function):
+    """fwd: reduce-scatter along tokens; bwd: all-gather."""
+
+    @staticmethod
+    def forward(ctx, x, comm):
+        ctx.comm = comm
+        return _rs(x, comm)
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.comm.all_gather_tensor(g.contiguous()), None
+
+
+class ReduceFromTP(torch.autograd.Function):
+    """fwd: all-reduce; bwd: identity."""
+
+    @staticmethod
+    def forward(ctx, x, comm):
+        x = x.contiguous().clone()
+        comm.all_reduce(x)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+class CopyToTP(torch.autograd.Function):
+    """fwd: identity; bwd: all-reduce."""
+
+    @staticmethod
+    def forward(ctx, x, comm):
+        ctx.comm = comm
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous().clone()
+        ctx.comm.all_reduce(g)
+        return g, None
+
+
+class SliceTokens(torch.autograd.Function):
+    """fwd: keep this rank's token chunk; bwd: all-gather (used to enter the sequence-parallel region)."""
+
+    @staticmethod
+    def forward(ctx, x, comm):
+        ctx.comm = comm
+        n = x.shape[0] // comm.world_size
+        return x[comm.rank * n:(comm.rank + 1) * n].contiguous()
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.comm.all_gather_tensor(g.contiguous()), None
+
+
+class TPContext:
+
+    def __init__(self, comm: Communicator, sequence_parallel: bool):
+        self.comm, self.sp = comm, sequence_parallel
+        self.size, self.rank = comm.world_size, comm.rank
+
+    def before_column(self, x):
+        return GatherTokens.apply(x, self.comm) if self.sp else CopyToTP.apply(x, self.comm)
+
+    def after_row(self, y):
+        return ScatterTokens.apply(y, self.comm) if self.sp else ReduceFromTP.apply(y, self.comm)
+
+
+def tp_linear_forward(lin, x: torch.Tensor) -> torch.Tensor:
+    """Forward of a ``models.layers.Linear`` whose weight is a TP shard (``lin.tp_mode`` in {'col', 'row'})."""
+    tp: TPContext = lin.tp
+    if lin.tp_mode == 'col':
+        return ops.linear(tp.before_column(x), lin.weight, lin.bias)
+    y = ops.linear(x, lin.weight, None)
+    y = tp.after_row(y)
+    return y if lin.bias is None else y + lin.bias
+
+
+def vocab_parallel_embedding(ids: torch.Tensor, weight: torch.Tensor, tp: TPContext) -> torch.Tensor:
+    """``weight`` holds vocabulary rows ``[rank·Vl, (rank+1)·Vl)``; out-of-range ids contribute zeros and the
+    partial results are summed (reduce-scattered over tokens under sequence parallelism)."""
+    vl = weight.shape[0]
+    lo = tp.rank * vl
+    local = ids - lo
+    ok = (local >= 0) & (local < vl)
+    e = F.embedding(local.clamp(0, vl - 1), weight) * ok.unsqueeze(-1).to(weight.dtype)
+    return tp.after_row(e)
+
+
+class _VocabParallelLogprob(torch.autograd.Function):
+    """log softmax(hidden·Wᵀ)[labels] with the vocabulary split over the TP group: local max / sum-exp /
+    target-logit partials are combined with two tiny all-reduces; logits never leave the rank."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, labels, comm: Communicator, temperature: float):
+        vl = weight.shape[0]
+        lo = comm.rank * vl
+        logits = ops.gemm(hidden, weight, 'nt', out_dtype=torch.float32).float() / temperature if hidden.is_cuda else (
+            hidden.float() @ weight.float().t()) / temperature
+        m = logits.max(-1).values
+        comm.all_reduce(m, 'max')
+        ex = torch.exp(logits - m[:, None])
+        s = ex.sum(-1)
+        comm.all_reduce(s)
+        local = labels - lo
+        ok = (local >= 0) & (local < vl)
+        tgt = logits.gather(-1, local.clamp(0, vl - 1)[:, None]).squeeze(-1) * ok
+        comm.all_reduce(tgt)
+        lse = m + torch.log(s)
+        ctx.save_for_backward(hidden, weight, ex / s[:, None], local, ok)
+        ctx.comm, ctx.temperature = comm, temperature
+        return tgt - lse
+
+    @staticmethod
+    def backward(ctx, g):
+        hidden, weight, p, local, ok = ctx.saved_tensors
+        d = -p * g[:, None]
+        idx = local.clamp(0, weight.shape[0] - 1)
+        d.scatter_add_(-1, idx[:, None], (g * ok)[:, None])
+        d = (d / ctx.temperature).to(hidden.dtype)
+        gh = ops.gemm(d, weight, 'nn') if hidden.is_cuda and hidden.dtype == torch.bfloat16 else (d.float() @ weight.float()).to(hidden.dtype)
+        gh = gh.contiguous()  # partial over this rank's vocabulary shard; the caller's gather / copy op sums the shards
+        gw = ops.gemm(d, hidden, 'tn') if hidden.is_cuda and hidden.dtype == torch.bfloat16 else (d.float().t() @ hidden.float()).to(weight.dtype)
+        return gh, gw, None, None, None
+
+
+def vocab_parallel_logprob(hidden, weight, labels, tp: TPContext, temperature: float = 1.0):
+    return _VocabParallelLogprob.apply(hidden, weight, labels.clamp_min(0), tp.comm, temperature)
+
+
+def apply_tensor_parallel(model, cfg, comm: Communicator, sequence_parallel: bool) -> Optional[TPContext]:
+    """Replace every parallelisable weight by this rank's shard (cut from the identically initialised full
+    tensor) and switch the modules to their TP forward."""
+    if comm.world_size <= 1:
+        return None
+    tp = TPContext(comm, sequence_parallel)
+    assert cfg.num_key_value_heads % tp.size == 0 and cfg.num_attention_heads % tp.size == 0, 'heads must divide over tp'
+    names = dict(model.named_parameters())
+    with torch.no_grad():
+        for name, p in list(names.items()):
+            # internal names are relative to the chunk; layer indices are global already
+            shard = tp_shard(name, p.data, cfg, tp.rank, tp.size)
+            if shard.shape != p.shape:
+                p.data = shard.contiguous().clone()
+    for layer in model.layers:
+        at = layer.self_attn
+        at.hq, at.hkv = cfg.num_attention_heads // tp.size, cfg.num_key_value_heads // tp.size
+        for lin, mode in ((at.qkv_proj, 'col'), (at.o_proj, 'row')):
+            lin.tp, lin.tp_mode = tp, mode
+        if not layer.is_moe:
+            layer.mlp.gate_up_proj.tp, layer.mlp.gate_up_proj.tp_mode = tp, 'col'
+            layer.mlp.down_proj.tp, layer.mlp.down_proj.tp_mode = tp, 'row'
+    model.tp = tp
+    return tp

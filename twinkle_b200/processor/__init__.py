@@ -149,7 +149,7 @@ class InputProcessor:
         mbs = self.micro_batch_size or len(items)
         return [items[i:i + mbs] for i in range(0, len(items), mbs)]
 
-    def _pack(self, items: List[Dict[str, torch.Tensor]]) -> MicroBatch:
+    def _pack(self, items: List[Dict[str, torch.Tensor]], pad_multiple: Optional[int] = None, split: bool = True) -> MicroBatch:
         """Concatenate sequences.  With context parallelism each sequence is
         padded to a multiple of 2·cp (zig-zag halves); with Ulysses the whole
         row is padded to a multiple of sp and each rank keeps one contiguous
@@ -172,7 +172,7 @@ class InputProcessor:
         # the whole row must divide evenly among the sequence-parallel ranks:
         # extend the last sequence with ignored tokens
         total = sum(lens)
-        tail = (-total) % max(self.sp_size, 1)
+        tail = (-total) % max(pad_multiple if pad_multiple is not None else self.sp_size, 1)
         if tail and ids:
             last = int(poss[-1][-1]) if poss[-1].numel() else -1
             ids[-1] = torch.cat([ids[-1], torch.full((tail, ), self.pad_token_id, dtype=torch.long)])
@@ -188,7 +188,7 @@ class InputProcessor:
         if any('routed_experts' in it for it in items):
             extras['routed_experts'] = [it.get('routed_experts') for it in items]
         mb.extras = extras or None
-        return self._split_parallel(mb)
+        return self._split_parallel(mb) if split else mb
 
     def _split_parallel(self, mb: MicroBatch) -> MicroBatch:
         """Keep this rank's share of every sequence: contiguous slices for
