@@ -28,7 +28,7 @@ constexpr int OUTER_ATOM = BT * 64 * 2;       // 16 KiB
 constexpr int INNER_BYTES = BI * D * 2;       // 16 KiB (two [64][64] atoms)
 constexpr int INNER_ATOM = BI * 64 * 2;       // 8 KiB
 constexpr int PT_BYTES = BT * BI * 2;         // 16 KiB ([128][64] atom)
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;  // warps 0-7 compute (two groups of 4, each takes half of the inner-block columns), 8 producer, 9 MMA
 // dkdv: K, V (outer) | Q×2, dO×2 (inner) | Pᵀ, dSᵀ | lse/delta staging | barriers
 constexpr int KV_SMEM_K = 0, KV_SMEM_V = OUTER_BYTES, KV_SMEM_Q = 2 * OUTER_BYTES, KV_SMEM_DO = KV_SMEM_Q + 2 * INNER_BYTES,
               KV_SMEM_PT = KV_SMEM_DO + 2 * INNER_BYTES, KV_SMEM_DST = KV_SMEM_PT + PT_BYTES, KV_SMEM_STAT = KV_SMEM_DST + PT_BYTES,
@@ -102,13 +102,13 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       mbar_init(&qdo_full[i], 1);
       mbar_init(&qdo_empty[i], 1);
       mbar_init(&sd_full[i], 1);
-      mbar_init(&sd_empty[i], 128);
+      mbar_init(&sd_empty[i], 256);
     }
-    mbar_init(pds_ready, 128);
+    mbar_init(pds_ready, 256);
     mbar_init(acc_done, 1);
     fence_barrier_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -119,7 +119,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   // TMEM columns: Sᵀ buffers [0,64) [64,128); dPᵀ buffers [128,192) [192,256); dV [256,384); dK [384,512)
   const uint32_t t_dv = tmem_base + 256, t_dk = tmem_base + 384;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // producer warp: lane 0 drives TMA; all lanes stage lse (log2 units) and δ of each query block in smem
     if (lane == 0) {
       mbar_expect_tx(kv_full, 2 * OUTER_BYTES);
@@ -159,7 +159,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         tma_load_3d(smem + KV_SMEM_DO + st * INNER_BYTES + INNER_ATOM, &tmDO, &qdo_full[st], 64, head, row);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(BT, BI, false, false);   // [128 kv] x [64 q], K = d
       constexpr uint32_t idesc_acc = umma_idesc_bf16(BT, D, false, true);   // [128 kv] x [128 d], K = q (B MN-major)
@@ -209,8 +209,9 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       }
     }
   } else {
-    const int row = warp * 32 + lane;
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    const int wg = warp >> 2;                       // which half of the 64 inner-block columns this thread handles
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int kv_pos = kv0 + row;
     const bool row_valid = kv_pos < seq_len;
     bool ok = true;
@@ -219,12 +220,10 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       const int qb0 = (qb_begin + it % per_head) * BI;
       if (!mbar_wait(&sd_full[st], (it >> 1) & 1, p.err, ERR_ATTN_WAIT)) { ok = false; break; }
       tc_fence_after();
-      // Pᵀ / dSᵀ smem is free once the accumulating MMAs of the previous iteration retired
-      if (it > 0 && !mbar_wait(acc_done, (it - 1) & 1, p.err, ERR_ATTN_WAIT)) { ok = false; break; }
       const float* lse2 = stat + st * 2 * BI;
       const float* dl = lse2 + BI;
-#pragma unroll 1
-      for (int c = 0; c < BI / 32; ++c) {
+      {
+        const int c = wg;
         uint32_t s[32], dp[32];
         tmem_ld32(tmem_base + st * 64 + c * 32 + lane_off, s);
         tmem_ld32(tmem_base + 128 + st * 64 + c * 32 + lane_off, dp);
@@ -245,11 +244,14 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           pk[i >> 1] = pack_bf16(pv[0], pv[1]);
           dsk[i >> 1] = pack_bf16(dv[0], dv[1]);
         }
+        // S/dP are in registers: the TMEM buffers can be refilled while we finish
+        tc_fence_before();
+        mbar_arrive(&sd_empty[st]);
+        // Pᵀ / dSᵀ smem is free once the accumulating MMAs of the previous iteration retired
+        if (it > 0 && !mbar_wait(acc_done, (it - 1) & 1, p.err, ERR_ATTN_WAIT)) { ok = false; break; }
         store_row_chunk_sw128(smem + KV_SMEM_PT, 128, row, c * 32, pk);
         store_row_chunk_sw128(smem + KV_SMEM_DST, 128, row, c * 32, dsk);
       }
-      tc_fence_before();
-      mbar_arrive(&sd_empty[st]);
       fence_proxy_async();
       mbar_arrive(pds_ready);
     }
@@ -258,7 +260,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       bf16* dkrow = p.dk + (static_cast<size_t>(seq_start + kv_pos) * p.hkv + kv_head) * D;
       bf16* dvrow = p.dv + (static_cast<size_t>(seq_start + kv_pos) * p.hkv + kv_head) * D;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 2 * wg; c < 2 * wg + 2; ++c) {
         uint32_t a[32], b[32];
         tmem_ld32(t_dv + lane_off + c * 32, a);
         tmem_ld32(t_dk + lane_off + c * 32, b);
@@ -281,7 +283,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       // no query attends to this tile (cannot happen with causal self-attention, kept for safety)
       bf16* dkrow = p.dk + (static_cast<size_t>(seq_start + kv_pos) * p.hkv + kv_head) * D;
       bf16* dvrow = p.dv + (static_cast<size_t>(seq_start + kv_pos) * p.hkv + kv_head) * D;
-      for (int i = 0; i < D; i += 8) {
+      for (int i = wg * 64; i < wg * 64 + 64; i += 8) {
         *reinterpret_cast<uint4*>(dkrow + i) = make_uint4(0, 0, 0, 0);
         *reinterpret_cast<uint4*>(dvrow + i) = make_uint4(0, 0, 0, 0);
       }
@@ -289,7 +291,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
@@ -328,13 +330,13 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
       mbar_init(&sd_full[i], 1);
-      mbar_init(&sd_empty[i], 128);
+      mbar_init(&sd_empty[i], 256);
     }
-    mbar_init(ds_ready, 128);
+    mbar_init(ds_ready, 256);
     mbar_init(acc_done, 1);
     fence_barrier_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -345,7 +347,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   // TMEM columns: S buffers [0,64) [64,128); dP buffers [128,192) [192,256); dQ [256,384)
   const uint32_t t_dq = tmem_base + 256;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0) {
       mbar_expect_tx(qdo_full, 2 * OUTER_BYTES);
       tma_load_3d(smem + DQ_SMEM_Q, &tmQ, qdo_full, 0, head, seq_start + q0);
@@ -363,7 +365,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tma_load_3d(smem + DQ_SMEM_V + st * INNER_BYTES + INNER_ATOM, &tmV, &kv_full[st], 64, kv_head, row);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(BT, BI, false, false);   // [128 q] x [64 kv], K = d
       constexpr uint32_t idesc_acc = umma_idesc_bf16(BT, D, false, true);   // [128 q] x [128 d], K = kv (B MN-major)
@@ -408,8 +410,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
     }
   } else {
-    const int row = warp * 32 + lane;
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    const int wg = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int q_pos = q0 + row;
     const bool row_valid = q_pos < seq_len;
     float lse2 = INFINITY, dl = 0.f;
@@ -423,10 +426,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const int st = it & 1;
       if (!mbar_wait(&sd_full[st], (it >> 1) & 1, p.err, ERR_ATTN_WAIT)) { ok = false; break; }
       tc_fence_after();
-      if (it > 0 && !mbar_wait(acc_done, (it - 1) & 1, p.err, ERR_ATTN_WAIT)) { ok = false; break; }
       const int kvb = it * BI;
-#pragma unroll 1
-      for (int c = 0; c < BI / 32; ++c) {
+      {
+        const int c = wg;
         uint32_t s[32], dp[32];
         tmem_ld32(tmem_base + st * 64 + c * 32 + lane_off, s);
         tmem_ld32(tmem_base + 128 + st * 64 + c * 32 + lane_off, dp);
@@ -444,10 +446,11 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
           dsk[i >> 1] = pack_bf16(dv[0], dv[1]);
         }
+        tc_fence_before();
+        mbar_arrive(&sd_empty[st]);
+        if (it > 0 && !mbar_wait(acc_done, (it - 1) & 1, p.err, ERR_ATTN_WAIT)) { ok = false; break; }
         store_row_chunk_sw128(smem + DQ_SMEM_DS, 128, row, c * 32, dsk);
       }
-      tc_fence_before();
-      mbar_arrive(&sd_empty[st]);
       fence_proxy_async();
       mbar_arrive(ds_ready);
     }
@@ -455,7 +458,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc_fence_after();
       bf16* dqrow = p.dq + (static_cast<size_t>(seq_start + q_pos) * p.hq + head) * D;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 2 * wg; c < 2 * wg + 2; ++c) {
         uint32_t a[32];
         tmem_ld32(t_dq + lane_off + c * 32, a);
         tmem_ld_wait();
@@ -473,7 +476,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }

@@ -24,8 +24,9 @@ constexpr int BQ = 128, BKV = 128, D = 128;
 constexpr int TILE_BYTES = 128 * 128 * 2;  // 32 KiB, two [128][64] swizzle atoms
 constexpr int ATOM_BYTES = 128 * 64 * 2;   // 16 KiB
 constexpr int SMEM_Q = 0, SMEM_K = TILE_BYTES, SMEM_V = 3 * TILE_BYTES, SMEM_P = 5 * TILE_BYTES, SMEM_BAR = 6 * TILE_BYTES;
-constexpr int SMEM_TOTAL = SMEM_BAR + 256 + 1024;
-constexpr int THREADS = 192;
+constexpr int SMEM_XCHG = SMEM_BAR + 256;           // row max (2 parities x 2 halves x 128) + row sums (2 x 128) floats
+constexpr int SMEM_TOTAL = SMEM_XCHG + 6 * 128 * 4 + 1024;
+constexpr int THREADS = 320;  // warps 0-7 softmax (two groups of 4: each owns 64 of the 128 S columns), 8 producer, 9 MMA
 constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
 }  // namespace fa
 
@@ -75,13 +76,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(&v_full[i], 1);
       mbar_init(&kv_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 128);
+      mbar_init(&s_empty[i], 256);
     }
-    mbar_init(p_ready, 128);
+    mbar_init(p_ready, 256);
     mbar_init(o_done, 1);
     fence_barrier_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -91,7 +92,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   const uint32_t tmem_o = tmem_base + 256;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------- producer
     if (lane == 0) {
       tma_prefetch_desc(&tmQ);
@@ -112,7 +113,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tma_load_3d(smem + SMEM_V + st * TILE_BYTES + ATOM_BYTES, &tmV, &v_full[st], 64, kv_head, row);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ----------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(BQ, BKV, false, false);
@@ -158,34 +159,47 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else {
     // -------------------------------------------------------------- softmax
-    const int row = warp * 32 + lane;                // row inside the tile == TMEM lane
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    // Thread = (query row, half of the 128 key columns).  The 64 scores of its half stay in registers from the
+    // max pass to the exp pass (one TMEM read per block); the two halves of a row agree on the row maximum
+    // through shared memory + one named barrier per block.  A thread whose wait failed keeps taking part in the
+    // barriers (doing no work) so that no thread is ever left waiting at one.
+    const int wg = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;          // row inside the tile == TMEM lane
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int q_pos = q0 + row;                      // position inside the sequence
+    float* xmax = reinterpret_cast<float*>(smem + SMEM_XCHG);   // [parity][half][128]
+    float* xsum = xmax + 4 * 128;                                 // [half][128]
     float m_used = -INFINITY, l_sum = 0.f;
-    bool ok = true;
+    bool dead = false;
     for (int j = 0; j < n_blocks; ++j) {
-      if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, p.err, ERR_ATTN_WAIT)) { ok = false; break; }
-      tc_fence_after();
-      const uint32_t ts = tmem_base + (j & 1) * 128 + lane_off;
-      const int kv0 = j * BKV;
-      const bool need_mask = (kv0 + BKV > kv_end) || (p.causal && kv0 + BKV > q0);
-      // pass 1: row maximum of the scaled, masked scores
+      if (!dead && !mbar_wait(&s_full[j & 1], (j >> 1) & 1, p.err, ERR_ATTN_WAIT)) dead = true;
+      const int kv0 = j * BKV + wg * 64;
+      float sc[64];
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(ts + c * 32, r);
+      if (!dead) {
+        tc_fence_after();
+        const uint32_t ts = tmem_base + (j & 1) * 128 + wg * 64 + lane_off;
+        uint32_t r0[32], r1[32];
+        tmem_ld32(ts, r0);
+        tmem_ld32(ts + 32, r1);
         tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(&s_empty[j & 1]);                 // scores are in registers: the TMEM buffer may be refilled
+        const bool need_mask = (kv0 + 64 > kv_end) || (p.causal && kv0 + 64 > q0);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(r[i]) * p.scale_log2;
+        for (int i = 0; i < 64; ++i) {
+          float sv = __uint_as_float(i < 32 ? r0[i] : r1[i - 32]) * p.scale_log2;
           if (need_mask) {
-            const int col = kv0 + c * 32 + i;
-            if (col >= kv_end || (p.causal && col > q_pos)) s = -INFINITY;
+            const int col = kv0 + i;
+            if (col >= kv_end || (p.causal && col > q_pos)) sv = -INFINITY;
           }
-          mx = fmaxf(mx, s);
+          sc[i] = sv;
+          mx = fmaxf(mx, sv);
         }
       }
+      xmax[((j & 1) * 2 + wg) * 128 + row] = mx;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      mx = fmaxf(mx, xmax[((j & 1) * 2 + (wg ^ 1)) * 128 + row]);
       float alpha = 1.f;
       bool rescale = false;
       if (mx > m_used + RESCALE_THRESHOLD || m_used == -INFINITY) {
@@ -196,56 +210,49 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         l_sum *= alpha;
       }
       // P buffer and O accumulator are free once the previous P·V has retired
-      if (j > 0 && !mbar_wait(o_done, (j - 1) & 1, p.err, ERR_ATTN_WAIT)) { ok = false; break; }
+      if (!dead && j > 0 && !mbar_wait(o_done, (j - 1) & 1, p.err, ERR_ATTN_WAIT)) dead = true;
+      if (dead) continue;
       tc_fence_after();
       if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t r[32];
-          tmem_ld32(tmem_o + lane_off + c * 32, r);
+          tmem_ld32(tmem_o + lane_off + wg * 64 + c * 32, r);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st32(tmem_o + lane_off + c * 32, r);
+          tmem_st32(tmem_o + lane_off + wg * 64 + c * 32, r);
         }
         tmem_st_wait();
       }
-      // pass 2: probabilities → bf16 → swizzled smem, row sum
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(ts + c * 32, r);
-        tmem_ld_wait();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float s0 = __uint_as_float(r[i]) * p.scale_log2, s1 = __uint_as_float(r[i + 1]) * p.scale_log2;
-          if (need_mask) {
-            const int col = kv0 + c * 32 + i;
-            if (col >= kv_end || (p.causal && col > q_pos)) s0 = -INFINITY;
-            if (col + 1 >= kv_end || (p.causal && col + 1 > q_pos)) s1 = -INFINITY;
-          }
-          const float p0 = exp2f(s0 - m_used), p1 = exp2f(s1 - m_used);
+          const float p0 = exp2f(sc[c * 32 + i] - m_used), p1 = exp2f(sc[c * 32 + i + 1] - m_used);
           // the sum uses the bf16-rounded values so that numerator and denominator match
           const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
           l_sum += __low2float(pb) + __high2float(pb);
           packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
         }
-        store_row_chunk_sw128(smem + SMEM_P, 128, row, c * 32, packed);
+        store_row_chunk_sw128(smem + SMEM_P, 128, row, wg * 64 + c * 32, packed);
       }
       tc_fence_before();
-      mbar_arrive(&s_empty[j & 1]);
       fence_proxy_async();
       mbar_arrive(p_ready);
     }
     // ------------------------------------------------------------- epilogue
-    if (ok && n_blocks > 0 && mbar_wait(o_done, (n_blocks - 1) & 1, p.err, ERR_ATTN_WAIT)) {
+    xsum[wg * 128 + row] = l_sum;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    l_sum += xsum[(wg ^ 1) * 128 + row];
+    if (!dead && n_blocks > 0 && mbar_wait(o_done, (n_blocks - 1) & 1, p.err, ERR_ATTN_WAIT)) {
       tc_fence_after();
       const float inv_l = (l_sum > 0.f) ? 1.f / l_sum : 0.f;
       const bool valid = q_pos < seq_len;
       bf16* orow = p.out + (static_cast<size_t>(seq_start + q_pos) * p.hq + head) * D;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 2 * wg; c < 2 * wg + 2; ++c) {
         uint32_t r[32];
         tmem_ld32(tmem_o + lane_off + c * 32, r);
         tmem_ld_wait();
@@ -260,12 +267,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
       }
-      if (valid) p.lse[static_cast<size_t>(head) * p.T + seq_start + q_pos] = (m_used + log2f(l_sum)) * 0.6931471805599453f;
+      if (valid && wg == 0) p.lse[static_cast<size_t>(head) * p.T + seq_start + q_pos] = (m_used + log2f(l_sum)) * 0.6931471805599453f;
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
