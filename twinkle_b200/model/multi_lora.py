@@ -134,17 +134,17 @@ class MultiLora:
 
     def batch_for_segments(self, segments: List[Tuple[Optional[str], int]], device) -> LoraBatch:
         """Several tenants in one packed row: ``segments`` = (tenant|None, n_tokens) in order."""
-        starts, slots, ranks, scales, targets = [0], [], [], [], []
+        segs, targets, lo = [], [], 0
         for name, n in segments:
-            starts.append(starts[-1] + n)
             if name is None:
-                slots.append(-1), ranks.append(0), scales.append(0.0), targets.append(None)
+                segs.append((lo, lo + n, -1, 0, 0.0))
+                targets.append(None)
             else:
                 t = self.tenants[name]
-                slots.append(t.slot), ranks.append(t.config.r), scales.append(t.config.scaling), targets.append(t.target)
-        return LoraBatch(torch.tensor(starts, dtype=torch.int32, device=device), torch.tensor(slots, dtype=torch.int32, device=device),
-                         torch.tensor(ranks, dtype=torch.int32, device=device),
-                         torch.tensor(scales, dtype=torch.float32, device=device), targets)
+                segs.append((lo, lo + n, t.slot, t.config.r, t.config.scaling))
+                targets.append(t.target)
+            lo += n
+        return LoraBatch(segs, device, targets)
 
     # ------------------------------------------------ per-tenant parameters
     def tenant_slices(self, tenant: str) -> List[Tuple[str, torch.nn.Parameter, int]]:

@@ -164,15 +164,7 @@ class MoEBlock(nn.Module):
         self.record_routing = False
 
     def route(self, x: torch.Tensor, forced: Optional[torch.Tensor]):
-        logits = self.gate(x)
-        probs = torch.softmax(logits.float(), -1)
-        if forced is not None:
-            idx = forced.to(probs.device).long()
-            w = probs.gather(-1, idx)
-        else:
-            w, idx = probs.topk(self.cfg.num_experts_per_tok, -1)
-        if self.cfg.norm_topk_prob:
-            w = w / w.sum(-1, keepdim=True)
+        w, idx, probs, _hist = ops.moe_router(self.gate(x), self.cfg.num_experts_per_tok, self.cfg.norm_topk_prob, forced)
         return w, idx, probs
 
     def forward(self, x: torch.Tensor, forced: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -15,7 +15,6 @@ from __future__ import annotations
 import math
 import re
 from contextlib import contextmanager
-from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -24,22 +23,41 @@ import torch.nn as nn
 from .. import ops
 
 
-@dataclass
 class LoraBatch:
-    """Per-forward LoRA routing: segment ``i`` covers token rows
-    ``seg_starts[i]:seg_starts[i+1]`` and uses ``seg_slots[i]`` (−1 = base only)."""
-    seg_starts: torch.Tensor  # int32 [n+1]
-    seg_slots: torch.Tensor  # int32 [n]
-    seg_ranks: torch.Tensor  # int32 [n]
-    seg_scales: torch.Tensor  # fp32 [n]
-    targets: List[Optional[object]] = field(default_factory=list)  # per segment: compiled target filter
+    """Per-forward LoRA routing: segment ``i`` covers token rows ``lo:hi`` and uses adapter slot ``slot``
+    (−1 = base only) at rank ``rank`` with scale ``scale``.  Segments are kept on the host (they are built
+    from Python integers) so that no kernel launch needs a device→host read; device copies are cached."""
+
+    def __init__(self, segments, device, targets=None):
+        self.host = [(int(lo), int(hi), int(slot), int(rank), float(scale)) for lo, hi, slot, rank, scale in segments]
+        self.device = device
+        self.targets: List[Optional[object]] = list(targets) if targets is not None else [None] * len(self.host)
+        self._cache: Dict[tuple, tuple] = {}
+
+    def tensors(self, keep: Optional[tuple] = None):
+        """(seg_starts int32 [n+1], seg_slots int32 [n], seg_ranks int32 [n], seg_scales fp32 [n], host list) with
+        the slots of segments where ``keep[i]`` is False forced to −1."""
+        key = keep if keep is not None else ()
+        hit = self._cache.get(key)
+        if hit is None:
+            host = [(lo, hi, (s if (keep is None or keep[i]) else -1), r, c) for i, (lo, hi, s, r, c) in enumerate(self.host)]
+            dev = self.device
+            hit = (torch.tensor([h[0] for h in host] + [host[-1][1] if host else 0], dtype=torch.int32, device=dev),
+                   torch.tensor([h[2] for h in host], dtype=torch.int32, device=dev),
+                   torch.tensor([h[3] for h in host], dtype=torch.int32, device=dev),
+                   torch.tensor([h[4] for h in host], dtype=torch.float32, device=dev), host)
+            self._cache[key] = hit
+        return hit
+
+    # tensor views of the unfiltered routing (used by code that inspects the batch)
+    seg_starts = property(lambda self: self.tensors()[0])
+    seg_slots = property(lambda self: self.tensors()[1])
+    seg_ranks = property(lambda self: self.tensors()[2])
+    seg_scales = property(lambda self: self.tensors()[3])
 
     @staticmethod
     def single(num_tokens: int, slot: int, rank: int, scale: float, device, target=None) -> 'LoraBatch':
-        return LoraBatch(torch.tensor([0, num_tokens], dtype=torch.int32, device=device),
-                         torch.tensor([slot], dtype=torch.int32, device=device),
-                         torch.tensor([rank], dtype=torch.int32, device=device),
-                         torch.tensor([scale], dtype=torch.float32, device=device), [target])
+        return LoraBatch([(0, num_tokens, slot, rank, scale)], device, [target])
 
 
 class _LoraContext:
@@ -125,16 +143,16 @@ class Linear(nn.Module):
         prefix = self.full_name.rsplit('.', 1)[0] if '.' in self.full_name else ''
         outs: List[Optional[torch.Tensor]] = []
         for pname, n in self.parts:
-            slots = lb.seg_slots
-            if lb.targets and any(t is not None for t in lb.targets):
-                keep = [t is None or t.matches(f'{prefix}.{pname}' if prefix else pname, pname) for t in lb.targets]
+            keep = None
+            if any(t is not None for t in lb.targets):
+                keep = tuple(t is None or t.matches(f'{prefix}.{pname}' if prefix else pname, pname) for t in lb.targets)
                 if not any(keep):
                     outs.append(None)
                     continue
-                if not all(keep):
-                    slots = torch.where(torch.tensor(keep, device=slots.device), slots, torch.full_like(slots, -1))
-            outs.append(ops.sgmv(x2, self.lora_A[pname], self.lora_B[pname], lb.seg_starts, slots, lb.seg_ranks,
-                                 lb.seg_scales))
+                if all(keep):
+                    keep = None
+            st, sl, rk, sc, host = lb.tensors(keep)
+            outs.append(ops.sgmv(x2, self.lora_A[pname], self.lora_B[pname], st, sl, rk, sc, host))
         if all(o is None for o in outs):
             return None
         outs = [o if o is not None else x2.new_zeros(x2.shape[0], n) for o, (_, n) in zip(outs, self.parts)]

@@ -386,27 +386,70 @@ def sumsq(t: torch.Tensor) -> torch.Tensor:
 
 # -------------------------------------------------------------------- lora
 class _SGMV(torch.autograd.Function):
+    """Segmented multi-LoRA on the tensor cores: shrink and expand are two expert-grouped tcgen05 GEMMs in
+    which a *segment of tokens* plays the role of an expert and ``seg_slots`` maps it to its adapter block
+    (−1 = no adapter → rows stay zero).  The rank mask (``r`` ≤ pool rank) and the ``alpha/r`` scale are one
+    small element-wise pass over the ``[T, R]`` intermediate.  Weight gradients are per-segment ``tn`` GEMMs
+    over 64-row-aligned token windows whose rows outside the segment are zeroed."""
 
     @staticmethod
-    def forward(ctx, x, lora_a, lora_b, seg_starts, seg_slots, seg_ranks, seg_scales):
-        h = ext().sgmv_shrink(x, lora_a, seg_starts, seg_slots, seg_ranks)  # [T, R] fp32→bf16
-        y = ext().sgmv_expand(h, lora_b, seg_starts, seg_slots, seg_ranks, seg_scales)
-        ctx.save_for_backward(x, lora_a, lora_b, h, seg_starts, seg_slots, seg_ranks, seg_scales)
+    def forward(ctx, x, lora_a, lora_b, seg_starts, seg_slots, seg_ranks, seg_scales, host_segments):
+        E = ext()
+        R = lora_a.shape[1]
+        rowmask = _sgmv_rowmask(host_segments, R, x.device, x.dtype)           # [T, R] = scale where col < rank else 0
+        h = E.grouped_gemm(x, lora_a, seg_starts, 'nt', seg_slots)             # [T, R]
+        hm = h * rowmask
+        y = E.grouped_gemm(hm, lora_b, seg_starts, 'nt', seg_slots)            # [T, N]
+        ctx.save_for_backward(x, lora_a, lora_b, hm, rowmask, seg_starts, seg_slots)
+        ctx.host_segments = host_segments
         return y
 
     @staticmethod
     def backward(ctx, gy):
-        x, a, b, h, st, sl, rk, sc = ctx.saved_tensors
+        E = ext()
+        x, a, b, hm, rowmask, st, sl = ctx.saved_tensors
         gy = gy.contiguous()
-        gx, ga, gb = ext().sgmv_bwd(gy, x, a, b, h, st, sl, rk, sc, ctx.needs_input_grad[0])
-        return gx, ga.to(a.dtype), gb.to(b.dtype), None, None, None, None
+        ghm = E.grouped_gemm(gy, b, st, 'nn', sl)                               # [T, R]   (b[s] is [N, R] = [K, N_out])
+        gh = ghm * rowmask
+        gx = E.grouped_gemm(gh, a, st, 'nn', sl) if ctx.needs_input_grad[0] else None
+        ga = torch.zeros_like(a, dtype=torch.float32)
+        gb = torch.zeros_like(b, dtype=torch.float32)
+        T = x.shape[0]
+        for (lo, hi, slot, rank, scale) in ctx.host_segments:
+            if slot < 0 or rank == 0 or hi <= lo:
+                continue
+            a0, b0 = lo // 64 * 64, min((hi + 63) // 64 * 64, T)
+            ghs, hms = gh[a0:b0].clone(), hm[a0:b0].clone()
+            ghs[:lo - a0].zero_(), ghs[hi - a0:].zero_()
+            hms[:lo - a0].zero_(), hms[hi - a0:].zero_()
+            E.gemm(ghs, x[a0:b0], 'tn', ga[slot], True, None)                   # dA[slot] += ghᵀ x
+            E.gemm(gy[a0:b0], hms, 'tn', gb[slot], True, None)                  # dB[slot] += gyᵀ h
+        return gx, ga.to(a.dtype), gb.to(b.dtype), None, None, None, None, None
 
 
-def sgmv(x, lora_a, lora_b, seg_starts, seg_slots, seg_ranks, seg_scales):
-    """Multi-tenant LoRA delta for a token-segmented batch (see ``reference.sgmv``)."""
+def _sgmv_rowmask(host_segments, R: int, device, dtype) -> torch.Tensor:
+    rows = []
+    col = torch.arange(R, device=device)
+    for (lo, hi, slot, rank, scale) in host_segments:
+        m = (col < rank).to(dtype) * (scale if slot >= 0 else 0.0)
+        rows.append(m.unsqueeze(0).expand(hi - lo, R))
+    return torch.cat(rows, 0) if rows else torch.zeros(0, R, device=device, dtype=dtype)
+
+
+def sgmv(x, lora_a, lora_b, seg_starts, seg_slots, seg_ranks, seg_scales, host_segments=None):
+    """Multi-tenant LoRA delta for a token-segmented batch (see ``reference.sgmv``).  ``host_segments`` =
+    ``[(lo, hi, slot, rank, scale)]`` mirrors the device tensors so the CUDA path needs no device read."""
     if _cuda(x) and x.dtype == torch.bfloat16:
-        return _SGMV.apply(x, lora_a, lora_b, seg_starts.to(torch.int32), seg_slots.to(torch.int32),
-                           seg_ranks.to(torch.int32), seg_scales.float())
+        if host_segments is None:
+            starts = seg_starts.tolist()
+            host_segments = [(starts[i], starts[i + 1], int(s), int(r), float(c)) for i, (s, r, c) in enumerate(
+                zip(seg_slots.tolist(), seg_ranks.tolist(), seg_scales.tolist()))]
+        T = x.shape[0]
+        if any(hi > T for (_, hi, _, _, _) in host_segments):  # an open-ended segment ("all remaining tokens")
+            host_segments = [(lo, min(hi, T), s, r, c) for (lo, hi, s, r, c) in host_segments if lo < T]
+            seg_starts = torch.tensor([h[0] for h in host_segments] + [host_segments[-1][1]], dtype=torch.int32, device=x.device)
+            seg_slots = torch.tensor([h[2] for h in host_segments], dtype=torch.int32, device=x.device)
+        return _SGMV.apply(x.contiguous(), lora_a, lora_b, seg_starts, seg_slots, seg_ranks, seg_scales, host_segments)
     return _sgmv_autograd_cpu(x, lora_a, lora_b, seg_starts, seg_slots, seg_ranks, seg_scales)
 
 
@@ -424,11 +467,51 @@ def _sgmv_autograd_cpu(x, lora_a, lora_b, seg_starts, seg_slots, seg_ranks, seg_
 
 
 # --------------------------------------------------------------------- moe
-def moe_router(logits, top_k: int, renormalize: bool = True):
-    """(weights [T,k] fp32, indices [T,k] int64, probs [T,E] fp32); differentiable
-    through ``weights``/``probs`` on the PyTorch path; the CUDA kernel also returns
-    the per-expert histogram used by dispatch."""
-    return ref.moe_router(logits, top_k, renormalize)
+class _Router(torch.autograd.Function):
+    """Fused fp32 softmax + top-k + renormalisation + expert histogram.  Backward is the closed form on the
+    ``[T, E]`` probabilities (a few element-wise passes over a small tensor)."""
+
+    @staticmethod
+    def forward(ctx, logits, top_k, renorm, forced):
+        w, idx, probs, hist = ext().moe_router(logits.contiguous(), top_k, renorm)
+        if forced is not None:  # router replay: keep the probabilities, take the given experts
+            idx = forced.to(idx.device).long()
+            w = probs.gather(-1, idx)
+            if renorm:
+                w = w / w.sum(-1, keepdim=True)
+        ctx.save_for_backward(probs, idx, w)
+        ctx.renorm = renorm
+        ctx.mark_non_differentiable(idx, hist)
+        return w, idx, probs, hist
+
+    @staticmethod
+    def backward(ctx, gw, _gidx, gprobs, _ghist):
+        probs, idx, w = ctx.saved_tensors
+        dp = gprobs.clone() if gprobs is not None else torch.zeros_like(probs)
+        if gw is not None:
+            if ctx.renorm:
+                S = probs.gather(-1, idx).sum(-1, keepdim=True)
+                g_sel = (gw - (gw * w).sum(-1, keepdim=True)) / S
+            else:
+                g_sel = gw
+            dp.scatter_add_(-1, idx, g_sel)
+        dlogits = probs * (dp - (probs * dp).sum(-1, keepdim=True))
+        return dlogits, None, None, None
+
+
+def moe_router(logits, top_k: int, renormalize: bool = True, forced=None):
+    """(weights [T,k] fp32, indices [T,k] int64, probs [T,E] fp32, histogram [E] | None)."""
+    if _cuda(logits):
+        return _Router.apply(logits, top_k, renormalize, forced)
+    probs = torch.softmax(logits.float(), -1)
+    if forced is not None:
+        idx = forced.long()
+        w = probs.gather(-1, idx)
+    else:
+        w, idx = probs.topk(top_k, -1)
+    if renormalize:
+        w = w / w.sum(-1, keepdim=True)
+    return w, idx, probs, None
 
 
 class _GroupedGemm(torch.autograd.Function):
@@ -436,13 +519,13 @@ class _GroupedGemm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, offsets):
         ctx.save_for_backward(x, weight, offsets)
-        return ext().grouped_gemm(x, weight, offsets, 'nt')
+        return ext().grouped_gemm(x, weight, offsets, 'nt', None)
 
     @staticmethod
     def backward(ctx, gy):
         x, weight, offsets = ctx.saved_tensors
         gy = gy.contiguous()
-        gx = ext().grouped_gemm(gy, weight, offsets, 'nn') if ctx.needs_input_grad[0] else None
+        gx = ext().grouped_gemm(gy, weight, offsets, 'nn', None) if ctx.needs_input_grad[0] else None
         gw = ext().grouped_gemm_wgrad(gy, x, offsets, weight.shape[0]).to(weight.dtype) if ctx.needs_input_grad[1] else None
         return gx, gw, None
 
@@ -459,8 +542,13 @@ def grouped_gemm(x, weight, offsets):
 
 
 def sample_tokens(logits, temperature=1.0, top_k=-1, top_p=1.0, generator=None, seeds=None):
-    if _cuda(logits) and seeds is not None:
-        return ext().sample_tokens(logits.contiguous(), float(temperature), int(top_k), float(top_p), seeds)
+    """(tokens [B], logprob of each under the processed distribution [B]).  On CUDA every row draws from its
+    own counter-based stream keyed by ``seeds[row]`` (fresh seeds when none are given)."""
+    if _cuda(logits):
+        if seeds is None:
+            seeds = torch.randint(0, 2**62, (logits.shape[0], ), device=logits.device, dtype=torch.int64, generator=generator)
+        tok, lp = ext().sample_tokens(logits.float().contiguous(), float(temperature), int(top_k), float(top_p), seeds)
+        return tok, lp
     return ref.sample_tokens(logits, temperature, top_k, top_p, generator)
 
 

@@ -6,7 +6,7 @@
 namespace tk {
 torch::Tensor gemm(const torch::Tensor&, const torch::Tensor&, const std::string&, const c10::optional<torch::Tensor>&, bool,
                    c10::optional<torch::ScalarType>);
-torch::Tensor grouped_gemm(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const std::string&);
+torch::Tensor grouped_gemm(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const std::string&, const c10::optional<torch::Tensor>&);
 torch::Tensor grouped_gemm_wgrad(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, int64_t);
 std::vector<torch::Tensor> rmsnorm_fwd(const torch::Tensor&, const torch::Tensor&, double, double);
 std::vector<torch::Tensor> rmsnorm_bwd(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, double);
@@ -35,12 +35,15 @@ void peer_all_gather(torch::Tensor, const std::vector<int64_t>&, int64_t, int64_
 void peer_reduce_scatter_acc(torch::Tensor, const std::vector<int64_t>&, int64_t, double, const c10::optional<torch::Tensor>&, int64_t);
 void ulysses_exchange(const torch::Tensor&, const std::vector<int64_t>&, int64_t, bool, int64_t);
 void peer_copy_cast(const torch::Tensor&, const std::vector<int64_t>&, int64_t);
+torch::Tensor paged_attn_decode(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, double);
+std::vector<torch::Tensor> sample_tokens(const torch::Tensor&, double, int64_t, double, const torch::Tensor&);
+std::vector<torch::Tensor> moe_router(const torch::Tensor&, int64_t, bool);
 }  // namespace tk
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &tk::gemm, py::arg("a"), py::arg("b"), py::arg("layout") = "nt", py::arg("out") = py::none(),
         py::arg("accumulate") = false, py::arg("out_dtype") = py::none());
-  m.def("grouped_gemm", &tk::grouped_gemm);
+  m.def("grouped_gemm", &tk::grouped_gemm, py::arg("x"), py::arg("w"), py::arg("offsets"), py::arg("layout") = "nt", py::arg("group_map") = py::none());
   m.def("grouped_gemm_wgrad", &tk::grouped_gemm_wgrad);
   m.def("rmsnorm_fwd", &tk::rmsnorm_fwd);
   m.def("rmsnorm_bwd", &tk::rmsnorm_bwd);
@@ -62,6 +65,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("peer_reduce_scatter_acc", &tk::peer_reduce_scatter_acc);
   m.def("ulysses_exchange", &tk::ulysses_exchange);
   m.def("peer_copy_cast", &tk::peer_copy_cast);
+  m.def("paged_attn_decode", &tk::paged_attn_decode);
+  m.def("sample_tokens", &tk::sample_tokens);
+  m.def("moe_router", &tk::moe_router);
   m.def("read_and_clear_error", &tk::read_and_clear_error, "Value of the device error word (0 = healthy); clears it.");
   m.def("num_sms", &tk::num_sms);
   m.def("launch_count", &tk::launch_count, "Number of kernels launched by this extension so far.");

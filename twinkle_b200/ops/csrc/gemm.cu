@@ -43,6 +43,7 @@ struct GemmParams {
   int num_groups;
   int group_rows_b;    // rows of B per group (N for NT, K for NN)
   int mode;            // 0 dense, 1 grouped over M (A rows by expert), 2 grouped wgrad (K range by expert)
+  const int* group_map;  // optional: group g uses weight block group_map[g] (< 0: group skipped); nullptr = identity
 };
 
 struct TileCoord {
@@ -75,6 +76,7 @@ __device__ __forceinline__ bool grouped_m_tile(const GemmParams& p, int tile, Gr
   int num_n = (p.N + BN - 1) / BN;
   while (c.e < p.num_groups) {
     int rows = p.offsets[c.e + 1] - p.offsets[c.e];
+    if (p.group_map != nullptr && p.group_map[c.e] < 0) rows = 0;
     int tiles_e = ((rows + BM - 1) / BM) * num_n;
     if (tile < c.tiles_before + tiles_e) {
       int r = tile - c.tiles_before;
@@ -158,7 +160,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       TileCoord t;
       bool ok = true;
       for (int tile = blockIdx.x; ok && next_tile<MODE>(p, tile, cur, t); tile += gridDim.x) {
-        const int b_row0 = (MODE == 1) ? t.group * p.group_rows_b : 0;
+        const int b_row0 = (MODE == 1) ? (p.group_map ? p.group_map[t.group] : t.group) * p.group_rows_b : 0;
         for (int k0 = t.k_begin; k0 < t.k_end; k0 += BK) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.err, ERR_PRODUCER_WAIT)) { ok = false; break; }
           uint8_t* sa = smem + stage * STAGE_BYTES;
@@ -381,7 +383,7 @@ torch::Tensor gemm(const torch::Tensor& a, const torch::Tensor& b, const std::st
                         : make_tmap_2d(b.data_ptr(), b.size(1), b.size(0), b.stride(0), BK, BN);
   GemmParams p{};
   p.out = out.data_ptr(); p.M = M; p.N = N; p.K = K; p.ldo = out.stride(0); p.out_fp32 = fp32; p.accumulate = accumulate;
-  p.err = error_word(); p.offsets = nullptr; p.num_groups = 1; p.group_rows_b = 0; p.mode = 0;
+  p.err = error_word(); p.offsets = nullptr; p.num_groups = 1; p.group_rows_b = 0; p.mode = 0; p.group_map = nullptr;
   int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   launch(a_mn, b_mn, 0, ta, tb, p, tiles, at::cuda::getCurrentCUDAStream());
   return out;
@@ -389,21 +391,26 @@ torch::Tensor gemm(const torch::Tensor& a, const torch::Tensor& b, const std::st
 
 // Expert-grouped GEMM.  x [R, K] with expert e owning rows [offsets[e], offsets[e+1]) (offsets multiples of 128;
 // padding rows are zero); weight [E, N, K] (nt) or [E, K, N] (nn).  Returns [R, N].
-torch::Tensor grouped_gemm(const torch::Tensor& x, const torch::Tensor& w, const torch::Tensor& offsets, const std::string& layout) {
+torch::Tensor grouped_gemm(const torch::Tensor& x, const torch::Tensor& w, const torch::Tensor& offsets, const std::string& layout,
+                           const c10::optional<torch::Tensor>& group_map) {
   check_operand(x, "x");
   TORCH_CHECK(w.is_cuda() && w.scalar_type() == torch::kBFloat16 && w.dim() == 3 && w.is_contiguous(), "weight [E, *, *] bf16 contiguous");
   TORCH_CHECK(offsets.is_cuda() && offsets.scalar_type() == torch::kInt32 && offsets.is_contiguous(), "offsets int32 on device");
   c10::cuda::CUDAGuard guard(x.device());
-  const int E = w.size(0), R = x.size(0), K = x.size(1);
-  TORCH_CHECK(offsets.numel() == E + 1, "offsets must have E+1 entries");
+  const int R = x.size(0), K = x.size(1);
+  const bool mapped = group_map.has_value() && group_map->defined();
+  const int E = mapped ? static_cast<int>(group_map->numel()) : static_cast<int>(w.size(0));
+  if (mapped) TORCH_CHECK(group_map->is_cuda() && group_map->scalar_type() == torch::kInt32 && group_map->is_contiguous(), "group_map int32 on device");
+  TORCH_CHECK(offsets.numel() == E + 1, "offsets must have one more entry than there are groups");
   int N;
   bool b_mn;
   if (layout == "nt") { N = w.size(1); TORCH_CHECK(w.size(2) == K, "nt: K mismatch"); b_mn = false; }
   else if (layout == "nn") { N = w.size(2); TORCH_CHECK(w.size(1) == K, "nn: K mismatch"); b_mn = true; }
   else TORCH_CHECK(false, "grouped layout must be nt|nn");
-  auto out = torch::empty({R, N}, x.options());
+  // with a map some groups may be skipped (no adapter): their rows must read as zero
+  auto out = mapped ? torch::zeros({R, N}, x.options()) : torch::empty({R, N}, x.options());
   if (R == 0) return out;
-  auto w2 = w.view({E * w.size(1), w.size(2)});
+  auto w2 = w.view({w.size(0) * w.size(1), w.size(2)});
   check_operand(w2, "weight");
   CUtensorMap ta = make_tmap_2d(x.data_ptr(), x.size(1), x.size(0), x.stride(0), BK, BM);
   CUtensorMap tb = b_mn ? make_tmap_2d(w2.data_ptr(), w2.size(1), w2.size(0), w2.stride(0), 64, BK)
@@ -411,6 +418,7 @@ torch::Tensor grouped_gemm(const torch::Tensor& x, const torch::Tensor& w, const
   GemmParams p{};
   p.out = out.data_ptr(); p.M = R; p.N = N; p.K = K; p.ldo = N; p.out_fp32 = 0; p.accumulate = 0; p.err = error_word();
   p.offsets = offsets.data_ptr<int>(); p.num_groups = E; p.group_rows_b = w.size(1); p.mode = 1;
+  p.group_map = mapped ? group_map->data_ptr<int>() : nullptr;
   // upper bound of tiles: every expert wastes at most one partial M-tile
   int tiles = ((R + BM - 1) / BM + E) * ((N + BN - 1) / BN);
   launch(false, b_mn, 1, ta, tb, p, tiles, at::cuda::getCurrentCUDAStream());
@@ -429,7 +437,7 @@ torch::Tensor grouped_gemm_wgrad(const torch::Tensor& dy, const torch::Tensor& x
   CUtensorMap tb = make_tmap_2d(x.data_ptr(), x.size(1), x.size(0), x.stride(0), 64, BK);
   GemmParams p{};
   p.out = out.data_ptr(); p.M = N; p.N = K; p.K = dy.size(0); p.ldo = K; p.out_fp32 = 1; p.accumulate = 0; p.err = error_word();
-  p.offsets = offsets.data_ptr<int>(); p.num_groups = static_cast<int>(E); p.group_rows_b = 0; p.mode = 2;
+  p.offsets = offsets.data_ptr<int>(); p.num_groups = static_cast<int>(E); p.group_rows_b = 0; p.mode = 2; p.group_map = nullptr;
   int tiles = static_cast<int>(E) * ((N + BM - 1) / BM) * ((K + BN - 1) / BN);
   launch(true, true, 2, ta, tb, p, tiles, at::cuda::getCurrentCUDAStream());
   return out;

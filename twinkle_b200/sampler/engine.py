@@ -103,13 +103,11 @@ class NativeEngine:
     def _lora_for(self, seqs: Sequence[_Seq], lens: Sequence[int]) -> Optional[LoraBatch]:
         if all(s.slot < 0 for s in seqs):
             return None
-        starts = [0]
-        for n in lens:
-            starts.append(starts[-1] + n)
-        dev = self.device
-        return LoraBatch(torch.tensor(starts, dtype=torch.int32, device=dev), torch.tensor([s.slot for s in seqs], dtype=torch.int32, device=dev),
-                         torch.tensor([s.lora_rank for s in seqs], dtype=torch.int32, device=dev),
-                         torch.tensor([s.lora_scale for s in seqs], dtype=torch.float32, device=dev), [s.lora_target for s in seqs])
+        segs, lo = [], 0
+        for s, n in zip(seqs, lens):
+            segs.append((lo, lo + n, s.slot, s.lora_rank, s.lora_scale))
+            lo += n
+        return LoraBatch(segs, self.device, [s.lora_target for s in seqs])
 
     # ------------------------------------------------------------- prefill
     @torch.no_grad()
@@ -191,7 +189,7 @@ class NativeEngine:
                     vals = lg[j, seen]
                     lg[j, seen] = torch.where(vals > 0, vals / rp, vals * rp)
             gen = seqs[idxs[0]].generator if len(idxs) == 1 else None
-            tok, lp = ops.ref.sample_tokens(lg, temp, tk, tp, gen) if (gen is not None or not lg.is_cuda) else ops.sample_tokens(lg, temp, tk, tp)
+            tok, lp = ops.ref.sample_tokens(lg, temp, tk, tp, gen) if not lg.is_cuda else ops.sample_tokens(lg, temp, tk, tp, gen)
             for j, i in enumerate(idxs):
                 out_tok[i], out_lp[i] = int(tok[j]), float(lp[j])
                 k = seqs[i].params.logprobs
