@@ -97,6 +97,8 @@ class TransformersModel(TwinkleModel):
         self.strategy_name = strategy
         self.comm_backend = comm_backend
         self.device = torch.device(device) if device is not None else Platform.current_device()
+        if self.device.type == 'cuda' and self.device.index is None:
+            self.device = torch.device('cuda', torch.cuda.current_device())
         on_gpu = self.device.type == 'cuda'
         if on_gpu:
             torch.cuda.set_device(self.device)
