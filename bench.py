@@ -46,6 +46,7 @@ def parse():
     ap.add_argument('--layers', type=int, default=None, help='debug only: overrides the layer count (result marked invalid)')
     ap.add_argument('--comm', default='auto', choices=['auto', 'nccl', 'symm'])
     ap.add_argument('--no-e2e', action='store_true')
+    ap.add_argument('--sp', type=int, default=None, help='Ulysses degree (default min(4, gpus))')
     return ap.parse_args()
 
 
@@ -155,7 +156,7 @@ def main():
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
         import datetime
         dist.init_process_group('nccl', device_id=torch.device('cuda', local), timeout=datetime.timedelta(seconds=300))
-    sp = min(4, world)
+    sp = args.sp or min(4, world)
     mesh = DeviceMesh.from_sizes(fsdp_size=world, dp_size=None, ulysses_size=sp) if world > 1 else DeviceMesh.from_sizes(dp_size=1)
     cfg = preset(args.model) if args.layers is None else preset(args.model, num_hidden_layers=args.layers)
     model = TransformersModel(config=cfg, device_mesh=mesh, seed=0, comm_backend=args.comm, grad_dtype='fp32')
