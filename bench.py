@@ -169,8 +169,12 @@ def main():
     dev_feats = [{k: v.cuda(non_blocking=True) for k, v in f.items()} for f in feats]
     h2d_bytes = sum(v.numel() * v.element_size() for f in feats for v in f.values()) // sp
 
+    # one micro-batch holds 65536 tokens per rank when the sharded state leaves room for it (N >= 2): parameters are
+    # gathered and gradients reduce-scattered once per step instead of once per sequence
+    micro = n_local_seqs if world > 1 else 1
+
     def step(batch, read_loss: bool):
-        out = model.forward_backward(inputs=batch, micro_batch_size=1)
+        out = model.forward_backward(inputs=batch, micro_batch_size=micro)
         model.clip_grad_and_step(max_grad_norm=1.0)
         return float(out['loss']) if read_loss else None
 
@@ -218,7 +222,7 @@ def main():
             'config': {'model': 'Qwen3-8B architecture' if args.layers is None else f'INVALID-debug-{args.layers}-layers',
                        'global_batch': args.seqs_per_gpu * world, 'seq_len': args.seq_len,
                        'parallelism': f'fsdp{world}' + (f'+ulysses{sp}' if sp > 1 else ''), 'optimizer': 'AdamW fp32 master',
-                       'recompute': 'per-layer', 'l2': 'inputs per step exceed the 126 MB L2 (65536 tokens x 4096 hidden bf16 = 512 MiB per activation)',
+                       'recompute': 'per-layer', 'micro_batches_per_step': n_local_seqs // micro, 'l2': 'inputs per step exceed the 126 MB L2 (65536 tokens x 4096 hidden bf16 = 512 MiB per activation)',
                        'comm': args.comm},
             'clocks': clocks, 'e2e': e2e, 'gpu_launches': int(launches), 'peak_mem_gib': round(peak, 1),
             'model_flops_per_token': cfg.flops_per_token(avg_context=0.0), 'kernel_error_word': err,
