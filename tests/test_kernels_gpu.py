@@ -45,6 +45,40 @@ def test_gemm(E, layout, shape):
     assert E.read_and_clear_error() == 0
 
 
+@pytest.mark.parametrize('layout', ['nt', 'nn', 'tn'])
+@pytest.mark.parametrize('shape', [(4096, 2048, 512), (4000, 2504, 200), (2304, 4096, 4096)])
+def test_gemm_sm_pair(E, layout, shape):
+    """256x256 tiles on SM pairs (cta_group::2) against fp32, including ragged M / N / K and accumulate."""
+    M, N, K = shape
+    torch.manual_seed(0)
+    if layout == 'nt':
+        a, b = torch.randn(M, K, device='cuda').bfloat16(), torch.randn(N, K, device='cuda').bfloat16()
+        r = a.float() @ b.float().t()
+    elif layout == 'nn':
+        a, b = torch.randn(M, K, device='cuda').bfloat16(), torch.randn(K, N, device='cuda').bfloat16()
+        r = a.float() @ b.float()
+    else:
+        a, b = torch.randn(K, M, device='cuda').bfloat16(), torch.randn(K, N, device='cuda').bfloat16()
+        r = a.float().t() @ b.float()
+    E.set_gemm_pair(1)
+    try:
+        n0 = E.launch_count()
+        o = E.gemm(a, b, layout)
+        acc = torch.ones(M, N, device='cuda', dtype=torch.float32)
+        E.gemm(a, b, layout, acc, True)
+        torch.cuda.synchronize()
+    finally:
+        E.set_gemm_pair(0)
+    assert E.launch_count() - n0 == 2
+    assert rel(o, r) < 4e-3
+    assert rel(acc - 1, r) < 1e-4
+    try:
+        single = E.gemm(a, b, layout)  # single-CTA tiles
+    finally:
+        E.set_gemm_pair(1)
+    assert rel(o, single) < 1e-6  # same products, same fp32 accumulation order per k-step
+
+
 def test_grouped_gemm(E):
     from twinkle_b200.ops import reference as ref
     torch.manual_seed(0)

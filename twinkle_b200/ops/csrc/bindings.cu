@@ -38,6 +38,7 @@ void peer_copy_cast(const torch::Tensor&, const std::vector<int64_t>&, int64_t);
 torch::Tensor paged_attn_decode(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, double);
 std::vector<torch::Tensor> sample_tokens(const torch::Tensor&, double, int64_t, double, const torch::Tensor&);
 std::vector<torch::Tensor> moe_router(const torch::Tensor&, int64_t, bool);
+void set_gemm_pair(int64_t);
 }  // namespace tk
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -68,6 +69,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("paged_attn_decode", &tk::paged_attn_decode);
   m.def("sample_tokens", &tk::sample_tokens);
   m.def("moe_router", &tk::moe_router);
+  m.def("set_gemm_pair", &tk::set_gemm_pair);
   m.def("read_and_clear_error", &tk::read_and_clear_error, "Value of the device error word (0 = healthy); clears it.");
   m.def("num_sms", &tk::num_sms);
   m.def("launch_count", &tk::launch_count, "Number of kernels launched by this extension so far.");

@@ -350,6 +350,16 @@ static void check_operand(const torch::Tensor& t, const char* name) {
   TORCH_CHECK(reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0, name, " must be 16-byte aligned");
 }
 
+bool gemm_pair_launch(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, void* out, int M, int N, int K, int ldo,
+                      bool out_fp32, bool accumulate, cudaStream_t stream);
+
+// 0: single-CTA tiles only; 1: SM-pair kernel (gemm2.cu) for shapes with enough 256x256 tiles to fill the device.
+static int g_pair_mode = [] {
+  const char* e = getenv("TK_GEMM_PAIR");
+  return e ? atoi(e) : 1;
+}();
+void set_gemm_pair(int64_t mode) { g_pair_mode = static_cast<int>(mode); }
+
 // out = a·bᵀ (nt) | a·b (nn) | aᵀ·b (tn)
 torch::Tensor gemm(const torch::Tensor& a, const torch::Tensor& b, const std::string& layout,
                    const c10::optional<torch::Tensor>& out_opt, bool accumulate, c10::optional<torch::ScalarType> out_dtype) {
@@ -376,6 +386,15 @@ torch::Tensor gemm(const torch::Tensor& a, const torch::Tensor& b, const std::st
               "out rows must be 16-byte aligned");
   if (M == 0 || N == 0) return out;
   if (K == 0) { if (!accumulate) out.zero_(); return out; }
+  if (g_pair_mode && ((M + 255) / 256) * ((N + 255) / 256) >= num_sms() / 2) {
+    CUtensorMap pa = a_mn ? make_tmap_2d(a.data_ptr(), a.size(1), a.size(0), a.stride(0), 64, BK)
+                          : make_tmap_2d(a.data_ptr(), a.size(1), a.size(0), a.stride(0), BK, 128);
+    CUtensorMap pb = b_mn ? make_tmap_2d(b.data_ptr(), b.size(1), b.size(0), b.stride(0), 64, BK)
+                          : make_tmap_2d(b.data_ptr(), b.size(1), b.size(0), b.stride(0), BK, 128);
+    if (gemm_pair_launch(a_mn, b_mn, pa, pb, out.data_ptr(), M, N, K, static_cast<int>(out.stride(0)), fp32, accumulate,
+                         at::cuda::getCurrentCUDAStream()))
+      return out;
+  }
   // a row-major [R, C] matrix is a 2-D tensor map with dims {C, R}
   CUtensorMap ta = a_mn ? make_tmap_2d(a.data_ptr(), a.size(1), a.size(0), a.stride(0), 64, BK)
                         : make_tmap_2d(a.data_ptr(), a.size(1), a.size(0), a.stride(0), BK, BM);

@@ -1,0 +1,328 @@
+// bf16 GEMM with SM pairs: tcgen05.mma.cta_group::2 on 256x256 output tiles (dense mode of gemm.cu's kernel).
+//
+// A thread-block cluster of two CTAs (one SM each) owns one 256x256 tile of D.  CTA r of the pair loads rows
+// [128r, 128r+128) of the A tile and rows [128r, 128r+128) of the B tile, so one SM pulls 32 KB of operands per
+// 256x256x64 step instead of the 48 KB a 128x256 single-CTA tile needs; its tensor memory receives the 128x256
+// half of the accumulator that belongs to its A rows.  One elected thread of the even CTA issues the MMAs for
+// the pair.
+//
+// Barrier plumbing (s = stage, b = accumulator buffer):
+//   full[s]       lives in the leader; 1 arrival (leader's expect_tx for both CTAs' bytes) + the bytes of all four
+//                 TMA loads (the odd CTA's loads name the leader's barrier through its cluster address)
+//   empty[s]      one per CTA; tcgen05.commit with a 2-CTA multicast mask frees the stage in both
+//   tmem_full[b]  one per CTA; same multicast commit after the last k-step of a tile
+//   tmem_empty[b] lives in the leader; 8 arrivals = 4 epilogue warps of each CTA (remote arrive from the odd one)
+// No TMA load carries a cluster multicast qualifier: every operand box is fetched by the CTA that uses it.
+// All waits are bounded (common.cuh); both CTAs always meet at a cluster barrier before TMEM is released.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "common.cuh"
+#include "host.h"
+
+namespace tk {
+namespace g2 {
+
+constexpr int TM = 256, TN = 256, BK = 64, UMMA_K = 16, STAGES = 6;
+constexpr int HALF_M = 128, HALF_N = 128;
+constexpr int A_BYTES = HALF_M * BK * 2, B_BYTES = HALF_N * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;  // 32 KB per CTA
+constexpr int THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int GROUP_M = 8;
+
+struct Params {
+  void* out;
+  int M, N, K, ldo, out_fp32, accumulate;
+  int* err;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t cta) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.aligned;\n\tbarrier.cluster.wait.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// 2-D tiled load whose completion bytes go to a barrier that may sit in the peer CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at this shared-memory offset in both CTAs of the pair once the issued MMAs retire.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+
+__device__ __forceinline__ bool tile_coord(const Params& p, int tile, int& m0, int& n0) {
+  const int num_m = (p.M + TM - 1) / TM, num_n = (p.N + TN - 1) / TN;
+  if (tile >= num_m * num_n) return false;
+  const int per_group = GROUP_M * num_n;
+  const int g = tile / per_group, first_m = g * GROUP_M;
+  const int gsize = min(num_m - first_m, GROUP_M);
+  const int r = tile - g * per_group;
+  m0 = (first_m + r % gsize) * TM;
+  n0 = (r / gsize) * TN;
+  return true;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full = empty_bar + STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();  // 0 = leader of the pair
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 8);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything can signal them
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer (one per CTA)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int m0, n0;
+      bool ok = true;
+      for (int tile = pair; ok && tile_coord(p, tile, m0, n0); tile += num_pairs) {
+        const int am = m0 + static_cast<int>(cta) * HALF_M, bn = n0 + static_cast<int>(cta) * HALF_N;
+        for (int k0 = 0; k0 < p.K; k0 += BK) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.err, ERR_PRODUCER_WAIT)) { ok = false; break; }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          if (cta == 0) mbar_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
+          if constexpr (!A_MN) {
+            tma_load_2d_pair(sa, &tmA, bar, k0, am);                                  // box {64 K, 128 rows}
+          } else {
+#pragma unroll
+            for (int j = 0; j < HALF_M / 64; ++j) tma_load_2d_pair(sa + j * (64 * BK * 2), &tmA, bar, am + j * 64, k0);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d_pair(sb, &tmB, bar, k0, bn);
+          } else {
+#pragma unroll
+            for (int j = 0; j < HALF_N / 64; ++j) tma_load_2d_pair(sb + j * (64 * BK * 2), &tmB, bar, bn + j * 64, k0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok && cta == 0) {
+        for (int s = 0; s < STAGES; ++s) mbar_wait(&full_bar[s], 0, nullptr, 0);  // bounded drain of copies in flight
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer (leader CTA only)
+    if (lane == 0 && cta == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(TM, TN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0, acc = 0, acc_phase = 0;
+      int m0, n0;
+      bool ok = true;
+      for (int tile = pair; ok && tile_coord(p, tile, m0, n0); tile += num_pairs) {
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.err, ERR_MMA_WAIT_TMEM)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * TN;
+        uint32_t first = 1;
+        for (int k0 = 0; k0 < p.K; k0 += BK) {
+          if (!mbar_wait(&full_bar[stage], phase, p.err, ERR_MMA_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t ad = A_MN ? umma_desc(sa + k * (UMMA_K * 128), 64 * BK * 2, 1024) : umma_desc(sa + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t bd = B_MN ? umma_desc(sb + k * (UMMA_K * 128), 64 * BK * 2, 1024) : umma_desc(sb + k * (UMMA_K * 2), 16, 1024);
+            umma_bf16_pair(d_tmem, ad, bd, idesc, first ? 0u : 1u);
+            first = 0;
+          }
+          umma_commit_pair(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit_pair(&tmem_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+    const int q = warp & 3;
+    uint32_t acc = 0, acc_phase = 0;
+    int m0, n0;
+    bool ok = true;
+    for (int tile = pair; ok && tile_coord(p, tile, m0, n0); tile += num_pairs) {
+      if (!mbar_wait(&tmem_full[acc], acc_phase, p.err, ERR_EPI_WAIT)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + static_cast<int>(cta) * HALF_M + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const size_t out_row = static_cast<size_t>(row);
+#pragma unroll 1
+      for (int c = 0; c < TN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + acc * TN + c * 32 + (static_cast<uint32_t>(q * 32) << 16), r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (!row_ok || col0 >= p.N) continue;
+        if (p.out_fp32) {
+          float* o = reinterpret_cast<float*>(p.out) + out_row * p.ldo + col0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            if (col0 + j + 4 <= p.N) {
+              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+              if (p.accumulate) {
+                const float4 old = *reinterpret_cast<float4*>(o + j);
+                v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+              }
+              *reinterpret_cast<float4*>(o + j) = v;
+            } else {
+              for (int jj = j; jj < j + 4 && col0 + jj < p.N; ++jj) o[jj] = __uint_as_float(r[jj]) + (p.accumulate ? o[jj] : 0.f);
+            }
+          }
+        } else {
+          __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + out_row * p.ldo + col0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (col0 + j + 8 <= p.N) {
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[j + e]);
+              if (p.accumulate) {
+                const uint4 old = *reinterpret_cast<uint4*>(o + j);
+                const float2 a0 = unpack_bf16(old.x), a1 = unpack_bf16(old.y), a2 = unpack_bf16(old.z), a3 = unpack_bf16(old.w);
+                f[0] += a0.x; f[1] += a0.y; f[2] += a1.x; f[3] += a1.y;
+                f[4] += a2.x; f[5] += a2.y; f[6] += a3.x; f[7] += a3.y;
+              }
+              *reinterpret_cast<uint4*>(o + j) = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+            } else {
+              for (int jj = j; jj < j + 8 && col0 + jj < p.N; ++jj)
+                o[jj] = __float2bfloat16(__uint_as_float(r[jj]) + (p.accumulate ? __bfloat162float(o[jj]) : 0.f));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[acc]), 0));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // nobody in the pair touches the other's shared or tensor memory after this point
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+}  // namespace g2
+
+// Number of SM pairs that can be resident at once for this kernel (cached per device); 0 when clusters cannot launch.
+template <typename Kern>
+static int max_pairs(Kern kern) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(num_sms() & ~1, 1, 1);
+  cfg.blockDim = dim3(g2::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = g2::SMEM_BYTES;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+// Dense GEMM on SM pairs; same contract as the single-CTA path.  Returns false when the shape is not eligible
+// (the caller then uses the single-CTA kernel).
+bool gemm_pair_launch(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, void* out, int M, int N, int K, int ldo,
+                      bool out_fp32, bool accumulate, cudaStream_t stream) {
+  g2::Params p{out, M, N, K, ldo, out_fp32 ? 1 : 0, accumulate ? 1 : 0, error_word()};
+  const int tiles = ((M + g2::TM - 1) / g2::TM) * ((N + g2::TN - 1) / g2::TN);
+#define TK_LAUNCH2(AM, BMN)                                                                                            \
+  do {                                                                                                                 \
+    static int pairs = -1;                                                                                             \
+    auto kern = g2::gemm_tcgen05_pair_kernel<AM, BMN>;                                                                 \
+    if (pairs < 0) {                                                                                                   \
+      TK_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, g2::SMEM_BYTES));          \
+      pairs = max_pairs(kern);                                                                                         \
+    }                                                                                                                  \
+    if (pairs <= 0) return false;                                                                                      \
+    const int grid = 2 * std::min(tiles, std::min(pairs, num_sms() / 2));                                              \
+    kern<<<grid, g2::THREADS, g2::SMEM_BYTES, stream>>>(ta, tb, p);                                                    \
+  } while (0)
+  if (!a_mn && !b_mn) TK_LAUNCH2(false, false);
+  else if (!a_mn && b_mn) TK_LAUNCH2(false, true);
+  else if (a_mn && b_mn) TK_LAUNCH2(true, true);
+  else return false;
+#undef TK_LAUNCH2
+  count_launch();
+  TK_CUDA_CHECK(cudaGetLastError());
+  return true;
+}
+
+}  // namespace tk

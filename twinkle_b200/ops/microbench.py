@@ -143,8 +143,12 @@ def main() -> None:
     ap.add_argument('--iters', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--no-flush', action='store_true')
+    ap.add_argument('--pair', type=int, default=None, help='1: SM-pair GEMM kernel, 0: single-CTA tiles (default: library setting)')
     a = ap.parse_args()
     torch.manual_seed(0)
+    if a.pair is not None:
+        from twinkle_b200 import ops as _ops
+        _ops.ext().set_gemm_pair(a.pair)
     fn, flops, byts = make(a.op, a)
     ms = time_op(fn, a.iters, a.warmup, not a.no_flush)
     pk = peaks()
