@@ -47,6 +47,8 @@ def parse():
     ap.add_argument('--comm', default='auto', choices=['auto', 'nccl', 'symm'])
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--sp', type=int, default=None, help='Ulysses degree (default min(4, gpus))')
+    ap.add_argument('--config', default='dense', choices=['dense', 'moe'],
+                    help="dense: Qwen3-8B full-parameter SFT (headline); moe: Qwen3-30B-A3B LoRA r=16 SFT with expert parallel = gpus")
     return ap.parse_args()
 
 
@@ -95,15 +97,16 @@ class ClockSampler:
         return {'sm_mhz': sm[len(sm) // 2] if sm else None, 'sm_max_mhz': mx, 'reasons': sorted(reasons), 'samples': len(sm)}
 
 
-def synthetic_sequences(n_seqs: int, seq_len: int, vocab: int, seed: int):
-    """Each sequence = documents of length U[512, 8192] packed to exactly ``seq_len`` tokens."""
+def synthetic_sequences(n_seqs: int, seq_len: int, vocab: int, seed: int, pack: bool = True):
+    """Each sequence = documents of length U[512, 8192] packed to exactly ``seq_len`` tokens (``pack``), or one
+    document of ``seq_len`` tokens."""
     import torch
     g = torch.Generator().manual_seed(seed)
     feats = []
     for _ in range(n_seqs):
         lens, total = [], 0
         while total < seq_len:
-            L = int(torch.randint(512, 8193, (1, ), generator=g))
+            L = int(torch.randint(512, 8193, (1, ), generator=g)) if pack else seq_len
             L = min(L, seq_len - total)
             lens.append(L)
             total += L
@@ -156,26 +159,51 @@ def main():
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
         import datetime
         dist.init_process_group('nccl', device_id=torch.device('cuda', local), timeout=datetime.timedelta(seconds=300))
-    sp = args.sp or min(4, world)
-    mesh = DeviceMesh.from_sizes(fsdp_size=world, dp_size=None, ulysses_size=sp) if world > 1 else DeviceMesh.from_sizes(dp_size=1)
-    cfg = preset(args.model) if args.layers is None else preset(args.model, num_hidden_layers=args.layers)
-    model = TransformersModel(config=cfg, device_mesh=mesh, seed=0, comm_backend=args.comm, grad_dtype='fp32')
-    model.set_optimizer('AdamW', lr=1e-5, weight_decay=0.01)
+    moe = args.config == 'moe'
+    if moe:
+        # BASELINE config 3: 48 layers, hidden 2048, 32 q / 4 kv heads, 128 experts top-8 (FFN 768), aux loss 1e-3,
+        # LoRA r=16 on attention and expert linears, sequences of 4096 tokens, 8 sequences per GPU (64 at N=8),
+        # experts split over all ranks (EP = N), everything else flat-bucket FSDP over the same ranks.
+        if args.model == 'qwen3-8b':
+            args.model = 'qwen3-30b-a3b'
+        if args.seq_len == 32768:
+            args.seq_len = 4096
+        if args.seqs_per_gpu == 2:
+            args.seqs_per_gpu = 8
+        sp = 1
+        mesh = DeviceMesh.from_sizes(fsdp_size=world, dp_size=None, ep_size=world) if world > 1 else DeviceMesh.from_sizes(dp_size=1)
+    else:
+        sp = args.sp or min(4, world)
+        mesh = DeviceMesh.from_sizes(fsdp_size=world, dp_size=None, ulysses_size=sp) if world > 1 else DeviceMesh.from_sizes(dp_size=1)
+    over = {} if args.layers is None else {'num_hidden_layers': args.layers}
+    if moe:
+        over['router_aux_loss_coef'] = 1e-3
+    cfg = preset(args.model, **over)
+    if moe:
+        from twinkle_b200.model import LoraConfig
+        model = TransformersModel(config=cfg, device_mesh=mesh, seed=0, comm_backend=args.comm, grad_dtype='fp32', max_loras=1, max_r=16)
+        model.add_adapter_to_model('sft', LoraConfig(r=16, lora_alpha=32, target_modules='all-linear'))
+        model.set_optimizer('AdamW', lr=1e-4, weight_decay=0.01, adapter_name='sft')
+        akw = {'adapter_name': 'sft'}
+    else:
+        model = TransformersModel(config=cfg, device_mesh=mesh, seed=0, comm_backend=args.comm, grad_dtype='fp32')
+        model.set_optimizer('AdamW', lr=1e-5, weight_decay=0.01)
+        akw = {}
     data_ws = mesh.data_world_size
     n_local_seqs = args.seqs_per_gpu * sp          # sequences this rank's data group processes per step
     data_rank = mesh.data_rank or 0
     tokens_per_step_global = args.seqs_per_gpu * world * args.seq_len
-    feats = synthetic_sequences(n_local_seqs, args.seq_len, cfg.vocab_size, seed=1000 + data_rank)
+    feats = synthetic_sequences(n_local_seqs, args.seq_len, cfg.vocab_size, seed=1000 + data_rank, pack=not moe)
     dev_feats = [{k: v.cuda(non_blocking=True) for k, v in f.items()} for f in feats]
     h2d_bytes = sum(v.numel() * v.element_size() for f in feats for v in f.values()) // sp
 
     # one micro-batch holds 65536 tokens per rank when the sharded state leaves room for it (N >= 2): parameters are
     # gathered and gradients reduce-scattered once per step instead of once per sequence
-    micro = n_local_seqs if world > 1 else 1
+    micro = n_local_seqs if (world > 1 or moe) else 1
 
     def step(batch, read_loss: bool):
-        out = model.forward_backward(inputs=batch, micro_batch_size=micro)
-        model.clip_grad_and_step(max_grad_norm=1.0)
+        out = model.forward_backward(inputs=batch, micro_batch_size=micro, **akw)
+        model.clip_grad_and_step(max_grad_norm=1.0, **akw)
         return float(out['loss']) if read_loss else None
 
     def timed(batch, steps, read_loss):
@@ -215,13 +243,13 @@ def main():
         value = tokens_per_step_global * args.steps / (ms / 1e3)
         peak = torch.cuda.max_memory_allocated() / 2**30
         line = {
-            'metric': 'train tokens/s/box Qwen3-8B FSDP2 (+Ulysses SP) full-parameter SFT', 'value': value, 'unit': 'tokens/s',
+            'metric': ('train tokens/s/box Qwen3-30B-A3B EP LoRA SFT' if moe else 'train tokens/s/box Qwen3-8B FSDP2 (+Ulysses SP) full-parameter SFT'), 'value': value, 'unit': 'tokens/s',
             'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': ms / args.steps, 'higher_is_better': True,
             'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic (uniform token ids, packed docs U[512,8192], random-init weights)',
             'impl': 'ours',
-            'config': {'model': 'Qwen3-8B architecture' if args.layers is None else f'INVALID-debug-{args.layers}-layers',
+            'config': {'model': ('Qwen3-30B-A3B architecture, LoRA r=16' if moe else 'Qwen3-8B architecture') if args.layers is None else f'INVALID-debug-{args.layers}-layers',
                        'global_batch': args.seqs_per_gpu * world, 'seq_len': args.seq_len,
-                       'parallelism': f'fsdp{world}' + (f'+ulysses{sp}' if sp > 1 else ''), 'optimizer': 'AdamW fp32 master',
+                       'parallelism': f'fsdp{world}' + (f'+ulysses{sp}' if sp > 1 else '') + (f'+ep{world}' if moe else ''), 'optimizer': 'AdamW fp32 master',
                        'recompute': 'per-layer', 'micro_batches_per_step': n_local_seqs // micro, 'l2': 'inputs per step exceed the 126 MB L2 (65536 tokens x 4096 hidden bf16 = 512 MiB per activation)',
                        'comm': args.comm},
             'clocks': clocks, 'e2e': e2e, 'gpu_launches': int(launches), 'peak_mem_gib': round(peak, 1),

@@ -120,17 +120,18 @@ class Experts(nn.Module):
         lb = current_lora_batch()
         if lb is None or self.max_loras == 0:
             return None
-        slots = [int(s) for s in lb.seg_slots.tolist() if int(s) >= 0]
-        if not slots:
+        active = [i for i, h in enumerate(lb.host) if h[2] >= 0]
+        if not active:
             return None
-        if len(set(slots)) > 1:
+        if len({lb.host[i][2] for i in active}) > 1:
             raise NotImplementedError('expert LoRA serves one tenant per forward; token-level tenants mix only in dense linears')
-        slot = slots[0]
-        i = lb.seg_slots.tolist().index(slot)
+        i = active[0]
+        _, _, slot, r, scale = lb.host[i]
         t = lb.targets[i] if lb.targets else None
         if t is not None and not t.matches('mlp.experts.' + which, which):
             return None
-        r, scale = int(lb.seg_ranks[i]), float(lb.seg_scales[i])
+        if r == 0:
+            return None
         a = self.lora[which + '_A'][slot, :, :r]  # [E, r, in]
         b = self.lora[which + '_B'][slot, :, :, :r]  # [E, out, r]
         h = ops.grouped_gemm(x, a, offsets)
