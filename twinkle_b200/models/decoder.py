@@ -115,7 +115,8 @@ class Experts(nn.Module):
         self.lora['down_A'] = mk_a(i)
         self.lora['down_B'] = nn.Parameter(torch.zeros(max_loras, e, h, max_r, device=dev, dtype=dt))
 
-    def _expert_lora(self, x, offsets, which: str):
+    def _expert_lora(self, which: str):
+        """(A [E, r, in], B [E, out, r], scale) of the tenant active in this forward, or None."""
         from .layers import current_lora_batch
         lb = current_lora_batch()
         if lb is None or self.max_loras == 0:
@@ -132,23 +133,15 @@ class Experts(nn.Module):
             return None
         if r == 0:
             return None
-        a = self.lora[which + '_A'][slot, :, :r]  # [E, r, in]
-        b = self.lora[which + '_B'][slot, :, :, :r]  # [E, out, r]
-        h = ops.grouped_gemm(x, a, offsets)
-        return ops.grouped_gemm(h, b, offsets) * scale
+        return self.lora[which + '_A'][slot, :, :r], self.lora[which + '_B'][slot, :, :, :r], scale
 
     def forward(self, x_sorted: torch.Tensor, offsets: torch.Tensor) -> torch.Tensor:
         """``x_sorted`` rows grouped by local expert; ``offsets [E_local+1]``."""
-        gu = ops.grouped_gemm(x_sorted, self.gate_up_proj, offsets)
-        d = self._expert_lora(x_sorted, offsets, 'gate_up')
-        if d is not None:
-            gu = gu + d
+        lo = self._expert_lora('gate_up')
+        gu = ops.expert_linear(x_sorted, self.gate_up_proj, offsets, *(lo or ()))
         act = ops.swiglu(gu)
-        y = ops.grouped_gemm(act, self.down_proj, offsets)
-        d = self._expert_lora(act, offsets, 'down')
-        if d is not None:
-            y = y + d
-        return y
+        lo = self._expert_lora('down')
+        return ops.expert_linear(act, self.down_proj, offsets, *(lo or ()))
 
 
 class MoEBlock(nn.Module):
@@ -165,7 +158,7 @@ class MoEBlock(nn.Module):
         self.record_routing = False
 
     def route(self, x: torch.Tensor, forced: Optional[torch.Tensor]):
-        w, idx, probs, _hist = ops.moe_router(self.gate(x), self.cfg.num_experts_per_tok, self.cfg.norm_topk_prob, forced)
+        w, idx, probs, self._hist = ops.moe_router(self.gate(x), self.cfg.num_experts_per_tok, self.cfg.norm_topk_prob, forced)
         return w, idx, probs
 
     def forward(self, x: torch.Tensor, forced: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -180,16 +173,14 @@ class MoEBlock(nn.Module):
         if mp is not None:
             return mp.forward(self, x, w, idx)
         # local: expert-sorted layout whose segments start on 128-row boundaries (grouped GEMM tiles and the
-        # per-expert wgrad reduction ranges then never straddle two experts); padding rows are zero
+        # per-expert wgrad reduction ranges then never straddle two experts); padding rows are zero.  Dispatch and
+        # combine are gathers through index maps built on the device — no host read anywhere in the block.
         from ..parallel.expert import expert_layout
-        flat = idx.reshape(-1)
-        order, rows, offsets, bound = expert_layout(flat, E, 128 if x.is_cuda else 1)
-        tok = order // k
-        xs = x.new_zeros(bound, H).index_copy(0, rows, x.index_select(0, tok))
-        y = self.experts(xs, offsets).index_select(0, rows)
-        y = y * w.reshape(-1)[order].to(y.dtype).unsqueeze(-1)
-        out = torch.zeros(T, H, dtype=y.dtype, device=x.device)
-        return out.index_add(0, tok, y)
+        order, rows, offsets, bound = expert_layout(idx.reshape(-1), E, 128 if x.is_cuda else 1, self._hist)
+        row_of, src_tok, slot_of_row = ops.moe_index_maps(order, rows, bound, k)
+        xs = ops.moe_dispatch(x, src_tok, row_of)
+        y = self.experts(xs, offsets)
+        return ops.moe_combine(y, w, row_of, src_tok, slot_of_row)
 
 
 class DecoderLayer(nn.Module):

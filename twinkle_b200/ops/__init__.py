@@ -479,6 +479,7 @@ class _Router(torch.autograd.Function):
             w = probs.gather(-1, idx)
             if renorm:
                 w = w / w.sum(-1, keepdim=True)
+            hist = torch.zeros_like(hist).scatter_add_(0, idx.reshape(-1), torch.ones(idx.numel(), dtype=hist.dtype, device=hist.device))
         ctx.save_for_backward(probs, idx, w)
         ctx.renorm = renorm
         ctx.mark_non_differentiable(idx, hist)
@@ -539,6 +540,130 @@ def grouped_gemm(x, weight, offsets):
     for e in range(weight.shape[0]):
         outs.append(x[off[e]:off[e + 1]] @ weight[e].t().to(x.dtype))
     return torch.cat(outs, 0)
+
+
+# ------------------------------------------------------- moe token permutation
+def moe_index_maps(order: torch.Tensor, rows: torch.Tensor, bound: int, k: int):
+    """From the expert sort (``order[i]`` = flat (token, slot) index of the i-th sorted pair, ``rows[i]`` = its row in
+    the expert-grouped layout) build the two gather maps: ``row_of [T, k]`` (row of every (token, slot)),
+    ``src_tok [bound]`` (token feeding each row, −1 = padding) and ``slot_of_row [bound]`` (flat index, −1 = padding)."""
+    n = order.numel()
+    dev = order.device
+    row_of = torch.empty(n, dtype=torch.int32, device=dev)
+    row_of[order] = rows.to(torch.int32)
+    slot_of_row = torch.full((bound, ), -1, dtype=torch.int32, device=dev)
+    slot_of_row[rows] = order.to(torch.int32)
+    src_tok = torch.where(slot_of_row >= 0, slot_of_row // k, slot_of_row)
+    return row_of.view(-1, k), src_tok, slot_of_row
+
+
+def _rows_gather(x, src, scale=None):
+    if _cuda(x) and x.dtype == torch.bfloat16:
+        return ext().moe_rows_gather(x.contiguous(), src, scale)
+    out = x.index_select(0, src.clamp_min(0).long()) * (src >= 0).to(x.dtype).unsqueeze(-1)
+    return out if scale is None else out * scale.to(x.dtype).unsqueeze(-1)
+
+
+def _rows_combine(y, row_of, w=None):
+    if _cuda(y) and y.dtype == torch.bfloat16:
+        return ext().moe_rows_combine(y.contiguous(), row_of, None if w is None else w.float().contiguous())
+    g = y.index_select(0, row_of.reshape(-1).clamp_min(0).long()).view(row_of.shape[0], row_of.shape[1], -1)
+    m = (row_of >= 0).to(y.dtype)
+    if w is not None:
+        m = m * w.to(y.dtype)
+    return (g * m.unsqueeze(-1)).sum(1)
+
+
+class _MoEDispatch(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, x, src_tok, row_of):
+        ctx.save_for_backward(row_of)
+        return _rows_gather(x, src_tok)
+
+    @staticmethod
+    def backward(ctx, g):
+        row_of, = ctx.saved_tensors
+        return _rows_combine(g.contiguous(), row_of), None, None
+
+
+class _MoECombine(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, y, w, row_of, src_tok, slot_of_row):
+        ctx.save_for_backward(y, w, row_of, src_tok, slot_of_row)
+        return _rows_combine(y, row_of, w)
+
+    @staticmethod
+    def backward(ctx, g):
+        y, w, row_of, src_tok, slot_of_row = ctx.saved_tensors
+        g = g.contiguous()
+        w_row = w.reshape(-1).float().index_select(0, slot_of_row.clamp_min(0).long())
+        gy = _rows_gather(g, src_tok, w_row)
+        if _cuda(y) and y.dtype == torch.bfloat16:
+            gw = ext().moe_combine_wgrad(g, y, row_of)
+        else:
+            yy = y.index_select(0, row_of.reshape(-1).clamp_min(0).long()).view(row_of.shape[0], row_of.shape[1], -1)
+            gw = (yy.float() * g.float().unsqueeze(1)).sum(-1) * (row_of >= 0)
+        return gy, gw.to(w.dtype), None, None, None
+
+
+def moe_dispatch(x, src_tok, row_of):
+    """Token rows → expert-grouped rows (zero padding rows); backward sums every token's k rows."""
+    return _MoEDispatch.apply(x, src_tok, row_of)
+
+
+def moe_combine(y, w, row_of, src_tok, slot_of_row):
+    """``out[t] = Σ_j w[t, j] · y[row_of[t, j]]`` with gradients for ``y`` and the routing weights ``w``."""
+    return _MoECombine.apply(y, w, row_of, src_tok, slot_of_row)
+
+
+class _ExpertLinearLora(torch.autograd.Function):
+    """``y = x Wᵀ + s · (x Aᵀ) Bᵀ`` per expert over expert-grouped rows: the LoRA expand GEMM accumulates into the
+    base GEMM's output inside its epilogue, so the [rows, out] tensor is written once and never re-read by an
+    element-wise add or scale."""
+
+    @staticmethod
+    def forward(ctx, x, weight, a, b, offsets, scale):
+        E = ext()
+        y = E.grouped_gemm(x, weight, offsets, 'nt', None)
+        h = E.grouped_gemm(x, a, offsets, 'nt', None)                     # [rows, r]
+        bs = (b.float() * scale).to(b.dtype)                               # [E, out, r] — scale folded into the small operand
+        E.grouped_gemm(h, bs, offsets, 'nt', None, y, True)
+        ctx.save_for_backward(x, weight, a, bs, h, offsets)
+        ctx.scale = scale
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        E = ext()
+        x, weight, a, bs, h, offsets = ctx.saved_tensors
+        gy = gy.contiguous()
+        n_e = weight.shape[0]
+        gh = E.grouped_gemm(gy, bs, offsets, 'nn', None)                   # [rows, r] = gy · (s·B)
+        gx = None
+        if ctx.needs_input_grad[0]:
+            gx = E.grouped_gemm(gy, weight, offsets, 'nn', None)
+            E.grouped_gemm(gh, a, offsets, 'nn', None, gx, True)
+        gw = E.grouped_gemm_wgrad(gy, x, offsets, n_e).to(weight.dtype) if ctx.needs_input_grad[1] else None
+        ga = E.grouped_gemm_wgrad(gh, x, offsets, n_e).to(a.dtype) if ctx.needs_input_grad[2] else None
+        gb = (E.grouped_gemm_wgrad(gy, h, offsets, n_e) * ctx.scale).to(bs.dtype) if ctx.needs_input_grad[3] else None
+        return gx, gw, ga, gb, None, None
+
+
+def expert_linear(x, weight, offsets, lora_a=None, lora_b=None, scale: float = 1.0):
+    """Per-expert linear over expert-grouped rows with an optional per-expert LoRA pair (``lora_a [E, r, in]``,
+    ``lora_b [E, out, r]``)."""
+    if lora_a is None:
+        return grouped_gemm(x, weight, offsets)
+    if _cuda(x) and x.dtype == torch.bfloat16:
+        r = lora_a.shape[1]
+        if r % 8:  # TMA rows must be 16-byte multiples: pad the rank with zero rows / columns
+            pad = 8 - r % 8
+            lora_a = torch.nn.functional.pad(lora_a, (0, 0, 0, pad))
+            lora_b = torch.nn.functional.pad(lora_b, (0, pad))
+        return _ExpertLinearLora.apply(x, weight, lora_a.contiguous(), lora_b.contiguous(), offsets.to(torch.int32), float(scale))
+    return grouped_gemm(x, weight, offsets) + grouped_gemm(grouped_gemm(x, lora_a, offsets), lora_b, offsets) * scale
 
 
 def sample_tokens(logits, temperature=1.0, top_k=-1, top_p=1.0, generator=None, seeds=None):

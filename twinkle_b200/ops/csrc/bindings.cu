@@ -6,7 +6,8 @@
 namespace tk {
 torch::Tensor gemm(const torch::Tensor&, const torch::Tensor&, const std::string&, const c10::optional<torch::Tensor>&, bool,
                    c10::optional<torch::ScalarType>);
-torch::Tensor grouped_gemm(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const std::string&, const c10::optional<torch::Tensor>&);
+torch::Tensor grouped_gemm(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const std::string&, const c10::optional<torch::Tensor>&,
+                           const c10::optional<torch::Tensor>&, bool);
 torch::Tensor grouped_gemm_wgrad(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, int64_t);
 std::vector<torch::Tensor> rmsnorm_fwd(const torch::Tensor&, const torch::Tensor&, double, double);
 std::vector<torch::Tensor> rmsnorm_bwd(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, double);
@@ -39,12 +40,16 @@ torch::Tensor paged_attn_decode(const torch::Tensor&, const torch::Tensor&, cons
 std::vector<torch::Tensor> sample_tokens(const torch::Tensor&, double, int64_t, double, const torch::Tensor&);
 std::vector<torch::Tensor> moe_router(const torch::Tensor&, int64_t, bool);
 void set_gemm_pair(int64_t);
+torch::Tensor moe_rows_gather(const torch::Tensor&, const torch::Tensor&, const c10::optional<torch::Tensor>&);
+torch::Tensor moe_rows_combine(const torch::Tensor&, const torch::Tensor&, const c10::optional<torch::Tensor>&);
+torch::Tensor moe_combine_wgrad(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&);
 }  // namespace tk
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &tk::gemm, py::arg("a"), py::arg("b"), py::arg("layout") = "nt", py::arg("out") = py::none(),
         py::arg("accumulate") = false, py::arg("out_dtype") = py::none());
-  m.def("grouped_gemm", &tk::grouped_gemm, py::arg("x"), py::arg("w"), py::arg("offsets"), py::arg("layout") = "nt", py::arg("group_map") = py::none());
+  m.def("grouped_gemm", &tk::grouped_gemm, py::arg("x"), py::arg("w"), py::arg("offsets"), py::arg("layout") = "nt", py::arg("group_map") = py::none(),
+        py::arg("out") = py::none(), py::arg("accumulate") = false);
   m.def("grouped_gemm_wgrad", &tk::grouped_gemm_wgrad);
   m.def("rmsnorm_fwd", &tk::rmsnorm_fwd);
   m.def("rmsnorm_bwd", &tk::rmsnorm_bwd);
@@ -70,6 +75,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sample_tokens", &tk::sample_tokens);
   m.def("moe_router", &tk::moe_router);
   m.def("set_gemm_pair", &tk::set_gemm_pair);
+  m.def("moe_rows_gather", &tk::moe_rows_gather);
+  m.def("moe_rows_combine", &tk::moe_rows_combine);
+  m.def("moe_combine_wgrad", &tk::moe_combine_wgrad);
   m.def("read_and_clear_error", &tk::read_and_clear_error, "Value of the device error word (0 = healthy); clears it.");
   m.def("num_sms", &tk::num_sms);
   m.def("launch_count", &tk::launch_count, "Number of kernels launched by this extension so far.");

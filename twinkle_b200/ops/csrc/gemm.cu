@@ -411,7 +411,7 @@ torch::Tensor gemm(const torch::Tensor& a, const torch::Tensor& b, const std::st
 // Expert-grouped GEMM.  x [R, K] with expert e owning rows [offsets[e], offsets[e+1]) (offsets multiples of 128;
 // padding rows are zero); weight [E, N, K] (nt) or [E, K, N] (nn).  Returns [R, N].
 torch::Tensor grouped_gemm(const torch::Tensor& x, const torch::Tensor& w, const torch::Tensor& offsets, const std::string& layout,
-                           const c10::optional<torch::Tensor>& group_map) {
+                           const c10::optional<torch::Tensor>& group_map, const c10::optional<torch::Tensor>& out_opt, bool accumulate) {
   check_operand(x, "x");
   TORCH_CHECK(w.is_cuda() && w.scalar_type() == torch::kBFloat16 && w.dim() == 3 && w.is_contiguous(), "weight [E, *, *] bf16 contiguous");
   TORCH_CHECK(offsets.is_cuda() && offsets.scalar_type() == torch::kInt32 && offsets.is_contiguous(), "offsets int32 on device");
@@ -427,7 +427,15 @@ torch::Tensor grouped_gemm(const torch::Tensor& x, const torch::Tensor& w, const
   else if (layout == "nn") { N = w.size(2); TORCH_CHECK(w.size(1) == K, "nn: K mismatch"); b_mn = true; }
   else TORCH_CHECK(false, "grouped layout must be nt|nn");
   // with a map some groups may be skipped (no adapter): their rows must read as zero
-  auto out = mapped ? torch::zeros({R, N}, x.options()) : torch::empty({R, N}, x.options());
+  torch::Tensor out;
+  if (out_opt.has_value() && out_opt->defined()) {
+    out = *out_opt;  // `accumulate`: out += x·W (rows outside every group keep their value)
+    TORCH_CHECK(out.is_cuda() && out.scalar_type() == torch::kBFloat16 && out.dim() == 2 && out.size(0) == R && out.size(1) == N && out.is_contiguous(),
+                "out must be [R, N] bf16 contiguous");
+  } else {
+    TORCH_CHECK(!accumulate, "accumulate needs out");
+    out = mapped ? torch::zeros({R, N}, x.options()) : torch::empty({R, N}, x.options());
+  }
   if (R == 0) return out;
   auto w2 = w.view({w.size(0) * w.size(1), w.size(2)});
   check_operand(w2, "weight");
@@ -435,7 +443,7 @@ torch::Tensor grouped_gemm(const torch::Tensor& x, const torch::Tensor& w, const
   CUtensorMap tb = b_mn ? make_tmap_2d(w2.data_ptr(), w2.size(1), w2.size(0), w2.stride(0), 64, BK)
                         : make_tmap_2d(w2.data_ptr(), w2.size(1), w2.size(0), w2.stride(0), BK, BN);
   GemmParams p{};
-  p.out = out.data_ptr(); p.M = R; p.N = N; p.K = K; p.ldo = N; p.out_fp32 = 0; p.accumulate = 0; p.err = error_word();
+  p.out = out.data_ptr(); p.M = R; p.N = N; p.K = K; p.ldo = N; p.out_fp32 = 0; p.accumulate = accumulate ? 1 : 0; p.err = error_word();
   p.offsets = offsets.data_ptr<int>(); p.num_groups = E; p.group_rows_b = w.size(1); p.mode = 1;
   p.group_map = mapped ? group_map->data_ptr<int>() : nullptr;
   // upper bound of tiles: every expert wastes at most one partial M-tile

@@ -1,0 +1,191 @@
+// Token permutation kernels of the MoE block: dispatch (token rows → expert-grouped rows) and combine
+// (expert-grouped rows → weighted sum per token).  Both directions are pure gathers — every destination row
+// has exactly one writer — so there are no atomics and the result is deterministic:
+//   rows_gather   : out[r] = scale[r] · x[src[r]]                 (src[r] < 0 → zero row)        dispatch fwd, combine bwd
+//   rows_combine  : out[t] = Σ_j w[t,j] · y[row_of[t,j]]          (row_of < 0 → skipped)          combine fwd, dispatch bwd
+//   combine_wgrad : dw[t,j] = <g[t], y[row_of[t,j]]>                                               router-weight gradient
+// One warp per destination row; 16-byte accesses; bf16 data, fp32 math.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "common.cuh"
+#include "host.h"
+
+namespace tk {
+
+using bf16 = __nv_bfloat16;
+
+__global__ void __launch_bounds__(256) rows_gather_kernel(const bf16* __restrict__ x, const int* __restrict__ src, const float* __restrict__ scale,
+                                                           bf16* __restrict__ out, int R, int H) {
+  const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = H >> 3;
+  for (int r = blockIdx.x * warps + (threadIdx.x >> 5); r < R; r += gridDim.x * warps) {
+    const int s = src[r];
+    uint4* o = reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * H);
+    if (s < 0) {
+      for (int v = lane; v < nvec; v += 32) o[v] = make_uint4(0u, 0u, 0u, 0u);
+      continue;
+    }
+    const uint4* in = reinterpret_cast<const uint4*>(x + static_cast<size_t>(s) * H);
+    if (scale == nullptr) {
+      for (int v = lane; v < nvec; v += 32) o[v] = in[v];
+    } else {
+      const float c = scale[r];
+      for (int v = lane; v < nvec; v += 32) {
+        uint4 u = in[v];
+        uint32_t* p = &u.x;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = unpack_bf16(p[k]);
+          p[k] = pack_bf16(f.x * c, f.y * c);
+        }
+        o[v] = u;
+      }
+    }
+  }
+}
+
+template <int K>
+__global__ void __launch_bounds__(256) rows_combine_kernel(const bf16* __restrict__ y, const int* __restrict__ row_of, const float* __restrict__ w,
+                                                            bf16* __restrict__ out, int T, int H) {
+  const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = H >> 3;
+  for (int t = blockIdx.x * warps + (threadIdx.x >> 5); t < T; t += gridDim.x * warps) {
+    int rows[K];
+    float ws[K];
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      rows[j] = row_of[static_cast<size_t>(t) * K + j];
+      ws[j] = w ? w[static_cast<size_t>(t) * K + j] : 1.f;
+    }
+    uint4* o = reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H);
+    for (int v = lane; v < nvec; v += 32) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < K; ++j) {
+        if (rows[j] < 0) continue;
+        const uint4 u = reinterpret_cast<const uint4*>(y + static_cast<size_t>(rows[j]) * H)[v];
+        const uint32_t* p = &u.x;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = unpack_bf16(p[k]);
+          acc[2 * k] += ws[j] * f.x;
+          acc[2 * k + 1] += ws[j] * f.y;
+        }
+      }
+      o[v] = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+    }
+  }
+}
+
+template <int K>
+__global__ void __launch_bounds__(256) combine_wgrad_kernel(const bf16* __restrict__ g, const bf16* __restrict__ y, const int* __restrict__ row_of,
+                                                             float* __restrict__ dw, int T, int H) {
+  const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = H >> 3;
+  for (int t = blockIdx.x * warps + (threadIdx.x >> 5); t < T; t += gridDim.x * warps) {
+    float acc[K];
+    int rows[K];
+#pragma unroll
+    for (int j = 0; j < K; ++j) { acc[j] = 0.f; rows[j] = row_of[static_cast<size_t>(t) * K + j]; }
+    const uint4* gr = reinterpret_cast<const uint4*>(g + static_cast<size_t>(t) * H);
+    for (int v = lane; v < nvec; v += 32) {
+      const uint4 ug = gr[v];
+      const uint32_t* pg = &ug.x;
+      float gf[8];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) { const float2 f = unpack_bf16(pg[k]); gf[2 * k] = f.x; gf[2 * k + 1] = f.y; }
+#pragma unroll
+      for (int j = 0; j < K; ++j) {
+        if (rows[j] < 0) continue;
+        const uint4 u = reinterpret_cast<const uint4*>(y + static_cast<size_t>(rows[j]) * H)[v];
+        const uint32_t* p = &u.x;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = unpack_bf16(p[k]);
+          acc[j] += gf[2 * k] * f.x + gf[2 * k + 1] * f.y;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      const float s = warp_sum(acc[j]);
+      if (lane == 0) dw[static_cast<size_t>(t) * K + j] = s;
+    }
+  }
+}
+
+static void check_rows(const torch::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16 && t.dim() == 2 && t.is_contiguous() && t.size(1) % 8 == 0, name,
+              ": [rows, H] bf16 contiguous with H % 8 == 0");
+}
+static int grid_for(long rows) { return static_cast<int>(std::max<long>(1, std::min<long>((rows + 7) / 8, static_cast<long>(num_sms()) * 8))); }
+
+torch::Tensor moe_rows_gather(const torch::Tensor& x, const torch::Tensor& src, const c10::optional<torch::Tensor>& scale) {
+  check_rows(x, "x");
+  TORCH_CHECK(src.is_cuda() && src.scalar_type() == torch::kInt32 && src.is_contiguous(), "src int32");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int R = src.numel(), H = x.size(1);
+  auto out = torch::empty({R, H}, x.options());
+  if (R == 0) return out;
+  const float* sc = nullptr;
+  if (scale.has_value() && scale->defined()) {
+    TORCH_CHECK(scale->scalar_type() == torch::kFloat32 && scale->numel() == R && scale->is_contiguous(), "scale fp32 [R]");
+    sc = scale->data_ptr<float>();
+  }
+  rows_gather_kernel<<<grid_for(R), 256, 0, at::cuda::getCurrentCUDAStream()>>>(reinterpret_cast<const bf16*>(x.data_ptr()), src.data_ptr<int>(), sc,
+                                                                               reinterpret_cast<bf16*>(out.data_ptr()), R, H);
+  count_launch();
+  TK_CUDA_CHECK(cudaGetLastError());
+  return out;
+}
+
+#define TK_K_SWITCH(K, BODY)                                   \
+  switch (K) {                                                 \
+    case 1: { constexpr int KK = 1; BODY; break; }             \
+    case 2: { constexpr int KK = 2; BODY; break; }             \
+    case 4: { constexpr int KK = 4; BODY; break; }             \
+    case 6: { constexpr int KK = 6; BODY; break; }             \
+    case 8: { constexpr int KK = 8; BODY; break; }             \
+    default: TORCH_CHECK(false, "top-k must be 1, 2, 4, 6 or 8"); \
+  }
+
+torch::Tensor moe_rows_combine(const torch::Tensor& y, const torch::Tensor& row_of, const c10::optional<torch::Tensor>& w) {
+  check_rows(y, "y");
+  TORCH_CHECK(row_of.is_cuda() && row_of.scalar_type() == torch::kInt32 && row_of.dim() == 2 && row_of.is_contiguous(), "row_of int32 [T, k]");
+  c10::cuda::CUDAGuard guard(y.device());
+  const int T = row_of.size(0), K = row_of.size(1), H = y.size(1);
+  auto out = torch::empty({T, H}, y.options());
+  if (T == 0) return out;
+  const float* wp = nullptr;
+  if (w.has_value() && w->defined()) {
+    TORCH_CHECK(w->scalar_type() == torch::kFloat32 && w->numel() == static_cast<int64_t>(T) * K && w->is_contiguous(), "w fp32 [T, k]");
+    wp = w->data_ptr<float>();
+  }
+  auto stream = at::cuda::getCurrentCUDAStream();
+  TK_K_SWITCH(K, (rows_combine_kernel<KK><<<grid_for(T), 256, 0, stream>>>(reinterpret_cast<const bf16*>(y.data_ptr()), row_of.data_ptr<int>(), wp,
+                                                                           reinterpret_cast<bf16*>(out.data_ptr()), T, H)));
+  count_launch();
+  TK_CUDA_CHECK(cudaGetLastError());
+  return out;
+}
+
+torch::Tensor moe_combine_wgrad(const torch::Tensor& g, const torch::Tensor& y, const torch::Tensor& row_of) {
+  check_rows(g, "g");
+  check_rows(y, "y");
+  TORCH_CHECK(row_of.scalar_type() == torch::kInt32 && row_of.dim() == 2 && row_of.is_contiguous() && row_of.size(0) == g.size(0), "row_of int32 [T, k]");
+  TORCH_CHECK(g.size(1) == y.size(1), "H mismatch");
+  c10::cuda::CUDAGuard guard(y.device());
+  const int T = row_of.size(0), K = row_of.size(1), H = y.size(1);
+  auto dw = torch::empty({T, K}, y.options().dtype(torch::kFloat32));
+  if (T == 0) return dw;
+  auto stream = at::cuda::getCurrentCUDAStream();
+  TK_K_SWITCH(K, (combine_wgrad_kernel<KK><<<grid_for(T), 256, 0, stream>>>(reinterpret_cast<const bf16*>(g.data_ptr()), reinterpret_cast<const bf16*>(y.data_ptr()),
+                                                                            row_of.data_ptr<int>(), dw.data_ptr<float>(), T, H)));
+  count_launch();
+  TK_CUDA_CHECK(cudaGetLastError());
+  return dw;
+}
+
+}  // namespace tk

@@ -55,13 +55,17 @@ def ep_replica_group_for(mesh):
     return _EP_GROUPS.get((id(mesh), mesh.ep_size or 1), (None, None))[1]
 
 
-def expert_layout(expert_ids: torch.Tensor, num_experts: int, align: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, int]:
+def expert_layout(expert_ids: torch.Tensor, num_experts: int, align: int,
+                  counts: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, int]:
     """Rows for an expert-grouped GEMM.  ``expert_ids [n]`` → (``order`` = argsort by expert, ``rows [n]`` =
     destination row of ``order[i]``, ``offsets [E+1]`` int32 with every expert's segment starting on a
     multiple of ``align``, upper bound of total rows known without a device sync)."""
     n = expert_ids.numel()
     order = torch.argsort(expert_ids, stable=True)
-    counts = torch.bincount(expert_ids, minlength=num_experts)
+    if counts is None:  # scatter-add instead of bincount: no device→host read
+        counts = torch.zeros(num_experts, dtype=torch.int64, device=expert_ids.device).scatter_add_(
+            0, expert_ids, torch.ones_like(expert_ids, dtype=torch.int64))
+    counts = counts.to(torch.int64)
     padded = (counts + align - 1) // align * align
     offsets = torch.zeros(num_experts + 1, dtype=torch.int64, device=expert_ids.device)
     offsets[1:] = padded.cumsum(0)
