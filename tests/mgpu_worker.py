@@ -10,6 +10,43 @@ import torch
 import torch.distributed as dist
 
 
+def ep_checks(rank, world, dev, report):
+    """Expert parallel over all ranks (NCCL all-to-all and peer-memory pulls) vs the single-GPU curve."""
+    from twinkle_b200.model import TransformersModel
+    from twinkle_b200.models.config import preset
+    from twinkle_b200.utils.device_mesh import DeviceMesh
+    cfg = preset('qwen3-30b-a3b', num_hidden_layers=2, hidden_size=512, num_attention_heads=4, num_key_value_heads=2,
+                 vocab_size=1024, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=256, router_aux_loss_coef=0.0)
+    g = torch.Generator().manual_seed(11)
+    feats = []
+    for _ in range(2 * world):
+        ids = torch.randint(0, cfg.vocab_size, (129, ), generator=g)
+        feats.append({'input_ids': ids[:-1], 'labels': ids[1:]})
+
+    def curve(mesh, backend, my_feats):
+        m = TransformersModel(config=cfg, device_mesh=mesh, seed=0, comm_backend=backend, device=dev)
+        m.set_optimizer('AdamW', lr=1e-3)
+        out = []
+        for _ in range(4):
+            o = m.forward_backward(inputs=my_feats)
+            m.clip_grad_and_step(max_grad_norm=1.0)
+            t = torch.tensor([o['loss'] * o['num_tokens'], o['num_tokens']], device=dev, dtype=torch.float64)
+            if mesh.world_size > 1:
+                dist.all_reduce(t)
+            out.append(float(t[0] / t[1]))
+        return out
+
+    single = [curve(DeviceMesh.from_sizes(dp_size=1), 'nccl', feats) if rank == 0 else None]
+    dist.broadcast_object_list(single, src=0)
+    single = single[0]
+    for backend in ('nccl', 'symm'):
+        mesh = DeviceMesh.from_sizes(fsdp_size=world, dp_size=None, ep_size=world)
+        sl = mesh.get_slice(len(feats), mesh.get_data_rank_from_global_rank(rank))
+        c = curve(mesh, backend, feats[sl])
+        diff = max(abs(a - b) for a, b in zip(single, c))
+        report(f'ep{world}_{backend}_matches_single', diff < 4e-2, single=single, multi=c)
+
+
 def main():
     rank, world, local = int(os.environ['RANK']), int(os.environ['WORLD_SIZE']), int(os.environ['LOCAL_RANK'])
     torch.cuda.set_device(local)
@@ -30,6 +67,14 @@ def main():
         if not t.item():
             dist.destroy_process_group()
             sys.exit(1)
+
+    only = os.environ.get('TK_MGPU_ONLY', '')
+    if only == 'ep':
+        ep_checks(rank, world, dev, report)
+        report('error_word_end', E.read_and_clear_error() == 0)
+        dist.barrier()
+        dist.destroy_process_group()
+        return
 
     # ---- 1. peer all-gather / reduce-scatter kernels against NCCL
     sc = SymmCommunicator(None, dev)
@@ -108,6 +153,7 @@ def main():
         c = curve(mesh, backend, feats)
         diff = max(abs(a - b) for a, b in zip(single, c))
         report(f'ulysses{world}_{backend}_matches_single', diff < 3e-2, single=single, multi=c)
+    ep_checks(rank, world, dev, report)
     report('error_word_end', E.read_and_clear_error() == 0)
     dist.barrier()
     dist.destroy_process_group()

@@ -176,7 +176,7 @@ class TransformersModel(TwinkleModel):
         comm = self._dp_comm()
         if self.device_mesh.ep_size and self.device_mesh.ep_size > 1 and self.config.is_moe:
             from ..parallel.expert import apply_expert_parallel
-            apply_expert_parallel(self.model, self.device_mesh, self.config)
+            apply_expert_parallel(self.model, self.device_mesh, self.config, self.comm_backend)
         if self.sp_size > 1:
             from ..parallel.ulysses import apply_ulysses
             apply_ulysses(self.model, self.device_mesh, self.config, self.comm_backend)
@@ -476,18 +476,35 @@ class TransformersModel(TwinkleModel):
         denom = comm.all_reduce_scalar(og.train_status.num_tokens, 'sum')
         denom = denom if denom > 0 else 1.0
         sq = torch.zeros((), dtype=torch.float32, device=self.device)
+        sq_ep = torch.zeros((), dtype=torch.float32, device=self.device)  # expert-parallel tensors: distinct per EP rank
+        has_ep = False
         slices = self._trainable_lora_slices(og)
         if slices:
             for _, p, slot in slices:
                 if p.grad is not None:
-                    sq = sq + ops.sumsq(p.grad[slot].contiguous())
+                    v = ops.sumsq(p.grad[slot].contiguous())
+                    if getattr(p, '_ep_local', False):
+                        sq_ep, has_ep = sq_ep + v, True
+                    else:
+                        sq = sq + v
         elif self.engine is not None:
             sq_sh = self.engine.grad_norm_sq()
             comm.all_reduce(sq_sh)
             sq = sq + sq_sh
             for _, p in self.engine.replicated:
                 if p.requires_grad and p.grad is not None:
-                    sq = sq + ops.sumsq(p.grad)
+                    v = ops.sumsq(p.grad)
+                    if getattr(p, '_ep_local', False):
+                        sq_ep, has_ep = sq_ep + v, True
+                    else:
+                        sq = sq + v
+        ep_comm = getattr(self.model, '_ep_comm', None)
+        if ep_comm is not None and ep_comm.world_size > 1:  # every EP rank joins, with or without local expert grads
+            sq_ep = sq_ep.reshape(1)
+            ep_comm.all_reduce(sq_ep)
+            sq = sq + sq_ep[0]
+        elif has_ep:
+            sq = sq + sq_ep
         norm = float(sq.sqrt()) / denom
         if self.device.type == 'cuda':
             code = ops.ext().read_and_clear_error()

@@ -43,6 +43,10 @@ void set_gemm_pair(int64_t);
 torch::Tensor moe_rows_gather(const torch::Tensor&, const torch::Tensor&, const c10::optional<torch::Tensor>&);
 torch::Tensor moe_rows_combine(const torch::Tensor&, const torch::Tensor&, const c10::optional<torch::Tensor>&);
 torch::Tensor moe_combine_wgrad(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&);
+torch::Tensor ep_rows_gather(const std::vector<int64_t>&, const std::vector<int64_t>&, const std::vector<int64_t>&, const torch::Tensor&, const torch::Tensor&, int64_t,
+                             const torch::Tensor&);
+torch::Tensor ep_rows_combine(const std::vector<int64_t>&, const torch::Tensor&, const torch::Tensor&, const c10::optional<torch::Tensor>&, int64_t);
+torch::Tensor ep_combine_wgrad(const torch::Tensor&, const std::vector<int64_t>&, const torch::Tensor&, const torch::Tensor&);
 }  // namespace tk
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -78,6 +82,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_rows_gather", &tk::moe_rows_gather);
   m.def("moe_rows_combine", &tk::moe_rows_combine);
   m.def("moe_combine_wgrad", &tk::moe_combine_wgrad);
+  m.def("ep_rows_gather", &tk::ep_rows_gather);
+  m.def("ep_rows_combine", &tk::ep_rows_combine);
+  m.def("ep_combine_wgrad", &tk::ep_combine_wgrad);
   m.def("read_and_clear_error", &tk::read_and_clear_error, "Value of the device error word (0 = healthy); clears it.");
   m.def("num_sms", &tk::num_sms);
   m.def("launch_count", &tk::launch_count, "Number of kernels launched by this extension so far.");

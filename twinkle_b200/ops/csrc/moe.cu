@@ -189,3 +189,200 @@ torch::Tensor moe_combine_wgrad(const torch::Tensor& g, const torch::Tensor& y, 
 }
 
 }  // namespace tk
+
+// ------------------------------------------------------------------------------------------------------------
+// Expert-parallel variants: the same gathers, but the source rows live in the symmetric buffers of the peer GPUs
+// of the expert-parallel group and are read over NVLink from inside the kernel (plain peer loads).  The
+// all-to-all "dispatch" is therefore fused with the regrouping into the 128-aligned expert layout, and the
+// all-to-all "combine" with the weighted sum over the k experts of a token: no staging buffer, no NCCL call and no
+// host-side split sizes.  Callers publish their buffers, pass one cross-GPU flag barrier, then launch these.
+namespace tk {
+
+constexpr int EP_MAX_PEERS = 8;
+struct EpPtrs {
+  const void* p[EP_MAX_PEERS];
+};
+
+// out[r] = scale · x_s[tok_s[pos]] with s = src_rank[r], pos = src_pos[r]; s < 0 → zero row.
+// `total_rows` (device int) is checked against R once: rows that did not fit are reported through the error word.
+__global__ void __launch_bounds__(256) ep_rows_gather_kernel(EpPtrs xs, EpPtrs toks, EpPtrs ws, int use_w, const int* __restrict__ src_rank,
+                                                              const int* __restrict__ src_pos, bf16* __restrict__ out, int R, int H,
+                                                              const int* __restrict__ total_rows, int* err) {
+  if (blockIdx.x == 0 && threadIdx.x == 0 && total_rows != nullptr && *total_rows > R) atomicCAS(err, 0, ERR_BOUNDS);
+  const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = H >> 3;
+  for (int r = blockIdx.x * warps + (threadIdx.x >> 5); r < R; r += gridDim.x * warps) {
+    const int s = src_rank[r];
+    uint4* o = reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * H);
+    if (s < 0) {
+      for (int v = lane; v < nvec; v += 32) o[v] = make_uint4(0u, 0u, 0u, 0u);
+      continue;
+    }
+    const int pos = src_pos[r];
+    const int tok = reinterpret_cast<const int*>(toks.p[s])[pos];
+    const float c = use_w ? reinterpret_cast<const float*>(ws.p[s])[pos] : 1.f;
+    const uint4* in = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(xs.p[s]) + static_cast<size_t>(tok) * H);
+    for (int v = lane; v < nvec; v += 32) {
+      uint4 u = in[v];
+      if (use_w) {
+        uint32_t* p = &u.x;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = unpack_bf16(p[k]);
+          p[k] = pack_bf16(f.x * c, f.y * c);
+        }
+      }
+      o[v] = u;
+    }
+  }
+}
+
+// out[t] = Σ_j w[t,j] · y_{d}[row] with d = dst_rank[t,j] (< 0 → skipped), row = dst_row[t,j].
+template <int K>
+__global__ void __launch_bounds__(256) ep_rows_combine_kernel(EpPtrs ys, const int* __restrict__ dst_rank, const int* __restrict__ dst_row,
+                                                               const float* __restrict__ w, bf16* __restrict__ out, int T, int H) {
+  const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = H >> 3;
+  for (int t = blockIdx.x * warps + (threadIdx.x >> 5); t < T; t += gridDim.x * warps) {
+    const uint4* src[K];
+    float ws[K];
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      const int d = dst_rank[static_cast<size_t>(t) * K + j];
+      const int row = dst_row[static_cast<size_t>(t) * K + j];
+      src[j] = d < 0 ? nullptr : reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(ys.p[d]) + static_cast<size_t>(row) * H);
+      ws[j] = w ? w[static_cast<size_t>(t) * K + j] : 1.f;
+    }
+    uint4* o = reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H);
+    for (int v = lane; v < nvec; v += 32) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < K; ++j) {
+        if (src[j] == nullptr) continue;
+        const uint4 u = src[j][v];
+        const uint32_t* p = &u.x;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = unpack_bf16(p[k]);
+          acc[2 * k] += ws[j] * f.x;
+          acc[2 * k + 1] += ws[j] * f.y;
+        }
+      }
+      o[v] = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+    }
+  }
+}
+
+// dw[t,j] = <g[t], y_{d}[row]>
+template <int K>
+__global__ void __launch_bounds__(256) ep_combine_wgrad_kernel(const bf16* __restrict__ g, EpPtrs ys, const int* __restrict__ dst_rank,
+                                                                const int* __restrict__ dst_row, float* __restrict__ dw, int T, int H) {
+  const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = H >> 3;
+  for (int t = blockIdx.x * warps + (threadIdx.x >> 5); t < T; t += gridDim.x * warps) {
+    const uint4* src[K];
+    float acc[K];
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      const int d = dst_rank[static_cast<size_t>(t) * K + j];
+      const int row = dst_row[static_cast<size_t>(t) * K + j];
+      src[j] = d < 0 ? nullptr : reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(ys.p[d]) + static_cast<size_t>(row) * H);
+      acc[j] = 0.f;
+    }
+    const uint4* gr = reinterpret_cast<const uint4*>(g + static_cast<size_t>(t) * H);
+    for (int v = lane; v < nvec; v += 32) {
+      const uint4 ug = gr[v];
+      const uint32_t* pg = &ug.x;
+      float gf[8];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) { const float2 f = unpack_bf16(pg[k]); gf[2 * k] = f.x; gf[2 * k + 1] = f.y; }
+#pragma unroll
+      for (int j = 0; j < K; ++j) {
+        if (src[j] == nullptr) continue;
+        const uint4 u = src[j][v];
+        const uint32_t* p = &u.x;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = unpack_bf16(p[k]);
+          acc[j] += gf[2 * k] * f.x + gf[2 * k + 1] * f.y;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      const float s = warp_sum(acc[j]);
+      if (lane == 0) dw[static_cast<size_t>(t) * K + j] = s;
+    }
+  }
+}
+
+static EpPtrs to_ptrs(const std::vector<int64_t>& v) {
+  TORCH_CHECK(v.size() <= EP_MAX_PEERS, "expert-parallel group larger than ", EP_MAX_PEERS);
+  EpPtrs p{};
+  for (size_t i = 0; i < v.size(); ++i) p.p[i] = reinterpret_cast<const void*>(v[i]);
+  return p;
+}
+static void check_i32(const torch::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kInt32 && t.is_contiguous(), name, " must be a contiguous int32 CUDA tensor");
+}
+
+torch::Tensor ep_rows_gather(const std::vector<int64_t>& x_ptrs, const std::vector<int64_t>& tok_ptrs, const std::vector<int64_t>& w_ptrs,
+                             const torch::Tensor& src_rank, const torch::Tensor& src_pos, int64_t H, const torch::Tensor& total_rows) {
+  check_i32(src_rank, "src_rank");
+  check_i32(src_pos, "src_pos");
+  check_i32(total_rows, "total_rows");
+  TORCH_CHECK(H % 8 == 0 && src_rank.numel() == src_pos.numel(), "bad shapes");
+  c10::cuda::CUDAGuard guard(src_rank.device());
+  const int R = src_rank.numel();
+  auto out = torch::empty({R, H}, src_rank.options().dtype(torch::kBFloat16));
+  if (R == 0) return out;
+  ep_rows_gather_kernel<<<grid_for(R), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+      to_ptrs(x_ptrs), to_ptrs(tok_ptrs), to_ptrs(w_ptrs), w_ptrs.empty() ? 0 : 1, src_rank.data_ptr<int>(), src_pos.data_ptr<int>(),
+      reinterpret_cast<bf16*>(out.data_ptr()), R, static_cast<int>(H), total_rows.data_ptr<int>(), error_word());
+  count_launch();
+  TK_CUDA_CHECK(cudaGetLastError());
+  return out;
+}
+
+torch::Tensor ep_rows_combine(const std::vector<int64_t>& y_ptrs, const torch::Tensor& dst_rank, const torch::Tensor& dst_row,
+                              const c10::optional<torch::Tensor>& w, int64_t H) {
+  check_i32(dst_rank, "dst_rank");
+  check_i32(dst_row, "dst_row");
+  TORCH_CHECK(dst_rank.dim() == 2 && dst_row.sizes() == dst_rank.sizes() && H % 8 == 0, "bad shapes");
+  c10::cuda::CUDAGuard guard(dst_rank.device());
+  const int T = dst_rank.size(0), K = dst_rank.size(1);
+  auto out = torch::empty({T, H}, dst_rank.options().dtype(torch::kBFloat16));
+  if (T == 0) return out;
+  const float* wp = nullptr;
+  if (w.has_value() && w->defined()) {
+    TORCH_CHECK(w->scalar_type() == torch::kFloat32 && w->is_contiguous() && w->numel() == static_cast<int64_t>(T) * K, "w fp32 [T, k]");
+    wp = w->data_ptr<float>();
+  }
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const EpPtrs ys = to_ptrs(y_ptrs);
+  TK_K_SWITCH(K, (ep_rows_combine_kernel<KK><<<grid_for(T), 256, 0, stream>>>(ys, dst_rank.data_ptr<int>(), dst_row.data_ptr<int>(), wp,
+                                                                              reinterpret_cast<bf16*>(out.data_ptr()), T, static_cast<int>(H))));
+  count_launch();
+  TK_CUDA_CHECK(cudaGetLastError());
+  return out;
+}
+
+torch::Tensor ep_combine_wgrad(const torch::Tensor& g, const std::vector<int64_t>& y_ptrs, const torch::Tensor& dst_rank, const torch::Tensor& dst_row) {
+  check_rows(g, "g");
+  check_i32(dst_rank, "dst_rank");
+  check_i32(dst_row, "dst_row");
+  c10::cuda::CUDAGuard guard(g.device());
+  const int T = dst_rank.size(0), K = dst_rank.size(1), H = g.size(1);
+  TORCH_CHECK(g.size(0) == T, "row mismatch");
+  auto dw = torch::empty({T, K}, g.options().dtype(torch::kFloat32));
+  if (T == 0) return dw;
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const EpPtrs ys = to_ptrs(y_ptrs);
+  TK_K_SWITCH(K, (ep_combine_wgrad_kernel<KK><<<grid_for(T), 256, 0, stream>>>(reinterpret_cast<const bf16*>(g.data_ptr()), ys, dst_rank.data_ptr<int>(),
+                                                                               dst_row.data_ptr<int>(), dw.data_ptr<float>(), T, H)));
+  count_launch();
+  TK_CUDA_CHECK(cudaGetLastError());
+  return dw;
+}
+
+}  // namespace tk

@@ -132,16 +132,32 @@ class ExpertParallel:
         return out.index_add(0, tok, ret)
 
 
-def apply_expert_parallel(model, mesh, cfg, backend: str = 'auto') -> None:
+def apply_expert_parallel(model, mesh, cfg, backend: str = 'auto'):
     """Keep only this rank's experts (a view of the freshly initialised full tensors, so every layout starts
     from identical values) and route MoE blocks through ``ExpertParallel``."""
     dev = next(model.parameters()).device
     comm = Communicator(ep_group_for(mesh), dev)
     if comm.world_size <= 1:
         return
-    strat = ExpertParallel(comm, cfg.num_experts)
+    strat = None
+    if dev.type == 'cuda' and backend in ('auto', 'symm'):
+        try:
+            from .expert_symm import SymmExpertParallel
+            from .symm import SymmCommunicator
+            strat = SymmExpertParallel(SymmCommunicator(comm.group, dev), cfg.num_experts)
+        except Exception as e:  # the NCCL data plane stays correct
+            if backend == 'symm':
+                raise
+            import logging
+            logging.getLogger('twinkle_b200').warning(f'peer-memory expert parallel unavailable ({e}); using NCCL all-to-all')
+    if strat is None:
+        strat = ExpertParallel(comm, cfg.num_experts)
     El = strat.local
     lo = comm.rank * El
+    rep_group = ep_replica_group_for(mesh)
+    rep_comm = Communicator(rep_group, dev) if rep_group is not None else None
+    if rep_comm is not None and rep_comm.world_size <= 1:
+        rep_comm = None
     for layer in model.layers:
         if not getattr(layer, 'is_moe', False):
             continue
@@ -151,5 +167,12 @@ def apply_expert_parallel(model, mesh, cfg, backend: str = 'auto') -> None:
             ex.down_proj = torch.nn.Parameter(ex.down_proj.data[lo:lo + El].clone(), requires_grad=ex.down_proj.requires_grad)
             for key in list(ex.lora.keys()):
                 ex.lora[key] = torch.nn.Parameter(ex.lora[key].data[:, lo:lo + El].clone())
+        # expert tensors differ per EP rank: their gradients are summed only over the ranks that hold the same
+        # experts, and their squared norms are summed over the EP group when the global norm is taken
+        for p in [ex.gate_up_proj, ex.down_proj] + list(ex.lora.values()):
+            p._ep_local = True
+            p._ep_replica_comm = rep_comm
         ex.num_local, ex.first_expert = El, lo
         layer.mlp.moe_parallel = strat
+    model._ep_comm = comm
+    return strat

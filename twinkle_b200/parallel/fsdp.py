@@ -467,7 +467,12 @@ class FSDPEngine:
         if self.comm.world_size > 1:
             for _, p in self.replicated:
                 if p.requires_grad and p.grad is not None:
-                    self.comm.all_reduce(p.grad)
+                    if getattr(p, '_ep_local', False):  # distinct experts per rank: reduce over same-expert replicas only
+                        rc = getattr(p, '_ep_replica_comm', None)
+                        if rc is not None:
+                            rc.all_reduce(p.grad)
+                    else:
+                        self.comm.all_reduce(p.grad)
 
     def end_forward_only(self) -> None:
         self.root.reshard(self.pool)
