@@ -47,6 +47,44 @@ def ep_checks(rank, world, dev, report):
         report(f'ep{world}_{backend}_matches_single', diff < 4e-2, single=single, multi=c)
 
 
+def megatron_checks(rank, world, dev, report):
+    """Tensor × pipeline parallel backend on GPUs (NCCL p2p + TP collectives) vs the single-GPU curve."""
+    from twinkle_b200.model import TransformersModel
+    from twinkle_b200.model.megatron import MegatronModel
+    from twinkle_b200.models.config import preset
+    from twinkle_b200.utils.device_mesh import DeviceMesh
+    cfg = preset('qwen3-8b', num_hidden_layers=4, hidden_size=512, intermediate_size=1024, num_attention_heads=8,
+                 num_key_value_heads=2, vocab_size=4096)
+    g = torch.Generator().manual_seed(13)
+    feats = []
+    for n in (256, 192, 128, 256):
+        ids = torch.randint(0, cfg.vocab_size, (n + 1, ), generator=g)
+        feats.append({'input_ids': ids[:-1], 'labels': ids[1:]})
+
+    def curve(m):
+        m.set_optimizer('AdamW', lr=1e-3)
+        out = []
+        for _ in range(3):
+            o = m.forward_backward(inputs=feats, micro_batch_size=1)
+            m.clip_grad_and_step(max_grad_norm=1.0)
+            out.append(float(o['loss']))
+        return out
+
+    single = [curve(TransformersModel(config=cfg, device_mesh=DeviceMesh.from_sizes(dp_size=1), seed=0, comm_backend='nccl', device=dev))
+              if rank == 0 else None]
+    dist.broadcast_object_list(single, src=0)
+    single = single[0]
+    layouts = [(2, 1, 1), (1, 2, 1)] if world == 2 else [(2, 2, 2), (2, 2, 1)]
+    for tp, pp, vpp in layouts:
+        mesh = DeviceMesh.from_sizes(tp_size=tp, pp_size=pp, dp_size=world // (tp * pp), vpp_size=vpp, sequence_parallel=tp > 1)
+        c = curve(MegatronModel(config=cfg, device_mesh=mesh, seed=0, device=dev))
+        vals = [None] * world
+        dist.all_gather_object(vals, c)
+        c = next(v for v in vals if v and v[0] == v[0] and v[0] != 0.0)  # a rank that holds the loss (last stage)
+        diff = max(abs(a - b) for a, b in zip(single, c))
+        report(f'megatron_tp{tp}_pp{pp}_vpp{vpp}_matches_single', diff < 5e-2, single=single, multi=c)
+
+
 def main():
     rank, world, local = int(os.environ['RANK']), int(os.environ['WORLD_SIZE']), int(os.environ['LOCAL_RANK'])
     torch.cuda.set_device(local)
@@ -69,8 +107,8 @@ def main():
             sys.exit(1)
 
     only = os.environ.get('TK_MGPU_ONLY', '')
-    if only == 'ep':
-        ep_checks(rank, world, dev, report)
+    if only in ('ep', 'megatron'):
+        (ep_checks if only == 'ep' else megatron_checks)(rank, world, dev, report)
         report('error_word_end', E.read_and_clear_error() == 0)
         dist.barrier()
         dist.destroy_process_group()
