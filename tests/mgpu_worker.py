@@ -47,6 +47,93 @@ def ep_checks(rank, world, dev, report):
         report(f'ep{world}_{backend}_matches_single', diff < 4e-2, single=single, multi=c)
 
 
+def tp_fused_checks(rank, world, dev, report):
+    """GEMM+collective kernels against NCCL collectives around torch matmuls, with device-side timing."""
+    from twinkle_b200 import ops
+    from twinkle_b200.parallel.symm import SymmCommunicator
+    from twinkle_b200.parallel.tensor_fused import FusedTP
+    E = ops.ext()
+    f = FusedTP(SymmCommunicator(None, dev))
+    tp = world
+    torch.manual_seed(100 + rank)
+
+    def rel(a, b):
+        return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
+
+    def timeit(fn, iters=8):
+        for _ in range(3):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / iters], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    T, H, I = 8192, 5120, 25600
+    rows = T // tp
+    # column-parallel: gather(x) @ W_col^T, W_col [I/tp, H]
+    x = torch.randn(rows, H, device=dev).bfloat16()
+    wc = (torch.randn(I // tp, H, device=dev) * 0.02).bfloat16()
+    full = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
+    dist.all_gather_into_tensor(full, x)
+    want = full.float() @ wc.float().t()
+    y, gathered = f.ag_gemm(x, wc, 'nt')
+    torch.cuda.synchronize()
+    report('ag_gemm_nt', torch.equal(gathered, full) and rel(y, want) < 4e-3, rel=rel(y, want))
+    # row-parallel: reduce_scatter(a @ W_row^T), a [T, I/tp], W_row [H, I/tp]
+    a = torch.randn(T, I // tp, device=dev).bfloat16()
+    wr = (torch.randn(H, I // tp, device=dev) * 0.02).bfloat16()
+    part = (a.float() @ wr.float().t())
+    dist.all_reduce(part)
+    want_rs = part[rank * rows:(rank + 1) * rows]
+    out = f.gemm_rs(a, wr, 'nt')
+    torch.cuda.synchronize()
+    report('gemm_rs_nt', rel(out, want_rs) < 6e-3, rel=rel(out, want_rs))
+    # dgrad forms ('nn')
+    gy = torch.randn(T, I // tp, device=dev).bfloat16()
+    part = gy.float() @ wc.float()
+    dist.all_reduce(part)
+    out = f.gemm_rs(gy, wc, 'nn')
+    torch.cuda.synchronize()
+    report('gemm_rs_nn', rel(out, part[rank * rows:(rank + 1) * rows]) < 6e-3)
+    gl = torch.randn(rows, H, device=dev).bfloat16()
+    gfull = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
+    dist.all_gather_into_tensor(gfull, gl)
+    gx, gg = f.ag_gemm(gl, wr, 'nn')
+    torch.cuda.synchronize()
+    report('ag_gemm_nn', torch.equal(gg, gfull) and rel(gx, gfull.float() @ wr.float()) < 4e-3)
+
+    # timing against NCCL + library GEMM (device events, max over ranks)
+    def nccl_col():
+        dist.all_gather_into_tensor(full, x)
+        return torch.nn.functional.linear(full, wc)
+
+    def nccl_row():
+        p_ = torch.nn.functional.linear(a, wr)
+        o = torch.empty(rows, H, device=dev, dtype=torch.bfloat16)
+        dist.reduce_scatter_tensor(o, p_)
+        return o
+
+    t_ag, t_ag_ref = timeit(lambda: f.ag_gemm(x, wc, 'nt')), timeit(nccl_col)
+    t_rs, t_rs_ref = timeit(lambda: f.gemm_rs(a, wr, 'nt')), timeit(nccl_row)
+    flops = 2.0 * T * H * (I // tp)
+    link = 770e9
+    ag_bytes = (tp - 1) * rows * H * 2          # what one rank must pull
+    rs_bytes = (tp - 1) * rows * H * 2          # what one rank must push
+    roof_ag = max(flops / 1722.5e12, ag_bytes / link) * 1e3
+    roof_rs = max(flops / 1722.5e12, rs_bytes / link) * 1e3
+    report('tp_fused_timing', True, tp=tp, shape=[T, H, I // tp], ag_gemm_ms=t_ag, nccl_ag_plus_gemm_ms=t_ag_ref, gemm_rs_ms=t_rs,
+           gemm_plus_nccl_rs_ms=t_rs_ref, roofline_ms_ag=roof_ag, roofline_ms_rs=roof_rs, frac_of_roofline_ag=roof_ag / t_ag,
+           frac_of_roofline_rs=roof_rs / t_rs)
+    report('tp_fused_error_word', E.read_and_clear_error() == 0)
+
+
 def megatron_checks(rank, world, dev, report):
     """Tensor × pipeline parallel backend on GPUs (NCCL p2p + TP collectives) vs the single-GPU curve."""
     from twinkle_b200.model import TransformersModel
@@ -57,7 +144,7 @@ def megatron_checks(rank, world, dev, report):
                  num_key_value_heads=2, vocab_size=4096)
     g = torch.Generator().manual_seed(13)
     feats = []
-    for n in (256, 192, 128, 256):
+    for n in (1024, 512, 768, 1024):  # multiples of 256 rows per TP rank: the fused GEMM+collective kernels take these
         ids = torch.randint(0, cfg.vocab_size, (n + 1, ), generator=g)
         feats.append({'input_ids': ids[:-1], 'labels': ids[1:]})
 
@@ -107,8 +194,8 @@ def main():
             sys.exit(1)
 
     only = os.environ.get('TK_MGPU_ONLY', '')
-    if only in ('ep', 'megatron'):
-        (ep_checks if only == 'ep' else megatron_checks)(rank, world, dev, report)
+    if only in ('ep', 'megatron', 'tp_fused'):
+        {'ep': ep_checks, 'megatron': megatron_checks, 'tp_fused': tp_fused_checks}[only](rank, world, dev, report)
         report('error_word_end', E.read_and_clear_error() == 0)
         dist.barrier()
         dist.destroy_process_group()

@@ -35,7 +35,7 @@ from ..models.decoder import DecoderModel, PackedBatch, build_model
 from ..module.scheduler import scheduler_mapping
 from ..parallel.comm import Communicator
 from ..parallel.pipeline import PipelineRunner
-from ..parallel.tensor import SliceTokens, apply_tensor_parallel
+from ..parallel.tensor import SliceTokens, apply_tensor_parallel, make_fused_tp
 from ..processor import InputProcessor
 from ..utils.device_mesh import DeviceMesh
 from ..utils.platform import Platform
@@ -61,9 +61,10 @@ def split_layers(num_layers: int, pp: int, vpp: int) -> List[List[Tuple[int, int
 class MegatronModel(TwinkleModel):
 
     def __init__(self, model_id: Optional[str] = None, config=None, device_mesh: DeviceMesh = None, mixed_precision: str = 'bf16',
-                 seed: int = 0, device=None, **kwargs):
+                 seed: int = 0, device=None, comm_backend: str = 'auto', **kwargs):
         self._try_init_process_group()
         self.device_mesh = device_mesh or DeviceMesh.from_sizes(dp_size=Platform.get_world_size())
+        self.comm_backend = comm_backend
         mesh = self.device_mesh
         self.device = torch.device(device) if device is not None else Platform.current_device()
         on_gpu = self.device.type == 'cuda'
@@ -95,6 +96,7 @@ class MegatronModel(TwinkleModel):
         # ---- model chunks of this pipeline rank
         self.layer_plan = split_layers(cfg.num_hidden_layers, self.pp_size, self.vpp)
         self.chunks: List[DecoderModel] = []
+        fused_tp = make_fused_tp(self.tp_comm, self.device, bool(mesh.sequence_parallel), comm_backend) if self.tp_size > 1 else None
         load_dir = model_id if model_id and os.path.isdir(str(model_id)) else None
         for c, (lo, hi) in enumerate(self.layer_plan[self.pp_rank]):
             first = self.pp_rank == 0 and c == 0
@@ -104,7 +106,7 @@ class MegatronModel(TwinkleModel):
                             has_embed=need_embed, has_head=last)
             # parameter names carry GLOBAL layer indices so that seeds / bridge names agree across layouts
             self._rename_for_init(m, lo, seed, load_dir)
-            apply_tensor_parallel(m, cfg, self.tp_comm, mesh.sequence_parallel)
+            apply_tensor_parallel(m, cfg, self.tp_comm, mesh.sequence_parallel, fused_tp)
             self.chunks.append(m)
         self.sequence_parallel = bool(mesh.sequence_parallel and self.tp_size > 1)
         self.runner = PipelineRunner(self.pp_group, self.pp_rank, self.pp_size, self.vpp, self.compute_dtype, self.device)

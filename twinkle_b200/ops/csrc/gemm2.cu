@@ -13,6 +13,14 @@
 //   tmem_full[b]  one per CTA; same multicast commit after the last k-step of a tile
 //   tmem_empty[b] lives in the leader; 8 arrivals = 4 epilogue warps of each CTA (remote arrive from the odd one)
 // No TMA load carries a cluster multicast qualifier: every operand box is fetched by the CTA that uses it.
+//
+// Two variants fuse a tensor-parallel collective into the same kernel (FUSE template parameter):
+//   FUSE_RS  GEMM → reduce-scatter: the epilogue stores every finished tile straight into the staging slot
+//            [this rank] of the GPU that owns those output rows (plain peer stores over NVLink), remote chunks
+//            first, so the transfer of tile i overlaps the math of tile i+1; the owner then sums its tp slots.
+//   FUSE_AG  all-gather → GEMM: a few extra CTAs of the same launch pull the peers' activation shards into the
+//            local gathered A matrix (plain peer loads) and bump a per-chunk ready counter; the TMA producers
+//            order their tiles local-chunk-first and wait (bounded) for a chunk's counter before loading from it.
 // All waits are bounded (common.cuh); both CTAs always meet at a cluster barrier before TMEM is released.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -31,11 +39,41 @@ constexpr int THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 constexpr int GROUP_M = 8;
 
+constexpr int FUSE_NONE = 0, FUSE_RS = 1, FUSE_AG = 2;
+constexpr int MAX_TP = 8;
+
 struct Params {
   void* out;
   int M, N, K, ldo, out_fp32, accumulate;
   int* err;
+  // tensor-parallel fusion
+  int tp, rank, rows_per_rank;     // M = tp · rows_per_rank
+  void* peer[MAX_TP];              // FUSE_RS: staging base [tp, rows_per_rank, N] of every rank; FUSE_AG: x shard of every rank
+  void* gathered;                  // FUSE_AG: local [M, K] matrix the copier CTAs fill (the A operand)
+  int* ready;                      // FUSE_AG: per-chunk counters, monotonically increasing across calls
+  int ready_target;                // FUSE_AG: value a chunk's counter reaches when all copiers finished it in this call
+  int copy_ctas;                   // FUSE_AG: CTAs [0, copy_ctas) copy (even number), the rest compute in pairs
 };
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// Bounded wait until chunk `c` of the gathered matrix is complete.
+__device__ __forceinline__ bool wait_chunk(const Params& p, int c) {
+  const int* flag = p.ready + c;
+  if (ld_acquire_gpu(flag) >= p.ready_target) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t it = 0;; ++it) {
+    if (ld_acquire_gpu(flag) >= p.ready_target) return true;
+    if ((it & 0xff) == 0xff) {
+      if (global_timer_ns() - t0 > 2000000000ull) { atomicCAS(p.err, 0, ERR_PEER_FLAG); return false; }
+      if (*reinterpret_cast<volatile int*>(p.err) != 0) return false;
+    }
+  }
+}
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -84,6 +122,7 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
                ::"r"(smem_u32(bar)), "h"(mask) : "memory");
 }
 
+template <int FUSE>
 __device__ __forceinline__ bool tile_coord(const Params& p, int tile, int& m0, int& n0) {
   const int num_m = (p.M + TM - 1) / TM, num_n = (p.N + TN - 1) / TN;
   if (tile >= num_m * num_n) return false;
@@ -91,12 +130,21 @@ __device__ __forceinline__ bool tile_coord(const Params& p, int tile, int& m0, i
   const int g = tile / per_group, first_m = g * GROUP_M;
   const int gsize = min(num_m - first_m, GROUP_M);
   const int r = tile - g * per_group;
-  m0 = (first_m + r % gsize) * TM;
+  int mt = first_m + r % gsize;
+  if constexpr (FUSE != FUSE_NONE) {
+    // walk the row chunks in ring order: FUSE_RS sends remote chunks first and keeps its own for last,
+    // FUSE_AG starts on its own chunk while the copiers fetch the others in the same order
+    const int tiles_per_chunk = p.rows_per_rank / TM;
+    const int pos = mt / tiles_per_chunk, within = mt - pos * tiles_per_chunk;
+    const int c = (p.rank + pos + (FUSE == FUSE_RS ? 1 : 0)) % p.tp;
+    mt = c * tiles_per_chunk + within;
+  }
+  m0 = mt * TM;
   n0 = (r / gsize) * TN;
   return true;
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, int FUSE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -109,7 +157,28 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta = cluster_ctarank();  // 0 = leader of the pair
-  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int first_gemm = (FUSE == FUSE_AG) ? p.copy_ctas : 0;
+  const int pair = (static_cast<int>(blockIdx.x) - first_gemm) >> 1;
+  const int num_pairs = (static_cast<int>(gridDim.x) - first_gemm) >> 1;
+
+  if constexpr (FUSE == FUSE_AG) {
+    if (static_cast<int>(blockIdx.x) < p.copy_ctas) {
+      // ------------------------------------------------------ copier CTAs: pull the shards, chunk by chunk
+      // (lowest block indices, so they are resident before the compute CTAs that wait for them)
+      const int ncopy = p.copy_ctas, me = blockIdx.x;
+      const long vec_per_chunk = static_cast<long>(p.rows_per_rank) * p.K / 8;  // 16-byte vectors
+      for (int pos = 0; pos < p.tp; ++pos) {
+        const int c = (p.rank + pos) % p.tp;
+        const uint4* src = reinterpret_cast<const uint4*>(p.peer[c]);
+        uint4* dst = reinterpret_cast<uint4*>(p.gathered) + static_cast<long>(c) * vec_per_chunk;
+        for (long i = static_cast<long>(me) * THREADS + threadIdx.x; i < vec_per_chunk; i += static_cast<long>(ncopy) * THREADS) dst[i] = src[i];
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) atomicAdd(p.ready + c, 1);
+      }
+      return;  // a copier cluster holds copiers only: nothing of the pair protocol below concerns it
+    }
+  }
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmA);
@@ -141,8 +210,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       uint32_t phase = 0;
       int m0, n0;
       bool ok = true;
-      for (int tile = pair; ok && tile_coord(p, tile, m0, n0); tile += num_pairs) {
+      for (int tile = pair; ok && tile_coord<FUSE>(p, tile, m0, n0); tile += num_pairs) {
         const int am = m0 + static_cast<int>(cta) * HALF_M, bn = n0 + static_cast<int>(cta) * HALF_N;
+        if constexpr (FUSE == FUSE_AG) {
+          if (!wait_chunk(p, m0 / p.rows_per_rank)) { ok = false; break; }
+          fence_proxy_async_all();  // the copiers' generic-proxy stores are ordered before this thread's TMA reads
+        }
         for (int k0 = 0; k0 < p.K; k0 += BK) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.err, ERR_PRODUCER_WAIT)) { ok = false; break; }
           uint8_t* sa = smem + stage * STAGE_BYTES;
@@ -176,7 +249,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       uint32_t phase = 0, acc = 0, acc_phase = 0;
       int m0, n0;
       bool ok = true;
-      for (int tile = pair; ok && tile_coord(p, tile, m0, n0); tile += num_pairs) {
+      for (int tile = pair; ok && tile_coord<FUSE>(p, tile, m0, n0); tile += num_pairs) {
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.err, ERR_MMA_WAIT_TMEM)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * TN;
@@ -207,12 +280,19 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     uint32_t acc = 0, acc_phase = 0;
     int m0, n0;
     bool ok = true;
-    for (int tile = pair; ok && tile_coord(p, tile, m0, n0); tile += num_pairs) {
+    for (int tile = pair; ok && tile_coord<FUSE>(p, tile, m0, n0); tile += num_pairs) {
       if (!mbar_wait(&tmem_full[acc], acc_phase, p.err, ERR_EPI_WAIT)) { ok = false; break; }
       tc_fence_after();
       const int row = m0 + static_cast<int>(cta) * HALF_M + q * 32 + lane;
       const bool row_ok = row < p.M;
-      const size_t out_row = static_cast<size_t>(row);
+      size_t out_row = static_cast<size_t>(row);
+      void* out_base = p.out;
+      if constexpr (FUSE == FUSE_RS) {
+        // rows of chunk c belong to rank c: write them into slot [this rank] of that GPU's staging buffer
+        const int c = min(row / p.rows_per_rank, p.tp - 1);
+        out_base = p.peer[c];
+        out_row = static_cast<size_t>(p.rank) * p.rows_per_rank + (row - c * p.rows_per_rank);
+      }
 #pragma unroll 1
       for (int c = 0; c < TN / 32; ++c) {
         uint32_t r[32];
@@ -221,7 +301,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         const int col0 = n0 + c * 32;
         if (!row_ok || col0 >= p.N) continue;
         if (p.out_fp32) {
-          float* o = reinterpret_cast<float*>(p.out) + out_row * p.ldo + col0;
+          float* o = reinterpret_cast<float*>(out_base) + out_row * p.ldo + col0;
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
             if (col0 + j + 4 <= p.N) {
@@ -236,7 +316,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             }
           }
         } else {
-          __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + out_row * p.ldo + col0;
+          __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out_base) + out_row * p.ldo + col0;
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
             if (col0 + j + 8 <= p.N) {
@@ -301,12 +381,13 @@ static int max_pairs(Kern kern) {
 // (the caller then uses the single-CTA kernel).
 bool gemm_pair_launch(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, void* out, int M, int N, int K, int ldo,
                       bool out_fp32, bool accumulate, cudaStream_t stream) {
-  g2::Params p{out, M, N, K, ldo, out_fp32 ? 1 : 0, accumulate ? 1 : 0, error_word()};
+  g2::Params p{};
+  p.out = out; p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.out_fp32 = out_fp32 ? 1 : 0; p.accumulate = accumulate ? 1 : 0; p.err = error_word();
   const int tiles = ((M + g2::TM - 1) / g2::TM) * ((N + g2::TN - 1) / g2::TN);
 #define TK_LAUNCH2(AM, BMN)                                                                                            \
   do {                                                                                                                 \
     static int pairs = -1;                                                                                             \
-    auto kern = g2::gemm_tcgen05_pair_kernel<AM, BMN>;                                                                 \
+    auto kern = g2::gemm_tcgen05_pair_kernel<AM, BMN, g2::FUSE_NONE>;                                                                 \
     if (pairs < 0) {                                                                                                   \
       TK_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, g2::SMEM_BYTES));          \
       pairs = max_pairs(kern);                                                                                         \
@@ -323,6 +404,127 @@ bool gemm_pair_launch(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtenso
   count_launch();
   TK_CUDA_CHECK(cudaGetLastError());
   return true;
+}
+
+
+// ------------------------------------------------------------------------------------------------ fused TP paths
+static void check_bf16_2d(const torch::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16 && t.dim() == 2 && t.is_contiguous(), name, " must be a contiguous 2-D bf16 CUDA tensor");
+  TORCH_CHECK(t.size(1) % 8 == 0 && reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0, name, ": rows must be 16-byte multiples");
+}
+
+template <int FUSE>
+static void launch_fused(bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const g2::Params& p, int copy_ctas, cudaStream_t stream) {
+  const int tiles = ((p.M + g2::TM - 1) / g2::TM) * ((p.N + g2::TN - 1) / g2::TN);
+#define TK_LAUNCH_F(BMN)                                                                                               \
+  do {                                                                                                                 \
+    static int pairs = -1;                                                                                             \
+    auto kern = g2::gemm_tcgen05_pair_kernel<false, BMN, FUSE>;                                                        \
+    if (pairs < 0) {                                                                                                   \
+      TK_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, g2::SMEM_BYTES));          \
+      pairs = max_pairs(kern);                                                                                         \
+    }                                                                                                                  \
+    TORCH_CHECK(pairs > copy_ctas / 2, "SM-pair kernel cannot be resident on this device");                           \
+    const int avail = std::min(pairs, num_sms() / 2) - copy_ctas / 2;                                                  \
+    const int grid = copy_ctas + 2 * std::min(tiles, avail);                                                           \
+    kern<<<grid, g2::THREADS, g2::SMEM_BYTES, stream>>>(ta, tb, p);                                                    \
+  } while (0)
+  if (b_mn) TK_LAUNCH_F(true); else TK_LAUNCH_F(false);
+#undef TK_LAUNCH_F
+  count_launch();
+  TK_CUDA_CHECK(cudaGetLastError());
+}
+
+// Row-parallel linear with the reduce-scatter in the epilogue.  a [T, Kl] (this rank's K slice of the activations),
+// w [N, Kl] ('nt') or [Kl, N] ('nn').  Tile rows of chunk c are stored into slot [rank] of rank c's staging buffer
+// (`stage_ptrs[c]`, layout [tp, T/tp, N] bf16).  The caller passes a cross-GPU barrier and sums its own slots.
+void gemm_rs(const torch::Tensor& a, const torch::Tensor& w, const std::string& layout, const std::vector<int64_t>& stage_ptrs, int64_t rank) {
+  check_bf16_2d(a, "a");
+  check_bf16_2d(w, "w");
+  const int tp = stage_ptrs.size();
+  TORCH_CHECK(tp >= 1 && tp <= g2::MAX_TP, "tp out of range");
+  const bool b_mn = layout == "nn";
+  TORCH_CHECK(b_mn || layout == "nt", "layout must be nt|nn");
+  const int M = a.size(0), K = a.size(1), N = b_mn ? w.size(1) : w.size(0);
+  TORCH_CHECK((b_mn ? w.size(0) : w.size(1)) == K, "K mismatch");
+  TORCH_CHECK(M % tp == 0 && (M / tp) % g2::TM == 0, "rows per rank must be a multiple of ", g2::TM);
+  TORCH_CHECK(K % 8 == 0 && N % 8 == 0, "K and N must be multiples of 8");
+  c10::cuda::CUDAGuard guard(a.device());
+  CUtensorMap ta = make_tmap_2d(a.data_ptr(), K, M, a.stride(0), g2::BK, 128);
+  CUtensorMap tb = b_mn ? make_tmap_2d(w.data_ptr(), w.size(1), w.size(0), w.stride(0), 64, g2::BK)
+                        : make_tmap_2d(w.data_ptr(), w.size(1), w.size(0), w.stride(0), g2::BK, 128);
+  g2::Params p{};
+  p.out = nullptr; p.M = M; p.N = N; p.K = K; p.ldo = N; p.out_fp32 = 0; p.accumulate = 0; p.err = error_word();
+  p.tp = tp; p.rank = static_cast<int>(rank); p.rows_per_rank = M / tp;
+  for (int i = 0; i < tp; ++i) p.peer[i] = reinterpret_cast<void*>(stage_ptrs[i]);
+  launch_fused<g2::FUSE_RS>(b_mn, ta, tb, p, 0, at::cuda::getCurrentCUDAStream());
+}
+
+// Column-parallel linear with the all-gather in the prologue.  `x_ptrs[c]` = rank c's [rows_per_rank, K] bf16 shard
+// (symmetric memory); returns {y [tp·rows_per_rank, N], gathered [tp·rows_per_rank, K]}.  `ready` holds tp int32
+// counters that only ever grow: call number `epoch` (1, 2, …) waits for copy_ctas·epoch.
+std::vector<torch::Tensor> gemm_ag(const std::vector<int64_t>& x_ptrs, int64_t rows_per_rank, const torch::Tensor& w, const std::string& layout,
+                                   int64_t rank, const torch::Tensor& ready, int64_t epoch, int64_t copy_ctas) {
+  check_bf16_2d(w, "w");
+  const int tp = x_ptrs.size();
+  TORCH_CHECK(tp >= 1 && tp <= g2::MAX_TP, "tp out of range");
+  TORCH_CHECK(ready.is_cuda() && ready.scalar_type() == torch::kInt32 && ready.numel() >= tp && ready.is_contiguous(), "ready: int32 [tp]");
+  TORCH_CHECK(copy_ctas >= 2 && copy_ctas % 2 == 0 && copy_ctas <= 64, "copy_ctas must be even, 2..64");
+  const bool b_mn = layout == "nn";
+  TORCH_CHECK(b_mn || layout == "nt", "layout must be nt|nn");
+  const int K = b_mn ? w.size(0) : w.size(1), N = b_mn ? w.size(1) : w.size(0);
+  TORCH_CHECK(rows_per_rank % g2::TM == 0, "rows per rank must be a multiple of ", g2::TM);
+  TORCH_CHECK(K % 8 == 0 && N % 8 == 0, "K and N must be multiples of 8");
+  TORCH_CHECK(epoch * copy_ctas < (1ll << 30), "ready counters exhausted: reset them");
+  c10::cuda::CUDAGuard guard(w.device());
+  const int M = tp * static_cast<int>(rows_per_rank);
+  auto gathered = torch::empty({M, K}, w.options());
+  auto out = torch::empty({M, N}, w.options());
+  CUtensorMap ta = make_tmap_2d(gathered.data_ptr(), K, M, K, g2::BK, 128);
+  CUtensorMap tb = b_mn ? make_tmap_2d(w.data_ptr(), w.size(1), w.size(0), w.stride(0), 64, g2::BK)
+                        : make_tmap_2d(w.data_ptr(), w.size(1), w.size(0), w.stride(0), g2::BK, 128);
+  g2::Params p{};
+  p.out = out.data_ptr(); p.M = M; p.N = N; p.K = K; p.ldo = N; p.out_fp32 = 0; p.accumulate = 0; p.err = error_word();
+  p.tp = tp; p.rank = static_cast<int>(rank); p.rows_per_rank = static_cast<int>(rows_per_rank);
+  for (int i = 0; i < tp; ++i) p.peer[i] = reinterpret_cast<void*>(x_ptrs[i]);
+  p.gathered = gathered.data_ptr(); p.ready = ready.data_ptr<int>(); p.ready_target = static_cast<int>(epoch * copy_ctas);
+  p.copy_ctas = static_cast<int>(copy_ctas);
+  launch_fused<g2::FUSE_AG>(b_mn, ta, tb, p, static_cast<int>(copy_ctas), at::cuda::getCurrentCUDAStream());
+  return {out, gathered};
+}
+
+// out[r, :] = Σ_s stage[s, r, :]  (fp32 sum of the tp staging slots, bf16 result)
+__global__ void __launch_bounds__(256) stage_reduce_kernel(const uint4* __restrict__ stage, uint4* __restrict__ out, long vecs, int tp) {
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < vecs; i += static_cast<long>(gridDim.x) * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < tp; ++s) {
+      const uint4 u = stage[static_cast<long>(s) * vecs + i];
+      const uint32_t* q = &u.x;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = unpack_bf16(q[k]);
+        acc[2 * k] += f.x;
+        acc[2 * k + 1] += f.y;
+      }
+    }
+    out[i] = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+  }
+}
+
+torch::Tensor tp_stage_reduce(const torch::Tensor& stage) {
+  TORCH_CHECK(stage.is_cuda() && stage.scalar_type() == torch::kBFloat16 && stage.dim() == 3 && stage.is_contiguous(), "stage [tp, rows, N] bf16");
+  c10::cuda::CUDAGuard guard(stage.device());
+  const int tp = stage.size(0);
+  auto out = torch::empty({stage.size(1), stage.size(2)}, stage.options());
+  const long vecs = out.numel() / 8;
+  TORCH_CHECK(out.numel() % 8 == 0, "rows·N must be a multiple of 8");
+  if (vecs == 0) return out;
+  const int grid = static_cast<int>(std::min<long>((vecs + 255) / 256, static_cast<long>(num_sms()) * 8));
+  stage_reduce_kernel<<<grid, 256, 0, at::cuda::getCurrentCUDAStream()>>>(reinterpret_cast<const uint4*>(stage.data_ptr()),
+                                                                          reinterpret_cast<uint4*>(out.data_ptr()), vecs, tp);
+  count_launch();
+  TK_CUDA_CHECK(cudaGetLastError());
+  return out;
 }
 
 }  // namespace tk

@@ -105,6 +105,7 @@ class TPContext:
     def __init__(self, comm: Communicator, sequence_parallel: bool):
         self.comm, self.sp = comm, sequence_parallel
         self.size, self.rank = comm.world_size, comm.rank
+        self.fused = None  # parallel.tensor_fused.FusedTP when the group has a peer-memory communicator
 
     def before_column(self, x):
         return GatherTokens.apply(x, self.comm) if self.sp else CopyToTP.apply(x, self.comm)
@@ -116,6 +117,15 @@ class TPContext:
 def tp_linear_forward(lin, x: torch.Tensor) -> torch.Tensor:
     """Forward of a ``models.layers.Linear`` whose weight is a TP shard (``lin.tp_mode`` in {'col', 'row'})."""
     tp: TPContext = lin.tp
+    f = tp.fused
+    if f is not None and tp.sp and x.is_cuda and x.dim() == 2:
+        from .tensor_fused import ColumnLinearFused, FusedTP, RowLinearFused
+        if lin.tp_mode == 'col' and FusedTP.eligible(x.shape[0], x.shape[1], lin.weight.shape[0], x.dtype):
+            y = ColumnLinearFused.apply(x, lin.weight, f)
+            return y if lin.bias is None else y + lin.bias
+        if lin.tp_mode == 'row' and x.shape[0] % tp.size == 0 and FusedTP.eligible(x.shape[0] // tp.size, x.shape[1], lin.weight.shape[0], x.dtype):
+            y = RowLinearFused.apply(x, lin.weight, f)
+            return y if lin.bias is None else y + lin.bias
     if lin.tp_mode == 'col':
         return ops.linear(tp.before_column(x), lin.weight, lin.bias)
     y = ops.linear(x, lin.weight, None)
@@ -175,12 +185,29 @@ def vocab_parallel_logprob(hidden, weight, labels, tp: TPContext, temperature: f
     return _VocabParallelLogprob.apply(hidden, weight, labels.clamp_min(0), tp.comm, temperature)
 
 
-def apply_tensor_parallel(model, cfg, comm: Communicator, sequence_parallel: bool) -> Optional[TPContext]:
+def make_fused_tp(comm: Communicator, device, sequence_parallel: bool, backend: str = 'auto'):
+    """A ``FusedTP`` (peer-memory GEMM+collective kernels) for this TP group, or None when NCCL collectives are to be used."""
+    if not (sequence_parallel and device.type == 'cuda' and backend in ('auto', 'symm') and 1 < comm.world_size <= 8):
+        return None
+    try:
+        from .symm import SymmCommunicator
+        from .tensor_fused import FusedTP
+        return FusedTP(SymmCommunicator(comm.group, device))
+    except Exception as e:  # NCCL collectives around the GEMM stay correct
+        if backend == 'symm':
+            raise
+        import logging
+        logging.getLogger('twinkle_b200').warning(f'fused tensor-parallel kernels unavailable ({e}); using NCCL collectives')
+        return None
+
+
+def apply_tensor_parallel(model, cfg, comm: Communicator, sequence_parallel: bool, fused=None) -> Optional[TPContext]:
     """Replace every parallelisable weight by this rank's shard (cut from the identically initialised full
     tensor) and switch the modules to their TP forward."""
     if comm.world_size <= 1:
         return None
     tp = TPContext(comm, sequence_parallel)
+    tp.fused = fused
     assert cfg.num_key_value_heads % tp.size == 0 and cfg.num_attention_heads % tp.size == 0, 'heads must divide over tp'
     names = dict(model.named_parameters())
     with torch.no_grad():
