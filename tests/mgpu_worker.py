@@ -121,6 +121,7 @@ def tp_fused_checks(rank, world, dev, report):
         return o
 
     t_ag, t_ag_ref = timeit(lambda: f.ag_gemm(x, wc, 'nt')), timeit(nccl_col)
+    t_gemm_only = timeit(lambda: torch.nn.functional.linear(full, wc))
     t_rs, t_rs_ref = timeit(lambda: f.gemm_rs(a, wr, 'nt')), timeit(nccl_row)
     flops = 2.0 * T * H * (I // tp)
     link = 770e9
@@ -129,7 +130,7 @@ def tp_fused_checks(rank, world, dev, report):
     roof_ag = max(flops / 1722.5e12, ag_bytes / link) * 1e3
     roof_rs = max(flops / 1722.5e12, rs_bytes / link) * 1e3
     report('tp_fused_timing', True, tp=tp, shape=[T, H, I // tp], ag_gemm_ms=t_ag, nccl_ag_plus_gemm_ms=t_ag_ref, gemm_rs_ms=t_rs,
-           gemm_plus_nccl_rs_ms=t_rs_ref, roofline_ms_ag=roof_ag, roofline_ms_rs=roof_rs, frac_of_roofline_ag=roof_ag / t_ag,
+           gemm_plus_nccl_rs_ms=t_rs_ref, library_gemm_only_ms=t_gemm_only, copier_ctas=f.copier_ctas(T, H, I // tp), roofline_ms_ag=roof_ag, roofline_ms_rs=roof_rs, frac_of_roofline_ag=roof_ag / t_ag,
            frac_of_roofline_rs=roof_rs / t_rs)
     report('tp_fused_error_word', E.read_and_clear_error() == 0)
 

@@ -146,7 +146,8 @@ __device__ __forceinline__ bool tile_coord(const Params& p, int tile, int& m0, i
 
 template <bool A_MN, bool B_MN, int FUSE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
-gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmL,
+                         const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -165,16 +166,50 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     if (static_cast<int>(blockIdx.x) < p.copy_ctas) {
       // ------------------------------------------------------ copier CTAs: pull the shards, chunk by chunk
       // (lowest block indices, so they are resident before the compute CTAs that wait for them)
-      const int ncopy = p.copy_ctas, me = blockIdx.x;
-      const long vec_per_chunk = static_cast<long>(p.rows_per_rank) * p.K / 8;  // 16-byte vectors
-      for (int pos = 0; pos < p.tp; ++pos) {
-        const int c = (p.rank + pos) % p.tp;
-        const uint4* src = reinterpret_cast<const uint4*>(p.peer[c]);
-        uint4* dst = reinterpret_cast<uint4*>(p.gathered) + static_cast<long>(c) * vec_per_chunk;
-        for (long i = static_cast<long>(me) * THREADS + threadIdx.x; i < vec_per_chunk; i += static_cast<long>(ncopy) * THREADS) dst[i] = src[i];
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) atomicAdd(p.ready + c, 1);
+      // One thread drives a ring of 32 KB bulk copies (peer global → shared → local global): plain loads cannot keep
+      // enough bytes in flight to cover the NVLink round trip, 6 x 32 KB per CTA can.
+      if (threadIdx.x == 0) {
+        constexpr uint32_t PIECE = STAGE_BYTES;  // 32 KB
+        for (int s_ = 0; s_ < STAGES; ++s_) mbar_init(&full_bar[s_], 1);
+        fence_barrier_init();
+        fence_proxy_async_all();
+        const int ncopy = p.copy_ctas, me = blockIdx.x;
+        const long chunk_bytes = static_cast<long>(p.rows_per_rank) * p.K * 2;
+        const long pieces = (chunk_bytes + PIECE - 1) / PIECE;
+        uint32_t issued = 0, done = 0;  // pieces issued / stored by this CTA over all chunks (ring position = n % STAGES)
+        bool ok = true;
+        for (int pos = 1; ok && pos < p.tp; ++pos) {  // the local shard is read in place by the compute CTAs
+          const int c = (p.rank + pos) % p.tp;
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(p.peer[c]);
+          uint8_t* dst = reinterpret_cast<uint8_t*>(p.gathered) + static_cast<long>(c) * chunk_bytes;
+          const long mine = me < pieces ? (pieces - me + ncopy - 1) / ncopy : 0;  // pieces me, me+ncopy, …
+          long li = 0, si = 0;                                                    // next piece to load / to store
+          while (si < mine) {
+            // keep STAGES-1 loads in flight; the stage being refilled was stored one iteration ago
+            while (li < mine && li - si < STAGES - 1) {
+              const long off = (me + li * ncopy) * static_cast<long>(PIECE);
+              const uint32_t bytes = static_cast<uint32_t>(min(static_cast<long>(PIECE), chunk_bytes - off));
+              const int st = issued % STAGES;
+              asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");  // all but the newest store have left shared memory
+              mbar_expect_tx(&full_bar[st], bytes);
+              asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                           ::"r"(smem_u32(smem + st * PIECE)), "l"(src + off), "r"(bytes), "r"(smem_u32(&full_bar[st])) : "memory");
+              ++issued; ++li;
+            }
+            const int st = done % STAGES;
+            if (!mbar_wait(&full_bar[st], (done / STAGES) & 1, p.err, ERR_PEER_FLAG)) { ok = false; break; }
+            const long off = (me + si * ncopy) * static_cast<long>(PIECE);
+            const uint32_t bytes = static_cast<uint32_t>(min(static_cast<long>(PIECE), chunk_bytes - off));
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                         ::"l"(dst + off), "r"(smem_u32(smem + st * PIECE)), "r"(bytes) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            ++done; ++si;
+          }
+          asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");         // my part of chunk c is written
+          fence_proxy_async_all();
+          __threadfence();
+          if (ok) atomicAdd(p.ready + c, 1);
+        }
       }
       return;  // a copier cluster holds copiers only: nothing of the pair protocol below concerns it
     }
@@ -183,6 +218,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if constexpr (FUSE == FUSE_AG) tma_prefetch_desc(&tmL);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -212,9 +248,17 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       bool ok = true;
       for (int tile = pair; ok && tile_coord<FUSE>(p, tile, m0, n0); tile += num_pairs) {
         const int am = m0 + static_cast<int>(cta) * HALF_M, bn = n0 + static_cast<int>(cta) * HALF_N;
+        const CUtensorMap* mapA = &tmA;
+        int a_row = am;
         if constexpr (FUSE == FUSE_AG) {
-          if (!wait_chunk(p, m0 / p.rows_per_rank)) { ok = false; break; }
-          fence_proxy_async_all();  // the copiers' generic-proxy stores are ordered before this thread's TMA reads
+          const int c = m0 / p.rows_per_rank;
+          if (c == p.rank) {  // own shard: straight from where it already lives
+            mapA = &tmL;
+            a_row = am - c * p.rows_per_rank;
+          } else {
+            if (!wait_chunk(p, c)) { ok = false; break; }
+            fence_proxy_async_all();  // the copiers' writes are ordered before this thread's TMA reads
+          }
         }
         for (int k0 = 0; k0 < p.K; k0 += BK) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.err, ERR_PRODUCER_WAIT)) { ok = false; break; }
@@ -223,7 +267,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
           if (cta == 0) mbar_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
           if constexpr (!A_MN) {
-            tma_load_2d_pair(sa, &tmA, bar, k0, am);                                  // box {64 K, 128 rows}
+            tma_load_2d_pair(sa, mapA, bar, k0, a_row);                              // box {64 K, 128 rows}
           } else {
 #pragma unroll
             for (int j = 0; j < HALF_M / 64; ++j) tma_load_2d_pair(sa + j * (64 * BK * 2), &tmA, bar, am + j * 64, k0);
@@ -394,7 +438,7 @@ bool gemm_pair_launch(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtenso
     }                                                                                                                  \
     if (pairs <= 0) return false;                                                                                      \
     const int grid = 2 * std::min(tiles, std::min(pairs, num_sms() / 2));                                              \
-    kern<<<grid, g2::THREADS, g2::SMEM_BYTES, stream>>>(ta, tb, p);                                                    \
+    kern<<<grid, g2::THREADS, g2::SMEM_BYTES, stream>>>(ta, tb, ta, p);                                                \
   } while (0)
   if (!a_mn && !b_mn) TK_LAUNCH2(false, false);
   else if (!a_mn && b_mn) TK_LAUNCH2(false, true);
@@ -414,7 +458,8 @@ static void check_bf16_2d(const torch::Tensor& t, const char* name) {
 }
 
 template <int FUSE>
-static void launch_fused(bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const g2::Params& p, int copy_ctas, cudaStream_t stream) {
+static void launch_fused(bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tl, const g2::Params& p, int copy_ctas,
+                         cudaStream_t stream) {
   const int tiles = ((p.M + g2::TM - 1) / g2::TM) * ((p.N + g2::TN - 1) / g2::TN);
 #define TK_LAUNCH_F(BMN)                                                                                               \
   do {                                                                                                                 \
@@ -427,7 +472,7 @@ static void launch_fused(bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb
     TORCH_CHECK(pairs > copy_ctas / 2, "SM-pair kernel cannot be resident on this device");                           \
     const int avail = std::min(pairs, num_sms() / 2) - copy_ctas / 2;                                                  \
     const int grid = copy_ctas + 2 * std::min(tiles, avail);                                                           \
-    kern<<<grid, g2::THREADS, g2::SMEM_BYTES, stream>>>(ta, tb, p);                                                    \
+    kern<<<grid, g2::THREADS, g2::SMEM_BYTES, stream>>>(ta, tb, tl, p);                                                \
   } while (0)
   if (b_mn) TK_LAUNCH_F(true); else TK_LAUNCH_F(false);
 #undef TK_LAUNCH_F
@@ -457,14 +502,14 @@ void gemm_rs(const torch::Tensor& a, const torch::Tensor& w, const std::string& 
   p.out = nullptr; p.M = M; p.N = N; p.K = K; p.ldo = N; p.out_fp32 = 0; p.accumulate = 0; p.err = error_word();
   p.tp = tp; p.rank = static_cast<int>(rank); p.rows_per_rank = M / tp;
   for (int i = 0; i < tp; ++i) p.peer[i] = reinterpret_cast<void*>(stage_ptrs[i]);
-  launch_fused<g2::FUSE_RS>(b_mn, ta, tb, p, 0, at::cuda::getCurrentCUDAStream());
+  launch_fused<g2::FUSE_RS>(b_mn, ta, tb, ta, p, 0, at::cuda::getCurrentCUDAStream());
 }
 
 // Column-parallel linear with the all-gather in the prologue.  `x_ptrs[c]` = rank c's [rows_per_rank, K] bf16 shard
 // (symmetric memory); returns {y [tp·rows_per_rank, N], gathered [tp·rows_per_rank, K]}.  `ready` holds tp int32
-// counters that only ever grow: call number `epoch` (1, 2, …) waits for copy_ctas·epoch.
+// counters that only ever grow: every call adds copy_ctas to each and waits for `ready_target` = the new total.
 std::vector<torch::Tensor> gemm_ag(const std::vector<int64_t>& x_ptrs, int64_t rows_per_rank, const torch::Tensor& w, const std::string& layout,
-                                   int64_t rank, const torch::Tensor& ready, int64_t epoch, int64_t copy_ctas) {
+                                   int64_t rank, const torch::Tensor& ready, int64_t ready_target, int64_t copy_ctas) {
   check_bf16_2d(w, "w");
   const int tp = x_ptrs.size();
   TORCH_CHECK(tp >= 1 && tp <= g2::MAX_TP, "tp out of range");
@@ -475,7 +520,7 @@ std::vector<torch::Tensor> gemm_ag(const std::vector<int64_t>& x_ptrs, int64_t r
   const int K = b_mn ? w.size(0) : w.size(1), N = b_mn ? w.size(1) : w.size(0);
   TORCH_CHECK(rows_per_rank % g2::TM == 0, "rows per rank must be a multiple of ", g2::TM);
   TORCH_CHECK(K % 8 == 0 && N % 8 == 0, "K and N must be multiples of 8");
-  TORCH_CHECK(epoch * copy_ctas < (1ll << 30), "ready counters exhausted: reset them");
+  TORCH_CHECK(ready_target > 0 && ready_target < (1ll << 30), "ready counters exhausted: reset them");
   c10::cuda::CUDAGuard guard(w.device());
   const int M = tp * static_cast<int>(rows_per_rank);
   auto gathered = torch::empty({M, K}, w.options());
@@ -487,9 +532,13 @@ std::vector<torch::Tensor> gemm_ag(const std::vector<int64_t>& x_ptrs, int64_t r
   p.out = out.data_ptr(); p.M = M; p.N = N; p.K = K; p.ldo = N; p.out_fp32 = 0; p.accumulate = 0; p.err = error_word();
   p.tp = tp; p.rank = static_cast<int>(rank); p.rows_per_rank = static_cast<int>(rows_per_rank);
   for (int i = 0; i < tp; ++i) p.peer[i] = reinterpret_cast<void*>(x_ptrs[i]);
-  p.gathered = gathered.data_ptr(); p.ready = ready.data_ptr<int>(); p.ready_target = static_cast<int>(epoch * copy_ctas);
+  p.gathered = gathered.data_ptr(); p.ready = ready.data_ptr<int>(); p.ready_target = static_cast<int>(ready_target);
   p.copy_ctas = static_cast<int>(copy_ctas);
-  launch_fused<g2::FUSE_AG>(b_mn, ta, tb, p, static_cast<int>(copy_ctas), at::cuda::getCurrentCUDAStream());
+  // the rank's own shard: read in place by the compute CTAs, and copied into `gathered` for the caller's wgrad
+  CUtensorMap tl = make_tmap_2d(reinterpret_cast<void*>(x_ptrs[rank]), K, rows_per_rank, K, g2::BK, 128);
+  TK_CUDA_CHECK(cudaMemcpyAsync(static_cast<char*>(gathered.data_ptr()) + rank * rows_per_rank * K * 2, reinterpret_cast<void*>(x_ptrs[rank]),
+                                rows_per_rank * K * 2, cudaMemcpyDeviceToDevice, at::cuda::getCurrentCUDAStream()));
+  launch_fused<g2::FUSE_AG>(b_mn, ta, tb, tl, p, static_cast<int>(copy_ctas), at::cuda::getCurrentCUDAStream());
   return {out, gathered};
 }
 

@@ -24,11 +24,11 @@ from .. import ops
 
 class FusedTP:
 
-    def __init__(self, comm, copy_ctas: int = 8):
+    def __init__(self, comm, copy_ctas: int = 0):
         self.comm, self.tp, self.rank = comm, comm.world_size, comm.rank
-        self.copy_ctas = copy_ctas
+        self.copy_ctas = copy_ctas  # 0: sized per call so that the pulls take about half the GEMM's time
         self.ready = torch.zeros(16, dtype=torch.int32, device=comm.device)
-        self.epoch = 0
+        self.ready_total = 0
         self._bufs: Dict[Tuple, List[torch.Tensor]] = {}
         self._uses: Dict[Tuple, int] = {}
 
@@ -50,12 +50,22 @@ class FusedTP:
         buf = self._buf(('x', rows, k), rows * k, x_local.dtype).view(rows, k)
         buf.copy_(x_local)
         self.comm.barrier_kernel()  # every rank's shard is in place
-        self.epoch += 1
-        if self.epoch * self.copy_ctas >= (1 << 30):
+        n = w.shape[0] if layout == 'nt' else w.shape[1]
+        ctas = self.copy_ctas or self.copier_ctas(rows * self.tp, k, n)
+        if self.ready_total + ctas >= (1 << 30):
             self.ready.zero_()
-            self.epoch = 1
-        y, gathered = ops.ext().gemm_ag(self.comm.peer_ptrs(buf), rows, w, layout, self.rank, self.ready, self.epoch, self.copy_ctas)
+            self.ready_total = 0
+        self.ready_total += ctas
+        y, gathered = ops.ext().gemm_ag(self.comm.peer_ptrs(buf), rows, w, layout, self.rank, self.ready, self.ready_total, ctas)
         return y, gathered
+
+    def copier_ctas(self, t: int, k: int, n: int) -> int:
+        """CTAs of the launch that copy instead of compute: each keeps 160 KB in flight (≈ 50 GB/s over NVLink); enough of
+        them that the remote shards arrive in about half the time the tensor cores need for the whole product."""
+        remote_bytes = (self.tp - 1) * (t // self.tp) * k * 2
+        gemm_s = 2.0 * t * k * n / 1.5e15
+        need = remote_bytes / (0.5 * gemm_s * 50e9)
+        return int(min(16, max(2, 2 * round(need / 2 + 0.5))))
 
     def gemm_rs(self, a: torch.Tensor, w: torch.Tensor, layout: str) -> torch.Tensor:
         """reduce_scatter(a · Wᵀ | a · W) along rows."""
