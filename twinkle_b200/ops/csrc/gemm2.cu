@@ -156,6 +156,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   uint64_t* tmem_empty = tmem_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
 
+  // the reduce-scatter variant gives its sixth stage to the epilogue as a staging area for coalesced peer stores
+  constexpr int NST = (FUSE == FUSE_RS) ? STAGES - 1 : STAGES;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta = cluster_ctarank();  // 0 = leader of the pair
   const int first_gemm = (FUSE == FUSE_AG) ? p.copy_ctas : 0;
@@ -278,11 +280,11 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 #pragma unroll
             for (int j = 0; j < HALF_N / 64; ++j) tma_load_2d_pair(sb + j * (64 * BK * 2), &tmB, bar, bn + j * 64, k0);
           }
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == NST) { stage = 0; phase ^= 1; }
         }
       }
       if (!ok && cta == 0) {
-        for (int s = 0; s < STAGES; ++s) mbar_wait(&full_bar[s], 0, nullptr, 0);  // bounded drain of copies in flight
+        for (int s = 0; s < NST; ++s) mbar_wait(&full_bar[s], 0, nullptr, 0);  // bounded drain of copies in flight
       }
     }
   } else if (warp == 1) {
@@ -311,7 +313,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             first = 0;
           }
           umma_commit_pair(&empty_bar[stage]);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == NST) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit_pair(&tmem_full[acc]);
         acc ^= 1;
@@ -337,6 +339,44 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         out_base = p.peer[c];
         out_row = static_cast<size_t>(p.rank) * p.rows_per_rank + (row - c * p.rows_per_rank);
       }
+      if constexpr (FUSE == FUSE_RS) {
+        // Stage 32 rows x 128 columns (bf16) per warp in shared memory, then let every half-warp store one whole
+        // 256-byte row segment: NVLink sees long contiguous writes instead of 64-byte pieces of 32 different rows.
+        uint8_t* stg = smem + (STAGES - 1) * STAGE_BYTES + q * 8192;
+        const int row0 = m0 + static_cast<int>(cta) * HALF_M + q * 32;
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll 1
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t r[32];
+            tmem_ld32(tmem_base + acc * TN + (half * 4 + cc) * 32 + (static_cast<uint32_t>(q * 32) << 16), r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int chunk = (cc * 4 + j) ^ (lane & 15);
+              *reinterpret_cast<uint4*>(stg + lane * 256 + chunk * 16) =
+                  make_uint4(pack_bf16(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1])), pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3])),
+                             pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5])), pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7])));
+            }
+          }
+          __syncwarp();
+          const int j = lane & 15;
+          const int col = n0 + half * 128 + j * 8;
+#pragma unroll 4
+          for (int it = 0; it < 16; ++it) {
+            const int lr = it * 2 + (lane >> 4);
+            const int grow = row0 + lr;
+            const uint4 v = *reinterpret_cast<const uint4*>(stg + lr * 256 + ((j ^ (lr & 15)) * 16));
+            if (grow < p.M && col + 8 <= p.N) {
+              const int c = min(grow / p.rows_per_rank, p.tp - 1);
+              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.peer[c]) +
+                                 (static_cast<size_t>(p.rank) * p.rows_per_rank + (grow - c * p.rows_per_rank)) * p.ldo + col;
+              *reinterpret_cast<uint4*>(o) = v;
+            }
+          }
+          __syncwarp();
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < TN / 32; ++c) {
         uint32_t r[32];
