@@ -81,7 +81,7 @@ class MLP(nn.Module):
         self.down_proj = Linear(i, cfg.hidden_size, name='down_proj')
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.down_proj(ops.swiglu(self.gate_up_proj(x)))
+        return self.down_proj(ops.swiglu(self.gate_up_proj(x)), value_unused=True)
 
 
 class Experts(nn.Module):
@@ -199,8 +199,8 @@ class DecoderLayer(nn.Module):
         n = self.post_attention_layernorm(h)
         if self.is_moe:
             forced = batch.routed_experts[self.layer_idx] if batch.routed_experts is not None else None
-            return h + self.mlp(n, forced)
-        return h + self.mlp(n)
+            return ops.add(h, self.mlp(n, forced), value_unused=True)
+        return ops.add(h, self.mlp(n), value_unused=True)
 
 
 class DecoderModel(nn.Module):

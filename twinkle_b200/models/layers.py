@@ -158,11 +158,13 @@ class Linear(nn.Module):
         outs = [o if o is not None else x2.new_zeros(x2.shape[0], n) for o, (_, n) in zip(outs, self.parts)]
         return outs[0] if len(outs) == 1 else torch.cat(outs, -1)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, value_unused: bool = False) -> torch.Tensor:
+        """``value_unused``: this is the last linear of a layer; when the layer is only re-run to rebuild its graph the
+        base product is skipped (the LoRA branch still runs: its intermediate is needed by its own backward)."""
         if self.tp_mode is not None:
             from ..parallel.tensor import tp_linear_forward
             return tp_linear_forward(self, x)
-        y = ops.linear(x, self.weight, self.bias, self.wgrad_out if self.weight.requires_grad else None)
+        y = ops.linear(x, self.weight, self.bias, self.wgrad_out if self.weight.requires_grad else None, value_unused)
         lb = _CTX.batch
         if lb is not None and self.max_loras > 0:
             x2 = x.reshape(-1, x.shape[-1])

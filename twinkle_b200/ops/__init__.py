@@ -49,14 +49,55 @@ def _cuda(t: torch.Tensor) -> bool:
 
 
 # ------------------------------------------------------------------ linear
+class _DeadValues:
+    """While a layer is re-run only to rebuild its autograd graph (activation recompute in backward), the values of
+    its last operations are never read: their backward needs the operands, not the result.  Inside this context
+    the operations that opt in return uninitialised tensors of the right shape instead of computing."""
+    on = False
+
+
+class dead_values:
+
+    def __enter__(self):
+        self.prev, _DeadValues.on = _DeadValues.on, True
+
+    def __exit__(self, *exc):
+        _DeadValues.on = self.prev
+        return False
+
+
+def dead_values_enabled() -> bool:
+    return _DeadValues.on
+
+
+class _AddDead(torch.autograd.Function):
+    """``a + b`` whose value nobody reads: returns an uninitialised tensor, passes the gradient to both."""
+
+    @staticmethod
+    def forward(ctx, a, b):
+        return torch.empty_like(a)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, g
+
+
+def add(a: torch.Tensor, b: torch.Tensor, value_unused: bool = False) -> torch.Tensor:
+    if value_unused and _DeadValues.on and a.is_cuda:
+        return _AddDead.apply(a, b)
+    return a + b
+
+
 class _Linear(torch.autograd.Function):
     """y = x @ Wᵀ with three tcgen05 GEMM layouts: NT forward, NN for dX, TN for dW."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, wgrad_out):
+    def forward(ctx, x, weight, bias, wgrad_out, dead=False):
         ctx.save_for_backward(x, weight)
         ctx.has_bias = bias is not None
         ctx.wgrad_out = wgrad_out
+        if dead:  # graph only: dX needs W and dW needs x, nobody needs x·Wᵀ
+            return torch.empty(*x.shape[:-1], weight.shape[0], dtype=x.dtype, device=x.device)
         x2 = x.reshape(-1, x.shape[-1])
         y = gemm(x2, weight, 'nt')
         if bias is not None:
@@ -82,7 +123,7 @@ class _Linear(torch.autograd.Function):
                 gw = gemm(g2, x2, 'tn')
         if ctx.has_bias and ctx.needs_input_grad[2]:
             gb = g2.float().sum(0).to(gy.dtype)
-        return gx, gw, gb, None
+        return gx, gw, gb, None, None
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, layout: str = 'nt', out: Optional[torch.Tensor] = None,
@@ -102,9 +143,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, layout: str = 'nt', out: Optional[tor
     return r.to(out_dtype or a.dtype)
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, wgrad_out: Optional[torch.Tensor] = None):
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, wgrad_out: Optional[torch.Tensor] = None,
+           value_unused: bool = False):
+    """``value_unused``: the caller never reads the result when the graph is being rebuilt (see ``dead_values``)."""
     if _cuda(x) and x.dtype == torch.bfloat16:
-        return _Linear.apply(x, weight, bias, wgrad_out)
+        return _Linear.apply(x, weight, bias, wgrad_out, value_unused and _DeadValues.on)
     return torch.nn.functional.linear(x, weight, bias)
 
 

@@ -47,19 +47,25 @@ __global__ void rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __res
   }
 }
 
-// dx = rstd·(g·w' − x·rstd²·mean(g·w'·x)),  dw += Σ_rows g·x·rstd  (block partials in smem → global atomics)
+// dx = rstd·(g·w' − x·rstd²·mean(g·w'·x)),  dw += Σ_rows g·x·rstd.
+// Every warp keeps a private fp32 copy of dw in shared memory: lane l only ever touches the columns of its own
+// 16-byte vectors, so the accumulation needs no atomics; the warps' copies are summed once at the end and added to
+// the global result with one atomic per column and block.
 __global__ void rmsnorm_bwd_kernel(const bf16* __restrict__ g, const bf16* __restrict__ x, const bf16* __restrict__ w,
                                    const float* __restrict__ rstd, bf16* __restrict__ dx, float* __restrict__ dw, int rows, int H,
                                    float offset) {
-  extern __shared__ float s_dw[];
-  for (int i = threadIdx.x; i < H; i += blockDim.x) s_dw[i] = 0.f;
-  __syncthreads();
-  const int warps_per_block = blockDim.x >> 5, lane = threadIdx.x & 31;
+  extern __shared__ float s_dw[];  // [warps][H]
+  const int warps_per_block = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nvec = H >> 3;
-  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
+  float* my = s_dw + static_cast<size_t>(warp) * H;
+  for (int v = lane; v < nvec; v += 32) {
+    reinterpret_cast<float4*>(my)[2 * v] = make_float4(0.f, 0.f, 0.f, 0.f);
+    reinterpret_cast<float4*>(my)[2 * v + 1] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  for (int row = blockIdx.x * warps_per_block + warp; row < rows; row += gridDim.x * warps_per_block) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * H);
     const uint4* gr = reinterpret_cast<const uint4*>(g + static_cast<size_t>(row) * H);
-    const uint4* wr = reinterpret_cast<const uint4*>(w);
     const float r = rstd[row];
     float dot = 0.f;
     for (int v = lane; v < nvec; v += 32) {
@@ -75,21 +81,28 @@ __global__ void rmsnorm_bwd_kernel(const bf16* __restrict__ g, const bf16* __res
     const float coef = dot * r * r / H;
     uint4* dxr = reinterpret_cast<uint4*>(dx + static_cast<size_t>(row) * H);
     for (int v = lane; v < nvec; v += 32) {
-      uint4 ux = xr[v], ug = gr[v], uw = wr[v], o;
+      uint4 ux = xr[v], ug = gr[v], uw = wr[v], o;   // second read of the row comes from L1/L2
       const uint32_t* px = &ux.x; const uint32_t* pg = &ug.x; const uint32_t* pw = &uw.x; uint32_t* po = &o.x;
+      float4 d0 = reinterpret_cast<float4*>(my)[2 * v], d1 = reinterpret_cast<float4*>(my)[2 * v + 1];
+      float acc[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         float2 a = unpack_bf16(px[k]), b = unpack_bf16(pg[k]), c = unpack_bf16(pw[k]);
-        float d0 = r * (b.x * (c.x + offset) - a.x * coef), d1 = r * (b.y * (c.y + offset) - a.y * coef);
-        po[k] = pack_bf16(d0, d1);
-        atomicAdd(&s_dw[v * 8 + 2 * k], b.x * a.x * r);
-        atomicAdd(&s_dw[v * 8 + 2 * k + 1], b.y * a.y * r);
+        po[k] = pack_bf16(r * (b.x * (c.x + offset) - a.x * coef), r * (b.y * (c.y + offset) - a.y * coef));
+        acc[2 * k] += b.x * a.x * r;
+        acc[2 * k + 1] += b.y * a.y * r;
       }
+      reinterpret_cast<float4*>(my)[2 * v] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      reinterpret_cast<float4*>(my)[2 * v + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
       dxr[v] = o;
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < H; i += blockDim.x) atomicAdd(&dw[i], s_dw[i]);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float t = 0.f;
+    for (int wi = 0; wi < warps_per_block; ++wi) t += s_dw[static_cast<size_t>(wi) * H + i];
+    atomicAdd(&dw[i], t);
+  }
 }
 
 std::vector<torch::Tensor> rmsnorm_fwd(const torch::Tensor& x, const torch::Tensor& w, double eps, double offset) {
@@ -117,8 +130,18 @@ std::vector<torch::Tensor> rmsnorm_bwd(const torch::Tensor& g, const torch::Tens
   auto dx = torch::empty_like(x);
   auto dw = torch::zeros({H}, x.options().dtype(torch::kFloat32));
   if (rows == 0) return {dx, dw};
-  int blocks = std::min((rows + 7) / 8, num_sms() * 2);
-  rmsnorm_bwd_kernel<<<blocks, 256, H * sizeof(float), at::cuda::getCurrentCUDAStream()>>>(
+  // one private fp32 dw row per warp: as many warps as fit into shared memory (at most 8)
+  int warps = 8;
+  while (warps > 1 && static_cast<size_t>(warps) * H * sizeof(float) > 200 * 1024) warps >>= 1;
+  const size_t smem = static_cast<size_t>(warps) * H * sizeof(float);
+  TORCH_CHECK(smem <= 200 * 1024, "hidden size too large for the RMSNorm backward kernel");
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    TK_CUDA_CHECK(cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    configured = 200 * 1024;
+  }
+  int blocks = std::min((rows + warps - 1) / warps, num_sms());
+  rmsnorm_bwd_kernel<<<blocks, warps * 32, smem, at::cuda::getCurrentCUDAStream()>>>(
       reinterpret_cast<const bf16*>(g.data_ptr()), reinterpret_cast<const bf16*>(x.data_ptr()), reinterpret_cast<const bf16*>(w.data_ptr()),
       rstd.data_ptr<float>(), reinterpret_cast<bf16*>(dx.data_ptr()), dw.data_ptr<float>(), rows, H, static_cast<float>(offset));
   count_launch();

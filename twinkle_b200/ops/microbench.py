@@ -82,6 +82,11 @@ def make(op: str, a) -> Tuple[Callable[[], None], float, float]:
             with torch.no_grad():
                 ops.rmsnorm(x, w, 1e-6)
         return f, 0.0, 4.0 * a.tokens * a.hidden
+    if op == 'rmsnorm_bwd':
+        x, w = torch.randn(a.tokens, a.hidden, device=dev, dtype=bf), torch.ones(a.hidden, device=dev, dtype=bf)
+        g = torch.randn_like(x)
+        _, rstd = E.rmsnorm_fwd(x, w, 1e-6, 0.0)
+        return (lambda: E.rmsnorm_bwd(g, x, w, rstd, 0.0)), 0.0, 6.0 * a.tokens * a.hidden
     if op == 'swiglu':
         gu = torch.randn(a.tokens, 2 * a.hidden, device=dev, dtype=bf)
 

@@ -356,7 +356,8 @@ class _LayerFn(torch.autograd.Function):
         unit.prepare_grads(engine.pool)
         xd = x.detach().requires_grad_(True)
         with torch.enable_grad(), engine.restore_context(ctx.lora_ctx), (
-                ops.AttentionStash('reuse', ctx.attn) if ctx.attn is not None else nullcontext()):
+                ops.AttentionStash('reuse', ctx.attn) if ctx.attn is not None else nullcontext()), ops.dead_values():
+            # the layer is re-run for its graph only: the final projection and residual add are not computed
             y = layer(xd, cos, sin, batch)
             outs, grads = [y], [gy]
             if getattr(layer, 'is_moe', False) and layer.mlp.last_aux is not None:
