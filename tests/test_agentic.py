@@ -1,0 +1,161 @@
+"""Agentic package: tool dispatch, multi-turn rollout with a scripted sampler, environments, condensing, router
+sampler, rewards and filters (reference tests: tests/agentic/*)."""
+import json
+
+from twinkle_b200.agentic import (CoTReward, DeadLoopFilter, DedupFilter, Env, EnvPool, EnvTool, ExtractCondensed, F1Reward, FunctionTool,
+                                  HardFilter, KeywordCondenser, MessageSanityFilter, MultiTurnCondenseRollout, MultiTurnRollout, NativeChunker,
+                                  PIIFilter, RefuseFilter, RouterSampler, StepResult, TokenSoupFilter, ToolExploreReward, ToolManager,
+                                  f1_score, normalize_messages, parse_tool_calls)
+from twinkle_b200.data_format.sampling import SampledSequence, SampleResponse, SamplingParams
+
+
+class ScriptedSampler:
+    """Replies with the next scripted text for each trajectory (keyed by its first user message)."""
+
+    def __init__(self, scripts, logprob=-0.1):
+        self.scripts, self.turn, self.logprob, self.calls = scripts, {}, logprob, 0
+
+    def sample(self, trajectories, sampling_params=None, **kw):
+        self.calls += 1
+        out = []
+        for t in trajectories:
+            key = next(m['content'] for m in t['messages'] if m['role'] == 'user')
+            i = self.turn.get(key, 0)
+            self.turn[key] = i + 1
+            text = self.scripts[key][min(i, len(self.scripts[key]) - 1)]
+            toks = list(range(len(text.split())))
+            out.append(SampleResponse(sequences=[SampledSequence(stop_reason='stop', tokens=toks, logprobs=[self.logprob] * len(toks), decoded=text)]))
+        return out
+
+
+def _call(name, **args):
+    return '<tool_call>' + json.dumps({'name': name, 'arguments': args}) + '</tool_call>'
+
+
+def test_tool_manager_and_parse():
+    def add(a: int, b: int) -> int:
+        """Add two integers."""
+        return a + b
+
+    tm = ToolManager([FunctionTool(add)])
+    assert tm.names() == ['add'] and tm.tool_infos()[0]['parameters']['required'] == ['a', 'b']
+    calls = parse_tool_calls('thinking… ' + _call('add', a=2, b=3) + ' and ' + _call('nope'))
+    assert [c['tool_name'] for c in calls] == ['add', 'nope']
+    assert tm(calls[0]) == '5'
+    assert tm(calls[1]).startswith('Error: unknown tool')
+    assert 'not valid JSON' in tm({'tool_name': 'add', 'arguments': '{bad'})
+
+
+def test_multi_turn_rollout_runs_tools_until_answer():
+    def lookup(key: str) -> str:
+        return {'capital:fr': 'Paris'}.get(key, 'unknown')
+
+    scripts = {'q1': [_call('lookup', key='capital:fr'), 'The answer is <answer>Paris</answer>'],
+               'q2': ['<answer>42</answer>']}
+    sampler = ScriptedSampler(scripts)
+    ro = MultiTurnRollout(sampler, ToolManager([FunctionTool(lookup)]), max_turns=4, sampling_params=SamplingParams(max_tokens=32))
+    out = ro([{'messages': [{'role': 'user', 'content': 'q1'}]}, {'messages': [{'role': 'user', 'content': 'q2'}]}])
+    roles = [m['role'] for m in out[0]['messages']]
+    assert roles == ['user', 'assistant', 'tool', 'assistant']
+    assert out[0]['messages'][2]['content'] == 'Paris' and out[0]['messages'][1]['tool_calls'][0]['tool_name'] == 'lookup'
+    assert [m['role'] for m in out[1]['messages']] == ['user', 'assistant']
+    assert out[0]['user_data']['rollout'] == {'turns': 2, 'tool_calls': 1, 'tokens': out[0]['user_data']['rollout']['tokens'], 'stop': 'answer'}
+    assert sampler.calls == 2  # both trajectories share turn 1, only the first needs turn 2
+    assert F1Reward()(out, ['Paris', '41']) == [1.0, 0.0]
+    assert ToolExploreReward()(out, ['Paris', '42']) == [0.1, 0.0]
+    assert CoTReward()([{'messages': [{'role': 'assistant', 'content': 'First this. Then that. <answer>x</answer>'}]}]) == [1.0]
+
+
+class CountEnv(Env):
+    """Reach the target by calling ``inc``; reward 1 when reached."""
+
+    def reset(self, trajectory=None):
+        self.v, self.target = 0, int((trajectory or {}).get('user_data', {}).get('target', 2))
+        return StepResult('start')
+
+    def step(self, tool_name, arguments):
+        self.v += int(arguments.get('by', 1))
+        done = self.v >= self.target
+        return StepResult(f'value={self.v}', 1.0 if done else 0.0, done)
+
+    def tools(self):
+        return [{'tool_name': 'inc', 'description': 'increase', 'parameters': {'type': 'object', 'properties': {'by': {'type': 'integer'}}}}]
+
+
+def test_env_pool_rollout_stops_when_episode_ends():
+    pool = EnvPool(CountEnv, 2)
+    scripts = {'go': [_call('inc', by=1)] * 5}
+    ro = MultiTurnRollout(ScriptedSampler(scripts), pool.managers, max_turns=6)
+    out = ro([{'messages': [{'role': 'user', 'content': 'go'}], 'user_data': {'target': 2}}])
+    assert out[0]['user_data']['rollout']['stop'] == 'env_done' and out[0]['user_data']['rollout']['turns'] == 2
+    assert out[0]['user_data']['env_reward'] == 1.0
+
+
+def test_chunk_condense_extract_roundtrip():
+    long = ('Quarterly revenue rose sharply in the northern region. ' + 'The warehouse inventory figures were audited again. ' * 40)
+    traj = {'messages': [{'role': 'user', 'content': 'summarise'}, {'role': 'tool', 'content': long, 'tool_call_id': 'c1'},
+                         {'role': 'assistant', 'content': 'ok'}]}
+    chunks = NativeChunker(chunk_size=700)(traj)
+    assert all(len(c.content) <= 1400 for c in chunks) and ''.join(c.content for c in chunks if c.role == 'tool') == long
+    cond = KeywordCondenser(min_chars=300, budget_chars=160, keep_last=1)(chunks)
+    condensed = [c for c in cond if c.condensed]
+    assert condensed and all(len(c.content) <= 160 for c in condensed) and 'Quarterly revenue' in condensed[0].content
+    view = cond.to_trajectory()
+    assert sum(len(m['content']) for m in view['messages']) < len(long) / 2 and '[block 1, condensed]' in view['messages'][1]['content']
+    tool = ExtractCondensed(cond)
+    assert condensed[0].original in tool('extract_condensed', {'blocks': [1]}) and 'unknown' in tool('extract_condensed', {'blocks': [99]})
+
+
+def test_condense_rollout_presents_short_view_and_serves_originals():
+    long = 'Alpha beta gamma delta. ' * 800
+    seen = {}
+
+    class Spy(ScriptedSampler):
+
+        def sample(self, trajectories, sampling_params=None, **kw):
+            seen['chars'] = sum(len(m['content']) for m in trajectories[0]['messages'])
+            seen['tools'] = [t['tool_name'] for t in trajectories[0].get('tools') or []]
+            return super().sample(trajectories, sampling_params, **kw)
+
+    scripts = {'start': [_call('extract_condensed', blocks=[1]), '<answer>done</answer>']}
+    ro = MultiTurnCondenseRollout(Spy(scripts), condense_above_chars=2000, condenser=KeywordCondenser(min_chars=500, keep_last=0), max_turns=3)
+    out = ro([{'messages': [{'role': 'user', 'content': 'start'}, {'role': 'tool', 'content': long, 'tool_call_id': 'x'}]}])
+    assert seen['chars'] < len(long) / 3 and 'extract_condensed' in seen['tools']
+    tool_msgs = [m for m in out[0]['messages'] if m['role'] == 'tool']
+    assert tool_msgs[0]['content'] == long          # stored trajectory keeps the full text
+    assert tool_msgs[1]['content'].startswith('[block 1] Alpha beta')
+
+
+def test_router_sampler_reroutes_low_confidence():
+    cheap, strong = ScriptedSampler({'a': ['weak'], 'b': ['fine']}, logprob=-0.1), ScriptedSampler({'a': ['strong'], 'b': ['strong']})
+    cheap_resp = cheap.sample
+
+    def shaky(trajs, sp=None, **kw):
+        rs = cheap_resp(trajs, sp, **kw)
+        rs[0].sequences[0].logprobs = [-3.0] * 3  # first trajectory looks unreliable
+        return rs
+
+    cheap.sample = shaky
+    r = RouterSampler(cheap, strong, min_mean_logp=-1.0)
+    out = r.sample([{'messages': [{'role': 'user', 'content': 'a'}]}, {'messages': [{'role': 'user', 'content': 'b'}]}], SamplingParams(max_tokens=8))
+    assert [o.sequences[0].decoded for o in out] == ['strong', 'fine'] and r.routed == 1
+
+
+def test_filters_and_normaliser():
+    ok = {'messages': [{'role': 'user', 'content': 'hi'}, {'role': 'assistant', 'content': 'A clear and useful reply about sorting algorithms.'}]}
+    assert all(f.keep(ok) for f in (RefuseFilter(), DeadLoopFilter(), TokenSoupFilter(), HardFilter(), MessageSanityFilter(), PIIFilter()))
+    d = DedupFilter()
+    assert d.keep(ok) and not d.keep(json.loads(json.dumps(ok)))
+    assert not RefuseFilter().keep({'messages': [{'role': 'assistant', 'content': "I'm sorry, but I can't help with that."}]})
+    loop = {'messages': [{'role': 'assistant', 'content': '\n'.join(['the same long line again'] * 6)}]}
+    assert not DeadLoopFilter().keep(loop)
+    soup = {'messages': [{'role': 'assistant', 'content': ' '.join(['zq'] * 200)}]}
+    assert not TokenSoupFilter().keep(soup)
+    assert not PIIFilter().keep({'messages': [{'role': 'assistant', 'content': 'mail me at jo@example.com'}]})
+    masked = {'messages': [{'role': 'assistant', 'content': 'mail me at jo@example.com'}]}
+    assert PIIFilter(mask=True).keep(masked) and masked['messages'][0]['content'] == 'mail me at <email>'
+    assert not MessageSanityFilter().keep({'messages': [{'role': 'user', 'content': 'a'}, {'role': 'user', 'content': 'b'}]})
+    n = normalize_messages({'messages': [{'role': 'System', 'content': ' '}, {'role': 'user', 'content': [{'type': 'text', 'text': 'x'}]},
+                                         {'role': 'assistant', 'content': None, 'tool_calls': [{'id': '1', 'function': {'name': 'f', 'arguments': '{}'}}]}]})
+    assert [m['role'] for m in n['messages']] == ['user', 'assistant'] and n['messages'][1]['tool_calls'][0]['tool_name'] == 'f'
+    assert abs(f1_score('the cats sat', 'cat sat down') - 2 * (2 / 2) * (2 / 3) / ((2 / 2) + (2 / 3))) < 1e-9
