@@ -186,6 +186,8 @@ class TorchSampler(Sampler):
         HF names overwrite base weights (fused tensors are reassembled from their parts)."""
         base: Dict[str, torch.Tensor] = {}
         lora: Dict[str, torch.Tensor] = {}
+        if isinstance(weights, dict):
+            weights = weights.items()
         for k, v in weights:
             (lora if 'lora_' in k else base)[k] = v
         if base:
@@ -197,10 +199,12 @@ class TorchSampler(Sampler):
                     if all(x in base for x in names):
                         p.copy_(hf_to_internal(n, self.config, base.__getitem__).to(p.device, p.dtype))
         if lora:
-            if not self.multi_lora.has(self._synced_adapter):
+            # a named tenant keeps its own slot (multi-tenant RL); without a name the single "synced" slot is used
+            name = kwargs.get('adapter_name') or self._synced_adapter
+            if not self.multi_lora.has(name):
                 cfg = LoraConfig.from_any(peft_config or {'r': next(iter(lora.values())).shape[0] if lora else 8})
-                self.multi_lora.acquire_lora(self._synced_adapter, cfg)
-            self.multi_lora.set_state_dict(self._synced_adapter, {k: v.to(self.device) for k, v in lora.items()})
+                self.multi_lora.acquire_lora(name, cfg)
+            self.multi_lora.set_state_dict(name, {k: v.to(self.device) for k, v in lora.items()})
         self.engine.reset_prefix_cache()
 
     receive_weights = update_weights
