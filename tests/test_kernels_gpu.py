@@ -243,3 +243,25 @@ def test_tiny_model_matches_cpu_reference(E):
     lg, gg = run(gpu_model, 'cuda')
     assert abs(float(lc) - float(lg)) < 2e-2, (lc, lg)
     assert rel(gg, gc) < 3e-2
+
+
+def test_flash_attention_separate_key_ranges(E):
+    """Queries of an entry attend to a longer key range of their own, causal diagonal aligned bottom-right
+    (what context parallelism feeds the kernel): forward and all three gradients vs fp32."""
+    from twinkle_b200 import ops
+    torch.manual_seed(3)
+    hq, hkv, d = 8, 2, 128
+    q_lens, k_lens = [128, 200, 64, 300], [384, 200, 640, 428]
+    cu_q = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device='cuda')
+    cu_k = torch.tensor([0] + list(torch.tensor(k_lens).cumsum(0)), dtype=torch.int32, device='cuda')
+    q = torch.randn(sum(q_lens), hq, d, device='cuda').bfloat16().requires_grad_(True)
+    k = torch.randn(sum(k_lens), hkv, d, device='cuda').bfloat16().requires_grad_(True)
+    v = torch.randn(sum(k_lens), hkv, d, device='cuda').bfloat16().requires_grad_(True)
+    o = ops.flash_attn_varlen(q, k, v, cu_q, max(q_lens), True, cu_seqlens_k=cu_k, max_seqlen_k=max(k_lens))
+    g = torch.randn_like(o)
+    o.backward(g)
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    orf = ops.ref.attention_varlen(qr, kr, vr, cu_q, True, None, False, cu_k)
+    orf.backward(g.float())
+    assert rel(o, orf) < 6e-3
+    assert rel(q.grad, qr.grad) < 1.5e-2 and rel(k.grad, kr.grad) < 1.5e-2 and rel(v.grad, vr.grad) < 1.5e-2

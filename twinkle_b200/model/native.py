@@ -157,7 +157,9 @@ class TransformersModel(TwinkleModel):
         if not hasattr(self, '_comm'):
             group = None
             if dist.is_available() and dist.is_initialized():
-                dims = [d for d in ('dp', 'fsdp') if self.device_mesh.has_dim(d)]
+                # context-parallel ranks hold different tokens of the same sequences: for parameters and gradients they
+                # are data ranks like any other
+                dims = [d for d in ('dp', 'fsdp', 'cp') if self.device_mesh.has_dim(d)]
                 if dims and self.device_mesh.world_size == dist.get_world_size() and len(dims) < len(self.device_mesh.mesh_dim_names):
                     group = self.device_mesh.get_dim_group(tuple(dims))
             self._comm = Communicator(group, self.device, single=self.device_mesh.world_size == 1)
@@ -180,6 +182,9 @@ class TransformersModel(TwinkleModel):
         if self.sp_size > 1:
             from ..parallel.ulysses import apply_ulysses
             apply_ulysses(self.model, self.device_mesh, self.config, self.comm_backend)
+        if (self.device_mesh.cp_world_size or 1) > 1:
+            from ..parallel.context import apply_context_parallel
+            apply_context_parallel(self.model, self.device_mesh)
         if comm.world_size > 1 and self.comm_backend in ('auto', 'symm') and self.device.type == 'cuda':
             try:
                 from ..parallel.symm import SymmCommunicator
@@ -241,7 +246,7 @@ class TransformersModel(TwinkleModel):
         mb = mb.to(self.device)
         extras = mb.extras or {}
         batch = PackedBatch(mb.input_ids, mb.position_ids, mb.cu_seqlens, mb.max_seqlen, mb.labels,
-                            routed_experts=self._routed_for(extras, mb))
+                            routed_experts=self._routed_for(extras, mb), seq_lens=list(mb.seq_lens))
         loss_obj = og.loss_instance
         want_entropy = bool(getattr(loss_obj, 'require_entropy', False))
         want_logits = return_logits or bool(getattr(loss_obj, 'require_logits', False))
@@ -322,6 +327,32 @@ class TransformersModel(TwinkleModel):
             if out.get('logits') is not None:
                 out['logits'] = gather_tokens(out['logits'], comm)
             labels = comm.all_gather_tensor(labels)
+        cp = self.device_mesh.cp_world_size or 1
+        if cp > 1:
+            # zig-zag shards: concatenate the peers' pieces (differentiable for this rank's own piece) and put every
+            # token back at its position in the full packed row, so the loss sees whole sequences on every rank
+            from ..parallel.context import cp_group_for
+            from ..parallel.ulysses import gather_tokens
+            from ..processor import zigzag_indices
+            if not hasattr(self, '_cp'):
+                self._cp = Communicator(cp_group_for(self.device_mesh), self.device)
+            comm = self._cp
+            pieces = []
+            for r in range(cp):
+                off = 0
+                for n in mb.seq_lens:
+                    pieces.append(zigzag_indices(n, cp, r) + off)
+                    off += n
+            perm = torch.cat(pieces).to(self.device)
+
+            def full_row(x, fill, differentiable):
+                g = gather_tokens(x, comm) if differentiable else comm.all_gather_tensor(x)
+                return g.new_full((perm.numel(), ) + tuple(g.shape[1:]), fill).index_copy(0, perm, g)
+
+            for k in ('logps', 'entropies', 'logits'):
+                if out.get(k) is not None:
+                    out[k] = full_row(out[k], 0, True)
+            labels = full_row(labels, -100, False)
         out['packed_labels'] = labels
         for k in ('logps', 'entropies', 'logits'):
             if out.get(k) is not None:
@@ -336,7 +367,7 @@ class TransformersModel(TwinkleModel):
         loss = res['loss'] if isinstance(res, dict) else res
         nt = res.get('num_tokens', 0) if isinstance(res, dict) else 0
         nt_f = float(nt) if nt is not None else 0.0
-        contrib = (nt_f if nt_f > 0 else 1.0) / self.sp_size
+        contrib = (nt_f if nt_f > 0 else 1.0) / (self.sp_size * (self.device_mesh.cp_world_size or 1))
         if out.get('aux_loss') is not None and torch.is_tensor(out['aux_loss']):
             # scale so that after the later division by the denominator the aux term is O(coef)
             loss = loss + out['aux_loss'] * (nt_f if nt_f > 0 else 1.0)

@@ -36,6 +36,7 @@ class PackedBatch:
     # router replay: per layer [T, k] expert ids to force (reference moe/router_replay.py)
     routed_experts: Optional[List[torch.Tensor]] = None
     inputs_embeds: Optional[torch.Tensor] = None
+    seq_lens: Optional[List[int]] = None  # full (un-split) sequence lengths on the host; needed by context parallelism
 
 
 class Attention(nn.Module):
@@ -64,6 +65,9 @@ class Attention(nn.Module):
         if kv_sink is not None:  # sampler prefill: keep K/V for the paged cache
             kv_sink(self.layer_idx, k, v)
         ap = self.attn_parallel
+        if ap is not None and hasattr(ap, 'attention'):  # context parallel: zig-zag local chunks against gathered keys
+            o = ap.attention(q, k, v, batch.seq_lens, 1.0 / math.sqrt(self.d))
+            return self.o_proj(o.reshape(o.shape[0], -1))
         if ap is not None:
             q, k, v = ap.scatter_heads(q, k, v)  # [T_local,H,D] → [T_full,H/sp,D]
         o = ops.flash_attn_varlen(q, k, v, batch.cu_seqlens, batch.max_seqlen, True, 1.0 / math.sqrt(self.d))

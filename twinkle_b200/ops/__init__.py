@@ -246,18 +246,19 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
 class _FlashAttnVarlen(torch.autograd.Function):
 
     @staticmethod
-    def forward(ctx, q, k, v, cu_seqlens, max_seqlen, causal, scale):
-        out, lse = ext().flash_attn_fwd(q, k, v, cu_seqlens, max_seqlen, causal, scale)
-        ctx.save_for_backward(q, k, v, out, lse, cu_seqlens)
-        ctx.args = (max_seqlen, causal, scale)
-        return out
+    def forward(ctx, q, k, v, cu_seqlens, max_seqlen, causal, scale, cu_k=None, max_seqlen_k=0):
+        out, lse = ext().flash_attn_fwd(q, k, v, cu_seqlens, max_seqlen, causal, scale, cu_k)
+        ctx.save_for_backward(q, k, v, out, lse, cu_seqlens, cu_k if cu_k is not None else cu_seqlens)
+        ctx.args = (max_seqlen, causal, scale, cu_k is not None, max_seqlen_k)
+        ctx.mark_non_differentiable(lse)
+        return out, lse
 
     @staticmethod
-    def backward(ctx, gout):
-        q, k, v, out, lse, cu = ctx.saved_tensors
-        max_seqlen, causal, scale = ctx.args
-        dq, dk, dv = ext().flash_attn_bwd(gout.contiguous(), q, k, v, out, lse, cu, max_seqlen, causal, scale)
-        return dq, dk, dv, None, None, None, None
+    def backward(ctx, gout, _glse):
+        q, k, v, out, lse, cu, cu_k = ctx.saved_tensors
+        max_seqlen, causal, scale, has_k, max_k = ctx.args
+        dq, dk, dv = ext().flash_attn_bwd(gout.contiguous(), q, k, v, out, lse, cu, max_seqlen, causal, scale, cu_k if has_k else None, max_k)
+        return dq, dk, dv, None, None, None, None, None, None
 
 
 class _FlashAttnReuse(torch.autograd.Function):
@@ -295,9 +296,18 @@ class AttentionStash:
         AttentionStash.current = self._prev
 
 
-def flash_attn_varlen(q, k, v, cu_seqlens, max_seqlen: int, causal: bool = True, scale: Optional[float] = None):
-    """Packed causal attention with GQA.  ``q [T,Hq,D]``, ``k,v [T,Hkv,D]``."""
+def flash_attn_varlen(q, k, v, cu_seqlens, max_seqlen: int, causal: bool = True, scale: Optional[float] = None,
+                      cu_seqlens_k=None, max_seqlen_k: int = 0, return_lse: bool = False):
+    """Packed causal attention with GQA.  ``q [T,Hq,D]``, ``k,v [Tk,Hkv,D]``.  ``cu_seqlens_k``: the keys of every
+    sequence are a (longer) range of their own; the causal diagonal is aligned bottom-right."""
     scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
+    if cu_seqlens_k is not None or return_lse:
+        if _cuda(q) and q.dtype == torch.bfloat16:
+            out, lse = _FlashAttnVarlen.apply(q.contiguous(), k.contiguous(), v.contiguous(), cu_seqlens.to(torch.int32), int(max_seqlen), causal,
+                                              scale, None if cu_seqlens_k is None else cu_seqlens_k.to(torch.int32), int(max_seqlen_k))
+        else:
+            out, lse = ref.attention_varlen(q, k, v, cu_seqlens, causal, scale, True, cu_seqlens_k)
+        return (out, lse) if return_lse else out
     if _cuda(q) and q.dtype == torch.bfloat16:
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         cu = cu_seqlens.to(torch.int32)
@@ -310,7 +320,7 @@ def flash_attn_varlen(q, k, v, cu_seqlens, max_seqlen: int, causal: bool = True,
             out, lse = st.items[st._i]
             st._i += 1
             return _FlashAttnReuse.apply(q, k, v, out, lse, cu, int(max_seqlen), causal, scale)
-        return _FlashAttnVarlen.apply(q, k, v, cu, int(max_seqlen), causal, scale)
+        return _FlashAttnVarlen.apply(q, k, v, cu, int(max_seqlen), causal, scale)[0]
     return ref.attention_varlen(q, k, v, cu_seqlens, causal, scale)
 
 

@@ -46,6 +46,7 @@ struct BwdParams {
   int T, hq, hkv;
   float scale, scale_log2;
   int causal;
+  const int* cu_k;   // key/value boundaries (== cu for self-attention over the same packing)
   int* err;
 };
 
@@ -72,13 +73,15 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO, const BwdParams p) {
   using namespace fb;
   const int kv_head = blockIdx.x, seq = blockIdx.z;
-  const int seq_start = p.cu[seq], seq_len = p.cu[seq + 1] - seq_start;
-  const int n_tiles = (seq_len + BT - 1) / BT;
+  const int seq_start = p.cu[seq], seq_len = p.cu[seq + 1] - seq_start;          // queries
+  const int kv_start = p.cu_k[seq], kv_len = p.cu_k[seq + 1] - kv_start;         // keys / values
+  const int q_off = kv_len - seq_len;            // causal: query row r sees keys 0 … r + q_off
+  const int n_tiles = (kv_len + BT - 1) / BT;
   if (static_cast<int>(blockIdx.y) >= n_tiles) return;
   const int kv0 = blockIdx.y * BT;               // early tiles have the most query blocks → scheduled first
   const int G = p.hq / p.hkv;
-  const int qb_begin = p.causal ? kv0 / BI : 0;
   const int qb_end = (seq_len + BI - 1) / BI;
+  const int qb_begin = p.causal ? min(max(kv0 - q_off, 0) / BI, qb_end) : 0;
   const int per_head = qb_end - qb_begin;
   const int n_iter = per_head * G;
 
@@ -123,10 +126,10 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     // producer warp: lane 0 drives TMA; all lanes stage lse (log2 units) and δ of each query block in smem
     if (lane == 0) {
       mbar_expect_tx(kv_full, 2 * OUTER_BYTES);
-      tma_load_3d(smem + KV_SMEM_K, &tmK, kv_full, 0, kv_head, seq_start + kv0);
-      tma_load_3d(smem + KV_SMEM_K + OUTER_ATOM, &tmK, kv_full, 64, kv_head, seq_start + kv0);
-      tma_load_3d(smem + KV_SMEM_V, &tmV, kv_full, 0, kv_head, seq_start + kv0);
-      tma_load_3d(smem + KV_SMEM_V + OUTER_ATOM, &tmV, kv_full, 64, kv_head, seq_start + kv0);
+      tma_load_3d(smem + KV_SMEM_K, &tmK, kv_full, 0, kv_head, kv_start + kv0);
+      tma_load_3d(smem + KV_SMEM_K + OUTER_ATOM, &tmK, kv_full, 64, kv_head, kv_start + kv0);
+      tma_load_3d(smem + KV_SMEM_V, &tmV, kv_full, 0, kv_head, kv_start + kv0);
+      tma_load_3d(smem + KV_SMEM_V + OUTER_ATOM, &tmV, kv_full, 64, kv_head, kv_start + kv0);
     }
     for (int it = 0; it < n_iter; ++it) {
       const int st = it & 1;
@@ -213,7 +216,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int kv_pos = kv0 + row;
-    const bool row_valid = kv_pos < seq_len;
+    const bool row_valid = kv_pos < kv_len;
     bool ok = true;
     for (int it = 0; it < n_iter; ++it) {
       const int st = it & 1;
@@ -237,7 +240,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             const int col = c * 32 + i + e;
             const int qpos = qb0 + col;
             float pr = exp2f(__uint_as_float(s[i + e]) * p.scale_log2 - lse2[col]);
-            if (!row_valid || (p.causal && qpos < kv_pos)) pr = 0.f;
+            if (!row_valid || (p.causal && qpos + q_off < kv_pos)) pr = 0.f;
             pv[e] = pr;
             dv[e] = pr * (__uint_as_float(dp[i + e]) - dl[col]);
           }
@@ -257,8 +260,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
     if (ok && n_iter > 0 && mbar_wait(acc_done, (n_iter - 1) & 1, p.err, ERR_ATTN_WAIT)) {
       tc_fence_after();
-      bf16* dkrow = p.dk + (static_cast<size_t>(seq_start + kv_pos) * p.hkv + kv_head) * D;
-      bf16* dvrow = p.dv + (static_cast<size_t>(seq_start + kv_pos) * p.hkv + kv_head) * D;
+      bf16* dkrow = p.dk + (static_cast<size_t>(kv_start + kv_pos) * p.hkv + kv_head) * D;
+      bf16* dvrow = p.dv + (static_cast<size_t>(kv_start + kv_pos) * p.hkv + kv_head) * D;
 #pragma unroll 1
       for (int c = 2 * wg; c < 2 * wg + 2; ++c) {
         uint32_t a[32], b[32];
@@ -281,8 +284,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       }
     } else if (n_iter == 0 && row_valid) {
       // no query attends to this tile (cannot happen with causal self-attention, kept for safety)
-      bf16* dkrow = p.dk + (static_cast<size_t>(seq_start + kv_pos) * p.hkv + kv_head) * D;
-      bf16* dvrow = p.dv + (static_cast<size_t>(seq_start + kv_pos) * p.hkv + kv_head) * D;
+      bf16* dkrow = p.dk + (static_cast<size_t>(kv_start + kv_pos) * p.hkv + kv_head) * D;
+      bf16* dvrow = p.dv + (static_cast<size_t>(kv_start + kv_pos) * p.hkv + kv_head) * D;
       for (int i = wg * 64; i < wg * 64 + 64; i += 8) {
         *reinterpret_cast<uint4*>(dkrow + i) = make_uint4(0, 0, 0, 0);
         *reinterpret_cast<uint4*>(dvrow + i) = make_uint4(0, 0, 0, 0);
@@ -308,7 +311,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (static_cast<int>(blockIdx.y) >= n_tiles) return;
   const int q0 = (n_tiles - 1 - blockIdx.y) * BT;
   const int kv_head = head / (p.hq / p.hkv);
-  const int kv_end = p.causal ? min(seq_len, q0 + BT) : seq_len;
+  const int kv_start = p.cu_k[seq], kv_len = p.cu_k[seq + 1] - kv_start;
+  const int q_off = kv_len - seq_len;
+  const int kv_end = p.causal ? max(0, min(kv_len, q0 + BT + q_off)) : kv_len;
   const int n_iter = (kv_end + BI - 1) / BI;
 
   extern __shared__ uint8_t smem_raw[];
@@ -357,7 +362,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       for (int it = 0; it < n_iter; ++it) {
         const int st = it & 1;
         if (it >= 2 && !mbar_wait(&kv_empty[st], ((it >> 1) - 1) & 1, p.err, ERR_ATTN_WAIT)) break;
-        const int row = seq_start + it * BI;
+        const int row = kv_start + it * BI;
         mbar_expect_tx(&kv_full[st], 2 * INNER_BYTES);
         tma_load_3d(smem + DQ_SMEM_K + st * INNER_BYTES, &tmK, &kv_full[st], 0, kv_head, row);
         tma_load_3d(smem + DQ_SMEM_K + st * INNER_BYTES + INNER_ATOM, &tmK, &kv_full[st], 64, kv_head, row);
@@ -441,7 +446,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           for (int e = 0; e < 2; ++e) {
             const int kv_pos = kvb + c * 32 + i + e;
             float pr = exp2f(__uint_as_float(s[i + e]) * p.scale_log2 - lse2);
-            if (kv_pos >= seq_len || (p.causal && kv_pos > q_pos)) pr = 0.f;
+            if (kv_pos >= kv_len || (p.causal && kv_pos > q_pos + q_off)) pr = 0.f;
             dv[e] = pr * (__uint_as_float(dp[i + e]) - dl);
           }
           dsk[i >> 1] = pack_bf16(dv[0], dv[1]);
@@ -484,7 +489,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
 std::vector<torch::Tensor> flash_attn_bwd(const torch::Tensor& dout, const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v,
                                           const torch::Tensor& out, const torch::Tensor& lse, const torch::Tensor& cu, int64_t max_seqlen,
-                                          bool causal, double scale) {
+                                          bool causal, double scale, const c10::optional<torch::Tensor>& cu_k, int64_t max_seqlen_k) {
   TORCH_CHECK(dout.is_contiguous() && q.is_contiguous() && k.is_contiguous() && v.is_contiguous() && out.is_contiguous(), "contiguous inputs");
   TORCH_CHECK(dout.scalar_type() == torch::kBFloat16 && dout.sizes() == q.sizes(), "dout like q");
   c10::cuda::CUDAGuard guard(q.device());
@@ -504,6 +509,11 @@ std::vector<torch::Tensor> flash_attn_bwd(const torch::Tensor& dout, const torch
   p.lse = lse.data_ptr<float>(); p.delta = delta.data_ptr<float>(); p.cu = cu.data_ptr<int>();
   p.T = T; p.hq = hq; p.hkv = hkv; p.scale = static_cast<float>(scale); p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
   p.causal = causal; p.err = error_word();
+  p.cu_k = p.cu;
+  if (cu_k.has_value() && cu_k->defined()) {
+    TORCH_CHECK(cu_k->is_cuda() && cu_k->scalar_type() == torch::kInt32 && cu_k->is_contiguous() && cu_k->numel() == cu.numel(), "cu_k like cu");
+    p.cu_k = cu_k->data_ptr<int>();
+  }
   static bool configured = false;
   if (!configured) {
     TK_CUDA_CHECK(cudaFuncSetAttribute(flash_bwd_dkdv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, fb::KV_SMEM_TOTAL));
@@ -511,9 +521,10 @@ std::vector<torch::Tensor> flash_attn_bwd(const torch::Tensor& dout, const torch
     configured = true;
   }
   const int tiles = (static_cast<int>(max_seqlen) + fb::BT - 1) / fb::BT;
+  const int tiles_k = (static_cast<int>(max_seqlen_k > 0 ? max_seqlen_k : max_seqlen) + fb::BT - 1) / fb::BT;
   {
     CUtensorMap tq = make_head_tmap(q, fb::BI), tdo = make_head_tmap(dout, fb::BI), tk_ = make_head_tmap(k, fb::BT), tv = make_head_tmap(v, fb::BT);
-    dim3 grid(hkv, tiles, nseq);
+    dim3 grid(hkv, tiles_k, nseq);
     flash_bwd_dkdv_kernel<<<grid, fb::THREADS, fb::KV_SMEM_TOTAL, stream>>>(tq, tk_, tv, tdo, p);
   }
   {

@@ -33,7 +33,8 @@ constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
 struct FwdParams {
   bf16* out;          // [T, Hq, D]
   float* lse;         // [Hq, T]  natural-log LSE of the scaled scores
-  const int* cu;      // [n+1]
+  const int* cu;      // [n+1] query boundaries
+  const int* cu_k;    // [n+1] key/value boundaries (== cu for self-attention over the same packing)
   int T, hq, hkv;
   float scale_log2;   // softmax scale · log2(e)
   int causal;
@@ -52,7 +53,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int qt = n_qtiles - 1 - blockIdx.y;
   const int q0 = qt * BQ;
   const int kv_head = head / (p.hq / p.hkv);
-  const int kv_end = p.causal ? min(seq_len, q0 + BQ) : seq_len;
+  // keys may be longer than queries (a query chunk against a key prefix): the causal diagonal is aligned to the
+  // bottom-right corner, i.e. query row r sees keys 0 … r + q_off
+  const int kv_start = p.cu_k[seq], kv_len = p.cu_k[seq + 1] - kv_start;
+  const int q_off = kv_len - seq_len;
+  const int kv_end = p.causal ? max(0, min(kv_len, q0 + BQ + q_off)) : kv_len;
   const int n_blocks = (kv_end + BKV - 1) / BKV;
 
   extern __shared__ uint8_t smem_raw[];
@@ -104,7 +109,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int j = 0; j < n_blocks; ++j) {
         const int st = j & 1;
         if (j >= 2 && !mbar_wait(&kv_empty[st], ((j >> 1) - 1) & 1, p.err, ERR_ATTN_WAIT)) break;
-        const int row = seq_start + j * BKV;
+        const int row = kv_start + j * BKV;
         mbar_expect_tx(&k_full[st], TILE_BYTES);
         tma_load_3d(smem + SMEM_K + st * TILE_BYTES, &tmK, &k_full[st], 0, kv_head, row);
         tma_load_3d(smem + SMEM_K + st * TILE_BYTES + ATOM_BYTES, &tmK, &k_full[st], 64, kv_head, row);
@@ -185,13 +190,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_ld_wait();
         tc_fence_before();
         mbar_arrive(&s_empty[j & 1]);                 // scores are in registers: the TMEM buffer may be refilled
-        const bool need_mask = (kv0 + 64 > kv_end) || (p.causal && kv0 + 64 > q0);
+        const bool need_mask = (kv0 + 64 > kv_end) || (p.causal && kv0 + 64 > q0 + q_off);
 #pragma unroll
         for (int i = 0; i < 64; ++i) {
           float sv = __uint_as_float(i < 32 ? r0[i] : r1[i - 32]) * p.scale_log2;
           if (need_mask) {
             const int col = kv0 + i;
-            if (col >= kv_end || (p.causal && col > q_pos)) sv = -INFINITY;
+            if (col >= kv_end || (p.causal && col > q_pos + q_off)) sv = -INFINITY;
           }
           sc[i] = sv;
           mx = fmaxf(mx, sv);
@@ -284,7 +289,7 @@ CUtensorMap make_head_tmap(const torch::Tensor& t, int rows) {
 }
 
 std::vector<torch::Tensor> flash_attn_fwd(const torch::Tensor& q, const torch::Tensor& k, const torch::Tensor& v, const torch::Tensor& cu,
-                                          int64_t max_seqlen, bool causal, double scale) {
+                                          int64_t max_seqlen, bool causal, double scale, const c10::optional<torch::Tensor>& cu_k) {
   TORCH_CHECK(q.is_cuda() && q.scalar_type() == torch::kBFloat16 && q.dim() == 3 && q.is_contiguous(), "q [T,Hq,128] bf16 contiguous");
   TORCH_CHECK(k.is_contiguous() && v.is_contiguous() && k.sizes() == v.sizes() && k.scalar_type() == torch::kBFloat16, "k/v [T,Hkv,128]");
   TORCH_CHECK(q.size(2) == 128 && k.size(2) == 128, "head_dim must be 128");
@@ -298,6 +303,11 @@ std::vector<torch::Tensor> flash_attn_fwd(const torch::Tensor& q, const torch::T
   CUtensorMap tq = make_head_tmap(q, 128), tk_ = make_head_tmap(k, 128), tv = make_head_tmap(v, 128);
   FwdParams p{};
   p.out = reinterpret_cast<bf16*>(out.data_ptr()); p.lse = lse.data_ptr<float>(); p.cu = cu.data_ptr<int>();
+  p.cu_k = p.cu;
+  if (cu_k.has_value() && cu_k->defined()) {
+    TORCH_CHECK(cu_k->is_cuda() && cu_k->scalar_type() == torch::kInt32 && cu_k->is_contiguous() && cu_k->numel() == cu.numel(), "cu_k like cu");
+    p.cu_k = cu_k->data_ptr<int>();
+  }
   p.T = T; p.hq = hq; p.hkv = hkv; p.scale_log2 = static_cast<float>(scale * 1.4426950408889634); p.causal = causal; p.err = error_word();
   static bool configured = false;
   if (!configured) {

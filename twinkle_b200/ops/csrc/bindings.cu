@@ -25,9 +25,10 @@ std::vector<torch::Tensor> logprob_fwd(const torch::Tensor&, const torch::Tensor
 torch::Tensor logprob_bwd(torch::Tensor, const torch::Tensor&, const torch::Tensor&, const c10::optional<torch::Tensor>&,
                           const torch::Tensor&, const c10::optional<torch::Tensor>&, double);
 std::vector<torch::Tensor> flash_attn_fwd(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, int64_t,
-                                          bool, double);
+                                          bool, double, const c10::optional<torch::Tensor>&);
 std::vector<torch::Tensor> flash_attn_bwd(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&,
-                                          const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, int64_t, bool, double);
+                                          const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, int64_t, bool, double,
+                                          const c10::optional<torch::Tensor>&, int64_t);
 std::tuple<torch::Tensor, py::bytes, int64_t> symm_alloc(int64_t);
 int64_t symm_open(const py::bytes&);
 void symm_close(int64_t);
@@ -68,8 +69,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sumsq", &tk::sumsq);
   m.def("logprob_fwd", &tk::logprob_fwd);
   m.def("logprob_bwd", &tk::logprob_bwd);
-  m.def("flash_attn_fwd", &tk::flash_attn_fwd);
-  m.def("flash_attn_bwd", &tk::flash_attn_bwd);
+  m.def("flash_attn_fwd", &tk::flash_attn_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("cu"), py::arg("max_seqlen"), py::arg("causal"),
+        py::arg("scale"), py::arg("cu_k") = py::none());
+  m.def("flash_attn_bwd", &tk::flash_attn_bwd, py::arg("dout"), py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("lse"), py::arg("cu"),
+        py::arg("max_seqlen"), py::arg("causal"), py::arg("scale"), py::arg("cu_k") = py::none(), py::arg("max_seqlen_k") = 0);
   m.def("symm_alloc", &tk::symm_alloc, "cudaMalloc'ed uint8 tensor + its CUDA IPC handle");
   m.def("symm_open", &tk::symm_open);
   m.def("symm_close", &tk::symm_close);

@@ -14,57 +14,119 @@ namespace tk {
 using bf16 = __nv_bfloat16;
 
 // ---------------------------------------------------------------- paged decode
-// One CTA per (sequence, kv head); 4 warps split the context tokens; lane l owns dims [4l, 4l+4).
-// Each warp keeps an online-softmax state per query head of the group; warps are merged through smem.
-template <int G>
+// One CTA per (sequence, kv head, group of GH query heads); 4 warps.  A warp handles 4 context tokens per step —
+// 8 lanes per token, 16 dims (two 16-byte loads of K, two of V) per lane — and two steps are issued back to back, so
+// 32 token rows per CTA are in flight.  Every lane group keeps an online-softmax state per query head; lane groups
+// and warps are merged at the end.
+template <int GH>
 __global__ void __launch_bounds__(128) paged_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const bf16* __restrict__ vc,
-                                                           const int* __restrict__ tables, const int* __restrict__ seq_lens, bf16* __restrict__ out,
-                                                           int hq, int hkv, int block_size, int max_blocks, float scale_log2) {
+                                                            const int* __restrict__ tables, const int* __restrict__ seq_lens, bf16* __restrict__ out,
+                                                            int hq, int hkv, int block_size, int max_blocks, float scale_log2, int G) {
   constexpr int D = 128;
-  const int b = blockIdx.x, kvh = blockIdx.y;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.x, kvh = blockIdx.y, h0 = kvh * G + blockIdx.z * GH;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, grp = lane >> 3, sub = lane & 7;  // sub owns dims [16·sub, 16·sub+16)
   const int n = seq_lens[b];
-  float qv[G][4];
+  float qv[GH][16];
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    const uint2 raw = *reinterpret_cast<const uint2*>(q + (static_cast<size_t>(b) * hq + kvh * G + g) * D + lane * 4);
-    const float2 a = unpack_bf16(raw.x), c = unpack_bf16(raw.y);
-    qv[g][0] = a.x * scale_log2; qv[g][1] = a.y * scale_log2; qv[g][2] = c.x * scale_log2; qv[g][3] = c.y * scale_log2;
-  }
-  float m[G], l[G], acc[G][4];
+  for (int g = 0; g < GH; ++g) {
+    const uint4* qp = reinterpret_cast<const uint4*>(q + (static_cast<size_t>(b) * hq + h0 + g) * D + sub * 16);
 #pragma unroll
-  for (int g = 0; g < G; ++g) { m[g] = -INFINITY; l[g] = 0.f; acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f; }
-  const int* table = tables + static_cast<size_t>(b) * max_blocks;
-  for (int t = warp; t < n; t += 4) {
-    const int blk = table[t / block_size], off = t % block_size;
-    const size_t base = ((static_cast<size_t>(blk) * block_size + off) * hkv + kvh) * D + lane * 4;
-    const uint2 kr = *reinterpret_cast<const uint2*>(kc + base);
-    const uint2 vr = *reinterpret_cast<const uint2*>(vc + base);
-    const float2 k0 = unpack_bf16(kr.x), k1 = unpack_bf16(kr.y), v0 = unpack_bf16(vr.x), v1 = unpack_bf16(vr.y);
+    for (int h = 0; h < 2; ++h) {
+      const uint4 u = qp[h];
+      const uint32_t* pu = &u.x;
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float s = warp_sum(qv[g][0] * k0.x + qv[g][1] * k0.y + qv[g][2] * k1.x + qv[g][3] * k1.y);
-      const float mn = fmaxf(m[g], s);
-      const float corr = exp2f(m[g] - mn), p = exp2f(s - mn);
-      l[g] = l[g] * corr + p;
-      acc[g][0] = acc[g][0] * corr + p * v0.x; acc[g][1] = acc[g][1] * corr + p * v0.y;
-      acc[g][2] = acc[g][2] * corr + p * v1.x; acc[g][3] = acc[g][3] * corr + p * v1.y;
-      m[g] = mn;
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = unpack_bf16(pu[k]);
+        qv[g][h * 8 + 2 * k] = f.x * scale_log2;
+        qv[g][h * 8 + 2 * k + 1] = f.y * scale_log2;
+      }
     }
   }
-  __shared__ float s_m[4][G], s_l[4][G], s_acc[4][G][D];
+  float m[GH], l[GH], acc[GH][16];
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
+  for (int g = 0; g < GH; ++g) {
+    m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+    for (int d = 0; d < 16; ++d) acc[g][d] = 0.f;
+  }
+  const int* table = tables + static_cast<size_t>(b) * max_blocks;
+  // token handled by (warp, grp) in half-step u of iteration `base`: t = base + grp + 16·u.  The loop bound depends on
+  // the warp only, so all 32 lanes stay in the loop together (the shuffles below name the full warp).
+  for (int base = warp * 4; base < n; base += 32) {
+    const int t0 = base + grp;
+    uint4 kr[2][2], vr[2][2];
+    bool live[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int t = t0 + u * 16;
+      live[u] = t < n;
+      if (live[u]) {
+        const int blk = table[t / block_size], off = t % block_size;
+        const size_t base = ((static_cast<size_t>(blk) * block_size + off) * hkv + kvh) * D + sub * 16;
+        const uint4* kp = reinterpret_cast<const uint4*>(kc + base);
+        const uint4* vp = reinterpret_cast<const uint4*>(vc + base);
+        kr[u][0] = kp[0]; kr[u][1] = kp[1];
+        vr[u][0] = vp[0]; vr[u][1] = vp[1];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      float kf[16], vf[16];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t* pk = &kr[u][h].x;
+        const uint32_t* pv = &vr[u][h].x;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 a = unpack_bf16(pk[k]), c = unpack_bf16(pv[k]);
+          kf[h * 8 + 2 * k] = a.x; kf[h * 8 + 2 * k + 1] = a.y;
+          vf[h * 8 + 2 * k] = c.x; vf[h * 8 + 2 * k + 1] = c.y;
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < GH; ++g) {
+        float s = 0.f;
+#pragma unroll
+        for (int d = 0; d < 16; ++d) s += qv[g][d] * kf[d];
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        if (live[u]) {  // uniform inside an 8-lane group
+          const float mn = fmaxf(m[g], s);
+          const float corr = exp2f(m[g] - mn), p = exp2f(s - mn);
+          l[g] = l[g] * corr + p;
+#pragma unroll
+          for (int d = 0; d < 16; ++d) acc[g][d] = acc[g][d] * corr + p * vf[d];
+          m[g] = mn;
+        }
+      }
+    }
+  }
+  // merge the 4 lane groups of the warp, then the 4 warps
+  __shared__ float s_m[4][GH], s_l[4][GH], s_acc[4][GH][D];
+#pragma unroll
+  for (int g = 0; g < GH; ++g) {
+#pragma unroll
+    for (int o = 8; o <= 16; o <<= 1) {
+      const float mo = __shfl_xor_sync(0xffffffffu, m[g], o), lo = __shfl_xor_sync(0xffffffffu, l[g], o);
+      const float mn = fmaxf(m[g], mo);
+      const float c0 = (m[g] == -INFINITY) ? 0.f : exp2f(m[g] - mn), c1 = (mo == -INFINITY) ? 0.f : exp2f(mo - mn);
+#pragma unroll
+      for (int d = 0; d < 16; ++d) acc[g][d] = acc[g][d] * c0 + __shfl_xor_sync(0xffffffffu, acc[g][d], o) * c1;
+      l[g] = l[g] * c0 + lo * c1;
+      m[g] = mn;
+    }
     if (lane == 0) { s_m[warp][g] = m[g]; s_l[warp][g] = l[g]; }
+    if (grp == 0) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) s_acc[warp][g][lane * 4 + i] = acc[g][i];
+      for (int d = 0; d < 16; ++d) s_acc[warp][g][sub * 16 + d] = acc[g][d];
+    }
   }
   __syncthreads();
-  // thread d (0..127) finishes dimension d of every head of the group
-  const int d = threadIdx.x;
+  const int d = threadIdx.x;  // thread d (0..127) finishes dimension d of every head of the group
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    float mm = fmaxf(fmaxf(s_m[0][g], s_m[1][g]), fmaxf(s_m[2][g], s_m[3][g]));
+  for (int g = 0; g < GH; ++g) {
+    const float mm = fmaxf(fmaxf(s_m[0][g], s_m[1][g]), fmaxf(s_m[2][g], s_m[3][g]));
     float ll = 0.f, o = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
@@ -72,7 +134,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const bf16* __restric
       ll += s_l[w][g] * c;
       o += s_acc[w][g][d] * c;
     }
-    out[(static_cast<size_t>(b) * hq + kvh * G + g) * D + d] = __float2bfloat16(ll > 0.f ? o / ll : 0.f);
+    out[(static_cast<size_t>(b) * hq + h0 + g) * D + d] = __float2bfloat16(ll > 0.f ? o / ll : 0.f);
   }
 }
 
@@ -85,19 +147,20 @@ torch::Tensor paged_attn_decode(const torch::Tensor& q, const torch::Tensor& kc,
   const int B = q.size(0), hq = q.size(1), hkv = kc.size(2), G = hq / hkv;
   auto out = torch::empty_like(q);
   if (B == 0) return out;
-  dim3 grid(B, hkv);
   const float sl2 = static_cast<float>(scale * 1.4426950408889634);
   auto stream = at::cuda::getCurrentCUDAStream();
+  // query heads of a group are processed GH at a time (register budget): G = 8 → two CTAs per (sequence, kv head)
+  const int GH = G >= 4 ? 4 : G;
+  TORCH_CHECK(G == 1 || G == 2 || G == 4 || G == 8, "GQA group size must be 1, 2, 4 or 8");
+  dim3 grid(B, hkv, G / GH);
 #define TK_DEC(GG)                                                                                                                   \
   paged_decode_kernel<GG><<<grid, 128, 0, stream>>>(reinterpret_cast<const bf16*>(q.data_ptr()), reinterpret_cast<const bf16*>(kc.data_ptr()), \
       reinterpret_cast<const bf16*>(vc.data_ptr()), tables.data_ptr<int>(), seq_lens.data_ptr<int>(), reinterpret_cast<bf16*>(out.data_ptr()),  \
-      hq, hkv, static_cast<int>(kc.size(1)), static_cast<int>(tables.size(1)), sl2)
-  switch (G) {
+      hq, hkv, static_cast<int>(kc.size(1)), static_cast<int>(tables.size(1)), sl2, G)
+  switch (GH) {
     case 1: TK_DEC(1); break;
     case 2: TK_DEC(2); break;
-    case 4: TK_DEC(4); break;
-    case 8: TK_DEC(8); break;
-    default: TORCH_CHECK(false, "GQA group size must be 1, 2, 4 or 8");
+    default: TK_DEC(4); break;
   }
 #undef TK_DEC
   count_launch();
@@ -130,36 +193,57 @@ __global__ void __launch_bounds__(512) sample_kernel(const float* __restrict__ l
   __shared__ int sh_i[32];
   const int row = blockIdx.x;
   const float* x = logits + static_cast<size_t>(row) * V;
-  float mx = -INFINITY;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, x[i] * inv_temp);
-  mx = block_reduce(mx, true, sh);
-  float z = 0.f;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) z += __expf(x[i] * inv_temp - mx);
-  z = block_reduce(z, false, sh);
+  // max and sum-exp in one pass (online softmax per thread, merged across the block)
+  float mx = -INFINITY, z = 0.f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float y = x[i] * inv_temp;
+    if (y > mx) { z = z * __expf(mx - y) + 1.f; mx = y; } else { z += __expf(y - mx); }
+  }
+  {
+    const float m_all = block_reduce(mx, true, sh);
+    z = block_reduce(z * __expf(mx - m_all), false, sh);
+    mx = m_all;
+  }
   float tau = 0.f, kept_mass = 1.f;  // threshold on p = e^{x−mx}/z
   const bool use_k = top_k > 0 && top_k < V, use_p = top_p < 1.f;
   if (!greedy && (use_k || use_p)) {
-    // τ_k: highest threshold that still keeps ≥ k tokens; τ_p: highest that still keeps mass ≥ top_p.
-    // The kept set must respect both limits → τ = max(τ_k, τ_p).
-    for (int which = 0; which < 2; ++which) {
-      if ((which == 0 && !use_k) || (which == 1 && !use_p)) continue;
-      float lo = 0.f, hi = 1.f / z;  // p_max = 1/z
-      for (int it = 0; it < 30; ++it) {
-        const float mid = 0.5f * (lo + hi);
-        float acc = 0.f;
-        for (int i = threadIdx.x; i < V; i += blockDim.x) {
-          const float p = __expf(x[i] * inv_temp - mx) / z;
-          if (p >= mid) acc += (which == 0) ? 1.f : p;
+    // τ_k: highest threshold that still keeps ≥ k tokens; τ_p: highest that still keeps mass ≥ top_p; the kept set
+    // respects both limits → τ = max(τ_k, τ_p).  Each pass over the row tests 15 thresholds per search (16-way
+    // narrowing of [lo, hi)), so 8 passes resolve both thresholds to 2⁻³² of the largest probability.
+    constexpr int NT = 15;
+    float lo_k = 0.f, hi_k = 1.f / z, lo_p = 0.f, hi_p = 1.f / z;  // p_max = 1/z
+    const float inv_z = 1.f / z;
+    for (int it = 0; it < 8; ++it) {
+      float ck[NT], cp[NT];
+#pragma unroll
+      for (int j = 0; j < NT; ++j) { ck[j] = 0.f; cp[j] = 0.f; }
+      const float dk = (hi_k - lo_k) * (1.f / 16.f), dp = (hi_p - lo_p) * (1.f / 16.f);
+      for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float p = __expf(x[i] * inv_temp - mx) * inv_z;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          ck[j] += (p >= lo_k + dk * (j + 1)) ? 1.f : 0.f;
+          cp[j] += (p >= lo_p + dp * (j + 1)) ? p : 0.f;
         }
-        acc = block_reduce(acc, false, sh);
-        const bool ok = (which == 0) ? (acc >= static_cast<float>(top_k)) : (acc >= top_p);
-        if (ok) lo = mid; else hi = mid;
       }
-      tau = fmaxf(tau, lo);
+      int jk = -1, jp = -1;
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        const float a_k = use_k ? block_reduce(ck[j], false, sh) : 0.f;
+        const float a_p = use_p ? block_reduce(cp[j], false, sh) : 0.f;
+        if (a_k >= static_cast<float>(top_k)) jk = j;   // counts and masses fall with j: the last j that passes is the highest
+        if (a_p >= top_p) jp = j;
+      }
+      const float nlo_k = lo_k + dk * (jk + 1), nlo_p = lo_p + dp * (jp + 1);
+      hi_k = (jk == NT - 1) ? hi_k : nlo_k + dk;
+      hi_p = (jp == NT - 1) ? hi_p : nlo_p + dp;
+      lo_k = nlo_k;
+      lo_p = nlo_p;
     }
+    tau = fmaxf(use_k ? lo_k : 0.f, use_p ? lo_p : 0.f);
     float mass = 0.f;
     for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      const float p = __expf(x[i] * inv_temp - mx) / z;
+      const float p = __expf(x[i] * inv_temp - mx) * inv_z;
       if (p >= tau) mass += p;
     }
     kept_mass = block_reduce(mass, false, sh);

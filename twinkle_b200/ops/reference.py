@@ -67,10 +67,11 @@ def geglu(gate_up: torch.Tensor) -> torch.Tensor:
 
 # ----------------------------------------------------------------- attention
 def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor, causal: bool = True,
-                     scale: Optional[float] = None, return_lse: bool = False):
-    """Packed attention.  ``q [T,Hq,D]``, ``k,v [T,Hkv,D]``, ``cu_seqlens`` int
+                     scale: Optional[float] = None, return_lse: bool = False, cu_seqlens_k: Optional[torch.Tensor] = None):
+    """Packed attention.  ``q [T,Hq,D]``, ``k,v [Tk,Hkv,D]``, ``cu_seqlens`` int
     ``[n+1]``; tokens of different segments never attend to each other; GQA by
-    repeating each kv head ``Hq/Hkv`` times."""
+    repeating each kv head ``Hq/Hkv`` times.  With ``cu_seqlens_k`` the keys of a segment may be longer than its
+    queries; the causal diagonal is then aligned bottom-right (query row r sees keys 0 … r + Lk − Lq)."""
     T, Hq, D = q.shape
     Hkv = k.shape[1]
     rep = Hq // Hkv
@@ -78,16 +79,17 @@ def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
     out = torch.empty_like(q)
     lse = torch.empty(Hq, T, dtype=torch.float32, device=q.device)
     bounds = cu_seqlens.tolist()
-    for a, b in zip(bounds[:-1], bounds[1:]):
+    kb = bounds if cu_seqlens_k is None else cu_seqlens_k.tolist()
+    for a, b, ka, kbnd in zip(bounds[:-1], bounds[1:], kb[:-1], kb[1:]):
         if b <= a:
             continue
         qs = q[a:b].float().transpose(0, 1)  # [Hq, L, D]
-        ks = k[a:b].float().transpose(0, 1).repeat_interleave(rep, 0)
-        vs = v[a:b].float().transpose(0, 1).repeat_interleave(rep, 0)
+        ks = k[ka:kbnd].float().transpose(0, 1).repeat_interleave(rep, 0)
+        vs = v[ka:kbnd].float().transpose(0, 1).repeat_interleave(rep, 0)
         s = qs @ ks.transpose(1, 2) * scale
         if causal:
-            L = b - a
-            s = s.masked_fill(torch.ones(L, L, dtype=torch.bool, device=q.device).triu(1), float('-inf'))
+            L, Lk = b - a, kbnd - ka
+            s = s.masked_fill(torch.ones(L, Lk, dtype=torch.bool, device=q.device).triu(1 + Lk - L), float('-inf'))
         l = torch.logsumexp(s, -1)
         p = torch.exp(s - l[..., None])
         out[a:b] = (p @ vs).transpose(0, 1).to(q.dtype)

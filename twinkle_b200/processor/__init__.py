@@ -79,7 +79,7 @@ class InputProcessor:
 
     def __init__(self, device_mesh=None, padding_free: bool = True, padding_side: str = 'right', pad_token_id: int = 0,
                  framework: str = 'native', micro_batch_size: Optional[int] = None, max_tokens_per_micro_batch: Optional[int] = None,
-                 sp_size: Optional[int] = None, sp_rank: Optional[int] = None, cp_size: int = 1, cp_rank: int = 0,
+                 sp_size: Optional[int] = None, sp_rank: Optional[int] = None, cp_size: Optional[int] = None, cp_rank: Optional[int] = None,
                  pad_to_multiple_of: int = 1, **kwargs):
         self.device_mesh = device_mesh
         self.padding_free, self.padding_side, self.pad_token_id = padding_free, padding_side, pad_token_id
@@ -88,7 +88,8 @@ class InputProcessor:
         self.max_tokens_per_micro_batch = max_tokens_per_micro_batch
         self.sp_size = sp_size if sp_size is not None else ((device_mesh.ulysses_size or 1) if device_mesh is not None else 1)
         self.sp_rank = sp_rank if sp_rank is not None else (device_mesh.ulysses_rank if device_mesh is not None else 0)
-        self.cp_size, self.cp_rank = cp_size, cp_rank
+        self.cp_size = cp_size if cp_size is not None else ((device_mesh.cp_world_size or 1) if device_mesh is not None else 1)
+        self.cp_rank = cp_rank if cp_rank is not None else ((device_mesh.cp_rank or 0) if device_mesh is not None else 0)
         self.pad_to_multiple_of = pad_to_multiple_of
 
     # ------------------------------------------------------------- features
