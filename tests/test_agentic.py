@@ -159,3 +159,25 @@ def test_filters_and_normaliser():
                                          {'role': 'assistant', 'content': None, 'tool_calls': [{'id': '1', 'function': {'name': 'f', 'arguments': '{}'}}]}]})
     assert [m['role'] for m in n['messages']] == ['user', 'assistant'] and n['messages'][1]['tool_calls'][0]['tool_name'] == 'f'
     assert abs(f1_score('the cats sat', 'cat sat down') - 2 * (2 / 2) * (2 / 3) / ((2 / 2) + (2 / 3))) < 1e-9
+
+
+def test_tool_call_formats_round_trip():
+    from twinkle_b200.template.tools import get_format, parse_tool_calls, tools_system_prompt
+    call = {'tool_name': 'read_file', 'arguments': {'path': 'a.py', 'lines': '1-5'}}
+    for name in ('hermes', 'react', 'cline', 'vcp'):
+        f = get_format(name)
+        text = 'Let me look.\n' + f.render(call) + '\n'
+        assert f.detect(text), name
+        got = f.parse(text)
+        assert len(got) == 1 and got[0]['tool_name'] == 'read_file', (name, got)
+        args = got[0]['arguments']
+        assert {k: str(v) for k, v in args.items()} == {'path': 'a.py', 'lines': '1-5'}, (name, args)
+        assert 'Let me look.' in f.strip(text) and 'read_file' not in f.strip(text), name
+    calls, rest, fmt = parse_tool_calls('Thought: need it\nAction: search\nAction Input: {"q": "b200"}\nObservation: …')
+    assert fmt == 'react' and calls[0]['arguments'] == {'q': 'b200'}
+    calls, rest, fmt = parse_tool_calls('<thinking>hm</thinking> no tools here')
+    assert calls == [] and fmt is None
+    vcp = get_format('vcp')
+    nested = vcp.render({'tool_name': 'echo', 'arguments': {'text': 'has 「末」 inside'}})
+    assert vcp.parse(nested)[0]['arguments']['text'] == 'has 「末」 inside'
+    assert '<tool_call>' in tools_system_prompt([{'tool_name': 'x', 'description': 'd', 'parameters': {}}])

@@ -26,22 +26,11 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const bf16* __restric
   const int b = blockIdx.x, kvh = blockIdx.y, h0 = kvh * G + blockIdx.z * GH;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, grp = lane >> 3, sub = lane & 7;  // sub owns dims [16·sub, 16·sub+16)
   const int n = seq_lens[b];
-  float qv[GH][16];
-#pragma unroll
-  for (int g = 0; g < GH; ++g) {
-    const uint4* qp = reinterpret_cast<const uint4*>(q + (static_cast<size_t>(b) * hq + h0 + g) * D + sub * 16);
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const uint4 u = qp[h];
-      const uint32_t* pu = &u.x;
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float2 f = unpack_bf16(pu[k]);
-        qv[g][h * 8 + 2 * k] = f.x * scale_log2;
-        qv[g][h * 8 + 2 * k + 1] = f.y * scale_log2;
-      }
-    }
-  }
+  // the query (pre-scaled, fp32) lives in shared memory: registers are kept for two iterations' worth of K/V rows
+  __shared__ float s_q[GH][D];
+  for (int i = threadIdx.x; i < GH * D; i += blockDim.x)
+    s_q[i / D][i % D] = __bfloat162float(q[(static_cast<size_t>(b) * hq + h0 + i / D) * D + i % D]) * scale_log2;
+  __syncthreads();
   float m[GH], l[GH], acc[GH][16];
 #pragma unroll
   for (int g = 0; g < GH; ++g) {
@@ -51,26 +40,29 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const bf16* __restric
   }
   const int* table = tables + static_cast<size_t>(b) * max_blocks;
   // token handled by (warp, grp) in half-step u of iteration `base`: t = base + grp + 16·u.  The loop bound depends on
-  // the warp only, so all 32 lanes stay in the loop together (the shuffles below name the full warp).
-  for (int base = warp * 4; base < n; base += 32) {
-    const int t0 = base + grp;
-    uint4 kr[2][2], vr[2][2];
-    bool live[2];
+  // the warp only, so all 32 lanes stay in the loop together (the shuffles below name the full warp).  The rows of
+  // iteration i+1 are requested before iteration i is consumed.
+  uint4 kr[2][2], vr[2][2], kn[2][2], vn[2][2];
+  auto fetch = [&](int base, uint4 (&kk)[2][2], uint4 (&vv)[2][2]) {
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
-      const int t = t0 + u * 16;
-      live[u] = t < n;
-      if (live[u]) {
+      const int t = base + grp + u * 16;
+      if (t < n) {
         const int blk = table[t / block_size], off = t % block_size;
-        const size_t base = ((static_cast<size_t>(blk) * block_size + off) * hkv + kvh) * D + sub * 16;
-        const uint4* kp = reinterpret_cast<const uint4*>(kc + base);
-        const uint4* vp = reinterpret_cast<const uint4*>(vc + base);
-        kr[u][0] = kp[0]; kr[u][1] = kp[1];
-        vr[u][0] = vp[0]; vr[u][1] = vp[1];
+        const size_t base_off = ((static_cast<size_t>(blk) * block_size + off) * hkv + kvh) * D + sub * 16;
+        const uint4* kp = reinterpret_cast<const uint4*>(kc + base_off);
+        const uint4* vp = reinterpret_cast<const uint4*>(vc + base_off);
+        kk[u][0] = kp[0]; kk[u][1] = kp[1];
+        vv[u][0] = vp[0]; vv[u][1] = vp[1];
       }
     }
+  };
+  if (warp * 4 < n) fetch(warp * 4, kr, vr);
+  for (int base = warp * 4; base < n; base += 32) {
+    if (base + 32 < n) fetch(base + 32, kn, vn);
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
+      const bool live = base + grp + u * 16 < n;
       float kf[16], vf[16];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -86,12 +78,17 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const bf16* __restric
 #pragma unroll
       for (int g = 0; g < GH; ++g) {
         float s = 0.f;
+        const float4* qs = reinterpret_cast<const float4*>(&s_q[g][sub * 16]);
 #pragma unroll
-        for (int d = 0; d < 16; ++d) s += qv[g][d] * kf[d];
+        for (int d4 = 0; d4 < 4; ++d4) {
+          const float4 qq = qs[d4];
+          s += qq.x * kf[4 * d4] + qq.y * kf[4 * d4 + 1] + qq.z * kf[4 * d4 + 2] + qq.w * kf[4 * d4 + 3];
+        }
+        if (!live) s = 0.f;  // rows that were not fetched hold stale registers
         s += __shfl_xor_sync(0xffffffffu, s, 1);
         s += __shfl_xor_sync(0xffffffffu, s, 2);
         s += __shfl_xor_sync(0xffffffffu, s, 4);
-        if (live[u]) {  // uniform inside an 8-lane group
+        if (live) {  // uniform inside an 8-lane group
           const float mn = fmaxf(m[g], s);
           const float corr = exp2f(m[g] - mn), p = exp2f(s - mn);
           l[g] = l[g] * corr + p;
@@ -100,6 +97,11 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const bf16* __restric
           m[g] = mn;
         }
       }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      kr[u][0] = kn[u][0]; kr[u][1] = kn[u][1];
+      vr[u][0] = vn[u][0]; vr[u][1] = vn[u][1];
     }
   }
   // merge the 4 lane groups of the warp, then the 4 warps
