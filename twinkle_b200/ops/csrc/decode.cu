@@ -49,11 +49,10 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const bf16* __restric
       const int t = base + grp + u * 16;
       if (t < n) {
         const int blk = table[t / block_size], off = t % block_size;
-        const size_t base_off = ((static_cast<size_t>(blk) * block_size + off) * hkv + kvh) * D + sub * 16;
-        const uint4* kp = reinterpret_cast<const uint4*>(kc + base_off);
-        const uint4* vp = reinterpret_cast<const uint4*>(vc + base_off);
-        kk[u][0] = kp[0]; kk[u][1] = kp[1];
-        vv[u][0] = vp[0]; vv[u][1] = vp[1];
+        // lane `sub` owns dims [8·sub, 8·sub+8) and [64+8·sub, 64+8·sub+8): each load instruction covers 128 contiguous bytes per token
+        const size_t base_off = ((static_cast<size_t>(blk) * block_size + off) * hkv + kvh) * D + sub * 8;
+        kk[u][0] = *reinterpret_cast<const uint4*>(kc + base_off); kk[u][1] = *reinterpret_cast<const uint4*>(kc + base_off + 64);
+        vv[u][0] = *reinterpret_cast<const uint4*>(vc + base_off); vv[u][1] = *reinterpret_cast<const uint4*>(vc + base_off + 64);
       }
     }
   };
@@ -78,11 +77,14 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const bf16* __restric
 #pragma unroll
       for (int g = 0; g < GH; ++g) {
         float s = 0.f;
-        const float4* qs = reinterpret_cast<const float4*>(&s_q[g][sub * 16]);
 #pragma unroll
-        for (int d4 = 0; d4 < 4; ++d4) {
-          const float4 qq = qs[d4];
-          s += qq.x * kf[4 * d4] + qq.y * kf[4 * d4 + 1] + qq.z * kf[4 * d4 + 2] + qq.w * kf[4 * d4 + 3];
+        for (int h = 0; h < 2; ++h) {
+          const float4* qs = reinterpret_cast<const float4*>(&s_q[g][h * 64 + sub * 8]);
+#pragma unroll
+          for (int d4 = 0; d4 < 2; ++d4) {
+            const float4 qq = qs[d4];
+            s += qq.x * kf[h * 8 + 4 * d4] + qq.y * kf[h * 8 + 4 * d4 + 1] + qq.z * kf[h * 8 + 4 * d4 + 2] + qq.w * kf[h * 8 + 4 * d4 + 3];
+          }
         }
         if (!live) s = 0.f;  // rows that were not fetched hold stale registers
         s += __shfl_xor_sync(0xffffffffu, s, 1);
@@ -121,7 +123,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const bf16* __restric
     if (lane == 0) { s_m[warp][g] = m[g]; s_l[warp][g] = l[g]; }
     if (grp == 0) {
 #pragma unroll
-      for (int d = 0; d < 16; ++d) s_acc[warp][g][sub * 16 + d] = acc[g][d];
+      for (int d = 0; d < 16; ++d) s_acc[warp][g][(d >> 3) * 64 + sub * 8 + (d & 7)] = acc[g][d];
     }
   }
   __syncthreads();

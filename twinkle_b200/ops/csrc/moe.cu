@@ -211,7 +211,9 @@ __global__ void __launch_bounds__(256) ep_rows_gather_kernel(EpPtrs xs, EpPtrs t
   if (blockIdx.x == 0 && threadIdx.x == 0 && total_rows != nullptr && *total_rows > R) atomicCAS(err, 0, ERR_BOUNDS);
   const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
   const int nvec = H >> 3;
-  for (int r = blockIdx.x * warps + (threadIdx.x >> 5); r < R; r += gridDim.x * warps) {
+  // rows past the last expert segment belong to no GEMM tile and are never read: leave them untouched
+  const int used = total_rows != nullptr ? min(R, *total_rows) : R;
+  for (int r = blockIdx.x * warps + (threadIdx.x >> 5); r < used; r += gridDim.x * warps) {
     const int s = src_rank[r];
     uint4* o = reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * H);
     if (s < 0) {

@@ -161,7 +161,7 @@ class SymmExpertParallel:
     older set have been issued on its stream — so no extra "buffer free" barrier is needed.
     """
 
-    def __init__(self, comm, num_experts: int, capacity_factor: float = 2.0):
+    def __init__(self, comm, num_experts: int, capacity_factor: float = 1.5):
         self.comm, self.ep, self.rank = comm, comm.world_size, comm.rank
         assert num_experts % self.ep == 0
         self.num_experts, self.local = num_experts, num_experts // self.ep
