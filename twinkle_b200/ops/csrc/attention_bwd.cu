@@ -232,20 +232,31 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         tmem_ld32(tmem_base + 128 + st * 64 + c * 32 + lane_off, dp);
         tmem_ld_wait();
         uint32_t pk[16], dsk[16];
+        // only blocks that touch the causal diagonal need per-element masking; rows past the end of the keys are
+        // zeroed wholesale; query rows past the end carry lse = +inf and vanish through exp2
+        const bool diag = p.causal && (qb0 + q_off < kv0 + BT - 1);
+        const float4* l4 = reinterpret_cast<const float4*>(lse2 + c * 32);
+        const float4* d4 = reinterpret_cast<const float4*>(dl + c * 32);
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float pv[2], dv[2];
+        for (int i = 0; i < 32; i += 4) {
+          const float4 lv = l4[i >> 2], dv4 = d4[i >> 2];
+          const float ls[4] = {lv.x, lv.y, lv.z, lv.w}, ds[4] = {dv4.x, dv4.y, dv4.z, dv4.w};
+          float pv[4], dv[4];
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int col = c * 32 + i + e;
-            const int qpos = qb0 + col;
-            float pr = exp2f(__uint_as_float(s[i + e]) * p.scale_log2 - lse2[col]);
-            if (!row_valid || (p.causal && qpos + q_off < kv_pos)) pr = 0.f;
+          for (int e = 0; e < 4; ++e) {
+            float pr = exp2f(__uint_as_float(s[i + e]) * p.scale_log2 - ls[e]);
+            if (diag && (qb0 + c * 32 + i + e + q_off < kv_pos)) pr = 0.f;
             pv[e] = pr;
-            dv[e] = pr * (__uint_as_float(dp[i + e]) - dl[col]);
+            dv[e] = pr * (__uint_as_float(dp[i + e]) - ds[e]);
           }
           pk[i >> 1] = pack_bf16(pv[0], pv[1]);
+          pk[(i >> 1) + 1] = pack_bf16(pv[2], pv[3]);
           dsk[i >> 1] = pack_bf16(dv[0], dv[1]);
+          dsk[(i >> 1) + 1] = pack_bf16(dv[2], dv[3]);
+        }
+        if (!row_valid) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) { pk[i] = 0u; dsk[i] = 0u; }
         }
         // S/dP are in registers: the TMEM buffers can be refilled while we finish
         tc_fence_before();
@@ -439,14 +450,18 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tmem_ld32(tmem_base + 128 + st * 64 + c * 32 + lane_off, dp);
         tmem_ld_wait();
         uint32_t dsk[16];
+        // masking is needed only where the block crosses the causal diagonal of this query tile or the end of the keys
+        const bool edge = (kvb + BI > kv_len) || (p.causal && kvb + BI - 1 > q0 + q_off);
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           float dv[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int kv_pos = kvb + c * 32 + i + e;
             float pr = exp2f(__uint_as_float(s[i + e]) * p.scale_log2 - lse2);
-            if (kv_pos >= kv_len || (p.causal && kv_pos > q_pos + q_off)) pr = 0.f;
+            if (edge) {
+              const int kv_pos = kvb + c * 32 + i + e;
+              if (kv_pos >= kv_len || (p.causal && kv_pos > q_pos + q_off)) pr = 0.f;
+            }
             dv[e] = pr * (__uint_as_float(dp[i + e]) - dl);
           }
           dsk[i >> 1] = pack_bf16(dv[0], dv[1]);

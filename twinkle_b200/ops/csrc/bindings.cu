@@ -32,7 +32,7 @@ std::vector<torch::Tensor> flash_attn_bwd(const torch::Tensor&, const torch::Ten
 std::tuple<torch::Tensor, py::bytes, int64_t> symm_alloc(int64_t);
 int64_t symm_open(const py::bytes&);
 void symm_close(int64_t);
-void symm_barrier(const std::vector<int64_t>&, int64_t, int64_t);
+void symm_barrier(const std::vector<int64_t>&, int64_t, int64_t, int64_t);
 void peer_all_gather(torch::Tensor, const std::vector<int64_t>&, int64_t, int64_t, int64_t);
 void peer_reduce_scatter_acc(torch::Tensor, const std::vector<int64_t>&, int64_t, double, const c10::optional<torch::Tensor>&, int64_t);
 void ulysses_exchange(const torch::Tensor&, const std::vector<int64_t>&, int64_t, bool, int64_t);
@@ -76,7 +76,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("symm_alloc", &tk::symm_alloc, "cudaMalloc'ed uint8 tensor + its CUDA IPC handle");
   m.def("symm_open", &tk::symm_open);
   m.def("symm_close", &tk::symm_close);
-  m.def("symm_barrier", &tk::symm_barrier);
+  m.def("symm_barrier", &tk::symm_barrier, py::arg("flag_ptrs"), py::arg("rank"), py::arg("epoch"), py::arg("timeout_ms") = 3000);
   m.def("peer_all_gather", &tk::peer_all_gather);
   m.def("peer_reduce_scatter_acc", &tk::peer_reduce_scatter_acc);
   m.def("ulysses_exchange", &tk::ulysses_exchange);

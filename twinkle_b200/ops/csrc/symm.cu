@@ -86,7 +86,7 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
 }
 
 // flags: each rank owns int[MAX_PEERS]; slot k of rank r is written by rank k.
-__global__ void symm_barrier_kernel(PeerPtrs flags, int rank, int world, int epoch, int* err) {
+__global__ void symm_barrier_kernel(PeerPtrs flags, int rank, int world, int epoch, int* err, unsigned long long limit_ns) {
   const int t = threadIdx.x;
   if (t < world) {
     __threadfence_system();
@@ -99,7 +99,7 @@ __global__ void symm_barrier_kernel(PeerPtrs flags, int rank, int world, int epo
     uint32_t it = 0;
     while (ld_acquire_sys(mine) < epoch) {
       if ((++it & 0xff) == 0) {
-        if (global_timer_ns() - t0 > 3000000000ull) {  // 3 s
+        if (global_timer_ns() - t0 > limit_ns) {  // default 3 s
           atomicCAS(err, 0, ERR_PEER_FLAG);
           break;
         }
@@ -109,12 +109,13 @@ __global__ void symm_barrier_kernel(PeerPtrs flags, int rank, int world, int epo
   }
 }
 
-void symm_barrier(const std::vector<int64_t>& flag_ptrs, int64_t rank, int64_t epoch) {
+void symm_barrier(const std::vector<int64_t>& flag_ptrs, int64_t rank, int64_t epoch, int64_t timeout_ms) {
   PeerPtrs f{};
   const int world = flag_ptrs.size();
   TORCH_CHECK(world <= MAX_PEERS, "too many peers");
   for (int i = 0; i < world; ++i) f.p[i] = reinterpret_cast<void*>(flag_ptrs[i]);
-  symm_barrier_kernel<<<1, 32, 0, at::cuda::getCurrentCUDAStream()>>>(f, static_cast<int>(rank), world, static_cast<int>(epoch), error_word());
+  symm_barrier_kernel<<<1, 32, 0, at::cuda::getCurrentCUDAStream()>>>(f, static_cast<int>(rank), world, static_cast<int>(epoch), error_word(),
+                                                                      static_cast<unsigned long long>(timeout_ms > 0 ? timeout_ms : 3000) * 1000000ull);
   count_launch();
   TK_CUDA_CHECK(cudaGetLastError());
 }

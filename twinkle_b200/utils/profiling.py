@@ -1,0 +1,79 @@
+"""Device-side timing and profiler ranges.
+
+The reference has no GPU timing beyond wall-clock ``iters/s`` (``src/twinkle/metric/train_metric.py:52-60``).  Here a
+step is timed on the device with CUDA events on the launching stream, reduced with MAX over the ranks of a group
+(the number every multi-GPU figure in this repository is quoted as), and the fused paths are wrapped in NVTX ranges
+so a timeline shows them by name.
+"""
+from __future__ import annotations
+
+import time
+from contextlib import contextmanager
+from typing import Dict, List, Optional
+
+import torch
+
+
+class DeviceTimer:
+    """``with timer('fwd'): …`` records one interval; ``summary()`` returns mean milliseconds per name, max over ranks.
+    On CPU it falls back to ``time.perf_counter``."""
+
+    def __init__(self, group=None, enabled: bool = True):
+        self.group, self.enabled = group, enabled
+        self._open: Dict[str, List] = {}
+        self._host: Dict[str, List[float]] = {}
+
+    @contextmanager
+    def __call__(self, name: str):
+        if not self.enabled:
+            yield
+            return
+        cuda = torch.cuda.is_available()
+        with nvtx_range(name):
+            if cuda:
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                yield
+                b.record()
+                self._open.setdefault(name, []).append((a, b))
+            else:
+                t0 = time.perf_counter()
+                yield
+                self._host.setdefault(name, []).append((time.perf_counter() - t0) * 1e3)
+
+    def summary(self, reset: bool = True) -> Dict[str, float]:
+        out: Dict[str, float] = {}
+        if self._open:
+            torch.cuda.synchronize()
+        for name, pairs in self._open.items():
+            ms = [a.elapsed_time(b) for a, b in pairs]
+            out[name] = sum(ms) / len(ms)
+        for name, ms in self._host.items():
+            out[name] = sum(ms) / len(ms)
+        import torch.distributed as dist
+        if out and dist.is_available() and dist.is_initialized() and (self.group is not None or dist.get_world_size() > 1):
+            names = sorted(out)
+            dev = 'cuda' if (torch.cuda.is_available() and dist.get_backend(self.group) == 'nccl') else 'cpu'
+            t = torch.tensor([out[n] for n in names], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+            out = dict(zip(names, t.tolist()))
+        if reset:
+            self._open, self._host = {}, {}
+        return out
+
+
+@contextmanager
+def nvtx_range(name: str):
+    """NVTX range when CUDA is present (visible in Nsight timelines), no-op otherwise."""
+    if torch.cuda.is_available():
+        torch.cuda.nvtx.range_push(name)
+        try:
+            yield
+        finally:
+            torch.cuda.nvtx.range_pop()
+    else:
+        yield
+
+
+def tokens_per_second(num_tokens: float, ms: float) -> float:
+    return num_tokens / (ms / 1e3) if ms > 0 else 0.0
