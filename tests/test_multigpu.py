@@ -1,4 +1,7 @@
-"""2-GPU parity: peer-memory collectives vs NCCL, sharded and sequence-parallel training vs one GPU."""
+"""Multi-GPU parity checks, one short torchrun per group (2 ranks): fused tensor-parallel GEMM+collective kernels vs
+NCCL + library GEMM, expert parallel (NCCL and peer-memory modes) vs one GPU, tensor x pipeline parallel vs one GPU.
+``TK_MGPU_FULL=1`` adds the long group (peer all-gather / reduce-scatter / Ulysses kernels and FSDP / Ulysses
+training parity in both communication modes)."""
 import json
 import os
 import subprocess
@@ -9,14 +12,32 @@ import pytest
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
 
-def test_two_gpu_checks():
+def _run(only: str, port: int, timeout: int):
     import torch
     n = min(torch.cuda.device_count(), 2)
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, NCCL_NVLS_ENABLE='0')
+    env = dict(os.environ, NCCL_NVLS_ENABLE='0', TK_MGPU_ONLY=only)
     r = subprocess.run([sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', f'--nproc-per-node={n}', '--master-addr', '127.0.0.1',
-                        '--master-port', '29631', os.path.join(root, 'tests', 'mgpu_worker.py')], capture_output=True, text=True,
-                       timeout=900, env=env)
+                        '--master-port', str(port), os.path.join(root, 'tests', 'mgpu_worker.py')], capture_output=True, text=True,
+                       timeout=timeout, env=env)
     lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith('{')]
     assert r.returncode == 0, (r.stdout[-3000:], r.stderr[-3000:])
     assert lines and all(l['ok'] for l in lines), lines
+    return lines
+
+
+def test_fused_tensor_parallel_kernels():
+    _run('tp_fused', 29631, 240)
+
+
+def test_expert_parallel_matches_single_gpu():
+    _run('ep', 29632, 240)
+
+
+def test_tensor_pipeline_parallel_matches_single_gpu():
+    _run('megatron', 29633, 240)
+
+
+@pytest.mark.skipif(os.environ.get('TK_MGPU_FULL') != '1', reason='long group: set TK_MGPU_FULL=1')
+def test_peer_collectives_and_fsdp_ulysses_parity():
+    _run('', 29634, 1500)
