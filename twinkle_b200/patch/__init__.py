@@ -28,7 +28,7 @@ class Patch:
 class FusedCEPatch(Patch):
 
     def __call__(self, model, **kwargs):
-        self._prev = model.task
+        self._prev = getattr(model, 'task', None)
         model.task = 'fused_lm_ce'
         return self
 
@@ -39,7 +39,7 @@ class FusedCEPatch(Patch):
 class EmbeddingPatch(Patch):
 
     def __call__(self, model, **kwargs):
-        self._prev = model.task
+        self._prev = getattr(model, 'task', None)
         model.task = 'embedding'
         return self
 
