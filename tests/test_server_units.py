@@ -1,0 +1,129 @@
+"""Server building blocks without any HTTP: atomic state updates under contention, cleanup-leader election and
+hand-over, session sweep, rate limiter / preflight, config validation, and the hang guards fed with bad payloads
+(reference tiers: tests/server/state/*, tests/server/utils/*, tests/server/config/*, nccl-safe e2e payload list)."""
+import threading
+
+import pytest
+import torch
+
+from twinkle_b200.server.state import FileBackend, MemoryBackend, ServerState
+
+
+@pytest.mark.parametrize('make', [lambda p: MemoryBackend(), lambda p: FileBackend(str(p / 's.json'))])
+def test_update_atomic_under_contention(tmp_path, make):
+    b = make(tmp_path)
+    n_threads, n_each = 8, 25
+
+    def work():
+        for _ in range(n_each):
+            b.update_atomic('counter', lambda cur: (cur or 0) + 1)
+
+    ts = [threading.Thread(target=work) for _ in range(n_threads)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert b.get('counter') == n_threads * n_each
+    assert b.set_nx('once', 1) and not b.set_nx('once', 2) and b.get('once') == 1
+    b.set('a:1', 1)
+    b.set('a:2', 2)
+    assert sorted(b.keys('a:')) == ['a:1', 'a:2'] and b.count('a:') == 2 and b.mget(['a:1', 'zzz']) == [1, None]
+    assert b.delete('a:1') and not b.exists('a:1')
+
+
+def test_single_leader_and_handover(tmp_path):
+    backend = FileBackend(str(tmp_path / 'lease.json'))
+    replicas = [ServerState(backend, replica_id=f'r{i}') for i in range(4)]
+    now = 1000.0
+    got = [r.try_acquire_leadership(now) for r in replicas]
+    assert sum(got) == 1
+    leader = replicas[got.index(True)]
+    assert leader.try_acquire_leadership(now + 1)                      # renewing keeps it
+    assert not any(r.try_acquire_leadership(now + 1) for r in replicas if r is not leader)
+    leader.release_leadership()
+    got2 = [r.try_acquire_leadership(now + 2) for r in replicas if r is not leader]
+    assert sum(got2) == 1                                               # hand-over after release
+    # an expired lease is taken by whoever asks first
+    taker = replicas[0]
+    assert taker.try_acquire_leadership(now + 10_000)
+
+
+def test_sweep_expires_silent_sessions_and_their_resources():
+    st = ServerState(MemoryBackend(), replica_id='r0')
+    live = st.create_session('alice')
+    dead = st.create_session('bob')
+    st.register_model('m-live', 'alice', 'base', live)
+    st.register_model('m-dead', 'bob', 'base', dead)
+    st.create_sampling_session('bob', 'base', None, dead)
+    rec = st.backend.get(f'session:{dead}')
+    rec['heartbeat'] -= 10_000
+    st.backend.set(f'session:{dead}', rec)
+    removed = st.sweep(session_timeout=1800)
+    assert removed['sessions'] == [dead] and removed['models'] == ['m-dead'] and len(removed['sampling']) == 1
+    assert st.get_model('m-live') is not None and st.get_session(live) is not None
+    assert st.gauges()['sessions'] == 1
+
+
+def test_rate_limiter_and_preflight():
+    from twinkle_b200.server.config import TaskQueueConfig
+    from twinkle_b200.server.queue import PreflightError, RateLimiter, TaskQueueMixin
+    clock = [0.0]
+    rl = RateLimiter(rps=2, tps=100, window=1.0, clock=lambda: clock[0])
+    assert rl.acquire('t', 60)[0] and rl.acquire('t', 30)[0]
+    ok, why = rl.acquire('t', 1)
+    assert not ok and 'request rate' in why
+    clock[0] = 1.5                                                      # window slides
+    assert rl.acquire('t', 90)[0]
+    ok, why = rl.acquire('t', 50)
+    assert not ok and 'token rate' in why
+    assert rl.acquire('other', 50)[0]                                   # limits are per key
+
+    class App(TaskQueueMixin):
+        pass
+
+    app = App()
+    app._init_task_queue(ServerState(MemoryBackend()), TaskQueueConfig(max_input_tokens=100, rps_limit=1000, tps_limit=1e9))
+    app.preflight('tok', input_tokens=100, batch_size=4, data_world_size=4)
+    with pytest.raises(PreflightError) as e:
+        app.preflight('tok', input_tokens=101)
+    assert e.value.status_code == 413
+    with pytest.raises(PreflightError, match='smaller than the data-parallel world size'):
+        app.preflight('tok', batch_size=2, data_world_size=4)
+    with pytest.raises(PreflightError, match='multiple of'):
+        app.preflight('tok', batch_size=6, data_world_size=2, batch_size_multiple=4)
+    with pytest.raises(Exception):
+        TaskQueueConfig(rps_limit=0)
+    with pytest.raises(Exception):
+        TaskQueueConfig(no_such_field=1)
+
+
+def test_bad_payloads_do_not_break_the_next_step():
+    """The payloads of the reference's nccl-safe e2e list, fed straight into the model API with the hang guards on:
+    every call returns (zero loss instead of an exception that would leave peers waiting) and the next good step works."""
+    import os
+    from twinkle_b200.model import LoraConfig, MultiLoraTransformersModel
+    os.environ['TWINKLE_FAIL_FAST'] = '0'
+    try:
+        m = MultiLoraTransformersModel(model_id='tiny-dense', max_loras=1, max_r=8, seed=0)
+        m.add_adapter_to_model('a', LoraConfig(r=8, lora_alpha=16, target_modules='all-linear'))
+        m.set_optimizer('AdamW', lr=1e-3, adapter_name='a')
+        m.set_loss('GRPOLoss', adapter_name='a')
+        good = [{'input_ids': list(range(1, 33)), 'labels': [-100] * 16 + list(range(18, 34))} for _ in range(2)]
+        bad_calls = [
+            dict(old_logps=[[0.0] * 3, [0.0] * 3], advantages=[1.0, -1.0]),                       # wrong old_logps length
+            dict(old_logps=[[float('nan')] * 16] * 2, advantages=[1.0, -1.0]),                    # NaN log-probs
+            dict(advantages=[1e30, -1e30]),                                                       # extreme advantages
+        ]
+        for kw in bad_calls:
+            out = m.forward_backward(inputs=good, adapter_name='a', **kw)
+            assert 'loss' in out
+            m.clip_grad_and_step(adapter_name='a')
+        masked = [{'input_ids': list(range(1, 33)), 'labels': [-100] * 32} for _ in range(2)]    # all labels masked
+        m.forward_backward(inputs=masked, adapter_name='a', advantages=[1.0, -1.0])
+        m.clip_grad_and_step(adapter_name='a')
+        out = m.forward_backward(inputs=good, adapter_name='a', advantages=[1.0, -1.0])
+        norm = m.clip_grad_and_step(adapter_name='a')
+        assert torch.isfinite(torch.tensor(float(out['loss']))) and norm is not None
+        for n, p in m.model.named_parameters():
+            if 'lora' in n:
+                assert torch.isfinite(p).all(), n
+    finally:
+        os.environ.pop('TWINKLE_FAIL_FAST', None)
