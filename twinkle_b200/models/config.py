@@ -10,7 +10,7 @@ from __future__ import annotations
 import json
 import os
 from dataclasses import asdict, dataclass, field
-from typing import Any, Dict, Optional
+from typing import List, Any, Dict, Optional
 
 
 @dataclass
@@ -41,6 +41,13 @@ class DecoderConfig:
     max_position_embeddings: int = 40960
     pad_token_id: Optional[int] = None
     eos_token_id: Optional[int] = None
+    # hybrid stacks: per-layer 'full_attention' | 'linear_attention' (Gated DeltaNet); None = all full attention
+    layer_types: Optional[List[str]] = None
+    linear_num_key_heads: int = 16
+    linear_num_value_heads: int = 32
+    linear_key_head_dim: int = 128
+    linear_value_head_dim: int = 128
+    linear_conv_kernel_dim: int = 4
 
     @property
     def is_moe(self) -> bool:
@@ -133,6 +140,10 @@ PRESETS: Dict[str, Dict[str, Any]] = {
     'tiny-dense': dict(vocab_size=1024, hidden_size=256, intermediate_size=688, num_hidden_layers=2, num_attention_heads=4,
                        num_key_value_heads=2, head_dim=64, rope_theta=1e4, tie_word_embeddings=True, qk_norm=True,
                        torch_dtype='float32'),
+    'tiny-hybrid': dict(vocab_size=1024, hidden_size=256, intermediate_size=688, num_hidden_layers=4, num_attention_heads=4,
+                        num_key_value_heads=2, head_dim=64, rope_theta=1e4, tie_word_embeddings=True, qk_norm=True, torch_dtype='float32',
+                        layer_types=['linear_attention', 'full_attention', 'linear_attention', 'full_attention'], linear_num_key_heads=2,
+                        linear_num_value_heads=4, linear_key_head_dim=32, linear_value_head_dim=32),
     'tiny-moe': dict(vocab_size=1024, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
                      head_dim=64, rope_theta=1e4, tie_word_embeddings=True, num_experts=8, num_experts_per_tok=2,
                      moe_intermediate_size=128, router_aux_loss_coef=1e-3, torch_dtype='float32'),

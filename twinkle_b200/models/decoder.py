@@ -193,13 +193,24 @@ class DecoderLayer(nn.Module):
         super().__init__()
         self.layer_idx = layer_idx
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.rms_norm_offset)
-        self.self_attn = Attention(cfg, layer_idx)
+        self.is_linear = bool(cfg.layer_types) and cfg.layer_types[layer_idx] == 'linear_attention'
+        if self.is_linear:
+            from .linear_attention import GatedDeltaNet
+            self.self_attn = GatedDeltaNet(cfg.hidden_size, cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim,
+                                           cfg.linear_value_head_dim, cfg.linear_conv_kernel_dim, cfg.rms_norm_eps)
+        else:
+            self.self_attn = Attention(cfg, layer_idx)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.rms_norm_offset)
         self.mlp = MoEBlock(cfg, layer_idx) if cfg.is_moe else MLP(cfg)
         self.is_moe = cfg.is_moe
 
     def forward(self, x: torch.Tensor, cos, sin, batch: PackedBatch, kv_sink=None) -> torch.Tensor:
-        h = x + self.self_attn(self.input_layernorm(x), cos, sin, batch, kv_sink)
+        if self.is_linear:
+            if kv_sink is not None:
+                raise NotImplementedError('the paged-KV sampler does not carry Gated DeltaNet state yet')
+            h = x + self.self_attn(self.input_layernorm(x), batch.cu_seqlens)
+        else:
+            h = x + self.self_attn(self.input_layernorm(x), cos, sin, batch, kv_sink)
         n = self.post_attention_layernorm(h)
         if self.is_moe:
             forced = batch.routed_experts[self.layer_idx] if batch.routed_experts is not None else None

@@ -1,0 +1,156 @@
+"""Gated DeltaNet linear attention (the "linear_attention" layers of Qwen3.5 / Qwen3-Next style hybrids).
+
+What it covers: the reference's sequence-parallel wrapper around FLA's Triton kernels
+(``model/transformers/strategy/sequence_parallel/linear_attention_sp.py:266-308``: in-projection → short causal
+conv1d → ``chunk_gated_delta_rule`` → gated RMSNorm → out-projection, with Ulysses head scatter).  The state update
+per head is
+
+    S_t = α_t · S_{t-1} · (I − β_t k_t k_tᵀ) + β_t k_t v_tᵀ ,      o_t = S_tᵀ q_t            (S ∈ R^{dk×dv})
+
+with decay α_t = exp(g_t) ∈ (0, 1] and write strength β_t ∈ (0, 1).  Two evaluators are provided: the plain recurrence
+(exact, O(T) sequential steps) and a chunk-parallel form (WY / UT transform inside chunks of ``chunk`` tokens, one
+sequential step per chunk) that is what training uses.  Both take packed sequences through ``cu_seqlens``: state and
+convolution history are reset at every boundary.  This layer runs on PyTorch ops (no hand-written kernel yet).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .layers import Linear
+
+
+def gated_delta_rule_recurrent(q, k, v, g, beta, scale: Optional[float] = None, state=None):
+    """``q, k [T, H, dk]``, ``v [T, H, dv]``, ``g, beta [T, H]`` → (``o [T, H, dv]``, final state ``[H, dk, dv]``)."""
+    T, H, dk = q.shape
+    dv = v.shape[-1]
+    scale = dk ** -0.5 if scale is None else scale
+    S = q.new_zeros(H, dk, dv, dtype=torch.float32) if state is None else state.float().clone()
+    out = []
+    qf, kf, vf, gf, bf = q.float() * scale, k.float(), v.float(), g.float(), beta.float()
+    for t in range(T):
+        S = S * gf[t].exp()[:, None, None]
+        kv = torch.einsum('hk,hkv->hv', kf[t], S)                       # what the memory currently returns for k_t
+        S = S + torch.einsum('hk,hv->hkv', kf[t], (vf[t] - kv) * bf[t][:, None])
+        out.append(torch.einsum('hk,hkv->hv', qf[t], S))
+    return torch.stack(out).to(q.dtype), S
+
+
+def gated_delta_rule_chunked(q, k, v, g, beta, scale: Optional[float] = None, chunk: int = 64, state=None):
+    """Same contract as the recurrence, evaluated chunk-parallel."""
+    T, H, dk = q.shape
+    dv = v.shape[-1]
+    scale = dk ** -0.5 if scale is None else scale
+    pad = (-T) % chunk
+    if pad:
+        q, k, v = (F.pad(x, (0, 0, 0, 0, 0, pad)) for x in (q, k, v))
+        g, beta = F.pad(g, (0, 0, 0, pad)), F.pad(beta, (0, 0, 0, pad))
+    N = (T + pad) // chunk
+    # [H, N, C, ·]
+    qc = (q.float() * scale).view(N, chunk, H, dk).permute(2, 0, 1, 3)
+    kc = k.float().view(N, chunk, H, dk).permute(2, 0, 1, 3)
+    vc = v.float().view(N, chunk, H, dv).permute(2, 0, 1, 3)
+    bc = beta.float().view(N, chunk, H).permute(2, 0, 1)
+    gc = g.float().view(N, chunk, H).permute(2, 0, 1).cumsum(-1)       # log decay from the chunk start (inclusive)
+    kb, vb = kc * bc[..., None], vc * bc[..., None]
+    tri = torch.ones(chunk, chunk, dtype=torch.bool, device=q.device)
+    strict_lower, lower = tri.tril(-1), tri.tril()
+    rel = (gc[..., :, None] - gc[..., None, :]).masked_fill(~lower, float('-inf')).exp()    # decay from token j to token i ≥ j
+    # (I + A)^{-1} with A = strictly-lower(β_i k_i·k_j · decay): forward substitution, row by row
+    A = -(kb @ kc.transpose(-1, -2) * rel).masked_fill(~strict_lower, 0.0)
+    rows = [A[..., 0, :]]
+    for i in range(1, chunk):                                            # out of place: the loop stays differentiable
+        a = A[..., i, :]
+        rows.append(a + (a[..., :i, None] * torch.stack(rows, -2)).sum(-2))
+    A = torch.stack(rows, -2) + torch.eye(chunk, device=q.device)
+    u = A @ vb                                                          # values corrected for intra-chunk interactions
+    w = A @ (kb * gc.exp()[..., None])                                   # what must be subtracted per unit of incoming state
+    S = q.new_zeros(H, dk, dv, dtype=torch.float32) if state is None else state.float().clone()
+    outs = []
+    for n in range(N):
+        qn, kn, gn = qc[:, n], kc[:, n], gc[:, n]
+        v_new = u[:, n] - w[:, n] @ S
+        attn = (qn @ kn.transpose(-1, -2) * rel[:, n]).masked_fill(~lower, 0.0)
+        outs.append((qn * gn.exp()[..., None]) @ S + attn @ v_new)
+        last = gn[:, -1]
+        S = S * last.exp()[:, None, None] + (kn * (last[:, None] - gn).exp()[..., None]).transpose(-1, -2) @ v_new
+    o = torch.stack(outs, 1).permute(1, 2, 0, 3).reshape(N * chunk, H, dv)[:T]
+    return o.to(q.dtype), S
+
+
+def gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, scale: Optional[float] = None, chunk: int = 64, recurrent: bool = False):
+    """Packed sequences: every segment starts from an empty state."""
+    fn = gated_delta_rule_recurrent if recurrent else (lambda *a, **kw: gated_delta_rule_chunked(*a, chunk=chunk, **kw))
+    bounds = cu_seqlens.tolist()
+    outs = [fn(q[a:b], k[a:b], v[a:b], g[a:b], beta[a:b], scale)[0] for a, b in zip(bounds[:-1], bounds[1:]) if b > a]
+    return torch.cat(outs, 0) if outs else q.new_zeros(0, q.shape[1], v.shape[-1])
+
+
+def causal_conv1d_varlen(x: torch.Tensor, weight: torch.Tensor, cu_seqlens: torch.Tensor, activation: bool = True) -> torch.Tensor:
+    """Depth-wise causal convolution over packed tokens: ``x [T, C]``, ``weight [C, W]``; no leakage across segments."""
+    T, C = x.shape
+    W = weight.shape[1]
+    bounds = cu_seqlens.tolist()
+    outs = []
+    for a, b in zip(bounds[:-1], bounds[1:]):
+        if b <= a:
+            continue
+        seg = F.pad(x[a:b].t().unsqueeze(0), (W - 1, 0))                # [1, C, L + W − 1]
+        outs.append(F.conv1d(seg, weight.unsqueeze(1).to(x.dtype), groups=C)[0].t())
+    y = torch.cat(outs, 0) if outs else x.new_zeros(0, C)
+    return F.silu(y) if activation else y
+
+
+class GatedDeltaNet(nn.Module):
+    """Drop-in replacement of the softmax-attention block for ``linear_attention`` layers."""
+
+    def __init__(self, hidden_size: int, num_k_heads: int, num_v_heads: int, head_k_dim: int, head_v_dim: int, conv_kernel: int = 4,
+                 eps: float = 1e-6, chunk: int = 64):
+        super().__init__()
+        assert num_v_heads % num_k_heads == 0
+        self.hk, self.hv, self.dk, self.dv, self.chunk, self.eps = num_k_heads, num_v_heads, head_k_dim, head_v_dim, chunk, eps
+        kd, vd = num_k_heads * head_k_dim, num_v_heads * head_v_dim
+        self.in_proj_qkvz = Linear(hidden_size, 2 * kd + 2 * vd, name='in_proj_qkvz')
+        self.in_proj_ba = Linear(hidden_size, 2 * num_v_heads, name='in_proj_ba')
+        self.conv_weight = nn.Parameter(torch.empty(2 * kd + vd, conv_kernel))
+        self.dt_bias = nn.Parameter(torch.ones(num_v_heads))
+        self.A_log = nn.Parameter(torch.zeros(num_v_heads))
+        self.norm_weight = nn.Parameter(torch.ones(head_v_dim))
+        self.out_proj = Linear(vd, hidden_size, name='out_proj')
+        self.attn_parallel = None  # Ulysses strategy: heads are scattered exactly like softmax attention heads
+        nn.init.kaiming_uniform_(self.conv_weight, a=math.sqrt(5))
+
+    def forward(self, x: torch.Tensor, cu_seqlens: torch.Tensor) -> torch.Tensor:
+        T = x.shape[0]
+        kd, vd = self.hk * self.dk, self.hv * self.dv
+        qkvz = self.in_proj_qkvz(x)
+        qkv, z = qkvz[:, :2 * kd + vd], qkvz[:, 2 * kd + vd:]
+        b, a = self.in_proj_ba(x).chunk(2, -1)
+        beta = torch.sigmoid(b.float())
+        g = -self.A_log.float().exp() * F.softplus(a.float() + self.dt_bias.float())      # log decay ≤ 0
+        ap = self.attn_parallel
+        if ap is None:
+            qkv = causal_conv1d_varlen(qkv, self.conv_weight, cu_seqlens)
+        q, k, v = qkv[:, :kd].view(T, self.hk, self.dk), qkv[:, kd:2 * kd].view(T, self.hk, self.dk), qkv[:, 2 * kd:].view(T, self.hv, self.dv)
+        rep = self.hv // self.hk
+        if ap is not None:
+            # sequence → head exchange first (every rank then owns whole sequences for a slice of the heads), then the
+            # convolution with this rank's slice of the depth-wise filters; the exchange is the same one attention uses
+            q, k, v = ap.scatter_heads(q.contiguous(), k.contiguous(), v.contiguous())
+            beta, g = ap.scatter_scalar_heads(beta), ap.scatter_scalar_heads(g)
+            q, k, v = ap.conv_after_scatter(q, k, v, self.conv_weight, cu_seqlens, self.hk, self.hv, self.dk, self.dv)
+        q, k = F.normalize(q.float(), dim=-1).to(x.dtype), F.normalize(k.float(), dim=-1).to(x.dtype)
+        if rep > 1:
+            q, k = q.repeat_interleave(rep, 1), k.repeat_interleave(rep, 1)
+        o = gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, chunk=self.chunk)
+        if ap is not None:
+            o = ap.gather_heads(o.contiguous())
+        # gated RMSNorm per head, gate z
+        of = o.float()
+        of = of * torch.rsqrt(of.pow(2).mean(-1, keepdim=True) + self.eps) * self.norm_weight.float()
+        of = of * F.silu(z.float().view(T, self.hv, self.dv))
+        return self.out_proj(of.to(x.dtype).reshape(T, vd))

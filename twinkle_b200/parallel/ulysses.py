@@ -98,7 +98,7 @@ def _symm_out(comm, shape, dtype, tag):
 def _seq_to_head(x: torch.Tensor, comm: Communicator) -> torch.Tensor:
     sp = comm.world_size
     t, h, d = x.shape
-    if hasattr(comm, 'ulysses_exchange') and x.is_cuda:
+    if hasattr(comm, 'ulysses_exchange') and x.is_cuda and (d * x.element_size()) % 16 == 0 and x.dtype == torch.bfloat16:
         out = _symm_out(comm, (sp * t, h // sp, d), x.dtype, 's2h')
         comm.ulysses_exchange(x.contiguous(), out, True, h)
         return out.clone()
@@ -113,7 +113,7 @@ def _head_to_seq(x: torch.Tensor, comm: Communicator) -> torch.Tensor:
     sp = comm.world_size
     tt, hl, d = x.shape
     t = tt // sp
-    if hasattr(comm, 'ulysses_exchange') and x.is_cuda:
+    if hasattr(comm, 'ulysses_exchange') and x.is_cuda and (d * x.element_size()) % 16 == 0 and x.dtype == torch.bfloat16:
         out = _symm_out(comm, (t, sp * hl, d), x.dtype, 'h2s')
         comm.ulysses_exchange(x.contiguous(), out, False, sp * hl)
         return out.clone()
@@ -145,6 +145,27 @@ class UlyssesAttention:
 
     def gather_heads(self, o):
         return _HeadGather.apply(o.contiguous(), self.comm)
+
+    # ---- linear attention (Gated DeltaNet): per-head scalars and the depth-wise convolution follow the heads
+    def scatter_scalar_heads(self, x):
+        """``[T_local, H]`` → ``[T_full, H/sp]``."""
+        return _HeadScatter.apply(x.unsqueeze(-1).contiguous(), self.comm).squeeze(-1)
+
+    def conv_after_scatter(self, q, k, v, conv_weight, cu_seqlens, hk, hv, dk, dv):
+        """Causal conv1d on whole sequences with this rank's slice of the depth-wise filters (channels are laid out
+        ``[q heads | k heads | v heads]``; the rank owns heads ``[r·H/sp, (r+1)·H/sp)`` of each block)."""
+        from ..models.linear_attention import causal_conv1d_varlen
+        sp, r = self.sp, self.comm.rank
+        hkl, hvl = hk // sp, hv // sp
+        kd = hk * dk
+        wq = conv_weight[r * hkl * dk:(r + 1) * hkl * dk]
+        wk = conv_weight[kd + r * hkl * dk:kd + (r + 1) * hkl * dk]
+        wv = conv_weight[2 * kd + r * hvl * dv:2 * kd + (r + 1) * hvl * dv]
+        T = q.shape[0]
+        x = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], -1)
+        y = causal_conv1d_varlen(x, torch.cat([wq, wk, wv], 0), cu_seqlens)
+        a, b = hkl * dk, 2 * hkl * dk
+        return y[:, :a].reshape(T, hkl, dk), y[:, a:b].reshape(T, hkl, dk), y[:, b:].reshape(T, hvl, dv)
 
 
 class _GatherTokens(torch.autograd.Function):
@@ -182,5 +203,12 @@ def apply_ulysses(model, mesh, cfg, backend: str = 'auto') -> None:
             if backend == 'symm':
                 raise
     strat = UlyssesAttention(comm, cfg.num_key_value_heads)
+    linear = None
     for layer in model.layers:
-        layer.self_attn.attn_parallel = strat
+        if getattr(layer, 'is_linear', False):
+            if linear is None:
+                assert cfg.linear_num_key_heads % comm.world_size == 0, 'linear-attention key heads must divide over the Ulysses group'
+                linear = UlyssesAttention(comm, cfg.linear_num_key_heads)
+            layer.self_attn.attn_parallel = linear
+        else:
+            layer.self_attn.attn_parallel = strat
