@@ -12,6 +12,7 @@ paged cache; decode runs one token per live sequence through ``ops.paged_attenti
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, field
 from typing import Any, Callable, Dict, Iterator, List, Optional, Sequence, Tuple
 
@@ -98,6 +99,8 @@ class NativeEngine:
         self.max_batch = max_batch
         self.decode_text = decode
         self.capture_routing = False
+        self.use_cuda_graphs = bool(int(os.environ.get('TWINKLE_SAMPLER_CUDA_GRAPHS', '1')))
+        self._graphs: Dict[Tuple[int, int], Dict[str, Any]] = {}
 
     # --------------------------------------------------------------- LoRA
     def _lora_for(self, seqs: Sequence[_Seq], lens: Sequence[int]) -> Optional[LoraBatch]:
@@ -138,21 +141,14 @@ class NativeEngine:
         return hidden
 
     # --------------------------------------------------------------- decode
-    @torch.no_grad()
-    def decode_step(self, seqs: List[_Seq], last_tokens: torch.Tensor) -> torch.Tensor:
-        """One token for every sequence; returns logits ``[B, V]`` (fp32)."""
-        cfg, B = self.cfg, len(seqs)
-        positions = torch.tensor([s.length - 1 for s in seqs], device=self.device)
+    def _decode_body(self, tokens, positions, table, seq_lens, lora: Optional[LoraBatch]) -> torch.Tensor:
+        """One decode token per row from device tensors only (what a CUDA graph captures)."""
+        cfg, B = self.cfg, tokens.shape[0]
         cos, sin = ops.rope_tables(positions, cfg.head_dim, cfg.rope_theta)
-        max_blocks = max(len(s.blocks) for s in seqs)
-        table = torch.zeros(B, max_blocks, dtype=torch.int32, device=self.device)
-        for i, s in enumerate(seqs):
-            table[i, :len(s.blocks)] = torch.tensor(s.blocks, dtype=torch.int32)
-        seq_lens = torch.tensor([s.length for s in seqs], dtype=torch.int32, device=self.device)
-        x = self.model.embed_tokens(last_tokens)
-        blk = table[torch.arange(B, device=self.device), (positions // self.cache.block_size)].long()
+        x = self.model.embed_tokens(tokens)
+        blk = table.gather(1, (positions // self.cache.block_size).unsqueeze(1)).squeeze(1).long()
         off = positions % self.cache.block_size
-        with lora_batch(self._lora_for(seqs, [1] * B)):
+        with lora_batch(lora):
             for li, layer in enumerate(self.model.layers):
                 at = layer.self_attn
                 h = layer.input_layernorm(x)
@@ -168,6 +164,71 @@ class NativeEngine:
                 x = x + (layer.mlp(n) if not layer.is_moe else layer.mlp(n, None))
             x = self.model.norm(x)
         return self.model.logits(x).float()
+
+    def _graph_for(self, B: int, max_blocks: int):
+        """A captured decode step for batch bucket ``B`` and block-table width ``max_blocks`` (both powers of two).
+        Inputs live in static tensors that ``decode_step`` fills before every replay; rows beyond the live batch have
+        length 0 and write their K/V into block 0, which no sequence owns."""
+        key = (B, max_blocks)
+        ent = self._graphs.get(key)
+        if ent is not None:
+            return ent
+        dev = self.device
+        st = {'tokens': torch.zeros(B, dtype=torch.long, device=dev), 'positions': torch.zeros(B, dtype=torch.long, device=dev),
+              'table': torch.zeros(B, max_blocks, dtype=torch.int32, device=dev), 'seq_lens': torch.zeros(B, dtype=torch.int32, device=dev)}
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):  # warm-up outside the capture: one-time kernel attribute set-up, allocator warm-up
+            for _ in range(2):
+                self._decode_body(st['tokens'], st['positions'], st['table'], st['seq_lens'], None)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            st['logits'] = self._decode_body(st['tokens'], st['positions'], st['table'], st['seq_lens'], None)
+        st['graph'] = graph
+        self._graphs[key] = st
+        return st
+
+    @torch.no_grad()
+    def decode_step(self, seqs: List[_Seq], last_tokens: torch.Tensor) -> torch.Tensor:
+        """One token for every sequence; returns logits ``[B, V]`` (fp32).  On a GPU the per-token work of a whole
+        layer stack is a few dozen short kernels, so the step is replayed from a CUDA graph (one per batch-size
+        bucket) unless adapters or routing capture need the eager path."""
+        B = len(seqs)
+        positions = torch.tensor([s.length - 1 for s in seqs], device=self.device)
+        max_blocks = max(len(s.blocks) for s in seqs)
+        lora = self._lora_for(seqs, [1] * B)
+        use_graph = (self.use_cuda_graphs and self.device.type == 'cuda' and lora is None and not self.capture_routing and not self.cfg.is_moe
+                     and not any(getattr(l, 'is_linear', False) for l in self.model.layers))
+        if use_graph:
+            Bb = 1 << max(B - 1, 0).bit_length()
+            Mb = 1 << max(max_blocks - 1, 0).bit_length()
+            try:
+                st = self._graph_for(Bb, Mb)
+            except Exception as e:  # capture is an optimisation: the eager path below is always valid
+                self.use_cuda_graphs = False
+                import logging
+                logging.getLogger('twinkle_b200').warning(f'CUDA-graph capture of the decode step failed ({type(e).__name__}: {e}); running eagerly')
+                st = None
+            if st is not None:
+                table = torch.zeros(Bb, Mb, dtype=torch.int32)
+                for i, s in enumerate(seqs):
+                    table[i, :len(s.blocks)] = torch.tensor(s.blocks, dtype=torch.int32)
+                lens = torch.zeros(Bb, dtype=torch.int32)
+                lens[:B] = torch.tensor([s.length for s in seqs], dtype=torch.int32)
+                st['table'].copy_(table, non_blocking=True)
+                st['seq_lens'].copy_(lens, non_blocking=True)
+                st['tokens'].zero_()
+                st['tokens'][:B].copy_(last_tokens)
+                st['positions'].zero_()
+                st['positions'][:B].copy_(positions)
+                st['graph'].replay()
+                return st['logits'][:B]
+        table = torch.zeros(B, max_blocks, dtype=torch.int32, device=self.device)
+        for i, s in enumerate(seqs):
+            table[i, :len(s.blocks)] = torch.tensor(s.blocks, dtype=torch.int32)
+        seq_lens = torch.tensor([s.length for s in seqs], dtype=torch.int32, device=self.device)
+        return self._decode_body(last_tokens, positions, table, seq_lens, lora)
 
     # ------------------------------------------------------------- sampling
     def _sample(self, seqs: List[_Seq], logits: torch.Tensor) -> Tuple[List[int], List[float], List[Optional[List[Tuple[int, float]]]]]:
