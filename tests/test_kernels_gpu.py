@@ -265,3 +265,20 @@ def test_flash_attention_separate_key_ranges(E):
     orf.backward(g.float())
     assert rel(o, orf) < 6e-3
     assert rel(q.grad, qr.grad) < 1.5e-2 and rel(k.grad, kr.grad) < 1.5e-2 and rel(v.grad, vr.grad) < 1.5e-2
+
+
+@pytest.mark.parametrize('layout', ['nt', 'nn', 'tn'])
+def test_gemm_sm_pair_staged_epilogue(E, layout):
+    """bf16 outputs written through the shared-memory staged epilogue equal the direct-store epilogue bit for bit."""
+    M, N, K = 4000, 2504, 520
+    torch.manual_seed(1)
+    shapes = {'nt': ((M, K), (N, K)), 'nn': ((M, K), (K, N)), 'tn': ((K, M), (K, N))}[layout]
+    a, b = (torch.randn(s, device='cuda').bfloat16() for s in shapes)
+    direct = E.gemm(a, b, layout)
+    E.set_gemm_staged(1)
+    try:
+        staged = E.gemm(a, b, layout)
+        torch.cuda.synchronize()
+    finally:
+        E.set_gemm_staged(0)
+    assert torch.equal(direct, staged)

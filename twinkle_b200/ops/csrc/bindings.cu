@@ -41,6 +41,7 @@ torch::Tensor paged_attn_decode(const torch::Tensor&, const torch::Tensor&, cons
 std::vector<torch::Tensor> sample_tokens(const torch::Tensor&, double, int64_t, double, const torch::Tensor&);
 std::vector<torch::Tensor> moe_router(const torch::Tensor&, int64_t, bool);
 void set_gemm_pair(int64_t);
+void set_gemm_staged(int64_t);
 void gemm_rs(const torch::Tensor&, const torch::Tensor&, const std::string&, const std::vector<int64_t>&, int64_t);
 std::vector<torch::Tensor> gemm_ag(const std::vector<int64_t>&, int64_t, const torch::Tensor&, const std::string&, int64_t, const torch::Tensor&, int64_t, int64_t);
 torch::Tensor tp_stage_reduce(const torch::Tensor&);
@@ -85,6 +86,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sample_tokens", &tk::sample_tokens);
   m.def("moe_router", &tk::moe_router);
   m.def("set_gemm_pair", &tk::set_gemm_pair);
+  m.def("set_gemm_staged", &tk::set_gemm_staged);
   m.def("gemm_rs", &tk::gemm_rs);
   m.def("gemm_ag", &tk::gemm_ag);
   m.def("tp_stage_reduce", &tk::tp_stage_reduce);

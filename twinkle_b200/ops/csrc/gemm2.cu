@@ -39,7 +39,7 @@ constexpr int THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 constexpr int GROUP_M = 8;
 
-constexpr int FUSE_NONE = 0, FUSE_RS = 1, FUSE_AG = 2;
+constexpr int FUSE_NONE = 0, FUSE_RS = 1, FUSE_AG = 2, FUSE_STAGED = 3;  // STAGED: plain GEMM, bf16 output written through the staged epilogue
 constexpr int MAX_TP = 8;
 
 struct Params {
@@ -131,7 +131,7 @@ __device__ __forceinline__ bool tile_coord(const Params& p, int tile, int& m0, i
   const int gsize = min(num_m - first_m, GROUP_M);
   const int r = tile - g * per_group;
   int mt = first_m + r % gsize;
-  if constexpr (FUSE != FUSE_NONE) {
+  if constexpr (FUSE == FUSE_RS || FUSE == FUSE_AG) {
     // walk the row chunks in ring order: FUSE_RS sends remote chunks first and keeps its own for last,
     // FUSE_AG starts on its own chunk while the copiers fetch the others in the same order
     const int tiles_per_chunk = p.rows_per_rank / TM;
@@ -157,7 +157,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
 
   // the reduce-scatter variant gives its sixth stage to the epilogue as a staging area for coalesced peer stores
-  constexpr int NST = (FUSE == FUSE_RS) ? STAGES - 1 : STAGES;
+  constexpr int NST = (FUSE == FUSE_RS || FUSE == FUSE_STAGED) ? STAGES - 1 : STAGES;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta = cluster_ctarank();  // 0 = leader of the pair
   const int first_gemm = (FUSE == FUSE_AG) ? p.copy_ctas : 0;
@@ -339,9 +339,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         out_base = p.peer[c];
         out_row = static_cast<size_t>(p.rank) * p.rows_per_rank + (row - c * p.rows_per_rank);
       }
-      if constexpr (FUSE == FUSE_RS) {
+      if constexpr (FUSE == FUSE_RS || FUSE == FUSE_STAGED) {
         // Stage 32 rows x 128 columns (bf16) per warp in shared memory, then let every half-warp store one whole
-        // 256-byte row segment: NVLink sees long contiguous writes instead of 64-byte pieces of 32 different rows.
+        // 256-byte row segment: NVLink (and the local memory system) sees long contiguous writes instead of 64-byte
+        // pieces of 32 different rows.
         uint8_t* stg = smem + (STAGES - 1) * STAGE_BYTES + q * 8192;
         const int row0 = m0 + static_cast<int>(cta) * HALF_M + q * 32;
 #pragma unroll 1
@@ -368,9 +369,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             const int grow = row0 + lr;
             const uint4 v = *reinterpret_cast<const uint4*>(stg + lr * 256 + ((j ^ (lr & 15)) * 16));
             if (grow < p.M && col + 8 <= p.N) {
-              const int c = min(grow / p.rows_per_rank, p.tp - 1);
-              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.peer[c]) +
-                                 (static_cast<size_t>(p.rank) * p.rows_per_rank + (grow - c * p.rows_per_rank)) * p.ldo + col;
+              __nv_bfloat16* o;
+              if constexpr (FUSE == FUSE_RS) {
+                const int c = min(grow / p.rows_per_rank, p.tp - 1);
+                o = reinterpret_cast<__nv_bfloat16*>(p.peer[c]) +
+                    (static_cast<size_t>(p.rank) * p.rows_per_rank + (grow - c * p.rows_per_rank)) * p.ldo + col;
+              } else {
+                o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(grow) * p.ldo + col;
+              }
               *reinterpret_cast<uint4*>(o) = v;
             }
           }
@@ -461,6 +467,13 @@ static int max_pairs(Kern kern) {
   return n;
 }
 
+// 1: bf16 outputs go through the shared-memory staged epilogue (5 operand stages); 0: direct stores (6 stages).
+static int g_staged_epilogue = [] {
+  const char* e = getenv("TK_GEMM_STAGED");
+  return e ? atoi(e) : 0;
+}();
+void set_gemm_staged(int64_t v) { g_staged_epilogue = static_cast<int>(v); }
+
 // Dense GEMM on SM pairs; same contract as the single-CTA path.  Returns false when the shape is not eligible
 // (the caller then uses the single-CTA kernel).
 bool gemm_pair_launch(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb, void* out, int M, int N, int K, int ldo,
@@ -480,10 +493,31 @@ bool gemm_pair_launch(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtenso
     const int grid = 2 * std::min(tiles, std::min(pairs, num_sms() / 2));                                              \
     kern<<<grid, g2::THREADS, g2::SMEM_BYTES, stream>>>(ta, tb, ta, p);                                                \
   } while (0)
-  if (!a_mn && !b_mn) TK_LAUNCH2(false, false);
-  else if (!a_mn && b_mn) TK_LAUNCH2(false, true);
-  else if (a_mn && b_mn) TK_LAUNCH2(true, true);
-  else return false;
+#define TK_LAUNCH2S(AM, BMN)                                                                                           \
+  do {                                                                                                                 \
+    static int pairs = -1;                                                                                             \
+    auto kern = g2::gemm_tcgen05_pair_kernel<AM, BMN, g2::FUSE_STAGED>;                                                \
+    if (pairs < 0) {                                                                                                   \
+      TK_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, g2::SMEM_BYTES));          \
+      pairs = max_pairs(kern);                                                                                         \
+    }                                                                                                                  \
+    if (pairs <= 0) return false;                                                                                      \
+    const int grid = 2 * std::min(tiles, std::min(pairs, num_sms() / 2));                                              \
+    kern<<<grid, g2::THREADS, g2::SMEM_BYTES, stream>>>(ta, tb, ta, p);                                                \
+  } while (0)
+  const bool staged = g_staged_epilogue && !out_fp32 && !accumulate && N % 8 == 0;
+  if (staged) {
+    if (!a_mn && !b_mn) TK_LAUNCH2S(false, false);
+    else if (!a_mn && b_mn) TK_LAUNCH2S(false, true);
+    else if (a_mn && b_mn) TK_LAUNCH2S(true, true);
+    else return false;
+  } else {
+    if (!a_mn && !b_mn) TK_LAUNCH2(false, false);
+    else if (!a_mn && b_mn) TK_LAUNCH2(false, true);
+    else if (a_mn && b_mn) TK_LAUNCH2(true, true);
+    else return false;
+  }
+#undef TK_LAUNCH2S
 #undef TK_LAUNCH2
   count_launch();
   TK_CUDA_CHECK(cudaGetLastError());

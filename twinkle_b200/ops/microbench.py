@@ -148,9 +148,13 @@ def main() -> None:
     ap.add_argument('--iters', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--no-flush', action='store_true')
+    ap.add_argument('--staged', type=int, default=None, help='1: staged epilogue of the SM-pair GEMM (bf16 outputs)')
     ap.add_argument('--pair', type=int, default=None, help='1: SM-pair GEMM kernel, 0: single-CTA tiles (default: library setting)')
     a = ap.parse_args()
     torch.manual_seed(0)
+    if a.staged is not None:
+        from twinkle_b200 import ops as _ops2
+        _ops2.ext().set_gemm_staged(a.staged)
     if a.pair is not None:
         from twinkle_b200 import ops as _ops
         _ops.ext().set_gemm_pair(a.pair)
