@@ -274,11 +274,11 @@ def test_gemm_sm_pair_staged_epilogue(E, layout):
     torch.manual_seed(1)
     shapes = {'nt': ((M, K), (N, K)), 'nn': ((M, K), (K, N)), 'tn': ((K, M), (K, N))}[layout]
     a, b = (torch.randn(s, device='cuda').bfloat16() for s in shapes)
-    direct = E.gemm(a, b, layout)
-    E.set_gemm_staged(1)
+    staged = E.gemm(a, b, layout)          # default
+    E.set_gemm_staged(0)
     try:
-        staged = E.gemm(a, b, layout)
+        direct = E.gemm(a, b, layout)
         torch.cuda.synchronize()
     finally:
-        E.set_gemm_staged(0)
+        E.set_gemm_staged(1)
     assert torch.equal(direct, staged)

@@ -470,7 +470,7 @@ static int max_pairs(Kern kern) {
 // 1: bf16 outputs go through the shared-memory staged epilogue (5 operand stages); 0: direct stores (6 stages).
 static int g_staged_epilogue = [] {
   const char* e = getenv("TK_GEMM_STAGED");
-  return e ? atoi(e) : 0;
+  return e ? atoi(e) : 1;
 }();
 void set_gemm_staged(int64_t v) { g_staged_epilogue = static_cast<int>(v); }
 
