@@ -1,0 +1,103 @@
+"""Small utilities: truncation strategies, quantised-checkpoint dequantisers, streaming safetensors writer / lazy
+reader, single-winner notification claim, rewards, model-hub alias handling."""
+import json
+import os
+import uuid
+
+import pytest
+import torch
+
+
+def test_template_truncation_strategies():
+    from twinkle_b200.template import Template
+    msgs = {'messages': [{'role': 'user', 'content': 'x' * 60}, {'role': 'assistant', 'content': 'y' * 60}]}
+    full = Template(model_id=None, max_length=None).encode(msgs)
+    n = len(full['input_ids'])
+    assert n > 40
+    with pytest.raises(ValueError):
+        Template(model_id=None, max_length=32, truncation_strategy='raise').encode(msgs)
+    left = Template(model_id=None, max_length=32, truncation_strategy='left').encode(msgs)
+    right = Template(model_id=None, max_length=32, truncation_strategy='right').encode(msgs)
+    assert len(left['input_ids']) == 32 and len(right['input_ids']) == 32
+    assert left['input_ids'] == full['input_ids'][-32:] or left['input_ids'][-5:] == full['input_ids'][-5:]
+    assert right['input_ids'][:5] == full['input_ids'][:5]
+    parts = Template(model_id=None, max_length=32, truncation_strategy='split').encode(msgs)
+    assert isinstance(parts, list) and sum(len(p['input_ids']) for p in parts) == n
+    gone = Template(model_id=None, max_length=32, truncation_strategy='delete').batch_encode([msgs])
+    assert gone == []
+
+
+def test_dequantizers():
+    from twinkle_b200.utils.dequantizer import Dequantizer, dequant_fp8_block, dequant_mxfp4
+    w = torch.randn(200, 300)
+    scale = torch.rand(2, 3) + 0.5                                   # one scale per 128×128 block
+    q = (w / scale.repeat_interleave(128, 0)[:200].repeat_interleave(128, 1)[:, :300]).to(torch.float8_e4m3fn)
+    back = dequant_fp8_block(q, scale, dtype=torch.float32)
+    assert back.shape == w.shape and float((back - w).abs().max()) < 0.2 * float(w.abs().max())
+    got = Dequantizer.maybe_dequantize('layer.weight', q, lambda n: scale if n == 'layer.weight_scale_inv' else None)
+    assert got.dtype == torch.bfloat16 and torch.allclose(got.float(), back, atol=0.05, rtol=0.05)
+    assert Dequantizer.maybe_dequantize('x', w, lambda n: None) is w
+    # mxfp4: nibble 2 = 1.0, nibble 10 = -1.0 (sign bit set); scale byte 128 → ×2
+    blocks = torch.full((1, 16), (10 << 4) | 2, dtype=torch.uint8)
+    vals = dequant_mxfp4(blocks, torch.tensor([128], dtype=torch.uint8), dtype=torch.float32)
+    assert vals.shape == (32, ) and vals[0] == 2.0 and vals[1] == -2.0
+
+
+def test_streaming_safetensors_roundtrip(tmp_path):
+    from twinkle_b200.utils.safetensors_io import SafetensorLazyLoader, StreamingSafetensorSaver
+    saver = StreamingSafetensorSaver(str(tmp_path), max_shard_bytes=4096)   # tiny shards → several files + an index
+    tensors = {f'layer.{i}.weight': torch.randn(32, 16) for i in range(6)}
+    saver.add_many(tensors.items())
+    files = saver.finalize()
+    assert len(files) > 1 and os.path.isfile(os.path.join(str(tmp_path), 'model.safetensors.index.json'))
+    idx = json.load(open(os.path.join(str(tmp_path), 'model.safetensors.index.json')))
+    assert set(idx['weight_map']) == set(tensors)
+    loader = SafetensorLazyLoader(str(tmp_path))
+    assert sorted(loader.keys()) == sorted(tensors) and 'layer.3.weight' in loader
+    assert all(torch.equal(loader.get(k), v) for k, v in tensors.items())
+    assert torch.equal(loader.get_slice('layer.2.weight')[4:8], tensors['layer.2.weight'][4:8])
+    loader.close()
+    peft = StreamingSafetensorSaver(str(tmp_path / 'ad'), peft=True)
+    peft.add('base_model.model.x.lora_A.weight', torch.zeros(2, 2))
+    assert [os.path.basename(f) for f in peft.finalize()] == ['adapter_model.safetensors']
+
+
+def test_claim_once_and_notifier(monkeypatch):
+    from twinkle_b200.notifier import Notifier
+    from twinkle_b200.utils.parallel import claim_once
+    key = f'test-{uuid.uuid4().hex}'
+    assert claim_once(key, ttl=60) is True and claim_once(key, ttl=60) is False   # one winner per key and window
+    sent = []
+
+    class Capture(Notifier):
+        def _send(self, text):
+            sent.append(text)
+
+    n = Capture(dedup_ttl=60)
+    msg = f'boom {uuid.uuid4().hex}'
+    assert n.notify(msg) and not n.notify(msg) and sent == [msg]                   # the same report goes out once
+    n.to_env()
+    back = Notifier.from_env()
+    assert back is not None and type(back).__name__ in ('Capture', 'Notifier')
+
+
+def test_rewards():
+    from twinkle_b200.reward import CountdownReward, FormatReward, GSM8KAccuracyReward, MathReward, extract_boxed
+    t = lambda text: {'messages': [{'role': 'user', 'content': 'q'}, {'role': 'assistant', 'content': text}]}
+    assert GSM8KAccuracyReward()([t('so 6*7 #### 42'), t('#### 41'), t('the answer is 1,000')], ['42', '42', '1000']) == [1.0, 0.0, 1.0]
+    assert extract_boxed(r'thus \\boxed{\\frac{1}{2}} done') == r'\\frac{1}{2}'
+    assert MathReward()([t(r'\\boxed{3.50}'), t(r'\\boxed{4}')], ['3.5', '5']) == [1.0, 0.0]
+    fmt = FormatReward()([t('<think>a</think><answer>b</answer>'), t('no tags')])
+    assert fmt[0] > fmt[1]
+    cd = CountdownReward()([t('<answer>(3+4)*2</answer>'), t('<answer>3+4+2</answer>')], [{'target': 14, 'nums': [3, 4, 2]}] * 2)
+    assert cd == [1.0, 0.0] or cd[0] > cd[1]
+
+
+def test_hub_local_paths_and_aliases(tmp_path):
+    from twinkle_b200.hub import HubOperation
+    d = tmp_path / 'model'
+    d.mkdir()
+    (d / 'config.json').write_text('{}')
+    assert HubOperation.download_model(str(d)) == str(d)                          # local directories pass through
+    with pytest.raises(Exception):
+        HubOperation.download_model('ms://definitely/not-cached-anywhere')        # offline: no silent network access
