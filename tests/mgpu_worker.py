@@ -173,6 +173,64 @@ def megatron_checks(rank, world, dev, report):
         report(f'megatron_tp{tp}_pp{pp}_vpp{vpp}_matches_single', diff < 5e-2, single=single, multi=c)
 
 
+def ulysses_fused_checks(rank, world, dev, report):
+    """q|k|v projection with the sequence → head exchange in its epilogue: the kernel against GEMM + all-to-all, then
+    Ulysses training with the fused projection against the same run with the separate exchange kernels."""
+    from twinkle_b200 import ops
+    from twinkle_b200.parallel import ulysses as U
+    from twinkle_b200.parallel.comm import Communicator
+    from twinkle_b200.parallel.symm import SymmCommunicator
+    sc = SymmCommunicator(None, dev)
+    plain = Communicator(None, dev)
+    t, K, hq, hkv, d = 384, 512, 4 * world, 2 * world, 128  # 384 rows: one full 256-row tile and a partial one
+    g = torch.Generator(device='cpu').manual_seed(3)
+    w = (torch.randn((hq + 2 * hkv) * d, K, generator=g) / K ** 0.5).to(dev).bfloat16()
+    x = torch.randn(t, K, generator=torch.Generator(device='cpu').manual_seed(10 + rank)).to(dev).bfloat16()
+    n_local = (hq + 2 * hkv) * d // world
+    for it in range(3):  # both buffers of the pair are used and reused
+        out = U._symm_out(sc, (world * t, n_local), torch.bfloat16, 'qkv_test')
+        sc.head_scatter_gemm(x, w, out, t, hq * d // 128, hkv * d // 128)
+        y = ops.gemm(x, w, 'nt')
+        secs = [y[:, :hq * d].reshape(t, hq, d), y[:, hq * d:(hq + hkv) * d].reshape(t, hkv, d), y[:, (hq + hkv) * d:].reshape(t, hkv, d)]
+        want = torch.cat([U._seq_to_head(s_.contiguous(), plain).reshape(world * t, -1) for s_ in secs], dim=-1)
+        torch.cuda.synchronize()
+        report(f'head_scatter_gemm_{it}', bool(torch.equal(out, want)), max_err=float((out.float() - want.float()).abs().max()))
+        x = x + 1
+    # training parity
+    from twinkle_b200.model import TransformersModel
+    from twinkle_b200.models.config import preset
+    from twinkle_b200.utils.device_mesh import DeviceMesh
+    cfg = preset('qwen3-8b', num_hidden_layers=2, hidden_size=512, intermediate_size=1024, num_attention_heads=4 * world,
+                 num_key_value_heads=world, vocab_size=4096)
+    gg = torch.Generator().manual_seed(7)
+    feats = []
+    for n in (257, 193, 301, 257):
+        ids = torch.randint(0, cfg.vocab_size, (n, ), generator=gg)
+        feats.append({'input_ids': ids[:-1], 'labels': ids[1:]})
+
+    def curve(fused):
+        os.environ['TWINKLE_ULYSSES_FUSED'] = '1' if fused else '0'
+        mesh = DeviceMesh.from_sizes(fsdp_size=world, dp_size=None, ulysses_size=world)
+        m = TransformersModel(config=cfg, device_mesh=mesh, seed=0, comm_backend='symm', device=dev)
+        m.set_optimizer('AdamW', lr=1e-3)
+        out = []
+        for _ in range(3):
+            o = m.forward_backward(inputs=feats, micro_batch_size=2)
+            gn = m.clip_grad_and_step(max_grad_norm=1.0)
+            out.append((float(o['loss']), float(gn) if gn is not None else 0.0))
+        return out
+
+    before = ops.ext().launch_count()
+    a = curve(False)
+    mid = ops.ext().launch_count()
+    b = curve(True)
+    after = ops.ext().launch_count()
+    os.environ['TWINKLE_ULYSSES_FUSED'] = '0'
+    diff = max(abs(p - q) for ra, rb in zip(a, b) for p, q in zip(ra, rb))
+    report('ulysses_fused_matches_separate', diff < 2e-2, separate=a, fused=b, launches_separate=mid - before, launches_fused=after - mid)
+    report('ulysses_fused_fewer_launches', after - mid < mid - before)
+
+
 def main():
     rank, world, local = int(os.environ['RANK']), int(os.environ['WORLD_SIZE']), int(os.environ['LOCAL_RANK'])
     torch.cuda.set_device(local)
@@ -195,8 +253,8 @@ def main():
             sys.exit(1)
 
     only = os.environ.get('TK_MGPU_ONLY', '')
-    if only in ('ep', 'megatron', 'tp_fused'):
-        {'ep': ep_checks, 'megatron': megatron_checks, 'tp_fused': tp_fused_checks}[only](rank, world, dev, report)
+    if only in ('ep', 'megatron', 'tp_fused', 'ulysses_fused'):
+        {'ep': ep_checks, 'megatron': megatron_checks, 'tp_fused': tp_fused_checks, 'ulysses_fused': ulysses_fused_checks}[only](rank, world, dev, report)
         report('error_word_end', E.read_and_clear_error() == 0)
         dist.barrier()
         dist.destroy_process_group()

@@ -282,3 +282,32 @@ def test_gemm_sm_pair_staged_epilogue(E, layout):
     finally:
         E.set_gemm_staged(1)
     assert torch.equal(direct, staged)
+
+
+@pytest.mark.parametrize('sp,t', [(2, 600), (4, 256)])
+def test_gemm_head_scatter_epilogue(E, sp, t):
+    """q|k|v projection whose epilogue stores every 128-column block into the buffer of the rank owning those heads.
+    The ranks of the group run one after another on this GPU with local buffers standing in for the peers' memory
+    (the kernel waits on nothing), and are compared with an fp32 matmul sliced the same way."""
+    K, qb, kb = 520, 2 * sp, sp                       # q blocks and kv blocks of 128 columns; N = (qb + 2 kb) * 128
+    N = (qb + 2 * kb) * 128
+    torch.manual_seed(2)
+    w = (torch.randn(N, K, device='cuda') / K ** 0.5).bfloat16()
+    xs = [torch.randn(t, K, device='cuda').bfloat16() for _ in range(sp)]
+    bufs = [torch.full((sp * t, N // sp), float('nan'), device='cuda', dtype=torch.bfloat16) for _ in range(sp)]
+    ptrs = [b.data_ptr() for b in bufs]
+    for r in range(sp):
+        E.gemm_head_scatter(xs[r], w, ptrs, r, t, qb, kb)
+    torch.cuda.synchronize()
+    assert E.read_and_clear_error() == 0
+    ql, kl = qb // sp * 128, kb // sp * 128
+    for c in range(sp):
+        rows = []
+        for r in range(sp):
+            y = xs[r].float() @ w.float().t()
+            q, k, v = y[:, :qb * 128], y[:, qb * 128:(qb + kb) * 128], y[:, (qb + kb) * 128:]
+            rows.append(torch.cat([q[:, c * ql:(c + 1) * ql], k[:, c * kl:(c + 1) * kl], v[:, c * kl:(c + 1) * kl]], -1))
+        want = torch.cat(rows, 0)
+        got = bufs[c].float()
+        assert not torch.isnan(got).any(), 'a block was not written'
+        assert torch.allclose(got, want, atol=2e-2, rtol=2e-2), float((got - want).abs().max())

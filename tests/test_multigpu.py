@@ -38,6 +38,10 @@ def test_tensor_pipeline_parallel_matches_single_gpu():
     _run('megatron', 29633, 240)
 
 
+def test_ulysses_projection_with_fused_head_scatter():
+    _run('ulysses_fused', 29635, 240)
+
+
 @pytest.mark.skipif(os.environ.get('TK_MGPU_FULL') != '1', reason='long group: set TK_MGPU_FULL=1')
 def test_peer_collectives_and_fsdp_ulysses_parity():
     _run('', 29634, 1500)

@@ -37,6 +37,9 @@ class PackedBatch:
     routed_experts: Optional[List[torch.Tensor]] = None
     inputs_embeds: Optional[torch.Tensor] = None
     seq_lens: Optional[List[int]] = None  # full (un-split) sequence lengths on the host; needed by context parallelism
+    # (cos, sin) of the whole row; set by the model forward when the Ulysses strategy scatters heads inside the q|k|v
+    # projection, because q/k-norm and RoPE then run after the exchange on all tokens of this rank's heads
+    rope_full: Optional[tuple] = None
 
 
 class Attention(nn.Module):
@@ -58,13 +61,22 @@ class Attention(nn.Module):
 
     def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, batch: PackedBatch,
                 kv_sink=None) -> torch.Tensor:
-        qkv = self.qkv_proj(x)
         qw = self.q_norm.weight if self.q_norm is not None else None
         kw = self.k_norm.weight if self.k_norm is not None else None
+        ap = self.attn_parallel
+        if ap is not None and getattr(batch, 'rope_full', None) is not None and kv_sink is None and hasattr(ap, 'project_scatter'):
+            # projection whose epilogue already delivers [T_full, (Hq + 2 Hkv)/sp · D] to every peer
+            qkv_full = ap.project_scatter(x, self.qkv_proj, self.hq, self.hkv, self.d)
+            if qkv_full is not None:
+                q, k, v = ops.qkv_norm_rope(qkv_full, qw, kw, batch.rope_full[0], batch.rope_full[1], self.hq // ap.sp, self.hkv // ap.sp,
+                                            self.d, self.cfg.rms_norm_eps)
+                o = ops.flash_attn_varlen(q, k, v, batch.cu_seqlens, batch.max_seqlen, True, 1.0 / math.sqrt(self.d))
+                o = ap.gather_heads(o)
+                return self.o_proj(o.reshape(o.shape[0], -1))
+        qkv = self.qkv_proj(x)
         q, k, v = ops.qkv_norm_rope(qkv, qw, kw, cos, sin, self.hq, self.hkv, self.d, self.cfg.rms_norm_eps)
         if kv_sink is not None:  # sampler prefill: keep K/V for the paged cache
             kv_sink(self.layer_idx, k, v)
-        ap = self.attn_parallel
         if ap is not None and hasattr(ap, 'attention'):  # context parallel: zig-zag local chunks against gathered keys
             o = ap.attention(q, k, v, batch.seq_lens, 1.0 / math.sqrt(self.d))
             return self.o_proj(o.reshape(o.shape[0], -1))
@@ -281,6 +293,14 @@ class DecoderModel(nn.Module):
     def forward(self, batch: PackedBatch, hidden: Optional[torch.Tensor] = None, kv_sink=None) -> torch.Tensor:
         x = self.embed(batch) if hidden is None else hidden
         cos, sin = ops.rope_tables(batch.position_ids, self.cfg.head_dim, self.cfg.rope_theta)
+        full = None
+        for layer in self.layers:
+            ap = getattr(getattr(layer, 'self_attn', None), 'attn_parallel', None)
+            if ap is not None and hasattr(ap, 'full_rope') and not getattr(layer, 'is_linear', False):
+                full = ap.full_rope(cos, sin)  # None unless the fused projection + exchange is in use
+                break
+        if full is not None or getattr(batch, 'rope_full', None) is not None:
+            batch.rope_full = full
         run = self.layer_runner
         for layer in self.layers:
             if run is not None:

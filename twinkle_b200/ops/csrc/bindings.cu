@@ -43,6 +43,7 @@ std::vector<torch::Tensor> moe_router(const torch::Tensor&, int64_t, bool);
 void set_gemm_pair(int64_t);
 void set_gemm_staged(int64_t);
 void gemm_rs(const torch::Tensor&, const torch::Tensor&, const std::string&, const std::vector<int64_t>&, int64_t);
+void gemm_head_scatter(const torch::Tensor&, const torch::Tensor&, const std::vector<int64_t>&, int64_t, int64_t, int64_t, int64_t);
 std::vector<torch::Tensor> gemm_ag(const std::vector<int64_t>&, int64_t, const torch::Tensor&, const std::string&, int64_t, const torch::Tensor&, int64_t, int64_t);
 torch::Tensor tp_stage_reduce(const torch::Tensor&);
 torch::Tensor moe_rows_gather(const torch::Tensor&, const torch::Tensor&, const c10::optional<torch::Tensor>&);
@@ -88,6 +89,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("set_gemm_pair", &tk::set_gemm_pair);
   m.def("set_gemm_staged", &tk::set_gemm_staged);
   m.def("gemm_rs", &tk::gemm_rs);
+  m.def("gemm_head_scatter", &tk::gemm_head_scatter);
   m.def("gemm_ag", &tk::gemm_ag);
   m.def("tp_stage_reduce", &tk::tp_stage_reduce);
   m.def("moe_rows_gather", &tk::moe_rows_gather);

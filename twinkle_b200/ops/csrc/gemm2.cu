@@ -40,6 +40,7 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 constexpr int GROUP_M = 8;
 
 constexpr int FUSE_NONE = 0, FUSE_RS = 1, FUSE_AG = 2, FUSE_STAGED = 3;  // STAGED: plain GEMM, bf16 output written through the staged epilogue
+constexpr int FUSE_HS = 4;  // head scatter: fused q|k|v projection whose epilogue performs the Ulysses sequence→head exchange
 constexpr int MAX_TP = 8;
 
 struct Params {
@@ -53,6 +54,10 @@ struct Params {
   int* ready;                      // FUSE_AG: per-chunk counters, monotonically increasing across calls
   int ready_target;                // FUSE_AG: value a chunk's counter reaches when all copiers finished it in this call
   int copy_ctas;                   // FUSE_AG: CTAs [0, copy_ctas) copy (even number), the rest compute in pairs
+  // FUSE_HS: the N columns are [q | k | v] in blocks of 128; peer c owns q blocks [c·qb/tp, (c+1)·qb/tp) and the same
+  // share of the k and of the v blocks.  peer[c] = its buffer [tp·rows_per_rank, hs_ld]; this rank fills rows
+  // [rank·rows_per_rank, +M) with the peer's blocks packed as [q_local | k_local | v_local].
+  int hs_q_blocks, hs_kv_blocks, hs_ld;
 };
 
 __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
@@ -157,7 +162,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
 
   // the reduce-scatter variant gives its sixth stage to the epilogue as a staging area for coalesced peer stores
-  constexpr int NST = (FUSE == FUSE_RS || FUSE == FUSE_STAGED) ? STAGES - 1 : STAGES;
+  constexpr int NST = (FUSE == FUSE_RS || FUSE == FUSE_STAGED || FUSE == FUSE_HS) ? STAGES - 1 : STAGES;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta = cluster_ctarank();  // 0 = leader of the pair
   const int first_gemm = (FUSE == FUSE_AG) ? p.copy_ctas : 0;
@@ -339,7 +344,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         out_base = p.peer[c];
         out_row = static_cast<size_t>(p.rank) * p.rows_per_rank + (row - c * p.rows_per_rank);
       }
-      if constexpr (FUSE == FUSE_RS || FUSE == FUSE_STAGED) {
+      if constexpr (FUSE == FUSE_RS || FUSE == FUSE_STAGED || FUSE == FUSE_HS) {
         // Stage 32 rows x 128 columns (bf16) per warp in shared memory, then let every half-warp store one whole
         // 256-byte row segment: NVLink (and the local memory system) sees long contiguous writes instead of 64-byte
         // pieces of 32 different rows.
@@ -363,6 +368,17 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           __syncwarp();
           const int j = lane & 15;
           const int col = n0 + half * 128 + j * 8;
+          int hs_peer = 0, hs_col = 0;
+          if constexpr (FUSE == FUSE_HS) {
+            // which peer owns this block of 128 columns, and where it sits in that peer's packed [q | k | v] row
+            const int b = n0 / 128 + half, qb = p.hs_q_blocks, kb = p.hs_kv_blocks, qpl = qb / p.tp, kpl = kb / p.tp;
+            int db;
+            if (b < qb) { hs_peer = b / qpl; db = b - hs_peer * qpl; }
+            else if (b < qb + kb) { const int bb = b - qb; hs_peer = bb / kpl; db = qpl + bb - hs_peer * kpl; }
+            else { const int bb = b - qb - kb; hs_peer = bb / kpl; db = qpl + kpl + bb - hs_peer * kpl; }
+            hs_peer = min(hs_peer, p.tp - 1);  // blocks past N are never stored (column check below)
+            hs_col = db * 128 + j * 8;
+          }
 #pragma unroll 4
           for (int it = 0; it < 16; ++it) {
             const int lr = it * 2 + (lane >> 4);
@@ -374,6 +390,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 const int c = min(grow / p.rows_per_rank, p.tp - 1);
                 o = reinterpret_cast<__nv_bfloat16*>(p.peer[c]) +
                     (static_cast<size_t>(p.rank) * p.rows_per_rank + (grow - c * p.rows_per_rank)) * p.ldo + col;
+              } else if constexpr (FUSE == FUSE_HS) {
+                o = reinterpret_cast<__nv_bfloat16*>(p.peer[hs_peer]) + (static_cast<size_t>(p.rank) * p.rows_per_rank + grow) * p.hs_ld + hs_col;
               } else {
                 o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(grow) * p.ldo + col;
               }
@@ -577,6 +595,36 @@ void gemm_rs(const torch::Tensor& a, const torch::Tensor& w, const std::string& 
   p.tp = tp; p.rank = static_cast<int>(rank); p.rows_per_rank = M / tp;
   for (int i = 0; i < tp; ++i) p.peer[i] = reinterpret_cast<void*>(stage_ptrs[i]);
   launch_fused<g2::FUSE_RS>(b_mn, ta, tb, ta, p, 0, at::cuda::getCurrentCUDAStream());
+}
+
+// Fused q|k|v projection with the Ulysses sequence→head exchange in the epilogue.  x [T_local, K], w [N, K] with
+// N = (q_blocks + 2·kv_blocks)·128 laid out [q | k | v].  `dest_ptrs[c]` = rank c's buffer [sp·rows_per_rank, N/sp] bf16
+// (symmetric memory); this rank writes rows [rank·rows_per_rank, +T_local) of every peer's buffer.  The caller brackets
+// the call with cross-GPU barriers (buffers free before, pushes landed after).
+void gemm_head_scatter(const torch::Tensor& x, const torch::Tensor& w, const std::vector<int64_t>& dest_ptrs, int64_t rank, int64_t rows_per_rank,
+                       int64_t q_blocks, int64_t kv_blocks) {
+  check_bf16_2d(x, "x");
+  check_bf16_2d(w, "w");
+  const int sp = dest_ptrs.size();
+  TORCH_CHECK(sp >= 1 && sp <= g2::MAX_TP, "group size out of range");
+  TORCH_CHECK(rank >= 0 && rank < sp, "rank out of range");
+  const int M = x.size(0), K = x.size(1), N = w.size(0);
+  TORCH_CHECK(w.size(1) == K, "K mismatch");
+  TORCH_CHECK(q_blocks > 0 && kv_blocks > 0 && q_blocks % sp == 0 && kv_blocks % sp == 0, "q and kv column blocks must divide over the group");
+  TORCH_CHECK(N == (q_blocks + 2 * kv_blocks) * 128, "w rows must be (q_blocks + 2 kv_blocks) * 128");
+  TORCH_CHECK(M <= rows_per_rank, "more rows than a rank's share of the destination");
+  TORCH_CHECK(K % 8 == 0, "K must be a multiple of 8");
+  for (int i = 0; i < sp; ++i) TORCH_CHECK(dest_ptrs[i] % 16 == 0, "destination buffers must be 16-byte aligned");
+  if (M == 0) return;
+  c10::cuda::CUDAGuard guard(x.device());
+  CUtensorMap ta = make_tmap_2d(x.data_ptr(), K, M, x.stride(0), g2::BK, 128);
+  CUtensorMap tb = make_tmap_2d(w.data_ptr(), w.size(1), w.size(0), w.stride(0), g2::BK, 128);
+  g2::Params p{};
+  p.out = nullptr; p.M = M; p.N = N; p.K = K; p.ldo = N; p.out_fp32 = 0; p.accumulate = 0; p.err = error_word();
+  p.tp = sp; p.rank = static_cast<int>(rank); p.rows_per_rank = static_cast<int>(rows_per_rank);
+  for (int i = 0; i < sp; ++i) p.peer[i] = reinterpret_cast<void*>(dest_ptrs[i]);
+  p.hs_q_blocks = static_cast<int>(q_blocks); p.hs_kv_blocks = static_cast<int>(kv_blocks); p.hs_ld = N / sp;
+  launch_fused<g2::FUSE_HS>(false, ta, tb, ta, p, 0, at::cuda::getCurrentCUDAStream());
 }
 
 // Column-parallel linear with the all-gather in the prologue.  `x_ptrs[c]` = rank c's [rows_per_rank, K] bf16 shard

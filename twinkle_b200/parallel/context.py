@@ -94,7 +94,7 @@ def cp_group_for(mesh):
     import torch.distributed as dist
     if not (dist.is_available() and dist.is_initialized()) or not mesh.has_dim('cp') or mesh.get_dim_size('cp') <= 1:
         return None
-    key = id(mesh)
+    key = mesh.signature()
     if key not in _CP_GROUPS:
         _CP_GROUPS[key] = mesh.get_dim_group('cp')
     return _CP_GROUPS[key]

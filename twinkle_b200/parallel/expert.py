@@ -30,7 +30,7 @@ def ep_group_for(mesh):
     ep = mesh.ep_size or 1
     if ep <= 1 or not (dist.is_available() and dist.is_initialized()):
         return None
-    key = (id(mesh), ep)
+    key = (mesh.signature(), ep)
     if key in _EP_GROUPS:
         return _EP_GROUPS[key][0]
     ranks = sorted(mesh._coord_of, key=lambda r: (mesh._flat_data_index(r), r))
@@ -52,7 +52,7 @@ def ep_group_for(mesh):
 
 def ep_replica_group_for(mesh):
     ep_group_for(mesh)
-    return _EP_GROUPS.get((id(mesh), mesh.ep_size or 1), (None, None))[1]
+    return _EP_GROUPS.get((mesh.signature(), mesh.ep_size or 1), (None, None))[1]
 
 
 def expert_layout(expert_ids: torch.Tensor, num_experts: int, align: int,

@@ -136,6 +136,15 @@ class SymmCommunicator(Communicator):
         self.barrier_kernel()  # all pushes landed
         return out
 
+    def head_scatter_gemm(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows_per_rank: int, q_blocks: int, kv_blocks: int) -> torch.Tensor:
+        """``x·wᵀ`` with every 128-column block written into the symmetric ``out`` of the rank that owns its heads."""
+        ptrs = self.peer_ptrs(out)
+        assert ptrs is not None, 'destination must be symmetric memory'
+        self.barrier_kernel()  # every rank is done reading the buffer's previous contents
+        self.ext.gemm_head_scatter(x, w, ptrs, self.rank, rows_per_rank, q_blocks, kv_blocks)
+        self.barrier_kernel()  # all tiles of all ranks landed
+        return out
+
     def check(self) -> None:
         code = self.ext.read_and_clear_error()
         if code:

@@ -29,7 +29,7 @@ def sp_group_for(mesh):
     sp = mesh.ulysses_size or 1
     if sp <= 1 or not (dist.is_available() and dist.is_initialized()):
         return None
-    key = (id(mesh), sp)
+    key = (mesh.signature(), sp)
     if key in _SP_GROUPS:
         return _SP_GROUPS[key]
     # order ranks by their flat data index so that consecutive ``sp`` of them share a data rank
@@ -76,20 +76,19 @@ class _HeadGather(torch.autograd.Function):
         return _seq_to_head(g.contiguous(), ctx.comm), None
 
 
-_SYMM_OUT = {}
-
-
 def _symm_out(comm, shape, dtype, tag):
     """Destination buffers in symmetric memory, two per (shape, direction) used alternately so a
-    consumer of the previous exchange never races with the next push."""
-    key = (id(comm), tuple(shape), dtype, tag)
-    ent = _SYMM_OUT.get(key)
+    consumer of the previous exchange never races with the next push.  The cache lives on the
+    communicator, so it goes away with the symmetric arena it points into."""
+    cache = comm.__dict__.setdefault('_exchange_buffers', {})
+    key = (tuple(shape), dtype, tag)
+    ent = cache.get(key)
     if ent is None:
         n = 1
         for v in shape:
             n *= v
         ent = {'bufs': [comm.alloc(n, dtype).view(shape) for _ in range(2)], 'next': 0}
-        _SYMM_OUT[key] = ent
+        cache[key] = ent
     t = ent['bufs'][ent['next']]
     ent['next'] ^= 1
     return t
@@ -123,6 +122,51 @@ def _head_to_seq(x: torch.Tensor, comm: Communicator) -> torch.Tensor:
     return recv.transpose(0, 1).reshape(t, sp * hl, d)  # [t, sp, hl, d] → heads back in order
 
 
+def fused_projection_enabled() -> bool:
+    """``TWINKLE_ULYSSES_FUSED=1``: the q|k|v projection scatters heads to the peers from its own epilogue."""
+    import os
+    return os.environ.get('TWINKLE_ULYSSES_FUSED', '0') == '1'
+
+
+class _ProjectScatter(torch.autograd.Function):
+    """``x [T_local, H] · Wqkvᵀ`` delivered as ``[T_local·sp, (Hq + 2 Hkv)/sp · D]`` on every peer: the GEMM epilogue
+    stores each 128-column block into the buffer of the rank that owns those heads (reference
+    ``sequence_parallel/utils.py:345-401`` does projection, then three all-to-alls).  Backward returns the three
+    gradient sections with the head → sequence exchange and runs the usual dX / dW GEMMs."""
+
+    @staticmethod
+    def forward(ctx, x, weight, strat, hq, hkv, d, wgrad_out):
+        comm, sp = strat.comm, strat.sp
+        t = x.shape[0]
+        out = _symm_out(comm, (sp * t, weight.shape[0] // sp), x.dtype, 'qkv')
+        comm.head_scatter_gemm(x, weight, out, t, hq * d // 128, hkv * d // 128)
+        ctx.save_for_backward(x, weight)
+        ctx.strat, ctx.dims, ctx.wgrad_out = strat, (hq, hkv, d), wgrad_out
+        # saved by the consumer for its backward, while the symmetric buffer is reused two exchanges later
+        return out.clone() if any(ctx.needs_input_grad[:2]) else out
+
+    @staticmethod
+    def backward(ctx, g):
+        from .. import ops
+        x, weight = ctx.saved_tensors
+        comm, sp = ctx.strat.comm, ctx.strat.sp
+        hq, hkv, d = ctx.dims
+        tt = g.shape[0]
+        ql, kl = hq // sp * d, hkv // sp * d
+        parts = [_head_to_seq(g[:, a:b].reshape(tt, (b - a) // d, d).contiguous(), comm).reshape(tt // sp, -1)
+                 for a, b in ((0, ql), (ql, ql + kl), (ql + kl, ql + 2 * kl))]
+        g2 = torch.cat(parts, dim=-1)
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            gx = ops.gemm(g2, weight, 'nn')
+        if ctx.needs_input_grad[1]:
+            if ctx.wgrad_out is not None:
+                ops.gemm(g2, x, 'tn', out=ctx.wgrad_out, accumulate=True)
+            else:
+                gw = ops.gemm(g2, x, 'tn')
+        return gx, gw, None, None, None, None, None
+
+
 class UlyssesAttention:
     """Strategy object plugged into ``Attention.attn_parallel``."""
 
@@ -145,6 +189,32 @@ class UlyssesAttention:
 
     def gather_heads(self, o):
         return _HeadGather.apply(o.contiguous(), self.comm)
+
+    # ---- exchange inside the projection
+    def _fusable(self, hq: int, hkv: int, d: int) -> bool:
+        return (fused_projection_enabled() and hasattr(self.comm, 'head_scatter_gemm') and self.kv_rep == 1
+                and (hq * d) % (128 * self.sp) == 0 and (hkv * d) % (128 * self.sp) == 0 and hq % self.sp == 0)
+
+    def full_rope(self, cos, sin):
+        """(cos, sin) of all tokens of the row (ranks hold consecutive chunks), or None when the fused path is off."""
+        if not (fused_projection_enabled() and hasattr(self.comm, 'head_scatter_gemm') and cos.is_cuda):
+            return None
+        with torch.no_grad():
+            return self.comm.all_gather_tensor(cos), self.comm.all_gather_tensor(sin)
+
+    def project_scatter(self, x, proj, hq: int, hkv: int, d: int):
+        """q|k|v projection + sequence → head exchange in one kernel; None when this call cannot use it (bias, LoRA
+        on the projection, tensor parallelism, dtype, head counts that do not split into 128-column blocks)."""
+        from ..models.layers import current_lora_batch
+        if not (self._fusable(hq, hkv, d) and x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and proj.bias is None
+                and getattr(proj, 'tp_mode', None) is None and x.shape[-1] % 8 == 0):
+            return None
+        if getattr(proj, 'max_loras', 0) > 0 and current_lora_batch() is not None:
+            return None
+        w = proj.weight
+        if w.dtype != torch.bfloat16 or not w.is_contiguous():
+            return None
+        return _ProjectScatter.apply(x.contiguous(), w, self, hq, hkv, d, proj.wgrad_out if w.requires_grad else None)
 
     # ---- linear attention (Gated DeltaNet): per-head scalars and the depth-wise convolution follow the heads
     def scatter_scalar_heads(self, x):

@@ -42,6 +42,12 @@ class DeviceMesh:
     sequence_parallel: bool = False
     device_type: Optional[str] = None
 
+    def signature(self) -> tuple:
+        """Hashable description of the layout.  Caches of process groups are keyed by it: equal meshes share their
+        groups, and a key can never be taken over by a different mesh that reuses a freed object's address."""
+        m = np.asarray(self.mesh)
+        return (m.shape, m.tobytes(), tuple(self.mesh_dim_names or ()), self.ep_size, self.etp_size, self.ep_fsdp_size, self.ulysses_size)
+
     # ------------------------------------------------------------------ build
     @staticmethod
     def from_sizes(*, world_size: int = 1, dp_size: Optional[int] = 1, fsdp_size: Optional[int] = None,
