@@ -31,3 +31,45 @@ def test_dpo_loss_falls():
 def test_server_cookbook_native_backend():
     losses = _load('server_tinker_client').main(['--backend', 'native', '--steps', '2'])
     assert losses[1] < losses[0]
+
+
+def test_gkd_off_and_on_policy():
+    off = _load('gkd').main(['--steps', '4'])
+    assert off[-1] < off[0]
+    on = _load('gkd').main(['--mode', 'on', '--steps', '2', '--max-tokens', '6'])
+    assert len(on) == 2 and all(x == x and x >= 0 for x in on)
+    topk = _load('gkd').main(['--steps', '3', '--topk', '8'])
+    assert topk[-1] < topk[0]
+
+
+def test_embedding_infonce_learns_retrieval():
+    r = _load('embedding_infonce').main(['--steps', '15'])
+    assert r['losses'][-1] < 0.2 * r['losses'][0] and r['acc_after'] >= r['acc_before'] and r['acc_after'] == 1.0
+
+
+def test_moe_routing_replay():
+    r = _load('moe_routing_replay').main([])
+    assert r['matches_sampler'] and r['replay_kept'] and not r['free_kept']
+    assert all(rec == n - 1 for rec, n in zip(r['recorded'], r['lens']))     # every fed token recorded: prompt and decode steps
+
+
+def test_server_twinkle_client_native_backend():
+    r = _load('server_twinkle_client').main(['--backend', 'native', '--epochs', '2'])
+    assert r['losses'][-1] < r['losses'][0] and r['path'].startswith('twinkle://') and len(r['tokens']) == 4
+    assert any(run.get('training_run_id') or run.get('run_id') or run for run in r['runs'])
+
+
+def test_http_twin_positional_arguments():
+    import pytest
+    from twinkle_b200.client import MultiLoraTransformersModel
+    seen = {}
+    twin = MultiLoraTransformersModel.__new__(MultiLoraTransformersModel)
+    twin._call = lambda method, adapter, **kw: seen.update(method=method, adapter=adapter, kw=kw)
+    twin.set_optimizer('AdamW', lr=1e-3, adapter_name='a')
+    assert seen == dict(method='set_optimizer', adapter='a', kw=dict(optimizer_cls='AdamW', lr=1e-3))
+    with pytest.raises(TypeError):
+        twin.set_optimizer('AdamW', 'extra')
+    with pytest.raises(TypeError):
+        twin.set_loss('GRPOLoss', loss_cls='DPOLoss')
+    with pytest.raises(TypeError):
+        twin.forward_backward([{'input_ids': [1]}])          # inputs are keyword-only, as on the local model

@@ -140,10 +140,28 @@ class MultiLoraTransformersModel:
         r = self.c.t.post(self.prefix + '/twinkle/add_adapter_to_model', {'session_id': self.c.session_id, 'config': cfg})
         self.adapters[adapter_name] = r['adapter_name']
 
+    # names of the leading positional parameters of the server-side methods, so ``set_optimizer('AdamW', lr=…)`` reads
+    # the same against a local model and against this twin
+    _POSITIONAL = {'set_loss': ('loss_cls', ), 'set_optimizer': ('optimizer_cls', ), 'set_lr_scheduler': ('scheduler_cls', ),
+                   'set_template': ('template_cls', ), 'set_processor': ('processor_cls', ), 'add_metric': ('metric_cls', 'is_training'),
+                   'apply_patch': ('patch_cls', ), 'calculate_metric': ('is_training', ), 'save': ('name', 'output_dir'),
+                   'load': ('name', 'output_dir'), 'resume_from_checkpoint': ('checkpoint_dir', )}
+
     def __getattr__(self, name: str):
         if name.startswith('_'):
             raise AttributeError(name)
-        return lambda *a, adapter_name=None, **kw: self._call(name, adapter_name, **kw)
+
+        def call(*a, adapter_name=None, **kw):
+            names = self._POSITIONAL.get(name, ())
+            if len(a) > len(names):
+                raise TypeError(f'{name}() takes {len(names)} positional argument(s) over HTTP ({", ".join(names) or "none"}); pass the rest by keyword')
+            for k, v in zip(names, a):
+                if k in kw:
+                    raise TypeError(f'{name}() got multiple values for {k!r}')
+                kw[k] = v
+            return self._call(name, adapter_name, **kw)
+
+        return call
 
 
 class TorchSampler:

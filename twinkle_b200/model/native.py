@@ -285,11 +285,23 @@ class TransformersModel(TwinkleModel):
         r = extras.get('routed_experts') if extras else None
         if not r or any(x is None for x in r):
             return None
-        # per-feature [L, T_i, k] → per-layer [ΣT, k]
+        # per-feature [L, T_i, k] → per-layer [ΣT, k].  A sampler records one row per token it fed through the model,
+        # which is one fewer than the feature holds (the last sampled token is never fed; reference
+        # processor/base.py:826-850 pads the same gap): missing rows become -1 = route freely, extra rows are cut.
         per_layer = []
         n_layers = len(r[0])
+        lens = list(mb.seq_lens) if len(mb.seq_lens) == len(r) else [None] * len(r)
+
+        def fit(t, n):
+            t = torch.as_tensor(t).long()
+            if n is None or t.shape[0] == n:
+                return t
+            if t.shape[0] > n:
+                return t[:n]
+            return torch.cat([t, torch.full((n - t.shape[0], t.shape[1]), -1, dtype=torch.long)], 0)
+
         for l in range(n_layers):
-            per_layer.append(torch.cat([torch.as_tensor(x[l]) for x in r], 0).to(self.device))
+            per_layer.append(torch.cat([fit(x[l], n) for x, n in zip(r, lens)], 0).to(self.device))
         if mb.local_index is not None:
             per_layer = [p[mb.local_index.to(p.device)] for p in per_layer]
         return per_layer

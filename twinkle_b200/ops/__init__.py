@@ -527,8 +527,9 @@ class _Router(torch.autograd.Function):
     @staticmethod
     def forward(ctx, logits, top_k, renorm, forced):
         w, idx, probs, hist = ext().moe_router(logits.contiguous(), top_k, renorm)
-        if forced is not None:  # router replay: keep the probabilities, take the given experts
-            idx = forced.to(idx.device).long()
+        if forced is not None:  # router replay: keep the probabilities, take the given experts (rows of -1: no replay)
+            forced = forced.to(idx.device).long()
+            idx = torch.where(forced[:, :1] < 0, idx, forced)
             w = probs.gather(-1, idx)
             if renorm:
                 w = w / w.sum(-1, keepdim=True)
@@ -558,11 +559,11 @@ def moe_router(logits, top_k: int, renormalize: bool = True, forced=None):
     if _cuda(logits):
         return _Router.apply(logits, top_k, renormalize, forced)
     probs = torch.softmax(logits.float(), -1)
-    if forced is not None:
-        idx = forced.long()
+    w, idx = probs.topk(top_k, -1)
+    if forced is not None:  # rows of -1 keep the router's own choice (tokens the sampler did not record)
+        forced = forced.long()
+        idx = torch.where(forced[:, :1] < 0, idx, forced)
         w = probs.gather(-1, idx)
-    else:
-        w, idx = probs.topk(top_k, -1)
     if renormalize:
         w = w / w.sum(-1, keepdim=True)
     return w, idx, probs, None

@@ -228,7 +228,15 @@ class NativeEngine:
         for i, s in enumerate(seqs):
             table[i, :len(s.blocks)] = torch.tensor(s.blocks, dtype=torch.int32)
         seq_lens = torch.tensor([s.length for s in seqs], dtype=torch.int32, device=self.device)
-        return self._decode_body(last_tokens, positions, table, seq_lens, lora)
+        self.model.set_record_routing(self.capture_routing)
+        logits = self._decode_body(last_tokens, positions, table, seq_lens, lora)
+        if self.capture_routing:
+            routed = self.model.collect_routed_experts()  # per layer [B, k]: the experts of the token just fed
+            if routed is not None:
+                for i, s in enumerate(seqs):
+                    rows = [r[i:i + 1].cpu() for r in routed]
+                    s.routed = rows if s.routed is None else [torch.cat([a, b], 0) for a, b in zip(s.routed, rows)]
+        return logits
 
     # ------------------------------------------------------------- sampling
     def _sample(self, seqs: List[_Seq], logits: torch.Tensor) -> Tuple[List[int], List[float], List[Optional[List[Tuple[int, float]]]]]:
