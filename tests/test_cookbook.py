@@ -73,3 +73,15 @@ def test_http_twin_positional_arguments():
         twin.set_loss('GRPOLoss', loss_cls='DPOLoss')
     with pytest.raises(TypeError):
         twin.forward_backward([{'input_ids': [1]}])          # inputs are keyword-only, as on the local model
+
+
+def test_sft_pipeline_cli_trains_saves_resumes_and_evaluates(tmp_path):
+    mod = _load('sft_pipeline_cli')
+    common = ['--model', 'tiny-dense', '--use-lora', 'true', '--lr', '2e-3', '--bs', '4', '--output-dir', str(tmp_path)]
+    first = mod.main(common + ['--max-steps', '3'])
+    assert first['step'] == 3 and first['consumed'] == 12 and os.path.isdir(first['checkpoint'])
+    assert float(first['eval']['loss']) > 0.0                                   # forward_only + calculate_loss feed the evaluation metric
+    second = mod.main(common + ['--max-steps', '6', '--resume-from-checkpoint', first['checkpoint']])
+    assert second['step'] == 6 and len(second['losses']) == 3 and second['consumed'] == 24
+    assert second['losses'][0] < first['losses'][0]                             # continues from the trained adapter, not from scratch
+    assert float(second['eval']['loss']) < float(first['eval']['loss'])

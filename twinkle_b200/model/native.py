@@ -402,6 +402,7 @@ class TransformersModel(TwinkleModel):
         out = self._forward_micro(mbs[0], og, True, temperature, return_logits, disable_lora)
         og.train_status.inputs, og.train_status.outputs, og.train_status.forward_kwargs = feats, out, kwargs
         self._forward_ran = True
+        og.last_forward_training = True
         return self._public_outputs(out)
 
     @remote_function(dispatch='slice_dp', collect=collect_tensor_dict)
@@ -409,12 +410,15 @@ class TransformersModel(TwinkleModel):
                      disable_lora: bool = False, micro_batch_size: Optional[int] = None, **kwargs) -> ModelOutput:
         og = self._group(adapter_name)
         feats = self._encode(inputs, og)
-        outs = []
+        outs, raw = [], []
         for mb in self._processor(og, micro_batch_size)(feats):
             o = self._forward_micro(mb, og, False, temperature, return_logits, disable_lora)
             self.engine.end_forward_only()
+            raw.append(o)
             outs.append(self._public_outputs(o))
-        og.eval_status.inputs, og.eval_status.outputs = feats, outs[-1] if outs else None
+        # what calculate_loss evaluates next: every micro-batch of this call, with the caller's loss arguments
+        og.eval_status.inputs, og.eval_status.outputs, og.eval_status.forward_kwargs = feats, raw, kwargs
+        og.last_forward_training = False
         return collect_tensor_dict(outs) if len(outs) > 1 else outs[0]
 
     @staticmethod
@@ -429,12 +433,32 @@ class TransformersModel(TwinkleModel):
 
     @remote_function(collect='mean')
     def calculate_loss(self, adapter_name: Optional[str] = None, **kwargs) -> float:
+        """Loss of the latest forward.  After ``forward`` it is the training loss that ``backward`` will differentiate;
+        after ``forward_only`` it is an evaluation loss over every micro-batch of that call, accumulated into the
+        evaluation metrics (reference ``transformers.py:620-665`` picks the status by the module's train/eval mode)."""
         og = self._group(adapter_name)
-        st = og.train_status
+        if getattr(og, 'last_forward_training', True):
+            st = og.train_status
+            kw = dict(st.forward_kwargs or {})
+            kw.update(kwargs)
+            loss, _ = self._loss_micro(og, st.outputs, kw)
+            return float(loss.detach())
+        st = og.eval_status
         kw = dict(st.forward_kwargs or {})
         kw.update(kwargs)
-        loss, _ = self._loss_micro(og, st.outputs, kw)
-        return float(loss.detach())
+        outs = st.outputs if isinstance(st.outputs, list) else [st.outputs]
+        total, tokens = 0.0, 0.0
+        with torch.no_grad():
+            for o in outs:
+                loss, nt = self._loss_micro(og, o, kw, is_training=False)
+                total += float(loss.detach())
+                tokens += nt
+                for m in st.metrics:
+                    m.accumulate({'labels': o.get('labels')}, {'loss': float(loss.detach()), 'num_tokens': nt, 'logps': o.get('logps')},
+                                 step_done=False, loss_instance=getattr(og.loss_instance, 'loss', og.loss_instance))
+        st.loss_value = None
+        st.outputs = outs  # _loss_micro leaves the last micro-batch there
+        return total / tokens if tokens > 0 else total / max(len(outs), 1)
 
     @remote_function()
     def backward(self, adapter_name: Optional[str] = None, **kwargs) -> None:
@@ -580,6 +604,7 @@ class TransformersModel(TwinkleModel):
                 if 'weight_decay' in optim_params and g['weight_decay'] > 0:
                     g['weight_decay'] = optim_params['weight_decay']
         og.optim_steps += 1
+        opt._opt_called = True  # the fused update below is this optimizer's step; stock LR schedulers check the flag
         scale = self._pending_scale.pop(og.adapter_name, 1.0)
         fence = getattr(self._dp_comm(), 'step_barrier', None)
         if fence is not None:
