@@ -85,3 +85,12 @@ def test_sft_pipeline_cli_trains_saves_resumes_and_evaluates(tmp_path):
     assert second['step'] == 6 and len(second['losses']) == 3 and second['consumed'] == 24
     assert second['losses'][0] < first['losses'][0]                             # continues from the trained adapter, not from scratch
     assert float(second['eval']['loss']) < float(first['eval']['loss'])
+
+
+def test_grpo_pool_disaggregated_trainer_and_sampler_groups():
+    """Two FSDP trainer workers and one sampler worker in separate processes; weights cross through the checkpoint
+    engine.  After every sync the sampler's log-probs are the trainer's (bf16 transport rounding only)."""
+    hist = _load('grpo_pool_disaggregated').main(['--steps', '3', '--device', 'cpu', '--prompts', '2', '--group', '4', '--max-tokens', '6'])
+    assert len(hist) == 3 and all(h['samples'] == 8 for h in hist)
+    assert hist[0]['sync_bytes'] > 10 * hist[1]['sync_bytes'] > 0          # first sync carries the base weights, later ones the adapter
+    assert all(h['logp_drift'] < 0.03 for h in hist), hist

@@ -88,6 +88,14 @@ class MultiLora:
             p.requires_grad_('lora' in n)
         self._initial_A: Dict[str, torch.Tensor] = {n: p.detach().clone() for n, p in self.pool_parameters() if self._is_A(n)}
 
+    def sync_initial(self, comm) -> None:
+        """Make the saved initial ``A`` values (what a released slot is reset to) the first rank's on every rank of a
+        data-parallel group, so that a re-used slot starts equal everywhere."""
+        if comm is None or comm.world_size <= 1:
+            return
+        for n in sorted(self._initial_A):
+            comm.broadcast(self._initial_A[n], 0)
+
     @staticmethod
     def _is_A(name: str) -> bool:
         return 'lora_A' in name or name.endswith('_A')

@@ -38,6 +38,7 @@ from ..utils.logger import get_logger
 from ..utils.nccl_safe import collective_safe
 from ..utils.platform import Platform
 from ..utils.safetensors_io import SafetensorLazyLoader, StreamingSafetensorSaver
+from ..checkpoint_engine import CheckpointEngineMixin
 from .base import TwinkleModel
 from .multi_lora import LoraConfig, MultiLora
 from .optimizer_group import AdamHyper, OptimizerGroup, TrainStatus
@@ -75,7 +76,7 @@ class EngineOptimizer(torch.optim.Optimizer):
 
 
 @remote_class()
-class TransformersModel(TwinkleModel):
+class TransformersModel(TwinkleModel, CheckpointEngineMixin):
     """Full-parameter or single-adapter training on the owned decoder.
 
     ``model_id`` is a directory with ``config.json`` + safetensors, or the name
@@ -199,6 +200,8 @@ class TransformersModel(TwinkleModel):
             ignored = lambda n: '.mlp.experts.' in n  # experts are EP-local, not FSDP-sharded over the dp group
         self.engine = FSDPEngine(self.model, comm, self.compute_dtype, self.device, grad_dtype=self.grad_dtype, ignored=ignored,
                                  keep_attention=self.keep_attention)
+        if self.multi_lora is not None:
+            self.multi_lora.sync_initial(comm)
 
     def _group(self, adapter_name: Optional[str]) -> OptimizerGroup:
         name = adapter_name or _DEFAULT
@@ -788,9 +791,25 @@ class TransformersModel(TwinkleModel):
         self._lora_state.pop(adapter_name, None)
         self._pending_scale.pop(adapter_name, None)
 
+    @remote_function(collect='first')
     def get_peft_config_dict(self, adapter_name: Optional[str] = None) -> Dict[str, Any]:
         og = self._group(adapter_name)
         return og.adapter_config.to_peft_dict() if og.adapter_config is not None else {}
+
+    # ---- trainer end of a weight sync across worker groups (reference transformers.py:1507-1616)
+    @remote_function(collect='first')
+    def prepare_checkpoint_engine(self, role: str = 'send', **kwargs) -> Dict[str, Any]:
+        return CheckpointEngineMixin.prepare_checkpoint_engine(self, role, **kwargs)
+
+    @remote_function(collect='first', lazy_collect=True)
+    def send_weights(self, adapter_name: Optional[str] = None, merge_and_sync: bool = False, lora_only: bool = False, **kwargs) -> Dict[str, float]:
+        """Runs on every rank of the model group (gathering sharded parameters is collective); the first rank feeds
+        the engine.  Returns to the driver at once so that the sampler's ``receive_weights`` can run alongside."""
+        return self._send_weights(adapter_name, merge_and_sync, lora_only)
+
+    @remote_function()
+    def finalize_checkpoint_engine(self) -> None:
+        CheckpointEngineMixin.finalize_checkpoint_engine(self)
 
     def _load_adapter_file(self, adapter_name: str, directory: str) -> None:
         from safetensors.torch import load_file

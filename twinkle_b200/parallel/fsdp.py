@@ -411,6 +411,18 @@ class FSDPEngine:
             if m is not None:
                 root_params += split(n, m)
         self.root = FSDPUnit('root', root_params, comm, compute_dtype, self.device, grad_dtype)
+        if comm.world_size > 1:
+            # Replicated trainables (LoRA pools) are initialised from each process's own random stream; their gradients are
+            # summed over ranks, so they only stay equal if they start equal: the first rank's values are the ones used
+            # (what FSDP's sync_module_states does for the reference, native_fsdp.py:190-205).
+            with torch.no_grad():
+                for _, p in self.replicated:
+                    if getattr(p, '_ep_local', False):
+                        rc = getattr(p, '_ep_replica_comm', None)
+                        if rc is not None and rc.world_size > 1:
+                            rc.broadcast(p.data, 0)
+                    else:
+                        comm.broadcast(p.data, 0)
         if hasattr(comm, 'sync_all'):
             comm.sync_all()  # every rank's shards are initialised before anyone pulls them
         model.layer_runner = self._run_layer

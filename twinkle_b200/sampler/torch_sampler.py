@@ -25,12 +25,13 @@ from ..models.decoder import build_model
 from ..template import Template
 from ..utils.device_mesh import DeviceMesh
 from ..utils.platform import Platform
+from ..checkpoint_engine import CheckpointEngineMixin
 from .base import Sampler
 from .engine import NativeEngine
 
 
 @remote_class()
-class TorchSampler(Sampler):
+class TorchSampler(Sampler, CheckpointEngineMixin):
 
     def __init__(self, model_id: Optional[str] = None, config: Union[DecoderConfig, Dict[str, Any], None] = None,
                  device_mesh: DeviceMesh = None, engine_args: Optional[Dict[str, Any]] = None, seed: int = 42, device=None,
@@ -207,7 +208,22 @@ class TorchSampler(Sampler):
             self.multi_lora.set_state_dict(name, {k: v.to(self.device) for k, v in lora.items()})
         self.engine.reset_prefix_cache()
 
-    receive_weights = update_weights
+    # ---- sampler end of a weight sync across worker groups (reference vllm_sampler.py:439-487)
+    @remote_function(collect='first')
+    def prepare_checkpoint_engine(self, role: str = 'recv', **kwargs) -> Dict[str, Any]:
+        return CheckpointEngineMixin.prepare_checkpoint_engine(self, role, **kwargs)
+
+    @remote_function(collect='first')
+    def receive_weights(self, weights=None, peft_config: Optional[Dict[str, Any]] = None, **kwargs):
+        """With ``weights``: same as ``update_weights``.  Without: take them from the prepared checkpoint engine;
+        returns the number of bytes received."""
+        if weights is not None:
+            return self.update_weights(weights, peft_config=peft_config, **kwargs)
+        return self._receive_weights(peft_config=peft_config, **kwargs)
+
+    @remote_function()
+    def finalize_checkpoint_engine(self) -> None:
+        CheckpointEngineMixin.finalize_checkpoint_engine(self)
 
     @remote_function(collect='first')
     def get_state_keys(self) -> List[str]:
