@@ -94,3 +94,13 @@ def test_grpo_pool_disaggregated_trainer_and_sampler_groups():
     assert len(hist) == 3 and all(h['samples'] == 8 for h in hist)
     assert hist[0]['sync_bytes'] > 10 * hist[1]['sync_bytes'] > 0          # first sync carries the base weights, later ones the adapter
     assert all(h['logp_drift'] < 0.03 for h in hist), hist
+
+
+def test_tinker_dpo_then_resume_after_server_restart():
+    r = _load('server_tinker_dpo_resume').main(['--steps', '3'])
+    assert abs(r['losses'][0] - 0.6931) < 1e-3 and r['losses'][-1] < r['losses'][0]       # starts at log 2: policy == reference
+    assert r['metrics']['rewards/accuracies'] >= 0.5 and r['metrics']['rewards/margins'] > 0 and 'grad_norm' in r['metrics']
+    assert abs(r['next_uninterrupted'][0] - r['next_resumed'][0]) < 1e-4                  # adapter restored exactly
+    assert abs(r['next_uninterrupted'][1] - r['next_resumed'][1]) < 1e-4                  # and the Adam moments and step count
+    assert r['info']['is_lora'] and r['info']['lora_rank'] == 8 and r['info']['base_model'] == 'tiny-dense'
+    assert len(r['runs']) >= 1 and len(r['tokens']) == 4

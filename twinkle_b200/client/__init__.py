@@ -284,8 +284,9 @@ class TrainingClient:
     def forward_backward(self, data: List[Dict[str, Any]], loss_fn: str = 'cross_entropy', loss_fn_config=None) -> APIFuture:
         return self._post('forward_backward', forward_backward_input={'data': data, 'loss_fn': loss_fn, 'loss_fn_config': loss_fn_config})
 
-    def forward(self, data: List[Dict[str, Any]], loss_fn: str = 'cross_entropy') -> APIFuture:
-        return self._post('forward', forward_input={'data': data, 'loss_fn': loss_fn})
+    def forward(self, data: List[Dict[str, Any]], loss_fn: str = 'cross_entropy', loss_fn_config=None) -> APIFuture:
+        """No gradients.  ``loss_fn_config={'disable_lora': True}`` scores with the frozen base (DPO reference log-probs)."""
+        return self._post('forward', forward_input={'data': data, 'loss_fn': loss_fn, 'loss_fn_config': loss_fn_config})
 
     def optim_step(self, adam_params: Optional[Dict[str, Any]] = None) -> APIFuture:
         return self._post('optim_step', adam_params=adam_params or {'learning_rate': 1e-4})
@@ -298,6 +299,13 @@ class TrainingClient:
 
     def save_weights_for_sampler(self, name: str) -> APIFuture:
         return self._post('save_weights_for_sampler', path=name, session_id=self.session_id)
+
+    def save_weights_and_get_sampling_client(self, name: Optional[str] = None) -> 'SamplingClient':
+        """Save the current adapter for the sampler and return a client that samples from exactly those weights."""
+        r = self.save_weights_for_sampler(name or f'sampler-{uuid.uuid4().hex[:8]}').result()
+        info = self.get_info()
+        base = (info.get('model_data') or {}).get('model_name') or info.get('base_model') or info.get('model_name')
+        return SamplingClient(self.t, base, r['path'], self.session_id)
 
     def get_info(self):
         return self.t.post('/get_info', {'model_id': self.model_id}, model_id=self.model_id)
@@ -338,6 +346,46 @@ class TinkerClient:
 
     def create_sampling_client(self, base_model: str, model_path: Optional[str] = None) -> SamplingClient:
         return SamplingClient(self.t, base_model, model_path, self.session_id)
+
+    def create_training_client_from_state(self, path: str, with_optimizer: bool = False, base_model: Optional[str] = None, **kw) -> TrainingClient:
+        """A new training client that starts from a saved checkpoint (``twinkle://…/weights/<name>``): base model and
+        LoRA rank are read from the checkpoint, the adapter weights are loaded, and with ``with_optimizer`` the optimizer
+        and scheduler state too, so training continues as if it had not stopped."""
+        info = self.t.post('/weights_info', {'tinker_path': path})
+        base = base_model or info.get('base_model')
+        if not base:
+            raise ValueError(f'{path}: the checkpoint does not name its base model; pass base_model=')
+        tc = self.create_lora_training_client(base, rank=int(info.get('lora_rank') or kw.pop('rank', 8)), **kw)
+        tc._post('load_weights', path=path, optimizer=with_optimizer).result()
+        return tc
+
+    def create_training_client_from_state_with_optimizer(self, path: str, **kw) -> TrainingClient:
+        return self.create_training_client_from_state(path, with_optimizer=True, **kw)
+
+    def create_rest_client(self) -> 'RestClient':
+        return RestClient(self.t)
+
+
+class RestClient:
+    """Read-only bookkeeping calls of the Tinker protocol: training runs, their checkpoints, checkpoint details."""
+
+    def __init__(self, transport: Transport):
+        self.t = transport
+
+    def list_training_runs(self) -> List[Dict[str, Any]]:
+        return self.t.get('/training_runs')['training_runs']
+
+    def get_training_run(self, run_id: str) -> Dict[str, Any]:
+        return self.t.get(f'/training_runs/{run_id}')
+
+    def list_checkpoints(self, run_id: str) -> List[Dict[str, Any]]:
+        return self.t.get(f'/training_runs/{run_id}/checkpoints')['checkpoints']
+
+    def delete_checkpoint(self, run_id: str, checkpoint_id: str):
+        return self.t.request('DELETE', f'/training_runs/{run_id}/checkpoints/{checkpoint_id}')
+
+    def get_weights_info(self, path: str) -> Dict[str, Any]:
+        return self.t.post('/weights_info', {'tinker_path': path})
 
 
 def init_tinker_client(base_url: Optional[str] = None, token: Optional[str] = None, **kw) -> TinkerClient:

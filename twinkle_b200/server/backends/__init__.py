@@ -84,15 +84,25 @@ def split_loss_inputs(features: List[Dict[str, Any]]) -> Dict[str, Any]:
     return kw
 
 
+FORWARD_OPTIONS = ('disable_lora', )  # keys of ``loss_fn_config`` that steer the forward pass, not the loss
+
+
+def forward_options(loss_fn_config: Optional[Dict[str, Any]]) -> Dict[str, Any]:
+    """``{'disable_lora': True}`` runs the frozen base model: how a client gets reference log-probs for DPO from the same
+    server-side model (reference ``server/model/backends/common.py:120-150``)."""
+    return {k: bool(v) for k, v in (loss_fn_config or {}).items() if k in FORWARD_OPTIONS}
+
+
 def choose_loss(loss_fn: str, features: List[Dict[str, Any]], loss_fn_config: Optional[Dict[str, Any]] = None):
     from ...loss import CrossEntropyLoss, DPOLoss, GRPOLoss, torch_loss_mapping
-    cfg = dict(loss_fn_config or {})
+    cfg = {k: v for k, v in (loss_fn_config or {}).items() if k not in FORWARD_OPTIONS}
     if loss_fn == 'cross_entropy':
         return CrossEntropyLoss(**cfg)
     if loss_fn in ('importance_sampling', 'ppo'):
         if any('ref_logps' in f for f in features):
-            return DPOLoss(**cfg)
-        return GRPOLoss(**cfg)
+            # the wire names carry a dpo_ prefix (dpo_beta, dpo_loss_type, dpo_sft_weight); plain names are accepted too
+            return DPOLoss(**{(k[4:] if k.startswith('dpo_') else k): v for k, v in cfg.items()})
+        return GRPOLoss(**{k: v for k, v in cfg.items() if not k.startswith('dpo_')})
     if loss_fn in torch_loss_mapping:
         return torch_loss_mapping[loss_fn](**cfg)
     raise ValueError(f'unknown loss_fn {loss_fn!r}')

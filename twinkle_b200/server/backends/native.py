@@ -8,7 +8,7 @@ from __future__ import annotations
 
 from typing import Any, Dict, List, Optional
 
-from . import build_fwdbwd_output, choose_loss, clean_metrics, datum_to_input_feature, split_loss_inputs
+from . import build_fwdbwd_output, choose_loss, clean_metrics, datum_to_input_feature, forward_options, split_loss_inputs
 
 
 class NativeModelBackend:
@@ -38,15 +38,29 @@ class NativeModelBackend:
                                 loss_fn_config: Optional[Dict[str, Any]] = None) -> Dict[str, Any]:
         feats = [datum_to_input_feature(d) for d in datums]
         self.model.check_length(feats)
-        self.model.set_loss(choose_loss(loss_fn, feats, loss_fn_config), adapter_name=adapter_name)
+        loss = choose_loss(loss_fn, feats, loss_fn_config)
+        self.model.set_loss(loss, adapter_name=adapter_name)
+        if type(loss).__name__ == 'DPOLoss':
+            self._ensure_metric(adapter_name, 'DPOMetric')      # reward margins / accuracies come back with the step's metrics
         kw = split_loss_inputs(feats)
+        opts = forward_options(loss_fn_config)
         clean = [{k: v for k, v in f.items() if k in ('input_ids', 'labels', 'position_ids')} for f in feats]
         if backward:
-            out = self.model.forward_backward(inputs=clean, adapter_name=adapter_name, **kw)
+            out = self.model.forward_backward(inputs=clean, adapter_name=adapter_name, **opts, **kw)
         else:
-            out = self.model.forward_only(inputs=clean, adapter_name=adapter_name)
+            out = self.model.forward_only(inputs=clean, adapter_name=adapter_name, **opts)
         metrics = self.model.calculate_metric(True, adapter_name=adapter_name) if backward else {}
+        if backward:
+            # calculating drains the accumulators; the step that follows reports the same window (loss statistics such as
+            # the DPO reward margins) together with its own gradient norm
+            self._window_metrics = getattr(self, '_window_metrics', {})
+            self._window_metrics[adapter_name] = clean_metrics(metrics)
         return build_fwdbwd_output(clean, out, metrics)
+
+    def _ensure_metric(self, adapter_name: str, metric: str) -> None:
+        og = self.model._group(adapter_name)
+        if not any(type(m).__name__ == metric for m in og.train_status.metrics):
+            self.model.add_metric(metric, is_training=True, adapter_name=adapter_name)
 
     def tinker_step(self, adapter_name: str, adam_params: Optional[Dict[str, Any]] = None) -> Dict[str, Any]:
         og = self.model._group(adapter_name)
@@ -60,7 +74,8 @@ class NativeModelBackend:
         self.model.step(adapter_name=adapter_name, optim_params=optim)
         self.model.zero_grad(adapter_name=adapter_name)
         self.model.lr_step(adapter_name=adapter_name)
-        return {'metrics': {'grad_norm': float(norm), **clean_metrics(self.model.calculate_metric(True, adapter_name=adapter_name))}}
+        window = getattr(self, '_window_metrics', {}).pop(adapter_name, {})
+        return {'metrics': {**window, 'grad_norm': float(norm), **clean_metrics(self.model.calculate_metric(True, adapter_name=adapter_name))}}
 
     def save(self, name: str, output_dir: str, adapter_name: Optional[str] = None, **kw) -> str:
         return self.model.save(name, output_dir, adapter_name=adapter_name, **kw)

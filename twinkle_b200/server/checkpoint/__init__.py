@@ -151,7 +151,7 @@ class CheckpointManager:
         m = os.path.join(d, 'metadata.json')
         if os.path.isfile(m):
             with open(m) as f:
-                info.update({k: v for k, v in json.load(f).items() if k not in info})
+                info.update({k: v for k, v in json.load(f).items() if info.get(k) is None})
         return info
 
     parse_adapter_uri = staticmethod(parse_uri)
