@@ -70,10 +70,23 @@ class _Tenant:
 
 class MultiLora:
 
-    def __init__(self, model: DecoderModel, max_loras: int = 5, max_r: int = 32, expert_lora: bool = True):
+    def __init__(self, model: DecoderModel, max_loras: int = 5, max_r: int = 32, expert_lora: bool = True, seed: Optional[int] = None):
+        """``seed``: the pool's ``A`` matrices are drawn from their own random stream, so two models built with the same
+        seed hold the same pool whatever else consumed random numbers before (and the caller's stream is left alone)."""
         self.model, self.max_loras, self.max_r = model, max_loras, max_r
         self.tenants: Dict[str, _Tenant] = {}
         self.modules: List[Tuple[str, Any]] = []
+        dev = next(model.parameters()).device
+        with torch.random.fork_rng(devices=[dev] if dev.type == 'cuda' else [], enabled=seed is not None):
+            if seed is not None:
+                torch.manual_seed(0x10A5EED + int(seed))
+            self._build_pools(model, max_loras, max_r, expert_lora)
+        # base weights are frozen once a pool exists; only pool tensors train
+        for n, p in model.named_parameters():
+            p.requires_grad_('lora' in n)
+        self._initial_A: Dict[str, torch.Tensor] = {n: p.detach().clone() for n, p in self.pool_parameters() if self._is_A(n)}
+
+    def _build_pools(self, model, max_loras: int, max_r: int, expert_lora: bool) -> None:
         for name, m in model.lora_modules():
             if isinstance(m, Linear):
                 if name == 'lm_head' or name.endswith('.gate'):
@@ -83,10 +96,6 @@ class MultiLora:
             elif isinstance(m, Experts) and expert_lora:
                 m.add_lora_pool(max_loras, max_r)
                 self.modules.append((name, m))
-        # base weights are frozen once a pool exists; only pool tensors train
-        for n, p in model.named_parameters():
-            p.requires_grad_('lora' in n)
-        self._initial_A: Dict[str, torch.Tensor] = {n: p.detach().clone() for n, p in self.pool_parameters() if self._is_A(n)}
 
     def sync_initial(self, comm) -> None:
         """Make the saved initial ``A`` values (what a released slot is reset to) the first rank's on every rank of a

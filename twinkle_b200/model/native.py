@@ -773,7 +773,7 @@ class TransformersModel(TwinkleModel, CheckpointEngineMixin):
         cfg = LoraConfig.from_any(config_or_dir)
         if self.multi_lora is None:
             max_loras, max_r = self._pool_cfg
-            self.multi_lora = MultiLora(self.model, max_loras or 1, max_r or cfg.r)
+            self.multi_lora = MultiLora(self.model, max_loras or 1, max_r or cfg.r, seed=self.seed)
         self.multi_lora.acquire_lora(adapter_name, cfg)
         og = OptimizerGroup(adapter_name=adapter_name, adapter_config=cfg,
                             gradient_accumulation_steps=kwargs.get('gradient_accumulation_steps', 1))
@@ -1034,7 +1034,7 @@ class MultiLoraTransformersModel(TransformersModel):
                  max_r: int = 32, max_length: int = 8192, **kwargs):
         super().__init__(model_id=model_id, config=config, device_mesh=device_mesh, max_loras=max_loras, max_r=max_r, **kwargs)
         self.max_length = max_length
-        self.multi_lora = MultiLora(self.model, max_loras, max_r)
+        self.multi_lora = MultiLora(self.model, max_loras, max_r, seed=self.seed)
 
     def _group(self, adapter_name: Optional[str]) -> OptimizerGroup:
         if not adapter_name:
