@@ -2,6 +2,11 @@
 and condensing, a confidence-routed sampler, answer-overlap rewards and trajectory quality filters
 (reference package ``twinkle_agentic``)."""
 from .context import (Chunk, Chunker, Chunks, Condenser, ExtractCondensed, KeywordCondenser, MultiTurnCondenseRollout, NativeChunker)
+from .preprocess import (ChrMinScorer, CodeDetector, ComplexLogicDetector, FixUnicodeFilter, IntentClassifier, IntentDetector, LLMBackend,
+                         MathDetector, MessageNormalizer, ModelFilter, OpenAIBackend, ParaphraseScorer, PassNScorer, QualityPreprocessor,
+                         ReasoningDetector, RemoveRepeatSentencesFilter, RoundContext, RoundScoreFilter, SamplerBackend, ScoreResult,
+                         SIFDScorer, SpecialCharsFilter, TokenNumFilter, ToolCallDetector, UserDissatisfactionDetector,
+                         chr_min_distinct, count_tokens, ifd_family, special_char_ratio)
 from .quality import (CoTReward, DeadLoopFilter, DedupFilter, F1Reward, HardFilter, MessageSanityFilter, PIIFilter, RefuseFilter,
                       RouterSampler, ScoreFilter, TokenSoupFilter, ToolExploreReward, f1_score, normalize_messages)
 from .rollout import (APIMultiTurnRollout, ChatAPI, MultiTurnRollout, OpenAIChatAPI, Rollout, extend_with_bridge, parse_tool_calls,
