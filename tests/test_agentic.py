@@ -181,3 +181,48 @@ def test_tool_call_formats_round_trip():
     nested = vcp.render({'tool_name': 'echo', 'arguments': {'text': 'has 「末」 inside'}})
     assert vcp.parse(nested)[0]['arguments']['text'] == 'has 「末」 inside'
     assert '<tool_call>' in tools_system_prompt([{'tool_name': 'x', 'description': 'd', 'parameters': {}}])
+
+
+def test_model_condenser_batches_pads_and_rejects_useless_replies():
+    from twinkle_b200.agentic import Chunk, Chunks, ModelCondenser
+    from twinkle_b200.data_format import SampledSequence, SampleResponse
+
+    class S:
+        template = None
+
+        def __init__(self):
+            self.calls = []
+
+        def sample(self, trajs, params, **kw):
+            self.calls.append((len(trajs), params.max_tokens, kw))
+            out = []
+            for t in trajs:
+                text = t['messages'][1]['content']
+                if 'KEEPME' in text:
+                    reply = 'x' * 5000  # longer than the passage → rejected
+                elif 'FENCE' in text:
+                    reply = '```\nshort fenced digest\n```'
+                else:
+                    reply = 'digest of ' + text.split('Question the reader cares about: ')[1].split('\n')[0]
+                out.append(SampleResponse(sequences=[SampledSequence('stop', [1], decoded=reply)]))
+            return out
+
+    long = lambda tag: tag + ' ' + 'lorem ipsum ' * 80  # noqa: E731
+    chunks = Chunks([Chunk('user', 'Question: who?', 0), Chunk('tool', long('A'), 1), Chunk('tool', long('KEEPME'), 2), Chunk('tool', long('FENCE'), 3),
+                     Chunk('tool', 'short', 4), Chunk('tool', long('SKIP: raw'), 5), Chunk('assistant', long('B'), 6)], {'messages': []})
+    s = S()
+    cond = ModelCondenser(s, compression_ratio=4.0, batch_size=2, skip_pattern=r'^SKIP:',
+                          related_query=lambda c: c.content[len('Question: '):] if c.content.startswith('Question: ') else None)
+    out = list(cond(chunks))
+    assert [c.condensed for c in out] == [False, True, False, True, False, False, False]
+    assert out[1].content == 'digest of who?' and out[1].original.startswith('A lorem') and out[1].block == 1
+    assert out[3].content == 'short fenced digest' and out[3].block == 2
+    assert [c[0] for c in s.calls] == [2, 2] and s.calls[0][2] == {'use_base_model': True}  # 3 jobs → one full batch + one padded
+    assert s.calls[0][1] >= 32
+    assert list(cond(Chunks(out, {'messages': []})))[1].content == 'digest of who?'  # idempotent on condensed chunks
+    assert ModelCondenser(s, lora_path='/x')._ask([{'text': 't', 'budget': 10, 'query': 'q'}]) and s.calls[-1][2] == {'adapter_path': '/x'}
+    import pytest
+    with pytest.raises(ValueError):
+        ModelCondenser(s, compression_ratio=1.0)
+    with pytest.raises(ValueError):
+        ModelCondenser(s, user_prompt_template='no slots')

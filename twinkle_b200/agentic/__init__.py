@@ -1,7 +1,8 @@
 """Agentic training support: tools and environments, multi-turn rollouts (sampler- or API-driven), context chunking
 and condensing, a confidence-routed sampler, answer-overlap rewards and trajectory quality filters
 (reference package ``twinkle_agentic``)."""
-from .context import (Chunk, Chunker, Chunks, Condenser, ExtractCondensed, KeywordCondenser, MultiTurnCondenseRollout, NativeChunker)
+from .context import (Chunk, Chunker, Chunks, Condenser, ExtractCondensed, KeywordCondenser, ModelCondenser, MultiTurnCondenseRollout,
+                      NativeChunker)
 from .preprocess import (ChrMinScorer, CodeDetector, ComplexLogicDetector, FixUnicodeFilter, IntentClassifier, IntentDetector, LLMBackend,
                          MathDetector, MessageNormalizer, ModelFilter, OpenAIBackend, ParaphraseScorer, PassNScorer, QualityPreprocessor,
                          ReasoningDetector, RemoveRepeatSentencesFilter, RoundContext, RoundScoreFilter, SamplerBackend, ScoreResult,

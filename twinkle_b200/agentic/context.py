@@ -170,6 +170,109 @@ class KeywordCondenser(Condenser):
         return digest
 
 
+_CONDENSE_SYSTEM = ('You compress passages for a reader who must still answer questions from them. Keep names, numbers, dates, '
+                    'identifiers and causal links; drop filler. Output the compressed passage only.')
+_CONDENSE_USER = 'Question the reader cares about: {query}\n\nCompress the passage below to at most about {budget} characters.\n\n{text}'
+_FENCED = re.compile(r'^```[\w-]*\n([\s\S]*?)\n?```$')
+
+
+class ModelCondenser(Condenser):
+    """Condenses chunks by asking a language model (through a sampler of this framework) for a shorter restatement.
+
+    A chunk is sent when its role is condensable, it is at least ``min_chars`` long, not among the newest ``keep_last``
+    chunks, not already condensed and does not match ``skip_pattern``. ``compression_ratio`` sets the character budget
+    named in the prompt (never below ``min_budget_chars``) and the token limit of the request; the model's text is not
+    cut to the budget, but a reply that is empty, has no letters or digits, or is not strictly shorter than the
+    passage is discarded and the passage kept. ``related_query(chunk)`` marks chunks that carry the question; the most
+    recent one is put in the prompts of the chunks that follow. Requests go out in batches of ``batch_size`` (the last
+    batch padded with a repeat so data-parallel samplers get a full batch). By default the base model answers
+    (``use_base_model=True`` is passed to the sampler so a policy adapter under training is bypassed); ``lora_path``
+    selects a dedicated adapter instead.
+
+    Parity: reference ``src/twinkle_agentic/condenser/model.py:104-455``."""
+
+    def __init__(self, sampler, compression_ratio: float = 3.0, sampling_params=None, system_prompt: str = _CONDENSE_SYSTEM,
+                 user_prompt_template: str = _CONDENSE_USER, min_chars: int = 600, min_budget_chars: int = 120, keep_last: int = 0,
+                 roles: Sequence[str] = ('tool', ), skip_pattern: Optional[str] = None, related_query=None, batch_size: int = 8,
+                 lora_path: Optional[str] = None, template=None, chars_per_token: float = 3.0):
+        if compression_ratio <= 1:
+            raise ValueError('compression_ratio must be > 1')
+        if '{text}' not in user_prompt_template or '{budget}' not in user_prompt_template:
+            raise ValueError('user_prompt_template needs {budget} and {text}')
+        self.sampler, self.ratio, self.sampling_params = sampler, float(compression_ratio), sampling_params
+        self.system_prompt, self.user_prompt_template = system_prompt, user_prompt_template
+        self.min_chars, self.min_budget, self.keep_last, self.roles = min_chars, min_budget_chars, keep_last, set(roles)
+        self.skip_re = re.compile(skip_pattern, re.M) if skip_pattern else None
+        self.related_query, self.batch_size, self.lora_path = related_query, max(1, batch_size), lora_path
+        self.template, self.chars_per_token = template if template is not None else getattr(sampler, 'template', None), chars_per_token
+
+    def eligible(self, c: Chunk, index: int, total: int) -> bool:
+        if c.condensed or c.role not in self.roles or len(c.content) < self.min_chars or index >= total - self.keep_last:
+            return False
+        return not (self.skip_re and self.skip_re.search(c.content))
+
+    def budget(self, text: str) -> int:
+        return max(self.min_budget, math.ceil(len(text) / self.ratio))
+
+    def _special_tokens(self) -> Sequence[str]:
+        tok = getattr(self.template, 'tokenizer', None)
+        return tuple(t for t in (getattr(tok, 'all_special_tokens', None) or ()) if isinstance(t, str) and t)
+
+    def clean(self, reply: str, original: str) -> Optional[str]:
+        text = (reply or '').strip()
+        m = _FENCED.match(text)
+        if m:
+            text = m.group(1).strip()
+        for t in self._special_tokens():
+            text = text.replace(t, '')
+        text = text.strip()
+        if not text or not any(ch.isalnum() for ch in text) or len(text) >= len(original):
+            return None
+        return text
+
+    def _ask(self, jobs: List[Dict[str, Any]]) -> List[str]:
+        from ..data_format import SamplingParams
+        trajs = [{'messages': [{'role': 'system', 'content': self.system_prompt},
+                               {'role': 'user', 'content': self.user_prompt_template.format(budget=j['budget'], text=j['text'], query=j['query'])}]}
+                 for j in jobs]
+        params = self.sampling_params or SamplingParams(temperature=0.0, max_tokens=max(32, int(max(j['budget'] for j in jobs) / self.chars_per_token * 1.5)))
+        kw = {'adapter_path': self.lora_path} if self.lora_path else {'use_base_model': True}
+        out: List[str] = []
+        for i in range(0, len(trajs), self.batch_size):
+            batch = trajs[i:i + self.batch_size]
+            real = len(batch)
+            batch = batch + [batch[-1]] * (self.batch_size - real if len(trajs) > self.batch_size else 0)
+            resps = self.sampler.sample(batch, params, **kw)
+            for r in list(resps)[:real]:
+                seqs = getattr(r, 'sequences', None) if not isinstance(r, dict) else r.get('sequences')
+                seq = seqs[0] if seqs else None
+                out.append(((getattr(seq, 'decoded', None) if not isinstance(seq, dict) else seq.get('decoded')) or '') if seq is not None else '')
+        return out
+
+    def __call__(self, chunks: Chunks, **kwargs) -> Chunks:
+        items = list(chunks)
+        jobs, query = [], None
+        for i, c in enumerate(items):
+            if self.related_query is not None:
+                q = self.related_query(c)
+                if q:
+                    query = q
+            if self.eligible(c, i, len(items)):
+                jobs.append({'index': i, 'text': c.content, 'budget': self.budget(c.content), 'query': query or '(not stated)'})
+        if not jobs:
+            return chunks
+        replies = self._ask(jobs)
+        next_block = 1 + max([c.block or 0 for c in items] + [0])
+        for j, reply in zip(jobs, replies):
+            c = items[j['index']]
+            text = self.clean(reply, c.content)
+            if text is None:
+                continue
+            items[j['index']] = Chunk(c.role, text, c.message_index, c.tool_call_id, True, c.content, next_block, dict(c.extra))
+            next_block += 1
+        return Chunks(items, chunks.trajectory)
+
+
 class ExtractCondensed(Tool):
     """Tool through which the policy gets the original text of condensed blocks back."""
 

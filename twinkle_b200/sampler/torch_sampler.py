@@ -138,7 +138,9 @@ class TorchSampler(Sampler, CheckpointEngineMixin):
             sp.seed = self.seed
         feats = self._prompts(inputs)
         prompts = [[int(t) for t in f['input_ids']] for f in feats]
-        name = self._resolve_adapter(adapter_name, adapter_path) if self.multi_lora is not None else None
+        # ``use_base_model=True`` bypasses every adapter, the synced policy adapter included (a condenser or judge that shares
+        # the sampler with the policy under training must not see half-trained weights)
+        name = self._resolve_adapter(adapter_name, adapter_path) if self.multi_lora is not None and not kwargs.get('use_base_model') else None
         lora = None
         if name is not None:
             t = self.multi_lora.tenants[name]
