@@ -226,3 +226,75 @@ def test_model_condenser_batches_pads_and_rejects_useless_replies():
         ModelCondenser(s, compression_ratio=1.0)
     with pytest.raises(ValueError):
         ModelCondenser(s, user_prompt_template='no slots')
+
+
+class _Obs:
+
+    def __init__(self, observation, reward=0.0, done=False):
+        self.observation, self.reward, self.done = observation, reward, done
+
+
+class CounterEnvironment:
+    """OpenEnv-style environment: counts up by the action's ``by`` and ends at ``limit``."""
+
+    def __init__(self, limit=3):
+        self.limit, self.n = limit, 0
+
+    def reset(self):
+        self.n = 0
+        return _Obs({'text': 'n=0'})
+
+    def step(self, action):
+        by = action.by if hasattr(action, 'by') else action['by']
+        self.n += by
+        return {'observation': f'n={self.n}', 'reward': float(by), 'done': self.n >= self.limit}
+
+
+class CounterAction:
+
+    def __init__(self, by=1):
+        self.by = by
+
+
+def test_openenv_adapter_and_sharded_pool(monkeypatch):
+    from twinkle_b200.agentic import EnvPoolAdapter, EnvTool, OpenEnv, ShardedEnvPool, ToolManager, normalize_result, observation_text
+    env = OpenEnv(env_cls=f'{__name__}:CounterEnvironment', env_kwargs={'limit': 2}, action_cls=CounterAction)
+    assert env.reset().observation == 'n=0'
+    r = env.step('act', {'by': 2})
+    assert (r.observation, r.reward, r.done) == ('n=2', 2.0, True)
+    mapped = OpenEnv(env_cls=CounterEnvironment, action_mapper=lambda name, args: {'by': 5 if name == 'jump' else 1})
+    assert mapped.step('jump', {}).observation == 'n=5' and mapped.tools()[0]['tool_name'] == 'act'
+    assert observation_text({'foo': 1}) == '{"foo": 1}' and observation_text(None) == '' and normalize_result('plain')['observation'] == 'plain'
+    import pytest
+    with pytest.raises(ValueError):
+        OpenEnv()
+    with pytest.raises(ValueError):
+        OpenEnv(env_cls='NoDots')
+
+    # two "workers" built by hand: rank 0 owns slots 0-1, rank 1 owns slot 2
+    pools = []
+    for rank in (0, 1):
+        monkeypatch.setenv('RANK', str(rank))
+        monkeypatch.setenv('WORLD_SIZE', '2')
+        pools.append(ShardedEnvPool(pool_size=3, env_kwargs={'env_cls': CounterEnvironment, 'env_kwargs': {'limit': 2}}))
+    assert [(p._start, p._end) for p in pools] == [(0, 2), (2, 3)]
+    assert pools[0].reset(2) is None and pools[1].reset(2)['observation'] == 'n=0'
+    parts = [p.step_batch([0, 1, 2], ['act'] * 3, [{'by': 1}, {'by': 2}, {'by': 1}]) for p in pools]
+    from twinkle_b200.agentic.openenv import _merge_by_slot
+    merged = _merge_by_slot(parts)
+    assert [m['observation'] for m in merged] == ['n=1', 'n=2', 'n=1'] and [m['done'] for m in merged] == [False, True, False]
+    assert pools[0].step(0, 'act', {'by': 1})['episode_reward'] == 2.0
+
+    monkeypatch.setenv('RANK', '0')
+    monkeypatch.setenv('WORLD_SIZE', '1')
+    pool = ShardedEnvPool(pool_size=2, env_kwargs={'env_cls': CounterEnvironment})
+    a, b = pool.get_adapters(2)
+    assert isinstance(a, EnvPoolAdapter) and a.reset().observation == 'n=0'
+    assert a.step('act', {'by': 2}).info == {'episode_reward': 2.0} and a.episode_reward == 2.0 and b.episode_reward == 0.0
+    bad = a.step('act', {'nope': 1})
+    assert bad.done and bad.observation.startswith('Error:')
+    tm = ToolManager(EnvTool.from_env(b))
+    assert tm({'tool_name': 'act', 'arguments': {'by': 1}}) == 'n=1'
+    with pytest.raises(ValueError):
+        pool.get_adapters(3)
+    pool.close()
