@@ -298,3 +298,60 @@ def test_openenv_adapter_and_sharded_pool(monkeypatch):
     with pytest.raises(ValueError):
         pool.get_adapters(3)
     pool.close()
+
+
+def test_client_multi_turn_rollout_token_exact_state():
+    import pytest
+    from twinkle_b200.agentic import FunctionTool, ToolManager
+    from twinkle_b200.client import ClientMultiTurnRollout
+    from twinkle_b200.template import Template
+    tpl = Template(model_id=None)
+
+    def add(a: int, b: int) -> int:
+        """Add two integers."""
+        return a + b
+
+    class HttpLikeSampler:
+        """Answers like the JSON of ``/twinkle/sample``: first a tool call, then a final answer; one trajectory runs
+        into the length limit at once."""
+
+        def __init__(self):
+            self.batches = []
+
+        def sample(self, feats, sp):
+            self.batches.append(len(feats))
+            out = []
+            for f in feats:
+                text_so_far = tpl.decode(f['input_ids'], skip_special_tokens=False)
+                if 'LONG' in text_so_far:
+                    reply, reason = 'cut off', 'length'
+                elif 'tool_response' in text_so_far or '"role": "tool"' in text_so_far or '5' in text_so_far.split('add')[-1]:
+                    reply, reason = 'The sum is 5.', 'stop'
+                else:
+                    reply, reason = '<tool_call>\n{"name": "add", "arguments": {"a": 2, "b": 3}}\n</tool_call>', 'stop'
+                toks = tpl.tokenizer.encode(reply)
+                out.append({'sequences': [{'stop_reason': reason, 'tokens': toks, 'logprobs': [-0.1] * len(toks), 'decoded': reply,
+                                           'new_input_feature': Template.concat_input_feature(f, toks)}]})
+            return out
+
+    s = HttpLikeSampler()
+    roll = ClientMultiTurnRollout(s, tpl, ToolManager([FunctionTool(add)]), {'max_tokens': 64}, max_turns=3)
+    res = roll([{'messages': [{'role': 'user', 'content': 'what is 2+3? use add'}]}, {'messages': [{'role': 'user', 'content': 'LONG one'}]}])
+    assert s.batches == [2, 1]  # the finished trajectory is left out of the second call
+    a, b = res
+    assert [m['role'] for m in a['messages']] == ['user', 'assistant', 'tool', 'assistant'] and a['messages'][2]['content'] == '5'
+    assert a['turns'] == 2 and a['stop_reason'] == 'stop' and not a['truncated']
+    assert b['turns'] == 1 and b['stop_reason'] == 'length'
+    labels = a['input_feature']['labels']
+    assert sum(1 for x in labels if x != -100) == len(a['logprobs']) and len(labels) == len(a['input_feature']['input_ids'])
+    # a single allowed turn that ends in a tool call is a truncation
+    one = ClientMultiTurnRollout(HttpLikeSampler(), tpl, ToolManager([FunctionTool(add)]), {'max_tokens': 64}, max_turns=1)(
+        [{'messages': [{'role': 'user', 'content': 'use add'}]}])[0]
+    assert one['truncated'] and one['stop_reason'] == 'max_turns' and one['messages'][-1]['role'] == 'assistant'
+    with pytest.raises(ValueError):
+        ClientMultiTurnRollout(HttpLikeSampler(), tpl, None, {'max_tokens': 8})([{'messages': [{'role': 'user', 'content': 'use add'}]}])
+    with pytest.raises(TypeError):
+        roll({'messages': []})
+    with pytest.raises(ValueError):
+        ClientMultiTurnRollout(s, tpl, sampling_params={'num_samples': 2})
+    assert roll([]) == []

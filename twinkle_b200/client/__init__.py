@@ -181,8 +181,9 @@ class TorchSampler:
     def sample(self, inputs, sampling_params=None, adapter_name=None, adapter_path=None, **kw):
         sp = sampling_params.to_dict() if hasattr(sampling_params, 'to_dict') else sampling_params
         r = self.c.t.post(self.prefix + '/twinkle/sample', {'inputs': _wire(inputs), 'sampling_params': sp, 'adapter_name': adapter_name,
-                                                             'adapter_path': adapter_path})
-        return r['result']
+                                                             'adapter_path': adapter_path, **kw})
+        from ..data_format import SampleResponse
+        return [SampleResponse.from_dict(x) if isinstance(x, dict) and 'sequences' in x else x for x in r['result']]
 
 
 vLLMSampler = TorchSampler
@@ -386,6 +387,118 @@ class RestClient:
 
     def get_weights_info(self, path: str) -> Dict[str, Any]:
         return self.t.post('/weights_info', {'tinker_path': path})
+
+
+class ClientMultiTurnRollout:
+    """Multi-turn tool-use rollout driven from the client: every round is ONE batched ``/twinkle/sample`` call for the
+    trajectories still running (``sampler`` is the HTTP twin above), tools run locally, and the token-level state
+    (``new_input_feature`` returned by the server, extended locally with the tool turns and the next generation
+    prompt) is what goes back — the conversation is never re-templated, so the sampled tokens and their log-probs stay
+    exactly those the policy produced. Needs a local ``template`` for the bridge tokens.
+
+    Returns the trajectories (same order) with ``messages`` extended and ``logprobs`` / ``turns`` / ``stop_reason`` /
+    ``truncated`` / ``input_feature`` set. Transport errors of the sampler propagate unchanged.
+
+    Parity: reference ``src/twinkle_client/rollout/multi_turn.py:30-291``."""
+
+    def __init__(self, sampler, template, tool_manager=None, sampling_params=None, max_turns: int = 6, max_trajectory_tokens: Optional[int] = None):
+        from ..data_format import SamplingParams
+        if template is None:
+            raise ValueError('a local Template is required')
+        if max_turns < 1:
+            raise ValueError(f'max_turns must be >= 1, got {max_turns}')
+        if max_trajectory_tokens is not None and max_trajectory_tokens < 1:
+            raise ValueError(f'max_trajectory_tokens must be >= 1 or None, got {max_trajectory_tokens}')
+        self.sampler, self.template, self.tool_manager = sampler, template, tool_manager
+        self.sampling_params = sampling_params or SamplingParams(max_tokens=512)
+        if isinstance(self.sampling_params, dict):
+            self.sampling_params = SamplingParams.from_dict(self.sampling_params)
+        if self.sampling_params.num_samples != 1:
+            raise ValueError('num_samples must be 1 in a multi-turn rollout')
+        self.max_turns, self.max_trajectory_tokens = max_turns, max_trajectory_tokens
+
+    def _managers(self, tm, n: int):
+        if tm is None:
+            return [None] * n
+        if isinstance(tm, (list, tuple)):
+            if len(tm) != n:
+                raise ValueError('one tool manager per trajectory is required')
+            return list(tm)
+        return [tm.copy() if hasattr(tm, 'copy') else tm for _ in range(n)]
+
+    def __call__(self, trajectories: List[Dict[str, Any]], **kwargs) -> List[Dict[str, Any]]:
+        from ..agentic.rollout import extend_with_bridge, parse_tool_calls, strip_tool_calls
+        if isinstance(trajectories, dict):
+            raise TypeError('expected a list of trajectories; wrap a single one as [trajectory]')
+        trajs = [dict(t, messages=[dict(m) for m in t.get('messages', [])]) for t in trajectories]
+        n = len(trajs)
+        if n == 0:
+            return []
+        managers = self._managers(kwargs.get('tool_manager', self.tool_manager), n)
+        sp = kwargs.get('sampling_params', self.sampling_params)
+        for t, m in zip(trajs, managers):
+            if m is not None and not t.get('tools'):
+                t['tools'] = m.tool_infos()
+        feats = [dict(self.template.encode(t, add_generation_prompt=True)) for t in trajs]
+        logprobs: List[List[float]] = [[] for _ in range(n)]
+        stop: List[Optional[str]] = [None] * n
+        turns, truncated, done = [0] * n, [False] * n, [False] * n
+        for _ in range(self.max_turns):
+            live = [i for i in range(n) if not done[i]]
+            if not live:
+                break
+            resps = self.sampler.sample([feats[i] for i in live], sp)
+            for k, i in enumerate(live):
+                turns[i] += 1
+                seq = resps[k]['sequences'][0]
+                nf = seq.get('new_input_feature')
+                if not nf or 'input_ids' not in nf:
+                    raise RuntimeError(f'sampler returned no new_input_feature.input_ids at batch index {k} (trajectory {i})')
+                feats[i] = dict(nf)
+                lp, toks = seq.get('logprobs'), seq.get('tokens') or []
+                if lp is not None:
+                    if len(lp) != len(toks):
+                        raise RuntimeError(f'{len(lp)} logprobs for {len(toks)} sampled tokens at turn {turns[i]} (trajectory {i})')
+                    logprobs[i].extend(lp)
+                stop[i] = seq.get('stop_reason')
+                text = seq.get('decoded')
+                if text is None:
+                    text = self.template.decode(toks)
+                calls = parse_tool_calls(text)
+                msg: Dict[str, Any] = {'role': 'assistant', 'content': strip_tool_calls(text) if calls else text}
+                if calls:
+                    msg['tool_calls'] = calls
+                before = list(trajs[i]['messages'])
+                trajs[i]['messages'].append(msg)
+                if stop[i] == 'length':
+                    done[i] = True
+                    continue
+                if self.max_trajectory_tokens is not None and len(feats[i]['input_ids']) >= self.max_trajectory_tokens:
+                    truncated[i] = done[i] = True
+                    continue
+                if not calls:
+                    done[i] = True
+                    continue
+                if managers[i] is None:
+                    raise ValueError(f'trajectory {i} produced tool calls but no tool_manager was given')
+                if turns[i] >= self.max_turns:  # wants another tool round but has none left
+                    truncated[i], stop[i], done[i] = True, 'max_turns', True
+                    continue
+                tool_msgs = [{'role': 'tool', 'content': managers[i](c), 'tool_call_id': c.get('id', '')} for c in calls]
+                trajs[i]['messages'].extend(tool_msgs)
+                feats[i] = extend_with_bridge(self.template, feats[i], before + [msg], tool_msgs, tools=trajs[i].get('tools'))
+                if self.max_trajectory_tokens is not None and len(feats[i]['input_ids']) >= self.max_trajectory_tokens:
+                    truncated[i] = done[i] = True
+        out = []
+        for i, t in enumerate(trajs):
+            labels = feats[i].get('labels')
+            if labels is not None and logprobs[i]:
+                trained = sum(1 for x in labels if int(x) != -100)
+                if trained != len(logprobs[i]):
+                    raise RuntimeError(f'trajectory {i}: {len(logprobs[i])} logprobs for {trained} trained positions')
+            t.update(logprobs=logprobs[i], turns=turns[i], stop_reason=stop[i], truncated=truncated[i], input_feature=feats[i])
+            out.append(t)
+        return out
 
 
 def init_tinker_client(base_url: Optional[str] = None, token: Optional[str] = None, **kw) -> TinkerClient:

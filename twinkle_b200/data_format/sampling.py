@@ -52,6 +52,20 @@ class SamplingParams:
     def to_dict(self) -> Dict[str, Any]:
         return asdict(self)
 
+    def __getitem__(self, key: str):
+        return getattr(self, key)
+
+    def get(self, key: str, default=None):
+        return getattr(self, key, default)
+
+    @classmethod
+    def from_dict(cls, d: Union['SampleResponse', Dict[str, Any]]) -> 'SampleResponse':
+        """Rebuilds the record from its JSON form (what the sampler routes of the server return)."""
+        if isinstance(d, cls):
+            return d
+        seqs = [s if isinstance(s, SampledSequence) else SampledSequence.from_dict(s) for s in d.get('sequences') or []]
+        return cls(sequences=seqs, prompt_logprobs=d.get('prompt_logprobs'), topk_prompt_logprobs=d.get('topk_prompt_logprobs'))
+
     @classmethod
     def from_dict(cls, d: Optional[Dict[str, Any]]) -> 'SamplingParams':
         d = dict(d or {})
@@ -76,6 +90,16 @@ class SampledSequence:
     new_input_feature: Optional[Dict[str, Any]] = None
     routed_experts: Any = None
 
+    def __getitem__(self, key: str):  # records that crossed HTTP were dicts once; both spellings keep working
+        return getattr(self, key)
+
+    def get(self, key: str, default=None):
+        return getattr(self, key, default)
+
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> 'SampledSequence':
+        return cls(**{k: d.get(k) for k in ('stop_reason', 'tokens', 'logprobs', 'topk_logprobs', 'decoded', 'new_input_feature', 'routed_experts')})
+
 
 @dataclass
 class SampleResponse:
@@ -85,3 +109,17 @@ class SampleResponse:
 
     def to_dict(self) -> Dict[str, Any]:
         return asdict(self)
+
+    def __getitem__(self, key: str):
+        return getattr(self, key)
+
+    def get(self, key: str, default=None):
+        return getattr(self, key, default)
+
+    @classmethod
+    def from_dict(cls, d: Union['SampleResponse', Dict[str, Any]]) -> 'SampleResponse':
+        """Rebuilds the record from its JSON form (what the sampler routes of the server return)."""
+        if isinstance(d, cls):
+            return d
+        seqs = [s if isinstance(s, SampledSequence) else SampledSequence.from_dict(s) for s in d.get('sequences') or []]
+        return cls(sequences=seqs, prompt_logprobs=d.get('prompt_logprobs'), topk_prompt_logprobs=d.get('topk_prompt_logprobs'))

@@ -403,7 +403,8 @@ class SamplerApp(TaskQueueMixin):
             token = request.state.token
             path = self._adapter_path(token, b)
             res = await self.schedule_task_and_wait(lambda: self.backend.sample(b.get('inputs') or [], b.get('sampling_params'),
-                                                                                adapter_name=b.get('adapter_name'), adapter_path=path), token=token)
+                                                                                adapter_name=b.get('adapter_name'), adapter_path=path,
+                                                                                **({'use_base_model': True} if b.get('use_base_model') else {})), token=token)
             return {'status': 'ok', 'result': self._to_wire(res)}
 
         @app.post('/twinkle/sample_stream')

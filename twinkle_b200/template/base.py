@@ -285,12 +285,15 @@ class Template:
 
     @staticmethod
     def concat_input_feature(prompt: InputFeature, new_tokens: Sequence[int]) -> InputFeature:
-        """Prompt ⊕ sampled tokens; (rolled) labels only on the sampled part:
-        ``labels[t] = input_ids[t+1]`` for positions whose next token was sampled."""
-        p = list(prompt['input_ids'])
+        """Prompt ⊕ sampled tokens. (Rolled) labels are added on the sampled part — ``labels[t] = input_ids[t+1]`` for
+        positions whose next token was sampled — and the prompt keeps the labels it came with, so a feature that is
+        extended turn after turn in a multi-turn rollout ends up with every sampled token as a target."""
+        p = [int(t) for t in prompt['input_ids']]
         new = [int(t) for t in new_tokens]
         ids = p + new
-        labels = [IGNORE] * len(ids)
+        old = prompt.get('labels')
+        old = [int(x) for x in old] if old is not None and len(old) == len(p) else [IGNORE] * len(p)
+        labels = old + [IGNORE] * len(new)
         for t in range(len(p) - 1, len(ids) - 1):
             labels[t] = ids[t + 1]
         n = len(ids)
