@@ -178,3 +178,36 @@ def test_device_mesh_arithmetic():
     assert len(last) == 4
     with pytest.raises(Exception):
         DeviceMesh.from_sizes(fsdp_size=3, dp_size=None, ulysses_size=2).data_world_size
+
+
+def test_graded_math_and_multimodal_rewards():
+    import math
+    from twinkle_b200.preprocessor import CompetitionMathGRPOProcessor
+    from twinkle_b200.reward import (MultiModalAccuracyReward, OlympiadBenchAccuracyReward, OlympiadBenchFormatReward, OlympiadBenchQualityReward,
+                                     all_boxed, normalize_math_answer, reward_mapping, split_answers)
+    a = lambda c, **ud: {'messages': [{'role': 'assistant', 'content': c}], 'user_data': ud}  # noqa: E731
+    assert all_boxed('a \\boxed{\\frac{1}{2}} b \\boxed{x}') == ['\\frac{1}{2}', 'x']
+    assert normalize_math_answer('$\\dfrac{1}{2}$') == '0.5' and normalize_math_answer('1,000.50') == '1000.5' and normalize_math_answer('\\text{Yes}.') == 'yes'
+    assert split_answers('(1,2),(3,4), 5') == ['(1,2)', '(3,4)', '5']
+    acc = OlympiadBenchAccuracyReward()
+    got = acc([a('so \\boxed{\\frac{1}{2}}', ground_truth='0.5'), a('x \\boxed{10}', ground_truth='11'),
+               a('\\boxed{1}, \\boxed{(3,4)}', ground_truth='(3,4),2', is_multiple_answer=True), a('no box', ground_truth='1'),
+               a('\\boxed{7}', ground_truth=[('unused', 0)])])
+    assert got[0] == 1.0 and got[1] == pytest.approx(0.99 * math.exp(-5 / 11)) and got[2] == 0.5 and got[3] == 0.0
+    assert acc([{'messages': [{'role': 'assistant', 'content': '\\boxed{1,000}'}], 'user_data': [('ground_truth', '$1000$')]}]) == [1.0]  # pair-list user_data
+    assert acc([a('\\boxed{3}')], ground_truths=['the answer is \\boxed{3}']) == [1.0]
+    fmt = OlympiadBenchFormatReward()([a('\\boxed{3}'), a('\\boxed{1} \\boxed{2} \\boxed{3}'), a('\\boxed{1}' + 'x' * 300), a('nothing')])
+    assert fmt == [1.0, pytest.approx(0.4), 0.7, 0.0]
+    q = OlympiadBenchQualityReward()
+    txt = 'Step 1: x = 1 + 2 = 3. Then y = x * 2 = 6, z = y / 3 - 1 ^ 2. Therefore the answer is \\boxed{6}'
+    assert q.reasoning(txt) == 1.0 and q.reasoning('hello') == 0.0
+    assert [q.length(n) for n in (50, 200, 1000, 6000)] == [pytest.approx(0.15), pytest.approx(0.65), 1.0, 0.25] and q.length(3000) == pytest.approx(0.5)
+    assert q.non_repetition('ab ' * 100) < 0.2 and q.non_repetition('short') == 1.0
+    assert q([a(txt)])[0] == pytest.approx(0.4 + 0.3 * q.length(len(txt)) + 0.3 * q.non_repetition(txt))
+    mm = MultiModalAccuracyReward()([a('<think>..</think><answer> 3 </answer>', ground_truth='3'),
+                                     a('<answer>Yes</answer>', ground_truth='no', solution='<answer> yes </answer>'), a('3', ground_truth='3'),
+                                     a('<answer>3.0</answer>', ground_truth=3), a('<answer>4</answer>', ground_truth=3)])
+    assert mm == [1.0, 1.0, 0.0, 1.0, 0.0]
+    assert {'OlympiadBenchAccuracyReward', 'MultiModalAccuracyReward'} <= set(reward_mapping)
+    row = CompetitionMathGRPOProcessor()([{'problem': '1+1?', 'solution': 'It is \\boxed{2}.'}])[0]
+    assert [m['role'] for m in row['messages']] == ['system', 'user'] and row['user_data'] == {'solution': 'It is \\boxed{2}.', 'ground_truth': '2'}

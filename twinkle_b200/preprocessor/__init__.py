@@ -84,6 +84,17 @@ class CompetitionMathProcessor(Preprocessor):
         return _traj(row.get('problem', ''), row.get('solution'), 'Put the final answer in \\\\boxed{}.', user_data={'ground_truth': row.get('solution', '')})
 
 
+class CompetitionMathGRPOProcessor(Preprocessor):
+    """Prompt-only rows for RL on competition math: the policy is told to answer with the boxed result alone; the worked
+    solution travels in ``user_data`` (``solution`` and, extracted from its last ``\\boxed{}``, ``ground_truth``)."""
+
+    def preprocess(self, row):
+        from ..reward import extract_boxed
+        sol = row.get('solution', '')
+        return _traj(row.get('problem', ''), None, 'You are a helpful math assistant. Respond with only the final answer in the form '
+                     '\\boxed{...} and nothing else.', user_data={'solution': sol, 'ground_truth': extract_boxed(sol) or sol})
+
+
 class CountdownProcessor(Preprocessor):
 
     def preprocess(self, row):
@@ -125,6 +136,6 @@ class MaxLengthFilter(DataFilter):
         return sum(len(str(m.get('content', ''))) for m in row.get('messages', [])) <= self.max_chars
 
 
-preprocessor_mapping = {c.__name__: c for c in (AlpacaProcessor, SelfCognitionProcessor, GSM8KProcessor, GSM8KPromptProcessor,
+preprocessor_mapping = {c.__name__: c for c in (AlpacaProcessor, SelfCognitionProcessor, GSM8KProcessor, GSM8KPromptProcessor, CompetitionMathGRPOProcessor,
                                                 CompetitionMathProcessor, CountdownProcessor, EmojiDPOProcessor, CLEVRProcessor,
                                                 OlympiadBenchProcessor, MaxLengthFilter)}
