@@ -127,3 +127,36 @@ def test_bad_payloads_do_not_break_the_next_step():
                 assert torch.isfinite(p).all(), n
     finally:
         os.environ.pop('TWINKLE_FAIL_FAST', None)
+
+
+def test_exception_hierarchy_and_status_mapping(tmp_path):
+    import pytest
+    from twinkle_b200.server.backends import BackendSelector
+    from twinkle_b200.server.config import ServerConfig
+    from twinkle_b200.server.exceptions import (ConcurrencyError, ConfigError, ConfigParseError, ResourceExhaustedError, StateBackendError,
+                                                TwinkleServerError, status_code_of)
+    from twinkle_b200.server.queue import PreflightError
+    from twinkle_b200.server.state import MemoryBackend, ServerState
+    with pytest.raises(ConfigError) as ei:
+        BackendSelector.model('hf')
+    assert ei.value.field == 'backend' and ei.value.value == 'hf' and 'mock' in ei.value.allowed and "allowed: ['mock'" in str(ei.value)
+    assert isinstance(ei.value, ValueError) and status_code_of(ei.value) == 400
+    with pytest.raises(ConfigError):
+        BackendSelector.sampler('')
+    bad = tmp_path / 'bad.yaml'
+    bad.write_text('applications: [unclosed')
+    with pytest.raises(ConfigParseError):
+        ServerConfig.from_yaml(str(bad))
+    bad.write_text('- just\n- a list\n')
+    with pytest.raises(ConfigParseError):
+        ServerConfig.from_yaml(str(bad))
+    with pytest.raises(FileNotFoundError):
+        ServerConfig.from_yaml(str(tmp_path / 'missing.yaml'))
+    st = ServerState(MemoryBackend(), per_token_model_limit=1)
+    st.register_model('m1', 'tok', 'base', None)
+    with pytest.raises(ResourceExhaustedError) as ei:
+        st.register_model('m2', 'tok', 'base', None)
+    assert isinstance(ei.value, PermissionError) and status_code_of(ei.value) == 429
+    assert issubclass(ConcurrencyError, StateBackendError) and issubclass(PreflightError, TwinkleServerError)
+    assert [status_code_of(e) for e in (StateBackendError('x'), ConcurrencyError('x'), PreflightError('x', 413), KeyError('k'), TimeoutError(),
+                                        PermissionError(), TypeError(), RuntimeError())] == [503, 409, 413, 404, 504, 403, 400, 500]

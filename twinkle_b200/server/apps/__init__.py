@@ -26,6 +26,7 @@ from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 
 from ..backends import BackendSelector
 from ..checkpoint import CheckpointManager
+from ..exceptions import TwinkleServerError, status_code_of
 from ..queue import PreflightError, TaskQueueMixin
 from ..state import ServerState
 from ..telemetry import get_registry, get_tracer
@@ -70,9 +71,8 @@ def install_middleware(app: FastAPI, name: str, replica_id: str, require_request
                         resp = JSONResponse({'detail': str(e)}, status_code=e.status_code)
                     except HTTPException as e:
                         resp = JSONResponse({'detail': e.detail}, status_code=e.status_code)
-                    except (KeyError, ValueError, PermissionError, FileNotFoundError) as e:
-                        code = 404 if isinstance(e, (KeyError, FileNotFoundError)) else (403 if isinstance(e, PermissionError) else 400)
-                        resp = JSONResponse({'detail': f'{type(e).__name__}: {e}'}, status_code=code)
+                    except (TwinkleServerError, KeyError, ValueError, PermissionError, FileNotFoundError) as e:
+                        resp = JSONResponse({'detail': f'{type(e).__name__}: {e}'}, status_code=status_code_of(e))
                     except Exception as e:  # exception boundary: never leak a traceback, always answer
                         resp = JSONResponse({'detail': f'internal error: {type(e).__name__}: {e}'}, status_code=500)
                 status = resp.status_code

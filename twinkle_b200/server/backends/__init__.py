@@ -22,6 +22,7 @@ from typing import Any, Dict, List, Optional, Sequence
 import numpy as np
 
 from ...utils.seed import stable_seed
+from ..exceptions import ConfigError
 
 
 # ----------------------------------------------------------------- datum I/O
@@ -288,7 +289,7 @@ class BackendSelector:
     @staticmethod
     def model(kind: str, **kwargs):
         if kind not in BackendSelector.MODEL:
-            raise ValueError(f'unknown model backend {kind!r}; choose from {BackendSelector.MODEL}')
+            raise ConfigError('backend', kind, BackendSelector.MODEL)
         if kind == 'mock':
             return MockModel(**kwargs)
         from .native import NativeModelBackend
@@ -297,7 +298,7 @@ class BackendSelector:
     @staticmethod
     def sampler(kind: str, **kwargs):
         if kind not in BackendSelector.SAMPLER:
-            raise ValueError(f'unknown sampler type {kind!r}; choose from {BackendSelector.SAMPLER}')
+            raise ConfigError('sampler_type', kind, BackendSelector.SAMPLER)
         if kind == 'mock':
             return MockSampler(**kwargs)
         from ...sampler import TorchSampler

@@ -157,8 +157,15 @@ class ServerConfig(_Strict):
 
     @classmethod
     def from_yaml(cls, path: str) -> 'ServerConfig':
+        from ..exceptions import ConfigParseError
         with open(path) as f:
-            return cls(**(yaml.safe_load(f) or {}))
+            try:
+                doc = yaml.safe_load(f)
+            except yaml.YAMLError as e:
+                raise ConfigParseError(f'{path}: not valid YAML: {e}') from e
+        if doc is not None and not isinstance(doc, dict):
+            raise ConfigParseError(f'{path}: the top level must be a mapping, found {type(doc).__name__}')
+        return cls(**(doc or {}))
 
     @model_validator(mode='after')
     def _unique(self):

@@ -19,6 +19,7 @@ import uuid
 from dataclasses import dataclass, field
 from enum import Enum
 from typing import Any, Awaitable, Callable, Deque, Dict, Optional, Tuple
+from ..exceptions import TwinkleServerError
 
 
 class TaskStatus(str, Enum):
@@ -29,7 +30,7 @@ class TaskStatus(str, Enum):
     FAILED = 'failed'
 
 
-class PreflightError(Exception):
+class PreflightError(TwinkleServerError):
 
     def __init__(self, message: str, status_code: int = 400):
         super().__init__(message)

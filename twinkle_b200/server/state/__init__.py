@@ -16,6 +16,7 @@ import threading
 import time
 import uuid
 from typing import Any, Callable, Dict, Iterable, List, Optional
+from ..exceptions import ConcurrencyError, ResourceExhaustedError, StateBackendError
 
 LEASE_TTL = 30.0
 LEASE_RENEW = 10.0
@@ -172,6 +173,7 @@ class FileBackend(StateBackend):
 
 
 class RedisBackend(StateBackend):  # pragma: no cover - needs the optional redis package and a server
+    MAX_RETRIES = 64
 
     def __init__(self, url: str, prefix: str = 'twinkle'):
         import redis  # type: ignore
@@ -195,7 +197,7 @@ class RedisBackend(StateBackend):  # pragma: no cover - needs the optional redis
         import redis  # type: ignore
         k = self.prefix + key
         with self.r.pipeline() as p:
-            while True:
+            for _attempt in range(self.MAX_RETRIES):
                 try:
                     p.watch(k)
                     cur = p.get(k)
@@ -209,6 +211,9 @@ class RedisBackend(StateBackend):  # pragma: no cover - needs the optional redis
                     return new
                 except redis.WatchError:
                     continue
+                except redis.RedisError as e:
+                    raise StateBackendError(f'redis update of {key!r} failed: {e}') from e
+        raise ConcurrencyError(f'update of {key!r} lost {self.MAX_RETRIES} races in a row')
 
 
 def build_backend(cfg) -> StateBackend:
@@ -261,7 +266,7 @@ class ServerState:
                        info: Optional[Dict[str, Any]] = None) -> None:
         n = sum(1 for k in self.backend.keys('model:') if (self.backend.get(k) or {}).get('token') == token)
         if n >= self.per_token_model_limit:
-            raise PermissionError(f'model limit reached for this token ({self.per_token_model_limit})')
+            raise ResourceExhaustedError(f'model limit reached for this token ({self.per_token_model_limit})')
         self.backend.set(f'model:{model_id}', {'token': token, 'base_model': base_model, 'session_id': session_id,
                                                'replica_id': replica_id or self.replica_id, 'created': time.time(), **(info or {})})
 
