@@ -160,3 +160,30 @@ def test_exception_hierarchy_and_status_mapping(tmp_path):
     assert issubclass(ConcurrencyError, StateBackendError) and issubclass(PreflightError, TwinkleServerError)
     assert [status_code_of(e) for e in (StateBackendError('x'), ConcurrencyError('x'), PreflightError('x', 413), KeyError('k'), TimeoutError(),
                                         PermissionError(), TypeError(), RuntimeError())] == [503, 409, 413, 404, 504, 403, 400, 500]
+
+
+def test_wire_types_validate_bodies_and_parse_paths():
+    import pytest
+    from twinkle_b200.client.types import (REQUESTS, ParsedCheckpointTwinklePath, RequestError, SampleResponseModelList, TrainingRunsResponse,
+                                           UploadToHubRequest, validate_request)
+    out = validate_request('clip_grad_and_step', {'model_id': 'm1', 'extra_flag': 7}, aliases={'model_id': 'adapter_name'})
+    assert out['adapter_name'] == 'm1' and out['max_grad_norm'] == 1.0 and out['norm_type'] == 2 and out['extra_flag'] == 7
+    with pytest.raises(RequestError) as ei:
+        validate_request('set_loss', {'adapter_name': 'a'})
+    assert 'loss_cls' in str(ei.value) and ei.value.status_code == 400
+    with pytest.raises(RequestError):
+        validate_request('forward', {'adapter_name': 'a'})
+    assert validate_request('unknown_route', {'x': 1}) == {'x': 1}
+    assert REQUESTS['forward_only'](inputs=[1]).adapter_name is None
+    assert UploadToHubRequest(checkpoint_dir={'twinkle_path': 'twinkle://r/weights/c'}, hub_model_id='u/m').checkpoint_dir == 'twinkle://r/weights/c'
+    with pytest.raises(Exception):
+        UploadToHubRequest(checkpoint_dir={}, hub_model_id='u/m')
+    p = ParsedCheckpointTwinklePath.parse('twinkle://run1/sampler_weights/step-3')
+    assert (p.training_run_id, p.checkpoint_type, p.checkpoint_id) == ('run1', 'sampler', 'step-3')
+    for bad in ('twinkle://run1/weights', '/tmp/x', 'twinkle://run1/other/x'):
+        with pytest.raises(ValueError):
+            ParsedCheckpointTwinklePath.parse(bad)
+    r = SampleResponseModelList(result=[{'sequences': [{'stop_reason': 'stop', 'tokens': [1, 2], 'logprobs': [-0.1, -0.2]}]}])
+    assert r.result[0].sequences[0].tokens == [1, 2]
+    runs = TrainingRunsResponse(training_runs=[{'training_run_id': 'r', 'last_checkpoint': {'checkpoint_id': 'c'}}], cursor={'total_count': 1})
+    assert runs.training_runs[0].last_checkpoint.checkpoint_type == 'training' and runs.cursor.limit == 100

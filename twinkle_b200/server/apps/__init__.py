@@ -26,6 +26,7 @@ from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 
 from ..backends import BackendSelector
 from ..checkpoint import CheckpointManager
+from ...client.types import validate_request
 from ..exceptions import TwinkleServerError, status_code_of
 from ..queue import PreflightError, TaskQueueMixin
 from ..state import ServerState
@@ -279,6 +280,7 @@ class ModelApp(TaskQueueMixin):
             async def handler(request: Request):
                 b = await body_of(request)
                 token = request.state.token
+                validate_request(method, b, aliases={'model_id': 'adapter_name'})  # a missing field is a 400 naming it
                 name = b.pop('adapter_name', None) or b.pop('model_id', None)
                 adapter = self.adapter_of(name, token) if name in self.adapters else name
                 kwargs = {k: v for k, v in b.items() if k not in ('session_id', )}
