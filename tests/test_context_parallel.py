@@ -63,3 +63,29 @@ def test_cp2_training_matches_single_process():
     for c in multi:
         for a, b in zip(single, c):
             assert abs(a - b) < 2e-4, (single, c)
+
+
+def test_ulysses_kv_replication_keeps_gqa_pairing_for_any_group_size():
+    """Emulated head exchange: after repeating every K/V head ``sp/gcd(kv, sp)`` times, rank r's slice of query heads
+    attends to its slice of K/V heads and the concatenation equals full GQA attention."""
+    import torch.nn.functional as F
+    from twinkle_b200.parallel.ulysses import kv_replication
+    assert [kv_replication(8, s) for s in (1, 2, 4, 8, 16, 3, 6, 12)] == [1, 1, 1, 1, 2, 3, 3, 3]
+    torch.manual_seed(0)
+    t, d = 10, 8
+    for hq, hkv, sp in ((24, 8, 3), (24, 8, 6), (12, 4, 6), (12, 6, 4), (32, 8, 16), (8, 8, 4), (6, 2, 3)):
+        q, k, v = torch.randn(t, hq, d), torch.randn(t, hkv, d), torch.randn(t, hkv, d)
+        grp = hq // hkv
+        full = F.scaled_dot_product_attention(q.transpose(0, 1), k.repeat_interleave(grp, 1).transpose(0, 1),
+                                              v.repeat_interleave(grp, 1).transpose(0, 1), is_causal=True).transpose(0, 1)
+        rep = kv_replication(hkv, sp)
+        kr, vr = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
+        assert kr.shape[1] % sp == 0 and (hq // sp) % (kr.shape[1] // sp) == 0
+        parts = []
+        for r in range(sp):
+            ql = q[:, r * hq // sp:(r + 1) * hq // sp]
+            kl, vl = (x[:, r * x.shape[1] // sp:(r + 1) * x.shape[1] // sp] for x in (kr, vr))
+            g = ql.shape[1] // kl.shape[1]
+            parts.append(F.scaled_dot_product_attention(ql.transpose(0, 1), kl.repeat_interleave(g, 1).transpose(0, 1),
+                                                        vl.repeat_interleave(g, 1).transpose(0, 1), is_causal=True).transpose(0, 1))
+        assert torch.allclose(torch.cat(parts, 1), full, atol=1e-6), (hq, hkv, sp)

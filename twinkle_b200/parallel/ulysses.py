@@ -14,6 +14,7 @@ writes each head slice straight into the destination rank's buffer.
 """
 from __future__ import annotations
 
+import math
 from typing import List, Optional, Tuple
 
 import torch
@@ -167,18 +168,23 @@ class _ProjectScatter(torch.autograd.Function):
         return gx, gw, None, None, None, None, None
 
 
+def kv_replication(num_kv_heads: int, sp: int) -> int:
+    """How often every K/V head is repeated before the head exchange so that the K/V heads divide over ``sp`` ranks:
+    ``sp / gcd(num_kv_heads, sp)``. With query heads divisible by ``sp`` (required anyway) and a whole number of query
+    heads per K/V head, the repeated heads always split so that each rank's query heads find their K/V head locally
+    (``sp/gcd`` divides the group size), for every ``sp`` — 8 K/V heads over 16 ranks, or 2 over 3. This takes the
+    place of a ring among the ranks that share a K/V head (reference ``sequence_parallel/utils.py:90-99`` derives
+    ``rp = ulysses / gcd`` ring ranks there); the price is ``kv_rep`` × the K/V volume in the exchange."""
+    return sp // math.gcd(num_kv_heads, sp)
+
+
 class UlyssesAttention:
     """Strategy object plugged into ``Attention.attn_parallel``."""
 
     def __init__(self, comm: Communicator, num_kv_heads: int):
         self.comm = comm
         self.sp = comm.world_size
-        self.kv_rep = 1
-        if num_kv_heads % self.sp != 0:
-            # fewer kv heads than ranks: replicate kv heads so every rank gets one
-            if self.sp % num_kv_heads != 0:
-                raise ValueError(f'kv heads {num_kv_heads} incompatible with sp={self.sp}; use ring attention')
-            self.kv_rep = self.sp // num_kv_heads
+        self.kv_rep = kv_replication(num_kv_heads, self.sp)
 
     def scatter_heads(self, q, k, v):
         if self.kv_rep > 1:
@@ -272,6 +278,9 @@ def apply_ulysses(model, mesh, cfg, backend: str = 'auto') -> None:
         except Exception:
             if backend == 'symm':
                 raise
+    if cfg.num_attention_heads % comm.world_size != 0:
+        raise ValueError(f'{cfg.num_attention_heads} query heads do not divide over ulysses_size={comm.world_size}; '
+                         f"shard the sequence with the mesh's cp dimension (zig-zag context parallelism) instead")
     strat = UlyssesAttention(comm, cfg.num_key_value_heads)
     linear = None
     for layer in model.layers:
