@@ -149,6 +149,15 @@ def test_swiglu_adamw_sumsq(E):
     yr = ref.swiglu(gur)
     yr.backward(g.float())
     assert rel(y, yr) < 4e-3 and rel(gu.grad, gur.grad) < 4e-3
+    # tanh-GELU gate (Gemma MLPs): same kernels with the other activation; 3-D input goes through as rows
+    gu3 = torch.randn(3, 171, 2 * 1536, device='cuda').bfloat16().requires_grad_(True)
+    y3 = ops.geglu(gu3)
+    g3 = torch.randn_like(y3)
+    y3.backward(g3)
+    gu3r = gu3.detach().float().requires_grad_(True)
+    y3r = ref.geglu(gu3r)
+    y3r.backward(g3.float())
+    assert y3.shape == (3, 171, 1536) and rel(y3, y3r) < 4e-3 and rel(gu3.grad, gu3r.grad) < 4e-3
     n = 1 << 20
     m0 = torch.randn(n, device='cuda')
     m, ea, es = m0.clone(), torch.zeros(n, device='cuda'), torch.zeros(n, device='cuda')

@@ -101,3 +101,19 @@ def test_hub_local_paths_and_aliases(tmp_path):
     assert HubOperation.download_model(str(d)) == str(d)                          # local directories pass through
     with pytest.raises(Exception):
         HubOperation.download_model('ms://definitely/not-cached-anywhere')        # offline: no silent network access
+
+
+def test_geglu_reference_path_and_kernel_bundle_covers_gemma():
+    import torch
+    import torch.nn.functional as F
+    from twinkle_b200 import ops
+    from twinkle_b200.kernel import b200_builtin
+    x = torch.randn(2, 5, 16, requires_grad=True)
+    y = ops.geglu(x)
+    g, u = x.chunk(2, -1)
+    assert torch.allclose(y, F.gelu(g, approximate='tanh') * u, atol=1e-6)
+    y.sum().backward()
+    assert x.grad is not None and x.grad.shape == x.shape
+    names = {k.__name__ for k in b200_builtin()}
+    assert {'Qwen3RMSNorm', 'Qwen3MLP', 'LlamaRMSNorm'} <= names
+    assert not ({'Gemma2RMSNorm', 'Gemma2MLP'} & names) or {'Gemma2RMSNorm', 'Gemma2MLP'} <= names  # both or neither

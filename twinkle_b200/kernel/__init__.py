@@ -112,6 +112,12 @@ def _swiglu_mlp_forward(self, x):
     return ops.linear(ops.swiglu(torch.cat([g, u], -1)), self.down_proj.weight)
 
 
+def _geglu_mlp_forward(self, x):
+    from .. import ops
+    g, u = ops.linear(x, self.gate_proj.weight), ops.linear(x, self.up_proj.weight)
+    return ops.linear(ops.geglu(torch.cat([g, u], -1)), self.down_proj.weight)
+
+
 def b200_builtin() -> Dict[Any, Any]:
     """HF module classes → sm_100a kernels (only classes importable in this environment are listed)."""
     m: Dict[Any, Any] = {}
@@ -127,11 +133,21 @@ def b200_builtin() -> Dict[Any, Any]:
         m[LlamaMLP] = {'cuda': _swiglu_mlp_forward}
     except Exception:
         pass
-    try:
-        from transformers.models.gemma2.modeling_gemma2 import Gemma2RMSNorm
-        m[Gemma2RMSNorm] = {'cuda': _gemma_rmsnorm_forward}
-    except Exception:
-        pass
+    # Gemma family: weight stored as an offset from one ("1 + w"), tanh-GELU gated MLP
+    for mod, norm, mlp in (('gemma', 'GemmaRMSNorm', 'GemmaMLP'), ('gemma2', 'Gemma2RMSNorm', 'Gemma2MLP'), ('gemma3', 'Gemma3RMSNorm', 'Gemma3MLP')):
+        try:
+            pkg = __import__(f'transformers.models.{mod}.modeling_{mod}', fromlist=[norm, mlp])
+            m[getattr(pkg, norm)] = {'cuda': _gemma_rmsnorm_forward}
+            m[getattr(pkg, mlp)] = {'cuda': _geglu_mlp_forward}
+        except Exception:
+            pass
+    # Qwen3.5 / Qwen3-Next norms use the same "1 + w" form
+    for mod, norm in (('qwen3_next', 'Qwen3NextRMSNorm'), ('qwen3_5', 'Qwen3_5RMSNorm')):
+        try:
+            pkg = __import__(f'transformers.models.{mod}.modeling_{mod}', fromlist=[norm])
+            m[getattr(pkg, norm)] = {'cuda': _gemma_rmsnorm_forward}
+        except Exception:
+            pass
     return m
 
 

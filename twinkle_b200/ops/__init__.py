@@ -242,6 +242,28 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     return ref.swiglu(gate_up)
 
 
+class _GeGLU(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, gate_up):
+        ctx.save_for_backward(gate_up)
+        return ext().geglu_fwd(gate_up)
+
+    @staticmethod
+    def backward(ctx, gy):
+        (gate_up, ) = ctx.saved_tensors
+        return ext().geglu_bwd(gy.contiguous(), gate_up)
+
+
+def geglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """``[T, 2I]`` laid out as ``[gate | up]`` → ``gelu_tanh(gate) * up`` (Gemma-family MLPs); same kernel family as
+    :func:`swiglu` (reference ``kernel/liger_impls/swiglu.py:26-32``)."""
+    if _cuda(gate_up) and gate_up.dtype == torch.bfloat16:
+        lead = gate_up.shape[:-1]
+        return _GeGLU.apply(gate_up.reshape(-1, gate_up.shape[-1])).reshape(*lead, -1)
+    return ref.geglu(gate_up)
+
+
 # --------------------------------------------------------------- attention
 class _FlashAttnVarlen(torch.autograd.Function):
 

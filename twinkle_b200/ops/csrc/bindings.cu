@@ -18,6 +18,8 @@ std::vector<torch::Tensor> qk_norm_rope_bwd(const torch::Tensor&, const torch::T
                                             const torch::Tensor&, int64_t, int64_t, int64_t);
 torch::Tensor swiglu_fwd(const torch::Tensor&);
 torch::Tensor swiglu_bwd(const torch::Tensor&, const torch::Tensor&);
+torch::Tensor geglu_fwd(const torch::Tensor&);
+torch::Tensor geglu_bwd(const torch::Tensor&, const torch::Tensor&);
 void adamw_step(torch::Tensor, torch::Tensor, torch::Tensor, const torch::Tensor&, const c10::optional<torch::Tensor>&, double, double,
                 double, double, double, int64_t, double);
 torch::Tensor sumsq(const torch::Tensor&);
@@ -67,6 +69,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("qk_norm_rope_bwd", &tk::qk_norm_rope_bwd);
   m.def("swiglu_fwd", &tk::swiglu_fwd);
   m.def("swiglu_bwd", &tk::swiglu_bwd);
+  m.def("geglu_fwd", &tk::geglu_fwd);
+  m.def("geglu_bwd", &tk::geglu_bwd);
   m.def("adamw_step", &tk::adamw_step);
   m.def("sumsq", &tk::sumsq);
   m.def("logprob_fwd", &tk::logprob_fwd);

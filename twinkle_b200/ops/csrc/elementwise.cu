@@ -320,7 +320,31 @@ std::vector<torch::Tensor> qk_norm_rope_bwd(const torch::Tensor& gq, const torch
   return {dqkv, dqw, dkw};
 }
 
-// -------------------------------------------------------------------- SwiGLU
+// ----------------------------------------------------------- SwiGLU / GeGLU
+// GELU = false: act(x) = x * sigmoid(x).  GELU = true: tanh-approximated GELU, act(x) = 0.5 x (1 + tanh(c (x + 0.044715 x^3))).
+template <bool GELU>
+__device__ __forceinline__ float glu_act(float x) {
+  if (GELU) {
+    const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    return 0.5f * x * (1.f + tanhf(u));
+  }
+  return x / (1.f + __expf(-x));
+}
+
+// act(x) and d act / dx
+template <bool GELU>
+__device__ __forceinline__ float2 glu_act_grad(float x) {
+  if (GELU) {
+    const float x2 = x * x;
+    const float t = tanhf(0.7978845608028654f * (x + 0.044715f * x * x2));
+    const float du = 0.7978845608028654f * (1.f + 3.f * 0.044715f * x2);
+    return make_float2(0.5f * x * (1.f + t), 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * du);
+  }
+  const float s = 1.f / (1.f + __expf(-x));
+  return make_float2(x * s, s * (1.f + x * (1.f - s)));
+}
+
+template <bool GELU>
 __global__ void swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, long rows, int I) {
   const int vec_per_row = I >> 3;
   const long total = rows * vec_per_row;
@@ -334,12 +358,13 @@ __global__ void swiglu_fwd_kernel(const bf16* __restrict__ gu, bf16* __restrict_
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       float2 a = unpack_bf16(pg[k]), b = unpack_bf16(pu[k]);
-      po[k] = pack_bf16(a.x / (1.f + __expf(-a.x)) * b.x, a.y / (1.f + __expf(-a.y)) * b.y);
+      po[k] = pack_bf16(glu_act<GELU>(a.x) * b.x, glu_act<GELU>(a.y) * b.y);
     }
     *reinterpret_cast<uint4*>(out + r * I + c * 8) = o;
   }
 }
 
+template <bool GELU>
 __global__ void swiglu_bwd_kernel(const bf16* __restrict__ gy, const bf16* __restrict__ gu, bf16* __restrict__ dgu, long rows, int I) {
   const int vec_per_row = I >> 3;
   const long total = rows * vec_per_row;
@@ -354,16 +379,16 @@ __global__ void swiglu_bwd_kernel(const bf16* __restrict__ gy, const bf16* __res
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       float2 a = unpack_bf16(pg[k]), b = unpack_bf16(pu[k]), d = unpack_bf16(py[k]);
-      float s0 = 1.f / (1.f + __expf(-a.x)), s1 = 1.f / (1.f + __expf(-a.y));
-      pog[k] = pack_bf16(d.x * b.x * s0 * (1.f + a.x * (1.f - s0)), d.y * b.y * s1 * (1.f + a.y * (1.f - s1)));
-      pou[k] = pack_bf16(d.x * a.x * s0, d.y * a.y * s1);
+      const float2 f0 = glu_act_grad<GELU>(a.x), f1 = glu_act_grad<GELU>(a.y);
+      pog[k] = pack_bf16(d.x * b.x * f0.y, d.y * b.y * f1.y);
+      pou[k] = pack_bf16(d.x * f0.x, d.y * f1.x);
     }
     *reinterpret_cast<uint4*>(dgu + r * 2 * I + c * 8) = og;
     *reinterpret_cast<uint4*>(dgu + r * 2 * I + I + c * 8) = ou;
   }
 }
 
-torch::Tensor swiglu_fwd(const torch::Tensor& gu) {
+static torch::Tensor glu_fwd(const torch::Tensor& gu, bool gelu) {
   TORCH_CHECK(gu.is_cuda() && gu.scalar_type() == torch::kBFloat16 && gu.is_contiguous() && gu.dim() == 2, "gate_up [rows, 2I] bf16");
   const long rows = gu.size(0);
   const int I = gu.size(1) / 2;
@@ -373,14 +398,22 @@ torch::Tensor swiglu_fwd(const torch::Tensor& gu) {
   if (rows == 0) return out;
   long total = rows * (I / 8);
   int blocks = static_cast<int>(std::min<long>((total + 255) / 256, num_sms() * 16L));
-  swiglu_fwd_kernel<<<blocks, 256, 0, at::cuda::getCurrentCUDAStream()>>>(reinterpret_cast<const bf16*>(gu.data_ptr()),
-                                                                         reinterpret_cast<bf16*>(out.data_ptr()), rows, I);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const bf16* in = reinterpret_cast<const bf16*>(gu.data_ptr());
+  bf16* o = reinterpret_cast<bf16*>(out.data_ptr());
+  if (gelu) swiglu_fwd_kernel<true><<<blocks, 256, 0, stream>>>(in, o, rows, I);
+  else swiglu_fwd_kernel<false><<<blocks, 256, 0, stream>>>(in, o, rows, I);
   count_launch();
   TK_CUDA_CHECK(cudaGetLastError());
   return out;
 }
 
-torch::Tensor swiglu_bwd(const torch::Tensor& gy, const torch::Tensor& gu) {
+torch::Tensor swiglu_fwd(const torch::Tensor& gu) { return glu_fwd(gu, false); }
+torch::Tensor geglu_fwd(const torch::Tensor& gu) { return glu_fwd(gu, true); }
+
+static torch::Tensor glu_bwd(const torch::Tensor& gy, const torch::Tensor& gu, bool gelu) {
+  TORCH_CHECK(gy.is_cuda() && gy.scalar_type() == torch::kBFloat16 && gy.is_contiguous() && gu.is_contiguous() && gy.dim() == 2 &&
+              gy.size(0) == gu.size(0) && gy.size(1) * 2 == gu.size(1), "grad [rows, I] bf16 for gate_up [rows, 2I]");
   const long rows = gu.size(0);
   const int I = gu.size(1) / 2;
   c10::cuda::CUDAGuard guard(gu.device());
@@ -388,12 +421,19 @@ torch::Tensor swiglu_bwd(const torch::Tensor& gy, const torch::Tensor& gu) {
   if (rows == 0) return dgu;
   long total = rows * (I / 8);
   int blocks = static_cast<int>(std::min<long>((total + 255) / 256, num_sms() * 16L));
-  swiglu_bwd_kernel<<<blocks, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
-      reinterpret_cast<const bf16*>(gy.data_ptr()), reinterpret_cast<const bf16*>(gu.data_ptr()), reinterpret_cast<bf16*>(dgu.data_ptr()), rows, I);
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const bf16* g = reinterpret_cast<const bf16*>(gy.data_ptr());
+  const bf16* in = reinterpret_cast<const bf16*>(gu.data_ptr());
+  bf16* o = reinterpret_cast<bf16*>(dgu.data_ptr());
+  if (gelu) swiglu_bwd_kernel<true><<<blocks, 256, 0, stream>>>(g, in, o, rows, I);
+  else swiglu_bwd_kernel<false><<<blocks, 256, 0, stream>>>(g, in, o, rows, I);
   count_launch();
   TK_CUDA_CHECK(cudaGetLastError());
   return dgu;
 }
+
+torch::Tensor swiglu_bwd(const torch::Tensor& gy, const torch::Tensor& gu) { return glu_bwd(gy, gu, false); }
+torch::Tensor geglu_bwd(const torch::Tensor& gy, const torch::Tensor& gu) { return glu_bwd(gy, gu, true); }
 
 // --------------------------------------------------------------------- AdamW
 // fp32 master/moments; gradient fp32 or bf16, multiplied by grad_scale on read;
