@@ -117,3 +117,52 @@ def test_geglu_reference_path_and_kernel_bundle_covers_gemma():
     names = {k.__name__ for k in b200_builtin()}
     assert {'Qwen3RMSNorm', 'Qwen3MLP', 'LlamaRMSNorm'} <= names
     assert not ({'Gemma2RMSNorm', 'Gemma2MLP'} & names) or {'Gemma2RMSNorm', 'Gemma2MLP'} <= names  # both or neither
+
+
+def test_misc_helpers(tmp_path):
+    import base64
+    import torch
+    from twinkle_b200.models.decoder import DecoderConfig, build_model
+    from twinkle_b200.utils.misc import (align_logps_to_mask, call_with_supported_kwargs, copy_files_by_pattern, deep_getattr, find_all_linears,
+                                         get_llm_model, get_runtime_meta, has_signature_parameter, load_mm_file)
+
+    class A:
+        b = {'c': type('C', (), {'d': 5})()}
+
+    assert deep_getattr(A(), 'b.c.d') == 5 and deep_getattr(A(), 'b.x.d', 'dflt') == 'dflt'
+
+    def f(a, b=2):
+        return a + b
+
+    assert call_with_supported_kwargs(f, 1, b=3, zzz=9) == 4 and call_with_supported_kwargs(lambda **kw: sorted(kw), x=1, y=2) == ['x', 'y']
+    assert has_signature_parameter(f, 'b') and not has_signature_parameter(f, 'c')
+    src, dst = tmp_path / 's', tmp_path / 'd'
+    (src / 'sub').mkdir(parents=True)
+    for name in ('tokenizer.json', 'config.json', 'model.safetensors', 'sub/vocab.txt', 'sub/skip.bin'):
+        (src / name).write_text('x')
+    assert copy_files_by_pattern(str(src), str(dst), ['*.json', '*.txt'], exclude_patterns='config*') == ['sub/vocab.txt', 'tokenizer.json']
+    assert copy_files_by_pattern(str(src), str(dst), '*.json') == ['config.json']  # existing files are not copied again
+    assert 'rank=' in get_runtime_meta() and 'pid=' in get_runtime_meta()
+
+    from twinkle_b200.models.config import PRESETS
+    m = build_model(DecoderConfig(**PRESETS['tiny-dense']))
+    wrapper = type('W', (), {'model': type('V', (), {'model': m})()})()
+    assert get_llm_model(wrapper) is m
+    assert find_all_linears(wrapper) == ['down_proj', 'gate_proj', 'k_proj', 'o_proj', 'q_proj', 'up_proj', 'v_proj']
+    moe = find_all_linears(build_model(DecoderConfig(**PRESETS['tiny-moe'])))
+    assert 'gate' not in moe and {'gate_up_proj', 'down_proj', 'q_proj'} <= set(moe)
+
+    mask = torch.tensor([[0, 1, 1, 0], [1, 1, 1, 1], [0, 0, 0, 0]], dtype=torch.bool)
+    out = align_logps_to_mask([[0.5, 0.25, 9.0], 2.0, [1.0]], mask, torch.float32)
+    assert out.tolist() == [[0, 0.5, 0.25, 0], [2, 2, 2, 2], [0, 0, 0, 0]]
+    dense = torch.ones(3, 4)
+    assert align_logps_to_mask(dense, mask, torch.float32) is not None and align_logps_to_mask('x', mask, torch.float32) is None
+    assert align_logps_to_mask(torch.tensor([[1.0, 2.0]]), mask, torch.float32)[0].tolist() == [0, 1, 2, 0]
+
+    assert load_mm_file(b'abc').read() == b'abc' and load_mm_file('data:image/png;base64,' + base64.b64encode(b'xyz').decode()).read() == b'xyz'
+    p = tmp_path / 'f.bin'
+    p.write_bytes(b'123')
+    assert load_mm_file(str(p)).read() == b'123' and load_mm_file(7) == 7
+    import pytest
+    with pytest.raises(FileNotFoundError):
+        load_mm_file('/no/such/file!!')
