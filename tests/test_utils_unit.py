@@ -166,3 +166,14 @@ def test_misc_helpers(tmp_path):
     import pytest
     with pytest.raises(FileNotFoundError):
         load_mm_file('/no/such/file!!')
+
+
+def test_safe_arithmetic_rejects_everything_but_arithmetic():
+    import pytest
+    from twinkle_b200.reward import CountdownReward, safe_arithmetic
+    assert safe_arithmetic('(1+2)*3/ -3') == -3.0 and safe_arithmetic('2.5*4') == 10.0
+    for bad in ('__import__("os").system("true")', '2**10', 'a+1', '1/0', '(' * 300, '[1][0]', 'True+1'):
+        with pytest.raises(ValueError):
+            safe_arithmetic(bad)
+    t = lambda c: {'messages': [{'role': 'assistant', 'content': c}]}  # noqa: E731
+    assert CountdownReward()([t('<answer>(3+5)*2 = 16</answer>'), t('<answer>3+5</answer>')], [{'nums': [2, 3, 5], 'target': 16}] * 2) == [1.0, 0.0]

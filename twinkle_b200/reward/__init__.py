@@ -52,6 +52,33 @@ def extract_boxed(text: str) -> Optional[str]:
     return None
 
 
+def safe_arithmetic(expr: str) -> float:
+    """Value of an expression made of numbers, ``+ - * /``, unary minus and parentheses; anything else (names, calls,
+    powers, attribute access) raises ``ValueError``. Model output is never handed to ``eval``."""
+    import ast
+    import operator as op
+    ops = {ast.Add: op.add, ast.Sub: op.sub, ast.Mult: op.mul, ast.Div: op.truediv}
+
+    def ev(n):
+        if isinstance(n, ast.Expression):
+            return ev(n.body)
+        if isinstance(n, ast.Constant) and isinstance(n.value, (int, float)) and not isinstance(n.value, bool):
+            return float(n.value)
+        if isinstance(n, ast.BinOp) and type(n.op) in ops:
+            return ops[type(n.op)](ev(n.left), ev(n.right))
+        if isinstance(n, ast.UnaryOp) and isinstance(n.op, (ast.USub, ast.UAdd)):
+            v = ev(n.operand)
+            return -v if isinstance(n.op, ast.USub) else v
+        raise ValueError(f'not plain arithmetic: {ast.dump(n)[:60]}')
+
+    if len(expr) > 200:
+        raise ValueError('expression too long')
+    try:
+        return ev(ast.parse(expr.strip(), mode='eval'))
+    except (SyntaxError, ZeroDivisionError, RecursionError) as e:
+        raise ValueError(str(e)) from None
+
+
 class Reward:
 
     def __call__(self, trajectories: Sequence[Any], ground_truths: Optional[Sequence[Any]] = None, **kwargs) -> List[float]:  # pragma: no cover
@@ -135,7 +162,7 @@ class CountdownReward(Reward):
                 if re.fullmatch(r'[\d\s\+\-\*/\(\)\.]+', eq):
                     nums = sorted(int(x) for x in re.findall(r'\d+', eq))
                     try:
-                        if nums == sorted(gt['nums']) and abs(eval(eq, {'__builtins__': {}}) - gt['target']) < 1e-6:
+                        if nums == sorted(gt['nums']) and abs(safe_arithmetic(eq) - gt['target']) < 1e-6:
                             ok = 1.0
                     except Exception:
                         ok = 0.0
@@ -359,4 +386,4 @@ class MultiModalAccuracyReward(Reward):
 reward_mapping = {c.__name__: c for c in (GSM8KAccuracyReward, GSM8KFormatReward, FormatReward, MathReward, F1Reward,
                                           CountdownReward, OlympiadBenchReward, OlympiadBenchAccuracyReward, OlympiadBenchFormatReward,
                                           OlympiadBenchQualityReward, MultiModalAccuracyReward)}
-__all__ = ['Reward', 'reward_mapping', 'all_boxed', 'normalize_math_answer', 'split_answers', 'numeric_match', 'numeric_similarity'] + list(reward_mapping)
+__all__ = ['Reward', 'reward_mapping', 'safe_arithmetic', 'all_boxed', 'normalize_math_answer', 'split_answers', 'numeric_match', 'numeric_similarity'] + list(reward_mapping)
