@@ -122,6 +122,8 @@ class ComputeWorker:
             self.queues.setdefault(task.queue_key, collections.deque()).append(task)
             depth = sum(len(q) for q in self.queues.values())
             self._cv.notify()
+        if self.metrics is not None:
+            self.metrics.set_gauge('twinkle_queue_depth', depth)
         self.state.set_future(task.request_id, TaskStatus.QUEUED.value, queue_depth=depth)
 
     def _next(self) -> Optional[_Task]:
@@ -190,6 +192,9 @@ class ComputeWorker:
                 self.metrics.observe_task(time.monotonic() - start, waited)
 
     def _finish(self, t: _Task, status: TaskStatus, result: Any = None, error: Optional[str] = None, **extra) -> None:
+        if self.metrics is not None:
+            self.metrics.inc('twinkle_tasks_total', status=status.value)
+            self.metrics.set_gauge('twinkle_queue_depth', self.depth())
         # a blocking caller gets the object itself; only fire-and-poll tasks need the result in the state
         # backend, which must be JSON-serialisable there
         if t.done is not None and not t.done.done():
@@ -226,6 +231,9 @@ class TaskQueueMixin:
                 raise PreflightError(f'batch size {batch_size} must be a multiple of {batch_size_multiple}')
         ok, why = self.rate_limiter.acquire(token, input_tokens)
         if not ok:
+            m = getattr(self.worker, 'metrics', None)
+            if m is not None:
+                m.inc('twinkle_rate_limit_rejections_total')
             raise PreflightError(why, 429)
 
     def schedule_task(self, fn: Callable[[], Any], *, token: str, model_id: str = '', input_tokens: int = 0, batch_size: Optional[int] = None,
