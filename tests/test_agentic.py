@@ -355,3 +355,34 @@ def test_client_multi_turn_rollout_token_exact_state():
     with pytest.raises(ValueError):
         ClientMultiTurnRollout(s, tpl, sampling_params={'num_samples': 2})
     assert roll([]) == []
+
+
+def test_template_tool_call_parsing_and_react_rollout():
+    from twinkle_b200.agentic import FunctionTool, MultiTurnRollout, ToolManager
+    from twinkle_b200.data_format import SampledSequence, SampleResponse
+    from twinkle_b200.template import Template
+    t = Template(model_id=None)
+    msg = t.response_message('ok <tool_call>\n{"name": "add", "arguments": {"a": 1}}\n</tool_call>')
+    assert msg['content'] == 'ok' and msg['tool_calls'][0]['tool_name'] == 'add' and msg['tool_calls'][0]['arguments'] == {'a': 1}
+    assert t.response_message('plain') == {'role': 'assistant', 'content': 'plain'}
+    react = Template(model_id=None, agent_template='react')
+    text = 'Thought: add them\nAction: add\nAction Input: {"a": 2, "b": 3}'
+    assert react.parse_tool_call(text)[0]['arguments'] == {'a': 2, 'b': 3} and react.clean_tool_call(text) == 'Thought: add them'
+    assert react.parse_tool_call('<tool_call>\n{"name": "add", "arguments": {}}\n</tool_call>') == []  # only the configured syntax
+
+    def add(a: int, b: int) -> int:
+        """Add."""
+        return a + b
+
+    class S:
+
+        def sample(self, trajs, sp, **kw):
+            out = []
+            for tr in trajs:
+                done = any(m['role'] == 'tool' for m in tr['messages'])
+                out.append(SampleResponse(sequences=[SampledSequence('stop', [1], decoded='Final Answer: 5' if done else text)]))
+            return out
+
+    res = MultiTurnRollout(S(), ToolManager([FunctionTool(add)]), max_turns=3, tool_format='react')([{'messages': [{'role': 'user', 'content': '2+3?'}]}])[0]
+    assert [m['role'] for m in res['messages']] == ['user', 'assistant', 'tool', 'assistant'] and res['messages'][2]['content'] == '5'
+    assert res['messages'][1]['content'] == 'Thought: add them' and res['user_data']['rollout']['tool_calls'] == 1

@@ -77,7 +77,9 @@ class MultiTurnRollout(Rollout):
 
     def __init__(self, sampler, tool_manager: Union[ToolManager, Sequence[ToolManager], Callable[[Sequence[Trajectory]], List[ToolManager]], None] = None,
                  max_turns: int = 8, sampling_params: Optional[SamplingParams] = None, stop_on_no_tool_call: bool = True,
-                 trace_dir: Optional[str] = None, adapter_name: Optional[str] = None):
+                 trace_dir: Optional[str] = None, adapter_name: Optional[str] = None, tool_format: str = 'hermes'):
+        # tool_format: 'hermes' (the <tool_call> JSON blocks Qwen models write), 'react', 'cline', 'vcp', or 'auto' (first that matches)
+        self.tool_format = tool_format
         self.sampler, self.tool_manager = sampler, tool_manager
         self.max_turns, self.stop_on_no_tool_call = max_turns, stop_on_no_tool_call
         self.sampling_params = sampling_params or SamplingParams(max_tokens=512)
@@ -118,8 +120,15 @@ class MultiTurnRollout(Rollout):
             for i, resp in zip(live, resps):
                 seq = resp.sequences[0]
                 text = seq.decoded if seq.decoded is not None else ''
-                calls = parse_tool_calls(text)
-                msg: Message = {'role': 'assistant', 'content': strip_tool_calls(text) if calls else text}
+                if self.tool_format == 'hermes':
+                    calls = parse_tool_calls(text)
+                    clean = strip_tool_calls(text) if calls else text
+                else:
+                    from ..template.tools import parse_tool_calls as parse_any
+                    fmts = ('hermes', 'vcp', 'react', 'cline') if self.tool_format == 'auto' else (self.tool_format, )
+                    known = managers[i].names() if managers[i] is not None else None
+                    calls, clean, _ = parse_any(text, fmts, known_tools=known)
+                msg: Message = {'role': 'assistant', 'content': clean}
                 if calls:
                     msg['tool_calls'] = calls
                 trajs[i]['messages'].append(msg)

@@ -299,6 +299,29 @@ class Template:
         n = len(ids)
         return {'input_ids': ids, 'labels': labels, 'attention_mask': [1] * n, 'position_ids': list(range(n)), 'length': n}
 
+    # ------------------------------------------------------------ tool calls
+    def _tool_formats(self):
+        return (self.agent_template, ) if self.agent_template else ('hermes', 'vcp', 'react', 'cline')
+
+    def parse_tool_call(self, text: str, known_tools: Optional[Sequence[str]] = None) -> List[Dict[str, Any]]:
+        """Tool calls written in a completion, in the template's ``agent_template`` syntax (``hermes`` / ``react`` /
+        ``cline`` / ``vcp``) or, when none is set, in the first syntax that matches. Empty list when there is none."""
+        from .tools import parse_tool_calls
+        return parse_tool_calls(text or '', self._tool_formats(), known_tools=known_tools)[0]
+
+    def clean_tool_call(self, text: str, known_tools: Optional[Sequence[str]] = None) -> str:
+        """The completion without its tool-call syntax (what goes into the assistant message's ``content``)."""
+        from .tools import parse_tool_calls
+        return parse_tool_calls(text or '', self._tool_formats(), known_tools=known_tools)[1]
+
+    def response_message(self, text: str) -> Dict[str, Any]:
+        """Assistant message for a decoded completion: content with the call syntax removed, ``tool_calls`` when any."""
+        calls = self.parse_tool_call(text)
+        msg: Dict[str, Any] = {'role': 'assistant', 'content': self.clean_tool_call(text) if calls else (text or '')}
+        if calls:
+            msg['tool_calls'] = calls
+        return msg
+
     def pre_forward_hook(self, inputs: Dict[str, Any]) -> Dict[str, Any]:
         """Multimodal templates merge vision embeddings here; text models pass through."""
         return inputs
