@@ -177,3 +177,42 @@ def test_safe_arithmetic_rejects_everything_but_arithmetic():
             safe_arithmetic(bad)
     t = lambda c: {'messages': [{'role': 'assistant', 'content': c}]}  # noqa: E731
     assert CountdownReward()([t('<answer>(3+5)*2 = 16</answer>'), t('<answer>3+5</answer>')], [{'nums': [2, 3, 5], 'target': 16}] * 2) == [1.0, 0.0]
+
+
+def test_reasoning_split_and_qwen3_chat_template_patches():
+    import jinja2
+    from twinkle_b200.patch import apply_context, apply_patch
+    from twinkle_b200.template import Template
+    t = Template(model_id=None)
+    traj = {'messages': [{'role': 'assistant', 'content': '<think>\nhm\n</think>\n\nans </think> tail'},
+                         {'role': 'assistant', 'content': 'no opening tag </think> rest'}]}
+    out = t._to_standard_reasoning_content(traj)['messages']
+    assert out[0]['reasoning_content'] == 'hm' and out[0]['content'] == 'ans </think> tail'
+    assert 'reasoning_content' not in out[1] and out[1]['content'] == 'no opening tag </think> rest'
+
+    shipped = ("{%- for message in messages %}{%- set content = message.content %}{%- set reasoning_content = '' %}\n"
+               "            {%- if '</think>' in content %}\n"
+               "                {%- set reasoning_content = content.split('</think>')[0].rstrip('\\n').split('<think>')[-1].lstrip('\\n') %}\n"
+               "                {%- set content = content.split('</think>')[-1].lstrip('\\n') %}\n"
+               "            {%- endif %}\n"
+               "[R={{ reasoning_content }}|C={{ content }}]{%- endfor %}\n"
+               "{%- if multi %}\n    {{- raise_exception('No user query found in messages.') }}\n{%- endif %}")
+
+    class Tok:
+        chat_template = shipped
+
+    tok, env = Tok(), jinja2.Environment()
+    msgs = [{'content': '<think>\nhm\n</think>\n\nans </think> tail'}, {'content': 'no open </think> rest'}]
+    assert env.from_string(shipped).render(messages=msgs, multi=False) == '[R=hm|C= tail][R=no open |C= rest]'  # the defect
+    with apply_context(tok, 'Qwen3ChatTemplate') as p:
+        assert p.applied
+        assert env.from_string(tok.chat_template).render(messages=msgs, multi=False) == '[R=hm|C=ans </think> tail][R=|C=no open </think> rest]'
+        q = apply_patch(tok, 'Qwen3AllowToolTailTemplate')
+        assert q.applied and env.from_string(tok.chat_template).render(messages=[], multi=True) == ''
+        q.unpatch(tok)
+    assert tok.chat_template == shipped
+
+    class Other:
+        chat_template = '{{ messages }}'
+
+    assert not apply_patch(Other(), 'Qwen3ChatTemplate').applied

@@ -53,9 +53,71 @@ class NoSplitModulesPatch(Patch):
         return self
 
 
+class Qwen3ChatTemplate(Patch):
+    """Repairs the reasoning split of the Qwen3 / Qwen3.5 chat template held by a HF tokenizer (``tokenizer.chat_template``
+    is Jinja text). The shipped template takes everything before the LAST ``</think>`` as reasoning even when the content
+    never opened a ``<think>`` block, and drops text between several closing tags; a re-rendered conversation then differs
+    from the tokens that were sampled, which breaks token-exact multi-turn rollouts. The patched block requires the
+    content to start with ``<think>`` and splits at the first closing tag only. Tokenizers whose template does not
+    contain the block are left alone (``applied`` tells). Reference: ``patch/qwen3_chat_template.py:62-92``."""
+
+    _BLOCK = None
+
+    @classmethod
+    def _pattern(cls):
+        import re
+        if cls._BLOCK is None:
+            cls._BLOCK = re.compile(
+                r"(?P<ind>[ \t]*)\{%-\s*if\s+'</think>'\s+in\s+content\s*%\}\s*"
+                r"\{%-\s*set\s+reasoning_content\s*=\s*content\.split\('</think>'\)\[0\][^%]*?%\}\s*"
+                r"\{%-\s*set\s+content\s*=\s*content\.split\('</think>'\)\[-1\][^%]*?%\}\s*"
+                r"\{%-\s*endif\s*%\}")
+        return cls._BLOCK
+
+    def __call__(self, tokenizer, **kwargs):
+        self._prev, self.applied = getattr(tokenizer, 'chat_template', None), False
+        if isinstance(self._prev, str):
+            def fixed(m):
+                i = m.group('ind')
+                return (f"{i}{{%- if content.startswith('<think>') and '</think>' in content %}}\n"
+                        f"{i}    {{%- set _parts = content.split('</think>', 1) %}}\n"
+                        f"{i}    {{%- set reasoning_content = _parts[0].split('<think>', 1)[1].strip('\\n') %}}\n"
+                        f"{i}    {{%- set content = _parts[1].lstrip('\\n') %}}\n"
+                        f"{i}{{%- endif %}}")
+            new, n = self._pattern().subn(fixed, self._prev)
+            if n:
+                tokenizer.chat_template, self.applied = new, True
+        return self
+
+    def unpatch(self, tokenizer):
+        if self.applied:
+            tokenizer.chat_template = self._prev
+
+
+class Qwen3AllowToolTailTemplate(Patch):
+    """Lets the Qwen3 chat template render a message list that has no user query before its tool messages (a
+    continuation that starts at a tool result): the template's ``raise_exception('No user query found in messages.')``
+    becomes a comment. Reference: ``patch/qwen3_chat_template.py:94-124``."""
+
+    def __call__(self, tokenizer, **kwargs):
+        import re
+        self._prev, self.applied = getattr(tokenizer, 'chat_template', None), False
+        if isinstance(self._prev, str):
+            new, n = re.subn(r"\{\{-\s*raise_exception\('No user query found in messages\.'\)\s*\}\}",
+                             '{#- no user query before the tool messages: allowed -#}', self._prev)
+            if n:
+                tokenizer.chat_template, self.applied = new, True
+        return self
+
+    def unpatch(self, tokenizer):
+        if self.applied:
+            tokenizer.chat_template = self._prev
+
+
 patch_mapping = {'FusedCEPatch': FusedCEPatch, 'TransformersFusedCEPatch': FusedCEPatch, 'EmbeddingPatch': EmbeddingPatch,
                  'TransformersEmbeddingPatch': EmbeddingPatch, 'MegatronEmbeddingPatch': EmbeddingPatch,
-                 'NoSplitModulesPatch': NoSplitModulesPatch}
+                 'NoSplitModulesPatch': NoSplitModulesPatch, 'Qwen3ChatTemplate': Qwen3ChatTemplate,
+                 'Qwen3AllowToolTailTemplate': Qwen3AllowToolTailTemplate}
 
 
 def apply_patch(model, patch_cls, **kwargs) -> Patch:

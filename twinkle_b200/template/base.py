@@ -147,9 +147,12 @@ class Template:
         """``<think>…</think>`` inside assistant content moves to ``reasoning_content``."""
         for m in traj.get('messages') or []:
             c = m.get('content')
-            if m.get('role') == 'assistant' and isinstance(c, str) and '</think>' in c and not m.get('reasoning_content'):
+            # only a block that opens the content counts: a stray closing tag in the middle of an answer stays content, and
+            # everything after the FIRST closing tag is kept (later stray tags included), so rendering round-trips
+            if (m.get('role') == 'assistant' and isinstance(c, str) and c.lstrip().startswith('<think>') and '</think>' in c
+                    and not m.get('reasoning_content')):
                 head, tail = c.split('</think>', 1)
-                m['reasoning_content'] = head.replace('<think>', '').strip()
+                m['reasoning_content'] = head.split('<think>', 1)[1].strip()
                 m['content'] = tail.lstrip('\n')
         return traj
 
