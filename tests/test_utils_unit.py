@@ -202,13 +202,14 @@ def test_reasoning_split_and_qwen3_chat_template_patches():
         chat_template = shipped
 
     tok, env = Tok(), jinja2.Environment()
+    render = lambda src, **kw: env.from_string(src).render(**kw).replace('\n', '')  # noqa: E731
     msgs = [{'content': '<think>\nhm\n</think>\n\nans </think> tail'}, {'content': 'no open </think> rest'}]
-    assert env.from_string(shipped).render(messages=msgs, multi=False) == '[R=hm|C= tail][R=no open |C= rest]'  # the defect
+    assert render(shipped, messages=msgs, multi=False) == '[R=hm|C= tail][R=no open |C= rest]'  # the defect
     with apply_context(tok, 'Qwen3ChatTemplate') as p:
         assert p.applied
-        assert env.from_string(tok.chat_template).render(messages=msgs, multi=False) == '[R=hm|C=ans </think> tail][R=|C=no open </think> rest]'
+        assert render(tok.chat_template, messages=msgs, multi=False) == '[R=hm|C=ans </think> tail][R=|C=no open </think> rest]'
         q = apply_patch(tok, 'Qwen3AllowToolTailTemplate')
-        assert q.applied and env.from_string(tok.chat_template).render(messages=[], multi=True) == ''
+        assert q.applied and render(tok.chat_template, messages=[], multi=True) == ''
         q.unpatch(tok)
     assert tok.chat_template == shipped
 
