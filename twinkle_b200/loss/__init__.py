@@ -17,5 +17,6 @@ torch_loss_mapping = {
 for _c in list(torch_loss_mapping.values()):
     torch_loss_mapping[_c.__name__] = _c
 torch_loss_mapping['LigerFusedLinearCrossEntropyLoss'] = FusedLinearCrossEntropyLoss
+torch_loss_mapping['liger_fused_linear_cross_entropy'] = FusedLinearCrossEntropyLoss  # the reference's registry key for the same loss
 
 __all__ = ['Loss', 'torch_loss_mapping'] + sorted({c.__name__ for c in torch_loss_mapping.values()})
