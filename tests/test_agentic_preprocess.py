@@ -251,3 +251,30 @@ def test_quality_preprocessor_runs_mixed_steps_and_logs_drops(tmp_path):
     lines = [json.loads(l) for l in log.read_text().splitlines()]
     assert [l['step'] for l in lines] == ['DedupFilter', 'SpecialCharsFilter'] and lines[1]['row']['drop_reason'] == 'special_chars_ratio'
     assert QualityPreprocessor([lambda rs: []])(rows) == []
+
+
+def test_pii_rewriter_detects_validates_and_stays_consistent():
+    from twinkle_b200.agentic import PIIPresidioFilter, PIIRewriter, Strategy
+    from twinkle_b200.agentic.pii import cn_id_ok, hash_short, iban_ok, luhn_ok
+    assert luhn_ok('4111 1111 1111 1111') and not luhn_ok('4111 1111 1111 1112') and not luhn_ok('1234')
+    assert cn_id_ok('11010519491231002X') and not cn_id_ok('110105194912310021')
+    assert iban_ok('GB82 WEST 1234 5698 7654 32') and not iban_ok('GB82 WEST 1234 5698 7654 33')
+    text = ('Mail bob.smith@corp.io or call +1 415-555-2671 / 13812345678. Card 4111 1111 1111 1111, not 4111 1111 1111 1112. SSN 123-45-6789. '
+            'IP 10.1.2.3, version 1.2.3.4.5, id 11010519491231002X, iban GB82 WEST 1234 5698 7654 32, see https://x.y/z?a=1. bob.smith@corp.io again')
+    r = PIIRewriter()
+    ents = [e for _, _, e in r.detect(text)]
+    assert ents == ['EMAIL_ADDRESS', 'PHONE_NUMBER', 'CN_PHONE', 'CREDIT_CARD', 'US_SSN', 'IP_ADDRESS', 'CN_ID', 'IBAN_CODE', 'URL', 'EMAIL_ADDRESS']
+    rows, dropped = r([{'messages': [{'role': 'user', 'content': text}, {'role': 'assistant', 'content': [{'type': 'text', 'text': 'bob.smith@corp.io'}]}]}])
+    out = rows[0]['messages'][0]['content']
+    assert dropped == [] and 'bob.smith' not in out and '4111 1111 1111 1112' in out and '1.2.3.4.5' in out and out.endswith('@example.com again')
+    fake = out.split('Mail ')[1].split(' ')[0]
+    assert out.count(fake) == 2 and '192.0.2.' in out and 'https://example.com/' in out and '. ' in out.split('https://example.com/')[1][:12]
+    assert '411************1111' in out and '138****5678' in out and r.last_report['EMAIL_ADDRESS'] == 2
+    assert rows[0]['messages'][1]['content'][0]['text'] == 'bob.smith@corp.io'  # only string contents are rewritten
+    h = PIIRewriter(entity_strategy={'EMAIL_ADDRESS': 'hash', 'US_SSN': Strategy.REDACT}, entities=['EMAIL_ADDRESS', 'US_SSN'], salt='s')
+    assert h.rewrite('a@b.co 123-45-6789 10.1.2.3') == f"{hash_short('a@b.co', 's')}  10.1.2.3"
+    ner = PIIRewriter(ner_fn=lambda t: [(t.index('Alice'), t.index('Alice') + 5, 'PERSON')] if 'Alice' in t else [])
+    assert 'Alice' not in ner.rewrite('Alice wrote to alice@x.org') and ' wrote to ' in ner.rewrite('Alice wrote to alice@x.org')
+    with pytest.raises(ValueError):
+        PIIRewriter(entity_strategy={'URL': 'scramble'})
+    assert PIIPresidioFilter is PIIRewriter

@@ -4,6 +4,7 @@ and condensing, a confidence-routed sampler, answer-overlap rewards and trajecto
 from .context import (Chunk, Chunker, Chunks, Condenser, ExtractCondensed, KeywordCondenser, ModelCondenser, MultiTurnCondenseRollout,
                       NativeChunker)
 from .openenv import EnvPoolAdapter, OpenEnv, ShardedEnvPool, normalize_result, observation_text
+from .pii import PIIPresidioFilter, PIIRewriter, Strategy
 from .preprocess import (ChrMinScorer, CodeDetector, ComplexLogicDetector, FixUnicodeFilter, IntentClassifier, IntentDetector, LLMBackend,
                          MathDetector, MessageNormalizer, ModelFilter, OpenAIBackend, ParaphraseScorer, PassNScorer, QualityPreprocessor,
                          ReasoningDetector, RemoveRepeatSentencesFilter, RoundContext, RoundScoreFilter, SamplerBackend, ScoreResult,
