@@ -93,3 +93,25 @@ def test_hybrid_model_trains_and_ulysses_matches_single_process():
     for c in run_ranks(_hybrid_curve, 2, 4):
         for a, b in zip(single, c):
             assert abs(a - b) < 3e-4, (single, c)
+
+
+def test_sampler_carries_linear_attention_state_through_decode():
+    """Hybrid stack in the paged sampler: log-probs of sampled tokens must equal those of one teacher-forced forward
+    over prompt ⊕ tokens (the decode path continues the convolution window and the recurrent state per sequence)."""
+    from twinkle_b200.data_format import SamplingParams
+    from twinkle_b200.models.decoder import PackedBatch
+    from twinkle_b200.sampler import TorchSampler
+    s = TorchSampler(model_id='tiny-hybrid', weight_seed=0, enable_lora=False)
+    prompts = [{'input_ids': [5, 6, 7, 8, 9]}, {'input_ids': [11, 12]}]       # second prompt shorter than the conv window
+    resps = s.sample(prompts, SamplingParams(max_tokens=6, temperature=1.0, seed=3, logprobs=1, num_samples=2))
+    assert [len(r.sequences) for r in resps] == [2, 2]
+    for p, r in zip(prompts, resps):
+        for seq in r.sequences:
+            ids = torch.tensor(p['input_ids'] + seq.tokens)
+            n = len(ids)
+            batch = PackedBatch(ids, torch.arange(n), torch.tensor([0, n], dtype=torch.int32), n)
+            with torch.no_grad():
+                hidden = s.model(batch)
+                lp, _ = s.model.token_logprobs(hidden[:-1], ids[1:])
+            want = lp[len(p['input_ids']) - 1:]
+            assert torch.allclose(torch.tensor(seq.logprobs), want.float(), atol=2e-4), (seq.logprobs, want)

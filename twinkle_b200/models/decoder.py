@@ -218,9 +218,11 @@ class DecoderLayer(nn.Module):
 
     def forward(self, x: torch.Tensor, cos, sin, batch: PackedBatch, kv_sink=None) -> torch.Tensor:
         if self.is_linear:
-            if kv_sink is not None:
-                raise NotImplementedError('the paged-KV sampler does not carry Gated DeltaNet state yet')
-            h = x + self.self_attn(self.input_layernorm(x), batch.cu_seqlens)
+            lin = getattr(kv_sink, 'linear_state', None) if kv_sink is not None else None  # sampler prefill: keep conv tail + state
+            if kv_sink is not None and lin is None:
+                raise NotImplementedError('this kv_sink does not take linear-attention state (give it a linear_state attribute)')
+            sink = (lambda conv, st: lin(self.layer_idx, conv, st)) if lin is not None else None
+            h = x + self.self_attn(self.input_layernorm(x), batch.cu_seqlens, state_sink=sink)
         else:
             h = x + self.self_attn(self.input_layernorm(x), cos, sin, batch, kv_sink)
         n = self.post_attention_layernorm(h)

@@ -82,12 +82,17 @@ def gated_delta_rule_chunked(q, k, v, g, beta, scale: Optional[float] = None, ch
     return o.to(q.dtype), S
 
 
-def gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, scale: Optional[float] = None, chunk: int = 64, recurrent: bool = False):
-    """Packed sequences: every segment starts from an empty state."""
+def gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, scale: Optional[float] = None, chunk: int = 64, recurrent: bool = False,
+                            return_states: bool = False):
+    """Packed sequences: every segment starts from an empty state. With ``return_states`` also the final state of every
+    (non-empty) segment, stacked ``[n, H, dk, dv]`` — what a decoder carries on from after the prompt."""
     fn = gated_delta_rule_recurrent if recurrent else (lambda *a, **kw: gated_delta_rule_chunked(*a, chunk=chunk, **kw))
     bounds = cu_seqlens.tolist()
-    outs = [fn(q[a:b], k[a:b], v[a:b], g[a:b], beta[a:b], scale)[0] for a, b in zip(bounds[:-1], bounds[1:]) if b > a]
-    return torch.cat(outs, 0) if outs else q.new_zeros(0, q.shape[1], v.shape[-1])
+    res = [fn(q[a:b], k[a:b], v[a:b], g[a:b], beta[a:b], scale) for a, b in zip(bounds[:-1], bounds[1:]) if b > a]
+    out = torch.cat([r[0] for r in res], 0) if res else q.new_zeros(0, q.shape[1], v.shape[-1])
+    if return_states:
+        return out, (torch.stack([r[1] for r in res]) if res else q.new_zeros(0, q.shape[1], q.shape[2], v.shape[-1], dtype=torch.float32))
+    return out
 
 
 def causal_conv1d_varlen(x: torch.Tensor, weight: torch.Tensor, cu_seqlens: torch.Tensor, activation: bool = True) -> torch.Tensor:
@@ -124,11 +129,19 @@ class GatedDeltaNet(nn.Module):
         self.attn_parallel = None  # Ulysses strategy: heads are scattered exactly like softmax attention heads
         nn.init.kaiming_uniform_(self.conv_weight, a=math.sqrt(5))
 
-    def forward(self, x: torch.Tensor, cu_seqlens: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, cu_seqlens: torch.Tensor, state_sink=None) -> torch.Tensor:
+        """``state_sink(conv_tail [n, W−1, C], state [n, Hv, dk, dv])``, when given, receives what :meth:`step` needs to
+        continue every segment token by token: the last ``W−1`` pre-convolution rows (zero-padded on the left for short
+        segments) and the final recurrent state."""
         T = x.shape[0]
         kd, vd = self.hk * self.dk, self.hv * self.dv
         qkvz = self.in_proj_qkvz(x)
         qkv, z = qkvz[:, :2 * kd + vd], qkvz[:, 2 * kd + vd:]
+        if state_sink is not None:
+            assert self.attn_parallel is None, 'decoding state is collected on unsharded sequences'
+            w1 = self.conv_weight.shape[1] - 1
+            bounds = cu_seqlens.tolist()
+            tails = [F.pad(qkv[max(a, b - w1):b], (0, 0, w1 - min(w1, b - a), 0)) for a, b in zip(bounds[:-1], bounds[1:]) if b > a]
         b, a = self.in_proj_ba(x).chunk(2, -1)
         beta = torch.sigmoid(b.float())
         g = -self.A_log.float().exp() * F.softplus(a.float() + self.dt_bias.float())      # log decay ≤ 0
@@ -146,7 +159,11 @@ class GatedDeltaNet(nn.Module):
         q, k = F.normalize(q.float(), dim=-1).to(x.dtype), F.normalize(k.float(), dim=-1).to(x.dtype)
         if rep > 1:
             q, k = q.repeat_interleave(rep, 1), k.repeat_interleave(rep, 1)
-        o = gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, chunk=self.chunk)
+        if state_sink is not None:
+            o, states = gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, chunk=self.chunk, return_states=True)
+            state_sink(torch.stack(tails) if tails else qkv.new_zeros(0, w1, qkv.shape[1]), states)
+        else:
+            o = gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, chunk=self.chunk)
         if ap is not None:
             o = ap.gather_heads(o.contiguous())
         # gated RMSNorm per head, gate z
@@ -154,3 +171,30 @@ class GatedDeltaNet(nn.Module):
         of = of * torch.rsqrt(of.pow(2).mean(-1, keepdim=True) + self.eps) * self.norm_weight.float()
         of = of * F.silu(z.float().view(T, self.hv, self.dv))
         return self.out_proj(of.to(x.dtype).reshape(T, vd))
+
+    @torch.no_grad()
+    def step(self, x: torch.Tensor, conv_state: torch.Tensor, state: torch.Tensor):
+        """One token per row: ``x [B, hidden]``, ``conv_state [B, W−1, C]`` (previous pre-convolution rows),
+        ``state [B, Hv, dk, dv]`` (fp32) → (``y [B, hidden]``, new ``conv_state``, new ``state``). Same arithmetic as
+        :meth:`forward` on a sequence extended by this token."""
+        B = x.shape[0]
+        kd, vd = self.hk * self.dk, self.hv * self.dv
+        qkvz = self.in_proj_qkvz(x)
+        qkv, z = qkvz[:, :2 * kd + vd], qkvz[:, 2 * kd + vd:]
+        b, a = self.in_proj_ba(x).chunk(2, -1)
+        beta = torch.sigmoid(b.float())
+        g = -self.A_log.float().exp() * F.softplus(a.float() + self.dt_bias.float())
+        window = torch.cat([conv_state.to(qkv.dtype), qkv.unsqueeze(1)], 1)                    # [B, W, C]
+        conv = F.silu((window * self.conv_weight.t().to(qkv.dtype).unsqueeze(0)).sum(1))       # depth-wise causal conv, last position
+        q, k, v = conv[:, :kd].view(B, self.hk, self.dk), conv[:, kd:2 * kd].view(B, self.hk, self.dk), conv[:, 2 * kd:].view(B, self.hv, self.dv)
+        q, k = F.normalize(q.float(), dim=-1), F.normalize(k.float(), dim=-1)
+        rep = self.hv // self.hk
+        if rep > 1:
+            q, k = q.repeat_interleave(rep, 1), k.repeat_interleave(rep, 1)
+        S = state.float() * g.exp()[:, :, None, None]
+        kv = torch.einsum('bhk,bhkv->bhv', k, S)
+        S = S + torch.einsum('bhk,bhv->bhkv', k, (v.float() - kv) * beta[:, :, None])
+        o = torch.einsum('bhk,bhkv->bhv', q * self.dk ** -0.5, S)
+        o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + self.eps) * self.norm_weight.float()
+        o = o * F.silu(z.float().view(B, self.hv, self.dv))
+        return self.out_proj(o.to(x.dtype).reshape(B, vd)), window[:, 1:].contiguous(), S

@@ -75,6 +75,7 @@ class _Seq:
     generator: Optional[torch.Generator] = None
     routed: Optional[List[torch.Tensor]] = None
     text_tail: str = ''
+    linear: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)  # layer → (conv rows, recurrent state) of linear-attention layers
 
     @property
     def length(self) -> int:
@@ -129,6 +130,11 @@ class NativeEngine:
             for s, a, b in zip(seqs, bounds[:-1], bounds[1:]):
                 self.cache.write(layer, s.blocks, 0, k[a:b], v[a:b])
 
+        def linear_state(layer: int, conv: torch.Tensor, state: torch.Tensor) -> None:  # hybrid stacks: what decode continues from
+            for i, s in enumerate(seqs):
+                s.linear[layer] = (conv[i], state[i])
+
+        sink.linear_state = linear_state
         batch = PackedBatch(ids, pos, cu, max(lens))
         self.model.set_record_routing(self.capture_routing)
         with lora_batch(self._lora_for(seqs, lens)):
@@ -141,8 +147,9 @@ class NativeEngine:
         return hidden
 
     # --------------------------------------------------------------- decode
-    def _decode_body(self, tokens, positions, table, seq_lens, lora: Optional[LoraBatch]) -> torch.Tensor:
-        """One decode token per row from device tensors only (what a CUDA graph captures)."""
+    def _decode_body(self, tokens, positions, table, seq_lens, lora: Optional[LoraBatch], seqs: Optional[List[_Seq]] = None) -> torch.Tensor:
+        """One decode token per row from device tensors only (what a CUDA graph captures). Linear-attention layers of
+        hybrid stacks keep their state on the sequences (``seqs``) and always run eagerly."""
         cfg, B = self.cfg, tokens.shape[0]
         cos, sin = ops.rope_tables(positions, cfg.head_dim, cfg.rope_theta)
         x = self.model.embed_tokens(tokens)
@@ -152,6 +159,16 @@ class NativeEngine:
             for li, layer in enumerate(self.model.layers):
                 at = layer.self_attn
                 h = layer.input_layernorm(x)
+                if getattr(layer, 'is_linear', False):
+                    conv = torch.stack([s.linear[li][0] for s in seqs])
+                    st = torch.stack([s.linear[li][1] for s in seqs])
+                    y, conv, st = at.step(h, conv, st)
+                    for i, s in enumerate(seqs):
+                        s.linear[li] = (conv[i], st[i])
+                    x = x + y
+                    n = layer.post_attention_layernorm(x)
+                    x = x + (layer.mlp(n) if not layer.is_moe else layer.mlp(n, None))
+                    continue
                 qkv = at.qkv_proj(h)
                 qw = at.q_norm.weight if at.q_norm is not None else None
                 kw = at.k_norm.weight if at.k_norm is not None else None
@@ -229,7 +246,7 @@ class NativeEngine:
             table[i, :len(s.blocks)] = torch.tensor(s.blocks, dtype=torch.int32)
         seq_lens = torch.tensor([s.length for s in seqs], dtype=torch.int32, device=self.device)
         self.model.set_record_routing(self.capture_routing)
-        logits = self._decode_body(last_tokens, positions, table, seq_lens, lora)
+        logits = self._decode_body(last_tokens, positions, table, seq_lens, lora, seqs)
         if self.capture_routing:
             routed = self.model.collect_routed_experts()  # per layer [B, k]: the experts of the token just fed
             if routed is not None:
@@ -351,7 +368,7 @@ class NativeEngine:
                 live = nxt
         for s in seqs:
             self.cache.release(s.blocks)
-            s.blocks = []
+            s.blocks, s.linear = [], {}
             if not s.params.scoring_only:
                 responses[s.request].sequences.append(SampledSequence(stop_reason=s.stop_reason, tokens=s.tokens, logprobs=s.logprobs,
                                                                       topk_logprobs=s.topk or None, routed_experts=s.routed))
