@@ -115,3 +115,28 @@ def test_sampler_carries_linear_attention_state_through_decode():
                 lp, _ = s.model.token_logprobs(hidden[:-1], ids[1:])
             want = lp[len(p['input_ids']) - 1:]
             assert torch.allclose(torch.tensor(seq.logprobs), want.float(), atol=2e-4), (seq.logprobs, want)
+
+
+def test_hybrid_checkpoint_round_trip_keeps_layer_types(tmp_path):
+    import glob
+    from safetensors import safe_open
+    from twinkle_b200.model import TransformersModel
+    from twinkle_b200.models.config import DecoderConfig
+    m = TransformersModel(model_id='tiny-hybrid', seed=0)
+    ids = torch.randint(0, 1024, (41, ), generator=torch.Generator().manual_seed(2))
+    batch = [{'input_ids': ids[:-1].tolist(), 'labels': ids[1:].tolist()}]
+    out = m.save('ck', str(tmp_path))
+    cfg = DecoderConfig.from_pretrained(out)
+    assert cfg.layer_types == ['linear_attention', 'full_attention', 'linear_attention', 'full_attention']
+    assert (cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim) == (2, 4, 32, 32)
+    names = set()
+    for f in glob.glob(out + '/*.safetensors'):
+        with safe_open(f, 'pt') as fh:
+            names |= set(fh.keys())
+            if 'model.layers.0.linear_attn.conv1d.weight' in fh.keys():
+                assert fh.get_tensor('model.layers.0.linear_attn.conv1d.weight').dim() == 3   # Conv1d layout [C, 1, W]
+    assert {'model.layers.0.linear_attn.in_proj_qkvz.weight', 'model.layers.0.linear_attn.A_log', 'model.layers.0.linear_attn.norm.weight',
+            'model.layers.1.self_attn.q_proj.weight'} <= names and 'model.layers.0.self_attn.conv_weight' not in names
+    m2 = TransformersModel(model_id=out, seed=9)
+    a, b = m.forward_only(inputs=batch), m2.forward_only(inputs=batch)
+    assert torch.allclose(torch.as_tensor(a['logps']).float(), torch.as_tensor(b['logps']).float(), atol=1e-5)

@@ -106,3 +106,46 @@ def test_expert_parallel_training_matches_single_process():
         for (l1, n1), (l2, n2) in zip(single, c):
             assert abs(l1 - l2) < 2e-4, (single, c)
             assert abs(n1 - n2) < 2e-3 * max(1.0, n1), (single, c)
+
+
+def test_shared_expert_math_and_hf_round_trip(tmp_path):
+    """MoE block with an always-on gated expert: output = routed + sigmoid(gate·x)·MLP(x); the HF checkpoint written
+    by ``save`` (shared expert split into gate/up/down, config field kept) loads back to the same loss."""
+    import torch.nn.functional as F
+    from twinkle_b200.model import TransformersModel
+    from twinkle_b200.models.config import DecoderConfig
+    m = TransformersModel(model_id='tiny-moe-shared', seed=0)
+    blk = m.model.layers[0].mlp
+    assert blk.shared_expert is not None and blk.shared_expert_gate.weight.shape == (1, 256)
+    x = torch.randn(12, 256)
+    with torch.no_grad():
+        full = blk(x)
+        shared, gate = blk.shared_expert, blk.shared_expert_gate
+        blk.shared_expert = blk.shared_expert_gate = None
+        routed = blk(x)
+        blk.shared_expert, blk.shared_expert_gate = shared, gate
+        g, u = F.linear(x, shared.gate_up_proj.weight).chunk(2, -1)
+        want = routed + torch.sigmoid(F.linear(x, gate.weight)) * F.linear(F.silu(g) * u, shared.down_proj.weight)
+    assert torch.allclose(full, want, atol=1e-5)
+    ids = torch.randint(0, 1024, (33, ), generator=torch.Generator().manual_seed(1))
+    batch = [{'input_ids': ids[:-1].tolist(), 'labels': ids[1:].tolist()}]
+    m.set_optimizer('AdamW', lr=1e-2)
+    first = m.forward_backward(inputs=batch)['loss']
+    before = gate.weight.detach().clone()
+    m.clip_grad_and_step(max_grad_norm=1.0)
+    assert not torch.equal(before, gate.weight.detach())          # the shared path trains
+    out = m.save('ck', str(tmp_path))
+    cfg = DecoderConfig.from_pretrained(out)
+    assert cfg.shared_expert_intermediate_size == 192 and cfg.num_experts == 8
+    from safetensors import safe_open
+    import glob
+    names = set()
+    for f in glob.glob(out + '/*.safetensors'):
+        with safe_open(f, 'pt') as fh:
+            names |= set(fh.keys())
+    assert {'model.layers.0.mlp.shared_expert.gate_proj.weight', 'model.layers.0.mlp.shared_expert.up_proj.weight',
+            'model.layers.0.mlp.shared_expert.down_proj.weight', 'model.layers.0.mlp.shared_expert_gate.weight'} <= names
+    m2 = TransformersModel(model_id=out, seed=5)
+    a, b = m.forward_only(inputs=batch, return_logits=False), m2.forward_only(inputs=batch, return_logits=False)
+    assert torch.allclose(torch.as_tensor(a['logps']).float(), torch.as_tensor(b['logps']).float(), atol=1e-5)
+    assert float(first) > 0

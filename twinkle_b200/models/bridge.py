@@ -50,9 +50,16 @@ def internal_to_hf(name: str, tensor: torch.Tensor, cfg: DecoderConfig) -> List[
         q, k, v = tensor.split([cfg.q_size, cfg.kv_size, cfg.kv_size], dim=0)
         return [(_hf_layer(i, f'self_attn.q_proj.{kind}'), q), (_hf_layer(i, f'self_attn.k_proj.{kind}'), k),
                 (_hf_layer(i, f'self_attn.v_proj.{kind}'), v)]
-    if rest == 'mlp.gate_up_proj.weight':
+    if rest in ('mlp.gate_up_proj.weight', 'mlp.shared_expert.gate_up_proj.weight'):
         g, u = tensor.chunk(2, dim=0)
-        return [(_hf_layer(i, 'mlp.gate_proj.weight'), g), (_hf_layer(i, 'mlp.up_proj.weight'), u)]
+        pre = rest[:-len('gate_up_proj.weight')]
+        return [(_hf_layer(i, pre + 'gate_proj.weight'), g), (_hf_layer(i, pre + 'up_proj.weight'), u)]
+    if rest == 'self_attn.conv_weight':          # depth-wise filters: HF keeps Conv1d's [C, 1, W], attention block named linear_attn
+        return [(_hf_layer(i, 'linear_attn.conv1d.weight'), tensor.unsqueeze(1))]
+    if rest == 'self_attn.norm_weight':
+        return [(_hf_layer(i, 'linear_attn.norm.weight'), tensor)]
+    if rest.startswith('self_attn.') and cfg.layer_types and cfg.layer_types[i] == 'linear_attention':
+        return [(_hf_layer(i, 'linear_attn.' + rest[len('self_attn.'):]), tensor)]
     if rest == 'mlp.experts.gate_up_proj':
         out = []
         for e in range(tensor.shape[0]):
@@ -78,8 +85,15 @@ def hf_names_for(name: str, cfg: DecoderConfig) -> List[str]:
     if rest.startswith('self_attn.qkv_proj.'):
         kind = rest.rsplit('.', 1)[1]
         return [_hf_layer(i, f'self_attn.{p}_proj.{kind}') for p in 'qkv']
-    if rest == 'mlp.gate_up_proj.weight':
-        return [_hf_layer(i, 'mlp.gate_proj.weight'), _hf_layer(i, 'mlp.up_proj.weight')]
+    if rest in ('mlp.gate_up_proj.weight', 'mlp.shared_expert.gate_up_proj.weight'):
+        pre = rest[:-len('gate_up_proj.weight')]
+        return [_hf_layer(i, pre + 'gate_proj.weight'), _hf_layer(i, pre + 'up_proj.weight')]
+    if rest == 'self_attn.conv_weight':
+        return [_hf_layer(i, 'linear_attn.conv1d.weight')]
+    if rest == 'self_attn.norm_weight':
+        return [_hf_layer(i, 'linear_attn.norm.weight')]
+    if rest.startswith('self_attn.') and cfg.layer_types and cfg.layer_types[i] == 'linear_attention':
+        return [_hf_layer(i, 'linear_attn.' + rest[len('self_attn.'):])]
     if rest == 'mlp.experts.gate_up_proj':
         return [_hf_layer(i, f'mlp.experts.{e}.{p}_proj.weight') for e in range(cfg.num_experts) for p in ('gate', 'up')]
     if rest == 'mlp.experts.down_proj':
@@ -101,6 +115,8 @@ def hf_to_internal(name: str, cfg: DecoderConfig, get: Callable[[str], torch.Ten
         lo, hi = expert_range or (0, cfg.num_experts)
         return torch.stack([get(_hf_layer(i, f'mlp.experts.{e}.down_proj.weight')) for e in range(lo, hi)])
     parts = [get(n) for n in hf_names_for(name, cfg)]
+    if rest == 'self_attn.conv_weight' and parts[0].dim() == 3:
+        return parts[0].squeeze(1)
     return parts[0] if len(parts) == 1 else torch.cat(parts, 0)
 
 

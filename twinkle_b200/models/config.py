@@ -101,6 +101,12 @@ class DecoderConfig:
             num_experts=cfg.get('num_experts', cfg.get('num_local_experts', 0)) or 0,
             num_experts_per_tok=cfg.get('num_experts_per_tok', 8), moe_intermediate_size=cfg.get('moe_intermediate_size', 768),
             norm_topk_prob=bool(cfg.get('norm_topk_prob', True)), router_aux_loss_coef=float(cfg.get('router_aux_loss_coef', 0.0)),
+            shared_expert_intermediate_size=int(cfg.get('shared_expert_intermediate_size', 0) or 0),
+            rms_norm_offset=float(cfg.get('rms_norm_offset', 1.0 if mt.startswith('gemma') else 0.0)),
+            layer_types=list(cfg['layer_types']) if cfg.get('layer_types') and 'linear_attention' in cfg['layer_types'] else None,
+            linear_num_key_heads=cfg.get('linear_num_key_heads', 16), linear_num_value_heads=cfg.get('linear_num_value_heads', 32),
+            linear_key_head_dim=cfg.get('linear_key_head_dim', 128), linear_value_head_dim=cfg.get('linear_value_head_dim', 128),
+            linear_conv_kernel_dim=cfg.get('linear_conv_kernel_dim', 4),
             initializer_range=cfg.get('initializer_range', 0.02), model_type=mt,
             torch_dtype=str(cfg.get('torch_dtype', cfg.get('dtype', 'bfloat16'))),
             max_position_embeddings=cfg.get('max_position_embeddings', 40960), pad_token_id=cfg.get('pad_token_id'),
@@ -127,6 +133,14 @@ class DecoderConfig:
             d.update(num_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
                      moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob,
                      router_aux_loss_coef=self.router_aux_loss_coef, decoder_sparse_step=1, mlp_only_layers=[])
+            if self.shared_expert_intermediate_size:
+                d['shared_expert_intermediate_size'] = self.shared_expert_intermediate_size
+        if self.rms_norm_offset:
+            d['rms_norm_offset'] = self.rms_norm_offset
+        if self.layer_types:
+            d.update(layer_types=list(self.layer_types), linear_num_key_heads=self.linear_num_key_heads,
+                     linear_num_value_heads=self.linear_num_value_heads, linear_key_head_dim=self.linear_key_head_dim,
+                     linear_value_head_dim=self.linear_value_head_dim, linear_conv_kernel_dim=self.linear_conv_kernel_dim)
         return d
 
     def save_pretrained(self, path: str) -> None:
@@ -147,6 +161,9 @@ PRESETS: Dict[str, Dict[str, Any]] = {
     'tiny-moe': dict(vocab_size=1024, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
                      head_dim=64, rope_theta=1e4, tie_word_embeddings=True, num_experts=8, num_experts_per_tok=2,
                      moe_intermediate_size=128, router_aux_loss_coef=1e-3, torch_dtype='float32'),
+    'tiny-moe-shared': dict(vocab_size=1024, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                            head_dim=64, rope_theta=1e4, tie_word_embeddings=True, num_experts=8, num_experts_per_tok=2,
+                            moe_intermediate_size=128, shared_expert_intermediate_size=192, torch_dtype='float32'),
     'qwen3-0.6b': dict(hidden_size=1024, intermediate_size=3072, num_hidden_layers=28, num_attention_heads=16,
                        num_key_value_heads=8, head_dim=128, tie_word_embeddings=True),
     'qwen3-8b': dict(hidden_size=4096, intermediate_size=12288, num_hidden_layers=36, num_attention_heads=32,

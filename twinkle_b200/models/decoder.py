@@ -96,8 +96,10 @@ class MLP(nn.Module):
         self.gate_up_proj = Linear(cfg.hidden_size, 2 * i, parts=[('gate_proj', i), ('up_proj', i)])
         self.down_proj = Linear(i, cfg.hidden_size, name='down_proj')
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.down_proj(ops.swiglu(self.gate_up_proj(x)), value_unused=True)
+    def forward(self, x: torch.Tensor, value_unused: bool = True) -> torch.Tensor:
+        """``value_unused=True`` (the block's output only feeds the residual add) lets a recompute pass skip the last GEMM;
+        callers that multiply or otherwise read the output pass ``False``."""
+        return self.down_proj(ops.swiglu(self.gate_up_proj(x)), value_unused=value_unused)
 
 
 class Experts(nn.Module):
@@ -168,6 +170,13 @@ class MoEBlock(nn.Module):
         self.cfg, self.layer_idx = cfg, layer_idx
         self.gate = Linear(cfg.hidden_size, cfg.num_experts, name='gate')
         self.experts = Experts(cfg)
+        # an always-on expert beside the routed ones, scaled per token by a sigmoid gate (Qwen2-MoE / Qwen3-Next style);
+        # replicated under expert parallelism (reference ``moe/expert_parallel.py:329-382``)
+        if cfg.shared_expert_intermediate_size > 0:
+            self.shared_expert = MLP(cfg, cfg.shared_expert_intermediate_size)
+            self.shared_expert_gate = Linear(cfg.hidden_size, 1, name='shared_expert_gate')
+        else:
+            self.shared_expert = self.shared_expert_gate = None
         self.moe_parallel = None  # expert-parallel strategy or None
         self.last_routed: Optional[torch.Tensor] = None
         self.last_aux: Optional[torch.Tensor] = None
@@ -187,7 +196,7 @@ class MoEBlock(nn.Module):
             self.last_aux = ops.ref.moe_aux_loss(probs, idx, E)
         mp = self.moe_parallel
         if mp is not None:
-            return mp.forward(self, x, w, idx)
+            return self._with_shared(x, mp.forward(self, x, w, idx))
         # local: expert-sorted layout whose segments start on 128-row boundaries (grouped GEMM tiles and the
         # per-expert wgrad reduction ranges then never straddle two experts); padding rows are zero.  Dispatch and
         # combine are gathers through index maps built on the device — no host read anywhere in the block.
@@ -196,7 +205,13 @@ class MoEBlock(nn.Module):
         row_of, src_tok, slot_of_row = ops.moe_index_maps(order, rows, bound, k)
         xs = ops.moe_dispatch(x, src_tok, row_of)
         y = self.experts(xs, offsets)
-        return ops.moe_combine(y, w, row_of, src_tok, slot_of_row)
+        return self._with_shared(x, ops.moe_combine(y, w, row_of, src_tok, slot_of_row))
+
+    def _with_shared(self, x: torch.Tensor, routed: torch.Tensor) -> torch.Tensor:
+        if self.shared_expert is None:
+            return routed
+        gate = torch.sigmoid(self.shared_expert_gate(x).float()).to(x.dtype)
+        return routed + gate * self.shared_expert(x, value_unused=False)
 
 
 class DecoderLayer(nn.Module):
