@@ -217,3 +217,39 @@ def test_reasoning_split_and_qwen3_chat_template_patches():
         chat_template = '{{ messages }}'
 
     assert not apply_patch(Other(), 'Qwen3ChatTemplate').applied
+
+
+def test_rope_scaling_matches_transformers_and_travels_in_config():
+    import pytest
+    import torch
+    from twinkle_b200.models.config import DecoderConfig
+    from twinkle_b200.ops.reference import rope_inv_freq, rope_tables
+    variants = ({'rope_type': 'llama3', 'factor': 8.0, 'low_freq_factor': 1.0, 'high_freq_factor': 4.0, 'original_max_position_embeddings': 8192},
+                {'rope_type': 'yarn', 'factor': 4.0, 'original_max_position_embeddings': 32768}, {'rope_type': 'linear', 'factor': 2.0})
+    try:
+        from transformers import LlamaConfig
+        from transformers.modeling_rope_utils import ROPE_INIT_FUNCTIONS
+        for rs in variants:
+            c = LlamaConfig(hidden_size=4096, num_attention_heads=32, max_position_embeddings=131072, rope_parameters={**rs, 'rope_theta': 500000.0})
+            want, att = ROPE_INIT_FUNCTIONS[rs['rope_type']](c, 'cpu')
+            got, a = rope_inv_freq(128, 500000.0, rs)
+            assert torch.allclose(want, got, rtol=1e-6, atol=0) and a == pytest.approx(att)
+    except (ImportError, TypeError, KeyError):  # other transformers versions spell the config differently
+        pass
+    plain, _ = rope_inv_freq(128, 1e6)
+    lin, _ = rope_inv_freq(128, 1e6, {'type': 'linear', 'factor': 4.0})
+    assert torch.allclose(lin * 4, plain)
+    l3, _ = rope_inv_freq(128, 5e5, variants[0])
+    base, _ = rope_inv_freq(128, 5e5)
+    assert torch.equal(l3[:8], base[:8]) and torch.allclose(l3[-1], base[-1] / 8)       # fast dims untouched, slowest ÷ factor
+    cos, sin = rope_tables(torch.arange(4), 128, 5e5, variants[1])
+    assert cos[0, 0] == pytest.approx(0.1 * torch.log(torch.tensor(4.0)).item() + 1.0)   # yarn scales cos/sin
+    with pytest.raises(NotImplementedError):
+        rope_inv_freq(128, 1e6, {'rope_type': 'longrope', 'factor': 2.0})
+    cfg = DecoderConfig.from_hf({'model_type': 'llama', 'hidden_size': 256, 'num_attention_heads': 4, 'max_position_embeddings': 131072,
+                                 'rope_scaling': {'rope_type': 'llama3', 'factor': 8.0, 'low_freq_factor': 1.0, 'high_freq_factor': 4.0,
+                                                  'original_max_position_embeddings': 8192}, 'rope_theta': 5e5})
+    assert cfg.rope_scaling['rope_type'] == 'llama3' and not cfg.qk_norm
+    assert DecoderConfig.from_hf(cfg.to_hf()).rope_scaling == cfg.rope_scaling
+    assert DecoderConfig.from_hf({'model_type': 'qwen3', 'rope_scaling': None}).rope_scaling is None
+    assert DecoderConfig.from_hf({'model_type': 'qwen3', 'rope_parameters': {'rope_type': 'default', 'rope_theta': 1e6}}).rope_scaling is None

@@ -177,7 +177,7 @@ class MegatronModel(TwinkleModel):
                     pass
             else:
                 h = x
-            cos, sin = ops.rope_tables(batch.position_ids, self.config.head_dim, self.config.rope_theta)
+            cos, sin = ops.rope_tables(batch.position_ids, self.config.head_dim, self.config.rope_theta, self.config.rope_scaling)
             for layer in m.layers:
                 h = layer(h, cos, sin, batch)
             if not m.has_head:

@@ -13,6 +13,21 @@ from dataclasses import asdict, dataclass, field
 from typing import List, Any, Dict, Optional
 
 
+def _rope_scaling_of(cfg: Dict[str, Any]) -> Optional[Dict[str, Any]]:
+    """``rope_scaling`` (or the newer ``rope_parameters``) of a HF config when it describes a long-context variant."""
+    rs = cfg.get('rope_scaling') or cfg.get('rope_parameters')
+    if not isinstance(rs, dict):
+        return None
+    kind = rs.get('rope_type', rs.get('type', 'default'))
+    if kind in (None, 'default'):
+        return None
+    out = {k: v for k, v in rs.items() if k != 'rope_theta'}
+    out.setdefault('rope_type', kind)
+    if kind in ('llama3', 'yarn') and not out.get('original_max_position_embeddings'):
+        out['original_max_position_embeddings'] = cfg.get('max_position_embeddings', 4096)
+    return out
+
+
 @dataclass
 class DecoderConfig:
     vocab_size: int = 151936
@@ -24,6 +39,7 @@ class DecoderConfig:
     head_dim: int = 128
     rms_norm_eps: float = 1e-6
     rope_theta: float = 1e6
+    rope_scaling: Optional[Dict[str, Any]] = None  # HF mapping: {'rope_type': 'llama3' | 'yarn' | 'linear', 'factor': …}
     tie_word_embeddings: bool = False
     qk_norm: bool = True
     attention_bias: bool = False
@@ -96,7 +112,7 @@ class DecoderConfig:
             num_attention_heads=heads, num_key_value_heads=cfg.get('num_key_value_heads', heads),
             head_dim=cfg.get('head_dim') or cfg.get('hidden_size', 4096) // heads, rms_norm_eps=cfg.get('rms_norm_eps', 1e-6),
             rope_theta=float(cfg.get('rope_theta', (cfg.get('rope_parameters') or {}).get('rope_theta', 1e6))),
-            tie_word_embeddings=bool(cfg.get('tie_word_embeddings', False)),
+            rope_scaling=_rope_scaling_of(cfg), tie_word_embeddings=bool(cfg.get('tie_word_embeddings', False)),
             qk_norm=mt.startswith('qwen3'), attention_bias=bool(cfg.get('attention_bias', mt == 'qwen2')),
             num_experts=cfg.get('num_experts', cfg.get('num_local_experts', 0)) or 0,
             num_experts_per_tok=cfg.get('num_experts_per_tok', 8), moe_intermediate_size=cfg.get('moe_intermediate_size', 768),
@@ -137,6 +153,8 @@ class DecoderConfig:
                 d['shared_expert_intermediate_size'] = self.shared_expert_intermediate_size
         if self.rms_norm_offset:
             d['rms_norm_offset'] = self.rms_norm_offset
+        if self.rope_scaling:
+            d['rope_scaling'] = dict(self.rope_scaling)
         if self.layer_types:
             d.update(layer_types=list(self.layer_types), linear_num_key_heads=self.linear_num_key_heads,
                      linear_num_value_heads=self.linear_num_value_heads, linear_key_head_dim=self.linear_key_head_dim,

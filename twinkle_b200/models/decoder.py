@@ -309,7 +309,7 @@ class DecoderModel(nn.Module):
 
     def forward(self, batch: PackedBatch, hidden: Optional[torch.Tensor] = None, kv_sink=None) -> torch.Tensor:
         x = self.embed(batch) if hidden is None else hidden
-        cos, sin = ops.rope_tables(batch.position_ids, self.cfg.head_dim, self.cfg.rope_theta)
+        cos, sin = ops.rope_tables(batch.position_ids, self.cfg.head_dim, self.cfg.rope_theta, self.cfg.rope_scaling)
         full = None
         for layer in self.layers:
             ap = getattr(getattr(layer, 'self_attn', None), 'attn_parallel', None)

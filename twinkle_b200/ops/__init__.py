@@ -218,8 +218,8 @@ def qkv_norm_rope(qkv: torch.Tensor, q_weight, k_weight, cos, sin, hq: int, hkv:
     return q, k, v
 
 
-def rope_tables(positions: torch.Tensor, head_dim: int, theta: float = 1e6):
-    return ref.rope_tables(positions, head_dim, theta)
+def rope_tables(positions: torch.Tensor, head_dim: int, theta: float = 1e6, scaling: Optional[dict] = None):
+    return ref.rope_tables(positions, head_dim, theta, scaling)
 
 
 # ------------------------------------------------------------------ swiglu

@@ -28,10 +28,64 @@ def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, e
 
 
 # ---------------------------------------------------------------------- rope
-def rope_tables(positions: torch.Tensor, head_dim: int, theta: float = 1e6) -> Tuple[torch.Tensor, torch.Tensor]:
-    """cos/sin ``[T, head_dim/2]`` in fp32 for integer ``positions [T]``."""
-    inv_freq = 1.0 / (theta**(torch.arange(0, head_dim, 2, dtype=torch.float32, device=positions.device) / head_dim))
+def rope_inv_freq(head_dim: int, theta: float, scaling: Optional[dict] = None, device=None) -> Tuple[torch.Tensor, float]:
+    """Inverse frequencies ``[head_dim/2]`` and the factor applied to cos/sin, for plain RoPE or a long-context variant
+    given as a Hugging Face ``rope_scaling`` mapping (``rope_type`` / ``type``):
+
+    * ``linear``: all frequencies ÷ ``factor``;
+    * ``llama3``: wavelengths above ``original_max / low_freq_factor`` ÷ ``factor``, those below
+      ``original_max / high_freq_factor`` unchanged, a linear blend between;
+    * ``yarn``: per-dimension blend of interpolated (÷ ``factor``) and original frequencies along a ramp between the
+      dimensions that complete ``beta_fast`` and ``beta_slow`` rotations over the original window; cos/sin scaled by
+      ``attention_factor`` (default ``0.1·ln(factor) + 1``).
+
+    ``default`` / ``None`` give plain RoPE. Other types raise."""
+    import math
+    inv = 1.0 / (theta**(torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
+    kind = (scaling or {}).get('rope_type', (scaling or {}).get('type', 'default'))
+    if not scaling or kind in ('default', None):
+        return inv, 1.0
+    factor = float(scaling.get('factor', 1.0))
+    if kind == 'linear':
+        return inv / factor, 1.0
+    if kind == 'llama3':
+        lo, hi = float(scaling.get('low_freq_factor', 1.0)), float(scaling.get('high_freq_factor', 4.0))
+        orig = float(scaling['original_max_position_embeddings'])
+        wavelen = 2 * math.pi / inv
+        smooth = ((orig / wavelen - lo) / (hi - lo)).clamp(0.0, 1.0)
+        blended = (1 - smooth) * inv / factor + smooth * inv
+        out = torch.where(wavelen > orig / lo, inv / factor, torch.where(wavelen < orig / hi, inv, blended))
+        return out, 1.0
+    if kind == 'yarn':
+        orig = float(scaling.get('original_max_position_embeddings') or scaling.get('max_position_embeddings', 4096))
+        fast, slow = float(scaling.get('beta_fast') or 32), float(scaling.get('beta_slow') or 1)
+        att = scaling.get('attention_factor')
+        if att is None:
+            ms, ms_all = scaling.get('mscale'), scaling.get('mscale_all_dim')
+            get = lambda sc, m=1.0: 1.0 if sc <= 1 else 0.1 * m * math.log(sc) + 1.0  # noqa: E731
+            att = get(factor, ms) / get(factor, ms_all) if ms and ms_all else get(factor)
+
+        def corr_dim(rot: float) -> float:
+            return head_dim * math.log(orig / (rot * 2 * math.pi)) / (2 * math.log(theta))
+
+        low, high = corr_dim(fast), corr_dim(slow)
+        if scaling.get('truncate', True):
+            low, high = math.floor(low), math.ceil(high)
+        low, high = max(low, 0), min(high, head_dim - 1)
+        if low == high:
+            high += 0.001
+        ramp = ((torch.arange(head_dim // 2, dtype=torch.float32, device=device) - low) / (high - low)).clamp(0, 1)
+        keep = 1 - ramp                                  # 1 → original frequency, 0 → interpolated
+        return inv / factor * (1 - keep) + inv * keep, float(att)
+    raise NotImplementedError(f'rope scaling type {kind!r} is not supported (default, linear, llama3, yarn are)')
+
+
+def rope_tables(positions: torch.Tensor, head_dim: int, theta: float = 1e6, scaling: Optional[dict] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin ``[T, head_dim/2]`` in fp32 for integer ``positions [T]`` (see :func:`rope_inv_freq` for ``scaling``)."""
+    inv_freq, att = rope_inv_freq(head_dim, theta, scaling, positions.device)
     ang = positions.float()[:, None] * inv_freq[None, :]
+    if att != 1.0:
+        return ang.cos() * att, ang.sin() * att
     return ang.cos(), ang.sin()
 
 

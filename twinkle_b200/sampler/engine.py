@@ -151,7 +151,7 @@ class NativeEngine:
         """One decode token per row from device tensors only (what a CUDA graph captures). Linear-attention layers of
         hybrid stacks keep their state on the sequences (``seqs``) and always run eagerly."""
         cfg, B = self.cfg, tokens.shape[0]
-        cos, sin = ops.rope_tables(positions, cfg.head_dim, cfg.rope_theta)
+        cos, sin = ops.rope_tables(positions, cfg.head_dim, cfg.rope_theta, cfg.rope_scaling)
         x = self.model.embed_tokens(tokens)
         blk = table.gather(1, (positions // self.cache.block_size).unsqueeze(1)).squeeze(1).long()
         off = positions % self.cache.block_size
