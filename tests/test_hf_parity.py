@@ -1,0 +1,75 @@
+"""The owned decoder against the Hugging Face implementations of the families it claims: random tiny models saved by
+``transformers`` must give the same logits after loading here (fp32, CPU), and a checkpoint saved here must load in
+``transformers`` with the same logits."""
+import pytest
+import torch
+
+transformers = pytest.importorskip('transformers')
+
+COMMON = dict(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              max_position_embeddings=512, rope_theta=10000.0)
+
+
+def _cases():
+    T = transformers
+    return {
+        'qwen3': (lambda: T.Qwen3Config(head_dim=32, tie_word_embeddings=False, **COMMON), 'Qwen3ForCausalLM'),
+        'llama_tied': (lambda: T.LlamaConfig(tie_word_embeddings=True, **COMMON), 'LlamaForCausalLM'),
+        'llama3_rope': (lambda: T.LlamaConfig(tie_word_embeddings=False, **{**COMMON, 'max_position_embeddings': 4096},
+                                              rope_scaling={'rope_type': 'llama3', 'factor': 8.0, 'low_freq_factor': 1.0, 'high_freq_factor': 4.0,
+                                                            'original_max_position_embeddings': 64}), 'LlamaForCausalLM'),
+        'qwen2_bias': (lambda: T.Qwen2Config(tie_word_embeddings=False, **COMMON), 'Qwen2ForCausalLM'),
+        'qwen3_moe': (lambda: T.Qwen3MoeConfig(head_dim=32, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, norm_topk_prob=True,
+                                               decoder_sparse_step=1, mlp_only_layers=[], **COMMON), 'Qwen3MoeForCausalLM'),
+        'qwen2_moe_shared': (lambda: T.Qwen2MoeConfig(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=96,
+                                                      norm_topk_prob=False, decoder_sparse_step=1, mlp_only_layers=[], **COMMON), 'Qwen2MoeForCausalLM'),
+    }
+
+
+def _hf_model(name):
+    make, cls = _cases()[name]
+    try:
+        cfg = make()
+        hf = getattr(transformers, cls)(cfg).float().eval()
+    except Exception as e:  # a transformers build without this family or with other argument names
+        pytest.skip(f'{name}: {type(e).__name__}: {e}')
+    torch.manual_seed(0)
+    for n, p in hf.named_parameters():  # non-trivial norms and biases, so that a swapped or dropped tensor shows
+        if 'norm' in n:
+            torch.nn.init.normal_(p, 1.0, 0.1)
+        elif p.dim() == 1:
+            torch.nn.init.normal_(p, 0.0, 0.1)
+    return hf
+
+
+def _ours(path, ids):
+    from twinkle_b200.model import TransformersModel
+    from twinkle_b200.models.decoder import PackedBatch
+    m = TransformersModel(model_id=path)
+    n = ids.shape[0]
+    with torch.no_grad():
+        return m, m.model.logits(m.model(PackedBatch(ids, torch.arange(n), torch.tensor([0, n], dtype=torch.int32), n))).float()
+
+
+@pytest.mark.parametrize('name', list(_cases()))
+def test_hf_checkpoint_gives_the_same_logits_here(name, tmp_path):
+    hf = _hf_model(name)
+    hf.save_pretrained(str(tmp_path / 'hf'), safe_serialization=True)
+    ids = torch.randint(0, 512, (1, 150 if name == 'llama3_rope' else 37), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = hf(ids).logits[0]
+    _, got = _ours(str(tmp_path / 'hf'), ids[0])
+    assert torch.allclose(got, want, atol=2e-5), float((got - want).abs().max())
+
+
+@pytest.mark.parametrize('name', ['qwen3', 'qwen3_moe'])
+def test_checkpoint_saved_here_loads_in_transformers(name, tmp_path):
+    hf = _hf_model(name)
+    hf.save_pretrained(str(tmp_path / 'hf'), safe_serialization=True)
+    ids = torch.randint(0, 512, (1, 29), generator=torch.Generator().manual_seed(2))
+    m, ours = _ours(str(tmp_path / 'hf'), ids[0])
+    out = m.save('export', str(tmp_path / 'ours'))
+    back = getattr(transformers, _cases()[name][1]).from_pretrained(out).float().eval()
+    with torch.no_grad():
+        theirs = back(ids).logits[0]
+    assert torch.allclose(ours, theirs, atol=2e-5), float((ours - theirs).abs().max())

@@ -113,7 +113,7 @@ class DecoderConfig:
             head_dim=cfg.get('head_dim') or cfg.get('hidden_size', 4096) // heads, rms_norm_eps=cfg.get('rms_norm_eps', 1e-6),
             rope_theta=float(cfg.get('rope_theta', (cfg.get('rope_parameters') or {}).get('rope_theta', 1e6))),
             rope_scaling=_rope_scaling_of(cfg), tie_word_embeddings=bool(cfg.get('tie_word_embeddings', False)),
-            qk_norm=mt.startswith('qwen3'), attention_bias=bool(cfg.get('attention_bias', mt == 'qwen2')),
+            qk_norm=mt.startswith('qwen3'), attention_bias=bool(cfg.get('attention_bias', mt in ('qwen2', 'qwen2_moe'))),
             num_experts=cfg.get('num_experts', cfg.get('num_local_experts', 0)) or 0,
             num_experts_per_tok=cfg.get('num_experts_per_tok', 8), moe_intermediate_size=cfg.get('moe_intermediate_size', 768),
             norm_topk_prob=bool(cfg.get('norm_topk_prob', True)), router_aux_loss_coef=float(cfg.get('router_aux_loss_coef', 0.0)),
