@@ -63,7 +63,9 @@ def initialize(mode: str = 'local', nproc_per_node: Optional[int] = None, groups
         if not groups:
             n = nproc_per_node or (global_device_mesh.world_size if global_device_mesh is not None else 1)
             groups = [DeviceGroup(name='default', ranks=list(range(n)), device_type=Platform.device_prefix())]
-        _STATE['pool'] = WorkerPoolManager(groups, seed=seed)
+        # pool_listen='host:port' + external_groups=[names]: those groups' workers join from other nodes (see infra/agent.py)
+        _STATE['pool'] = WorkerPoolManager(groups, seed=seed, listen=kwargs.get('pool_listen'), external_groups=kwargs.get('external_groups'),
+                                           join_timeout=float(kwargs.get('join_timeout', 600.0)))
     _STATE.update(mode=mode, seed=seed, mesh=global_device_mesh, groups=groups, lazy_collect=lazy_collect,
                   notifier=notifier, initialized=True, full_determinism=full_determinism)
 

@@ -75,13 +75,34 @@ def _worker_main(conn, env: Dict[str, str]) -> None:
         pass
 
 
+class _ExternalProcess:
+    """Stands in for ``multiprocessing.Process`` when the worker lives in another process tree (usually on another
+    node) and only its connection is known here; it ends when it reads ``stop`` or loses the connection."""
+    exitcode = None
+
+    def __init__(self, name: str):
+        self.name, self._alive = name, True
+
+    def is_alive(self) -> bool:
+        return self._alive
+
+    def join(self, timeout: Optional[float] = None) -> None:
+        self._alive = False
+
+    def terminate(self) -> None:
+        self._alive = False
+
+
 class _Worker:
 
-    def __init__(self, ctx, env: Dict[str, str], name: str):
-        self.conn, child = ctx.Pipe(duplex=True)
-        self.proc = ctx.Process(target=_worker_main, args=(child, env), name=name, daemon=True)
-        self.proc.start()
-        child.close()
+    def __init__(self, ctx, env: Optional[Dict[str, str]], name: str, conn=None):
+        if conn is None:
+            self.conn, child = ctx.Pipe(duplex=True)
+            self.proc = ctx.Process(target=_worker_main, args=(child, env), name=name, daemon=True)
+            self.proc.start()
+            child.close()
+        else:  # a worker that connected over TCP (started by ``python -m twinkle_b200.infra.agent`` somewhere)
+            self.conn, self.proc = conn, _ExternalProcess(name)
         self._seq = 0
         self._lock = threading.Lock()
         self._futures: Dict[int, Future] = {}
@@ -139,9 +160,24 @@ class _Worker:
 class WorkerPoolManager:
     """Owns the worker processes of every ``DeviceGroup``; workers start on first use of their group."""
 
-    def __init__(self, groups: Sequence[DeviceGroup], seed: int = 42, master_addr: str = '127.0.0.1'):
+    def __init__(self, groups: Sequence[DeviceGroup], seed: int = 42, master_addr: str = '127.0.0.1', listen: Optional[str] = None,
+                 external_groups: Optional[Sequence[str]] = None, join_timeout: float = 600.0):
+        """``listen='host:port'`` opens a TCP listener for workers that are started elsewhere; the groups named in
+        ``external_groups`` are then not spawned here but waited for (``join_timeout`` seconds). Connections are
+        authenticated with the shared secret in ``TWINKLE_POOL_AUTHKEY`` (HMAC challenge of
+        ``multiprocessing.connection``); requests are pickled code, so the listener belongs on a cluster-private network."""
         self.groups = {g.name: g for g in groups}
         self.seed, self.master_addr = seed, master_addr
+        self.external = set(external_groups or ())
+        self.join_timeout, self._listener = join_timeout, None
+        if listen or self.external:
+            from multiprocessing.connection import Listener
+            key = os.environ.get('TWINKLE_POOL_AUTHKEY')
+            if not key:
+                raise RuntimeError('TWINKLE_POOL_AUTHKEY must be set (same value on every node) before workers can join over TCP')
+            host, _, port = (listen or '0.0.0.0:0').rpartition(':')
+            self._listener = Listener((host or '0.0.0.0', int(port or 0)), authkey=key.encode())
+            self.listen_address = self._listener.address
         self._ctx = mp.get_context('spawn')
         self._workers: Dict[str, List[_Worker]] = {}
         self._next_oid = 0
@@ -179,8 +215,51 @@ class WorkerPoolManager:
             if group not in self._workers:
                 if group not in self.groups:
                     raise KeyError(f'unknown device group {group!r}; known: {sorted(self.groups)}')
-                self._workers[group] = [_Worker(self._ctx, env, f'twinkle-{group}-{i}') for i, env in enumerate(self.placement(group))]
+                if group in self.external:
+                    self._workers[group] = self._accept_external(group)
+                else:
+                    self._workers[group] = [_Worker(self._ctx, env, f'twinkle-{group}-{i}') for i, env in enumerate(self.placement(group))]
             return self._workers[group]
+
+    def _accept_external(self, group: str) -> List[_Worker]:
+        """Waits until every rank of ``group`` has connected. A joining worker says ``('hello', group, rank, address of
+        its node, a free port there)``; once all are in, each gets its environment — ``MASTER_ADDR`` / ``MASTER_PORT`` are
+        those reported by rank 0, so the group's ``torch.distributed`` rendezvous happens on rank 0's node."""
+        import time
+        envs = self.placement(group)
+        conns: Dict[int, Any] = {}
+        hello: Dict[int, tuple] = {}
+        deadline = time.monotonic() + self.join_timeout
+        sock = self._listener._listener._socket
+        while len(conns) < len(envs):
+            left = deadline - time.monotonic()
+            if left <= 0:
+                for c in conns.values():
+                    c.close()
+                raise TimeoutError(f"group '{group}': {len(conns)} of {len(envs)} workers joined within {self.join_timeout:.0f} s")
+            sock.settimeout(min(left, 1.0))
+            try:
+                c = self._listener.accept()
+            except (TimeoutError, OSError):
+                continue
+            try:
+                msg = cloudpickle.loads(c.recv_bytes())
+            except (EOFError, OSError):
+                continue
+            if not (isinstance(msg, tuple) and len(msg) == 5 and msg[0] == 'hello' and msg[1] == group and 0 <= int(msg[2]) < len(envs)
+                    and int(msg[2]) not in conns):
+                c.send_bytes(cloudpickle.dumps(('refused', f'unexpected hello {msg!r:.80}')))
+                c.close()
+                continue
+            conns[int(msg[2])], hello[int(msg[2])] = c, msg
+        addr, port = hello[0][3], hello[0][4]
+        workers = []
+        for r, env in enumerate(envs):
+            env = {k: v for k, v in env.items() if k not in ('CUDA_VISIBLE_DEVICES', 'LOCAL_RANK', 'LOCAL_WORLD_SIZE')}  # the agent pins devices
+            env.update(MASTER_ADDR=str(addr), MASTER_PORT=str(port))
+            conns[r].send_bytes(cloudpickle.dumps(('welcome', env)))
+            workers.append(_Worker(None, None, f'twinkle-{group}-{r}@{hello[r][3]}', conn=conns[r]))
+        return workers
 
     def new_object_id(self) -> int:
         with self._lock:
@@ -193,6 +272,9 @@ class WorkerPoolManager:
             self._workers = {}
         for w in all_workers:
             w.stop()
+        if self._listener is not None:
+            self._listener.close()
+            self._listener = None
 
 
 class RemoteProxy:
