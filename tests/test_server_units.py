@@ -187,3 +187,48 @@ def test_wire_types_validate_bodies_and_parse_paths():
     assert r.result[0].sequences[0].tokens == [1, 2]
     runs = TrainingRunsResponse(training_runs=[{'training_run_id': 'r', 'last_checkpoint': {'checkpoint_id': 'c'}}], cursor={'total_count': 1})
     assert runs.training_runs[0].last_checkpoint.checkpoint_type == 'training' and runs.cursor.limit == 100
+
+
+def test_otlp_json_export_of_metrics_and_spans():
+    from twinkle_b200.server.telemetry import MetricsRegistry, Tracer
+    from twinkle_b200.server.telemetry.otlp import OTLPExporter
+    reg, tr = MetricsRegistry(), Tracer()
+    reg.inc('twinkle_http_requests_total', app='gateway', status=200)
+    reg.inc('twinkle_http_requests_total', app='gateway', status=200)
+    reg.set_gauge('twinkle_queue_depth', 3)
+    for v in (0.1, 0.2, 0.3, 0.4):
+        reg.observe('twinkle_task_execution_seconds', v)
+    with tr.span('POST /forward', model_id='m1', app='model'):
+        pass
+    try:
+        with tr.span('POST /boom'):
+            raise ValueError('x')
+    except ValueError:
+        pass
+    sent = []
+    ex = OTLPExporter('http://collector:4317/', 'svc', post=lambda url, body: sent.append((url, body)))
+    assert ex.endpoint == 'http://collector:4318' and ex.export(reg, tr)
+    (murl, m), (turl, t) = sent
+    assert murl.endswith('/v1/metrics') and turl.endswith('/v1/traces')
+    res = m['resourceMetrics'][0]
+    assert res['resource']['attributes'][0] == {'key': 'service.name', 'value': {'stringValue': 'svc'}}
+    by = {x['name']: x for x in res['scopeMetrics'][0]['metrics']}
+    s = by['twinkle_http_requests_total']['sum']
+    assert s['isMonotonic'] and s['aggregationTemporality'] == 2 and s['dataPoints'][0]['asDouble'] == 2.0
+    assert {'key': 'status', 'value': {'intValue': '200'}} in s['dataPoints'][0]['attributes']
+    assert by['twinkle_queue_depth']['gauge']['dataPoints'][0]['asDouble'] == 3.0
+    summ = by['twinkle_task_execution_seconds']['summary']['dataPoints'][0]
+    assert summ['count'] == '4' and abs(summ['sum'] - 1.0) < 1e-9 and summ['quantileValues'][0] == {'quantile': 0.5, 'value': 0.3}
+    spans = t['resourceSpans'][0]['scopeSpans'][0]['spans']
+    assert [x['name'] for x in spans] == ['POST /forward', 'POST /boom'] and len(spans[0]['traceId']) == 32 and len(spans[0]['spanId']) == 16
+    assert spans[0]['status'] == {'code': 1} and spans[1]['status']['code'] == 2 and 'ValueError' in spans[1]['status']['message']
+    assert {'key': 'twinkle.model_id', 'value': {'stringValue': 'm1'}} in spans[0]['attributes']
+    assert int(spans[0]['endTimeUnixNano']) >= int(spans[0]['startTimeUnixNano'])
+    sent.clear()
+    assert ex.export(reg, tr) and [u for u, _ in sent] == ['http://collector:4318/v1/metrics']     # spans are sent once
+
+    def down(url, body):
+        raise OSError('unreachable')
+
+    bad = OTLPExporter('http://c:4318', post=down)
+    assert bad.export(reg, tr) is False and bad.failures == 1

@@ -81,14 +81,23 @@ class ServerLauncher:
             prefix = gateway_spec.route_prefix.rstrip('/')
             self.root.mount(prefix or '/', self.gateway.app)
 
+        self._otlp_stop = None
+
         @self.root.on_event('startup')
         async def _start():
             self._lifecycle_task = asyncio.get_event_loop().create_task(self._lifecycle())
+            t = self.config.telemetry
+            if t.enabled and t.otlp_endpoint and not t.debug:
+                from .telemetry import get_tracer
+                from .telemetry.otlp import OTLPExporter
+                self._otlp_stop = OTLPExporter(t.otlp_endpoint, t.service_name).start(get_registry(), get_tracer(), t.metrics_interval_s)
 
         @self.root.on_event('shutdown')
         async def _stop():
             if self._lifecycle_task:
                 self._lifecycle_task.cancel()
+            if self._otlp_stop is not None:
+                self._otlp_stop.set()  # one last push of metrics and spans
             self.state.release_leadership()
 
     async def _lifecycle(self) -> None:
