@@ -695,7 +695,7 @@ class SIFDScorer:
 
 _JUDGE_PROMPT = ('You are grading an answer against a reference. Decide whether the candidate answer is correct and complete with '
                  'respect to the reference; wording may differ. Reply with <verdict>PASS</verdict> or <verdict>FAIL</verdict>.')
-_VERDICT = re.compile(r'<verdict>\s*(PASS|FAIL)\s*</verdict>', re.I)
+_PASS_FAIL_TAG = re.compile(r'<verdict>\s*(PASS|FAIL)\s*</verdict>', re.I)
 
 
 class PassNScorer:
@@ -719,7 +719,7 @@ class PassNScorer:
 
     @staticmethod
     def parse_verdict(text: str) -> Optional[bool]:
-        found = _VERDICT.findall(text or '')
+        found = _PASS_FAIL_TAG.findall(text or '')
         if found:
             return found[-1].upper() == 'PASS'
         t = (text or '').upper()

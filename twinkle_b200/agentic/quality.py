@@ -2,9 +2,8 @@
 
 What it covers: reference ``src/twinkle_agentic/sampler/router_sampler.py``, ``reward/f1.py`` and the rule-based
 members of ``preprocessor/`` (dedup, refusal, dead-loop, token-soup, hard limits, score threshold, PII, message
-sanity / normalisation).  The reference's model-backed filters (LLM judge, intent classifier, Presidio, data-juicer
-operators) call external models or packages that are not available offline; their rule-based counterparts are
-provided and the model-backed ones accept any ``score_fn`` callable instead.
+sanity / normalisation).  These are ``DataFilter`` objects (``keep(row) -> bool``).  The steps that rewrite rows, call a
+language model or score rounds from log-probabilities live in ``preprocess.py`` and ``pii.py``.
 """
 from __future__ import annotations
 
