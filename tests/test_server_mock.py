@@ -142,3 +142,30 @@ def test_admission_control_and_state(server, tmp_path):
     assert gone['sessions'] == [sid] and gone['models'] == ['m1']
     with pytest.raises(Exception):
         ServerConfig(applications=[{'name': 'x', 'import_path': 'model', 'args': {'model_id': 'a', 'bogus': 1}}])
+
+
+def test_openai_chat_completions_tools_reasoning_logprobs_and_stream(server):
+    import json
+    from twinkle_b200.client import Transport
+    t = Transport(app=server.root, token='alice')
+    backend = server.sampler_apps[0].backend
+    backend.script = [{'text': '<think>\nneed the sum\n</think>\n\nLet me add. <tool_call>\n{"name": "add", "arguments": {"a": 2, "b": 3}}\n</tool_call>',
+                       'stop_reason': 'stop'}]
+    tools = [{'type': 'function', 'function': {'name': 'add', 'description': 'Add.', 'parameters': {'type': 'object', 'properties': {}}}}]
+    body = {'model': 'mock-base', 'messages': [{'role': 'user', 'content': [{'type': 'text', 'text': 'what is 2+3?'}]}], 'tools': tools, 'max_tokens': 64,
+            'logprobs': True}
+    r = t.post('/chat/completions', body)
+    ch = r['choices'][0]
+    assert r['object'] == 'chat.completion' and ch['finish_reason'] == 'tool_calls'
+    assert ch['message']['reasoning_content'] == 'need the sum' and ch['message']['content'] == 'Let me add.'
+    call = ch['message']['tool_calls'][0]
+    assert call['type'] == 'function' and call['function']['name'] == 'add' and json.loads(call['function']['arguments']) == {'a': 2, 'b': 3}
+    assert len(ch['logprobs']['content']) == r['usage']['completion_tokens'] and ch['logprobs']['content'][0]['logprob'] <= 0
+    assert r['usage']['total_tokens'] == r['usage']['prompt_tokens'] + r['usage']['completion_tokens']
+    # a follow-up in OpenAI wire form (function-style tool call + tool result) is accepted
+    backend.script = [{'text': 'The sum is 5.', 'stop_reason': 'stop'}]
+    follow = {'model': 'mock-base', 'tools': tools, 'max_tokens': 16, 'messages': body['messages'] + [
+        {'role': 'assistant', 'content': None, 'tool_calls': [call]}, {'role': 'tool', 'tool_call_id': call['id'], 'content': '5'}]}
+    r2 = t.post('/chat/completions', follow)
+    assert r2['choices'][0]['message'] == {'role': 'assistant', 'content': 'The sum is 5.'} and r2['choices'][0]['finish_reason'] == 'stop'
+    assert [m['id'] for m in t.get('/models')['data']] == ['mock-base']

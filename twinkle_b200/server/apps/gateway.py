@@ -259,28 +259,73 @@ class GatewayApp:
             sampler = self.router.sampler_for(b.get('model'))
             sp = {'max_tokens': b.get('max_tokens') or b.get('max_completion_tokens') or 256, 'temperature': b.get('temperature', 1.0),
                   'top_p': b.get('top_p', 1.0), 'seed': b.get('seed'), 'stop': b.get('stop'), 'num_samples': b.get('n', 1)}
-            traj = {'messages': b.get('messages') or [], 'tools': b.get('tools')}
+            from ...agentic.quality import normalize_messages
+            from ...data_format import tool_call_to_openai
+            tools = [{'tool_name': (t.get('function') or t).get('name'), 'description': (t.get('function') or t).get('description', ''),
+                      'parameters': (t.get('function') or t).get('parameters', {})} for t in (b.get('tools') or [])]
+            # OpenAI wire messages (function-style tool calls, list-of-parts contents) → the internal message form
+            traj = normalize_messages({'messages': b.get('messages') or []})
+            if tools:
+                traj['tools'] = tools
+            want_lp = bool(b.get('logprobs'))
+            if want_lp:
+                sp['logprobs'] = int(b.get('top_logprobs') or 1)
             if sampler.backend.template is None:
                 sampler.backend.set_template('Template', model_id=sampler.args.model_id)
+            tpl = sampler.backend.template
             created, cid = int(time.time()), 'chatcmpl-' + uuid.uuid4().hex[:24]
             if b.get('stream') and hasattr(sampler.backend, 'sample_stream'):
                 async def gen():
                     loop = asyncio.get_event_loop()
                     it = sampler.backend.sample_stream([traj], sp)
+                    base = {'id': cid, 'object': 'chat.completion.chunk', 'created': created, 'model': b.get('model')}
+                    yield 'data: ' + json.dumps({**base, 'choices': [{'index': 0, 'delta': {'role': 'assistant', 'content': ''}, 'finish_reason': None}]}) + '\n\n'
+                    final = None
                     while True:
                         item = await loop.run_in_executor(None, lambda: next(it, None))
-                        if item is None or item.get('done'):
+                        if item is None:
                             break
-                        chunk = {'id': cid, 'object': 'chat.completion.chunk', 'created': created, 'model': b.get('model'),
-                                 'choices': [{'index': item['index'], 'delta': {'content': item['text']}, 'finish_reason': None}]}
-                        yield 'data: ' + json.dumps(chunk) + '\n\n'
+                        if item.get('done'):
+                            final = item
+                            break
+                        yield 'data: ' + json.dumps({**base, 'choices': [{'index': item['index'], 'delta': {'content': item['text']},
+                                                                           'finish_reason': None}]}) + '\n\n'
+                    reasons = {}
+                    for r in (final or {}).get('responses') or []:
+                        for i, q in enumerate(getattr(r, 'sequences', None) or (r.get('sequences') if isinstance(r, dict) else []) or []):
+                            reasons[i] = (getattr(q, 'stop_reason', None) if not isinstance(q, dict) else q.get('stop_reason')) or 'stop'
+                    for i, why in sorted(reasons.items()) or [(0, 'stop')]:
+                        yield 'data: ' + json.dumps({**base, 'choices': [{'index': i, 'delta': {}, 'finish_reason': 'stop' if why == 'stop' else 'length'}]}) + '\n\n'
                     yield 'data: [DONE]\n\n'
                 return StreamingResponse(gen(), media_type='text/event-stream')
             res = await sampler.schedule_task_and_wait(lambda: sampler.backend.sample([traj], sp), token=request.state.token)
             seqs = res[0].sequences
             n_prompt = len(seqs[0].new_input_feature['input_ids']) - len(seqs[0].tokens) if seqs else 0
-            return {'id': cid, 'object': 'chat.completion', 'created': created, 'model': b.get('model'),
-                    'choices': [{'index': i, 'message': {'role': 'assistant', 'content': s.decoded or ''},
-                                 'finish_reason': 'stop' if s.stop_reason == 'stop' else 'length'} for i, s in enumerate(seqs)],
+            choices = []
+            for i, q in enumerate(seqs):
+                text = q.decoded or ''
+                reasoning = ''
+                if text.lstrip().startswith('<think>') and '</think>' in text:
+                    head, text = text.split('</think>', 1)
+                    reasoning, text = head.split('<think>', 1)[1].strip(), text.lstrip('\n')
+                msg = tpl.response_message(text) if hasattr(tpl, 'response_message') else {'role': 'assistant', 'content': text}
+                out = {'role': 'assistant', 'content': msg['content'] or (None if msg.get('tool_calls') else '')}
+                if reasoning:
+                    out['reasoning_content'] = reasoning
+                if msg.get('tool_calls'):
+                    out['tool_calls'] = [tool_call_to_openai(c) for c in msg['tool_calls']]
+                choice = {'index': i, 'message': out,
+                          'finish_reason': 'tool_calls' if msg.get('tool_calls') and q.stop_reason == 'stop' else ('stop' if q.stop_reason == 'stop' else 'length')}
+                if want_lp and q.logprobs is not None:
+                    dec = (lambda t: tpl.decode([t], skip_special_tokens=False)) if hasattr(tpl, 'decode') else str
+                    content = []
+                    for k, (t, lp) in enumerate(zip(q.tokens, q.logprobs)):
+                        ent = {'token': dec(t), 'logprob': lp, 'bytes': None}
+                        if q.topk_logprobs and k < len(q.topk_logprobs) and q.topk_logprobs[k]:
+                            ent['top_logprobs'] = [{'token': dec(a), 'logprob': b_, 'bytes': None} for a, b_ in q.topk_logprobs[k]]
+                        content.append(ent)
+                    choice['logprobs'] = {'content': content}
+                choices.append(choice)
+            return {'id': cid, 'object': 'chat.completion', 'created': created, 'model': b.get('model'), 'choices': choices,
                     'usage': {'prompt_tokens': n_prompt, 'completion_tokens': sum(len(s.tokens) for s in seqs),
                               'total_tokens': n_prompt + sum(len(s.tokens) for s in seqs)}}

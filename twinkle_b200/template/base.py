@@ -39,6 +39,7 @@ class ByteChatTokenizer:
         self.eos_token_id = self.special['<|im_end|>']
         self.eos_token = '<|im_end|>'
         self.pad_token = '<|pad|>'
+        self.all_special_tokens = [t for t in self.SPECIAL if t.startswith('<|')]
 
     def __len__(self):
         return self.vocab_size
@@ -76,7 +77,8 @@ class ByteChatTokenizer:
                 if buf:
                     parts.append(buf.decode('utf-8', errors='replace'))
                     buf = bytearray()
-                if not skip_special_tokens and t in self.inv:
+                # like the Qwen tokenizers: <tool_call> / <think> are single tokens but ordinary text, only control tokens are skipped
+                if t in self.inv and (not skip_special_tokens or not self.inv[t].startswith('<|')):
                     parts.append(self.inv[t])
         if buf:
             parts.append(buf.decode('utf-8', errors='replace'))
