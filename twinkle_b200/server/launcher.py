@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import argparse
 import asyncio
+import contextlib
 import os
 import signal
 import sys
@@ -37,7 +38,7 @@ class ServerLauncher:
         self.state = ServerState(build_backend(config.persistence))
         self.checkpoints = CheckpointManager()
         self.router = Router()
-        self.root = FastAPI(title='twinkle-b200-server')
+        self.root = FastAPI(title='twinkle-b200-server', lifespan=self._lifespan)
         self.model_apps: List[ModelApp] = []
         self.sampler_apps: List[SamplerApp] = []
         self.processor_apps: List[ProcessorApp] = []
@@ -83,17 +84,19 @@ class ServerLauncher:
 
         self._otlp_stop = None
 
-        @self.root.on_event('startup')
-        async def _start():
-            self._lifecycle_task = asyncio.get_event_loop().create_task(self._lifecycle())
-            t = self.config.telemetry
-            if t.enabled and t.otlp_endpoint and not t.debug:
-                from .telemetry import get_tracer
-                from .telemetry.otlp import OTLPExporter
-                self._otlp_stop = OTLPExporter(t.otlp_endpoint, t.service_name).start(get_registry(), get_tracer(), t.metrics_interval_s)
-
-        @self.root.on_event('shutdown')
-        async def _stop():
+    @contextlib.asynccontextmanager
+    async def _lifespan(self, app):
+        """Start-up: the lifecycle loop and, when configured, the OTLP exporter. Shut-down: stop both, push what is left,
+        give up the cleanup lease."""
+        self._lifecycle_task = asyncio.get_event_loop().create_task(self._lifecycle())
+        t = self.config.telemetry
+        if t.enabled and t.otlp_endpoint and not t.debug:
+            from .telemetry import get_tracer
+            from .telemetry.otlp import OTLPExporter
+            self._otlp_stop = OTLPExporter(t.otlp_endpoint, t.service_name).start(get_registry(), get_tracer(), t.metrics_interval_s)
+        try:
+            yield
+        finally:
             if self._lifecycle_task:
                 self._lifecycle_task.cancel()
             if self._otlp_stop is not None:
