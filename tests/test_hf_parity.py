@@ -73,3 +73,50 @@ def test_checkpoint_saved_here_loads_in_transformers(name, tmp_path):
     with torch.no_grad():
         theirs = back(ids).logits[0]
     assert torch.allclose(ours, theirs, atol=2e-5), float((ours - theirs).abs().max())
+
+
+@pytest.mark.parametrize('name', ['qwen3', 'qwen3_moe'])
+def test_adapter_saved_in_peft_layout_merges_into_the_hf_model(name, tmp_path):
+    """PEFT key names and the split of fused projections: merging ``scale · B @ A`` of every saved adapter tensor into
+    the Hugging Face weight it names must reproduce the logits of the adapted model here."""
+    from safetensors.torch import load_file
+    from twinkle_b200.model import LoraConfig
+    from twinkle_b200.models.decoder import PackedBatch
+    hf = _hf_model(name)
+    hf.save_pretrained(str(tmp_path / 'hf'), safe_serialization=True)
+    ids = torch.randint(0, 512, (1, 33), generator=torch.Generator().manual_seed(3))
+    m, base = _ours(str(tmp_path / 'hf'), ids[0])
+    m.add_adapter_to_model('a', LoraConfig(r=4, lora_alpha=8, target_modules='all-linear'))
+    m.set_optimizer('AdamW', lr=5e-2, adapter_name='a')
+    batch = [{'input_ids': ids[0, :-1].tolist(), 'labels': ids[0, 1:].tolist()}]
+    for _ in range(2):                                       # B starts at zero: two steps make the adapter matter
+        m.forward_backward(inputs=batch, adapter_name='a')
+        m.clip_grad_and_step(adapter_name='a')
+    out = m.save('adapter', str(tmp_path / 'ad'), adapter_name='a')
+    n = ids.shape[1]
+    with torch.no_grad():
+        adapted = torch.as_tensor(m.forward_only(inputs=[{'input_ids': ids[0].tolist(), 'labels': ids[0].tolist()}], adapter_name='a', return_logits=True)['logits']).float()
+    adapted = adapted.reshape(-1, adapted.shape[-1])[:n]
+    assert float((adapted - base).abs().max()) > 1e-3         # the adapter changed the model
+    import json
+    cfg = json.load(open(out + '/adapter_config.json'))
+    assert cfg['peft_type'] == 'LORA' and cfg['r'] == 4
+    scale = cfg['lora_alpha'] / cfg['r']
+    sd = load_file(out + '/adapter_model.safetensors')
+    params = dict(hf.named_parameters())
+    merged = 0
+    with torch.no_grad():
+        for k, a in sd.items():
+            if '.lora_A.' not in k:
+                continue
+            b = sd[k.replace('.lora_A.', '.lora_B.')]
+            target = k[len('base_model.model.'):].replace('.lora_A.weight', '')
+            if target + '.weight' in params:
+                params[target + '.weight'] += scale * (b.float() @ a.float())
+                merged += 1
+            else:                                             # fused expert tensors of newer transformers: [E, out, in] per expert index
+                pytest.skip(f'{target}: this transformers build stores the module differently')
+    assert merged > 0
+    with torch.no_grad():
+        theirs = hf(ids).logits[0]
+    assert torch.allclose(adapted, theirs, atol=5e-5), float((adapted - theirs).abs().max())
