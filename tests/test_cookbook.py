@@ -104,3 +104,10 @@ def test_tinker_dpo_then_resume_after_server_restart():
     assert abs(r['next_uninterrupted'][1] - r['next_resumed'][1]) < 1e-4                  # and the Adam moments and step count
     assert r['info']['is_lora'] and r['info']['lora_rank'] == 8 and r['info']['base_model'] == 'tiny-dense'
     assert len(r['runs']) >= 1 and len(r['tokens']) == 4
+
+
+def test_vision_language_sft_full_and_lora(tmp_path):
+    full = _load('mm_sft').main(['--steps', '6', '--batch', '4', '--out', str(tmp_path)])
+    assert full[-1] < 0.7 * full[0] and os.path.isfile(os.path.join(str(tmp_path), 'final', 'config.json'))
+    lora = _load('mm_sft').main(['--steps', '4', '--batch', '4', '--lora-rank', '4', '--lr', '1e-2'])
+    assert lora[-1] < lora[0]

@@ -1,0 +1,213 @@
+"""Qwen2-VL family: the vision tower, the (time, height, width) rotary positions, preprocessing, the chat template's image
+placeholders, packed batches with images, training through the public model API, and checkpoints in both directions —
+with ``transformers``' implementation as the oracle where it is installed."""
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from twinkle_b200.models.vision import VisionConfig, VisionTower, mrope_tables, patchify, preprocess_image, rope_index, smart_resize
+
+VC = dict(depth=2, embed_dim=64, hidden_size=128, num_heads=4, mlp_ratio=2, patch_size=14, spatial_merge_size=2, temporal_patch_size=2, in_channels=3)
+
+
+def _hf():
+    T = pytest.importorskip('transformers')
+    try:
+        cfg = T.Qwen2VLConfig(
+            text_config=dict(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                             max_position_embeddings=512, rope_theta=10000.0, rope_scaling={'type': 'mrope', 'mrope_section': [4, 6, 6]},
+                             tie_word_embeddings=False),
+            vision_config=VC, image_token_id=500, video_token_id=501, vision_start_token_id=502, vision_end_token_id=503)
+        torch.manual_seed(0)
+        return T, cfg, T.Qwen2VLForConditionalGeneration(cfg).float().eval()
+    except Exception as e:
+        pytest.skip(f'this transformers build cannot make a tiny Qwen2-VL: {type(e).__name__}: {e}')
+
+
+def _sample():
+    grid = torch.tensor([[1, 4, 6], [1, 2, 2]])
+    n1, n2 = 4 * 6 // 4, 2 * 2 // 4
+    ids = [5, 6, 502] + [500] * n1 + [503, 7, 8, 502] + [500] * n2 + [503, 9, 10, 11]
+    pix = torch.randn(int((grid[:, 0] * grid[:, 1] * grid[:, 2]).sum()), 3 * 2 * 14 * 14, generator=torch.Generator().manual_seed(1))
+    return ids, grid, pix
+
+
+def test_positions_and_tables_by_hand():
+    ids = [1, 2, 9, 9, 9, 9, 9, 9, 3, 4]                       # one image with a merged 2 × 3 grid
+    pos = rope_index(ids, [(1, 4, 6)], image_token_id=9)
+    assert pos[:, :2].tolist() == [[0, 1]] * 3
+    assert pos[0, 2:8].tolist() == [2] * 6 and pos[1, 2:8].tolist() == [2, 2, 2, 3, 3, 3] and pos[2, 2:8].tolist() == [2, 3, 4, 2, 3, 4]
+    assert pos[:, 8:].tolist() == [[5, 6]] * 3                  # text resumes after the largest position used (2 + 3)
+    with pytest.raises(ValueError):
+        rope_index(ids[:5], [(1, 4, 6)], 9)
+    with pytest.raises(ValueError):
+        rope_index([1, 2, 3], [(1, 4, 6)], 9)
+    same = torch.arange(7).expand(3, -1)
+    cos, sin = mrope_tables(same, 16, 1e4, [2, 3, 3])
+    inv = 1.0 / (1e4**(torch.arange(0, 16, 2).float() / 16))
+    assert torch.allclose(cos, (torch.arange(7).float()[:, None] * inv).cos())      # equal components = ordinary RoPE
+    mixed = torch.tensor([[1], [10], [100]])
+    cos, _ = mrope_tables(mixed, 16, 1e4, [2, 3, 3])
+    want = torch.cat([1 * inv[:2], 10 * inv[2:5], 100 * inv[5:]]).cos()
+    assert torch.allclose(cos[0], want)
+    assert smart_resize(100, 150) == (112, 140) and smart_resize(10, 10)[0] % 28 == 0 and smart_resize(5000, 5000)[0] * smart_resize(5000, 5000)[1] <= 14 * 14 * 4 * 1280
+    frames = torch.arange(3 * 28 * 56, dtype=torch.float32).view(1, 3, 28, 56)
+    flat, g = patchify(frames, VisionConfig(**VC))
+    assert g == (1, 2, 4) and flat.shape == (8, 1176)
+    # patches come merge-group by merge-group: rows 0-3 are the left 2 × 2 block, and the single frame fills both temporal slots
+    first = flat[1].view(3, 2, 14, 14)
+    assert torch.equal(first[:, 0], frames[0, :, 0:14, 14:28]) and torch.equal(first[:, 0], first[:, 1])
+    assert torch.equal(flat[2].view(3, 2, 14, 14)[:, 0], frames[0, :, 14:28, 0:14])
+
+
+def test_tower_positions_and_full_model_match_transformers():
+    T, cfg, hf = _hf()
+    from twinkle_b200.models.bridge import hf_to_internal
+    from twinkle_b200.models.config import DecoderConfig
+    from twinkle_b200.models.decoder import PackedBatch, build_model
+    ids, grid, pix = _sample()
+    tower = VisionTower(VisionConfig.from_hf(cfg.vision_config.to_dict())).float().eval()
+    tower.load_state_dict({k[len('model.visual.'):]: v for k, v in hf.state_dict().items() if k.startswith('model.visual.')})
+    ids_t = torch.tensor([ids])
+    mm = (ids_t == 500).int()
+    with torch.no_grad():
+        try:
+            want_feats = hf.model.visual(pix, grid_thw=grid)
+            want_pos = hf.model.get_rope_index(ids_t, mm_token_type_ids=mm, image_grid_thw=grid)[0][:, 0]
+            want = hf(input_ids=ids_t, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=mm).logits[0]
+        except TypeError as e:
+            pytest.skip(f'different call signature in this transformers build: {e}')
+        want_feats = getattr(want_feats, 'pooler_output', want_feats[0] if isinstance(want_feats, tuple) else want_feats)
+        assert torch.allclose(tower(pix, grid), want_feats, atol=1e-5)
+    assert torch.equal(rope_index(ids, grid.tolist(), 500), want_pos)
+    dc = DecoderConfig.from_hf(cfg.to_dict())
+    assert dc.mrope_section == [4, 6, 6] and dc.attention_bias and not dc.qk_norm and dc.image_token_id == 500 and dc.rope_scaling is None
+    m = build_model(dc)
+    sd = hf.state_dict()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            p.copy_(hf_to_internal(n, dc, lambda k: sd[k]))
+        n = len(ids)
+        got = m.logits(m(PackedBatch(torch.tensor(ids), rope_index(ids, grid.tolist(), 500), torch.tensor([0, n], dtype=torch.int32), n,
+                                     pixel_values=pix, image_grid_thw=grid)))
+    assert torch.allclose(got, want, atol=2e-5), float((got - want).abs().max())
+
+
+def test_preprocessing_matches_the_hf_image_processor():
+    T = pytest.importorskip('transformers')
+    Image = pytest.importorskip('PIL.Image')
+    try:
+        ip = T.Qwen2VLImageProcessor(min_pixels=56 * 56, max_pixels=14 * 14 * 4 * 1280)
+    except Exception as e:
+        pytest.skip(str(e))
+    vc = VisionConfig(**VC)
+    for shape, tol in (((84, 112, 3), 1e-5), ((100, 150, 3), 0.02), ((30, 500, 3), 0.02)):   # no resize: exact; resized: one 8-bit level
+        arr = (np.random.RandomState(0).rand(*shape) * 255).astype('uint8')
+        out = ip(images=[Image.fromarray(arr)], return_tensors='pt')
+        pv, g = preprocess_image(arr, vc)
+        assert out['image_grid_thw'].tolist() == [list(g)] and float((out['pixel_values'] - pv).abs().max()) <= tol
+
+
+def test_template_processor_training_and_checkpoints(tmp_path):
+    from twinkle_b200.model import TransformersModel
+    from twinkle_b200.models.config import DecoderConfig
+    from twinkle_b200.processor import InputProcessor
+    m = TransformersModel(model_id='tiny-vl', seed=0)
+    m.set_template('Qwen2VLTemplate', vision_config=m.config.vision, max_length=4096)
+    g = torch.Generator().manual_seed(0)
+    img1, img2 = torch.rand(3, 60, 90, generator=g) * 255, (torch.rand(40, 40, 3, generator=g) * 255).numpy()
+    trajs = [{'messages': [{'role': 'user', 'content': [{'type': 'image', 'image': img1}, {'type': 'text', 'text': 'what is this?'}]},
+                           {'role': 'assistant', 'content': 'a cat'}]},
+             {'messages': [{'role': 'user', 'content': 'hello'}, {'role': 'assistant', 'content': 'hi there'}]},
+             {'messages': [{'role': 'user', 'content': 'compare <image> with text'}, {'role': 'assistant', 'content': 'ok'}], 'images': [img2]}]
+    tpl = m._group(None).template
+    f = tpl.encode(trajs[0])
+    t, h, w = f['image_grid_thw'][0]
+    assert (t, h, w) == (1, 4, 6) and f['input_ids'].count(tpl.image_token_id) == t * h * w // 4 and f['pixel_values'].shape == (24, 1176)
+    assert f['mrope_position_ids'].shape == (3, len(f['input_ids'])) and f['position_ids'] == list(range(len(f['input_ids'])))
+    assert all(l == -100 for i, l in zip(f['input_ids'], f['labels']) if i == tpl.image_token_id)   # no loss on placeholders
+    assert 'pixel_values' not in tpl.encode(trajs[1])
+    with pytest.raises(ValueError):
+        tpl.encode({'messages': [{'role': 'user', 'content': '<image>'}], 'images': []})
+    mb, = InputProcessor()(tpl.batch_encode(trajs))
+    T_ = mb.input_ids.numel()
+    assert mb.extras['mrope_position_ids'].shape == (3, T_) and mb.extras['image_grid_thw'].tolist() == [[1, 4, 6], [1, 4, 4]]
+    assert mb.extras['pixel_values'].shape[0] == 24 + 16 and mb.cu_seqlens.numel() == 4   # 40 × 40 is scaled up to the minimum pixel count
+    a, b = int(mb.cu_seqlens[1]), int(mb.cu_seqlens[2])
+    assert mb.extras['mrope_position_ids'][:, a:b].tolist() == [list(range(b - a))] * 3            # the text-only sequence in the middle
+    with pytest.raises(NotImplementedError):
+        InputProcessor(sp_size=2, sp_rank=0)(tpl.batch_encode(trajs))
+
+    m.set_optimizer('AdamW', lr=1e-2)
+    w0 = m.model.visual.patch_embed.proj.weight.detach().clone()
+    losses = []
+    for _ in range(4):
+        losses.append(float(m.forward_backward(inputs=trajs)['loss']))
+        m.clip_grad_and_step(max_grad_norm=1.0)
+    assert losses[-1] < 0.6 * losses[0] and not torch.equal(w0, m.model.visual.patch_embed.proj.weight)   # the tower trains too
+    out = m.save('ck', str(tmp_path))
+    cfg = json.load(open(out + '/config.json'))
+    assert cfg['model_type'] == 'qwen2_vl' and cfg['vision_config']['embed_dim'] == 64 and cfg['text_config']['rope_scaling']['mrope_section'] == [8, 12, 12]
+    assert DecoderConfig.from_pretrained(out).vision == m.config.vision
+    m2 = TransformersModel(model_id=out, seed=3)
+    m2.set_template('Qwen2VLTemplate', vision_config=m2.config.vision, max_length=4096)
+    la, lb = m.forward_only(inputs=trajs), m2.forward_only(inputs=trajs)
+    assert torch.allclose(torch.as_tensor(la['logps']).float(), torch.as_tensor(lb['logps']).float(), atol=1e-5)
+    T = pytest.importorskip('transformers')
+    try:
+        back = T.Qwen2VLForConditionalGeneration.from_pretrained(out).float().eval()
+    except Exception as e:
+        pytest.skip(f'transformers could not load the export: {type(e).__name__}: {e}')
+    ids = torch.tensor([f['input_ids']])
+    with torch.no_grad():
+        try:
+            theirs = back(input_ids=ids, pixel_values=f['pixel_values'], image_grid_thw=torch.tensor(f['image_grid_thw']),
+                          mm_token_type_ids=(ids == tpl.image_token_id).int()).logits[0]
+        except TypeError as e:
+            pytest.skip(str(e))
+        ours = torch.as_tensor(m.forward_only(inputs=[trajs[0]], return_logits=True)['logits']).float().reshape(-1, theirs.shape[-1])[:theirs.shape[0]]
+    assert torch.allclose(ours, theirs, atol=5e-5), float((ours - theirs).abs().max())
+
+
+def _vl_trajs():
+    g = torch.Generator().manual_seed(5)
+    mk = lambda h, w: torch.rand(3, h, w, generator=g) * 255  # noqa: E731
+    return [{'messages': [{'role': 'user', 'content': [{'type': 'image', 'image': mk(60, 90)}, {'type': 'text', 'text': 'what is this?'}]},
+                          {'role': 'assistant', 'content': 'a cat on a mat'}]},
+            {'messages': [{'role': 'user', 'content': [{'type': 'text', 'text': 'and this one'}, {'type': 'image', 'image': mk(56, 56)}]},
+                          {'role': 'assistant', 'content': 'a dog'}]}]
+
+
+def _vl_curve(rank, world, steps):
+    import torch.distributed as dist
+    from twinkle_b200.model import TransformersModel
+    from twinkle_b200.utils.device_mesh import DeviceMesh
+    mesh = DeviceMesh.from_sizes(fsdp_size=world, dp_size=None) if world > 1 else DeviceMesh.from_sizes(dp_size=1)
+    m = TransformersModel(model_id='tiny-vl', device_mesh=mesh, seed=0)
+    m.set_template('Qwen2VLTemplate', vision_config=m.config.vision, max_length=4096)
+    m.set_optimizer('AdamW', lr=3e-3, weight_decay=0.0)
+    trajs = _vl_trajs()
+    sl = mesh.get_slice(len(trajs), mesh.get_data_rank_from_global_rank(rank))
+    curve = []
+    for _ in range(steps):
+        out = m.forward_backward(inputs=trajs[sl])
+        m.clip_grad_and_step(max_grad_norm=1.0)
+        t = torch.tensor([out['loss'] * out['num_tokens'], out['num_tokens']], dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t)
+        curve.append(float(t[0] / t[1]))
+    return curve
+
+
+def test_sharded_training_with_images_matches_one_process():
+    """Two gloo ranks, parameters (vision tower included, in the root unit) sharded over both, one image sample each:
+    the global loss curve equals the single-process run on both samples."""
+    from tests.dist_utils import run_ranks
+    single = _vl_curve(0, 1, 3)
+    multi = run_ranks(_vl_curve, 2, 3)
+    assert single[-1] < single[0]
+    for c in multi:
+        for a, b in zip(single, c):
+            assert abs(a - b) < 3e-4, (single, c)

@@ -250,6 +250,11 @@ class TransformersModel(TwinkleModel, CheckpointEngineMixin):
         extras = mb.extras or {}
         batch = PackedBatch(mb.input_ids, mb.position_ids, mb.cu_seqlens, mb.max_seqlen, mb.labels,
                             routed_experts=self._routed_for(extras, mb), seq_lens=list(mb.seq_lens))
+        if extras.get('pixel_values') is not None:  # vision-language batch: patches, grids and three-component positions
+            dt = next(self.model.parameters()).dtype
+            batch.pixel_values = extras['pixel_values'].to(self.device, dt)
+            batch.image_grid_thw = extras['image_grid_thw'].to(self.device)
+            batch.position_ids = extras['mrope_position_ids'].to(self.device)
         loss_obj = og.loss_instance
         want_entropy = bool(getattr(loss_obj, 'require_entropy', False))
         want_logits = return_logits or bool(getattr(loss_obj, 'require_logits', False))

@@ -33,8 +33,19 @@ def _hf_layer(i: int, rest: str) -> str:
     return f'model.layers.{i}.{rest}'
 
 
+def _vl(name: str, cfg: DecoderConfig) -> str:
+    """Vision-language checkpoints nest the language model: ``model.X`` → ``model.language_model.X``."""
+    return 'model.language_model.' + name[len('model.'):] if cfg.vision and name.startswith('model.') else name
+
+
 def internal_to_hf(name: str, tensor: torch.Tensor, cfg: DecoderConfig) -> List[Tuple[str, torch.Tensor]]:
     """One internal (full, un-sharded) tensor → one or more HF tensors."""
+    if name.startswith('visual.'):
+        return [('model.' + name, tensor)]
+    return [(_vl(n, cfg), t) for n, t in _internal_to_hf_text(name, tensor, cfg)]
+
+
+def _internal_to_hf_text(name: str, tensor: torch.Tensor, cfg: DecoderConfig) -> List[Tuple[str, torch.Tensor]]:
     if name == 'embed_tokens.weight':
         return [('model.embed_tokens.weight', tensor)]
     if name == 'norm.weight':
@@ -73,6 +84,12 @@ def internal_to_hf(name: str, tensor: torch.Tensor, cfg: DecoderConfig) -> List[
 
 def hf_names_for(name: str, cfg: DecoderConfig) -> List[str]:
     """HF tensor names that make up one internal tensor (in concat order)."""
+    if name.startswith('visual.'):
+        return ['model.' + name]
+    return [_vl(n, cfg) for n in _hf_names_for_text(name, cfg)]
+
+
+def _hf_names_for_text(name: str, cfg: DecoderConfig) -> List[str]:
     meta = torch.empty(0)
     if name == 'embed_tokens.weight':
         return ['model.embed_tokens.weight']
@@ -107,6 +124,16 @@ def hf_to_internal(name: str, cfg: DecoderConfig, get: Callable[[str], torch.Ten
     m = _LAYER.match(name)
     rest = m.group(2) if m else ''
     i = int(m.group(1)) if m else -1
+    if cfg.vision:
+        raw = get
+
+        def get(n: str) -> torch.Tensor:  # noqa: F811 — older checkpoints keep ``visual.*`` / ``model.layers.*`` at the top level
+            for cand in (n, n.replace('model.language_model.', 'model.', 1), n.replace('model.visual.', 'visual.', 1), _vl(n, cfg)):
+                try:
+                    return raw(cand)
+                except KeyError:
+                    continue
+            raise KeyError(n)
     if rest == 'mlp.experts.gate_up_proj':
         lo, hi = expert_range or (0, cfg.num_experts)
         return torch.stack([torch.cat([get(_hf_layer(i, f'mlp.experts.{e}.gate_proj.weight')),

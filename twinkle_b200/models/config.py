@@ -19,7 +19,7 @@ def _rope_scaling_of(cfg: Dict[str, Any]) -> Optional[Dict[str, Any]]:
     if not isinstance(rs, dict):
         return None
     kind = rs.get('rope_type', rs.get('type', 'default'))
-    if kind in (None, 'default'):
+    if kind in (None, 'default', 'mrope'):  # mrope is a position layout (see DecoderConfig.mrope_section), not a frequency change
         return None
     out = {k: v for k, v in rs.items() if k != 'rope_theta'}
     out.setdefault('rope_type', kind)
@@ -64,6 +64,14 @@ class DecoderConfig:
     linear_key_head_dim: int = 128
     linear_value_head_dim: int = 128
     linear_conv_kernel_dim: int = 4
+    # vision-language (Qwen2-VL family): the vision tower's config.json section, placeholder token ids, and the split of
+    # the rotary half-dimension over (time, height, width) positions
+    vision: Optional[Dict[str, Any]] = None
+    image_token_id: Optional[int] = None
+    video_token_id: Optional[int] = None
+    vision_start_token_id: Optional[int] = None
+    vision_end_token_id: Optional[int] = None
+    mrope_section: Optional[List[int]] = None
 
     @property
     def is_moe(self) -> bool:
@@ -102,9 +110,16 @@ class DecoderConfig:
     @classmethod
     def from_hf(cls, cfg: Dict[str, Any]) -> 'DecoderConfig':
         cfg = dict(cfg)
+        top = cfg
         if 'text_config' in cfg:
             cfg = dict(cfg['text_config'])
         mt = cfg.get('model_type', 'qwen3')
+        vision = top.get('vision_config')
+        if vision is not None:
+            vision = dict(vision)
+            if vision.get('model_type', top.get('model_type', 'qwen2_vl')) not in ('qwen2_vl', ):
+                raise NotImplementedError(f"vision tower of type {vision.get('model_type')!r} is not supported (qwen2_vl is)")
+        rs_any = cfg.get('rope_scaling') or cfg.get('rope_parameters') or top.get('rope_scaling') or {}
         heads = cfg.get('num_attention_heads', 32)
         out = cls(
             vocab_size=cfg.get('vocab_size', 151936), hidden_size=cfg.get('hidden_size', 4096),
@@ -113,7 +128,7 @@ class DecoderConfig:
             head_dim=cfg.get('head_dim') or cfg.get('hidden_size', 4096) // heads, rms_norm_eps=cfg.get('rms_norm_eps', 1e-6),
             rope_theta=float(cfg.get('rope_theta', (cfg.get('rope_parameters') or {}).get('rope_theta', 1e6))),
             rope_scaling=_rope_scaling_of(cfg), tie_word_embeddings=bool(cfg.get('tie_word_embeddings', False)),
-            qk_norm=mt.startswith('qwen3'), attention_bias=bool(cfg.get('attention_bias', mt in ('qwen2', 'qwen2_moe'))),
+            qk_norm=mt.startswith('qwen3'), attention_bias=bool(cfg.get('attention_bias', mt.startswith('qwen2'))),
             num_experts=cfg.get('num_experts', cfg.get('num_local_experts', 0)) or 0,
             num_experts_per_tok=cfg.get('num_experts_per_tok', 8), moe_intermediate_size=cfg.get('moe_intermediate_size', 768),
             norm_topk_prob=bool(cfg.get('norm_topk_prob', True)), router_aux_loss_coef=float(cfg.get('router_aux_loss_coef', 0.0)),
@@ -123,6 +138,9 @@ class DecoderConfig:
             linear_num_key_heads=cfg.get('linear_num_key_heads', 16), linear_num_value_heads=cfg.get('linear_num_value_heads', 32),
             linear_key_head_dim=cfg.get('linear_key_head_dim', 128), linear_value_head_dim=cfg.get('linear_value_head_dim', 128),
             linear_conv_kernel_dim=cfg.get('linear_conv_kernel_dim', 4),
+            vision=vision, image_token_id=top.get('image_token_id'), video_token_id=top.get('video_token_id'),
+            vision_start_token_id=top.get('vision_start_token_id'), vision_end_token_id=top.get('vision_end_token_id'),
+            mrope_section=list(rs_any['mrope_section']) if isinstance(rs_any, dict) and rs_any.get('mrope_section') else None,
             initializer_range=cfg.get('initializer_range', 0.02), model_type=mt,
             torch_dtype=str(cfg.get('torch_dtype', cfg.get('dtype', 'bfloat16'))),
             max_position_embeddings=cfg.get('max_position_embeddings', 40960), pad_token_id=cfg.get('pad_token_id'),
@@ -155,6 +173,13 @@ class DecoderConfig:
             d['rms_norm_offset'] = self.rms_norm_offset
         if self.rope_scaling:
             d['rope_scaling'] = dict(self.rope_scaling)
+        if self.vision:
+            text = dict(d, model_type='qwen2_vl_text', rope_scaling={'type': 'mrope', 'mrope_section': list(self.mrope_section or [])})
+            text.pop('architectures', None)
+            return {'architectures': ['Qwen2VLForConditionalGeneration'], 'model_type': 'qwen2_vl', 'text_config': text,
+                    'vision_config': dict(self.vision), 'image_token_id': self.image_token_id, 'video_token_id': self.video_token_id,
+                    'vision_start_token_id': self.vision_start_token_id, 'vision_end_token_id': self.vision_end_token_id,
+                    'tie_word_embeddings': self.tie_word_embeddings, 'torch_dtype': self.torch_dtype}
         if self.layer_types:
             d.update(layer_types=list(self.layer_types), linear_num_key_heads=self.linear_num_key_heads,
                      linear_num_value_heads=self.linear_num_value_heads, linear_key_head_dim=self.linear_key_head_dim,
@@ -179,6 +204,12 @@ PRESETS: Dict[str, Dict[str, Any]] = {
     'tiny-moe': dict(vocab_size=1024, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
                      head_dim=64, rope_theta=1e4, tie_word_embeddings=True, num_experts=8, num_experts_per_tok=2,
                      moe_intermediate_size=128, router_aux_loss_coef=1e-3, torch_dtype='float32'),
+    'tiny-vl': dict(vocab_size=1024, hidden_size=256, intermediate_size=688, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                    head_dim=64, rope_theta=1e4, tie_word_embeddings=True, qk_norm=False, attention_bias=True, torch_dtype='float32',
+                    model_type='qwen2_vl_text', mrope_section=[8, 12, 12], image_token_id=265, video_token_id=267, vision_start_token_id=264,
+                    vision_end_token_id=266,  # ids of these tokens in the byte-level test tokenizer
+                    vision=dict(depth=2, embed_dim=64, hidden_size=256, num_heads=4, mlp_ratio=2, patch_size=14,
+                                                          spatial_merge_size=2, temporal_patch_size=2, in_channels=3)),
     'tiny-moe-shared': dict(vocab_size=1024, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
                             head_dim=64, rope_theta=1e4, tie_word_embeddings=True, num_experts=8, num_experts_per_tok=2,
                             moe_intermediate_size=128, shared_expert_intermediate_size=192, torch_dtype='float32'),

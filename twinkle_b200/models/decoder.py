@@ -40,6 +40,10 @@ class PackedBatch:
     # (cos, sin) of the whole row; set by the model forward when the Ulysses strategy scatters heads inside the q|k|v
     # projection, because q/k-norm and RoPE then run after the exchange on all tokens of this rank's heads
     rope_full: Optional[tuple] = None
+    # vision-language: flat patches of every image in the batch (in token order) and their (t, h, w) patch grids; the
+    # tower's output replaces the embeddings of the image placeholder tokens. position_ids is then [3, T].
+    pixel_values: Optional[torch.Tensor] = None
+    image_grid_thw: Optional[torch.Tensor] = None
 
 
 class Attention(nn.Module):
@@ -266,6 +270,11 @@ class DecoderModel(nn.Module):
         else:
             self.lm_head = None
         self.has_head = has_head
+        if cfg.vision and has_embed:
+            from .vision import VisionConfig, VisionTower
+            self.visual = VisionTower(VisionConfig.from_hf(cfg.vision))
+        else:
+            self.visual = None
         for name, m in self.named_modules():
             if isinstance(m, Linear):
                 m.full_name = name
@@ -304,12 +313,26 @@ class DecoderModel(nn.Module):
             return batch.inputs_embeds
         if self.tp is not None:
             from ..parallel.tensor import vocab_parallel_embedding
-            return vocab_parallel_embedding(batch.input_ids, self.embed_tokens.weight, self.tp)
-        return self.embed_tokens(batch.input_ids)
+            x = vocab_parallel_embedding(batch.input_ids, self.embed_tokens.weight, self.tp)
+        else:
+            x = self.embed_tokens(batch.input_ids)
+        if batch.pixel_values is not None and self.visual is not None:
+            feats = self.visual(batch.pixel_values, batch.image_grid_thw)
+            where = batch.input_ids == self.cfg.image_token_id
+            if self.cfg.video_token_id is not None:
+                where = where | (batch.input_ids == self.cfg.video_token_id)
+            if int(where.sum()) != feats.shape[0]:
+                raise ValueError(f'{int(where.sum())} image placeholder tokens in the batch but the tower produced {feats.shape[0]} embeddings')
+            x = x.masked_scatter(where[:, None], feats.to(x.dtype))
+        return x
 
     def forward(self, batch: PackedBatch, hidden: Optional[torch.Tensor] = None, kv_sink=None) -> torch.Tensor:
         x = self.embed(batch) if hidden is None else hidden
-        cos, sin = ops.rope_tables(batch.position_ids, self.cfg.head_dim, self.cfg.rope_theta, self.cfg.rope_scaling)
+        if batch.position_ids.dim() == 2:  # [3, T] (time, height, width) positions of a vision-language batch
+            from .vision import mrope_tables
+            cos, sin = mrope_tables(batch.position_ids, self.cfg.head_dim, self.cfg.rope_theta, self.cfg.mrope_section)
+        else:
+            cos, sin = ops.rope_tables(batch.position_ids, self.cfg.head_dim, self.cfg.rope_theta, self.cfg.rope_scaling)
         full = None
         for layer in self.layers:
             ap = getattr(getattr(layer, 'self_attn', None), 'attn_parallel', None)

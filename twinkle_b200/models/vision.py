@@ -1,0 +1,268 @@
+"""Vision side of the Qwen2-VL family: the patch encoder that turns images into embeddings at the language model's
+width, the three-component ("multimodal") rotary position tables, the position index that lays images out on a
+(time, height, width) grid inside the token stream, and the image → patch preprocessing.
+
+Parameter names and shapes follow the Hugging Face checkpoint (``visual.patch_embed.proj``, ``visual.blocks.N.{norm1,
+attn.qkv, attn.proj, norm2, mlp.fc1, mlp.fc2}``, ``visual.merger.{ln_q, mlp.0, mlp.2}``), so weights load by name.
+
+The reference trains such models through ``transformers`` (``cookbook/mm/fsdp2.py``; ``template/base.py:611-667``
+``pre_forward_hook``); here the tower is part of the owned model, its output is scattered into the embedding stream of
+the packed batch, and the language model's RoPE kernels take the multimodal tables unchanged (they are per-token tables).
+Attention inside the tower is dense per image (no causal mask, head width ≠ 128) and runs on PyTorch's SDPA."""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+@dataclass
+class VisionConfig:
+    depth: int = 32
+    embed_dim: int = 1280
+    hidden_size: int = 3584          # output width = the language model's hidden size
+    num_heads: int = 16
+    mlp_ratio: float = 4.0
+    patch_size: int = 14
+    spatial_merge_size: int = 2
+    temporal_patch_size: int = 2
+    in_channels: int = 3
+
+    @classmethod
+    def from_hf(cls, d: Dict[str, Any]) -> 'VisionConfig':
+        keys = ('depth', 'embed_dim', 'hidden_size', 'num_heads', 'mlp_ratio', 'patch_size', 'spatial_merge_size', 'temporal_patch_size', 'in_channels')
+        return cls(**{k: d[k] for k in keys if k in d})
+
+    def to_hf(self) -> Dict[str, Any]:
+        return {'model_type': 'qwen2_vl', **self.__dict__, 'hidden_act': 'quick_gelu'}
+
+    @property
+    def patch_dim(self) -> int:
+        return self.in_channels * self.temporal_patch_size * self.patch_size * self.patch_size
+
+
+class _PatchEmbed(nn.Module):
+
+    def __init__(self, cfg: VisionConfig):
+        super().__init__()
+        # kept in Conv3d layout [E, C, T, P, P] so the checkpoint tensor loads as is; applied as one GEMM over flat patches
+        self.proj = nn.Conv3d(cfg.in_channels, cfg.embed_dim, (cfg.temporal_patch_size, cfg.patch_size, cfg.patch_size),
+                              stride=(cfg.temporal_patch_size, cfg.patch_size, cfg.patch_size), bias=False)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        w = self.proj.weight
+        return F.linear(x.to(w.dtype), w.view(w.shape[0], -1))
+
+
+class _Attn(nn.Module):
+
+    def __init__(self, dim: int, heads: int):
+        super().__init__()
+        self.heads = heads
+        self.qkv = nn.Linear(dim, 3 * dim, bias=True)
+        self.proj = nn.Linear(dim, dim, bias=True)
+
+    def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, bounds: Sequence[int]) -> torch.Tensor:
+        n, dim = x.shape
+        q, k, v = self.qkv(x).view(n, 3, self.heads, dim // self.heads).unbind(1)
+        q, k = _rotate(q, cos, sin), _rotate(k, cos, sin)
+        outs = []
+        for a, b in zip(bounds[:-1], bounds[1:]):           # one frame (or image) attends within itself
+            o = F.scaled_dot_product_attention(q[a:b].transpose(0, 1), k[a:b].transpose(0, 1), v[a:b].transpose(0, 1))
+            outs.append(o.transpose(0, 1))
+        return self.proj(torch.cat(outs, 0).reshape(n, dim))
+
+
+def _rotate(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotate-half RoPE with half-width tables ``[N, D/2]`` on ``x [N, H, D]`` (pairs ``(i, i + D/2)``), in fp32."""
+    d2 = x.shape[-1] // 2
+    xf = x.float()
+    x1, x2 = xf[..., :d2], xf[..., d2:]
+    c, s = cos[:, None, :], sin[:, None, :]
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], -1).to(x.dtype)
+
+
+class _Mlp(nn.Module):
+
+    def __init__(self, dim: int, hidden: int):
+        super().__init__()
+        self.fc1, self.fc2 = nn.Linear(dim, hidden), nn.Linear(hidden, dim)
+
+    def forward(self, x):
+        h = self.fc1(x)
+        return self.fc2(h * torch.sigmoid(1.702 * h))      # "quick" GELU
+
+
+class _Block(nn.Module):
+
+    def __init__(self, cfg: VisionConfig):
+        super().__init__()
+        self.norm1, self.norm2 = nn.LayerNorm(cfg.embed_dim, eps=1e-6), nn.LayerNorm(cfg.embed_dim, eps=1e-6)
+        self.attn = _Attn(cfg.embed_dim, cfg.num_heads)
+        self.mlp = _Mlp(cfg.embed_dim, int(cfg.embed_dim * cfg.mlp_ratio))
+
+    def forward(self, x, cos, sin, bounds):
+        x = x + self.attn(self.norm1(x), cos, sin, bounds)
+        return x + self.mlp(self.norm2(x))
+
+
+class _Merger(nn.Module):
+    """Joins every ``merge × merge`` neighbourhood (consecutive in patch order) into one token of the language model's width."""
+
+    def __init__(self, cfg: VisionConfig):
+        super().__init__()
+        self.group = cfg.embed_dim * cfg.spatial_merge_size**2
+        self.ln_q = nn.LayerNorm(cfg.embed_dim, eps=1e-6)
+        self.mlp = nn.Sequential(nn.Linear(self.group, self.group), nn.GELU(), nn.Linear(self.group, cfg.hidden_size))
+
+    def forward(self, x):
+        return self.mlp(self.ln_q(x).view(-1, self.group))
+
+
+class VisionTower(nn.Module):
+
+    def __init__(self, cfg: VisionConfig):
+        super().__init__()
+        self.cfg = cfg
+        self.patch_embed = _PatchEmbed(cfg)
+        self.blocks = nn.ModuleList([_Block(cfg) for _ in range(cfg.depth)])
+        self.merger = _Merger(cfg)
+
+    def rotary_tables(self, grid_thw: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """cos/sin ``[N, head_dim/2]``: the first quarter of the head rotates with the patch's row, the second with its
+        column (patches are ordered merge-group by merge-group, as the preprocessing emits them)."""
+        m, dev = self.cfg.spatial_merge_size, grid_thw.device
+        quarter = self.cfg.embed_dim // self.cfg.num_heads // 4
+        inv = 1.0 / (10000.0**(torch.arange(0, 2 * quarter, 2, dtype=torch.float32, device=dev) / (2 * quarter)))
+        pos = []
+        for t, h, w in grid_thw.tolist():
+            hp = torch.arange(h, device=dev)[:, None].expand(h, w).reshape(h // m, m, w // m, m).permute(0, 2, 1, 3).flatten()
+            wp = torch.arange(w, device=dev)[None, :].expand(h, w).reshape(h // m, m, w // m, m).permute(0, 2, 1, 3).flatten()
+            pos.append(torch.stack([hp, wp], -1).repeat(t, 1))
+        pos = torch.cat(pos, 0).float()
+        ang = torch.cat([pos[:, 0:1] * inv[None, :], pos[:, 1:2] * inv[None, :]], -1)
+        return ang.cos(), ang.sin()
+
+    def forward(self, pixel_values: torch.Tensor, grid_thw: torch.Tensor) -> torch.Tensor:
+        """``pixel_values [N, C·T·P·P]`` (flat patches of all images, in order), ``grid_thw [n_images, 3]`` →
+        ``[N / merge², hidden_size]``."""
+        x = self.patch_embed(pixel_values)
+        cos, sin = self.rotary_tables(grid_thw)
+        frames = torch.repeat_interleave(grid_thw[:, 1] * grid_thw[:, 2], grid_thw[:, 0])
+        bounds = [0] + frames.cumsum(0).tolist()
+        for blk in self.blocks:
+            x = blk(x, cos, sin, bounds)
+        return self.merger(x)
+
+
+# ------------------------------------------------------------------------------------------ positions in the LLM
+def mrope_tables(position_ids: torch.Tensor, head_dim: int, theta: float, section: Sequence[int]) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin ``[T, head_dim/2]`` from ``position_ids [3, T]`` (time, height, width): frequency ``j`` uses the component
+    whose section (``section`` sums to ``head_dim/2``) contains ``j``. Text tokens carry the same value in all three
+    components, which reduces to ordinary RoPE."""
+    half = head_dim // 2
+    assert sum(section) == half, f'mrope sections {list(section)} must sum to head_dim/2 = {half}'
+    inv = 1.0 / (theta**(torch.arange(0, head_dim, 2, dtype=torch.float32, device=position_ids.device) / head_dim))
+    comp = torch.repeat_interleave(torch.arange(3, device=position_ids.device), torch.tensor(list(section), device=position_ids.device))
+    pos = position_ids.float()[comp, :].t()                  # [T, half]: the component each frequency follows
+    ang = pos * inv[None, :]
+    return ang.cos(), ang.sin()
+
+
+def rope_index(input_ids: Sequence[int], grids: Sequence[Sequence[int]], image_token_id: int, merge: int = 2,
+               video_token_id: Optional[int] = None) -> torch.Tensor:
+    """Positions ``[3, L]`` of one sequence whose images appear as runs of ``image_token_id`` (``t·h·w / merge²`` tokens
+    per image, in the order of ``grids``). Text advances all three components together; an image keeps time fixed and
+    spreads height and width over its merged grid; the text after it continues from the largest position used + 1."""
+    ids = list(int(t) for t in input_ids)
+    out = torch.zeros(3, len(ids), dtype=torch.long)
+    nxt, i, g = 0, 0, 0
+    special = {image_token_id} | ({video_token_id} if video_token_id is not None else set())
+    while i < len(ids):
+        if ids[i] in special:
+            t, h, w = grids[g]
+            g += 1
+            gh, gw = h // merge, w // merge
+            n = t * gh * gw
+            if ids[i:i + n] != [ids[i]] * n:
+                raise ValueError(f'image {g - 1}: expected a run of {n} placeholder tokens at position {i}')
+            tt = torch.arange(t).view(-1, 1, 1).expand(t, gh, gw).flatten()
+            hh = torch.arange(gh).view(1, -1, 1).expand(t, gh, gw).flatten()
+            ww = torch.arange(gw).view(1, 1, -1).expand(t, gh, gw).flatten()
+            out[:, i:i + n] = torch.stack([tt, hh, ww]) + nxt
+            nxt += max(t, gh, gw)
+            i += n
+        else:
+            out[:, i] = nxt
+            nxt += 1
+            i += 1
+    if g != len(grids):
+        raise ValueError(f'{len(grids)} images given but {g} placeholder runs found')
+    return out
+
+
+# ---------------------------------------------------------------------------------------------- preprocessing
+IMAGE_MEAN = (0.48145466, 0.4578275, 0.40821073)
+IMAGE_STD = (0.26862954, 0.26130258, 0.27577711)
+
+
+def smart_resize(height: int, width: int, factor: int = 28, min_pixels: int = 56 * 56, max_pixels: int = 14 * 14 * 4 * 1280) -> Tuple[int, int]:
+    """Nearest size whose sides are multiples of ``factor`` with the pixel count inside ``[min_pixels, max_pixels]`` and
+    the aspect ratio kept as far as possible."""
+    if max(height, width) / max(min(height, width), 1) > 200:
+        raise ValueError(f'aspect ratio of {height}x{width} exceeds 200')
+    h, w = max(factor, round(height / factor) * factor), max(factor, round(width / factor) * factor)
+    if h * w > max_pixels:
+        beta = math.sqrt(height * width / max_pixels)
+        h, w = math.floor(height / beta / factor) * factor, math.floor(width / beta / factor) * factor
+    elif h * w < min_pixels:
+        beta = math.sqrt(min_pixels / (height * width))
+        h, w = math.ceil(height * beta / factor) * factor, math.ceil(width * beta / factor) * factor
+    return max(h, factor), max(w, factor)
+
+
+def patchify(frames: torch.Tensor, cfg: VisionConfig) -> Tuple[torch.Tensor, Tuple[int, int, int]]:
+    """``frames [T, C, H, W]`` (already resized so that H, W are multiples of ``patch·merge``, normalised) →
+    (``[t·h·w, C·Tp·P·P]`` flat patches ordered merge-group by merge-group, ``(t, h, w)``). A single image is repeated
+    to fill the temporal patch."""
+    tp, p, m = cfg.temporal_patch_size, cfg.patch_size, cfg.spatial_merge_size
+    if frames.shape[0] % tp:
+        frames = torch.cat([frames, frames[-1:].expand(tp - frames.shape[0] % tp, -1, -1, -1)], 0)
+    T, C, H, W = frames.shape
+    t, h, w = T // tp, H // p, W // p
+    x = frames.reshape(t, tp, C, h // m, m, p, w // m, m, p)
+    x = x.permute(0, 3, 6, 4, 7, 2, 1, 5, 8)                # t, h/m, w/m, m, m, C, tp, p, p
+    return x.reshape(t * h * w, C * tp * p * p), (t, h, w)
+
+
+def preprocess_image(image: Any, cfg: VisionConfig, min_pixels: int = 56 * 56, max_pixels: int = 14 * 14 * 4 * 1280) -> Tuple[torch.Tensor, Tuple[int, int, int]]:
+    """A PIL image, a path / URL / bytes (see ``utils.misc.load_image``) or a ``[C, H, W]`` / ``[H, W, C]`` array in 0…255 →
+    normalised flat patches and the patch grid."""
+    if not torch.is_tensor(image):
+        import numpy as np
+        if not hasattr(image, 'shape'):
+            from ..utils.misc import load_image
+            image = np.asarray(load_image(image))
+        image = torch.as_tensor(np.asarray(image))
+    x = image.float()
+    if x.dim() == 3 and x.shape[-1] in (1, 3) and x.shape[0] not in (1, 3):
+        x = x.permute(2, 0, 1)
+    if x.shape[0] == 1:
+        x = x.expand(3, -1, -1)
+    factor = cfg.patch_size * cfg.spatial_merge_size
+    h, w = smart_resize(x.shape[1], x.shape[2], factor, min_pixels, max_pixels)
+    if (h, w) != tuple(x.shape[1:]):
+        try:  # the same resampling as the Hugging Face processor (PIL bicubic on 8-bit pixels), so features match its output
+            import numpy as np
+            from PIL import Image
+            pil = Image.fromarray(x.clamp(0, 255).round().byte().permute(1, 2, 0).numpy()).resize((w, h), resample=Image.BICUBIC)
+            x = torch.as_tensor(np.array(pil)).permute(2, 0, 1).float()
+        except ImportError:
+            x = F.interpolate(x[None], size=(h, w), mode='bicubic', align_corners=False, antialias=True)[0].clamp(0, 255)
+    mean, std = torch.tensor(IMAGE_MEAN).view(3, 1, 1), torch.tensor(IMAGE_STD).view(3, 1, 1)
+    x = (x / 255.0 - mean) / std
+    return patchify(x[None], cfg)

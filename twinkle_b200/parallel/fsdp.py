@@ -407,7 +407,8 @@ class FSDPEngine:
             self.units.append(FSDPUnit(f'layers.{layer.layer_idx}', split(f'layers.{layer.layer_idx}', layer), comm,
                                        compute_dtype, self.device, grad_dtype))
         root_params = []
-        for n, m in (('embed_tokens', model.embed_tokens), ('norm', model.norm), ('lm_head', model.lm_head)):
+        for n, m in (('embed_tokens', model.embed_tokens), ('norm', model.norm), ('lm_head', model.lm_head),
+                     ('visual', getattr(model, 'visual', None))):  # the vision tower lives (and is sharded) with the root unit
             if m is not None:
                 root_params += split(n, m)
         self.root = FSDPUnit('root', root_params, comm, compute_dtype, self.device, grad_dtype)

@@ -108,7 +108,7 @@ class InputProcessor:
                     ids, labels = ids[am], labels[am]
                     pos = torch.arange(ids.numel()) if f.get('position_ids') is None else pos[am]
             item = {'input_ids': ids, 'labels': labels, 'position_ids': pos}
-            for k in ('routed_experts', ):
+            for k in ('routed_experts', 'pixel_values', 'image_grid_thw', 'mrope_position_ids'):
                 if f.get(k) is not None:
                     item[k] = f[k]
             out.append(item)
@@ -188,6 +188,22 @@ class InputProcessor:
         extras = {}
         if any('routed_experts' in it for it in items):
             extras['routed_experts'] = [it.get('routed_experts') for it in items]
+        if any('pixel_values' in it for it in items):
+            if self.sp_size > 1 or self.cp_size > 1:
+                raise NotImplementedError('batches with images are not split over sequence- or context-parallel ranks')
+            # images travel beside the packed row: all patches in token order, their grids, and (time, height, width)
+            # positions for every token (text-only sequences and padding count up in all three components alike)
+            mpos = []
+            for it, n in zip(items, lens):
+                m = torch.as_tensor(it['mrope_position_ids']).long() if 'mrope_position_ids' in it else torch.arange(it['input_ids'].numel()).expand(3, -1)
+                extra = n - m.shape[1]
+                if extra > 0:
+                    start = int(m.max()) + 1 if m.numel() else 0
+                    m = torch.cat([m, torch.arange(start, start + extra).expand(3, -1)], 1)
+                mpos.append(m)
+            extras['mrope_position_ids'] = torch.cat(mpos, 1)
+            extras['pixel_values'] = torch.cat([torch.as_tensor(it['pixel_values']) for it in items if 'pixel_values' in it], 0)
+            extras['image_grid_thw'] = torch.cat([torch.as_tensor(it['image_grid_thw']).long().view(-1, 3) for it in items if 'pixel_values' in it], 0)
         mb.extras = extras or None
         return self._split_parallel(mb) if split else mb
 

@@ -29,7 +29,8 @@ IGNORE = -100
 
 class ByteChatTokenizer:
     """UTF-8 bytes + a few ChatML control tokens.  ids 0..255 are bytes."""
-    SPECIAL = ['<|pad|>', '<|im_start|>', '<|im_end|>', '<|endoftext|>', '<tool_call>', '</tool_call>', '<think>', '</think>']
+    SPECIAL = ['<|pad|>', '<|im_start|>', '<|im_end|>', '<|endoftext|>', '<tool_call>', '</tool_call>', '<think>', '</think>',
+               '<|vision_start|>', '<|image_pad|>', '<|vision_end|>', '<|video_pad|>']
 
     def __init__(self, vocab_size: int = 1024):
         self.special = {t: 256 + i for i, t in enumerate(self.SPECIAL)}
@@ -352,5 +353,84 @@ class DeepseekV4Template(Template):
     pass
 
 
+class Qwen2VLTemplate(Template):
+    """Chat template for the Qwen2-VL family: images given as content parts (``{'type': 'image', 'image': path | URL | bytes |
+    PIL | array}``) or as ``trajectory['images']`` matched to ``<image>`` markers in the text become
+    ``<|vision_start|><|image_pad|>…<|vision_end|>`` with one pad token per merged patch. The encoded feature carries
+    ``pixel_values`` (flat patches of all images), ``image_grid_thw`` and ``mrope_position_ids`` ``[3, L]`` (time / height
+    / width positions); ``position_ids`` stays the plain token index. Truncation that would cut through an image raises.
+
+    ``vision_config`` is the tower's config (a ``models.vision.VisionConfig`` or its dict); ``min_pixels`` / ``max_pixels``
+    bound the resized image. Reference: ``template/base.py:611-667`` + the HF processor it delegates to."""
+
+    IMAGE_MARK = '<|vision_start|><|image_pad|><|vision_end|>'
+
+    def __init__(self, *a, vision_config=None, min_pixels: int = 56 * 56, max_pixels: int = 14 * 14 * 4 * 1280, **kw):
+        super().__init__(*a, **kw)
+        from ..models.vision import VisionConfig
+        self.vision_config = vision_config if isinstance(vision_config, VisionConfig) else VisionConfig.from_hf(dict(vision_config or {}))
+        self.min_pixels, self.max_pixels = min_pixels, max_pixels
+        self.image_token_id = self.tokenizer.convert_tokens_to_ids('<|image_pad|>')
+        self._vision: List[Tuple[Any, Tuple[int, int, int]]] = []
+        self.pre_pipeline = self.pre_pipeline + [self._collect_images]
+        self.post_pipeline = self.post_pipeline + [self._attach_vision]
+
+    def _collect_images(self, traj: Trajectory) -> Trajectory:
+        from ..models.vision import preprocess_image
+        loose = list(traj.get('images') or [])
+        sources: List[Any] = []
+        for m in traj.get('messages') or []:
+            c = m.get('content')
+            if isinstance(c, list):
+                text = ''
+                for part in c:
+                    if part.get('type') in ('image', 'image_url'):
+                        src = part.get('image', part.get('image_url'))
+                        sources.append(src.get('url') if isinstance(src, dict) else src)
+                        text += self.IMAGE_MARK
+                    else:
+                        text += part.get('text', '')
+                m['content'] = text
+            elif isinstance(c, str) and '<image>' in c:
+                for _ in range(c.count('<image>')):
+                    if not loose:
+                        raise ValueError('more <image> markers than entries in trajectory["images"]')
+                    sources.append(loose.pop(0))
+                m['content'] = c.replace('<image>', self.IMAGE_MARK)
+        self._vision = [preprocess_image(src, self.vision_config, self.min_pixels, self.max_pixels) for src in sources]
+        return traj
+
+    def _render(self, messages, tools=None, add_generation_prompt: bool = False) -> List[int]:
+        ids = super()._render(messages, tools, add_generation_prompt)
+        if not self._vision:
+            return ids
+        merge2 = self.vision_config.spatial_merge_size**2
+        out, k = [], 0
+        for t in ids:
+            if t == self.image_token_id and k < len(self._vision):
+                g = self._vision[k][1]
+                out.extend([t] * (g[0] * g[1] * g[2] // merge2))
+                k += 1
+            else:
+                out.append(t)
+        return out
+
+    def _attach_vision(self, feats: List[InputFeature]) -> List[InputFeature]:
+        if not self._vision:
+            return feats
+        import torch
+        from ..models.vision import rope_index
+        if len(feats) != 1:
+            raise ValueError('a trajectory with images cannot be split into several features; raise max_length')
+        f = feats[0]
+        grids = [g for _, g in self._vision]
+        f['pixel_values'] = torch.cat([p for p, _ in self._vision], 0)                      # type: ignore[typeddict-unknown-key]
+        f['image_grid_thw'] = [list(g) for g in grids]                                      # type: ignore[typeddict-unknown-key]
+        f['mrope_position_ids'] = rope_index(f['input_ids'], grids, self.image_token_id,   # type: ignore[typeddict-unknown-key]
+                                             self.vision_config.spatial_merge_size)
+        return feats
+
+
 template_mapping = {'Template': Template, 'default': Template, 'Qwen3Template': Qwen3Template, 'qwen3': Qwen3Template,
-                    'Qwen3_5Template': Qwen3_5Template, 'qwen3_5': Qwen3_5Template, 'DeepseekV4Template': DeepseekV4Template}
+                    'Qwen3_5Template': Qwen3_5Template, 'qwen3_5': Qwen3_5Template, 'DeepseekV4Template': DeepseekV4Template,
+                    'Qwen2VLTemplate': Qwen2VLTemplate, 'qwen2_vl': Qwen2VLTemplate}
