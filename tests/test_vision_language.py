@@ -211,3 +211,19 @@ def test_sharded_training_with_images_matches_one_process():
     for c in multi:
         for a, b in zip(single, c):
             assert abs(a - b) < 3e-4, (single, c)
+
+
+def test_clevr_rows_flow_through_template_and_reward():
+    from twinkle_b200.preprocessor import CLEVRProcessor
+    from twinkle_b200.reward import MultiModalAccuracyReward
+    from twinkle_b200.template import template_mapping
+    img = torch.rand(3, 56, 56) * 255
+    row, = CLEVRProcessor()([{'problem': 'How many cubes?', 'solution': '<answer> 3 </answer>', 'image': img}])
+    assert row['images'][0] is img and row['user_data']['ground_truth'] == '3'
+    tpl = template_mapping['Qwen2VLTemplate'](model_id=None, vision_config=VC, max_length=4096)
+    f = tpl.encode(row)
+    assert f['image_grid_thw'] == [[1, 4, 4]] and f['input_ids'].count(tpl.image_token_id) == 4
+    text = tpl.decode(f['input_ids'], skip_special_tokens=False)
+    assert text.index('<|vision_start|>') < text.index('How many cubes?')          # an unmarked image precedes the question
+    done = dict(row, messages=row['messages'][:1] + [{'role': 'assistant', 'content': 'I count. <answer>3</answer>'}])
+    assert MultiModalAccuracyReward()([done]) == [1.0]

@@ -113,9 +113,16 @@ class EmojiDPOProcessor(Preprocessor):
 class CLEVRProcessor(Preprocessor):
 
     def preprocess(self, row):
-        t = _traj(row.get('problem', row.get('question', '')), row.get('solution'))
+        """Visual question answering rows (``problem`` / ``question``, ``solution`` possibly wrapped in ``<answer>`` tags, ``image``):
+        the image goes to ``images`` (the vision-language template places it before the question), the answer also to
+        ``user_data`` for the multimodal accuracy reward."""
+        sol = row.get('solution')
+        t = _traj(row.get('problem', row.get('question', '')), sol)
         if row.get('image') is not None:
             t['images'] = [row['image']]
+        if sol is not None:
+            m = re.search(r'<answer>\s*(.*?)\s*</answer>', str(sol), re.S)
+            t['user_data'] = {'solution': sol, 'ground_truth': m.group(1) if m else str(sol)}
         return t
 
 

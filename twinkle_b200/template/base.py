@@ -397,6 +397,13 @@ class Qwen2VLTemplate(Template):
                         raise ValueError('more <image> markers than entries in trajectory["images"]')
                     sources.append(loose.pop(0))
                 m['content'] = c.replace('<image>', self.IMAGE_MARK)
+        if loose:  # images without a marker go in front of the first user turn, in order
+            first = next((m for m in traj.get('messages') or [] if m.get('role') == 'user'), None)
+            if first is None:
+                raise ValueError('trajectory["images"] given but there is no user message to attach them to')
+            n_before = sum(str(m.get('content', '')).count(self.IMAGE_MARK) for m in traj['messages'][:traj['messages'].index(first)])
+            first['content'] = self.IMAGE_MARK * len(loose) + str(first.get('content') or '')
+            sources[n_before:n_before] = loose
         self._vision = [preprocess_image(src, self.vision_config, self.min_pixels, self.max_pixels) for src in sources]
         return traj
 
