@@ -227,3 +227,31 @@ def test_clevr_rows_flow_through_template_and_reward():
     assert text.index('<|vision_start|>') < text.index('How many cubes?')          # an unmarked image precedes the question
     done = dict(row, messages=row['messages'][:1] + [{'role': 'assistant', 'content': 'I count. <answer>3</answer>'}])
     assert MultiModalAccuracyReward()([done]) == [1.0]
+
+
+def test_sampler_takes_images_and_continues_positions():
+    """Sampled log-probs after a prompt with an image equal one teacher-forced forward over prompt ⊕ tokens with the
+    (time, height, width) positions continued; the returned feature is ready for training."""
+    from twinkle_b200.data_format import SamplingParams
+    from twinkle_b200.model import TransformersModel
+    from twinkle_b200.sampler import TorchSampler
+    s = TorchSampler(model_id='tiny-vl', weight_seed=0, enable_lora=False)
+    s.set_template('Qwen2VLTemplate', vision_config=s.config.vision, max_length=4096)
+    img = torch.rand(3, 56, 84, generator=torch.Generator().manual_seed(4)) * 255
+    trajs = [{'messages': [{'role': 'user', 'content': [{'type': 'image', 'image': img}, {'type': 'text', 'text': 'describe'}]}]},
+             {'messages': [{'role': 'user', 'content': 'no image here'}]}]
+    resps = s.sample(trajs, SamplingParams(max_tokens=5, temperature=1.0, seed=2, logprobs=1))
+    f = resps[0].sequences[0].new_input_feature
+    n_new = len(resps[0].sequences[0].tokens)
+    assert f['mrope_position_ids'].shape[1] == len(f['input_ids']) and f['pixel_values'].shape[0] == 4 * 6
+    tail = f['mrope_position_ids'][:, -n_new:]
+    assert torch.equal(tail[0], tail[1]) and torch.equal(tail[0], tail[2]) and int(tail[0, 0]) < len(f['input_ids']) - n_new   # compressed by the image
+    assert 'pixel_values' not in resps[1].sequences[0].new_input_feature
+    m = TransformersModel(model_id='tiny-vl', seed=0)                        # same preset and seed = same weights as the sampler
+    for r in resps:
+        q = r.sequences[0]
+        out = m.forward_only(inputs=[q.new_input_feature])
+        lp = torch.as_tensor(out['logps']).float().reshape(-1)
+        labels = torch.tensor(q.new_input_feature['labels'])
+        got = lp[:labels.numel()][labels != -100]
+        assert torch.allclose(got, torch.tensor(q.logprobs), atol=2e-4), (got, q.logprobs)

@@ -75,6 +75,8 @@ class _Seq:
     generator: Optional[torch.Generator] = None
     routed: Optional[List[torch.Tensor]] = None
     text_tail: str = ''
+    vision: Optional[Dict[str, Any]] = None   # pixel_values, image_grid_thw, mrope_position_ids [3, L] of a prompt with images
+    rope_delta: int = 0                        # rotary position − token index for the tokens after the prompt (images compress positions)
     linear: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)  # layer → (conv rows, recurrent state) of linear-attention layers
 
     @property
@@ -136,6 +138,20 @@ class NativeEngine:
 
         sink.linear_state = linear_state
         batch = PackedBatch(ids, pos, cu, max(lens))
+        if any(s.vision for s in seqs):  # prompts with images: patches, grids and (time, height, width) positions beside the row
+            p3, pix, grids = [], [], []
+            for s, n in zip(seqs, lens):
+                if s.vision:
+                    m = torch.as_tensor(s.vision['mrope_position_ids']).long()
+                    pix.append(torch.as_tensor(s.vision['pixel_values']))
+                    grids.append(torch.as_tensor(s.vision['image_grid_thw']).long().view(-1, 3))
+                    s.rope_delta = int(m.max()) + 1 - n
+                else:
+                    m = torch.arange(n).expand(3, -1)
+                p3.append(m)
+            batch.position_ids = torch.cat(p3, 1).to(self.device)
+            batch.pixel_values = torch.cat(pix, 0).to(self.device, self.dtype)
+            batch.image_grid_thw = torch.cat(grids, 0).to(self.device)
         self.model.set_record_routing(self.capture_routing)
         with lora_batch(self._lora_for(seqs, lens)):
             hidden = self.model(batch, kv_sink=sink)
@@ -147,11 +163,13 @@ class NativeEngine:
         return hidden
 
     # --------------------------------------------------------------- decode
-    def _decode_body(self, tokens, positions, table, seq_lens, lora: Optional[LoraBatch], seqs: Optional[List[_Seq]] = None) -> torch.Tensor:
+    def _decode_body(self, tokens, positions, table, seq_lens, lora: Optional[LoraBatch], seqs: Optional[List[_Seq]] = None,
+                     rope_positions: Optional[torch.Tensor] = None) -> torch.Tensor:
         """One decode token per row from device tensors only (what a CUDA graph captures). Linear-attention layers of
         hybrid stacks keep their state on the sequences (``seqs``) and always run eagerly."""
         cfg, B = self.cfg, tokens.shape[0]
-        cos, sin = ops.rope_tables(positions, cfg.head_dim, cfg.rope_theta, cfg.rope_scaling)
+        # ``positions`` index the KV cache; the rotary position differs from it after a prompt with images
+        cos, sin = ops.rope_tables(positions if rope_positions is None else rope_positions, cfg.head_dim, cfg.rope_theta, cfg.rope_scaling)
         x = self.model.embed_tokens(tokens)
         blk = table.gather(1, (positions // self.cache.block_size).unsqueeze(1)).squeeze(1).long()
         off = positions % self.cache.block_size
@@ -216,7 +234,7 @@ class NativeEngine:
         max_blocks = max(len(s.blocks) for s in seqs)
         lora = self._lora_for(seqs, [1] * B)
         use_graph = (self.use_cuda_graphs and self.device.type == 'cuda' and lora is None and not self.capture_routing and not self.cfg.is_moe
-                     and not any(getattr(l, 'is_linear', False) for l in self.model.layers))
+                     and not any(getattr(l, 'is_linear', False) for l in self.model.layers) and not any(s.rope_delta for s in seqs))
         if use_graph:
             Bb = 1 << max(B - 1, 0).bit_length()
             Mb = 1 << max(max_blocks - 1, 0).bit_length()
@@ -246,7 +264,9 @@ class NativeEngine:
             table[i, :len(s.blocks)] = torch.tensor(s.blocks, dtype=torch.int32)
         seq_lens = torch.tensor([s.length for s in seqs], dtype=torch.int32, device=self.device)
         self.model.set_record_routing(self.capture_routing)
-        logits = self._decode_body(last_tokens, positions, table, seq_lens, lora, seqs)
+        deltas = [s.rope_delta for s in seqs]
+        rope_pos = positions + torch.tensor(deltas, device=self.device) if any(deltas) else None
+        logits = self._decode_body(last_tokens, positions, table, seq_lens, lora, seqs, rope_pos)
         if self.capture_routing:
             routed = self.model.collect_routed_experts()  # per layer [B, k]: the experts of the token just fed
             if routed is not None:
@@ -302,7 +322,8 @@ class NativeEngine:
     # ----------------------------------------------------------------- API
     @torch.no_grad()
     def generate(self, prompts: List[List[int]], params: List[SamplingParams], lora: Optional[List[Optional[Dict[str, Any]]]] = None,
-                 eos_token_id: Optional[int] = None, on_token: Optional[Callable[[int, int, float], None]] = None) -> List[SampleResponse]:
+                 eos_token_id: Optional[int] = None, on_token: Optional[Callable[[int, int, float], None]] = None,
+                 vision: Optional[List[Optional[Dict[str, Any]]]] = None) -> List[SampleResponse]:
         """``prompts[i]`` is sampled ``params[i].num_samples`` times.  ``lora[i]`` = ``{slot, rank, scale, target}`` or None."""
         responses = [SampleResponse() for _ in prompts]
         seqs: List[_Seq] = []
@@ -312,7 +333,8 @@ class NativeEngine:
                 g = None
                 if sp.seed is not None:
                     g = torch.Generator(device=self.device).manual_seed(sp.seed + n)
-                seqs.append(_Seq(i, list(pr), sp, lo.get('slot', -1), lo.get('rank', 0), lo.get('scale', 0.0), lo.get('target'), generator=g))
+                seqs.append(_Seq(i, list(pr), sp, lo.get('slot', -1), lo.get('rank', 0), lo.get('scale', 0.0), lo.get('target'), generator=g,
+                                 vision=vision[i] if vision else None))
         for lo_i in range(0, len(seqs), self.max_batch):
             self._run_group(seqs[lo_i:lo_i + self.max_batch], responses, eos_token_id, on_token)
         return responses

@@ -147,10 +147,16 @@ class TorchSampler(Sampler, CheckpointEngineMixin):
             lora = [{'slot': t.slot, 'rank': t.config.r, 'scale': t.config.scaling, 'target': t.target}] * len(prompts)
         eos = self.template.eos_token_id if self.template is not None else self.config.eos_token_id
         self.engine.capture_routing = bool(kwargs.get('return_routed_experts', self.config.is_moe))
-        responses = self.engine.generate(prompts, [sp] * len(prompts), lora, eos)
+        vision = [{k: f[k] for k in ('pixel_values', 'image_grid_thw', 'mrope_position_ids')} if f.get('pixel_values') is not None else None for f in feats]
+        responses = self.engine.generate(prompts, [sp] * len(prompts), lora, eos, vision=vision if any(vision) else None)
         for f, r in zip(feats, responses):
             for s in r.sequences:
                 s.new_input_feature = Template.concat_input_feature(f, s.tokens)
+                if f.get('pixel_values') is not None:  # the images stay with the feature; sampled tokens continue the positions
+                    m = torch.as_tensor(f['mrope_position_ids']).long()
+                    nxt = int(m.max()) + 1
+                    s.new_input_feature.update(pixel_values=f['pixel_values'], image_grid_thw=f['image_grid_thw'],
+                                               mrope_position_ids=torch.cat([m, torch.arange(nxt, nxt + len(s.tokens)).expand(3, -1)], 1))
                 if s.routed_experts is not None:
                     s.new_input_feature['routed_experts'] = s.routed_experts
                 if self.template is not None:
