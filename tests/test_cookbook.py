@@ -111,3 +111,8 @@ def test_vision_language_sft_full_and_lora(tmp_path):
     assert full[-1] < 0.7 * full[0] and os.path.isfile(os.path.join(str(tmp_path), 'final', 'config.json'))
     lora = _load('mm_sft').main(['--steps', '4', '--batch', '4', '--lora-rank', '4', '--lr', '1e-2'])
     assert lora[-1] < lora[0]
+
+
+def test_multimodal_grpo_runs_and_keeps_images_in_training_features():
+    hist = _load('mm_grpo').main(['--steps', '2', '--prompts', '2', '--group', '2', '--max-tokens', '4'])
+    assert len(hist) == 2 and all(h['sequences'] == 4 and h['loss'] == h['loss'] for h in hist)
