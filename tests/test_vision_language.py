@@ -12,23 +12,29 @@ from twinkle_b200.models.vision import VisionConfig, VisionTower, mrope_tables, 
 VC = dict(depth=2, embed_dim=64, hidden_size=128, num_heads=4, mlp_ratio=2, patch_size=14, spatial_merge_size=2, temporal_patch_size=2, in_channels=3)
 
 
-def _hf():
+VC25 = dict(depth=3, hidden_size=64, out_hidden_size=128, intermediate_size=96, num_heads=4, patch_size=14, spatial_merge_size=2, temporal_patch_size=2,
+            in_channels=3, window_size=56, fullatt_block_indexes=[1])     # 2 × 2 merge groups per window; block 1 attends over the whole frame
+
+
+def _hf(family='qwen2_vl'):
     T = pytest.importorskip('transformers')
     try:
-        cfg = T.Qwen2VLConfig(
+        conf, cls, vc = ((T.Qwen2VLConfig, T.Qwen2VLForConditionalGeneration, VC) if family == 'qwen2_vl' else
+                         (T.Qwen2_5_VLConfig, T.Qwen2_5_VLForConditionalGeneration, VC25))
+        cfg = conf(
             text_config=dict(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
                              max_position_embeddings=512, rope_theta=10000.0, rope_scaling={'type': 'mrope', 'mrope_section': [4, 6, 6]},
                              tie_word_embeddings=False),
-            vision_config=VC, image_token_id=500, video_token_id=501, vision_start_token_id=502, vision_end_token_id=503)
+            vision_config=vc, image_token_id=500, video_token_id=501, vision_start_token_id=502, vision_end_token_id=503)
         torch.manual_seed(0)
-        return T, cfg, T.Qwen2VLForConditionalGeneration(cfg).float().eval()
+        return T, cfg, cls(cfg).float().eval()
     except Exception as e:
-        pytest.skip(f'this transformers build cannot make a tiny Qwen2-VL: {type(e).__name__}: {e}')
+        pytest.skip(f'this transformers build cannot make a tiny {family}: {type(e).__name__}: {e}')
 
 
-def _sample():
-    grid = torch.tensor([[1, 4, 6], [1, 2, 2]])
-    n1, n2 = 4 * 6 // 4, 2 * 2 // 4
+def _sample(grid=((1, 4, 6), (1, 2, 2))):
+    grid = torch.tensor(grid)
+    n1, n2 = (int(g[0] * g[1] * g[2]) // 4 for g in grid)
     ids = [5, 6, 502] + [500] * n1 + [503, 7, 8, 502] + [500] * n2 + [503, 9, 10, 11]
     pix = torch.randn(int((grid[:, 0] * grid[:, 1] * grid[:, 2]).sum()), 3 * 2 * 14 * 14, generator=torch.Generator().manual_seed(1))
     return ids, grid, pix
@@ -62,12 +68,13 @@ def test_positions_and_tables_by_hand():
     assert torch.equal(flat[2].view(3, 2, 14, 14)[:, 0], frames[0, :, 14:28, 0:14])
 
 
-def test_tower_positions_and_full_model_match_transformers():
-    T, cfg, hf = _hf()
+@pytest.mark.parametrize('family', ['qwen2_vl', 'qwen2_5_vl'])
+def test_tower_positions_and_full_model_match_transformers(family, tmp_path):
+    T, cfg, hf = _hf(family)
     from twinkle_b200.models.bridge import hf_to_internal
     from twinkle_b200.models.config import DecoderConfig
     from twinkle_b200.models.decoder import PackedBatch, build_model
-    ids, grid, pix = _sample()
+    ids, grid, pix = _sample() if family == 'qwen2_vl' else _sample(((1, 6, 10), (1, 8, 6)))   # several windows, ragged edges
     tower = VisionTower(VisionConfig.from_hf(cfg.vision_config.to_dict())).float().eval()
     tower.load_state_dict({k[len('model.visual.'):]: v for k, v in hf.state_dict().items() if k.startswith('model.visual.')})
     ids_t = torch.tensor([ids])
@@ -76,12 +83,16 @@ def test_tower_positions_and_full_model_match_transformers():
         try:
             want_feats = hf.model.visual(pix, grid_thw=grid)
             want_pos = hf.model.get_rope_index(ids_t, mm_token_type_ids=mm, image_grid_thw=grid)[0][:, 0]
-            want = hf(input_ids=ids_t, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=mm).logits[0]
+            mine = rope_index(ids, grid.tolist(), 500)
+            want = hf(input_ids=ids_t, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=mm, position_ids=mine[:, None, :]).logits[0]
         except TypeError as e:
             pytest.skip(f'different call signature in this transformers build: {e}')
         want_feats = getattr(want_feats, 'pooler_output', want_feats[0] if isinstance(want_feats, tuple) else want_feats)
         assert torch.allclose(tower(pix, grid), want_feats, atol=1e-5)
-    assert torch.equal(rope_index(ids, grid.tolist(), 500), want_pos)
+    # height and width rows always agree. The time row of an image is its start position, as in the model's original
+    # implementation; this transformers build multiplies it by tokens_per_second for Qwen2.5-VL images, so it is compared
+    # for Qwen2-VL only (the logits above were computed from the same positions on both sides)
+    assert torch.equal(mine[1:], want_pos[1:]) and (family != 'qwen2_vl' or torch.equal(mine, want_pos))
     dc = DecoderConfig.from_hf(cfg.to_dict())
     assert dc.mrope_section == [4, 6, 6] and dc.attention_bias and not dc.qk_norm and dc.image_token_id == 500 and dc.rope_scaling is None
     m = build_model(dc)
@@ -93,6 +104,11 @@ def test_tower_positions_and_full_model_match_transformers():
         got = m.logits(m(PackedBatch(torch.tensor(ids), rope_index(ids, grid.tolist(), 500), torch.tensor([0, n], dtype=torch.int32), n,
                                      pixel_values=pix, image_grid_thw=grid)))
     assert torch.allclose(got, want, atol=2e-5), float((got - want).abs().max())
+    # the config goes out in the family's own layout and comes back unchanged
+    dc.save_pretrained(str(tmp_path))
+    written = json.load(open(str(tmp_path / 'config.json')))
+    assert written['model_type'] == family and written['architectures'][0].endswith('ForConditionalGeneration')
+    assert DecoderConfig.from_pretrained(str(tmp_path)).vision == dc.vision
 
 
 def test_preprocessing_matches_the_hf_image_processor():

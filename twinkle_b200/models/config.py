@@ -73,6 +73,11 @@ class DecoderConfig:
     vision_end_token_id: Optional[int] = None
     mrope_section: Optional[List[int]] = None
 
+    def __post_init__(self):
+        if self.vision is not None:
+            from .vision import VisionConfig
+            self.vision = VisionConfig.from_hf(self.vision).to_hf()  # only the fields the tower uses, in the family's spelling
+
     @property
     def is_moe(self) -> bool:
         return self.num_experts > 0
@@ -117,8 +122,8 @@ class DecoderConfig:
         vision = top.get('vision_config')
         if vision is not None:
             vision = dict(vision)
-            if vision.get('model_type', top.get('model_type', 'qwen2_vl')) not in ('qwen2_vl', ):
-                raise NotImplementedError(f"vision tower of type {vision.get('model_type')!r} is not supported (qwen2_vl is)")
+            if vision.get('model_type', top.get('model_type', 'qwen2_vl')) not in ('qwen2_vl', 'qwen2_5_vl'):
+                raise NotImplementedError(f"vision tower of type {vision.get('model_type')!r} is not supported (qwen2_vl and qwen2_5_vl are)")
         rs_any = cfg.get('rope_scaling') or cfg.get('rope_parameters') or top.get('rope_scaling') or {}
         heads = cfg.get('num_attention_heads', 32)
         out = cls(
@@ -174,9 +179,12 @@ class DecoderConfig:
         if self.rope_scaling:
             d['rope_scaling'] = dict(self.rope_scaling)
         if self.vision:
-            text = dict(d, model_type='qwen2_vl_text', rope_scaling={'type': 'mrope', 'mrope_section': list(self.mrope_section or [])})
+            v25 = 'out_hidden_size' in self.vision
+            text = dict(d, model_type='qwen2_5_vl_text' if v25 else 'qwen2_vl_text',
+                        rope_scaling={'type': 'mrope', 'mrope_section': list(self.mrope_section or [])})
             text.pop('architectures', None)
-            return {'architectures': ['Qwen2VLForConditionalGeneration'], 'model_type': 'qwen2_vl', 'text_config': text,
+            return {'architectures': ['Qwen2_5_VLForConditionalGeneration' if v25 else 'Qwen2VLForConditionalGeneration'],
+                    'model_type': 'qwen2_5_vl' if v25 else 'qwen2_vl', 'text_config': text,
                     'vision_config': dict(self.vision), 'image_token_id': self.image_token_id, 'video_token_id': self.video_token_id,
                     'vision_start_token_id': self.vision_start_token_id, 'vision_end_token_id': self.vision_end_token_id,
                     'tie_word_embeddings': self.tie_word_embeddings, 'torch_dtype': self.torch_dtype}

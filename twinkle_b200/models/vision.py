@@ -31,14 +31,34 @@ class VisionConfig:
     spatial_merge_size: int = 2
     temporal_patch_size: int = 2
     in_channels: int = 3
+    # Qwen2.5-VL: RMSNorm + gated SiLU MLP (``intermediate_size``), attention inside ``window_size``-pixel windows except in
+    # the blocks listed in ``fullatt_block_indexes``
+    arch: str = 'qwen2_vl'
+    intermediate_size: int = 0
+    window_size: int = 112
+    fullatt_block_indexes: Tuple[int, ...] = ()
 
     @classmethod
     def from_hf(cls, d: Dict[str, Any]) -> 'VisionConfig':
-        keys = ('depth', 'embed_dim', 'hidden_size', 'num_heads', 'mlp_ratio', 'patch_size', 'spatial_merge_size', 'temporal_patch_size', 'in_channels')
+        d = dict(d)
+        if 'out_hidden_size' in d:  # Qwen2.5-VL spelling: hidden_size = tower width, out_hidden_size = language model width
+            d.update(arch='qwen2_5_vl', embed_dim=d['hidden_size'], hidden_size=d['out_hidden_size'],
+                     fullatt_block_indexes=tuple(d.get('fullatt_block_indexes') or ()))
+        elif 'fullatt_block_indexes' in d:
+            d['fullatt_block_indexes'] = tuple(d['fullatt_block_indexes'] or ())
+        keys = ('depth', 'embed_dim', 'hidden_size', 'num_heads', 'mlp_ratio', 'patch_size', 'spatial_merge_size', 'temporal_patch_size', 'in_channels',
+                'arch', 'intermediate_size', 'window_size', 'fullatt_block_indexes')
         return cls(**{k: d[k] for k in keys if k in d})
 
     def to_hf(self) -> Dict[str, Any]:
-        return {'model_type': 'qwen2_vl', **self.__dict__, 'hidden_act': 'quick_gelu'}
+        base = dict(depth=self.depth, num_heads=self.num_heads, patch_size=self.patch_size, spatial_merge_size=self.spatial_merge_size,
+                    temporal_patch_size=self.temporal_patch_size, in_channels=self.in_channels)
+        if self.arch == 'qwen2_5_vl':
+            return {'model_type': 'qwen2_5_vl', **base, 'hidden_size': self.embed_dim, 'out_hidden_size': self.hidden_size,
+                    'intermediate_size': self.intermediate_size, 'window_size': self.window_size,
+                    'fullatt_block_indexes': list(self.fullatt_block_indexes), 'hidden_act': 'silu'}
+        return {'model_type': 'qwen2_vl', **base, 'embed_dim': self.embed_dim, 'hidden_size': self.hidden_size, 'mlp_ratio': self.mlp_ratio,
+                'hidden_act': 'quick_gelu'}
 
     @property
     def patch_dim(self) -> int:
@@ -97,13 +117,27 @@ class _Mlp(nn.Module):
         return self.fc2(h * torch.sigmoid(1.702 * h))      # "quick" GELU
 
 
+class _GatedMlp(nn.Module):
+
+    def __init__(self, dim: int, hidden: int):
+        super().__init__()
+        self.gate_proj, self.up_proj, self.down_proj = nn.Linear(dim, hidden), nn.Linear(dim, hidden), nn.Linear(hidden, dim)
+
+    def forward(self, x):
+        return self.down_proj(F.silu(self.gate_proj(x)) * self.up_proj(x))
+
+
+def _norm(cfg: VisionConfig) -> nn.Module:
+    return nn.RMSNorm(cfg.embed_dim, eps=1e-6) if cfg.arch == 'qwen2_5_vl' else nn.LayerNorm(cfg.embed_dim, eps=1e-6)
+
+
 class _Block(nn.Module):
 
     def __init__(self, cfg: VisionConfig):
         super().__init__()
-        self.norm1, self.norm2 = nn.LayerNorm(cfg.embed_dim, eps=1e-6), nn.LayerNorm(cfg.embed_dim, eps=1e-6)
+        self.norm1, self.norm2 = _norm(cfg), _norm(cfg)
         self.attn = _Attn(cfg.embed_dim, cfg.num_heads)
-        self.mlp = _Mlp(cfg.embed_dim, int(cfg.embed_dim * cfg.mlp_ratio))
+        self.mlp = _GatedMlp(cfg.embed_dim, cfg.intermediate_size) if cfg.arch == 'qwen2_5_vl' else _Mlp(cfg.embed_dim, int(cfg.embed_dim * cfg.mlp_ratio))
 
     def forward(self, x, cos, sin, bounds):
         x = x + self.attn(self.norm1(x), cos, sin, bounds)
@@ -116,7 +150,7 @@ class _Merger(nn.Module):
     def __init__(self, cfg: VisionConfig):
         super().__init__()
         self.group = cfg.embed_dim * cfg.spatial_merge_size**2
-        self.ln_q = nn.LayerNorm(cfg.embed_dim, eps=1e-6)
+        self.ln_q = _norm(cfg)
         self.mlp = nn.Sequential(nn.Linear(self.group, self.group), nn.GELU(), nn.Linear(self.group, cfg.hidden_size))
 
     def forward(self, x):
@@ -147,6 +181,28 @@ class VisionTower(nn.Module):
         ang = torch.cat([pos[:, 0:1] * inv[None, :], pos[:, 1:2] * inv[None, :]], -1)
         return ang.cos(), ang.sin()
 
+    def window_order(self, grid_thw: torch.Tensor) -> Tuple[torch.Tensor, List[int]]:
+        """Qwen2.5-VL: a permutation of the merge groups that makes every ``window_size``-pixel window contiguous, and the
+        patch boundaries of the windows in that order (edge windows are smaller)."""
+        m = self.cfg.spatial_merge_size
+        vw = self.cfg.window_size // m // self.cfg.patch_size          # window side in merge groups
+        order, bounds, base = [], [0], 0
+        for t, h, w in grid_thw.tolist():
+            gh, gw = h // m, w // m
+            idx = torch.arange(t * gh * gw).view(t, gh, gw)
+            ph, pw = vw - gh % vw, vw - gw % vw
+            pad = F.pad(idx, (0, pw, 0, ph), value=-100)
+            nh, nw = (gh + ph) // vw, (gw + pw) // vw
+            win = pad.view(t, nh, vw, nw, vw).permute(0, 1, 3, 2, 4).reshape(t, nh * nw, vw, vw)
+            counts = (win != -100).sum((2, 3)).reshape(-1)
+            flat = win.reshape(-1)
+            order.append(flat[flat != -100] + base)
+            for c in counts.tolist():
+                if c:
+                    bounds.append(bounds[-1] + c * m * m)
+            base += t * gh * gw
+        return torch.cat(order).to(grid_thw.device), bounds
+
     def forward(self, pixel_values: torch.Tensor, grid_thw: torch.Tensor) -> torch.Tensor:
         """``pixel_values [N, C·T·P·P]`` (flat patches of all images, in order), ``grid_thw [n_images, 3]`` →
         ``[N / merge², hidden_size]``."""
@@ -154,9 +210,18 @@ class VisionTower(nn.Module):
         cos, sin = self.rotary_tables(grid_thw)
         frames = torch.repeat_interleave(grid_thw[:, 1] * grid_thw[:, 2], grid_thw[:, 0])
         bounds = [0] + frames.cumsum(0).tolist()
-        for blk in self.blocks:
-            x = blk(x, cos, sin, bounds)
-        return self.merger(x)
+        if self.cfg.arch != 'qwen2_5_vl':
+            for blk in self.blocks:
+                x = blk(x, cos, sin, bounds)
+            return self.merger(x)
+        unit = self.cfg.spatial_merge_size**2
+        order, win_bounds = self.window_order(grid_thw)
+        regroup = lambda t: t.view(t.shape[0] // unit, unit, -1)[order].reshape(t.shape[0], -1)  # noqa: E731
+        x, cos, sin = regroup(x), regroup(cos), regroup(sin)
+        # a frame's patches stay contiguous under the window order, so the per-frame boundaries are unchanged
+        for i, blk in enumerate(self.blocks):
+            x = blk(x, cos, sin, bounds if i in self.cfg.fullatt_block_indexes else win_bounds)
+        return self.merger(x)[torch.argsort(order)]
 
 
 # ------------------------------------------------------------------------------------------ positions in the LLM
