@@ -271,3 +271,41 @@ def test_sampler_takes_images_and_continues_positions():
         labels = torch.tensor(q.new_input_feature['labels'])
         got = lp[:labels.numel()][labels != -100]
         assert torch.allclose(got, torch.tensor(q.logprobs), atol=2e-4), (got, q.logprobs)
+
+
+def test_video_frames_match_transformers_qwen2_vl():
+    """A video part (list of frames): two frames share a temporal patch, positions advance along time per patch-pair, and the
+    whole model's logits equal ``transformers``' when it is given the same patches as ``pixel_values_videos``."""
+    T, cfg, hf = _hf('qwen2_vl')
+    from twinkle_b200.models.bridge import hf_to_internal
+    from twinkle_b200.models.config import DecoderConfig
+    from twinkle_b200.models.decoder import PackedBatch, build_model
+    from twinkle_b200.models.vision import preprocess_video
+    g = torch.Generator().manual_seed(7)
+    frames = [torch.rand(3, 56, 84, generator=g) * 255 for _ in range(3)]            # odd count: the last frame is repeated
+    pix, grid = preprocess_video(frames, VisionConfig(**VC), min_pixels=56 * 56)
+    assert grid == (2, 4, 6) and pix.shape == (48, 1176)
+    n_vid = 2 * 4 * 6 // 4
+    ids = [5, 502] + [501] * n_vid + [503, 7, 8]
+    pos = rope_index(ids, [grid], 500, video_token_id=501)
+    assert pos[0, 2:2 + n_vid].tolist() == [2] * 6 + [3] * 6 and pos[:, -2:].tolist() == [[6, 7]] * 3      # max(t, h/2, w/2) = 3 → text resumes at 2 + 3 + 1
+    ids_t, grid_t = torch.tensor([ids]), torch.tensor([grid])
+    with torch.no_grad():
+        try:
+            want = hf(input_ids=ids_t, pixel_values_videos=pix, video_grid_thw=grid_t, mm_token_type_ids=(ids_t == 501).int() * 2,
+                      position_ids=pos[:, None, :]).logits[0]
+        except TypeError as e:
+            pytest.skip(str(e))
+    dc = DecoderConfig.from_hf(cfg.to_dict())
+    m = build_model(dc)
+    sd = hf.state_dict()
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            p.copy_(hf_to_internal(n, dc, lambda k: sd[k]))
+        got = m.logits(m(PackedBatch(torch.tensor(ids), pos, torch.tensor([0, len(ids)], dtype=torch.int32), len(ids), pixel_values=pix, image_grid_thw=grid_t)))
+    assert torch.allclose(got, want, atol=2e-5), float((got - want).abs().max())
+    from twinkle_b200.template import template_mapping
+    tpl = template_mapping['Qwen2VLTemplate'](model_id=None, vision_config=VC, max_length=4096)
+    f = tpl.encode({'messages': [{'role': 'user', 'content': [{'type': 'video', 'video': frames}, {'type': 'text', 'text': 'what happens?'}]},
+                                 {'role': 'assistant', 'content': 'it moves'}]})
+    assert f['input_ids'].count(tpl.video_token_id) == f['pixel_values'].shape[0] // 4 and f['mrope_position_ids'].shape[1] == len(f['input_ids'])

@@ -331,3 +331,29 @@ def preprocess_image(image: Any, cfg: VisionConfig, min_pixels: int = 56 * 56, m
     mean, std = torch.tensor(IMAGE_MEAN).view(3, 1, 1), torch.tensor(IMAGE_STD).view(3, 1, 1)
     x = (x / 255.0 - mean) / std
     return patchify(x[None], cfg)
+
+
+def preprocess_video(frames: Sequence[Any], cfg: VisionConfig, min_pixels: int = 128 * 28 * 28, max_pixels: int = 768 * 28 * 28) -> Tuple[torch.Tensor, Tuple[int, int, int]]:
+    """A list of frames (anything :func:`preprocess_image` takes, all of one size) → flat patches and the ``(t, h, w)`` grid;
+    ``temporal_patch_size`` consecutive frames share a patch, an odd tail frame is repeated."""
+    if not len(frames):
+        raise ValueError('a video needs at least one frame')
+    import numpy as np
+    tensors = []
+    for fr in frames:
+        if not torch.is_tensor(fr):
+            if not hasattr(fr, 'shape'):
+                from ..utils.misc import load_image
+                fr = np.asarray(load_image(fr))
+            fr = torch.as_tensor(np.array(fr))
+        x = fr.float()
+        if x.dim() == 3 and x.shape[-1] in (1, 3) and x.shape[0] not in (1, 3):
+            x = x.permute(2, 0, 1)
+        tensors.append(x.expand(3, -1, -1) if x.shape[0] == 1 else x)
+    x = torch.stack(tensors)
+    factor = cfg.patch_size * cfg.spatial_merge_size
+    h, w = smart_resize(x.shape[2], x.shape[3], factor, min_pixels, max_pixels)
+    if (h, w) != tuple(x.shape[2:]):
+        x = F.interpolate(x, size=(h, w), mode='bicubic', align_corners=False, antialias=True).clamp(0, 255)
+    mean, std = torch.tensor(IMAGE_MEAN).view(1, 3, 1, 1), torch.tensor(IMAGE_STD).view(1, 3, 1, 1)
+    return patchify((x / 255.0 - mean) / std, cfg)

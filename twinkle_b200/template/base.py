@@ -364,6 +364,7 @@ class Qwen2VLTemplate(Template):
     bound the resized image. Reference: ``template/base.py:611-667`` + the HF processor it delegates to."""
 
     IMAGE_MARK = '<|vision_start|><|image_pad|><|vision_end|>'
+    VIDEO_MARK = '<|vision_start|><|video_pad|><|vision_end|>'
 
     def __init__(self, *a, vision_config=None, min_pixels: int = 56 * 56, max_pixels: int = 14 * 14 * 4 * 1280, **kw):
         super().__init__(*a, **kw)
@@ -371,14 +372,15 @@ class Qwen2VLTemplate(Template):
         self.vision_config = vision_config if isinstance(vision_config, VisionConfig) else VisionConfig.from_hf(dict(vision_config or {}))
         self.min_pixels, self.max_pixels = min_pixels, max_pixels
         self.image_token_id = self.tokenizer.convert_tokens_to_ids('<|image_pad|>')
+        self.video_token_id = self.tokenizer.convert_tokens_to_ids('<|video_pad|>')
         self._vision: List[Tuple[Any, Tuple[int, int, int]]] = []
         self.pre_pipeline = self.pre_pipeline + [self._collect_images]
         self.post_pipeline = self.post_pipeline + [self._attach_vision]
 
     def _collect_images(self, traj: Trajectory) -> Trajectory:
-        from ..models.vision import preprocess_image
+        from ..models.vision import preprocess_image, preprocess_video
         loose = list(traj.get('images') or [])
-        sources: List[Any] = []
+        sources: List[Any] = []                    # an image source, or ('video', [frames]) for a video part
         for m in traj.get('messages') or []:
             c = m.get('content')
             if isinstance(c, list):
@@ -388,6 +390,9 @@ class Qwen2VLTemplate(Template):
                         src = part.get('image', part.get('image_url'))
                         sources.append(src.get('url') if isinstance(src, dict) else src)
                         text += self.IMAGE_MARK
+                    elif part.get('type') == 'video':      # a list of frames (decoding video files is left to the caller)
+                        sources.append(('video', list(part['video'])))
+                        text += self.VIDEO_MARK
                     else:
                         text += part.get('text', '')
                 m['content'] = text
@@ -404,7 +409,8 @@ class Qwen2VLTemplate(Template):
             n_before = sum(str(m.get('content', '')).count(self.IMAGE_MARK) for m in traj['messages'][:traj['messages'].index(first)])
             first['content'] = self.IMAGE_MARK * len(loose) + str(first.get('content') or '')
             sources[n_before:n_before] = loose
-        self._vision = [preprocess_image(src, self.vision_config, self.min_pixels, self.max_pixels) for src in sources]
+        self._vision = [preprocess_video(src[1], self.vision_config) if isinstance(src, tuple) and len(src) == 2 and src[0] == 'video'
+                        else preprocess_image(src, self.vision_config, self.min_pixels, self.max_pixels) for src in sources]
         return traj
 
     def _render(self, messages, tools=None, add_generation_prompt: bool = False) -> List[int]:
@@ -414,7 +420,7 @@ class Qwen2VLTemplate(Template):
         merge2 = self.vision_config.spatial_merge_size**2
         out, k = [], 0
         for t in ids:
-            if t == self.image_token_id and k < len(self._vision):
+            if t in (self.image_token_id, self.video_token_id) and k < len(self._vision):
                 g = self._vision[k][1]
                 out.extend([t] * (g[0] * g[1] * g[2] // merge2))
                 k += 1
@@ -434,7 +440,7 @@ class Qwen2VLTemplate(Template):
         f['pixel_values'] = torch.cat([p for p, _ in self._vision], 0)                      # type: ignore[typeddict-unknown-key]
         f['image_grid_thw'] = [list(g) for g in grids]                                      # type: ignore[typeddict-unknown-key]
         f['mrope_position_ids'] = rope_index(f['input_ids'], grids, self.image_token_id,   # type: ignore[typeddict-unknown-key]
-                                             self.vision_config.spatial_merge_size)
+                                             self.vision_config.spatial_merge_size, video_token_id=self.video_token_id)
         return feats
 
 
