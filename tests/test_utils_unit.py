@@ -253,3 +253,18 @@ def test_rope_scaling_matches_transformers_and_travels_in_config():
     assert DecoderConfig.from_hf(cfg.to_hf()).rope_scaling == cfg.rope_scaling
     assert DecoderConfig.from_hf({'model_type': 'qwen3', 'rope_scaling': None}).rope_scaling is None
     assert DecoderConfig.from_hf({'model_type': 'qwen3', 'rope_parameters': {'rope_type': 'default', 'rope_theta': 1e6}}).rope_scaling is None
+
+
+def test_image_sources_can_be_restricted(tmp_path, monkeypatch):
+    import base64
+    import pytest
+    from twinkle_b200.utils.misc import load_mm_file
+    f = tmp_path / 'x.bin'
+    f.write_bytes(b'abc')
+    assert load_mm_file(str(f)).read() == b'abc'
+    monkeypatch.setenv('TWINKLE_MM_SOURCES', 'data')
+    with pytest.raises(PermissionError):
+        load_mm_file(str(f))
+    with pytest.raises(PermissionError):
+        load_mm_file('http://example.invalid/a.png')
+    assert load_mm_file('data:image/png;base64,' + base64.b64encode(b'xyz').decode()).read() == b'xyz'

@@ -309,3 +309,19 @@ def test_video_frames_match_transformers_qwen2_vl():
     f = tpl.encode({'messages': [{'role': 'user', 'content': [{'type': 'video', 'video': frames}, {'type': 'text', 'text': 'what happens?'}]},
                                  {'role': 'assistant', 'content': 'it moves'}]})
     assert f['input_ids'].count(tpl.video_token_id) == f['pixel_values'].shape[0] // 4 and f['mrope_position_ids'].shape[1] == len(f['input_ids'])
+
+
+def test_images_travel_as_data_urls_over_http():
+    from twinkle_b200.client import _wire
+    from twinkle_b200.models.vision import preprocess_image
+    from twinkle_b200.utils.misc import image_to_data_url
+    img = (torch.rand(3, 56, 84, generator=torch.Generator().manual_seed(1)) * 255).round()
+    url = image_to_data_url(img)
+    assert url.startswith('data:image/png;base64,') and image_to_data_url('file.png') == 'file.png'
+    a, ga = preprocess_image(img, VisionConfig(**VC))
+    b, gb = preprocess_image(url, VisionConfig(**VC))                 # what the server does with the wire form
+    assert ga == gb and torch.equal(a, b)                             # PNG is lossless for 8-bit pixels
+    body = _wire({'inputs': [{'messages': [{'role': 'user', 'content': [{'type': 'image', 'image': img}, {'type': 'text', 'text': 'hi'}]}]},
+                             {'messages': [{'role': 'user', 'content': '<image> hi'}], 'images': [img.permute(1, 2, 0).numpy()]}]})
+    part = body['inputs'][0]['messages'][0]['content'][0]
+    assert part['image'] == url and body['inputs'][1]['images'][0] == url and body['inputs'][0]['messages'][0]['content'][1] == {'type': 'text', 'text': 'hi'}

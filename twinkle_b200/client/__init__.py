@@ -239,6 +239,17 @@ def InputProcessor(**kw):
 def _wire(v):
     if isinstance(v, RemoteObject):
         return {'__object__': v.object_id}
+    if isinstance(v, dict) and (v.get('type') in ('image', 'image_url', 'video') or 'images' in v):
+        # pictures inside chat messages / trajectories travel as PNG data URLs, not as nested number lists
+        from ..utils.misc import image_to_data_url
+        v = dict(v)
+        if v.get('type') in ('image', 'image_url') and v.get('image') is not None:
+            v['image'] = image_to_data_url(v['image'])
+        if v.get('type') == 'video' and v.get('video') is not None:
+            v['video'] = [image_to_data_url(fr) for fr in v['video']]
+        if isinstance(v.get('images'), (list, tuple)):
+            v['images'] = [image_to_data_url(i) for i in v['images']]
+        return {k: _wire(x) for k, x in v.items()}
     try:
         import torch
         if torch.is_tensor(v):

@@ -125,6 +125,9 @@ class ServerLauncher:
 
     def launch(self, block: bool = True) -> None:
         import uvicorn
+        # images in requests of a served instance: inline data only, unless the operator widens it (no file reads or URL
+        # fetches on a tenant's behalf); in-process use of the launcher leaves the process environment alone
+        os.environ.setdefault('TWINKLE_MM_SOURCES', 'data')
         h = self.config.http_options
         cfg = uvicorn.Config(self.root, host=h.host, port=h.port, log_level='warning')
         server = uvicorn.Server(cfg)

@@ -147,12 +147,19 @@ def load_mm_file(path: Any):
     if not isinstance(path, str):
         return path
     p = path.strip()
+    # which kinds of string sources are honoured: a server that takes requests from tenants sets TWINKLE_MM_SOURCES=data so
+    # that a request cannot make it read its own files or fetch URLs on the tenant's behalf
+    allowed = {x.strip() for x in os.environ.get('TWINKLE_MM_SOURCES', 'data,file,http').split(',') if x.strip()}
     if p.startswith(('http://', 'https://')):
+        if 'http' not in allowed:
+            raise PermissionError('fetching images from URLs is disabled here (TWINKLE_MM_SOURCES)')
         import requests
         r = requests.get(p, timeout=float(os.environ.get('TWINKLE_MM_TIMEOUT', '20')))
         r.raise_for_status()
         return BytesIO(r.content)
-    if os.path.exists(p):
+    if len(p) < 4096 and not p.startswith('data:') and os.path.exists(p):
+        if 'file' not in allowed:
+            raise PermissionError('reading images from local paths is disabled here (TWINKLE_MM_SOURCES)')
         with open(p, 'rb') as f:
             return BytesIO(f.read())
     import base64
@@ -170,3 +177,25 @@ def load_image(image: Any):
     if isinstance(src, BytesIO):
         src = Image.open(src)
     return src.convert('RGB') if getattr(src, 'mode', 'RGB') != 'RGB' else src
+
+
+def image_to_data_url(image: Any) -> Any:
+    """What travels in a JSON request for an image: strings (paths on the server, URLs, base64) pass; bytes, PIL images and
+    ``[C, H, W]`` / ``[H, W, C]`` arrays in 0…255 become a PNG ``data:`` URL that :func:`load_mm_file` reads back."""
+    import base64
+    if isinstance(image, str):
+        return image
+    if isinstance(image, bytes):
+        return 'data:application/octet-stream;base64,' + base64.b64encode(image).decode()
+    from PIL import Image
+    if not isinstance(image, Image.Image):
+        import numpy as np
+        arr = image.detach().cpu().numpy() if hasattr(image, 'detach') else np.asarray(image)
+        if arr.ndim == 3 and arr.shape[0] in (1, 3) and arr.shape[-1] not in (1, 3):
+            arr = arr.transpose(1, 2, 0)
+        if arr.ndim == 3 and arr.shape[-1] == 1:
+            arr = arr[..., 0]
+        image = Image.fromarray(np.clip(np.rint(arr), 0, 255).astype('uint8'))
+    buf = BytesIO()
+    image.save(buf, format='PNG')
+    return 'data:image/png;base64,' + base64.b64encode(buf.getvalue()).decode()
