@@ -16,27 +16,37 @@ VC25 = dict(depth=3, hidden_size=64, out_hidden_size=128, intermediate_size=96, 
             in_channels=3, window_size=56, fullatt_block_indexes=[1])     # 2 × 2 merge groups per window; block 1 attends over the whole frame
 
 
+VC3 = dict(depth=3, hidden_size=64, out_hidden_size=128, intermediate_size=96, num_heads=4, patch_size=16, spatial_merge_size=2, temporal_patch_size=2,
+           in_channels=3, num_position_embeddings=64, deepstack_visual_indexes=[0, 1])    # position table 8 × 8; two deep-stack taps
+
+
 def _hf(family='qwen2_vl'):
     T = pytest.importorskip('transformers')
     try:
-        conf, cls, vc = ((T.Qwen2VLConfig, T.Qwen2VLForConditionalGeneration, VC) if family == 'qwen2_vl' else
-                         (T.Qwen2_5_VLConfig, T.Qwen2_5_VLForConditionalGeneration, VC25))
-        cfg = conf(
-            text_config=dict(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
-                             max_position_embeddings=512, rope_theta=10000.0, rope_scaling={'type': 'mrope', 'mrope_section': [4, 6, 6]},
-                             tie_word_embeddings=False),
-            vision_config=vc, image_token_id=500, video_token_id=501, vision_start_token_id=502, vision_end_token_id=503)
+        conf, cls, vc = {'qwen2_vl': (T.Qwen2VLConfig, T.Qwen2VLForConditionalGeneration, VC),
+                         'qwen2_5_vl': (T.Qwen2_5_VLConfig, T.Qwen2_5_VLForConditionalGeneration, VC25),
+                         'qwen3_vl': (T.Qwen3VLConfig, T.Qwen3VLForConditionalGeneration, VC3)}[family]
+        text = dict(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=3 if family == 'qwen3_vl' else 2, num_attention_heads=4,
+                    num_key_value_heads=2, max_position_embeddings=512, rope_theta=10000.0, tie_word_embeddings=False,
+                    rope_scaling={'type': 'mrope', 'mrope_section': [4, 6, 6]})
+        if family == 'qwen3_vl':
+            text.update(head_dim=32, rope_scaling={'rope_type': 'default', 'mrope_section': [4, 6, 6], 'mrope_interleaved': True})
+        cfg = conf(text_config=text, vision_config=vc, image_token_id=500, video_token_id=501, vision_start_token_id=502, vision_end_token_id=503)
         torch.manual_seed(0)
-        return T, cfg, cls(cfg).float().eval()
+        hf = cls(cfg).float().eval()
+        for n, p in hf.named_parameters():   # non-trivial norms and biases so that a dropped or swapped tensor shows
+            if p.dim() == 1:
+                torch.nn.init.normal_(p, 1.0 if ('norm' in n or 'ln_q' in n) and 'bias' not in n else 0.0, 0.1)
+        return T, cfg, hf
     except Exception as e:
         pytest.skip(f'this transformers build cannot make a tiny {family}: {type(e).__name__}: {e}')
 
 
-def _sample(grid=((1, 4, 6), (1, 2, 2))):
+def _sample(grid=((1, 4, 6), (1, 2, 2)), patch=14):
     grid = torch.tensor(grid)
     n1, n2 = (int(g[0] * g[1] * g[2]) // 4 for g in grid)
     ids = [5, 6, 502] + [500] * n1 + [503, 7, 8, 502] + [500] * n2 + [503, 9, 10, 11]
-    pix = torch.randn(int((grid[:, 0] * grid[:, 1] * grid[:, 2]).sum()), 3 * 2 * 14 * 14, generator=torch.Generator().manual_seed(1))
+    pix = torch.randn(int((grid[:, 0] * grid[:, 1] * grid[:, 2]).sum()), 3 * 2 * patch * patch, generator=torch.Generator().manual_seed(1))
     return ids, grid, pix
 
 
@@ -68,13 +78,14 @@ def test_positions_and_tables_by_hand():
     assert torch.equal(flat[2].view(3, 2, 14, 14)[:, 0], frames[0, :, 14:28, 0:14])
 
 
-@pytest.mark.parametrize('family', ['qwen2_vl', 'qwen2_5_vl'])
+@pytest.mark.parametrize('family', ['qwen2_vl', 'qwen2_5_vl', 'qwen3_vl'])
 def test_tower_positions_and_full_model_match_transformers(family, tmp_path):
     T, cfg, hf = _hf(family)
     from twinkle_b200.models.bridge import hf_to_internal
     from twinkle_b200.models.config import DecoderConfig
     from twinkle_b200.models.decoder import PackedBatch, build_model
-    ids, grid, pix = _sample() if family == 'qwen2_vl' else _sample(((1, 6, 10), (1, 8, 6)))   # several windows, ragged edges
+    ids, grid, pix = (_sample() if family == 'qwen2_vl' else _sample(((1, 6, 10), (1, 8, 6))) if family == 'qwen2_5_vl' else   # several windows, ragged edges
+                      _sample(((1, 4, 6), (1, 6, 4)), patch=16))
     tower = VisionTower(VisionConfig.from_hf(cfg.vision_config.to_dict())).float().eval()
     tower.load_state_dict({k[len('model.visual.'):]: v for k, v in hf.state_dict().items() if k.startswith('model.visual.')})
     ids_t = torch.tensor([ids])
@@ -87,14 +98,18 @@ def test_tower_positions_and_full_model_match_transformers(family, tmp_path):
             want = hf(input_ids=ids_t, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=mm, position_ids=mine[:, None, :]).logits[0]
         except TypeError as e:
             pytest.skip(f'different call signature in this transformers build: {e}')
+        deep_want = list(getattr(want_feats, 'deepstack_features', None) or [])
         want_feats = getattr(want_feats, 'pooler_output', want_feats[0] if isinstance(want_feats, tuple) else want_feats)
-        assert torch.allclose(tower(pix, grid), want_feats, atol=1e-5)
+        got_feats, deep_got = tower(pix, grid, return_deepstack=True)
+        assert torch.allclose(got_feats, want_feats, atol=1e-5) and len(deep_got) == len(deep_want) == (2 if family == 'qwen3_vl' else 0)
+        assert all(torch.allclose(a, b, atol=1e-5) for a, b in zip(deep_got, deep_want))
     # height and width rows always agree. The time row of an image is its start position, as in the model's original
     # implementation; this transformers build multiplies it by tokens_per_second for Qwen2.5-VL images, so it is compared
     # for Qwen2-VL only (the logits above were computed from the same positions on both sides)
-    assert torch.equal(mine[1:], want_pos[1:]) and (family != 'qwen2_vl' or torch.equal(mine, want_pos))
+    assert torch.equal(mine[1:], want_pos[1:]) and (family == 'qwen2_5_vl' or torch.equal(mine, want_pos))
     dc = DecoderConfig.from_hf(cfg.to_dict())
-    assert dc.mrope_section == [4, 6, 6] and dc.attention_bias and not dc.qk_norm and dc.image_token_id == 500 and dc.rope_scaling is None
+    assert dc.mrope_section == [4, 6, 6] and dc.image_token_id == 500 and dc.rope_scaling is None
+    assert (dc.attention_bias, dc.qk_norm, dc.mrope_interleaved) == ((False, True, True) if family == 'qwen3_vl' else (True, False, False))
     m = build_model(dc)
     sd = hf.state_dict()
     with torch.no_grad():
@@ -325,3 +340,43 @@ def test_images_travel_as_data_urls_over_http():
                              {'messages': [{'role': 'user', 'content': '<image> hi'}], 'images': [img.permute(1, 2, 0).numpy()]}]})
     part = body['inputs'][0]['messages'][0]['content'][0]
     assert part['image'] == url and body['inputs'][1]['images'][0] == url and body['inputs'][0]['messages'][0]['content'][1] == {'type': 'text', 'text': 'hi'}
+
+
+def test_qwen3_vl_trains_through_the_public_api_and_exports(tmp_path):
+    """Deep-stack features pass through the engine's layer loop (and their mergers train); the saved checkpoint reloads here
+    and in ``transformers`` with the same outputs."""
+    from twinkle_b200.model import TransformersModel
+    m = TransformersModel(model_id='tiny-vl3', seed=0)
+    m.set_template('Qwen2VLTemplate', vision_config=m.config.vision, max_length=4096)
+    g = torch.Generator().manual_seed(0)
+    trajs = [{'messages': [{'role': 'user', 'content': [{'type': 'image', 'image': torch.rand(3, 64, 96, generator=g) * 255}, {'type': 'text', 'text': 'what?'}]},
+                           {'role': 'assistant', 'content': 'a red ball'}]},
+             {'messages': [{'role': 'user', 'content': 'plain text'}, {'role': 'assistant', 'content': 'yes'}]}]
+    tpl = m._group(None).template
+    f = tpl.encode(trajs[0])
+    assert f['image_grid_thw'] == [[1, 4, 6]] and f['pixel_values'].shape == (24, 3 * 2 * 16 * 16)
+    m.set_optimizer('AdamW', lr=1e-2)
+    w0 = m.model.visual.deepstack_merger_list[1].linear_fc2.weight.detach().clone()
+    losses = []
+    for _ in range(4):
+        losses.append(float(m.forward_backward(inputs=trajs)['loss']))
+        m.clip_grad_and_step(max_grad_norm=1.0)
+    assert losses[-1] < 0.7 * losses[0] and not torch.equal(w0, m.model.visual.deepstack_merger_list[1].linear_fc2.weight)
+    out = m.save('ck', str(tmp_path))
+    cfg = json.load(open(out + '/config.json'))
+    assert cfg['model_type'] == 'qwen3_vl' and cfg['text_config']['rope_scaling']['mrope_interleaved'] is True
+    m2 = TransformersModel(model_id=out, seed=1)
+    m2.set_template('Qwen2VLTemplate', vision_config=m2.config.vision, max_length=4096)
+    la, lb = m.forward_only(inputs=trajs), m2.forward_only(inputs=trajs)
+    assert torch.allclose(torch.as_tensor(la['logps']).float(), torch.as_tensor(lb['logps']).float(), atol=1e-5)
+    T = pytest.importorskip('transformers')
+    try:
+        back = T.Qwen3VLForConditionalGeneration.from_pretrained(out).float().eval()
+        ids = torch.tensor([f['input_ids']])
+        with torch.no_grad():
+            theirs = back(input_ids=ids, pixel_values=f['pixel_values'], image_grid_thw=torch.tensor(f['image_grid_thw']),
+                          mm_token_type_ids=(ids == tpl.image_token_id).int()).logits[0]
+    except (TypeError, AttributeError, OSError, ValueError) as e:
+        pytest.skip(f'transformers could not run the export: {type(e).__name__}: {e}')
+    ours = torch.as_tensor(m.forward_only(inputs=[trajs[0]], return_logits=True)['logits']).float().reshape(-1, theirs.shape[-1])[:theirs.shape[0]]
+    assert torch.allclose(ours, theirs, atol=5e-5), float((ours - theirs).abs().max())

@@ -72,6 +72,7 @@ class DecoderConfig:
     vision_start_token_id: Optional[int] = None
     vision_end_token_id: Optional[int] = None
     mrope_section: Optional[List[int]] = None
+    mrope_interleaved: bool = False  # Qwen3-VL lays the three position components out t h w t h w … instead of in blocks
 
     def __post_init__(self):
         if self.vision is not None:
@@ -122,8 +123,8 @@ class DecoderConfig:
         vision = top.get('vision_config')
         if vision is not None:
             vision = dict(vision)
-            if vision.get('model_type', top.get('model_type', 'qwen2_vl')) not in ('qwen2_vl', 'qwen2_5_vl'):
-                raise NotImplementedError(f"vision tower of type {vision.get('model_type')!r} is not supported (qwen2_vl and qwen2_5_vl are)")
+            if vision.get('model_type', top.get('model_type', 'qwen2_vl')) not in ('qwen2_vl', 'qwen2_5_vl', 'qwen3_vl'):
+                raise NotImplementedError(f"vision tower of type {vision.get('model_type')!r} is not supported (qwen2_vl, qwen2_5_vl and qwen3_vl are)")
         rs_any = cfg.get('rope_scaling') or cfg.get('rope_parameters') or top.get('rope_scaling') or {}
         heads = cfg.get('num_attention_heads', 32)
         out = cls(
@@ -146,6 +147,7 @@ class DecoderConfig:
             vision=vision, image_token_id=top.get('image_token_id'), video_token_id=top.get('video_token_id'),
             vision_start_token_id=top.get('vision_start_token_id'), vision_end_token_id=top.get('vision_end_token_id'),
             mrope_section=list(rs_any['mrope_section']) if isinstance(rs_any, dict) and rs_any.get('mrope_section') else None,
+            mrope_interleaved=bool(isinstance(rs_any, dict) and rs_any.get('mrope_interleaved')),
             initializer_range=cfg.get('initializer_range', 0.02), model_type=mt,
             torch_dtype=str(cfg.get('torch_dtype', cfg.get('dtype', 'bfloat16'))),
             max_position_embeddings=cfg.get('max_position_embeddings', 40960), pad_token_id=cfg.get('pad_token_id'),
@@ -179,12 +181,15 @@ class DecoderConfig:
         if self.rope_scaling:
             d['rope_scaling'] = dict(self.rope_scaling)
         if self.vision:
-            v25 = 'out_hidden_size' in self.vision
-            text = dict(d, model_type='qwen2_5_vl_text' if v25 else 'qwen2_vl_text',
-                        rope_scaling={'type': 'mrope', 'mrope_section': list(self.mrope_section or [])})
+            fam = self.vision.get('model_type', 'qwen2_vl')
+            rope = {'type': 'mrope', 'mrope_section': list(self.mrope_section or [])}
+            if fam == 'qwen3_vl':
+                rope = {'rope_type': 'default', 'mrope_section': list(self.mrope_section or []), 'mrope_interleaved': self.mrope_interleaved}
+            text = dict(d, model_type=fam + '_text', rope_scaling=rope)
             text.pop('architectures', None)
-            return {'architectures': ['Qwen2_5_VLForConditionalGeneration' if v25 else 'Qwen2VLForConditionalGeneration'],
-                    'model_type': 'qwen2_5_vl' if v25 else 'qwen2_vl', 'text_config': text,
+            arch = {'qwen2_vl': 'Qwen2VLForConditionalGeneration', 'qwen2_5_vl': 'Qwen2_5_VLForConditionalGeneration',
+                    'qwen3_vl': 'Qwen3VLForConditionalGeneration'}[fam]
+            return {'architectures': [arch], 'model_type': fam, 'text_config': text,
                     'vision_config': dict(self.vision), 'image_token_id': self.image_token_id, 'video_token_id': self.video_token_id,
                     'vision_start_token_id': self.vision_start_token_id, 'vision_end_token_id': self.vision_end_token_id,
                     'tie_word_embeddings': self.tie_word_embeddings, 'torch_dtype': self.torch_dtype}
@@ -218,6 +223,12 @@ PRESETS: Dict[str, Dict[str, Any]] = {
                     vision_end_token_id=266,  # ids of these tokens in the byte-level test tokenizer
                     vision=dict(depth=2, embed_dim=64, hidden_size=256, num_heads=4, mlp_ratio=2, patch_size=14,
                                                           spatial_merge_size=2, temporal_patch_size=2, in_channels=3)),
+    'tiny-vl3': dict(vocab_size=1024, hidden_size=256, intermediate_size=688, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+                     head_dim=64, rope_theta=1e4, tie_word_embeddings=True, qk_norm=True, torch_dtype='float32', model_type='qwen3_vl_text',
+                     mrope_section=[8, 12, 12], mrope_interleaved=True, image_token_id=265, video_token_id=267, vision_start_token_id=264,
+                     vision_end_token_id=266,
+                     vision=dict(depth=3, hidden_size=64, out_hidden_size=256, intermediate_size=96, num_heads=4, patch_size=16, spatial_merge_size=2,
+                                 temporal_patch_size=2, in_channels=3, num_position_embeddings=64, deepstack_visual_indexes=[0, 2])),
     'tiny-moe-shared': dict(vocab_size=1024, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
                             head_dim=64, rope_theta=1e4, tie_word_embeddings=True, num_experts=8, num_experts_per_tok=2,
                             moe_intermediate_size=128, shared_expert_intermediate_size=192, torch_dtype='float32'),

@@ -44,6 +44,8 @@ class PackedBatch:
     # tower's output replaces the embeddings of the image placeholder tokens. position_ids is then [3, T].
     pixel_values: Optional[torch.Tensor] = None
     image_grid_thw: Optional[torch.Tensor] = None
+    # (row indices of the placeholder tokens, features per early layer) — set by ``embed`` for towers with deep-stack outputs
+    deepstack: Optional[tuple] = None
 
 
 class Attention(nn.Module):
@@ -317,20 +319,21 @@ class DecoderModel(nn.Module):
         else:
             x = self.embed_tokens(batch.input_ids)
         if batch.pixel_values is not None and self.visual is not None:
-            feats = self.visual(batch.pixel_values, batch.image_grid_thw)
+            feats, deep = self.visual(batch.pixel_values, batch.image_grid_thw, return_deepstack=True)
             where = batch.input_ids == self.cfg.image_token_id
             if self.cfg.video_token_id is not None:
                 where = where | (batch.input_ids == self.cfg.video_token_id)
             if int(where.sum()) != feats.shape[0]:
                 raise ValueError(f'{int(where.sum())} image placeholder tokens in the batch but the tower produced {feats.shape[0]} embeddings')
             x = x.masked_scatter(where[:, None], feats.to(x.dtype))
+            batch.deepstack = (where.nonzero(as_tuple=True)[0], deep) if deep else None
         return x
 
     def forward(self, batch: PackedBatch, hidden: Optional[torch.Tensor] = None, kv_sink=None) -> torch.Tensor:
         x = self.embed(batch) if hidden is None else hidden
         if batch.position_ids.dim() == 2:  # [3, T] (time, height, width) positions of a vision-language batch
             from .vision import mrope_tables
-            cos, sin = mrope_tables(batch.position_ids, self.cfg.head_dim, self.cfg.rope_theta, self.cfg.mrope_section)
+            cos, sin = mrope_tables(batch.position_ids, self.cfg.head_dim, self.cfg.rope_theta, self.cfg.mrope_section, self.cfg.mrope_interleaved)
         else:
             cos, sin = ops.rope_tables(batch.position_ids, self.cfg.head_dim, self.cfg.rope_theta, self.cfg.rope_scaling)
         full = None
@@ -347,6 +350,9 @@ class DecoderModel(nn.Module):
                 x = run(layer, x, cos, sin, batch)
             else:
                 x = layer(x, cos, sin, batch, kv_sink)
+            ds = batch.deepstack
+            if ds is not None and layer.layer_idx < len(ds[1]):  # deep stack: the tower's early features join the first layers' outputs
+                x = x.index_add(0, ds[0], ds[1][layer.layer_idx].to(x.dtype))
         if self.norm is not None:
             x = self.norm(x)
         return x

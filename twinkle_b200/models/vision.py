@@ -37,28 +37,43 @@ class VisionConfig:
     intermediate_size: int = 0
     window_size: int = 112
     fullatt_block_indexes: Tuple[int, ...] = ()
+    # Qwen3-VL: learned position table (a square grid, interpolated to the image's patch grid), tanh-GELU MLP, and extra
+    # mergers after the listed blocks whose outputs are added to the language model's first layers ("deep stack")
+    num_position_embeddings: int = 0
+    deepstack_visual_indexes: Tuple[int, ...] = ()
 
     @classmethod
     def from_hf(cls, d: Dict[str, Any]) -> 'VisionConfig':
         d = dict(d)
-        if 'out_hidden_size' in d:  # Qwen2.5-VL spelling: hidden_size = tower width, out_hidden_size = language model width
+        if 'num_position_embeddings' in d and d.get('num_position_embeddings'):
+            d.update(arch='qwen3_vl', embed_dim=d['hidden_size'], hidden_size=d['out_hidden_size'],
+                     deepstack_visual_indexes=tuple(d.get('deepstack_visual_indexes') or ()))
+        elif 'out_hidden_size' in d:  # Qwen2.5-VL spelling: hidden_size = tower width, out_hidden_size = language model width
             d.update(arch='qwen2_5_vl', embed_dim=d['hidden_size'], hidden_size=d['out_hidden_size'],
                      fullatt_block_indexes=tuple(d.get('fullatt_block_indexes') or ()))
         elif 'fullatt_block_indexes' in d:
             d['fullatt_block_indexes'] = tuple(d['fullatt_block_indexes'] or ())
         keys = ('depth', 'embed_dim', 'hidden_size', 'num_heads', 'mlp_ratio', 'patch_size', 'spatial_merge_size', 'temporal_patch_size', 'in_channels',
-                'arch', 'intermediate_size', 'window_size', 'fullatt_block_indexes')
+                'arch', 'intermediate_size', 'window_size', 'fullatt_block_indexes', 'num_position_embeddings', 'deepstack_visual_indexes')
         return cls(**{k: d[k] for k in keys if k in d})
 
     def to_hf(self) -> Dict[str, Any]:
         base = dict(depth=self.depth, num_heads=self.num_heads, patch_size=self.patch_size, spatial_merge_size=self.spatial_merge_size,
                     temporal_patch_size=self.temporal_patch_size, in_channels=self.in_channels)
+        if self.arch == 'qwen3_vl':
+            return {'model_type': 'qwen3_vl', **base, 'hidden_size': self.embed_dim, 'out_hidden_size': self.hidden_size,
+                    'intermediate_size': self.intermediate_size, 'num_position_embeddings': self.num_position_embeddings,
+                    'deepstack_visual_indexes': list(self.deepstack_visual_indexes), 'hidden_act': 'gelu_pytorch_tanh'}
         if self.arch == 'qwen2_5_vl':
             return {'model_type': 'qwen2_5_vl', **base, 'hidden_size': self.embed_dim, 'out_hidden_size': self.hidden_size,
                     'intermediate_size': self.intermediate_size, 'window_size': self.window_size,
                     'fullatt_block_indexes': list(self.fullatt_block_indexes), 'hidden_act': 'silu'}
         return {'model_type': 'qwen2_vl', **base, 'embed_dim': self.embed_dim, 'hidden_size': self.hidden_size, 'mlp_ratio': self.mlp_ratio,
                 'hidden_act': 'quick_gelu'}
+
+    @property
+    def image_mean_std(self) -> Tuple[Tuple[float, ...], Tuple[float, ...]]:
+        return ((0.5, 0.5, 0.5), (0.5, 0.5, 0.5)) if self.arch == 'qwen3_vl' else (IMAGE_MEAN, IMAGE_STD)
 
     @property
     def patch_dim(self) -> int:
@@ -71,11 +86,11 @@ class _PatchEmbed(nn.Module):
         super().__init__()
         # kept in Conv3d layout [E, C, T, P, P] so the checkpoint tensor loads as is; applied as one GEMM over flat patches
         self.proj = nn.Conv3d(cfg.in_channels, cfg.embed_dim, (cfg.temporal_patch_size, cfg.patch_size, cfg.patch_size),
-                              stride=(cfg.temporal_patch_size, cfg.patch_size, cfg.patch_size), bias=False)
+                              stride=(cfg.temporal_patch_size, cfg.patch_size, cfg.patch_size), bias=cfg.arch == 'qwen3_vl')
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         w = self.proj.weight
-        return F.linear(x.to(w.dtype), w.view(w.shape[0], -1))
+        return F.linear(x.to(w.dtype), w.view(w.shape[0], -1), self.proj.bias)
 
 
 class _Attn(nn.Module):
@@ -127,6 +142,30 @@ class _GatedMlp(nn.Module):
         return self.down_proj(F.silu(self.gate_proj(x)) * self.up_proj(x))
 
 
+class _TanhGeluMlp(nn.Module):
+
+    def __init__(self, dim: int, hidden: int):
+        super().__init__()
+        self.linear_fc1, self.linear_fc2 = nn.Linear(dim, hidden), nn.Linear(hidden, dim)
+
+    def forward(self, x):
+        return self.linear_fc2(F.gelu(self.linear_fc1(x), approximate='tanh'))
+
+
+class _Merger3(nn.Module):
+    """Qwen3-VL merger; ``postshuffle`` normalises the joined ``merge²`` group instead of every patch."""
+
+    def __init__(self, cfg: VisionConfig, postshuffle: bool = False):
+        super().__init__()
+        self.group, self.postshuffle = cfg.embed_dim * cfg.spatial_merge_size**2, postshuffle
+        self.norm = nn.LayerNorm(self.group if postshuffle else cfg.embed_dim, eps=1e-6)
+        self.linear_fc1, self.linear_fc2 = nn.Linear(self.group, self.group), nn.Linear(self.group, cfg.hidden_size)
+
+    def forward(self, x):
+        x = self.norm(x.view(-1, self.group) if self.postshuffle else x).view(-1, self.group)
+        return self.linear_fc2(F.gelu(self.linear_fc1(x)))
+
+
 def _norm(cfg: VisionConfig) -> nn.Module:
     return nn.RMSNorm(cfg.embed_dim, eps=1e-6) if cfg.arch == 'qwen2_5_vl' else nn.LayerNorm(cfg.embed_dim, eps=1e-6)
 
@@ -137,7 +176,8 @@ class _Block(nn.Module):
         super().__init__()
         self.norm1, self.norm2 = _norm(cfg), _norm(cfg)
         self.attn = _Attn(cfg.embed_dim, cfg.num_heads)
-        self.mlp = _GatedMlp(cfg.embed_dim, cfg.intermediate_size) if cfg.arch == 'qwen2_5_vl' else _Mlp(cfg.embed_dim, int(cfg.embed_dim * cfg.mlp_ratio))
+        self.mlp = (_GatedMlp(cfg.embed_dim, cfg.intermediate_size) if cfg.arch == 'qwen2_5_vl' else
+                    _TanhGeluMlp(cfg.embed_dim, cfg.intermediate_size) if cfg.arch == 'qwen3_vl' else _Mlp(cfg.embed_dim, int(cfg.embed_dim * cfg.mlp_ratio)))
 
     def forward(self, x, cos, sin, bounds):
         x = x + self.attn(self.norm1(x), cos, sin, bounds)
@@ -164,7 +204,29 @@ class VisionTower(nn.Module):
         self.cfg = cfg
         self.patch_embed = _PatchEmbed(cfg)
         self.blocks = nn.ModuleList([_Block(cfg) for _ in range(cfg.depth)])
-        self.merger = _Merger(cfg)
+        if cfg.arch == 'qwen3_vl':
+            self.pos_embed = nn.Embedding(cfg.num_position_embeddings, cfg.embed_dim)
+            self.merger = _Merger3(cfg)
+            self.deepstack_merger_list = nn.ModuleList([_Merger3(cfg, postshuffle=True) for _ in cfg.deepstack_visual_indexes])
+        else:
+            self.merger = _Merger(cfg)
+
+    def position_embeddings(self, grid_thw: torch.Tensor) -> torch.Tensor:
+        """Qwen3-VL: the learned ``side × side`` position table sampled bilinearly at every patch of an ``h × w`` grid
+        (corners aligned), repeated per frame, in merge-group order ``[N, embed_dim]``."""
+        side = int(self.cfg.num_position_embeddings**0.5)
+        m, table, out = self.cfg.spatial_merge_size, self.pos_embed.weight, []
+        for t, h, w in grid_thw.tolist():
+            hi, wi = torch.linspace(0, side - 1, h, device=table.device), torch.linspace(0, side - 1, w, device=table.device)
+            h0, w0 = hi.int(), wi.int()
+            h1, w1 = (h0 + 1).clamp(max=side - 1), (w0 + 1).clamp(max=side - 1)
+            dh, dw = (hi - h0)[:, None], (wi - w0)[None, :]
+            corner = lambda a, b: table[(a[:, None] * side + b[None, :]).long().flatten()].view(h, w, -1)  # noqa: E731
+            e = (corner(h0, w0) * ((1 - dh) * (1 - dw))[..., None] + corner(h0, w1) * ((1 - dh) * dw)[..., None] +
+                 corner(h1, w0) * (dh * (1 - dw))[..., None] + corner(h1, w1) * (dh * dw)[..., None])
+            e = e.view(h // m, m, w // m, m, -1).permute(0, 2, 1, 3, 4).reshape(h * w, -1)
+            out.append(e.repeat(t, 1))
+        return torch.cat(out, 0)
 
     def rotary_tables(self, grid_thw: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """cos/sin ``[N, head_dim/2]``: the first quarter of the head rotates with the patch's row, the second with its
@@ -203,13 +265,24 @@ class VisionTower(nn.Module):
             base += t * gh * gw
         return torch.cat(order).to(grid_thw.device), bounds
 
-    def forward(self, pixel_values: torch.Tensor, grid_thw: torch.Tensor) -> torch.Tensor:
+    def forward(self, pixel_values: torch.Tensor, grid_thw: torch.Tensor, return_deepstack: bool = False):
         """``pixel_values [N, C·T·P·P]`` (flat patches of all images, in order), ``grid_thw [n_images, 3]`` →
-        ``[N / merge², hidden_size]``."""
+        ``[N / merge², hidden_size]``; with ``return_deepstack`` also the list of deep-stack features (same shape each;
+        empty for towers without them)."""
         x = self.patch_embed(pixel_values)
         cos, sin = self.rotary_tables(grid_thw)
         frames = torch.repeat_interleave(grid_thw[:, 1] * grid_thw[:, 2], grid_thw[:, 0])
         bounds = [0] + frames.cumsum(0).tolist()
+        if self.cfg.arch == 'qwen3_vl':
+            x = x + self.position_embeddings(grid_thw).to(x.dtype)
+            deep = []
+            for i, blk in enumerate(self.blocks):
+                x = blk(x, cos, sin, bounds)
+                if i in self.cfg.deepstack_visual_indexes:
+                    deep.append(self.deepstack_merger_list[self.cfg.deepstack_visual_indexes.index(i)](x))
+            return (self.merger(x), deep) if return_deepstack else self.merger(x)
+        if return_deepstack:
+            return self.forward(pixel_values, grid_thw), []
         if self.cfg.arch != 'qwen2_5_vl':
             for blk in self.blocks:
                 x = blk(x, cos, sin, bounds)
@@ -225,14 +298,18 @@ class VisionTower(nn.Module):
 
 
 # ------------------------------------------------------------------------------------------ positions in the LLM
-def mrope_tables(position_ids: torch.Tensor, head_dim: int, theta: float, section: Sequence[int]) -> Tuple[torch.Tensor, torch.Tensor]:
+def mrope_tables(position_ids: torch.Tensor, head_dim: int, theta: float, section: Sequence[int], interleaved: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """cos/sin ``[T, head_dim/2]`` from ``position_ids [3, T]`` (time, height, width): frequency ``j`` uses the component
     whose section (``section`` sums to ``head_dim/2``) contains ``j``. Text tokens carry the same value in all three
     components, which reduces to ordinary RoPE."""
     half = head_dim // 2
     assert sum(section) == half, f'mrope sections {list(section)} must sum to head_dim/2 = {half}'
     inv = 1.0 / (theta**(torch.arange(0, head_dim, 2, dtype=torch.float32, device=position_ids.device) / head_dim))
-    comp = torch.repeat_interleave(torch.arange(3, device=position_ids.device), torch.tensor(list(section), device=position_ids.device))
+    if interleaved:  # Qwen3-VL: t h w t h w … over the low frequencies (height on j ≡ 1, width on j ≡ 2 mod 3, while their sections last), time elsewhere
+        j = torch.arange(half, device=position_ids.device)
+        comp = torch.where((j % 3 == 1) & (j < 3 * section[1]), 1, torch.where((j % 3 == 2) & (j < 3 * section[2]), 2, 0))
+    else:
+        comp = torch.repeat_interleave(torch.arange(3, device=position_ids.device), torch.tensor(list(section), device=position_ids.device))
     pos = position_ids.float()[comp, :].t()                  # [T, half]: the component each frequency follows
     ang = pos * inv[None, :]
     return ang.cos(), ang.sin()
@@ -328,7 +405,7 @@ def preprocess_image(image: Any, cfg: VisionConfig, min_pixels: int = 56 * 56, m
             x = torch.as_tensor(np.array(pil)).permute(2, 0, 1).float()
         except ImportError:
             x = F.interpolate(x[None], size=(h, w), mode='bicubic', align_corners=False, antialias=True)[0].clamp(0, 255)
-    mean, std = torch.tensor(IMAGE_MEAN).view(3, 1, 1), torch.tensor(IMAGE_STD).view(3, 1, 1)
+    mean, std = (torch.tensor(v).view(3, 1, 1) for v in cfg.image_mean_std)
     x = (x / 255.0 - mean) / std
     return patchify(x[None], cfg)
 
@@ -355,5 +432,5 @@ def preprocess_video(frames: Sequence[Any], cfg: VisionConfig, min_pixels: int =
     h, w = smart_resize(x.shape[2], x.shape[3], factor, min_pixels, max_pixels)
     if (h, w) != tuple(x.shape[2:]):
         x = F.interpolate(x, size=(h, w), mode='bicubic', align_corners=False, antialias=True).clamp(0, 255)
-    mean, std = torch.tensor(IMAGE_MEAN).view(1, 3, 1, 1), torch.tensor(IMAGE_STD).view(1, 3, 1, 1)
+    mean, std = (torch.tensor(v).view(1, 3, 1, 1) for v in cfg.image_mean_std)
     return patchify((x / 255.0 - mean) / std, cfg)
