@@ -19,6 +19,8 @@ def _cases():
                                               rope_scaling={'rope_type': 'llama3', 'factor': 8.0, 'low_freq_factor': 1.0, 'high_freq_factor': 4.0,
                                                             'original_max_position_embeddings': 64}), 'LlamaForCausalLM'),
         'qwen2_bias': (lambda: T.Qwen2Config(tie_word_embeddings=False, **COMMON), 'Qwen2ForCausalLM'),
+        'mistral': (lambda: T.MistralConfig(sliding_window=None, **COMMON), 'MistralForCausalLM'),
+        'seed_oss': (lambda: T.SeedOssConfig(head_dim=32, **COMMON), 'SeedOssForCausalLM'),
         'qwen3_moe': (lambda: T.Qwen3MoeConfig(head_dim=32, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, norm_topk_prob=True,
                                                decoder_sparse_step=1, mlp_only_layers=[], **COMMON), 'Qwen3MoeForCausalLM'),
         'qwen2_moe_shared': (lambda: T.Qwen2MoeConfig(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=96,
@@ -120,3 +122,17 @@ def test_adapter_saved_in_peft_layout_merges_into_the_hf_model(name, tmp_path):
     with torch.no_grad():
         theirs = hf(ids).logits[0]
     assert torch.allclose(adapted, theirs, atol=5e-5), float((adapted - theirs).abs().max())
+
+
+def test_unknown_architectures_are_refused_not_guessed(tmp_path, monkeypatch):
+    """Granite shares every config field with Llama but scales embeddings, residuals, attention and logits: loading it as a
+    Llama would run and be wrong. Unknown ``model_type`` values are refused unless explicitly allowed."""
+    from twinkle_b200.models.config import DecoderConfig
+    cfg = {'model_type': 'granite', 'hidden_size': 128, 'num_attention_heads': 4, 'num_hidden_layers': 2, 'vocab_size': 512}
+    with pytest.raises(NotImplementedError, match='granite'):
+        DecoderConfig.from_hf(cfg)
+    monkeypatch.setenv('TWINKLE_ALLOW_UNKNOWN_ARCH', '1')
+    assert DecoderConfig.from_hf(cfg).hidden_size == 128
+    monkeypatch.delenv('TWINKLE_ALLOW_UNKNOWN_ARCH')
+    with pytest.raises(NotImplementedError):
+        DecoderConfig.from_hf({'model_type': 'qwen2_vl', 'text_config': {'model_type': 'qwen2_vl_text'}, 'vision_config': {'model_type': 'siglip'}})

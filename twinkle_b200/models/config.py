@@ -13,6 +13,11 @@ from dataclasses import asdict, dataclass, field
 from typing import List, Any, Dict, Optional
 
 
+# config.json ``model_type`` values whose layer maths is what ``models/decoder.py`` computes (each checked against transformers)
+SUPPORTED_MODEL_TYPES = frozenset({'llama', 'mistral', 'qwen2', 'qwen2_moe', 'qwen3', 'qwen3_moe', 'seed_oss', 'qwen2_vl', 'qwen2_vl_text',
+                                   'qwen2_5_vl', 'qwen2_5_vl_text', 'qwen3_vl', 'qwen3_vl_text'})
+
+
 def _rope_scaling_of(cfg: Dict[str, Any]) -> Optional[Dict[str, Any]]:
     """``rope_scaling`` (or the newer ``rope_parameters``) of a HF config when it describes a long-context variant."""
     rs = cfg.get('rope_scaling') or cfg.get('rope_parameters')
@@ -120,6 +125,11 @@ class DecoderConfig:
         if 'text_config' in cfg:
             cfg = dict(cfg['text_config'])
         mt = cfg.get('model_type', 'qwen3')
+        if mt not in SUPPORTED_MODEL_TYPES and not os.environ.get('TWINKLE_ALLOW_UNKNOWN_ARCH'):
+            # an unknown type may differ in ways a shared field list does not show (scaled embeddings or residuals, other
+            # norms, partial rotary …): better refused than silently computed wrongly
+            raise NotImplementedError(f'model_type {mt!r} is not among the decoder families implemented here {sorted(SUPPORTED_MODEL_TYPES)}; '
+                                      'set TWINKLE_ALLOW_UNKNOWN_ARCH=1 to load it as a Llama-style decoder anyway')
         vision = top.get('vision_config')
         if vision is not None:
             vision = dict(vision)
