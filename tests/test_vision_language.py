@@ -168,8 +168,6 @@ def test_template_processor_training_and_checkpoints(tmp_path):
     assert mb.extras['pixel_values'].shape[0] == 24 + 16 and mb.cu_seqlens.numel() == 4   # 40 × 40 is scaled up to the minimum pixel count
     a, b = int(mb.cu_seqlens[1]), int(mb.cu_seqlens[2])
     assert mb.extras['mrope_position_ids'][:, a:b].tolist() == [list(range(b - a))] * 3            # the text-only sequence in the middle
-    with pytest.raises(NotImplementedError):
-        InputProcessor(sp_size=2, sp_rank=0)(tpl.batch_encode(trajs))
 
     m.set_optimizer('AdamW', lr=1e-2)
     w0 = m.model.visual.patch_embed.proj.weight.detach().clone()
@@ -211,12 +209,12 @@ def _vl_trajs():
                           {'role': 'assistant', 'content': 'a dog'}]}]
 
 
-def _vl_curve(rank, world, steps):
+def _vl_curve(rank, world, steps, sp=1, preset='tiny-vl'):
     import torch.distributed as dist
     from twinkle_b200.model import TransformersModel
     from twinkle_b200.utils.device_mesh import DeviceMesh
-    mesh = DeviceMesh.from_sizes(fsdp_size=world, dp_size=None) if world > 1 else DeviceMesh.from_sizes(dp_size=1)
-    m = TransformersModel(model_id='tiny-vl', device_mesh=mesh, seed=0)
+    mesh = DeviceMesh.from_sizes(fsdp_size=world, dp_size=None, ulysses_size=sp if sp > 1 else None) if world > 1 else DeviceMesh.from_sizes(dp_size=1)
+    m = TransformersModel(model_id=preset, device_mesh=mesh, seed=0)
     m.set_template('Qwen2VLTemplate', vision_config=m.config.vision, max_length=4096)
     m.set_optimizer('AdamW', lr=3e-3, weight_decay=0.0)
     trajs = _vl_trajs()
@@ -228,6 +226,7 @@ def _vl_curve(rank, world, steps):
         t = torch.tensor([out['loss'] * out['num_tokens'], out['num_tokens']], dtype=torch.float64)
         if world > 1:
             dist.all_reduce(t)
+            t = t / sp  # sequence-parallel peers report the same data group's numbers
         curve.append(float(t[0] / t[1]))
     return curve
 
@@ -380,3 +379,23 @@ def test_qwen3_vl_trains_through_the_public_api_and_exports(tmp_path):
         pytest.skip(f'transformers could not run the export: {type(e).__name__}: {e}')
     ours = torch.as_tensor(m.forward_only(inputs=[trajs[0]], return_logits=True)['logits']).float().reshape(-1, theirs.shape[-1])[:theirs.shape[0]]
     assert torch.allclose(ours, theirs, atol=5e-5), float((ours - theirs).abs().max())
+
+
+def test_sequence_parallel_split_of_image_batches_matches_one_process():
+    """Two gloo ranks that split every sequence (Ulysses): each runs the tower on all images and keeps the features of the
+    placeholder tokens in its half of the row; deep-stack features (Qwen3-VL preset) follow the same rows."""
+    from tests.dist_utils import run_ranks
+    from twinkle_b200.processor import InputProcessor
+    from twinkle_b200.template import template_mapping
+    tpl = template_mapping['Qwen2VLTemplate'](model_id=None, vision_config=VC, max_length=4096)
+    feats = tpl.batch_encode(_vl_trajs())
+    full, = InputProcessor()(feats)
+    halves = [InputProcessor(sp_size=2, sp_rank=r)(feats)[0] for r in (0, 1)]
+    n_ph = int((full.input_ids == tpl.image_token_id).sum())
+    assert torch.equal(torch.cat([h.extras['vision_rows'] for h in halves]), torch.arange(n_ph))
+    assert torch.equal(torch.cat([h.extras['mrope_position_ids'] for h in halves], 1)[:, :full.input_ids.numel()], full.extras['mrope_position_ids'])
+    for preset in ('tiny-vl', 'tiny-vl3'):
+        single = _vl_curve(0, 1, 2, 1, preset)
+        for c in run_ranks(_vl_curve, 2, 2, 2, preset):
+            for a, b in zip(single, c):
+                assert abs(a - b) < 3e-4, (preset, single, c)

@@ -255,6 +255,8 @@ class TransformersModel(TwinkleModel, CheckpointEngineMixin):
             batch.pixel_values = extras['pixel_values'].to(self.device, dt)
             batch.image_grid_thw = extras['image_grid_thw'].to(self.device)
             batch.position_ids = extras['mrope_position_ids'].to(self.device)
+            if extras.get('vision_rows') is not None:
+                batch.vision_rows = extras['vision_rows'].to(self.device)
         loss_obj = og.loss_instance
         want_entropy = bool(getattr(loss_obj, 'require_entropy', False))
         want_logits = return_logits or bool(getattr(loss_obj, 'require_logits', False))

@@ -46,6 +46,8 @@ class PackedBatch:
     image_grid_thw: Optional[torch.Tensor] = None
     # (row indices of the placeholder tokens, features per early layer) — set by ``embed`` for towers with deep-stack outputs
     deepstack: Optional[tuple] = None
+    # under sequence / context parallelism: rows of the tower's output that belong to this rank's placeholder tokens
+    vision_rows: Optional[torch.Tensor] = None
 
 
 class Attention(nn.Module):
@@ -320,6 +322,8 @@ class DecoderModel(nn.Module):
             x = self.embed_tokens(batch.input_ids)
         if batch.pixel_values is not None and self.visual is not None:
             feats, deep = self.visual(batch.pixel_values, batch.image_grid_thw, return_deepstack=True)
+            if batch.vision_rows is not None:
+                feats, deep = feats[batch.vision_rows], [d[batch.vision_rows] for d in deep]
             where = batch.input_ids == self.cfg.image_token_id
             if self.cfg.video_token_id is not None:
                 where = where | (batch.input_ids == self.cfg.video_token_id)

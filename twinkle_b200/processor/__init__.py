@@ -108,7 +108,7 @@ class InputProcessor:
                     ids, labels = ids[am], labels[am]
                     pos = torch.arange(ids.numel()) if f.get('position_ids') is None else pos[am]
             item = {'input_ids': ids, 'labels': labels, 'position_ids': pos}
-            for k in ('routed_experts', 'pixel_values', 'image_grid_thw', 'mrope_position_ids'):
+            for k in ('routed_experts', 'pixel_values', 'image_grid_thw', 'mrope_position_ids', 'placeholder_ids'):
                 if f.get(k) is not None:
                     item[k] = f[k]
             out.append(item)
@@ -189,8 +189,6 @@ class InputProcessor:
         if any('routed_experts' in it for it in items):
             extras['routed_experts'] = [it.get('routed_experts') for it in items]
         if any('pixel_values' in it for it in items):
-            if self.sp_size > 1 or self.cp_size > 1:
-                raise NotImplementedError('batches with images are not split over sequence- or context-parallel ranks')
             # images travel beside the packed row: all patches in token order, their grids, and (time, height, width)
             # positions for every token (text-only sequences and padding count up in all three components alike)
             mpos = []
@@ -203,9 +201,22 @@ class InputProcessor:
                 mpos.append(m)
             extras['mrope_position_ids'] = torch.cat(mpos, 1)
             extras['pixel_values'] = torch.cat([torch.as_tensor(it['pixel_values']) for it in items if 'pixel_values' in it], 0)
+            extras['placeholder_ids'] = sorted({int(t) for it in items for t in (it.get('placeholder_ids') or ())})
             extras['image_grid_thw'] = torch.cat([torch.as_tensor(it['image_grid_thw']).long().view(-1, 3) for it in items if 'pixel_values' in it], 0)
         mb.extras = extras or None
-        return self._split_parallel(mb) if split else mb
+        if not split:
+            return mb
+        out = self._split_parallel(mb)
+        if out.local_index is not None and extras.get('pixel_values') is not None:
+            # sequence / context parallel: every rank runs the tower on all images (they are small next to the language
+            # model) and keeps the features of the placeholder tokens in its share of the row, plus its columns of the positions
+            is_ph = torch.zeros(input_ids.numel(), dtype=torch.bool)
+            for it_ids in (extras.get('placeholder_ids') or ()):
+                is_ph |= input_ids == it_ids
+            ordinal = torch.cumsum(is_ph.long(), 0) - 1
+            local = out.local_index
+            out.extras = dict(extras, mrope_position_ids=extras['mrope_position_ids'][:, local], vision_rows=ordinal[local][is_ph[local]])
+        return out
 
     def _split_parallel(self, mb: MicroBatch) -> MicroBatch:
         """Keep this rank's share of every sequence: contiguous slices for

@@ -438,6 +438,7 @@ class Qwen2VLTemplate(Template):
         f = feats[0]
         grids = [g for _, g in self._vision]
         f['pixel_values'] = torch.cat([p for p, _ in self._vision], 0)                      # type: ignore[typeddict-unknown-key]
+        f['placeholder_ids'] = [self.image_token_id, self.video_token_id]                   # type: ignore[typeddict-unknown-key]
         f['image_grid_thw'] = [list(g) for g in grids]                                      # type: ignore[typeddict-unknown-key]
         f['mrope_position_ids'] = rope_index(f['input_ids'], grids, self.image_token_id,   # type: ignore[typeddict-unknown-key]
                                              self.vision_config.spatial_merge_size, video_token_id=self.video_token_id)
