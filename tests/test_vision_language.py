@@ -399,3 +399,34 @@ def test_sequence_parallel_split_of_image_batches_matches_one_process():
         for c in run_ranks(_vl_curve, 2, 2, 2, preset):
             for a, b in zip(single, c):
                 assert abs(a - b) < 3e-4, (preset, single, c)
+
+
+def test_qwen3_vl_moe_checkpoint_with_fused_experts(tmp_path):
+    """Mixture-of-experts language model under the Qwen3-VL tower; the checkpoint keeps the experts as fused 3-D tensors."""
+    T = pytest.importorskip('transformers')
+    from twinkle_b200.model import TransformersModel
+    from twinkle_b200.models.decoder import PackedBatch
+    try:
+        cfg = T.Qwen3VLMoeConfig(
+            text_config=dict(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                             head_dim=32, max_position_embeddings=512, rope_theta=10000.0, tie_word_embeddings=False, num_experts=4, num_experts_per_tok=2,
+                             moe_intermediate_size=48, decoder_sparse_step=1, mlp_only_layers=[], norm_topk_prob=True,
+                             rope_scaling={'rope_type': 'default', 'mrope_section': [4, 6, 6], 'mrope_interleaved': True}),
+            vision_config=dict(VC3, depth=2, deepstack_visual_indexes=[0]), image_token_id=500, video_token_id=501, vision_start_token_id=502,
+            vision_end_token_id=503)
+        torch.manual_seed(0)
+        hf = T.Qwen3VLMoeForConditionalGeneration(cfg).float().eval()
+        hf.save_pretrained(str(tmp_path / 'hf'), safe_serialization=True)
+        grid, pix = torch.tensor([[1, 4, 6]]), torch.randn(24, 3 * 2 * 16 * 16, generator=torch.Generator().manual_seed(2))
+        ids = [5, 6, 502] + [500] * 6 + [503, 7, 8]
+        ids_t = torch.tensor([ids])
+        with torch.no_grad():
+            want = hf(input_ids=ids_t, pixel_values=pix, image_grid_thw=grid, mm_token_type_ids=(ids_t == 500).int()).logits[0]
+    except (AttributeError, TypeError) as e:
+        pytest.skip(f'{type(e).__name__}: {e}')
+    m = TransformersModel(model_id=str(tmp_path / 'hf'))
+    assert m.config.is_moe and m.config.mrope_interleaved and m.config.to_hf()['model_type'] == 'qwen3_vl_moe'
+    with torch.no_grad():
+        got = m.model.logits(m.model(PackedBatch(torch.tensor(ids), rope_index(ids, grid.tolist(), 500), torch.tensor([0, len(ids)], dtype=torch.int32),
+                                                 len(ids), pixel_values=pix, image_grid_thw=grid)))
+    assert torch.allclose(got.float(), want, atol=2e-5), float((got - want).abs().max())

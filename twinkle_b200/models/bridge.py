@@ -134,6 +134,22 @@ def hf_to_internal(name: str, cfg: DecoderConfig, get: Callable[[str], torch.Ten
                 except KeyError:
                     continue
             raise KeyError(n)
+    if rest in ('mlp.experts.gate_up_proj', 'mlp.experts.down_proj'):
+        # checkpoints written by newer transformers keep the experts fused, in this package's own layout
+        # ([E, 2I, H] gate|up and [E, H, I]); older ones have one tensor per expert and projection
+        try:
+            fused = get(_hf_layer(i, rest))
+        except KeyError:
+            fused = None
+        if fused is not None:
+            lo, hi = expert_range or (0, cfg.num_experts)
+            want = (2 * cfg.moe_intermediate_size, cfg.hidden_size) if rest.endswith('gate_up_proj') else (cfg.hidden_size, cfg.moe_intermediate_size)
+            if tuple(fused.shape[1:]) != want:
+                if tuple(fused.shape[1:]) == want[::-1]:
+                    fused = fused.transpose(1, 2)       # [E, in, out] variant
+                else:
+                    raise ValueError(f'{name}: fused expert tensor of shape {tuple(fused.shape)}; expected [E, {want[0]}, {want[1]}]')
+            return fused[lo:hi].contiguous()
     if rest == 'mlp.experts.gate_up_proj':
         lo, hi = expert_range or (0, cfg.num_experts)
         return torch.stack([torch.cat([get(_hf_layer(i, f'mlp.experts.{e}.gate_proj.weight')),

@@ -15,7 +15,7 @@ from typing import List, Any, Dict, Optional
 
 # config.json ``model_type`` values whose layer maths is what ``models/decoder.py`` computes (each checked against transformers)
 SUPPORTED_MODEL_TYPES = frozenset({'llama', 'mistral', 'qwen2', 'qwen2_moe', 'qwen3', 'qwen3_moe', 'seed_oss', 'qwen2_vl', 'qwen2_vl_text',
-                                   'qwen2_5_vl', 'qwen2_5_vl_text', 'qwen3_vl', 'qwen3_vl_text'})
+                                   'qwen2_5_vl', 'qwen2_5_vl_text', 'qwen3_vl', 'qwen3_vl_text', 'qwen3_vl_moe', 'qwen3_vl_moe_text'})
 
 
 def _rope_scaling_of(cfg: Dict[str, Any]) -> Optional[Dict[str, Any]]:
@@ -133,7 +133,7 @@ class DecoderConfig:
         vision = top.get('vision_config')
         if vision is not None:
             vision = dict(vision)
-            if vision.get('model_type', top.get('model_type', 'qwen2_vl')) not in ('qwen2_vl', 'qwen2_5_vl', 'qwen3_vl'):
+            if vision.get('model_type', top.get('model_type', 'qwen2_vl')) not in ('qwen2_vl', 'qwen2_5_vl', 'qwen3_vl', 'qwen3_vl_moe'):
                 raise NotImplementedError(f"vision tower of type {vision.get('model_type')!r} is not supported (qwen2_vl, qwen2_5_vl and qwen3_vl are)")
         rs_any = cfg.get('rope_scaling') or cfg.get('rope_parameters') or top.get('rope_scaling') or {}
         heads = cfg.get('num_attention_heads', 32)
@@ -192,15 +192,18 @@ class DecoderConfig:
             d['rope_scaling'] = dict(self.rope_scaling)
         if self.vision:
             fam = self.vision.get('model_type', 'qwen2_vl')
+            if fam == 'qwen3_vl' and self.is_moe:
+                fam = 'qwen3_vl_moe'
             rope = {'type': 'mrope', 'mrope_section': list(self.mrope_section or [])}
-            if fam == 'qwen3_vl':
+            if fam.startswith('qwen3_vl'):
                 rope = {'rope_type': 'default', 'mrope_section': list(self.mrope_section or []), 'mrope_interleaved': self.mrope_interleaved}
             text = dict(d, model_type=fam + '_text', rope_scaling=rope)
             text.pop('architectures', None)
             arch = {'qwen2_vl': 'Qwen2VLForConditionalGeneration', 'qwen2_5_vl': 'Qwen2_5_VLForConditionalGeneration',
-                    'qwen3_vl': 'Qwen3VLForConditionalGeneration'}[fam]
+                    'qwen3_vl': 'Qwen3VLForConditionalGeneration', 'qwen3_vl_moe': 'Qwen3VLMoeForConditionalGeneration'}[fam]
+            vis = dict(self.vision, model_type=fam) if fam == 'qwen3_vl_moe' else dict(self.vision)
             return {'architectures': [arch], 'model_type': fam, 'text_config': text,
-                    'vision_config': dict(self.vision), 'image_token_id': self.image_token_id, 'video_token_id': self.video_token_id,
+                    'vision_config': vis, 'image_token_id': self.image_token_id, 'video_token_id': self.video_token_id,
                     'vision_start_token_id': self.vision_start_token_id, 'vision_end_token_id': self.vision_end_token_id,
                     'tie_word_embeddings': self.tie_word_embeddings, 'torch_dtype': self.torch_dtype}
         if self.layer_types:
