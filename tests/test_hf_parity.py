@@ -20,6 +20,8 @@ def _cases():
                                                             'original_max_position_embeddings': 64}), 'LlamaForCausalLM'),
         'qwen2_bias': (lambda: T.Qwen2Config(tie_word_embeddings=False, **COMMON), 'Qwen2ForCausalLM'),
         'mistral': (lambda: T.MistralConfig(sliding_window=None, **COMMON), 'MistralForCausalLM'),
+        'mixtral': (lambda: T.MixtralConfig(num_local_experts=4, num_experts_per_tok=2, sliding_window=None, **{**COMMON, 'intermediate_size': 96}),
+                    'MixtralForCausalLM'),
         'seed_oss': (lambda: T.SeedOssConfig(head_dim=32, **COMMON), 'SeedOssForCausalLM'),
         'qwen3_moe': (lambda: T.Qwen3MoeConfig(head_dim=32, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, norm_topk_prob=True,
                                                decoder_sparse_step=1, mlp_only_layers=[], **COMMON), 'Qwen3MoeForCausalLM'),
@@ -64,7 +66,7 @@ def test_hf_checkpoint_gives_the_same_logits_here(name, tmp_path):
     assert torch.allclose(got, want, atol=2e-5), float((got - want).abs().max())
 
 
-@pytest.mark.parametrize('name', ['qwen3', 'qwen3_moe'])
+@pytest.mark.parametrize('name', ['qwen3', 'qwen3_moe', 'mixtral', 'qwen2_moe_shared'])
 def test_checkpoint_saved_here_loads_in_transformers(name, tmp_path):
     hf = _hf_model(name)
     hf.save_pretrained(str(tmp_path / 'hf'), safe_serialization=True)

@@ -33,6 +33,21 @@ def _hf_layer(i: int, rest: str) -> str:
     return f'model.layers.{i}.{rest}'
 
 
+_MIXTRAL = ((re.compile(r'\.mlp\.experts\.(\d+)\.gate_proj\.'), r'.block_sparse_moe.experts.\1.w1.'),
+            (re.compile(r'\.mlp\.experts\.(\d+)\.up_proj\.'), r'.block_sparse_moe.experts.\1.w3.'),
+            (re.compile(r'\.mlp\.experts\.(\d+)\.down_proj\.'), r'.block_sparse_moe.experts.\1.w2.'),
+            (re.compile(r'\.mlp\.gate\.'), '.block_sparse_moe.gate.'))
+
+
+def _family(name: str, cfg: DecoderConfig) -> str:
+    """Checkpoint spelling of a tensor name for families that differ from the Qwen / Llama one (Mixtral: ``block_sparse_moe``
+    with ``w1`` = gate, ``w3`` = up, ``w2`` = down)."""
+    if cfg.model_type == 'mixtral':
+        for pat, rep in _MIXTRAL:
+            name = pat.sub(rep, name)
+    return name
+
+
 def _vl(name: str, cfg: DecoderConfig) -> str:
     """Vision-language checkpoints nest the language model: ``model.X`` → ``model.language_model.X``."""
     return 'model.language_model.' + name[len('model.'):] if cfg.vision and name.startswith('model.') else name
@@ -42,7 +57,7 @@ def internal_to_hf(name: str, tensor: torch.Tensor, cfg: DecoderConfig) -> List[
     """One internal (full, un-sharded) tensor → one or more HF tensors."""
     if name.startswith('visual.'):
         return [('model.' + name, tensor)]
-    return [(_vl(n, cfg), t) for n, t in _internal_to_hf_text(name, tensor, cfg)]
+    return [(_family(_vl(n, cfg), cfg), t) for n, t in _internal_to_hf_text(name, tensor, cfg)]
 
 
 def _internal_to_hf_text(name: str, tensor: torch.Tensor, cfg: DecoderConfig) -> List[Tuple[str, torch.Tensor]]:
@@ -86,7 +101,7 @@ def hf_names_for(name: str, cfg: DecoderConfig) -> List[str]:
     """HF tensor names that make up one internal tensor (in concat order)."""
     if name.startswith('visual.'):
         return ['model.' + name]
-    return [_vl(n, cfg) for n in _hf_names_for_text(name, cfg)]
+    return [_family(_vl(n, cfg), cfg) for n in _hf_names_for_text(name, cfg)]
 
 
 def _hf_names_for_text(name: str, cfg: DecoderConfig) -> List[str]:
@@ -124,6 +139,11 @@ def hf_to_internal(name: str, cfg: DecoderConfig, get: Callable[[str], torch.Ten
     m = _LAYER.match(name)
     rest = m.group(2) if m else ''
     i = int(m.group(1)) if m else -1
+    if cfg.model_type == 'mixtral':
+        plain = get
+
+        def get(n: str) -> torch.Tensor:  # noqa: F811
+            return plain(_family(n, cfg))
     if cfg.vision:
         raw = get
 

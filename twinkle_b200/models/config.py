@@ -14,7 +14,7 @@ from typing import List, Any, Dict, Optional
 
 
 # config.json ``model_type`` values whose layer maths is what ``models/decoder.py`` computes (each checked against transformers)
-SUPPORTED_MODEL_TYPES = frozenset({'llama', 'mistral', 'qwen2', 'qwen2_moe', 'qwen3', 'qwen3_moe', 'seed_oss', 'qwen2_vl', 'qwen2_vl_text',
+SUPPORTED_MODEL_TYPES = frozenset({'llama', 'mistral', 'mixtral', 'qwen2', 'qwen2_moe', 'qwen3', 'qwen3_moe', 'seed_oss', 'qwen2_vl', 'qwen2_vl_text',
                                    'qwen2_5_vl', 'qwen2_5_vl_text', 'qwen3_vl', 'qwen3_vl_text', 'qwen3_vl_moe', 'qwen3_vl_moe_text'})
 
 
@@ -146,7 +146,8 @@ class DecoderConfig:
             rope_scaling=_rope_scaling_of(cfg), tie_word_embeddings=bool(cfg.get('tie_word_embeddings', False)),
             qk_norm=mt.startswith('qwen3'), attention_bias=bool(cfg.get('attention_bias', mt.startswith('qwen2'))),
             num_experts=cfg.get('num_experts', cfg.get('num_local_experts', 0)) or 0,
-            num_experts_per_tok=cfg.get('num_experts_per_tok', 8), moe_intermediate_size=cfg.get('moe_intermediate_size', 768),
+            num_experts_per_tok=cfg.get('num_experts_per_tok', 8),
+            moe_intermediate_size=cfg.get('moe_intermediate_size', cfg.get('intermediate_size', 768) if mt == 'mixtral' else 768),
             norm_topk_prob=bool(cfg.get('norm_topk_prob', True)), router_aux_loss_coef=float(cfg.get('router_aux_loss_coef', 0.0)),
             shared_expert_intermediate_size=int(cfg.get('shared_expert_intermediate_size', 0) or 0),
             rms_norm_offset=float(cfg.get('rms_norm_offset', 1.0 if mt.startswith('gemma') else 0.0)),
@@ -171,8 +172,10 @@ class DecoderConfig:
 
     def to_hf(self) -> Dict[str, Any]:
         arch = 'Qwen3MoeForCausalLM' if self.is_moe else ('Qwen3ForCausalLM' if self.qk_norm else 'LlamaForCausalLM')
+        arch = {'mixtral': 'MixtralForCausalLM', 'qwen2_moe': 'Qwen2MoeForCausalLM', 'qwen2': 'Qwen2ForCausalLM', 'mistral': 'MistralForCausalLM',
+                'seed_oss': 'SeedOssForCausalLM'}.get(self.model_type, arch)
         d = {
-            'architectures': [arch], 'model_type': 'qwen3_moe' if self.is_moe else self.model_type,
+            'architectures': [arch], 'model_type': self.model_type if self.model_type in ('mixtral', 'qwen2_moe') else ('qwen3_moe' if self.is_moe else self.model_type),
             'vocab_size': self.vocab_size, 'hidden_size': self.hidden_size, 'intermediate_size': self.intermediate_size,
             'num_hidden_layers': self.num_hidden_layers, 'num_attention_heads': self.num_attention_heads,
             'num_key_value_heads': self.num_key_value_heads, 'head_dim': self.head_dim, 'rms_norm_eps': self.rms_norm_eps,
@@ -186,6 +189,8 @@ class DecoderConfig:
                      router_aux_loss_coef=self.router_aux_loss_coef, decoder_sparse_step=1, mlp_only_layers=[])
             if self.shared_expert_intermediate_size:
                 d['shared_expert_intermediate_size'] = self.shared_expert_intermediate_size
+            if self.model_type == 'mixtral':
+                d.update(num_local_experts=self.num_experts, intermediate_size=self.moe_intermediate_size, sliding_window=None)
         if self.rms_norm_offset:
             d['rms_norm_offset'] = self.rms_norm_offset
         if self.rope_scaling:
