@@ -209,11 +209,14 @@ def _vl_trajs():
                           {'role': 'assistant', 'content': 'a dog'}]}]
 
 
-def _vl_curve(rank, world, steps, sp=1, preset='tiny-vl'):
+def _vl_curve(rank, world, steps, sp=1, preset='tiny-vl', cp=False):
     import torch.distributed as dist
     from twinkle_b200.model import TransformersModel
     from twinkle_b200.utils.device_mesh import DeviceMesh
-    mesh = DeviceMesh.from_sizes(fsdp_size=world, dp_size=None, ulysses_size=sp if sp > 1 else None) if world > 1 else DeviceMesh.from_sizes(dp_size=1)
+    if cp:
+        mesh = DeviceMesh.from_sizes(dp_size=1, cp_size=world)
+    else:
+        mesh = DeviceMesh.from_sizes(fsdp_size=world, dp_size=None, ulysses_size=sp if sp > 1 else None) if world > 1 else DeviceMesh.from_sizes(dp_size=1)
     m = TransformersModel(model_id=preset, device_mesh=mesh, seed=0)
     m.set_template('Qwen2VLTemplate', vision_config=m.config.vision, max_length=4096)
     m.set_optimizer('AdamW', lr=3e-3, weight_decay=0.0)
@@ -430,3 +433,13 @@ def test_qwen3_vl_moe_checkpoint_with_fused_experts(tmp_path):
         got = m.model.logits(m.model(PackedBatch(torch.tensor(ids), rope_index(ids, grid.tolist(), 500), torch.tensor([0, len(ids)], dtype=torch.int32),
                                                  len(ids), pixel_values=pix, image_grid_thw=grid)))
     assert torch.allclose(got.float(), want, atol=2e-5), float((got - want).abs().max())
+
+
+def test_context_parallel_split_of_image_batches_matches_one_process():
+    """Zig-zag context parallelism over 2 gloo ranks: each rank holds two chunks of every sequence; placeholder features and
+    position columns follow the same index."""
+    from tests.dist_utils import run_ranks
+    single = _vl_curve(0, 1, 2, 1, 'tiny-vl')
+    for c in run_ranks(_vl_curve, 2, 2, 2, 'tiny-vl', True):     # sp argument 2: both ranks report the same data group's numbers
+        for a, b in zip(single, c):
+            assert abs(a - b) < 3e-4, (single, c)
