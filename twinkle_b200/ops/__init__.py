@@ -207,9 +207,24 @@ class _QKNormRope(torch.autograd.Function):
         return gqkv, gqw.to(qw.dtype), gkw.to(kw.dtype), None, None, None, None, None, None
 
 
+_WARNED_HEAD_DIM = set()
+
+
+def _head_dim_ok(d: int) -> bool:
+    """The attention-side kernels are written for 128-wide heads (every Qwen3 / Llama-3 size). Other widths — the tiny
+    presets used in tests, vision towers — run on the PyTorch restatement; said once per width."""
+    if d == 128:
+        return True
+    if d not in _WARNED_HEAD_DIM:
+        _WARNED_HEAD_DIM.add(d)
+        import logging
+        logging.getLogger('twinkle_b200').warning(f'head_dim {d}: attention, q/k-norm + RoPE and paged decode run on PyTorch ops (the sm_100a kernels are for head_dim 128)')
+    return False
+
+
 def qkv_norm_rope(qkv: torch.Tensor, q_weight, k_weight, cos, sin, hq: int, hkv: int, d: int, eps: float = 1e-6):
     """Split fused qkv, apply q/k RMSNorm (if weights given) and RoPE."""
-    if _cuda(qkv) and qkv.dtype == torch.bfloat16 and q_weight is not None:
+    if _cuda(qkv) and qkv.dtype == torch.bfloat16 and q_weight is not None and _head_dim_ok(d):
         return _QKNormRope.apply(qkv, q_weight, k_weight, cos, sin, hq, hkv, d, eps)
     T = qkv.shape[0]
     q, k, v = qkv.split([hq * d, hkv * d, hkv * d], dim=-1)
@@ -324,13 +339,13 @@ def flash_attn_varlen(q, k, v, cu_seqlens, max_seqlen: int, causal: bool = True,
     sequence are a (longer) range of their own; the causal diagonal is aligned bottom-right."""
     scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
     if cu_seqlens_k is not None or return_lse:
-        if _cuda(q) and q.dtype == torch.bfloat16:
+        if _cuda(q) and q.dtype == torch.bfloat16 and _head_dim_ok(q.shape[-1]):
             out, lse = _FlashAttnVarlen.apply(q.contiguous(), k.contiguous(), v.contiguous(), cu_seqlens.to(torch.int32), int(max_seqlen), causal,
                                               scale, None if cu_seqlens_k is None else cu_seqlens_k.to(torch.int32), int(max_seqlen_k))
         else:
             out, lse = ref.attention_varlen(q, k, v, cu_seqlens, causal, scale, True, cu_seqlens_k)
         return (out, lse) if return_lse else out
-    if _cuda(q) and q.dtype == torch.bfloat16:
+    if _cuda(q) and q.dtype == torch.bfloat16 and _head_dim_ok(q.shape[-1]):
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         cu = cu_seqlens.to(torch.int32)
         st = AttentionStash.current
@@ -348,7 +363,7 @@ def flash_attn_varlen(q, k, v, cu_seqlens, max_seqlen: int, causal: bool = True,
 
 def paged_attention_decode(q, k_cache, v_cache, block_tables, seq_lens, scale: Optional[float] = None):
     scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
-    if _cuda(q) and q.dtype == torch.bfloat16:
+    if _cuda(q) and q.dtype == torch.bfloat16 and _head_dim_ok(q.shape[-1]):
         return ext().paged_attn_decode(q.contiguous(), k_cache, v_cache, block_tables.to(torch.int32),
                                        seq_lens.to(torch.int32), scale)
     return ref.paged_attention_decode(q, k_cache, v_cache, block_tables, seq_lens, scale)
