@@ -443,3 +443,39 @@ def test_context_parallel_split_of_image_batches_matches_one_process():
     for c in run_ranks(_vl_curve, 2, 2, 2, 'tiny-vl', True):     # sp argument 2: both ranks report the same data group's numbers
         for a, b in zip(single, c):
             assert abs(a - b) < 3e-4, (single, c)
+
+
+def test_images_through_the_http_server_native_backend(tmp_path, monkeypatch):
+    """Train-as-a-service with pictures: the client twin sends chat messages whose image parts travel as PNG data URLs, the
+    server's model app (native backend, vision-language preset) encodes them and trains a LoRA adapter; the sampler app
+    answers an image prompt."""
+    monkeypatch.setenv('TWINKLE_DEFAULT_SAVE_DIR', str(tmp_path / 'ckpt'))
+    from twinkle_b200.client import MultiLoraTransformersModel, TorchSampler, TwinkleClient
+    from twinkle_b200.server import ServerLauncher
+    name = 'tiny-vl'
+    server = ServerLauncher({'persistence': {'mode': 'memory'}, 'applications': [
+        {'name': 'gateway', 'route_prefix': '/', 'import_path': 'server', 'args': {'supported_models': [name]}},
+        {'name': 'model', 'route_prefix': f'/model/{name}', 'import_path': 'model', 'args': {'model_id': name, 'backend': 'transformers', 'max_loras': 2}},
+        {'name': 'sampler', 'route_prefix': f'/sampler/{name}', 'import_path': 'sampler', 'args': {'model_id': name, 'sampler_type': 'torch'}}]})
+    client = TwinkleClient(app=server.root, token='demo', heartbeat_interval=5.0)
+    try:
+        g = torch.Generator().manual_seed(0)
+        batch = [{'messages': [{'role': 'user', 'content': [{'type': 'image', 'image': (torch.rand(3, 56, 84, generator=g) * 255).round()},
+                                                            {'type': 'text', 'text': 'what is it?'}]}, {'role': 'assistant', 'content': 'a boat'}]},
+                 {'messages': [{'role': 'user', 'content': 'and in words?'}, {'role': 'assistant', 'content': 'a small boat'}]}]
+        model = MultiLoraTransformersModel(name, client=client)
+        model.add_adapter_to_model('run', {'r': 4, 'lora_alpha': 8, 'target_modules': 'all-linear'})
+        model.set_template('Qwen2VLTemplate', adapter_name='run', vision_config=VC | {'hidden_size': 256}, max_length=4096)
+        model.set_optimizer('AdamW', lr=1e-2, adapter_name='run')
+        losses = []
+        for _ in range(3):
+            losses.append(float(model.forward_backward(inputs=batch, adapter_name='run')['loss']))
+            model.clip_grad_and_step(max_grad_norm=1.0, adapter_name='run')
+        assert losses[-1] < losses[0]
+        sampler = TorchSampler(name, client=client)
+        sampler.set_template('Qwen2VLTemplate', vision_config=VC | {'hidden_size': 256}, max_length=4096)
+        res = sampler.sample([{'messages': batch[0]['messages'][:1]}], {'max_tokens': 3})
+        seq = res[0]['sequences'][0]
+        assert len(seq['tokens']) <= 3 and len(seq['new_input_feature']['input_ids']) > 24 // 4
+    finally:
+        client.close()
