@@ -479,3 +479,23 @@ def test_images_through_the_http_server_native_backend(tmp_path, monkeypatch):
         assert len(seq['tokens']) <= 3 and len(seq['new_input_feature']['input_ids']) > 24 // 4
     finally:
         client.close()
+
+
+def test_video_time_positions_follow_real_time_for_qwen2_5_vl():
+    ids = [1] + [8] * 12 + [2]                                   # a video of 3 temporal patches on a merged 2 × 2 grid
+    plain = rope_index(ids, [(3, 4, 4)], 9, video_token_id=8)
+    assert plain[0, 1:13].tolist() == [1] * 4 + [2] * 4 + [3] * 4 and plain[:, -1].tolist() == [4, 4, 4]
+    timed = rope_index(ids, [(3, 4, 4)], 9, video_token_id=8, time_steps=[2.0])      # e.g. 2 frames per patch at 2 fps × 2 tokens per second
+    assert timed[0, 1:13].tolist() == [1] * 4 + [3] * 4 + [5] * 4 and timed[1:, 1:13].tolist() == plain[1:, 1:13].tolist()
+    assert timed[:, -1].tolist() == [6, 6, 6]                     # text resumes after the last time position
+    from twinkle_b200.template import template_mapping
+    frames = [torch.rand(3, 56, 56) * 255 for _ in range(4)]
+    msg = lambda **kw: {'messages': [{'role': 'user', 'content': [dict(type='video', video=frames, **kw), {'type': 'text', 'text': 'go'}]}]}  # noqa: E731
+    t25 = template_mapping['Qwen2VLTemplate'](model_id=None, vision_config=VC25, max_length=8192)
+    a, b = t25.encode(msg()), t25.encode(msg(fps=1.0))
+    ta, tb = a['mrope_position_ids'][0], b['mrope_position_ids'][0]
+    vid = torch.tensor(a['input_ids']) == t25.video_token_id
+    ua, ub = ta[vid].unique().tolist(), tb[vid].unique().tolist()
+    assert len(ua) == len(ub) == 2 and ua[1] - ua[0] == 1 and ub[1] - ub[0] == 4      # 2 frames per patch ÷ 1 fps × 2 tokens per second
+    t2 = template_mapping['Qwen2VLTemplate'](model_id=None, vision_config=VC, max_length=8192)
+    assert torch.equal(t2.encode(msg(fps=1.0))['mrope_position_ids'], t2.encode(msg())['mrope_position_ids'])   # Qwen2-VL counts patches

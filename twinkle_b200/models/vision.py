@@ -32,7 +32,8 @@ class VisionConfig:
     temporal_patch_size: int = 2
     in_channels: int = 3
     # Qwen2.5-VL: RMSNorm + gated SiLU MLP (``intermediate_size``), attention inside ``window_size``-pixel windows except in
-    # the blocks listed in ``fullatt_block_indexes``
+    # the blocks listed in ``fullatt_block_indexes``; ``tokens_per_second`` scales video time positions
+    tokens_per_second: float = 2.0
     arch: str = 'qwen2_vl'
     intermediate_size: int = 0
     window_size: int = 112
@@ -54,7 +55,8 @@ class VisionConfig:
         elif 'fullatt_block_indexes' in d:
             d['fullatt_block_indexes'] = tuple(d['fullatt_block_indexes'] or ())
         keys = ('depth', 'embed_dim', 'hidden_size', 'num_heads', 'mlp_ratio', 'patch_size', 'spatial_merge_size', 'temporal_patch_size', 'in_channels',
-                'arch', 'intermediate_size', 'window_size', 'fullatt_block_indexes', 'num_position_embeddings', 'deepstack_visual_indexes')
+                'arch', 'intermediate_size', 'window_size', 'fullatt_block_indexes', 'num_position_embeddings', 'deepstack_visual_indexes',
+                'tokens_per_second')
         return cls(**{k: d[k] for k in keys if k in d})
 
     def to_hf(self) -> Dict[str, Any]:
@@ -67,7 +69,7 @@ class VisionConfig:
         if self.arch == 'qwen2_5_vl':
             return {'model_type': 'qwen2_5_vl', **base, 'hidden_size': self.embed_dim, 'out_hidden_size': self.hidden_size,
                     'intermediate_size': self.intermediate_size, 'window_size': self.window_size,
-                    'fullatt_block_indexes': list(self.fullatt_block_indexes), 'hidden_act': 'silu'}
+                    'fullatt_block_indexes': list(self.fullatt_block_indexes), 'hidden_act': 'silu', 'tokens_per_second': self.tokens_per_second}
         return {'model_type': 'qwen2_vl', **base, 'embed_dim': self.embed_dim, 'hidden_size': self.hidden_size, 'mlp_ratio': self.mlp_ratio,
                 'hidden_act': 'quick_gelu'}
 
@@ -316,10 +318,12 @@ def mrope_tables(position_ids: torch.Tensor, head_dim: int, theta: float, sectio
 
 
 def rope_index(input_ids: Sequence[int], grids: Sequence[Sequence[int]], image_token_id: int, merge: int = 2,
-               video_token_id: Optional[int] = None) -> torch.Tensor:
+               video_token_id: Optional[int] = None, time_steps: Optional[Sequence[float]] = None) -> torch.Tensor:
     """Positions ``[3, L]`` of one sequence whose images appear as runs of ``image_token_id`` (``t·h·w / merge²`` tokens
     per image, in the order of ``grids``). Text advances all three components together; an image keeps time fixed and
-    spreads height and width over its merged grid; the text after it continues from the largest position used + 1."""
+    spreads height and width over its merged grid; the text after it continues from the largest position used + 1.
+    ``time_steps[g]`` (Qwen2.5-VL videos: seconds per temporal patch × the tower's ``tokens_per_second``) stretches the
+    time axis of entry ``g`` so that positions follow real time; 1 (the default, and always for images) counts patches."""
     ids = list(int(t) for t in input_ids)
     out = torch.zeros(3, len(ids), dtype=torch.long)
     nxt, i, g = 0, 0, 0
@@ -332,11 +336,12 @@ def rope_index(input_ids: Sequence[int], grids: Sequence[Sequence[int]], image_t
             n = t * gh * gw
             if ids[i:i + n] != [ids[i]] * n:
                 raise ValueError(f'image {g - 1}: expected a run of {n} placeholder tokens at position {i}')
-            tt = torch.arange(t).view(-1, 1, 1).expand(t, gh, gw).flatten()
+            step = float(time_steps[g - 1]) if time_steps is not None and time_steps[g - 1] is not None else 1.0
+            tt = (torch.arange(t) * step).long().view(-1, 1, 1).expand(t, gh, gw).flatten()
             hh = torch.arange(gh).view(1, -1, 1).expand(t, gh, gw).flatten()
             ww = torch.arange(gw).view(1, 1, -1).expand(t, gh, gw).flatten()
             out[:, i:i + n] = torch.stack([tt, hh, ww]) + nxt
-            nxt += max(t, gh, gw)
+            nxt += max(int(tt.max()) + 1, gh, gw)
             i += n
         else:
             out[:, i] = nxt

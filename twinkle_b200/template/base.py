@@ -391,7 +391,7 @@ class Qwen2VLTemplate(Template):
                         sources.append(src.get('url') if isinstance(src, dict) else src)
                         text += self.IMAGE_MARK
                     elif part.get('type') == 'video':      # a list of frames (decoding video files is left to the caller)
-                        sources.append(('video', list(part['video'])))
+                        sources.append(('video', list(part['video']), part.get('fps')))   # fps: sampled frames per second, if known
                         text += self.VIDEO_MARK
                     else:
                         text += part.get('text', '')
@@ -409,7 +409,11 @@ class Qwen2VLTemplate(Template):
             n_before = sum(str(m.get('content', '')).count(self.IMAGE_MARK) for m in traj['messages'][:traj['messages'].index(first)])
             first['content'] = self.IMAGE_MARK * len(loose) + str(first.get('content') or '')
             sources[n_before:n_before] = loose
-        self._vision = [preprocess_video(src[1], self.vision_config) if isinstance(src, tuple) and len(src) == 2 and src[0] == 'video'
+        vc = self.vision_config
+        # Qwen2.5-VL lays video frames out in real time: one temporal patch spans temporal_patch_size / fps seconds
+        self._time_steps = [(vc.temporal_patch_size / float(src[2]) * vc.tokens_per_second if vc.arch == 'qwen2_5_vl' and isinstance(src, tuple)
+                             and len(src) == 3 and src[0] == 'video' and src[2] else None) for src in sources]
+        self._vision = [preprocess_video(src[1], self.vision_config) if isinstance(src, tuple) and len(src) == 3 and src[0] == 'video'
                         else preprocess_image(src, self.vision_config, self.min_pixels, self.max_pixels) for src in sources]
         return traj
 
@@ -441,7 +445,8 @@ class Qwen2VLTemplate(Template):
         f['placeholder_ids'] = [self.image_token_id, self.video_token_id]                   # type: ignore[typeddict-unknown-key]
         f['image_grid_thw'] = [list(g) for g in grids]                                      # type: ignore[typeddict-unknown-key]
         f['mrope_position_ids'] = rope_index(f['input_ids'], grids, self.image_token_id,   # type: ignore[typeddict-unknown-key]
-                                             self.vision_config.spatial_merge_size, video_token_id=self.video_token_id)
+                                             self.vision_config.spatial_merge_size, video_token_id=self.video_token_id,
+                                             time_steps=getattr(self, '_time_steps', None))
         return feats
 
 
