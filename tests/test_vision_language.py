@@ -499,3 +499,26 @@ def test_video_time_positions_follow_real_time_for_qwen2_5_vl():
     assert len(ua) == len(ub) == 2 and ua[1] - ua[0] == 1 and ub[1] - ub[0] == 4      # 2 frames per patch ÷ 1 fps × 2 tokens per second
     t2 = template_mapping['Qwen2VLTemplate'](model_id=None, vision_config=VC, max_length=8192)
     assert torch.equal(t2.encode(msg(fps=1.0))['mrope_position_ids'], t2.encode(msg())['mrope_position_ids'])   # Qwen2-VL counts patches
+
+
+def test_dataset_encode_and_dataloader_carry_images():
+    """The data-layer route of the multimodal cookbook: rows with image parts → ``Dataset.set_template`` + ``encode`` →
+    ``DataLoader`` batches of features (with patches) → ``forward_backward``."""
+    from twinkle_b200.dataloader import DataLoader
+    from twinkle_b200.dataset import Dataset, DatasetMeta
+    from twinkle_b200.model import TransformersModel
+    g = torch.Generator().manual_seed(0)
+    rows = [{'messages': [{'role': 'user', 'content': [{'type': 'image', 'image': torch.rand(3, 56, 56, generator=g) * 255}, {'type': 'text', 'text': f'q{i}'}]},
+                          {'role': 'assistant', 'content': f'answer {i}'}]} for i in range(4)]
+    m = TransformersModel(model_id='tiny-vl', seed=0)
+    ds = Dataset(DatasetMeta(data=rows))
+    ds.set_template('Qwen2VLTemplate', vision_config=m.config.vision, max_length=4096)
+    ds.encode()
+    assert {'pixel_values', 'image_grid_thw', 'mrope_position_ids', 'input_ids', 'labels'} <= set(ds[0]) and ds[0]['pixel_values'].shape == (16, 1176)
+    m.set_optimizer('AdamW', lr=1e-2)
+    losses = []
+    for _ in range(2):
+        for batch in DataLoader(ds, batch_size=2, shuffle=False):
+            losses.append(float(m.forward_backward(inputs=batch)['loss']))
+            m.clip_grad_and_step(max_grad_norm=1.0)
+    assert len(losses) == 4 and losses[2] < losses[0] and losses[3] < losses[1]       # second pass over the same batches is cheaper
