@@ -522,3 +522,19 @@ def test_dataset_encode_and_dataloader_carry_images():
             losses.append(float(m.forward_backward(inputs=batch)['loss']))
             m.clip_grad_and_step(max_grad_norm=1.0)
     assert len(losses) == 4 and losses[2] < losses[0] and losses[3] < losses[1]       # second pass over the same batches is cheaper
+
+
+def test_packed_documents_with_images_train_like_separate_ones():
+    from twinkle_b200.dataset.packing import concat_features
+    from twinkle_b200.model import TransformersModel
+    m = TransformersModel(model_id='tiny-vl', seed=0)
+    m.set_template('Qwen2VLTemplate', vision_config=m.config.vision, max_length=4096)
+    tpl = m._group(None).template
+    feats = tpl.batch_encode(_vl_trajs() + [{'messages': [{'role': 'user', 'content': 'text only'}, {'role': 'assistant', 'content': 'fine'}]}])
+    packed = concat_features(feats)
+    assert packed['pixel_values'].shape[0] == sum(f['pixel_values'].shape[0] for f in feats[:2]) and len(packed['image_grid_thw']) == 2
+    assert packed['mrope_position_ids'].shape == (3, len(packed['input_ids'])) and packed['position_ids'].count(0) == 3
+    a, b = m.forward_only(inputs=feats), m.forward_only(inputs=[packed])
+    la = torch.cat([torch.as_tensor(x).float().reshape(-1)[:len(f['input_ids'])] for x, f in zip(a['logps'], feats)])
+    lb = torch.as_tensor(b['logps']).float().reshape(-1)[:la.numel()]
+    assert torch.allclose(la, lb, atol=1e-5)                 # same log-probs token for token: no attention across documents, same positions

@@ -41,7 +41,18 @@ def concat_features(rows: Sequence[Dict[str, Any]]) -> Dict[str, Any]:
         ids += list(r['input_ids'])
         labels += list(r.get('labels', [-100] * n))
         pos += list(range(n))
-    return {'input_ids': ids, 'labels': labels, 'position_ids': pos, 'attention_mask': [1] * len(ids), 'length': len(ids)}
+    out = {'input_ids': ids, 'labels': labels, 'position_ids': pos, 'attention_mask': [1] * len(ids), 'length': len(ids)}
+    if any(r.get('pixel_values') is not None for r in rows):
+        # documents with images: patches and grids in document order; every document keeps its own (time, height, width)
+        # positions (they restart per document like the plain index), text-only documents count up in all three alike
+        import torch
+        with_img = [r for r in rows if r.get('pixel_values') is not None]
+        out['pixel_values'] = torch.cat([torch.as_tensor(r['pixel_values']) for r in with_img], 0)
+        out['image_grid_thw'] = [list(map(int, g)) for r in with_img for g in r['image_grid_thw']]
+        out['mrope_position_ids'] = torch.cat([torch.as_tensor(r['mrope_position_ids']).long() if r.get('mrope_position_ids') is not None
+                                               else torch.arange(len(r['input_ids'])).expand(3, -1) for r in rows], 1)
+        out['placeholder_ids'] = sorted({int(t) for r in with_img for t in (r.get('placeholder_ids') or ())})
+    return out
 
 
 @remote_class(execute='first')
