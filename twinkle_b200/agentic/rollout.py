@@ -68,6 +68,14 @@ def extend_with_bridge(template, feature: Dict[str, Any], messages: List[Message
     if 'completion_mask' in feature:
         out['completion_mask'] = list(feature['completion_mask']) + [0] * len(bridge)
     out['length'] = len(out['input_ids'])
+    if feature.get('mrope_position_ids') is not None:  # vision-language state: the appended text continues all three position rows
+        import torch
+        m = torch.as_tensor(feature['mrope_position_ids']).long()
+        nxt = int(m.max()) + 1 if m.numel() else 0
+        out['mrope_position_ids'] = torch.cat([m, torch.arange(nxt, nxt + len(bridge)).expand(3, -1)], 1)
+    for k in ('position_ids', 'attention_mask'):
+        if k in out:
+            out[k] = list(range(out['length'])) if k == 'position_ids' else [1] * out['length']
     return out
 
 

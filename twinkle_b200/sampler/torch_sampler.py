@@ -152,11 +152,6 @@ class TorchSampler(Sampler, CheckpointEngineMixin):
         for f, r in zip(feats, responses):
             for s in r.sequences:
                 s.new_input_feature = Template.concat_input_feature(f, s.tokens)
-                if f.get('pixel_values') is not None:  # the images stay with the feature; sampled tokens continue the positions
-                    m = torch.as_tensor(f['mrope_position_ids']).long()
-                    nxt = int(m.max()) + 1
-                    s.new_input_feature.update(pixel_values=f['pixel_values'], image_grid_thw=f['image_grid_thw'],
-                                               mrope_position_ids=torch.cat([m, torch.arange(nxt, nxt + len(s.tokens)).expand(3, -1)], 1))
                 if s.routed_experts is not None:
                     s.new_input_feature['routed_experts'] = s.routed_experts
                 if self.template is not None:

@@ -303,7 +303,16 @@ class Template:
         for t in range(len(p) - 1, len(ids) - 1):
             labels[t] = ids[t + 1]
         n = len(ids)
-        return {'input_ids': ids, 'labels': labels, 'attention_mask': [1] * n, 'position_ids': list(range(n)), 'length': n}
+        out = {'input_ids': ids, 'labels': labels, 'attention_mask': [1] * n, 'position_ids': list(range(n)), 'length': n}
+        if prompt.get('pixel_values') is not None:  # images stay with the feature; sampled text continues all three position rows
+            import torch
+            m = torch.as_tensor(prompt['mrope_position_ids']).long()
+            nxt = int(m.max()) + 1 if m.numel() else 0
+            out.update(pixel_values=prompt['pixel_values'], image_grid_thw=prompt['image_grid_thw'],
+                       mrope_position_ids=torch.cat([m, torch.arange(nxt, nxt + len(new)).expand(3, -1)], 1))
+            if prompt.get('placeholder_ids') is not None:
+                out['placeholder_ids'] = prompt['placeholder_ids']
+        return out
 
     # ------------------------------------------------------------ tool calls
     def _tool_formats(self):
