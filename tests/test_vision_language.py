@@ -538,3 +538,38 @@ def test_packed_documents_with_images_train_like_separate_ones():
     la = torch.cat([torch.as_tensor(x).float().reshape(-1)[:len(f['input_ids'])] for x, f in zip(a['logps'], feats)])
     lb = torch.as_tensor(b['logps']).float().reshape(-1)[:la.numel()]
     assert torch.allclose(la, lb, atol=1e-5)                 # same log-probs token for token: no attention across documents, same positions
+
+
+def test_tinker_datums_with_image_tensors(tmp_path, monkeypatch):
+    """The Tinker-style route for pictures: the client preprocesses, puts one placeholder per merged patch in the tokens and
+    sends ``pixel_values`` / ``image_grid_thw`` in ``loss_fn_inputs``; the server rebuilds the positions and trains."""
+    monkeypatch.setenv('TWINKLE_DEFAULT_SAVE_DIR', str(tmp_path / 'ckpt'))
+    monkeypatch.setenv('TWINKLE_POLL_INTERVAL', '0.02')
+    from twinkle_b200.client import TinkerClient
+    from twinkle_b200.models.config import preset
+    from twinkle_b200.server import ServerLauncher
+    from twinkle_b200.server.backends import datum_to_input_feature
+    cfg = preset('tiny-vl')
+    pix, grid = preprocess_image(torch.rand(3, 56, 84, generator=torch.Generator().manual_seed(0)) * 255, VisionConfig.from_hf(cfg.vision))
+    n_pad = grid[0] * grid[1] * grid[2] // 4
+    tokens = [40, 41, cfg.vision_start_token_id] + [cfg.image_token_id] * n_pad + [cfg.vision_end_token_id, 42, 43, 44, 45]
+    datum = {'model_input': {'chunks': [{'type': 'encoded_text', 'tokens': tokens}]},
+             'loss_fn_inputs': {'target_tokens': {'data': tokens[1:] + [0], 'dtype': 'int64', 'shape': [len(tokens)]},
+                                'weights': {'data': [0.0] * (len(tokens) - 4) + [1.0, 1.0, 1.0, 0.0], 'dtype': 'float32', 'shape': [len(tokens)]},
+                                'pixel_values': {'data': pix.flatten().tolist(), 'dtype': 'float32', 'shape': list(pix.shape)},
+                                'image_grid_thw': {'data': list(grid), 'dtype': 'int64', 'shape': [1, 3]}}}
+    f = datum_to_input_feature(datum, cfg)
+    assert f['pixel_values'].shape == pix.shape and f['image_grid_thw'] == [list(grid)] and f['mrope_position_ids'].shape == (3, len(tokens))
+    with pytest.raises(ValueError):
+        datum_to_input_feature(datum, preset('tiny-dense'))
+    server = ServerLauncher({'persistence': {'mode': 'memory'}, 'applications': [
+        {'name': 'gateway', 'route_prefix': '/', 'import_path': 'server', 'args': {'supported_models': ['tiny-vl']}},
+        {'name': 'model', 'route_prefix': '/model/tiny-vl', 'import_path': 'model', 'args': {'model_id': 'tiny-vl', 'backend': 'transformers', 'max_loras': 2}}]})
+    trainer = TinkerClient(app=server.root, token='demo').create_lora_training_client('tiny-vl', rank=4)
+    nll = []
+    for _ in range(3):
+        out = trainer.forward_backward([datum]).result()
+        trainer.optim_step({'learning_rate': 1e-2}).result()
+        lp = out['loss_fn_outputs'][0]['logprobs']['data']
+        nll.append(-sum(lp[-4:-1]))
+    assert nll[-1] < nll[0]

@@ -39,7 +39,18 @@ def from_tensor_data(td: Any) -> List[Any]:
     return list(td)
 
 
-def datum_to_input_feature(datum: Dict[str, Any]) -> Dict[str, Any]:
+def _tensor_of(td: Any):
+    """A ``TensorData`` record (flat ``data`` + ``shape``) as a torch tensor."""
+    import torch
+    t = torch.tensor(from_tensor_data(td), dtype=torch.int64 if isinstance(td, dict) and str(td.get('dtype', '')).startswith('int') else torch.float32)
+    shape = td.get('shape') if isinstance(td, dict) else None
+    return t.view(*shape) if shape else t
+
+
+def datum_to_input_feature(datum: Dict[str, Any], model_config: Any = None) -> Dict[str, Any]:
+    """Tinker datum → input feature. Vision-language clients send preprocessed ``pixel_values`` and ``image_grid_thw`` in
+    ``loss_fn_inputs`` (the tokens already hold one placeholder per merged patch); with the model's config at hand the
+    three-row positions are rebuilt here (reference ``server/common/datum.py:11-60``)."""
     mi = datum.get('model_input') or {}
     if 'chunks' in mi:
         ids = [t for c in mi['chunks'] for t in c.get('tokens', [])]
@@ -59,6 +70,18 @@ def datum_to_input_feature(datum: Dict[str, Any]) -> Dict[str, Any]:
     for src, dst in (('logprobs', 'old_logps'), ('advantages', 'advantages'), ('ref_logps', 'ref_logps')):
         if lf.get(src) is not None:
             feat[dst] = [float(x) for x in from_tensor_data(lf[src])]
+    if lf.get('pixel_values') is not None and lf.get('image_grid_thw') is not None:
+        feat['pixel_values'] = _tensor_of(lf['pixel_values'])
+        grid = _tensor_of(lf['image_grid_thw']).long().view(-1, 3)
+        feat['image_grid_thw'] = grid.tolist()
+        image_id = getattr(model_config, 'image_token_id', None)
+        if image_id is None:
+            raise ValueError('this datum carries images but the model behind the endpoint is not a vision-language model')
+        from ...models.vision import rope_index
+        vision = getattr(model_config, 'vision', None) or {}
+        feat['mrope_position_ids'] = rope_index(feat['input_ids'], feat['image_grid_thw'], image_id, int(vision.get('spatial_merge_size', 2)),
+                                                video_token_id=getattr(model_config, 'video_token_id', None))
+        feat['placeholder_ids'] = [t for t in (image_id, getattr(model_config, 'video_token_id', None)) if t is not None]
     return feat
 
 

@@ -36,7 +36,7 @@ class NativeModelBackend:
 
     def tinker_forward_backward(self, datums: List[Dict[str, Any]], adapter_name: str, loss_fn: str = 'cross_entropy', backward: bool = True,
                                 loss_fn_config: Optional[Dict[str, Any]] = None) -> Dict[str, Any]:
-        feats = [datum_to_input_feature(d) for d in datums]
+        feats = [datum_to_input_feature(d, getattr(self.model, 'config', None)) for d in datums]
         self.model.check_length(feats)
         loss = choose_loss(loss_fn, feats, loss_fn_config)
         self.model.set_loss(loss, adapter_name=adapter_name)
