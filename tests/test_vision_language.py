@@ -573,3 +573,21 @@ def test_tinker_datums_with_image_tensors(tmp_path, monkeypatch):
         lp = out['loss_fn_outputs'][0]['logprobs']['data']
         nll.append(-sum(lp[-4:-1]))
     assert nll[-1] < nll[0]
+
+
+@pytest.mark.parametrize('which', ['freeze_vision', 'freeze_llm'])
+def test_freezing_one_side_of_a_vision_language_model(which):
+    from twinkle_b200.model import TransformersModel
+    m = TransformersModel(model_id='tiny-vl', seed=0, **{which: True})
+    m.set_template('Qwen2VLTemplate', vision_config=m.config.vision, max_length=4096)
+    m.set_optimizer('AdamW', lr=1e-2)
+    tower0 = m.model.visual.merger.mlp[2].weight.detach().clone()
+    llm0 = m.model.layers[0].mlp.down_proj.weight.detach().clone()
+    trajs = _vl_trajs()
+    losses = []
+    for _ in range(3):
+        losses.append(float(m.forward_backward(inputs=trajs)['loss']))
+        m.clip_grad_and_step(max_grad_norm=1.0)
+    tower_moved = not torch.equal(tower0, m.model.visual.merger.mlp[2].weight)
+    llm_moved = not torch.equal(llm0, m.model.layers[0].mlp.down_proj.weight)
+    assert (tower_moved, llm_moved) == ((False, True) if which == 'freeze_vision' else (True, False)) and losses[-1] < losses[0]

@@ -125,6 +125,14 @@ class TransformersModel(TwinkleModel, CheckpointEngineMixin):
                                                init=load_dir is None)
         if load_dir is not None:
             self._load_hf_weights(load_dir)
+        # vision-language models: ``freeze_vision=True`` keeps the tower as it is in a full-parameter run (it is frozen
+        # anyway under LoRA); ``freeze_llm=True`` trains the tower and its mergers only (connector alignment)
+        if kwargs.get('freeze_vision') and getattr(self.model, 'visual', None) is not None:
+            self.model.visual.requires_grad_(False)
+        if kwargs.get('freeze_llm'):
+            for n, p in self.model.named_parameters():
+                if not n.startswith('visual.'):
+                    p.requires_grad_(False)
         self.multi_lora: Optional[MultiLora] = None
         self._pool_cfg = (max_loras, max_r)
         self.engine: Optional[FSDPEngine] = None
