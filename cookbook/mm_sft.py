@@ -32,12 +32,13 @@ def main(argv=None):
     ap.add_argument('--lr', type=float, default=3e-3)
     ap.add_argument('--lora-rank', type=int, default=0, help='0 = train everything (tower included); > 0 = LoRA on the language model')
     ap.add_argument('--fsdp', type=int, default=1)
+    ap.add_argument('--freeze-vision', action='store_true', help='full run with the tower kept fixed')
     ap.add_argument('--out', default=None)
     a = ap.parse_args(argv)
     from twinkle_b200.model import LoraConfig, TransformersModel
     from twinkle_b200.utils.device_mesh import DeviceMesh
     mesh = DeviceMesh.from_sizes(fsdp_size=a.fsdp, dp_size=None) if a.fsdp > 1 else DeviceMesh.from_sizes(dp_size=1)
-    model = TransformersModel(model_id=a.model, device_mesh=mesh, seed=0)
+    model = TransformersModel(model_id=a.model, device_mesh=mesh, seed=0, freeze_vision=a.freeze_vision)
     name = None
     if a.lora_rank > 0:
         name = 'mm'
