@@ -47,6 +47,8 @@ def parse():
     ap.add_argument('--comm', default='auto', choices=['auto', 'nccl', 'symm'])
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--sp', type=int, default=None, help='Ulysses degree (default min(4, gpus))')
+    ap.add_argument('--ref-micro', type=int, default=1, help='reference arm: sequences per forward_backward call')
+    ap.add_argument('--cpu-debug', action='store_true', help='reference arm: run on CPU/gloo (debug only, result invalid)')
     ap.add_argument('--config', default='dense', choices=['dense', 'moe'],
                     help="dense: Qwen3-8B full-parameter SFT (headline); moe: Qwen3-30B-A3B LoRA r=16 SFT with expert parallel = gpus")
     return ap.parse_args()
@@ -122,20 +124,16 @@ def synthetic_sequences(n_seqs: int, seq_len: int, vocab: int, seed: int, pack: 
 
 
 def run_reference(args):
-    out = {'impl': 'reference'}
+    """The unmodified reference through its own public API (``baseline/reference_arm.py``); nothing of this
+    repository's package is imported on that path."""
+    sys.path.insert(0, os.path.join(ROOT, 'baseline'))
     try:
-        sys.path.insert(0, os.path.join(ROOT, 'baseline', '_ref'))
-        import twinkle  # noqa: F401
-        from twinkle.model import TransformersModel  # noqa: F401  (imports peft unconditionally)
+        import reference_arm
     except Exception as e:
-        out['unavailable'] = (f'reference model layer cannot be imported offline: {type(e).__name__}: {e} '
-                              '(twinkle.model imports peft unconditionally; peft is neither installed nor in the wheelhouse)')
         if int(os.environ.get('RANK', '0')) == 0:
-            print(json.dumps(out))
+            print(json.dumps({'impl': 'reference', 'unavailable': f'baseline/reference_arm.py cannot be imported: {type(e).__name__}: {e}'}))
         return
-    out['unavailable'] = 'reference import succeeded but no offline weights/config path is wired for it in this build'
-    if int(os.environ.get('RANK', '0')) == 0:
-        print(json.dumps(out))
+    reference_arm.run(args, synthetic_sequences, ClockSampler)
 
 
 def main():
