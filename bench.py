@@ -236,6 +236,14 @@ def main():
         e2e = {'value': tokens_per_step_global * args.steps / (ms_e / 1e3), 'unit': 'tokens/s', 'h2d_bytes_per_step': h2d_bytes,
                'd2h_bytes_per_step': 8, 'ms_per_step': ms_e / args.steps, 'loss': loss}
     clocks = sampler.stop() if rank == 0 else None
+    # one more step with the phase clock on (outside both timed regions): device time per communication phase
+    from twinkle_b200.utils.profiling import PHASES
+    PHASES.start()
+    step(dev_feats, False)
+    phases = PHASES.stop()
+    plane = model.data_plane()
+    if world > 1 and args.comm == 'auto' and any(v in ('nccl', 'gloo') for v in plane.values()):
+        raise SystemExit(f'--comm auto fell back to library collectives on {plane}; the peer-memory data plane did not come up')
     err = ops.ext().read_and_clear_error()
     if rank == 0:
         value = tokens_per_step_global * args.steps / (ms / 1e3)
@@ -249,9 +257,10 @@ def main():
                        'global_batch': args.seqs_per_gpu * world, 'seq_len': args.seq_len,
                        'parallelism': f'fsdp{world}' + (f'+ulysses{sp}' if sp > 1 else '') + (f'+ep{world}' if moe else ''), 'optimizer': 'AdamW fp32 master',
                        'recompute': 'per-layer', 'micro_batches_per_step': n_local_seqs // micro, 'l2': 'inputs per step exceed the 126 MB L2 (65536 tokens x 4096 hidden bf16 = 512 MiB per activation)',
-                       'comm': args.comm},
+                       'comm': args.comm, 'data_plane': plane},
             'clocks': clocks, 'e2e': e2e, 'gpu_launches': int(launches), 'peak_mem_gib': round(peak, 1),
             'model_flops_per_token': cfg.flops_per_token(avg_context=0.0), 'kernel_error_word': err,
+            'phases_ms_per_step': phases,
         }
         print(json.dumps(line))
     if world > 1:

@@ -145,7 +145,7 @@ class MultiLoraTransformersModel:
     _POSITIONAL = {'set_loss': ('loss_cls', ), 'set_optimizer': ('optimizer_cls', ), 'set_lr_scheduler': ('scheduler_cls', ),
                    'set_template': ('template_cls', ), 'set_processor': ('processor_cls', ), 'add_metric': ('metric_cls', 'is_training'),
                    'apply_patch': ('patch_cls', ), 'calculate_metric': ('is_training', ), 'save': ('name', 'output_dir'),
-                   'load': ('name', 'output_dir'), 'resume_from_checkpoint': ('checkpoint_dir', )}
+                   'load': ('name', 'output_dir'), 'resume_from_checkpoint': ('name', )}
 
     def __getattr__(self, name: str):
         if name.startswith('_'):

@@ -211,6 +211,32 @@ class TransformersModel(TwinkleModel, CheckpointEngineMixin):
         if self.multi_lora is not None:
             self.multi_lora.sync_initial(comm)
 
+    def data_plane(self) -> Dict[str, str]:
+        """Which transport each sharded path resolved to at run time: ``'symm'`` (peer-memory kernels over NVLink),
+        ``'nccl'`` / ``'gloo'`` (library collectives) or ``'local'`` (one rank).  ``comm_backend='auto'`` falls back
+        to the library path when the peer-memory communicator cannot be built; this makes that visible."""
+        self._lazy_wrap_model()
+
+        def kind(c) -> str:
+            if c is None or getattr(c, 'world_size', 1) <= 1:
+                return 'local'
+            if hasattr(c, 'peer_ptrs'):
+                return 'symm'
+            return 'nccl' if getattr(c, 'cuda', False) else 'gloo'
+
+        out = {'fsdp': kind(self.engine.comm)}
+        for layer in self.model.layers:
+            strat = getattr(getattr(layer, 'self_attn', None), 'attn_parallel', None)
+            if strat is not None and hasattr(strat, 'comm'):
+                out['ulysses'] = kind(strat.comm)
+                break
+        for layer in self.model.layers:
+            ep = getattr(getattr(layer, 'mlp', None), 'moe_parallel', None)
+            if ep is not None:
+                out['expert'] = 'symm' if type(ep).__name__ == 'SymmExpertParallel' else kind(getattr(ep, 'comm', None))
+                break
+        return out
+
     def _group(self, adapter_name: Optional[str]) -> OptimizerGroup:
         name = adapter_name or _DEFAULT
         if name not in self.optimizer_groups:
@@ -518,11 +544,14 @@ class TransformersModel(TwinkleModel, CheckpointEngineMixin):
         for g in groups:
             hi = lo + len(g)
             mb = proc._pack(g)
-            out = self._forward_micro(mb, og, True, temperature, False, disable_lora)
-            self._forward_ran = True
-            loss, nt = self._loss_micro(og, out, self._slice_kwargs(kwargs, lo, hi, n))
-            loss.backward()
-            self.engine.end_backward()
+            from ..utils.profiling import PHASES
+            with PHASES('forward'):
+                out = self._forward_micro(mb, og, True, temperature, False, disable_lora)
+                self._forward_ran = True
+                loss, nt = self._loss_micro(og, out, self._slice_kwargs(kwargs, lo, hi, n))
+            with PHASES('backward'):
+                loss.backward()
+                self.engine.end_backward()
             self._backward_ran = True
             og.train_status.loss_value = None
             total_loss += float(loss.detach())
@@ -686,9 +715,12 @@ class TransformersModel(TwinkleModel, CheckpointEngineMixin):
 
     @remote_function(collect='first')
     def clip_grad_and_step(self, max_grad_norm: float = 1.0, norm_type=2, adapter_name: Optional[str] = None, **kwargs):
-        norm = self.clip_grad_norm(max_grad_norm, norm_type, adapter_name=adapter_name, **kwargs)
-        self.step(adapter_name=adapter_name, **kwargs)
-        self.zero_grad(adapter_name=adapter_name, **kwargs)
+        from ..utils.profiling import PHASES
+        with PHASES('grad_norm'):
+            norm = self.clip_grad_norm(max_grad_norm, norm_type, adapter_name=adapter_name, **kwargs)
+        with PHASES('optimizer'):
+            self.step(adapter_name=adapter_name, **kwargs)
+            self.zero_grad(adapter_name=adapter_name, **kwargs)
         self.lr_step(adapter_name=adapter_name, **kwargs)
         og = self._group(adapter_name)
         for m in og.train_status.metrics:
@@ -955,7 +987,7 @@ class TransformersModel(TwinkleModel, CheckpointEngineMixin):
         rank = Platform.get_rank()
         f = os.path.join(path, f'optimizer_rank{rank}.pt' if Platform.get_world_size() > 1 else 'optimizer.pt')
         if os.path.isfile(f):
-            state = torch.load(f, map_location='cpu', weights_only=False)
+            state = torch.load(f, map_location='cpu', weights_only=True)
             og.optim_steps = state.get('optim_steps', 0)
             if og.optimizer is None:
                 self.set_optimizer('AdamW', adapter_name=og.adapter_name or None)
@@ -974,10 +1006,10 @@ class TransformersModel(TwinkleModel, CheckpointEngineMixin):
                     by_name[k].load_optimizer_state(v)
         sched = os.path.join(path, 'scheduler.pt')
         if os.path.isfile(sched) and og.lr_scheduler is not None:
-            og.lr_scheduler.load_state_dict(torch.load(sched, map_location='cpu', weights_only=False))
+            og.lr_scheduler.load_state_dict(torch.load(sched, map_location='cpu', weights_only=True))
         rng = os.path.join(path, f'rng_state_rank{rank}.pt' if Platform.get_world_size() > 1 else 'rng_state.pt')
         if os.path.isfile(rng):
-            Platform.set_rng_state(torch.load(rng, map_location='cpu', weights_only=False))
+            Platform.set_rng_state(torch.load(rng, map_location='cpu', weights_only=True))
         ts = os.path.join(path, 'trainer_state.json')
         info = {'cur_step': 0, 'consumed_train_samples': 0, 'gradient_accumulation_steps': og.gradient_accumulation_steps}
         if os.path.isfile(ts):

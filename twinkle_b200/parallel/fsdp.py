@@ -40,6 +40,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from .. import ops
+from ..utils.profiling import PHASES
 from .comm import Communicator
 
 
@@ -125,7 +126,8 @@ class FlatBucket:
 
     def wait_unshard(self) -> None:
         if self._gather_event is not None:
-            self.comm.wait(self._gather_event)
+            with PHASES('fsdp_gather_wait'):
+                self.comm.wait(self._gather_event)
             self._gather_event = None
         self._bind(self.full)
 

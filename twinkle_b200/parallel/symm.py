@@ -24,6 +24,7 @@ import torch
 import torch.distributed as dist
 
 from .. import ops
+from ..utils.profiling import PHASES
 from .comm import Communicator
 
 
@@ -119,9 +120,10 @@ class SymmCommunicator(Communicator):
         ptrs = self.peer_ptrs(full_grad)
         if ptrs is None or grad_shard.dtype != torch.float32 or full_grad.dtype != torch.bfloat16:
             return super().reduce_scatter_accumulate(grad_shard, full_grad, scale)
-        # every rank must have finished writing this layer's gradients before anyone reads them
-        self.barrier_kernel()
-        self.ext.peer_reduce_scatter_acc(grad_shard, ptrs, self.rank, scale, None, 4 * self.copy_blocks)
+        with PHASES('fsdp_reduce_scatter'):
+            # every rank must have finished writing this layer's gradients before anyone reads them
+            self.barrier_kernel()
+            self.ext.peer_reduce_scatter_acc(grad_shard, ptrs, self.rank, scale, None, 4 * self.copy_blocks)
 
     def step_barrier(self) -> None:
         """Fences the optimizer step: peers finished reading my shards / gradient buffers."""
@@ -131,9 +133,10 @@ class SymmCommunicator(Communicator):
     def ulysses_exchange(self, x: torch.Tensor, out: torch.Tensor, seq_to_head: bool, heads_total: int) -> torch.Tensor:
         ptrs = self.peer_ptrs(out)
         assert ptrs is not None, 'destination must be symmetric memory'
-        self.barrier_kernel()  # destination buffers are free (previous consumers done)
-        self.ext.ulysses_exchange(x, ptrs, self.rank, seq_to_head, heads_total)
-        self.barrier_kernel()  # all pushes landed
+        with PHASES('ulysses_exchange'):
+            self.barrier_kernel()  # destination buffers are free (previous consumers done)
+            self.ext.ulysses_exchange(x, ptrs, self.rank, seq_to_head, heads_total)
+            self.barrier_kernel()  # all pushes landed
         return out
 
     def head_scatter_gemm(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows_per_rank: int, q_blocks: int, kv_blocks: int) -> torch.Tensor:

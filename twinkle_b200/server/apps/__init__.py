@@ -122,6 +122,8 @@ class ModelApp(TaskQueueMixin):
 
     def create_adapter(self, token: str, session_id: Optional[str], lora_config: Optional[Dict[str, Any]], model_id: Optional[str] = None) -> str:
         model_id = model_id or uuid.uuid4().hex
+        if model_id in self.adapters:  # a client-chosen id must not take over another tenant's (or its own live) entry
+            raise HTTPException(409, f'model {model_id!r} already exists on this replica')
         adapter = f'{session_id or "nosession"}-{model_id[:12]}'
         cfg = dict(self.args.adapter_config or {})
         cfg.update({k: v for k, v in (lora_config or {}).items() if v is not None})
@@ -175,6 +177,8 @@ class ModelApp(TaskQueueMixin):
             b = await body_of(request)
             token = request.state.token
             mid = b.get('model_id') or uuid.uuid4().hex
+            if mid in self.adapters:
+                raise HTTPException(409, f'model {mid!r} already exists on this replica')
 
             def work():
                 self.create_adapter(token, b.get('session_id'), b.get('lora_config'), mid)
@@ -188,6 +192,7 @@ class ModelApp(TaskQueueMixin):
             a = self.adapters.get(b.get('model_id', ''))
             if a is None:
                 raise HTTPException(404, 'unknown model')
+            self.adapter_of(b['model_id'], request.state.token)
             return {'model_id': b['model_id'], 'model_data': {'model_name': self.args.model_id, 'arch': 'decoder'}, 'is_lora': True,
                     'lora_rank': a['lora_config'].get('r')}
 
@@ -273,7 +278,7 @@ class ModelApp(TaskQueueMixin):
             return {'status': 'ok', 'adapter_name': mid}
 
         generic = ['forward', 'forward_only', 'calculate_loss', 'backward', 'forward_backward', 'clip_grad_norm', 'step', 'zero_grad', 'lr_step',
-                   'clip_grad_and_step', 'get_train_configs', 'set_loss', 'set_optimizer', 'set_lr_scheduler', 'resume_from_checkpoint',
+                   'clip_grad_and_step', 'get_train_configs', 'set_loss', 'set_optimizer', 'set_lr_scheduler',
                    'apply_patch', 'add_metric', 'set_template', 'set_processor', 'calculate_metric', 'get_state_dict']
 
         def _generic(method: str):
@@ -282,7 +287,10 @@ class ModelApp(TaskQueueMixin):
                 token = request.state.token
                 validate_request(method, b, aliases={'model_id': 'adapter_name'})  # a missing field is a 400 naming it
                 name = b.pop('adapter_name', None) or b.pop('model_id', None)
-                adapter = self.adapter_of(name, token) if name in self.adapters else name
+                b.pop('model_id', None)
+                # every named adapter resolves through the ownership table: an unknown name is a 404, another token's a
+                # 403 — the backend's internal adapter names are never accepted from a client
+                adapter = self.adapter_of(name, token) if name else None
                 kwargs = {k: v for k, v in b.items() if k not in ('session_id', )}
                 n_inputs = len(kwargs.get('inputs') or []) if isinstance(kwargs.get('inputs'), list) else None
                 res = await self.schedule_task_and_wait(lambda: self.backend.generic_call(method, adapter_name=adapter, **kwargs), token=token,
@@ -316,6 +324,23 @@ class ModelApp(TaskQueueMixin):
             path = self.checkpoints.resolve_load_path(token, b.get('path') or b.get('name', ''))
             await self.schedule_task_and_wait(lambda: self.backend.load(None, path, adapter_name=adapter), token=token, model_id=name)
             return {'status': 'ok'}
+
+        @app.post('/twinkle/resume_from_checkpoint')
+        async def tw_resume(request: Request):
+            """Weights + optimizer / scheduler / RNG / progress counters of a checkpoint this token saved.  The body names
+            it as ``name`` (the field of the request record) or ``checkpoint_dir``; a ``twinkle://`` path returned by
+            ``save`` resolves to the token's own directory (reference ``server/model/twinkle_handlers.py`` resume route)."""
+            b = await body_of(request)
+            token, name = request.state.token, b.get('adapter_name') or b.get('model_id')
+            ck = b.get('name') or b.get('checkpoint_dir')
+            if not ck:
+                raise HTTPException(400, "resume_from_checkpoint needs 'name' (or 'checkpoint_dir')")
+            adapter = self.adapter_of(name, token) if name else None
+            path = self.checkpoints.resolve_load_path(token, ck)
+            res = await self.schedule_task_and_wait(lambda: self.backend.generic_call('resume_from_checkpoint', checkpoint_dir=path, adapter_name=adapter,
+                                                                                      resume_only_model=bool(b.get('resume_only_model', False))),
+                                                    token=token, model_id=name or '')
+            return {'status': 'ok', 'result': res}
 
         @app.post('/twinkle/upload_to_hub')
         async def tw_upload(request: Request):

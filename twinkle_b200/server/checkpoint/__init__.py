@@ -127,16 +127,32 @@ class CheckpointManager:
             return True
         return False
 
+    def _allowed_roots(self, token: str) -> List[str]:
+        roots = [os.path.join(self.root, token_dir(token))]
+        roots += [r for r in os.environ.get('TWINKLE_ALLOWED_LOAD_DIRS', '').split(os.pathsep) if r]
+        return [os.path.realpath(r) for r in roots]
+
     def resolve_load_path(self, token: str, path: str) -> str:
-        """URI → local directory (must belong to the token); plain existing directories pass through."""
+        """URI → local directory of the token's own run.  A plain directory is accepted only when, after resolving
+        symlinks, it lies under the token's own root or under a root the operator listed in
+        ``TWINKLE_ALLOWED_LOAD_DIRS``: a served instance must not read (and un-pickle optimizer state from) arbitrary
+        server-local paths a client names (the reference takes ``twinkle://`` URIs checked per token, or hub ids).
+        Anything that is not a local path is treated as a hub id."""
+        if not path:
+            raise ValueError('empty checkpoint path')
         if path.startswith(SCHEMES):
             run, kind, name = parse_uri(path)
             d = self.path_for(token, run, name, kind)
             if not os.path.isdir(d):
                 raise FileNotFoundError(f'checkpoint {path} not found for this token')
             return d
-        if os.path.isdir(path):
-            return path
+        if os.path.exists(path) or os.path.isabs(path) or path.startswith('.'):
+            real = os.path.realpath(path)
+            if not os.path.isdir(real):
+                raise FileNotFoundError(f'checkpoint directory {path!r} not found')
+            if not any(real == r or real.startswith(r + os.sep) for r in self._allowed_roots(token)):
+                raise PermissionError(f'{path!r} is outside this token\'s checkpoint root; use the twinkle:// path returned by save')
+            return real
         from ...hub import HubOperation
         return HubOperation.download_model(path)
 

@@ -77,3 +77,57 @@ def nvtx_range(name: str):
 
 def tokens_per_second(num_tokens: float, ms: float) -> float:
     return num_tokens / (ms / 1e3) if ms > 0 else 0.0
+
+
+class PhaseClock:
+    """Process-wide accumulator of device time per named phase of a training step.
+
+    The engines bracket their communication phases (``with PHASES('ulysses_exchange'): …``); each bracket records a
+    pair of CUDA events on the current stream, so the figure is the time the *launching stream* spent between the two
+    points — for a phase that only waits on a side stream (``fsdp_gather_wait``) that is exactly the stall.  Off by
+    default (one attribute test per bracket); ``bench.py`` switches it on for one extra step after its timed region
+    and prints the totals, so the limiter of a multi-GPU step is named by a number.
+    """
+
+    def __init__(self):
+        self.enabled = False
+        self._pairs: Dict[str, List] = {}
+        self._counts: Dict[str, int] = {}
+
+    @contextmanager
+    def __call__(self, name: str):
+        if not self.enabled or not torch.cuda.is_available():
+            yield
+            return
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        try:
+            yield
+        finally:
+            b.record()
+            self._pairs.setdefault(name, []).append((a, b))
+
+    def start(self) -> None:
+        self._pairs, self.enabled = {}, True
+
+    def stop(self, group=None) -> Dict[str, Dict[str, float]]:
+        """Totals per phase since ``start``: ``{name: {'ms': total, 'n': brackets}}``, max over the ranks of ``group``."""
+        self.enabled = False
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        names = sorted(self._pairs)
+        ms = [sum(a.elapsed_time(b) for a, b in self._pairs[n]) for n in names]
+        cnt = [len(self._pairs[n]) for n in names]
+        self._pairs = {}
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+            # every rank brackets the same phases in the same order, so the name lists agree
+            dev = 'cuda' if dist.get_backend(group) == 'nccl' else 'cpu'
+            t = torch.tensor(ms, dtype=torch.float64, device=dev)
+            if t.numel():
+                dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+            ms = t.tolist()
+        return {n: {'ms': round(m, 3), 'n': c} for n, m, c in zip(names, ms, cnt)}
+
+
+PHASES = PhaseClock()
