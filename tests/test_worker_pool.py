@@ -78,3 +78,31 @@ def test_tcp_pool_needs_a_shared_secret(monkeypatch):
             m.workers('far')
     finally:
         m.shutdown()
+
+
+def test_placement_counts_devices_not_workers():
+    """``ranks`` counts devices: 8 ranks with 2 devices per worker are 4 workers, each owning two consecutive devices by
+    *position* in the group; a group whose ranks do not start at 0 still gets its own devices."""
+    from twinkle_b200.infra.worker_pool import WorkerPoolManager
+    groups = [DeviceGroup(name='wide', ranks=8, device_type='cuda', gpus_per_worker=2),
+              DeviceGroup(name='tail', ranks=[4, 5, 6, 7], device_type='cuda', visible_devices=['4', '5', '6', '7']),
+              DeviceGroup(name='plain', ranks=[6, 7], device_type='cuda'),
+              DeviceGroup(name='host', ranks=2, device_type='cpu')]
+    mgr = WorkerPoolManager(groups)
+    wide = mgr.placement('wide')
+    assert len(wide) == 4 == groups[0].num_workers()
+    assert [e['RANK'] for e in wide] == ['0', '1', '2', '3'] and all(e['WORLD_SIZE'] == '4' for e in wide)
+    assert [e['TWINKLE_WORKER_DEVICES'] for e in wide] == ['0,1', '2,3', '4,5', '6,7']
+    assert [e['TWINKLE_GLOBAL_RANK'] for e in wide] == ['0', '2', '4', '6']
+    # a worker sees its own devices first (LOCAL_RANK 0), then the rest of its group
+    assert wide[1]['CUDA_VISIBLE_DEVICES'].split(',')[:2] == ['2', '3'] and sorted(wide[1]['CUDA_VISIBLE_DEVICES'].split(',')) == [str(i) for i in range(8)]
+    assert all(e['LOCAL_RANK'] == '0' for e in wide)
+    tail = mgr.placement('tail')
+    assert [e['TWINKLE_WORKER_DEVICES'] for e in tail] == ['4', '5', '6', '7']
+    assert [e['TWINKLE_GLOBAL_RANK'] for e in tail] == ['4', '5', '6', '7'] and all(e['WORLD_SIZE'] == '4' for e in tail)
+    plain = mgr.placement('plain')
+    assert [e['TWINKLE_WORKER_DEVICES'] for e in plain] == ['6', '7']          # never devices 0 and 1 of another group
+    host = mgr.placement('host')
+    assert all(e['CUDA_VISIBLE_DEVICES'] == '' for e in host) and [e['LOCAL_RANK'] for e in host] == ['0', '1']
+    with pytest.raises(ValueError):
+        WorkerPoolManager([DeviceGroup(name='odd', ranks=3, device_type='cuda', gpus_per_worker=2)]).placement('odd')

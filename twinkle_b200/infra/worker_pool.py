@@ -184,12 +184,22 @@ class WorkerPoolManager:
         self._lock = threading.Lock()
 
     def placement(self, group: str) -> List[Dict[str, str]]:
-        """Environment of every rank of ``group`` (also what a test can inspect without starting processes)."""
+        """Environment of every worker of ``group`` (also what a test can inspect without starting processes).
+
+        ``ranks`` counts devices, as in the reference (``infra/_ray/resource_manager.py:186-201``): a group of
+        ``len(ranks)`` devices with ``gpus_per_worker = g`` runs ``len(ranks) // g`` workers, and worker ``i`` owns the
+        ``g`` consecutive devices at *position* ``i·g`` of the group — ``visible_devices`` when given, else the rank
+        numbers themselves (on one node a rank is a device index).  The worker sees its own devices first (so
+        ``LOCAL_RANK`` is 0) followed by the other devices of the group, which keeps CUDA IPC / peer mappings between
+        the group's workers possible."""
         g = self.groups[group]
         ranks = g.rank_list()
         port = str(find_free_port())
         envs = []
         per = max(int(g.gpus_per_worker or 1), 1)
+        if len(ranks) % per != 0:
+            raise ValueError(f"group '{group}': {len(ranks)} ranks do not divide into workers of {per} devices")
+        n = len(ranks) // per
         vd = getattr(g, 'visible_devices', None)
         if vd is None:
             visible = None
@@ -197,13 +207,17 @@ class WorkerPoolManager:
             visible = [str(x) for x in vd]
         else:
             visible = [x for x in str(vd).split(',') if x != '']
-        for i, r in enumerate(ranks):
-            env = {'RANK': str(i), 'LOCAL_RANK': str(i), 'WORLD_SIZE': str(len(ranks)), 'LOCAL_WORLD_SIZE': str(len(ranks)),
-                   'MASTER_ADDR': self.master_addr, 'MASTER_PORT': port, 'TWINKLE_GROUP': group, 'TWINKLE_GLOBAL_RANK': str(r),
+        if visible is not None and len(visible) < len(ranks):
+            raise ValueError(f"group '{group}': {len(ranks)} ranks but only {len(visible)} visible devices")
+        for i in range(n):
+            env = {'RANK': str(i), 'LOCAL_RANK': str(i), 'WORLD_SIZE': str(n), 'LOCAL_WORLD_SIZE': str(n),
+                   'MASTER_ADDR': self.master_addr, 'MASTER_PORT': port, 'TWINKLE_GROUP': group, 'TWINKLE_GLOBAL_RANK': str(ranks[i * per]),
                    'TWINKLE_SEED': str(self.seed)}
-            if g.device_type in ('cuda', 'gpu') and (visible is not None or per > 1):
-                pool = visible or [str(x) for x in range(max(ranks) * per + per)]
-                env['CUDA_VISIBLE_DEVICES'] = ','.join(pool[r * per:(r + 1) * per])
+            if g.device_type in ('cuda', 'gpu'):
+                pool = visible[:len(ranks)] if visible is not None else [str(r) for r in ranks]
+                own = pool[i * per:(i + 1) * per]
+                env['CUDA_VISIBLE_DEVICES'] = ','.join(own + [d for d in pool if d not in own])
+                env['TWINKLE_WORKER_DEVICES'] = ','.join(own)
                 env['LOCAL_RANK'] = '0'
             elif g.device_type == 'cpu':
                 env['CUDA_VISIBLE_DEVICES'] = ''
