@@ -49,8 +49,11 @@ def parse():
     ap.add_argument('--sp', type=int, default=None, help='Ulysses degree (default min(4, gpus))')
     ap.add_argument('--ref-micro', type=int, default=1, help='reference arm: sequences per forward_backward call')
     ap.add_argument('--cpu-debug', action='store_true', help='reference arm: run on CPU/gloo (debug only, result invalid)')
-    ap.add_argument('--config', default='dense', choices=['dense', 'moe'],
-                    help="dense: Qwen3-8B full-parameter SFT (headline); moe: Qwen3-30B-A3B LoRA r=16 SFT with expert parallel = gpus")
+    ap.add_argument('--config', default='both', choices=['both', 'dense', 'moe'],
+                    help="dense: Qwen3-8B full-parameter SFT; moe: Qwen3-30B-A3B LoRA r=16 SFT with expert parallel = gpus; "
+                         "both (default): the two halves of the headline metric one after the other, each in a process of its own, "
+                         "printed as one line (the dense fields at top level, the mixture-of-experts result under 'moe')")
+    ap.add_argument('--moe-steps', type=int, default=10, help="cap on timed steps of the 'moe' half when --config both")
     return ap.parse_args()
 
 
@@ -136,8 +139,59 @@ def run_reference(args):
     reference_arm.run(args, synthetic_sequences, ClockSampler)
 
 
+def run_both(args):
+    """Runs ``--config dense`` and then ``--config moe`` as child processes of this rank (the parent never touches the
+    GPU, so each half starts from an empty device and a failure of the second cannot lose the first) and prints the
+    dense line with the mixture-of-experts result under ``'moe'``.  Children rendezvous on ports next to the launcher's;
+    ``TORCHELASTIC_USE_AGENT_STORE`` is cleared so that their rank 0 hosts the store."""
+    rank = int(os.environ.get('RANK', '0'))
+    base_port = int(os.environ.get('MASTER_PORT', '29500'))
+    results = {}
+    for k, (cfg, steps, warmup) in enumerate((('dense', args.steps, args.warmup),
+                                              ('moe', min(args.steps, args.moe_steps), min(args.warmup, 3)))):
+        env = dict(os.environ)
+        env['MASTER_PORT'] = str(base_port + 17 + k)
+        env['MASTER_ADDR'] = env.get('MASTER_ADDR', '127.0.0.1')
+        env.pop('TORCHELASTIC_USE_AGENT_STORE', None)
+        cmd = [sys.executable, os.path.abspath(__file__), '--config', cfg, '--gpus', str(args.gpus), '--steps', str(steps), '--warmup', str(max(warmup, 3)),
+               '--comm', args.comm, '--impl', args.impl, '--ref-micro', str(args.ref_micro)]
+        if args.no_e2e:
+            cmd.append('--no-e2e')
+        if args.layers is not None:
+            cmd += ['--layers', str(args.layers)]
+        if args.sp is not None and cfg == 'dense':
+            cmd += ['--sp', str(args.sp)]
+        try:
+            r = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, text=True, timeout=2400 if cfg == 'dense' else 1200)
+            line = None
+            for ln in r.stdout.splitlines():
+                if ln.startswith('{'):
+                    try:
+                        line = json.loads(ln)
+                    except ValueError:
+                        pass
+            if line is None:
+                line = {'unavailable': f'{cfg} half exited with code {r.returncode} and printed no result line'}
+        except subprocess.TimeoutExpired:
+            line = {'unavailable': f'{cfg} half did not finish within its time limit'}
+        results[cfg] = line
+    if rank != 0:
+        return
+    out = dict(results['dense'])
+    moe = results['moe']
+    out['moe'] = moe if 'unavailable' in moe else {k: moe.get(k) for k in ('metric', 'value', 'unit', 'steps', 'warmup', 'ms_per_step', 'config', 'e2e',
+                                                                            'gpu_launches', 'peak_mem_gib', 'clocks', 'phases_ms_per_step',
+                                                                            'kernel_error_word', 'impl') if k in moe}
+    if 'gpu_launches' in out and isinstance(moe.get('gpu_launches'), int):
+        out['gpu_launches_by_config'] = {'dense': out['gpu_launches'], 'moe': moe['gpu_launches']}
+    print(json.dumps(out), flush=True)
+
+
 def main():
     args = parse()
+    if args.config == 'both':
+        run_both(args)
+        return
     if args.impl == 'reference':
         run_reference(args)
         return

@@ -253,6 +253,9 @@ def main():
             sys.exit(1)
 
     only = os.environ.get('TK_MGPU_ONLY', '')
+    stop_after_kernels = only == 'peer'
+    if only in ('peer', 'fsdp'):
+        only = ''
     if only in ('ep', 'megatron', 'tp_fused', 'ulysses_fused'):
         {'ep': ep_checks, 'megatron': megatron_checks, 'tp_fused': tp_fused_checks, 'ulysses_fused': ulysses_fused_checks}[only](rank, world, dev, report)
         report('error_word_end', E.read_and_clear_error() == 0)
@@ -292,8 +295,26 @@ def main():
     c = U._head_to_seq(a, plain)
     d = U._head_to_seq(a, sc)
     torch.cuda.synchronize()
-    report('ulysses_push', bool(torch.equal(a, b) and torch.equal(c, d) and torch.equal(c, x)))
+    report('ulysses_exchange', bool(torch.equal(a, b) and torch.equal(c, d) and torch.equal(c, x)))
+    # receive-side exchange of several tensors at once (q, k, v with different head counts), both directions, repeated so
+    # that both staging buffers of each pair are used and reused, and its first-generation (push) twin
+    for it in range(3):
+        xs = [torch.randn(t, h, D, device=dev).bfloat16() for h in (8 * world, 2 * world, 2 * world)]
+        want = [U._seq_to_head(z, plain) for z in xs]
+        got = sc.exchange_heads(xs, True)
+        back = sc.exchange_heads(got, False)
+        torch.cuda.synchronize()
+        report(f'ulysses_pull_{it}', all(torch.equal(g_, w_) for g_, w_ in zip(got, want)) and all(torch.equal(b_, z) for b_, z in zip(back, xs)))
+    sc.legacy_kernels = True
+    b2 = U._seq_to_head(x, sc)
+    torch.cuda.synchronize()
+    sc.legacy_kernels = False
+    report('ulysses_push_legacy', bool(torch.equal(a, b2)))
     report('error_word', E.read_and_clear_error() == 0)
+    if stop_after_kernels:
+        dist.barrier()
+        dist.destroy_process_group()
+        return
 
     # ---- 3. training parity: FSDP(+Ulysses) on W GPUs vs the single-GPU curve of the same global batch
     from twinkle_b200.model import TransformersModel
@@ -337,7 +358,6 @@ def main():
         c = curve(mesh, backend, feats)
         diff = max(abs(a - b) for a, b in zip(single, c))
         report(f'ulysses{world}_{backend}_matches_single', diff < 3e-2, single=single, multi=c)
-    ep_checks(rank, world, dev, report)
     report('error_word_end', E.read_and_clear_error() == 0)
     dist.barrier()
     dist.destroy_process_group()

@@ -49,9 +49,23 @@ def is_built() -> bool:
 
 
 def build_extension(verbose: bool = False, jobs: Optional[int] = None) -> str:
-    """Compile each source to an object (in parallel) and link ``_C.so``."""
+    """Compile each source to an object (in parallel) and link ``_C.so``.  Processes that arrive together (the ranks
+    of one job) take a file lock in turn: the first builds, the others find the stamp current and return."""
     if is_built():
         return _SO
+    import fcntl
+    lock = open(os.path.join(_HERE, '.build.lock'), 'w')
+    fcntl.flock(lock, fcntl.LOCK_EX)
+    try:
+        if is_built():
+            return _SO
+        return _build_locked(verbose, jobs)
+    finally:
+        fcntl.flock(lock, fcntl.LOCK_UN)
+        lock.close()
+
+
+def _build_locked(verbose: bool, jobs: Optional[int]) -> str:
     import torch
     from torch.utils import cpp_extension as ce
     from concurrent.futures import ThreadPoolExecutor
@@ -109,11 +123,9 @@ def load_extension():
         if not torch.cuda.is_available() and os.environ.get('TWINKLE_B200_BUILD', '0') != '1' and not os.path.isfile(_SO):
             raise ImportError('twinkle_b200.ops._C is not built (run `python -c "import __graft_entry__ as g; g.build()"`)')
         if not os.path.isfile(_SO) or os.environ.get('TWINKLE_B200_BUILD', '0') == '1' or torch.cuda.is_available():
-            try:
-                build_extension()
-            except Exception:
-                if not os.path.isfile(_SO):
-                    raise
+            # a binary whose stamp does not match the sources is never loaded in place of a failed rebuild: the
+            # numbers and tests of a run must come from the code in the tree
+            build_extension()
     spec = importlib.util.spec_from_file_location('twinkle_b200.ops._C', _SO)
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)  # type: ignore[union-attr]

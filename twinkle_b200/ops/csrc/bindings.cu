@@ -36,6 +36,8 @@ int64_t symm_open(const py::bytes&);
 void symm_close(int64_t);
 void symm_barrier(const std::vector<int64_t>&, int64_t, int64_t, int64_t);
 void peer_all_gather(torch::Tensor, const std::vector<int64_t>&, int64_t, int64_t, int64_t);
+void peer_pull(const std::vector<int64_t>&, const std::vector<int64_t>&, const std::vector<int64_t>&, const std::vector<int64_t>&,
+               const std::vector<int64_t>&, const std::vector<int64_t>&, int64_t);
 void peer_reduce_scatter_acc(torch::Tensor, const std::vector<int64_t>&, int64_t, double, const c10::optional<torch::Tensor>&, int64_t);
 void ulysses_exchange(const torch::Tensor&, const std::vector<int64_t>&, int64_t, bool, int64_t);
 void peer_copy_cast(const torch::Tensor&, const std::vector<int64_t>&, int64_t);
@@ -84,6 +86,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("symm_close", &tk::symm_close);
   m.def("symm_barrier", &tk::symm_barrier, py::arg("flag_ptrs"), py::arg("rank"), py::arg("epoch"), py::arg("timeout_ms") = 3000);
   m.def("peer_all_gather", &tk::peer_all_gather);
+  m.def("peer_pull", &tk::peer_pull, py::arg("src"), py::arg("dst"), py::arg("src_stride"), py::arg("dst_stride"), py::arg("chunk_bytes"),
+        py::arg("rows"), py::arg("blocks_per_job"));
   m.def("peer_reduce_scatter_acc", &tk::peer_reduce_scatter_acc);
   m.def("ulysses_exchange", &tk::ulysses_exchange);
   m.def("peer_copy_cast", &tk::peer_copy_cast);

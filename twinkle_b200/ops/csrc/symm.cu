@@ -5,6 +5,8 @@
 //   symm_barrier                    cross-GPU barrier: every rank writes an epoch into each peer's flag
 //                                   slot (st.release.sys) and waits for all slots (ld.acquire.sys, bounded)
 //   peer_all_gather                 pull: out[k] = peer_k.shard for every k (16-byte peer loads)
+//   peer_pull                       strided pull of rows × chunk bytes per (peer, section) job, 8 loads in flight
+//                                   per thread: Ulysses head↔sequence exchange, parameter all-gather
 //   peer_reduce_scatter_acc         pull: grad_shard += scale · Σ_k peer_k.full[rank slice]  (bf16 → fp32,
 //                                   cast + scale + accumulate fused; optional Σg² partial)
 //   peer_all_to_all_heads           Ulysses head↔sequence exchange: each rank pushes its slices straight
@@ -142,6 +144,89 @@ void peer_all_gather(torch::Tensor out, const std::vector<int64_t>& shard_ptrs, 
   dim3 grid(static_cast<unsigned>(blocks_per_peer), world);
   peer_all_gather_kernel<<<grid, 512, 0, at::cuda::getCurrentCUDAStream()>>>(reinterpret_cast<uint4*>(out.data_ptr()), s, shard_bytes / 16,
                                                                              static_cast<int>(rank), aliased ? 1 : 0);
+  count_launch();
+  TK_CUDA_CHECK(cudaGetLastError());
+}
+
+
+// ------------------------------------------------------------- strided pull
+// The general receive-side copy of this file: a launch carries up to MAX_JOBS jobs, each "rows × chunk bytes from
+// src (row stride src_stride) to dst (row stride dst_stride)".  The source of a job is usually another GPU's
+// symmetric buffer; the destination is always local.  One job per (peer, tensor section) expresses the Ulysses
+// head↔sequence exchange in both directions (a rank pulls exactly the head slice / token chunk it will own) and, with
+// rows = 1, the parameter all-gather.  Every thread keeps UNROLL independent 16-byte loads in flight before it
+// stores, which is what the NVLink round trip needs: with one load per thread in flight the same copy ran several
+// times slower.  No shared memory is used, so the kernel can share SMs with a resident GEMM when it runs on a side
+// stream.
+constexpr int MAX_JOBS = 48;
+struct PullJob {
+  const uint8_t* src;
+  uint8_t* dst;
+  long src_stride, dst_stride;  // bytes between rows
+  int chunk_vecs;               // 16-byte vectors per row
+  int rows;
+};
+struct PullJobs {
+  PullJob j[MAX_JOBS];
+};
+
+__device__ __forceinline__ uint4 ld_global_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+template <int UNROLL>
+__global__ void __launch_bounds__(512) peer_pull_kernel(const __grid_constant__ PullJobs jobs) {
+  const PullJob& job = jobs.j[blockIdx.y];
+  const long nvec = static_cast<long>(job.rows) * job.chunk_vecs;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  const int cv = job.chunk_vecs;
+  for (long base = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; base < nvec; base += stride * UNROLL) {
+    uint4 r[UNROLL];
+    long doff[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long v = base + u * stride;
+      if (v < nvec) {
+        const long row = v / cv;
+        const long c = (v - row * cv) << 4;
+        r[u] = ld_global_v4(job.src + row * job.src_stride + c);
+        doff[u] = row * job.dst_stride + c;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long v = base + u * stride;
+      if (v < nvec) *reinterpret_cast<uint4*>(job.dst + doff[u]) = r[u];
+    }
+  }
+}
+
+// jobs: parallel lists (source address, destination address, source row stride, destination row stride, bytes per
+// row, rows).  Addresses, strides and row sizes must be multiples of 16 bytes.
+void peer_pull(const std::vector<int64_t>& src, const std::vector<int64_t>& dst, const std::vector<int64_t>& src_stride,
+               const std::vector<int64_t>& dst_stride, const std::vector<int64_t>& chunk_bytes, const std::vector<int64_t>& rows,
+               int64_t blocks_per_job) {
+  const size_t n = src.size();
+  TORCH_CHECK(n > 0 && n <= MAX_JOBS, "peer_pull: between 1 and ", MAX_JOBS, " jobs per launch");
+  TORCH_CHECK(dst.size() == n && src_stride.size() == n && dst_stride.size() == n && chunk_bytes.size() == n && rows.size() == n,
+              "peer_pull: job lists differ in length");
+  PullJobs J{};
+  long max_vecs = 0;
+  for (size_t i = 0; i < n; ++i) {
+    TORCH_CHECK(src[i] % 16 == 0 && dst[i] % 16 == 0 && src_stride[i] % 16 == 0 && dst_stride[i] % 16 == 0 && chunk_bytes[i] % 16 == 0,
+                "peer_pull: addresses, strides and row sizes must be multiples of 16 bytes");
+    TORCH_CHECK(chunk_bytes[i] / 16 < (1L << 31) && rows[i] < (1L << 31) && rows[i] >= 0, "peer_pull: job too large");
+    J.j[i] = PullJob{reinterpret_cast<const uint8_t*>(src[i]), reinterpret_cast<uint8_t*>(dst[i]), static_cast<long>(src_stride[i]),
+                     static_cast<long>(dst_stride[i]), static_cast<int>(chunk_bytes[i] / 16), static_cast<int>(rows[i])};
+    max_vecs = std::max<long>(max_vecs, rows[i] * (chunk_bytes[i] / 16));
+  }
+  if (max_vecs == 0) return;
+  constexpr int UNROLL = 8;
+  const long want = (max_vecs + 512L * UNROLL - 1) / (512L * UNROLL);
+  const unsigned bx = static_cast<unsigned>(std::max<long>(1, std::min<long>(want, blocks_per_job)));
+  peer_pull_kernel<UNROLL><<<dim3(bx, static_cast<unsigned>(n)), 512, 0, at::cuda::getCurrentCUDAStream()>>>(J);
   count_launch();
   TK_CUDA_CHECK(cudaGetLastError());
 }

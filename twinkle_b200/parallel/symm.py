@@ -67,6 +67,10 @@ class SymmCommunicator(Communicator):
         self._flags = SymmBuffer(self, 4096)
         self._epoch = 0
         self.copy_blocks = 16  # CTAs per peer stream: enough to fill an NVLink port, few enough to leave SMs to the GEMMs
+        # TWINKLE_SYMM_LEGACY=1 keeps the first-generation kernels (push exchange with two barriers, one load in flight
+        # per thread in the all-gather) for A/B measurements
+        import os
+        self.legacy_kernels = os.environ.get('TWINKLE_SYMM_LEGACY', '0') == '1'
 
     # ----------------------------------------------------------- allocation
     def alloc(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
@@ -110,7 +114,17 @@ class SymmCommunicator(Communicator):
         ev_in = torch.cuda.current_stream().record_event()
         with torch.cuda.stream(self._stream):
             self._stream.wait_event(ev_in)
-            self.ext.peer_all_gather(out, ptrs, nbytes, self.rank, self.copy_blocks)
+            if self.legacy_kernels or nbytes % 16:
+                self.ext.peer_all_gather(out, ptrs, nbytes, self.rank, self.copy_blocks)
+            else:
+                # one job per peer, starting with the next rank so that no GPU's egress serves every reader at once;
+                # the own shard is copied too unless the gathered buffer aliases it
+                base = out.data_ptr()
+                order = [(self.rank + k) % self.world_size for k in range(1, self.world_size + 1)]
+                order = [r for r in order if not (r == self.rank and base + r * nbytes == ptrs[r])]
+                n = len(order)
+                self.ext.peer_pull([ptrs[r] for r in order], [base + r * nbytes for r in order], [nbytes] * n, [nbytes] * n, [nbytes] * n, [1] * n,
+                                   self.copy_blocks)
             done = self._stream.record_event()
         out.record_stream(self._stream)
         return done
@@ -138,6 +152,61 @@ class SymmCommunicator(Communicator):
             self.ext.ulysses_exchange(x, ptrs, self.rank, seq_to_head, heads_total)
             self.barrier_kernel()  # all pushes landed
         return out
+
+    # Receive-side exchange: every rank stages its tensors in symmetric memory, ONE barrier says "staged", then each
+    # rank pulls exactly the slices it will own into ordinary (allocator-owned) memory.  The staging buffers rotate in
+    # pairs: a buffer is rewritten two exchanges of its kind later, and the barrier of the exchange in between is
+    # passed only after every peer has finished pulling from it, so no second barrier is needed.  The results are
+    # plain tensors that autograd may keep for as long as it likes.
+    def _stage(self, x: torch.Tensor, tag: str) -> torch.Tensor:
+        cache = self.__dict__.setdefault('_stage_buffers', {})
+        key = (tuple(x.shape), x.dtype, tag)
+        ent = cache.get(key)
+        if ent is None:
+            ent = {'bufs': [self.alloc(x.numel(), x.dtype).view(x.shape) for _ in range(2)], 'next': 0}
+            cache[key] = ent
+        buf = ent['bufs'][ent['next']]
+        ent['next'] ^= 1
+        buf.copy_(x)
+        return buf
+
+    def exchange_heads(self, xs, seq_to_head: bool):
+        """``seq_to_head``: each ``[t, H, D]`` (this rank's tokens, all heads) → ``[sp·t, H/sp, D]`` (all tokens of the
+        row, this rank's heads).  Otherwise the inverse: ``[sp·t, h, D]`` → ``[t, sp·h, D]``.  All tensors of ``xs`` go
+        through one barrier and one kernel launch."""
+        sp, me = self.world_size, self.rank
+        with PHASES('ulysses_stage'):
+            staged = [self._stage(x if x.is_contiguous() else x.contiguous(), f'x{i}{int(seq_to_head)}') for i, x in enumerate(xs)]
+        with PHASES('ulysses_barrier'):
+            self.barrier_kernel()
+        outs, src, dst, ss, ds, cb, rows = [], [], [], [], [], [], []
+        for x, st in zip(xs, staged):
+            es = x.element_size()
+            ptrs = self.peer_ptrs(st)
+            if seq_to_head:
+                t, H, D = x.shape
+                hl = H // sp
+                chunk = hl * D * es
+                out = torch.empty((sp * t, hl, D), dtype=x.dtype, device=x.device)
+                for k in range(1, sp + 1):
+                    r = (me + k) % sp
+                    src.append(ptrs[r] + me * chunk); ss.append(H * D * es)
+                    dst.append(out.data_ptr() + r * t * chunk); ds.append(chunk)
+                    cb.append(chunk); rows.append(t)
+            else:
+                tt, hl, D = x.shape
+                t = tt // sp
+                chunk = hl * D * es
+                out = torch.empty((t, sp * hl, D), dtype=x.dtype, device=x.device)
+                for k in range(1, sp + 1):
+                    r = (me + k) % sp
+                    src.append(ptrs[r] + me * t * chunk); ss.append(chunk)
+                    dst.append(out.data_ptr() + r * chunk); ds.append(sp * chunk)
+                    cb.append(chunk); rows.append(t)
+            outs.append(out)
+        with PHASES('ulysses_pull'):
+            self.ext.peer_pull(src, dst, ss, ds, cb, rows, max(8, (4 * self.ext.num_sms()) // len(src)))
+        return outs
 
     def head_scatter_gemm(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows_per_rank: int, q_blocks: int, kv_blocks: int) -> torch.Tensor:
         """``x·wᵀ`` with every 128-column block written into the symmetric ``out`` of the rank that owns its heads."""

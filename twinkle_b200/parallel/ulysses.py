@@ -77,6 +77,25 @@ class _HeadGather(torch.autograd.Function):
         return _seq_to_head(g.contiguous(), ctx.comm), None
 
 
+def _pulls(comm, x: torch.Tensor) -> bool:
+    return (hasattr(comm, 'exchange_heads') and not comm.legacy_kernels and x.is_cuda and x.dim() == 3
+            and (x.shape[-1] * x.element_size()) % 16 == 0)
+
+
+class _ExchangeMany(torch.autograd.Function):
+    """Several tensors through ONE exchange (one barrier, one kernel): q, k and v on the way in, their gradients on the
+    way back.  ``seq_to_head`` picks the forward direction; backward runs the inverse."""
+
+    @staticmethod
+    def forward(ctx, comm, seq_to_head: bool, *xs):
+        ctx.comm, ctx.s2h = comm, seq_to_head
+        return tuple(comm.exchange_heads(list(xs), seq_to_head))
+
+    @staticmethod
+    def backward(ctx, *gs):
+        return (None, None) + tuple(ctx.comm.exchange_heads([g.contiguous() for g in gs], not ctx.s2h))
+
+
 def _symm_out(comm, shape, dtype, tag):
     """Destination buffers in symmetric memory, two per (shape, direction) used alternately so a
     consumer of the previous exchange never races with the next push.  The cache lives on the
@@ -190,10 +209,14 @@ class UlyssesAttention:
         if self.kv_rep > 1:
             k = k.repeat_interleave(self.kv_rep, dim=1)
             v = v.repeat_interleave(self.kv_rep, dim=1)
+        if _pulls(self.comm, q) and q.dtype == k.dtype == v.dtype:
+            return _ExchangeMany.apply(self.comm, True, q, k, v)
         return (_HeadScatter.apply(q.contiguous(), self.comm), _HeadScatter.apply(k.contiguous(), self.comm),
                 _HeadScatter.apply(v.contiguous(), self.comm))
 
     def gather_heads(self, o):
+        if _pulls(self.comm, o):
+            return _ExchangeMany.apply(self.comm, False, o)[0]
         return _HeadGather.apply(o.contiguous(), self.comm)
 
     # ---- exchange inside the projection

@@ -111,7 +111,9 @@ class PhaseClock:
         self._pairs, self.enabled = {}, True
 
     def stop(self, group=None) -> Dict[str, Dict[str, float]]:
-        """Totals per phase since ``start``: ``{name: {'ms': total, 'n': brackets}}``, max over the ranks of ``group``."""
+        """Totals per phase since ``start``: ``{name: {'ms': total, 'ms_min': total, 'n': brackets}}`` — ``ms`` is the
+        maximum over the ranks of ``group`` and ``ms_min`` the minimum.  A phase that contains a cross-GPU wait shows the
+        skew between ranks as the gap between the two: the rank that arrives last waits for nobody."""
         self.enabled = False
         if torch.cuda.is_available():
             torch.cuda.synchronize()
@@ -124,10 +126,14 @@ class PhaseClock:
             # every rank brackets the same phases in the same order, so the name lists agree
             dev = 'cuda' if dist.get_backend(group) == 'nccl' else 'cpu'
             t = torch.tensor(ms, dtype=torch.float64, device=dev)
+            lo = t.clone()
             if t.numel():
                 dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
-            ms = t.tolist()
-        return {n: {'ms': round(m, 3), 'n': c} for n, m, c in zip(names, ms, cnt)}
+                dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=group)
+            ms, ms_lo = t.tolist(), lo.tolist()
+        else:
+            ms_lo = ms
+        return {n: {'ms': round(m, 3), 'ms_min': round(l, 3), 'n': c} for n, m, l, c in zip(names, ms, ms_lo, cnt)}
 
 
 PHASES = PhaseClock()
