@@ -96,6 +96,7 @@ class TransformersModel(TwinkleModel, CheckpointEngineMixin):
         self.model_id = model_id
         self.seed = seed
         self.strategy_name = strategy
+        self.fsdp_group_dims = tuple(fsdp_group_dims) if fsdp_group_dims else None
         self.comm_backend = comm_backend
         self.device = torch.device(device) if device is not None else Platform.current_device()
         if self.device.type == 'cuda' and self.device.index is None:
@@ -178,6 +179,25 @@ class TransformersModel(TwinkleModel, CheckpointEngineMixin):
     def sp_size(self) -> int:
         return self.device_mesh.ulysses_size or 1
 
+    def _hybrid_shard_dims(self) -> Optional[Tuple[str, ...]]:
+        """Axes the parameters are sharded over when that is NOT the whole data group.  ``fsdp_group_dims=('fsdp',)``
+        asks for it outright; ``strategy='accelerate'`` on a mesh with both ``dp`` and ``fsdp`` larger than one means
+        the same thing, as in the reference (``strategy/accelerate.py:106-110``: replicate over ``dp``, shard over
+        ``fsdp``); ``native_fsdp`` shards over the flattened mesh (``strategy/native_fsdp.py:445-451``)."""
+        m = self.device_mesh
+        data_dims = [d for d in ('dp', 'fsdp', 'cp') if m.has_dim(d)]
+        dims = tuple(self.fsdp_group_dims) if self.fsdp_group_dims else None
+        if dims is None and self.strategy_name == 'accelerate' and (m.dp_world_size or 1) > 1 and (m.fsdp_world_size or 1) > 1:
+            dims = ('fsdp', )
+        if dims is None or set(dims) >= set(data_dims) or not (dist.is_available() and dist.is_initialized()):
+            return None
+        if (m.ep_size or 1) > 1 or self.sp_size > 1:
+            raise NotImplementedError('hybrid sharding combines with neither expert nor sequence parallelism here; use the flat sharding of native_fsdp')
+        for d in dims:
+            if not m.has_dim(d):
+                raise ValueError(f"fsdp_group_dims names axis '{d}' that the mesh {m.mesh_dim_names} does not have")
+        return dims
+
     def _lazy_wrap_model(self) -> None:
         """First use: LoRA pool (if any) → expert parallel → sequence parallel →
         sharding engine.  Mirrors the order of the reference's
@@ -206,8 +226,24 @@ class TransformersModel(TwinkleModel, CheckpointEngineMixin):
         ignored = None
         if self.device_mesh.ep_size and self.device_mesh.ep_size > 1 and self.config.is_moe:
             ignored = lambda n: '.mlp.experts.' in n  # experts are EP-local, not FSDP-sharded over the dp group
+        replica = None
+        shard_dims = self._hybrid_shard_dims()
+        if shard_dims is not None:
+            # hybrid sharding: shard inside the listed axes, replicate (and all-reduce gradients) over the other data axes
+            other = tuple(d for d in ('dp', 'fsdp', 'cp') if self.device_mesh.has_dim(d) and d not in shard_dims)
+            shard = Communicator(self.device_mesh.get_dim_group(shard_dims), self.device)
+            replica = Communicator(self.device_mesh.get_dim_group(other), self.device)
+            if shard.world_size > 1 and self.comm_backend in ('auto', 'symm') and self.device.type == 'cuda':
+                try:
+                    from ..parallel.symm import SymmCommunicator
+                    shard = SymmCommunicator(shard.group, self.device)
+                except Exception as e:
+                    if self.comm_backend == 'symm':
+                        raise
+                    logger.warning(f'peer-memory communicator unavailable ({e}); using NCCL collectives')
+            comm = shard
         self.engine = FSDPEngine(self.model, comm, self.compute_dtype, self.device, grad_dtype=self.grad_dtype, ignored=ignored,
-                                 keep_attention=self.keep_attention)
+                                 keep_attention=self.keep_attention, replica_comm=replica)
         if self.multi_lora is not None:
             self.multi_lora.sync_initial(comm)
 
@@ -587,6 +623,8 @@ class TransformersModel(TwinkleModel, CheckpointEngineMixin):
         if not og.do_grad_sync(kwargs.get('gradient_accumulation_steps')):
             return og._last_grad_norm or 0.0
         comm = self._dp_comm()
+        if self.engine is not None:
+            self.engine.finish_grads()
         denom = comm.all_reduce_scalar(og.train_status.num_tokens, 'sum')
         denom = denom if denom > 0 else 1.0
         sq = torch.zeros((), dtype=torch.float32, device=self.device)
@@ -603,7 +641,7 @@ class TransformersModel(TwinkleModel, CheckpointEngineMixin):
                         sq = sq + v
         elif self.engine is not None:
             sq_sh = self.engine.grad_norm_sq()
-            comm.all_reduce(sq_sh)
+            self.engine.comm.all_reduce(sq_sh)  # over the shard group: under hybrid sharding the replicas hold equal shards
             sq = sq + sq_sh
             for _, p in self.engine.replicated:
                 if p.requires_grad and p.grad is not None:
@@ -651,6 +689,8 @@ class TransformersModel(TwinkleModel, CheckpointEngineMixin):
                 if 'weight_decay' in optim_params and g['weight_decay'] > 0:
                     g['weight_decay'] = optim_params['weight_decay']
         og.optim_steps += 1
+        if self.engine is not None:
+            self.engine.finish_grads()
         opt._opt_called = True  # the fused update below is this optimizer's step; stock LR schedulers check the flag
         scale = self._pending_scale.pop(og.adapter_name, 1.0)
         fence = getattr(self._dp_comm(), 'step_barrier', None)

@@ -378,10 +378,20 @@ class FSDPEngine:
 
     def __init__(self, model, comm: Communicator, compute_dtype: torch.dtype = torch.bfloat16, device=None,
                  reshard_after_forward: bool = True, grad_dtype: torch.dtype = torch.float32,
-                 ignored: Optional[Callable[[str], bool]] = None, keep_attention: bool = True):
+                 ignored: Optional[Callable[[str], bool]] = None, keep_attention: bool = True,
+                 replica_comm: Optional[Communicator] = None):
         """``keep_attention``: the forward keeps each layer's attention output + log-sum-exp (≈ tokens·Hq·D
-        bf16 per layer) so the recompute in backward skips the attention forward kernel."""
+        bf16 per layer) so the recompute in backward skips the attention forward kernel.
+
+        ``replica_comm`` (hybrid sharding): ``comm`` spans one shard group only (the mesh's ``fsdp`` axis) and
+        ``replica_comm`` the ranks that hold the same shard in the other groups (the ``dp`` axis).  Parameters, master
+        weights and optimizer state are then replicated across shard groups, and the gradient shards are summed over
+        ``replica_comm`` once per optimizer step (reference ``strategy/accelerate.py:106-110``: ``dp_replicate`` ×
+        ``dp_shard``)."""
         self.model, self.comm = model, comm
+        self.replica_comm = replica_comm if (replica_comm is not None and replica_comm.world_size > 1) else None
+        self._grads_pending = False
+        self._replicated_stash: List[Tuple[nn.Parameter, Optional[torch.Tensor]]] = []
         self.keep_attention = keep_attention and torch.device(device or 'cpu').type == 'cuda'
         self.device = device or next(model.parameters()).device
         self.compute_dtype = compute_dtype
@@ -426,6 +436,8 @@ class FSDPEngine:
                             rc.broadcast(p.data, 0)
                     else:
                         comm.broadcast(p.data, 0)
+                        if self.replica_comm is not None:
+                            self.replica_comm.broadcast(p.data, 0)
         if hasattr(comm, 'sync_all'):
             comm.sync_all()  # every rank's shards are initialised before anyone pulls them
         model.layer_runner = self._run_layer
@@ -469,6 +481,15 @@ class FSDPEngine:
         self.root.wait_unshard()
         if need_grad:
             self.root.prepare_grads(self.pool)
+            for p, before in self._replicated_stash:  # a forward whose backward never ran: put its stash back
+                if before is not None:
+                    p.grad = before if p.grad is None else p.grad.add_(before)
+            self._replicated_stash = []
+            if self.comm.world_size > 1 or self.replica_comm is not None:
+                for _, p in self.replicated:
+                    if p.requires_grad:
+                        self._replicated_stash.append((p, p.grad))
+                        p.grad = None
         self._root_live = True
         if self.units:
             self.units[0].unshard_async(self.pool)
@@ -479,16 +500,38 @@ class FSDPEngine:
         for u in self.units:
             u.reshard(self.pool)
         self._root_live = False
-        # replicated trainables: sum over ranks
-        if self.comm.world_size > 1:
-            for _, p in self.replicated:
-                if p.requires_grad and p.grad is not None:
-                    if getattr(p, '_ep_local', False):  # distinct experts per rank: reduce over same-expert replicas only
-                        rc = getattr(p, '_ep_replica_comm', None)
-                        if rc is not None:
-                            rc.all_reduce(p.grad)
-                    else:
-                        self.comm.all_reduce(p.grad)
+        self._grads_pending = True
+        # Replicated trainables (LoRA pools): this backward's gradient is summed over the ranks and then added to what
+        # earlier micro-batches (or other tenants' backward passes) left in ``.grad``.  Summing the accumulated tensor
+        # instead would re-add the earlier contributions once per rank.
+        stash, self._replicated_stash = self._replicated_stash, []
+        for p, before in stash:
+            g = p.grad
+            if g is None:
+                p.grad = before
+                continue
+            if getattr(p, '_ep_local', False):  # distinct experts per rank: reduce over same-expert replicas only
+                rc = getattr(p, '_ep_replica_comm', None)
+                if rc is not None:
+                    rc.all_reduce(g)
+            else:
+                if self.comm.world_size > 1:
+                    self.comm.all_reduce(g)
+                if self.replica_comm is not None:
+                    self.replica_comm.all_reduce(g)
+            if before is not None:
+                g.add_(before)
+
+    def finish_grads(self) -> None:
+        """Hybrid sharding: the gradient shards, accumulated over the micro-batches inside each shard group, are summed
+        over the replica groups once per optimizer step.  Idempotent until the next backward."""
+        if not self._grads_pending:
+            return
+        self._grads_pending = False
+        if self.replica_comm is not None:
+            for b in self.trainable_buckets():
+                if b.grad_shard is not None:
+                    self.replica_comm.all_reduce(b.grad_shard)
 
     def end_forward_only(self) -> None:
         self.root.reshard(self.pool)
@@ -511,6 +554,7 @@ class FSDPEngine:
             b.zero_grad()
         for _, p in self.replicated:
             p.grad = None
+        self._grads_pending = False
 
     def grad_norm_sq(self) -> torch.Tensor:
         """Σ‖g‖² of the sharded gradients (this rank's shards only; caller all-reduces)."""
