@@ -233,30 +233,53 @@ void peer_pull(const std::vector<int64_t>& src, const std::vector<int64_t>& dst,
 
 // ----------------------------------------------------------- reduce-scatter
 // grad_shard[i] += scale · Σ_k full_k[rank·n + i]; reads 8 bf16 per peer per step, accumulates in fp32.
-__global__ void peer_reduce_scatter_kernel(float* __restrict__ grad_shard, PeerPtrs fulls, long shard_numel, int rank, int world,
-                                           float scale, float* __restrict__ sumsq) {
+__global__ void __launch_bounds__(512) peer_reduce_scatter_kernel(float* __restrict__ grad_shard, PeerPtrs fulls, long shard_numel, int rank, int world,
+                                                                  float scale, float* __restrict__ sumsq) {
+  constexpr int U = 4;  // vectors per thread per round: U × world 16-byte peer loads in flight before the first add
   const long nvec = shard_numel >> 3;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
   float local_sq = 0.f;
-  for (long v = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; v < nvec; v += static_cast<long>(gridDim.x) * blockDim.x) {
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (long v0 = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; v0 < nvec; v0 += stride * U) {
+    float acc[U][8];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc[u][q] = 0.f;
     // start with a different peer on every rank so the NVSwitch ports are loaded evenly
     for (int j = 0; j < world; ++j) {
       const int k = (rank + j) % world;
-      const uint4 u = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(fulls.p[k]) + static_cast<long>(rank) * shard_numel)[v];
-      const uint32_t* pu = &u.x;
+      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(fulls.p[k]) + static_cast<long>(rank) * shard_numel);
+      uint4 u4[U];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const float2 f = unpack_bf16(pu[q]);
-        acc[2 * q] += f.x;
-        acc[2 * q + 1] += f.y;
+      for (int u = 0; u < U; ++u) {
+        const long v = v0 + u * stride;
+        if (v < nvec) u4[u] = ld_global_v4(src + v);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long v = v0 + u * stride;
+        if (v < nvec) {
+          const uint32_t* pu = &u4[u].x;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 f = unpack_bf16(pu[q]);
+            acc[u][2 * q] += f.x;
+            acc[u][2 * q + 1] += f.y;
+          }
+        }
       }
     }
-    float4* g = reinterpret_cast<float4*>(grad_shard + v * 8);
-    float4 a = g[0], b = g[1];
-    a.x += acc[0] * scale; a.y += acc[1] * scale; a.z += acc[2] * scale; a.w += acc[3] * scale;
-    b.x += acc[4] * scale; b.y += acc[5] * scale; b.z += acc[6] * scale; b.w += acc[7] * scale;
-    g[0] = a; g[1] = b;
-    if (sumsq) local_sq += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long v = v0 + u * stride;
+      if (v >= nvec) continue;
+      float4* g = reinterpret_cast<float4*>(grad_shard + v * 8);
+      float4 a = g[0], b = g[1];
+      a.x += acc[u][0] * scale; a.y += acc[u][1] * scale; a.z += acc[u][2] * scale; a.w += acc[u][3] * scale;
+      b.x += acc[u][4] * scale; b.y += acc[u][5] * scale; b.z += acc[u][6] * scale; b.w += acc[u][7] * scale;
+      g[0] = a; g[1] = b;
+      if (sumsq) local_sq += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+    }
   }
   if (sumsq) {
     local_sq = warp_sum(local_sq);

@@ -79,6 +79,9 @@ class Communicator:
             dist.reduce_scatter_tensor(tmp, full_grad, op=dist.ReduceOp.SUM, group=self.group)
         grad_shard.add_(tmp.to(grad_shard.dtype), alpha=scale)
 
+    def wait_reduce_scatters(self, all_but: int = 0) -> None:
+        """Library reduce-scatters run on the calling stream: nothing is outstanding."""
+
     # -------------------------------------------------------------- reduce
     def all_reduce(self, t: torch.Tensor, op: str = 'sum') -> torch.Tensor:
         if self.world_size > 1:

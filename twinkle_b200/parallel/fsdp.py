@@ -268,18 +268,20 @@ class BufferPool:
         self.free.setdefault((t.numel(), t.dtype), []).append(t)
 
     # Flat gradient buffers.  With a peer-memory communicator they live in symmetric memory (peers pull
-    # their slice) and rotate through a ring of two per size: a buffer is rewritten only after the next
-    # unit's barrier, by which time every peer has finished reading it.
+    # their slice) and rotate through a ring of three per size.  The reduce-scatter of a unit runs on a side
+    # stream; a buffer is rewritten only after this rank has completed the reduce-scatter issued after the one
+    # that read it, by which time every peer has finished pulling from it.
     def take_grad(self, numel: int, dtype: torch.dtype, comm) -> torch.Tensor:
         if not hasattr(comm, 'alloc') or comm.world_size == 1 or torch.device(self.device).type != 'cuda':
             return self.take(numel, dtype)
         ring = self.__dict__.setdefault('_rings', {}).setdefault((numel, dtype), {'bufs': [], 'next': 0})
-        if len(ring['bufs']) < 2:
+        if len(ring['bufs']) < 3:
             ring['bufs'].append(comm.alloc(numel, dtype))
             ring['next'] = 0
             return ring['bufs'][-1]
         t = ring['bufs'][ring['next']]
-        ring['next'] ^= 1
+        ring['next'] = (ring['next'] + 1) % 3
+        comm.wait_reduce_scatters(all_but=1)
         return t
 
     def give_grad(self, t: torch.Tensor) -> None:
@@ -499,6 +501,7 @@ class FSDPEngine:
         self.root.reshard(self.pool)
         for u in self.units:
             u.reshard(self.pool)
+        self.comm.wait_reduce_scatters()  # the gradient shards are complete before anything reads them
         self._root_live = False
         self._grads_pending = True
         # Replicated trainables (LoRA pools): this backward's gradient is summed over the ranks and then added to what

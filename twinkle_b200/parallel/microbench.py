@@ -72,7 +72,11 @@ def main() -> None:
     fg.normal_()
     gs = torch.zeros(numel // world, dtype=torch.float32, device=dev)
     sc.sync_all()
-    out['reduce_scatter_acc'] = entry(timeit(lambda: sc.reduce_scatter_accumulate(gs, fg, 1.0)), recv)
+    def symm_rs():
+        sc.reduce_scatter_accumulate(gs, fg, 1.0)   # runs on the communicator's side stream
+        sc.wait_reduce_scatters()
+
+    out['reduce_scatter_acc'] = entry(timeit(symm_rs), recv)
     tmp = torch.empty(numel // world, dtype=torch.bfloat16, device=dev)
 
     def nccl_rs():

@@ -66,7 +66,13 @@ class SymmCommunicator(Communicator):
         self._by_ptr: Dict[int, Tuple[SymmBuffer, int]] = {}
         self._flags = SymmBuffer(self, 4096)
         self._epoch = 0
-        self.copy_blocks = 16  # CTAs per peer stream: enough to fill an NVLink port, few enough to leave SMs to the GEMMs
+        # the gradient reduce-scatter runs on a stream of its own with its own flag set: barriers of two streams that
+        # shared one epoch counter could pair up differently on different ranks
+        self._rs_flags = SymmBuffer(self, 4096)
+        self._rs_epoch = 0
+        self._rs_stream = torch.cuda.Stream(device=self.device)
+        self._rs_events: List[torch.cuda.Event] = []
+        self.copy_blocks = 32  # CTAs per peer: with 64 KB in flight each, enough for most of a peer's NVLink bandwidth; few enough to leave SMs to the GEMMs
         # TWINKLE_SYMM_LEGACY=1 keeps the first-generation kernels (push exchange with two barriers, one load in flight
         # per thread in the all-gather) for A/B measurements
         import os
@@ -134,13 +140,33 @@ class SymmCommunicator(Communicator):
         ptrs = self.peer_ptrs(full_grad)
         if ptrs is None or grad_shard.dtype != torch.float32 or full_grad.dtype != torch.bfloat16:
             return super().reduce_scatter_accumulate(grad_shard, full_grad, scale)
-        with PHASES('fsdp_reduce_scatter'):
-            # every rank must have finished writing this layer's gradients before anyone reads them
-            self.barrier_kernel()
-            self.ext.peer_reduce_scatter_acc(grad_shard, ptrs, self.rank, scale, None, 4 * self.copy_blocks)
+        # Off the compute stream: the barrier (every rank has finished writing this unit's gradients) and the pull
+        # overlap the backward pass of the next unit instead of stalling it on the slowest rank.
+        ready = torch.cuda.current_stream().record_event()
+        with torch.cuda.stream(self._rs_stream):
+            self._rs_stream.wait_event(ready)
+            with PHASES('fsdp_reduce_scatter'):
+                self._rs_epoch += 1
+                self.ext.symm_barrier(self._rs_flags.ptrs, self.rank, self._rs_epoch)
+                self.ext.peer_reduce_scatter_acc(grad_shard, ptrs, self.rank, scale, None, 4 * self.copy_blocks)
+            self._rs_events.append(self._rs_stream.record_event())
+        grad_shard.record_stream(self._rs_stream)
+        full_grad.record_stream(self._rs_stream)
+        del self._rs_events[:-4]
+
+    def wait_reduce_scatters(self, all_but: int = 0) -> None:
+        """The compute stream waits for the reduce-scatters issued so far, except the newest ``all_but``.  With
+        ``all_but=1`` this is the condition for rewriting a gradient buffer of a three-deep ring: once this rank has
+        passed the barrier of the reduce-scatter issued after the one that read the buffer, every peer has finished
+        pulling from it."""
+        evs = self._rs_events[:len(self._rs_events) - all_but] if all_but else self._rs_events
+        if evs:
+            with PHASES('fsdp_reduce_scatter_wait'):
+                torch.cuda.current_stream().wait_event(evs[-1])
 
     def step_barrier(self) -> None:
         """Fences the optimizer step: peers finished reading my shards / gradient buffers."""
+        self.wait_reduce_scatters()
         self.barrier_kernel()
 
     # ---------------------------------------------------------------- Ulysses

@@ -96,6 +96,37 @@ class _ExchangeMany(torch.autograd.Function):
         return (None, None) + tuple(ctx.comm.exchange_heads([g.contiguous() for g in gs], not ctx.s2h))
 
 
+class _ExchangeReuse(torch.autograd.Function):
+    """The recompute pass of a layer: the forward values are the tensors the first forward already received (kept by
+    the engine beside the attention output), so nothing crosses NVLink; backward still returns the gradients with the
+    inverse exchange."""
+
+    @staticmethod
+    def forward(ctx, comm, seq_to_head: bool, kept, *xs):
+        ctx.comm, ctx.s2h = comm, seq_to_head
+        return tuple(t.view(t.shape) for t in kept)
+
+    @staticmethod
+    def backward(ctx, *gs):
+        return (None, None, None) + tuple(ctx.comm.exchange_heads([g.contiguous() for g in gs], not ctx.s2h))
+
+
+def _exchange(comm, seq_to_head: bool, xs):
+    """One exchange of ``xs``; inside the sharding engine's per-layer forward the results are kept, and its recompute
+    pass takes them back instead of exchanging again (two of the six cross-GPU meeting points per layer go away)."""
+    from .. import ops
+    st = ops.AttentionStash.current
+    if st is not None and st.mode == 'save' and not torch.is_grad_enabled():
+        outs = tuple(comm.exchange_heads(list(xs), seq_to_head))
+        st.items.append(outs)
+        return outs
+    if st is not None and st.mode == 'reuse' and st._i < len(st.items):
+        kept = st.items[st._i]
+        st._i += 1
+        return _ExchangeReuse.apply(comm, seq_to_head, kept, *xs)
+    return _ExchangeMany.apply(comm, seq_to_head, *xs)
+
+
 def _symm_out(comm, shape, dtype, tag):
     """Destination buffers in symmetric memory, two per (shape, direction) used alternately so a
     consumer of the previous exchange never races with the next push.  The cache lives on the
@@ -210,13 +241,13 @@ class UlyssesAttention:
             k = k.repeat_interleave(self.kv_rep, dim=1)
             v = v.repeat_interleave(self.kv_rep, dim=1)
         if _pulls(self.comm, q) and q.dtype == k.dtype == v.dtype:
-            return _ExchangeMany.apply(self.comm, True, q, k, v)
+            return _exchange(self.comm, True, (q, k, v))
         return (_HeadScatter.apply(q.contiguous(), self.comm), _HeadScatter.apply(k.contiguous(), self.comm),
                 _HeadScatter.apply(v.contiguous(), self.comm))
 
     def gather_heads(self, o):
         if _pulls(self.comm, o):
-            return _ExchangeMany.apply(self.comm, False, o)[0]
+            return _exchange(self.comm, False, (o, ))[0]
         return _HeadGather.apply(o.contiguous(), self.comm)
 
     # ---- exchange inside the projection
