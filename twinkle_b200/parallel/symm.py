@@ -35,7 +35,16 @@ class SymmBuffer:
 
     def __init__(self, comm: 'SymmCommunicator', nbytes: int):
         E = ops.ext()
-        self.raw, handle, offset = E.symm_alloc(nbytes)
+        try:
+            self.raw, handle, offset = E.symm_alloc(nbytes)
+        except RuntimeError as e:
+            if 'out of memory' not in str(e):
+                raise
+            # symmetric buffers come straight from the driver; blocks that PyTorch's caching allocator holds but does
+            # not use are given back first
+            torch.cuda.synchronize()
+            torch.cuda.empty_cache()
+            self.raw, handle, offset = E.symm_alloc(nbytes)
         self.nbytes = self.raw.numel()
         infos = comm.gather_object((handle, offset, self.nbytes))
         if len({i[2] for i in infos}) != 1:

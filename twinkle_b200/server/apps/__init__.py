@@ -95,13 +95,18 @@ async def body_of(request: Request) -> Dict[str, Any]:
 # =============================================================== Model app
 class ModelApp(TaskQueueMixin):
 
-    def __init__(self, args, state: ServerState, queue_cfg, checkpoints: CheckpointManager, name: str = 'model'):
+    def __init__(self, args, state: ServerState, queue_cfg, checkpoints: CheckpointManager, name: str = 'model',
+                 remote_group: Optional[str] = None):
+        """``remote_group``: name of the worker-pool device group that hosts the backend (one worker per rank of the
+        application's ``device_group``); ``None`` keeps the backend inside the server process."""
         self.args, self.checkpoints, self.name = args, checkpoints, name
         self.replica_id = f'{name}-{uuid.uuid4().hex[:8]}'
         self._init_task_queue(state, args.queue_config or queue_cfg, get_registry())
         kw = dict(model_id=args.model_id, max_loras=args.max_loras)
         if args.backend != 'mock':
             kw.update(device_mesh=args.device_mesh.build(), max_r=args.max_r, max_length=args.max_length)
+            if remote_group is not None:
+                kw['remote_group'] = remote_group
         self.backend = BackendSelector.model(args.backend, **kw)
         self.adapters: Dict[str, Dict[str, Any]] = {}  # model_id → {adapter, token, session, created, last_used}
         self.uploads: Dict[str, str] = {}
@@ -168,7 +173,10 @@ class ModelApp(TaskQueueMixin):
 
         @app.get('/healthz')
         async def healthz():
-            ok = bool(self.backend.ping())
+            try:  # with a worker group behind the backend this is a round trip to every worker
+                ok = bool(self.backend.ping())
+            except Exception:
+                ok = False
             return JSONResponse({'status': 'ok' if ok else 'unhealthy', 'replica_id': self.replica_id, 'queue_depth': self.worker.depth(),
                                  'adapters': len(self.adapters)}, status_code=200 if ok else 503)
 
@@ -366,13 +374,16 @@ class ModelApp(TaskQueueMixin):
 # ============================================================= Sampler app
 class SamplerApp(TaskQueueMixin):
 
-    def __init__(self, args, state: ServerState, queue_cfg, checkpoints: CheckpointManager, name: str = 'sampler'):
+    def __init__(self, args, state: ServerState, queue_cfg, checkpoints: CheckpointManager, name: str = 'sampler',
+                 remote_group: Optional[str] = None):
         self.args, self.checkpoints, self.name = args, checkpoints, name
         self.replica_id = f'{name}-{uuid.uuid4().hex[:8]}'
         self._init_task_queue(state, args.queue_config or queue_cfg, get_registry())
         kw: Dict[str, Any] = dict(model_id=args.model_id)
         if args.sampler_type != 'mock':
             kw.update(engine_args=args.engine_args, max_loras=args.max_loras)
+            if remote_group is not None:
+                kw.update(remote_group=remote_group, device_mesh=args.device_mesh.build())
         self.backend = BackendSelector.sampler(args.sampler_type, **kw)
         self.app = FastAPI(title='twinkle-sampler')
         install_middleware(self.app, name, self.replica_id, require_request_id=True)
@@ -437,7 +448,8 @@ class SamplerApp(TaskQueueMixin):
         @app.post('/twinkle/sample_stream')
         async def sample_stream(request: Request):
             b = await body_of(request)
-            if not hasattr(self.backend, 'sample_stream'):
+            if not hasattr(self.backend, 'sample_stream') or getattr(self.backend, '_remote_proxy', None) is not None:
+                # a sampler that lives in a worker group answers whole responses; the stream carries one final event
                 res = self.backend.sample(b.get('inputs') or [], b.get('sampling_params'))
 
                 async def one():

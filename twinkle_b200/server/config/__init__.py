@@ -93,6 +93,7 @@ class ModelArgs(_Strict):
     device_group: DeviceGroupSpec = Field(default_factory=DeviceGroupSpec)
     device_mesh: DeviceMeshSpec = Field(default_factory=DeviceMeshSpec)
     backend: Literal['mock', 'transformers', 'megatron'] = 'transformers'
+    workers: Literal['auto', 'pool', 'inline'] = 'auto'  # auto: a worker group when device_group has more than one rank
     adapter_config: Dict[str, Any] = Field(default_factory=dict)
     queue_config: Optional[TaskQueueConfig] = None
     max_loras: int = 5
@@ -108,6 +109,7 @@ class SamplerArgs(_Strict):
     device_group: DeviceGroupSpec = Field(default_factory=lambda: DeviceGroupSpec(name='sampler'))
     device_mesh: DeviceMeshSpec = Field(default_factory=DeviceMeshSpec)
     sampler_type: Literal['mock', 'vllm', 'torch'] = 'torch'
+    workers: Literal['auto', 'pool', 'inline'] = 'auto'
     engine_args: Dict[str, Any] = Field(default_factory=dict)
     queue_config: Optional[TaskQueueConfig] = None
     max_loras: int = 4

@@ -56,17 +56,51 @@ class ServerLauncher:
         os.environ['TWINKLE_TELEMETRY_ENABLED'] = '1' if self.config.telemetry.enabled else '0'
         os.environ.setdefault('TWINKLE_FAIL_FAST', '0')  # a bad request must not wedge the collectives of the model workers
 
+    def _worker_groups(self) -> Dict[str, Any]:
+        """Applications whose ``device_group`` has more than one rank (or that ask for ``workers: pool``) get a group of
+        worker processes — one per rank, devices assigned by the group's position — and their backend is built there
+        (reference ``src/twinkle/server/model/app.py:50-234``, ``server/utils/device_utils.py:1-40``).  Returns
+        application name → ``DeviceGroup``; starts the pool when there is at least one."""
+        from ..utils.device_mesh import DeviceGroup
+        groups: Dict[str, Any] = {}
+        for spec in self.config.applications:
+            if spec.import_path not in ('model', 'sampler'):
+                continue
+            a = spec.typed_args
+            if getattr(a, 'backend', getattr(a, 'sampler_type', '')) == 'mock':
+                continue
+            g = a.device_group
+            n = g.ranks if isinstance(g.ranks, int) else len(g.ranks)
+            mode = getattr(a, 'workers', 'auto')
+            if mode == 'inline' or (mode == 'auto' and n <= 1):
+                continue
+            mesh_world = a.device_mesh.build().world_size
+            if mesh_world != n // max(g.gpus_per_worker, 1):
+                raise ValueError(f"application '{spec.name}': device_mesh spans {mesh_world} ranks but device_group has "
+                                 f'{n} ranks / {g.gpus_per_worker} per worker')
+            groups[spec.name] = DeviceGroup(name=f'{spec.name}', ranks=g.ranks, device_type=g.device_type, gpus_per_worker=g.gpus_per_worker)
+        if groups:
+            from .. import infra
+            if infra.get_mode() == 'pool':
+                raise RuntimeError('a worker pool is already running in this process; the server starts its own')
+            infra.initialize(mode='pool', groups=list(groups.values()), lazy_collect=False)
+            self._owns_pool = True
+        return groups
+
     def _build(self) -> None:
         gateway_spec = None
+        self._owns_pool = False
+        groups = self._worker_groups()
         for spec in self.config.applications:
             a = spec.typed_args
+            rg = spec.name if spec.name in groups else None
             if spec.import_path == 'model':
-                m = ModelApp(a, self.state, self.config.task_queue, self.checkpoints, spec.name)
+                m = ModelApp(a, self.state, self.config.task_queue, self.checkpoints, spec.name, remote_group=rg)
                 self.model_apps.append(m)
                 self.router.add_model(m)
                 self.root.mount(spec.route_prefix.rstrip('/'), m.app)
             elif spec.import_path == 'sampler':
-                s = SamplerApp(a, self.state, self.config.task_queue, self.checkpoints, spec.name)
+                s = SamplerApp(a, self.state, self.config.task_queue, self.checkpoints, spec.name, remote_group=rg)
                 self.sampler_apps.append(s)
                 self.router.add_sampler(s)
                 self.root.mount(spec.route_prefix.rstrip('/'), s.app)
@@ -144,6 +178,10 @@ class ServerLauncher:
         if s is not None:
             s.should_exit = True
             self._thread.join(timeout=10)
+        if getattr(self, '_owns_pool', False):
+            from .. import infra
+            infra.shutdown()
+            self._owns_pool = False
 
 
 def launch_server(config: Union[ServerConfig, Dict[str, Any], None] = None, config_path: Optional[str] = None, block: bool = True) -> ServerLauncher:
