@@ -97,3 +97,60 @@ def test_tp_pp_matches_single_and_roundtrips(tmp_path, tp, pp, vpp):
             continue
         assert k in loader, k
         assert torch.allclose(loader.get(k), v, atol=2e-4), k
+
+
+def _resume_worker(rank, world, tmp, tp, pp, dp, recompute):
+    """Trains 2 steps, saves everything, trains 2 more (reference continuation); a second model of the same layout resumes
+    from the checkpoint and must produce the same two losses, bit for bit, and the same counters."""
+    from twinkle_b200.model.megatron import MegatronModel
+    from twinkle_b200.models import preset
+    from twinkle_b200.utils.device_mesh import DeviceMesh
+    cfg = preset('tiny-dense', num_hidden_layers=4)
+    mesh = DeviceMesh.from_sizes(tp_size=tp, pp_size=pp, dp_size=dp, sequence_parallel=tp > 1)
+
+    def make():
+        m = MegatronModel(config=cfg, device_mesh=mesh, seed=0, recompute=recompute)
+        m.set_optimizer('AdamW', lr=2e-3)
+        m.set_lr_scheduler('CosineWarmupScheduler', num_warmup_steps=1, num_training_steps=8)
+        return m
+
+    feats = _feats()
+    sl = mesh.get_slice(len(feats), mesh.get_data_rank_from_global_rank(rank))
+
+    def run(m, n):
+        out = []
+        for _ in range(n):
+            o = m.forward_backward(inputs=feats[sl], micro_batch_size=1)
+            m.clip_grad_and_step(max_grad_norm=1.0)
+            out.append(o['loss'])
+        return out
+
+    a = make()
+    first = run(a, 2)
+    a.save('mid', tmp, save_optimizer=True)
+    cont = run(a, 2)
+    sharded = {n: tuple(st['master'].shape) for n, st in a._state.items()}
+    full = {n: p.numel() for n, p in a.named_parameters()}
+    b = make()
+    info = b.resume_from_checkpoint(os.path.join(tmp, 'mid'))
+    resumed = run(b, 2)
+    return {'first': first, 'cont': cont, 'resumed': resumed, 'info': info, 'state_numel': {n: s[0] for n, s in sharded.items()}, 'full': full}
+
+
+@pytest.mark.parametrize('tp,pp,dp,recompute', [(1, 2, 2, 'full'), (2, 1, 2, None)])
+def test_resume_restores_optimizer_scheduler_and_counters(tmp_path, tp, pp, dp, recompute):
+    res = run_ranks(_resume_worker, tp * pp * dp, str(tmp_path), tp, pp, dp, recompute)
+    for r in res:
+        assert r['info']['cur_step'] == 2 and r['info']['consumed_train_samples'] == 2 * len(_feats())
+        assert r['resumed'] == r['cont'], (r['cont'], r['resumed'])          # same optimizer moments, schedule position and weights
+        # distributed optimizer: a rank keeps fp32 master + moments for 1/dp of every parameter it holds
+        for n, k in r['state_numel'].items():
+            assert k <= -(-r['full'][n] // dp)
+
+
+def test_layer_recompute_does_not_change_the_numbers(tmp_path):
+    a = run_ranks(_resume_worker, 4, str(tmp_path / 'a'), 1, 2, 2, 'full')
+    b = run_ranks(_resume_worker, 4, str(tmp_path / 'b'), 1, 2, 2, None)
+    for ra, rb in zip(a, b):
+        for x, y in zip(ra['first'] + ra['cont'], rb['first'] + rb['cont']):
+            assert abs(x - y) < 1e-5, (ra, rb)

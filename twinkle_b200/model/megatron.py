@@ -61,8 +61,15 @@ def split_layers(num_layers: int, pp: int, vpp: int) -> List[List[Tuple[int, int
 class MegatronModel(TwinkleModel):
 
     def __init__(self, model_id: Optional[str] = None, config=None, device_mesh: DeviceMesh = None, mixed_precision: str = 'bf16',
-                 seed: int = 0, device=None, comm_backend: str = 'auto', **kwargs):
+                 seed: int = 0, device=None, comm_backend: str = 'auto', recompute: Optional[str] = None,
+                 use_distributed_optimizer: bool = True, **kwargs):
+        """``recompute='full'`` re-runs every decoder layer in backward instead of keeping its activations (reference
+        ``recompute_granularity='full'``, ``megatron/strategy/megatron.py:90-107``).  ``use_distributed_optimizer``
+        shards the fp32 master weights and Adam moments of every parameter over the data-parallel ranks (each rank
+        updates its slice, the updated slices are all-gathered), as megatron-core's distributed optimizer does."""
         self._try_init_process_group()
+        self.recompute = recompute if recompute in ('full', 'selective') else None
+        self.use_distributed_optimizer = bool(use_distributed_optimizer)
         self.device_mesh = device_mesh or DeviceMesh.from_sizes(dp_size=Platform.get_world_size())
         self.comm_backend = comm_backend
         mesh = self.device_mesh
@@ -178,8 +185,13 @@ class MegatronModel(TwinkleModel):
             else:
                 h = x
             cos, sin = ops.rope_tables(batch.position_ids, self.config.head_dim, self.config.rope_theta, self.config.rope_scaling)
-            for layer in m.layers:
-                h = layer(h, cos, sin, batch)
+            if self.recompute is not None and torch.is_grad_enabled():
+                from torch.utils.checkpoint import checkpoint
+                for layer in m.layers:
+                    h = checkpoint(layer, h, cos, sin, batch, use_reentrant=False)
+            else:
+                for layer in m.layers:
+                    h = layer(h, cos, sin, batch)
             if not m.has_head:
                 return h
             h = m.norm(h)
@@ -227,6 +239,7 @@ class MegatronModel(TwinkleModel):
         og.train_status.num_tokens += tokens if tokens > 0 else calls
         og.cur_step += 1
         og.grad_ready = True
+        og.consumed_train_samples += n * max(self.dp_comm.world_size, 1)
         out: Dict[str, Any] = {'loss': loss_sum / tokens if tokens > 0 else loss_sum / max(calls, 1), 'num_tokens': tokens}
         if results:
             merged = collect_tensor_dict([{'logps': r['logps'], 'labels': r['labels']} for r in results])
@@ -335,18 +348,41 @@ class MegatronModel(TwinkleModel):
         og.optim_steps += 1
         gd = og.optimizer.param_groups[0]
         scale, self._pending_scale = self._pending_scale, 1.0
+        dp, r = self.dp_comm.world_size, self.dp_comm.rank
+        zero1 = self.use_distributed_optimizer and dp > 1
         for n, p in self._params():
             if p.grad is None:
                 continue
+            numel = p.numel()
+            lo, hi = self._state_range(numel)
             st = self._state.get(n)
             if st is None:
-                st = {'master': p.data.float().clone(), 'exp_avg': torch.zeros_like(p.data, dtype=torch.float32),
-                      'exp_avg_sq': torch.zeros_like(p.data, dtype=torch.float32)}
+                flat = p.data.view(-1)[lo:hi]
+                st = {'master': flat.float().clone(), 'exp_avg': torch.zeros(hi - lo, dtype=torch.float32, device=p.device),
+                      'exp_avg_sq': torch.zeros(hi - lo, dtype=torch.float32, device=p.device)}
                 self._state[n] = st
-            ops.adamw_step(st['master'].view(-1), st['exp_avg'].view(-1), st['exp_avg_sq'].view(-1), p.grad.contiguous().view(-1),
-                           p.data.view(-1), gd['lr'], gd['betas'][0], gd['betas'][1], gd['eps'], 0.0 if _no_decay(n) else gd['weight_decay'],
-                           og.optim_steps, scale)
+            wd = 0.0 if _no_decay(n) else gd['weight_decay']
+            if hi > lo:
+                ops.adamw_step(st['master'], st['exp_avg'], st['exp_avg_sq'], p.grad.contiguous().view(-1)[lo:hi], p.data.view(-1)[lo:hi],
+                               gd['lr'], gd['betas'][0], gd['betas'][1], gd['eps'], wd, og.optim_steps, scale)
+            if zero1:
+                # every rank updated its slice of the parameter; the slices are exchanged so all ranks hold the whole tensor
+                chunk = -(-numel // dp)
+                mine = torch.zeros(chunk, dtype=p.dtype, device=p.device)
+                mine[:hi - lo].copy_(p.data.view(-1)[lo:hi])
+                full = torch.empty(chunk * dp, dtype=p.dtype, device=p.device)
+                dist.all_gather_into_tensor(full, mine, group=self.dp_comm.group)
+                p.data.view(-1).copy_(full[:numel])
         og.grad_ready = False
+
+    def _state_range(self, numel: int) -> Tuple[int, int]:
+        """Slice of a flattened parameter whose optimizer state this rank keeps: the whole tensor, or one of ``dp``
+        contiguous chunks under the distributed optimizer."""
+        dp, r = self.dp_comm.world_size, self.dp_comm.rank
+        if not (self.use_distributed_optimizer and dp > 1):
+            return 0, numel
+        chunk = -(-numel // dp)
+        return min(r * chunk, numel), min((r + 1) * chunk, numel)
 
     @remote_function()
     def zero_grad(self, **kwargs) -> None:
@@ -476,6 +512,8 @@ class MegatronModel(TwinkleModel):
             with open(os.path.join(path, 'model.safetensors.index.json'), 'w') as f:
                 json.dump({'metadata': {}, 'weight_map': weight_map}, f)
             self.config.save_pretrained(path)
+        if kwargs.get('save_optimizer'):
+            self._save_training_state(path)
         if dist.is_available() and dist.is_initialized():
             dist.barrier()
         return path
@@ -491,13 +529,77 @@ class MegatronModel(TwinkleModel):
                 p.copy_(tp_shard(n, full, self.config, self.tp_rank, self.tp_size).to(p.device, p.dtype))
                 st = self._state.get(n)
                 if st is not None:
-                    st['master'].copy_(p.data.float())
+                    lo, hi = self._state_range(p.numel())
+                    st['master'].copy_(p.data.view(-1)[lo:hi].float())
+        if kwargs.get('load_optimizer'):
+            self._load_training_state(path)
 
-    def resume_from_checkpoint(self, checkpoint_dir: str, **kwargs) -> Dict[str, Any]:
+    # Training state.  Weights go through the bridge into one HF checkpoint; what the optimizer holds is layout-specific
+    # (a tensor-parallel shard of a pipeline stage, possibly one data-parallel slice of it), so every rank writes its
+    # own file ``optimizer_tpXX_ppXX_dpXX.pt`` and resuming requires the same layout — as the reference's
+    # megatron-core distributed checkpoint does (``megatron/megatron.py:1078-1243``).
+    def _rank_tag(self) -> str:
+        return f'tp{self.tp_rank:02d}_pp{self.pp_rank:02d}_dp{self.dp_comm.rank:02d}'
+
+    def _save_training_state(self, path: str) -> None:
+        og = self._group()
+        os.makedirs(path, exist_ok=True)
+        state = {'layout': {'tp': self.tp_size, 'pp': self.pp_size, 'vpp': self.vpp, 'dp': self.dp_comm.world_size,
+                            'distributed_optimizer': bool(self.use_distributed_optimizer and self.dp_comm.world_size > 1)},
+                 'optim_steps': og.optim_steps, 'hyper': og.optimizer.state_dict()['param_groups'] if og.optimizer else None,
+                 'params': {n: {k: v.detach().cpu() for k, v in st.items()} for n, st in self._state.items()}}
+        torch.save(state, os.path.join(path, f'optimizer_{self._rank_tag()}.pt'))
+        torch.save(Platform.get_rng_state(), os.path.join(path, f'rng_state_{self._rank_tag()}.pt'))
+        if Platform.is_master():
+            if og.lr_scheduler is not None:
+                torch.save(og.lr_scheduler.state_dict(), os.path.join(path, 'scheduler.pt'))
+            with open(os.path.join(path, 'trainer_state.json'), 'w') as f:
+                json.dump({'checkpoint_version': 1, 'cur_step': og.cur_step, 'gradient_accumulation_steps': og.gradient_accumulation_steps,
+                           'consumed_train_samples': og.consumed_train_samples, 'optim_steps': og.optim_steps}, f)
+
+    def _load_training_state(self, path: str) -> Dict[str, Any]:
+        og = self._group()
+        f = os.path.join(path, f'optimizer_{self._rank_tag()}.pt')
+        if os.path.isfile(f):
+            state = torch.load(f, map_location='cpu', weights_only=True)
+            want = {'tp': self.tp_size, 'pp': self.pp_size, 'vpp': self.vpp, 'dp': self.dp_comm.world_size,
+                    'distributed_optimizer': bool(self.use_distributed_optimizer and self.dp_comm.world_size > 1)}
+            if state.get('layout') != want:
+                raise ValueError(f'optimizer state was saved for layout {state.get("layout")}, this run is {want}; '
+                                 'weights can be loaded into any layout, optimizer state only into the one that wrote it')
+            og.optim_steps = int(state.get('optim_steps', 0))
+            if og.optimizer is None:
+                self.set_optimizer('AdamW')
+            if state.get('hyper'):
+                for g, sv in zip(og.optimizer.param_groups, state['hyper']):
+                    for k in ('lr', 'betas', 'eps', 'weight_decay'):
+                        if k in sv:
+                            g[k] = sv[k] if k != 'betas' else tuple(sv[k])
+            self._state = {n: {k: v.to(self.device) for k, v in st.items()} for n, st in state['params'].items()}
+        sched = os.path.join(path, 'scheduler.pt')
+        if os.path.isfile(sched) and og.lr_scheduler is not None:
+            og.lr_scheduler.load_state_dict(torch.load(sched, map_location='cpu', weights_only=True))
+        rng = os.path.join(path, f'rng_state_{self._rank_tag()}.pt')
+        if os.path.isfile(rng):
+            Platform.set_rng_state(torch.load(rng, map_location='cpu', weights_only=True))
+        info = {'cur_step': 0, 'consumed_train_samples': 0, 'gradient_accumulation_steps': og.gradient_accumulation_steps}
+        ts = os.path.join(path, 'trainer_state.json')
+        if os.path.isfile(ts):
+            with open(ts) as fh:
+                info.update(json.load(fh))
+            og.cur_step, og.consumed_train_samples = info['cur_step'], info['consumed_train_samples']
+            og.gradient_accumulation_steps = info['gradient_accumulation_steps']
+        return info
+
+    @remote_function(collect='first')
+    def resume_from_checkpoint(self, checkpoint_dir: str, *, resume_only_model: bool = False, **kwargs) -> Dict[str, Any]:
+        """Weights, then (unless ``resume_only_model``) optimizer / scheduler / RNG state and the progress counters."""
         self.load(None, checkpoint_dir)
         og = self._group()
-        return {'cur_step': og.cur_step, 'consumed_train_samples': og.consumed_train_samples,
-                'gradient_accumulation_steps': og.gradient_accumulation_steps}
+        if resume_only_model:
+            return {'cur_step': 0, 'consumed_train_samples': 0, 'gradient_accumulation_steps': og.gradient_accumulation_steps}
+        info = self._load_training_state(checkpoint_dir)
+        return {k: info[k] for k in ('cur_step', 'consumed_train_samples', 'gradient_accumulation_steps')}
 
 
 @remote_class()
