@@ -1,0 +1,111 @@
+"""Adapters on the tensor- / pipeline-parallel backend: pools follow the TP shards (A replicated / B sharded on
+column-parallel linears, the reverse on row-parallel ones), every tenant has its own optimizer state, and adapters
+travel as PEFT files between layouts (reference ``src/twinkle/model/megatron/multi_lora_megatron.py:34-451``,
+``model/multi_lora.py:289-475``)."""
+import os
+
+import pytest
+import torch
+
+from tests.dist_utils import run_ranks
+
+
+def _feats(seed=11):
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for n in (64, 48, 32, 64):
+        ids = torch.randint(0, 1024, (n + 1, ), generator=g)
+        out.append({'input_ids': ids[:-1].tolist(), 'labels': ids[1:].tolist()})
+    return out
+
+
+def _make(tp, pp, dp=1):
+    from twinkle_b200.model.megatron import MultiLoraMegatronModel
+    from twinkle_b200.models import preset
+    from twinkle_b200.utils.device_mesh import DeviceMesh
+    cfg = preset('tiny-dense', num_hidden_layers=4)
+    mesh = DeviceMesh.from_sizes(tp_size=tp, pp_size=pp, dp_size=dp, sequence_parallel=tp > 1)
+    return MultiLoraMegatronModel(config=cfg, device_mesh=mesh, seed=0, max_loras=2, max_r=8)
+
+
+def _train(m, name, steps, feats, lr=5e-3):
+    out = []
+    for _ in range(steps):
+        o = m.forward_backward(inputs=feats, adapter_name=name, micro_batch_size=1)
+        n = m.clip_grad_and_step(max_grad_norm=1.0, adapter_name=name)
+        out.append((o['loss'], n))
+    return out
+
+
+def _single(tmp):
+    """One process: warm an adapter up (so B is non-zero), save it, keep training; a second tenant of another rank trains
+    in between and must not disturb the first."""
+    m = _make(1, 1)
+    m.add_adapter_to_model('a', {'r': 4, 'lora_alpha': 8, 'target_modules': 'all-linear'})
+    m.set_optimizer('AdamW', lr=5e-3, adapter_name='a')
+    _train(m, 'a', 2, _feats())
+    m.save('warm', tmp, adapter_name='a', save_optimizer=True)
+    ref = _train(m, 'a', 3, _feats())
+    m.save('ref', tmp, adapter_name='a')
+    return ref
+
+
+def _sharded(rank, world, tmp, tp, pp):
+    m = _make(tp, pp)
+    m.add_adapter_to_model('a', os.path.join(tmp, 'warm'))            # PEFT file written by the single-process layout
+    m.set_optimizer('AdamW', lr=5e-3, adapter_name='a')
+    m.add_adapter_to_model('b', {'r': 8, 'lora_alpha': 16, 'target_modules': ['q_proj', 'down_proj']})
+    m.set_optimizer('AdamW', lr=1e-2, adapter_name='b')
+    # the optimizer state of 'a' cannot cross layouts (it is per shard); the first step after a fresh state equals the
+    # reference only if Adam starts fresh there too, so the reference is re-run from the same point below
+    curve, other = [], []
+    for i in range(3):
+        curve += _train(m, 'a', 1, _feats())
+        other += _train(m, 'b', 1, _feats(seed=5))                     # a second tenant between the first one's steps
+    m.save('out', tmp, adapter_name='a')
+    return curve, other
+
+
+@pytest.mark.parametrize('tp,pp', [(2, 2), (2, 1)])
+def test_tensor_parallel_adapters_match_single_process(tmp_path, tp, pp):
+    from twinkle_b200.utils.safetensors_io import SafetensorLazyLoader
+    tmp = str(tmp_path)
+    _single(tmp)
+    # reference continuation from the warm adapter with a fresh optimizer, in one process
+    m = _make(1, 1)
+    m.add_adapter_to_model('a', os.path.join(tmp, 'warm'))
+    m.set_optimizer('AdamW', lr=5e-3, adapter_name='a')
+    ref = _train(m, 'a', 3, _feats())
+    m.save('ref2', tmp, adapter_name='a')
+    res = run_ranks(_sharded, tp * pp, tmp, tp, pp)
+    for curve, other in res:
+        for (l0, n0), (l1, n1) in zip(ref, curve):
+            assert abs(l0 - l1) < 3e-4 and abs(n0 - n1) < 3e-3 * max(n0, 1.0), (ref, curve)
+        assert other[-1][0] < other[0][0]                                 # the second tenant trains as well
+    a, b = SafetensorLazyLoader(os.path.join(tmp, 'ref2')), SafetensorLazyLoader(os.path.join(tmp, 'out'))
+    keys = sorted(a.keys())
+    assert keys == sorted(b.keys()) and len(keys) == 4 * 7 * 2            # 4 layers x (q, k, v, o, gate, up, down) x (A, B)
+    for k in keys:
+        assert a.get(k).shape == b.get(k).shape, k
+        assert torch.allclose(a.get(k), b.get(k), atol=5e-4), (k, float((a.get(k) - b.get(k)).abs().max()))
+
+
+def _resume(rank, world, tmp):
+    m = _make(2, 1)
+    m.add_adapter_to_model('a', {'r': 4, 'lora_alpha': 8})
+    m.set_optimizer('AdamW', lr=5e-3, adapter_name='a')
+    _train(m, 'a', 2, _feats())
+    m.save('mid', tmp, adapter_name='a', save_optimizer=True)
+    cont = _train(m, 'a', 2, _feats())
+    m2 = _make(2, 1)
+    m2.add_adapter_to_model('a', {'r': 4, 'lora_alpha': 8})
+    m2.set_optimizer('AdamW', lr=5e-3, adapter_name='a')
+    info = m2.resume_from_checkpoint(os.path.join(tmp, 'mid'), adapter_name='a')
+    again = _train(m2, 'a', 2, _feats())
+    return cont, again, info
+
+
+def test_tenant_optimizer_state_resumes(tmp_path):
+    for cont, again, info in run_ranks(_resume, 2, str(tmp_path)):
+        assert info['cur_step'] == 2
+        assert cont == again, (cont, again)

@@ -604,23 +604,74 @@ class MegatronModel(TwinkleModel):
 
 @remote_class()
 class MultiLoraMegatronModel(MegatronModel):
-    """Adapters on the pipeline backend.  LoRA pools attach to un-sharded linears only, so tensor parallelism
-    must be 1 here (pipeline and data parallelism are free); with tp > 1 use the sharded backend."""
+    """Tenants' adapters on the tensor- / pipeline-parallel backend over one frozen base (reference
+    ``src/twinkle/model/megatron/multi_lora_megatron.py:34-451``).
+
+    Every chunk of this rank carries a slot pool.  On tensor-parallel linears the pools follow the shards: ``A``
+    replicated and ``B`` row-sharded on column-parallel linears, ``A`` column-sharded and ``B`` replicated on
+    row-parallel ones; gradients of the replicated halves are partial sums and are all-reduced over the TP group.
+    Each tenant has its own optimizer state (fp32 master + Adam moments of its slot slices), gradient norm, progress
+    counters and scheduler (``multi_lora_megatron.py:213-291``); adapters are saved and loaded in PEFT format with the
+    TP shards and pipeline stages merged into one ``adapter_model.safetensors``."""
 
     def __init__(self, *args, max_loras: int = 5, max_r: int = 32, max_length: int = 8192, **kwargs):
+        kwargs.setdefault('use_distributed_optimizer', False)  # adapter state is small: every data-parallel rank keeps it whole
         super().__init__(*args, **kwargs)
-        if self.tp_size > 1:
-            raise NotImplementedError('multi-LoRA on the pipeline backend requires tp_size == 1')
         from .multi_lora import MultiLora
         self.max_length = max_length
-        self.pools = [MultiLora(m, max_loras, max_r) for m in self.chunks]
+        seed = kwargs.get('seed', 0)
+        self.pools = [MultiLora(m, max_loras, max_r, seed=seed * 1000 + self.pp_rank * 16 + c) for c, m in enumerate(self.chunks)]
+        self._sync_pools()
         self.optimizer_groups = {}
+        self._tenant_state: Dict[str, Dict[str, Dict[str, torch.Tensor]]] = {}
+        self._tenant_scale: Dict[str, float] = {}
+
+    # ------------------------------------------------------------ pool plumbing
+    def _pool_params(self):
+        """(global parameter name, parameter, tp_mode of its module) for every pool tensor of this rank."""
+        for m, pool in zip(self.chunks, self.pools):
+            mods = dict(pool.modules)
+            for n, p in pool.pool_parameters():
+                mod_name = n.split('.lora')[0]
+                yield self._global_name(n, m._layer_offset), p, getattr(mods.get(mod_name), 'tp_mode', None)
+
+    def _sync_pools(self) -> None:
+        """Replicated pool tensors start equal: over the TP group for the replicated halves, over the data-parallel
+        group for everything (each process drew its pool from its own stream position)."""
+        from ..parallel.tensor import lora_param_is_replicated
+        with torch.no_grad():
+            for pool in self.pools:
+                init = pool._initial_A
+                for n, p, mode in self._pool_params_of(pool):
+                    if self.tp_size > 1 and lora_param_is_replicated(n, mode):
+                        self.tp_comm.broadcast(p.data, 0)
+                    if self.dp_comm.world_size > 1:
+                        self.dp_comm.broadcast(p.data, 0)
+                    if n in init:
+                        init[n].copy_(p.data)
+
+    def _pool_params_of(self, pool):
+        mods = dict(pool.modules)
+        for n, p in pool.pool_parameters():
+            yield n, p, getattr(mods.get(n.split('.lora')[0]), 'tp_mode', None)
+
+    def _tenant_slices(self, adapter_name: str):
+        """(global name, pool parameter, slot, tp_mode) of every pool tensor the tenant trains on this rank."""
+        out = []
+        for m, pool in zip(self.chunks, self.pools):
+            mods = dict(pool.modules)
+            for n, p, slot in pool.tenant_slices(adapter_name):
+                out.append((self._global_name(n, m._layer_offset), p, slot, getattr(mods.get(n.split('.lora')[0]), 'tp_mode', None)))
+        return out
 
     def _group(self, adapter_name=None) -> OptimizerGroup:
         if adapter_name is None:
             adapter_name = getattr(self, '_active', None)
+        if adapter_name not in self.optimizer_groups:
+            raise KeyError(f'unknown adapter {adapter_name!r}; call add_adapter_to_model first')
         return self.optimizer_groups[adapter_name]
 
+    @remote_function()
     def add_adapter_to_model(self, adapter_name: str, config_or_dir, **kwargs) -> None:
         from .multi_lora import LoraConfig
         cfg = LoraConfig.from_any(config_or_dir)
@@ -628,11 +679,15 @@ class MultiLoraMegatronModel(MegatronModel):
             pool.acquire_lora(adapter_name, cfg)
         self.optimizer_groups[adapter_name] = OptimizerGroup(adapter_name=adapter_name, adapter_config=cfg)
         self._active = adapter_name
+        if isinstance(config_or_dir, str) and os.path.isfile(os.path.join(config_or_dir, 'adapter_model.safetensors')):
+            self._load_adapter(adapter_name, config_or_dir)
 
+    @remote_function()
     def remove_adapter(self, adapter_name: str, **kwargs) -> None:
         for pool in self.pools:
             pool.release_lora(adapter_name)
         self.optimizer_groups.pop(adapter_name, None)
+        self._tenant_state.pop(adapter_name, None)
 
     def check_length(self, inputs, max_length=None) -> None:
         limit = max_length or self.max_length
@@ -640,14 +695,295 @@ class MultiLoraMegatronModel(MegatronModel):
             if len(f.get('input_ids', [])) > limit:
                 raise ValueError(f'input exceeds max_length {limit}')
 
-    def forward_backward(self, *, inputs, adapter_name: Optional[str] = None, **kwargs):
-        from ..models.layers import lora_batch
-        self._active = adapter_name
+    # ------------------------------------------------------------ training
+    def _lora_scope(self, adapter_name: str):
+        from ..models.layers import LoraBatch, lora_batch
         t = self.pools[0].tenants[adapter_name]
-        lb_factory = lambda n: self.pools[0].batch_for(adapter_name, n, self.device)
-        # one tenant per call: the same routing applies to every micro-batch (segment covers all tokens)
-        from ..models.layers import LoraBatch
-        big = LoraBatch.single(1 << 30, t.slot, t.config.r, t.config.scaling, self.device, t.target)
-        with lora_batch(big):
-            return MegatronModel.forward_backward.__wrapped__(self, inputs=inputs, **kwargs) if hasattr(
-                MegatronModel.forward_backward, '__wrapped__') else super().forward_backward(inputs=inputs, **kwargs)
+        # one tenant per call: a single segment that covers every token of every micro-batch
+        return lora_batch(LoraBatch.single(1 << 30, t.slot, t.config.r, t.config.scaling, self.device, t.target))
+
+    @remote_function(dispatch='slice_dp', collect=collect_tensor_dict)
+    def forward_backward(self, *, inputs, adapter_name: Optional[str] = None, **kwargs):
+        self._active = adapter_name = adapter_name or getattr(self, '_active', None)
+        self._group(adapter_name)
+        with self._lora_scope(adapter_name):
+            return MegatronModel.forward_backward.__wrapped__(self, inputs=inputs, adapter_name=adapter_name, **kwargs)
+
+    @remote_function(dispatch='slice_dp', collect=collect_tensor_dict)
+    def forward_only(self, *, inputs, adapter_name: Optional[str] = None, disable_lora: bool = False, **kwargs):
+        self._active = adapter_name = adapter_name or getattr(self, '_active', None)
+        if disable_lora:
+            return MegatronModel.forward_only.__wrapped__(self, inputs=inputs, **kwargs)
+        with self._lora_scope(adapter_name):
+            return MegatronModel.forward_only.__wrapped__(self, inputs=inputs, **kwargs)
+
+    forward = forward_only
+
+    @remote_function(collect='first')
+    def clip_grad_norm(self, max_grad_norm: float = 1.0, norm_type=2, adapter_name: Optional[str] = None, **kwargs) -> float:
+        from ..parallel.tensor import lora_param_is_replicated
+        adapter_name = adapter_name or self._active
+        og = self._group(adapter_name)
+        sq = torch.zeros((), dtype=torch.float32, device=self.device)
+        for n, p, slot, mode in self._tenant_slices(adapter_name):
+            if p.grad is None:
+                continue
+            g = p.grad[slot]
+            rep = lora_param_is_replicated(n, mode)
+            if self.dp_comm.world_size > 1 or (self.tp_size > 1 and rep):
+                g = g.contiguous()
+                if self.dp_comm.world_size > 1:
+                    self.dp_comm.all_reduce(g)
+                if self.tp_size > 1 and rep:
+                    self.tp_comm.all_reduce(g)  # the ranks' partial sums of a replicated tensor's gradient
+                p.grad[slot].copy_(g)
+            v = ops.sumsq(p.grad[slot].contiguous())
+            sq = sq + (v / self.tp_size if (self.tp_size > 1 and rep) else v)
+        if self.tp_size > 1:
+            self.tp_comm.all_reduce(sq)
+        if self.pp_size > 1:
+            dist.all_reduce(sq, group=self.pp_group)
+        denom = self.dp_comm.all_reduce_scalar(og.train_status.num_tokens, 'sum') or 1.0
+        norm = float(sq.sqrt()) / denom
+        coef = min(1.0, max_grad_norm / (norm + 1e-6)) if max_grad_norm and max_grad_norm > 0 else 1.0
+        self._tenant_scale[adapter_name] = coef / denom
+        og._last_grad_norm = norm
+        og.train_status.num_tokens = 0.0
+        return norm
+
+    @remote_function()
+    def step(self, adapter_name: Optional[str] = None, optim_params: Optional[Dict[str, Any]] = None, **kwargs) -> None:
+        adapter_name = adapter_name or self._active
+        og = self._group(adapter_name)
+        if og.optimizer is None:
+            self.set_optimizer('AdamW', adapter_name=adapter_name)
+        gd = og.optimizer.param_groups[0]
+        if optim_params:
+            for k in ('lr', 'eps', 'weight_decay'):
+                if k in optim_params:
+                    gd[k] = optim_params[k]
+            if 'betas' in optim_params:
+                gd['betas'] = tuple(optim_params['betas'])
+        og.optim_steps += 1
+        scale = self._tenant_scale.pop(adapter_name, 1.0)
+        state = self._tenant_state.setdefault(adapter_name, {})
+        for n, p, slot, _ in self._tenant_slices(adapter_name):
+            if p.grad is None:
+                continue
+            view = p.data[slot]
+            st = state.get(n)
+            if st is None:
+                st = {'master': view.float().clone(), 'exp_avg': torch.zeros_like(view, dtype=torch.float32),
+                      'exp_avg_sq': torch.zeros_like(view, dtype=torch.float32)}
+                state[n] = st
+            ops.adamw_step(st['master'].view(-1), st['exp_avg'].view(-1), st['exp_avg_sq'].view(-1), p.grad[slot].contiguous().view(-1),
+                           view.view(-1), gd['lr'], gd['betas'][0], gd['betas'][1], gd['eps'], gd['weight_decay'], og.optim_steps, scale)
+        og.grad_ready = False
+
+    @remote_function()
+    def zero_grad(self, adapter_name: Optional[str] = None, **kwargs) -> None:
+        adapter_name = adapter_name or self._active
+        for _, p, slot, _ in self._tenant_slices(adapter_name):
+            if p.grad is not None:
+                p.grad[slot].zero_()
+
+    @remote_function()
+    def lr_step(self, adapter_name: Optional[str] = None, **kwargs) -> None:
+        og = self._group(adapter_name or self._active)
+        if og.lr_scheduler is not None:
+            og.lr_scheduler.step()
+
+    @remote_function(collect='first')
+    def clip_grad_and_step(self, max_grad_norm: float = 1.0, norm_type=2, adapter_name: Optional[str] = None, **kwargs):
+        norm = self.clip_grad_norm(max_grad_norm, norm_type, adapter_name=adapter_name)
+        self.step(adapter_name=adapter_name, **kwargs)
+        self.zero_grad(adapter_name=adapter_name)
+        self.lr_step(adapter_name=adapter_name)
+        return norm
+
+    @remote_function()
+    def set_loss(self, loss_cls, adapter_name: Optional[str] = None, **kwargs) -> None:
+        if isinstance(loss_cls, str):
+            loss_cls = torch_loss_mapping[loss_cls]
+        self._group(adapter_name).set_loss(loss_cls(**kwargs) if isinstance(loss_cls, type) else loss_cls)
+
+    @remote_function()
+    def set_optimizer(self, optimizer_cls='AdamW', adapter_name: Optional[str] = None, **kwargs) -> None:
+        og = self._group(adapter_name)
+        h = AdamHyper(lr=kwargs.get('lr', 1e-4), betas=tuple(kwargs.get('betas', (0.9, 0.999))), eps=kwargs.get('eps', 1e-8),
+                      weight_decay=kwargs.get('weight_decay', 0.0))
+        og.hyper = h
+        og.optimizer = EngineOptimizer(h, [n for n, *_ in self._tenant_slices(og.adapter_name)], [])
+
+    @remote_function()
+    def set_lr_scheduler(self, scheduler_cls, adapter_name: Optional[str] = None, **kwargs) -> None:
+        og = self._group(adapter_name)
+        if og.optimizer is None:
+            self.set_optimizer('AdamW', adapter_name=og.adapter_name)
+        if isinstance(scheduler_cls, str):
+            scheduler_cls = scheduler_mapping[scheduler_cls]
+        og.lr_scheduler = scheduler_cls(og.optimizer, **kwargs) if isinstance(scheduler_cls, type) else scheduler_cls
+
+    def calculate_metric(self, is_training: bool = True, adapter_name: Optional[str] = None, **kwargs) -> Dict[str, Any]:
+        out: Dict[str, Any] = {}
+        for m in self._group(adapter_name).status(is_training).metrics:
+            out.update(m.calculate())
+        return out
+
+    def add_metric(self, metric_cls, is_training=None, adapter_name: Optional[str] = None, **kwargs) -> None:
+        from ..metric import metric_mapping
+        m = metric_mapping[metric_cls](**kwargs) if isinstance(metric_cls, str) else metric_cls
+        self._group(adapter_name).train_status.metrics.append(m)
+
+    # ---------------------------------------------------------- adapters on disk
+    def _adapter_state_dict(self, adapter_name: str) -> Dict[str, torch.Tensor]:
+        """PEFT-named tensors of the tenant for the layers of this pipeline stage, TP shards merged (collective over the
+        TP group)."""
+        from ..models.bridge import lora_internal_to_peft
+        t = self.pools[0].tenants[adapter_name]
+        r = t.config.r
+        sd: Dict[str, torch.Tensor] = {}
+        for m, pool in zip(self.chunks, self.pools):
+            for mod_name, mod in pool.modules:
+                gname = self._global_name(mod_name, m._layer_offset)
+                prefix = gname.rsplit('.', 1)[0] if '.' in gname else ''
+                mode = getattr(mod, 'tp_mode', None)
+                for pname, _ in mod.parts:
+                    if not t.target.matches(f'{prefix}.{pname}' if prefix else pname, pname):
+                        continue
+                    a = mod.lora_A[pname][t.slot, :r].detach().contiguous()
+                    b = mod.lora_B[pname][t.slot, :, :r].detach().contiguous()
+                    if self.tp_size > 1 and mode == 'col':      # B rows are sharded
+                        parts = [torch.empty_like(b) for _ in range(self.tp_size)]
+                        dist.all_gather(parts, b, group=self.tp_comm.group)
+                        b = torch.cat(parts, 0)
+                    elif self.tp_size > 1 and mode == 'row':    # A columns are sharded
+                        parts = [torch.empty_like(a) for _ in range(self.tp_size)]
+                        dist.all_gather(parts, a, group=self.tp_comm.group)
+                        a = torch.cat(parts, 1)
+                    sd[lora_internal_to_peft(gname, pname, 'A')] = a.clone()
+                    sd[lora_internal_to_peft(gname, pname, 'B')] = b.clone()
+        return sd
+
+    @remote_function(collect='first')
+    def get_state_dict(self, adapter_name: Optional[str] = None, **kwargs) -> Dict[str, torch.Tensor]:
+        if adapter_name is None:
+            return MegatronModel.get_state_dict.__wrapped__(self, **kwargs)
+        return self._adapter_state_dict(adapter_name)
+
+    @remote_function(collect='first')
+    def save(self, name: Optional[str] = None, output_dir: Optional[str] = None, adapter_name: Optional[str] = None,
+             save_optimizer: bool = False, **kwargs) -> str:
+        """``adapter_model.safetensors`` + ``adapter_config.json`` of one tenant (all pipeline stages and TP shards
+        merged); with ``save_optimizer`` also the tenant's optimizer slices per rank, scheduler and counters."""
+        if adapter_name is None:
+            return MegatronModel.save.__wrapped__(self, name, output_dir, save_optimizer=save_optimizer, **kwargs)
+        og = self._group(adapter_name)
+        path = os.path.join(output_dir or './output', name) if name else (output_dir or './output')
+        os.makedirs(path, exist_ok=True)
+        sd = {k: v.cpu() for k, v in self._adapter_state_dict(adapter_name).items()}
+        if self.pp_size > 1:
+            gathered = [None] * self.pp_size
+            dist.all_gather_object(gathered, sd, group=self.pp_group)
+            sd = {k: v for part in gathered for k, v in part.items()}
+        if Platform.is_master():
+            from safetensors.torch import save_file
+            save_file({k: v.contiguous() for k, v in sd.items()}, os.path.join(path, 'adapter_model.safetensors'), metadata={'format': 'pt'})
+            with open(os.path.join(path, 'adapter_config.json'), 'w') as f:
+                json.dump(og.adapter_config.to_peft_dict(), f, indent=2)
+        if save_optimizer:
+            st = {'optim_steps': og.optim_steps, 'hyper': og.optimizer.state_dict()['param_groups'] if og.optimizer else None,
+                  'params': {n: {k: v.cpu() for k, v in d.items()} for n, d in self._tenant_state.get(adapter_name, {}).items()}}
+            torch.save(st, os.path.join(path, f'optimizer_{self._rank_tag()}.pt'))
+            if Platform.is_master():
+                if og.lr_scheduler is not None:
+                    torch.save(og.lr_scheduler.state_dict(), os.path.join(path, 'scheduler.pt'))
+                with open(os.path.join(path, 'trainer_state.json'), 'w') as f:
+                    json.dump({'checkpoint_version': 1, 'cur_step': og.cur_step, 'gradient_accumulation_steps': og.gradient_accumulation_steps,
+                               'consumed_train_samples': og.consumed_train_samples, 'optim_steps': og.optim_steps}, f)
+        if dist.is_available() and dist.is_initialized():
+            dist.barrier()
+        return path
+
+    @torch.no_grad()
+    def _load_adapter(self, adapter_name: str, path: str) -> None:
+        """Every rank reads the PEFT file and keeps the shards of the layers it holds."""
+        from ..models.bridge import lora_internal_to_peft
+        loader = SafetensorLazyLoader(path)
+        t = self.pools[0].tenants[adapter_name]
+        for m, pool in zip(self.chunks, self.pools):
+            for mod_name, mod in pool.modules:
+                gname = self._global_name(mod_name, m._layer_offset)
+                mode = getattr(mod, 'tp_mode', None)
+                for pname, _ in mod.parts:
+                    ka, kb = lora_internal_to_peft(gname, pname, 'A'), lora_internal_to_peft(gname, pname, 'B')
+                    if ka not in loader or kb not in loader:
+                        continue
+                    a, b = loader.get(ka), loader.get(kb)
+                    if self.tp_size > 1 and mode == 'col':
+                        n = b.shape[0] // self.tp_size
+                        b = b[self.tp_rank * n:(self.tp_rank + 1) * n]
+                    elif self.tp_size > 1 and mode == 'row':
+                        n = a.shape[1] // self.tp_size
+                        a = a[:, self.tp_rank * n:(self.tp_rank + 1) * n]
+                    r = a.shape[0]
+                    mod.lora_A[pname][t.slot].zero_()
+                    mod.lora_B[pname][t.slot].zero_()
+                    mod.lora_A[pname][t.slot, :r].copy_(a)
+                    mod.lora_B[pname][t.slot, :, :r].copy_(b)
+        loader.close()
+
+    @remote_function()
+    def load(self, name: Optional[str] = None, output_dir: Optional[str] = None, adapter_name: Optional[str] = None,
+             load_optimizer: bool = False, **kwargs) -> None:
+        path = os.path.join(output_dir or './output', name) if name else (output_dir or './output')
+        if adapter_name is None or not os.path.isfile(os.path.join(path, 'adapter_model.safetensors')):
+            return MegatronModel.load.__wrapped__(self, name, output_dir, load_optimizer=load_optimizer, **kwargs)
+        if adapter_name not in self.optimizer_groups:
+            self.add_adapter_to_model(adapter_name, path)
+        else:
+            self._load_adapter(adapter_name, path)
+        # the fp32 masters of the tenant's optimizer follow the loaded values
+        for n, p, slot, _ in self._tenant_slices(adapter_name):
+            st = self._tenant_state.get(adapter_name, {}).get(n)
+            if st is not None:
+                st['master'].copy_(p.data[slot].float())
+        if load_optimizer:
+            self._load_tenant_state(adapter_name, path)
+
+    def _load_tenant_state(self, adapter_name: str, path: str) -> Dict[str, Any]:
+        og = self._group(adapter_name)
+        f = os.path.join(path, f'optimizer_{self._rank_tag()}.pt')
+        if os.path.isfile(f):
+            st = torch.load(f, map_location='cpu', weights_only=True)
+            og.optim_steps = int(st.get('optim_steps', 0))
+            if og.optimizer is None:
+                self.set_optimizer('AdamW', adapter_name=adapter_name)
+            if st.get('hyper'):
+                for g, sv in zip(og.optimizer.param_groups, st['hyper']):
+                    for k in ('lr', 'betas', 'eps', 'weight_decay'):
+                        if k in sv:
+                            g[k] = sv[k] if k != 'betas' else tuple(sv[k])
+            self._tenant_state[adapter_name] = {n: {k: v.to(self.device) for k, v in d.items()} for n, d in st['params'].items()}
+        sched = os.path.join(path, 'scheduler.pt')
+        if os.path.isfile(sched) and og.lr_scheduler is not None:
+            og.lr_scheduler.load_state_dict(torch.load(sched, map_location='cpu', weights_only=True))
+        info = {'cur_step': 0, 'consumed_train_samples': 0, 'gradient_accumulation_steps': og.gradient_accumulation_steps}
+        ts = os.path.join(path, 'trainer_state.json')
+        if os.path.isfile(ts):
+            with open(ts) as fh:
+                info.update(json.load(fh))
+            og.cur_step, og.consumed_train_samples = info['cur_step'], info['consumed_train_samples']
+        return info
+
+    @remote_function(collect='first')
+    def resume_from_checkpoint(self, checkpoint_dir: str, *, adapter_name: Optional[str] = None, resume_only_model: bool = False,
+                               **kwargs) -> Dict[str, Any]:
+        if adapter_name is None:
+            return MegatronModel.resume_from_checkpoint.__wrapped__(self, checkpoint_dir, resume_only_model=resume_only_model, **kwargs)
+        self.load(None, checkpoint_dir, adapter_name=adapter_name)
+        og = self._group(adapter_name)
+        if resume_only_model:
+            return {'cur_step': 0, 'consumed_train_samples': 0, 'gradient_accumulation_steps': og.gradient_accumulation_steps}
+        info = self._load_tenant_state(adapter_name, checkpoint_dir)
+        return {k: info[k] for k in ('cur_step', 'consumed_train_samples', 'gradient_accumulation_steps')}

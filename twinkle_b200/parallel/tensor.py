@@ -118,6 +118,24 @@ def tp_linear_forward(lin, x: torch.Tensor) -> torch.Tensor:
     """Forward of a ``models.layers.Linear`` whose weight is a TP shard (``lin.tp_mode`` in {'col', 'row'})."""
     tp: TPContext = lin.tp
     f = tp.fused
+    from ..models.layers import current_lora_batch
+    lb = current_lora_batch() if lin.max_loras > 0 else None
+    if lb is not None:
+        # Adapters on a sharded linear (reference ``model/multi_lora.py:289-475``).  Column-parallel: ``A`` is replicated
+        # and ``B`` holds this rank's output rows, so the delta lands on the local output shard.  Row-parallel: ``A``
+        # holds this rank's input columns and ``B`` is replicated; ``B·(A_r x_r)`` is added to the partial product
+        # BEFORE the reduction, which sums the ranks' parts of ``A x`` for free.
+        if lin.tp_mode == 'col':
+            xg = tp.before_column(x)
+            y = ops.linear(xg, lin.weight, lin.bias)
+            d = lin._lora_delta(xg.reshape(-1, xg.shape[-1]), lb)
+            return y if d is None else y + d.view(y.shape)
+        y = ops.linear(x, lin.weight, None)
+        d = lin._lora_delta(x.reshape(-1, x.shape[-1]), lb)
+        if d is not None:
+            y = y + d.view(y.shape)
+        y = tp.after_row(y)
+        return y if lin.bias is None else y + lin.bias
     if f is not None and tp.sp and x.is_cuda and x.dim() == 2:
         from .tensor_fused import ColumnLinearFused, FusedTP, RowLinearFused
         if lin.tp_mode == 'col' and FusedTP.eligible(x.shape[0], x.shape[1], lin.weight.shape[0], x.dtype):
@@ -219,10 +237,25 @@ def apply_tensor_parallel(model, cfg, comm: Communicator, sequence_parallel: boo
     for layer in model.layers:
         at = layer.self_attn
         at.hq, at.hkv = cfg.num_attention_heads // tp.size, cfg.num_key_value_heads // tp.size
-        for lin, mode in ((at.qkv_proj, 'col'), (at.o_proj, 'row')):
-            lin.tp, lin.tp_mode = tp, mode
+        pairs = [(at.qkv_proj, 'col'), (at.o_proj, 'row')]
         if not layer.is_moe:
-            layer.mlp.gate_up_proj.tp, layer.mlp.gate_up_proj.tp_mode = tp, 'col'
-            layer.mlp.down_proj.tp, layer.mlp.down_proj.tp_mode = tp, 'row'
+            pairs += [(layer.mlp.gate_up_proj, 'col'), (layer.mlp.down_proj, 'row')]
+        for lin, mode in pairs:
+            lin.tp, lin.tp_mode = tp, mode
+            # the module's declared sizes follow its shard, so that an adapter pool created afterwards has the local
+            # shapes (B rows of a column-parallel part, A columns of a row-parallel input)
+            if mode == 'col':
+                lin.parts = [(n, k // tp.size) for n, k in lin.parts]
+                lin.out_features //= tp.size
+            else:
+                lin.in_features //= tp.size
     model.tp = tp
     return tp
+
+
+def lora_param_is_replicated(name: str, tp_mode: Optional[str]) -> bool:
+    """Whether an adapter-pool tensor of a tensor-parallel linear is the same on every rank of the group (its gradient is
+    then a partial sum that must be all-reduced): ``A`` of a column-parallel linear and ``B`` of a row-parallel one.
+    The other two are shards."""
+    is_a = 'lora_A' in name
+    return (tp_mode == 'col' and is_a) or (tp_mode == 'row' and not is_a) or tp_mode is None
