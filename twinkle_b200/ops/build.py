@@ -32,6 +32,19 @@ def _sources() -> List[str]:
     return sorted(glob.glob(os.path.join(_CSRC, '*.cu')) + glob.glob(os.path.join(_CSRC, '*.cpp')))
 
 
+def _local_includes(path: str, seen=None) -> List[str]:
+    """In-tree headers reachable from ``path`` through ``#include "…"`` lines (sorted, each once)."""
+    import re
+    seen = set() if seen is None else seen
+    with open(path, errors='replace') as f:
+        for name in re.findall(r'^\s*#\s*include\s*"([^"]+)"', f.read(), flags=re.M):
+            hdr = os.path.join(_CSRC, name)
+            if os.path.isfile(hdr) and hdr not in seen:
+                seen.add(hdr)
+                _local_includes(hdr, seen)
+    return sorted(seen)
+
+
 def _digest() -> str:
     h = hashlib.sha1()
     for f in _sources() + sorted(glob.glob(os.path.join(_CSRC, '*.cuh')) + glob.glob(os.path.join(_CSRC, '*.h'))):
@@ -82,7 +95,7 @@ def _build_locked(verbose: bool, jobs: Optional[int]) -> str:
         obj = os.path.join(build_dir, os.path.basename(src) + '.o')
         dep_stamp = obj + '.sha'
         h = hashlib.sha1(open(src, 'rb').read())
-        for hdr in sorted(glob.glob(os.path.join(_CSRC, '*.cuh')) + glob.glob(os.path.join(_CSRC, '*.h'))):
+        for hdr in _local_includes(src):  # only the headers this source pulls in: touching one header rebuilds its users
             h.update(open(hdr, 'rb').read())
         h.update(' '.join(NVCC_FLAGS).encode())
         if os.path.isfile(obj) and os.path.isfile(dep_stamp) and open(dep_stamp).read() == h.hexdigest():

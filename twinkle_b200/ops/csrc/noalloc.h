@@ -21,6 +21,11 @@ extern "C" {
 // The first call on a device does the set-up (symbol address look-up, SM count); make that call before any stream
 // capture begins.  Calls on one device share the scratch: two calls that overlap in time (different streams or
 // threads) race — issue them on one stream or order them with events.
+// Two host threads that both make the first call on a device at the same moment both run the set-up; they write the
+// same values, so the outcome is the same, but the set-up is not otherwise synchronised — if the first call may come
+// from several threads, make one call up front.  The scratch is guaranteed to be back at zero only after a call
+// that returned 0 has completed on the device: after −3 (launch failed) or a kernel that was aborted, its contents
+// are unspecified and the next result may be wrong until the library is reloaded.
 // Returns 0, or a negative code: −1 bad shape / alignment, −2 set-up failed, −3 launch failed (see tk_noalloc_strerror).
 int tk_rmsnorm_bwd_noalloc(const void* g, const void* x, const void* w, const float* rstd, void* dx, float* dw, int rows, int H,
                            float offset, cudaStream_t stream);

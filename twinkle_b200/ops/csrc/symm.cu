@@ -16,6 +16,7 @@
 // No TMA multicast and no library kernel ever touches a peer pointer; every wait is bounded and reports
 // through the error word.
 #include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDACachingAllocator.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <pybind11/pybind11.h>
 #include <torch/extension.h>
@@ -44,7 +45,18 @@ std::tuple<torch::Tensor, py::bytes, int64_t> symm_alloc(int64_t nbytes) {
   void* ptr = nullptr;
   const int64_t gran = 2 << 20;  // whole 2 MiB pages: every symmetric buffer owns its driver block
   nbytes = (nbytes + gran - 1) / gran * gran;
-  TK_CUDA_CHECK(cudaMalloc(&ptr, nbytes));
+  cudaError_t rc = cudaMalloc(&ptr, nbytes);
+  if (rc == cudaErrorMemoryAllocation) {
+    // Symmetric buffers come straight from the driver, next to PyTorch's caching allocator.  Blocks that the allocator
+    // holds but does not use are handed back and the request is made once more; the failed attempt's error code is
+    // cleared so that it does not surface in an unrelated later call.
+    (void)cudaGetLastError();
+    TK_CUDA_CHECK(cudaDeviceSynchronize());
+    c10::cuda::CUDACachingAllocator::emptyCache();
+    rc = cudaMalloc(&ptr, nbytes);
+    if (rc != cudaSuccess) (void)cudaGetLastError();
+  }
+  TORCH_CHECK(rc == cudaSuccess, "symmetric allocation of ", nbytes, " bytes failed: ", cudaGetErrorString(rc));
   TK_CUDA_CHECK(cudaMemset(ptr, 0, nbytes));
   TK_CUDA_CHECK(cudaDeviceSynchronize());
   cudaIpcMemHandle_t h;

@@ -35,16 +35,7 @@ class SymmBuffer:
 
     def __init__(self, comm: 'SymmCommunicator', nbytes: int):
         E = ops.ext()
-        try:
-            self.raw, handle, offset = E.symm_alloc(nbytes)
-        except RuntimeError as e:
-            if 'out of memory' not in str(e):
-                raise
-            # symmetric buffers come straight from the driver; blocks that PyTorch's caching allocator holds but does
-            # not use are given back first
-            torch.cuda.synchronize()
-            torch.cuda.empty_cache()
-            self.raw, handle, offset = E.symm_alloc(nbytes)
+        self.raw, handle, offset = E.symm_alloc(nbytes)  # retries once after emptying PyTorch's cache when the driver is out of memory
         self.nbytes = self.raw.numel()
         infos = comm.gather_object((handle, offset, self.nbytes))
         if len({i[2] for i in infos}) != 1:

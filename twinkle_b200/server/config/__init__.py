@@ -5,7 +5,8 @@ Parity: reference ``src/twinkle/server/config/server_config.py:28-82``, ``applic
 ``http_options``, ``telemetry``, ``persistence {mode: memory|file|redis}``, ``task_queue`` and a list of
 ``applications`` (``import_path`` ∈ server | model | sampler | processor) with typed ``args``.
 The reference deploys through Ray Serve; here every application is a FastAPI sub-app mounted at its
-``route_prefix`` in one uvicorn process, with model/sampler workers in a torchrun-style worker pool.
+``route_prefix`` in one uvicorn process; a model or sampler application whose ``device_group`` has more than one rank
+(or ``workers: pool``) builds its backend in a worker-pool device group, one process per rank.
 """
 from __future__ import annotations
 
