@@ -31,6 +31,12 @@ class PreferenceLoss(Loss):
         return logps, mask, seq
 
     @staticmethod
+    def _nll(chosen_seq_logps: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+        """Negative log-likelihood of the chosen rows per chosen *token* over the whole batch (total divided by the
+        number of chosen tokens, reference ``loss/dpo.py:64-71``), not a mean of per-sequence means."""
+        return -chosen_seq_logps.sum() / mask[0::2].sum().clamp_min(1)
+
+    @staticmethod
     def _align_ref(ref, logps, mask):
         """Reference logps may be per-token ``[B, S']`` (S' ≥ or ≤ S), or
         already per-sequence ``[B]``."""
@@ -61,16 +67,26 @@ class DPOLoss(PreferenceLoss):
         self.reference_free, self.sft_weight = reference_free, sft_weight
 
     def __call__(self, inputs: Dict[str, Any], outputs: Dict[str, Any], *, ref_outputs=None, ref_logps=None,
-                 **kwargs) -> LossOutput:
+                 ref_chosen_logps=None, ref_rejected_logps=None, **kwargs) -> LossOutput:
+        """The reference policy comes as ``ref_outputs`` / ``ref_logps`` (per token or per sequence, rows interleaved
+        like the batch) or as the two sequence-level vectors ``ref_chosen_logps`` / ``ref_rejected_logps``
+        (reference ``src/twinkle/loss/dpo.py:257-320``)."""
         logps, mask, seq = self._seq_logps(inputs, outputs)
         pc, pr = seq[0::2], seq[1::2]
-        ref = self._align_ref(ref_outputs if ref_outputs is not None else ref_logps, logps, mask)
-        if ref is None and not self.reference_free:
-            return LossOutput(loss=logps.sum() * 0.0, num_tokens=0)
-        if ref is None:
-            rc = rr = torch.zeros_like(pc)
+        ref = None
+        if ref_chosen_logps is not None and ref_rejected_logps is not None:
+            rc = torch.as_tensor(ref_chosen_logps).to(pc.device, pc.dtype).reshape(-1)
+            rr = torch.as_tensor(ref_rejected_logps).to(pc.device, pc.dtype).reshape(-1)
+            if rc.numel() != pc.numel() or rr.numel() != pr.numel():
+                raise ValueError(f'ref_chosen_logps / ref_rejected_logps must hold one value per pair ({pc.numel()}), got {rc.numel()} / {rr.numel()}')
         else:
-            rc, rr = ref[0::2], ref[1::2]
+            ref = self._align_ref(ref_outputs if ref_outputs is not None else ref_logps, logps, mask)
+            if ref is None and not self.reference_free:
+                return LossOutput(loss=logps.sum() * 0.0, num_tokens=0)
+            if ref is None:
+                rc = rr = torch.zeros_like(pc)
+            else:
+                rc, rr = ref[0::2], ref[1::2]
         dc, dr = pc - rc, pr - rr
         z = self.beta * (dc - dr)
         if self.loss_type == 'sigmoid':
@@ -79,13 +95,12 @@ class DPOLoss(PreferenceLoss):
         elif self.loss_type == 'hinge':
             per_pair = torch.relu(1 - z)
         elif self.loss_type == 'ipo':
-            per_pair = (z / self.beta - 1 / (2 * self.beta))**2
+            per_pair = (z - 1 / (2 * self.beta))**2  # on the β-scaled margin, as the reference (dpo.py:234-237)
         else:  # kto_pair
             per_pair = 1 - torch.sigmoid(self.beta * dc) + torch.sigmoid(self.beta * dr)
         loss = per_pair.mean()
         if self.sft_weight > 0:
-            n_c = mask[0::2].sum(-1).clamp_min(1)
-            loss = loss + self.sft_weight * (-(pc / n_c)).mean()
+            loss = loss + self.sft_weight * self._nll(pc, mask)
         self.last_stats = {
             'rewards/chosen': float((self.beta * dc).mean().detach()), 'rewards/rejected': float((self.beta * dr).mean().detach()),
             'rewards/margins': float((self.beta * (dc - dr)).mean().detach()), 'rewards/accuracies': float((dc > dr).float().mean()),
@@ -118,8 +133,7 @@ class CPOLoss(PreferenceLoss):
     def __call__(self, inputs, outputs, **kwargs) -> LossOutput:
         logps, mask, seq = self._seq_logps(inputs, outputs)
         pref = -F.logsigmoid(self.beta * (seq[0::2] - seq[1::2])).mean()
-        nll = -(seq[0::2] / mask[0::2].sum(-1).clamp_min(1)).mean()
-        return LossOutput(loss=pref + self.bc_coef * nll, num_tokens=0)
+        return LossOutput(loss=pref + self.bc_coef * self._nll(seq[0::2], mask), num_tokens=0)
 
 
 class ORPOLoss(PreferenceLoss):
@@ -134,5 +148,5 @@ class ORPOLoss(PreferenceLoss):
         avg = seq / mask.sum(-1).clamp_min(1)
         c, r = avg[0::2], avg[1::2]
         log_odds = (c - r) - (torch.log1p(-torch.exp(c).clamp(max=1 - 1e-6)) - torch.log1p(-torch.exp(r).clamp(max=1 - 1e-6)))
-        loss = (-c).mean() - self.lambda_orpo * F.logsigmoid(log_odds).mean()
+        loss = self._nll(seq[0::2], mask) - self.lambda_orpo * F.logsigmoid(log_odds).mean()
         return LossOutput(loss=loss, num_tokens=0)

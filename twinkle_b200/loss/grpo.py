@@ -50,7 +50,7 @@ def align_to_mask(values, mask: torch.Tensor, dtype=torch.float32) -> torch.Tens
         elif r.numel() == n_valid:
             out[b, m] = r
         elif r.numel() >= S:
-            out[b] = r[:S] * m.to(dtype)
+            out[b, m] = r[:S][m]  # indexed, not multiplied: a NaN or inf parked in a padding position must not reach the loss
         else:
             raise AssertionError(f'row {b}: cannot align {r.numel()} values to {n_valid} target tokens of a length-{S} row')
     return out
@@ -120,14 +120,16 @@ class GSPOLoss(GRPOLoss):
 
     def _log_ratio(self, logps, old_logps, mask):
         m = mask.to(logps.dtype)
-        seq = ((logps - old_logps) * m).sum(-1, keepdim=True) / m.sum(-1, keepdim=True).clamp_min(1.0)
-        return torch.clamp(seq, -20.0, 20.0).expand_as(logps)
+        # every token's log ratio is clamped first, then averaged (reference ``loss/grpo.py:323-324``)
+        lr = torch.clamp(logps - old_logps, -20.0, 20.0)
+        seq = (lr * m).sum(-1, keepdim=True) / m.sum(-1, keepdim=True).clamp_min(1.0)
+        return seq.expand_as(logps)
 
 
 class SAPOLoss(GRPOLoss):
     """Soft gate ``σ(τ(r−1))·4/τ`` with a temperature chosen by the sign of A."""
 
-    def __init__(self, tau_pos: float = 1.0, tau_neg: float = 1.05, **kw):
+    def __init__(self, tau_pos: float = 1.0, tau_neg: float = 1.0, **kw):
         super().__init__(**kw)
         self.tau_pos, self.tau_neg = tau_pos, tau_neg
 
@@ -140,7 +142,7 @@ class SAPOLoss(GRPOLoss):
 class CISPOLoss(GRPOLoss):
 
     def _surrogate(self, ratio, adv, logps):
-        return -torch.clamp(ratio, max=1.0 + self.epsilon_high).detach() * adv * logps
+        return -torch.clamp(ratio, max=1.0 + self.epsilon).detach() * adv * logps  # reference loss/grpo.py:379
 
     def _aggregate(self, per_token, mask, **kwargs):
         n = kwargs.get('num_items_in_batch')
