@@ -321,8 +321,11 @@ class AttentionStash:
     them in the same order instead of recomputing."""
     current = None
 
-    def __init__(self, mode: str, items=None):
+    def __init__(self, mode: str, items=None, exchanges=None):
+        """``items``: attention outputs; ``exchanges``: tensors received by sequence-parallel exchanges of the same
+        layer (``None`` = do not keep them: the recompute pass exchanges again)."""
         self.mode, self.items, self._i = mode, ([] if items is None else items), 0
+        self.exchanges, self._j = exchanges, 0
 
     def __enter__(self):
         self._prev = AttentionStash.current

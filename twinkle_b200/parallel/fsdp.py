@@ -338,12 +338,17 @@ class _LayerFn(torch.autograd.Function):
         if idx + 1 < len(engine.units):
             engine.units[idx + 1].unshard_async(engine.pool)
         ctx.attn = [] if engine.keep_attention else None
-        with torch.no_grad(), (ops.AttentionStash('save', ctx.attn) if ctx.attn is not None else nullcontext()):
+        ctx.exch = [] if (ctx.attn is not None and engine.keep_exchanges is not False) else None
+        with torch.no_grad(), (ops.AttentionStash('save', ctx.attn, ctx.exch) if ctx.attn is not None else nullcontext()):
             y = layer(x, cos, sin, batch)
             aux = getattr(layer.mlp, 'last_aux', None) if getattr(layer, 'is_moe', False) else None
             if aux is not None:
                 engine.aux_values.append(aux.detach())
                 layer.mlp.last_aux = None
+        if engine.keep_exchanges is None:
+            engine.decide_keep_exchanges(ctx.exch)
+            if engine.keep_exchanges is False:
+                ctx.exch = None
         if engine.reshard_after_forward and idx != len(engine.units) - 1:
             unit.reshard(engine.pool)
         return y
@@ -360,7 +365,7 @@ class _LayerFn(torch.autograd.Function):
         unit.prepare_grads(engine.pool)
         xd = x.detach().requires_grad_(True)
         with torch.enable_grad(), engine.restore_context(ctx.lora_ctx), (
-                ops.AttentionStash('reuse', ctx.attn) if ctx.attn is not None else nullcontext()), ops.dead_values():
+                ops.AttentionStash('reuse', ctx.attn, ctx.exch) if ctx.attn is not None else nullcontext()), ops.dead_values():
             # the layer is re-run for its graph only: the final projection and residual add are not computed
             y = layer(xd, cos, sin, batch)
             outs, grads = [y], [gy]
@@ -369,7 +374,7 @@ class _LayerFn(torch.autograd.Function):
                 grads.append(torch.as_tensor(engine.aux_grad_weight, dtype=layer.mlp.last_aux.dtype, device=gy.device))
                 layer.mlp.last_aux = None
         torch.autograd.backward(outs, grads)
-        ctx.attn = None
+        ctx.attn = ctx.exch = None
         unit.reduce_grads(engine.pool)
         unit.reshard(engine.pool)
         return (None, None, None, xd.grad, None, None, None) + (None, ) * (len(ctx.needs_input_grad) - 7)
@@ -394,6 +399,9 @@ class FSDPEngine:
         self.replica_comm = replica_comm if (replica_comm is not None and replica_comm.world_size > 1) else None
         self._grads_pending = False
         self._replicated_stash: List[Tuple[nn.Parameter, Optional[torch.Tensor]]] = []
+        # whether a layer's forward keeps what its sequence-parallel exchanges received, so that the recompute pass
+        # need not exchange again: decided after the first layer of the first forward from the memory that is left
+        self.keep_exchanges: Optional[bool] = None
         self.keep_attention = keep_attention and torch.device(device or 'cpu').type == 'cuda'
         self.device = device or next(model.parameters()).device
         self.compute_dtype = compute_dtype
@@ -447,6 +455,30 @@ class FSDPEngine:
         self._root_live = False
         self._ctx_capture: Callable[[], object] = lambda: None
         self._ctx_restore = None
+
+    def decide_keep_exchanges(self, first_layer_kept) -> None:
+        """Keeping the received tensors costs ``layers x bytes(first layer's exchanges)``; it is switched on when that
+        fits beside what is still to be allocated (fp32 gradient shards and Adam moments appear on first use) and a
+        margin for the transient activations of the recompute pass and the output head."""
+        if torch.device(self.device).type != 'cuda':
+            self.keep_exchanges = bool(first_layer_kept)
+            return
+        if not first_layer_kept:
+            self.keep_exchanges = False
+            return
+        per_layer = sum(t.numel() * t.element_size() for outs in first_layer_kept for t in outs)
+        pending = 0
+        for b in self.trainable_buckets():
+            if b.grad_shard is None:
+                pending += 4 * b.shard_numel
+            if b.exp_avg is None:
+                pending += 8 * b.shard_numel
+        free, _ = torch.cuda.mem_get_info(self.device)
+        free += torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
+        margin = 56 << 30
+        fits = free - pending - margin > per_layer * len(self.units)
+        # the ranks of an exchange must agree (one that exchanged again while its peer did not would wait for nobody)
+        self.keep_exchanges = bool(self.comm.all_reduce_scalar(1.0 if fits else 0.0, 'min') > 0.5)
 
     # context (LoRA routing) must be identical in the recompute
     def capture_context(self):

@@ -116,13 +116,13 @@ def _exchange(comm, seq_to_head: bool, xs):
     pass takes them back instead of exchanging again (two of the six cross-GPU meeting points per layer go away)."""
     from .. import ops
     st = ops.AttentionStash.current
-    if st is not None and st.mode == 'save' and not torch.is_grad_enabled():
+    if st is not None and st.exchanges is not None and st.mode == 'save' and not torch.is_grad_enabled():
         outs = tuple(comm.exchange_heads(list(xs), seq_to_head))
-        st.items.append(outs)
+        st.exchanges.append(outs)
         return outs
-    if st is not None and st.mode == 'reuse' and st._i < len(st.items):
-        kept = st.items[st._i]
-        st._i += 1
+    if st is not None and st.exchanges is not None and st.mode == 'reuse' and st._j < len(st.exchanges):
+        kept = st.exchanges[st._j]
+        st._j += 1
         return _ExchangeReuse.apply(comm, seq_to_head, kept, *xs)
     return _ExchangeMany.apply(comm, seq_to_head, *xs)
 
