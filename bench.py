@@ -1,5 +1,10 @@
 #!/usr/bin/env python
-"""Headline benchmark: training tokens/s of Qwen3-8B-architecture full-parameter SFT.
+"""Headline benchmark: training tokens/s of Qwen3-8B-architecture full-parameter SFT, and of Qwen3-30B-A3B LoRA SFT.
+
+By default (``--config both``) the two halves of the headline metric run one after the other, each in a process of
+its own: the dense result fills the top-level fields of the printed line, the mixture-of-experts result sits under
+``"moe"`` (BASELINE config 3: 48 layers, hidden 2048, 128 experts top-8, LoRA r=16 on attention and expert linears,
+8 sequences of 4096 tokens per GPU, experts split over all ranks).  ``--config dense`` / ``--config moe`` run one half.
 
     python bench.py --gpus N --steps K --warmup W            (N = 1)
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
@@ -18,7 +23,11 @@ launching stream, max over ranks.  ``value`` times steps whose inputs already si
 inputs taken from pinned host memory every step and the loss read back to the host.  Inputs of one step
 (65536 tokens × hidden activations) exceed the 126 MB L2 many times over, so no explicit flush is needed.
 
-``--impl reference`` runs the unmodified reference from ``baseline/_ref`` if it can be imported.
+``--impl reference`` runs the unmodified reference package from ``baseline/_ref`` through its own public API
+(``baseline/reference_arm.py``; nothing of this repository's package is imported on that path) for the dense half and
+prints the same line with ``"impl": "reference"``.  After the timed regions one more step runs with the phase clock on
+and its per-phase device times are printed as ``phases_ms_per_step``; ``config.data_plane`` says which transport each
+sharded path resolved to, and a silent fall-back of ``--comm auto`` to library collectives ends the run with an error.
 """
 from __future__ import annotations
 
