@@ -154,3 +154,40 @@ def test_layer_recompute_does_not_change_the_numbers(tmp_path):
     for ra, rb in zip(a, b):
         for x, y in zip(ra['first'] + ra['cont'], rb['first'] + rb['cont']):
             assert abs(x - y) < 1e-5, (ra, rb)
+
+
+def _cp_worker(rank, world, tp, pp, cp, steps):
+    from twinkle_b200.model.megatron import MegatronModel
+    from twinkle_b200.models import preset
+    from twinkle_b200.utils.device_mesh import DeviceMesh
+    cfg = preset('tiny-dense', num_hidden_layers=4)
+    mesh = DeviceMesh.from_sizes(tp_size=tp, pp_size=pp, cp_size=cp, dp_size=world // (tp * pp * cp), sequence_parallel=tp > 1)
+    m = MegatronModel(config=cfg, device_mesh=mesh, seed=0)
+    m.set_optimizer('AdamW', lr=1e-3)
+    curve = []
+    for _ in range(steps):
+        o = m.forward_backward(inputs=_feats(), micro_batch_size=2)
+        n = m.clip_grad_and_step(max_grad_norm=1.0)
+        curve.append((o['loss'], n))
+    return curve
+
+
+@pytest.mark.parametrize('tp,pp,cp', [(1, 1, 2), (2, 1, 2), (1, 2, 2)])
+def test_context_parallel_axis_matches_single(tp, pp, cp):
+    """Zig-zag context parallelism on the tensor / pipeline backend: keys and values gathered per layer, whole sequences
+    for the loss, context-parallel ranks reduced like data ranks (reference ``megatron/strategy/megatron.py:90-107``:
+    ``context_parallel_size``)."""
+    from twinkle_b200.model import TransformersModel
+    from twinkle_b200.models import preset
+    from twinkle_b200.utils.device_mesh import DeviceMesh
+    cfg = preset('tiny-dense', num_hidden_layers=4)
+    one = TransformersModel(config=cfg, device_mesh=DeviceMesh.from_sizes(dp_size=1), seed=0)
+    one.set_optimizer('AdamW', lr=1e-3)
+    single = []
+    for _ in range(3):
+        o = one.forward_backward(inputs=_feats(), micro_batch_size=2)
+        n = one.clip_grad_and_step(max_grad_norm=1.0)
+        single.append((o['loss'], n))
+    for curve in run_ranks(_cp_worker, tp * pp * cp, tp, pp, cp, 3):
+        for (a, na), (b, nb) in zip(single, curve):
+            assert abs(a - b) < 3e-4 and abs(na - nb) < 3e-3 * max(na, 1.0), (single, curve)

@@ -94,7 +94,10 @@ class MegatronModel(TwinkleModel):
         multi = dist.is_available() and dist.is_initialized() and mesh.world_size > 1
         self.tp_comm = Communicator(mesh.get_dim_group('tp') if multi and mesh.has_dim('tp') else None, self.device, single=self.tp_size == 1)
         self.pp_group = mesh.get_dim_group('pp') if multi and mesh.has_dim('pp') else None
-        dp_dims = tuple(d for d in ('dp', 'fsdp') if mesh.has_dim(d))
+        # context-parallel ranks hold different tokens of the same sequences: for parameters and gradients they are data
+        # ranks like any other
+        self.cp_size = mesh.cp_world_size or 1
+        dp_dims = tuple(d for d in ('dp', 'fsdp', 'cp') if mesh.has_dim(d))
         dp_world = 1
         for d in dp_dims:
             dp_world *= mesh.get_dim_size(d)
@@ -114,8 +117,15 @@ class MegatronModel(TwinkleModel):
             # parameter names carry GLOBAL layer indices so that seeds / bridge names agree across layouts
             self._rename_for_init(m, lo, seed, load_dir)
             apply_tensor_parallel(m, cfg, self.tp_comm, mesh.sequence_parallel, fused_tp)
+            if self.cp_size > 1:
+                from ..parallel.context import apply_context_parallel
+                apply_context_parallel(m, mesh)  # zig-zag shards, keys / values gathered per layer (``parallel/context.py``)
             self.chunks.append(m)
         self.sequence_parallel = bool(mesh.sequence_parallel and self.tp_size > 1)
+        self.cp_comm = None
+        if self.cp_size > 1:
+            from ..parallel.context import cp_group_for
+            self.cp_comm = Communicator(cp_group_for(mesh), self.device)
         self.runner = PipelineRunner(self.pp_group, self.pp_rank, self.pp_size, self.vpp, self.compute_dtype, self.device)
         self.optimizer_groups: Dict[str, OptimizerGroup] = {'': OptimizerGroup(adapter_name='')}
         self._state: Dict[str, Dict[str, torch.Tensor]] = {}
@@ -166,18 +176,20 @@ class MegatronModel(TwinkleModel):
         og.processor = proc
         proc.micro_batch_size = micro_batch_size or 1
         proc.sp_size = 1
+        proc.cp_size, proc.cp_rank = self.cp_size, (self.device_mesh.cp_rank or 0)
         items = proc.normalize(feats)
-        mult = self.tp_size if self.sequence_parallel else 1
+        # a rank's share of the row (1/cp of every sequence, in two zig-zag halves) must divide over the tp group
+        mult = (self.tp_size if self.sequence_parallel else 1) * (2 * self.cp_size if self.cp_size > 1 else 1)
         mbs = []
         for g in proc.split_micro_batches(items):
-            mbs.append(proc._pack(g, pad_multiple=mult, split=False))  # tokens must divide over the tp group
+            mbs.append(proc._pack(g, pad_multiple=mult, split=self.cp_size > 1))
         return feats, mbs
 
     def _forward_chunk(self, mbs, og, loss_kwargs, results):
         def run(chunk: int, micro: int, x: Optional[torch.Tensor]) -> torch.Tensor:
             m = self.chunks[chunk]
             mb = mbs[micro].to(self.device)
-            batch = PackedBatch(mb.input_ids, mb.position_ids, mb.cu_seqlens, mb.max_seqlen, mb.labels)
+            batch = PackedBatch(mb.input_ids, mb.position_ids, mb.cu_seqlens, mb.max_seqlen, mb.labels, seq_lens=list(mb.seq_lens))
             if x is None:
                 h = m.embed(batch)
                 if m.tp is not None and not m.tp.sp:
@@ -196,12 +208,18 @@ class MegatronModel(TwinkleModel):
                 return h
             h = m.norm(h)
             logps, _ = m.token_logprobs(h, mb.labels)
+            labels = mb.labels
+            if self.cp_comm is not None:  # whole sequences for the loss on every context-parallel rank
+                from ..parallel.context import gather_zigzag_rows
+                logps = gather_zigzag_rows(logps, self.cp_comm, mb.seq_lens, 0, True)
+                labels = gather_zigzag_rows(labels, self.cp_comm, mb.seq_lens, -100, False)
             out = {'logps': InputProcessor.unpack_packed_sequences(logps, mb.seq_lens, 0),
-                   'labels': InputProcessor.unpack_packed_sequences(mb.labels, mb.seq_lens, -100)}
+                   'labels': InputProcessor.unpack_packed_sequences(labels, mb.seq_lens, -100)}
             res = og.loss_instance({'labels': out['labels']}, out, **loss_kwargs(micro))
             loss = res['loss'] if isinstance(res, dict) else res
             nt = float(res.get('num_tokens', 0) or 0) if isinstance(res, dict) else 0.0
-            results.append({'logps': out['logps'].detach(), 'labels': out['labels'], 'num_tokens': nt, 'loss': float(loss.detach())})
+            nt /= self.cp_size                      # every context-parallel peer reports the same rows
+            results.append({'logps': out['logps'].detach(), 'labels': out['labels'], 'num_tokens': nt, 'loss': float(loss.detach()) / self.cp_size})
             return loss
 
         return run
@@ -291,8 +309,8 @@ class MegatronModel(TwinkleModel):
                 continue
             if self.dp_comm.world_size > 1:
                 self.dp_comm.all_reduce(p.grad)
-            if self.tp_size > 1 and tp_rule(n, self.config) is None:
-                self.tp_comm.all_reduce(p.grad)
+            if self.sequence_parallel and tp_rule(n, self.config) is None:
+                self.tp_comm.all_reduce(p.grad)  # replicated tensors saw different tokens on each tp rank
         denom = self.dp_comm.all_reduce_scalar(og.train_status.num_tokens, 'sum') or 1.0
         # 2. global norm: tp-sharded tensors are disjoint (sum over tp), replicated ones counted once; sum over pp
         sq = torch.zeros((), dtype=torch.float32, device=self.device)

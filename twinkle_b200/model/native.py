@@ -423,23 +423,13 @@ class TransformersModel(TwinkleModel, CheckpointEngineMixin):
         if cp > 1:
             # zig-zag shards: concatenate the peers' pieces (differentiable for this rank's own piece) and put every
             # token back at its position in the full packed row, so the loss sees whole sequences on every rank
-            from ..parallel.context import cp_group_for
-            from ..parallel.ulysses import gather_tokens
-            from ..processor import zigzag_indices
+            from ..parallel.context import cp_group_for, gather_zigzag_rows
             if not hasattr(self, '_cp'):
                 self._cp = Communicator(cp_group_for(self.device_mesh), self.device)
             comm = self._cp
-            pieces = []
-            for r in range(cp):
-                off = 0
-                for n in mb.seq_lens:
-                    pieces.append(zigzag_indices(n, cp, r) + off)
-                    off += n
-            perm = torch.cat(pieces).to(self.device)
 
             def full_row(x, fill, differentiable):
-                g = gather_tokens(x, comm) if differentiable else comm.all_gather_tensor(x)
-                return g.new_full((perm.numel(), ) + tuple(g.shape[1:]), fill).index_copy(0, perm, g)
+                return gather_zigzag_rows(x, comm, mb.seq_lens, fill, differentiable)
 
             for k in ('logps', 'entropies', 'logits'):
                 if out.get(k) is not None:

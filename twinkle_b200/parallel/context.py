@@ -86,6 +86,24 @@ class ContextParallelAttention:
         return ops.flash_attn_varlen(q, kg, vg, cu_q, max_q, True, scale, cu_seqlens_k=cu_k, max_seqlen_k=max_k)
 
 
+def gather_zigzag_rows(x: torch.Tensor, comm: Communicator, seq_lens: Sequence[int], fill, differentiable: bool) -> torch.Tensor:
+    """Per-token values of the context-parallel peers put back at their positions in the full packed row: every rank
+    ends up with whole sequences (the loss needs them), and — when ``differentiable`` — back-propagates only into its
+    own zig-zag pieces, so the loss is counted once."""
+    from ..processor import zigzag_indices
+    from .ulysses import gather_tokens
+    cp = comm.world_size
+    pieces = []
+    for r in range(cp):
+        off = 0
+        for n in seq_lens:
+            pieces.append(zigzag_indices(n, cp, r) + off)
+            off += n
+    perm = torch.cat(pieces).to(x.device)
+    g = gather_tokens(x, comm) if differentiable else comm.all_gather_tensor(x)
+    return g.new_full((perm.numel(), ) + tuple(g.shape[1:]), fill).index_copy(0, perm, g)
+
+
 _CP_GROUPS = {}
 
 
