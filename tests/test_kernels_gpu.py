@@ -20,20 +20,22 @@ def E():
 
 def rel(a, b):
     """Error of ``a`` against the reference ``b`` as one number that a norm alone cannot hide things from: the
-    relative Frobenius error, the worst row's error (against the typical row norm, weighted 1/4) and the worst
-    element's error (against the reference's RMS, weighted 1/16).  A single wrong 16-byte vector in a 4096 x 4096
-    output moves the Frobenius term by 1e-3 but the element term by ~1e-1, so ragged-tail and stray-store bugs fail
-    the same bounds that rounding passes."""
-    a, b = a.float(), b.float()
+    relative Frobenius error, the worst row's error (against that row's own norm plus the typical row norm, weighted
+    1/4) and the worst element's error (against its own magnitude plus the reference's RMS, weighted 1/16).  A single
+    wrong 16-byte vector in a 4096 x 4096 output moves the Frobenius term by 1e-3 but the element term by ~5e-2, so
+    ragged-tail and stray-store bugs fail the same bounds that rounding passes; the per-row / per-element scales keep
+    heavy-tailed tensors (a softmax gradient with one large entry per row) from tripping on ordinary rounding."""
+    a, b = a.detach().float(), b.detach().float()
     d = a - b
     fro = float(d.norm() / (b.norm() + 1e-12))
     if b.dim() < 1 or b.numel() == 0:
         return fro
     rms = float(b.pow(2).mean().sqrt()) + 1e-12
-    elem = float(d.abs().max()) / rms
-    rows = d.reshape(-1, d.shape[-1]) if d.dim() > 1 else d.reshape(1, -1)
-    typical_row = rms * math.sqrt(rows.shape[-1])
-    row = float(rows.norm(dim=-1).max()) / typical_row
+    elem = float((d.abs() / (b.abs() + rms)).max())
+    rows_d = d.reshape(-1, d.shape[-1]) if d.dim() > 1 else d.reshape(1, -1)
+    rows_b = b.reshape(-1, b.shape[-1]) if b.dim() > 1 else b.reshape(1, -1)
+    typical_row = rms * math.sqrt(rows_b.shape[-1])
+    row = float((rows_d.norm(dim=-1) / (rows_b.norm(dim=-1) + typical_row)).max())
     return max(fro, row / 4.0, elem / 16.0)
 
 
