@@ -362,3 +362,46 @@ def test_gemm_head_scatter_epilogue(E, sp, t):
         got = bufs[c].float()
         assert not torch.isnan(got).any(), 'a block was not written'
         assert torch.allclose(got, want, atol=2e-2, rtol=2e-2), float((got - want).abs().max())
+
+
+def test_ep_peer_kernels_refuse_out_of_range_indices(E):
+    """The expert-parallel pull kernels turn every index into a peer address only after a range check: a position or a
+    token outside the peers' buffers yields a zero row and ERR_BOUNDS in the error word, and while the word is set the
+    kernels touch no peer memory at all.  One GPU stands in for the group (the 'peers' are local buffers)."""
+    torch.manual_seed(0)
+    H, T, n = 64, 16, 32
+    x = torch.randn(T, H, device='cuda').bfloat16()
+    tok = torch.randint(0, T, (n, ), device='cuda', dtype=torch.int32)
+    src_rank = torch.zeros(8, dtype=torch.int32, device='cuda')
+    src_pos = torch.arange(8, dtype=torch.int32, device='cuda')
+    total = torch.tensor([8], dtype=torch.int32, device='cuda')
+    good = E.ep_rows_gather([x.data_ptr()], [tok.data_ptr()], [], src_rank, src_pos, H, total, n, T)
+    assert torch.equal(good, x[tok[:8].long()]) and E.read_and_clear_error() == 0
+    # a token id beyond the activation buffer, a position beyond the token list, a rank beyond the group
+    tok_bad = tok.clone()
+    tok_bad[3] = T + 5
+    pos_bad = src_pos.clone()
+    pos_bad[5] = n + 7
+    rank_bad = src_rank.clone()
+    rank_bad[6] = 3
+    out = E.ep_rows_gather([x.data_ptr()], [tok_bad.data_ptr()], [], rank_bad, pos_bad, H, total, n, T)
+    torch.cuda.synchronize()
+    for r in (3, 5, 6):
+        assert float(out[r].float().abs().sum()) == 0.0
+    for r in (0, 1, 2, 4, 7):
+        assert torch.equal(out[r], x[tok[r].long()])
+    # the word is still set here: the next launch must not read anything (the output is left as it was allocated)
+    E.ep_rows_gather([x.data_ptr()], [tok.data_ptr()], [], src_rank, src_pos, H, total, n, T)
+    assert E.read_and_clear_error() == 7
+    # combine: a row past the peers' capacity is skipped and reported
+    y = torch.randn(10, H, device='cuda').bfloat16()
+    dst_rank = torch.zeros(4, 2, dtype=torch.int32, device='cuda')
+    dst_row = torch.tensor([[0, 1], [2, 3], [4, 99], [5, 6]], dtype=torch.int32, device='cuda')
+    w = torch.ones(4, 2, device='cuda')
+    out = E.ep_rows_combine([y.data_ptr()], dst_rank, dst_row, w, H, 10)
+    torch.cuda.synchronize()
+    assert rel(out[2], y[4].float()) < 1e-2 and rel(out[0], (y[0].float() + y[1].float())) < 1e-2
+    assert E.read_and_clear_error() == 7
+    dw = E.ep_combine_wgrad(out.contiguous(), [y.data_ptr()], dst_rank, dst_row, 10)
+    torch.cuda.synchronize()
+    assert float(dw[2, 1]) == 0.0 and E.read_and_clear_error() == 7

@@ -54,9 +54,9 @@ torch::Tensor moe_rows_gather(const torch::Tensor&, const torch::Tensor&, const 
 torch::Tensor moe_rows_combine(const torch::Tensor&, const torch::Tensor&, const c10::optional<torch::Tensor>&);
 torch::Tensor moe_combine_wgrad(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&);
 torch::Tensor ep_rows_gather(const std::vector<int64_t>&, const std::vector<int64_t>&, const std::vector<int64_t>&, const torch::Tensor&, const torch::Tensor&, int64_t,
-                             const torch::Tensor&);
-torch::Tensor ep_rows_combine(const std::vector<int64_t>&, const torch::Tensor&, const torch::Tensor&, const c10::optional<torch::Tensor>&, int64_t);
-torch::Tensor ep_combine_wgrad(const torch::Tensor&, const std::vector<int64_t>&, const torch::Tensor&, const torch::Tensor&);
+                             const torch::Tensor&, int64_t, int64_t);
+torch::Tensor ep_rows_combine(const std::vector<int64_t>&, const torch::Tensor&, const torch::Tensor&, const c10::optional<torch::Tensor>&, int64_t, int64_t);
+torch::Tensor ep_combine_wgrad(const torch::Tensor&, const std::vector<int64_t>&, const torch::Tensor&, const torch::Tensor&, int64_t);
 }  // namespace tk
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {

@@ -205,9 +205,14 @@ struct EpPtrs {
 
 // out[r] = scale · x_s[tok_s[pos]] with s = src_rank[r], pos = src_pos[r]; s < 0 → zero row.
 // `total_rows` (device int) is checked against R once: rows that did not fit are reported through the error word.
+// Every index that becomes a peer address is range-checked first (source rank against the group size, position against
+// the capacity of the peers' token lists, token against the rows of the peers' activation buffers): a bad one records
+// ERR_BOUNDS and yields a zero row instead of a wild NVLink read.  Once the error word is set (a peer never arrived at
+// the barrier before this launch, or an earlier check failed) no peer memory is touched at all.
 __global__ void __launch_bounds__(256) ep_rows_gather_kernel(EpPtrs xs, EpPtrs toks, EpPtrs ws, int use_w, const int* __restrict__ src_rank,
                                                               const int* __restrict__ src_pos, bf16* __restrict__ out, int R, int H,
-                                                              const int* __restrict__ total_rows, int* err) {
+                                                              const int* __restrict__ total_rows, int* err, int n_peers, int tok_cap, int x_rows) {
+  if (*reinterpret_cast<volatile int*>(err) != 0) return;
   if (blockIdx.x == 0 && threadIdx.x == 0 && total_rows != nullptr && *total_rows > R) atomicCAS(err, 0, ERR_BOUNDS);
   const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
   const int nvec = H >> 3;
@@ -221,7 +226,13 @@ __global__ void __launch_bounds__(256) ep_rows_gather_kernel(EpPtrs xs, EpPtrs t
       continue;
     }
     const int pos = src_pos[r];
-    const int tok = reinterpret_cast<const int*>(toks.p[s])[pos];
+    int tok = -1;
+    if (s < n_peers && pos >= 0 && pos < tok_cap) tok = reinterpret_cast<const int*>(toks.p[s])[pos];
+    if (tok < 0 || tok >= x_rows) {
+      if (lane == 0) atomicCAS(err, 0, ERR_BOUNDS);
+      for (int v = lane; v < nvec; v += 32) o[v] = make_uint4(0u, 0u, 0u, 0u);
+      continue;
+    }
     const float c = use_w ? reinterpret_cast<const float*>(ws.p[s])[pos] : 1.f;
     const uint4* in = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(xs.p[s]) + static_cast<size_t>(tok) * H);
     for (int v = lane; v < nvec; v += 32) {
@@ -242,7 +253,9 @@ __global__ void __launch_bounds__(256) ep_rows_gather_kernel(EpPtrs xs, EpPtrs t
 // out[t] = Σ_j w[t,j] · y_{d}[row] with d = dst_rank[t,j] (< 0 → skipped), row = dst_row[t,j].
 template <int K>
 __global__ void __launch_bounds__(256) ep_rows_combine_kernel(EpPtrs ys, const int* __restrict__ dst_rank, const int* __restrict__ dst_row,
-                                                               const float* __restrict__ w, bf16* __restrict__ out, int T, int H) {
+                                                               const float* __restrict__ w, bf16* __restrict__ out, int T, int H, int* err,
+                                                               int n_peers, int y_rows) {
+  if (*reinterpret_cast<volatile int*>(err) != 0) return;
   const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
   const int nvec = H >> 3;
   for (int t = blockIdx.x * warps + (threadIdx.x >> 5); t < T; t += gridDim.x * warps) {
@@ -252,7 +265,9 @@ __global__ void __launch_bounds__(256) ep_rows_combine_kernel(EpPtrs ys, const i
     for (int j = 0; j < K; ++j) {
       const int d = dst_rank[static_cast<size_t>(t) * K + j];
       const int row = dst_row[static_cast<size_t>(t) * K + j];
-      src[j] = d < 0 ? nullptr : reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(ys.p[d]) + static_cast<size_t>(row) * H);
+      const bool bad = d >= n_peers || (d >= 0 && (row < 0 || row >= y_rows));
+      if (bad && lane == 0) atomicCAS(err, 0, ERR_BOUNDS);
+      src[j] = (d < 0 || bad) ? nullptr : reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(ys.p[d]) + static_cast<size_t>(row) * H);
       ws[j] = w ? w[static_cast<size_t>(t) * K + j] : 1.f;
     }
     uint4* o = reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H);
@@ -278,7 +293,9 @@ __global__ void __launch_bounds__(256) ep_rows_combine_kernel(EpPtrs ys, const i
 // dw[t,j] = <g[t], y_{d}[row]>
 template <int K>
 __global__ void __launch_bounds__(256) ep_combine_wgrad_kernel(const bf16* __restrict__ g, EpPtrs ys, const int* __restrict__ dst_rank,
-                                                                const int* __restrict__ dst_row, float* __restrict__ dw, int T, int H) {
+                                                                const int* __restrict__ dst_row, float* __restrict__ dw, int T, int H, int* err,
+                                                                int n_peers, int y_rows) {
+  if (*reinterpret_cast<volatile int*>(err) != 0) return;
   const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
   const int nvec = H >> 3;
   for (int t = blockIdx.x * warps + (threadIdx.x >> 5); t < T; t += gridDim.x * warps) {
@@ -288,7 +305,9 @@ __global__ void __launch_bounds__(256) ep_combine_wgrad_kernel(const bf16* __res
     for (int j = 0; j < K; ++j) {
       const int d = dst_rank[static_cast<size_t>(t) * K + j];
       const int row = dst_row[static_cast<size_t>(t) * K + j];
-      src[j] = d < 0 ? nullptr : reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(ys.p[d]) + static_cast<size_t>(row) * H);
+      const bool bad = d >= n_peers || (d >= 0 && (row < 0 || row >= y_rows));
+      if (bad && lane == 0) atomicCAS(err, 0, ERR_BOUNDS);
+      src[j] = (d < 0 || bad) ? nullptr : reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(ys.p[d]) + static_cast<size_t>(row) * H);
       acc[j] = 0.f;
     }
     const uint4* gr = reinterpret_cast<const uint4*>(g + static_cast<size_t>(t) * H);
@@ -328,8 +347,11 @@ static void check_i32(const torch::Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kInt32 && t.is_contiguous(), name, " must be a contiguous int32 CUDA tensor");
 }
 
+// `tok_cap`: entries of every peer's token (and weight) list; `x_rows`: rows of every peer's activation buffer.
 torch::Tensor ep_rows_gather(const std::vector<int64_t>& x_ptrs, const std::vector<int64_t>& tok_ptrs, const std::vector<int64_t>& w_ptrs,
-                             const torch::Tensor& src_rank, const torch::Tensor& src_pos, int64_t H, const torch::Tensor& total_rows) {
+                             const torch::Tensor& src_rank, const torch::Tensor& src_pos, int64_t H, const torch::Tensor& total_rows,
+                             int64_t tok_cap, int64_t x_rows) {
+  TORCH_CHECK(tok_cap > 0 && x_rows > 0 && tok_ptrs.size() == x_ptrs.size(), "ep_rows_gather: capacities of the peers' buffers are required");
   check_i32(src_rank, "src_rank");
   check_i32(src_pos, "src_pos");
   check_i32(total_rows, "total_rows");
@@ -340,14 +362,16 @@ torch::Tensor ep_rows_gather(const std::vector<int64_t>& x_ptrs, const std::vect
   if (R == 0) return out;
   ep_rows_gather_kernel<<<grid_for(R), 256, 0, at::cuda::getCurrentCUDAStream()>>>(
       to_ptrs(x_ptrs), to_ptrs(tok_ptrs), to_ptrs(w_ptrs), w_ptrs.empty() ? 0 : 1, src_rank.data_ptr<int>(), src_pos.data_ptr<int>(),
-      reinterpret_cast<bf16*>(out.data_ptr()), R, static_cast<int>(H), total_rows.data_ptr<int>(), error_word());
+      reinterpret_cast<bf16*>(out.data_ptr()), R, static_cast<int>(H), total_rows.data_ptr<int>(), error_word(), static_cast<int>(x_ptrs.size()),
+      static_cast<int>(tok_cap), static_cast<int>(x_rows));
   count_launch();
   TK_CUDA_CHECK(cudaGetLastError());
   return out;
 }
 
 torch::Tensor ep_rows_combine(const std::vector<int64_t>& y_ptrs, const torch::Tensor& dst_rank, const torch::Tensor& dst_row,
-                              const c10::optional<torch::Tensor>& w, int64_t H) {
+                              const c10::optional<torch::Tensor>& w, int64_t H, int64_t y_rows) {
+  TORCH_CHECK(y_rows > 0, "ep_rows_combine: the row capacity of the peers' buffers is required");
   check_i32(dst_rank, "dst_rank");
   check_i32(dst_row, "dst_row");
   TORCH_CHECK(dst_rank.dim() == 2 && dst_row.sizes() == dst_rank.sizes() && H % 8 == 0, "bad shapes");
@@ -363,13 +387,16 @@ torch::Tensor ep_rows_combine(const std::vector<int64_t>& y_ptrs, const torch::T
   auto stream = at::cuda::getCurrentCUDAStream();
   const EpPtrs ys = to_ptrs(y_ptrs);
   TK_K_SWITCH(K, (ep_rows_combine_kernel<KK><<<grid_for(T), 256, 0, stream>>>(ys, dst_rank.data_ptr<int>(), dst_row.data_ptr<int>(), wp,
-                                                                              reinterpret_cast<bf16*>(out.data_ptr()), T, static_cast<int>(H))));
+                                                                              reinterpret_cast<bf16*>(out.data_ptr()), T, static_cast<int>(H), error_word(),
+                                                                              static_cast<int>(y_ptrs.size()), static_cast<int>(y_rows))));
   count_launch();
   TK_CUDA_CHECK(cudaGetLastError());
   return out;
 }
 
-torch::Tensor ep_combine_wgrad(const torch::Tensor& g, const std::vector<int64_t>& y_ptrs, const torch::Tensor& dst_rank, const torch::Tensor& dst_row) {
+torch::Tensor ep_combine_wgrad(const torch::Tensor& g, const std::vector<int64_t>& y_ptrs, const torch::Tensor& dst_rank, const torch::Tensor& dst_row,
+                               int64_t y_rows) {
+  TORCH_CHECK(y_rows > 0, "ep_combine_wgrad: the row capacity of the peers' buffers is required");
   check_rows(g, "g");
   check_i32(dst_rank, "dst_rank");
   check_i32(dst_row, "dst_row");
@@ -381,7 +408,8 @@ torch::Tensor ep_combine_wgrad(const torch::Tensor& g, const std::vector<int64_t
   auto stream = at::cuda::getCurrentCUDAStream();
   const EpPtrs ys = to_ptrs(y_ptrs);
   TK_K_SWITCH(K, (ep_combine_wgrad_kernel<KK><<<grid_for(T), 256, 0, stream>>>(reinterpret_cast<const bf16*>(g.data_ptr()), ys, dst_rank.data_ptr<int>(),
-                                                                               dst_row.data_ptr<int>(), dw.data_ptr<float>(), T, H)));
+                                                                               dst_row.data_ptr<int>(), dw.data_ptr<float>(), T, H, error_word(),
+                                                                               static_cast<int>(y_ptrs.size()), static_cast<int>(y_rows))));
   count_launch();
   TK_CUDA_CHECK(cudaGetLastError());
   return dw;

@@ -97,10 +97,13 @@ def ep_metadata(flat_idx: torch.Tensor, counts_all: torch.Tensor, me: int, k: in
 
 
 # --------------------------------------------------------------------- peer pulls (CUDA kernels / CPU emulation)
-def pull_rows(x_bufs, tok_bufs, w_bufs, meta: EPMeta, H: int) -> torch.Tensor:
-    """``out[r] = (w_s[pos]) · x_s[tok_s[pos]]``; buffers are per-rank tensors (CPU) or device pointers (CUDA)."""
+def pull_rows(x_bufs, tok_bufs, w_bufs, meta: EPMeta, H: int, tok_cap: int = 0, x_rows: int = 0) -> torch.Tensor:
+    """``out[r] = (w_s[pos]) · x_s[tok_s[pos]]``; buffers are per-rank tensors (CPU) or device pointers (CUDA).
+    ``tok_cap`` / ``x_rows``: capacities of every peer's token list and activation buffer — the kernel checks each
+    position and token it reads from a peer against them before using it as an address."""
     if isinstance(x_bufs[0], int):
-        return ops.ext().ep_rows_gather(list(x_bufs), list(tok_bufs), list(w_bufs) if w_bufs else [], meta.src_rank, meta.src_pos, H, meta.total_rows)
+        return ops.ext().ep_rows_gather(list(x_bufs), list(tok_bufs), list(w_bufs) if w_bufs else [], meta.src_rank, meta.src_pos, H, meta.total_rows,
+                                        tok_cap, x_rows)
     out = x_bufs[0].new_zeros(meta.src_rank.numel(), H)
     for s in range(len(x_bufs)):
         m = meta.src_rank == s
@@ -112,10 +115,10 @@ def pull_rows(x_bufs, tok_bufs, w_bufs, meta: EPMeta, H: int) -> torch.Tensor:
     return out
 
 
-def pull_combine(y_bufs, meta: EPMeta, w: Optional[torch.Tensor], H: int) -> torch.Tensor:
-    """``out[t] = Σ_j w[t, j] · y_d[row]``."""
+def pull_combine(y_bufs, meta: EPMeta, w: Optional[torch.Tensor], H: int, y_rows: int = 0) -> torch.Tensor:
+    """``out[t] = Σ_j w[t, j] · y_d[row]`` (``y_rows``: row capacity of every peer's buffer, checked in the kernel)."""
     if isinstance(y_bufs[0], int):
-        return ops.ext().ep_rows_combine(list(y_bufs), meta.dst_rank, meta.dst_row, None if w is None else w.float().contiguous(), H)
+        return ops.ext().ep_rows_combine(list(y_bufs), meta.dst_rank, meta.dst_row, None if w is None else w.float().contiguous(), H, y_rows)
     T, k = meta.dst_rank.shape
     out = y_bufs[0].new_zeros(T, H)
     for d in range(len(y_bufs)):
@@ -126,10 +129,10 @@ def pull_combine(y_bufs, meta: EPMeta, w: Optional[torch.Tensor], H: int) -> tor
     return out
 
 
-def pull_wgrad(g: torch.Tensor, y_bufs, meta: EPMeta) -> torch.Tensor:
+def pull_wgrad(g: torch.Tensor, y_bufs, meta: EPMeta, y_rows: int = 0) -> torch.Tensor:
     """``dw[t, j] = <g[t], y_d[row]>``."""
     if isinstance(y_bufs[0], int):
-        return ops.ext().ep_combine_wgrad(g.contiguous(), list(y_bufs), meta.dst_rank, meta.dst_row)
+        return ops.ext().ep_combine_wgrad(g.contiguous(), list(y_bufs), meta.dst_rank, meta.dst_row, y_rows)
     T, k = meta.dst_rank.shape
     dw = torch.zeros(T, k, dtype=torch.float32, device=g.device)
     for d in range(len(y_bufs)):
@@ -231,7 +234,7 @@ class _EPDispatch(torch.autograd.Function):
         counts_all = torch.empty(strat.ep, strat.num_experts, dtype=torch.int32, device=x.device)
         strat.comm.ext.peer_all_gather(counts_all, s.counts_ptrs, strat.num_experts * 4, strat.rank, 1)
         meta = ep_metadata(flat, counts_all, strat.rank, k, cap, 128)
-        xs = pull_rows(s.x_ptrs, s.tok_ptrs, None, meta, x.shape[1])
+        xs = pull_rows(s.x_ptrs, s.tok_ptrs, None, meta, x.shape[1], s.tok.numel(), s.x.shape[0])
         ctx.strat, ctx.meta, ctx.H = strat, meta, x.shape[1]
         ctx.set_materialize_grads(False)
         return xs, meta
@@ -241,7 +244,7 @@ class _EPDispatch(torch.autograd.Function):
         if gxs is None:
             return None, None, None, None, None, None
         s = ctx.strat.publish(y=gxs.contiguous())
-        gx = pull_combine(s.y_ptrs, ctx.meta, None, ctx.H)
+        gx = pull_combine(s.y_ptrs, ctx.meta, None, ctx.H, s.y.shape[0])
         return gx, None, None, None, None, None
 
 
@@ -250,7 +253,7 @@ class _EPCombine(torch.autograd.Function):
     @staticmethod
     def forward(ctx, ys, w, strat: SymmExpertParallel, meta: EPMeta):
         s = strat.publish(y=ys)
-        out = pull_combine(s.y_ptrs, meta, w, ys.shape[1])
+        out = pull_combine(s.y_ptrs, meta, w, ys.shape[1], s.y.shape[0])
         ctx.save_for_backward(ys, w)
         ctx.strat, ctx.meta = strat, meta
         return out
@@ -262,6 +265,6 @@ class _EPCombine(torch.autograd.Function):
         g = g.contiguous()
         w_sorted = w.reshape(-1).float()[meta.order]
         s = strat.publish(x=g, y=ys, tok=meta.tok_sorted, w=w_sorted)
-        gys = pull_rows(s.x_ptrs, s.tok_ptrs, s.w_ptrs, meta, g.shape[1])
-        gw = pull_wgrad(g, s.y_ptrs, meta)
+        gys = pull_rows(s.x_ptrs, s.tok_ptrs, s.w_ptrs, meta, g.shape[1], s.tok.numel(), s.x.shape[0])
+        gw = pull_wgrad(g, s.y_ptrs, meta, s.y.shape[0])
         return gys, gw.to(w.dtype), None, None
