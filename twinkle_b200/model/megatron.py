@@ -144,8 +144,14 @@ class MegatronModel(TwinkleModel):
                     t = loader.get(src) if src else hf_to_internal(g, self.config, loader.get)
                     p.copy_(t.to(p.dtype))
                 elif p.dim() > 1:
-                    gen = torch.Generator(device='cpu').manual_seed(stable_seed(seed, g))
-                    p.copy_(torch.randn(p.shape, generator=gen, dtype=torch.float32).mul_(self.config.initializer_range))
+                    # the same rule as ``DecoderModel.init_weights``: one stream per (global) parameter name, drawn on the
+                    # host for small tensors and on the device for large ones, so every layout starts from the same values
+                    if p.numel() <= 2**24 or p.device.type == 'cpu':
+                        gen = torch.Generator(device='cpu').manual_seed(stable_seed(seed, g))
+                        p.copy_(torch.randn(p.shape, generator=gen, dtype=torch.float32).mul_(self.config.initializer_range))
+                    else:
+                        gd = torch.Generator(device=p.device).manual_seed(stable_seed(seed, g))
+                        p.normal_(0.0, self.config.initializer_range, generator=gd)
         m._layer_offset = lo
 
     @staticmethod
