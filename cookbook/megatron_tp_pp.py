@@ -85,7 +85,12 @@ def main(argv=None):
               'micro_batches': a.micro_batches, 'recompute': a.recompute, 'comm': a.comm, 'losses': losses, 'ms_per_step': ms,
               'tokens_per_s': (a.seq_len * a.micro_batches * max(world // (a.tp * a.pp), 1)) / (ms / 1e3) if ms else None,
               'peak_mem_gib': round(torch.cuda.max_memory_allocated() / 2**30, 1) if cuda else None}
-    out_dir = a.out or tempfile.mkdtemp(prefix='tk_hf_')
+    out_dir = a.out
+    if out_dir is None:  # one directory for all ranks
+        box = [tempfile.mkdtemp(prefix='tk_hf_') if rank == 0 else None]
+        if world > 1:
+            dist.broadcast_object_list(box, src=0)
+        out_dir = box[0]
     if a.roundtrip:
         import time
         t_save = time.time()
