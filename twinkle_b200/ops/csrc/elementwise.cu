@@ -152,113 +152,168 @@ std::vector<torch::Tensor> rmsnorm_bwd(const torch::Tensor& g, const torch::Tens
 // ------------------------------------------------------- q/k-norm + RoPE (D=128)
 // One warp per (token, head).  Lane l holds elements [4l, 4l+4); the rotate-half partner of
 // element i (< 64) is i + 64, which lives in lane l ^ 16.
+// Each warp takes ROPE_U consecutive (token, head) items per round and issues all their loads before any arithmetic:
+// with one 256-byte load in flight per warp the kernel ran at a third of the memory bandwidth.
+constexpr int ROPE_U = 4;
+
 template <bool HAS_NORM>
-__global__ void qk_norm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw, const bf16* __restrict__ kw,
-                                        const float* __restrict__ cosb, const float* __restrict__ sinb, bf16* __restrict__ q,
-                                        bf16* __restrict__ k, bf16* __restrict__ v, float* __restrict__ rstd, int T, int hq, int hkv,
-                                        float eps) {
+__global__ void __launch_bounds__(256) qk_norm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw, const bf16* __restrict__ kw,
+                                                               const float* __restrict__ cosb, const float* __restrict__ sinb, bf16* __restrict__ q,
+                                                               bf16* __restrict__ k, bf16* __restrict__ v, float* __restrict__ rstd, int T, int hq,
+                                                               int hkv, float eps) {
   constexpr int D = 128;
   const int heads = hq + 2 * hkv;
   const int lane = threadIdx.x & 31;
   const long total = static_cast<long>(T) * heads;
-  for (long item = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); item < total;
-       item += static_cast<long>(gridDim.x) * (blockDim.x >> 5)) {
-    const int t = static_cast<int>(item / heads), h = static_cast<int>(item % heads);
-    const uint2 raw = *reinterpret_cast<const uint2*>(qkv + (static_cast<size_t>(t) * heads + h) * D + lane * 4);
-    if (h >= hq + hkv) {  // v: plain copy
-      *reinterpret_cast<uint2*>(v + (static_cast<size_t>(t) * hkv + (h - hq - hkv)) * D + lane * 4) = raw;
-      continue;
-    }
-    float2 a = unpack_bf16(raw.x), b = unpack_bf16(raw.y);
-    float xv[4] = {a.x, a.y, b.x, b.y};
-    const bool is_q = h < hq;
-    if (HAS_NORM) {
-      float ss = warp_sum(xv[0] * xv[0] + xv[1] * xv[1] + xv[2] * xv[2] + xv[3] * xv[3]);
-      const float r = rsqrtf(ss / D + eps);
-      if (lane == 0) rstd[static_cast<size_t>(t) * (hq + hkv) + h] = r;
-      const uint2 wraw = *reinterpret_cast<const uint2*>((is_q ? qw : kw) + lane * 4);
-      float2 wa = unpack_bf16(wraw.x), wb = unpack_bf16(wraw.y);
-      xv[0] *= r * wa.x; xv[1] *= r * wa.y; xv[2] *= r * wb.x; xv[3] *= r * wb.y;
-      // the reference path rounds the normalised value to bf16 before RoPE
+  const long nwarps = static_cast<long>(gridDim.x) * (blockDim.x >> 5);
+  const int fi = (lane & 15) * 4;  // frequency index of this lane's first element
+  float wq[4] = {1.f, 1.f, 1.f, 1.f}, wk[4] = {1.f, 1.f, 1.f, 1.f};
+  if (HAS_NORM) {
+    const uint2 a = *reinterpret_cast<const uint2*>(qw + lane * 4), b = *reinterpret_cast<const uint2*>(kw + lane * 4);
+    const float2 a0 = unpack_bf16(a.x), a1 = unpack_bf16(a.y), b0 = unpack_bf16(b.x), b1 = unpack_bf16(b.y);
+    wq[0] = a0.x; wq[1] = a0.y; wq[2] = a1.x; wq[3] = a1.y;
+    wk[0] = b0.x; wk[1] = b0.y; wk[2] = b1.x; wk[3] = b1.y;
+  }
+  for (long base = (static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * ROPE_U; base < total; base += nwarps * ROPE_U) {
+    uint2 raw[ROPE_U];
+    float4 cs[ROPE_U], sn4[ROPE_U];
+    int tt[ROPE_U], hh[ROPE_U];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) xv[i] = __bfloat162float(__float2bfloat16(xv[i]));
+    for (int u = 0; u < ROPE_U; ++u) {
+      const long item = base + u;
+      tt[u] = -1;
+      if (item < total) {
+        tt[u] = static_cast<int>(item / heads);
+        hh[u] = static_cast<int>(item - static_cast<long>(tt[u]) * heads);
+        raw[u] = *reinterpret_cast<const uint2*>(qkv + static_cast<size_t>(item) * D + lane * 4);
+        if (hh[u] < hq + hkv) {
+          cs[u] = *reinterpret_cast<const float4*>(cosb + static_cast<size_t>(tt[u]) * 64 + fi);
+          sn4[u] = *reinterpret_cast<const float4*>(sinb + static_cast<size_t>(tt[u]) * 64 + fi);
+        }
+      }
     }
-    const int fi = (lane & 15) * 4;  // frequency index of this lane's first element
-    const float4 c = *reinterpret_cast<const float4*>(cosb + static_cast<size_t>(t) * 64 + fi);
-    const float4 s = *reinterpret_cast<const float4*>(sinb + static_cast<size_t>(t) * 64 + fi);
-    const float cc[4] = {c.x, c.y, c.z, c.w}, sn[4] = {s.x, s.y, s.z, s.w};
-    float o[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float other = __shfl_xor_sync(0xffffffffu, xv[i], 16);
-      o[i] = (lane < 16) ? (xv[i] * cc[i] - other * sn[i]) : (xv[i] * cc[i] + other * sn[i]);
+    for (int u = 0; u < ROPE_U; ++u) {
+      if (tt[u] < 0) continue;  // uniform over the warp
+      const int t = tt[u], h = hh[u];
+      if (h >= hq + hkv) {  // v: plain copy
+        *reinterpret_cast<uint2*>(v + (static_cast<size_t>(t) * hkv + (h - hq - hkv)) * D + lane * 4) = raw[u];
+        continue;
+      }
+      float2 a = unpack_bf16(raw[u].x), b = unpack_bf16(raw[u].y);
+      float xv[4] = {a.x, a.y, b.x, b.y};
+      const bool is_q = h < hq;
+      if (HAS_NORM) {
+        float ss = warp_sum(xv[0] * xv[0] + xv[1] * xv[1] + xv[2] * xv[2] + xv[3] * xv[3]);
+        const float r = rsqrtf(ss / D + eps);
+        if (lane == 0) rstd[static_cast<size_t>(t) * (hq + hkv) + h] = r;
+        // the reference path rounds the normalised value to bf16 before RoPE
+#pragma unroll
+        for (int i = 0; i < 4; ++i) xv[i] = __bfloat162float(__float2bfloat16(xv[i] * (r * (is_q ? wq[i] : wk[i]))));
+      }
+      const float cc[4] = {cs[u].x, cs[u].y, cs[u].z, cs[u].w}, sn[4] = {sn4[u].x, sn4[u].y, sn4[u].z, sn4[u].w};
+      float o[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float other = __shfl_xor_sync(0xffffffffu, xv[i], 16);
+        o[i] = (lane < 16) ? (xv[i] * cc[i] - other * sn[i]) : (xv[i] * cc[i] + other * sn[i]);
+      }
+      uint2 outv = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
+      bf16* dst = is_q ? q + (static_cast<size_t>(t) * hq + h) * D : k + (static_cast<size_t>(t) * hkv + (h - hq)) * D;
+      *reinterpret_cast<uint2*>(dst + lane * 4) = outv;
     }
-    uint2 outv = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
-    bf16* dst = is_q ? q + (static_cast<size_t>(t) * hq + h) * D : k + (static_cast<size_t>(t) * hkv + (h - hq)) * D;
-    *reinterpret_cast<uint2*>(dst + lane * 4) = outv;
   }
 }
 
 template <bool HAS_NORM>
-__global__ void qk_norm_rope_bwd_kernel(const bf16* __restrict__ gq, const bf16* __restrict__ gk, const bf16* __restrict__ gv,
-                                        const bf16* __restrict__ qkv, const bf16* __restrict__ qw, const bf16* __restrict__ kw,
-                                        const float* __restrict__ cosb, const float* __restrict__ sinb, const float* __restrict__ rstd,
-                                        bf16* __restrict__ dqkv, float* __restrict__ dqw, float* __restrict__ dkw, int T, int hq,
-                                        int hkv) {
+__global__ void __launch_bounds__(256) qk_norm_rope_bwd_kernel(const bf16* __restrict__ gq, const bf16* __restrict__ gk, const bf16* __restrict__ gv,
+                                                               const bf16* __restrict__ qkv, const bf16* __restrict__ qw, const bf16* __restrict__ kw,
+                                                               const float* __restrict__ cosb, const float* __restrict__ sinb,
+                                                               const float* __restrict__ rstd, bf16* __restrict__ dqkv, float* __restrict__ dqw,
+                                                               float* __restrict__ dkw, int T, int hq, int hkv) {
   constexpr int D = 128;
+  constexpr int U = 2;  // items per warp per round, all loads issued before the arithmetic
   __shared__ float s_dw[2][D];
   for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) (&s_dw[0][0])[i] = 0.f;
   __syncthreads();
   const int heads = hq + 2 * hkv;
   const int lane = threadIdx.x & 31;
   const long total = static_cast<long>(T) * heads;
+  const long nwarps = static_cast<long>(gridDim.x) * (blockDim.x >> 5);
+  const int fi = (lane & 15) * 4;
+  float wq[4] = {1.f, 1.f, 1.f, 1.f}, wk[4] = {1.f, 1.f, 1.f, 1.f};
+  if (HAS_NORM) {
+    const uint2 a = *reinterpret_cast<const uint2*>(qw + lane * 4), b = *reinterpret_cast<const uint2*>(kw + lane * 4);
+    const float2 a0 = unpack_bf16(a.x), a1 = unpack_bf16(a.y), b0 = unpack_bf16(b.x), b1 = unpack_bf16(b.y);
+    wq[0] = a0.x; wq[1] = a0.y; wq[2] = a1.x; wq[3] = a1.y;
+    wk[0] = b0.x; wk[1] = b0.y; wk[2] = b1.x; wk[3] = b1.y;
+  }
   float acc_w[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-  for (long item = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); item < total;
-       item += static_cast<long>(gridDim.x) * (blockDim.x >> 5)) {
-    const int t = static_cast<int>(item / heads), h = static_cast<int>(item % heads);
-    bf16* dst = dqkv + (static_cast<size_t>(t) * heads + h) * D + lane * 4;
-    if (h >= hq + hkv) {
-      *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(gv + (static_cast<size_t>(t) * hkv + (h - hq - hkv)) * D + lane * 4);
-      continue;
-    }
-    const bool is_q = h < hq;
-    const bf16* gsrc = is_q ? gq + (static_cast<size_t>(t) * hq + h) * D : gk + (static_cast<size_t>(t) * hkv + (h - hq)) * D;
-    const uint2 graw = *reinterpret_cast<const uint2*>(gsrc + lane * 4);
-    float2 ga = unpack_bf16(graw.x), gb = unpack_bf16(graw.y);
-    const float gy[4] = {ga.x, ga.y, gb.x, gb.y};
-    const int fi = (lane & 15) * 4;
-    const float4 c = *reinterpret_cast<const float4*>(cosb + static_cast<size_t>(t) * 64 + fi);
-    const float4 s = *reinterpret_cast<const float4*>(sinb + static_cast<size_t>(t) * 64 + fi);
-    const float cc[4] = {c.x, c.y, c.z, c.w}, sn[4] = {s.x, s.y, s.z, s.w};
-    float gn[4];  // gradient w.r.t. the (normalised) pre-RoPE value
+  for (long base = (static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * U; base < total; base += nwarps * U) {
+    uint2 graw[U], raw[U];
+    float4 cs[U], sn4[U];
+    float rr[U];
+    int tt[U], hh[U];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float other = __shfl_xor_sync(0xffffffffu, gy[i], 16);
-      gn[i] = (lane < 16) ? (gy[i] * cc[i] + other * sn[i]) : (gy[i] * cc[i] - other * sn[i]);
+    for (int u = 0; u < U; ++u) {
+      const long item = base + u;
+      tt[u] = -1;
+      if (item < total) {
+        const int t = static_cast<int>(item / heads), h = static_cast<int>(item - static_cast<long>(t) * heads);
+        tt[u] = t; hh[u] = h;
+        if (h >= hq + hkv) {
+          graw[u] = *reinterpret_cast<const uint2*>(gv + (static_cast<size_t>(t) * hkv + (h - hq - hkv)) * D + lane * 4);
+        } else {
+          const bf16* gsrc = h < hq ? gq + (static_cast<size_t>(t) * hq + h) * D : gk + (static_cast<size_t>(t) * hkv + (h - hq)) * D;
+          graw[u] = *reinterpret_cast<const uint2*>(gsrc + lane * 4);
+          cs[u] = *reinterpret_cast<const float4*>(cosb + static_cast<size_t>(t) * 64 + fi);
+          sn4[u] = *reinterpret_cast<const float4*>(sinb + static_cast<size_t>(t) * 64 + fi);
+          if (HAS_NORM) {
+            raw[u] = *reinterpret_cast<const uint2*>(qkv + static_cast<size_t>(item) * D + lane * 4);
+            rr[u] = rstd[static_cast<size_t>(t) * (hq + hkv) + h];
+          }
+        }
+      }
     }
-    if (!HAS_NORM) {
-      *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(gn[0], gn[1]), pack_bf16(gn[2], gn[3]));
-      continue;
-    }
-    const uint2 raw = *reinterpret_cast<const uint2*>(qkv + (static_cast<size_t>(t) * heads + h) * D + lane * 4);
-    float2 xa = unpack_bf16(raw.x), xb = unpack_bf16(raw.y);
-    const float xv[4] = {xa.x, xa.y, xb.x, xb.y};
-    const uint2 wraw = *reinterpret_cast<const uint2*>((is_q ? qw : kw) + lane * 4);
-    float2 wa = unpack_bf16(wraw.x), wb = unpack_bf16(wraw.y);
-    const float wv[4] = {wa.x, wa.y, wb.x, wb.y};
-    const float r = rstd[static_cast<size_t>(t) * (hq + hkv) + h];
-    float dot = 0.f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) dot += gn[i] * wv[i] * xv[i];
-    dot = warp_sum(dot);
-    const float coef = dot * r * r / D;
-    float dx[4];
+    for (int u = 0; u < U; ++u) {
+      if (tt[u] < 0) continue;  // uniform over the warp
+      const int t = tt[u], h = hh[u];
+      bf16* dst = dqkv + (static_cast<size_t>(t) * heads + h) * D + lane * 4;
+      if (h >= hq + hkv) {
+        *reinterpret_cast<uint2*>(dst) = graw[u];
+        continue;
+      }
+      const bool is_q = h < hq;
+      float2 ga = unpack_bf16(graw[u].x), gb = unpack_bf16(graw[u].y);
+      const float gy[4] = {ga.x, ga.y, gb.x, gb.y};
+      const float cc[4] = {cs[u].x, cs[u].y, cs[u].z, cs[u].w}, sn[4] = {sn4[u].x, sn4[u].y, sn4[u].z, sn4[u].w};
+      float gn[4];  // gradient w.r.t. the (normalised) pre-RoPE value
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      dx[i] = r * (gn[i] * wv[i] - xv[i] * coef);
-      acc_w[is_q ? 0 : 1][i] += gn[i] * xv[i] * r;
+      for (int i = 0; i < 4; ++i) {
+        const float other = __shfl_xor_sync(0xffffffffu, gy[i], 16);
+        gn[i] = (lane < 16) ? (gy[i] * cc[i] + other * sn[i]) : (gy[i] * cc[i] - other * sn[i]);
+      }
+      if (!HAS_NORM) {
+        *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(gn[0], gn[1]), pack_bf16(gn[2], gn[3]));
+        continue;
+      }
+      float2 xa = unpack_bf16(raw[u].x), xb = unpack_bf16(raw[u].y);
+      const float xv[4] = {xa.x, xa.y, xb.x, xb.y};
+      const float r = rr[u];
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) dot += gn[i] * (is_q ? wq[i] : wk[i]) * xv[i];
+      dot = warp_sum(dot);
+      const float coef = dot * r * r / D;
+      float dx[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        dx[i] = r * (gn[i] * (is_q ? wq[i] : wk[i]) - xv[i] * coef);
+        acc_w[is_q ? 0 : 1][i] += gn[i] * xv[i] * r;
+      }
+      *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(dx[0], dx[1]), pack_bf16(dx[2], dx[3]));
     }
-    *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(dx[0], dx[1]), pack_bf16(dx[2], dx[3]));
   }
   if (HAS_NORM) {
 #pragma unroll
@@ -289,7 +344,7 @@ std::vector<torch::Tensor> qk_norm_rope_fwd(const torch::Tensor& qkv, const torc
   auto rstd = torch::empty({T, hq + hkv}, qkv.options().dtype(torch::kFloat32));
   if (T == 0) return {q, k, v, rstd};
   long items = static_cast<long>(T) * (hq + 2 * hkv);
-  int blocks = static_cast<int>(std::min<long>((items + 7) / 8, num_sms() * 16L));
+  int blocks = static_cast<int>(std::max<long>(1, std::min<long>((items + 8 * ROPE_U - 1) / (8 * ROPE_U), num_sms() * 8L)));
   qk_norm_rope_fwd_kernel<true><<<blocks, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
       reinterpret_cast<const bf16*>(qkv.data_ptr()), reinterpret_cast<const bf16*>(qw.data_ptr()), reinterpret_cast<const bf16*>(kw.data_ptr()),
       cosb.data_ptr<float>(), sinb.data_ptr<float>(), reinterpret_cast<bf16*>(q.data_ptr()), reinterpret_cast<bf16*>(k.data_ptr()),
