@@ -122,6 +122,9 @@ class MegatronModel(TwinkleModel):
                 apply_context_parallel(m, mesh)  # zig-zag shards, keys / values gathered per layer (``parallel/context.py``)
             self.chunks.append(m)
         self.sequence_parallel = bool(mesh.sequence_parallel and self.tp_size > 1)
+        self.ep_comm, self.ep_rank, self.ep_size = None, 0, 1
+        if (mesh.ep_size or 1) > 1 and cfg.is_moe:
+            self._apply_expert_parallel(mesh, comm_backend)
         self.cp_comm = None
         if self.cp_size > 1:
             from ..parallel.context import cp_group_for
@@ -130,6 +133,66 @@ class MegatronModel(TwinkleModel):
         self.optimizer_groups: Dict[str, OptimizerGroup] = {'': OptimizerGroup(adapter_name='')}
         self._state: Dict[str, Dict[str, torch.Tensor]] = {}
         self._pending_scale = 1.0
+
+    # ------------------------------------------------------------ expert parallel
+    def _apply_expert_parallel(self, mesh: DeviceMesh, backend: str) -> None:
+        """Experts split over ``ep`` consecutive data-parallel ranks (same tp / pp / cp coordinates); attention and router
+        stay as they are (reference ``megatron/strategy/megatron.py:90-107``: ``expert_model_parallel_size``; expert
+        tensor parallelism is not built — experts are whole on a rank).  A rank's expert tensors are shared with every rank
+        that holds the same experts of the same layers: the other data-parallel blocks, the context-parallel peers and,
+        under sequence parallelism, the tensor-parallel peers (they route different tokens); gradients are summed over
+        exactly that set."""
+        from ..parallel.expert import ExpertParallel, shard_experts
+        ep = int(mesh.ep_size)
+        if self.tp_size > 1 and not self.sequence_parallel:
+            raise NotImplementedError('expert parallel with tensor parallel needs sequence_parallel=True (each tp rank then routes its own tokens)')
+        names = list(mesh.mesh_dim_names)
+        data_dims = [d for d in ('dp', 'fsdp') if d in names]
+        coords = {r: mesh.coord_of(r) for r in mesh.mesh.reshape(-1).tolist()}
+
+        def key_of(r, dims):
+            return tuple(coords[r][names.index(d)] for d in dims if d in names)
+
+        me = dist.get_rank()
+        lines: Dict[tuple, List[int]] = {}
+        for r in sorted(coords):
+            lines.setdefault(key_of(r, [d for d in names if d not in data_dims]), []).append(r)
+        ep_group, my_pos, pos_of = None, 0, {}
+        for other in sorted(lines):
+            line = sorted(lines[other], key=lambda r: key_of(r, data_dims))
+            if len(line) % ep != 0:
+                raise ValueError(f'ep_size={ep} does not divide the {len(line)} data-parallel ranks')
+            for i in range(0, len(line), ep):
+                block = line[i:i + ep]
+                g = dist.new_group(ranks=block)
+                for j, r in enumerate(block):
+                    pos_of[r] = j
+                if me in block:
+                    ep_group, my_pos = g, block.index(me)
+        rep_group = None
+        pp_i = names.index('pp') if 'pp' in names else None
+        for stage in sorted({coords[r][pp_i] if pp_i is not None else 0 for r in coords}):
+            for j in range(ep):
+                members = sorted(r for r in coords if pos_of[r] == j and (coords[r][pp_i] if pp_i is not None else 0) == stage)
+                g = dist.new_group(ranks=members)
+                if me in members:
+                    rep_group = g if len(members) > 1 else None
+        self.ep_comm = Communicator(ep_group, self.device)
+        strat = None
+        if self.device.type == 'cuda' and backend in ('auto', 'symm'):
+            try:
+                from ..parallel.expert_symm import SymmExpertParallel
+                from ..parallel.symm import SymmCommunicator
+                strat = SymmExpertParallel(SymmCommunicator(ep_group, self.device), self.config.num_experts)
+            except Exception:
+                if backend == 'symm':
+                    raise
+        if strat is None:
+            strat = ExpertParallel(self.ep_comm, self.config.num_experts)
+        rep_comm = Communicator(rep_group, self.device) if rep_group is not None else None
+        for m in self.chunks:
+            shard_experts(m, strat, my_pos, rep_comm)
+        self.ep_rank, self.ep_size = my_pos, ep
 
     # ------------------------------------------------------------ weights
     def _rename_for_init(self, m: DecoderModel, lo: int, seed: int, load_dir: Optional[str]) -> None:
@@ -313,6 +376,11 @@ class MegatronModel(TwinkleModel):
         for n, p in self._params():
             if p.grad is None:
                 continue
+            if getattr(p, '_ep_local', False):  # experts: summed over the ranks that hold the same experts, nobody else
+                rc = getattr(p, '_ep_replica_comm', None)
+                if rc is not None and rc.world_size > 1:
+                    rc.all_reduce(p.grad)
+                continue
             if self.dp_comm.world_size > 1:
                 self.dp_comm.all_reduce(p.grad)
             if self.sequence_parallel and tp_rule(n, self.config) is None:
@@ -320,6 +388,7 @@ class MegatronModel(TwinkleModel):
         denom = self.dp_comm.all_reduce_scalar(og.train_status.num_tokens, 'sum') or 1.0
         # 2. global norm: tp-sharded tensors are disjoint (sum over tp), replicated ones counted once; sum over pp
         sq = torch.zeros((), dtype=torch.float32, device=self.device)
+        sq_ep = torch.zeros((), dtype=torch.float32, device=self.device)
         tied_dup = self.config.tie_word_embeddings and self.pp_size > 1 and self.pp_rank == self.pp_size - 1
         for n, p in self._params():
             if p.grad is None or (tied_dup and n == 'embed_tokens.weight'):
@@ -327,7 +396,14 @@ class MegatronModel(TwinkleModel):
             s = ops.sumsq(p.grad)
             if self.tp_size > 1 and tp_rule(n, self.config) is None:
                 s = s / self.tp_size
-            sq = sq + s
+            if getattr(p, '_ep_local', False):
+                sq_ep = sq_ep + s
+            else:
+                sq = sq + s
+        if self.ep_comm is not None:  # each EP rank holds different experts: their squared norms add up over the group
+            sq_ep = sq_ep.reshape(1)
+            self.ep_comm.all_reduce(sq_ep)
+            sq = sq + sq_ep[0]
         if self.tp_size > 1:
             self.tp_comm.all_reduce(sq)
         if self.pp_size > 1:
@@ -378,7 +454,8 @@ class MegatronModel(TwinkleModel):
             if p.grad is None:
                 continue
             numel = p.numel()
-            lo, hi = self._state_range(numel)
+            ep_local = bool(getattr(p, '_ep_local', False))  # differs per EP rank: never sliced over the data-parallel group
+            lo, hi = (0, numel) if ep_local else self._state_range(numel)
             st = self._state.get(n)
             if st is None:
                 flat = p.data.view(-1)[lo:hi]
@@ -389,7 +466,7 @@ class MegatronModel(TwinkleModel):
             if hi > lo:
                 ops.adamw_step(st['master'], st['exp_avg'], st['exp_avg_sq'], p.grad.contiguous().view(-1)[lo:hi], p.data.view(-1)[lo:hi],
                                gd['lr'], gd['betas'][0], gd['betas'][1], gd['eps'], wd, og.optim_steps, scale)
-            if zero1:
+            if zero1 and not ep_local:
                 # every rank updated its slice of the parameter; the slices are exchanged so all ranks hold the whole tensor
                 chunk = -(-numel // dp)
                 mine = torch.zeros(chunk, dtype=p.dtype, device=p.device)
@@ -489,6 +566,10 @@ class MegatronModel(TwinkleModel):
 
     # ---------------------------------------------------------- save / load
     def _gather_full(self, name: str, p: torch.Tensor) -> torch.Tensor:
+        if getattr(p, '_ep_local', False) and self.ep_comm is not None:  # all experts, in expert order
+            parts = [torch.empty_like(p) for _ in range(self.ep_comm.world_size)]
+            dist.all_gather(parts, p.detach().contiguous(), group=self.ep_comm.group)
+            return torch.cat(parts, 0)
         if self.tp_size == 1 or tp_rule(name, self.config) is None:
             return p.detach()
         parts = [torch.empty_like(p) for _ in range(self.tp_size)]
@@ -550,10 +631,14 @@ class MegatronModel(TwinkleModel):
             for n, p in self.named_parameters():
                 src_head = n == 'lm_head.weight' and 'lm_head.weight' not in loader
                 full = loader.get('model.embed_tokens.weight') if src_head else hf_to_internal(n, self.config, loader.get)
-                p.copy_(tp_shard(n, full, self.config, self.tp_rank, self.tp_size).to(p.device, p.dtype))
+                if getattr(p, '_ep_local', False) and self.ep_comm is not None:
+                    el = p.shape[0]
+                    p.copy_(full[self.ep_rank * el:(self.ep_rank + 1) * el].to(p.device, p.dtype))
+                else:
+                    p.copy_(tp_shard(n, full, self.config, self.tp_rank, self.tp_size).to(p.device, p.dtype))
                 st = self._state.get(n)
                 if st is not None:
-                    lo, hi = self._state_range(p.numel())
+                    lo, hi = (0, p.numel()) if getattr(p, '_ep_local', False) else self._state_range(p.numel())
                     st['master'].copy_(p.data.view(-1)[lo:hi].float())
         if kwargs.get('load_optimizer'):
             self._load_training_state(path)

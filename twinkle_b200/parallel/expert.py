@@ -132,6 +132,30 @@ class ExpertParallel:
         return out.index_add(0, tok, ret)
 
 
+def shard_experts(model, strat, ep_rank: int, rep_comm: Optional[Communicator]) -> None:
+    """Keep the experts ``[ep_rank·E_local, (ep_rank+1)·E_local)`` of every MoE block (cut from the identically
+    initialised full tensors), route the blocks through ``strat``, and mark the expert tensors as EP-local: their
+    gradients are summed over ``rep_comm`` (the ranks that hold the same experts), never over the whole data group."""
+    El = strat.local
+    lo = ep_rank * El
+    for layer in model.layers:
+        if not getattr(layer, 'is_moe', False):
+            continue
+        ex = layer.mlp.experts
+        with torch.no_grad():
+            ex.gate_up_proj = torch.nn.Parameter(ex.gate_up_proj.data[lo:lo + El].clone(), requires_grad=ex.gate_up_proj.requires_grad)
+            ex.down_proj = torch.nn.Parameter(ex.down_proj.data[lo:lo + El].clone(), requires_grad=ex.down_proj.requires_grad)
+            for key in list(ex.lora.keys()):
+                ex.lora[key] = torch.nn.Parameter(ex.lora[key].data[:, lo:lo + El].clone())
+        # expert tensors differ per EP rank: their gradients are summed only over the ranks that hold the same
+        # experts, and their squared norms are summed over the EP group when the global norm is taken
+        for p in [ex.gate_up_proj, ex.down_proj] + list(ex.lora.values()):
+            p._ep_local = True
+            p._ep_replica_comm = rep_comm
+        ex.num_local, ex.first_expert = El, lo
+        layer.mlp.moe_parallel = strat
+
+
 def apply_expert_parallel(model, mesh, cfg, backend: str = 'auto'):
     """Keep only this rank's experts (a view of the freshly initialised full tensors, so every layout starts
     from identical values) and route MoE blocks through ``ExpertParallel``."""
@@ -152,27 +176,10 @@ def apply_expert_parallel(model, mesh, cfg, backend: str = 'auto'):
             logging.getLogger('twinkle_b200').warning(f'peer-memory expert parallel unavailable ({e}); using NCCL all-to-all')
     if strat is None:
         strat = ExpertParallel(comm, cfg.num_experts)
-    El = strat.local
-    lo = comm.rank * El
     rep_group = ep_replica_group_for(mesh)
     rep_comm = Communicator(rep_group, dev) if rep_group is not None else None
     if rep_comm is not None and rep_comm.world_size <= 1:
         rep_comm = None
-    for layer in model.layers:
-        if not getattr(layer, 'is_moe', False):
-            continue
-        ex = layer.mlp.experts
-        with torch.no_grad():
-            ex.gate_up_proj = torch.nn.Parameter(ex.gate_up_proj.data[lo:lo + El].clone(), requires_grad=ex.gate_up_proj.requires_grad)
-            ex.down_proj = torch.nn.Parameter(ex.down_proj.data[lo:lo + El].clone(), requires_grad=ex.down_proj.requires_grad)
-            for key in list(ex.lora.keys()):
-                ex.lora[key] = torch.nn.Parameter(ex.lora[key].data[:, lo:lo + El].clone())
-        # expert tensors differ per EP rank: their gradients are summed only over the ranks that hold the same
-        # experts, and their squared norms are summed over the EP group when the global norm is taken
-        for p in [ex.gate_up_proj, ex.down_proj] + list(ex.lora.values()):
-            p._ep_local = True
-            p._ep_replica_comm = rep_comm
-        ex.num_local, ex.first_expert = El, lo
-        layer.mlp.moe_parallel = strat
+    shard_experts(model, strat, comm.rank, rep_comm)
     model._ep_comm = comm
     return strat
