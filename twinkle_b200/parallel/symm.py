@@ -18,6 +18,7 @@ error word.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -26,6 +27,59 @@ import torch.distributed as dist
 from .. import ops
 from ..utils.profiling import PHASES
 from .comm import Communicator
+
+
+def exchange_jobs(shape, elem_size: int, sp: int, me: int, seq_to_head: bool):
+    """Copy jobs of rank ``me`` for one tensor of the head ↔ sequence exchange, as byte offsets.
+
+    ``seq_to_head``: every rank stages ``[t, H, D]`` (its tokens, all heads); ``me`` pulls its head slice of every
+    peer's tokens into ``[sp·t, H/sp, D]``.  Otherwise every rank stages ``[sp·t, h, D]`` (all tokens, its heads) and
+    ``me`` pulls its token chunk of every peer's heads into ``[t, sp·h, D]``.  Returns ``(output shape, [(source rank,
+    source offset, source row stride, destination offset, destination row stride, bytes per row, rows)])``; peers are
+    visited starting with ``me + 1`` so that no GPU's egress serves every reader at the same moment."""
+    jobs = []
+    if seq_to_head:
+        t, H, D = shape
+        if H % sp:
+            raise ValueError(f'{H} heads do not divide over {sp} sequence-parallel ranks')
+        hl = H // sp
+        chunk = hl * D * elem_size
+        out_shape = (sp * t, hl, D)
+        for k in range(1, sp + 1):
+            r = (me + k) % sp
+            jobs.append((r, me * chunk, H * D * elem_size, r * t * chunk, chunk, chunk, t))
+    else:
+        tt, hl, D = shape
+        if tt % sp:
+            raise ValueError(f'{tt} token rows do not divide over {sp} sequence-parallel ranks')
+        t = tt // sp
+        chunk = hl * D * elem_size
+        out_shape = (t, sp * hl, D)
+        for k in range(1, sp + 1):
+            r = (me + k) % sp
+            jobs.append((r, me * t * chunk, chunk, r * chunk, sp * chunk, chunk, t))
+    return out_shape, jobs
+
+
+def check_jobs(jobs, src_bytes: int, dst_bytes: int) -> None:
+    """Debug aid (``TWINKLE_DEBUG_BOUNDS=1``): every byte a job reads lies inside the peers' staged tensor and every
+    byte it writes inside the output, rows are multiples of 16 bytes, and no two jobs write the same byte."""
+    import numpy as np
+    hit = np.zeros(max(dst_bytes // 16, 1), dtype=np.uint8)
+    for r, s_off, s_stride, d_off, d_stride, chunk, n in jobs:
+        if chunk % 16 or s_off % 16 or d_off % 16 or s_stride % 16 or d_stride % 16:
+            raise AssertionError(f'job for rank {r} is not 16-byte aligned: {(s_off, s_stride, d_off, d_stride, chunk)}')
+        if n and (s_off < 0 or s_off + (n - 1) * s_stride + chunk > src_bytes):
+            raise AssertionError(f'job for rank {r} reads past the staged tensor ({src_bytes} bytes)')
+        if n and (d_off < 0 or d_off + (n - 1) * d_stride + chunk > dst_bytes):
+            raise AssertionError(f'job for rank {r} writes past the output ({dst_bytes} bytes)')
+        if n:
+            rows = (d_off // 16 + np.arange(n, dtype=np.int64)[:, None] * (d_stride // 16) + np.arange(chunk // 16, dtype=np.int64)[None, :]).reshape(-1)
+            np.add.at(hit, rows, 1)
+    if hit.max(initial=0) > 1:
+        raise AssertionError('two jobs write the same bytes')
+    if dst_bytes >= 16 and hit.min(initial=1) < 1:
+        raise AssertionError('the jobs leave part of the output unwritten')
 
 
 class SymmBuffer:
@@ -75,7 +129,6 @@ class SymmCommunicator(Communicator):
         self.copy_blocks = 32  # CTAs per peer: with 64 KB in flight each, enough for most of a peer's NVLink bandwidth; few enough to leave SMs to the GEMMs
         # TWINKLE_SYMM_LEGACY=1 keeps the first-generation kernels (push exchange with two barriers, one load in flight
         # per thread in the all-gather) for A/B measurements
-        import os
         self.legacy_kernels = os.environ.get('TWINKLE_SYMM_LEGACY', '0') == '1'
 
     # ----------------------------------------------------------- allocation
@@ -206,29 +259,17 @@ class SymmCommunicator(Communicator):
         with PHASES('ulysses_barrier'):
             self.barrier_kernel()
         outs, src, dst, ss, ds, cb, rows = [], [], [], [], [], [], []
+        check = os.environ.get('TWINKLE_DEBUG_BOUNDS', '0') == '1'
         for x, st in zip(xs, staged):
-            es = x.element_size()
             ptrs = self.peer_ptrs(st)
-            if seq_to_head:
-                t, H, D = x.shape
-                hl = H // sp
-                chunk = hl * D * es
-                out = torch.empty((sp * t, hl, D), dtype=x.dtype, device=x.device)
-                for k in range(1, sp + 1):
-                    r = (me + k) % sp
-                    src.append(ptrs[r] + me * chunk); ss.append(H * D * es)
-                    dst.append(out.data_ptr() + r * t * chunk); ds.append(chunk)
-                    cb.append(chunk); rows.append(t)
-            else:
-                tt, hl, D = x.shape
-                t = tt // sp
-                chunk = hl * D * es
-                out = torch.empty((t, sp * hl, D), dtype=x.dtype, device=x.device)
-                for k in range(1, sp + 1):
-                    r = (me + k) % sp
-                    src.append(ptrs[r] + me * t * chunk); ss.append(chunk)
-                    dst.append(out.data_ptr() + r * chunk); ds.append(sp * chunk)
-                    cb.append(chunk); rows.append(t)
+            out_shape, jobs = exchange_jobs(tuple(x.shape), x.element_size(), sp, me, seq_to_head)
+            out = torch.empty(out_shape, dtype=x.dtype, device=x.device)
+            if check:
+                check_jobs(jobs, st.numel() * st.element_size(), out.numel() * out.element_size())
+            for r, s_off, s_stride, d_off, d_stride, chunk, n in jobs:
+                src.append(ptrs[r] + s_off); ss.append(s_stride)
+                dst.append(out.data_ptr() + d_off); ds.append(d_stride)
+                cb.append(chunk); rows.append(n)
             outs.append(out)
         with PHASES('ulysses_pull'):
             self.ext.peer_pull(src, dst, ss, ds, cb, rows, max(8, (4 * self.ext.num_sms()) // len(src)))
