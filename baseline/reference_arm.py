@@ -170,7 +170,7 @@ def run(args, synthetic_sequences, ClockSampler):
         out['unavailable'] = f'reference model construction failed: {type(e).__name__}: {str(e)[:300]}'
         return say(out)
 
-    data_rank = mesh.data_rank or 0
+    data_rank = int(mesh.data_rank or 0)
     n_local_seqs = args.seqs_per_gpu * sp
     tokens_per_step_global = args.seqs_per_gpu * world * args.seq_len
     vocab = cfg.vocab_size
