@@ -290,15 +290,22 @@ def main():
     for _ in range(args.warmup):
         step(dev_feats, False)
     sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    sampler.start()      # every rank samples its own GPU: the slowest clock of the job paces a synchronous step
     ms, launches, _ = timed(dev_feats, args.steps, False)
     e2e = None
     if not args.no_e2e:
         ms_e, _, loss = timed(feats, args.steps, True)
         e2e = {'value': tokens_per_step_global * args.steps / (ms_e / 1e3), 'unit': 'tokens/s', 'h2d_bytes_per_step': h2d_bytes,
                'd2h_bytes_per_step': 8, 'ms_per_step': ms_e / args.steps, 'loss': loss}
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop()
+    if world > 1:
+        mine = torch.tensor([float(clocks.get('sm_mhz') or 0.0)], device='cuda')
+        every = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        reasons = [None] * world
+        dist.all_gather_object(reasons, clocks.get('reasons') or [])
+        clocks['sm_mhz_per_rank'] = [float(t.item()) for t in every]
+        clocks['reasons'] = sorted({r for rs in reasons for r in rs})
     # one more step with the phase clock on (outside both timed regions): device time per communication phase
     from twinkle_b200.utils.profiling import PHASES
     PHASES.start()
