@@ -75,6 +75,18 @@ def make(op: str, a) -> Tuple[Callable[[], None], float, float]:
         o = ops.flash_attn_varlen(q, k, v, cu, a.seq, True)
         g = torch.randn_like(o)
         return (lambda: torch.autograd.grad(o, (q, k, v), g, retain_graph=True)), 2.5 * flops_fwd, 2.5 * byts
+    if op in ('rope', 'rope_bwd'):
+        T, hq, hkv = a.tokens, a.heads, a.kv_heads
+        qkv = torch.randn(T, (hq + 2 * hkv) * 128, device=dev, dtype=bf)
+        qw, kw = torch.ones(128, device=dev, dtype=bf), torch.ones(128, device=dev, dtype=bf)
+        pos = torch.arange(T, device=dev) % 8192
+        cos, sin = ops.rope_tables(pos, 128, 1e6)
+        byts = 2.0 * 2 * T * (hq + 2 * hkv) * 128
+        if op == 'rope':
+            return (lambda: E.qk_norm_rope_fwd(qkv, qw, kw, cos, sin, hq, hkv, 128, 1e-6)), 0.0, byts
+        q, k, v, rstd = E.qk_norm_rope_fwd(qkv, qw, kw, cos, sin, hq, hkv, 128, 1e-6)
+        gq, gk, gv = torch.randn_like(q), torch.randn_like(k), torch.randn_like(v)
+        return (lambda: E.qk_norm_rope_bwd(gq, gk, gv, qkv, qw, kw, cos, sin, rstd, hq, hkv, 128)), 0.0, 1.5 * byts
     if op == 'rmsnorm':
         x, w = torch.randn(a.tokens, a.hidden, device=dev, dtype=bf), torch.ones(a.hidden, device=dev, dtype=bf)
 
