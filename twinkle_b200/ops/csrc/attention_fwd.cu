@@ -214,25 +214,6 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         m_used = m_new;
         l_sum *= alpha;
       }
-      // The exponentials need only the scores and the row maximum, so they are computed (and packed to bf16 in
-      // registers) BEFORE the wait for the previous P·V: that MMA and the next S = Q·Kᵀ run underneath them.  Four
-      // partial row sums keep the additions off one dependency chain.
-      uint32_t packed[2][16];
-      if (!dead) {
-        float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float p0 = exp2f(sc[c * 32 + i] - m_used), p1 = exp2f(sc[c * 32 + i + 1] - m_used);
-            const float p2 = exp2f(sc[c * 32 + i + 2] - m_used), p3 = exp2f(sc[c * 32 + i + 3] - m_used);
-            ls0 += p0; ls1 += p1; ls2 += p2; ls3 += p3;
-            packed[c][i >> 1] = pack_bf16(p0, p1);
-            packed[c][(i >> 1) + 1] = pack_bf16(p2, p3);
-          }
-        }
-        l_sum += (ls0 + ls1) + (ls2 + ls3);
-      }
       // P buffer and O accumulator are free once the previous P·V has retired
       if (!dead && j > 0 && !mbar_wait(o_done, (j - 1) & 1, p.err, ERR_ATTN_WAIT)) dead = true;
       if (dead) continue;
@@ -250,7 +231,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_st_wait();
       }
 #pragma unroll
-      for (int c = 0; c < 2; ++c) store_row_chunk_sw128(smem + SMEM_P, 128, row, wg * 64 + c * 32, packed[c]);
+      for (int c = 0; c < 2; ++c) {
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = exp2f(sc[c * 32 + i] - m_used), p1 = exp2f(sc[c * 32 + i + 1] - m_used);
+          // the sum uses the bf16-rounded values so that numerator and denominator match
+          const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+          l_sum += __low2float(pb) + __high2float(pb);
+          packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
+        }
+        store_row_chunk_sw128(smem + SMEM_P, 128, row, wg * 64 + c * 32, packed);
+      }
       tc_fence_before();
       fence_proxy_async();
       mbar_arrive(p_ready);
