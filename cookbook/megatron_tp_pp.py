@@ -91,6 +91,9 @@ def main(argv=None):
         if world > 1:
             dist.broadcast_object_list(box, src=0)
         out_dir = box[0]
+    if rank == 0 and a.json:   # the timing first: the round trip below needs disk space and minutes at full size
+        import json
+        print(json.dumps(dict(result, stage='timed')), flush=True)
     if a.roundtrip:
         import time
         t_save = time.time()
