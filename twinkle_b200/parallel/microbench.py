@@ -32,20 +32,19 @@ def main() -> None:
     E = ops.ext()
     out = {'n_gpus': world, 'peer_copy_reference_gbs': 770.0}
 
+    from twinkle_b200.utils.profiling import DeviceTimer
+    timer = DeviceTimer()
+
     def timeit(fn, iters=10, warm=3):
+        """Mean milliseconds per call: CUDA events around ``iters`` back-to-back calls, maximum over ranks."""
         for _ in range(warm):
             fn()
         dist.barrier()
         torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(iters):
-            fn()
-        b.record()
-        torch.cuda.synchronize()
-        t = torch.tensor([a.elapsed_time(b) / iters], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t)
+        with timer('op'):
+            for _ in range(iters):
+                fn()
+        return timer.summary()['op'] / iters
 
     def entry(ms, recv_bytes):
         return {'ms': round(ms, 4), 'gbs': round(recv_bytes / ms / 1e6, 1)}

@@ -100,11 +100,13 @@ class PhaseClock:
             yield
             return
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.nvtx.range_push(name)  # the same brackets show up by name on a profiler timeline
         a.record()
         try:
             yield
         finally:
             b.record()
+            torch.cuda.nvtx.range_pop()
             self._pairs.setdefault(name, []).append((a, b))
 
     def start(self) -> None:
