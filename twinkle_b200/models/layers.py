@@ -164,7 +164,10 @@ class Linear(nn.Module):
         if self.tp_mode is not None:
             from ..parallel.tensor import tp_linear_forward
             return tp_linear_forward(self, x)
-        y = ops.linear(x, self.weight, self.bias, self.wgrad_out if self.weight.requires_grad else None, value_unused)
+        wgrad_out = None
+        if self.weight.requires_grad:  # set by the sharding engine while the flat gradient buffer is bound
+            wgrad_out = self.wgrad_out if self.wgrad_out is not None else getattr(self.weight, '_wgrad_out', None)
+        y = ops.linear(x, self.weight, self.bias, wgrad_out, value_unused)
         lb = _CTX.batch
         if lb is not None and self.max_loras > 0:
             x2 = x.reshape(-1, x.shape[-1])

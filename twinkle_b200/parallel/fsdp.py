@@ -105,12 +105,17 @@ class FlatBucket:
             p.data = flat[o:o + n].view(s)
 
     def _bind_grads(self, flat: Optional[torch.Tensor]) -> None:
+        """``.grad`` of every parameter becomes a view of the flat gradient buffer.  Weight matrices also carry the view
+        as ``_wgrad_out``: the linear layers' backward lets the dW GEMM accumulate straight into it instead of producing
+        a gradient tensor that autograd then adds in a second pass over the weight-sized buffer."""
         for p, o, s in zip(self.params, self.offsets, self.shapes):
             if flat is None:
                 p.grad = None
+                p._wgrad_out = None
             else:
                 n = math.prod(s) if s else 1
                 p.grad = flat[o:o + n].view(s)
+                p._wgrad_out = p.grad if (len(s) == 2 and flat.is_cuda) else None
 
     def _unbind(self) -> None:
         for p in self.params:
