@@ -95,13 +95,16 @@ def test_placement_counts_devices_not_workers():
     assert [e['TWINKLE_WORKER_DEVICES'] for e in wide] == ['0,1', '2,3', '4,5', '6,7']
     assert [e['TWINKLE_GLOBAL_RANK'] for e in wide] == ['0', '2', '4', '6']
     # a worker sees its own devices first (LOCAL_RANK 0), then the rest of its group
-    assert wide[1]['CUDA_VISIBLE_DEVICES'].split(',')[:2] == ['2', '3'] and sorted(wide[1]['CUDA_VISIBLE_DEVICES'].split(',')) == [str(i) for i in range(8)]
+    assert wide[1]['CUDA_VISIBLE_DEVICES'].split(',')[:2] == ['2', '3'] and sorted(set(wide[1]['CUDA_VISIBLE_DEVICES'].split(','))) == [str(i) for i in range(8)]
     assert all(e['LOCAL_RANK'] == '0' for e in wide)
     tail = mgr.placement('tail')
     assert [e['TWINKLE_WORKER_DEVICES'] for e in tail] == ['4', '5', '6', '7']
     assert [e['TWINKLE_GLOBAL_RANK'] for e in tail] == ['4', '5', '6', '7'] and all(e['WORLD_SIZE'] == '4' for e in tail)
     plain = mgr.placement('plain')
     assert [e['TWINKLE_WORKER_DEVICES'] for e in plain] == ['6', '7']          # never devices 0 and 1 of another group
+    # devices of the other GPU groups come last: visible for peer copies across groups, never device 0 of this worker
+    vis = plain[0]['CUDA_VISIBLE_DEVICES'].split(',')
+    assert vis[:2] == ['6', '7'] and set(vis) >= {'0', '1', '2', '3', '4', '5'} and len(vis) == len(set(vis))
     host = mgr.placement('host')
     assert all(e['CUDA_VISIBLE_DEVICES'] == '' for e in host) and [e['LOCAL_RANK'] for e in host] == ['0', '1']
     with pytest.raises(ValueError):

@@ -216,7 +216,15 @@ class WorkerPoolManager:
             if g.device_type in ('cuda', 'gpu'):
                 pool = visible[:len(ranks)] if visible is not None else [str(r) for r in ranks]
                 own = pool[i * per:(i + 1) * per]
-                env['CUDA_VISIBLE_DEVICES'] = ','.join(own + [d for d in pool if d not in own])
+                seen = own + [d for d in pool if d not in own]
+                for other in self.groups.values():
+                    if other is g or other.device_type not in ('cuda', 'gpu'):
+                        continue
+                    ov = getattr(other, 'visible_devices', None)
+                    olist = ([str(x) for x in ov] if isinstance(ov, (list, tuple)) else [x for x in str(ov).split(',') if x != '']) if ov is not None \
+                        else [str(r) for r in other.rank_list()]
+                    seen += [d for d in olist[:len(other.rank_list())] if d not in seen]
+                env['CUDA_VISIBLE_DEVICES'] = ','.join(seen)
                 env['TWINKLE_WORKER_DEVICES'] = ','.join(own)
                 env['LOCAL_RANK'] = '0'
             elif g.device_type == 'cpu':
