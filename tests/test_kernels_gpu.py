@@ -117,12 +117,15 @@ def test_grouped_gemm(E):
     assert rel(gw, gr) < 1e-5 and float(gw[1].abs().max()) == 0.0
 
 
-def test_rmsnorm(E):
+@pytest.mark.parametrize('rows,H', [(1000, 4096), (333, 1000), (257, 5120), (64, 8192), (33, 9216), (1, 128)])
+def test_rmsnorm(E, rows, H):
+    """Widths served by one / two column vectors per thread of the row-block backward (with a ragged last warp), wider
+    than it serves (one warp per row), and row counts that leave the last row group incomplete."""
     from twinkle_b200 import ops
     from twinkle_b200.ops import reference as ref
     torch.manual_seed(0)
-    x = torch.randn(1000, 4096, device='cuda').bfloat16().requires_grad_(True)
-    w = (torch.randn(4096, device='cuda') * 0.1 + 1).bfloat16().requires_grad_(True)
+    x = torch.randn(rows, H, device='cuda').bfloat16().requires_grad_(True)
+    w = (torch.randn(H, device='cuda') * 0.1 + 1).bfloat16().requires_grad_(True)
     y = ops.rmsnorm(x, w, 1e-6)
     g = torch.randn_like(y)
     y.backward(g)
@@ -132,11 +135,36 @@ def test_rmsnorm(E):
     assert rel(y, yr) < 4e-3 and rel(x.grad, xr.grad) < 4e-3 and rel(w.grad, wr.grad) < 4e-3
 
 
-def test_qk_norm_rope(E):
+def test_add_rmsnorm_fused(E):
+    """Residual add inside the norm kernel (forward) and the residual-stream gradient inside its backward kernel,
+    against the two-step fp32 reference; ``h`` must equal the bf16 sum bit for bit."""
     from twinkle_b200 import ops
     from twinkle_b200.ops import reference as ref
     torch.manual_seed(0)
-    T, hq, hkv, d = 777, 8, 2, 128
+    for rows, H in ((515, 4096), (77, 5120), (9, 9216)):
+        x = torch.randn(rows, H, device='cuda').bfloat16().requires_grad_(True)
+        r = torch.randn(rows, H, device='cuda').bfloat16().requires_grad_(True)
+        w = (torch.randn(H, device='cuda') * 0.1 + 1).bfloat16().requires_grad_(True)
+        y, h = ops.add_rmsnorm(x, r, w, 1e-6)
+        gy, gh = torch.randn_like(y), torch.randn_like(h)
+        torch.autograd.backward([y, h], [gy, gh])
+        assert torch.equal(h, x.detach() + r.detach())
+        xr, rr, wr = (t.detach().float().requires_grad_(True) for t in (x, r, w))
+        hr = (xr + rr) + ((xr + rr).bfloat16().float() - (xr + rr)).detach()
+        yr = ref.rmsnorm(hr, wr, 1e-6)
+        torch.autograd.backward([yr, hr], [gy.float(), gh.float()])
+        assert rel(y, yr) < 4e-3 and rel(w.grad, wr.grad) < 4e-3
+        assert rel(x.grad, xr.grad) < 4e-3 and torch.equal(x.grad, r.grad)
+
+
+@pytest.mark.parametrize('hq,hkv', [(8, 2), (5, 2), (3, 1), (32, 8)])
+def test_qk_norm_rope(E, hq, hkv):
+    """Head counts that fill the kernel's 8-heads-per-round walk exactly, leave a ragged last round, and put a q/k or
+    k/v boundary inside one warp's head pair."""
+    from twinkle_b200 import ops
+    from twinkle_b200.ops import reference as ref
+    torch.manual_seed(0)
+    T, d = 777, 128
     qkv = torch.randn(T, (hq + 2 * hkv) * d, device='cuda').bfloat16().requires_grad_(True)
     qw = (torch.randn(d, device='cuda') * 0.1 + 1).bfloat16().requires_grad_(True)
     kw = (torch.randn(d, device='cuda') * 0.1 + 1).bfloat16().requires_grad_(True)

@@ -245,10 +245,10 @@ class DecoderLayer(nn.Module):
             if kv_sink is not None and lin is None:
                 raise NotImplementedError('this kv_sink does not take linear-attention state (give it a linear_state attribute)')
             sink = (lambda conv, st: lin(self.layer_idx, conv, st)) if lin is not None else None
-            h = x + self.self_attn(self.input_layernorm(x), batch.cu_seqlens, state_sink=sink)
+            a = self.self_attn(self.input_layernorm(x), batch.cu_seqlens, state_sink=sink)
         else:
-            h = x + self.self_attn(self.input_layernorm(x), cos, sin, batch, kv_sink)
-        n = self.post_attention_layernorm(h)
+            a = self.self_attn(self.input_layernorm(x), cos, sin, batch, kv_sink)
+        n, h = self.post_attention_layernorm.forward_add(a, x)
         if self.is_moe:
             forced = batch.routed_experts[self.layer_idx] if batch.routed_experts is not None else None
             return ops.add(h, self.mlp(n, forced), value_unused=True)

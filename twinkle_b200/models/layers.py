@@ -187,6 +187,10 @@ class RMSNorm(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return ops.rmsnorm(x, self.weight, self.eps, self.offset)
 
+    def forward_add(self, x: torch.Tensor, residual: torch.Tensor):
+        """``(norm(x + residual), x + residual)`` — the residual add rides in the norm kernel."""
+        return ops.add_rmsnorm(x, residual, self.weight, self.eps, self.offset)
+
 
 class Embedding(nn.Module):
 

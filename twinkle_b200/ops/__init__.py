@@ -176,13 +176,36 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, offset: fl
     return ref.rmsnorm(x, weight, eps, offset)
 
 
+class _AddRMSNorm(torch.autograd.Function):
+    """``h = x + residual``; ``y = rmsnorm(h)`` in one kernel.  Backward: the gradient that reaches ``h`` directly (the
+    residual stream) is added inside the RMSNorm backward kernel, and the sum is the gradient of both inputs."""
+
+    @staticmethod
+    def forward(ctx, x, residual, weight, eps, offset):
+        x2 = x.reshape(-1, x.shape[-1])
+        r2 = residual.reshape(-1, x.shape[-1])
+        y, rstd, h = ext().rmsnorm_fwd(x2.contiguous(), weight, eps, offset, r2.contiguous())
+        ctx.save_for_backward(h, weight, rstd)
+        ctx.offset = offset
+        ctx.shape = x.shape
+        return y.view(x.shape), h.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, gy, gh):
+        h, weight, rstd = ctx.saved_tensors
+        if gy is None:
+            return gh, gh, None, None, None
+        gadd = gh.reshape(h.shape).contiguous() if gh is not None else None
+        gx, gw = ext().rmsnorm_bwd(gy.reshape(h.shape).contiguous(), h, weight, rstd, ctx.offset, gadd)
+        gx = gx.view(ctx.shape)
+        return gx, gx, gw.to(weight.dtype), None, None
+
+
 def add_rmsnorm(x, residual, weight, eps: float = 1e-6, offset: float = 0.0):
-    """Returns (normed, new_residual).  The add is a separate (cheap, fused by
-    the caching allocator-friendly kernel) step on CUDA so autograd sees two
-    differentiable ops."""
-    if _cuda(x) and x.dtype == torch.bfloat16:
-        new_res = x + residual
-        return rmsnorm(new_res, weight, eps, offset), new_res
+    """Returns ``(rmsnorm(x + residual), x + residual)``; one kernel on CUDA (the add costs no pass of its own, forward
+    or backward)."""
+    if _cuda(x) and x.dtype == torch.bfloat16 and residual.dtype == torch.bfloat16:
+        return _AddRMSNorm.apply(x, residual, weight, eps, offset)
     return ref.add_rmsnorm(x, residual, weight, eps, offset)
 
 

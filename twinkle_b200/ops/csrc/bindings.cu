@@ -9,8 +9,9 @@ torch::Tensor gemm(const torch::Tensor&, const torch::Tensor&, const std::string
 torch::Tensor grouped_gemm(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const std::string&, const c10::optional<torch::Tensor>&,
                            const c10::optional<torch::Tensor>&, bool);
 torch::Tensor grouped_gemm_wgrad(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, int64_t);
-std::vector<torch::Tensor> rmsnorm_fwd(const torch::Tensor&, const torch::Tensor&, double, double);
-std::vector<torch::Tensor> rmsnorm_bwd(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, double);
+std::vector<torch::Tensor> rmsnorm_fwd(const torch::Tensor&, const torch::Tensor&, double, double, const c10::optional<torch::Tensor>&);
+std::vector<torch::Tensor> rmsnorm_bwd(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, double,
+                                       const c10::optional<torch::Tensor>&);
 std::vector<torch::Tensor> qk_norm_rope_fwd(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&,
                                             const torch::Tensor&, int64_t, int64_t, int64_t, double);
 std::vector<torch::Tensor> qk_norm_rope_bwd(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&,
@@ -65,8 +66,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grouped_gemm", &tk::grouped_gemm, py::arg("x"), py::arg("w"), py::arg("offsets"), py::arg("layout") = "nt", py::arg("group_map") = py::none(),
         py::arg("out") = py::none(), py::arg("accumulate") = false);
   m.def("grouped_gemm_wgrad", &tk::grouped_gemm_wgrad);
-  m.def("rmsnorm_fwd", &tk::rmsnorm_fwd);
-  m.def("rmsnorm_bwd", &tk::rmsnorm_bwd);
+  m.def("rmsnorm_fwd", &tk::rmsnorm_fwd, py::arg("x"), py::arg("w"), py::arg("eps"), py::arg("offset"), py::arg("residual") = py::none());
+  m.def("rmsnorm_bwd", &tk::rmsnorm_bwd, py::arg("g"), py::arg("x"), py::arg("w"), py::arg("rstd"), py::arg("offset"),
+        py::arg("gadd") = py::none());
   m.def("qk_norm_rope_fwd", &tk::qk_norm_rope_fwd);
   m.def("qk_norm_rope_bwd", &tk::qk_norm_rope_bwd);
   m.def("swiglu_fwd", &tk::swiglu_fwd);

@@ -14,19 +14,40 @@ namespace tk {
 using bf16 = __nv_bfloat16;
 
 // ------------------------------------------------------------------ RMSNorm
-// One warp per row; lanes stride over 8-element vectors.
-__global__ void rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
-                                   float* __restrict__ rstd, int rows, int H, float eps, float offset) {
+// One warp per row; lanes stride over 8-element vectors.  With `res` the row normalised is h = bf16(x + res), which is
+// also written to `hsum` (the new residual stream): the add costs no pass of its own over the activations.
+__global__ void rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res, const bf16* __restrict__ w, bf16* __restrict__ y,
+                                   bf16* __restrict__ hsum, float* __restrict__ rstd, int rows, int H, float eps, float offset) {
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int nvec = H >> 3;
   for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * H);
     float ss = 0.f;
-    for (int v = lane; v < nvec; v += 32) {
-      uint4 u = xr[v];
-      float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
-      ss += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y + c.x * c.x + c.y * c.y + d.x * d.x + d.y * d.y;
+    if (res != nullptr) {
+      const uint4* rr = reinterpret_cast<const uint4*>(res + static_cast<size_t>(row) * H);
+      uint4* hr = reinterpret_cast<uint4*>(hsum + static_cast<size_t>(row) * H);
+      for (int v = lane; v < nvec; v += 32) {
+        const uint4 u = xr[v], q = rr[v];
+        const uint32_t* pu = &u.x; const uint32_t* pq = &q.x;
+        uint4 h;
+        uint32_t* ph = &h.x;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 a = unpack_bf16(pu[k]), b = unpack_bf16(pq[k]);
+          ph[k] = pack_bf16(a.x + b.x, a.y + b.y);
+          const float2 c = unpack_bf16(ph[k]);  // the norm sees the rounded sum, as it would after a separate add
+          ss += c.x * c.x + c.y * c.y;
+        }
+        hr[v] = h;
+      }
+      xr = hr;  // second pass: this lane re-reads the vectors it wrote itself
+    } else {
+      for (int v = lane; v < nvec; v += 32) {
+        uint4 u = xr[v];
+        float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+        ss += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y + c.x * c.x + c.y * c.y + d.x * d.x + d.y * d.y;
+      }
     }
     ss = warp_sum(ss);
     const float r = rsqrtf(ss / H + eps);
@@ -48,9 +69,115 @@ __global__ void rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __res
 }
 
 // dx = rstd·(g·w' − x·rstd²·mean(g·w'·x)),  dw += Σ_rows g·x·rstd.
-// Every warp keeps a private fp32 copy of dw in shared memory: lane l only ever touches the columns of its own
-// 16-byte vectors, so the accumulation needs no atomics; the warps' copies are summed once at the end and added to
-// the global result with one atomic per column and block.
+// Row-block form (H ≤ 8192): the whole block works on the same R rows at a time and a thread owns the same VPT 16-byte
+// column vectors in every row.  A row's g and x are read once into registers (2·R·VPT 16-byte loads per thread in
+// flight), the row dot products are reduced warp → shared memory → warp with one block barrier per R rows (the
+// partials are double-buffered), dx is produced from the registers, and dw lives in 8·VPT registers per thread for the
+// whole kernel — one global atomic per column and block at the end.  `gadd` (optional) is a gradient that reaches the
+// same tensor by another path (the residual stream): it is added to dx here instead of by a separate kernel.
+template <int VPT, int R>
+__global__ void __launch_bounds__(512, VPT == 1 ? 2 : 1)
+    rmsnorm_bwd_rows_kernel(const bf16* __restrict__ g, const bf16* __restrict__ x, const bf16* __restrict__ w, const float* __restrict__ rstd,
+                            const bf16* __restrict__ gadd, bf16* __restrict__ dx, float* __restrict__ dw, int rows, int H, float offset) {
+  __shared__ float s_part[2][R][16];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int nvec = H >> 3;
+  const float inv_h = 1.f / H;
+  float acc[VPT][8];
+  uint4 wv[VPT];
+  bool ok[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    ok[i] = v < nvec;
+    wv[i] = ok[i] ? reinterpret_cast<const uint4*>(w)[v] : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
+  }
+  uint32_t wp[VPT][4];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) { wp[i][0] = wv[i].x; wp[i][1] = wv[i].y; wp[i][2] = wv[i].z; wp[i][3] = wv[i].w; }
+  int buf = 0;
+#pragma unroll 1
+  for (long base = static_cast<long>(blockIdx.x) * R; base < rows; base += static_cast<long>(gridDim.x) * R, buf ^= 1) {
+    uint32_t ux[R][VPT][4], ug[R][VPT][4];
+    float r[R];
+#pragma unroll
+    for (int q = 0; q < R; ++q) {
+      const long row = base + q;
+      const bool live = row < rows;
+      r[q] = live ? rstd[row] : 0.f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int v = threadIdx.x + i * blockDim.x;
+        uint4 tx = make_uint4(0u, 0u, 0u, 0u), tg = tx;
+        if (live && ok[i]) {
+          tx = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * H)[v];
+          tg = reinterpret_cast<const uint4*>(g + static_cast<size_t>(row) * H)[v];
+        }
+        ux[q][i][0] = tx.x; ux[q][i][1] = tx.y; ux[q][i][2] = tx.z; ux[q][i][3] = tx.w;
+        ug[q][i][0] = tg.x; ug[q][i][1] = tg.y; ug[q][i][2] = tg.z; ug[q][i][3] = tg.w;
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < R; ++q) {
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 a = unpack_bf16(ux[q][i][k]), b = unpack_bf16(ug[q][i][k]), c = unpack_bf16(wp[i][k]);
+          dot += b.x * (c.x + offset) * a.x + b.y * (c.y + offset) * a.y;
+        }
+      }
+      dot = warp_sum(dot);
+      if (lane == 0) s_part[buf][q][warp] = dot;
+    }
+    __syncthreads();
+    // the packed values stay the only copy kept across the barrier: without this fence the compiler holds the unpacked
+    // fp32 values and products of the first pass for the second one, four times the registers
+#pragma unroll
+    for (int q = 0; q < R; ++q)
+#pragma unroll
+      for (int i = 0; i < VPT; ++i)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) asm volatile("" : "+r"(ux[q][i][k]), "+r"(ug[q][i][k]));
+#pragma unroll
+    for (int q = 0; q < R; ++q) {
+      const long row = base + q;
+      const float total = warp_sum(lane < nw ? s_part[buf][q][lane] : 0.f);
+      const float rq = r[q], coef = total * rq * rq * inv_h;  // rq = 0 for rows past the end: nothing is added to dw
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const bool store = ok[i] && row < rows;
+        uint4 ga = make_uint4(0u, 0u, 0u, 0u);  // bf16 zeros
+        if (gadd != nullptr && store) ga = reinterpret_cast<const uint4*>(gadd + static_cast<size_t>(row) * H)[threadIdx.x + i * blockDim.x];
+        const uint32_t pa[4] = {ga.x, ga.y, ga.z, ga.w};
+        uint32_t po[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 a = unpack_bf16(ux[q][i][k]), b = unpack_bf16(ug[q][i][k]), c = unpack_bf16(wp[i][k]), e = unpack_bf16(pa[k]);
+          po[k] = pack_bf16(rq * (b.x * (c.x + offset) - a.x * coef) + e.x, rq * (b.y * (c.y + offset) - a.y * coef) + e.y);
+          acc[i][2 * k] += b.x * a.x * rq;
+          acc[i][2 * k + 1] += b.y * a.y * rq;
+        }
+        if (store)
+          reinterpret_cast<uint4*>(dx + static_cast<size_t>(row) * H)[threadIdx.x + i * blockDim.x] = make_uint4(po[0], po[1], po[2], po[3]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    if (!ok[i]) continue;
+    const int c0 = (threadIdx.x + i * blockDim.x) * 8;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) atomicAdd(&dw[c0 + e], acc[i][e]);
+  }
+}
+
+// Wide rows (H > 8192): one warp per row.  Every warp keeps a private fp32 copy of dw in shared memory: lane l only ever
+// touches the columns of its own 16-byte vectors, so the accumulation needs no atomics; the warps' copies are summed
+// once at the end and added to the global result with one atomic per column and block.
 __global__ void rmsnorm_bwd_kernel(const bf16* __restrict__ g, const bf16* __restrict__ x, const bf16* __restrict__ w,
                                    const float* __restrict__ rstd, bf16* __restrict__ dx, float* __restrict__ dw, int rows, int H,
                                    float offset) {
@@ -105,31 +232,66 @@ __global__ void rmsnorm_bwd_kernel(const bf16* __restrict__ g, const bf16* __res
   }
 }
 
-std::vector<torch::Tensor> rmsnorm_fwd(const torch::Tensor& x, const torch::Tensor& w, double eps, double offset) {
+// Returns {y, rstd} or, with a residual, {y, rstd, h} where h = x + residual is the row that was normalised.
+std::vector<torch::Tensor> rmsnorm_fwd(const torch::Tensor& x, const torch::Tensor& w, double eps, double offset,
+                                       const c10::optional<torch::Tensor>& residual) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.dim() == 2 && x.is_contiguous(), "x: [rows,H] bf16 contiguous");
   TORCH_CHECK(w.scalar_type() == torch::kBFloat16 && w.is_contiguous() && w.numel() == x.size(1), "w: [H] bf16");
   const int rows = x.size(0), H = x.size(1);
   TORCH_CHECK(H % 8 == 0, "H must be a multiple of 8");
+  const bool has_res = residual.has_value() && residual->defined();
+  if (has_res)
+    TORCH_CHECK(residual->is_cuda() && residual->scalar_type() == torch::kBFloat16 && residual->is_contiguous() && residual->sizes() == x.sizes(),
+                "residual: same shape as x, bf16 contiguous");
   c10::cuda::CUDAGuard guard(x.device());
   auto y = torch::empty_like(x);
   auto rstd = torch::empty({rows}, x.options().dtype(torch::kFloat32));
-  if (rows == 0) return {y, rstd};
-  int blocks = std::min((rows + 7) / 8, num_sms() * 8);
-  rmsnorm_fwd_kernel<<<blocks, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
-      reinterpret_cast<const bf16*>(x.data_ptr()), reinterpret_cast<const bf16*>(w.data_ptr()), reinterpret_cast<bf16*>(y.data_ptr()),
-      rstd.data_ptr<float>(), rows, H, static_cast<float>(eps), static_cast<float>(offset));
-  count_launch();
-  TK_CUDA_CHECK(cudaGetLastError());
+  torch::Tensor h = has_res ? torch::empty_like(x) : torch::Tensor();
+  if (rows > 0) {
+    int blocks = std::min((rows + 7) / 8, num_sms() * 8);
+    rmsnorm_fwd_kernel<<<blocks, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
+        reinterpret_cast<const bf16*>(x.data_ptr()), has_res ? reinterpret_cast<const bf16*>(residual->data_ptr()) : nullptr,
+        reinterpret_cast<const bf16*>(w.data_ptr()), reinterpret_cast<bf16*>(y.data_ptr()),
+        has_res ? reinterpret_cast<bf16*>(h.data_ptr()) : nullptr, rstd.data_ptr<float>(), rows, H, static_cast<float>(eps),
+        static_cast<float>(offset));
+    count_launch();
+    TK_CUDA_CHECK(cudaGetLastError());
+  }
+  if (has_res) return {y, rstd, h};
   return {y, rstd};
 }
 
+// `gadd` (optional, same shape as x): dx = gadd + the RMSNorm input gradient.
 std::vector<torch::Tensor> rmsnorm_bwd(const torch::Tensor& g, const torch::Tensor& x, const torch::Tensor& w, const torch::Tensor& rstd,
-                                       double offset) {
+                                       double offset, const c10::optional<torch::Tensor>& gadd) {
   const int rows = x.size(0), H = x.size(1);
+  const bool has_add = gadd.has_value() && gadd->defined();
+  if (has_add)
+    TORCH_CHECK(gadd->is_cuda() && gadd->scalar_type() == torch::kBFloat16 && gadd->is_contiguous() && gadd->sizes() == x.sizes(),
+                "gadd: same shape as x, bf16 contiguous");
   c10::cuda::CUDAGuard guard(x.device());
   auto dx = torch::empty_like(x);
   auto dw = torch::zeros({H}, x.options().dtype(torch::kFloat32));
-  if (rows == 0) return {dx, dw};
+  if (rows == 0) {
+    if (has_add) dx.copy_(*gadd);
+    return {dx, dw};
+  }
+  if (H <= 8192) {
+    const int nvec = H / 8, vpt = nvec > 512 ? 2 : 1;
+    const int threads = std::min(512, ((nvec + vpt - 1) / vpt + 31) / 32 * 32);
+    constexpr int R = 2;
+    const int blocks = static_cast<int>(std::max<long>(1, std::min<long>((rows + R - 1L) / R, num_sms() * (vpt == 1 ? 2L : 1L))));
+    auto launch = [&](auto kern) {
+      kern<<<blocks, threads, 0, at::cuda::getCurrentCUDAStream()>>>(
+          reinterpret_cast<const bf16*>(g.data_ptr()), reinterpret_cast<const bf16*>(x.data_ptr()), reinterpret_cast<const bf16*>(w.data_ptr()),
+          rstd.data_ptr<float>(), has_add ? reinterpret_cast<const bf16*>(gadd->data_ptr()) : nullptr, reinterpret_cast<bf16*>(dx.data_ptr()),
+          dw.data_ptr<float>(), rows, H, static_cast<float>(offset));
+    };
+    if (vpt == 1) launch(rmsnorm_bwd_rows_kernel<1, R>); else launch(rmsnorm_bwd_rows_kernel<2, R>);
+    count_launch();
+    TK_CUDA_CHECK(cudaGetLastError());
+    return {dx, dw};
+  }
   // one private fp32 dw row per warp: as many warps as fit into shared memory (at most 8)
   int warps = 8;
   while (warps > 1 && static_cast<size_t>(warps) * H * sizeof(float) > 200 * 1024) warps >>= 1;
@@ -146,180 +308,217 @@ std::vector<torch::Tensor> rmsnorm_bwd(const torch::Tensor& g, const torch::Tens
       rstd.data_ptr<float>(), reinterpret_cast<bf16*>(dx.data_ptr()), dw.data_ptr<float>(), rows, H, static_cast<float>(offset));
   count_launch();
   TK_CUDA_CHECK(cudaGetLastError());
+  if (has_add) dx.add_(*gadd);
   return {dx, dw};
 }
 
 // ------------------------------------------------------- q/k-norm + RoPE (D=128)
-// One warp per (token, head).  Lane l holds elements [4l, 4l+4); the rotate-half partner of
-// element i (< 64) is i + 64, which lives in lane l ^ 16.
-// Each warp takes ROPE_U consecutive (token, head) items per round and issues all their loads before any arithmetic:
-// with one 256-byte load in flight per warp the kernel ran at a third of the memory bandwidth.
+// One warp per token.  The token's fused row [heads, 128] is contiguous, so the warp walks it in 512-byte steps: each
+// half-warp serves one head per step, lane j of the half holding elements [8j, 8j+8) with one 16-byte load; the
+// rotate-half partner of element i (< 64) is i + 64, which lives in lane j ^ 8 of the same half.  cos / sin of the token
+// are read once and kept in registers for all of its heads (read once per (token, head) they were two thirds of the
+// kernel's memory traffic), no index needs a division, and ROPE_U loads per lane are issued before any arithmetic.
 constexpr int ROPE_U = 4;
 
+__device__ __forceinline__ float half_warp_sum(float v) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& u, float (&x)[8]) {
+  const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+  x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y; x[4] = c.x; x[5] = c.y; x[6] = d.x; x[7] = d.y;
+}
+
+__device__ __forceinline__ uint4 pack8(const float (&x)[8]) {
+  return make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
+}
+
 template <bool HAS_NORM>
-__global__ void __launch_bounds__(256) qk_norm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw, const bf16* __restrict__ kw,
+__global__ void __launch_bounds__(256, 3) qk_norm_rope_fwd_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ qw, const bf16* __restrict__ kw,
                                                                const float* __restrict__ cosb, const float* __restrict__ sinb, bf16* __restrict__ q,
                                                                bf16* __restrict__ k, bf16* __restrict__ v, float* __restrict__ rstd, int T, int hq,
                                                                int hkv, float eps) {
   constexpr int D = 128;
   const int heads = hq + 2 * hkv;
-  const int lane = threadIdx.x & 31;
-  const long total = static_cast<long>(T) * heads;
-  const long nwarps = static_cast<long>(gridDim.x) * (blockDim.x >> 5);
-  const int fi = (lane & 15) * 4;  // frequency index of this lane's first element
-  float wq[4] = {1.f, 1.f, 1.f, 1.f}, wk[4] = {1.f, 1.f, 1.f, 1.f};
-  if (HAS_NORM) {
-    const uint2 a = *reinterpret_cast<const uint2*>(qw + lane * 4), b = *reinterpret_cast<const uint2*>(kw + lane * 4);
-    const float2 a0 = unpack_bf16(a.x), a1 = unpack_bf16(a.y), b0 = unpack_bf16(b.x), b1 = unpack_bf16(b.y);
-    wq[0] = a0.x; wq[1] = a0.y; wq[2] = a1.x; wq[3] = a1.y;
-    wk[0] = b0.x; wk[1] = b0.y; wk[2] = b1.x; wk[3] = b1.y;
-  }
-  for (long base = (static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * ROPE_U; base < total; base += nwarps * ROPE_U) {
-    uint2 raw[ROPE_U];
-    float4 cs[ROPE_U], sn4[ROPE_U];
-    int tt[ROPE_U], hh[ROPE_U];
+  const int lane = threadIdx.x & 31, half = lane >> 4, j = lane & 15;
+  const int fi = (j & 7) * 8;       // frequency index of this lane's first element
+  const bool upper = j >= 8;        // elements 64..127
+  const int nwarps = gridDim.x * (blockDim.x >> 5);
+  __shared__ float s_w[2][D];  // norm weights of q and k as fp32
+  for (int i = threadIdx.x; i < 2 * D; i += blockDim.x)
+    (&s_w[0][0])[i] = HAS_NORM ? __bfloat162float(i < D ? qw[i] : kw[i - D]) : 1.f;
+  __syncthreads();
+  for (int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < T; t += nwarps) {
+    float cc[8], sn[8];
+    {
+      const float4 c0 = *reinterpret_cast<const float4*>(cosb + static_cast<size_t>(t) * 64 + fi);
+      const float4 c1 = *reinterpret_cast<const float4*>(cosb + static_cast<size_t>(t) * 64 + fi + 4);
+      const float4 s0 = *reinterpret_cast<const float4*>(sinb + static_cast<size_t>(t) * 64 + fi);
+      const float4 s1 = *reinterpret_cast<const float4*>(sinb + static_cast<size_t>(t) * 64 + fi + 4);
+      cc[0] = c0.x; cc[1] = c0.y; cc[2] = c0.z; cc[3] = c0.w; cc[4] = c1.x; cc[5] = c1.y; cc[6] = c1.z; cc[7] = c1.w;
+      sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+      if (!upper) {
 #pragma unroll
-    for (int u = 0; u < ROPE_U; ++u) {
-      const long item = base + u;
-      tt[u] = -1;
-      if (item < total) {
-        tt[u] = static_cast<int>(item / heads);
-        hh[u] = static_cast<int>(item - static_cast<long>(tt[u]) * heads);
-        raw[u] = *reinterpret_cast<const uint2*>(qkv + static_cast<size_t>(item) * D + lane * 4);
-        if (hh[u] < hq + hkv) {
-          cs[u] = *reinterpret_cast<const float4*>(cosb + static_cast<size_t>(tt[u]) * 64 + fi);
-          sn4[u] = *reinterpret_cast<const float4*>(sinb + static_cast<size_t>(tt[u]) * 64 + fi);
-        }
+        for (int i = 0; i < 8; ++i) sn[i] = -sn[i];  // o = x·cos − partner·sin below 64, + above
       }
     }
+    const bf16* row = qkv + static_cast<size_t>(t) * heads * D + j * 8;
+    for (int h0 = 0; h0 < heads; h0 += 2 * ROPE_U) {
+      uint4 raw[ROPE_U];
 #pragma unroll
-    for (int u = 0; u < ROPE_U; ++u) {
-      if (tt[u] < 0) continue;  // uniform over the warp
-      const int t = tt[u], h = hh[u];
-      if (h >= hq + hkv) {  // v: plain copy
-        *reinterpret_cast<uint2*>(v + (static_cast<size_t>(t) * hkv + (h - hq - hkv)) * D + lane * 4) = raw[u];
-        continue;
+      for (int u = 0; u < ROPE_U; ++u) {
+        const int h = h0 + 2 * u + half;
+        raw[u] = h < heads ? *reinterpret_cast<const uint4*>(row + static_cast<size_t>(h) * D) : make_uint4(0u, 0u, 0u, 0u);
       }
-      float2 a = unpack_bf16(raw[u].x), b = unpack_bf16(raw[u].y);
-      float xv[4] = {a.x, a.y, b.x, b.y};
-      const bool is_q = h < hq;
-      if (HAS_NORM) {
-        float ss = warp_sum(xv[0] * xv[0] + xv[1] * xv[1] + xv[2] * xv[2] + xv[3] * xv[3]);
-        const float r = rsqrtf(ss / D + eps);
-        if (lane == 0) rstd[static_cast<size_t>(t) * (hq + hkv) + h] = r;
-        // the reference path rounds the normalised value to bf16 before RoPE
 #pragma unroll
-        for (int i = 0; i < 4; ++i) xv[i] = __bfloat162float(__float2bfloat16(xv[i] * (r * (is_q ? wq[i] : wk[i]))));
-      }
-      const float cc[4] = {cs[u].x, cs[u].y, cs[u].z, cs[u].w}, sn[4] = {sn4[u].x, sn4[u].y, sn4[u].z, sn4[u].w};
-      float o[4];
+      for (int u = 0; u < ROPE_U; ++u) {
+        const int h = h0 + 2 * u + half;
+        if (h0 + 2 * u >= heads) break;  // uniform over the warp
+        // every lane runs the arithmetic (the shuffles need the whole warp); what is stored depends on the head's kind
+        float xv[8];
+        unpack8(raw[u], xv);
+        const bool is_q = h < hq;
+        if (HAS_NORM) {
+          float ss = 0.f;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float other = __shfl_xor_sync(0xffffffffu, xv[i], 16);
-        o[i] = (lane < 16) ? (xv[i] * cc[i] - other * sn[i]) : (xv[i] * cc[i] + other * sn[i]);
+          for (int i = 0; i < 8; ++i) ss += xv[i] * xv[i];
+          ss = half_warp_sum(ss);
+          const float r = rsqrtf(ss / D + eps);
+          const float* wsrc = &s_w[is_q ? 0 : 1][j * 8];
+          const float4 w0 = *reinterpret_cast<const float4*>(wsrc), w1 = *reinterpret_cast<const float4*>(wsrc + 4);
+          const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+          if (j == 0 && h < hq + hkv) rstd[static_cast<size_t>(t) * (hq + hkv) + h] = r;
+          // the reference path rounds the normalised value to bf16 before RoPE
+#pragma unroll
+          for (int i = 0; i < 8; ++i) xv[i] = __bfloat162float(__float2bfloat16(xv[i] * (r * wv[i])));
+        }
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float other = __shfl_xor_sync(0xffffffffu, xv[i], 8);
+          o[i] = xv[i] * cc[i] + other * sn[i];
+        }
+        if (h >= heads) continue;
+        if (h >= hq + hkv) {  // v: plain copy
+          *reinterpret_cast<uint4*>(v + (static_cast<size_t>(t) * hkv + (h - hq - hkv)) * D + j * 8) = raw[u];
+        } else {
+          bf16* dst = is_q ? q + (static_cast<size_t>(t) * hq + h) * D : k + (static_cast<size_t>(t) * hkv + (h - hq)) * D;
+          *reinterpret_cast<uint4*>(dst + j * 8) = pack8(o);
+        }
       }
-      uint2 outv = make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
-      bf16* dst = is_q ? q + (static_cast<size_t>(t) * hq + h) * D : k + (static_cast<size_t>(t) * hkv + (h - hq)) * D;
-      *reinterpret_cast<uint2*>(dst + lane * 4) = outv;
     }
   }
 }
 
 template <bool HAS_NORM>
-__global__ void __launch_bounds__(256) qk_norm_rope_bwd_kernel(const bf16* __restrict__ gq, const bf16* __restrict__ gk, const bf16* __restrict__ gv,
+__global__ void __launch_bounds__(256, 3) qk_norm_rope_bwd_kernel(const bf16* __restrict__ gq, const bf16* __restrict__ gk, const bf16* __restrict__ gv,
                                                                const bf16* __restrict__ qkv, const bf16* __restrict__ qw, const bf16* __restrict__ kw,
                                                                const float* __restrict__ cosb, const float* __restrict__ sinb,
                                                                const float* __restrict__ rstd, bf16* __restrict__ dqkv, float* __restrict__ dqw,
                                                                float* __restrict__ dkw, int T, int hq, int hkv) {
   constexpr int D = 128;
-  constexpr int U = 2;  // items per warp per round, all loads issued before the arithmetic
+  constexpr int U = 2;  // head pairs per round: 2·U 16-byte loads per lane are issued before the arithmetic
   __shared__ float s_dw[2][D];
-  for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) (&s_dw[0][0])[i] = 0.f;
+  __shared__ float s_w[2][D];
+  for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) {
+    (&s_dw[0][0])[i] = 0.f;
+    (&s_w[0][0])[i] = HAS_NORM ? __bfloat162float(i < D ? qw[i] : kw[i - D]) : 1.f;
+  }
   __syncthreads();
   const int heads = hq + 2 * hkv;
-  const int lane = threadIdx.x & 31;
-  const long total = static_cast<long>(T) * heads;
-  const long nwarps = static_cast<long>(gridDim.x) * (blockDim.x >> 5);
-  const int fi = (lane & 15) * 4;
-  float wq[4] = {1.f, 1.f, 1.f, 1.f}, wk[4] = {1.f, 1.f, 1.f, 1.f};
-  if (HAS_NORM) {
-    const uint2 a = *reinterpret_cast<const uint2*>(qw + lane * 4), b = *reinterpret_cast<const uint2*>(kw + lane * 4);
-    const float2 a0 = unpack_bf16(a.x), a1 = unpack_bf16(a.y), b0 = unpack_bf16(b.x), b1 = unpack_bf16(b.y);
-    wq[0] = a0.x; wq[1] = a0.y; wq[2] = a1.x; wq[3] = a1.y;
-    wk[0] = b0.x; wk[1] = b0.y; wk[2] = b1.x; wk[3] = b1.y;
-  }
-  float acc_w[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-  for (long base = (static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * U; base < total; base += nwarps * U) {
-    uint2 graw[U], raw[U];
-    float4 cs[U], sn4[U];
-    float rr[U];
-    int tt[U], hh[U];
+  const int lane = threadIdx.x & 31, half = lane >> 4, j = lane & 15;
+  const int fi = (j & 7) * 8;
+  const bool upper = j >= 8;
+  const int nwarps = gridDim.x * (blockDim.x >> 5);
+  float acc_w[2][8];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long item = base + u;
-      tt[u] = -1;
-      if (item < total) {
-        const int t = static_cast<int>(item / heads), h = static_cast<int>(item - static_cast<long>(t) * heads);
-        tt[u] = t; hh[u] = h;
-        if (h >= hq + hkv) {
-          graw[u] = *reinterpret_cast<const uint2*>(gv + (static_cast<size_t>(t) * hkv + (h - hq - hkv)) * D + lane * 4);
-        } else {
-          const bf16* gsrc = h < hq ? gq + (static_cast<size_t>(t) * hq + h) * D : gk + (static_cast<size_t>(t) * hkv + (h - hq)) * D;
-          graw[u] = *reinterpret_cast<const uint2*>(gsrc + lane * 4);
-          cs[u] = *reinterpret_cast<const float4*>(cosb + static_cast<size_t>(t) * 64 + fi);
-          sn4[u] = *reinterpret_cast<const float4*>(sinb + static_cast<size_t>(t) * 64 + fi);
-          if (HAS_NORM) {
-            raw[u] = *reinterpret_cast<const uint2*>(qkv + static_cast<size_t>(item) * D + lane * 4);
+  for (int i = 0; i < 8; ++i) acc_w[0][i] = acc_w[1][i] = 0.f;
+  for (int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < T; t += nwarps) {
+    float cc[8], sn[8];
+    {
+      const float4 c0 = *reinterpret_cast<const float4*>(cosb + static_cast<size_t>(t) * 64 + fi);
+      const float4 c1 = *reinterpret_cast<const float4*>(cosb + static_cast<size_t>(t) * 64 + fi + 4);
+      const float4 s0 = *reinterpret_cast<const float4*>(sinb + static_cast<size_t>(t) * 64 + fi);
+      const float4 s1 = *reinterpret_cast<const float4*>(sinb + static_cast<size_t>(t) * 64 + fi + 4);
+      cc[0] = c0.x; cc[1] = c0.y; cc[2] = c0.z; cc[3] = c0.w; cc[4] = c1.x; cc[5] = c1.y; cc[6] = c1.z; cc[7] = c1.w;
+      sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+      if (upper) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sn[i] = -sn[i];  // transpose of the forward rotation: + below 64, − above
+      }
+    }
+    for (int h0 = 0; h0 < heads; h0 += 2 * U) {
+      uint4 graw[U], raw[U];
+      float rr[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int h = h0 + 2 * u + half;
+        graw[u] = raw[u] = make_uint4(0u, 0u, 0u, 0u);
+        rr[u] = 0.f;
+        if (h < heads) {
+          const bf16* gsrc = h < hq ? gq + (static_cast<size_t>(t) * hq + h) * D
+                                    : (h < hq + hkv ? gk + (static_cast<size_t>(t) * hkv + (h - hq)) * D
+                                                    : gv + (static_cast<size_t>(t) * hkv + (h - hq - hkv)) * D);
+          graw[u] = *reinterpret_cast<const uint4*>(gsrc + j * 8);
+          if (HAS_NORM && h < hq + hkv) {
+            raw[u] = *reinterpret_cast<const uint4*>(qkv + (static_cast<size_t>(t) * heads + h) * D + j * 8);
             rr[u] = rstd[static_cast<size_t>(t) * (hq + hkv) + h];
           }
         }
       }
-    }
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      if (tt[u] < 0) continue;  // uniform over the warp
-      const int t = tt[u], h = hh[u];
-      bf16* dst = dqkv + (static_cast<size_t>(t) * heads + h) * D + lane * 4;
-      if (h >= hq + hkv) {
-        *reinterpret_cast<uint2*>(dst) = graw[u];
-        continue;
-      }
-      const bool is_q = h < hq;
-      float2 ga = unpack_bf16(graw[u].x), gb = unpack_bf16(graw[u].y);
-      const float gy[4] = {ga.x, ga.y, gb.x, gb.y};
-      const float cc[4] = {cs[u].x, cs[u].y, cs[u].z, cs[u].w}, sn[4] = {sn4[u].x, sn4[u].y, sn4[u].z, sn4[u].w};
-      float gn[4];  // gradient w.r.t. the (normalised) pre-RoPE value
+      for (int u = 0; u < U; ++u) {
+        const int h = h0 + 2 * u + half;
+        if (h0 + 2 * u >= heads) break;  // uniform over the warp
+        const bool is_q = h < hq, is_v = h >= hq + hkv;
+        float gy[8], gn[8];  // gn: gradient w.r.t. the (normalised) pre-RoPE value
+        unpack8(graw[u], gy);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float other = __shfl_xor_sync(0xffffffffu, gy[i], 16);
-        gn[i] = (lane < 16) ? (gy[i] * cc[i] + other * sn[i]) : (gy[i] * cc[i] - other * sn[i]);
-      }
-      if (!HAS_NORM) {
-        *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(gn[0], gn[1]), pack_bf16(gn[2], gn[3]));
-        continue;
-      }
-      float2 xa = unpack_bf16(raw[u].x), xb = unpack_bf16(raw[u].y);
-      const float xv[4] = {xa.x, xa.y, xb.x, xb.y};
-      const float r = rr[u];
-      float dot = 0.f;
+        for (int i = 0; i < 8; ++i) {
+          const float other = __shfl_xor_sync(0xffffffffu, gy[i], 8);
+          gn[i] = gy[i] * cc[i] + other * sn[i];
+        }
+        uint4 outv;
+        if (HAS_NORM) {
+          float xv[8], wv[8];
+          unpack8(raw[u], xv);
+          const float* wsrc = &s_w[is_q ? 0 : 1][j * 8];
+          const float4 w0 = *reinterpret_cast<const float4*>(wsrc), w1 = *reinterpret_cast<const float4*>(wsrc + 4);
+          wv[0] = w0.x; wv[1] = w0.y; wv[2] = w0.z; wv[3] = w0.w; wv[4] = w1.x; wv[5] = w1.y; wv[6] = w1.z; wv[7] = w1.w;
+          const float r = rr[u];
+          float dot = 0.f;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) dot += gn[i] * (is_q ? wq[i] : wk[i]) * xv[i];
-      dot = warp_sum(dot);
-      const float coef = dot * r * r / D;
-      float dx[4];
+          for (int i = 0; i < 8; ++i) dot += gn[i] * wv[i] * xv[i];
+          dot = half_warp_sum(dot);
+          const float coef = dot * r * r / D;
+          float dx[8];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        dx[i] = r * (gn[i] * (is_q ? wq[i] : wk[i]) - xv[i] * coef);
-        acc_w[is_q ? 0 : 1][i] += gn[i] * xv[i] * r;
+          for (int i = 0; i < 8; ++i) {
+            dx[i] = r * (gn[i] * wv[i] - xv[i] * coef);
+            const float gw = gn[i] * xv[i] * r;  // zero for v heads and heads past the end (r = 0 there)
+            acc_w[0][i] += is_q ? gw : 0.f;
+            acc_w[1][i] += is_q ? 0.f : gw;
+          }
+          outv = pack8(dx);
+        } else {
+          outv = pack8(gn);
+        }
+        if (h >= heads) continue;
+        *reinterpret_cast<uint4*>(dqkv + (static_cast<size_t>(t) * heads + h) * D + j * 8) = is_v ? graw[u] : outv;
       }
-      *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(dx[0], dx[1]), pack_bf16(dx[2], dx[3]));
     }
   }
   if (HAS_NORM) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      atomicAdd(&s_dw[0][lane * 4 + i], acc_w[0][i]);
-      atomicAdd(&s_dw[1][lane * 4 + i], acc_w[1][i]);
+    for (int i = 0; i < 8; ++i) {
+      const float a = acc_w[0][i] + __shfl_xor_sync(0xffffffffu, acc_w[0][i], 16);
+      const float b = acc_w[1][i] + __shfl_xor_sync(0xffffffffu, acc_w[1][i], 16);
+      if (half == 0) {
+        atomicAdd(&s_dw[0][j * 8 + i], a);
+        atomicAdd(&s_dw[1][j * 8 + i], b);
+      }
     }
     __syncthreads();
     for (int i = threadIdx.x; i < D; i += blockDim.x) {
@@ -336,6 +535,7 @@ std::vector<torch::Tensor> qk_norm_rope_fwd(const torch::Tensor& qkv, const torc
   TORCH_CHECK(qkv.is_cuda() && qkv.scalar_type() == torch::kBFloat16 && qkv.is_contiguous() && qkv.dim() == 2, "qkv [T, heads*128] bf16");
   TORCH_CHECK(qkv.size(1) == (hq + 2 * hkv) * d, "qkv width mismatch");
   TORCH_CHECK(cosb.scalar_type() == torch::kFloat32 && cosb.is_contiguous() && cosb.size(1) == 64, "cos [T,64] fp32");
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(qkv.data_ptr()) % 16 == 0, "qkv must be 16-byte aligned");
   c10::cuda::CUDAGuard guard(qkv.device());
   const int T = qkv.size(0);
   auto q = torch::empty({T, hq, d}, qkv.options());
@@ -343,8 +543,7 @@ std::vector<torch::Tensor> qk_norm_rope_fwd(const torch::Tensor& qkv, const torc
   auto v = torch::empty({T, hkv, d}, qkv.options());
   auto rstd = torch::empty({T, hq + hkv}, qkv.options().dtype(torch::kFloat32));
   if (T == 0) return {q, k, v, rstd};
-  long items = static_cast<long>(T) * (hq + 2 * hkv);
-  int blocks = static_cast<int>(std::max<long>(1, std::min<long>((items + 8 * ROPE_U - 1) / (8 * ROPE_U), num_sms() * 8L)));
+  int blocks = static_cast<int>(std::max<long>(1, std::min<long>((T + 7L) / 8, num_sms() * 8L)));
   qk_norm_rope_fwd_kernel<true><<<blocks, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
       reinterpret_cast<const bf16*>(qkv.data_ptr()), reinterpret_cast<const bf16*>(qw.data_ptr()), reinterpret_cast<const bf16*>(kw.data_ptr()),
       cosb.data_ptr<float>(), sinb.data_ptr<float>(), reinterpret_cast<bf16*>(q.data_ptr()), reinterpret_cast<bf16*>(k.data_ptr()),
@@ -363,8 +562,7 @@ std::vector<torch::Tensor> qk_norm_rope_bwd(const torch::Tensor& gq, const torch
   auto dqw = torch::zeros({d}, qkv.options().dtype(torch::kFloat32));
   auto dkw = torch::zeros({d}, qkv.options().dtype(torch::kFloat32));
   if (T == 0) return {dqkv, dqw, dkw};
-  long items = static_cast<long>(T) * (hq + 2 * hkv);
-  int blocks = static_cast<int>(std::min<long>((items + 7) / 8, num_sms() * 8L));
+  int blocks = static_cast<int>(std::max<long>(1, std::min<long>((T + 7L) / 8, num_sms() * 8L)));
   qk_norm_rope_bwd_kernel<true><<<blocks, 256, 0, at::cuda::getCurrentCUDAStream()>>>(
       reinterpret_cast<const bf16*>(gq.data_ptr()), reinterpret_cast<const bf16*>(gk.data_ptr()), reinterpret_cast<const bf16*>(gv.data_ptr()),
       reinterpret_cast<const bf16*>(qkv.data_ptr()), reinterpret_cast<const bf16*>(qw.data_ptr()), reinterpret_cast<const bf16*>(kw.data_ptr()),

@@ -119,6 +119,23 @@ def make(op: str, a) -> Tuple[Callable[[], None], float, float]:
         p, g = torch.randn(n, device=dev), torch.randn(n, device=dev, dtype=bf)
         m, v, lo = torch.zeros(n, device=dev), torch.zeros(n, device=dev), torch.empty(n, device=dev, dtype=bf)
         return (lambda: ops.adamw_step(p, m, v, g, lo, 1e-4, 0.9, 0.95, 1e-8, 0.01, 1, 1.0)), 0.0, float(n) * (4 * 3 * 2 + 2 + 2)
+    if op == 'sgmv':
+        # four tenants share the batch: equal token segments, each on its own adapter slot (rank a.rank of a pool of 16)
+        T, H, N, r = a.tokens, a.hidden, a.n, a.rank
+        x = torch.randn(T, H, device=dev, dtype=bf)
+        A = torch.randn(4, 16, H, device=dev, dtype=bf) * 0.02
+        B = torch.randn(4, N, 16, device=dev, dtype=bf) * 0.02
+        cuts = [T * i // 4 for i in range(5)]
+        host = [(cuts[i], cuts[i + 1], i, r, 2.0) for i in range(4)]
+        st = torch.tensor(cuts, dtype=torch.int32, device=dev)
+        sl = torch.arange(4, dtype=torch.int32, device=dev)
+        rk = torch.full((4, ), r, dtype=torch.int32, device=dev)
+        sc = torch.full((4, ), 2.0, dtype=torch.float32, device=dev)
+
+        def f():
+            with torch.no_grad():
+                ops.sgmv(x, A, B, st, sl, rk, sc, host)
+        return f, 2.0 * T * r * (H + N), 2.0 * T * (H + N)
     if op == 'paged_decode':
         B, bs, ctx = a.batch, 16, a.seq
         nb = B * ((ctx + bs - 1) // bs)
@@ -156,6 +173,7 @@ def main() -> None:
     ap.add_argument('--hidden', type=int, default=4096)
     ap.add_argument('--vocab', type=int, default=151936)
     ap.add_argument('--batch', type=int, default=256)
+    ap.add_argument('--rank', type=int, default=16)
     ap.add_argument('--numel', type=int, default=1 << 28)
     ap.add_argument('--iters', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)

@@ -7,7 +7,8 @@ Measures, at the sizes of the Qwen3-8B training step (one decoder layer's parame
 65536 tokens per rank), every kernel the sharded engine puts between two GEMMs, and prints one JSON line on rank 0:
 the cross-GPU flag barrier, the parameter all-gather, the gradient reduce-scatter (+cast, scale, accumulate), the
 Ulysses head↔sequence exchange as one receive-side pull of q, k and v, the first-generation kernels of the same
-operations for comparison (``*_legacy``), and the NCCL collective each one replaces.  Times are CUDA events on the
+operations for comparison (``*_legacy``), the NCCL collective each one replaces, and the trainer → sampler weight push
+(one rank writing a bucket into a peer's landing zone, with and without the fp32 → bf16 cast).  Times are CUDA events on the
 launching stream after warm-up, maximum over ranks; ``gbs`` is the bytes a rank must receive over NVLink divided by
 that time, to be read against the measured peer-copy bandwidth of 770 GB/s per direction.
 """
@@ -106,6 +107,21 @@ def main() -> None:
                 dist.all_to_all_single(recv_, send)
 
         out['ulysses_qkv_nccl_all_to_all'] = entry(timeit(nccl_a2a), recv)
+    # ---- trainer → sampler weight push: rank 0 writes a 512 MiB bf16 bucket into rank 1's landing zone (and the same
+    # bucket from fp32 masters, cast on the way); only the sender works, the others wait at the barrier
+    n_w = 256 << 20
+    landing = sc.alloc(n_w, torch.bfloat16)
+    torch.manual_seed(1234)  # the same values on every rank, so that the receiver can check what landed
+    src16 = torch.randn(n_w, device=dev, dtype=torch.bfloat16)
+    src32 = torch.randn(n_w, device=dev, dtype=torch.float32)
+    sc.sync_all()
+    dst = [sc.peer_ptrs(landing)[1 % world]]
+    for tag, src in (('weight_push_bf16', src16), ('weight_push_fp32_cast', src32)):
+        out[tag] = entry(timeit((lambda s_=src: E.peer_copy_cast(s_, dst, 0)) if rank == 0 else (lambda: None), iters=5), n_w * 2)
+    sc.sync_all()
+    ok = torch.tensor([1.0 if (rank != 1 % world or torch.equal(landing, src32.bfloat16())) else 0.0], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    out['weight_push_received_ok'] = bool(ok.item() > 0.5)
     out['kernel_error_word'] = E.read_and_clear_error()
     if rank == 0:
         print(json.dumps(out), flush=True)
