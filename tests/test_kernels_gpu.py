@@ -465,3 +465,75 @@ def test_sharded_engine_training_matches_cpu(E):
     for (a, na), (b, nb) in zip(cpu, gpu):
         assert abs(a - b) < 3e-2 and abs(na - nb) < 5e-2 * max(na, 1.0), (cpu, gpu)
     assert E.read_and_clear_error() == 0
+
+
+def test_gated_delta_rule_and_conv_kernels(E):
+    """Linear-attention kernels against the fp32 recurrence / convolution on PyTorch: packed sequences (one of them a
+    single token, one empty), grouped heads, both key widths, state hand-over to a second call, gradients through the
+    autograd wrapper."""
+    import torch.nn.functional as F
+    from twinkle_b200 import ops
+    from twinkle_b200.models.linear_attention import causal_conv1d_varlen_torch, gated_delta_rule_recurrent
+    torch.manual_seed(0)
+    for dk, dv, hk, hv in ((128, 128, 2, 4), (64, 96, 3, 3)):
+        lens = [37, 1, 0, 150]
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device='cuda')
+        T = sum(lens)
+        qkv = torch.randn(T, 2 * hk * dk + hv * dv, device='cuda').bfloat16()       # slices of one fused row, as the layer passes them
+        q, k = qkv[:, :hk * dk].view(T, hk, dk), qkv[:, hk * dk:2 * hk * dk].view(T, hk, dk)
+        v = qkv[:, 2 * hk * dk:].view(T, hv, dv)
+        g = -torch.rand(T, hv, device='cuda') * 0.2
+        beta = torch.rand(T, hv, device='cuda')
+        o, fin = ops.gated_delta_rule_varlen(q, k, v, g, beta, cu, return_states=True)
+        assert fin.shape == (4, hv, dk, dv) and float(fin[2].abs().max()) == 0.0
+        rep = hv // hk
+        qn = F.normalize(q.float(), dim=-1).repeat_interleave(rep, 1)
+        kn = F.normalize(k.float(), dim=-1).repeat_interleave(rep, 1)
+        b = cu.tolist()
+        for i, (a_, b_) in enumerate(zip(b[:-1], b[1:])):
+            if b_ == a_:
+                continue
+            o_r, s_r = gated_delta_rule_recurrent(qn[a_:b_], kn[a_:b_], v[a_:b_].float(), g[a_:b_], beta[a_:b_])
+            assert rel(o[a_:b_], o_r) < 8e-3, (dk, i)
+            assert rel(fin[i], s_r) < 2e-3, (dk, i)
+        # continue sequence 3 in two calls: second call starts from the first one's state
+        a_, b_ = b[3], b[4]
+        mid = a_ + 70
+        cu1 = torch.tensor([0, 70], dtype=torch.int32, device='cuda')
+        cu2 = torch.tensor([0, b_ - mid], dtype=torch.int32, device='cuda')
+        o1, s1 = ops.gated_delta_rule_varlen(q[a_:mid], k[a_:mid], v[a_:mid], g[a_:mid].contiguous(), beta[a_:mid].contiguous(), cu1,
+                                             return_states=True)
+        o2, s2 = ops.gated_delta_rule_varlen(q[mid:b_], k[mid:b_], v[mid:b_], g[mid:b_].contiguous(), beta[mid:b_].contiguous(), cu2,
+                                             init_state=s1, return_states=True)
+        assert rel(torch.cat([o1, o2]), o[a_:b_]) < 1e-3 and rel(s2[0], fin[3]) < 1e-5
+    # gradients: kernel forward + PyTorch backward against the all-PyTorch fp32 function
+    T, hk, hv, dk, dv = 96, 2, 2, 64, 64
+    cu = torch.tensor([0, 40, 96], dtype=torch.int32, device='cuda')
+    ins = [torch.randn(T, hk, dk, device='cuda').bfloat16(), torch.randn(T, hk, dk, device='cuda').bfloat16(),
+           torch.randn(T, hv, dv, device='cuda').bfloat16(), -torch.rand(T, hv, device='cuda') * 0.2, torch.rand(T, hv, device='cuda')]
+    a = [t.clone().requires_grad_(True) for t in ins]
+    o = ops.gated_delta_rule_varlen(*a, cu)
+    go = torch.randn_like(o)
+    o.backward(go)
+    from twinkle_b200.models.linear_attention import gated_delta_rule_varlen_torch
+    r = [t.float().clone().requires_grad_(True) for t in ins]
+    o_ref = gated_delta_rule_varlen_torch(*r, cu.cpu(), None, chunk=32)
+    o_ref.backward(go.float())
+    assert rel(o, o_ref) < 8e-3
+    for x_, y_ in zip(a, r):
+        assert rel(x_.grad, y_.grad) < 2e-2
+    # convolution + SiLU, window never crossing a boundary; input is a column slice of a wider row
+    C, W = 256, 4
+    wide = torch.randn(T, C + 64, device='cuda').bfloat16()
+    x = wide[:, :C].requires_grad_(False)
+    w = (torch.randn(C, W, device='cuda') * 0.5).bfloat16()
+    for act in (True, False):
+        y = ops.causal_conv1d_varlen(x, w, cu, act)
+        y_ref = causal_conv1d_varlen_torch(x.float(), w.float(), cu, act)
+        assert rel(y, y_ref) < 6e-3
+    xg = x.clone().contiguous().requires_grad_(True)
+    wg = w.clone().requires_grad_(True)
+    ops.causal_conv1d_varlen(xg, wg, cu, True).backward(torch.ones(T, C, device='cuda').bfloat16())
+    xr, wr = x.float().clone().requires_grad_(True), w.float().clone().requires_grad_(True)
+    causal_conv1d_varlen_torch(xr, wr, cu, True).sum().backward()
+    assert rel(xg.grad, xr.grad) < 1e-2 and rel(wg.grad, wr.grad) < 1e-2

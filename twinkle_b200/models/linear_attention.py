@@ -10,7 +10,10 @@ per head is
 with decay α_t = exp(g_t) ∈ (0, 1] and write strength β_t ∈ (0, 1).  Two evaluators are provided: the plain recurrence
 (exact, O(T) sequential steps) and a chunk-parallel form (WY / UT transform inside chunks of ``chunk`` tokens, one
 sequential step per chunk) that is what training uses.  Both take packed sequences through ``cu_seqlens``: state and
-convolution history are reset at every boundary.  This layer runs on PyTorch ops (no hand-written kernel yet).
+convolution history are reset at every boundary.  On a GPU in bf16 the convolution (+SiLU) and the forward recurrence
+(with the q / k normalisation and the grouped-head repeat inside) are CUDA kernels (``ops/csrc/gdn.cu``: one warp per
+sequence × value head × 32 state columns, state in registers); their backward is autograd on the chunk-parallel
+evaluator below, which is also the CPU / fp32 path.
 """
 from __future__ import annotations
 
@@ -95,7 +98,38 @@ def gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, scale: Optional[float]
     return out
 
 
+def gated_delta_rule_varlen_torch(q, k, v, g, beta, cu_seqlens, scale: Optional[float] = None, chunk: int = 64, normalize: bool = True,
+                                  init_state=None, return_states: bool = False):
+    """The whole op on PyTorch: ``q, k [T, Hk, dk]`` are L2-normalised per head (``normalize``) and repeated to the ``Hv``
+    value heads, then every packed segment is evaluated chunk-parallel from ``init_state[i]`` (or an empty state)."""
+    rep = v.shape[1] // q.shape[1]
+    if normalize:
+        q, k = F.normalize(q.float(), dim=-1).to(q.dtype), F.normalize(k.float(), dim=-1).to(k.dtype)
+    if rep > 1:
+        q, k = q.repeat_interleave(rep, 1), k.repeat_interleave(rep, 1)
+    bounds = cu_seqlens.tolist()
+    segs = [(a, b) for a, b in zip(bounds[:-1], bounds[1:])]
+    res = []
+    for i, (a, b) in enumerate(segs):
+        st = init_state[i] if init_state is not None else None
+        if b > a:
+            res.append(gated_delta_rule_chunked(q[a:b], k[a:b], v[a:b], g[a:b], beta[a:b], scale, chunk=chunk, state=st))
+        else:   # an empty segment keeps its state
+            res.append((q.new_zeros(0, v.shape[1], v.shape[-1]),
+                        st.float() if st is not None else q.new_zeros(v.shape[1], q.shape[2], v.shape[-1], dtype=torch.float32)))
+    out = torch.cat([r[0] for r in res], 0) if res else q.new_zeros(0, v.shape[1], v.shape[-1])
+    if return_states:
+        return out, (torch.stack([r[1] for r in res]) if res else q.new_zeros(0, v.shape[1], q.shape[2], v.shape[-1], dtype=torch.float32))
+    return out
+
+
 def causal_conv1d_varlen(x: torch.Tensor, weight: torch.Tensor, cu_seqlens: torch.Tensor, activation: bool = True) -> torch.Tensor:
+    """Depth-wise causal convolution over packed tokens (kernel on a GPU in bf16, PyTorch otherwise)."""
+    from .. import ops
+    return ops.causal_conv1d_varlen(x, weight, cu_seqlens, activation)
+
+
+def causal_conv1d_varlen_torch(x: torch.Tensor, weight: torch.Tensor, cu_seqlens: torch.Tensor, activation: bool = True) -> torch.Tensor:
     """Depth-wise causal convolution over packed tokens: ``x [T, C]``, ``weight [C, W]``; no leakage across segments."""
     T, C = x.shape
     W = weight.shape[1]
@@ -149,21 +183,21 @@ class GatedDeltaNet(nn.Module):
         if ap is None:
             qkv = causal_conv1d_varlen(qkv, self.conv_weight, cu_seqlens)
         q, k, v = qkv[:, :kd].view(T, self.hk, self.dk), qkv[:, kd:2 * kd].view(T, self.hk, self.dk), qkv[:, 2 * kd:].view(T, self.hv, self.dv)
-        rep = self.hv // self.hk
         if ap is not None:
             # sequence → head exchange first (every rank then owns whole sequences for a slice of the heads), then the
             # convolution with this rank's slice of the depth-wise filters; the exchange is the same one attention uses
             q, k, v = ap.scatter_heads(q.contiguous(), k.contiguous(), v.contiguous())
             beta, g = ap.scatter_scalar_heads(beta), ap.scatter_scalar_heads(g)
             q, k, v = ap.conv_after_scatter(q, k, v, self.conv_weight, cu_seqlens, self.hk, self.hv, self.dk, self.dv)
-        q, k = F.normalize(q.float(), dim=-1).to(x.dtype), F.normalize(k.float(), dim=-1).to(x.dtype)
-        if rep > 1:
-            q, k = q.repeat_interleave(rep, 1), k.repeat_interleave(rep, 1)
+        from .. import ops
         if state_sink is not None:
-            o, states = gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, chunk=self.chunk, return_states=True)
+            o, states = ops.gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, chunk=self.chunk, return_states=True)
+            keep = (cu_seqlens[1:] > cu_seqlens[:-1]).tolist()
+            if not all(keep):   # the sink takes the non-empty segments only
+                states = states[torch.tensor(keep, device=states.device)]
             state_sink(torch.stack(tails) if tails else qkv.new_zeros(0, w1, qkv.shape[1]), states)
         else:
-            o = gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, chunk=self.chunk)
+            o = ops.gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, chunk=self.chunk)
         if ap is not None:
             o = ap.gather_heads(o.contiguous())
         # gated RMSNorm per head, gate z
@@ -187,14 +221,21 @@ class GatedDeltaNet(nn.Module):
         window = torch.cat([conv_state.to(qkv.dtype), qkv.unsqueeze(1)], 1)                    # [B, W, C]
         conv = F.silu((window * self.conv_weight.t().to(qkv.dtype).unsqueeze(0)).sum(1))       # depth-wise causal conv, last position
         q, k, v = conv[:, :kd].view(B, self.hk, self.dk), conv[:, kd:2 * kd].view(B, self.hk, self.dk), conv[:, 2 * kd:].view(B, self.hv, self.dv)
-        q, k = F.normalize(q.float(), dim=-1), F.normalize(k.float(), dim=-1)
-        rep = self.hv // self.hk
-        if rep > 1:
-            q, k = q.repeat_interleave(rep, 1), k.repeat_interleave(rep, 1)
-        S = state.float() * g.exp()[:, :, None, None]
-        kv = torch.einsum('bhk,bhkv->bhv', k, S)
-        S = S + torch.einsum('bhk,bhv->bhkv', k, (v.float() - kv) * beta[:, :, None])
-        o = torch.einsum('bhk,bhkv->bhv', q * self.dk ** -0.5, S)
+        from .. import ops
+        if ops.gdn_kernel_supported(q, v):
+            # every row is a one-token sequence that continues from its own state
+            cu = torch.arange(B + 1, dtype=torch.int32, device=x.device)
+            o, S = ops.gated_delta_rule_varlen(q, k, v, g, beta, cu, init_state=state, return_states=True)
+            o = o.float()
+        else:
+            q, k = F.normalize(q.float(), dim=-1), F.normalize(k.float(), dim=-1)
+            rep = self.hv // self.hk
+            if rep > 1:
+                q, k = q.repeat_interleave(rep, 1), k.repeat_interleave(rep, 1)
+            S = state.float() * g.exp()[:, :, None, None]
+            kv = torch.einsum('bhk,bhkv->bhv', k, S)
+            S = S + torch.einsum('bhk,bhv->bhkv', k, (v.float() - kv) * beta[:, :, None])
+            o = torch.einsum('bhk,bhkv->bhv', q * self.dk ** -0.5, S)
         o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + self.eps) * self.norm_weight.float()
         o = o * F.silu(z.float().view(B, self.hv, self.dv))
         return self.out_proj(o.to(x.dtype).reshape(B, vd)), window[:, 1:].contiguous(), S

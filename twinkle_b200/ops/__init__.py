@@ -395,6 +395,92 @@ def paged_attention_decode(q, k_cache, v_cache, block_tables, seq_lens, scale: O
     return ref.paged_attention_decode(q, k_cache, v_cache, block_tables, seq_lens, scale)
 
 
+# ------------------------------------------------------ gated delta net (linear attention)
+def _segment_starts(cu_seqlens: torch.Tensor, total: int) -> torch.Tensor:
+    """``[T]`` int32: for every packed token the index of the first token of its sequence."""
+    cu = cu_seqlens.to(torch.int64)
+    lens = cu[1:] - cu[:-1]
+    return torch.repeat_interleave(cu[:-1], lens, output_size=total).to(torch.int32)
+
+
+class _CausalConv1d(torch.autograd.Function):
+    """Forward: one kernel (depth-wise taps + SiLU, no leakage across packed sequences).  Backward: the gradient of the
+    same op formed by autograd on the PyTorch expression (the convolution is a small share of a layer's backward)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, cu_seqlens, activation):
+        ctx.save_for_backward(x, weight, cu_seqlens)
+        ctx.activation = activation
+        return ext().causal_conv1d_fwd(x, weight.to(x.dtype).contiguous(), _segment_starts(cu_seqlens, x.shape[0]), activation)
+
+    @staticmethod
+    def backward(ctx, gy):
+        from ..models.linear_attention import causal_conv1d_varlen_torch
+        x, weight, cu = ctx.saved_tensors
+        with torch.enable_grad():
+            xd, wd = x.detach().requires_grad_(True), weight.detach().requires_grad_(True)
+            y = causal_conv1d_varlen_torch(xd, wd, cu, ctx.activation)
+            gx, gw = torch.autograd.grad(y, (xd, wd), gy)
+        return gx, gw, None, None
+
+
+def causal_conv1d_varlen(x: torch.Tensor, weight: torch.Tensor, cu_seqlens: torch.Tensor, activation: bool = True) -> torch.Tensor:
+    """Depth-wise causal convolution (+ SiLU) over packed tokens: ``x [T, C]``, ``weight [C, W]``."""
+    from ..models.linear_attention import causal_conv1d_varlen_torch
+    if (_cuda(x) and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and 2 <= weight.shape[1] <= 4 and x.stride(1) == 1
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0):
+        return _CausalConv1d.apply(x, weight, cu_seqlens, activation)
+    return causal_conv1d_varlen_torch(x, weight, cu_seqlens, activation)
+
+
+def gdn_kernel_supported(q: torch.Tensor, v: torch.Tensor) -> bool:
+    return (_cuda(q) and q.dtype == torch.bfloat16 and v.dtype == torch.bfloat16 and q.shape[-1] in (64, 128)
+            and q.stride(2) == 1 and q.stride(1) == q.shape[2] and v.stride(2) == 1 and v.stride(1) == v.shape[2])
+
+
+class _GatedDeltaRule(torch.autograd.Function):
+    """Forward: the recurrent kernel (q / k L2 normalisation and the grouped-head repeat inside).  Backward: autograd
+    through the chunk-parallel PyTorch evaluator of the same function, re-run from the saved inputs."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, cu_seqlens, scale, chunk):
+        o, _ = ext().gdn_recurrent_fwd(q, k, v, g.float().contiguous(), beta.float().contiguous(), cu_seqlens.to(torch.int32).contiguous(),
+                                       None, scale, False)
+        ctx.save_for_backward(q, k, v, g, beta, cu_seqlens)
+        ctx.scale, ctx.chunk = scale, chunk
+        return o
+
+    @staticmethod
+    def backward(ctx, go):
+        from ..models.linear_attention import gated_delta_rule_varlen_torch
+        q, k, v, g, beta, cu = ctx.saved_tensors
+        with torch.enable_grad():
+            ins = [t.detach().requires_grad_(True) for t in (q, k, v, g, beta)]
+            o = gated_delta_rule_varlen_torch(*ins, cu, ctx.scale, chunk=ctx.chunk, normalize=True)
+            grads = torch.autograd.grad(o, ins, go)
+        return (*grads, None, None, None)
+
+
+def gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, scale: Optional[float] = None, chunk: int = 64, init_state=None,
+                            return_states: bool = False):
+    """Gated delta rule over packed sequences with **unnormalised** ``q, k [T, Hk, dk]`` (they are L2-normalised per head
+    inside), ``v [T, Hv, dv]`` (``Hv`` a multiple of ``Hk``), ``g`` (log decay) and ``beta [T, Hv]``.  Returns
+    ``o [T, Hv, dv]`` and, with ``return_states``, the final state per sequence ``[n, Hv, dk, dv]`` (fp32).
+    ``init_state`` continues from earlier tokens (decoding); it and ``return_states`` are inference-only."""
+    from ..models.linear_attention import gated_delta_rule_varlen_torch
+    scale = q.shape[-1] ** -0.5 if scale is None else scale
+    if gdn_kernel_supported(q, v) and gdn_kernel_supported(k, v):
+        if init_state is None and not return_states:
+            return _GatedDeltaRule.apply(q, k, v, g, beta, cu_seqlens, scale, chunk)
+        if not torch.is_grad_enabled() or not any(t.requires_grad for t in (q, k, v, g, beta)):
+            o, fin = ext().gdn_recurrent_fwd(q, k, v, g.float().contiguous(), beta.float().contiguous(),
+                                             cu_seqlens.to(torch.int32).contiguous(),
+                                             init_state.float().contiguous() if init_state is not None else None, scale, return_states)
+            return (o, fin) if return_states else o
+    return gated_delta_rule_varlen_torch(q, k, v, g, beta, cu_seqlens, scale, chunk=chunk, normalize=True, init_state=init_state,
+                                         return_states=return_states)
+
+
 # ------------------------------------------------------------- logprob / CE
 class _LogprobFromLogits(torch.autograd.Function):
 
@@ -543,13 +629,32 @@ class _SGMV(torch.autograd.Function):
         return gx, ga.to(a.dtype), gb.to(b.dtype), None, None, None, None, None
 
 
+_ROWMASKS: 'dict' = {}
+
+
 def _sgmv_rowmask(host_segments, R: int, device, dtype) -> torch.Tensor:
-    rows = []
-    col = torch.arange(R, device=device)
-    for (lo, hi, slot, rank, scale) in host_segments:
-        m = (col < rank).to(dtype) * (scale if slot >= 0 else 0.0)
-        rows.append(m.unsqueeze(0).expand(hi - lo, R))
-    return torch.cat(rows, 0) if rows else torch.zeros(0, R, device=device, dtype=dtype)
+    """``[T, R]``: the segment's scale in the first ``rank`` columns of its rows, zero elsewhere.  Every LoRA linear of
+    every layer asks for the same mask during one forward/backward (and its recompute), so the last few are kept: the
+    mask is built on the host and copied once instead of by a dozen small kernels per call."""
+    key = (tuple(host_segments), R, str(device), dtype)
+    hit = _ROWMASKS.get(key)
+    if hit is not None:
+        return hit
+    per_seg = torch.zeros(max(len(host_segments), 1), R, dtype=torch.float32)
+    lens = []
+    for i, (lo, hi, slot, rank, scale) in enumerate(host_segments):
+        if slot >= 0:
+            per_seg[i, :rank] = scale
+        lens.append(hi - lo)
+    if host_segments:
+        rep = torch.tensor(lens, dtype=torch.int64, device=device)
+        mask = per_seg[:len(host_segments)].to(device=device, dtype=dtype).repeat_interleave(rep, dim=0, output_size=sum(lens))
+    else:
+        mask = torch.zeros(0, R, device=device, dtype=dtype)
+    if len(_ROWMASKS) >= 16:
+        _ROWMASKS.pop(next(iter(_ROWMASKS)))
+    _ROWMASKS[key] = mask
+    return mask
 
 
 def sgmv(x, lora_a, lora_b, seg_starts, seg_slots, seg_ranks, seg_scales, host_segments=None):

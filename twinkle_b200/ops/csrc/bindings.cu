@@ -42,6 +42,9 @@ void peer_pull(const std::vector<int64_t>&, const std::vector<int64_t>&, const s
 void peer_reduce_scatter_acc(torch::Tensor, const std::vector<int64_t>&, int64_t, double, const c10::optional<torch::Tensor>&, int64_t);
 void ulysses_exchange(const torch::Tensor&, const std::vector<int64_t>&, int64_t, bool, int64_t);
 void peer_copy_cast(const torch::Tensor&, const std::vector<int64_t>&, int64_t);
+torch::Tensor causal_conv1d_fwd(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, bool);
+std::vector<torch::Tensor> gdn_recurrent_fwd(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&,
+                                             const torch::Tensor&, const torch::Tensor&, const c10::optional<torch::Tensor>&, double, bool);
 torch::Tensor paged_attn_decode(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, double);
 std::vector<torch::Tensor> sample_tokens(const torch::Tensor&, double, int64_t, double, const torch::Tensor&);
 std::vector<torch::Tensor> moe_router(const torch::Tensor&, int64_t, bool);
@@ -93,6 +96,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("peer_reduce_scatter_acc", &tk::peer_reduce_scatter_acc);
   m.def("ulysses_exchange", &tk::ulysses_exchange);
   m.def("peer_copy_cast", &tk::peer_copy_cast);
+  m.def("causal_conv1d_fwd", &tk::causal_conv1d_fwd);
+  m.def("gdn_recurrent_fwd", &tk::gdn_recurrent_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("g"), py::arg("beta"), py::arg("cu"),
+        py::arg("init_state") = py::none(), py::arg("scale") = 1.0, py::arg("want_state") = false);
   m.def("paged_attn_decode", &tk::paged_attn_decode);
   m.def("sample_tokens", &tk::sample_tokens);
   m.def("moe_router", &tk::moe_router);

@@ -149,6 +149,27 @@ def make(op: str, a) -> Tuple[Callable[[], None], float, float]:
         lg = torch.randn(a.batch, a.vocab, device=dev)
         seeds = torch.arange(a.batch, device=dev, dtype=torch.int64)
         return (lambda: ops.sample_tokens(lg, 0.8, 50, 0.95, seeds=seeds)), 0.0, 4.0 * a.batch * a.vocab
+    if op in ('gdn', 'gdn_torch'):
+        # Gated DeltaNet forward: 16 key / 32 value heads of 128, packed documents of --seq tokens
+        T, hk, hv, d = a.tokens, 16, 32, 128
+        n_seq = max(T // a.seq, 1)
+        cu = torch.arange(0, n_seq + 1, device=dev, dtype=torch.int32) * a.seq
+        q, k = torch.randn(T, hk, d, device=dev, dtype=bf), torch.randn(T, hk, d, device=dev, dtype=bf)
+        v = torch.randn(T, hv, d, device=dev, dtype=bf)
+        g, beta = -torch.rand(T, hv, device=dev) * 0.1, torch.rand(T, hv, device=dev)
+        byts = 2.0 * T * d * (2 * hk + 2 * hv) + 8.0 * T * hv
+        flops = 2.0 * T * hv * d * d * 3            # S·k, S·q and the rank-1 update
+        if op == 'gdn':
+            def f():
+                with torch.no_grad():
+                    ops.gated_delta_rule_varlen(q, k, v, g, beta, cu)
+        else:
+            from twinkle_b200.models.linear_attention import gated_delta_rule_varlen_torch
+
+            def f():
+                with torch.no_grad():
+                    gated_delta_rule_varlen_torch(q, k, v, g, beta, cu)
+        return f, flops, byts
     if op == 'router':
         lg = torch.randn(a.tokens, 128, device=dev, dtype=bf)
 
