@@ -125,7 +125,8 @@ class ModelApp(TaskQueueMixin):
         a['last_used'] = time.time()
         return a['adapter']
 
-    def create_adapter(self, token: str, session_id: Optional[str], lora_config: Optional[Dict[str, Any]], model_id: Optional[str] = None) -> str:
+    def create_adapter(self, token: str, session_id: Optional[str], lora_config: Optional[Dict[str, Any]], model_id: Optional[str] = None,
+                       save_dir: Optional[str] = None, user_metadata: Optional[Dict[str, Any]] = None) -> str:
         model_id = model_id or uuid.uuid4().hex
         if model_id in self.adapters:  # a client-chosen id must not take over another tenant's (or its own live) entry
             raise HTTPException(409, f'model {model_id!r} already exists on this replica')
@@ -146,7 +147,8 @@ class ModelApp(TaskQueueMixin):
         self.adapters[model_id] = {'adapter': adapter, 'token': token, 'session_id': session_id, 'created': time.time(), 'last_used': time.time(),
                                    'lora_config': cfg}
         self.state.register_replica(self.replica_id, self.args.model_id, self.args.max_loras, len(self.adapters))
-        self.checkpoints.create_run(token, model_id, self.args.model_id, is_lora=True, lora_rank=cfg['r'])
+        self.checkpoints.create_run(token, model_id, self.args.model_id, lora_config={**cfg, 'rank': cfg['r']}, is_lora=True,
+                                    save_dir=save_dir, user_metadata=user_metadata)
         return model_id
 
     def unload(self, model_id: str) -> None:
@@ -189,7 +191,7 @@ class ModelApp(TaskQueueMixin):
                 raise HTTPException(409, f'model {mid!r} already exists on this replica')
 
             def work():
-                self.create_adapter(token, b.get('session_id'), b.get('lora_config'), mid)
+                self.create_adapter(token, b.get('session_id'), b.get('lora_config'), mid, b.get('save_dir'), b.get('user_metadata'))
                 return {'model_id': mid, 'type': 'create_model'}
 
             return self.schedule_task(work, token=token, model_id=mid, request_id=request.state.request_id)
@@ -282,7 +284,8 @@ class ModelApp(TaskQueueMixin):
             b = await body_of(request)
             token = request.state.token
             mid = await self.schedule_task_and_wait(lambda: self.create_adapter(token, b.get('session_id'), b.get('config') or b.get('lora_config'),
-                                                                               b.get('adapter_name')), token=token)
+                                                                               b.get('adapter_name'), b.get('save_dir'), b.get('user_metadata')),
+                                                    token=token)
             return {'status': 'ok', 'adapter_name': mid}
 
         generic = ['forward', 'forward_only', 'calculate_loss', 'backward', 'forward_backward', 'clip_grad_norm', 'step', 'zero_grad', 'lr_step',

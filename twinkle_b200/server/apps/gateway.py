@@ -205,9 +205,8 @@ class GatewayApp:
             return await _call(self.router.sampler_for(base).app, '/tinker/asample', request, b)
 
         # ---------------------------------------------- runs / checkpoints
-        async def list_runs(request: Request):
-            runs = self.checkpoints.list_runs(request.state.token)
-            return {'training_runs': runs, 'cursor': {'offset': 0, 'limit': len(runs), 'total_count': len(runs)}}
+        async def list_runs(request: Request, limit: int = 20, offset: int = 0):
+            return self.checkpoints.runs.list_runs(request.state.token, limit, offset)
 
         async def get_run(run_id: str, request: Request):
             r = self.checkpoints.get_run(request.state.token, run_id)
