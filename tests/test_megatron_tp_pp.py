@@ -202,13 +202,14 @@ def _moe_feats():
     return out
 
 
-def _ep_worker(rank, world, tmp, tp, pp, ep, steps):
+def _ep_worker(rank, world, tmp, tp, pp, ep, steps, etp=1, sp=None):
     from twinkle_b200.model.megatron import MegatronModel
     from twinkle_b200.models import preset
     from twinkle_b200.utils.device_mesh import DeviceMesh
     cfg = preset('tiny-moe', router_aux_loss_coef=0.0, num_hidden_layers=2 * pp)
     dp = world // (tp * pp)
-    mesh = DeviceMesh.from_sizes(tp_size=tp, pp_size=pp, dp_size=dp, ep_size=ep, sequence_parallel=tp > 1)
+    mesh = DeviceMesh.from_sizes(tp_size=tp, pp_size=pp, dp_size=dp, ep_size=ep, etp_size=etp,
+                                 sequence_parallel=(tp > 1) if sp is None else sp)
     m = MegatronModel(config=cfg, device_mesh=mesh, seed=0)
     m.set_optimizer('AdamW', lr=1e-3)
     feats = _moe_feats()
@@ -229,6 +230,8 @@ def _ep_worker(rank, world, tmp, tp, pp, ep, steps):
     m.load('moe', tmp)
     same = all(torch.equal(before[k], v) for k, v in m.get_state_dict().items())
     n_experts_local = m.chunks[0].layers[0].mlp.experts.gate_up_proj.shape[0]
+    if etp > 1:
+        return curve, same, tuple(m.chunks[0].layers[0].mlp.experts.gate_up_proj.shape), sorted(before)
     return curve, same, n_experts_local, sorted(before)
 
 
@@ -258,3 +261,73 @@ def test_expert_parallel_axis_matches_single(tmp_path, tp, pp, ep, world):
     for k in keys:
         if k != 'lm_head.weight':
             assert k in loader, k
+
+
+@pytest.mark.parametrize('tp,pp,ep,world,sp', [(2, 1, 1, 2, True), (2, 1, 1, 2, False), (2, 1, 2, 4, True)])
+def test_expert_tensor_parallel_matches_single(tmp_path, tp, pp, ep, world, sp):
+    """Every expert's intermediate dimension split over the tensor-parallel group (reference
+    ``megatron/strategy/megatron.py:90-107``: ``expert_tensor_parallel_size``), with and without sequence-parallel
+    activations and together with expert parallelism: loss curve and gradient norm of one process, shard shapes, and
+    a bitwise round trip through the HF checkpoint (expert slices gathered over both groups)."""
+    from twinkle_b200.model import TransformersModel
+    from twinkle_b200.models import preset
+    from twinkle_b200.utils.device_mesh import DeviceMesh
+    cfg = preset('tiny-moe', router_aux_loss_coef=0.0, num_hidden_layers=2 * pp)
+    one = TransformersModel(config=cfg, device_mesh=DeviceMesh.from_sizes(dp_size=1), seed=0)
+    one.set_optimizer('AdamW', lr=1e-3)
+    single = []
+    for _ in range(3):
+        o = one.forward_backward(inputs=_moe_feats(), micro_batch_size=1)
+        n = one.clip_grad_and_step(max_grad_norm=1.0)
+        single.append((o['loss'], n))
+    want = (cfg.num_experts // ep, 2 * cfg.moe_intermediate_size // tp, cfg.hidden_size)
+    for curve, same, shape, saved in run_ranks(_ep_worker, world, str(tmp_path), tp, pp, ep, 3, tp, sp):
+        assert same and shape == want, (shape, want)
+        for (a, na), (b, nb) in zip(single, curve):
+            assert abs(a - b) < 5e-4 and abs(na - nb) < 5e-3 * max(na, 1.0), (single, curve)
+    from twinkle_b200.utils.safetensors_io import SafetensorLazyLoader
+    loader = SafetensorLazyLoader(os.path.join(str(tmp_path), 'moe'))
+    ref = one.get_state_dict()
+    assert loader.get('model.layers.0.mlp.experts.3.down_proj.weight').shape == ref['model.layers.0.mlp.experts.3.down_proj.weight'].shape
+
+
+def _aux_worker(rank, world, tp, pp, steps):
+    from twinkle_b200.model.megatron import MegatronModel
+    from twinkle_b200.models import preset
+    from twinkle_b200.utils.device_mesh import DeviceMesh
+    cfg = preset('tiny-moe', router_aux_loss_coef=0.05, num_hidden_layers=2 * pp)
+    mesh = DeviceMesh.from_sizes(tp_size=tp, pp_size=pp, dp_size=world // (tp * pp), sequence_parallel=tp > 1)
+    m = MegatronModel(config=cfg, device_mesh=mesh, seed=0)
+    m.set_optimizer('AdamW', lr=1e-3)
+    curve = []
+    for _ in range(steps):
+        o = m.forward_backward(inputs=_moe_feats(), micro_batch_size=2)
+        curve.append((o['loss'], m.clip_grad_and_step(max_grad_norm=1.0)))
+    return curve
+
+
+@pytest.mark.parametrize('tp,pp', [(1, 2), (2, 1)])
+def test_router_load_balance_loss_on_the_pipeline_backend(tp, pp):
+    """The router's auxiliary loss of every pipeline stage's own layers enters that stage's backward and the reported
+    loss.  Without tensor parallelism the numbers are those of one process; with sequence-parallel activations every
+    rank balances its own token slice, which changes the term slightly but must still train."""
+    from twinkle_b200.model import TransformersModel
+    from twinkle_b200.models import preset
+    from twinkle_b200.utils.device_mesh import DeviceMesh
+    single = {}
+    for coef in (0.05, 0.0):
+        cfg = preset('tiny-moe', router_aux_loss_coef=coef, num_hidden_layers=2 * pp)
+        one = TransformersModel(config=cfg, device_mesh=DeviceMesh.from_sizes(dp_size=1), seed=0)
+        one.set_optimizer('AdamW', lr=1e-3)
+        single[coef] = []
+        for _ in range(3):
+            o = one.forward_backward(inputs=_moe_feats(), micro_batch_size=2)
+            single[coef].append((o['loss'], one.clip_grad_and_step(max_grad_norm=1.0)))
+    assert abs(single[0.05][0][1] - single[0.0][0][1]) > 1e-3      # the term is there at all: it changes the gradient
+    for curve in run_ranks(_aux_worker, 2, tp, pp, 3):
+        for (a, na), (b, nb) in zip(single[0.05], curve):
+            if tp == 1:
+                assert abs(a - b) < 5e-4 and abs(na - nb) < 5e-3 * max(na, 1.0), (single[0.05], curve)
+            else:
+                assert abs(a - b) < 2e-2 and abs(na - nb) < 5e-2 * max(na, 1.0), (single[0.05], curve)
+        assert curve[-1][0] < curve[0][0]

@@ -58,6 +58,19 @@ def split_layers(num_layers: int, pp: int, vpp: int) -> List[List[Tuple[int, int
 
 
 @remote_class()
+class _AttachAux(torch.autograd.Function):
+    """Passes a pipeline chunk's activations through and gives ``aux`` (a scalar loss term of the chunk's own layers) a
+    unit gradient when the activations' gradient arrives, so the term needs no pass of its own through the schedule."""
+
+    @staticmethod
+    def forward(ctx, h, aux):
+        return h.view_as(h)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, (g if g.dim() == 0 else torch.ones((), dtype=g.dtype, device=g.device))
+
+
 class MegatronModel(TwinkleModel):
 
     def __init__(self, model_id: Optional[str] = None, config=None, device_mesh: DeviceMesh = None, mixed_precision: str = 'bf16',
@@ -107,6 +120,14 @@ class MegatronModel(TwinkleModel):
         self.layer_plan = split_layers(cfg.num_hidden_layers, self.pp_size, self.vpp)
         self.chunks: List[DecoderModel] = []
         fused_tp = make_fused_tp(self.tp_comm, self.device, bool(mesh.sequence_parallel), comm_backend) if self.tp_size > 1 else None
+        # expert tensor parallelism: 1 (experts whole on a rank, the default here) or the tensor-parallel degree
+        self.etp_size = int(mesh.etp_size or 1) if (cfg.is_moe and self.tp_size > 1) else 1
+        if self.etp_size not in (1, self.tp_size):
+            raise ValueError(f'etp_size={self.etp_size}: experts are either whole (1) or split over the whole tensor-parallel group ({self.tp_size})')
+        if self.etp_size > 1:
+            if cfg.moe_intermediate_size % self.tp_size:
+                raise ValueError('moe_intermediate_size must divide over the tensor-parallel group')
+            cfg.expert_tensor_parallel = True   # read by the sharding rules (models/bridge.py::tp_rule)
         load_dir = model_id if model_id and os.path.isdir(str(model_id)) else None
         for c, (lo, hi) in enumerate(self.layer_plan[self.pp_rank]):
             first = self.pp_rank == 0 and c == 0
@@ -122,6 +143,7 @@ class MegatronModel(TwinkleModel):
                 apply_context_parallel(m, mesh)  # zig-zag shards, keys / values gathered per layer (``parallel/context.py``)
             self.chunks.append(m)
         self.sequence_parallel = bool(mesh.sequence_parallel and self.tp_size > 1)
+        self._n_moe_layers = max(1, cfg.num_hidden_layers if cfg.is_moe else 1)
         self.ep_comm, self.ep_rank, self.ep_size = None, 0, 1
         if (mesh.ep_size or 1) > 1 and cfg.is_moe:
             self._apply_expert_parallel(mesh, comm_backend)
@@ -141,7 +163,9 @@ class MegatronModel(TwinkleModel):
         tensor parallelism is not built — experts are whole on a rank).  A rank's expert tensors are shared with every rank
         that holds the same experts of the same layers: the other data-parallel blocks, the context-parallel peers and,
         under sequence parallelism, the tensor-parallel peers (they route different tokens); gradients are summed over
-        exactly that set."""
+        exactly that set.  With expert tensor parallelism the tensor-parallel peers hold different slices of the same
+        experts instead: they are not in that set, and every rank of a tensor-parallel group sends the group's whole token
+        set to its own expert-parallel line."""
         from ..parallel.expert import ExpertParallel, shard_experts
         ep = int(mesh.ep_size)
         if self.tp_size > 1 and not self.sequence_parallel:
@@ -171,12 +195,15 @@ class MegatronModel(TwinkleModel):
                     ep_group, my_pos = g, block.index(me)
         rep_group = None
         pp_i = names.index('pp') if 'pp' in names else None
+        tp_i = names.index('tp') if ('tp' in names and self.etp_size > 1) else None
         for stage in sorted({coords[r][pp_i] if pp_i is not None else 0 for r in coords}):
-            for j in range(ep):
-                members = sorted(r for r in coords if pos_of[r] == j and (coords[r][pp_i] if pp_i is not None else 0) == stage)
-                g = dist.new_group(ranks=members)
-                if me in members:
-                    rep_group = g if len(members) > 1 else None
+            for slice_ in sorted({coords[r][tp_i] if tp_i is not None else 0 for r in coords}):
+                for j in range(ep):
+                    members = sorted(r for r in coords if pos_of[r] == j and (coords[r][pp_i] if pp_i is not None else 0) == stage
+                                     and (coords[r][tp_i] if tp_i is not None else 0) == slice_)
+                    g = dist.new_group(ranks=members)
+                    if me in members:
+                        rep_group = g if len(members) > 1 else None
         self.ep_comm = Communicator(ep_group, self.device)
         strat = None
         if self.device.type == 'cuda' and backend in ('auto', 'symm'):
@@ -254,7 +281,9 @@ class MegatronModel(TwinkleModel):
             mbs.append(proc._pack(g, pad_multiple=mult, split=self.cp_size > 1))
         return feats, mbs
 
-    def _forward_chunk(self, mbs, og, loss_kwargs, results):
+    def _forward_chunk(self, mbs, og, loss_kwargs, results, aux_report: Optional[List[float]] = None):
+        aux_report = aux_report if aux_report is not None else []
+
         def run(chunk: int, micro: int, x: Optional[torch.Tensor]) -> torch.Tensor:
             m = self.chunks[chunk]
             mb = mbs[micro].to(self.device)
@@ -273,8 +302,22 @@ class MegatronModel(TwinkleModel):
             else:
                 for layer in m.layers:
                     h = layer(h, cos, sin, batch)
+            # router load-balance loss of this chunk's layers: per token of the micro-batch it weighs
+            # coef / (number of mixture layers) like on the sharded backend; its gradient enters with the chunk's backward
+            aux_term = None
+            if self.config.is_moe and self.config.router_aux_loss_coef > 0 and torch.is_grad_enabled():
+                auxes = [l.mlp.last_aux for l in m.layers if getattr(l, 'is_moe', False) and l.mlp.last_aux is not None]
+                for l in m.layers:
+                    if getattr(l, 'is_moe', False):
+                        l.mlp.last_aux = None
+                if auxes:
+                    nt_mb = float((mb.labels != -100).sum()) or 1.0
+                    # sequence-parallel peers each hold 1/tp of these tokens; context-parallel peers count their own labels
+                    share = self.tp_size if self.sequence_parallel else 1
+                    aux_term = torch.stack(auxes).sum() * (self.config.router_aux_loss_coef * nt_mb / (self._n_moe_layers * share))
+                    aux_report.append(float(aux_term.detach()))
             if not m.has_head:
-                return h
+                return h if aux_term is None else _AttachAux.apply(h, aux_term)
             h = m.norm(h)
             logps, _ = m.token_logprobs(h, mb.labels)
             labels = mb.labels
@@ -289,7 +332,8 @@ class MegatronModel(TwinkleModel):
             nt = float(res.get('num_tokens', 0) or 0) if isinstance(res, dict) else 0.0
             nt /= self.cp_size                      # every context-parallel peer reports the same rows
             results.append({'logps': out['logps'].detach(), 'labels': out['labels'], 'num_tokens': nt, 'loss': float(loss.detach()) / self.cp_size})
-            return loss
+            # the reported loss stays the language-model loss (as on the sharded backend); the term only adds its gradient
+            return loss if aux_term is None else _AttachAux.apply(loss, aux_term)
 
         return run
 
@@ -313,7 +357,8 @@ class MegatronModel(TwinkleModel):
             return TransformersModel._slice_kwargs(kwargs, micro * per, min((micro + 1) * per, n), n)
 
         results: List[Dict[str, Any]] = []
-        self.runner.run(len(mbs), self._forward_chunk(mbs, og, loss_kwargs, results), self._hidden_shape(mbs))
+        aux_report: List[float] = []
+        self.runner.run(len(mbs), self._forward_chunk(mbs, og, loss_kwargs, results, aux_report), self._hidden_shape(mbs))
         # loss / token count live on the last stage: share them with the whole pipeline group
         stats = torch.zeros(3, dtype=torch.float64, device=self.device if self.device.type == 'cuda' else 'cpu')
         if results:
@@ -383,8 +428,12 @@ class MegatronModel(TwinkleModel):
                 continue
             if self.dp_comm.world_size > 1:
                 self.dp_comm.all_reduce(p.grad)
-            if self.sequence_parallel and tp_rule(n, self.config) is None:
-                self.tp_comm.all_reduce(p.grad)  # replicated tensors saw different tokens on each tp rank
+            if self.tp_size > 1 and tp_rule(n, self.config) is None and (
+                    self.sequence_parallel or n.endswith(('self_attn.q_norm.weight', 'self_attn.k_norm.weight'))):
+                # replicated tensors whose gradient is a partial sum on each tp rank: under sequence parallelism all of
+                # them (every rank saw different tokens); always the per-head q / k norm weights (every rank applied them
+                # to its own heads)
+                self.tp_comm.all_reduce(p.grad)
         denom = self.dp_comm.all_reduce_scalar(og.train_status.num_tokens, 'sum') or 1.0
         # 2. global norm: tp-sharded tensors are disjoint (sum over tp), replicated ones counted once; sum over pp
         sq = torch.zeros((), dtype=torch.float32, device=self.device)
@@ -566,14 +615,15 @@ class MegatronModel(TwinkleModel):
 
     # ---------------------------------------------------------- save / load
     def _gather_full(self, name: str, p: torch.Tensor) -> torch.Tensor:
+        t = p.detach()
         if getattr(p, '_ep_local', False) and self.ep_comm is not None:  # all experts, in expert order
-            parts = [torch.empty_like(p) for _ in range(self.ep_comm.world_size)]
-            dist.all_gather(parts, p.detach().contiguous(), group=self.ep_comm.group)
-            return torch.cat(parts, 0)
+            parts = [torch.empty_like(t) for _ in range(self.ep_comm.world_size)]
+            dist.all_gather(parts, t.contiguous(), group=self.ep_comm.group)
+            t = torch.cat(parts, 0)
         if self.tp_size == 1 or tp_rule(name, self.config) is None:
-            return p.detach()
-        parts = [torch.empty_like(p) for _ in range(self.tp_size)]
-        dist.all_gather(parts, p.detach().contiguous(), group=self.tp_comm.group)
+            return t
+        parts = [torch.empty_like(t) for _ in range(self.tp_size)]
+        dist.all_gather(parts, t.contiguous(), group=self.tp_comm.group)
         return tp_unshard(name, parts, self.config)
 
     @remote_function(collect='first')
@@ -633,9 +683,8 @@ class MegatronModel(TwinkleModel):
                 full = loader.get('model.embed_tokens.weight') if src_head else hf_to_internal(n, self.config, loader.get)
                 if getattr(p, '_ep_local', False) and self.ep_comm is not None:
                     el = p.shape[0]
-                    p.copy_(full[self.ep_rank * el:(self.ep_rank + 1) * el].to(p.device, p.dtype))
-                else:
-                    p.copy_(tp_shard(n, full, self.config, self.tp_rank, self.tp_size).to(p.device, p.dtype))
+                    full = full[self.ep_rank * el:(self.ep_rank + 1) * el]
+                p.copy_(tp_shard(n, full, self.config, self.tp_rank, self.tp_size).to(p.device, p.dtype))
                 st = self._state.get(n)
                 if st is not None:
                     lo, hi = (0, p.numel()) if getattr(p, '_ep_local', False) else self._state_range(p.numel())

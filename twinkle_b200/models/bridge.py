@@ -201,6 +201,12 @@ def tp_rule(name: str, cfg: DecoderConfig):
         return ('col', [half, half])
     if rest in ('self_attn.o_proj.weight', 'mlp.down_proj.weight'):
         return ('row', None)
+    if getattr(cfg, 'expert_tensor_parallel', False):
+        # expert tensor parallelism: every expert's intermediate dimension is split over the group
+        if rest == 'mlp.experts.gate_up_proj':       # [E, 2I, H]: gate rows and up rows sharded separately
+            return ('ecol', [cfg.moe_intermediate_size, cfg.moe_intermediate_size])
+        if rest == 'mlp.experts.down_proj':          # [E, H, I]
+            return ('erow', None)
     return None
 
 
@@ -214,6 +220,10 @@ def tp_shard(name: str, full: torch.Tensor, cfg: DecoderConfig, tp_rank: int, tp
         return torch.cat([p.chunk(tp_size, dim=0)[tp_rank] for p in pieces], 0)
     if kind == 'row':
         return full.chunk(tp_size, dim=1)[tp_rank]
+    if kind == 'ecol':
+        return torch.cat([p.chunk(tp_size, dim=1)[tp_rank] for p in full.split(parts, dim=1)], 1)
+    if kind == 'erow':
+        return full.chunk(tp_size, dim=2)[tp_rank]
     return full.chunk(tp_size, dim=0)[tp_rank]  # vocab
 
 
@@ -229,6 +239,12 @@ def tp_unshard(name: str, shards: List[torch.Tensor], cfg: DecoderConfig) -> tor
         return torch.cat([torch.cat([split[r][j] for r in range(tp)], 0) for j in range(len(parts))], 0)
     if kind == 'row':
         return torch.cat(shards, 1)
+    if kind == 'ecol':
+        per = [p // tp for p in parts]
+        split = [s.split(per, dim=1) for s in shards]
+        return torch.cat([torch.cat([split[r][j] for r in range(tp)], 1) for j in range(len(parts))], 1)
+    if kind == 'erow':
+        return torch.cat(shards, 2)
     return torch.cat(shards, 0)
 
 

@@ -186,6 +186,7 @@ class MoEBlock(nn.Module):
         else:
             self.shared_expert = self.shared_expert_gate = None
         self.moe_parallel = None  # expert-parallel strategy or None
+        self.etp = None           # tensor-parallel context when every expert is split over the tensor-parallel group
         self.last_routed: Optional[torch.Tensor] = None
         self.last_aux: Optional[torch.Tensor] = None
         self.record_routing = False
@@ -202,9 +203,33 @@ class MoEBlock(nn.Module):
             self.last_routed = idx.detach()
         if self.cfg.router_aux_loss_coef > 0 and torch.is_grad_enabled():
             self.last_aux = ops.ref.moe_aux_loss(probs, idx, E)
+        if self.etp is not None:
+            return self._with_shared(x, self._forward_expert_tp(x, w, idx))
         mp = self.moe_parallel
         if mp is not None:
             return self._with_shared(x, mp.forward(self, x, w, idx))
+        return self._with_shared(x, self._routed_local(x, w, idx))
+
+    def _forward_expert_tp(self, x, w, idx):
+        """Expert tensor parallelism (reference ``megatron/strategy/megatron.py:90-107``: ``expert_tensor_parallel_size``):
+        every rank of the group holds ``1/tp`` of each expert's intermediate dimension, so it needs every token of the
+        group and produces a partial sum of every token's output.  Routing stays where the tokens are (the router's
+        gradient is then summed like that of any other replicated tensor); the routing *results* travel with the tokens."""
+        tp = self.etp
+        xf, wf = tp.before_column(x), tp.before_column(w)
+        idxf = tp.comm.all_gather_tensor(idx.contiguous()) if tp.sp else idx
+        mp = self.moe_parallel
+        if mp is not None:
+            self._hist = None       # the histogram was taken over this rank's tokens only
+            part = mp.forward(self, xf, wf, idxf)
+        else:
+            self._hist = None
+            part = self._routed_local(xf, wf, idxf)
+        return tp.after_row(part)
+
+    def _routed_local(self, x, w, idx):
+        T, H = x.shape
+        k, E = self.cfg.num_experts_per_tok, self.cfg.num_experts
         # local: expert-sorted layout whose segments start on 128-row boundaries (grouped GEMM tiles and the
         # per-expert wgrad reduction ranges then never straddle two experts); padding rows are zero.  Dispatch and
         # combine are gathers through index maps built on the device — no host read anywhere in the block.
@@ -213,7 +238,7 @@ class MoEBlock(nn.Module):
         row_of, src_tok, slot_of_row = ops.moe_index_maps(order, rows, bound, k)
         xs = ops.moe_dispatch(x, src_tok, row_of)
         y = self.experts(xs, offsets)
-        return self._with_shared(x, ops.moe_combine(y, w, row_of, src_tok, slot_of_row))
+        return ops.moe_combine(y, w, row_of, src_tok, slot_of_row)
 
     def _with_shared(self, x: torch.Tensor, routed: torch.Tensor) -> torch.Tensor:
         if self.shared_expert is None:

@@ -240,6 +240,8 @@ def apply_tensor_parallel(model, cfg, comm: Communicator, sequence_parallel: boo
         pairs = [(at.qkv_proj, 'col'), (at.o_proj, 'row')]
         if not layer.is_moe:
             pairs += [(layer.mlp.gate_up_proj, 'col'), (layer.mlp.down_proj, 'row')]
+        elif getattr(cfg, 'expert_tensor_parallel', False):
+            layer.mlp.etp = tp      # the expert tensors were cut above (bridge.tp_rule: 'ecol' / 'erow')
         for lin, mode in pairs:
             lin.tp, lin.tp_mode = tp, mode
             # the module's declared sizes follow its shard, so that an adapter pool created afterwards has the local
