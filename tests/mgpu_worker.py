@@ -262,8 +262,11 @@ def main():
         dist.destroy_process_group()
         return
 
-    # ---- 1. peer all-gather / reduce-scatter kernels against NCCL
+    # ---- 1. peer all-gather / reduce-scatter kernels against NCCL (guard zones around every symmetric tensor: a kernel
+    # that writes past its destination on a peer shows up in check_canaries)
+    os.environ['TWINKLE_SYMM_CANARIES'] = '1'
     sc = SymmCommunicator(None, dev)
+    os.environ.pop('TWINKLE_SYMM_CANARIES')
     n = 1 << 20
     shard = sc.alloc(n, torch.bfloat16)
     shard.copy_(torch.randn(n, device=dev).bfloat16() + rank)
@@ -309,6 +312,12 @@ def main():
     torch.cuda.synchronize()
     sc.legacy_kernels = False
     report('ulysses_push_legacy', bool(torch.equal(a, b2)))
+    dist.barrier()
+    try:
+        sc.check_canaries()
+        report('symmetric_guard_zones_intact', len(sc._guards) >= 2)
+    except RuntimeError as e:
+        report('symmetric_guard_zones_intact', False, detail=str(e))
     report('error_word', E.read_and_clear_error() == 0)
     if stop_after_kernels:
         dist.barrier()
@@ -357,6 +366,11 @@ def main():
         c = curve(mesh, backend, feats)
         diff = max(abs(a - b) for a, b in zip(single, c))
         report(f'ulysses{world}_{backend}_matches_single', diff < 3e-2, single=single, multi=c)
+    # context parallelism (zig-zag shards, keys / values gathered per layer) on the GPUs against the same single-GPU curve
+    mesh = DeviceMesh.from_sizes(dp_size=1, cp_size=world)
+    c = curve(mesh, 'nccl', feats)
+    diff = max(abs(a - b) for a, b in zip(single, c))
+    report(f'context_parallel{world}_matches_single', diff < 3e-2, single=single, multi=c)
     report('error_word_end', E.read_and_clear_error() == 0)
     dist.barrier()
     dist.destroy_process_group()

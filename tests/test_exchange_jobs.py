@@ -56,3 +56,30 @@ def test_bounds_check_rejects_bad_jobs():
         check_jobs([(r, s_off + 8, s_stride, d_off, d_stride, chunk, n)] + jobs[1:], src_bytes, dst_bytes)                # misaligned
     with pytest.raises(ValueError):
         exchange_jobs((8, 6, 16), 2, 4, 0, True)                                                                          # heads do not divide
+
+
+def test_guard_zones_around_symmetric_tensors_catch_a_stray_write():
+    """Placement with guard zones keeps 256-byte alignment and disjoint zones; a byte written just past a tensor (what a
+    peer kernel with a wrong extent would do) is reported next to that tensor."""
+    import torch
+    from twinkle_b200.parallel.symm import GUARD_PATTERN, damaged_guards, fill_guards, place_guarded
+    raw = torch.zeros(1 << 16, dtype=torch.uint8)
+    used, records = 0, []
+    for i, nbytes in enumerate((1000, 4096, 24)):
+        start, used = place_guarded(used, nbytes, 512)
+        assert start % 256 == 0 and used % 256 == 0 and start >= 512
+        fill_guards(raw, start, nbytes, 512)
+        records.append((f't{i}', start, nbytes, 512))
+    for (_, s0, n0, g0), (_, s1, _, g1) in zip(records, records[1:]):
+        assert s0 + n0 + g0 <= s1 - g1                       # zones of neighbours do not overlap
+    assert place_guarded(0, 100, 0) == (0, 256)              # without guards: plain aligned bump allocation
+    assert damaged_guards(raw, records) == []
+    _, s1, n1, _ = records[1]
+    raw[s1:s1 + n1].fill_(7)                                 # writing the tensor itself is fine
+    assert damaged_guards(raw, records) == []
+    raw[s1 + n1] = 0                                         # one byte past its end
+    bad = damaged_guards(raw, records)
+    assert len(bad) == 1 and bad[0].startswith('t1') and 'above' in bad[0]
+    raw[s1 + n1] = GUARD_PATTERN
+    raw[records[2][1] - 1] = 1                               # one byte before the next tensor
+    assert damaged_guards(raw, records)[0].startswith('t2 (below')

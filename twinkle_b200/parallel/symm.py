@@ -100,12 +100,40 @@ class SymmBuffer:
         self._comm_rank = comm.rank
         self.used = 0
 
-    def carve(self, nbytes: int) -> Optional[int]:
-        start = (self.used + 255) // 256 * 256
-        if start + nbytes > self.nbytes:
+    def carve(self, nbytes: int, guard: int = 0) -> Optional[int]:
+        start, end = place_guarded(self.used, nbytes, guard)
+        if end > self.nbytes and start + nbytes + guard > self.nbytes:
             return None
-        self.used = start + nbytes
+        self.used = min(end, self.nbytes)
         return start
+
+
+GUARD_BYTES = 4096
+GUARD_PATTERN = 0xA5
+
+
+def place_guarded(used: int, nbytes: int, guard: int) -> Tuple[int, int]:
+    """Where a tensor of ``nbytes`` goes in a chunk whose first free byte is ``used`` when ``guard`` bytes are kept on
+    both sides of it: ``(start of the tensor, first free byte afterwards)``, both 256-byte aligned."""
+    start = (used + guard + 255) // 256 * 256
+    return start, (start + nbytes + guard + 255) // 256 * 256
+
+
+def fill_guards(raw: torch.Tensor, start: int, nbytes: int, guard: int) -> None:
+    raw[start - guard:start].fill_(GUARD_PATTERN)
+    raw[start + nbytes:start + nbytes + guard].fill_(GUARD_PATTERN)
+
+
+def damaged_guards(raw: torch.Tensor, records) -> List[str]:
+    """Names of the tensors whose guard zone (before or after) no longer holds the pattern: something wrote outside a
+    neighbouring tensor.  ``records`` = ``[(name, start, nbytes, guard)]``."""
+    bad = []
+    for name, start, nbytes, guard in records:
+        lo_ok = bool((raw[start - guard:start] == GUARD_PATTERN).all())
+        hi_ok = bool((raw[start + nbytes:start + nbytes + guard] == GUARD_PATTERN).all())
+        if not (lo_ok and hi_ok):
+            bad.append(f'{name} ({"below" if not lo_ok else ""}{"+" if not lo_ok and not hi_ok else ""}{"above" if not hi_ok else ""})')
+    return bad
 
 
 class SymmCommunicator(Communicator):
@@ -132,20 +160,41 @@ class SymmCommunicator(Communicator):
         # TWINKLE_SYMM_LEGACY=1 keeps the first-generation kernels (push exchange with two barriers, one load in flight
         # per thread in the all-gather) for A/B measurements
         self.legacy_kernels = os.environ.get('TWINKLE_SYMM_LEGACY', '0') == '1'
+        # TWINKLE_SYMM_CANARIES=1 (debug aid; compute-sanitizer cannot follow writes that arrive from a peer GPU): every
+        # tensor carved from symmetric memory gets a guard zone on both sides, filled with a pattern that
+        # ``check_canaries`` verifies — a peer kernel that writes past a tensor's end is then caught at the next check
+        self.guard_bytes = GUARD_BYTES if os.environ.get('TWINKLE_SYMM_CANARIES', '0') == '1' else 0
+        self._guards: List[Tuple[SymmBuffer, str, int, int]] = []
 
     # ----------------------------------------------------------- allocation
     def alloc(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
         """A tensor living in symmetric memory (collective call: every rank of the group must make the
         same request at the same point)."""
         nbytes = numel * torch.empty(0, dtype=dtype).element_size()
-        off = self._chunks[-1].carve(nbytes) if self._chunks else None
+        g = self.guard_bytes
+        off = self._chunks[-1].carve(nbytes, g) if self._chunks else None
         if off is None:
-            self._chunks.append(SymmBuffer(self, max(nbytes, self.chunk_bytes)))
-            off = self._chunks[-1].carve(nbytes)
+            self._chunks.append(SymmBuffer(self, max(nbytes + 2 * g + 512, self.chunk_bytes)))
+            off = self._chunks[-1].carve(nbytes, g)
         buf = self._chunks[-1]
+        if g:
+            fill_guards(buf.raw, off, nbytes, g)
+            self._guards.append((buf, f'tensor #{len(self._guards)} ({numel} x {dtype})', off, nbytes))
         t = buf.raw[off:off + nbytes].view(dtype)
         self._by_ptr[t.data_ptr()] = (buf, off)
         return t
+
+    def check_canaries(self) -> None:
+        """Raises if any guard zone of this rank's symmetric tensors was overwritten (a no-op unless the communicator
+        was created with ``TWINKLE_SYMM_CANARIES=1``).  Synchronises the device."""
+        if not self._guards:
+            return
+        torch.cuda.synchronize(self.device)
+        bad: List[str] = []
+        for buf in {id(b): b for b, _, _, _ in self._guards}.values():
+            bad += damaged_guards(buf.raw, [(n, o, nb, self.guard_bytes) for b, n, o, nb in self._guards if b is buf])
+        if bad:
+            raise RuntimeError(f'rank {self.rank}: writes outside symmetric tensors detected next to: ' + '; '.join(bad))
 
     def peer_ptrs(self, t: torch.Tensor) -> Optional[List[int]]:
         hit = self._by_ptr.get(t.data_ptr())
