@@ -68,7 +68,7 @@ def _hybrid_curve(rank, world, steps):
     from twinkle_b200.utils.device_mesh import DeviceMesh
     torch.manual_seed(0)
     mesh = DeviceMesh.from_sizes(fsdp_size=world, dp_size=None, ulysses_size=world) if world > 1 else DeviceMesh.from_sizes(dp_size=1)
-    m = TransformersModel(model_id='tiny-hybrid', device_mesh=mesh, seed=0)
+    m = TransformersModel(model_id='tiny-hybrid', device_mesh=mesh, seed=0, device='cpu')   # fp32 on both sides of the comparison
     m.set_optimizer('AdamW', lr=2e-3, weight_decay=0.0)
     g = torch.Generator().manual_seed(9)
     feats = []
@@ -101,7 +101,7 @@ def test_sampler_carries_linear_attention_state_through_decode():
     from twinkle_b200.data_format import SamplingParams
     from twinkle_b200.models.decoder import PackedBatch
     from twinkle_b200.sampler import TorchSampler
-    s = TorchSampler(model_id='tiny-hybrid', weight_seed=0, enable_lora=False)
+    s = TorchSampler(model_id='tiny-hybrid', weight_seed=0, enable_lora=False, device='cpu')    # fp32: the 2e-4 bound below is not a bf16 bound
     prompts = [{'input_ids': [5, 6, 7, 8, 9]}, {'input_ids': [11, 12]}]       # second prompt shorter than the conv window
     resps = s.sample(prompts, SamplingParams(max_tokens=6, temperature=1.0, seed=3, logprobs=1, num_samples=2))
     assert [len(r.sequences) for r in resps] == [2, 2]
