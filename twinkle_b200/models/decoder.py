@@ -398,7 +398,13 @@ class DecoderModel(nn.Module):
             # backward of either op sums the per-vocabulary-shard partial gradients of the hidden states
             hidden = GatherTokens.apply(hidden, self.tp.comm) if self.tp.sp else CopyToTP.apply(hidden, self.tp.comm)
             return vocab_parallel_logprob(hidden, self.head_weight(), safe, self.tp, temperature), None
-        return ops.fused_linear_logprob(hidden, self.head_weight(), safe, temperature, with_entropy)
+        hw = self.head_weight()
+        # an untied head is a Linear weight: its dW chunks can go straight into the engine's fp32 gradient buffer (a bf16
+        # buffer is not used this way: the chunks are summed in fp32 first)
+        wgrad_out = getattr(hw, '_wgrad_out', None) if (hw.requires_grad and getattr(hw, '_direct_wgrad', False)) else None
+        if wgrad_out is not None and wgrad_out.dtype != torch.float32:
+            wgrad_out = None
+        return ops.fused_linear_logprob(hidden, hw, safe, temperature, with_entropy, wgrad_out=wgrad_out)
 
     def aux_loss(self) -> Optional[torch.Tensor]:
         terms = [l.mlp.last_aux for l in self.layers if getattr(l, 'is_moe', False) and l.mlp.last_aux is not None]

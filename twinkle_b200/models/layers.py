@@ -112,6 +112,9 @@ class Linear(nn.Module):
         super().__init__()
         self.in_features, self.out_features = in_features, out_features
         self.weight = nn.Parameter(torch.empty(out_features, in_features))
+        # every use of this weight goes through a backward that can add dW into a buffer it is handed (`_wgrad_out`),
+        # which lets a sharding engine skip the per-parameter gradient tensor altogether
+        self.weight._direct_wgrad = True
         self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
         self.parts = list(parts) if parts else [(name or 'linear', out_features)]
         assert sum(n for _, n in self.parts) == out_features

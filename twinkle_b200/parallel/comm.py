@@ -68,7 +68,7 @@ class Communicator:
     def reduce_scatter_accumulate(self, grad_shard: torch.Tensor, full_grad: torch.Tensor, scale: float = 1.0) -> None:
         """``grad_shard += scale · Σ_ranks full_grad[rank's slice]`` (fp32 accumulate)."""
         if self.world_size == 1:
-            grad_shard.add_(full_grad[:grad_shard.numel()].to(grad_shard.dtype), alpha=scale)
+            grad_shard.add_(full_grad[:grad_shard.numel()], alpha=scale)  # mixed-dtype add: one pass, no fp32 copy first
             return
         n = grad_shard.numel()
         if full_grad.device.type == 'cpu' or full_grad.dtype == torch.float32:
@@ -77,7 +77,7 @@ class Communicator:
         else:
             tmp = torch.empty(n, dtype=full_grad.dtype, device=full_grad.device)
             dist.reduce_scatter_tensor(tmp, full_grad, op=dist.ReduceOp.SUM, group=self.group)
-        grad_shard.add_(tmp.to(grad_shard.dtype), alpha=scale)
+        grad_shard.add_(tmp, alpha=scale)
 
     def wait_reduce_scatters(self, all_but: int = 0) -> None:
         """Library reduce-scatters run on the calling stream: nothing is outstanding."""

@@ -32,6 +32,7 @@ all-reduced.
 from __future__ import annotations
 
 import math
+import os
 from contextlib import nullcontext
 from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
 
@@ -144,6 +145,24 @@ class FlatBucket:
         self.full = None
 
     # ----------------------------------------------------------------- grads
+    def _direct_layout(self):
+        """Single-rank shard group with fp32 gradients on a GPU: the weights of linear layers take their dW GEMM's
+        output straight into the fp32 gradient (no bf16 copy of the layer's gradient, no cast-and-add pass over it
+        afterwards); the few other tensors (norm weights, embeddings, convolution filters) keep a compact bf16 side
+        buffer that autograd accumulates into and that is added per tensor.  Returns ``[(index, side offset)]`` of the
+        tensors on the side buffer and its size, or None when this layout does not apply."""
+        if not (self.world == 1 and self.grad_dtype == torch.float32 and self.compute_dtype != torch.float32
+                and self.shard.device.type == 'cuda' and os.environ.get('TWINKLE_DIRECT_WGRAD', '1') == '1'):
+            return None
+        if getattr(self, '_side_layout', None) is None:
+            side, off = [], 0
+            for i, (p, s) in enumerate(zip(self.params, self.shapes)):
+                if not (getattr(p, '_direct_wgrad', False) and len(s) == 2):
+                    side.append((i, off))
+                    off += _align(math.prod(s) if s else 1, 64)
+            self._side_layout = (side, off)
+        return self._side_layout
+
     def prepare_grads(self, pool: 'BufferPool') -> None:
         if not self.trainable:
             return
@@ -155,6 +174,22 @@ class FlatBucket:
                 self._bind_grads(self.grad_shard)
                 self.full_grad = None
                 return
+            direct = self._direct_layout()
+            if direct is not None:
+                side, size = direct
+                self._side_grad = pool.take(max(size, 64), self.compute_dtype)
+                self._side_grad.zero_()
+                on_side = dict(side)
+                for i, (p, o, s) in enumerate(zip(self.params, self.offsets, self.shapes)):
+                    n = math.prod(s) if s else 1
+                    if i in on_side:
+                        p.grad = self._side_grad[on_side[i]:on_side[i] + n].view(s)
+                        p._wgrad_out = None
+                    else:
+                        p.grad = None
+                        p._wgrad_out = self.grad_shard[o:o + n].view(s)
+                self.full_grad = None
+                return
         self.full_grad = pool.take_grad(self.numel, self.compute_dtype, self.comm)
         self.full_grad.zero_()
         self._bind_grads(self.full_grad)
@@ -164,6 +199,21 @@ class FlatBucket:
         if not self.trainable:
             return
         if self.full_grad is None:  # world==1, grads accumulate in place
+            side_grad = getattr(self, '_side_grad', None)
+            if side_grad is not None:
+                for i, so in self._side_layout[0]:
+                    o, s = self.offsets[i], self.shapes[i]
+                    n = math.prod(s) if s else 1
+                    g = self.params[i].grad
+                    if g is not None and g.data_ptr() != side_grad[so:so + n].data_ptr():   # autograd replaced the view
+                        self.grad_shard[o:o + n].add_(g.reshape(-1))
+                    else:
+                        self.grad_shard[o:o + n].add_(side_grad[so:so + n])
+                    self.params[i]._wgrad_out = None
+                for p in self.params:
+                    p._wgrad_out = None
+                pool.give(side_grad)
+                self._side_grad = None
             for p in self.params:
                 p.grad = None
             return
