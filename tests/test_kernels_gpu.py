@@ -115,6 +115,19 @@ def test_grouped_gemm(E):
     gw = E.grouped_gemm_wgrad(dy, x, off, Eg)
     gr = torch.stack([dy[offs[e]:offs[e + 1]].float().t() @ x[offs[e]:offs[e + 1]].float() for e in range(Eg)])
     assert rel(gw, gr) < 1e-5 and float(gw[1].abs().max()) == 0.0
+    # second operand pair (a rank-16 and a rank-72 low-rank term summed in tensor memory with the base product): both
+    # layouts, with the narrow operand far below / just above the kernel's 64-wide k-tile
+    for r in (16, 72):
+        x2 = torch.zeros(offs[-1], r, device='cuda').bfloat16()
+        for e, c in enumerate(counts):
+            x2[offs[e]:offs[e] + c] = torch.randn(c, r, device='cuda').bfloat16()
+        w2 = torch.randn(Eg, N, r, device='cuda').bfloat16()
+        both = want.float() + ref.grouped_gemm(x2, w2, off).float()
+        got = E.grouped_gemm(x, w, off, 'nt', None, None, False, x2, w2)
+        assert rel(got, both) < 4e-3
+        got = E.grouped_gemm(x, w.transpose(1, 2).contiguous(), off, 'nn', None, None, False, x2, w2.transpose(1, 2).contiguous())
+        assert rel(got, both) < 4e-3
+    assert E.read_and_clear_error() == 0
 
 
 @pytest.mark.parametrize('rows,H', [(1000, 4096), (333, 1000), (257, 5120), (64, 8192), (33, 9216), (1, 128)])

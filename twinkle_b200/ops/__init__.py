@@ -841,17 +841,21 @@ def moe_combine(y, w, row_of, src_tok, slot_of_row):
 
 
 class _ExpertLinearLora(torch.autograd.Function):
-    """``y = x Wᵀ + s · (x Aᵀ) Bᵀ`` per expert over expert-grouped rows: the LoRA expand GEMM accumulates into the
-    base GEMM's output inside its epilogue, so the [rows, out] tensor is written once and never re-read by an
-    element-wise add or scale."""
+    """``y = x Wᵀ + s · (x Aᵀ) Bᵀ`` per expert over expert-grouped rows.  The low-rank term rides in the base GEMM as a
+    second operand pair (``[x | h] · [W | s·B]ᵀ`` summed in tensor memory), forward and input-gradient alike, so the
+    ``[rows, out]`` / ``[rows, in]`` tensors are written once and never re-read by an accumulate pass.
+    ``TWINKLE_EXPERT_LORA_SPLIT=1`` keeps the earlier form (a separate rank-r GEMM accumulating into the output)."""
 
     @staticmethod
     def forward(ctx, x, weight, a, b, offsets, scale):
         E = ext()
-        y = E.grouped_gemm(x, weight, offsets, 'nt', None)
         h = E.grouped_gemm(x, a, offsets, 'nt', None)                     # [rows, r]
         bs = (b.float() * scale).to(b.dtype)                               # [E, out, r] — scale folded into the small operand
-        E.grouped_gemm(h, bs, offsets, 'nt', None, y, True)
+        if _EXPERT_LORA_SPLIT:
+            y = E.grouped_gemm(x, weight, offsets, 'nt', None)
+            E.grouped_gemm(h, bs, offsets, 'nt', None, y, True)
+        else:
+            y = E.grouped_gemm(x, weight, offsets, 'nt', None, None, False, h, bs)
         ctx.save_for_backward(x, weight, a, bs, h, offsets)
         ctx.scale = scale
         return y
@@ -865,12 +869,18 @@ class _ExpertLinearLora(torch.autograd.Function):
         gh = E.grouped_gemm(gy, bs, offsets, 'nn', None)                   # [rows, r] = gy · (s·B)
         gx = None
         if ctx.needs_input_grad[0]:
-            gx = E.grouped_gemm(gy, weight, offsets, 'nn', None)
-            E.grouped_gemm(gh, a, offsets, 'nn', None, gx, True)
+            if _EXPERT_LORA_SPLIT:
+                gx = E.grouped_gemm(gy, weight, offsets, 'nn', None)
+                E.grouped_gemm(gh, a, offsets, 'nn', None, gx, True)
+            else:
+                gx = E.grouped_gemm(gy, weight, offsets, 'nn', None, None, False, gh, a)
         gw = E.grouped_gemm_wgrad(gy, x, offsets, n_e).to(weight.dtype) if ctx.needs_input_grad[1] else None
         ga = E.grouped_gemm_wgrad(gh, x, offsets, n_e).to(a.dtype) if ctx.needs_input_grad[2] else None
         gb = (E.grouped_gemm_wgrad(gy, h, offsets, n_e) * ctx.scale).to(bs.dtype) if ctx.needs_input_grad[3] else None
         return gx, gw, ga, gb, None, None
+
+
+_EXPERT_LORA_SPLIT = os.environ.get('TWINKLE_EXPERT_LORA_SPLIT', '0') == '1'
 
 
 def expert_linear(x, weight, offsets, lora_a=None, lora_b=None, scale: float = 1.0):

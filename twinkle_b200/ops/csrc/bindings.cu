@@ -7,7 +7,7 @@ namespace tk {
 torch::Tensor gemm(const torch::Tensor&, const torch::Tensor&, const std::string&, const c10::optional<torch::Tensor>&, bool,
                    c10::optional<torch::ScalarType>);
 torch::Tensor grouped_gemm(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const std::string&, const c10::optional<torch::Tensor>&,
-                           const c10::optional<torch::Tensor>&, bool);
+                           const c10::optional<torch::Tensor>&, bool, const c10::optional<torch::Tensor>&, const c10::optional<torch::Tensor>&);
 torch::Tensor grouped_gemm_wgrad(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, int64_t);
 std::vector<torch::Tensor> rmsnorm_fwd(const torch::Tensor&, const torch::Tensor&, double, double, const c10::optional<torch::Tensor>&);
 std::vector<torch::Tensor> rmsnorm_bwd(const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, const torch::Tensor&, double,
@@ -67,7 +67,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &tk::gemm, py::arg("a"), py::arg("b"), py::arg("layout") = "nt", py::arg("out") = py::none(),
         py::arg("accumulate") = false, py::arg("out_dtype") = py::none());
   m.def("grouped_gemm", &tk::grouped_gemm, py::arg("x"), py::arg("w"), py::arg("offsets"), py::arg("layout") = "nt", py::arg("group_map") = py::none(),
-        py::arg("out") = py::none(), py::arg("accumulate") = false);
+        py::arg("out") = py::none(), py::arg("accumulate") = false, py::arg("x2") = py::none(), py::arg("w2") = py::none());
   m.def("grouped_gemm_wgrad", &tk::grouped_gemm_wgrad);
   m.def("rmsnorm_fwd", &tk::rmsnorm_fwd, py::arg("x"), py::arg("w"), py::arg("eps"), py::arg("offset"), py::arg("residual") = py::none());
   m.def("rmsnorm_bwd", &tk::rmsnorm_bwd, py::arg("g"), py::arg("x"), py::arg("w"), py::arg("rstd"), py::arg("offset"),

@@ -44,6 +44,10 @@ struct GemmParams {
   int group_rows_b;    // rows of B per group (N for NT, K for NN)
   int mode;            // 0 dense, 1 grouped over M (A rows by expert), 2 grouped wgrad (K range by expert)
   const int* group_map;  // optional: group g uses weight block group_map[g] (< 0: group skipped); nullptr = identity
+  // second operand pair of the M-grouped mode (0 = none): out = A·B + A2·B2 accumulated in tensor memory before the
+  // epilogue — how a low-rank (LoRA) term rides in the base GEMM instead of re-reading and re-writing the output
+  int K2;
+  int group_rows_b2;   // rows of B2 per group (N for NT, K2 for NN)
 };
 
 struct TileCoord {
@@ -118,7 +122,8 @@ __device__ __forceinline__ bool next_tile(const GemmParams& p, int tile, Grouped
 
 template <bool A_MN, bool B_MN, int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -160,27 +165,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       TileCoord t;
       bool ok = true;
       for (int tile = blockIdx.x; ok && next_tile<MODE>(p, tile, cur, t); tile += gridDim.x) {
-        const int b_row0 = (MODE == 1) ? (p.group_map ? p.group_map[t.group] : t.group) * p.group_rows_b : 0;
-        for (int k0 = t.k_begin; k0 < t.k_end; k0 += BK) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.err, ERR_PRODUCER_WAIT)) { ok = false; break; }
+        const int b_group = (MODE == 1) ? (p.group_map ? p.group_map[t.group] : t.group) : 0;
+        const int b_row0 = b_group * p.group_rows_b;
+        auto load_stage = [&](const CUtensorMap* mA, const CUtensorMap* mB, int k0, int brow) -> bool {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.err, ERR_PRODUCER_WAIT)) return false;
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
           mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
           if constexpr (!A_MN) {
-            tma_load_2d(sa, &tmA, &full_bar[stage], k0, t.m0);            // box {64 (K), 128 rows}
+            tma_load_2d(sa, mA, &full_bar[stage], k0, t.m0);            // box {64 (K), 128 rows}
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)                             // box {64 (M), 64 K-rows} each
-              tma_load_2d(sa + j * (64 * BK * 2), &tmA, &full_bar[stage], t.m0 + j * 64, k0);
+              tma_load_2d(sa + j * (64 * BK * 2), mA, &full_bar[stage], t.m0 + j * 64, k0);
           }
           if constexpr (!B_MN) {
-            tma_load_2d(sb, &tmB, &full_bar[stage], k0, b_row0 + t.n0);   // box {64 (K), 256 rows}
+            tma_load_2d(sb, mB, &full_bar[stage], k0, brow + t.n0);   // box {64 (K), 256 rows}
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sb + j * (64 * BK * 2), &tmB, &full_bar[stage], t.n0 + j * 64, b_row0 + k0);
+              tma_load_2d(sb + j * (64 * BK * 2), mB, &full_bar[stage], t.n0 + j * 64, brow + k0);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          return true;
+        };
+        for (int k0 = t.k_begin; ok && k0 < t.k_end; k0 += BK) ok = load_stage(&tmA, &tmB, k0, b_row0);
+        if constexpr (MODE == 1) {
+          // second pair: columns past K2 and rows past the tensors read as zero (out-of-range fill), so a K2 below the
+          // 64-wide k-tile costs one tile
+          for (int k0 = 0; ok && k0 < p.K2; k0 += BK) ok = load_stage(&tmA2, &tmB2, k0, b_group * p.group_rows_b2);
         }
       }
       if (!ok) {
@@ -205,7 +218,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (t.k_end <= t.k_begin) {
           // empty reduction range (expert without tokens): accumulator must read as zero → epilogue handles via flag
         }
-        for (int k0 = t.k_begin; k0 < t.k_end; k0 += BK) {
+        int k_tiles = (t.k_end > t.k_begin) ? (t.k_end - t.k_begin + BK - 1) / BK : 0;
+        if constexpr (MODE == 1) k_tiles += (p.K2 + BK - 1) / BK;
+        for (int kt = 0; kt < k_tiles; ++kt) {
           if (!mbar_wait(&full_bar[stage], phase, p.err, ERR_MMA_WAIT_FULL)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
@@ -237,7 +252,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     for (int tile = blockIdx.x; ok && next_tile<MODE>(p, tile, cur, t); tile += gridDim.x) {
       if (!mbar_wait(&tmem_full[acc], acc_phase, p.err, ERR_EPI_WAIT)) { ok = false; break; }
       tc_fence_after();
-      const bool empty_k = (t.k_end <= t.k_begin);
+      const bool empty_k = (t.k_end <= t.k_begin) && !(MODE == 1 && p.K2 > 0);
       const int row = t.m0 + q * 32 + lane;
       const bool row_ok = row < t.m_limit;
       size_t out_row = static_cast<size_t>(row);
@@ -312,7 +327,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
 // ------------------------------------------------------------------ host side
 static void launch(bool a_mn, bool b_mn, int mode, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int tiles,
-                   cudaStream_t stream) {
+                   cudaStream_t stream, const CUtensorMap* ta2 = nullptr, const CUtensorMap* tb2 = nullptr) {
+  const CUtensorMap& xa2 = ta2 ? *ta2 : ta;   // unused by the kernel unless p.K2 > 0
+  const CUtensorMap& xb2 = tb2 ? *tb2 : tb;
   int grid = std::min(tiles, num_sms());
   if (grid <= 0) return;
 #define TK_LAUNCH(AM, BMN, MD)                                                                                   \
@@ -323,7 +340,7 @@ static void launch(bool a_mn, bool b_mn, int mode, const CUtensorMap& ta, const 
       TK_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));        \
       configured = true;                                                                                         \
     }                                                                                                            \
-    kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);                                                  \
+    kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ta, tb, xa2, xb2, p);                                        \
   } while (0)
   if (mode == 0) {
     if (!a_mn && !b_mn) TK_LAUNCH(false, false, 0);
@@ -410,8 +427,11 @@ torch::Tensor gemm(const torch::Tensor& a, const torch::Tensor& b, const std::st
 
 // Expert-grouped GEMM.  x [R, K] with expert e owning rows [offsets[e], offsets[e+1]) (offsets multiples of 128;
 // padding rows are zero); weight [E, N, K] (nt) or [E, K, N] (nn).  Returns [R, N].
+// Optional second pair (x2 [R, K2], w2 [E, N, K2] (nt) or [E, K2, N] (nn)): returns x·W + x2·W2 from one pass — the sum
+// is formed in tensor memory, the output is written once.
 torch::Tensor grouped_gemm(const torch::Tensor& x, const torch::Tensor& w, const torch::Tensor& offsets, const std::string& layout,
-                           const c10::optional<torch::Tensor>& group_map, const c10::optional<torch::Tensor>& out_opt, bool accumulate) {
+                           const c10::optional<torch::Tensor>& group_map, const c10::optional<torch::Tensor>& out_opt, bool accumulate,
+                           const c10::optional<torch::Tensor>& x2_opt, const c10::optional<torch::Tensor>& w2_opt) {
   check_operand(x, "x");
   TORCH_CHECK(w.is_cuda() && w.scalar_type() == torch::kBFloat16 && w.dim() == 3 && w.is_contiguous(), "weight [E, *, *] bf16 contiguous");
   TORCH_CHECK(offsets.is_cuda() && offsets.scalar_type() == torch::kInt32 && offsets.is_contiguous(), "offsets int32 on device");
@@ -448,7 +468,32 @@ torch::Tensor grouped_gemm(const torch::Tensor& x, const torch::Tensor& w, const
   p.group_map = mapped ? group_map->data_ptr<int>() : nullptr;
   // upper bound of tiles: every expert wastes at most one partial M-tile
   int tiles = ((R + BM - 1) / BM + E) * ((N + BN - 1) / BN);
-  launch(false, b_mn, 1, ta, tb, p, tiles, at::cuda::getCurrentCUDAStream());
+  const bool dual = x2_opt.has_value() && x2_opt->defined();
+  if (!dual) {
+    launch(false, b_mn, 1, ta, tb, p, tiles, at::cuda::getCurrentCUDAStream());
+    return out;
+  }
+  TORCH_CHECK(w2_opt.has_value() && w2_opt->defined(), "second pair needs both operands");
+  const torch::Tensor& x2 = *x2_opt;
+  const torch::Tensor& wb = *w2_opt;
+  check_operand(x2, "x2");
+  TORCH_CHECK(x2.size(0) == R, "x2 rows");
+  TORCH_CHECK(wb.is_cuda() && wb.scalar_type() == torch::kBFloat16 && wb.dim() == 3 && wb.is_contiguous() && wb.size(0) == w.size(0),
+              "w2 [E, *, *] bf16 contiguous with the first pair's group count");
+  const int K2 = x2.size(1);
+  if (b_mn) {
+    TORCH_CHECK(wb.size(1) == K2 && wb.size(2) == N, "nn: w2 must be [E, K2, N]");
+  } else {
+    TORCH_CHECK(wb.size(1) == N && wb.size(2) == K2, "nt: w2 must be [E, N, K2]");
+  }
+  auto wb2 = wb.view({wb.size(0) * wb.size(1), wb.size(2)});
+  check_operand(wb2, "w2");
+  CUtensorMap ta2 = make_tmap_2d(x2.data_ptr(), x2.size(1), x2.size(0), x2.stride(0), BK, BM);
+  CUtensorMap tb2 = b_mn ? make_tmap_2d(wb2.data_ptr(), wb2.size(1), wb2.size(0), wb2.stride(0), 64, BK)
+                         : make_tmap_2d(wb2.data_ptr(), wb2.size(1), wb2.size(0), wb2.stride(0), BK, BN);
+  p.K2 = K2;
+  p.group_rows_b2 = wb.size(1);
+  launch(false, b_mn, 1, ta, tb, p, tiles, at::cuda::getCurrentCUDAStream(), &ta2, &tb2);
   return out;
 }
 
