@@ -19,6 +19,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 
 from .. import ops
 
@@ -174,10 +175,43 @@ class Linear(nn.Module):
         lb = _CTX.batch
         if lb is not None and self.max_loras > 0:
             x2 = x.reshape(-1, x.shape[-1])
+            fused = self._lora_into(x2, y, lb)
+            if fused is not None:
+                return fused
             d = self._lora_delta(x2, lb)
             if d is not None:
                 y = y + d.view(y.shape)
         return y
+
+    def _lora_into(self, x2: torch.Tensor, y: torch.Tensor, lb: LoraBatch) -> Optional[torch.Tensor]:
+        """GPU path: one shrink over the pools of all fused projections (stacked along the rank axis) and one expand
+        whose epilogue adds the delta into ``y`` in place — no per-projection launches, no concatenation, no separate
+        add.  Returns None when it does not apply (CPU / fp32, or tenants whose ``target_modules`` differ between the
+        fused projections)."""
+        if not ops.sgmv_fused_supported(x2) or y.dtype != torch.bfloat16 or not y.is_contiguous():
+            return None
+        prefix = self.full_name.rsplit('.', 1)[0] if '.' in self.full_name else ''
+        keep = None
+        if any(t is not None for t in lb.targets):
+            keeps = [tuple(t is None or t.matches(f'{prefix}.{pname}' if prefix else pname, pname) for t in lb.targets) for pname, _ in self.parts]
+            if any(k != keeps[0] for k in keeps[1:]):
+                return None
+            keep = keeps[0]
+            if not any(keep):
+                return y
+            if all(keep):
+                keep = None
+        st, sl, rk, sc, host = lb.tensors(keep)
+        names = [p for p, _ in self.parts]
+        if len(names) == 1:
+            a, b = self.lora_A[names[0]], self.lora_B[names[0]]
+        else:
+            P, R = len(names), self.max_r
+            a = torch.cat([self.lora_A[p] for p in names], 1)                                              # [S, P·R, K]
+            b = torch.cat([F.pad(self.lora_B[p], (i * R, (P - 1 - i) * R)) for i, p in enumerate(names)], 1)   # block-diagonal [S, N, P·R]
+        y2 = y.view(-1, y.shape[-1])
+        out = ops.sgmv(x2, a, b, st, sl, rk, sc, host, out=y2, repeat=len(names))
+        return out.view(y.shape)
 
 
 class RMSNorm(nn.Module):

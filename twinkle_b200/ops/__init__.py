@@ -595,15 +595,25 @@ class _SGMV(torch.autograd.Function):
     over 64-row-aligned token windows whose rows outside the segment are zeroed."""
 
     @staticmethod
-    def forward(ctx, x, lora_a, lora_b, seg_starts, seg_slots, seg_ranks, seg_scales, host_segments):
+    def forward(ctx, x, lora_a, lora_b, seg_starts, seg_slots, seg_ranks, seg_scales, host_segments, y_in=None, repeat=1):
+        """``y_in`` (optional): the base projection's output; the delta is accumulated into it by the expand GEMM's
+        epilogue instead of being produced as a tensor of its own and added.  ``repeat``: the pools of ``repeat``
+        fused projections stacked along the rank axis (``A [S, repeat·R, K]``, ``B`` block-diagonal) — the rank mask
+        then repeats per block."""
         E = ext()
         R = lora_a.shape[1]
-        rowmask = _sgmv_rowmask(host_segments, R, x.device, x.dtype)           # [T, R] = scale where col < rank else 0
+        rowmask = _sgmv_rowmask(host_segments, R // repeat, x.device, x.dtype, repeat)   # [T, R] = scale where col < rank else 0
         h = E.grouped_gemm(x, lora_a, seg_starts, 'nt', seg_slots)             # [T, R]
         hm = h * rowmask
-        y = E.grouped_gemm(hm, lora_b, seg_starts, 'nt', seg_slots)            # [T, N]
+        if y_in is not None:
+            E.grouped_gemm(hm, lora_b, seg_starts, 'nt', seg_slots, y_in, True)
+            ctx.mark_dirty(y_in)
+            y = y_in
+        else:
+            y = E.grouped_gemm(hm, lora_b, seg_starts, 'nt', seg_slots)        # [T, N]
         ctx.save_for_backward(x, lora_a, lora_b, hm, rowmask, seg_starts, seg_slots)
         ctx.host_segments = host_segments
+        ctx.has_y = y_in is not None
         return y
 
     @staticmethod
@@ -621,25 +631,34 @@ class _SGMV(torch.autograd.Function):
             if slot < 0 or rank == 0 or hi <= lo:
                 continue
             a0, b0 = lo // 64 * 64, min((hi + 63) // 64 * 64, T)
-            ghs, hms = gh[a0:b0].clone(), hm[a0:b0].clone()
-            ghs[:lo - a0].zero_(), ghs[hi - a0:].zero_()
-            hms[:lo - a0].zero_(), hms[hi - a0:].zero_()
+            if a0 == lo and (b0 == hi or hi == T):       # the segment fills its 64-row windows: no rows to blank out
+                ghs, hms = gh[a0:b0], hm[a0:b0]
+            else:
+                ghs, hms = gh[a0:b0].clone(), hm[a0:b0].clone()
+                ghs[:lo - a0].zero_(), ghs[hi - a0:].zero_()
+                hms[:lo - a0].zero_(), hms[hi - a0:].zero_()
             E.gemm(ghs, x[a0:b0], 'tn', ga[slot], True, None)                   # dA[slot] += ghᵀ x
             E.gemm(gy[a0:b0], hms, 'tn', gb[slot], True, None)                  # dB[slot] += gyᵀ h
-        return gx, ga.to(a.dtype), gb.to(b.dtype), None, None, None, None, None
+        return gx, ga.to(a.dtype), gb.to(b.dtype), None, None, None, None, None, (gy if ctx.has_y else None), None
 
 
 _ROWMASKS: 'dict' = {}
 
 
-def _sgmv_rowmask(host_segments, R: int, device, dtype) -> torch.Tensor:
+def _sgmv_rowmask(host_segments, R: int, device, dtype, repeat: int = 1) -> torch.Tensor:
     """``[T, R]``: the segment's scale in the first ``rank`` columns of its rows, zero elsewhere.  Every LoRA linear of
     every layer asks for the same mask during one forward/backward (and its recompute), so the last few are kept: the
     mask is built on the host and copied once instead of by a dozen small kernels per call."""
-    key = (tuple(host_segments), R, str(device), dtype)
+    key = (tuple(host_segments), R, str(device), dtype, repeat)
     hit = _ROWMASKS.get(key)
     if hit is not None:
         return hit
+    if repeat > 1:
+        mask = _sgmv_rowmask(host_segments, R, device, dtype).repeat(1, repeat)
+        if len(_ROWMASKS) >= 16:
+            _ROWMASKS.pop(next(iter(_ROWMASKS)))
+        _ROWMASKS[key] = mask
+        return mask
     per_seg = torch.zeros(max(len(host_segments), 1), R, dtype=torch.float32)
     lens = []
     for i, (lo, hi, slot, rank, scale) in enumerate(host_segments):
@@ -657,9 +676,16 @@ def _sgmv_rowmask(host_segments, R: int, device, dtype) -> torch.Tensor:
     return mask
 
 
-def sgmv(x, lora_a, lora_b, seg_starts, seg_slots, seg_ranks, seg_scales, host_segments=None):
+def sgmv_fused_supported(x: torch.Tensor) -> bool:
+    """Whether :func:`sgmv` can accumulate into the base output (``out=``) and take rank-stacked pools (``repeat=``)."""
+    return _cuda(x) and x.dtype == torch.bfloat16
+
+
+def sgmv(x, lora_a, lora_b, seg_starts, seg_slots, seg_ranks, seg_scales, host_segments=None, out=None, repeat: int = 1):
     """Multi-tenant LoRA delta for a token-segmented batch (see ``reference.sgmv``).  ``host_segments`` =
-    ``[(lo, hi, slot, rank, scale)]`` mirrors the device tensors so the CUDA path needs no device read."""
+    ``[(lo, hi, slot, rank, scale)]`` mirrors the device tensors so the CUDA path needs no device read.  On a GPU
+    ``out`` (the base projection's output ``[T, N]``) receives the delta in place and is returned; ``repeat`` says that
+    ``lora_a`` / ``lora_b`` stack that many projections' pools along the rank axis."""
     if _cuda(x) and x.dtype == torch.bfloat16:
         if host_segments is None:
             starts = seg_starts.tolist()
@@ -670,7 +696,8 @@ def sgmv(x, lora_a, lora_b, seg_starts, seg_slots, seg_ranks, seg_scales, host_s
             host_segments = [(lo, min(hi, T), s, r, c) for (lo, hi, s, r, c) in host_segments if lo < T]
             seg_starts = torch.tensor([h[0] for h in host_segments] + [host_segments[-1][1]], dtype=torch.int32, device=x.device)
             seg_slots = torch.tensor([h[2] for h in host_segments], dtype=torch.int32, device=x.device)
-        return _SGMV.apply(x.contiguous(), lora_a, lora_b, seg_starts, seg_slots, seg_ranks, seg_scales, host_segments)
+        return _SGMV.apply(x.contiguous(), lora_a, lora_b, seg_starts, seg_slots, seg_ranks, seg_scales, host_segments, out, repeat)
+    assert out is None and repeat == 1, 'in-place / stacked form is for the CUDA path'
     return _sgmv_autograd_cpu(x, lora_a, lora_b, seg_starts, seg_slots, seg_ranks, seg_scales)
 
 
