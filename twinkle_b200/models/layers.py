@@ -188,7 +188,7 @@ class Linear(nn.Module):
         whose epilogue adds the delta into ``y`` in place — no per-projection launches, no concatenation, no separate
         add.  Returns None when it does not apply (CPU / fp32, or tenants whose ``target_modules`` differ between the
         fused projections)."""
-        if not ops.sgmv_fused_supported(x2) or y.dtype != torch.bfloat16 or not y.is_contiguous():
+        if not ops.sgmv_fused_supported(x2) or y.dtype != torch.bfloat16 or y.dim() != 2 or not y.is_contiguous():
             return None
         prefix = self.full_name.rsplit('.', 1)[0] if '.' in self.full_name else ''
         keep = None
@@ -209,9 +209,7 @@ class Linear(nn.Module):
             P, R = len(names), self.max_r
             a = torch.cat([self.lora_A[p] for p in names], 1)                                              # [S, P·R, K]
             b = torch.cat([F.pad(self.lora_B[p], (i * R, (P - 1 - i) * R)) for i, p in enumerate(names)], 1)   # block-diagonal [S, N, P·R]
-        y2 = y.view(-1, y.shape[-1])
-        out = ops.sgmv(x2, a, b, st, sl, rk, sc, host, out=y2, repeat=len(names))
-        return out.view(y.shape)
+        return ops.sgmv(x2, a, b, st, sl, rk, sc, host, out=y, repeat=len(names))
 
 
 class RMSNorm(nn.Module):

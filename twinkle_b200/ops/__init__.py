@@ -99,10 +99,13 @@ class _Linear(torch.autograd.Function):
         if dead:  # graph only: dX needs W and dW needs x, nobody needs x·Wᵀ
             return torch.empty(*x.shape[:-1], weight.shape[0], dtype=x.dtype, device=x.device)
         x2 = x.reshape(-1, x.shape[-1])
-        y = gemm(x2, weight, 'nt')
+        # the result is allocated in its final shape (not returned as a view of a 2-D product): a later op may then
+        # accumulate into it in place, which autograd refuses for views created inside a custom Function
+        y = torch.empty(*x.shape[:-1], weight.shape[0], dtype=x.dtype, device=x.device)
+        gemm(x2, weight, 'nt', out=y.view(-1, weight.shape[0]))
         if bias is not None:
-            y = y + bias
-        return y.view(*x.shape[:-1], weight.shape[0])
+            y += bias
+        return y
 
     @staticmethod
     def backward(ctx, gy):
