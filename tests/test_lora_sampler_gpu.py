@@ -42,7 +42,7 @@ def test_grouped_gemm_group_map(E):
         lo += n
 
 
-@pytest.mark.parametrize('T', [777, 4096])
+@pytest.mark.parametrize('T', [777, 4096, 40000])     # 40000: segments long enough for the split-K weight gradients
 def test_sgmv_forward_backward(E, T):
     from twinkle_b200 import ops
     torch.manual_seed(2)
@@ -73,6 +73,40 @@ def test_sgmv_forward_backward(E, T):
     assert rel(b.grad, br.grad) < 8e-3
     # rows of slots nobody used and rank rows beyond a segment's rank get no gradient
     assert float(a.grad[1].abs().max()) == 0.0 and float(b.grad[1].abs().max()) == 0.0
+
+
+def test_sgmv_into_base_output_with_rank_stacked_pools(E):
+    """The form the fused q|k|v projection uses: pools of two projections stacked along the rank axis (block-diagonal
+    ``B``), the delta accumulated into the base output in place; against base + per-projection deltas in fp32."""
+    import torch.nn.functional as F
+    from twinkle_b200 import ops
+    torch.manual_seed(5)
+    T, S, R, K, n1, n2 = 1500, 3, 16, 256, 384, 128
+    a1, a2 = ((torch.randn(S, R, K, device='cuda') * 0.05).bfloat16().requires_grad_(True) for _ in range(2))
+    b1 = (torch.randn(S, n1, R, device='cuda') * 0.05).bfloat16().requires_grad_(True)
+    b2 = (torch.randn(S, n2, R, device='cuda') * 0.05).bfloat16().requires_grad_(True)
+    cuts, slots, ranks, scales = [0, 400, 900, T], [1, -1, 2], [16, 0, 8], [2.0, 0.0, 0.5]
+    st = torch.tensor(cuts, dtype=torch.int32, device='cuda')
+    sl = torch.tensor(slots, dtype=torch.int32, device='cuda')
+    rk = torch.tensor(ranks, dtype=torch.int32, device='cuda')
+    sc = torch.tensor(scales, dtype=torch.float32, device='cuda')
+    host = [(cuts[i], cuts[i + 1], slots[i], ranks[i], scales[i]) for i in range(3)]
+    x = torch.randn(T, K, device='cuda').bfloat16().requires_grad_(True)
+    base = torch.randn(T, n1 + n2, device='cuda').bfloat16().requires_grad_(True)
+    y0 = base * 1.0                                            # a non-leaf, as the projection's output is
+    a = torch.cat([a1, a2], 1)
+    b = torch.cat([F.pad(b1, (0, R)), F.pad(b2, (R, 0))], 1)
+    y = ops.sgmv(x, a, b, st, sl, rk, sc, host, out=y0, repeat=2)
+    assert y.data_ptr() == y0.data_ptr()
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, a1r, a2r, b1r, b2r, baser = (t.detach().float().requires_grad_(True) for t in (x, a1, a2, b1, b2, base))
+    yr = baser + torch.cat([ops._sgmv_autograd_cpu(xr, a1r, b1r, st, sl, rk, sc), ops._sgmv_autograd_cpu(xr, a2r, b2r, st, sl, rk, sc)], 1)
+    yr.backward(g.float())
+    assert rel(y, yr) < 6e-3 and rel(base.grad, baser.grad) == 0.0
+    for got, want in ((x.grad, xr.grad), (a1.grad, a1r.grad), (a2.grad, a2r.grad), (b1.grad, b1r.grad), (b2.grad, b2r.grad)):
+        assert rel(got, want) < 8e-3
+    assert torch.equal(y[400:900], base.detach()[400:900])      # the segment without an adapter keeps the base rows
 
 
 def test_paged_decode(E):

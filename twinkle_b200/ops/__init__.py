@@ -640,12 +640,36 @@ class _SGMV(torch.autograd.Function):
                 ghs, hms = gh[a0:b0].clone(), hm[a0:b0].clone()
                 ghs[:lo - a0].zero_(), ghs[hi - a0:].zero_()
                 hms[:lo - a0].zero_(), hms[hi - a0:].zero_()
-            E.gemm(ghs, x[a0:b0], 'tn', ga[slot], True, None)                   # dA[slot] += ghᵀ x
-            E.gemm(gy[a0:b0], hms, 'tn', gb[slot], True, None)                  # dB[slot] += gyᵀ h
+            n = b0 - a0
+            if n >= 8192:
+                # split-K: the outputs are a handful of tiles ([R, K] and [N, R]) over a reduction of n rows — as one
+                # GEMM that is a few CTAs walking the whole batch.  The K-grouped kernel gives every 1/32 of the rows
+                # its own CTAs; the partial sums are added afterwards (32 small fp32 tensors)
+                off = _split_k_offsets(n, x.device)
+                ga[slot] += E.grouped_gemm_wgrad(ghs, x[a0:b0], off, off.numel() - 1).sum(0)
+                gb[slot] += E.grouped_gemm_wgrad(gy[a0:b0], hms, off, off.numel() - 1).sum(0)
+            else:
+                E.gemm(ghs, x[a0:b0], 'tn', ga[slot], True, None)               # dA[slot] += ghᵀ x
+                E.gemm(gy[a0:b0], hms, 'tn', gb[slot], True, None)              # dB[slot] += gyᵀ h
         return gx, ga.to(a.dtype), gb.to(b.dtype), None, None, None, None, None, (gy if ctx.has_y else None), None
 
 
 _ROWMASKS: 'dict' = {}
+_SPLITK: 'dict' = {}
+
+
+def _split_k_offsets(n: int, device) -> torch.Tensor:
+    """int32 boundaries that cut ``n`` reduction rows into at most 32 chunks whose sizes are multiples of 64."""
+    key = (n, str(device))
+    hit = _SPLITK.get(key)
+    if hit is None:
+        chunk = max(1024, ((n + 31) // 32 + 63) // 64 * 64)
+        cuts = list(range(0, n, chunk)) + [n]
+        hit = torch.tensor(cuts, dtype=torch.int32, device=device)
+        if len(_SPLITK) >= 64:
+            _SPLITK.pop(next(iter(_SPLITK)))
+        _SPLITK[key] = hit
+    return hit
 
 
 def _sgmv_rowmask(host_segments, R: int, device, dtype, repeat: int = 1) -> torch.Tensor:
