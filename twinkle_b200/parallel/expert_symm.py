@@ -61,7 +61,7 @@ def ep_metadata(flat_idx: torch.Tensor, counts_all: torch.Tensor, me: int, k: in
     off = (pv.cumsum(1) - pv).reshape(-1)                       # [E] aligned start of every expert on its owner rank
 
     # ---- token side
-    order = torch.argsort(flat_idx, stable=True)
+    order = torch.argsort(_sort_keys(flat_idx, ca.shape[1]), stable=True)
     e_sorted = flat_idx[order]
     p = torch.arange(n, device=dev)
     row_sorted = off[e_sorted] + before[me][e_sorted] + (p - start[me][e_sorted])
@@ -225,11 +225,16 @@ class SymmExpertParallel:
         return s
 
 
+def _sort_keys(expert_ids: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """Expert ids as one-byte keys when they fit: the device radix sort then makes one pass instead of eight."""
+    return expert_ids.to(torch.uint8) if (expert_ids.is_cuda and num_experts <= 256) else expert_ids
+
+
 class _EPDispatch(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, strat: SymmExpertParallel, flat, hist, k, cap):
-        order = torch.argsort(flat, stable=True)
+        order = torch.argsort(_sort_keys(flat, strat.num_experts), stable=True)
         s = strat.publish(x=x, tok=(order // k).to(torch.int32), counts=hist)
         counts_all = torch.empty(strat.ep, strat.num_experts, dtype=torch.int32, device=x.device)
         strat.comm.ext.peer_all_gather(counts_all, s.counts_ptrs, strat.num_experts * 4, strat.rank, 1)

@@ -199,7 +199,55 @@ class _VocabParallelLogprob(torch.autograd.Function):
         return gh, gw, None, None, None
 
 
-def vocab_parallel_logprob(hidden, weight, labels, tp: TPContext, temperature: float = 1.0):
+class _VocabParallelLogprobChunked(torch.autograd.Function):
+    """GPU form of the op above on the log-prob kernels: the head GEMM runs chunk by chunk over the tokens and each
+    chunk's logits (bf16, this rank's vocabulary shard) are reduced to ``(target logit, log-sum-exp)`` by one kernel, so
+    neither fp32 logits nor probabilities are kept; the shards' statistics are merged with two small all-reduces.
+    Backward re-forms each chunk's logits, turns them in place into dlogits with the *global* log-sum-exp, and feeds the
+    two gradient GEMMs (the same scheme as the single-GPU ``ops.fused_linear_logprob``)."""
+
+    @staticmethod
+    def forward(ctx, hidden, weight, labels, comm: Communicator, temperature: float, chunk: int):
+        E = ops.ext()
+        T, vl = hidden.shape[0], weight.shape[0]
+        local = labels.to(torch.int64) - comm.rank * vl
+        local = torch.where((local >= 0) & (local < vl), local, torch.full_like(local, -1))   # −1: not in this shard
+        stats = torch.empty(2, T, dtype=torch.float32, device=hidden.device)                 # [shard lse, shard target logit]
+        for s in range(0, T, chunk):
+            e = min(s + chunk, T)
+            logits = ops.gemm(hidden[s:e], weight, 'nt')
+            lp, lse_l, _ = E.logprob_fwd(logits, local[s:e], temperature, False)
+            stats[0, s:e] = lse_l
+            stats[1, s:e] = lp + lse_l                     # the kernel reports (target − lse) with target = 0 outside the shard
+        m = stats[0].clone()
+        comm.all_reduce(m, 'max')
+        packed = torch.stack([torch.exp(stats[0] - m), stats[1]])
+        comm.all_reduce(packed)                            # Σ exp(lse_shard − m) and the target logit (one shard holds it)
+        lse = m + torch.log(packed[0])
+        ctx.save_for_backward(hidden, weight, local, lse)
+        ctx.comm, ctx.temperature, ctx.chunk = comm, temperature, chunk
+        return packed[1] - lse
+
+    @staticmethod
+    def backward(ctx, g):
+        E = ops.ext()
+        hidden, weight, local, lse = ctx.saved_tensors
+        T = hidden.shape[0]
+        g = g.contiguous().float()
+        gh = torch.empty_like(hidden)
+        gw = torch.zeros(weight.shape, dtype=torch.float32, device=weight.device)
+        for s in range(0, T, ctx.chunk):
+            e = min(s + ctx.chunk, T)
+            logits = ops.gemm(hidden[s:e], weight, 'nt')
+            d = E.logprob_bwd(logits, local[s:e], lse[s:e], None, g[s:e], None, ctx.temperature)
+            ops.gemm(d, weight, 'nn', out=gh[s:e])         # partial over this rank's shard; the caller's gather / copy op sums
+            ops.gemm(d, hidden[s:e], 'tn', out=gw, accumulate=True)
+        return gh, gw.to(weight.dtype), None, None, None, None
+
+
+def vocab_parallel_logprob(hidden, weight, labels, tp: TPContext, temperature: float = 1.0, chunk: int = 4096):
+    if hidden.is_cuda and hidden.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
+        return _VocabParallelLogprobChunked.apply(hidden.contiguous(), weight, labels.clamp_min(0), tp.comm, temperature, chunk)
     return _VocabParallelLogprob.apply(hidden, weight, labels.clamp_min(0), tp.comm, temperature)
 
 
