@@ -321,7 +321,9 @@ def main():
         line = {
             'metric': ('train tokens/s/box Qwen3-30B-A3B EP LoRA SFT' if moe else 'train tokens/s/box Qwen3-8B FSDP2 (+Ulysses SP) full-parameter SFT'), 'value': value, 'unit': 'tokens/s',
             'n_gpus': world, 'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': ms / args.steps, 'higher_is_better': True,
-            'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic (uniform token ids, packed docs U[512,8192], random-init weights)',
+            'scaling': 'weak', 'vs_baseline': None, 'dtype': 'bf16',
+            'data': (f'synthetic (uniform token ids, {args.seqs_per_gpu} full sequences of {args.seq_len} tokens per GPU, random-init weights)' if moe
+                     else 'synthetic (uniform token ids, packed docs U[512,8192], random-init weights)'),
             'impl': 'ours',
             'config': {'model': ('Qwen3-30B-A3B architecture, LoRA r=16' if moe else 'Qwen3-8B architecture') if args.layers is None else f'INVALID-debug-{args.layers}-layers',
                        'global_batch': args.seqs_per_gpu * world, 'seq_len': args.seq_len,
