@@ -159,8 +159,7 @@ class MegatronModel(TwinkleModel):
     # ------------------------------------------------------------ expert parallel
     def _apply_expert_parallel(self, mesh: DeviceMesh, backend: str) -> None:
         """Experts split over ``ep`` consecutive data-parallel ranks (same tp / pp / cp coordinates); attention and router
-        stay as they are (reference ``megatron/strategy/megatron.py:90-107``: ``expert_model_parallel_size``; expert
-        tensor parallelism is not built — experts are whole on a rank).  A rank's expert tensors are shared with every rank
+        stay as they are (reference ``megatron/strategy/megatron.py:90-107``: ``expert_model_parallel_size``).  A rank's expert tensors are shared with every rank
         that holds the same experts of the same layers: the other data-parallel blocks, the context-parallel peers and,
         under sequence parallelism, the tensor-parallel peers (they route different tokens); gradients are summed over
         exactly that set.  With expert tensor parallelism the tensor-parallel peers hold different slices of the same
@@ -778,6 +777,9 @@ class MultiLoraMegatronModel(MegatronModel):
         from .multi_lora import MultiLora
         self.max_length = max_length
         seed = kwargs.get('seed', 0)
+        if self.etp_size > 1:
+            # expert pools would follow the expert shards (B sliced, A replicated with partial gradients): not wired up
+            raise NotImplementedError('multi-LoRA on the tensor / pipeline backend does not combine with expert tensor parallelism (use etp_size=1)')
         self.pools = [MultiLora(m, max_loras, max_r, seed=seed * 1000 + self.pp_rank * 16 + c) for c, m in enumerate(self.chunks)]
         self._sync_pools()
         self.optimizer_groups = {}
