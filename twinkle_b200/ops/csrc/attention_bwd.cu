@@ -244,7 +244,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           float pv[4], dv[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            float pr = exp2f(__uint_as_float(s[i + e]) * p.scale_log2 - ls[e]);
+            float pr = fast_exp2(__uint_as_float(s[i + e]) * p.scale_log2 - ls[e]);
             if (diag && (qb0 + c * 32 + i + e + q_off < kv_pos)) pr = 0.f;
             pv[e] = pr;
             dv[e] = pr * (__uint_as_float(dp[i + e]) - ds[e]);
@@ -457,7 +457,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           float dv[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            float pr = exp2f(__uint_as_float(s[i + e]) * p.scale_log2 - lse2);
+            float pr = fast_exp2(__uint_as_float(s[i + e]) * p.scale_log2 - lse2);
             if (edge) {
               const int kv_pos = kvb + c * 32 + i + e;
               if (kv_pos >= kv_len || (p.causal && kv_pos > q_pos + q_off)) pr = 0.f;

@@ -235,7 +235,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = exp2f(sc[c * 32 + i] - m_used), p1 = exp2f(sc[c * 32 + i + 1] - m_used);
+          const float p0 = fast_exp2(sc[c * 32 + i] - m_used), p1 = fast_exp2(sc[c * 32 + i + 1] - m_used);
           // the sum uses the bf16-rounded values so that numerator and denominator match
           const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
           l_sum += __low2float(pb) + __high2float(pb);

@@ -192,6 +192,14 @@ __device__ __forceinline__ float2 unpack_bf16(uint32_t v) {
   return __bfloat1622float2(b);
 }
 
+// 2^x on the special-function unit in one instruction (`exp2f` adds range handling around it: several instructions per
+// value in loops that are bound by issue slots).  2^(−inf) = +0, results below the normal range flush to zero.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

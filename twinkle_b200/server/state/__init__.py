@@ -172,7 +172,7 @@ class FileBackend(StateBackend):
         self._txn(lambda doc: (doc.update(data={}, exp={}), True))
 
 
-class RedisBackend(StateBackend):  # pragma: no cover - needs the optional redis package and a server
+class RedisBackend(StateBackend):
     MAX_RETRIES = 64
 
     def __init__(self, url: str, prefix: str = 'twinkle'):
