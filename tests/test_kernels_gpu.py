@@ -226,6 +226,17 @@ def test_swiglu_adamw_sumsq(E):
         ref.adamw_step(mr, ear, esr, gr, None, 1e-3, 0.9, 0.999, 1e-8, 0.01, step, 0.5)
     assert rel(m, mr) < 1e-5 and rel(out, mr) < 4e-3
     assert abs(float(ops.sumsq(gr)) / float(gr.float().pow(2).sum()) - 1) < 1e-4
+    # a length that leaves a tail after the 4-element vectors, and views that start off the 16-byte grid (scalar path)
+    for lo, hi in ((0, 100003), (1, 100004)):
+        a = [t[lo:hi].clone() if lo == 0 else t[lo:hi] for t in (m0.clone(), torch.zeros(n, device='cuda'), torch.zeros(n, device='cuda'))]
+        b = [t[lo:hi].clone() for t in (m0, torch.zeros(n, device='cuda'), torch.zeros(n, device='cuda'))]
+        g32 = torch.randn(n, device='cuda')[lo:hi]
+        o32 = torch.empty(n, device='cuda')[lo:hi]
+        ops.adamw_step(a[0], a[1], a[2], g32, o32, 1e-3, 0.9, 0.999, 1e-8, 0.01, 1, 1.0)
+        ref.adamw_step(b[0], b[1], b[2], g32.clone(), None, 1e-3, 0.9, 0.999, 1e-8, 0.01, 1, 1.0)
+        assert rel(a[0], b[0]) < 1e-5 and rel(a[1], b[1]) < 1e-5 and rel(a[2], b[2]) < 1e-5 and torch.equal(o32, a[0])
+        assert abs(float(ops.sumsq(g32)) / float(g32.pow(2).sum()) - 1) < 1e-4
+        assert abs(float(ops.sumsq(gr[lo:hi])) / float(gr[lo:hi].float().pow(2).sum()) - 1) < 1e-4
 
 
 @pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32])

@@ -692,18 +692,53 @@ torch::Tensor geglu_bwd(const torch::Tensor& gy, const torch::Tensor& gu) { retu
 // fp32 master/moments; gradient fp32 or bf16, multiplied by grad_scale on read;
 // optional bf16 (or fp32) working copy written in the same pass.
 template <typename GradT, typename OutT>
-__global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v, const GradT* __restrict__ g,
-                             OutT* __restrict__ out, long n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
-                             float gscale) {
-  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long>(gridDim.x) * blockDim.x) {
+__device__ __forceinline__ void adamw_one(float& pi, float& mi, float& vi, float gi, float lr_wd, float b1, float b2, float eps,
+                                          float step_size, float inv_sqrt_bc2) {
+  pi *= lr_wd;
+  mi = b1 * mi + (1.f - b1) * gi;
+  vi = b2 * vi + (1.f - b2) * gi * gi;
+  const float denom = sqrtf(vi) * inv_sqrt_bc2 + eps;
+  pi -= step_size * __fdividef(mi, denom);
+}
+
+// Four elements per thread and iteration: 16-byte loads / stores of the fp32 state, 8- or 16-byte ones of the gradient and
+// the working copy.  `vec` says that every pointer is 16-byte (bf16: 8-byte) aligned; the tail and unaligned calls take
+// the scalar path.
+template <typename GradT, typename OutT>
+__global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
+                                                    const GradT* __restrict__ g, OutT* __restrict__ out, long n, float lr, float b1,
+                                                    float b2, float eps, float wd, float bc1, float bc2, float gscale, int vec) {
+  const float lr_wd = 1.f - lr * wd, step_size = lr / bc1, inv_sqrt_bc2 = 1.f / sqrtf(bc2);
+  const long tid = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x, nthreads = static_cast<long>(gridDim.x) * blockDim.x;
+  const long n4 = vec ? (n >> 2) : 0;
+  for (long q = tid; q < n4; q += nthreads) {
+    float4 pp = reinterpret_cast<float4*>(p)[q], mm = reinterpret_cast<float4*>(m)[q], vv = reinterpret_cast<float4*>(v)[q];
+    float gg[4];
+    if constexpr (std::is_same<GradT, float>::value) {
+      const float4 t = reinterpret_cast<const float4*>(g)[q];
+      gg[0] = t.x; gg[1] = t.y; gg[2] = t.z; gg[3] = t.w;
+    } else {
+      const uint2 t = reinterpret_cast<const uint2*>(g)[q];
+      const float2 a = unpack_bf16(t.x), b = unpack_bf16(t.y);
+      gg[0] = a.x; gg[1] = a.y; gg[2] = b.x; gg[3] = b.y;
+    }
+    adamw_one<GradT, OutT>(pp.x, mm.x, vv.x, gg[0] * gscale, lr_wd, b1, b2, eps, step_size, inv_sqrt_bc2);
+    adamw_one<GradT, OutT>(pp.y, mm.y, vv.y, gg[1] * gscale, lr_wd, b1, b2, eps, step_size, inv_sqrt_bc2);
+    adamw_one<GradT, OutT>(pp.z, mm.z, vv.z, gg[2] * gscale, lr_wd, b1, b2, eps, step_size, inv_sqrt_bc2);
+    adamw_one<GradT, OutT>(pp.w, mm.w, vv.w, gg[3] * gscale, lr_wd, b1, b2, eps, step_size, inv_sqrt_bc2);
+    reinterpret_cast<float4*>(p)[q] = pp;
+    reinterpret_cast<float4*>(m)[q] = mm;
+    reinterpret_cast<float4*>(v)[q] = vv;
+    if (out != nullptr) {
+      if constexpr (std::is_same<OutT, float>::value) reinterpret_cast<float4*>(out)[q] = pp;
+      else reinterpret_cast<uint2*>(out)[q] = make_uint2(pack_bf16(pp.x, pp.y), pack_bf16(pp.z, pp.w));
+    }
+  }
+  for (long i = n4 * 4 + tid; i < n; i += nthreads) {
     float gi;
     if constexpr (std::is_same<GradT, float>::value) gi = g[i]; else gi = __bfloat162float(g[i]);
-    gi *= gscale;
-    float pi = p[i] * (1.f - lr * wd);
-    const float mi = b1 * m[i] + (1.f - b1) * gi;
-    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
-    const float denom = sqrtf(vi / bc2) + eps;
-    pi -= lr * (mi / bc1) / denom;
+    float pi = p[i], mi = m[i], vi = v[i];
+    adamw_one<GradT, OutT>(pi, mi, vi, gi * gscale, lr_wd, b1, b2, eps, step_size, inv_sqrt_bc2);
     p[i] = pi; m[i] = mi; v[i] = vi;
     if (out != nullptr) {
       if constexpr (std::is_same<OutT, float>::value) out[i] = pi; else out[i] = __float2bfloat16(pi);
@@ -721,7 +756,7 @@ void adamw_step(torch::Tensor master, torch::Tensor exp_avg, torch::Tensor exp_a
   c10::cuda::CUDAGuard guard(master.device());
   const float bc1 = 1.f - static_cast<float>(std::pow(b1, static_cast<double>(step)));
   const float bc2 = 1.f - static_cast<float>(std::pow(b2, static_cast<double>(step)));
-  int blocks = static_cast<int>(std::min<long>((n + 255) / 256, num_sms() * 16L));
+  int blocks = static_cast<int>(std::min<long>((n / 4 + 255) / 256 + 1, num_sms() * 8L));
   auto stream = at::cuda::getCurrentCUDAStream();
   bf16* out_bf = nullptr;
   float* out_f = nullptr;
@@ -731,9 +766,12 @@ void adamw_step(torch::Tensor master, torch::Tensor exp_avg, torch::Tensor exp_a
     else if (out->scalar_type() == torch::kFloat32) { if (out->data_ptr() != master.data_ptr()) out_f = out->data_ptr<float>(); }
     else TORCH_CHECK(false, "out must be bf16 or fp32");
   }
+  auto al = [](const void* q, size_t a) { return q == nullptr || reinterpret_cast<uintptr_t>(q) % a == 0; };
+  const int vec = (al(master.data_ptr(), 16) && al(exp_avg.data_ptr(), 16) && al(exp_avg_sq.data_ptr(), 16) &&
+                   al(grad.data_ptr(), grad.scalar_type() == torch::kFloat32 ? 16 : 8) && al(out_bf, 8) && al(out_f, 16)) ? 1 : 0;
 #define TK_ADAM(GT, OT, OP)                                                                                                     \
   adamw_kernel<GT, OT><<<blocks, 256, 0, stream>>>(master.data_ptr<float>(), exp_avg.data_ptr<float>(), exp_avg_sq.data_ptr<float>(), \
-      reinterpret_cast<const GT*>(grad.data_ptr()), OP, n, (float)lr, (float)b1, (float)b2, (float)eps, (float)wd, bc1, bc2, (float)gscale)
+      reinterpret_cast<const GT*>(grad.data_ptr()), OP, n, (float)lr, (float)b1, (float)b2, (float)eps, (float)wd, bc1, bc2, (float)gscale, vec)
   if (grad.scalar_type() == torch::kFloat32) {
     if (out_f) TK_ADAM(float, float, out_f); else TK_ADAM(float, bf16, out_bf);
   } else if (grad.scalar_type() == torch::kBFloat16) {
@@ -750,7 +788,20 @@ void adamw_step(torch::Tensor master, torch::Tensor exp_avg, torch::Tensor exp_a
 template <typename T>
 __global__ void sumsq_kernel(const T* __restrict__ x, long n, float* __restrict__ out) {
   float acc = 0.f;
-  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n; i += static_cast<long>(gridDim.x) * blockDim.x) {
+  const long tid = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x, nthreads = static_cast<long>(gridDim.x) * blockDim.x;
+  constexpr int VEC = 16 / sizeof(T);
+  const long nv = (reinterpret_cast<uintptr_t>(x) % 16 == 0) ? n / VEC : 0;    // 16-byte loads when the base allows it
+  for (long q = tid; q < nv; q += nthreads) {
+    const uint4 u = reinterpret_cast<const uint4*>(x)[q];
+    if constexpr (std::is_same<T, float>::value) {
+      const float a = __uint_as_float(u.x), b = __uint_as_float(u.y), c = __uint_as_float(u.z), d = __uint_as_float(u.w);
+      acc += a * a + b * b + c * c + d * d;
+    } else {
+      const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+      acc += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y + c.x * c.x + c.y * c.y + d.x * d.x + d.y * d.y;
+    }
+  }
+  for (long i = nv * VEC + tid; i < n; i += nthreads) {
     float v;
     if constexpr (std::is_same<T, float>::value) v = x[i]; else v = __bfloat162float(x[i]);
     acc += v * v;
