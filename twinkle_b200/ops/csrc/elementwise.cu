@@ -693,10 +693,11 @@ torch::Tensor geglu_bwd(const torch::Tensor& gy, const torch::Tensor& gu) { retu
 // optional bf16 (or fp32) working copy written in the same pass.
 template <typename GradT, typename OutT>
 __device__ __forceinline__ void adamw_one(float& pi, float& mi, float& vi, float gi, float lr_wd, float b1, float b2, float eps,
-                                          float step_size, float inv_sqrt_bc2) {
+                                          float step_size, float inv_sqrt_bc2, float omb1, float omb2) {
+  // omb1 / omb2 = 1 − β formed in double on the host: 1.f − 0.999f is off by 5e-5 relative
   pi *= lr_wd;
-  mi = b1 * mi + (1.f - b1) * gi;
-  vi = b2 * vi + (1.f - b2) * gi * gi;
+  mi = b1 * mi + omb1 * gi;
+  vi = b2 * vi + omb2 * (gi * gi);
   const float denom = sqrtf(vi) * inv_sqrt_bc2 + eps;
   pi -= step_size * __fdividef(mi, denom);
 }
@@ -707,7 +708,8 @@ __device__ __forceinline__ void adamw_one(float& pi, float& mi, float& vi, float
 template <typename GradT, typename OutT>
 __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
                                                     const GradT* __restrict__ g, OutT* __restrict__ out, long n, float lr, float b1,
-                                                    float b2, float eps, float wd, float bc1, float bc2, float gscale, int vec) {
+                                                    float b2, float eps, float wd, float bc1, float bc2, float gscale, int vec, float omb1,
+                                                    float omb2) {
   const float lr_wd = 1.f - lr * wd, step_size = lr / bc1, inv_sqrt_bc2 = 1.f / sqrtf(bc2);
   const long tid = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x, nthreads = static_cast<long>(gridDim.x) * blockDim.x;
   const long n4 = vec ? (n >> 2) : 0;
@@ -722,10 +724,10 @@ __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, float
       const float2 a = unpack_bf16(t.x), b = unpack_bf16(t.y);
       gg[0] = a.x; gg[1] = a.y; gg[2] = b.x; gg[3] = b.y;
     }
-    adamw_one<GradT, OutT>(pp.x, mm.x, vv.x, gg[0] * gscale, lr_wd, b1, b2, eps, step_size, inv_sqrt_bc2);
-    adamw_one<GradT, OutT>(pp.y, mm.y, vv.y, gg[1] * gscale, lr_wd, b1, b2, eps, step_size, inv_sqrt_bc2);
-    adamw_one<GradT, OutT>(pp.z, mm.z, vv.z, gg[2] * gscale, lr_wd, b1, b2, eps, step_size, inv_sqrt_bc2);
-    adamw_one<GradT, OutT>(pp.w, mm.w, vv.w, gg[3] * gscale, lr_wd, b1, b2, eps, step_size, inv_sqrt_bc2);
+    adamw_one<GradT, OutT>(pp.x, mm.x, vv.x, gg[0] * gscale, lr_wd, b1, b2, eps, step_size, inv_sqrt_bc2, omb1, omb2);
+    adamw_one<GradT, OutT>(pp.y, mm.y, vv.y, gg[1] * gscale, lr_wd, b1, b2, eps, step_size, inv_sqrt_bc2, omb1, omb2);
+    adamw_one<GradT, OutT>(pp.z, mm.z, vv.z, gg[2] * gscale, lr_wd, b1, b2, eps, step_size, inv_sqrt_bc2, omb1, omb2);
+    adamw_one<GradT, OutT>(pp.w, mm.w, vv.w, gg[3] * gscale, lr_wd, b1, b2, eps, step_size, inv_sqrt_bc2, omb1, omb2);
     reinterpret_cast<float4*>(p)[q] = pp;
     reinterpret_cast<float4*>(m)[q] = mm;
     reinterpret_cast<float4*>(v)[q] = vv;
@@ -738,7 +740,7 @@ __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, float
     float gi;
     if constexpr (std::is_same<GradT, float>::value) gi = g[i]; else gi = __bfloat162float(g[i]);
     float pi = p[i], mi = m[i], vi = v[i];
-    adamw_one<GradT, OutT>(pi, mi, vi, gi * gscale, lr_wd, b1, b2, eps, step_size, inv_sqrt_bc2);
+    adamw_one<GradT, OutT>(pi, mi, vi, gi * gscale, lr_wd, b1, b2, eps, step_size, inv_sqrt_bc2, omb1, omb2);
     p[i] = pi; m[i] = mi; v[i] = vi;
     if (out != nullptr) {
       if constexpr (std::is_same<OutT, float>::value) out[i] = pi; else out[i] = __float2bfloat16(pi);
@@ -754,8 +756,8 @@ void adamw_step(torch::Tensor master, torch::Tensor exp_avg, torch::Tensor exp_a
   TORCH_CHECK(grad.numel() == n && exp_avg.numel() == n && exp_avg_sq.numel() == n && grad.is_contiguous(), "size mismatch");
   if (n == 0) return;
   c10::cuda::CUDAGuard guard(master.device());
-  const float bc1 = 1.f - static_cast<float>(std::pow(b1, static_cast<double>(step)));
-  const float bc2 = 1.f - static_cast<float>(std::pow(b2, static_cast<double>(step)));
+  const float bc1 = static_cast<float>(1.0 - std::pow(b1, static_cast<double>(step)));   // in double: 1 − β^t cancels badly in fp32
+  const float bc2 = static_cast<float>(1.0 - std::pow(b2, static_cast<double>(step)));
   int blocks = static_cast<int>(std::min<long>((n / 4 + 255) / 256 + 1, num_sms() * 8L));
   auto stream = at::cuda::getCurrentCUDAStream();
   bf16* out_bf = nullptr;
@@ -771,7 +773,8 @@ void adamw_step(torch::Tensor master, torch::Tensor exp_avg, torch::Tensor exp_a
                    al(grad.data_ptr(), grad.scalar_type() == torch::kFloat32 ? 16 : 8) && al(out_bf, 8) && al(out_f, 16)) ? 1 : 0;
 #define TK_ADAM(GT, OT, OP)                                                                                                     \
   adamw_kernel<GT, OT><<<blocks, 256, 0, stream>>>(master.data_ptr<float>(), exp_avg.data_ptr<float>(), exp_avg_sq.data_ptr<float>(), \
-      reinterpret_cast<const GT*>(grad.data_ptr()), OP, n, (float)lr, (float)b1, (float)b2, (float)eps, (float)wd, bc1, bc2, (float)gscale, vec)
+      reinterpret_cast<const GT*>(grad.data_ptr()), OP, n, (float)lr, (float)b1, (float)b2, (float)eps, (float)wd, bc1, bc2, (float)gscale, vec, \
+      (float)(1.0 - b1), (float)(1.0 - b2))
   if (grad.scalar_type() == torch::kFloat32) {
     if (out_f) TK_ADAM(float, float, out_f); else TK_ADAM(float, bf16, out_bf);
   } else if (grad.scalar_type() == torch::kBFloat16) {
