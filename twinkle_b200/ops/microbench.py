@@ -149,6 +149,34 @@ def make(op: str, a) -> Tuple[Callable[[], None], float, float]:
         lg = torch.randn(a.batch, a.vocab, device=dev)
         seeds = torch.arange(a.batch, device=dev, dtype=torch.int64)
         return (lambda: ops.sample_tokens(lg, 0.8, 50, 0.95, seeds=seeds)), 0.0, 4.0 * a.batch * a.vocab
+    if op in ('expert_lora', 'expert_lora_split', 'expert_base'):
+        # one expert projection of the Qwen3-30B-A3B block: rows = tokens x top-8 over 128 experts (128-row aligned
+        # segments), 2048 -> 1536, rank-16 LoRA pair per expert.  expert_base: the grouped GEMM alone; expert_lora: the
+        # low-rank term as a second operand pair of the same GEMM; expert_lora_split: shrink, base, then a separate
+        # rank-16 GEMM accumulating into the output
+        Eg, K, N, r = 128, 2048, 1536, 16
+        per = (a.tokens * 8 // Eg + 127) // 128 * 128
+        rows = per * Eg
+        off = torch.arange(0, Eg + 1, device=dev, dtype=torch.int32) * per
+        x = torch.randn(rows, K, device=dev, dtype=bf)
+        w = torch.randn(Eg, N, K, device=dev, dtype=bf) * 0.02
+        la = torch.randn(Eg, r, K, device=dev, dtype=bf) * 0.02
+        lb = torch.randn(Eg, N, r, device=dev, dtype=bf) * 0.02
+        flops = 2.0 * rows * K * N + (0.0 if op == 'expert_base' else 2.0 * rows * r * (K + N))
+        byts = 2.0 * (rows * K + rows * N + Eg * N * K)
+        if op == 'expert_base':
+            return (lambda: E.grouped_gemm(x, w, off, 'nt', None)), flops, byts
+        if op == 'expert_lora':
+            def f():
+                h = E.grouped_gemm(x, la, off, 'nt', None)
+                E.grouped_gemm(x, w, off, 'nt', None, None, False, h, lb)
+            return f, flops, byts
+
+        def f2():
+            y = E.grouped_gemm(x, w, off, 'nt', None)
+            h = E.grouped_gemm(x, la, off, 'nt', None)
+            E.grouped_gemm(h, lb, off, 'nt', None, y, True)
+        return f2, flops, byts
     if op in ('gdn', 'gdn_torch'):
         # Gated DeltaNet forward: 16 key / 32 value heads of 128, packed documents of --seq tokens
         T, hk, hv, d = a.tokens, 16, 32, 128
