@@ -25,6 +25,13 @@ def _cases():
         'seed_oss': (lambda: T.SeedOssConfig(head_dim=32, **COMMON), 'SeedOssForCausalLM'),
         'qwen3_moe': (lambda: T.Qwen3MoeConfig(head_dim=32, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, norm_topk_prob=True,
                                                decoder_sparse_step=1, mlp_only_layers=[], **COMMON), 'Qwen3MoeForCausalLM'),
+        # hybrid stack: Gated DeltaNet layers + full attention with an output gate, partial rotary and "1 + w" norms
+        'qwen3_5': (lambda: T.Qwen3_5TextConfig(head_dim=32, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=16,
+                                                linear_value_head_dim=16, linear_conv_kernel_dim=4, tie_word_embeddings=False,
+                                                layer_types=['linear_attention', 'full_attention', 'linear_attention', 'full_attention'],
+                                                **{**{k: v for k, v in COMMON.items() if k != 'rope_theta'}, 'num_hidden_layers': 4},
+                                                rope_parameters={'rope_type': 'default', 'rope_theta': 10000.0, 'partial_rotary_factor': 0.25}),
+                    'Qwen3_5ForCausalLM'),
         'qwen2_moe_shared': (lambda: T.Qwen2MoeConfig(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=96,
                                                       norm_topk_prob=False, decoder_sparse_step=1, mlp_only_layers=[], **COMMON), 'Qwen2MoeForCausalLM'),
     }
@@ -66,7 +73,7 @@ def test_hf_checkpoint_gives_the_same_logits_here(name, tmp_path):
     assert torch.allclose(got, want, atol=2e-5), float((got - want).abs().max())
 
 
-@pytest.mark.parametrize('name', ['qwen3', 'qwen3_moe', 'mixtral', 'qwen2_moe_shared'])
+@pytest.mark.parametrize('name', ['qwen3', 'qwen3_moe', 'mixtral', 'qwen2_moe_shared', 'qwen3_5'])
 def test_checkpoint_saved_here_loads_in_transformers(name, tmp_path):
     hf = _hf_model(name)
     hf.save_pretrained(str(tmp_path / 'hf'), safe_serialization=True)

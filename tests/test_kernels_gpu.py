@@ -491,6 +491,52 @@ def test_sharded_engine_training_matches_cpu(E):
     assert E.read_and_clear_error() == 0
 
 
+def test_qwen3_5_stack_trains_on_gpu_like_on_cpu(E):
+    """The Qwen3.5 text stack on the GPU (Gated DeltaNet kernels with 128-wide key heads, gated full attention with
+    partial rotary on the PyTorch attention path, LoRA over the four-part q|k|v|gate projection) against fp32 on the CPU."""
+    from twinkle_b200.model import MultiLoraTransformersModel, TransformersModel
+    from twinkle_b200.models import preset
+    from twinkle_b200.utils.device_mesh import DeviceMesh
+    cfg = preset('tiny-qwen3.5', hidden_size=512, intermediate_size=1024, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+                 linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=128, linear_value_head_dim=128, vocab_size=2048)
+    g = torch.Generator().manual_seed(11)
+    feats = []
+    for n in (161, 97, 130):
+        ids = torch.randint(0, cfg.vocab_size, (n, ), generator=g)
+        feats.append({'input_ids': ids[:-1], 'labels': ids[1:]})
+
+    def curve(device):
+        m = TransformersModel(config=cfg, device_mesh=DeviceMesh.from_sizes(dp_size=1), seed=0, device=device)
+        m.set_optimizer('AdamW', lr=1e-3)
+        out = []
+        for _ in range(3):
+            o = m.forward_backward(inputs=feats, micro_batch_size=3)
+            out.append((float(o['loss']), float(m.clip_grad_and_step(max_grad_norm=1.0))))
+        return out
+
+    cpu, gpu = curve('cpu'), curve('cuda')
+    assert cpu[0][0] > cpu[-1][0]
+    for (a, na), (b, nb) in zip(cpu, gpu):
+        assert abs(a - b) < 4e-2 and abs(na - nb) < 8e-2 * max(na, 1.0), (cpu, gpu)
+
+    def lora_curve(device):
+        m = MultiLoraTransformersModel(config=cfg, device_mesh=DeviceMesh.from_sizes(dp_size=1), seed=0, device=device, max_loras=2, max_r=8)
+        m.add_adapter_to_model('a', {'r': 8, 'lora_alpha': 16, 'target_modules': 'all-linear'})
+        m.set_optimizer('AdamW', lr=5e-3, adapter_name='a')
+        out = []
+        for _ in range(3):
+            o = m.forward_backward(inputs=feats, micro_batch_size=3, adapter_name='a')
+            m.clip_grad_and_step(max_grad_norm=1.0, adapter_name='a')
+            out.append(float(o['loss']))
+        return out
+
+    lc, lg = lora_curve('cpu'), lora_curve('cuda')
+    assert lc[-1] < lc[0]
+    for a, b in zip(lc, lg):
+        assert abs(a - b) < 4e-2, (lc, lg)
+    assert E.read_and_clear_error() == 0
+
+
 def test_gated_delta_rule_and_conv_kernels(E):
     """Linear-attention kernels against the fp32 recurrence / convolution on PyTorch: packed sequences (one of them a
     single token, one empty), grouped heads, both key widths, state hand-over to a second call, gradients through the
@@ -511,8 +557,9 @@ def test_gated_delta_rule_and_conv_kernels(E):
         o, fin = ops.gated_delta_rule_varlen(q, k, v, g, beta, cu, return_states=True)
         assert fin.shape == (4, hv, dk, dv) and float(fin[2].abs().max()) == 0.0
         rep = hv // hk
-        qn = F.normalize(q.float(), dim=-1).repeat_interleave(rep, 1)
-        kn = F.normalize(k.float(), dim=-1).repeat_interleave(rep, 1)
+        from twinkle_b200.models.linear_attention import l2norm
+        qn = l2norm(q).repeat_interleave(rep, 1)
+        kn = l2norm(k).repeat_interleave(rep, 1)
         b = cu.tolist()
         for i, (a_, b_) in enumerate(zip(b[:-1], b[1:])):
             if b_ == a_:

@@ -293,7 +293,7 @@ class MegatronModel(TwinkleModel):
                     pass
             else:
                 h = x
-            cos, sin = ops.rope_tables(batch.position_ids, self.config.head_dim, self.config.rope_theta, self.config.rope_scaling)
+            cos, sin = ops.rope_tables(batch.position_ids, self.config.rotary_dim, self.config.rope_theta, self.config.rope_scaling)
             if self.recompute is not None and torch.is_grad_enabled():
                 from torch.utils.checkpoint import checkpoint
                 for layer in m.layers:

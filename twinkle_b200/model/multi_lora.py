@@ -68,6 +68,19 @@ class _Tenant:
     target: TargetFilter
 
 
+def _interleave_gate(bq: torch.Tensor, bg: torch.Tensor, d: int) -> torch.Tensor:
+    """Rows of the query part and of the output-gate part ``[H·d, r]`` each → the checkpoint's q_proj row order
+    ``[head 0: query (d) | gate (d), head 1: …]``."""
+    h = bq.shape[0] // d
+    return torch.cat([bq.reshape(h, d, -1), bg.reshape(h, d, -1)], 1).reshape(2 * h * d, -1)
+
+
+def _split_gate(b: torch.Tensor, d: int):
+    h = b.shape[0] // (2 * d)
+    x = b.reshape(h, 2 * d, -1)
+    return x[:, :d].reshape(h * d, -1), x[:, d:].reshape(h * d, -1)
+
+
 class MultiLora:
 
     def __init__(self, model: DecoderModel, max_loras: int = 5, max_r: int = 32, expert_lora: bool = True, seed: Optional[int] = None):
@@ -175,7 +188,8 @@ class MultiLora:
                 for pname, _ in m.parts:
                     full = f'{prefix}.{pname}' if prefix else pname
                     if t.target.matches(full, pname):
-                        out.append((f'{mod_name}.lora_A.{pname}', m.lora_A[pname], t.slot))
+                        if not (pname == 'q_gate' and m.lora_A[pname] is m.lora_A.get('q_proj')):   # the gate shares q_proj's A: listed once
+                            out.append((f'{mod_name}.lora_A.{pname}', m.lora_A[pname], t.slot))
                         out.append((f'{mod_name}.lora_B.{pname}', m.lora_B[pname], t.slot))
             else:
                 for which in ('gate_up', 'down'):
@@ -196,10 +210,13 @@ class MultiLora:
             if isinstance(m, Linear):
                 for pname, _ in m.parts:
                     full = f'{prefix}.{pname}' if prefix else pname
-                    if not t.target.matches(full, pname):
-                        continue
+                    if pname == 'q_gate' or not t.target.matches(full, pname):
+                        continue            # the gate's rows travel inside q_proj's B (below)
+                    b = m.lora_B[pname][t.slot, :, :r].detach().clone()
+                    if pname == 'q_proj' and m.gate_head_dim:
+                        b = _interleave_gate(b, m.lora_B['q_gate'][t.slot, :, :r].detach(), m.gate_head_dim)
                     sd[lora_internal_to_peft(mod_name, pname, 'A')] = m.lora_A[pname][t.slot, :r].detach().clone()
-                    sd[lora_internal_to_peft(mod_name, pname, 'B')] = m.lora_B[pname][t.slot, :, :r].detach().clone()
+                    sd[lora_internal_to_peft(mod_name, pname, 'B')] = b
             else:
                 for which in ('gate_up', 'down'):
                     sd[lora_expert_to_peft(mod_name, which, 'A')] = m.lora[which + '_A'][t.slot, :, :r].detach().clone()
@@ -215,9 +232,13 @@ class MultiLora:
             if isinstance(m, Linear):
                 for pname, _ in m.parts:
                     ka, kb = lora_internal_to_peft(mod_name, pname, 'A'), lora_internal_to_peft(mod_name, pname, 'B')
-                    if ka in sd and kb in sd:
+                    if ka in sd and kb in sd and pname != 'q_gate':
                         a, b = sd[ka], sd[kb]
                         r = a.shape[0]
+                        if pname == 'q_proj' and m.gate_head_dim:      # [query | gate] rows interleaved per head → two parts
+                            b, bg = _split_gate(b, m.gate_head_dim)
+                            m.lora_B['q_gate'][t.slot].zero_()
+                            m.lora_B['q_gate'][t.slot, :, :r].copy_(bg)
                         m.lora_A[pname][t.slot].zero_()
                         m.lora_B[pname][t.slot].zero_()
                         m.lora_A[pname][t.slot, :r].copy_(a)

@@ -48,9 +48,21 @@ def _family(name: str, cfg: DecoderConfig) -> str:
     return name
 
 
+def _split_gdn(cfg: DecoderConfig) -> bool:
+    """Whether the linear-attention input projections are written the Qwen3.5 way (``in_proj_qkv`` / ``in_proj_z`` /
+    ``in_proj_b`` / ``in_proj_a``) rather than as this package's two fused tensors."""
+    return cfg.model_type.startswith('qwen3_5')
+
+
 def _vl(name: str, cfg: DecoderConfig) -> str:
     """Vision-language checkpoints nest the language model: ``model.X`` → ``model.language_model.X``."""
-    return 'model.language_model.' + name[len('model.'):] if cfg.vision and name.startswith('model.') else name
+    return 'model.language_model.' + name[len('model.'):] if _nested(cfg) and name.startswith('model.') else name
+
+
+def _nested(cfg: DecoderConfig) -> bool:
+    """Checkpoints whose decoder sits under ``model.language_model``: the vision-language families and Qwen3.5 (its text-only
+    class writes the same names as the full model)."""
+    return bool(cfg.vision) or cfg.model_type.startswith('qwen3_5')
 
 
 def internal_to_hf(name: str, tensor: torch.Tensor, cfg: DecoderConfig) -> List[Tuple[str, torch.Tensor]]:
@@ -73,9 +85,22 @@ def _internal_to_hf_text(name: str, tensor: torch.Tensor, cfg: DecoderConfig) ->
     i, rest = int(m.group(1)), m.group(2)
     if rest in ('self_attn.qkv_proj.weight', 'self_attn.qkv_proj.bias'):
         kind = rest.rsplit('.', 1)[1]
-        q, k, v = tensor.split([cfg.q_size, cfg.kv_size, cfg.kv_size], dim=0)
+        if cfg.attn_output_gate:
+            # HF keeps query and output gate in one projection, interleaved per head: [head 0: q (D) | gate (D), head 1: …]
+            q, k, v, g = tensor.split([cfg.q_size, cfg.kv_size, cfg.kv_size, cfg.q_size], dim=0)
+            hq, d = cfg.num_attention_heads, cfg.head_dim
+            q = torch.cat([q.reshape(hq, d, *q.shape[1:]), g.reshape(hq, d, *g.shape[1:])], 1).reshape(2 * cfg.q_size, *q.shape[1:])
+        else:
+            q, k, v = tensor.split([cfg.q_size, cfg.kv_size, cfg.kv_size], dim=0)
         return [(_hf_layer(i, f'self_attn.q_proj.{kind}'), q), (_hf_layer(i, f'self_attn.k_proj.{kind}'), k),
                 (_hf_layer(i, f'self_attn.v_proj.{kind}'), v)]
+    if rest == 'self_attn.in_proj_qkvz.weight' and _split_gdn(cfg):     # Qwen3.5 keeps q|k|v and z, and b and a, as separate linears
+        kd, vd = cfg.linear_num_key_heads * cfg.linear_key_head_dim, cfg.linear_num_value_heads * cfg.linear_value_head_dim
+        qkv, z = tensor.split([2 * kd + vd, vd], dim=0)
+        return [(_hf_layer(i, 'linear_attn.in_proj_qkv.weight'), qkv), (_hf_layer(i, 'linear_attn.in_proj_z.weight'), z)]
+    if rest == 'self_attn.in_proj_ba.weight' and _split_gdn(cfg):
+        b, a = tensor.chunk(2, dim=0)
+        return [(_hf_layer(i, 'linear_attn.in_proj_b.weight'), b), (_hf_layer(i, 'linear_attn.in_proj_a.weight'), a)]
     if rest in ('mlp.gate_up_proj.weight', 'mlp.shared_expert.gate_up_proj.weight'):
         g, u = tensor.chunk(2, dim=0)
         pre = rest[:-len('gate_up_proj.weight')]
@@ -117,6 +142,10 @@ def _hf_names_for_text(name: str, cfg: DecoderConfig) -> List[str]:
     if rest.startswith('self_attn.qkv_proj.'):
         kind = rest.rsplit('.', 1)[1]
         return [_hf_layer(i, f'self_attn.{p}_proj.{kind}') for p in 'qkv']
+    if rest == 'self_attn.in_proj_qkvz.weight' and _split_gdn(cfg):
+        return [_hf_layer(i, 'linear_attn.in_proj_qkv.weight'), _hf_layer(i, 'linear_attn.in_proj_z.weight')]
+    if rest == 'self_attn.in_proj_ba.weight' and _split_gdn(cfg):
+        return [_hf_layer(i, 'linear_attn.in_proj_b.weight'), _hf_layer(i, 'linear_attn.in_proj_a.weight')]
     if rest in ('mlp.gate_up_proj.weight', 'mlp.shared_expert.gate_up_proj.weight'):
         pre = rest[:-len('gate_up_proj.weight')]
         return [_hf_layer(i, pre + 'gate_proj.weight'), _hf_layer(i, pre + 'up_proj.weight')]
@@ -144,7 +173,7 @@ def hf_to_internal(name: str, cfg: DecoderConfig, get: Callable[[str], torch.Ten
 
         def get(n: str) -> torch.Tensor:  # noqa: F811
             return plain(_family(n, cfg))
-    if cfg.vision:
+    if _nested(cfg):
         raw = get
 
         def get(n: str) -> torch.Tensor:  # noqa: F811 — older checkpoints keep ``visual.*`` / ``model.layers.*`` at the top level
@@ -178,6 +207,11 @@ def hf_to_internal(name: str, cfg: DecoderConfig, get: Callable[[str], torch.Ten
         lo, hi = expert_range or (0, cfg.num_experts)
         return torch.stack([get(_hf_layer(i, f'mlp.experts.{e}.down_proj.weight')) for e in range(lo, hi)])
     parts = [get(n) for n in hf_names_for(name, cfg)]
+    if rest.startswith('self_attn.qkv_proj.') and cfg.attn_output_gate:
+        hq, d = cfg.num_attention_heads, cfg.head_dim
+        qg = parts[0].reshape(hq, 2 * d, *parts[0].shape[1:])
+        q, g = qg[:, :d].reshape(cfg.q_size, *parts[0].shape[1:]), qg[:, d:].reshape(cfg.q_size, *parts[0].shape[1:])
+        return torch.cat([q, parts[1], parts[2], g], 0)
     if rest == 'self_attn.conv_weight' and parts[0].dim() == 3:
         return parts[0].squeeze(1)
     return parts[0] if len(parts) == 1 else torch.cat(parts, 0)
@@ -195,7 +229,7 @@ def tp_rule(name: str, cfg: DecoderConfig):
         return None
     rest = m.group(2)
     if rest.startswith('self_attn.qkv_proj.'):
-        return ('col', [cfg.q_size, cfg.kv_size, cfg.kv_size])
+        return ('col', [cfg.q_size, cfg.kv_size, cfg.kv_size] + ([cfg.q_size] if cfg.attn_output_gate else []))
     if rest == 'mlp.gate_up_proj.weight':
         half = cfg.intermediate_size
         return ('col', [half, half])

@@ -15,7 +15,8 @@ from typing import List, Any, Dict, Optional
 
 # config.json ``model_type`` values whose layer maths is what ``models/decoder.py`` computes (each checked against transformers)
 SUPPORTED_MODEL_TYPES = frozenset({'llama', 'mistral', 'mixtral', 'qwen2', 'qwen2_moe', 'qwen3', 'qwen3_moe', 'seed_oss', 'qwen2_vl', 'qwen2_vl_text',
-                                   'qwen2_5_vl', 'qwen2_5_vl_text', 'qwen3_vl', 'qwen3_vl_text', 'qwen3_vl_moe', 'qwen3_vl_moe_text'})
+                                   'qwen2_5_vl', 'qwen2_5_vl_text', 'qwen3_vl', 'qwen3_vl_text', 'qwen3_vl_moe', 'qwen3_vl_moe_text',
+                                   'qwen3_5', 'qwen3_5_text'})
 
 
 def _rope_scaling_of(cfg: Dict[str, Any]) -> Optional[Dict[str, Any]]:
@@ -49,6 +50,10 @@ class DecoderConfig:
     qk_norm: bool = True
     attention_bias: bool = False
     rms_norm_offset: float = 0.0  # 1.0 for gemma-style "1 + w"
+    # Qwen3.5 full-attention layers: rotary embedding on the leading ``head_dim * partial_rotary_factor`` dims only, and a
+    # per-head sigmoid gate (a second half of the q projection) on the attention output; their q/k norms are "1 + w" too
+    partial_rotary_factor: float = 1.0
+    attn_output_gate: bool = False
     # MoE (num_experts == 0 → dense)
     num_experts: int = 0
     num_experts_per_tok: int = 8
@@ -107,6 +112,11 @@ class DecoderConfig:
         emb = self.vocab_size * h * (1 if self.tie_word_embeddings else 2)
         return L * per_layer + emb + h
 
+    @property
+    def rotary_dim(self) -> int:
+        """Leading dims of a head that carry the rotary embedding (even; the whole head unless ``partial_rotary_factor`` < 1)."""
+        return self.head_dim if self.partial_rotary_factor >= 1.0 else int(self.head_dim * self.partial_rotary_factor) // 2 * 2
+
     def flops_per_token(self, avg_context: float = 0.0) -> float:
         """Forward+backward matmul FLOPs per token (6·N_active + attention)."""
         h, L = self.hidden_size, self.num_hidden_layers
@@ -136,6 +146,9 @@ class DecoderConfig:
             if vision.get('model_type', top.get('model_type', 'qwen2_vl')) not in ('qwen2_vl', 'qwen2_5_vl', 'qwen3_vl', 'qwen3_vl_moe'):
                 raise NotImplementedError(f"vision tower of type {vision.get('model_type')!r} is not supported (qwen2_vl, qwen2_5_vl and qwen3_vl are)")
         rs_any = cfg.get('rope_scaling') or cfg.get('rope_parameters') or top.get('rope_scaling') or {}
+        q35 = mt.startswith('qwen3_5')
+        if q35 and vision is not None:
+            vision = None        # the language model of a Qwen3.5 checkpoint trains without its tower here (text-only batches)
         heads = cfg.get('num_attention_heads', 32)
         out = cls(
             vocab_size=cfg.get('vocab_size', 151936), hidden_size=cfg.get('hidden_size', 4096),
@@ -150,14 +163,16 @@ class DecoderConfig:
             moe_intermediate_size=cfg.get('moe_intermediate_size', cfg.get('intermediate_size', 768) if mt == 'mixtral' else 768),
             norm_topk_prob=bool(cfg.get('norm_topk_prob', True)), router_aux_loss_coef=float(cfg.get('router_aux_loss_coef', 0.0)),
             shared_expert_intermediate_size=int(cfg.get('shared_expert_intermediate_size', 0) or 0),
-            rms_norm_offset=float(cfg.get('rms_norm_offset', 1.0 if mt.startswith('gemma') else 0.0)),
+            rms_norm_offset=float(cfg.get('rms_norm_offset', 1.0 if (mt.startswith('gemma') or q35) else 0.0)),
+            partial_rotary_factor=float(cfg.get('partial_rotary_factor', (cfg.get('rope_parameters') or {}).get('partial_rotary_factor', 1.0)) or 1.0),
+            attn_output_gate=bool(cfg.get('attn_output_gate', q35)),
             layer_types=list(cfg['layer_types']) if cfg.get('layer_types') and 'linear_attention' in cfg['layer_types'] else None,
             linear_num_key_heads=cfg.get('linear_num_key_heads', 16), linear_num_value_heads=cfg.get('linear_num_value_heads', 32),
             linear_key_head_dim=cfg.get('linear_key_head_dim', 128), linear_value_head_dim=cfg.get('linear_value_head_dim', 128),
             linear_conv_kernel_dim=cfg.get('linear_conv_kernel_dim', 4),
             vision=vision, image_token_id=top.get('image_token_id'), video_token_id=top.get('video_token_id'),
             vision_start_token_id=top.get('vision_start_token_id'), vision_end_token_id=top.get('vision_end_token_id'),
-            mrope_section=list(rs_any['mrope_section']) if isinstance(rs_any, dict) and rs_any.get('mrope_section') else None,
+            mrope_section=list(rs_any['mrope_section']) if isinstance(rs_any, dict) and rs_any.get('mrope_section') and not q35 else None,
             mrope_interleaved=bool(isinstance(rs_any, dict) and rs_any.get('mrope_interleaved')),
             initializer_range=cfg.get('initializer_range', 0.02), model_type=mt,
             torch_dtype=str(cfg.get('torch_dtype', cfg.get('dtype', 'bfloat16'))),
@@ -215,6 +230,14 @@ class DecoderConfig:
             d.update(layer_types=list(self.layer_types), linear_num_key_heads=self.linear_num_key_heads,
                      linear_num_value_heads=self.linear_num_value_heads, linear_key_head_dim=self.linear_key_head_dim,
                      linear_value_head_dim=self.linear_value_head_dim, linear_conv_kernel_dim=self.linear_conv_kernel_dim)
+        if self.model_type.startswith('qwen3_5'):
+            # written as the text model of the family (what ``Qwen3_5ForCausalLM`` loads)
+            d.update(architectures=['Qwen3_5ForCausalLM'], model_type='qwen3_5_text', partial_rotary_factor=self.partial_rotary_factor,
+                     rope_parameters={'rope_type': 'default', 'rope_theta': self.rope_theta, 'partial_rotary_factor': self.partial_rotary_factor},
+                     layer_types=list(self.layer_types or ['full_attention'] * self.num_hidden_layers))
+            d.pop('rms_norm_offset', None)
+        elif self.partial_rotary_factor != 1.0 or self.attn_output_gate:
+            d.update(partial_rotary_factor=self.partial_rotary_factor, attn_output_gate=self.attn_output_gate)
         return d
 
     def save_pretrained(self, path: str) -> None:
@@ -232,6 +255,13 @@ PRESETS: Dict[str, Dict[str, Any]] = {
                         num_key_value_heads=2, head_dim=64, rope_theta=1e4, tie_word_embeddings=True, qk_norm=True, torch_dtype='float32',
                         layer_types=['linear_attention', 'full_attention', 'linear_attention', 'full_attention'], linear_num_key_heads=2,
                         linear_num_value_heads=4, linear_key_head_dim=32, linear_value_head_dim=32),
+    # the Qwen3.5 text stack in small: three Gated DeltaNet layers per full-attention layer, output gate, rotary on a quarter
+    # of the head, "1 + w" norms
+    'tiny-qwen3.5': dict(vocab_size=1024, hidden_size=256, intermediate_size=688, num_hidden_layers=4, num_attention_heads=4,
+                         num_key_value_heads=2, head_dim=64, rope_theta=1e4, tie_word_embeddings=True, qk_norm=True, torch_dtype='float32',
+                         model_type='qwen3_5_text', rms_norm_offset=1.0, partial_rotary_factor=0.25, attn_output_gate=True,
+                         layer_types=['linear_attention', 'linear_attention', 'linear_attention', 'full_attention'], linear_num_key_heads=2,
+                         linear_num_value_heads=4, linear_key_head_dim=32, linear_value_head_dim=32),
     'tiny-moe': dict(vocab_size=1024, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
                      head_dim=64, rope_theta=1e4, tie_word_embeddings=True, num_experts=8, num_experts_per_tok=2,
                      moe_intermediate_size=128, router_aux_loss_coef=1e-3, torch_dtype='float32'),

@@ -57,22 +57,48 @@ class Attention(nn.Module):
         self.cfg, self.layer_idx = cfg, layer_idx
         h, d = cfg.hidden_size, cfg.head_dim
         self.hq, self.hkv, self.d = cfg.num_attention_heads, cfg.num_key_value_heads, d
-        self.qkv_proj = Linear(h, cfg.q_size + 2 * cfg.kv_size, bias=cfg.attention_bias,
-                               parts=[('q_proj', cfg.q_size), ('k_proj', cfg.kv_size), ('v_proj', cfg.kv_size)])
+        # output gate (Qwen3.5, reference HF ``Qwen3_5Attention``): a second q-sized projection whose sigmoid scales the
+        # attention output per head and dim; kept as a fourth part of the fused projection, after q | k | v
+        self.gated = bool(cfg.attn_output_gate)
+        parts = [('q_proj', cfg.q_size), ('k_proj', cfg.kv_size), ('v_proj', cfg.kv_size)] + ([('q_gate', cfg.q_size)] if self.gated else [])
+        self.qkv_proj = Linear(h, sum(n for _, n in parts), bias=cfg.attention_bias, parts=parts)
+        if self.gated:
+            self.qkv_proj.gate_head_dim = d
         self.o_proj = Linear(cfg.q_size, h, bias=False, name='o_proj')
+        # the per-head norms follow the model's norm convention ("1 + w" for Qwen3.5; plain weights have offset 0)
+        self.norm_offset = float(cfg.rms_norm_offset) if cfg.qk_norm else 0.0
         if cfg.qk_norm:
-            self.q_norm = RMSNorm(d, cfg.rms_norm_eps)
-            self.k_norm = RMSNorm(d, cfg.rms_norm_eps)
+            self.q_norm = RMSNorm(d, cfg.rms_norm_eps, self.norm_offset)
+            self.k_norm = RMSNorm(d, cfg.rms_norm_eps, self.norm_offset)
         else:
             self.q_norm = self.k_norm = None
         self.attn_parallel = None  # Ulysses strategy or None
+
+    def heads(self, qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor):
+        """Fused projection output → ``(q [T,Hq,D], k [T,Hkv,D], v [T,Hkv,D], gate [T,Hq·D] | None)`` after the per-head
+        norms and the rotary embedding (head counts are this rank's under tensor parallelism)."""
+        qw = self.q_norm.weight if self.q_norm is not None else None
+        kw = self.k_norm.weight if self.k_norm is not None else None
+        gate = None
+        if self.gated:
+            w = (self.hq + 2 * self.hkv) * self.d
+            qkv, gate = qkv[:, :w], qkv[:, w:]
+        q, k, v = ops.qkv_norm_rope(qkv, qw, kw, cos, sin, self.hq, self.hkv, self.d, self.cfg.rms_norm_eps, self.norm_offset)
+        return q, k, v, gate
+
+    def project_out(self, o: torch.Tensor, gate: Optional[torch.Tensor]) -> torch.Tensor:
+        o = o.reshape(o.shape[0], -1)
+        if gate is not None:
+            o = o * torch.sigmoid(gate)
+        return self.o_proj(o)
 
     def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, batch: PackedBatch,
                 kv_sink=None) -> torch.Tensor:
         qw = self.q_norm.weight if self.q_norm is not None else None
         kw = self.k_norm.weight if self.k_norm is not None else None
         ap = self.attn_parallel
-        if ap is not None and getattr(batch, 'rope_full', None) is not None and kv_sink is None and hasattr(ap, 'project_scatter'):
+        if (ap is not None and getattr(batch, 'rope_full', None) is not None and kv_sink is None and hasattr(ap, 'project_scatter')
+                and not self.gated and self.norm_offset == 0.0):
             # projection whose epilogue already delivers [T_full, (Hq + 2 Hkv)/sp · D] to every peer
             qkv_full = ap.project_scatter(x, self.qkv_proj, self.hq, self.hkv, self.d)
             if qkv_full is not None:
@@ -81,19 +107,18 @@ class Attention(nn.Module):
                 o = ops.flash_attn_varlen(q, k, v, batch.cu_seqlens, batch.max_seqlen, True, 1.0 / math.sqrt(self.d))
                 o = ap.gather_heads(o)
                 return self.o_proj(o.reshape(o.shape[0], -1))
-        qkv = self.qkv_proj(x)
-        q, k, v = ops.qkv_norm_rope(qkv, qw, kw, cos, sin, self.hq, self.hkv, self.d, self.cfg.rms_norm_eps)
+        q, k, v, gate = self.heads(self.qkv_proj(x), cos, sin)
         if kv_sink is not None:  # sampler prefill: keep K/V for the paged cache
             kv_sink(self.layer_idx, k, v)
         if ap is not None and hasattr(ap, 'attention'):  # context parallel: zig-zag local chunks against gathered keys
             o = ap.attention(q, k, v, batch.seq_lens, 1.0 / math.sqrt(self.d))
-            return self.o_proj(o.reshape(o.shape[0], -1))
+            return self.project_out(o, gate)
         if ap is not None:
             q, k, v = ap.scatter_heads(q, k, v)  # [T_local,H,D] → [T_full,H/sp,D]
         o = ops.flash_attn_varlen(q, k, v, batch.cu_seqlens, batch.max_seqlen, True, 1.0 / math.sqrt(self.d))
         if ap is not None:
             o = ap.gather_heads(o)  # back to [T_local, Hq, D]
-        return self.o_proj(o.reshape(o.shape[0], -1))
+        return self.project_out(o, gate)   # the gate is per token of this rank: applied after the heads are back
 
 
 class MLP(nn.Module):
@@ -362,9 +387,9 @@ class DecoderModel(nn.Module):
         x = self.embed(batch) if hidden is None else hidden
         if batch.position_ids.dim() == 2:  # [3, T] (time, height, width) positions of a vision-language batch
             from .vision import mrope_tables
-            cos, sin = mrope_tables(batch.position_ids, self.cfg.head_dim, self.cfg.rope_theta, self.cfg.mrope_section, self.cfg.mrope_interleaved)
+            cos, sin = mrope_tables(batch.position_ids, self.cfg.rotary_dim, self.cfg.rope_theta, self.cfg.mrope_section, self.cfg.mrope_interleaved)
         else:
-            cos, sin = ops.rope_tables(batch.position_ids, self.cfg.head_dim, self.cfg.rope_theta, self.cfg.rope_scaling)
+            cos, sin = ops.rope_tables(batch.position_ids, self.cfg.rotary_dim, self.cfg.rope_theta, self.cfg.rope_scaling)
         full = None
         for layer in self.layers:
             ap = getattr(getattr(layer, 'self_attn', None), 'attn_parallel', None)

@@ -92,6 +92,8 @@ class TargetFilter:
             self._re = re.compile(spec)
 
     def matches(self, full_name: str, short_name: str) -> bool:
+        if short_name == 'q_gate':      # the output gate is the second half of HF's q_proj: one adapter covers both
+            short_name, full_name = 'q_proj', full_name[:-len('q_gate')] + 'q_proj'
         s = self.spec
         if s is None or s in ('all-linear', 'all'):
             return short_name not in ('lm_head', 'gate')  # PEFT's all-linear excludes the output head; router kept off
@@ -125,6 +127,7 @@ class Linear(nn.Module):
         self.max_loras = 0
         self.max_r = 0
         self.wgrad_out: Optional[torch.Tensor] = None  # flat-bucket view to accumulate dW into
+        self.gate_head_dim: Optional[int] = None  # set on a q|k|v|gate projection: head width used to interleave q and gate rows for export
         self.tp = None  # tensor-parallel context (parallel.tensor.TPContext)
         self.tp_mode: Optional[str] = None  # 'col' | 'row'
 
@@ -134,10 +137,15 @@ class Linear(nn.Module):
         device = device or self.weight.device
         self.max_loras, self.max_r = max_loras, max_r
         for pname, n in self.parts:
-            a = torch.empty(max_loras, max_r, self.in_features, dtype=dtype, device=device)
-            for s in range(max_loras):
-                nn.init.kaiming_uniform_(a[s], a=math.sqrt(5))
-            self.lora_A[pname] = nn.Parameter(a)
+            if pname == 'q_gate' and 'q_proj' in self.lora_A:
+                # query and output gate are one projection in the checkpoint format (and for PEFT): they share the
+                # adapter's A and each keeps its rows of B
+                self.lora_A[pname] = self.lora_A['q_proj']
+            else:
+                a = torch.empty(max_loras, max_r, self.in_features, dtype=dtype, device=device)
+                for s in range(max_loras):
+                    nn.init.kaiming_uniform_(a[s], a=math.sqrt(5))
+                self.lora_A[pname] = nn.Parameter(a)
             self.lora_B[pname] = nn.Parameter(torch.zeros(max_loras, n, max_r, dtype=dtype, device=device))
 
     def has_lora(self) -> bool:

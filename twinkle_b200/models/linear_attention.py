@@ -98,13 +98,20 @@ def gated_delta_rule_varlen(q, k, v, g, beta, cu_seqlens, scale: Optional[float]
     return out
 
 
+def l2norm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """``x / sqrt(Σx² + eps)`` over the last dim in fp32 — the q / k normalisation of the FLA kernels the Hugging Face
+    implementation follows (not ``F.normalize``, whose epsilon clamps the norm instead)."""
+    xf = x.float()
+    return xf * torch.rsqrt((xf * xf).sum(-1, keepdim=True) + eps)
+
+
 def gated_delta_rule_varlen_torch(q, k, v, g, beta, cu_seqlens, scale: Optional[float] = None, chunk: int = 64, normalize: bool = True,
                                   init_state=None, return_states: bool = False):
     """The whole op on PyTorch: ``q, k [T, Hk, dk]`` are L2-normalised per head (``normalize``) and repeated to the ``Hv``
     value heads, then every packed segment is evaluated chunk-parallel from ``init_state[i]`` (or an empty state)."""
     rep = v.shape[1] // q.shape[1]
     if normalize:
-        q, k = F.normalize(q.float(), dim=-1).to(q.dtype), F.normalize(k.float(), dim=-1).to(k.dtype)
+        q, k = l2norm(q).to(q.dtype), l2norm(k).to(k.dtype)
     if rep > 1:
         q, k = q.repeat_interleave(rep, 1), k.repeat_interleave(rep, 1)
     bounds = cu_seqlens.tolist()
@@ -228,7 +235,7 @@ class GatedDeltaNet(nn.Module):
             o, S = ops.gated_delta_rule_varlen(q, k, v, g, beta, cu, init_state=state, return_states=True)
             o = o.float()
         else:
-            q, k = F.normalize(q.float(), dim=-1), F.normalize(k.float(), dim=-1)
+            q, k = l2norm(q), l2norm(k)
             rep = self.hv // self.hk
             if rep > 1:
                 q, k = q.repeat_interleave(rep, 1), k.repeat_interleave(rep, 1)

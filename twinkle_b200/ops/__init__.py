@@ -248,14 +248,16 @@ def _head_dim_ok(d: int) -> bool:
     return False
 
 
-def qkv_norm_rope(qkv: torch.Tensor, q_weight, k_weight, cos, sin, hq: int, hkv: int, d: int, eps: float = 1e-6):
-    """Split fused qkv, apply q/k RMSNorm (if weights given) and RoPE."""
-    if _cuda(qkv) and qkv.dtype == torch.bfloat16 and q_weight is not None and _head_dim_ok(d):
-        return _QKNormRope.apply(qkv, q_weight, k_weight, cos, sin, hq, hkv, d, eps)
+def qkv_norm_rope(qkv: torch.Tensor, q_weight, k_weight, cos, sin, hq: int, hkv: int, d: int, eps: float = 1e-6, offset: float = 0.0):
+    """Split fused qkv, apply q/k RMSNorm (if weights given; ``offset`` 1.0 = "1 + w") and RoPE on the leading
+    ``2·cos.shape[-1]`` dims of every head.  The fused kernel serves full rotary with plain norm weights."""
+    if (_cuda(qkv) and qkv.dtype == torch.bfloat16 and q_weight is not None and _head_dim_ok(d) and offset == 0.0
+            and 2 * cos.shape[-1] == d):
+        return _QKNormRope.apply(qkv.contiguous(), q_weight, k_weight, cos, sin, hq, hkv, d, eps)
     T = qkv.shape[0]
     q, k, v = qkv.split([hq * d, hkv * d, hkv * d], dim=-1)
     q, k, v = q.reshape(T, hq, d), k.reshape(T, hkv, d), v.reshape(T, hkv, d)
-    q, k = ref.qk_norm_rope(q, k, q_weight, k_weight, cos, sin, eps)
+    q, k = ref.qk_norm_rope(q, k, q_weight, k_weight, cos, sin, eps, offset)
     return q, k, v
 
 

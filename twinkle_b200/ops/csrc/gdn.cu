@@ -134,7 +134,7 @@ __global__ void __launch_bounds__(32) gdn_recurrent_fwd_kernel(const bf16* __res
         dqk += kv_[c][e] * qv_[c][e];
       }
       sk = warp_sum(sk); sq = warp_sum(sq); dqk = warp_sum(dqk);
-      const float rk = 1.f / fmaxf(sqrtf(sk), 1e-12f), rq = scale / fmaxf(sqrtf(sq), 1e-12f);
+      const float rk = rsqrtf(sk + 1e-6f), rq = scale * rsqrtf(sq + 1e-6f);   // x / sqrt(Σx² + 1e-6), the FLA convention
 #pragma unroll
       for (int e = 0; e < EPL; ++e) {
         s_k[c][lane * EPL + e] = kv_[c][e] * rk;

@@ -90,20 +90,25 @@ def rope_tables(positions: torch.Tensor, head_dim: int, theta: float = 1e6, scal
 
 
 def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-    """Rotate-half convention (HF Llama/Qwen): pairs are (i, i + D/2).  ``x [T, H, D]``."""
-    d2 = x.shape[-1] // 2
+    """Rotate-half convention (HF Llama/Qwen): pairs are (i, i + R/2) inside the leading ``R = 2·cos.shape[-1]`` dims;
+    dims past ``R`` pass through (partial rotary).  ``x [T, H, D]``."""
+    rot = 2 * cos.shape[-1]
     xf = x.float()
-    x1, x2 = xf[..., :d2], xf[..., d2:]
+    x1, x2 = xf[..., :rot // 2], xf[..., rot // 2:rot]
     c, s = cos[:, None, :], sin[:, None, :]
-    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], -1).to(x.dtype)
+    parts = [x1 * c - x2 * s, x2 * c + x1 * s]
+    if rot < x.shape[-1]:
+        parts.append(xf[..., rot:])
+    return torch.cat(parts, -1).to(x.dtype)
 
 
 def qk_norm_rope(q: torch.Tensor, k: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
-                 cos: torch.Tensor, sin: torch.Tensor, eps: float = 1e-6) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Per-head RMSNorm on q and k (Qwen3) followed by RoPE.  ``q [T,Hq,D]``, ``k [T,Hkv,D]``."""
+                 cos: torch.Tensor, sin: torch.Tensor, eps: float = 1e-6, offset: float = 0.0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-head RMSNorm on q and k (Qwen3; ``offset`` 1.0 for the "1 + w" form of Qwen3.5) followed by RoPE.
+    ``q [T,Hq,D]``, ``k [T,Hkv,D]``."""
     if q_weight is not None:
-        q = rmsnorm(q, q_weight, eps)
-        k = rmsnorm(k, k_weight, eps)
+        q = rmsnorm(q, q_weight, eps, offset)
+        k = rmsnorm(k, k_weight, eps, offset)
     return apply_rope(q, cos, sin), apply_rope(k, cos, sin)
 
 

@@ -169,7 +169,7 @@ class NativeEngine:
         hybrid stacks keep their state on the sequences (``seqs``) and always run eagerly."""
         cfg, B = self.cfg, tokens.shape[0]
         # ``positions`` index the KV cache; the rotary position differs from it after a prompt with images
-        cos, sin = ops.rope_tables(positions if rope_positions is None else rope_positions, cfg.head_dim, cfg.rope_theta, cfg.rope_scaling)
+        cos, sin = ops.rope_tables(positions if rope_positions is None else rope_positions, cfg.rotary_dim, cfg.rope_theta, cfg.rope_scaling)
         x = self.model.embed_tokens(tokens)
         blk = table.gather(1, (positions // self.cache.block_size).unsqueeze(1)).squeeze(1).long()
         off = positions % self.cache.block_size
@@ -187,14 +187,11 @@ class NativeEngine:
                     n = layer.post_attention_layernorm(x)
                     x = x + (layer.mlp(n) if not layer.is_moe else layer.mlp(n, None))
                     continue
-                qkv = at.qkv_proj(h)
-                qw = at.q_norm.weight if at.q_norm is not None else None
-                kw = at.k_norm.weight if at.k_norm is not None else None
-                q, k, v = ops.qkv_norm_rope(qkv, qw, kw, cos, sin, at.hq, at.hkv, at.d, cfg.rms_norm_eps)
+                q, k, v, gate = at.heads(at.qkv_proj(h), cos, sin)
                 self.cache.k[li, blk, off] = k
                 self.cache.v[li, blk, off] = v
                 o = ops.paged_attention_decode(q, self.cache.k[li], self.cache.v[li], table, seq_lens, 1.0 / math.sqrt(at.d))
-                x = x + at.o_proj(o.reshape(B, -1))
+                x = x + at.project_out(o, gate)
                 n = layer.post_attention_layernorm(x)
                 x = x + (layer.mlp(n) if not layer.is_moe else layer.mlp(n, None))
             x = self.model.norm(x)
