@@ -111,6 +111,8 @@ def _internal_to_hf_text(name: str, tensor: torch.Tensor, cfg: DecoderConfig) ->
         return [(_hf_layer(i, 'linear_attn.norm.weight'), tensor)]
     if rest.startswith('self_attn.') and cfg.layer_types and cfg.layer_types[i] == 'linear_attention':
         return [(_hf_layer(i, 'linear_attn.' + rest[len('self_attn.'):]), tensor)]
+    if rest in ('mlp.experts.gate_up_proj', 'mlp.experts.down_proj') and cfg.model_type.startswith('qwen3_5'):
+        return [(_hf_layer(i, rest), tensor)]       # this family's checkpoints keep the experts fused, in the layout used here
     if rest == 'mlp.experts.gate_up_proj':
         out = []
         for e in range(tensor.shape[0]):
@@ -155,6 +157,8 @@ def _hf_names_for_text(name: str, cfg: DecoderConfig) -> List[str]:
         return [_hf_layer(i, 'linear_attn.norm.weight')]
     if rest.startswith('self_attn.') and cfg.layer_types and cfg.layer_types[i] == 'linear_attention':
         return [_hf_layer(i, 'linear_attn.' + rest[len('self_attn.'):])]
+    if rest in ('mlp.experts.gate_up_proj', 'mlp.experts.down_proj') and cfg.model_type.startswith('qwen3_5'):
+        return [_hf_layer(i, rest)]
     if rest == 'mlp.experts.gate_up_proj':
         return [_hf_layer(i, f'mlp.experts.{e}.{p}_proj.weight') for e in range(cfg.num_experts) for p in ('gate', 'up')]
     if rest == 'mlp.experts.down_proj':

@@ -16,7 +16,7 @@ from typing import List, Any, Dict, Optional
 # config.json ``model_type`` values whose layer maths is what ``models/decoder.py`` computes (each checked against transformers)
 SUPPORTED_MODEL_TYPES = frozenset({'llama', 'mistral', 'mixtral', 'qwen2', 'qwen2_moe', 'qwen3', 'qwen3_moe', 'seed_oss', 'qwen2_vl', 'qwen2_vl_text',
                                    'qwen2_5_vl', 'qwen2_5_vl_text', 'qwen3_vl', 'qwen3_vl_text', 'qwen3_vl_moe', 'qwen3_vl_moe_text',
-                                   'qwen3_5', 'qwen3_5_text'})
+                                   'qwen3_5', 'qwen3_5_text', 'qwen3_5_moe', 'qwen3_5_moe_text'})
 
 
 def _rope_scaling_of(cfg: Dict[str, Any]) -> Optional[Dict[str, Any]]:
@@ -161,7 +161,7 @@ class DecoderConfig:
             num_experts=cfg.get('num_experts', cfg.get('num_local_experts', 0)) or 0,
             num_experts_per_tok=cfg.get('num_experts_per_tok', 8),
             moe_intermediate_size=cfg.get('moe_intermediate_size', cfg.get('intermediate_size', 768) if mt == 'mixtral' else 768),
-            norm_topk_prob=bool(cfg.get('norm_topk_prob', True)), router_aux_loss_coef=float(cfg.get('router_aux_loss_coef', 0.0)),
+            norm_topk_prob=True if cfg.get('norm_topk_prob') is None else bool(cfg['norm_topk_prob']), router_aux_loss_coef=float(cfg.get('router_aux_loss_coef', 0.0)),
             shared_expert_intermediate_size=int(cfg.get('shared_expert_intermediate_size', 0) or 0),
             rms_norm_offset=float(cfg.get('rms_norm_offset', 1.0 if (mt.startswith('gemma') or q35) else 0.0)),
             partial_rotary_factor=float(cfg.get('partial_rotary_factor', (cfg.get('rope_parameters') or {}).get('partial_rotary_factor', 1.0)) or 1.0),
@@ -232,7 +232,8 @@ class DecoderConfig:
                      linear_value_head_dim=self.linear_value_head_dim, linear_conv_kernel_dim=self.linear_conv_kernel_dim)
         if self.model_type.startswith('qwen3_5'):
             # written as the text model of the family (what ``Qwen3_5ForCausalLM`` loads)
-            d.update(architectures=['Qwen3_5ForCausalLM'], model_type='qwen3_5_text', partial_rotary_factor=self.partial_rotary_factor,
+            d.update(architectures=['Qwen3_5MoeForCausalLM' if self.is_moe else 'Qwen3_5ForCausalLM'],
+                     model_type='qwen3_5_moe_text' if self.is_moe else 'qwen3_5_text', partial_rotary_factor=self.partial_rotary_factor,
                      rope_parameters={'rope_type': 'default', 'rope_theta': self.rope_theta, 'partial_rotary_factor': self.partial_rotary_factor},
                      layer_types=list(self.layer_types or ['full_attention'] * self.num_hidden_layers))
             d.pop('rms_norm_offset', None)
