@@ -39,6 +39,14 @@ def _cases():
                                                        **{k: v for k, v in COMMON.items() if k not in ('rope_theta', 'intermediate_size')},
                                                        rope_parameters={'rope_type': 'default', 'rope_theta': 10000.0, 'partial_rotary_factor': 0.25}),
                         'Qwen3_5MoeForCausalLM'),
+        'qwen3_next': (lambda: T.Qwen3NextConfig(head_dim=32, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=16,
+                                                 linear_value_head_dim=16, linear_conv_kernel_dim=4, tie_word_embeddings=False,
+                                                 layer_types=['linear_attention', 'full_attention'], num_experts=4, num_experts_per_tok=2,
+                                                 moe_intermediate_size=64, shared_expert_intermediate_size=96, norm_topk_prob=True,
+                                                 decoder_sparse_step=1, mlp_only_layers=[],
+                                                 **{k: v for k, v in COMMON.items() if k != 'rope_theta'},
+                                                 rope_parameters={'rope_type': 'default', 'rope_theta': 10000.0, 'partial_rotary_factor': 0.25}),
+                       'Qwen3NextForCausalLM'),
         'qwen2_moe_shared': (lambda: T.Qwen2MoeConfig(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=96,
                                                       norm_topk_prob=False, decoder_sparse_step=1, mlp_only_layers=[], **COMMON), 'Qwen2MoeForCausalLM'),
     }
@@ -80,7 +88,7 @@ def test_hf_checkpoint_gives_the_same_logits_here(name, tmp_path):
     assert torch.allclose(got, want, atol=2e-5), float((got - want).abs().max())
 
 
-@pytest.mark.parametrize('name', ['qwen3', 'qwen3_moe', 'mixtral', 'qwen2_moe_shared', 'qwen3_5', 'qwen3_5_moe'])
+@pytest.mark.parametrize('name', ['qwen3', 'qwen3_moe', 'mixtral', 'qwen2_moe_shared', 'qwen3_5', 'qwen3_5_moe', 'qwen3_next'])
 def test_checkpoint_saved_here_loads_in_transformers(name, tmp_path):
     hf = _hf_model(name)
     hf.save_pretrained(str(tmp_path / 'hf'), safe_serialization=True)

@@ -54,6 +54,24 @@ def _split_gdn(cfg: DecoderConfig) -> bool:
     return cfg.model_type.startswith('qwen3_5')
 
 
+def _grouped_gdn(cfg: DecoderConfig) -> bool:
+    """Qwen3-Next keeps the two fused linear-attention input projections, with their rows grouped per key head:
+    ``[q_g | k_g | v of the group's value heads | z of the same]`` and ``[b_g | a_g]``."""
+    return cfg.model_type == 'qwen3_next'
+
+
+def _gdn_regroup(t: torch.Tensor, cfg: DecoderConfig, which: str, to_hf: bool) -> torch.Tensor:
+    """Row permutation between this package's ``[q | k | v | z]`` / ``[b | a]`` order and the per-key-head grouping."""
+    hk, hv, dk, dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+    rep, tail = hv // hk, tuple(t.shape[1:])
+    sizes = [dk, dk, rep * dv, rep * dv] if which == 'qkvz' else [rep, rep]
+    if to_hf:
+        parts = t.split([hk * n for n in sizes], dim=0)
+        return torch.cat([p.reshape(hk, n, *tail) for p, n in zip(parts, sizes)], 1).reshape(t.shape[0], *tail)
+    parts = t.reshape(hk, sum(sizes), *tail).split(sizes, dim=1)
+    return torch.cat([p.reshape(hk * n, *tail) for p, n in zip(parts, sizes)], 0)
+
+
 def _vl(name: str, cfg: DecoderConfig) -> str:
     """Vision-language checkpoints nest the language model: ``model.X`` → ``model.language_model.X``."""
     return 'model.language_model.' + name[len('model.'):] if _nested(cfg) and name.startswith('model.') else name
@@ -94,6 +112,9 @@ def _internal_to_hf_text(name: str, tensor: torch.Tensor, cfg: DecoderConfig) ->
             q, k, v = tensor.split([cfg.q_size, cfg.kv_size, cfg.kv_size], dim=0)
         return [(_hf_layer(i, f'self_attn.q_proj.{kind}'), q), (_hf_layer(i, f'self_attn.k_proj.{kind}'), k),
                 (_hf_layer(i, f'self_attn.v_proj.{kind}'), v)]
+    if rest in ('self_attn.in_proj_qkvz.weight', 'self_attn.in_proj_ba.weight') and _grouped_gdn(cfg):
+        which = 'qkvz' if 'qkvz' in rest else 'ba'
+        return [(_hf_layer(i, 'linear_attn.' + rest[len('self_attn.'):]), _gdn_regroup(tensor, cfg, which, True))]
     if rest == 'self_attn.in_proj_qkvz.weight' and _split_gdn(cfg):     # Qwen3.5 keeps q|k|v and z, and b and a, as separate linears
         kd, vd = cfg.linear_num_key_heads * cfg.linear_key_head_dim, cfg.linear_num_value_heads * cfg.linear_value_head_dim
         qkv, z = tensor.split([2 * kd + vd, vd], dim=0)
@@ -218,6 +239,8 @@ def hf_to_internal(name: str, cfg: DecoderConfig, get: Callable[[str], torch.Ten
         return torch.cat([q, parts[1], parts[2], g], 0)
     if rest == 'self_attn.conv_weight' and parts[0].dim() == 3:
         return parts[0].squeeze(1)
+    if rest in ('self_attn.in_proj_qkvz.weight', 'self_attn.in_proj_ba.weight') and _grouped_gdn(cfg):
+        return _gdn_regroup(parts[0], cfg, 'qkvz' if 'qkvz' in rest else 'ba', False)
     return parts[0] if len(parts) == 1 else torch.cat(parts, 0)
 
 

@@ -16,7 +16,7 @@ from typing import List, Any, Dict, Optional
 # config.json ``model_type`` values whose layer maths is what ``models/decoder.py`` computes (each checked against transformers)
 SUPPORTED_MODEL_TYPES = frozenset({'llama', 'mistral', 'mixtral', 'qwen2', 'qwen2_moe', 'qwen3', 'qwen3_moe', 'seed_oss', 'qwen2_vl', 'qwen2_vl_text',
                                    'qwen2_5_vl', 'qwen2_5_vl_text', 'qwen3_vl', 'qwen3_vl_text', 'qwen3_vl_moe', 'qwen3_vl_moe_text',
-                                   'qwen3_5', 'qwen3_5_text', 'qwen3_5_moe', 'qwen3_5_moe_text'})
+                                   'qwen3_5', 'qwen3_5_text', 'qwen3_5_moe', 'qwen3_5_moe_text', 'qwen3_next'})
 
 
 def _rope_scaling_of(cfg: Dict[str, Any]) -> Optional[Dict[str, Any]]:
@@ -146,7 +146,7 @@ class DecoderConfig:
             if vision.get('model_type', top.get('model_type', 'qwen2_vl')) not in ('qwen2_vl', 'qwen2_5_vl', 'qwen3_vl', 'qwen3_vl_moe'):
                 raise NotImplementedError(f"vision tower of type {vision.get('model_type')!r} is not supported (qwen2_vl, qwen2_5_vl and qwen3_vl are)")
         rs_any = cfg.get('rope_scaling') or cfg.get('rope_parameters') or top.get('rope_scaling') or {}
-        q35 = mt.startswith('qwen3_5')
+        q35 = mt.startswith('qwen3_5') or mt == 'qwen3_next'      # the hybrid family: gated attention, partial rotary, "1 + w" norms
         if q35 and vision is not None:
             vision = None        # the language model of a Qwen3.5 checkpoint trains without its tower here (text-only batches)
         heads = cfg.get('num_attention_heads', 32)
@@ -230,7 +230,12 @@ class DecoderConfig:
             d.update(layer_types=list(self.layer_types), linear_num_key_heads=self.linear_num_key_heads,
                      linear_num_value_heads=self.linear_num_value_heads, linear_key_head_dim=self.linear_key_head_dim,
                      linear_value_head_dim=self.linear_value_head_dim, linear_conv_kernel_dim=self.linear_conv_kernel_dim)
-        if self.model_type.startswith('qwen3_5'):
+        if self.model_type == 'qwen3_next':
+            d.update(architectures=['Qwen3NextForCausalLM'], model_type='qwen3_next', partial_rotary_factor=self.partial_rotary_factor,
+                     rope_parameters={'rope_type': 'default', 'rope_theta': self.rope_theta, 'partial_rotary_factor': self.partial_rotary_factor},
+                     layer_types=list(self.layer_types or ['full_attention'] * self.num_hidden_layers))
+            d.pop('rms_norm_offset', None)
+        elif self.model_type.startswith('qwen3_5'):
             # written as the text model of the family (what ``Qwen3_5ForCausalLM`` loads)
             d.update(architectures=['Qwen3_5MoeForCausalLM' if self.is_moe else 'Qwen3_5ForCausalLM'],
                      model_type='qwen3_5_moe_text' if self.is_moe else 'qwen3_5_text', partial_rotary_factor=self.partial_rotary_factor,
