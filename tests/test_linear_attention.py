@@ -1,5 +1,6 @@
 """Gated DeltaNet: the chunk-parallel evaluator against the plain recurrence (values, final state, gradients), packed
 sequences without leakage, and the layer end to end."""
+import pytest
 import torch
 
 from twinkle_b200.models.linear_attention import (GatedDeltaNet, causal_conv1d_varlen, gated_delta_rule_chunked, gated_delta_rule_recurrent,
@@ -62,13 +63,13 @@ def test_layer_forward_backward():
     assert torch.allclose(layer(x2, cu)[:20], y[:20].detach(), atol=1e-6)
 
 
-def _hybrid_curve(rank, world, steps):
+def _hybrid_curve(rank, world, steps, model_id='tiny-hybrid'):
     import torch.distributed as dist
     from twinkle_b200.model import TransformersModel
     from twinkle_b200.utils.device_mesh import DeviceMesh
     torch.manual_seed(0)
     mesh = DeviceMesh.from_sizes(fsdp_size=world, dp_size=None, ulysses_size=world) if world > 1 else DeviceMesh.from_sizes(dp_size=1)
-    m = TransformersModel(model_id='tiny-hybrid', device_mesh=mesh, seed=0, device='cpu')   # fp32 on both sides of the comparison
+    m = TransformersModel(model_id=model_id, device_mesh=mesh, seed=0, device='cpu')   # fp32 on both sides of the comparison
     m.set_optimizer('AdamW', lr=2e-3, weight_decay=0.0)
     g = torch.Generator().manual_seed(9)
     feats = []
@@ -86,11 +87,14 @@ def _hybrid_curve(rank, world, steps):
     return curve
 
 
-def test_hybrid_model_trains_and_ulysses_matches_single_process():
+@pytest.mark.parametrize('model_id', ['tiny-hybrid', 'tiny-qwen3.5'])
+def test_hybrid_model_trains_and_ulysses_matches_single_process(model_id):
+    """Also for the Qwen3.5 stack: the attention output gate is applied per token after the heads are gathered back, and
+    the rotary tables cover a quarter of the head."""
     from tests.dist_utils import run_ranks
-    single = _hybrid_curve(0, 1, 4)
+    single = _hybrid_curve(0, 1, 4, model_id)
     assert single[-1] < single[0] - 0.2
-    for c in run_ranks(_hybrid_curve, 2, 4):
+    for c in run_ranks(_hybrid_curve, 2, 4, model_id):
         for a, b in zip(single, c):
             assert abs(a - b) < 3e-4, (single, c)
 
