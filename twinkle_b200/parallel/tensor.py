@@ -283,6 +283,9 @@ def apply_tensor_parallel(model, cfg, comm: Communicator, sequence_parallel: boo
             if shard.shape != p.shape:
                 p.data = shard.contiguous().clone()
     for layer in model.layers:
+        if getattr(layer, 'is_linear', False):
+            raise NotImplementedError('linear-attention (Gated DeltaNet) layers are not split over a tensor-parallel group; '
+                                      'use tp_size=1 for hybrid stacks (pipeline, data, sequence and context parallelism apply)')
         at = layer.self_attn
         at.hq, at.hkv = cfg.num_attention_heads // tp.size, cfg.num_key_value_heads // tp.size
         pairs = [(at.qkv_proj, 'col'), (at.o_proj, 'row')]
