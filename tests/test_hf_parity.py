@@ -47,6 +47,11 @@ def _cases():
                                                  **{k: v for k, v in COMMON.items() if k != 'rope_theta'},
                                                  rope_parameters={'rope_type': 'default', 'rope_theta': 10000.0, 'partial_rotary_factor': 0.25}),
                        'Qwen3NextForCausalLM'),
+        # GLM-4 family: rotary on half the head with (2i, 2i+1) pairs, biased q|k|v, fused gate_up; glm4 adds post-sub-layer norms
+        'glm': (lambda: T.GlmConfig(head_dim=32, pad_token_id=0, tie_word_embeddings=False, **{k: v for k, v in COMMON.items() if k != 'rope_theta'},
+                                    rope_parameters={'rope_type': 'default', 'rope_theta': 10000.0, 'partial_rotary_factor': 0.5}), 'GlmForCausalLM'),
+        'glm4': (lambda: T.Glm4Config(head_dim=32, pad_token_id=0, tie_word_embeddings=False, **{k: v for k, v in COMMON.items() if k != 'rope_theta'},
+                                      rope_parameters={'rope_type': 'default', 'rope_theta': 10000.0, 'partial_rotary_factor': 0.5}), 'Glm4ForCausalLM'),
         'qwen2_moe_shared': (lambda: T.Qwen2MoeConfig(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=96,
                                                       norm_topk_prob=False, decoder_sparse_step=1, mlp_only_layers=[], **COMMON), 'Qwen2MoeForCausalLM'),
     }
@@ -88,7 +93,7 @@ def test_hf_checkpoint_gives_the_same_logits_here(name, tmp_path):
     assert torch.allclose(got, want, atol=2e-5), float((got - want).abs().max())
 
 
-@pytest.mark.parametrize('name', ['qwen3', 'qwen3_moe', 'mixtral', 'qwen2_moe_shared', 'qwen3_5', 'qwen3_5_moe', 'qwen3_next'])
+@pytest.mark.parametrize('name', ['qwen3', 'qwen3_moe', 'mixtral', 'qwen2_moe_shared', 'qwen3_5', 'qwen3_5_moe', 'qwen3_next', 'glm', 'glm4'])
 def test_checkpoint_saved_here_loads_in_transformers(name, tmp_path):
     hf = _hf_model(name)
     hf.save_pretrained(str(tmp_path / 'hf'), safe_serialization=True)
@@ -160,3 +165,53 @@ def test_unknown_architectures_are_refused_not_guessed(tmp_path, monkeypatch):
     monkeypatch.delenv('TWINKLE_ALLOW_UNKNOWN_ARCH')
     with pytest.raises(NotImplementedError):
         DecoderConfig.from_hf({'model_type': 'qwen2_vl', 'text_config': {'model_type': 'qwen2_vl_text'}, 'vision_config': {'model_type': 'siglip'}})
+
+
+@pytest.mark.parametrize('name', ['qwen3', 'glm4', 'qwen3_5'])
+def test_adapter_trained_here_merges_into_the_hf_model(name, tmp_path):
+    """PEFT-shaped adapter tensors exported here, merged by hand into the Hugging Face model's own projections
+    (``W += α/r · B A``), give the logits this package computes with the adapter active — also where the checkpoint orders
+    rows differently (GLM's rotary pairing, Qwen3.5's query | gate interleave)."""
+    from twinkle_b200.model import MultiLoraTransformersModel
+    from twinkle_b200.models.decoder import PackedBatch
+    from twinkle_b200.models.layers import lora_batch
+    hf = _hf_model(name)
+    hf.save_pretrained(str(tmp_path / 'hf'), safe_serialization=True)
+    m = MultiLoraTransformersModel(model_id=str(tmp_path / 'hf'), device='cpu', max_loras=2, max_r=8, seed=0)
+    m.add_adapter_to_model('a', {'r': 4, 'lora_alpha': 8, 'target_modules': ['q_proj', 'k_proj', 'v_proj', 'o_proj', 'gate_proj', 'up_proj', 'down_proj']})
+    m.set_optimizer('AdamW', lr=2e-2, adapter_name='a')
+    g = torch.Generator().manual_seed(5)
+    batch = [{'input_ids': (ids := torch.randint(0, 512, (33, ), generator=g))[:-1].tolist(), 'labels': ids[1:].tolist()}]
+    for _ in range(3):
+        m.forward_backward(inputs=batch, adapter_name='a')
+        m.clip_grad_and_step(max_grad_norm=1.0, adapter_name='a')
+    ids = torch.randint(0, 512, (29, ), generator=torch.Generator().manual_seed(6))
+    n = ids.shape[0]
+    with torch.no_grad(), lora_batch(m.multi_lora.batch_for('a', n, 'cpu')):
+        ours = m.model.logits(m.model(PackedBatch(ids, torch.arange(n), torch.tensor([0, n], dtype=torch.int32), n))).float()
+    with torch.no_grad():
+        base = hf(ids[None]).logits[0]
+    sd = m.multi_lora.get_state_dict('a')
+    params = dict(hf.named_parameters())
+    merged = 0
+    with torch.no_grad():
+        for k, a in sd.items():
+            if not k.endswith('lora_A.weight'):
+                continue
+            b = sd[k.replace('lora_A', 'lora_B')]
+            target = k[len('base_model.model.'):-len('.lora_A.weight')] + '.weight'
+            if target not in params and target.replace('model.', 'model.language_model.', 1) in params:
+                target = target.replace('model.', 'model.language_model.', 1)
+            if target not in params:        # a projection the checkpoint keeps fused (GLM's gate_up): the adapter covers its half of the rows
+                fused = target.replace('mlp.gate_proj', 'mlp.gate_up_proj').replace('mlp.up_proj', 'mlp.gate_up_proj')
+                assert fused in params, target
+                w = params[fused]
+                half = w.shape[0] // 2
+                rows = slice(0, half) if 'gate_proj' in k else slice(half, None)
+                w[rows] += (b.float() @ a.float()) * 2.0
+            else:
+                params[target] += (b.float() @ a.float()) * 2.0
+            merged += 1
+        theirs = hf(ids[None]).logits[0]
+    assert merged >= 7 and not torch.allclose(base, theirs, atol=1e-3)
+    assert torch.allclose(ours, theirs, atol=5e-5), float((ours - theirs).abs().max())

@@ -199,6 +199,13 @@ class MultiLora:
                         out.append((f'{mod_name}.lora.{which}_B', m.lora[which + '_B'], t.slot))
         return out
 
+    def _rope_perm(self, pname: str, rows: int, to_hf: bool):
+        cfg = getattr(self.model, 'cfg', None)
+        if cfg is None or not getattr(cfg, 'rope_interleaved', False) or pname not in ('q_proj', 'k_proj'):
+            return None
+        from ..models.bridge import rope_row_perm
+        return rope_row_perm(cfg, rows // cfg.head_dim, to_hf)
+
     # ------------------------------------------------------------ state dict
     def get_state_dict(self, tenant: str) -> Dict[str, torch.Tensor]:
         """PEFT-named tensors sliced to the tenant's rank."""
@@ -213,6 +220,9 @@ class MultiLora:
                     if pname == 'q_gate' or not t.target.matches(full, pname):
                         continue            # the gate's rows travel inside q_proj's B (below)
                     b = m.lora_B[pname][t.slot, :, :r].detach().clone()
+                    perm = self._rope_perm(pname, b.shape[0], True)
+                    if perm is not None:
+                        b = b[perm]             # the checkpoint's rotary pairing: rows of q / k move with it
                     if pname == 'q_proj' and m.gate_head_dim:
                         b = _interleave_gate(b, m.lora_B['q_gate'][t.slot, :, :r].detach(), m.gate_head_dim)
                     sd[lora_internal_to_peft(mod_name, pname, 'A')] = m.lora_A[pname][t.slot, :r].detach().clone()
@@ -237,6 +247,9 @@ class MultiLora:
                         r = a.shape[0]
                         if pname == 'q_proj' and m.gate_head_dim:      # [query | gate] rows interleaved per head → two parts
                             b, bg = _split_gate(b, m.gate_head_dim)
+                        perm = self._rope_perm(pname, b.shape[0], False)
+                        if perm is not None:
+                            b = b[perm.to(b.device)]
                             m.lora_B['q_gate'][t.slot].zero_()
                             m.lora_B['q_gate'][t.slot, :, :r].copy_(bg)
                         m.lora_A[pname][t.slot].zero_()

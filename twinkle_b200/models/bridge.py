@@ -54,6 +54,17 @@ def _split_gdn(cfg: DecoderConfig) -> bool:
     return cfg.model_type.startswith('qwen3_5')
 
 
+def rope_row_perm(cfg: DecoderConfig, heads: int, to_hf: bool) -> Optional[torch.Tensor]:
+    """Row order of a q / k projection between this package's rotary convention (pairs ``(i, i + R/2)``) and a checkpoint
+    that pairs ``(2i, 2i+1)`` (GLM-4 family), for ``heads`` heads; ``None`` when the conventions agree.  ``out = w[perm]``."""
+    if not cfg.rope_interleaved:
+        return None
+    d, r = cfg.head_dim, cfg.rotary_dim
+    from_hf = torch.cat([torch.arange(0, r, 2), torch.arange(1, r, 2), torch.arange(r, d)])    # ours[j] = hf[from_hf[j]]
+    one = torch.argsort(from_hf) if to_hf else from_hf
+    return (torch.arange(heads)[:, None] * d + one[None, :]).reshape(-1)
+
+
 def _grouped_gdn(cfg: DecoderConfig) -> bool:
     """Qwen3-Next keeps the two fused linear-attention input projections, with their rows grouped per key head:
     ``[q_g | k_g | v of the group's value heads | z of the same]`` and ``[b_g | a_g]``."""
@@ -110,6 +121,8 @@ def _internal_to_hf_text(name: str, tensor: torch.Tensor, cfg: DecoderConfig) ->
             q = torch.cat([q.reshape(hq, d, *q.shape[1:]), g.reshape(hq, d, *g.shape[1:])], 1).reshape(2 * cfg.q_size, *q.shape[1:])
         else:
             q, k, v = tensor.split([cfg.q_size, cfg.kv_size, cfg.kv_size], dim=0)
+        if cfg.rope_interleaved:
+            q, k = q[rope_row_perm(cfg, cfg.num_attention_heads, True)], k[rope_row_perm(cfg, cfg.num_key_value_heads, True)]
         return [(_hf_layer(i, f'self_attn.q_proj.{kind}'), q), (_hf_layer(i, f'self_attn.k_proj.{kind}'), k),
                 (_hf_layer(i, f'self_attn.v_proj.{kind}'), v)]
     if rest in ('self_attn.in_proj_qkvz.weight', 'self_attn.in_proj_ba.weight') and _grouped_gdn(cfg):
@@ -122,6 +135,8 @@ def _internal_to_hf_text(name: str, tensor: torch.Tensor, cfg: DecoderConfig) ->
     if rest == 'self_attn.in_proj_ba.weight' and _split_gdn(cfg):
         b, a = tensor.chunk(2, dim=0)
         return [(_hf_layer(i, 'linear_attn.in_proj_b.weight'), b), (_hf_layer(i, 'linear_attn.in_proj_a.weight'), a)]
+    if rest == 'mlp.gate_up_proj.weight' and cfg.model_type in ('glm', 'glm4'):
+        return [(_hf_layer(i, rest), tensor)]           # fused [gate | up] in the checkpoint too
     if rest in ('mlp.gate_up_proj.weight', 'mlp.shared_expert.gate_up_proj.weight'):
         g, u = tensor.chunk(2, dim=0)
         pre = rest[:-len('gate_up_proj.weight')]
@@ -169,6 +184,8 @@ def _hf_names_for_text(name: str, cfg: DecoderConfig) -> List[str]:
         return [_hf_layer(i, 'linear_attn.in_proj_qkv.weight'), _hf_layer(i, 'linear_attn.in_proj_z.weight')]
     if rest == 'self_attn.in_proj_ba.weight' and _split_gdn(cfg):
         return [_hf_layer(i, 'linear_attn.in_proj_b.weight'), _hf_layer(i, 'linear_attn.in_proj_a.weight')]
+    if rest == 'mlp.gate_up_proj.weight' and cfg.model_type in ('glm', 'glm4'):
+        return [_hf_layer(i, rest)]
     if rest in ('mlp.gate_up_proj.weight', 'mlp.shared_expert.gate_up_proj.weight'):
         pre = rest[:-len('gate_up_proj.weight')]
         return [_hf_layer(i, pre + 'gate_proj.weight'), _hf_layer(i, pre + 'up_proj.weight')]
@@ -232,6 +249,8 @@ def hf_to_internal(name: str, cfg: DecoderConfig, get: Callable[[str], torch.Ten
         lo, hi = expert_range or (0, cfg.num_experts)
         return torch.stack([get(_hf_layer(i, f'mlp.experts.{e}.down_proj.weight')) for e in range(lo, hi)])
     parts = [get(n) for n in hf_names_for(name, cfg)]
+    if rest.startswith('self_attn.qkv_proj.') and cfg.rope_interleaved:
+        parts = [parts[0][rope_row_perm(cfg, cfg.num_attention_heads, False)], parts[1][rope_row_perm(cfg, cfg.num_key_value_heads, False)], parts[2]]
     if rest.startswith('self_attn.qkv_proj.') and cfg.attn_output_gate:
         hq, d = cfg.num_attention_heads, cfg.head_dim
         qg = parts[0].reshape(hq, 2 * d, *parts[0].shape[1:])

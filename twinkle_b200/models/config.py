@@ -16,7 +16,7 @@ from typing import List, Any, Dict, Optional
 # config.json ``model_type`` values whose layer maths is what ``models/decoder.py`` computes (each checked against transformers)
 SUPPORTED_MODEL_TYPES = frozenset({'llama', 'mistral', 'mixtral', 'qwen2', 'qwen2_moe', 'qwen3', 'qwen3_moe', 'seed_oss', 'qwen2_vl', 'qwen2_vl_text',
                                    'qwen2_5_vl', 'qwen2_5_vl_text', 'qwen3_vl', 'qwen3_vl_text', 'qwen3_vl_moe', 'qwen3_vl_moe_text',
-                                   'qwen3_5', 'qwen3_5_text', 'qwen3_5_moe', 'qwen3_5_moe_text', 'qwen3_next'})
+                                   'qwen3_5', 'qwen3_5_text', 'qwen3_5_moe', 'qwen3_5_moe_text', 'qwen3_next', 'glm', 'glm4'})
 
 
 def _rope_scaling_of(cfg: Dict[str, Any]) -> Optional[Dict[str, Any]]:
@@ -54,6 +54,11 @@ class DecoderConfig:
     # per-head sigmoid gate (a second half of the q projection) on the attention output; their q/k norms are "1 + w" too
     partial_rotary_factor: float = 1.0
     attn_output_gate: bool = False
+    # GLM-4 family: the checkpoint's rotary pairs are (2i, 2i+1); the bridge permutes the q / k projection rows into the
+    # (i, i + R/2) convention computed here (scores are unchanged by a common permutation of q and k dims), gate and up are
+    # one fused tensor in the checkpoint, and ``glm4`` norms each sub-layer's output before the residual add
+    rope_interleaved: bool = False
+    sandwich_norm: bool = False
     # MoE (num_experts == 0 → dense)
     num_experts: int = 0
     num_experts_per_tok: int = 8
@@ -166,6 +171,7 @@ class DecoderConfig:
             rms_norm_offset=float(cfg.get('rms_norm_offset', 1.0 if (mt.startswith('gemma') or q35) else 0.0)),
             partial_rotary_factor=float(cfg.get('partial_rotary_factor', (cfg.get('rope_parameters') or {}).get('partial_rotary_factor', 1.0)) or 1.0),
             attn_output_gate=bool(cfg.get('attn_output_gate', q35)),
+            rope_interleaved=bool(cfg.get('rope_interleaved', mt in ('glm', 'glm4'))), sandwich_norm=bool(cfg.get('sandwich_norm', mt == 'glm4')),
             layer_types=list(cfg['layer_types']) if cfg.get('layer_types') and 'linear_attention' in cfg['layer_types'] else None,
             linear_num_key_heads=cfg.get('linear_num_key_heads', 16), linear_num_value_heads=cfg.get('linear_num_value_heads', 32),
             linear_key_head_dim=cfg.get('linear_key_head_dim', 128), linear_value_head_dim=cfg.get('linear_value_head_dim', 128),
@@ -230,7 +236,11 @@ class DecoderConfig:
             d.update(layer_types=list(self.layer_types), linear_num_key_heads=self.linear_num_key_heads,
                      linear_num_value_heads=self.linear_num_value_heads, linear_key_head_dim=self.linear_key_head_dim,
                      linear_value_head_dim=self.linear_value_head_dim, linear_conv_kernel_dim=self.linear_conv_kernel_dim)
-        if self.model_type == 'qwen3_next':
+        if self.model_type in ('glm', 'glm4'):
+            d.update(architectures=['Glm4ForCausalLM' if self.model_type == 'glm4' else 'GlmForCausalLM'], model_type=self.model_type,
+                     partial_rotary_factor=self.partial_rotary_factor, pad_token_id=self.pad_token_id if self.pad_token_id is not None else 0,
+                     rope_parameters={'rope_type': 'default', 'rope_theta': self.rope_theta, 'partial_rotary_factor': self.partial_rotary_factor})
+        elif self.model_type == 'qwen3_next':
             d.update(architectures=['Qwen3NextForCausalLM'], model_type='qwen3_next', partial_rotary_factor=self.partial_rotary_factor,
                      rope_parameters={'rope_type': 'default', 'rope_theta': self.rope_theta, 'partial_rotary_factor': self.partial_rotary_factor},
                      layer_types=list(self.layer_types or ['full_attention'] * self.num_hidden_layers))

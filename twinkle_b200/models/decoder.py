@@ -288,6 +288,12 @@ class DecoderLayer(nn.Module):
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.rms_norm_offset)
         self.mlp = MoEBlock(cfg, layer_idx) if cfg.is_moe else MLP(cfg)
         self.is_moe = cfg.is_moe
+        # GLM-4: each sub-layer's output is normalised before it joins the residual stream
+        if cfg.sandwich_norm:
+            self.post_self_attn_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.rms_norm_offset)
+            self.post_mlp_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.rms_norm_offset)
+        else:
+            self.post_self_attn_layernorm = self.post_mlp_layernorm = None
 
     def forward(self, x: torch.Tensor, cos, sin, batch: PackedBatch, kv_sink=None) -> torch.Tensor:
         if self.is_linear:
@@ -298,11 +304,23 @@ class DecoderLayer(nn.Module):
             a = self.self_attn(self.input_layernorm(x), batch.cu_seqlens, state_sink=sink)
         else:
             a = self.self_attn(self.input_layernorm(x), cos, sin, batch, kv_sink)
-        n, h = self.post_attention_layernorm.forward_add(a, x)
+        n, h = self.after_attention(x, a)
+        forced = batch.routed_experts[self.layer_idx] if (self.is_moe and batch.routed_experts is not None) else None
+        return ops.add(h, self.feed_forward(n, forced), value_unused=True)
+
+    def after_attention(self, x: torch.Tensor, a: torch.Tensor):
+        """Token-mixer output ``a`` joins the residual stream ``x``: ``(input of the feed-forward block, new residual)``."""
+        if self.post_self_attn_layernorm is not None:
+            a = self.post_self_attn_layernorm(a)
+        return self.post_attention_layernorm.forward_add(a, x)
+
+    def feed_forward(self, n: torch.Tensor, forced=None) -> torch.Tensor:
+        """What the feed-forward block adds to the residual stream."""
         if self.is_moe:
-            forced = batch.routed_experts[self.layer_idx] if batch.routed_experts is not None else None
-            return ops.add(h, self.mlp(n, forced), value_unused=True)
-        return ops.add(h, self.mlp(n), value_unused=True)
+            m = self.mlp(n, forced)
+        else:
+            m = self.mlp(n, value_unused=self.post_mlp_layernorm is None)   # a following norm reads the value
+        return self.post_mlp_layernorm(m) if self.post_mlp_layernorm is not None else m
 
 
 class DecoderModel(nn.Module):

@@ -183,17 +183,15 @@ class NativeEngine:
                     y, conv, st = at.step(h, conv, st)
                     for i, s in enumerate(seqs):
                         s.linear[li] = (conv[i], st[i])
-                    x = x + y
-                    n = layer.post_attention_layernorm(x)
-                    x = x + (layer.mlp(n) if not layer.is_moe else layer.mlp(n, None))
+                    n, x = layer.after_attention(x, y)
+                    x = x + layer.feed_forward(n)
                     continue
                 q, k, v, gate = at.heads(at.qkv_proj(h), cos, sin)
                 self.cache.k[li, blk, off] = k
                 self.cache.v[li, blk, off] = v
                 o = ops.paged_attention_decode(q, self.cache.k[li], self.cache.v[li], table, seq_lens, 1.0 / math.sqrt(at.d))
-                x = x + at.project_out(o, gate)
-                n = layer.post_attention_layernorm(x)
-                x = x + (layer.mlp(n) if not layer.is_moe else layer.mlp(n, None))
+                n, x = layer.after_attention(x, at.project_out(o, gate))
+                x = x + layer.feed_forward(n)
             x = self.model.norm(x)
         return self.model.logits(x).float()
 
