@@ -331,3 +331,65 @@ def test_router_load_balance_loss_on_the_pipeline_backend(tp, pp):
             else:
                 assert abs(a - b) < 2e-2 and abs(na - nb) < 5e-2 * max(na, 1.0), (single[0.05], curve)
         assert curve[-1][0] < curve[0][0]
+
+
+def _reshard_worker(rank, world, tmp, src, dst):
+    """Trains 2 steps under layout ``src`` = (tp, pp, dp), saves weights and optimizer state, trains 2 more; a model of layout
+    ``dst`` resumes from the files of the first and must continue on the same curve."""
+    from twinkle_b200.model.megatron import MegatronModel
+    from twinkle_b200.models import preset
+    from twinkle_b200.utils.device_mesh import DeviceMesh
+    cfg = preset('tiny-dense', num_hidden_layers=4)
+    g = torch.Generator().manual_seed(13)
+    feats = []          # rows of one length: the mean over data-parallel ranks is then the mean over tokens at every dp size
+    for _ in range(4):
+        ids = torch.randint(0, 1024, (65, ), generator=g)
+        feats.append({'input_ids': ids[:-1].tolist(), 'labels': ids[1:].tolist()})
+
+    def make(tp, pp, dp):
+        mesh = DeviceMesh.from_sizes(tp_size=tp, pp_size=pp, dp_size=dp, sequence_parallel=tp > 1)
+        m = MegatronModel(config=cfg, device_mesh=mesh, seed=0)
+        m.set_optimizer('AdamW', lr=2e-3)
+        m.set_lr_scheduler('CosineWarmupScheduler', num_warmup_steps=1, num_training_steps=8)
+        return m, mesh
+
+    def run(m, mesh, n):
+        dr = mesh.get_data_rank_from_global_rank(rank)
+        sl = mesh.get_slice(len(feats), dr)
+        out = []
+        for _ in range(n):
+            o = m.forward_backward(inputs=feats[sl], micro_batch_size=1)
+            m.clip_grad_and_step(max_grad_norm=1.0)
+            out.append(o['loss'])
+        return dr, out
+
+    a, mesh_a = make(*src)
+    run(a, mesh_a, 2)
+    a.save('mid', tmp, save_optimizer=True)
+    cont = run(a, mesh_a, 2)
+    weights_a = {k: v.float().cpu().numpy() for k, v in a.get_state_dict().items()}     # by value through the result queue
+    b, mesh_b = make(*dst)
+    info = b.resume_from_checkpoint(os.path.join(tmp, 'mid'))
+    resumed = run(b, mesh_b, 2)
+    weights_b = {k: v.float().cpu().numpy() for k, v in b.get_state_dict().items()}
+    return {'cont': cont, 'resumed': resumed, 'info': info, 'wa': weights_a, 'wb': weights_b}
+
+
+@pytest.mark.parametrize('src,dst', [((2, 1, 2), (1, 2, 2)), ((1, 2, 2), (2, 2, 1)), ((2, 2, 1), (1, 1, 4))])
+def test_optimizer_state_loads_into_another_layout(tmp_path, src, dst):
+    res = run_ranks(_reshard_worker, 4, str(tmp_path), src, dst)
+    cont, resumed, wa, wb = {}, {}, {}, {}
+    for r in res:
+        assert r['info']['cur_step'] == 2
+        cont.setdefault(r['cont'][0], r['cont'][1])
+        resumed.setdefault(r['resumed'][0], r['resumed'][1])
+        wa.update(r['wa'])
+        wb.update(r['wb'])
+    # per-rank losses depend on which rows a rank got; their mean over the data-parallel ranks does not
+    mean = lambda d: [sum(v[i] for v in d.values()) / len(d) for i in range(2)]     # noqa: E731
+    for x, y in zip(mean(cont), mean(resumed)):
+        assert abs(x - y) < 2e-5, (cont, resumed)
+    # two more optimizer steps from resharded moments end on the same weights
+    for k in wa:
+        if k in wb:
+            assert abs(wa[k] - wb[k]).max() < 2e-5, k

@@ -20,7 +20,9 @@ megatron-core, TransformerEngine and ``mcore_bridge``; here the pieces are owned
 from __future__ import annotations
 
 import json
+import math
 import os
+import re
 from typing import Any, Dict, List, Optional, Tuple
 
 import torch
@@ -693,16 +695,23 @@ class MegatronModel(TwinkleModel):
 
     # Training state.  Weights go through the bridge into one HF checkpoint; what the optimizer holds is layout-specific
     # (a tensor-parallel shard of a pipeline stage, possibly one data-parallel slice of it), so every rank writes its
-    # own file ``optimizer_tpXX_ppXX_dpXX.pt`` and resuming requires the same layout — as the reference's
-    # megatron-core distributed checkpoint does (``megatron/megatron.py:1078-1243``).
+    # own file ``optimizer_tpXX_ppXX_dpXX.pt`` (the reference's megatron-core distributed checkpoint does the same,
+    # ``megatron/megatron.py:1078-1243``).  A run of the same layout reads its own file back; a run of another tensor /
+    # pipeline / data-parallel layout reassembles every tensor it needs from the files that hold its pieces
+    # (``_load_resharded_state``).
     def _rank_tag(self) -> str:
         return f'tp{self.tp_rank:02d}_pp{self.pp_rank:02d}_dp{self.dp_comm.rank:02d}'
+
+    def _layout(self) -> Dict[str, Any]:
+        return {'tp': self.tp_size, 'pp': self.pp_size, 'vpp': self.vpp, 'dp': self.dp_comm.world_size,
+                'distributed_optimizer': bool(self.use_distributed_optimizer and self.dp_comm.world_size > 1),
+                'ep': int(getattr(self, 'ep_size', 1) or 1), 'etp': int(getattr(self, 'etp_size', 1) or 1)}
 
     def _save_training_state(self, path: str) -> None:
         og = self._group()
         os.makedirs(path, exist_ok=True)
-        state = {'layout': {'tp': self.tp_size, 'pp': self.pp_size, 'vpp': self.vpp, 'dp': self.dp_comm.world_size,
-                            'distributed_optimizer': bool(self.use_distributed_optimizer and self.dp_comm.world_size > 1)},
+        shapes = {n: tuple(p.shape) for n, p in self._params()}
+        state = {'layout': self._layout(), 'shapes': {n: shapes[n] for n in self._state if n in shapes},
                  'optim_steps': og.optim_steps, 'hyper': og.optimizer.state_dict()['param_groups'] if og.optimizer else None,
                  'params': {n: {k: v.detach().cpu() for k, v in st.items()} for n, st in self._state.items()}}
         torch.save(state, os.path.join(path, f'optimizer_{self._rank_tag()}.pt'))
@@ -714,30 +723,91 @@ class MegatronModel(TwinkleModel):
                 json.dump({'checkpoint_version': 1, 'cur_step': og.cur_step, 'gradient_accumulation_steps': og.gradient_accumulation_steps,
                            'consumed_train_samples': og.consumed_train_samples, 'optim_steps': og.optim_steps}, f)
 
+    def _apply_saved_hyper(self, state: Dict[str, Any]) -> None:
+        og = self._group()
+        og.optim_steps = int(state.get('optim_steps', 0))
+        if og.optimizer is None:
+            self.set_optimizer('AdamW')
+        if state.get('hyper'):
+            for g, sv in zip(og.optimizer.param_groups, state['hyper']):
+                for k in ('lr', 'betas', 'eps', 'weight_decay'):
+                    if k in sv:
+                        g[k] = sv[k] if k != 'betas' else tuple(sv[k])
+
+    def _load_resharded_state(self, path: str, files: Dict[Tuple[int, int, int], str]) -> None:
+        """Optimizer state written under another tensor / pipeline / data-parallel layout.  For every parameter this rank
+        holds: the saved data-parallel slices of each saved tensor-parallel rank are joined into that rank's shard, the
+        shards into the full tensor (the same rule that splits weights, ``models/bridge.py::tp_unshard``), and the full
+        tensor is cut again for this rank's shard and data-parallel slice.  Files are memory-mapped, so only the tensors
+        a rank needs are read."""
+        wanted = dict(self._params())
+        if any(getattr(p, '_ep_local', False) for p in wanted.values()):
+            raise NotImplementedError('optimizer state of expert-parallel parameters loads only into the layout that wrote it')
+        found: Dict[str, Dict[Tuple[int, int], Dict[str, torch.Tensor]]] = {}
+        shapes: Dict[str, Dict[int, Tuple[int, ...]]] = {}
+        first = None
+        for (t, pstage, d), fn in sorted(files.items(), key=lambda kv: (kv[0][1], kv[0][0], kv[0][2])):
+            st = torch.load(fn, map_location='cpu', weights_only=True, mmap=True)
+            if first is None:
+                first = st
+            if 'shapes' not in st:
+                raise ValueError(f'{fn} has no shard shapes: it was written by a version that could only resume into the same layout')
+            lay = st.get('layout', {})
+            if lay.get('ep', 1) != 1:
+                raise NotImplementedError('optimizer state written under expert parallelism loads only into the layout that wrote it')
+            for n, tensors in st['params'].items():
+                if n in wanted and (t, d) not in found.setdefault(n, {}):      # a tied embedding sits on two stages: the first one wins
+                    found[n][(t, d)] = tensors
+                    shapes.setdefault(n, {})[t] = tuple(st['shapes'][n])
+        if first is None:
+            raise FileNotFoundError(f'no optimizer_tp*_pp*_dp*.pt files under {path}')
+        self._apply_saved_hyper(first)
+        sharded_dp = bool(first['layout'].get('distributed_optimizer'))
+        state: Dict[str, Dict[str, torch.Tensor]] = {}
+        for n, p in wanted.items():
+            if n not in found:
+                raise KeyError(f'optimizer state of {n} is not in the checkpoint under {path}')
+            tps = sorted({t for t, _ in found[n]})
+            lo, hi = self._state_range(p.numel())
+            entry = {}
+            for key in ('master', 'exp_avg', 'exp_avg_sq'):
+                shards = []
+                for t in tps:
+                    ds = sorted(d for tt, d in found[n] if tt == t)
+                    flat = torch.cat([found[n][(t, d)][key] for d in ds]) if sharded_dp else found[n][(t, ds[0])][key]
+                    shape = shapes[n][t]
+                    shards.append(flat[:math.prod(shape)].reshape(shape))
+                full = tp_unshard(n, shards, self.config)
+                mine = tp_shard(n, full, self.config, self.tp_rank, self.tp_size).reshape(-1)[lo:hi]
+                entry[key] = mine.to(self.device, torch.float32).clone()
+            state[n] = entry
+        self._state = state
+
     def _load_training_state(self, path: str) -> Dict[str, Any]:
         og = self._group()
         f = os.path.join(path, f'optimizer_{self._rank_tag()}.pt')
+        same_layout = False
         if os.path.isfile(f):
             state = torch.load(f, map_location='cpu', weights_only=True)
-            want = {'tp': self.tp_size, 'pp': self.pp_size, 'vpp': self.vpp, 'dp': self.dp_comm.world_size,
-                    'distributed_optimizer': bool(self.use_distributed_optimizer and self.dp_comm.world_size > 1)}
-            if state.get('layout') != want:
-                raise ValueError(f'optimizer state was saved for layout {state.get("layout")}, this run is {want}; '
-                                 'weights can be loaded into any layout, optimizer state only into the one that wrote it')
-            og.optim_steps = int(state.get('optim_steps', 0))
-            if og.optimizer is None:
-                self.set_optimizer('AdamW')
-            if state.get('hyper'):
-                for g, sv in zip(og.optimizer.param_groups, state['hyper']):
-                    for k in ('lr', 'betas', 'eps', 'weight_decay'):
-                        if k in sv:
-                            g[k] = sv[k] if k != 'betas' else tuple(sv[k])
-            self._state = {n: {k: v.to(self.device) for k, v in st.items()} for n, st in state['params'].items()}
+            want = self._layout()
+            same_layout = all(state.get('layout', {}).get(k, want[k] if k in ('ep', 'etp') else None) == v for k, v in want.items())
+            if same_layout:
+                self._apply_saved_hyper(state)
+                self._state = {n: {k: v.to(self.device) for k, v in st.items()} for n, st in state['params'].items()}
+        if not same_layout:
+            import glob
+            files = {}
+            for fn in glob.glob(os.path.join(path, 'optimizer_tp*_pp*_dp*.pt')):
+                m = re.match(r'optimizer_tp(\d+)_pp(\d+)_dp(\d+)\.pt$', os.path.basename(fn))
+                if m:
+                    files[(int(m.group(1)), int(m.group(2)), int(m.group(3)))] = fn
+            if files:
+                self._load_resharded_state(path, files)
         sched = os.path.join(path, 'scheduler.pt')
         if os.path.isfile(sched) and og.lr_scheduler is not None:
             og.lr_scheduler.load_state_dict(torch.load(sched, map_location='cpu', weights_only=True))
         rng = os.path.join(path, f'rng_state_{self._rank_tag()}.pt')
-        if os.path.isfile(rng):
+        if same_layout and os.path.isfile(rng):       # generator states belong to the ranks of the layout that wrote them
             Platform.set_rng_state(torch.load(rng, map_location='cpu', weights_only=True))
         info = {'cur_step': 0, 'consumed_train_samples': 0, 'gradient_accumulation_steps': og.gradient_accumulation_steps}
         ts = os.path.join(path, 'trainer_state.json')

@@ -247,11 +247,11 @@ class MultiLora:
                         r = a.shape[0]
                         if pname == 'q_proj' and m.gate_head_dim:      # [query | gate] rows interleaved per head → two parts
                             b, bg = _split_gate(b, m.gate_head_dim)
+                            m.lora_B['q_gate'][t.slot].zero_()
+                            m.lora_B['q_gate'][t.slot, :, :r].copy_(bg)
                         perm = self._rope_perm(pname, b.shape[0], False)
                         if perm is not None:
                             b = b[perm.to(b.device)]
-                            m.lora_B['q_gate'][t.slot].zero_()
-                            m.lora_B['q_gate'][t.slot, :, :r].copy_(bg)
                         m.lora_A[pname][t.slot].zero_()
                         m.lora_B[pname][t.slot].zero_()
                         m.lora_A[pname][t.slot, :r].copy_(a)
