@@ -109,3 +109,52 @@ def test_tenant_optimizer_state_resumes(tmp_path):
     for cont, again, info in run_ranks(_resume, 2, str(tmp_path)):
         assert info['cur_step'] == 2
         assert cont == again, (cont, again)
+
+
+_MOE_LORA = {'r': 4, 'lora_alpha': 8, 'target_modules': 'all-linear', 'target_parameters': ['mlp.experts.gate_up_proj', 'mlp.experts.down_proj']}
+
+
+def _make_moe(tp, etp=1, sp=True):
+    from twinkle_b200.model.megatron import MultiLoraMegatronModel
+    from twinkle_b200.models import preset
+    from twinkle_b200.utils.device_mesh import DeviceMesh
+    cfg = preset('tiny-moe', num_hidden_layers=2, router_aux_loss_coef=0.0)
+    mesh = DeviceMesh.from_sizes(tp_size=tp, dp_size=1, etp_size=etp, sequence_parallel=sp and tp > 1)
+    return MultiLoraMegatronModel(config=cfg, device_mesh=mesh, seed=0, max_loras=2, max_r=8)
+
+
+def _moe_sharded(rank, world, tmp, etp, sp):
+    m = _make_moe(world, etp, sp)
+    m.add_adapter_to_model('a', os.path.join(tmp, 'warm'))
+    m.set_optimizer('AdamW', lr=5e-3, adapter_name='a')
+    curve = _train(m, 'a', 3, _feats())
+    m.save('out', tmp, adapter_name='a')
+    return curve
+
+
+@pytest.mark.parametrize('etp,sp', [(1, True), (2, True), (2, False)])
+def test_expert_adapters_on_whole_and_split_experts(tmp_path, etp, sp):
+    """Adapters on the fused expert tensors: with the experts whole on every tensor-parallel rank and with every expert's
+    intermediate dimension split over the group, training from a PEFT file written by one process follows the one-process
+    curve and writes the same file back."""
+    from twinkle_b200.utils.safetensors_io import SafetensorLazyLoader
+    tmp = str(tmp_path)
+    m = _make_moe(1)
+    m.add_adapter_to_model('a', dict(_MOE_LORA))
+    m.set_optimizer('AdamW', lr=5e-3, adapter_name='a')
+    _train(m, 'a', 2, _feats())
+    m.save('warm', tmp, adapter_name='a')
+    m = _make_moe(1)
+    m.add_adapter_to_model('a', os.path.join(tmp, 'warm'))
+    m.set_optimizer('AdamW', lr=5e-3, adapter_name='a')
+    ref = _train(m, 'a', 3, _feats())
+    m.save('ref', tmp, adapter_name='a')
+    for curve in run_ranks(_moe_sharded, 2, tmp, etp, sp):
+        for (l0, n0), (l1, n1) in zip(ref, curve):
+            assert abs(l0 - l1) < 3e-4 and abs(n0 - n1) < 3e-3 * max(n0, 1.0), (ref, curve)
+    a, b = SafetensorLazyLoader(os.path.join(tmp, 'ref')), SafetensorLazyLoader(os.path.join(tmp, 'out'))
+    keys = sorted(a.keys())
+    assert keys == sorted(b.keys()) and sum('experts' in k for k in keys) == 2 * 2 * 2      # 2 layers x (gate_up, down) x (A, B)
+    for k in keys:
+        assert a.get(k).shape == b.get(k).shape, k
+        assert torch.allclose(a.get(k), b.get(k), atol=5e-4), (k, float((a.get(k) - b.get(k)).abs().max()))

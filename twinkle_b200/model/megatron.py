@@ -837,6 +837,9 @@ class MultiLoraMegatronModel(MegatronModel):
     Every chunk of this rank carries a slot pool.  On tensor-parallel linears the pools follow the shards: ``A``
     replicated and ``B`` row-sharded on column-parallel linears, ``A`` column-sharded and ``B`` replicated on
     row-parallel ones; gradients of the replicated halves are partial sums and are all-reduced over the TP group.
+    Expert pools (target-parameter LoRA on the fused expert tensors) are whole on every rank while the experts are, and
+    follow the expert shards under expert tensor parallelism (``gate_up``: ``B`` rows of this rank's gate and up slices;
+    ``down``: ``A`` columns of this rank's slice of the intermediate dimension).
     Each tenant has its own optimizer state (fp32 master + Adam moments of its slot slices), gradient norm, progress
     counters and scheduler (``multi_lora_megatron.py:213-291``); adapters are saved and loaded in PEFT format with the
     TP shards and pipeline stages merged into one ``adapter_model.safetensors``."""
@@ -847,9 +850,9 @@ class MultiLoraMegatronModel(MegatronModel):
         from .multi_lora import MultiLora
         self.max_length = max_length
         seed = kwargs.get('seed', 0)
-        if self.etp_size > 1:
-            # expert pools would follow the expert shards (B sliced, A replicated with partial gradients): not wired up
-            raise NotImplementedError('multi-LoRA on the tensor / pipeline backend does not combine with expert tensor parallelism (use etp_size=1)')
+        if self.ep_size > 1:
+            # expert pools would differ per expert-parallel rank (gradients summed over the replica groups only): not wired up
+            raise NotImplementedError('multi-LoRA on the tensor / pipeline backend does not combine with expert parallelism (use ep_size=1)')
         self.pools = [MultiLora(m, max_loras, max_r, seed=seed * 1000 + self.pp_rank * 16 + c) for c, m in enumerate(self.chunks)]
         self._sync_pools()
         self.optimizer_groups = {}
@@ -873,7 +876,7 @@ class MultiLoraMegatronModel(MegatronModel):
             for pool in self.pools:
                 init = pool._initial_A
                 for n, p, mode in self._pool_params_of(pool):
-                    if self.tp_size > 1 and lora_param_is_replicated(n, mode):
+                    if self.tp_size > 1 and lora_param_is_replicated(n, mode, self.etp_size > 1):
                         self.tp_comm.broadcast(p.data, 0)
                     if self.dp_comm.world_size > 1:
                         self.dp_comm.broadcast(p.data, 0)
@@ -959,7 +962,7 @@ class MultiLoraMegatronModel(MegatronModel):
             if p.grad is None:
                 continue
             g = p.grad[slot]
-            rep = lora_param_is_replicated(n, mode)
+            rep = lora_param_is_replicated(n, mode, self.etp_size > 1)
             if self.dp_comm.world_size > 1 or (self.tp_size > 1 and rep):
                 g = g.contiguous()
                 if self.dp_comm.world_size > 1:
@@ -1069,7 +1072,7 @@ class MultiLoraMegatronModel(MegatronModel):
     def _adapter_state_dict(self, adapter_name: str) -> Dict[str, torch.Tensor]:
         """PEFT-named tensors of the tenant for the layers of this pipeline stage, TP shards merged (collective over the
         TP group)."""
-        from ..models.bridge import lora_internal_to_peft
+        from ..models.bridge import lora_expert_to_peft, lora_internal_to_peft
         t = self.pools[0].tenants[adapter_name]
         r = t.config.r
         sd: Dict[str, torch.Tensor] = {}
@@ -1078,6 +1081,25 @@ class MultiLoraMegatronModel(MegatronModel):
                 gname = self._global_name(mod_name, m._layer_offset)
                 prefix = gname.rsplit('.', 1)[0] if '.' in gname else ''
                 mode = getattr(mod, 'tp_mode', None)
+                if not hasattr(mod, 'parts'):           # fused expert tensors
+                    for which in ('gate_up', 'down'):
+                        if not (t.target.matches(f'{gname}.{which}', which) or (t.config.target_parameters and any(
+                                which in tpn for tpn in t.config.target_parameters))):
+                            continue
+                        a = mod.lora[which + '_A'][t.slot, :, :r].detach().contiguous()           # [E, r, in]
+                        b = mod.lora[which + '_B'][t.slot, :, :, :r].detach().contiguous()        # [E, out, r]
+                        if self.etp_size > 1 and which == 'gate_up':      # B: this rank's gate rows, then its up rows
+                            parts = [torch.empty_like(b) for _ in range(self.tp_size)]
+                            dist.all_gather(parts, b, group=self.tp_comm.group)
+                            half = b.shape[1] // 2
+                            b = torch.cat([x[:, :half] for x in parts] + [x[:, half:] for x in parts], 1)
+                        elif self.etp_size > 1:                            # A: this rank's columns of the intermediate dimension
+                            parts = [torch.empty_like(a) for _ in range(self.tp_size)]
+                            dist.all_gather(parts, a, group=self.tp_comm.group)
+                            a = torch.cat(parts, 2)
+                        sd[lora_expert_to_peft(gname, which, 'A')] = a.clone()
+                        sd[lora_expert_to_peft(gname, which, 'B')] = b.clone()
+                    continue
                 for pname, _ in mod.parts:
                     if not t.target.matches(f'{prefix}.{pname}' if prefix else pname, pname):
                         continue
@@ -1138,13 +1160,32 @@ class MultiLoraMegatronModel(MegatronModel):
     @torch.no_grad()
     def _load_adapter(self, adapter_name: str, path: str) -> None:
         """Every rank reads the PEFT file and keeps the shards of the layers it holds."""
-        from ..models.bridge import lora_internal_to_peft
+        from ..models.bridge import lora_expert_to_peft, lora_internal_to_peft
         loader = SafetensorLazyLoader(path)
         t = self.pools[0].tenants[adapter_name]
         for m, pool in zip(self.chunks, self.pools):
             for mod_name, mod in pool.modules:
                 gname = self._global_name(mod_name, m._layer_offset)
                 mode = getattr(mod, 'tp_mode', None)
+                if not hasattr(mod, 'parts'):           # fused expert tensors
+                    for which in ('gate_up', 'down'):
+                        ka, kb = lora_expert_to_peft(gname, which, 'A'), lora_expert_to_peft(gname, which, 'B')
+                        if ka not in loader or kb not in loader:
+                            continue
+                        a, b = loader.get(ka), loader.get(kb)
+                        if self.etp_size > 1 and which == 'gate_up':
+                            half = b.shape[1] // 2
+                            n = half // self.tp_size
+                            b = torch.cat([b[:, self.tp_rank * n:(self.tp_rank + 1) * n], b[:, half + self.tp_rank * n:half + (self.tp_rank + 1) * n]], 1)
+                        elif self.etp_size > 1:
+                            n = a.shape[2] // self.tp_size
+                            a = a[:, :, self.tp_rank * n:(self.tp_rank + 1) * n]
+                        r = a.shape[1]
+                        mod.lora[which + '_A'][t.slot].zero_()
+                        mod.lora[which + '_B'][t.slot].zero_()
+                        mod.lora[which + '_A'][t.slot, :, :r].copy_(a)
+                        mod.lora[which + '_B'][t.slot, :, :, :r].copy_(b)
+                    continue
                 for pname, _ in mod.parts:
                     ka, kb = lora_internal_to_peft(gname, pname, 'A'), lora_internal_to_peft(gname, pname, 'B')
                     if ka not in loader or kb not in loader:

@@ -306,9 +306,13 @@ def apply_tensor_parallel(model, cfg, comm: Communicator, sequence_parallel: boo
     return tp
 
 
-def lora_param_is_replicated(name: str, tp_mode: Optional[str]) -> bool:
-    """Whether an adapter-pool tensor of a tensor-parallel linear is the same on every rank of the group (its gradient is
-    then a partial sum that must be all-reduced): ``A`` of a column-parallel linear and ``B`` of a row-parallel one.
-    The other two are shards."""
+def lora_param_is_replicated(name: str, tp_mode: Optional[str], expert_tp: bool = False) -> bool:
+    """Whether an adapter-pool tensor is the same on every rank of the tensor-parallel group (its gradient is then a
+    partial sum that must be all-reduced): ``A`` of a column-parallel linear and ``B`` of a row-parallel one; the other
+    two are shards.  Expert pools (``…experts.lora.gate_up_A`` …) are whole on every rank unless the experts themselves
+    are split over the group (``expert_tp``): then ``gate_up`` behaves like a column-parallel linear (``B`` holds this
+    rank's rows) and ``down`` like a row-parallel one (``A`` holds this rank's columns)."""
+    if '.lora.' in name:
+        return not expert_tp or name.endswith('gate_up_A') or name.endswith('down_B')
     is_a = 'lora_A' in name
     return (tp_mode == 'col' and is_a) or (tp_mode == 'row' and not is_a) or tp_mode is None
