@@ -1,4 +1,5 @@
 """Helpers to run a function on N CPU ranks (gloo) inside a test."""
+import io
 import os
 import socket
 import sys
@@ -25,7 +26,11 @@ def _entry(rank, world, port, fn, args, q):
         import torch.distributed as dist
         dist.init_process_group('gloo', rank=rank, world_size=world, init_method=f'tcp://127.0.0.1:{port}')
         out = fn(rank, world, *args)
-        q.put((rank, 'ok', out))
+        # by value: tensors put on a queue travel as file descriptors fetched from this process, which may be gone by the
+        # time the parent unpickles them
+        buf = io.BytesIO()
+        torch.save(out, buf)
+        q.put((rank, 'ok', buf.getvalue()))
         dist.barrier()
         dist.destroy_process_group()
     except Exception:
@@ -46,7 +51,7 @@ def run_ranks(fn, world: int, *args, timeout: float = 300.0):
             rank, status, payload = q.get(timeout=timeout)
             if status != 'ok':
                 raise RuntimeError(f'rank {rank} failed:\n{payload}')
-            results[rank] = payload
+            results[rank] = torch.load(io.BytesIO(payload), weights_only=False)
     finally:
         for p in procs:
             p.join(timeout=30)

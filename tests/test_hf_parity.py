@@ -52,6 +52,19 @@ def _cases():
                                     rope_parameters={'rope_type': 'default', 'rope_theta': 10000.0, 'partial_rotary_factor': 0.5}), 'GlmForCausalLM'),
         'glm4': (lambda: T.Glm4Config(head_dim=32, pad_token_id=0, tie_word_embeddings=False, **{k: v for k, v in COMMON.items() if k != 'rope_theta'},
                                       rope_parameters={'rope_type': 'default', 'rope_theta': 10000.0, 'partial_rotary_factor': 0.5}), 'Glm4ForCausalLM'),
+        # Phi-3: q|k|v and gate|up fused in the checkpoint, rotary on three quarters of the head; the long-context variant
+        # divides the frequencies by per-dimension factors (short ones up to the original window, long ones beyond)
+        'phi3': (lambda: T.Phi3Config(pad_token_id=0, tie_word_embeddings=False, **{k: v for k, v in COMMON.items() if k != 'rope_theta'},
+                                      rope_parameters={'rope_type': 'default', 'rope_theta': 10000.0, 'partial_rotary_factor': 0.75}), 'Phi3ForCausalLM'),
+        'phi3_longrope': (lambda: T.Phi3Config(pad_token_id=0, tie_word_embeddings=False, original_max_position_embeddings=64,
+                                               **{k: v for k, v in COMMON.items() if k != 'rope_theta'},
+                                               rope_parameters={'rope_type': 'longrope', 'rope_theta': 10000.0, 'original_max_position_embeddings': 64,
+                                                                'short_factor': [1.0 + 0.05 * i for i in range(16)],
+                                                                'long_factor': [1.5 + 0.2 * i for i in range(16)]}), 'Phi3ForCausalLM'),
+        # Gemma: "1 + w" norms, tanh-GELU gate, embeddings times √hidden, tied head
+        'gemma': (lambda: T.GemmaConfig(head_dim=32, **COMMON), 'GemmaForCausalLM'),
+        'llama_dynamic_ntk': (lambda: T.LlamaConfig(tie_word_embeddings=False, **{**COMMON, 'max_position_embeddings': 64},
+                                                    rope_scaling={'rope_type': 'dynamic', 'factor': 2.0}), 'LlamaForCausalLM'),
         'qwen2_moe_shared': (lambda: T.Qwen2MoeConfig(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=96,
                                                       norm_topk_prob=False, decoder_sparse_step=1, mlp_only_layers=[], **COMMON), 'Qwen2MoeForCausalLM'),
     }
@@ -86,14 +99,15 @@ def _ours(path, ids):
 def test_hf_checkpoint_gives_the_same_logits_here(name, tmp_path):
     hf = _hf_model(name)
     hf.save_pretrained(str(tmp_path / 'hf'), safe_serialization=True)
-    ids = torch.randint(0, 512, (1, 150 if name == 'llama3_rope' else 37), generator=torch.Generator().manual_seed(1))
+    ids = torch.randint(0, 512, (1, 150 if name in ('llama3_rope', 'phi3_longrope', 'llama_dynamic_ntk') else 37), generator=torch.Generator().manual_seed(1))
     with torch.no_grad():
         want = hf(ids).logits[0]
     _, got = _ours(str(tmp_path / 'hf'), ids[0])
     assert torch.allclose(got, want, atol=2e-5), float((got - want).abs().max())
 
 
-@pytest.mark.parametrize('name', ['qwen3', 'qwen3_moe', 'mixtral', 'qwen2_moe_shared', 'qwen3_5', 'qwen3_5_moe', 'qwen3_next', 'glm', 'glm4'])
+@pytest.mark.parametrize('name', ['qwen3', 'qwen3_moe', 'mixtral', 'qwen2_moe_shared', 'qwen3_5', 'qwen3_5_moe', 'qwen3_next', 'glm', 'glm4', 'phi3',
+                                  'phi3_longrope', 'gemma'])
 def test_checkpoint_saved_here_loads_in_transformers(name, tmp_path):
     hf = _hf_model(name)
     hf.save_pretrained(str(tmp_path / 'hf'), safe_serialization=True)
@@ -215,3 +229,47 @@ def test_adapter_trained_here_merges_into_the_hf_model(name, tmp_path):
         theirs = hf(ids[None]).logits[0]
     assert merged >= 7 and not torch.allclose(base, theirs, atol=1e-3)
     assert torch.allclose(ours, theirs, atol=5e-5), float((ours - theirs).abs().max())
+
+
+def test_internlm2_checkpoint_layout(tmp_path):
+    """InternLM2 is the Llama computation under other tensor names, with q, k and v in one ``wqkv`` grouped per key / value
+    head.  Its modelling code is not part of ``transformers``, so the checkpoint is built here from a Llama model by that
+    renaming; it must give the Llama logits, and saving it again must reproduce the file tensor for tensor."""
+    import json
+    import os
+
+    from safetensors.torch import load_file, save_file
+    hf = _hf_model('llama3_rope')
+    cfg = hf.config
+    hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.hidden_size // cfg.num_attention_heads
+    sd, out = hf.state_dict(), {}
+    out['model.tok_embeddings.weight'], out['model.norm.weight'], out['output.weight'] = sd['model.embed_tokens.weight'], sd['model.norm.weight'], sd['lm_head.weight']
+    for i in range(cfg.num_hidden_layers):
+        a, b = f'model.layers.{i}.', f'model.layers.{i}.'
+        q, k, v = (sd[a + f'self_attn.{p}_proj.weight'] for p in 'qkv')
+        g = hq // hkv
+        out[b + 'attention.wqkv.weight'] = torch.cat([q.reshape(hkv, g * d, -1), k.reshape(hkv, d, -1), v.reshape(hkv, d, -1)], 1).reshape(-1, q.shape[1])
+        for src, dst in (('self_attn.o_proj', 'attention.wo'), ('mlp.gate_proj', 'feed_forward.w1'), ('mlp.up_proj', 'feed_forward.w3'),
+                         ('mlp.down_proj', 'feed_forward.w2'), ('input_layernorm', 'attention_norm'), ('post_attention_layernorm', 'ffn_norm')):
+            out[b + dst + '.weight'] = sd[a + src + '.weight']
+    path = str(tmp_path / 'internlm2')
+    os.makedirs(path)
+    save_file({k: v.contiguous() for k, v in out.items()}, os.path.join(path, 'model.safetensors'), metadata={'format': 'pt'})
+    conf = {k: v for k, v in cfg.to_dict().items() if k in ('vocab_size', 'hidden_size', 'intermediate_size', 'num_hidden_layers', 'num_attention_heads',
+                                                            'num_key_value_heads', 'max_position_embeddings', 'rms_norm_eps', 'tie_word_embeddings')}
+    conf.update(model_type='internlm2', architectures=['InternLM2ForCausalLM'], bias=False, rope_theta=10000.0, torch_dtype='float32',
+                rope_scaling={'type': 'dynamic', 'factor': 2.0})
+    with open(os.path.join(path, 'config.json'), 'w') as f:
+        json.dump(conf, f)
+    hf.config.rope_parameters = {'rope_type': 'dynamic', 'factor': 2.0, 'rope_theta': 10000.0}          # the Llama twin of that config
+    hf = transformers.LlamaForCausalLM(hf.config).float().eval()
+    hf.load_state_dict(sd)
+    ids = torch.randint(0, 512, (1, 41), generator=torch.Generator().manual_seed(4))
+    with torch.no_grad():
+        want = hf(ids).logits[0]
+    m, got = _ours(path, ids[0])
+    assert torch.allclose(got, want, atol=2e-5), float((got - want).abs().max())
+    back = load_file(os.path.join(m.save('export', str(tmp_path / 'ours')), 'model.safetensors'))
+    assert sorted(back) == sorted(out)
+    for k in out:
+        assert torch.equal(back[k], out[k]), k

@@ -231,8 +231,7 @@ class MegatronModel(TwinkleModel):
             for name, p in m.named_parameters():
                 g = self._global_name(name, lo)
                 if loader is not None:
-                    src = 'model.embed_tokens.weight' if (g == 'lm_head.weight' and 'lm_head.weight' not in loader) else None
-                    t = loader.get(src) if src else hf_to_internal(g, self.config, loader.get)
+                    t = hf_to_internal(g, self.config, loader.get)       # a head the file does not carry comes from the embedding
                     p.copy_(t.to(p.dtype))
                 elif p.dim() > 1:
                     # the same rule as ``DecoderModel.init_weights``: one stream per (global) parameter name, drawn on the
@@ -680,8 +679,7 @@ class MegatronModel(TwinkleModel):
         loader = SafetensorLazyLoader(path)
         with torch.no_grad():
             for n, p in self.named_parameters():
-                src_head = n == 'lm_head.weight' and 'lm_head.weight' not in loader
-                full = loader.get('model.embed_tokens.weight') if src_head else hf_to_internal(n, self.config, loader.get)
+                full = hf_to_internal(n, self.config, loader.get)
                 if getattr(p, '_ep_local', False) and self.ep_comm is not None:
                     el = p.shape[0]
                     full = full[self.ep_rank * el:(self.ep_rank + 1) * el]

@@ -1005,8 +1005,7 @@ class TransformersModel(TwinkleModel, CheckpointEngineMixin):
             loader = SafetensorLazyLoader(path)
             names = [n for n, _ in self.model.named_parameters() if 'lora' not in n]
             for n in names:
-                t = hf_to_internal(n, self.config, loader.get) if not (n == 'lm_head.weight' and 'lm_head.weight' not in loader) \
-                    else loader.get('model.embed_tokens.weight')
+                t = hf_to_internal(n, self.config, loader.get)       # a head the file does not carry comes from the embedding
                 if self.engine is None or not self.engine.load_full_tensor(n, t):
                     dict(self.model.named_parameters())[n].data.copy_(t.to(self.device))
             loader.close()

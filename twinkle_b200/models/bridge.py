@@ -39,13 +39,45 @@ _MIXTRAL = ((re.compile(r'\.mlp\.experts\.(\d+)\.gate_proj\.'), r'.block_sparse_
             (re.compile(r'\.mlp\.gate\.'), '.block_sparse_moe.gate.'))
 
 
+_INTERNLM2 = (('model.embed_tokens.', 'model.tok_embeddings.'), ('lm_head.', 'output.'), ('.self_attn.qkv_proj.', '.attention.wqkv.'),
+              ('.self_attn.o_proj.', '.attention.wo.'), ('.mlp.gate_proj.', '.feed_forward.w1.'), ('.mlp.up_proj.', '.feed_forward.w3.'),
+              ('.mlp.down_proj.', '.feed_forward.w2.'), ('.input_layernorm.', '.attention_norm.'), ('.post_attention_layernorm.', '.ffn_norm.'))
+
+
 def _family(name: str, cfg: DecoderConfig) -> str:
     """Checkpoint spelling of a tensor name for families that differ from the Qwen / Llama one (Mixtral: ``block_sparse_moe``
-    with ``w1`` = gate, ``w3`` = up, ``w2`` = down)."""
+    with ``w1`` = gate, ``w3`` = up, ``w2`` = down; InternLM2: ``tok_embeddings`` / ``attention.wqkv`` / ``attention.wo`` /
+    ``feed_forward.w1|w3|w2`` / ``attention_norm`` / ``ffn_norm`` / ``output``)."""
     if cfg.model_type == 'mixtral':
         for pat, rep in _MIXTRAL:
             name = pat.sub(rep, name)
+    elif cfg.model_type == 'internlm2':
+        for a, b in _INTERNLM2:
+            if name.startswith(a) or (a[0] == '.' and a in name):
+                name = name.replace(a, b, 1)
     return name
+
+
+def _fused_qkv(cfg: DecoderConfig) -> bool:
+    """Families whose checkpoints keep q, k and v in one tensor: Phi-3 in this package's own ``[q | k | v]`` row order,
+    InternLM2 grouped per key / value head (``[the group's query heads | its key head | its value head]``)."""
+    return cfg.model_type in ('phi3', 'internlm2')
+
+
+def _fused_gate_up(cfg: DecoderConfig) -> bool:
+    """Families whose checkpoints keep ``[gate | up]`` as one tensor."""
+    return cfg.model_type in ('glm', 'glm4', 'phi3')
+
+
+def _wqkv_regroup(t: torch.Tensor, cfg: DecoderConfig, to_hf: bool) -> torch.Tensor:
+    """Row permutation between ``[q | k | v]`` and InternLM2's per-group order."""
+    hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+    g, tail = hq // hkv, tuple(t.shape[1:])
+    if to_hf:
+        q, k, v = t.split([hq * d, hkv * d, hkv * d], dim=0)
+        return torch.cat([q.reshape(hkv, g, d, *tail), k.reshape(hkv, 1, d, *tail), v.reshape(hkv, 1, d, *tail)], 1).reshape(t.shape[0], *tail)
+    x = t.reshape(hkv, g + 2, d, *tail)
+    return torch.cat([x[:, :g].reshape(hq * d, *tail), x[:, g].reshape(hkv * d, *tail), x[:, g + 1].reshape(hkv * d, *tail)], 0)
 
 
 def _split_gdn(cfg: DecoderConfig) -> bool:
@@ -112,6 +144,8 @@ def _internal_to_hf_text(name: str, tensor: torch.Tensor, cfg: DecoderConfig) ->
     if not m:
         raise KeyError(f'no HF mapping for {name}')
     i, rest = int(m.group(1)), m.group(2)
+    if rest in ('self_attn.qkv_proj.weight', 'self_attn.qkv_proj.bias') and _fused_qkv(cfg):
+        return [(_hf_layer(i, rest), _wqkv_regroup(tensor, cfg, True) if cfg.model_type == 'internlm2' else tensor)]
     if rest in ('self_attn.qkv_proj.weight', 'self_attn.qkv_proj.bias'):
         kind = rest.rsplit('.', 1)[1]
         if cfg.attn_output_gate:
@@ -135,7 +169,7 @@ def _internal_to_hf_text(name: str, tensor: torch.Tensor, cfg: DecoderConfig) ->
     if rest == 'self_attn.in_proj_ba.weight' and _split_gdn(cfg):
         b, a = tensor.chunk(2, dim=0)
         return [(_hf_layer(i, 'linear_attn.in_proj_b.weight'), b), (_hf_layer(i, 'linear_attn.in_proj_a.weight'), a)]
-    if rest == 'mlp.gate_up_proj.weight' and cfg.model_type in ('glm', 'glm4'):
+    if rest == 'mlp.gate_up_proj.weight' and _fused_gate_up(cfg):
         return [(_hf_layer(i, rest), tensor)]           # fused [gate | up] in the checkpoint too
     if rest in ('mlp.gate_up_proj.weight', 'mlp.shared_expert.gate_up_proj.weight'):
         g, u = tensor.chunk(2, dim=0)
@@ -177,6 +211,8 @@ def _hf_names_for_text(name: str, cfg: DecoderConfig) -> List[str]:
         return ['lm_head.weight']
     m = _LAYER.match(name)
     i, rest = int(m.group(1)), m.group(2)
+    if rest.startswith('self_attn.qkv_proj.') and _fused_qkv(cfg):
+        return [_hf_layer(i, rest)]
     if rest.startswith('self_attn.qkv_proj.'):
         kind = rest.rsplit('.', 1)[1]
         return [_hf_layer(i, f'self_attn.{p}_proj.{kind}') for p in 'qkv']
@@ -184,7 +220,7 @@ def _hf_names_for_text(name: str, cfg: DecoderConfig) -> List[str]:
         return [_hf_layer(i, 'linear_attn.in_proj_qkv.weight'), _hf_layer(i, 'linear_attn.in_proj_z.weight')]
     if rest == 'self_attn.in_proj_ba.weight' and _split_gdn(cfg):
         return [_hf_layer(i, 'linear_attn.in_proj_b.weight'), _hf_layer(i, 'linear_attn.in_proj_a.weight')]
-    if rest == 'mlp.gate_up_proj.weight' and cfg.model_type in ('glm', 'glm4'):
+    if rest == 'mlp.gate_up_proj.weight' and _fused_gate_up(cfg):
         return [_hf_layer(i, rest)]
     if rest in ('mlp.gate_up_proj.weight', 'mlp.shared_expert.gate_up_proj.weight'):
         pre = rest[:-len('gate_up_proj.weight')]
@@ -206,11 +242,12 @@ def _hf_names_for_text(name: str, cfg: DecoderConfig) -> List[str]:
 
 def hf_to_internal(name: str, cfg: DecoderConfig, get: Callable[[str], torch.Tensor],
                    expert_range: Optional[Tuple[int, int]] = None) -> torch.Tensor:
-    """Assemble one internal tensor from HF tensors fetched by ``get``."""
+    """Assemble one internal tensor from HF tensors fetched by ``get``.  An output head that the checkpoint does not carry
+    (tied embeddings saved once) is read from the embedding."""
     m = _LAYER.match(name)
     rest = m.group(2) if m else ''
     i = int(m.group(1)) if m else -1
-    if cfg.model_type == 'mixtral':
+    if cfg.model_type in ('mixtral', 'internlm2'):
         plain = get
 
         def get(n: str) -> torch.Tensor:  # noqa: F811
@@ -225,6 +262,11 @@ def hf_to_internal(name: str, cfg: DecoderConfig, get: Callable[[str], torch.Ten
                 except KeyError:
                     continue
             raise KeyError(n)
+    if name == 'lm_head.weight':
+        try:
+            return get(hf_names_for(name, cfg)[0])
+        except KeyError:
+            return get(hf_names_for('embed_tokens.weight', cfg)[0])
     if rest in ('mlp.experts.gate_up_proj', 'mlp.experts.down_proj'):
         # checkpoints written by newer transformers keep the experts fused, in this package's own layout
         # ([E, 2I, H] gate|up and [E, H, I]); older ones have one tensor per expert and projection
@@ -249,6 +291,8 @@ def hf_to_internal(name: str, cfg: DecoderConfig, get: Callable[[str], torch.Ten
         lo, hi = expert_range or (0, cfg.num_experts)
         return torch.stack([get(_hf_layer(i, f'mlp.experts.{e}.down_proj.weight')) for e in range(lo, hi)])
     parts = [get(n) for n in hf_names_for(name, cfg)]
+    if rest.startswith('self_attn.qkv_proj.') and cfg.model_type == 'internlm2':
+        return _wqkv_regroup(parts[0], cfg, False)
     if rest.startswith('self_attn.qkv_proj.') and cfg.rope_interleaved:
         parts = [parts[0][rope_row_perm(cfg, cfg.num_attention_heads, False)], parts[1][rope_row_perm(cfg, cfg.num_key_value_heads, False)], parts[2]]
     if rest.startswith('self_attn.qkv_proj.') and cfg.attn_output_gate:

@@ -16,7 +16,8 @@ from typing import List, Any, Dict, Optional
 # config.json ``model_type`` values whose layer maths is what ``models/decoder.py`` computes (each checked against transformers)
 SUPPORTED_MODEL_TYPES = frozenset({'llama', 'mistral', 'mixtral', 'qwen2', 'qwen2_moe', 'qwen3', 'qwen3_moe', 'seed_oss', 'qwen2_vl', 'qwen2_vl_text',
                                    'qwen2_5_vl', 'qwen2_5_vl_text', 'qwen3_vl', 'qwen3_vl_text', 'qwen3_vl_moe', 'qwen3_vl_moe_text',
-                                   'qwen3_5', 'qwen3_5_text', 'qwen3_5_moe', 'qwen3_5_moe_text', 'qwen3_next', 'glm', 'glm4'})
+                                   'qwen3_5', 'qwen3_5_text', 'qwen3_5_moe', 'qwen3_5_moe_text', 'qwen3_next', 'glm', 'glm4',
+                                   'phi3', 'internlm2', 'internlm3', 'gemma'})
 
 
 def _rope_scaling_of(cfg: Dict[str, Any]) -> Optional[Dict[str, Any]]:
@@ -29,8 +30,11 @@ def _rope_scaling_of(cfg: Dict[str, Any]) -> Optional[Dict[str, Any]]:
         return None
     out = {k: v for k, v in rs.items() if k != 'rope_theta'}
     out.setdefault('rope_type', kind)
-    if kind in ('llama3', 'yarn') and not out.get('original_max_position_embeddings'):
-        out['original_max_position_embeddings'] = cfg.get('max_position_embeddings', 4096)
+    if kind in ('llama3', 'yarn', 'longrope') and not out.get('original_max_position_embeddings'):
+        out['original_max_position_embeddings'] = cfg.get('original_max_position_embeddings') or cfg.get('max_position_embeddings', 4096)
+    if kind in ('dynamic', 'longrope'):      # these two compare the sequence length with the model's window
+        out.setdefault('max_position_embeddings', cfg.get('max_position_embeddings', 4096))
+    out.pop('partial_rotary_factor', None)
     return out
 
 
@@ -59,6 +63,13 @@ class DecoderConfig:
     # one fused tensor in the checkpoint, and ``glm4`` norms each sub-layer's output before the residual add
     rope_interleaved: bool = False
     sandwich_norm: bool = False
+    # Gemma: gate activation of the feed-forward block ('silu' | 'gelu_pytorch_tanh') and the factor √hidden on the
+    # token embeddings (rounded to the compute dtype, as the Hugging Face model forms it)
+    hidden_act: str = 'silu'
+    embed_scale: float = 1.0
+    # attention window of checkpoints trained with one (Mistral-7B-v0.1, Phi-3-mini): rows longer than the window are
+    # refused — every key inside the window is what the kernels here compute
+    sliding_window: Optional[int] = None
     # MoE (num_experts == 0 → dense)
     num_experts: int = 0
     num_experts_per_tok: int = 8
@@ -155,6 +166,14 @@ class DecoderConfig:
         if q35 and vision is not None:
             vision = None        # the language model of a Qwen3.5 checkpoint trains without its tower here (text-only batches)
         heads = cfg.get('num_attention_heads', 32)
+        window = cfg.get('sliding_window')
+        if mt.startswith('qwen') and not cfg.get('use_sliding_window'):
+            window = None                    # the Qwen configs carry a window size that is switched off by default
+        act = cfg.get('hidden_activation') or cfg.get('hidden_act') or 'silu'
+        if mt == 'gemma':
+            act = 'gelu_pytorch_tanh'        # what the Hugging Face model runs whatever the (legacy) field says
+        if act not in ('silu', 'gelu_pytorch_tanh'):
+            raise NotImplementedError(f'feed-forward activation {act!r} is not supported (silu and gelu_pytorch_tanh are)')
         out = cls(
             vocab_size=cfg.get('vocab_size', 151936), hidden_size=cfg.get('hidden_size', 4096),
             intermediate_size=cfg.get('intermediate_size', 12288), num_hidden_layers=cfg.get('num_hidden_layers', 36),
@@ -162,7 +181,10 @@ class DecoderConfig:
             head_dim=cfg.get('head_dim') or cfg.get('hidden_size', 4096) // heads, rms_norm_eps=cfg.get('rms_norm_eps', 1e-6),
             rope_theta=float(cfg.get('rope_theta', (cfg.get('rope_parameters') or {}).get('rope_theta', 1e6))),
             rope_scaling=_rope_scaling_of(cfg), tie_word_embeddings=bool(cfg.get('tie_word_embeddings', False)),
-            qk_norm=mt.startswith('qwen3'), attention_bias=bool(cfg.get('attention_bias', mt.startswith('qwen2'))),
+            qk_norm=mt.startswith('qwen3'),
+            attention_bias=bool(cfg.get('attention_bias', cfg.get('qkv_bias', cfg.get('bias', False)) if mt.startswith('internlm') else mt.startswith('qwen2'))),
+            hidden_act=act, embed_scale=float(cfg.get('embed_scale', cfg.get('hidden_size', 4096)**0.5 if mt == 'gemma' else 1.0)),
+            sliding_window=int(window) if window else None,
             num_experts=cfg.get('num_experts', cfg.get('num_local_experts', 0)) or 0,
             num_experts_per_tok=cfg.get('num_experts_per_tok', 8),
             moe_intermediate_size=cfg.get('moe_intermediate_size', cfg.get('intermediate_size', 768) if mt == 'mixtral' else 768),
@@ -201,7 +223,7 @@ class DecoderConfig:
             'num_hidden_layers': self.num_hidden_layers, 'num_attention_heads': self.num_attention_heads,
             'num_key_value_heads': self.num_key_value_heads, 'head_dim': self.head_dim, 'rms_norm_eps': self.rms_norm_eps,
             'rope_theta': self.rope_theta, 'tie_word_embeddings': self.tie_word_embeddings, 'attention_bias': self.attention_bias,
-            'hidden_act': 'silu', 'initializer_range': self.initializer_range, 'torch_dtype': self.torch_dtype,
+            'hidden_act': self.hidden_act, 'initializer_range': self.initializer_range, 'torch_dtype': self.torch_dtype,
             'max_position_embeddings': self.max_position_embeddings,
         }
         if self.is_moe:
@@ -214,6 +236,19 @@ class DecoderConfig:
                 d.update(num_local_experts=self.num_experts, intermediate_size=self.moe_intermediate_size, sliding_window=None)
         if self.rms_norm_offset:
             d['rms_norm_offset'] = self.rms_norm_offset
+        if self.sliding_window:
+            d['sliding_window'] = self.sliding_window
+        if self.model_type == 'phi3':
+            d.update(architectures=['Phi3ForCausalLM'], partial_rotary_factor=self.partial_rotary_factor,
+                     pad_token_id=self.pad_token_id, sliding_window=self.sliding_window,
+                     original_max_position_embeddings=(self.rope_scaling or {}).get('original_max_position_embeddings', self.max_position_embeddings))
+        elif self.model_type == 'gemma':
+            d.update(architectures=['GemmaForCausalLM'], hidden_activation=self.hidden_act)
+            d.pop('rms_norm_offset', None)
+        elif self.model_type == 'internlm2':
+            d.update(architectures=['InternLM2ForCausalLM'], bias=self.attention_bias)
+        elif self.model_type == 'internlm3':
+            d.update(architectures=['InternLM3ForCausalLM'], qkv_bias=self.attention_bias, bias=False)
         if self.rope_scaling:
             d['rope_scaling'] = dict(self.rope_scaling)
         if self.vision:

@@ -128,11 +128,12 @@ class MLP(nn.Module):
         i = intermediate or cfg.intermediate_size
         self.gate_up_proj = Linear(cfg.hidden_size, 2 * i, parts=[('gate_proj', i), ('up_proj', i)])
         self.down_proj = Linear(i, cfg.hidden_size, name='down_proj')
+        self.act = ops.geglu if cfg.hidden_act.startswith('gelu') else ops.swiglu
 
     def forward(self, x: torch.Tensor, value_unused: bool = True) -> torch.Tensor:
         """``value_unused=True`` (the block's output only feeds the residual add) lets a recompute pass skip the last GEMM;
         callers that multiply or otherwise read the output pass ``False``."""
-        return self.down_proj(ops.swiglu(self.gate_up_proj(x)), value_unused=value_unused)
+        return self.down_proj(self.act(self.gate_up_proj(x)), value_unused=value_unused)
 
 
 class Experts(nn.Module):
@@ -380,14 +381,21 @@ class DecoderModel(nn.Module):
         return self.lm_head.weight if self.lm_head is not None else self.embed_tokens.weight
 
     # ------------------------------------------------------------ forward
+    def embed_ids(self, ids: torch.Tensor) -> torch.Tensor:
+        """Token embeddings, times the family's factor (Gemma: √hidden, rounded to the embeddings' dtype first)."""
+        if self.tp is not None:
+            from ..parallel.tensor import vocab_parallel_embedding
+            x = vocab_parallel_embedding(ids, self.embed_tokens.weight, self.tp)
+        else:
+            x = self.embed_tokens(ids)
+        if self.cfg.embed_scale != 1.0:
+            x = x * torch.tensor(self.cfg.embed_scale, dtype=x.dtype, device=x.device)
+        return x
+
     def embed(self, batch: PackedBatch) -> torch.Tensor:
         if batch.inputs_embeds is not None:
             return batch.inputs_embeds
-        if self.tp is not None:
-            from ..parallel.tensor import vocab_parallel_embedding
-            x = vocab_parallel_embedding(batch.input_ids, self.embed_tokens.weight, self.tp)
-        else:
-            x = self.embed_tokens(batch.input_ids)
+        x = self.embed_ids(batch.input_ids)
         if batch.pixel_values is not None and self.visual is not None:
             feats, deep = self.visual(batch.pixel_values, batch.image_grid_thw, return_deepstack=True)
             if batch.vision_rows is not None:
@@ -402,6 +410,9 @@ class DecoderModel(nn.Module):
         return x
 
     def forward(self, batch: PackedBatch, hidden: Optional[torch.Tensor] = None, kv_sink=None) -> torch.Tensor:
+        if self.cfg.sliding_window and int(batch.max_seqlen) > self.cfg.sliding_window:
+            raise NotImplementedError(f'a row of {int(batch.max_seqlen)} tokens exceeds the attention window ({self.cfg.sliding_window}) this '
+                                      'checkpoint was trained with; windowed attention is not implemented — split or truncate the rows')
         x = self.embed(batch) if hidden is None else hidden
         if batch.position_ids.dim() == 2:  # [3, T] (time, height, width) positions of a vision-language batch
             from .vision import mrope_tables

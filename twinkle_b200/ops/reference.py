@@ -28,7 +28,8 @@ def add_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, e
 
 
 # ---------------------------------------------------------------------- rope
-def rope_inv_freq(head_dim: int, theta: float, scaling: Optional[dict] = None, device=None) -> Tuple[torch.Tensor, float]:
+def rope_inv_freq(head_dim: int, theta: float, scaling: Optional[dict] = None, device=None,
+                  seq_len: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, float]:
     """Inverse frequencies ``[head_dim/2]`` and the factor applied to cos/sin, for plain RoPE or a long-context variant
     given as a Hugging Face ``rope_scaling`` mapping (``rope_type`` / ``type``):
 
@@ -37,8 +38,14 @@ def rope_inv_freq(head_dim: int, theta: float, scaling: Optional[dict] = None, d
       ``original_max / high_freq_factor`` unchanged, a linear blend between;
     * ``yarn``: per-dimension blend of interpolated (÷ ``factor``) and original frequencies along a ramp between the
       dimensions that complete ``beta_fast`` and ``beta_slow`` rotations over the original window; cos/sin scaled by
-      ``attention_factor`` (default ``0.1·ln(factor) + 1``).
+      ``attention_factor`` (default ``0.1·ln(factor) + 1``);
+    * ``dynamic`` (NTK): the base grows with the sequence once it exceeds ``max_position_embeddings``:
+      ``θ · (factor · L / max − (factor − 1)) ^ (d / (d − 2))``;
+    * ``longrope`` (Phi-3 long-context): per-dimension divisors ``short_factor`` up to ``original_max_position_embeddings``
+      tokens and ``long_factor`` beyond, cos/sin scaled by ``√(1 + ln(factor) / ln(original_max))``.
 
+    The last two depend on the sequence length ``seq_len`` (a 0-dim tensor: largest position + 1, as Hugging Face takes
+    it; chosen on the device, no host read); without it they give their short-sequence form.
     ``default`` / ``None`` give plain RoPE. Other types raise."""
     import math
     inv = 1.0 / (theta**(torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
@@ -77,12 +84,33 @@ def rope_inv_freq(head_dim: int, theta: float, scaling: Optional[dict] = None, d
         ramp = ((torch.arange(head_dim // 2, dtype=torch.float32, device=device) - low) / (high - low)).clamp(0, 1)
         keep = 1 - ramp                                  # 1 → original frequency, 0 → interpolated
         return inv / factor * (1 - keep) + inv * keep, float(att)
-    raise NotImplementedError(f'rope scaling type {kind!r} is not supported (default, linear, llama3, yarn are)')
+    if kind == 'dynamic':
+        mx = float(scaling.get('max_position_embeddings', 0) or 0)
+        if seq_len is None or mx <= 0 or head_dim <= 2:
+            return inv, 1.0
+        grow = (factor * seq_len.float().clamp_min(mx) / mx - (factor - 1.0))**(head_dim / (head_dim - 2))
+        expo = torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim
+        return 1.0 / ((theta * grow)**expo), 1.0
+    if kind == 'longrope':
+        orig = float(scaling.get('original_max_position_embeddings') or scaling.get('max_position_embeddings', 4096))
+        short = torch.tensor(scaling['short_factor'], dtype=torch.float32, device=device)
+        ext = short
+        if seq_len is not None:
+            ext = torch.where(seq_len > orig, torch.tensor(scaling['long_factor'], dtype=torch.float32, device=device), short)
+        f = scaling.get('factor') or float(scaling.get('max_position_embeddings', orig)) / orig
+        att = scaling.get('attention_factor')
+        if att is None:
+            att = 1.0 if f <= 1.0 else math.sqrt(1 + math.log(f) / math.log(orig))
+        return inv / ext, float(att)
+    raise NotImplementedError(f'rope scaling type {kind!r} is not supported (default, linear, llama3, yarn, dynamic, longrope are)')
 
 
 def rope_tables(positions: torch.Tensor, head_dim: int, theta: float = 1e6, scaling: Optional[dict] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """cos/sin ``[T, head_dim/2]`` in fp32 for integer ``positions [T]`` (see :func:`rope_inv_freq` for ``scaling``)."""
-    inv_freq, att = rope_inv_freq(head_dim, theta, scaling, positions.device)
+    seq_len = None
+    if scaling and scaling.get('rope_type', scaling.get('type')) in ('dynamic', 'longrope') and positions.numel():
+        seq_len = positions.max() + 1
+    inv_freq, att = rope_inv_freq(head_dim, theta, scaling, positions.device, seq_len)
     ang = positions.float()[:, None] * inv_freq[None, :]
     if att != 1.0:
         return ang.cos() * att, ang.sin() * att

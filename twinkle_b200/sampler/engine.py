@@ -170,7 +170,7 @@ class NativeEngine:
         cfg, B = self.cfg, tokens.shape[0]
         # ``positions`` index the KV cache; the rotary position differs from it after a prompt with images
         cos, sin = ops.rope_tables(positions if rope_positions is None else rope_positions, cfg.rotary_dim, cfg.rope_theta, cfg.rope_scaling)
-        x = self.model.embed_tokens(tokens)
+        x = self.model.embed_ids(tokens)
         blk = table.gather(1, (positions // self.cache.block_size).unsqueeze(1)).squeeze(1).long()
         off = positions % self.cache.block_size
         with lora_batch(lora):
@@ -323,6 +323,9 @@ class NativeEngine:
         responses = [SampleResponse() for _ in prompts]
         seqs: List[_Seq] = []
         for i, (pr, sp) in enumerate(zip(prompts, params)):
+            if self.cfg.sliding_window and len(pr) + int(sp.max_tokens or 0) > self.cfg.sliding_window:
+                raise NotImplementedError(f'prompt {i}: {len(pr)} prompt + {sp.max_tokens} new tokens exceed the attention window '
+                                          f'({self.cfg.sliding_window}) this checkpoint was trained with; windowed attention is not implemented')
             lo = (lora[i] if lora else None) or {}
             for n in range(sp.num_samples):
                 g = None
