@@ -65,6 +65,20 @@ def _cases():
         'gemma': (lambda: T.GemmaConfig(head_dim=32, **COMMON), 'GemmaForCausalLM'),
         'llama_dynamic_ntk': (lambda: T.LlamaConfig(tie_word_embeddings=False, **{**COMMON, 'max_position_embeddings': 64},
                                                     rope_scaling={'rope_type': 'dynamic', 'factor': 2.0}), 'LlamaForCausalLM'),
+        # DeepSeek-V3: latent attention (query bottleneck, shared rotary key head, 48-wide scores / 24-wide values), a dense first
+        # layer, sigmoid router with selection bias and expert groups, ungated shared expert
+        'deepseek_v3': (lambda: T.DeepseekV3Config(moe_intermediate_size=64, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2, n_group=4,
+                                                   topk_group=2, first_k_dense_replace=1, q_lora_rank=48, kv_lora_rank=32, qk_nope_head_dim=32,
+                                                   qk_rope_head_dim=16, v_head_dim=24, routed_scaling_factor=2.5, norm_topk_prob=True,
+                                                   tie_word_embeddings=False, **{**COMMON, 'num_hidden_layers': 3, 'num_key_value_heads': 4}),
+                        'DeepseekV3ForCausalLM'),
+        'deepseek_v3_yarn': (lambda: T.DeepseekV3Config(moe_intermediate_size=64, n_routed_experts=4, n_shared_experts=2, num_experts_per_tok=2, n_group=1,
+                                                        topk_group=1, first_k_dense_replace=0, q_lora_rank=None, kv_lora_rank=32, qk_nope_head_dim=32,
+                                                        qk_rope_head_dim=16, v_head_dim=32, routed_scaling_factor=1.0, norm_topk_prob=False,
+                                                        tie_word_embeddings=False, **{**COMMON, 'num_key_value_heads': 4, 'max_position_embeddings': 4096},
+                                                        rope_scaling={'rope_type': 'yarn', 'factor': 40.0, 'beta_fast': 32, 'beta_slow': 1, 'mscale': 1.0,
+                                                                      'mscale_all_dim': 1.0, 'original_max_position_embeddings': 64}),
+                             'DeepseekV3ForCausalLM'),
         'qwen2_moe_shared': (lambda: T.Qwen2MoeConfig(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=96,
                                                       norm_topk_prob=False, decoder_sparse_step=1, mlp_only_layers=[], **COMMON), 'Qwen2MoeForCausalLM'),
     }
@@ -83,6 +97,9 @@ def _hf_model(name):
             torch.nn.init.normal_(p, 1.0, 0.1)
         elif p.dim() == 1:
             torch.nn.init.normal_(p, 0.0, 0.1)
+    for n, b in hf.named_buffers():
+        if n.endswith('e_score_correction_bias'):      # the selection bias is a buffer there; non-zero, so that it matters
+            torch.nn.init.normal_(b, 0.0, 0.2)
     return hf
 
 
@@ -99,7 +116,7 @@ def _ours(path, ids):
 def test_hf_checkpoint_gives_the_same_logits_here(name, tmp_path):
     hf = _hf_model(name)
     hf.save_pretrained(str(tmp_path / 'hf'), safe_serialization=True)
-    ids = torch.randint(0, 512, (1, 150 if name in ('llama3_rope', 'phi3_longrope', 'llama_dynamic_ntk') else 37), generator=torch.Generator().manual_seed(1))
+    ids = torch.randint(0, 512, (1, 150 if name in ('llama3_rope', 'phi3_longrope', 'llama_dynamic_ntk', 'deepseek_v3_yarn') else 37), generator=torch.Generator().manual_seed(1))
     with torch.no_grad():
         want = hf(ids).logits[0]
     _, got = _ours(str(tmp_path / 'hf'), ids[0])
@@ -107,7 +124,7 @@ def test_hf_checkpoint_gives_the_same_logits_here(name, tmp_path):
 
 
 @pytest.mark.parametrize('name', ['qwen3', 'qwen3_moe', 'mixtral', 'qwen2_moe_shared', 'qwen3_5', 'qwen3_5_moe', 'qwen3_next', 'glm', 'glm4', 'phi3',
-                                  'phi3_longrope', 'gemma'])
+                                  'phi3_longrope', 'gemma', 'deepseek_v3', 'deepseek_v3_yarn'])
 def test_checkpoint_saved_here_loads_in_transformers(name, tmp_path):
     hf = _hf_model(name)
     hf.save_pretrained(str(tmp_path / 'hf'), safe_serialization=True)

@@ -46,11 +46,14 @@ _INTERNLM2 = (('model.embed_tokens.', 'model.tok_embeddings.'), ('lm_head.', 'ou
 
 def _family(name: str, cfg: DecoderConfig) -> str:
     """Checkpoint spelling of a tensor name for families that differ from the Qwen / Llama one (Mixtral: ``block_sparse_moe``
-    with ``w1`` = gate, ``w3`` = up, ``w2`` = down; InternLM2: ``tok_embeddings`` / ``attention.wqkv`` / ``attention.wo`` /
+    with ``w1`` = gate, ``w3`` = up, ``w2`` = down; DeepSeek-V3: ``shared_experts`` and the router's selection bias under
+    ``mlp.gate``; InternLM2: ``tok_embeddings`` / ``attention.wqkv`` / ``attention.wo`` /
     ``feed_forward.w1|w3|w2`` / ``attention_norm`` / ``ffn_norm`` / ``output``)."""
     if cfg.model_type == 'mixtral':
         for pat, rep in _MIXTRAL:
             name = pat.sub(rep, name)
+    elif cfg.model_type in ('deepseek_v3', 'kimi_k2'):
+        name = name.replace('.mlp.shared_expert.', '.mlp.shared_experts.').replace('.mlp.e_score_correction_bias', '.mlp.gate.e_score_correction_bias')
     elif cfg.model_type == 'internlm2':
         for a, b in _INTERNLM2:
             if name.startswith(a) or (a[0] == '.' and a in name):
@@ -247,7 +250,7 @@ def hf_to_internal(name: str, cfg: DecoderConfig, get: Callable[[str], torch.Ten
     m = _LAYER.match(name)
     rest = m.group(2) if m else ''
     i = int(m.group(1)) if m else -1
-    if cfg.model_type in ('mixtral', 'internlm2'):
+    if cfg.model_type in ('mixtral', 'internlm2', 'deepseek_v3', 'kimi_k2'):
         plain = get
 
         def get(n: str) -> torch.Tensor:  # noqa: F811

@@ -8,6 +8,7 @@ One config class covers Qwen3 dense, Qwen3-MoE and Llama/Qwen2-style decoders
 from __future__ import annotations
 
 import json
+import math
 import os
 from dataclasses import asdict, dataclass, field
 from typing import List, Any, Dict, Optional
@@ -17,7 +18,7 @@ from typing import List, Any, Dict, Optional
 SUPPORTED_MODEL_TYPES = frozenset({'llama', 'mistral', 'mixtral', 'qwen2', 'qwen2_moe', 'qwen3', 'qwen3_moe', 'seed_oss', 'qwen2_vl', 'qwen2_vl_text',
                                    'qwen2_5_vl', 'qwen2_5_vl_text', 'qwen3_vl', 'qwen3_vl_text', 'qwen3_vl_moe', 'qwen3_vl_moe_text',
                                    'qwen3_5', 'qwen3_5_text', 'qwen3_5_moe', 'qwen3_5_moe_text', 'qwen3_next', 'glm', 'glm4',
-                                   'phi3', 'internlm2', 'internlm3', 'gemma'})
+                                   'phi3', 'internlm2', 'internlm3', 'gemma', 'deepseek_v3', 'kimi_k2'})
 
 
 def _rope_scaling_of(cfg: Dict[str, Any]) -> Optional[Dict[str, Any]]:
@@ -77,6 +78,27 @@ class DecoderConfig:
     norm_topk_prob: bool = True
     router_aux_loss_coef: float = 0.0
     shared_expert_intermediate_size: int = 0
+    # DeepSeek-V3 style routing: sigmoid scores, a per-expert selection bias that is not trained by the loss, experts in
+    # ``n_group`` groups of which the ``topk_group`` best (by their two best biased scores) stay eligible, weights scaled by
+    # ``routed_scaling_factor``; the first ``first_k_dense_replace`` layers keep a dense feed-forward block; the shared
+    # expert has no gate of its own
+    router_scoring: str = 'softmax'
+    router_bias: bool = False
+    n_group: int = 1
+    topk_group: int = 1
+    routed_scaling_factor: float = 1.0
+    first_k_dense_replace: int = 0
+    shared_expert_gate: bool = True
+    # multi-head latent attention (DeepSeek-V2/V3): queries through a rank-``q_lora_rank`` bottleneck (None = a plain
+    # projection), keys / values expanded from one rank-``kv_lora_rank`` latent per token (0 = ordinary attention); a head's
+    # query / key is ``qk_nope_head_dim`` position-free dims plus ``qk_rope_head_dim`` rotary dims whose key part is shared
+    # by all heads; values are ``v_head_dim`` wide
+    q_lora_rank: Optional[int] = None
+    kv_lora_rank: int = 0
+    qk_nope_head_dim: int = 128
+    qk_rope_head_dim: int = 64
+    v_head_dim: int = 128
+    mla_rope_interleave: bool = True
     initializer_range: float = 0.02
     model_type: str = 'qwen3'
     torch_dtype: str = 'bfloat16'
@@ -110,6 +132,26 @@ class DecoderConfig:
         return self.num_experts > 0
 
     @property
+    def is_mla(self) -> bool:
+        return self.kv_lora_rank > 0
+
+    def layer_is_moe(self, layer_idx: int) -> bool:
+        return self.num_experts > 0 and layer_idx >= self.first_k_dense_replace
+
+    @property
+    def attn_scale(self) -> float:
+        """Softmax scale of the attention scores: ``1/√d`` of the query / key width; DeepSeek's YaRN variant multiplies
+        it by the square of ``0.1·mscale_all_dim·ln(factor) + 1``."""
+        if not self.is_mla:
+            return self.head_dim**-0.5
+        sc = (self.qk_nope_head_dim + self.qk_rope_head_dim)**-0.5
+        rs = self.rope_scaling or {}
+        if rs.get('mscale_all_dim') and float(rs.get('factor', 1.0)) > 1.0:
+            m = 0.1 * float(rs['mscale_all_dim']) * math.log(float(rs['factor'])) + 1.0
+            sc = sc * m * m
+        return sc
+
+    @property
     def q_size(self) -> int:
         return self.num_attention_heads * self.head_dim
 
@@ -117,30 +159,39 @@ class DecoderConfig:
     def kv_size(self) -> int:
         return self.num_key_value_heads * self.head_dim
 
+    def _attn_weights(self) -> int:
+        h, nh = self.hidden_size, self.num_attention_heads
+        if self.is_mla:
+            qk = self.qk_nope_head_dim + self.qk_rope_head_dim
+            q = h * self.q_lora_rank + self.q_lora_rank * nh * qk if self.q_lora_rank else h * nh * qk
+            return q + h * (self.kv_lora_rank + self.qk_rope_head_dim) + self.kv_lora_rank * nh * (self.qk_nope_head_dim + self.v_head_dim) + nh * self.v_head_dim * h
+        return h * (self.q_size + 2 * self.kv_size) + self.q_size * h + (self.q_size * h if self.attn_output_gate else 0)
+
     def num_params(self) -> int:
         h, L = self.hidden_size, self.num_hidden_layers
-        attn = h * (self.q_size + 2 * self.kv_size) + self.q_size * h + (2 * self.head_dim if self.qk_norm else 0)
-        if self.is_moe:
-            ffn = self.num_experts * 3 * h * self.moe_intermediate_size + h * self.num_experts
-        else:
-            ffn = 3 * h * self.intermediate_size
-        per_layer = attn + ffn + 2 * h
+        attn = self._attn_weights() + (2 * self.head_dim if self.qk_norm else 0)
+        moe = self.num_experts * 3 * h * self.moe_intermediate_size + h * self.num_experts + 3 * h * self.shared_expert_intermediate_size
+        dense = 3 * h * self.intermediate_size
+        n_moe = sum(self.layer_is_moe(i) for i in range(L))
         emb = self.vocab_size * h * (1 if self.tie_word_embeddings else 2)
-        return L * per_layer + emb + h
+        return L * (attn + 2 * h) + n_moe * moe + (L - n_moe) * dense + emb + h
 
     @property
     def rotary_dim(self) -> int:
         """Leading dims of a head that carry the rotary embedding (even; the whole head unless ``partial_rotary_factor`` < 1)."""
+        if self.is_mla:
+            return self.qk_rope_head_dim
         return self.head_dim if self.partial_rotary_factor >= 1.0 else int(self.head_dim * self.partial_rotary_factor) // 2 * 2
 
     def flops_per_token(self, avg_context: float = 0.0) -> float:
         """Forward+backward matmul FLOPs per token (6·N_active + attention)."""
         h, L = self.hidden_size, self.num_hidden_layers
-        attn_w = h * (self.q_size + 2 * self.kv_size) + self.q_size * h
-        ffn_w = (self.num_experts_per_tok * 3 * h * self.moe_intermediate_size + h * self.num_experts) if self.is_moe \
-            else 3 * h * self.intermediate_size
-        dense = L * (attn_w + ffn_w) + self.vocab_size * h
-        attn = L * 2 * self.q_size * avg_context  # QKᵀ and PV, causal average context
+        attn_w = self._attn_weights()
+        moe_w = self.num_experts_per_tok * 3 * h * self.moe_intermediate_size + h * self.num_experts + 3 * h * self.shared_expert_intermediate_size
+        n_moe = sum(self.layer_is_moe(i) for i in range(L))
+        dense = L * attn_w + n_moe * moe_w + (L - n_moe) * 3 * h * self.intermediate_size + self.vocab_size * h
+        qk_v = (self.qk_nope_head_dim + self.qk_rope_head_dim + self.v_head_dim) * self.num_attention_heads if self.is_mla else 2 * self.q_size
+        attn = L * qk_v * avg_context  # QKᵀ and PV, causal average context
         return 6.0 * dense + 6.0 * attn
 
     # ---------------------------------------------------------------- HF I/O
@@ -166,6 +217,7 @@ class DecoderConfig:
         if q35 and vision is not None:
             vision = None        # the language model of a Qwen3.5 checkpoint trains without its tower here (text-only batches)
         heads = cfg.get('num_attention_heads', 32)
+        dsv3 = mt in ('deepseek_v3', 'kimi_k2')
         window = cfg.get('sliding_window')
         if mt.startswith('qwen') and not cfg.get('use_sliding_window'):
             window = None                    # the Qwen configs carry a window size that is switched off by default
@@ -178,18 +230,26 @@ class DecoderConfig:
             vocab_size=cfg.get('vocab_size', 151936), hidden_size=cfg.get('hidden_size', 4096),
             intermediate_size=cfg.get('intermediate_size', 12288), num_hidden_layers=cfg.get('num_hidden_layers', 36),
             num_attention_heads=heads, num_key_value_heads=cfg.get('num_key_value_heads', heads),
-            head_dim=cfg.get('head_dim') or cfg.get('hidden_size', 4096) // heads, rms_norm_eps=cfg.get('rms_norm_eps', 1e-6),
+            head_dim=(cfg.get('head_dim') or cfg.get('hidden_size', 4096) // heads) if not dsv3
+            else int(cfg.get('qk_nope_head_dim', 128)) + int(cfg.get('qk_rope_head_dim', 64)), rms_norm_eps=cfg.get('rms_norm_eps', 1e-6),
             rope_theta=float(cfg.get('rope_theta', (cfg.get('rope_parameters') or {}).get('rope_theta', 1e6))),
             rope_scaling=_rope_scaling_of(cfg), tie_word_embeddings=bool(cfg.get('tie_word_embeddings', False)),
             qk_norm=mt.startswith('qwen3'),
             attention_bias=bool(cfg.get('attention_bias', cfg.get('qkv_bias', cfg.get('bias', False)) if mt.startswith('internlm') else mt.startswith('qwen2'))),
+            router_scoring='sigmoid' if dsv3 else 'softmax', router_bias=dsv3, n_group=int(cfg.get('n_group') or 1) if dsv3 else 1,
+            topk_group=int(cfg.get('topk_group') or 1) if dsv3 else 1, routed_scaling_factor=float(cfg.get('routed_scaling_factor', 1.0)) if dsv3 else 1.0,
+            first_k_dense_replace=int(cfg.get('first_k_dense_replace', 0)) if dsv3 else 0, shared_expert_gate=not dsv3,
+            q_lora_rank=cfg.get('q_lora_rank') if dsv3 else None, kv_lora_rank=int(cfg.get('kv_lora_rank', 0)) if dsv3 else 0,
+            qk_nope_head_dim=int(cfg.get('qk_nope_head_dim', 128)), qk_rope_head_dim=int(cfg.get('qk_rope_head_dim', 64)),
+            v_head_dim=int(cfg.get('v_head_dim', 128)), mla_rope_interleave=bool(cfg.get('rope_interleave', True)),
             hidden_act=act, embed_scale=float(cfg.get('embed_scale', cfg.get('hidden_size', 4096)**0.5 if mt == 'gemma' else 1.0)),
             sliding_window=int(window) if window else None,
-            num_experts=cfg.get('num_experts', cfg.get('num_local_experts', 0)) or 0,
+            num_experts=cfg.get('num_experts', cfg.get('num_local_experts', cfg.get('n_routed_experts', 0))) or 0,
             num_experts_per_tok=cfg.get('num_experts_per_tok', 8),
             moe_intermediate_size=cfg.get('moe_intermediate_size', cfg.get('intermediate_size', 768) if mt == 'mixtral' else 768),
             norm_topk_prob=True if cfg.get('norm_topk_prob') is None else bool(cfg['norm_topk_prob']), router_aux_loss_coef=float(cfg.get('router_aux_loss_coef', 0.0)),
-            shared_expert_intermediate_size=int(cfg.get('shared_expert_intermediate_size', 0) or 0),
+            shared_expert_intermediate_size=int(cfg.get('shared_expert_intermediate_size', 0) or 0) if not dsv3
+            else int(cfg.get('moe_intermediate_size', 0)) * int(cfg.get('n_shared_experts') or 0),
             rms_norm_offset=float(cfg.get('rms_norm_offset', 1.0 if (mt.startswith('gemma') or q35) else 0.0)),
             partial_rotary_factor=float(cfg.get('partial_rotary_factor', (cfg.get('rope_parameters') or {}).get('partial_rotary_factor', 1.0)) or 1.0),
             attn_output_gate=bool(cfg.get('attn_output_gate', q35)),
@@ -238,7 +298,17 @@ class DecoderConfig:
             d['rms_norm_offset'] = self.rms_norm_offset
         if self.sliding_window:
             d['sliding_window'] = self.sliding_window
-        if self.model_type == 'phi3':
+        if self.is_mla:
+            d.update(architectures=['DeepseekV3ForCausalLM'], model_type=self.model_type, q_lora_rank=self.q_lora_rank, kv_lora_rank=self.kv_lora_rank,
+                     qk_nope_head_dim=self.qk_nope_head_dim, qk_rope_head_dim=self.qk_rope_head_dim, v_head_dim=self.v_head_dim,
+                     rope_interleave=self.mla_rope_interleave, head_dim=self.qk_rope_head_dim, n_routed_experts=self.num_experts,
+                     n_shared_experts=(self.shared_expert_intermediate_size // self.moe_intermediate_size) if self.num_experts else 0,
+                     n_group=self.n_group, topk_group=self.topk_group, routed_scaling_factor=self.routed_scaling_factor,
+                     first_k_dense_replace=self.first_k_dense_replace, norm_topk_prob=self.norm_topk_prob,
+                     num_experts_per_tok=self.num_experts_per_tok, moe_intermediate_size=self.moe_intermediate_size)
+            for k in ('num_experts', 'shared_expert_intermediate_size', 'decoder_sparse_step', 'mlp_only_layers'):
+                d.pop(k, None)
+        elif self.model_type == 'phi3':
             d.update(architectures=['Phi3ForCausalLM'], partial_rotary_factor=self.partial_rotary_factor,
                      pad_token_id=self.pad_token_id, sliding_window=self.sliding_window,
                      original_max_position_embeddings=(self.rope_scaling or {}).get('original_max_position_embeddings', self.max_position_embeddings))
@@ -313,6 +383,13 @@ PRESETS: Dict[str, Dict[str, Any]] = {
                          model_type='qwen3_5_text', rms_norm_offset=1.0, partial_rotary_factor=0.25, attn_output_gate=True,
                          layer_types=['linear_attention', 'linear_attention', 'linear_attention', 'full_attention'], linear_num_key_heads=2,
                          linear_num_value_heads=4, linear_key_head_dim=32, linear_value_head_dim=32),
+    # DeepSeek-V3 in small: latent attention with a query bottleneck, one dense layer then mixture-of-experts layers with sigmoid
+    # routing over expert groups, selection bias and an ungated shared expert
+    'tiny-deepseek': dict(vocab_size=1024, hidden_size=256, intermediate_size=688, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=4,
+                          head_dim=48, rope_theta=1e4, tie_word_embeddings=False, qk_norm=False, torch_dtype='float32', model_type='deepseek_v3',
+                          q_lora_rank=64, kv_lora_rank=32, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32, num_experts=8,
+                          num_experts_per_tok=2, moe_intermediate_size=128, shared_expert_intermediate_size=128, shared_expert_gate=False,
+                          router_scoring='sigmoid', router_bias=True, n_group=4, topk_group=2, routed_scaling_factor=2.5, first_k_dense_replace=1),
     'tiny-moe': dict(vocab_size=1024, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
                      head_dim=64, rope_theta=1e4, tie_word_embeddings=True, num_experts=8, num_experts_per_tok=2,
                      moe_intermediate_size=128, router_aux_loss_coef=1e-3, torch_dtype='float32'),

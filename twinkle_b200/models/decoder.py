@@ -19,6 +19,7 @@ from typing import Any, Dict, List, Optional, Tuple
 
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 
 from .. import ops
 from .config import DecoderConfig
@@ -73,6 +74,7 @@ class Attention(nn.Module):
         else:
             self.q_norm = self.k_norm = None
         self.attn_parallel = None  # Ulysses strategy or None
+        self.scale = 1.0 / math.sqrt(d)
 
     def heads(self, qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor):
         """Fused projection output → ``(q [T,Hq,D], k [T,Hkv,D], v [T,Hkv,D], gate [T,Hq·D] | None)`` after the per-head
@@ -85,6 +87,13 @@ class Attention(nn.Module):
             qkv, gate = qkv[:, :w], qkv[:, w:]
         q, k, v = ops.qkv_norm_rope(qkv, qw, kw, cos, sin, self.hq, self.hkv, self.d, self.cfg.rms_norm_eps, self.norm_offset)
         return q, k, v, gate
+
+    def heads_from(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor):
+        return self.heads(self.qkv_proj(x), cos, sin)
+
+    @staticmethod
+    def cache_entry(k: torch.Tensor, v: torch.Tensor):
+        return k, v
 
     def project_out(self, o: torch.Tensor, gate: Optional[torch.Tensor]) -> torch.Tensor:
         o = o.reshape(o.shape[0], -1)
@@ -119,6 +128,69 @@ class Attention(nn.Module):
         if ap is not None:
             o = ap.gather_heads(o)  # back to [T_local, Hq, D]
         return self.project_out(o, gate)   # the gate is per token of this rank: applied after the heads are back
+
+
+class MLAttention(nn.Module):
+    """Multi-head latent attention (DeepSeek-V2 / V3; Hugging Face ``DeepseekV3Attention``).  Queries come through a
+    low-rank bottleneck with a norm in the middle (or a plain projection), keys and values are expanded from one normalised
+    latent per token, and the rotary part of the key is a single head shared by all query heads.  Scores use the
+    ``qk_nope + qk_rope`` wide heads, values are ``v_head_dim`` wide, so this block runs the generic packed attention
+    (``ops.flash_attn_varlen`` routes widths other than 128 to its PyTorch form)."""
+
+    def __init__(self, cfg: DecoderConfig, layer_idx: int):
+        super().__init__()
+        self.cfg, self.layer_idx = cfg, layer_idx
+        h, nh = cfg.hidden_size, cfg.num_attention_heads
+        self.nh, self.nope, self.rope, self.vd = nh, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
+        qk = self.nope + self.rope
+        if cfg.q_lora_rank:
+            self.q_a_proj = Linear(h, cfg.q_lora_rank, bias=cfg.attention_bias, name='q_a_proj')
+            self.q_a_layernorm = RMSNorm(cfg.q_lora_rank, cfg.rms_norm_eps)
+            self.q_b_proj = Linear(cfg.q_lora_rank, nh * qk, name='q_b_proj')
+            self.q_proj = None
+        else:
+            self.q_proj = Linear(h, nh * qk, name='q_proj')
+            self.q_a_proj = self.q_a_layernorm = self.q_b_proj = None
+        self.kv_a_proj_with_mqa = Linear(h, cfg.kv_lora_rank + self.rope, bias=cfg.attention_bias, name='kv_a_proj_with_mqa')
+        self.kv_a_layernorm = RMSNorm(cfg.kv_lora_rank, cfg.rms_norm_eps)
+        self.kv_b_proj = Linear(cfg.kv_lora_rank, nh * (self.nope + self.vd), name='kv_b_proj')
+        self.o_proj = Linear(nh * self.vd, h, bias=cfg.attention_bias, name='o_proj')
+        self.attn_parallel = None
+        self.scale = cfg.attn_scale
+
+    def _rotate(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+        if self.cfg.mla_rope_interleave:     # checkpoint pairs are (2i, 2i+1): bring them to (i, i + R/2) first
+            x = x.reshape(*x.shape[:-1], self.rope // 2, 2).transpose(-1, -2).reshape(x.shape)
+        return ops.ref.apply_rope(x, cos, sin)
+
+    def heads_from(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor):
+        """Layer input → ``(q [T,H,Dqk], k [T,H,Dqk], v [T,H,Dv], None)`` with the rotary part applied."""
+        T = x.shape[0]
+        q = self.q_proj(x) if self.q_proj is not None else self.q_b_proj(self.q_a_layernorm(self.q_a_proj(x)))
+        q = q.view(T, self.nh, self.nope + self.rope)
+        ckv = self.kv_a_proj_with_mqa(x)
+        latent, k_rot = ckv[:, :self.cfg.kv_lora_rank], ckv[:, self.cfg.kv_lora_rank:]
+        kv = self.kv_b_proj(self.kv_a_layernorm(latent)).view(T, self.nh, self.nope + self.vd)
+        q_rot = self._rotate(q[..., self.nope:], cos, sin)
+        k_rot = self._rotate(k_rot.reshape(T, 1, self.rope), cos, sin).expand(T, self.nh, self.rope)
+        return torch.cat([q[..., :self.nope], q_rot], -1), torch.cat([kv[..., :self.nope], k_rot], -1), kv[..., self.nope:], None
+
+    def cache_entry(self, k: torch.Tensor, v: torch.Tensor):
+        """Keys and values as the paged cache keeps them: one width for both, values zero-padded to the score width."""
+        return k, F.pad(v, (0, k.shape[-1] - v.shape[-1]))
+
+    def project_out(self, o: torch.Tensor, gate=None) -> torch.Tensor:
+        return self.o_proj(o[..., :self.vd].reshape(o.shape[0], self.nh * self.vd))
+
+    def forward(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, batch: PackedBatch, kv_sink=None) -> torch.Tensor:
+        if self.attn_parallel is not None:
+            raise NotImplementedError('multi-head latent attention is not wired to the sequence-parallel attention strategies '
+                                      '(unequal key / value widths); use data, sharded-data, expert or pipeline parallelism')
+        q, k, v, _ = self.heads_from(x, cos, sin)
+        if kv_sink is not None:
+            kv_sink(self.layer_idx, *self.cache_entry(k, v))
+        o = ops.flash_attn_varlen(q, k, v, batch.cu_seqlens, batch.max_seqlen, True, self.scale)
+        return self.project_out(o)
 
 
 class MLP(nn.Module):
@@ -208,9 +280,11 @@ class MoEBlock(nn.Module):
         # replicated under expert parallelism (reference ``moe/expert_parallel.py:329-382``)
         if cfg.shared_expert_intermediate_size > 0:
             self.shared_expert = MLP(cfg, cfg.shared_expert_intermediate_size)
-            self.shared_expert_gate = Linear(cfg.hidden_size, 1, name='shared_expert_gate')
+            self.shared_expert_gate = Linear(cfg.hidden_size, 1, name='shared_expert_gate') if cfg.shared_expert_gate else None
         else:
             self.shared_expert = self.shared_expert_gate = None
+        # DeepSeek-V3: a per-expert bias that steers the selection only (balanced by a rule outside the loss, never by a gradient)
+        self.e_score_correction_bias = nn.Parameter(torch.zeros(cfg.num_experts), requires_grad=False) if cfg.router_bias else None
         self.moe_parallel = None  # expert-parallel strategy or None
         self.etp = None           # tensor-parallel context when every expert is split over the tensor-parallel group
         self.last_routed: Optional[torch.Tensor] = None
@@ -218,8 +292,32 @@ class MoEBlock(nn.Module):
         self.record_routing = False
 
     def route(self, x: torch.Tensor, forced: Optional[torch.Tensor]):
+        if self.cfg.router_scoring == 'sigmoid':
+            return self._route_sigmoid(x, forced)
         w, idx, probs, self._hist = ops.moe_router(self.gate(x), self.cfg.num_experts_per_tok, self.cfg.norm_topk_prob, forced)
         return w, idx, probs
+
+    def _route_sigmoid(self, x: torch.Tensor, forced: Optional[torch.Tensor]):
+        """DeepSeek-V3 routing (Hugging Face ``DeepseekV3MoE.route_tokens_to_experts``): sigmoid scores; the choice is made
+        on scores plus the selection bias, restricted to the ``topk_group`` expert groups whose two best biased scores sum
+        highest; the weights are the unbiased scores of the chosen experts, normalised and scaled."""
+        cfg = self.cfg
+        E, k = cfg.num_experts, cfg.num_experts_per_tok
+        scores = torch.sigmoid(F.linear(x.float(), self.gate.weight.float()))
+        choice = scores + self.e_score_correction_bias.float() if self.e_score_correction_bias is not None else scores
+        if cfg.n_group > 1:
+            grouped = choice.view(-1, cfg.n_group, E // cfg.n_group)
+            best = grouped.topk(2, dim=-1)[0].sum(-1).topk(cfg.topk_group, dim=-1, sorted=False)[1]
+            keep = torch.zeros_like(grouped[..., 0]).scatter_(1, best, 1.0).bool()
+            choice = grouped.masked_fill(~keep[..., None], 0.0).reshape(-1, E)
+        idx = choice.topk(k, dim=-1, sorted=False)[1]
+        if forced is not None:
+            idx = torch.where(forced[:, :1] < 0, idx, forced.long())
+        w = scores.gather(1, idx)
+        if cfg.norm_topk_prob:
+            w = w / (w.sum(-1, keepdim=True) + 1e-20)
+        self._hist = None
+        return w * cfg.routed_scaling_factor, idx, scores
 
     def forward(self, x: torch.Tensor, forced: Optional[torch.Tensor] = None) -> torch.Tensor:
         T, H = x.shape
@@ -269,6 +367,8 @@ class MoEBlock(nn.Module):
     def _with_shared(self, x: torch.Tensor, routed: torch.Tensor) -> torch.Tensor:
         if self.shared_expert is None:
             return routed
+        if self.shared_expert_gate is None:
+            return routed + self.shared_expert(x, value_unused=False)
         gate = torch.sigmoid(self.shared_expert_gate(x).float()).to(x.dtype)
         return routed + gate * self.shared_expert(x, value_unused=False)
 
@@ -285,10 +385,11 @@ class DecoderLayer(nn.Module):
             self.self_attn = GatedDeltaNet(cfg.hidden_size, cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim,
                                            cfg.linear_value_head_dim, cfg.linear_conv_kernel_dim, cfg.rms_norm_eps)
         else:
-            self.self_attn = Attention(cfg, layer_idx)
+            self.self_attn = MLAttention(cfg, layer_idx) if cfg.is_mla else Attention(cfg, layer_idx)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.rms_norm_offset)
-        self.mlp = MoEBlock(cfg, layer_idx) if cfg.is_moe else MLP(cfg)
-        self.is_moe = cfg.is_moe
+        self.is_moe = cfg.layer_is_moe(layer_idx)          # DeepSeek keeps a dense block in its first layers
+        self.first_moe_layer = cfg.first_k_dense_replace      # recorded routing lists have one entry per mixture-of-experts layer
+        self.mlp = MoEBlock(cfg, layer_idx) if self.is_moe else MLP(cfg)
         # GLM-4: each sub-layer's output is normalised before it joins the residual stream
         if cfg.sandwich_norm:
             self.post_self_attn_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.rms_norm_offset)
@@ -306,7 +407,7 @@ class DecoderLayer(nn.Module):
         else:
             a = self.self_attn(self.input_layernorm(x), cos, sin, batch, kv_sink)
         n, h = self.after_attention(x, a)
-        forced = batch.routed_experts[self.layer_idx] if (self.is_moe and batch.routed_experts is not None) else None
+        forced = batch.routed_experts[self.layer_idx - self.first_moe_layer] if (self.is_moe and batch.routed_experts is not None) else None
         return ops.add(h, self.feed_forward(n, forced), value_unused=True)
 
     def after_attention(self, x: torch.Tensor, a: torch.Tensor):

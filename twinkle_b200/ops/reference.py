@@ -163,7 +163,7 @@ def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
     Hkv = k.shape[1]
     rep = Hq // Hkv
     scale = 1.0 / math.sqrt(D) if scale is None else scale
-    out = torch.empty_like(q)
+    out = q.new_empty(T, Hq, v.shape[-1])          # values may be narrower than the score width (latent attention)
     lse = torch.empty(Hq, T, dtype=torch.float32, device=q.device)
     bounds = cu_seqlens.tolist()
     kb = bounds if cu_seqlens_k is None else cu_seqlens_k.tolist()

@@ -272,6 +272,9 @@ def apply_tensor_parallel(model, cfg, comm: Communicator, sequence_parallel: boo
     tensor) and switch the modules to their TP forward."""
     if comm.world_size <= 1:
         return None
+    if getattr(cfg, 'is_mla', False):
+        raise NotImplementedError('multi-head latent attention has no tensor-parallel split here; use tp_size=1 '
+                                  '(data, sharded-data, expert and pipeline parallelism apply)')
     tp = TPContext(comm, sequence_parallel)
     tp.fused = fused
     assert cfg.num_key_value_heads % tp.size == 0 and cfg.num_attention_heads % tp.size == 0, 'heads must divide over tp'

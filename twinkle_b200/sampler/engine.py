@@ -186,10 +186,9 @@ class NativeEngine:
                     n, x = layer.after_attention(x, y)
                     x = x + layer.feed_forward(n)
                     continue
-                q, k, v, gate = at.heads(at.qkv_proj(h), cos, sin)
-                self.cache.k[li, blk, off] = k
-                self.cache.v[li, blk, off] = v
-                o = ops.paged_attention_decode(q, self.cache.k[li], self.cache.v[li], table, seq_lens, 1.0 / math.sqrt(at.d))
+                q, k, v, gate = at.heads_from(h, cos, sin)
+                self.cache.k[li, blk, off], self.cache.v[li, blk, off] = at.cache_entry(k, v)
+                o = ops.paged_attention_decode(q, self.cache.k[li], self.cache.v[li], table, seq_lens, at.scale)
                 n, x = layer.after_attention(x, at.project_out(o, gate))
                 x = x + layer.feed_forward(n)
             x = self.model.norm(x)
