@@ -79,6 +79,13 @@ def _cases():
                                                         rope_scaling={'rope_type': 'yarn', 'factor': 40.0, 'beta_fast': 32, 'beta_slow': 1, 'mscale': 1.0,
                                                                       'mscale_all_dim': 1.0, 'original_max_position_embeddings': 64}),
                              'DeepseekV3ForCausalLM'),
+        # GLM-4.5: DeepSeek-V3's routing over grouped-query attention with q/k norms, biased q|k|v and rotary on half the head
+        'glm4_moe': (lambda: T.Glm4MoeConfig(head_dim=32, moe_intermediate_size=64, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2, n_group=2,
+                                             topk_group=1, first_k_dense_replace=1, routed_scaling_factor=1.5, norm_topk_prob=True, use_qk_norm=True,
+                                             attention_bias=True, tie_word_embeddings=False, pad_token_id=0,
+                                             **{**{k: v for k, v in COMMON.items() if k != 'rope_theta'}, 'num_hidden_layers': 3},
+                                             rope_parameters={'rope_type': 'default', 'rope_theta': 10000.0, 'partial_rotary_factor': 0.5}),
+                     'Glm4MoeForCausalLM'),
         'qwen2_moe_shared': (lambda: T.Qwen2MoeConfig(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=96,
                                                       norm_topk_prob=False, decoder_sparse_step=1, mlp_only_layers=[], **COMMON), 'Qwen2MoeForCausalLM'),
     }
@@ -124,7 +131,7 @@ def test_hf_checkpoint_gives_the_same_logits_here(name, tmp_path):
 
 
 @pytest.mark.parametrize('name', ['qwen3', 'qwen3_moe', 'mixtral', 'qwen2_moe_shared', 'qwen3_5', 'qwen3_5_moe', 'qwen3_next', 'glm', 'glm4', 'phi3',
-                                  'phi3_longrope', 'gemma', 'deepseek_v3', 'deepseek_v3_yarn'])
+                                  'phi3_longrope', 'gemma', 'deepseek_v3', 'deepseek_v3_yarn', 'glm4_moe'])
 def test_checkpoint_saved_here_loads_in_transformers(name, tmp_path):
     hf = _hf_model(name)
     hf.save_pretrained(str(tmp_path / 'hf'), safe_serialization=True)

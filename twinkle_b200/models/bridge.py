@@ -52,7 +52,7 @@ def _family(name: str, cfg: DecoderConfig) -> str:
     if cfg.model_type == 'mixtral':
         for pat, rep in _MIXTRAL:
             name = pat.sub(rep, name)
-    elif cfg.model_type in ('deepseek_v3', 'kimi_k2'):
+    elif cfg.model_type in ('deepseek_v3', 'kimi_k2', 'glm4_moe'):
         name = name.replace('.mlp.shared_expert.', '.mlp.shared_experts.').replace('.mlp.e_score_correction_bias', '.mlp.gate.e_score_correction_bias')
     elif cfg.model_type == 'internlm2':
         for a, b in _INTERNLM2:
@@ -250,7 +250,7 @@ def hf_to_internal(name: str, cfg: DecoderConfig, get: Callable[[str], torch.Ten
     m = _LAYER.match(name)
     rest = m.group(2) if m else ''
     i = int(m.group(1)) if m else -1
-    if cfg.model_type in ('mixtral', 'internlm2', 'deepseek_v3', 'kimi_k2'):
+    if cfg.model_type in ('mixtral', 'internlm2', 'deepseek_v3', 'kimi_k2', 'glm4_moe'):
         plain = get
 
         def get(n: str) -> torch.Tensor:  # noqa: F811

@@ -18,7 +18,7 @@ from typing import List, Any, Dict, Optional
 SUPPORTED_MODEL_TYPES = frozenset({'llama', 'mistral', 'mixtral', 'qwen2', 'qwen2_moe', 'qwen3', 'qwen3_moe', 'seed_oss', 'qwen2_vl', 'qwen2_vl_text',
                                    'qwen2_5_vl', 'qwen2_5_vl_text', 'qwen3_vl', 'qwen3_vl_text', 'qwen3_vl_moe', 'qwen3_vl_moe_text',
                                    'qwen3_5', 'qwen3_5_text', 'qwen3_5_moe', 'qwen3_5_moe_text', 'qwen3_next', 'glm', 'glm4',
-                                   'phi3', 'internlm2', 'internlm3', 'gemma', 'deepseek_v3', 'kimi_k2'})
+                                   'phi3', 'internlm2', 'internlm3', 'gemma', 'deepseek_v3', 'kimi_k2', 'glm4_moe'})
 
 
 def _rope_scaling_of(cfg: Dict[str, Any]) -> Optional[Dict[str, Any]]:
@@ -217,7 +217,8 @@ class DecoderConfig:
         if q35 and vision is not None:
             vision = None        # the language model of a Qwen3.5 checkpoint trains without its tower here (text-only batches)
         heads = cfg.get('num_attention_heads', 32)
-        dsv3 = mt in ('deepseek_v3', 'kimi_k2')
+        mla = mt in ('deepseek_v3', 'kimi_k2')
+        dsv3 = mla or mt == 'glm4_moe'        # GLM-4.5 routes like DeepSeek-V3 over ordinary grouped-query attention
         window = cfg.get('sliding_window')
         if mt.startswith('qwen') and not cfg.get('use_sliding_window'):
             window = None                    # the Qwen configs carry a window size that is switched off by default
@@ -230,16 +231,16 @@ class DecoderConfig:
             vocab_size=cfg.get('vocab_size', 151936), hidden_size=cfg.get('hidden_size', 4096),
             intermediate_size=cfg.get('intermediate_size', 12288), num_hidden_layers=cfg.get('num_hidden_layers', 36),
             num_attention_heads=heads, num_key_value_heads=cfg.get('num_key_value_heads', heads),
-            head_dim=(cfg.get('head_dim') or cfg.get('hidden_size', 4096) // heads) if not dsv3
+            head_dim=(cfg.get('head_dim') or cfg.get('hidden_size', 4096) // heads) if not mla
             else int(cfg.get('qk_nope_head_dim', 128)) + int(cfg.get('qk_rope_head_dim', 64)), rms_norm_eps=cfg.get('rms_norm_eps', 1e-6),
             rope_theta=float(cfg.get('rope_theta', (cfg.get('rope_parameters') or {}).get('rope_theta', 1e6))),
             rope_scaling=_rope_scaling_of(cfg), tie_word_embeddings=bool(cfg.get('tie_word_embeddings', False)),
-            qk_norm=mt.startswith('qwen3'),
+            qk_norm=mt.startswith('qwen3') or (mt == 'glm4_moe' and bool(cfg.get('use_qk_norm'))),
             attention_bias=bool(cfg.get('attention_bias', cfg.get('qkv_bias', cfg.get('bias', False)) if mt.startswith('internlm') else mt.startswith('qwen2'))),
             router_scoring='sigmoid' if dsv3 else 'softmax', router_bias=dsv3, n_group=int(cfg.get('n_group') or 1) if dsv3 else 1,
             topk_group=int(cfg.get('topk_group') or 1) if dsv3 else 1, routed_scaling_factor=float(cfg.get('routed_scaling_factor', 1.0)) if dsv3 else 1.0,
             first_k_dense_replace=int(cfg.get('first_k_dense_replace', 0)) if dsv3 else 0, shared_expert_gate=not dsv3,
-            q_lora_rank=cfg.get('q_lora_rank') if dsv3 else None, kv_lora_rank=int(cfg.get('kv_lora_rank', 0)) if dsv3 else 0,
+            q_lora_rank=cfg.get('q_lora_rank') if mla else None, kv_lora_rank=int(cfg.get('kv_lora_rank', 0)) if mla else 0,
             qk_nope_head_dim=int(cfg.get('qk_nope_head_dim', 128)), qk_rope_head_dim=int(cfg.get('qk_rope_head_dim', 64)),
             v_head_dim=int(cfg.get('v_head_dim', 128)), mla_rope_interleave=bool(cfg.get('rope_interleave', True)),
             hidden_act=act, embed_scale=float(cfg.get('embed_scale', cfg.get('hidden_size', 4096)**0.5 if mt == 'gemma' else 1.0)),
@@ -306,6 +307,14 @@ class DecoderConfig:
                      n_group=self.n_group, topk_group=self.topk_group, routed_scaling_factor=self.routed_scaling_factor,
                      first_k_dense_replace=self.first_k_dense_replace, norm_topk_prob=self.norm_topk_prob,
                      num_experts_per_tok=self.num_experts_per_tok, moe_intermediate_size=self.moe_intermediate_size)
+            for k in ('num_experts', 'shared_expert_intermediate_size', 'decoder_sparse_step', 'mlp_only_layers'):
+                d.pop(k, None)
+        elif self.model_type == 'glm4_moe':
+            d.update(architectures=['Glm4MoeForCausalLM'], model_type='glm4_moe', use_qk_norm=self.qk_norm, n_routed_experts=self.num_experts,
+                     n_shared_experts=self.shared_expert_intermediate_size // self.moe_intermediate_size, n_group=self.n_group,
+                     topk_group=self.topk_group, routed_scaling_factor=self.routed_scaling_factor, first_k_dense_replace=self.first_k_dense_replace,
+                     partial_rotary_factor=self.partial_rotary_factor,
+                     rope_parameters={'rope_type': 'default', 'rope_theta': self.rope_theta, 'partial_rotary_factor': self.partial_rotary_factor})
             for k in ('num_experts', 'shared_expert_intermediate_size', 'decoder_sparse_step', 'mlp_only_layers'):
                 d.pop(k, None)
         elif self.model_type == 'phi3':
