@@ -245,7 +245,7 @@ def test_rope_scaling_matches_transformers_and_travels_in_config():
     cos, sin = rope_tables(torch.arange(4), 128, 5e5, variants[1])
     assert cos[0, 0] == pytest.approx(0.1 * torch.log(torch.tensor(4.0)).item() + 1.0)   # yarn scales cos/sin
     with pytest.raises(NotImplementedError):
-        rope_inv_freq(128, 1e6, {'rope_type': 'longrope', 'factor': 2.0})
+        rope_inv_freq(128, 1e6, {'rope_type': 'su', 'factor': 2.0})            # an unknown variant is refused, not approximated
     cfg = DecoderConfig.from_hf({'model_type': 'llama', 'hidden_size': 256, 'num_attention_heads': 4, 'max_position_embeddings': 131072,
                                  'rope_scaling': {'rope_type': 'llama3', 'factor': 8.0, 'low_freq_factor': 1.0, 'high_freq_factor': 4.0,
                                                   'original_max_position_embeddings': 8192}, 'rope_theta': 5e5})
@@ -268,3 +268,32 @@ def test_image_sources_can_be_restricted(tmp_path, monkeypatch):
     with pytest.raises(PermissionError):
         load_mm_file('http://example.invalid/a.png')
     assert load_mm_file('data:image/png;base64,' + base64.b64encode(b'xyz').decode()).read() == b'xyz'
+
+
+def test_safe_mode_refuses_callables_for_remote_calls(monkeypatch):
+    """``TWINKLE_TRUST_REMOTE_CODE=0``: classes and callables are refused as arguments of remote classes and of calls
+    that go to workers (reference ``utils/unsafe.py``); unset or ``1`` lets them through."""
+    import twinkle_b200 as tw
+    from twinkle_b200.utils import any_callable, check_unsafe
+    assert any_callable({'a': [1, (2, len)]}) and any_callable(int) and not any_callable({'a': [1, 'x', {'b': 2.0}]})
+    monkeypatch.delenv('TWINKLE_TRUST_REMOTE_CODE', raising=False)
+    check_unsafe(len, cls=int)
+    monkeypatch.setenv('TWINKLE_TRUST_REMOTE_CODE', '0')
+    check_unsafe('CrossEntropyLoss', lr=1e-3)
+    with pytest.raises(ValueError):
+        check_unsafe(loss_cls=int)
+
+    @tw.remote_class()
+    class Box:
+
+        def __init__(self, x=None):
+            self.x = x
+
+    assert Box('name').x == 'name'
+    with pytest.raises(ValueError):
+        Box(lambda: 1)
+    monkeypatch.setenv('TWINKLE_TRUST_REMOTE_CODE', '1')
+    assert callable(Box(len).x)
+    for name in ('exists', 'requires', 'find_free_port', 'find_node_ip', 'trust_remote_code', 'check_unsafe', 'framework_util', 'torch_util',
+                 'Plugin', 'is_master', 'init_twinkle_client', 'init_tinker_client', '__release_datetime__'):
+        assert hasattr(tw, name), name

@@ -27,6 +27,7 @@ from typing import Any, Callable, Dict, List, Optional, Sequence, Union
 import numpy as np
 
 from ..utils.device_mesh import DeviceGroup, DeviceMesh
+from ..utils.loader import check_unsafe
 from ..utils.logger import get_logger
 from ..utils.platform import Platform
 
@@ -292,6 +293,7 @@ def remote_function(dispatch: Union[str, Callable] = 'all', execute: str = 'all'
         def wrapper(self, *args, **kwargs):
             proxy = getattr(self, '_remote_proxy', None)
             if proxy is not None:
+                check_unsafe(*args, **kwargs)       # safe mode: nothing executable travels to a worker
                 return proxy.call(fn.__name__, fn._remote_spec, args, kwargs)
             try:
                 return fn(self, *args, **kwargs)
@@ -326,6 +328,7 @@ def remote_class(execute: str = 'all'):
         @functools.wraps(orig_init)
         def new_init(self, *args, remote_group: Optional[str] = None, **kwargs):
             self._remote_proxy = None
+            check_unsafe(*args, **kwargs)
             if _STATE['mode'] == 'pool' and remote_group is not None and not os.environ.get('TWINKLE_WORKER'):
                 from .worker_pool import RemoteProxy
                 self._remote_proxy = RemoteProxy(_STATE['pool'], cls, remote_group, execute, args, kwargs, mesh_arg)

@@ -10,12 +10,32 @@ import importlib.util
 import inspect
 import os
 import sys
+from collections.abc import Mapping
 from types import ModuleType
 from typing import Any, Optional, Type, Union
 
 
 def trust_remote_code() -> bool:
     return os.environ.get('TWINKLE_TRUST_REMOTE_CODE', '0').lower() in ('1', 'true', 'yes')
+
+
+def any_callable(args: Any) -> bool:
+    """Whether a (nested) argument structure carries a callable or a class."""
+    if isinstance(args, Mapping):
+        return any(any_callable(a) for a in args.values())
+    if isinstance(args, (tuple, list, set, frozenset)):
+        return any(any_callable(a) for a in args)
+    return callable(args) or isinstance(args, type)
+
+
+def check_unsafe(*args, **kwargs) -> None:
+    """Safe mode of a served deployment (reference ``utils/unsafe.py:7-23``, applied in ``infra/__init__.py:569, 738``):
+    with ``TWINKLE_TRUST_REMOTE_CODE=0`` a call that would ship a callable or a class to a worker is refused — components
+    are then named by string only.  Unset (the default for local use) and ``1`` allow them; loading plugin *code* from a
+    directory or a hub id additionally needs the explicit ``1`` (:func:`trust_remote_code`)."""
+    if os.environ.get('TWINKLE_TRUST_REMOTE_CODE', '').lower() in ('0', 'false', 'no') and (any_callable(args) or any_callable(kwargs)):
+        raise ValueError('callables and classes are not accepted as arguments in safe mode (TWINKLE_TRUST_REMOTE_CODE=0): '
+                         'name the component by string')
 
 
 class Plugin:
