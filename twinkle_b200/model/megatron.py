@@ -295,6 +295,8 @@ class MegatronModel(TwinkleModel):
             else:
                 h = x
             cos, sin = ops.rope_tables(batch.position_ids, self.config.rotary_dim, self.config.rope_theta, self.config.rope_scaling)
+            if self.config.rope_local_theta:
+                batch.rope_local = ops.rope_tables(batch.position_ids, self.config.rotary_dim, self.config.rope_local_theta, None)
             if self.recompute is not None and torch.is_grad_enabled():
                 from torch.utils.checkpoint import checkpoint
                 for layer in m.layers:

@@ -54,6 +54,13 @@ def _family(name: str, cfg: DecoderConfig) -> str:
             name = pat.sub(rep, name)
     elif cfg.model_type in ('deepseek_v3', 'kimi_k2', 'glm4_moe'):
         name = name.replace('.mlp.shared_expert.', '.mlp.shared_experts.').replace('.mlp.e_score_correction_bias', '.mlp.gate.e_score_correction_bias')
+    elif cfg.model_type in ('gemma2', 'gemma3_text', 'gemma3'):
+        # four norms per layer there: input, after attention, before and after the feed-forward block
+        for a, b in (('.post_attention_layernorm.', '.pre_feedforward_layernorm.'), ('.post_self_attn_layernorm.', '.post_attention_layernorm.'),
+                     ('.post_mlp_layernorm.', '.post_feedforward_layernorm.')):
+            if a in name:
+                name = name.replace(a, b, 1)
+                break
     elif cfg.model_type == 'internlm2':
         for a, b in _INTERNLM2:
             if name.startswith(a) or (a[0] == '.' and a in name):
@@ -250,7 +257,7 @@ def hf_to_internal(name: str, cfg: DecoderConfig, get: Callable[[str], torch.Ten
     m = _LAYER.match(name)
     rest = m.group(2) if m else ''
     i = int(m.group(1)) if m else -1
-    if cfg.model_type in ('mixtral', 'internlm2', 'deepseek_v3', 'kimi_k2', 'glm4_moe'):
+    if cfg.model_type in ('mixtral', 'internlm2', 'deepseek_v3', 'kimi_k2', 'glm4_moe'):      # names that are built without hf_names_for
         plain = get
 
         def get(n: str) -> torch.Tensor:  # noqa: F811

@@ -18,7 +18,7 @@ from typing import List, Any, Dict, Optional
 SUPPORTED_MODEL_TYPES = frozenset({'llama', 'mistral', 'mixtral', 'qwen2', 'qwen2_moe', 'qwen3', 'qwen3_moe', 'seed_oss', 'qwen2_vl', 'qwen2_vl_text',
                                    'qwen2_5_vl', 'qwen2_5_vl_text', 'qwen3_vl', 'qwen3_vl_text', 'qwen3_vl_moe', 'qwen3_vl_moe_text',
                                    'qwen3_5', 'qwen3_5_text', 'qwen3_5_moe', 'qwen3_5_moe_text', 'qwen3_next', 'glm', 'glm4',
-                                   'phi3', 'internlm2', 'internlm3', 'gemma', 'deepseek_v3', 'kimi_k2', 'glm4_moe'})
+                                   'phi3', 'internlm2', 'internlm3', 'gemma', 'deepseek_v3', 'kimi_k2', 'glm4_moe', 'gemma2', 'gemma3_text', 'gemma3'})
 
 
 def _rope_scaling_of(cfg: Dict[str, Any]) -> Optional[Dict[str, Any]]:
@@ -71,6 +71,13 @@ class DecoderConfig:
     # attention window of checkpoints trained with one (Mistral-7B-v0.1, Phi-3-mini): rows longer than the window are
     # refused — every key inside the window is what the kernels here compute
     sliding_window: Optional[int] = None
+    # Gemma-2 / Gemma-3: scores through ``cap · tanh(s / cap)``, output logits likewise; softmax scale ``query_pre_attn_scalar^-½``
+    # instead of ``head_dim^-½``; sliding-window layers (``layer_types`` entries ``'sliding_attention'``) of Gemma-3 use a rotary
+    # base of their own, without the long-context scaling of the global layers
+    attn_logit_softcapping: Optional[float] = None
+    final_logit_softcapping: Optional[float] = None
+    query_pre_attn_scalar: Optional[float] = None
+    rope_local_theta: Optional[float] = None
     # MoE (num_experts == 0 → dense)
     num_experts: int = 0
     num_experts_per_tok: int = 8
@@ -138,12 +145,21 @@ class DecoderConfig:
     def layer_is_moe(self, layer_idx: int) -> bool:
         return self.num_experts > 0 and layer_idx >= self.first_k_dense_replace
 
+    def layer_window(self, layer_idx: int) -> Optional[int]:
+        """Attention window of a layer: the model's ``sliding_window`` on every layer, or only on those that ``layer_types``
+        marks ``'sliding_attention'``."""
+        if not self.sliding_window:
+            return None
+        if self.layer_types and 'sliding_attention' in self.layer_types:
+            return self.sliding_window if self.layer_types[layer_idx] == 'sliding_attention' else None
+        return self.sliding_window
+
     @property
     def attn_scale(self) -> float:
         """Softmax scale of the attention scores: ``1/√d`` of the query / key width; DeepSeek's YaRN variant multiplies
         it by the square of ``0.1·mscale_all_dim·ln(factor) + 1``."""
         if not self.is_mla:
-            return self.head_dim**-0.5
+            return float(self.query_pre_attn_scalar or self.head_dim)**-0.5
         sc = (self.qk_nope_head_dim + self.qk_rope_head_dim)**-0.5
         rs = self.rope_scaling or {}
         if rs.get('mscale_all_dim') and float(rs.get('factor', 1.0)) > 1.0:
@@ -222,6 +238,12 @@ class DecoderConfig:
         window = cfg.get('sliding_window')
         if mt.startswith('qwen') and not cfg.get('use_sliding_window'):
             window = None                    # the Qwen configs carry a window size that is switched off by default
+        gemma23 = mt in ('gemma2', 'gemma3_text', 'gemma3')
+        rope_local = cfg.get('rope_local_base_freq')
+        rp = cfg.get('rope_parameters')
+        if isinstance(rp, dict) and isinstance(rp.get('full_attention'), dict):      # per-layer-type rotary settings (Gemma-3)
+            rope_local = (rp.get('sliding_attention') or {}).get('rope_theta', rope_local)
+            cfg['rope_parameters'] = dict(rp['full_attention'])
         act = cfg.get('hidden_activation') or cfg.get('hidden_act') or 'silu'
         if mt == 'gemma':
             act = 'gelu_pytorch_tanh'        # what the Hugging Face model runs whatever the (legacy) field says
@@ -235,7 +257,7 @@ class DecoderConfig:
             else int(cfg.get('qk_nope_head_dim', 128)) + int(cfg.get('qk_rope_head_dim', 64)), rms_norm_eps=cfg.get('rms_norm_eps', 1e-6),
             rope_theta=float(cfg.get('rope_theta', (cfg.get('rope_parameters') or {}).get('rope_theta', 1e6))),
             rope_scaling=_rope_scaling_of(cfg), tie_word_embeddings=bool(cfg.get('tie_word_embeddings', False)),
-            qk_norm=mt.startswith('qwen3') or (mt == 'glm4_moe' and bool(cfg.get('use_qk_norm'))),
+            qk_norm=mt.startswith('qwen3') or mt.startswith('gemma3') or (mt == 'glm4_moe' and bool(cfg.get('use_qk_norm'))),
             attention_bias=bool(cfg.get('attention_bias', cfg.get('qkv_bias', cfg.get('bias', False)) if mt.startswith('internlm') else mt.startswith('qwen2'))),
             router_scoring='sigmoid' if dsv3 else 'softmax', router_bias=dsv3, n_group=int(cfg.get('n_group') or 1) if dsv3 else 1,
             topk_group=int(cfg.get('topk_group') or 1) if dsv3 else 1, routed_scaling_factor=float(cfg.get('routed_scaling_factor', 1.0)) if dsv3 else 1.0,
@@ -243,7 +265,11 @@ class DecoderConfig:
             q_lora_rank=cfg.get('q_lora_rank') if mla else None, kv_lora_rank=int(cfg.get('kv_lora_rank', 0)) if mla else 0,
             qk_nope_head_dim=int(cfg.get('qk_nope_head_dim', 128)), qk_rope_head_dim=int(cfg.get('qk_rope_head_dim', 64)),
             v_head_dim=int(cfg.get('v_head_dim', 128)), mla_rope_interleave=bool(cfg.get('rope_interleave', True)),
-            hidden_act=act, embed_scale=float(cfg.get('embed_scale', cfg.get('hidden_size', 4096)**0.5 if mt == 'gemma' else 1.0)),
+            hidden_act=act, embed_scale=float(cfg.get('embed_scale', cfg.get('hidden_size', 4096)**0.5 if mt.startswith('gemma') else 1.0)),
+            attn_logit_softcapping=cfg.get('attn_logit_softcapping') if gemma23 else None,
+            final_logit_softcapping=cfg.get('final_logit_softcapping') if gemma23 else None,
+            query_pre_attn_scalar=cfg.get('query_pre_attn_scalar') if gemma23 else None,
+            rope_local_theta=float(rope_local) if (rope_local and mt.startswith('gemma3')) else None,
             sliding_window=int(window) if window else None,
             num_experts=cfg.get('num_experts', cfg.get('num_local_experts', cfg.get('n_routed_experts', 0))) or 0,
             num_experts_per_tok=cfg.get('num_experts_per_tok', 8),
@@ -254,8 +280,8 @@ class DecoderConfig:
             rms_norm_offset=float(cfg.get('rms_norm_offset', 1.0 if (mt.startswith('gemma') or q35) else 0.0)),
             partial_rotary_factor=float(cfg.get('partial_rotary_factor', (cfg.get('rope_parameters') or {}).get('partial_rotary_factor', 1.0)) or 1.0),
             attn_output_gate=bool(cfg.get('attn_output_gate', q35)),
-            rope_interleaved=bool(cfg.get('rope_interleaved', mt in ('glm', 'glm4'))), sandwich_norm=bool(cfg.get('sandwich_norm', mt == 'glm4')),
-            layer_types=list(cfg['layer_types']) if cfg.get('layer_types') and 'linear_attention' in cfg['layer_types'] else None,
+            rope_interleaved=bool(cfg.get('rope_interleaved', mt in ('glm', 'glm4'))), sandwich_norm=bool(cfg.get('sandwich_norm', mt == 'glm4' or gemma23)),
+            layer_types=list(cfg['layer_types']) if cfg.get('layer_types') and ('linear_attention' in cfg['layer_types'] or ('sliding_attention' in cfg['layer_types'] and window)) else None,
             linear_num_key_heads=cfg.get('linear_num_key_heads', 16), linear_num_value_heads=cfg.get('linear_num_value_heads', 32),
             linear_key_head_dim=cfg.get('linear_key_head_dim', 128), linear_value_head_dim=cfg.get('linear_value_head_dim', 128),
             linear_conv_kernel_dim=cfg.get('linear_conv_kernel_dim', 4),
@@ -324,6 +350,18 @@ class DecoderConfig:
         elif self.model_type == 'gemma':
             d.update(architectures=['GemmaForCausalLM'], hidden_activation=self.hidden_act)
             d.pop('rms_norm_offset', None)
+        elif self.model_type in ('gemma2', 'gemma3_text', 'gemma3'):
+            g3 = self.model_type != 'gemma2'
+            d.update(architectures=['Gemma3ForCausalLM' if g3 else 'Gemma2ForCausalLM'], model_type='gemma3_text' if g3 else 'gemma2',
+                     hidden_activation=self.hidden_act, query_pre_attn_scalar=self.query_pre_attn_scalar, sliding_window=self.sliding_window,
+                     attn_logit_softcapping=self.attn_logit_softcapping, final_logit_softcapping=self.final_logit_softcapping,
+                     layer_types=list(self.layer_types or ['full_attention'] * self.num_hidden_layers))
+            if g3:
+                glob = dict(self.rope_scaling or {'rope_type': 'default'}, rope_theta=self.rope_theta)
+                d['rope_parameters'] = {'full_attention': glob, 'sliding_attention': {'rope_type': 'default', 'rope_theta': self.rope_local_theta or self.rope_theta}}
+                d.pop('rope_scaling', None)
+                d.pop('rope_theta', None)
+            d.pop('rms_norm_offset', None)
         elif self.model_type == 'internlm2':
             d.update(architectures=['InternLM2ForCausalLM'], bias=self.attention_bias)
         elif self.model_type == 'internlm3':
@@ -346,7 +384,9 @@ class DecoderConfig:
                     'vision_config': vis, 'image_token_id': self.image_token_id, 'video_token_id': self.video_token_id,
                     'vision_start_token_id': self.vision_start_token_id, 'vision_end_token_id': self.vision_end_token_id,
                     'tie_word_embeddings': self.tie_word_embeddings, 'torch_dtype': self.torch_dtype}
-        if self.layer_types:
+        if self.layer_types and 'linear_attention' not in self.layer_types:
+            d['layer_types'] = list(self.layer_types)
+        elif self.layer_types:
             d.update(layer_types=list(self.layer_types), linear_num_key_heads=self.linear_num_key_heads,
                      linear_num_value_heads=self.linear_num_value_heads, linear_key_head_dim=self.linear_key_head_dim,
                      linear_value_head_dim=self.linear_value_head_dim, linear_conv_kernel_dim=self.linear_conv_kernel_dim)

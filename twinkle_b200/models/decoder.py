@@ -41,6 +41,8 @@ class PackedBatch:
     # (cos, sin) of the whole row; set by the model forward when the Ulysses strategy scatters heads inside the q|k|v
     # projection, because q/k-norm and RoPE then run after the exchange on all tokens of this rank's heads
     rope_full: Optional[tuple] = None
+    # (cos, sin) from the rotary base of sliding-window layers, for families that give those layers their own (Gemma-3)
+    rope_local: Optional[tuple] = None
     # vision-language: flat patches of every image in the batch (in token order) and their (t, h, w) patch grids; the
     # tower's output replaces the embeddings of the image placeholder tokens. position_ids is then [3, T].
     pixel_values: Optional[torch.Tensor] = None
@@ -74,7 +76,10 @@ class Attention(nn.Module):
         else:
             self.q_norm = self.k_norm = None
         self.attn_parallel = None  # Ulysses strategy or None
-        self.scale = 1.0 / math.sqrt(d)
+        self.scale = cfg.attn_scale
+        self.window = cfg.layer_window(layer_idx)          # sliding-window layers see the last ``window`` keys only
+        self.softcap = cfg.attn_logit_softcapping
+        self.local_rope = bool(cfg.rope_local_theta) and self.window is not None     # Gemma-3: these layers rotate with their own base
 
     def heads(self, qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor):
         """Fused projection output → ``(q [T,Hq,D], k [T,Hkv,D], v [T,Hkv,D], gate [T,Hq·D] | None)`` after the per-head
@@ -90,6 +95,11 @@ class Attention(nn.Module):
 
     def heads_from(self, x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor):
         return self.heads(self.qkv_proj(x), cos, sin)
+
+    def _plain(self, max_seqlen: int) -> bool:
+        """Whether this layer is ordinary causal attention for rows up to ``max_seqlen`` (what the sequence-parallel
+        strategies and the fused paths compute)."""
+        return not self.softcap and (self.window is None or self.window >= int(max_seqlen))
 
     @staticmethod
     def cache_entry(k: torch.Tensor, v: torch.Tensor):
@@ -107,24 +117,29 @@ class Attention(nn.Module):
         kw = self.k_norm.weight if self.k_norm is not None else None
         ap = self.attn_parallel
         if (ap is not None and getattr(batch, 'rope_full', None) is not None and kv_sink is None and hasattr(ap, 'project_scatter')
-                and not self.gated and self.norm_offset == 0.0):
+                and not self.gated and self.norm_offset == 0.0 and self._plain(batch.max_seqlen) and not self.local_rope):
             # projection whose epilogue already delivers [T_full, (Hq + 2 Hkv)/sp · D] to every peer
             qkv_full = ap.project_scatter(x, self.qkv_proj, self.hq, self.hkv, self.d)
             if qkv_full is not None:
                 q, k, v = ops.qkv_norm_rope(qkv_full, qw, kw, batch.rope_full[0], batch.rope_full[1], self.hq // ap.sp, self.hkv // ap.sp,
                                             self.d, self.cfg.rms_norm_eps)
-                o = ops.flash_attn_varlen(q, k, v, batch.cu_seqlens, batch.max_seqlen, True, 1.0 / math.sqrt(self.d))
+                o = ops.flash_attn_varlen(q, k, v, batch.cu_seqlens, batch.max_seqlen, True, self.scale)
                 o = ap.gather_heads(o)
                 return self.o_proj(o.reshape(o.shape[0], -1))
+        if self.local_rope:
+            cos, sin = batch.rope_local
         q, k, v, gate = self.heads(self.qkv_proj(x), cos, sin)
         if kv_sink is not None:  # sampler prefill: keep K/V for the paged cache
             kv_sink(self.layer_idx, k, v)
+        if ap is not None and not self._plain(batch.max_seqlen):
+            raise NotImplementedError('sliding-window / soft-capped attention layers are not wired to the sequence-parallel attention '
+                                      'strategies; use data, sharded-data or pipeline parallelism, or rows no longer than the window')
         if ap is not None and hasattr(ap, 'attention'):  # context parallel: zig-zag local chunks against gathered keys
-            o = ap.attention(q, k, v, batch.seq_lens, 1.0 / math.sqrt(self.d))
+            o = ap.attention(q, k, v, batch.seq_lens, self.scale)
             return self.project_out(o, gate)
         if ap is not None:
             q, k, v = ap.scatter_heads(q, k, v)  # [T_local,H,D] → [T_full,H/sp,D]
-        o = ops.flash_attn_varlen(q, k, v, batch.cu_seqlens, batch.max_seqlen, True, 1.0 / math.sqrt(self.d))
+        o = ops.flash_attn_varlen(q, k, v, batch.cu_seqlens, batch.max_seqlen, True, self.scale, window=self.window, softcap=self.softcap)
         if ap is not None:
             o = ap.gather_heads(o)  # back to [T_local, Hq, D]
         return self.project_out(o, gate)   # the gate is per token of this rank: applied after the heads are back
@@ -511,15 +526,14 @@ class DecoderModel(nn.Module):
         return x
 
     def forward(self, batch: PackedBatch, hidden: Optional[torch.Tensor] = None, kv_sink=None) -> torch.Tensor:
-        if self.cfg.sliding_window and int(batch.max_seqlen) > self.cfg.sliding_window:
-            raise NotImplementedError(f'a row of {int(batch.max_seqlen)} tokens exceeds the attention window ({self.cfg.sliding_window}) this '
-                                      'checkpoint was trained with; windowed attention is not implemented — split or truncate the rows')
         x = self.embed(batch) if hidden is None else hidden
         if batch.position_ids.dim() == 2:  # [3, T] (time, height, width) positions of a vision-language batch
             from .vision import mrope_tables
             cos, sin = mrope_tables(batch.position_ids, self.cfg.rotary_dim, self.cfg.rope_theta, self.cfg.mrope_section, self.cfg.mrope_interleaved)
         else:
             cos, sin = ops.rope_tables(batch.position_ids, self.cfg.rotary_dim, self.cfg.rope_theta, self.cfg.rope_scaling)
+        if self.cfg.rope_local_theta:
+            batch.rope_local = ops.rope_tables(batch.position_ids, self.cfg.rotary_dim, self.cfg.rope_local_theta, None)
         full = None
         for layer in self.layers:
             ap = getattr(getattr(layer, 'self_attn', None), 'attn_parallel', None)
@@ -542,12 +556,22 @@ class DecoderModel(nn.Module):
         return x
 
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
-        return ops.linear(hidden, self.head_weight())
+        z = ops.linear(hidden, self.head_weight())
+        cap = self.cfg.final_logit_softcapping
+        return torch.tanh(z / cap) * cap if cap else z
 
     def token_logprobs(self, hidden: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0,
                        with_entropy: bool = False):
         """(logps [T] fp32, entropies|None) with ignored labels (−100) read as id 0."""
         safe = labels.clamp_min(0)
+        if self.cfg.final_logit_softcapping:
+            # capped logits (Gemma-2) are outside the fused head kernel: rows in chunks through the PyTorch form
+            lps, ents = [], []
+            for lo in range(0, hidden.shape[0], 4096):
+                lp, en = ops.ref.logprob_from_logits(self.logits(hidden[lo:lo + 4096]), safe[lo:lo + 4096], temperature, with_entropy)
+                lps.append(lp)
+                ents.append(en)
+            return torch.cat(lps), (torch.cat(ents) if with_entropy else None)
         if self.tp is not None:
             from ..parallel.tensor import CopyToTP, GatherTokens, vocab_parallel_logprob
             # backward of either op sums the per-vocabulary-shard partial gradients of the hidden states

@@ -154,11 +154,14 @@ def geglu(gate_up: torch.Tensor) -> torch.Tensor:
 
 # ----------------------------------------------------------------- attention
 def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor, causal: bool = True,
-                     scale: Optional[float] = None, return_lse: bool = False, cu_seqlens_k: Optional[torch.Tensor] = None):
+                     scale: Optional[float] = None, return_lse: bool = False, cu_seqlens_k: Optional[torch.Tensor] = None,
+                     window: Optional[int] = None, softcap: Optional[float] = None):
     """Packed attention.  ``q [T,Hq,D]``, ``k,v [Tk,Hkv,D]``, ``cu_seqlens`` int
     ``[n+1]``; tokens of different segments never attend to each other; GQA by
     repeating each kv head ``Hq/Hkv`` times.  With ``cu_seqlens_k`` the keys of a segment may be longer than its
-    queries; the causal diagonal is then aligned bottom-right (query row r sees keys 0 … r + Lk − Lq)."""
+    queries; the causal diagonal is then aligned bottom-right (query row r sees keys 0 … r + Lk − Lq).
+    ``window``: a query sees only the last ``window`` keys up to and including its own position (sliding-window
+    checkpoints); ``softcap``: scores pass through ``cap · tanh(s / cap)`` before the softmax (Gemma-2)."""
     T, Hq, D = q.shape
     Hkv = k.shape[1]
     rep = Hq // Hkv
@@ -174,9 +177,13 @@ def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
         ks = k[ka:kbnd].float().transpose(0, 1).repeat_interleave(rep, 0)
         vs = v[ka:kbnd].float().transpose(0, 1).repeat_interleave(rep, 0)
         s = qs @ ks.transpose(1, 2) * scale
+        if softcap:
+            s = torch.tanh(s / softcap) * softcap
         if causal:
             L, Lk = b - a, kbnd - ka
             s = s.masked_fill(torch.ones(L, Lk, dtype=torch.bool, device=q.device).triu(1 + Lk - L), float('-inf'))
+            if window and Lk > window:
+                s = s.masked_fill(torch.ones(L, Lk, dtype=torch.bool, device=q.device).tril(Lk - L - window), float('-inf'))
         l = torch.logsumexp(s, -1)
         p = torch.exp(s - l[..., None])
         out[a:b] = (p @ vs).transpose(0, 1).to(q.dtype)
@@ -185,7 +192,8 @@ def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
 
 
 def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
-                           seq_lens: torch.Tensor, scale: Optional[float] = None) -> torch.Tensor:
+                           seq_lens: torch.Tensor, scale: Optional[float] = None, window: Optional[int] = None,
+                           softcap: Optional[float] = None) -> torch.Tensor:
     """One query token per sequence against a paged KV cache.
     ``q [B,Hq,D]``; caches ``[num_blocks, block_size, Hkv, D]``; ``block_tables
     [B, max_blocks]`` int; ``seq_lens [B]`` (including the current token)."""
@@ -201,6 +209,10 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
         kk = k_cache[blocks].reshape(-1, Hkv, D)[:n].float().repeat_interleave(rep, 1)
         vv = v_cache[blocks].reshape(-1, Hkv, D)[:n].float().repeat_interleave(rep, 1)
         s = torch.einsum('hd,nhd->hn', q[b].float(), kk) * scale
+        if softcap:
+            s = torch.tanh(s / softcap) * softcap
+        if window and n > window:
+            s[:, :n - window] = float('-inf')
         out[b] = torch.einsum('hn,nhd->hd', torch.softmax(s, -1), vv).to(q.dtype)
     return out
 

@@ -170,6 +170,9 @@ class NativeEngine:
         cfg, B = self.cfg, tokens.shape[0]
         # ``positions`` index the KV cache; the rotary position differs from it after a prompt with images
         cos, sin = ops.rope_tables(positions if rope_positions is None else rope_positions, cfg.rotary_dim, cfg.rope_theta, cfg.rope_scaling)
+        local = None
+        if cfg.rope_local_theta:       # sliding-window layers of Gemma-3 rotate with a base of their own
+            local = ops.rope_tables(positions if rope_positions is None else rope_positions, cfg.rotary_dim, cfg.rope_local_theta, None)
         x = self.model.embed_ids(tokens)
         blk = table.gather(1, (positions // self.cache.block_size).unsqueeze(1)).squeeze(1).long()
         off = positions % self.cache.block_size
@@ -186,9 +189,10 @@ class NativeEngine:
                     n, x = layer.after_attention(x, y)
                     x = x + layer.feed_forward(n)
                     continue
-                q, k, v, gate = at.heads_from(h, cos, sin)
+                q, k, v, gate = at.heads_from(h, *(local if (local is not None and getattr(at, 'local_rope', False)) else (cos, sin)))
                 self.cache.k[li, blk, off], self.cache.v[li, blk, off] = at.cache_entry(k, v)
-                o = ops.paged_attention_decode(q, self.cache.k[li], self.cache.v[li], table, seq_lens, at.scale)
+                o = ops.paged_attention_decode(q, self.cache.k[li], self.cache.v[li], table, seq_lens, at.scale,
+                                               window=getattr(at, 'window', None), softcap=getattr(at, 'softcap', None))
                 n, x = layer.after_attention(x, at.project_out(o, gate))
                 x = x + layer.feed_forward(n)
             x = self.model.norm(x)
@@ -228,7 +232,9 @@ class NativeEngine:
         max_blocks = max(len(s.blocks) for s in seqs)
         lora = self._lora_for(seqs, [1] * B)
         use_graph = (self.use_cuda_graphs and self.device.type == 'cuda' and lora is None and not self.capture_routing and not self.cfg.is_moe
-                     and not any(getattr(l, 'is_linear', False) for l in self.model.layers) and not any(s.rope_delta for s in seqs))
+                     and not any(getattr(l, 'is_linear', False) for l in self.model.layers) and not any(s.rope_delta for s in seqs)
+                     # windows, score caps and latent attention decode through the PyTorch form, which reads lengths on the host
+                     and not self.cfg.sliding_window and not self.cfg.attn_logit_softcapping and not self.cfg.is_mla)
         if use_graph:
             Bb = 1 << max(B - 1, 0).bit_length()
             Mb = 1 << max(max_blocks - 1, 0).bit_length()
@@ -322,9 +328,6 @@ class NativeEngine:
         responses = [SampleResponse() for _ in prompts]
         seqs: List[_Seq] = []
         for i, (pr, sp) in enumerate(zip(prompts, params)):
-            if self.cfg.sliding_window and len(pr) + int(sp.max_tokens or 0) > self.cfg.sliding_window:
-                raise NotImplementedError(f'prompt {i}: {len(pr)} prompt + {sp.max_tokens} new tokens exceed the attention window '
-                                          f'({self.cfg.sliding_window}) this checkpoint was trained with; windowed attention is not implemented')
             lo = (lora[i] if lora else None) or {}
             for n in range(sp.num_samples):
                 g = None
