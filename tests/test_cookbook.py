@@ -116,3 +116,26 @@ def test_vision_language_sft_full_and_lora(tmp_path):
 def test_multimodal_grpo_runs_and_keeps_images_in_training_features():
     hist = _load('mm_grpo').main(['--steps', '2', '--prompts', '2', '--group', '2', '--max-tokens', '4'])
     assert len(hist) == 2 and all(h['sequences'] == 4 and h['loss'] == h['loss'] for h in hist)
+
+
+def test_deepseek_ep_lora_and_megatron_moe_scripts(tmp_path):
+    losses = _load('deepseek_ep_lora').main(['--steps', '4', '--seq-len', '48', '--seqs-per-rank', '2', '--out', str(tmp_path)])
+    assert losses[-1] < losses[0]
+    from safetensors.torch import load_file
+    keys = set(load_file(os.path.join(str(tmp_path), 'adapter', 'adapter_model.safetensors')))
+    assert any('mlp.experts.gate_up_proj' in k for k in keys) and any('q_b_proj' in k for k in keys) and not any('kv_a_proj_with_mqa' in k for k in keys)
+    losses = _load('megatron_tp_moe').main(['--steps', '3', '--seq-len', '48', '--micro-batches', '2'])
+    assert losses[-1] < losses[0]
+
+
+def test_server_config_examples_validate():
+    import glob
+
+    from twinkle_b200.server.config import ServerConfig
+    files = sorted(glob.glob(os.path.join(ROOT, 'cookbook', 'server_configs', '*.yaml')))
+    assert len(files) >= 3
+    for f in files:
+        cfg = ServerConfig.from_yaml(f)
+        assert cfg.applications[0].name == 'gateway'
+        for app in cfg.applications:
+            app.typed_args()                      # every application's arguments parse against its own schema

@@ -133,3 +133,13 @@ def test_pipeline_stages_match_one_process_and_tensor_parallel_is_refused():
 
     with pytest.raises(NotImplementedError):
         apply_tensor_parallel(build_model(preset('tiny-deepseek')), preset('tiny-deepseek'), _Two(), False)
+
+
+def test_adapter_config_can_exclude_modules():
+    """PEFT's ``exclude_modules`` (the reference's DeepSeek cookbook keeps one projection out of ``all-linear`` with it)."""
+    from twinkle_b200.model import MultiLoraTransformersModel
+    ml = MultiLoraTransformersModel(model_id='tiny-deepseek', seed=0, device='cpu', max_loras=1, max_r=8)
+    ml.add_adapter_to_model('a', {'r': 4, 'lora_alpha': 8, 'target_modules': 'all-linear', 'exclude_modules': ['kv_b_proj', 'o_proj']})
+    keys = set(ml.multi_lora.get_state_dict('a'))
+    assert any('q_b_proj' in k for k in keys) and not any('kv_b_proj' in k or '.o_proj.' in k for k in keys)
+    assert ml.optimizer_groups['a'].adapter_config.to_peft_dict()['exclude_modules'] == ['kv_b_proj', 'o_proj']

@@ -34,6 +34,7 @@ class LoraConfig:
     bias: str = 'none'
     task_type: str = 'CAUSAL_LM'
     target_parameters: Optional[List[str]] = None  # e.g. ['experts.gate_up_proj', 'experts.down_proj']
+    exclude_modules: Union[str, List[str], None] = None  # PEFT: module-name suffixes (or a full-match regex) kept out of ``target_modules``
     base_model_name_or_path: Optional[str] = None
 
     @property
@@ -50,8 +51,9 @@ class LoraConfig:
         if not isinstance(obj, dict):
             obj = {k: getattr(obj, k) for k in cls.__dataclass_fields__ if hasattr(obj, k)}
         known = {k: obj[k] for k in cls.__dataclass_fields__ if k in obj and obj[k] is not None}
-        if isinstance(known.get('target_modules'), (set, tuple)):
-            known['target_modules'] = sorted(known['target_modules'])
+        for k in ('target_modules', 'exclude_modules'):
+            if isinstance(known.get(k), (set, tuple)):
+                known[k] = sorted(known[k])
         return cls(**known)
 
     def to_peft_dict(self) -> Dict[str, Any]:
@@ -138,7 +140,7 @@ class MultiLora:
         free = [s for s in range(self.max_loras) if s not in used]
         if not free:
             raise RuntimeError(f'no free LoRA slot (max_loras={self.max_loras})')
-        self.tenants[tenant] = _Tenant(tenant, free[0], cfg, TargetFilter(cfg.target_modules))
+        self.tenants[tenant] = _Tenant(tenant, free[0], cfg, TargetFilter(cfg.target_modules, cfg.exclude_modules))
         return free[0]
 
     def release_lora(self, tenant: str) -> None:

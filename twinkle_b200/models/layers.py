@@ -83,17 +83,25 @@ def current_lora_batch() -> Optional[LoraBatch]:
 
 
 class TargetFilter:
-    """``'all-linear'``, a list of module-name suffixes, or a full-match regex."""
+    """``'all-linear'``, a list of module-name suffixes, or a full-match regex; ``exclude`` (same forms, PEFT's
+    ``exclude_modules``) takes modules back out."""
 
-    def __init__(self, spec):
+    def __init__(self, spec, exclude=None):
         self.spec = spec
         self._re = None
         if isinstance(spec, str) and spec not in ('all-linear', 'all'):
             self._re = re.compile(spec)
+        self.exclude = [exclude] if isinstance(exclude, str) and not any(c in exclude for c in '.*+?[(|') else exclude
+        self._ex_re = re.compile(exclude) if isinstance(self.exclude, str) else None
 
     def matches(self, full_name: str, short_name: str) -> bool:
         if short_name == 'q_gate':      # the output gate is the second half of HF's q_proj: one adapter covers both
             short_name, full_name = 'q_proj', full_name[:-len('q_gate')] + 'q_proj'
+        if self._ex_re is not None:
+            if self._ex_re.fullmatch(full_name):
+                return False
+        elif self.exclude and any(full_name == t or full_name.endswith('.' + t) or short_name == t for t in self.exclude):
+            return False
         s = self.spec
         if s is None or s in ('all-linear', 'all'):
             return short_name not in ('lm_head', 'gate')  # PEFT's all-linear excludes the output head; router kept off

@@ -79,6 +79,7 @@ class DeviceMeshSpec(_Strict):
     pp_size: Optional[int] = None
     cp_size: Optional[int] = None
     ep_size: Optional[int] = None
+    etp_size: Optional[int] = None
     ulysses_size: Optional[int] = None
     vpp_size: Optional[int] = None
     sequence_parallel: bool = False
