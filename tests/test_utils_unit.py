@@ -297,3 +297,22 @@ def test_safe_mode_refuses_callables_for_remote_calls(monkeypatch):
     for name in ('exists', 'requires', 'find_free_port', 'find_node_ip', 'trust_remote_code', 'check_unsafe', 'framework_util', 'torch_util',
                  'Plugin', 'is_master', 'init_twinkle_client', 'init_tinker_client', '__release_datetime__'):
         assert hasattr(tw, name), name
+
+
+def test_loader_expands_block_quantised_fp8_weights(tmp_path):
+    """A checkpoint that stores a weight in fp8 with a grid of inverse scales (one per 128 x 128 block) beside it reads as
+    bf16 through the lazy loader."""
+    from safetensors.torch import save_file
+
+    from twinkle_b200.utils.safetensors_io import SafetensorLazyLoader
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(256, 384, generator=g)
+    scale_inv = w.reshape(2, 128, 3, 128).abs().amax(dim=(1, 3)) / 448.0
+    q = (w.reshape(2, 128, 3, 128) / scale_inv[:, None, :, None]).reshape(256, 384).to(torch.float8_e4m3fn)
+    save_file({'model.layers.0.mlp.down_proj.weight': q, 'model.layers.0.mlp.down_proj.weight_scale_inv': scale_inv.contiguous(),
+               'model.norm.weight': torch.ones(8)}, str(tmp_path / 'model.safetensors'))
+    loader = SafetensorLazyLoader(str(tmp_path))
+    got = loader.get('model.layers.0.mlp.down_proj.weight')
+    assert got.dtype == torch.bfloat16 and got.shape == w.shape
+    assert float((got.float() - w).abs().max()) < 0.08 * float(w.abs().max())        # fp8 e4m3 keeps three mantissa bits
+    assert loader.get('model.norm.weight').dtype == torch.float32

@@ -46,7 +46,13 @@ class SafetensorLazyLoader:
         return self._open[fn]
 
     def get(self, name: str) -> torch.Tensor:
-        return self._handle(self._name_to_file[name]).get_tensor(name)
+        t = self._handle(self._name_to_file[name]).get_tensor(name)
+        if t.dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+            # block-quantised checkpoints (DeepSeek-V3 and the like) keep ``<name>_scale_inv`` beside an fp8 weight:
+            # expanded to bf16 on the way in, so every consumer of this loader sees ordinary weights
+            from .dequantizer import Dequantizer
+            t = Dequantizer.maybe_dequantize(name, t, lambda n: self._handle(self._name_to_file[n]).get_tensor(n) if n in self._name_to_file else None)
+        return t
 
     def get_slice(self, name: str):
         return self._handle(self._name_to_file[name]).get_slice(name)
