@@ -20,9 +20,28 @@ VC3 = dict(depth=3, hidden_size=64, out_hidden_size=128, intermediate_size=96, n
            in_channels=3, num_position_embeddings=64, deepstack_visual_indexes=[0, 1])    # position table 8 × 8; two deep-stack taps
 
 
+VC35 = dict(depth=3, hidden_size=64, out_hidden_size=128, intermediate_size=96, num_heads=4, patch_size=16, spatial_merge_size=2, temporal_patch_size=2,
+            in_channels=3, num_position_embeddings=64)      # the Qwen3-VL tower without deep-stack taps
+
+
 def _hf(family='qwen2_vl'):
     T = pytest.importorskip('transformers')
     try:
+        if family == 'qwen3_5':     # hybrid decoder (Gated DeltaNet + gated attention, rotary on a quarter of the head) behind the tower
+            text = dict(vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+                        head_dim=64, max_position_embeddings=512, tie_word_embeddings=False, linear_num_key_heads=2, linear_num_value_heads=4,
+                        linear_key_head_dim=16, linear_value_head_dim=16, linear_conv_kernel_dim=4,
+                        layer_types=['linear_attention', 'full_attention', 'linear_attention', 'full_attention'],
+                        rope_parameters={'rope_type': 'default', 'rope_theta': 10000.0, 'partial_rotary_factor': 0.25, 'mrope_section': [2, 3, 3],
+                                         'mrope_interleaved': True})
+            cfg = T.Qwen3_5Config(text_config=text, vision_config=VC35, image_token_id=500, video_token_id=501, vision_start_token_id=502,
+                                  vision_end_token_id=503)
+            torch.manual_seed(0)
+            hf = T.Qwen3_5ForConditionalGeneration(cfg).float().eval()
+            for n, p in hf.named_parameters():
+                if p.dim() == 1 and 'A_log' not in n and 'dt_bias' not in n:
+                    torch.nn.init.normal_(p, 0.0 if ('bias' in n or ('norm' in n and 'visual' not in n and 'linear_attn.norm' not in n)) else 1.0, 0.1)
+            return T, cfg, hf
         conf, cls, vc = {'qwen2_vl': (T.Qwen2VLConfig, T.Qwen2VLForConditionalGeneration, VC),
                          'qwen2_5_vl': (T.Qwen2_5_VLConfig, T.Qwen2_5_VLForConditionalGeneration, VC25),
                          'qwen3_vl': (T.Qwen3VLConfig, T.Qwen3VLForConditionalGeneration, VC3)}[family]
@@ -78,14 +97,14 @@ def test_positions_and_tables_by_hand():
     assert torch.equal(flat[2].view(3, 2, 14, 14)[:, 0], frames[0, :, 14:28, 0:14])
 
 
-@pytest.mark.parametrize('family', ['qwen2_vl', 'qwen2_5_vl', 'qwen3_vl'])
+@pytest.mark.parametrize('family', ['qwen2_vl', 'qwen2_5_vl', 'qwen3_vl', 'qwen3_5'])
 def test_tower_positions_and_full_model_match_transformers(family, tmp_path):
     T, cfg, hf = _hf(family)
     from twinkle_b200.models.bridge import hf_to_internal
     from twinkle_b200.models.config import DecoderConfig
     from twinkle_b200.models.decoder import PackedBatch, build_model
     ids, grid, pix = (_sample() if family == 'qwen2_vl' else _sample(((1, 6, 10), (1, 8, 6))) if family == 'qwen2_5_vl' else   # several windows, ragged edges
-                      _sample(((1, 4, 6), (1, 6, 4)), patch=16))
+                      _sample(((1, 4, 6), (1, 6, 4)), patch=16))       # Qwen3-VL and Qwen3.5: 16-pixel patches
     tower = VisionTower(VisionConfig.from_hf(cfg.vision_config.to_dict())).float().eval()
     tower.load_state_dict({k[len('model.visual.'):]: v for k, v in hf.state_dict().items() if k.startswith('model.visual.')})
     ids_t = torch.tensor([ids])
@@ -108,8 +127,8 @@ def test_tower_positions_and_full_model_match_transformers(family, tmp_path):
     # for Qwen2-VL only (the logits above were computed from the same positions on both sides)
     assert torch.equal(mine[1:], want_pos[1:]) and (family == 'qwen2_5_vl' or torch.equal(mine, want_pos))
     dc = DecoderConfig.from_hf(cfg.to_dict())
-    assert dc.mrope_section == [4, 6, 6] and dc.image_token_id == 500 and dc.rope_scaling is None
-    assert (dc.attention_bias, dc.qk_norm, dc.mrope_interleaved) == ((False, True, True) if family == 'qwen3_vl' else (True, False, False))
+    assert dc.mrope_section == ([2, 3, 3] if family == 'qwen3_5' else [4, 6, 6]) and dc.image_token_id == 500 and dc.rope_scaling is None
+    assert (dc.attention_bias, dc.qk_norm, dc.mrope_interleaved) == ((False, True, True) if family in ('qwen3_vl', 'qwen3_5') else (True, False, False))
     m = build_model(dc)
     sd = hf.state_dict()
     with torch.no_grad():
@@ -591,3 +610,43 @@ def test_freezing_one_side_of_a_vision_language_model(which):
     tower_moved = not torch.equal(tower0, m.model.visual.merger.mlp[2].weight)
     llm_moved = not torch.equal(llm0, m.model.layers[0].mlp.down_proj.weight)
     assert (tower_moved, llm_moved) == ((False, True) if which == 'freeze_vision' else (True, False)) and losses[-1] < losses[0]
+
+
+def test_qwen3_5_vision_language_trains_through_the_public_api_and_exports(tmp_path):
+    """Qwen3.5 with its tower: image parts through ``Qwen3_5Template`` (which takes the model's vision config by itself), training
+    of tower + hybrid decoder, and an export that reloads here and in ``transformers`` with the same outputs."""
+    from twinkle_b200.model import TransformersModel
+    m = TransformersModel(model_id='tiny-qwen3.5-vl', seed=0, device='cpu')
+    m.set_template('Qwen3_5Template', max_length=4096)
+    g = torch.Generator().manual_seed(0)
+    trajs = [{'messages': [{'role': 'user', 'content': [{'type': 'image', 'image': torch.rand(3, 64, 96, generator=g) * 255}, {'type': 'text', 'text': 'what?'}]},
+                           {'role': 'assistant', 'content': 'a red ball'}]},
+             {'messages': [{'role': 'user', 'content': 'plain text'}, {'role': 'assistant', 'content': 'yes'}]}]
+    tpl = m._group(None).template
+    f = tpl.encode(trajs[0])
+    assert f['image_grid_thw'] == [[1, 4, 6]] and f['pixel_values'].shape == (24, 3 * 2 * 16 * 16) and f['mrope_position_ids'].shape[0] == 3
+    m.set_optimizer('AdamW', lr=1e-2)
+    w0 = m.model.visual.merger.linear_fc2.weight.detach().clone()
+    losses = []
+    for _ in range(4):
+        losses.append(float(m.forward_backward(inputs=trajs)['loss']))
+        m.clip_grad_and_step(max_grad_norm=1.0)
+    assert losses[-1] < 0.8 * losses[0] and not torch.equal(w0, m.model.visual.merger.linear_fc2.weight)
+    out = m.save('ck', str(tmp_path))
+    cfg = json.load(open(out + '/config.json'))
+    assert cfg['model_type'] == 'qwen3_5' and cfg['text_config']['rope_parameters']['mrope_section'] == [2, 3, 3] and cfg['vision_config']['model_type'] == 'qwen3_5'
+    m2 = TransformersModel(model_id=out, seed=1, device='cpu')
+    m2.set_template('Qwen3_5Template', max_length=4096)
+    la, lb = m.forward_only(inputs=trajs), m2.forward_only(inputs=trajs)
+    assert torch.allclose(torch.as_tensor(la['logps']).float(), torch.as_tensor(lb['logps']).float(), atol=1e-5)
+    T = pytest.importorskip('transformers')
+    try:
+        back = T.Qwen3_5ForConditionalGeneration.from_pretrained(out).float().eval()
+        ids = torch.tensor([f['input_ids']])
+        with torch.no_grad():
+            theirs = back(input_ids=ids, pixel_values=f['pixel_values'], image_grid_thw=torch.tensor(f['image_grid_thw']),
+                          mm_token_type_ids=(ids == tpl.image_token_id).int()).logits[0]
+    except (TypeError, AttributeError, OSError, ValueError) as e:
+        pytest.skip(f'transformers could not run the export: {type(e).__name__}: {e}')
+    ours = torch.as_tensor(m.forward_only(inputs=[trajs[0]], return_logits=True)['logits']).float().reshape(-1, theirs.shape[-1])[:theirs.shape[0]]
+    assert torch.allclose(ours, theirs, atol=5e-5), float((ours - theirs).abs().max())

@@ -806,6 +806,9 @@ class TransformersModel(TwinkleModel, CheckpointEngineMixin):
         if isinstance(template_cls, str):
             template_cls = template_mapping.get(template_cls, Template)
         kwargs.setdefault('model_id', self.model_id)
+        from ..template.base import Qwen2VLTemplate
+        if isinstance(template_cls, type) and issubclass(template_cls, Qwen2VLTemplate) and self.config.vision:
+            kwargs.setdefault('vision_config', self.config.vision)      # image parts are cut into this model's own patch grid
         og.template = template_cls(**kwargs) if isinstance(template_cls, type) else template_cls
 
     @remote_function()

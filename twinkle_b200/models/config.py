@@ -226,12 +226,10 @@ class DecoderConfig:
         vision = top.get('vision_config')
         if vision is not None:
             vision = dict(vision)
-            if vision.get('model_type', top.get('model_type', 'qwen2_vl')) not in ('qwen2_vl', 'qwen2_5_vl', 'qwen3_vl', 'qwen3_vl_moe'):
-                raise NotImplementedError(f"vision tower of type {vision.get('model_type')!r} is not supported (qwen2_vl, qwen2_5_vl and qwen3_vl are)")
+            if vision.get('model_type', top.get('model_type', 'qwen2_vl')) not in ('qwen2_vl', 'qwen2_5_vl', 'qwen3_vl', 'qwen3_vl_moe', 'qwen3_5', 'qwen3_5_moe'):
+                raise NotImplementedError(f"vision tower of type {vision.get('model_type')!r} is not supported (qwen2_vl, qwen2_5_vl, qwen3_vl and qwen3_5 are)")
         rs_any = cfg.get('rope_scaling') or cfg.get('rope_parameters') or top.get('rope_scaling') or {}
         q35 = mt.startswith('qwen3_5') or mt == 'qwen3_next'      # the hybrid family: gated attention, partial rotary, "1 + w" norms
-        if q35 and vision is not None:
-            vision = None        # the language model of a Qwen3.5 checkpoint trains without its tower here (text-only batches)
         heads = cfg.get('num_attention_heads', 32)
         mla = mt in ('deepseek_v3', 'kimi_k2')
         dsv3 = mla or mt == 'glm4_moe'        # GLM-4.5 routes like DeepSeek-V3 over ordinary grouped-query attention
@@ -287,7 +285,7 @@ class DecoderConfig:
             linear_conv_kernel_dim=cfg.get('linear_conv_kernel_dim', 4),
             vision=vision, image_token_id=top.get('image_token_id'), video_token_id=top.get('video_token_id'),
             vision_start_token_id=top.get('vision_start_token_id'), vision_end_token_id=top.get('vision_end_token_id'),
-            mrope_section=list(rs_any['mrope_section']) if isinstance(rs_any, dict) and rs_any.get('mrope_section') and not q35 else None,
+            mrope_section=list(rs_any['mrope_section']) if isinstance(rs_any, dict) and rs_any.get('mrope_section') and (vision is not None or not q35) else None,
             mrope_interleaved=bool(isinstance(rs_any, dict) and rs_any.get('mrope_interleaved')),
             initializer_range=cfg.get('initializer_range', 0.02), model_type=mt,
             torch_dtype=str(cfg.get('torch_dtype', cfg.get('dtype', 'bfloat16'))),
@@ -368,7 +366,7 @@ class DecoderConfig:
             d.update(architectures=['InternLM3ForCausalLM'], qkv_bias=self.attention_bias, bias=False)
         if self.rope_scaling:
             d['rope_scaling'] = dict(self.rope_scaling)
-        if self.vision:
+        if self.vision and not self.model_type.startswith('qwen3_5'):
             fam = self.vision.get('model_type', 'qwen2_vl')
             if fam == 'qwen3_vl' and self.is_moe:
                 fam = 'qwen3_vl_moe'
@@ -406,6 +404,14 @@ class DecoderConfig:
                      rope_parameters={'rope_type': 'default', 'rope_theta': self.rope_theta, 'partial_rotary_factor': self.partial_rotary_factor},
                      layer_types=list(self.layer_types or ['full_attention'] * self.num_hidden_layers))
             d.pop('rms_norm_offset', None)
+            if self.vision:      # the full model: the Qwen3-VL tower without its deep-stack taps in front of the hybrid decoder
+                fam = 'qwen3_5_moe' if self.is_moe else 'qwen3_5'
+                d['rope_parameters'].update(mrope_section=list(self.mrope_section or []), mrope_interleaved=self.mrope_interleaved)
+                text = {k: v for k, v in d.items() if k != 'architectures'}
+                return {'architectures': ['Qwen3_5MoeForConditionalGeneration' if self.is_moe else 'Qwen3_5ForConditionalGeneration'], 'model_type': fam,
+                        'text_config': text, 'vision_config': dict(self.vision, model_type=fam), 'image_token_id': self.image_token_id,
+                        'video_token_id': self.video_token_id, 'vision_start_token_id': self.vision_start_token_id,
+                        'vision_end_token_id': self.vision_end_token_id, 'tie_word_embeddings': self.tie_word_embeddings, 'torch_dtype': self.torch_dtype}
         elif self.partial_rotary_factor != 1.0 or self.attn_output_gate:
             d.update(partial_rotary_factor=self.partial_rotary_factor, attn_output_gate=self.attn_output_gate)
         return d
@@ -454,6 +460,15 @@ PRESETS: Dict[str, Dict[str, Any]] = {
                      vision_end_token_id=266,
                      vision=dict(depth=3, hidden_size=64, out_hidden_size=256, intermediate_size=96, num_heads=4, patch_size=16, spatial_merge_size=2,
                                  temporal_patch_size=2, in_channels=3, num_position_embeddings=64, deepstack_visual_indexes=[0, 2])),
+    # Qwen3.5 vision-language in small: the Qwen3-VL tower (no deep-stack taps) in front of the hybrid decoder
+    'tiny-qwen3.5-vl': dict(vocab_size=1024, hidden_size=256, intermediate_size=688, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+                            head_dim=64, rope_theta=1e4, tie_word_embeddings=True, qk_norm=True, torch_dtype='float32', model_type='qwen3_5',
+                            rms_norm_offset=1.0, partial_rotary_factor=0.25, attn_output_gate=True,
+                            layer_types=['linear_attention', 'linear_attention', 'linear_attention', 'full_attention'], linear_num_key_heads=2,
+                            linear_num_value_heads=4, linear_key_head_dim=32, linear_value_head_dim=32, mrope_section=[2, 3, 3], mrope_interleaved=True,
+                            image_token_id=265, video_token_id=267, vision_start_token_id=264, vision_end_token_id=266,
+                            vision=dict(depth=2, hidden_size=64, out_hidden_size=256, intermediate_size=96, num_heads=4, patch_size=16, spatial_merge_size=2,
+                                        temporal_patch_size=2, in_channels=3, num_position_embeddings=64)),
     'tiny-moe-shared': dict(vocab_size=1024, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
                             head_dim=64, rope_theta=1e4, tie_word_embeddings=True, num_experts=8, num_experts_per_tok=2,
                             moe_intermediate_size=128, shared_expert_intermediate_size=192, torch_dtype='float32'),

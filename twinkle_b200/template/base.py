@@ -350,14 +350,6 @@ class Qwen3Template(Template):
     pass
 
 
-class Qwen3_5Template(Template):
-    """Hybrid-thinking chat format: an empty ``<think>`` block is emitted when
-    thinking is disabled so that the label mask matches generation."""
-
-    def __init__(self, *a, enable_thinking: bool = True, **kw):
-        super().__init__(*a, enable_thinking=enable_thinking, **kw)
-
-
 class DeepseekV4Template(Template):
     pass
 
@@ -459,6 +451,17 @@ class Qwen2VLTemplate(Template):
         return feats
 
 
+class Qwen3_5Template(Qwen2VLTemplate):
+    """Qwen3.5: the hybrid-thinking chat format (an empty ``<think>`` block is emitted when thinking is disabled, so that the
+    label mask matches generation) with the family's image and video parts (reference ``template/qwen3_5_vl.py:33-200``, where
+    the one class serves text and vision-language checkpoints alike).  Without ``vision_config`` — a text-only checkpoint —
+    it is a plain chat template; a trajectory that carries images then fails in the tower-less model, not here."""
+
+    def __init__(self, *a, enable_thinking: bool = True, vision_config=None, **kw):
+        super().__init__(*a, enable_thinking=enable_thinking, vision_config=vision_config, **kw)
+
+
 template_mapping = {'Template': Template, 'default': Template, 'Qwen3Template': Qwen3Template, 'qwen3': Qwen3Template,
                     'Qwen3_5Template': Qwen3_5Template, 'qwen3_5': Qwen3_5Template, 'DeepseekV4Template': DeepseekV4Template,
-                    'Qwen2VLTemplate': Qwen2VLTemplate, 'qwen2_vl': Qwen2VLTemplate}
+                    'Qwen2VLTemplate': Qwen2VLTemplate, 'qwen2_vl': Qwen2VLTemplate, 'Qwen3VLTemplate': Qwen2VLTemplate, 'qwen3_vl': Qwen2VLTemplate,
+                    'Qwen3_5VLTemplate': Qwen3_5Template, 'qwen3_5_vl': Qwen3_5Template}
