@@ -608,3 +608,42 @@ def test_gated_delta_rule_and_conv_kernels(E):
     xr, wr = x.float().clone().requires_grad_(True), w.float().clone().requires_grad_(True)
     causal_conv1d_varlen_torch(xr, wr, cu, True).sum().backward()
     assert rel(xg.grad, xr.grad) < 1e-2 and rel(wg.grad, wr.grad) < 1e-2
+
+
+def test_latent_attention_and_windowed_stacks_train_on_gpu_like_on_cpu(E):
+    """Two of the families that leave the plain Llama computation, in bf16 on the GPU against fp32 on the CPU: a DeepSeek-V3
+    shaped stack (latent attention with 128-wide score and value heads, so it runs the flash kernels; sigmoid group-limited
+    routing feeding the grouped expert GEMMs; frozen selection bias beside trained tensors) and a Gemma-2 shaped one (rows longer
+    than the attention window, capped scores and logits, GeGLU kernel, scaled embeddings, four norms per layer)."""
+    from twinkle_b200.model import TransformersModel
+    from twinkle_b200.models import preset
+    from twinkle_b200.utils.device_mesh import DeviceMesh
+    deepseek = preset('tiny-deepseek', hidden_size=512, intermediate_size=1024, q_lora_rank=128, kv_lora_rank=128, qk_nope_head_dim=64,
+                      qk_rope_head_dim=64, v_head_dim=128, head_dim=128, moe_intermediate_size=256, shared_expert_intermediate_size=256, vocab_size=2048)
+    gemma = preset('tiny-dense', model_type='gemma2', hidden_size=512, intermediate_size=1024, num_hidden_layers=4, num_attention_heads=4,
+                   num_key_value_heads=2, head_dim=128, vocab_size=2048, sliding_window=64, qk_norm=False,
+                   layer_types=['sliding_attention', 'full_attention', 'sliding_attention', 'full_attention'], sandwich_norm=True, rms_norm_offset=1.0,
+                   hidden_act='gelu_pytorch_tanh', embed_scale=512**0.5, query_pre_attn_scalar=128.0, attn_logit_softcapping=50.0,
+                   final_logit_softcapping=30.0)
+    g = torch.Generator().manual_seed(11)
+    feats = []
+    for n in (161, 97, 130):
+        ids = torch.randint(0, 2048, (n, ), generator=g)
+        feats.append({'input_ids': ids[:-1], 'labels': ids[1:]})
+
+    def curve(cfg, device):
+        m = TransformersModel(config=cfg, device_mesh=DeviceMesh.from_sizes(dp_size=1), seed=0, device=device)
+        m.set_optimizer('AdamW', lr=1e-3)
+        out = []
+        for _ in range(3):
+            o = m.forward_backward(inputs=feats, micro_batch_size=3)
+            m.clip_grad_and_step(max_grad_norm=1.0)
+            out.append(float(o['loss']))
+        return out
+
+    for cfg in (deepseek, gemma):
+        cpu, gpu = curve(cfg, 'cpu'), curve(cfg, 'cuda')
+        assert cpu[0] > cpu[-1] and gpu[0] > gpu[-1], (cpu, gpu)
+        for a, b in zip(cpu, gpu):
+            assert abs(a - b) < 8e-2, (cfg.model_type, cpu, gpu)
+    assert E.read_and_clear_error() == 0

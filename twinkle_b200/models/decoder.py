@@ -185,7 +185,7 @@ class MLAttention(nn.Module):
         q = q.view(T, self.nh, self.nope + self.rope)
         ckv = self.kv_a_proj_with_mqa(x)
         latent, k_rot = ckv[:, :self.cfg.kv_lora_rank], ckv[:, self.cfg.kv_lora_rank:]
-        kv = self.kv_b_proj(self.kv_a_layernorm(latent)).view(T, self.nh, self.nope + self.vd)
+        kv = self.kv_b_proj(self.kv_a_layernorm(latent.contiguous())).view(T, self.nh, self.nope + self.vd)
         q_rot = self._rotate(q[..., self.nope:], cos, sin)
         k_rot = self._rotate(k_rot.reshape(T, 1, self.rope), cos, sin).expand(T, self.nh, self.rope)
         return torch.cat([q[..., :self.nope], q_rot], -1), torch.cat([kv[..., :self.nope], k_rot], -1), kv[..., self.nope:], None

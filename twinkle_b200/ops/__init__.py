@@ -159,7 +159,7 @@ class _RMSNorm(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, weight, eps, offset):
-        x2 = x.reshape(-1, x.shape[-1])
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()       # a column slice of a wider tensor arrives strided
         y, rstd = ext().rmsnorm_fwd(x2, weight, eps, offset)
         ctx.save_for_backward(x2, weight, rstd)
         ctx.offset = offset
