@@ -81,6 +81,12 @@ def _cases():
                                                    qk_rope_head_dim=16, v_head_dim=24, routed_scaling_factor=2.5, norm_topk_prob=True,
                                                    tie_word_embeddings=False, **{**COMMON, 'num_hidden_layers': 3, 'num_key_value_heads': 4}),
                         'DeepseekV3ForCausalLM'),
+        # DeepSeek-V2 (Lite form: plain query projection): softmax scores, groups ranked by their best expert, weights scaled but not renormalised
+        'deepseek_v2': (lambda: T.DeepseekV2Config(moe_intermediate_size=64, n_routed_experts=8, n_shared_experts=2, num_experts_per_tok=2, n_group=4,
+                                                   topk_group=2, topk_method='group_limited_greedy', first_k_dense_replace=1, q_lora_rank=None,
+                                                   kv_lora_rank=32, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=24, routed_scaling_factor=16.0,
+                                                   tie_word_embeddings=False, **{**COMMON, 'num_hidden_layers': 3, 'num_key_value_heads': 4}),
+                        'DeepseekV2ForCausalLM'),
         'deepseek_v3_yarn': (lambda: T.DeepseekV3Config(moe_intermediate_size=64, n_routed_experts=4, n_shared_experts=2, num_experts_per_tok=2, n_group=1,
                                                         topk_group=1, first_k_dense_replace=0, q_lora_rank=None, kv_lora_rank=32, qk_nope_head_dim=32,
                                                         qk_rope_head_dim=16, v_head_dim=32, routed_scaling_factor=1.0, norm_topk_prob=False,
@@ -113,6 +119,9 @@ def _hf_model(name):
             torch.nn.init.normal_(p, 1.0, 0.1)
         elif p.dim() == 1:
             torch.nn.init.normal_(p, 0.0, 0.1)
+    for mod in hf.modules():       # this transformers build's DeepSeek-V2 group routing reads an attribute its constructor never sets
+        if hasattr(mod, 'topk_method') and not hasattr(mod, 'num_experts'):
+            mod.num_experts = hf.config.n_routed_experts
     for n, b in hf.named_buffers():
         if n.endswith('e_score_correction_bias'):      # the selection bias is a buffer there; non-zero, so that it matters
             torch.nn.init.normal_(b, 0.0, 0.2)
@@ -141,7 +150,7 @@ def test_hf_checkpoint_gives_the_same_logits_here(name, tmp_path):
 
 
 @pytest.mark.parametrize('name', ['qwen3', 'qwen3_moe', 'mixtral', 'qwen2_moe_shared', 'qwen3_5', 'qwen3_5_moe', 'qwen3_next', 'glm', 'glm4', 'phi3',
-                                  'phi3_longrope', 'gemma', 'deepseek_v3', 'deepseek_v3_yarn', 'glm4_moe', 'gemma2', 'gemma3'])
+                                  'phi3_longrope', 'gemma', 'deepseek_v2', 'deepseek_v3', 'deepseek_v3_yarn', 'glm4_moe', 'gemma2', 'gemma3'])
 def test_checkpoint_saved_here_loads_in_transformers(name, tmp_path):
     hf = _hf_model(name)
     hf.save_pretrained(str(tmp_path / 'hf'), safe_serialization=True)
@@ -149,6 +158,9 @@ def test_checkpoint_saved_here_loads_in_transformers(name, tmp_path):
     m, ours = _ours(str(tmp_path / 'hf'), ids[0])
     out = m.save('export', str(tmp_path / 'ours'))
     back = getattr(transformers, _cases()[name][1]).from_pretrained(out).float().eval()
+    for mod in back.modules():
+        if hasattr(mod, 'topk_method') and not hasattr(mod, 'num_experts'):
+            mod.num_experts = back.config.n_routed_experts
     with torch.no_grad():
         theirs = back(ids).logits[0]
     assert torch.allclose(ours, theirs, atol=6e-5 if name in ('gemma2', 'gemma3') else 2e-5), float((ours - theirs).abs().max())

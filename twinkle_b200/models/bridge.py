@@ -52,7 +52,7 @@ def _family(name: str, cfg: DecoderConfig) -> str:
     if cfg.model_type == 'mixtral':
         for pat, rep in _MIXTRAL:
             name = pat.sub(rep, name)
-    elif cfg.model_type in ('deepseek_v3', 'kimi_k2', 'glm4_moe'):
+    elif cfg.model_type in ('deepseek_v2', 'deepseek_v3', 'kimi_k2', 'glm4_moe'):
         name = name.replace('.mlp.shared_expert.', '.mlp.shared_experts.').replace('.mlp.e_score_correction_bias', '.mlp.gate.e_score_correction_bias')
     elif cfg.model_type in ('gemma2', 'gemma3_text', 'gemma3'):
         # four norms per layer there: input, after attention, before and after the feed-forward block
@@ -257,7 +257,7 @@ def hf_to_internal(name: str, cfg: DecoderConfig, get: Callable[[str], torch.Ten
     m = _LAYER.match(name)
     rest = m.group(2) if m else ''
     i = int(m.group(1)) if m else -1
-    if cfg.model_type in ('mixtral', 'internlm2', 'deepseek_v3', 'kimi_k2', 'glm4_moe'):      # names that are built without hf_names_for
+    if cfg.model_type in ('mixtral', 'internlm2', 'deepseek_v2', 'deepseek_v3', 'kimi_k2', 'glm4_moe'):      # names that are built without hf_names_for
         plain = get
 
         def get(n: str) -> torch.Tensor:  # noqa: F811

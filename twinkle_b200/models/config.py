@@ -18,7 +18,7 @@ from typing import List, Any, Dict, Optional
 SUPPORTED_MODEL_TYPES = frozenset({'llama', 'mistral', 'mixtral', 'qwen2', 'qwen2_moe', 'qwen3', 'qwen3_moe', 'seed_oss', 'qwen2_vl', 'qwen2_vl_text',
                                    'qwen2_5_vl', 'qwen2_5_vl_text', 'qwen3_vl', 'qwen3_vl_text', 'qwen3_vl_moe', 'qwen3_vl_moe_text',
                                    'qwen3_5', 'qwen3_5_text', 'qwen3_5_moe', 'qwen3_5_moe_text', 'qwen3_next', 'glm', 'glm4',
-                                   'phi3', 'internlm2', 'internlm3', 'gemma', 'deepseek_v3', 'kimi_k2', 'glm4_moe', 'gemma2', 'gemma3_text', 'gemma3'})
+                                   'phi3', 'internlm2', 'internlm3', 'gemma', 'deepseek_v2', 'deepseek_v3', 'kimi_k2', 'glm4_moe', 'gemma2', 'gemma3_text', 'gemma3'})
 
 
 def _rope_scaling_of(cfg: Dict[str, Any]) -> Optional[Dict[str, Any]]:
@@ -162,7 +162,7 @@ class DecoderConfig:
             return float(self.query_pre_attn_scalar or self.head_dim)**-0.5
         sc = (self.qk_nope_head_dim + self.qk_rope_head_dim)**-0.5
         rs = self.rope_scaling or {}
-        if rs.get('mscale_all_dim') and float(rs.get('factor', 1.0)) > 1.0:
+        if rs.get('mscale_all_dim') and float(rs.get('factor', 1.0)) > 1.0 and self.model_type != 'deepseek_v2':
             m = 0.1 * float(rs['mscale_all_dim']) * math.log(float(rs['factor'])) + 1.0
             sc = sc * m * m
         return sc
@@ -231,7 +231,8 @@ class DecoderConfig:
         rs_any = cfg.get('rope_scaling') or cfg.get('rope_parameters') or top.get('rope_scaling') or {}
         q35 = mt.startswith('qwen3_5') or mt == 'qwen3_next'      # the hybrid family: gated attention, partial rotary, "1 + w" norms
         heads = cfg.get('num_attention_heads', 32)
-        mla = mt in ('deepseek_v3', 'kimi_k2')
+        mla = mt in ('deepseek_v2', 'deepseek_v3', 'kimi_k2')
+        v2 = mt == 'deepseek_v2'      # softmax scores, groups ranked by their best expert, no selection bias, weights not renormalised
         dsv3 = mla or mt == 'glm4_moe'        # GLM-4.5 routes like DeepSeek-V3 over ordinary grouped-query attention
         window = cfg.get('sliding_window')
         if mt.startswith('qwen') and not cfg.get('use_sliding_window'):
@@ -257,7 +258,8 @@ class DecoderConfig:
             rope_scaling=_rope_scaling_of(cfg), tie_word_embeddings=bool(cfg.get('tie_word_embeddings', False)),
             qk_norm=mt.startswith('qwen3') or mt.startswith('gemma3') or (mt == 'glm4_moe' and bool(cfg.get('use_qk_norm'))),
             attention_bias=bool(cfg.get('attention_bias', cfg.get('qkv_bias', cfg.get('bias', False)) if mt.startswith('internlm') else mt.startswith('qwen2'))),
-            router_scoring='sigmoid' if dsv3 else 'softmax', router_bias=dsv3, n_group=int(cfg.get('n_group') or 1) if dsv3 else 1,
+            router_scoring=('softmax_grouped' if v2 else 'sigmoid') if dsv3 else 'softmax', router_bias=dsv3 and not v2,
+            n_group=int(cfg.get('n_group') or 1) if (dsv3 and not (v2 and cfg.get('topk_method', 'greedy') == 'greedy')) else 1,
             topk_group=int(cfg.get('topk_group') or 1) if dsv3 else 1, routed_scaling_factor=float(cfg.get('routed_scaling_factor', 1.0)) if dsv3 else 1.0,
             first_k_dense_replace=int(cfg.get('first_k_dense_replace', 0)) if dsv3 else 0, shared_expert_gate=not dsv3,
             q_lora_rank=cfg.get('q_lora_rank') if mla else None, kv_lora_rank=int(cfg.get('kv_lora_rank', 0)) if mla else 0,
@@ -272,7 +274,7 @@ class DecoderConfig:
             num_experts=cfg.get('num_experts', cfg.get('num_local_experts', cfg.get('n_routed_experts', 0))) or 0,
             num_experts_per_tok=cfg.get('num_experts_per_tok', 8),
             moe_intermediate_size=cfg.get('moe_intermediate_size', cfg.get('intermediate_size', 768) if mt == 'mixtral' else 768),
-            norm_topk_prob=True if cfg.get('norm_topk_prob') is None else bool(cfg['norm_topk_prob']), router_aux_loss_coef=float(cfg.get('router_aux_loss_coef', 0.0)),
+            norm_topk_prob=(True if cfg.get('norm_topk_prob') is None else bool(cfg['norm_topk_prob'])) and not v2, router_aux_loss_coef=float(cfg.get('router_aux_loss_coef', 0.0)),
             shared_expert_intermediate_size=int(cfg.get('shared_expert_intermediate_size', 0) or 0) if not dsv3
             else int(cfg.get('moe_intermediate_size', 0)) * int(cfg.get('n_shared_experts') or 0),
             rms_norm_offset=float(cfg.get('rms_norm_offset', 1.0 if (mt.startswith('gemma') or q35) else 0.0)),
@@ -324,7 +326,8 @@ class DecoderConfig:
         if self.sliding_window:
             d['sliding_window'] = self.sliding_window
         if self.is_mla:
-            d.update(architectures=['DeepseekV3ForCausalLM'], model_type=self.model_type, q_lora_rank=self.q_lora_rank, kv_lora_rank=self.kv_lora_rank,
+            d.update(architectures=['DeepseekV2ForCausalLM' if self.model_type == 'deepseek_v2' else 'DeepseekV3ForCausalLM'], model_type=self.model_type,
+                     topk_method='group_limited_greedy' if self.n_group > 1 else 'greedy', q_lora_rank=self.q_lora_rank, kv_lora_rank=self.kv_lora_rank,
                      qk_nope_head_dim=self.qk_nope_head_dim, qk_rope_head_dim=self.qk_rope_head_dim, v_head_dim=self.v_head_dim,
                      rope_interleave=self.mla_rope_interleave, head_dim=self.qk_rope_head_dim, n_routed_experts=self.num_experts,
                      n_shared_experts=(self.shared_expert_intermediate_size // self.moe_intermediate_size) if self.num_experts else 0,

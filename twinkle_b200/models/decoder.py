@@ -307,7 +307,7 @@ class MoEBlock(nn.Module):
         self.record_routing = False
 
     def route(self, x: torch.Tensor, forced: Optional[torch.Tensor]):
-        if self.cfg.router_scoring == 'sigmoid':
+        if self.cfg.router_scoring != 'softmax':
             return self._route_sigmoid(x, forced)
         w, idx, probs, self._hist = ops.moe_router(self.gate(x), self.cfg.num_experts_per_tok, self.cfg.norm_topk_prob, forced)
         return w, idx, probs
@@ -318,11 +318,14 @@ class MoEBlock(nn.Module):
         highest; the weights are the unbiased scores of the chosen experts, normalised and scaled."""
         cfg = self.cfg
         E, k = cfg.num_experts, cfg.num_experts_per_tok
-        scores = torch.sigmoid(F.linear(x.float(), self.gate.weight.float()))
+        logits = F.linear(x.float(), self.gate.weight.float())
+        v2 = cfg.router_scoring == 'softmax_grouped'        # DeepSeek-V2: softmax scores, a group is as good as its best expert
+        scores = torch.softmax(logits, -1) if v2 else torch.sigmoid(logits)
         choice = scores + self.e_score_correction_bias.float() if self.e_score_correction_bias is not None else scores
         if cfg.n_group > 1:
             grouped = choice.view(-1, cfg.n_group, E // cfg.n_group)
-            best = grouped.topk(2, dim=-1)[0].sum(-1).topk(cfg.topk_group, dim=-1, sorted=False)[1]
+            rank = grouped.max(-1)[0] if v2 else grouped.topk(2, dim=-1)[0].sum(-1)
+            best = rank.topk(cfg.topk_group, dim=-1, sorted=False)[1]
             keep = torch.zeros_like(grouped[..., 0]).scatter_(1, best, 1.0).bool()
             choice = grouped.masked_fill(~keep[..., None], 0.0).reshape(-1, E)
         idx = choice.topk(k, dim=-1, sorted=False)[1]
