@@ -158,3 +158,59 @@ def test_expert_adapters_on_whole_and_split_experts(tmp_path, etp, sp):
     for k in keys:
         assert a.get(k).shape == b.get(k).shape, k
         assert torch.allclose(a.get(k), b.get(k), atol=5e-4), (k, float((a.get(k) - b.get(k)).abs().max()))
+
+
+def _make_moe_ep(world, tp, ep, etp=1):
+    from twinkle_b200.model.megatron import MultiLoraMegatronModel
+    from twinkle_b200.models import preset
+    from twinkle_b200.utils.device_mesh import DeviceMesh
+    cfg = preset('tiny-moe', num_hidden_layers=2, router_aux_loss_coef=0.0)
+    mesh = DeviceMesh.from_sizes(tp_size=tp, dp_size=world // tp, ep_size=ep, etp_size=etp, sequence_parallel=tp > 1)
+    return MultiLoraMegatronModel(config=cfg, device_mesh=mesh, seed=0, max_loras=2, max_r=8), mesh
+
+
+def _moe_ep_worker(rank, world, tmp, tp, ep, etp):
+    import torch.distributed as dist
+    m, mesh = _make_moe_ep(world, tp, ep, etp)
+    m.add_adapter_to_model('a', os.path.join(tmp, 'warm'))
+    m.set_optimizer('AdamW', lr=5e-3, adapter_name='a')
+    feats = _feats()
+    sl = mesh.get_slice(len(feats), mesh.get_data_rank_from_global_rank(rank))
+    curve = []
+    for _ in range(3):
+        o = m.forward_backward(inputs=feats[sl], adapter_name='a', micro_batch_size=1)
+        n = m.clip_grad_and_step(max_grad_norm=1.0, adapter_name='a')
+        t = torch.tensor([o['loss'] * o['num_tokens'], o['num_tokens']], dtype=torch.float64)
+        dist.all_reduce(t, group=m.dp_comm.group)
+        curve.append((float(t[0] / t[1]), n))
+    m.save('out', tmp, adapter_name='a')
+    return curve, m.chunks[0].layers[0].mlp.experts.lora['gate_up_A'].shape[1]
+
+
+@pytest.mark.parametrize('world,tp,ep,etp', [(2, 1, 2, 1), (4, 2, 2, 1), (4, 2, 2, 2)])
+def test_expert_adapters_under_expert_parallelism(tmp_path, world, tp, ep, etp):
+    """Experts — and the adapter pools on them — split over an expert-parallel group (alone, beside tensor parallelism with
+    whole experts, and with every expert also split over the tensor-parallel group): the curve of one process, the same
+    PEFT file back with all experts gathered."""
+    from twinkle_b200.utils.safetensors_io import SafetensorLazyLoader
+    tmp = str(tmp_path)
+    m = _make_moe(1)
+    m.add_adapter_to_model('a', dict(_MOE_LORA))
+    m.set_optimizer('AdamW', lr=5e-3, adapter_name='a')
+    _train(m, 'a', 2, _feats())
+    m.save('warm', tmp, adapter_name='a')
+    m = _make_moe(1)
+    m.add_adapter_to_model('a', os.path.join(tmp, 'warm'))
+    m.set_optimizer('AdamW', lr=5e-3, adapter_name='a')
+    ref = _train(m, 'a', 3, _feats())
+    m.save('ref', tmp, adapter_name='a')
+    for curve, local in run_ranks(_moe_ep_worker, world, tmp, tp, ep, etp):
+        assert local == 8 // ep
+        for (l0, n0), (l1, n1) in zip(ref, curve):
+            assert abs(l0 - l1) < 3e-4 and abs(n0 - n1) < 3e-3 * max(n0, 1.0), (ref, curve)
+    a, b = SafetensorLazyLoader(os.path.join(tmp, 'ref')), SafetensorLazyLoader(os.path.join(tmp, 'out'))
+    keys = sorted(a.keys())
+    assert keys == sorted(b.keys())
+    for k in keys:
+        assert a.get(k).shape == b.get(k).shape, k
+        assert torch.allclose(a.get(k), b.get(k), atol=5e-4), (k, float((a.get(k) - b.get(k)).abs().max()))

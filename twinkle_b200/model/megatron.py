@@ -839,7 +839,8 @@ class MultiLoraMegatronModel(MegatronModel):
     row-parallel ones; gradients of the replicated halves are partial sums and are all-reduced over the TP group.
     Expert pools (target-parameter LoRA on the fused expert tensors) are whole on every rank while the experts are, and
     follow the expert shards under expert tensor parallelism (``gate_up``: ``B`` rows of this rank's gate and up slices;
-    ``down``: ``A`` columns of this rank's slice of the intermediate dimension).
+    ``down``: ``A`` columns of this rank's slice of the intermediate dimension); under expert parallelism a rank keeps the
+    pools of its own experts, with gradients summed over the ranks that hold the same experts and all experts gathered on save.
     Each tenant has its own optimizer state (fp32 master + Adam moments of its slot slices), gradient norm, progress
     counters and scheduler (``multi_lora_megatron.py:213-291``); adapters are saved and loaded in PEFT format with the
     TP shards and pipeline stages merged into one ``adapter_model.safetensors``."""
@@ -850,9 +851,6 @@ class MultiLoraMegatronModel(MegatronModel):
         from .multi_lora import MultiLora
         self.max_length = max_length
         seed = kwargs.get('seed', 0)
-        if self.ep_size > 1:
-            # expert pools would differ per expert-parallel rank (gradients summed over the replica groups only): not wired up
-            raise NotImplementedError('multi-LoRA on the tensor / pipeline backend does not combine with expert parallelism (use ep_size=1)')
         self.pools = [MultiLora(m, max_loras, max_r, seed=seed * 1000 + self.pp_rank * 16 + c) for c, m in enumerate(self.chunks)]
         self._sync_pools()
         self.optimizer_groups = {}
@@ -868,14 +866,36 @@ class MultiLoraMegatronModel(MegatronModel):
                 mod_name = n.split('.lora')[0]
                 yield self._global_name(n, m._layer_offset), p, getattr(mods.get(mod_name), 'tp_mode', None)
 
+    def _expert_replicas(self):
+        """Communicator over the ranks that hold the same experts as this one (None: nobody else does), when experts are
+        split over an expert-parallel group; the pools on the expert tensors follow the experts."""
+        if self.ep_size <= 1:
+            return None
+        for m in self.chunks:
+            for layer in m.layers:
+                if getattr(layer, 'is_moe', False):
+                    return getattr(layer.mlp.experts.gate_up_proj, '_ep_replica_comm', None)
+        return None
+
+    def _is_ep_pool(self, name: str) -> bool:
+        return self.ep_size > 1 and '.lora.' in name
+
     def _sync_pools(self) -> None:
         """Replicated pool tensors start equal: over the TP group for the replicated halves, over the data-parallel
-        group for everything (each process drew its pool from its own stream position)."""
+        group for everything (each process drew its pool from its own stream position).  Pools on expert-parallel
+        experts belong to this rank's experts: they are made equal only among the ranks that hold the same ones."""
         from ..parallel.tensor import lora_param_is_replicated
+        rc = self._expert_replicas()
         with torch.no_grad():
             for pool in self.pools:
                 init = pool._initial_A
                 for n, p, mode in self._pool_params_of(pool):
+                    if self._is_ep_pool(n):
+                        if rc is not None and rc.world_size > 1:
+                            rc.broadcast(p.data, 0)
+                        if n in init:
+                            init[n].copy_(p.data)
+                        continue
                     if self.tp_size > 1 and lora_param_is_replicated(n, mode, self.etp_size > 1):
                         self.tp_comm.broadcast(p.data, 0)
                     if self.dp_comm.world_size > 1:
@@ -958,11 +978,26 @@ class MultiLoraMegatronModel(MegatronModel):
         adapter_name = adapter_name or self._active
         og = self._group(adapter_name)
         sq = torch.zeros((), dtype=torch.float32, device=self.device)
+        sq_ep = torch.zeros((), dtype=torch.float32, device=self.device)
+        rc = self._expert_replicas()
         for n, p, slot, mode in self._tenant_slices(adapter_name):
             if p.grad is None:
                 continue
             g = p.grad[slot]
             rep = lora_param_is_replicated(n, mode, self.etp_size > 1)
+            if self._is_ep_pool(n):
+                # this rank's experts: gradients summed over the ranks that hold the same experts (other data blocks and, with
+                # whole experts, the tensor-parallel peers — they are in that group already); under expert tensor
+                # parallelism the replicated halves are partial sums over the tensor-parallel group as well
+                g = g.contiguous()
+                if rc is not None and rc.world_size > 1:
+                    rc.all_reduce(g)
+                if self.etp_size > 1 and rep:
+                    self.tp_comm.all_reduce(g)
+                p.grad[slot].copy_(g)
+                v = ops.sumsq(g)
+                sq_ep = sq_ep + (v / self.tp_size if (self.tp_size > 1 and rep) else v)
+                continue
             if self.dp_comm.world_size > 1 or (self.tp_size > 1 and rep):
                 g = g.contiguous()
                 if self.dp_comm.world_size > 1:
@@ -972,6 +1007,10 @@ class MultiLoraMegatronModel(MegatronModel):
                 p.grad[slot].copy_(g)
             v = ops.sumsq(p.grad[slot].contiguous())
             sq = sq + (v / self.tp_size if (self.tp_size > 1 and rep) else v)
+        if self.ep_comm is not None:       # every expert-parallel rank holds other experts: their squared norms add up
+            sq_ep = sq_ep.reshape(1)
+            self.ep_comm.all_reduce(sq_ep)
+            sq = sq + sq_ep[0]
         if self.tp_size > 1:
             self.tp_comm.all_reduce(sq)
         if self.pp_size > 1:
@@ -1088,6 +1127,11 @@ class MultiLoraMegatronModel(MegatronModel):
                             continue
                         a = mod.lora[which + '_A'][t.slot, :, :r].detach().contiguous()           # [E, r, in]
                         b = mod.lora[which + '_B'][t.slot, :, :, :r].detach().contiguous()        # [E, out, r]
+                        if self.ep_size > 1:       # all experts, in expert order
+                            pa, pb = [torch.empty_like(a) for _ in range(self.ep_size)], [torch.empty_like(b) for _ in range(self.ep_size)]
+                            dist.all_gather(pa, a, group=self.ep_comm.group)
+                            dist.all_gather(pb, b, group=self.ep_comm.group)
+                            a, b = torch.cat(pa, 0), torch.cat(pb, 0)
                         if self.etp_size > 1 and which == 'gate_up':      # B: this rank's gate rows, then its up rows
                             parts = [torch.empty_like(b) for _ in range(self.tp_size)]
                             dist.all_gather(parts, b, group=self.tp_comm.group)
@@ -1173,6 +1217,9 @@ class MultiLoraMegatronModel(MegatronModel):
                         if ka not in loader or kb not in loader:
                             continue
                         a, b = loader.get(ka), loader.get(kb)
+                        if self.ep_size > 1:
+                            el = a.shape[0] // self.ep_size
+                            a, b = a[self.ep_rank * el:(self.ep_rank + 1) * el], b[self.ep_rank * el:(self.ep_rank + 1) * el]
                         if self.etp_size > 1 and which == 'gate_up':
                             half = b.shape[1] // 2
                             n = half // self.tp_size
