@@ -333,21 +333,21 @@ def test_router_load_balance_loss_on_the_pipeline_backend(tp, pp):
         assert curve[-1][0] < curve[0][0]
 
 
-def _reshard_worker(rank, world, tmp, src, dst):
-    """Trains 2 steps under layout ``src`` = (tp, pp, dp), saves weights and optimizer state, trains 2 more; a model of layout
-    ``dst`` resumes from the files of the first and must continue on the same curve."""
+def _reshard_worker(rank, world, tmp, src, dst, moe=False):
+    """Trains 2 steps under layout ``src`` = (tp, pp, dp[, ep]), saves weights and optimizer state, trains 2 more; a model of
+    layout ``dst`` resumes from the files of the first and must continue on the same curve."""
     from twinkle_b200.model.megatron import MegatronModel
     from twinkle_b200.models import preset
     from twinkle_b200.utils.device_mesh import DeviceMesh
-    cfg = preset('tiny-dense', num_hidden_layers=4)
+    cfg = preset('tiny-moe', num_hidden_layers=2, router_aux_loss_coef=0.0) if moe else preset('tiny-dense', num_hidden_layers=4)
     g = torch.Generator().manual_seed(13)
     feats = []          # rows of one length: the mean over data-parallel ranks is then the mean over tokens at every dp size
     for _ in range(4):
         ids = torch.randint(0, 1024, (65, ), generator=g)
         feats.append({'input_ids': ids[:-1].tolist(), 'labels': ids[1:].tolist()})
 
-    def make(tp, pp, dp):
-        mesh = DeviceMesh.from_sizes(tp_size=tp, pp_size=pp, dp_size=dp, sequence_parallel=tp > 1)
+    def make(tp, pp, dp, ep=1):
+        mesh = DeviceMesh.from_sizes(tp_size=tp, pp_size=pp, dp_size=dp, ep_size=ep if ep > 1 else None, sequence_parallel=tp > 1)
         m = MegatronModel(config=cfg, device_mesh=mesh, seed=0)
         m.set_optimizer('AdamW', lr=2e-3)
         m.set_lr_scheduler('CosineWarmupScheduler', num_warmup_steps=1, num_training_steps=8)
@@ -375,9 +375,12 @@ def _reshard_worker(rank, world, tmp, src, dst):
     return {'cont': cont, 'resumed': resumed, 'info': info, 'wa': weights_a, 'wb': weights_b}
 
 
-@pytest.mark.parametrize('src,dst', [((2, 1, 2), (1, 2, 2)), ((1, 2, 2), (2, 2, 1)), ((2, 2, 1), (1, 1, 4))])
+@pytest.mark.parametrize('src,dst', [((2, 1, 2), (1, 2, 2)), ((1, 2, 2), (2, 2, 1)), ((2, 2, 1), (1, 1, 4)),
+                                     ((1, 1, 4, 2), (1, 2, 2, 2)), ((1, 1, 4, 4), (2, 1, 2, 1)), ((1, 2, 2, 1), (1, 1, 4, 2))])
 def test_optimizer_state_loads_into_another_layout(tmp_path, src, dst):
-    res = run_ranks(_reshard_worker, 4, str(tmp_path), src, dst)
+    """The last three cases move a mixture-of-experts model between expert-parallel layouts (ep 2 → ep 2 beside pipeline
+    stages, ep 4 → whole experts beside tensor parallelism, whole experts → ep 2)."""
+    res = run_ranks(_reshard_worker, 4, str(tmp_path), src, dst, len(src) == 4)
     cont, resumed, wa, wb = {}, {}, {}, {}
     for r in res:
         assert r['info']['cur_step'] == 2

@@ -711,7 +711,7 @@ class MegatronModel(TwinkleModel):
         og = self._group()
         os.makedirs(path, exist_ok=True)
         shapes = {n: tuple(p.shape) for n, p in self._params()}
-        state = {'layout': self._layout(), 'shapes': {n: shapes[n] for n in self._state if n in shapes},
+        state = {'layout': self._layout(), 'ep_rank': int(getattr(self, 'ep_rank', 0) or 0), 'shapes': {n: shapes[n] for n in self._state if n in shapes},
                  'optim_steps': og.optim_steps, 'hyper': og.optimizer.state_dict()['param_groups'] if og.optimizer else None,
                  'params': {n: {k: v.detach().cpu() for k, v in st.items()} for n, st in self._state.items()}}
         torch.save(state, os.path.join(path, f'optimizer_{self._rank_tag()}.pt'))
@@ -738,12 +738,12 @@ class MegatronModel(TwinkleModel):
         """Optimizer state written under another tensor / pipeline / data-parallel layout.  For every parameter this rank
         holds: the saved data-parallel slices of each saved tensor-parallel rank are joined into that rank's shard, the
         shards into the full tensor (the same rule that splits weights, ``models/bridge.py::tp_unshard``), and the full
-        tensor is cut again for this rank's shard and data-parallel slice.  Files are memory-mapped, so only the tensors
-        a rank needs are read."""
+        tensor is cut again for this rank's shard and data-parallel slice.  Expert tensors written under expert parallelism
+        are put together from the saved expert-parallel ranks in expert order first.  Files are memory-mapped, so only the
+        tensors a rank needs are read."""
         wanted = dict(self._params())
-        if any(getattr(p, '_ep_local', False) for p in wanted.values()):
-            raise NotImplementedError('optimizer state of expert-parallel parameters loads only into the layout that wrote it')
         found: Dict[str, Dict[Tuple[int, int], Dict[str, torch.Tensor]]] = {}
+        found_ep: Dict[str, Dict[Tuple[int, int], Dict[str, torch.Tensor]]] = {}     # expert tensors: (saved ep rank, tp rank) → state
         shapes: Dict[str, Dict[int, Tuple[int, ...]]] = {}
         first = None
         for (t, pstage, d), fn in sorted(files.items(), key=lambda kv: (kv[0][1], kv[0][0], kv[0][2])):
@@ -752,11 +752,15 @@ class MegatronModel(TwinkleModel):
                 first = st
             if 'shapes' not in st:
                 raise ValueError(f'{fn} has no shard shapes: it was written by a version that could only resume into the same layout')
-            lay = st.get('layout', {})
-            if lay.get('ep', 1) != 1:
-                raise NotImplementedError('optimizer state written under expert parallelism loads only into the layout that wrote it')
+            if st.get('layout', {}).get('ep', 1) != 1 and 'ep_rank' not in st:
+                raise ValueError(f'{fn} does not say which experts it holds: it loads only into the layout that wrote it')
             for n, tensors in st['params'].items():
-                if n in wanted and (t, d) not in found.setdefault(n, {}):      # a tied embedding sits on two stages: the first one wins
+                if n not in wanted:
+                    continue
+                if st['layout'].get('ep', 1) != 1 and n.endswith(('mlp.experts.gate_up_proj', 'mlp.experts.down_proj')):   # written per expert-parallel rank
+                    found_ep.setdefault(n, {}).setdefault((int(st.get('ep_rank', 0)), t), tensors)     # replicas hold the same values
+                    shapes.setdefault(n, {})[t] = tuple(st['shapes'][n])
+                elif (t, d) not in found.setdefault(n, {}):      # a tied embedding sits on two stages: the first one wins
                     found[n][(t, d)] = tensors
                     shapes.setdefault(n, {})[t] = tuple(st['shapes'][n])
         if first is None:
@@ -765,11 +769,29 @@ class MegatronModel(TwinkleModel):
         sharded_dp = bool(first['layout'].get('distributed_optimizer'))
         state: Dict[str, Dict[str, torch.Tensor]] = {}
         for n, p in wanted.items():
+            entry = {}
+            if n in found_ep:
+                # expert tensors are never sliced by the distributed optimizer: every saved expert-parallel rank holds whole
+                # tensors of its own experts.  All experts are put together in expert order, then cut for this rank.
+                eps, tps = sorted({j for j, _ in found_ep[n]}), sorted({t for _, t in found_ep[n]})
+                for key in ('master', 'exp_avg', 'exp_avg_sq'):
+                    blocks = [tp_unshard(n, [found_ep[n][(j, t)][key].reshape(shapes[n][t]) for t in tps], self.config) for j in eps]
+                    full = torch.cat(blocks, 0)
+                    if getattr(p, '_ep_local', False) and self.ep_size > 1:
+                        el = full.shape[0] // self.ep_size
+                        full = full[self.ep_rank * el:(self.ep_rank + 1) * el]
+                        mine = tp_shard(n, full, self.config, self.tp_rank, self.tp_size).reshape(-1)
+                    else:
+                        lo, hi = self._state_range(p.numel())
+                        mine = tp_shard(n, full, self.config, self.tp_rank, self.tp_size).reshape(-1)[lo:hi]
+                    entry[key] = mine.to(self.device, torch.float32).clone()
+                state[n] = entry
+                continue
             if n not in found:
                 raise KeyError(f'optimizer state of {n} is not in the checkpoint under {path}')
             tps = sorted({t for t, _ in found[n]})
-            lo, hi = self._state_range(p.numel())
-            entry = {}
+            ep_local = bool(getattr(p, '_ep_local', False)) and self.ep_size > 1
+            lo, hi = (0, p.numel()) if ep_local else self._state_range(p.numel())
             for key in ('master', 'exp_avg', 'exp_avg_sq'):
                 shards = []
                 for t in tps:
@@ -778,6 +800,9 @@ class MegatronModel(TwinkleModel):
                     shape = shapes[n][t]
                     shards.append(flat[:math.prod(shape)].reshape(shape))
                 full = tp_unshard(n, shards, self.config)
+                if ep_local:      # written with whole experts everywhere, read into an expert-parallel layout
+                    el = full.shape[0] // self.ep_size
+                    full = full[self.ep_rank * el:(self.ep_rank + 1) * el]
                 mine = tp_shard(n, full, self.config, self.tp_rank, self.tp_size).reshape(-1)[lo:hi]
                 entry[key] = mine.to(self.device, torch.float32).clone()
             state[n] = entry
