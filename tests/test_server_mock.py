@@ -105,6 +105,22 @@ def test_twinkle_client_and_processor(server):
     assert sum(1 for _ in dl) == 3
     time.sleep(0.15)
     assert c.status()['gauges']['sessions'] >= 1
+    # the manager calls of the reference client (``twinkle_client/manager.py``): health, capacity, sessions, paged runs, paths
+    from twinkle_b200.client import TwinkleClientError
+    assert c.health_check() and 'replicas' in c.get_capacity_info() and c.create_session({'purpose': 'test'}) != c.session_id
+    assert c.get_server_capabilities() == c.capabilities()
+    m.save(name='ck1', adapter_name='a')
+    runs, cursor = c.list_training_runs_with_cursor(limit=5)
+    assert runs and cursor['total_count'] == len(c.list_training_runs(limit=100)) and c.list_training_runs(limit=1, offset=len(runs)) == []
+    run = runs[0]['training_run_id']
+    assert c.get_training_run(run)['training_run_id'] == run and c.find_training_run_by_model(runs[0]['base_model'])
+    cks = c.list_checkpoints(run)
+    assert cks
+    info = c.get_checkpoint_path(run, 'weights/ck1')
+    assert info['twinkle_path'] == f'twinkle://{run}/weights/ck1' == c.get_checkpoint_twinkle_path(run, 'ck1') and info['path'].endswith('ck1')
+    assert c.get_latest_checkpoint_path(run) == info['path'] and c.get_weights_info(info['twinkle_path']) == c.weights_info(info['twinkle_path'])
+    with pytest.raises(TwinkleClientError):
+        c.get_training_run('no-such-run')
     c.close()
 
 

@@ -86,14 +86,72 @@ class TwinkleClient:
     def close(self) -> None:
         self._stop.set()
 
+    # -------------------------------------------------------------- server
     def capabilities(self):
         return self.t.get('/twinkle/get_server_capabilities')
 
-    def list_training_runs(self):
-        return self.t.get('/twinkle/training_runs')['training_runs']
+    get_server_capabilities = capabilities
+
+    def health_check(self) -> bool:
+        """Whether the server answers its health route (never raises)."""
+        try:
+            return self.t.get('/twinkle/healthz').get('status') == 'ok'
+        except Exception:
+            return False
+
+    def get_capacity_info(self) -> Dict[str, Any]:
+        """Free adapter slots and queue depths per replica (what the sticky router places new adapters by)."""
+        return self.t.get('/twinkle/capacity_info')
+
+    def create_session(self, metadata: Optional[Dict[str, Any]] = None) -> str:
+        """A further session on the same connection (the constructor opens the first and keeps it alive)."""
+        return self.t.post('/twinkle/create_session', {'sdk_version': 'twinkle_b200', 'user_metadata': metadata or {}})['session_id']
+
+    def status(self):
+        return self.t.get('/twinkle/status')
+
+    # ------------------------------------------------- runs and checkpoints
+    def list_training_runs(self, limit: int = 20, offset: int = 0, all_users: bool = False) -> List[Dict[str, Any]]:
+        """This token's training runs, newest first (reference ``twinkle_client/manager.py:204-228``; a token sees its own
+        runs only, so ``all_users`` is accepted and has no effect)."""
+        return self.list_training_runs_with_cursor(limit, offset, all_users)[0]
+
+    def list_training_runs_with_cursor(self, limit: int = 20, offset: int = 0, all_users: bool = False):
+        """``(runs, cursor)`` with ``cursor = {offset, limit, total_count}`` for paging."""
+        d = self.t.get(f'/twinkle/training_runs?limit={int(limit)}&offset={int(offset)}')
+        return d.get('training_runs', []), d.get('cursor', {})
+
+    def get_training_run(self, run_id: str) -> Dict[str, Any]:
+        return self.t.get(f'/twinkle/training_runs/{run_id}')
+
+    def find_training_run_by_model(self, base_model: str) -> List[Dict[str, Any]]:
+        return [r for r in self.list_training_runs(limit=100) if r.get('base_model') == base_model]
 
     def list_checkpoints(self, run_id: str):
         return self.t.get(f'/twinkle/training_runs/{run_id}/checkpoints')['checkpoints']
+
+    def get_checkpoint_path(self, run_id: str, checkpoint_id: str) -> Dict[str, Any]:
+        """``{path, twinkle_path, training_run_id, checkpoint_type, checkpoint_id}`` of a checkpoint named ``weights/<name>``,
+        ``sampler_weights/<name>`` or just ``<name>`` (a training checkpoint)."""
+        d = self.t.get(f'/twinkle/checkpoint_path/{run_id}/{checkpoint_id}')
+        kind, _, name = checkpoint_id.partition('/')
+        if not name:
+            kind, name = 'weights', checkpoint_id
+        return {'path': d.get('path', ''), 'twinkle_path': d.get('twinkle_path') or f'twinkle://{run_id}/{kind}/{name}', 'training_run_id': run_id,
+                'checkpoint_type': kind, 'checkpoint_id': checkpoint_id}
+
+    def get_checkpoint_twinkle_path(self, run_id: str, checkpoint_id: str) -> str:
+        return self.get_checkpoint_path(run_id, checkpoint_id)['twinkle_path']
+
+    def get_latest_checkpoint_path(self, run_id: str) -> Optional[str]:
+        """File-system path of the run's newest checkpoint (what a resumed job loads), or None."""
+        cks = self.list_checkpoints(run_id)
+        if not cks:
+            return None
+        last = cks[-1]
+        kind = 'sampler_weights' if last.get('checkpoint_type') == 'sampler' else 'weights'
+        name = str(last.get('checkpoint_id', '')).split('/')[-1]
+        return self.get_checkpoint_path(run_id, f'{kind}/{name}')['path']
 
     def delete_checkpoint(self, run_id: str, checkpoint_id: str):
         return self.t.request('DELETE', f'/twinkle/training_runs/{run_id}/checkpoints/{checkpoint_id}')
@@ -101,8 +159,11 @@ class TwinkleClient:
     def weights_info(self, path: str):
         return self.t.post('/twinkle/weights_info', {'path': path})
 
-    def status(self):
-        return self.t.get('/twinkle/status')
+    get_weights_info = weights_info
+
+
+# the reference client's name for a failed request
+TwinkleClientError = HttpError
 
 
 def init_twinkle_client(base_url: Optional[str] = None, token: Optional[str] = None, **kw) -> TwinkleClient:

@@ -245,7 +245,8 @@ class GatewayApp:
         @app.get('/twinkle/checkpoint_path/{run_id}/{checkpoint_id:path}')
         async def checkpoint_path(run_id: str, checkpoint_id: str, request: Request):
             kind, _, name = checkpoint_id.replace(':', '/').partition('/')
-            return {'path': self.checkpoints.path_for(request.state.token, run_id, name or kind, kind if name else 'weights')}
+            kind, name = (kind, name) if name else ('weights', kind)
+            return {'path': self.checkpoints.path_for(request.state.token, run_id, name, kind), 'twinkle_path': f'twinkle://{run_id}/{kind}/{name}'}
 
         # ------------------------------------------------ OpenAI-compatible
         @app.get('/models')
