@@ -103,6 +103,9 @@ def test_twinkle_client_and_processor(server):
     assert len(ds) == 6
     dl = DataLoader(ds, batch_size=2, shuffle=False, client=c)
     assert sum(1 for _ in dl) == 3
+    from twinkle_b200.client import LazyDataset, PackingDataset
+    meta = {'__class__': 'DatasetMeta', 'kwargs': {'data': [{'messages': [{'role': 'user', 'content': str(i)}, {'role': 'assistant', 'content': 'ok'}]} for i in range(6)]}}
+    assert len(LazyDataset(meta, client=c)) == 6 and hasattr(PackingDataset(meta, client=c), 'object_id')      # the other dataset twins of the reference client
     time.sleep(0.15)
     assert c.status()['gauges']['sessions'] >= 1
     # the manager calls of the reference client (``twinkle_client/manager.py``): health, capacity, sessions, paged runs, paths

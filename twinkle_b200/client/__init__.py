@@ -289,6 +289,24 @@ def Dataset(*args, **kw):
     return RemoteObject('Dataset', *args, **kw)
 
 
+def PackingDataset(*args, **kw):
+    """Server-side dataset that packs encoded rows into constant-volume bins (reference ``twinkle_client/dataset/packing_dataset.py``)."""
+    return RemoteObject('PackingDataset', *args, **kw)
+
+
+def IterableDataset(*args, **kw):
+    return RemoteObject('IterableDataset', *args, **kw)
+
+
+def IterablePackingDataset(*args, **kw):
+    return RemoteObject('IterablePackingDataset', *args, **kw)
+
+
+def LazyDataset(*args, **kw):
+    """Server-side dataset that encodes a row when it is read (reference ``twinkle_client/dataset/lazy_dataset.py``)."""
+    return RemoteObject('LazyDataset', *args, **kw)
+
+
 def DataLoader(dataset: RemoteObject, **kw):
     return RemoteObject('DataLoader', {'__object__': dataset.object_id}, **kw)
 
