@@ -1,31 +1,36 @@
-"""Relative links and referenced source paths in the user-facing Markdown files must exist."""
-import glob
+"""Relative links and file references in the user-facing Markdown resolve (reference ``tests/docs/test_markdown_links.py``)."""
 import os
 import re
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-DOCS = ['README.md', 'cookbook/README.md', 'cookbook/observability/README.md'] + sorted(
-    os.path.relpath(p, ROOT) for p in glob.glob(os.path.join(ROOT, 'docs', '**', '*.md'), recursive=True))
+PAGES = ['README.md', 'cookbook/README.md', 'cookbook/observability/README.md'] + sorted(
+    os.path.join('docs', f) for f in os.listdir(os.path.join(ROOT, 'docs')) if f.endswith('.md'))
 LINK = re.compile(r'\[[^\]]*\]\(([^)#\s]+)(?:#[^)]*)?\)')
 
 
-def test_relative_markdown_links_resolve():
-    broken = []
-    for doc in DOCS:
-        path = os.path.join(ROOT, doc)
-        if not os.path.exists(path):
+def test_relative_links_point_at_files():
+    bad = []
+    for page in PAGES:
+        path = os.path.join(ROOT, page)
+        if not os.path.isfile(path):
             continue
-        text = open(path, encoding='utf-8').read()
+        text = open(path).read()
         for target in LINK.findall(text):
             if re.match(r'^[a-z]+://|^mailto:', target):
                 continue
             if not os.path.exists(os.path.normpath(os.path.join(os.path.dirname(path), target))):
-                broken.append(f'{doc}: {target}')
-    assert not broken, broken
+                bad.append((page, target))
+    assert not bad, bad
 
 
-def test_cookbook_readme_lists_every_script():
-    text = open(os.path.join(ROOT, 'cookbook', 'README.md'), encoding='utf-8').read()
-    scripts = sorted(os.path.basename(p) for p in glob.glob(os.path.join(ROOT, 'cookbook', '*.py')))
-    missing = [s for s in scripts if s not in text]
-    assert not missing, f'cookbook/README.md does not mention {missing}'
+def test_cookbook_table_lists_every_script_and_only_scripts_that_exist():
+    text = open(os.path.join(ROOT, 'cookbook', 'README.md')).read()
+    listed = set(re.findall(r'^\| `([a-z0-9_]+\.py)` \|', text, flags=re.M))
+    present = {f for f in os.listdir(os.path.join(ROOT, 'cookbook')) if f.endswith('.py')}
+    assert listed == present, (sorted(listed - present), sorted(present - listed))
+
+
+def test_docs_index_lists_every_page():
+    text = open(os.path.join(ROOT, 'docs', 'index.md')).read()
+    pages = {f for f in os.listdir(os.path.join(ROOT, 'docs')) if f.endswith('.md') and f != 'index.md'}
+    assert pages == set(re.findall(r'\]\(([a-z0-9-]+\.md)\)', text)), pages
