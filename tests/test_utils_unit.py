@@ -316,3 +316,22 @@ def test_loader_expands_block_quantised_fp8_weights(tmp_path):
     assert got.dtype == torch.bfloat16 and got.shape == w.shape
     assert float((got.float() - w).abs().max()) < 0.08 * float(w.abs().max())        # fp8 e4m3 keeps three mantissa bits
     assert loader.get('model.norm.weight').dtype == torch.float32
+
+
+def test_hub_kernel_references():
+    """``kernel.hub``: 'repo:Layer' with exactly one of revision / version, immutable, resolved per device by ``resolve_value``."""
+    import dataclasses
+
+    from twinkle_b200.kernel import HubRef, hub, resolve_value
+    r = hub('org/repo:SiluAndMul', version=2)
+    assert (r.repo_id, r.layer_name, r.version, r.revision, r.backend) == ('org/repo', 'SiluAndMul', 2, None, None)
+    assert hub('ms://org/repo:Layer', revision='main', backend='cuda') == HubRef('ms://org/repo', 'Layer', 'main', None, 'cuda')   # colons in the repo id stay there
+    assert hub('org/repo', 'Layer', 'v1').revision == 'v1'
+    for bad in (dict(), dict(revision='a', version=1)):
+        with pytest.raises(ValueError):
+            hub('org/repo:Layer', **bad)
+    with pytest.raises(ValueError):
+        hub('org/repo', version=1)
+    with pytest.raises(dataclasses.FrozenInstanceError):
+        r.version = 3
+    assert resolve_value({'cuda': {'cuda': int}, 'npu': str}, 'cuda') is int and resolve_value({'npu': str}, 'cuda') is None

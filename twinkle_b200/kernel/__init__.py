@@ -17,24 +17,38 @@ import torch
 import torch.nn as nn
 
 
-@dataclass
+@dataclass(frozen=True)
 class HubRef:
-    """Reference to a kernel in a hub repository (resolved through the optional ``kernels`` package)."""
+    """Reference to a kernel layer in a hub repository, resolved when ``kernelize`` applies it (through the optional
+    ``kernels`` package).  Pinned by a ``revision`` (branch / tag / commit) or by a ``version`` number, never by both."""
     repo_id: str
     layer_name: Optional[str] = None
     revision: Optional[str] = None
+    version: Optional[int] = None
+    backend: Optional[str] = None
 
     def resolve(self):
         try:
             from kernels import get_kernel  # type: ignore
         except ImportError as e:
             raise ImportError('HubRef needs the `kernels` package, which is not installed') from e
-        mod = get_kernel(self.repo_id, revision=self.revision)
+        kw = {k: v for k, v in (('revision', self.revision), ('version', self.version), ('backend', self.backend)) if v is not None}
+        mod = get_kernel(self.repo_id, **kw)
         return getattr(mod, self.layer_name) if self.layer_name else mod
 
 
-def hub(repo_id: str, layer_name: Optional[str] = None, revision: Optional[str] = None) -> HubRef:
-    return HubRef(repo_id, layer_name, revision)
+def hub(ref: str, layer_name: Optional[str] = None, revision: Optional[str] = None, *, version: Optional[int] = None,
+        backend: Optional[str] = None) -> HubRef:
+    """``hub('org/repo:LayerName', revision='v1')`` or ``version=2`` (reference ``kernel/core.py:32-49``: exactly one of the
+    two pins is required; the part after the last colon names the layer).  ``hub('org/repo', 'LayerName', 'v1')`` is accepted
+    as well."""
+    if layer_name is None:
+        if ':' not in ref:
+            raise ValueError(f"a hub kernel is named 'repo_id:LayerName', got {ref!r}")
+        ref, layer_name = ref.rsplit(':', 1)
+    if (revision is None) == (version is None):
+        raise ValueError('exactly one of `revision` and `version` pins a hub kernel')
+    return HubRef(ref, layer_name, revision, version, backend)
 
 
 def resolve_value(value, device: str = 'cuda'):
