@@ -335,3 +335,18 @@ def test_hub_kernel_references():
     with pytest.raises(dataclasses.FrozenInstanceError):
         r.version = 3
     assert resolve_value({'cuda': {'cuda': int}, 'npu': str}, 'cuda') is int and resolve_value({'npu': str}, 'cuda') is None
+
+
+def test_device_placement_of_explicit_groups():
+    import numpy as np
+
+    from twinkle_b200 import DeviceGroup, DeviceMesh
+    from twinkle_b200.infra import get_device_placement
+    groups = [DeviceGroup(name='training_cluster', ranks=list(range(16)), device_type='cuda',
+                          _device_mesh={'main': DeviceMesh(device_type='cuda', mesh=np.arange(16).reshape(2, 2, 4), mesh_dim_names=('pp', 'dp', 'tp'))}),
+              DeviceGroup(name='inference_cluster', ranks=list(range(8)), device_type='cuda',
+                          _device_mesh={'inference': DeviceMesh(device_type='cuda', mesh=np.arange(8).reshape(2, 4), mesh_dim_names=('dp', 'tp'))})]
+    text = get_device_placement(groups)
+    assert "group 'training_cluster'" in text and "('pp', 'dp', 'tp')" in text and 'inference' in text
+    assert 'rank 13: coord (1, 1, 1) data_rank 1' in text          # pp 1, dp 1, tp 1
+    assert get_device_placement([]) == 'No device group provided.'

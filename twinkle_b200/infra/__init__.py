@@ -83,10 +83,14 @@ def get_global_device_mesh() -> Optional[DeviceMesh]:
     return _STATE['mesh']
 
 
-def get_device_placement() -> str:
-    """Human-readable table: group → ranks → mesh coordinates."""
+def get_device_placement(device_group: Optional[Sequence[DeviceGroup]] = None) -> str:
+    """Human-readable table: group → ranks → mesh coordinates, of the given device groups or of those ``initialize`` was
+    called with (reference ``infra/__init__.py:156-260``)."""
+    groups = list(device_group) if device_group is not None else _STATE['groups']
+    if not groups:
+        return 'No device group provided.'
     lines = []
-    for g in _STATE['groups']:
+    for g in groups:
         lines.append(f"group '{g.name}' ({g.device_type}, {g.gpus_per_worker} gpu/worker): ranks {g.rank_list()}")
         for cls_name, mesh in g._device_mesh.items():
             lines.append(f'  {cls_name}: dims {mesh.mesh_dim_names} shape {tuple(mesh.mesh.shape)}')
