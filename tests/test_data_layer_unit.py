@@ -189,3 +189,23 @@ def test_construct_class_and_plugin_guard(tmp_path, monkeypatch):
     monkeypatch.delenv('TWINKLE_TRUST_REMOTE_CODE', raising=False)
     with pytest.raises(Exception):
         construct_class(str(plug), None, loss_mod)     # refused unless remote code is trusted
+
+
+def test_arrow_and_feather_files_load_like_the_other_formats(tmp_path):
+    import pyarrow as pa
+    import pyarrow.feather as feather
+
+    from twinkle_b200.dataset import Dataset, DatasetMeta
+    table = pa.table({'query': ['a', 'b', 'c'], 'response': ['x', 'y', 'z']})
+    with pa.OSFile(str(tmp_path / 'file.arrow'), 'wb') as sink, pa.ipc.new_file(sink, table.schema) as w:
+        w.write_table(table)
+    with pa.OSFile(str(tmp_path / 'stream.arrow'), 'wb') as sink, pa.ipc.new_stream(sink, table.schema) as w:     # what `datasets` writes
+        w.write_table(table)
+    feather.write_feather(table, str(tmp_path / 'rows.feather'))
+    for fn in ('file.arrow', 'stream.arrow', 'rows.feather'):
+        ds = Dataset(DatasetMeta(str(tmp_path / fn)))
+        assert len(ds) == 3 and ds[1] == {'query': 'b', 'response': 'y'}
+    import pytest
+    os.makedirs(tmp_path / 'set.lance')
+    with pytest.raises(ImportError):          # the Lance reader is an optional package; the error says which
+        Dataset(DatasetMeta(str(tmp_path / 'set.lance')))

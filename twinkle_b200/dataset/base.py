@@ -4,7 +4,7 @@ Parity: reference ``src/twinkle/dataset/base.py:30-642`` (``DatasetMeta``, ``Dat
 ``set_template / encode / check / map / filter / add_dataset / mix_dataset / save_as``),
 ``lazy_dataset.py`` (deferred map/encode applied at ``__getitem__``), ``iterable_dataset.py``.
 
-Rows are plain dicts.  Local files (jsonl / json / csv / parquet) are read directly, in-memory
+Rows are plain dicts.  Local files (jsonl / json / csv / parquet / arrow / feather, Lance directories when `pylance` is installed) are read directly, in-memory
 lists / dicts / generators are accepted, hub ids go through ``HubOperation.load_dataset`` and become
 a list of rows.  ``data_slice`` selects row indices with wrap-around.
 """
@@ -64,6 +64,20 @@ def _read_rows(path: str) -> List[Dict[str, Any]]:
     if ext == '.parquet':
         import pyarrow.parquet as pq
         return pq.read_table(path).to_pylist()
+    if ext in ('.arrow', '.feather'):
+        import pyarrow as pa
+        with pa.memory_map(path) as src:
+            try:
+                return pa.ipc.open_file(src).read_all().to_pylist()
+            except pa.ArrowInvalid:          # the streaming layout that `datasets` writes
+                src.seek(0)
+                return pa.ipc.open_stream(src).read_all().to_pylist()
+    if ext == '.lance':                      # a Lance dataset is a directory; the reader is an optional package
+        try:
+            import lance  # type: ignore
+        except ImportError as e:
+            raise ImportError(f'{path}: reading Lance datasets needs the `pylance` package') from e
+        return lance.dataset(path).to_table().to_pylist()
     raise ValueError(f'unsupported dataset file type: {path}')
 
 
@@ -83,12 +97,12 @@ def load_rows(meta: DatasetMeta, **kwargs) -> List[Dict[str, Any]]:
         for p in ('ms://', 'hf://'):
             if path.startswith(p) and os.path.exists(path[len(p):]):
                 path = path[len(p):]
-        if os.path.isfile(path):
-            rows = _read_rows(path)
+        if os.path.isfile(path) or (os.path.isdir(path) and path.rstrip('/').lower().endswith('.lance')):
+            rows = _read_rows(path.rstrip('/'))
         elif os.path.isdir(path):
             rows = []
             for fn in sorted(os.listdir(path)):
-                if os.path.splitext(fn)[1].lower() in ('.jsonl', '.json', '.csv', '.parquet') and (
+                if os.path.splitext(fn)[1].lower() in ('.jsonl', '.json', '.csv', '.parquet', '.arrow', '.feather') and (
                         meta.split in fn or not any(s in fn for s in ('train', 'test', 'valid', 'dev'))):
                     rows += _read_rows(os.path.join(path, fn))
         else:
