@@ -1,6 +1,6 @@
 """Reference arm of ``bench.py``: the unmodified modelscope/twinkle package, driven through its public API.
 
-What runs is the reference's own code path for BASELINE config 2: ``twinkle.initialize(mode='local')``,
+What runs is the reference's own code path for the dense configuration (Qwen3-8B full-parameter SFT): ``twinkle.initialize(mode='local')``,
 ``TransformersModel(model_cls=AutoModelForCausalLM, config=<Qwen3-8B config>, strategy='native_fsdp')`` — i.e. the
 HF ``transformers`` Qwen3 modules, ``torch.distributed.fsdp.fully_shard`` over NCCL, the flash-attn 2 varlen
 kernels, the reference's Ulysses all-to-all attention wrapper, its ``InputProcessor(padding_free=True)``, its

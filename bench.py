@@ -3,14 +3,14 @@
 
 By default (``--config both``) the two halves of the headline metric run one after the other, each in a process of
 its own: the dense result fills the top-level fields of the printed line, the mixture-of-experts result sits under
-``"moe"`` (BASELINE config 3: 48 layers, hidden 2048, 128 experts top-8, LoRA r=16 on attention and expert linears,
+``"moe"`` (the Qwen3-30B-A3B expert-parallel LoRA configuration: 48 layers, hidden 2048, 128 experts top-8, LoRA r=16 on attention and expert linears,
 8 sequences of 4096 tokens per GPU, experts split over all ranks).  ``--config dense`` / ``--config moe`` run one half.
 
     python bench.py --gpus N --steps K --warmup W            (N = 1)
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port P bench.py --gpus N --steps K --warmup W
 
-Config (BASELINE config 2): 36 layers, hidden 4096, 32 q / 8 kv heads (head_dim 128), q/k RMSNorm,
+Dense configuration (Qwen3-8B full-parameter SFT): 36 layers, hidden 4096, 32 q / 8 kv heads (head_dim 128), q/k RMSNorm,
 SwiGLU 12288, vocab 151936, RoPE θ=1e6, random-init N(0, 0.02), bf16 compute, fp32 master weights +
 AdamW, sequences of 32768 tokens packed from documents with lengths uniform in [512, 8192], token ids
 uniform, varlen causal attention, activation recompute per layer.  Sharding: flat-bucket FSDP over all N
@@ -222,7 +222,7 @@ def main():
         dist.init_process_group('nccl', device_id=torch.device('cuda', local), timeout=datetime.timedelta(seconds=300))
     moe = args.config == 'moe'
     if moe:
-        # BASELINE config 3: 48 layers, hidden 2048, 32 q / 4 kv heads, 128 experts top-8 (FFN 768), aux loss 1e-3,
+        # Qwen3-30B-A3B expert-parallel LoRA configuration: 48 layers, hidden 2048, 32 q / 4 kv heads, 128 experts top-8 (FFN 768), aux loss 1e-3,
         # LoRA r=16 on attention and expert linears, sequences of 4096 tokens, 8 sequences per GPU (64 at N=8),
         # experts split over all ranks (EP = N), everything else flat-bucket FSDP over the same ranks.
         if args.model == 'qwen3-8b':

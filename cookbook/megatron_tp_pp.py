@@ -2,7 +2,7 @@
 
     python -m torch.distributed.run --nproc-per-node 8 cookbook/megatron_tp_pp.py --model qwen3-32b --tp 4 --pp 2 --vpp 2
 
-The benchmark form of BASELINE config 4 (Qwen3-32B architecture, TP 4 × PP 2, two virtual stages, 16 micro-batches of 8192
+The benchmark form of the tensor × pipeline configuration (Qwen3-32B architecture, TP 4 × PP 2, two virtual stages, 16 micro-batches of 8192
 tokens, random-init weights, synthetic token ids): device-timed steps (CUDA events, maximum over ranks) printed as one JSON
 line, then the weights written through the bridge to Hugging Face safetensors, reloaded and compared bit for bit:
 

@@ -1,4 +1,4 @@
-"""BASELINE config 1: tiny dense decoder, LoRA SFT, fp32, CPU, gloo world_size=2
+"""The smallest end-to-end configuration: tiny dense decoder, LoRA SFT, fp32, CPU, gloo world_size=2
 with sharded base weights; the 5-step loss curve must match a plain-PyTorch
 oracle (no engine, autograd + torch.optim.AdamW on the same LoRA slices)."""
 import torch

@@ -1,5 +1,5 @@
 """Tensor × pipeline parallel backend on CPU/gloo: schedules, parity with one process, bitwise HF round trip
-(BASELINE config 4 in miniature: TP=2 × PP=2, sequence-parallel activations, interleaved 1F1B with 2 virtual
+(the Qwen3-32B tensor × pipeline configuration in miniature: TP=2 × PP=2, sequence-parallel activations, interleaved 1F1B with 2 virtual
 stages)."""
 import os
 

@@ -3,7 +3,7 @@
 One config class covers Qwen3 dense, Qwen3-MoE and Llama/Qwen2-style decoders
 (q/k-norm optional, attention bias optional).  ``from_hf`` reads a Hugging Face
 ``config.json`` dict; ``to_hf`` writes one back, so checkpoints stay loadable by
-``transformers``.  Presets are the BASELINE architectures with random init.
+``transformers``.  Presets are the benchmark architectures with random init.
 """
 from __future__ import annotations
 
@@ -426,7 +426,7 @@ class DecoderConfig:
 
 
 PRESETS: Dict[str, Dict[str, Any]] = {
-    # BASELINE config 1
+    # the smallest end-to-end configuration (LoRA SFT on CPU)
     'tiny-dense': dict(vocab_size=1024, hidden_size=256, intermediate_size=688, num_hidden_layers=2, num_attention_heads=4,
                        num_key_value_heads=2, head_dim=64, rope_theta=1e4, tie_word_embeddings=True, qk_norm=True,
                        torch_dtype='float32'),
