@@ -99,7 +99,7 @@ def run(args, synthetic_sequences, ClockSampler):
             print(json.dumps(d), flush=True)
 
     if args.config != 'dense':
-        out['unavailable'] = ('config 3 (MoE LoRA) needs a working peft (LoRA layers + target_parameters wrappers); peft is '
+        out['unavailable'] = ('the mixture-of-experts LoRA configuration needs a working peft (LoRA layers + target_parameters wrappers); peft is '
                               'not installed and not in the offline wheelhouse, and the import shim only covers full-parameter training')
         return say(out)
     err = ensure_installed() if rank == 0 else None
