@@ -101,6 +101,12 @@ def _cases():
                                              **{**{k: v for k, v in COMMON.items() if k != 'rope_theta'}, 'num_hidden_layers': 3},
                                              rope_parameters={'rope_type': 'default', 'rope_theta': 10000.0, 'partial_rotary_factor': 0.5}),
                      'Glm4MoeForCausalLM'),
+        # GPT-OSS: sink logits in the softmax, alternating sliding-window layers, biases on every projection, the router and the
+        # experts, softmax over the top-k router logits, clamped gated unit, YaRN without truncation
+        'gpt_oss': (lambda: T.GptOssConfig(head_dim=32, num_local_experts=4, num_experts_per_tok=2, sliding_window=16, tie_word_embeddings=False,
+                                           **{**{k: v for k, v in COMMON.items() if k != 'rope_theta'}, 'intermediate_size': 64, 'num_hidden_layers': 4},
+                                           rope_parameters={'rope_type': 'yarn', 'factor': 8.0, 'beta_fast': 32.0, 'beta_slow': 1.0, 'truncate': False,
+                                                            'original_max_position_embeddings': 64, 'rope_theta': 150000.0}), 'GptOssForCausalLM'),
         'qwen2_moe_shared': (lambda: T.Qwen2MoeConfig(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64, shared_expert_intermediate_size=96,
                                                       norm_topk_prob=False, decoder_sparse_step=1, mlp_only_layers=[], **COMMON), 'Qwen2MoeForCausalLM'),
     }
@@ -141,7 +147,7 @@ def _ours(path, ids):
 def test_hf_checkpoint_gives_the_same_logits_here(name, tmp_path):
     hf = _hf_model(name)
     hf.save_pretrained(str(tmp_path / 'hf'), safe_serialization=True)
-    ids = torch.randint(0, 512, (1, 150 if name in ('llama3_rope', 'phi3_longrope', 'llama_dynamic_ntk', 'deepseek_v3_yarn') else 37), generator=torch.Generator().manual_seed(1))
+    ids = torch.randint(0, 512, (1, 150 if name in ('llama3_rope', 'phi3_longrope', 'llama_dynamic_ntk', 'deepseek_v3_yarn', 'gpt_oss') else 37), generator=torch.Generator().manual_seed(1))
     with torch.no_grad():
         want = hf(ids).logits[0]
     _, got = _ours(str(tmp_path / 'hf'), ids[0])
@@ -150,7 +156,7 @@ def test_hf_checkpoint_gives_the_same_logits_here(name, tmp_path):
 
 
 @pytest.mark.parametrize('name', ['qwen3', 'qwen3_moe', 'mixtral', 'qwen2_moe_shared', 'qwen3_5', 'qwen3_5_moe', 'qwen3_next', 'glm', 'glm4', 'phi3',
-                                  'phi3_longrope', 'gemma', 'deepseek_v2', 'deepseek_v3', 'deepseek_v3_yarn', 'glm4_moe', 'gemma2', 'gemma3'])
+                                  'phi3_longrope', 'gemma', 'deepseek_v2', 'deepseek_v3', 'deepseek_v3_yarn', 'glm4_moe', 'gemma2', 'gemma3', 'gpt_oss'])
 def test_checkpoint_saved_here_loads_in_transformers(name, tmp_path):
     hf = _hf_model(name)
     hf.save_pretrained(str(tmp_path / 'hf'), safe_serialization=True)

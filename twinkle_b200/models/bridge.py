@@ -54,6 +54,9 @@ def _family(name: str, cfg: DecoderConfig) -> str:
             name = pat.sub(rep, name)
     elif cfg.model_type in ('deepseek_v2', 'deepseek_v3', 'kimi_k2', 'glm4_moe'):
         name = name.replace('.mlp.shared_expert.', '.mlp.shared_experts.').replace('.mlp.e_score_correction_bias', '.mlp.gate.e_score_correction_bias')
+    elif cfg.model_type == 'gpt_oss':
+        name = (name.replace('.mlp.gate.', '.mlp.router.').replace('.mlp.experts.gate_up_bias', '.mlp.experts.gate_up_proj_bias')
+                .replace('.mlp.experts.down_bias', '.mlp.experts.down_proj_bias'))
     elif cfg.model_type in ('gemma2', 'gemma3_text', 'gemma3'):
         # four norms per layer there: input, after attention, before and after the feed-forward block
         for a, b in (('.post_attention_layernorm.', '.pre_feedforward_layernorm.'), ('.post_self_attn_layernorm.', '.post_attention_layernorm.'),
@@ -125,6 +128,23 @@ def _gdn_regroup(t: torch.Tensor, cfg: DecoderConfig, which: str, to_hf: bool) -
     return torch.cat([p.reshape(hk * n, *tail) for p, n in zip(parts, sizes)], 0)
 
 
+def _gpt_oss_expert(t: torch.Tensor, rest: str, to_hf: bool) -> torch.Tensor:
+    """GPT-OSS expert tensors: the checkpoint keeps ``[E, in, out]`` matrices with gate and up columns alternating
+    (``gate = [..., ::2]``, ``up = [..., 1::2]``) and biases alternating the same way; here matrices are ``[E, out, in]`` with
+    ``[gate | up]`` row blocks."""
+    if rest.endswith('gate_up_proj') or rest.endswith('gate_up_bias'):
+        if to_hf:
+            if t.dim() == 3:
+                t = t.transpose(1, 2)                       # [E, H, 2I] with [gate | up] columns
+            g, u = t.chunk(2, dim=-1)
+            return torch.stack([g, u], -1).flatten(-2).contiguous()
+        t = torch.cat([t[..., ::2], t[..., 1::2]], -1)
+        return t.transpose(1, 2).contiguous() if t.dim() == 3 else t.contiguous()
+    if rest.endswith('down_proj'):
+        return t.transpose(1, 2).contiguous()
+    return t
+
+
 def _vl(name: str, cfg: DecoderConfig) -> str:
     """Vision-language checkpoints nest the language model: ``model.X`` → ``model.language_model.X``."""
     return 'model.language_model.' + name[len('model.'):] if _nested(cfg) and name.startswith('model.') else name
@@ -193,6 +213,8 @@ def _internal_to_hf_text(name: str, tensor: torch.Tensor, cfg: DecoderConfig) ->
         return [(_hf_layer(i, 'linear_attn.' + rest[len('self_attn.'):]), tensor)]
     if rest in ('mlp.experts.gate_up_proj', 'mlp.experts.down_proj') and cfg.model_type.startswith('qwen3_5'):
         return [(_hf_layer(i, rest), tensor)]       # this family's checkpoints keep the experts fused, in the layout used here
+    if cfg.model_type == 'gpt_oss' and rest.startswith('mlp.experts.'):
+        return [(_hf_layer(i, rest), _gpt_oss_expert(tensor, rest, True))]
     if rest == 'mlp.experts.gate_up_proj':
         out = []
         for e in range(tensor.shape[0]):
@@ -243,6 +265,8 @@ def _hf_names_for_text(name: str, cfg: DecoderConfig) -> List[str]:
         return [_hf_layer(i, 'linear_attn.' + rest[len('self_attn.'):])]
     if rest in ('mlp.experts.gate_up_proj', 'mlp.experts.down_proj') and cfg.model_type.startswith('qwen3_5'):
         return [_hf_layer(i, rest)]
+    if cfg.model_type == 'gpt_oss' and rest.startswith('mlp.experts.'):
+        return [_hf_layer(i, rest)]
     if rest == 'mlp.experts.gate_up_proj':
         return [_hf_layer(i, f'mlp.experts.{e}.{p}_proj.weight') for e in range(cfg.num_experts) for p in ('gate', 'up')]
     if rest == 'mlp.experts.down_proj':
@@ -257,7 +281,7 @@ def hf_to_internal(name: str, cfg: DecoderConfig, get: Callable[[str], torch.Ten
     m = _LAYER.match(name)
     rest = m.group(2) if m else ''
     i = int(m.group(1)) if m else -1
-    if cfg.model_type in ('mixtral', 'internlm2', 'deepseek_v2', 'deepseek_v3', 'kimi_k2', 'glm4_moe'):      # names that are built without hf_names_for
+    if cfg.model_type in ('mixtral', 'internlm2', 'deepseek_v2', 'deepseek_v3', 'kimi_k2', 'glm4_moe', 'gpt_oss'):      # names that are built without hf_names_for
         plain = get
 
         def get(n: str) -> torch.Tensor:  # noqa: F811
@@ -277,6 +301,15 @@ def hf_to_internal(name: str, cfg: DecoderConfig, get: Callable[[str], torch.Ten
             return get(hf_names_for(name, cfg)[0])
         except KeyError:
             return get(hf_names_for('embed_tokens.weight', cfg)[0])
+    if cfg.model_type == 'gpt_oss' and rest.startswith('mlp.experts.'):
+        lo, hi = expert_range or (0, cfg.num_experts)
+        hf_name = hf_names_for(name, cfg)[0]
+        try:
+            t = get(hf_name)
+        except KeyError:            # the released checkpoints keep the expert matrices as MXFP4 blocks + scales
+            from ..utils.dequantizer import dequant_mxfp4
+            t = dequant_mxfp4(get(hf_name + '_blocks'), get(hf_name + '_scales')).transpose(1, 2)      # [E, out, in] → the [E, in, out] of the bf16 form
+        return _gpt_oss_expert(t, rest, False)[lo:hi].contiguous()
     if rest in ('mlp.experts.gate_up_proj', 'mlp.experts.down_proj'):
         # checkpoints written by newer transformers keep the experts fused, in this package's own layout
         # ([E, 2I, H] gate|up and [E, H, I]); older ones have one tensor per expert and projection

@@ -18,7 +18,7 @@ from typing import List, Any, Dict, Optional
 SUPPORTED_MODEL_TYPES = frozenset({'llama', 'mistral', 'mixtral', 'qwen2', 'qwen2_moe', 'qwen3', 'qwen3_moe', 'seed_oss', 'qwen2_vl', 'qwen2_vl_text',
                                    'qwen2_5_vl', 'qwen2_5_vl_text', 'qwen3_vl', 'qwen3_vl_text', 'qwen3_vl_moe', 'qwen3_vl_moe_text',
                                    'qwen3_5', 'qwen3_5_text', 'qwen3_5_moe', 'qwen3_5_moe_text', 'qwen3_next', 'glm', 'glm4',
-                                   'phi3', 'internlm2', 'internlm3', 'gemma', 'deepseek_v2', 'deepseek_v3', 'kimi_k2', 'glm4_moe', 'gemma2', 'gemma3_text', 'gemma3'})
+                                   'phi3', 'internlm2', 'internlm3', 'gemma', 'deepseek_v2', 'deepseek_v3', 'kimi_k2', 'glm4_moe', 'gemma2', 'gemma3_text', 'gemma3', 'gpt_oss'})
 
 
 def _rope_scaling_of(cfg: Dict[str, Any]) -> Optional[Dict[str, Any]]:
@@ -74,6 +74,13 @@ class DecoderConfig:
     # Gemma-2 / Gemma-3: scores through ``cap · tanh(s / cap)``, output logits likewise; softmax scale ``query_pre_attn_scalar^-½``
     # instead of ``head_dim^-½``; sliding-window layers (``layer_types`` entries ``'sliding_attention'``) of Gemma-3 use a rotary
     # base of their own, without the long-context scaling of the global layers
+    # GPT-OSS: a learned per-head sink logit in the attention softmax, biases on the output projection, the router and the expert
+    # tensors, routing = softmax over the top-k router logits, experts with the clamped ``(up + 1) · gate · σ(1.702 · gate)`` unit
+    attn_sinks: bool = False
+    o_proj_bias: bool = False
+    router_linear_bias: bool = False
+    expert_bias: bool = False
+    expert_act: str = 'swiglu'
     attn_logit_softcapping: Optional[float] = None
     final_logit_softcapping: Optional[float] = None
     query_pre_attn_scalar: Optional[float] = None
@@ -238,6 +245,7 @@ class DecoderConfig:
         if mt.startswith('qwen') and not cfg.get('use_sliding_window'):
             window = None                    # the Qwen configs carry a window size that is switched off by default
         gemma23 = mt in ('gemma2', 'gemma3_text', 'gemma3')
+        oss = mt == 'gpt_oss'
         rope_local = cfg.get('rope_local_base_freq')
         rp = cfg.get('rope_parameters')
         if isinstance(rp, dict) and isinstance(rp.get('full_attention'), dict):      # per-layer-type rotary settings (Gemma-3)
@@ -258,7 +266,7 @@ class DecoderConfig:
             rope_scaling=_rope_scaling_of(cfg), tie_word_embeddings=bool(cfg.get('tie_word_embeddings', False)),
             qk_norm=mt.startswith('qwen3') or mt.startswith('gemma3') or (mt == 'glm4_moe' and bool(cfg.get('use_qk_norm'))),
             attention_bias=bool(cfg.get('attention_bias', cfg.get('qkv_bias', cfg.get('bias', False)) if mt.startswith('internlm') else mt.startswith('qwen2'))),
-            router_scoring=('softmax_grouped' if v2 else 'sigmoid') if dsv3 else 'softmax', router_bias=dsv3 and not v2,
+            router_scoring=('softmax_grouped' if v2 else 'sigmoid') if dsv3 else ('topk_softmax' if oss else 'softmax'), router_bias=dsv3 and not v2,
             n_group=int(cfg.get('n_group') or 1) if (dsv3 and not (v2 and cfg.get('topk_method', 'greedy') == 'greedy')) else 1,
             topk_group=int(cfg.get('topk_group') or 1) if dsv3 else 1, routed_scaling_factor=float(cfg.get('routed_scaling_factor', 1.0)) if dsv3 else 1.0,
             first_k_dense_replace=int(cfg.get('first_k_dense_replace', 0)) if dsv3 else 0, shared_expert_gate=not dsv3,
@@ -266,6 +274,8 @@ class DecoderConfig:
             qk_nope_head_dim=int(cfg.get('qk_nope_head_dim', 128)), qk_rope_head_dim=int(cfg.get('qk_rope_head_dim', 64)),
             v_head_dim=int(cfg.get('v_head_dim', 128)), mla_rope_interleave=bool(cfg.get('rope_interleave', True)),
             hidden_act=act, embed_scale=float(cfg.get('embed_scale', cfg.get('hidden_size', 4096)**0.5 if mt.startswith('gemma') else 1.0)),
+            attn_sinks=oss, o_proj_bias=oss and bool(cfg.get('attention_bias', True)), router_linear_bias=oss, expert_bias=oss,
+            expert_act='clamped_glu' if oss else 'swiglu',
             attn_logit_softcapping=cfg.get('attn_logit_softcapping') if gemma23 else None,
             final_logit_softcapping=cfg.get('final_logit_softcapping') if gemma23 else None,
             query_pre_attn_scalar=cfg.get('query_pre_attn_scalar') if gemma23 else None,
@@ -273,7 +283,7 @@ class DecoderConfig:
             sliding_window=int(window) if window else None,
             num_experts=cfg.get('num_experts', cfg.get('num_local_experts', cfg.get('n_routed_experts', 0))) or 0,
             num_experts_per_tok=cfg.get('num_experts_per_tok', 8),
-            moe_intermediate_size=cfg.get('moe_intermediate_size', cfg.get('intermediate_size', 768) if mt == 'mixtral' else 768),
+            moe_intermediate_size=cfg.get('moe_intermediate_size', cfg.get('intermediate_size', 768) if mt in ('mixtral', 'gpt_oss') else 768),
             norm_topk_prob=(True if cfg.get('norm_topk_prob') is None else bool(cfg['norm_topk_prob'])) and not v2, router_aux_loss_coef=float(cfg.get('router_aux_loss_coef', 0.0)),
             shared_expert_intermediate_size=int(cfg.get('shared_expert_intermediate_size', 0) or 0) if not dsv3
             else int(cfg.get('moe_intermediate_size', 0)) * int(cfg.get('n_shared_experts') or 0),
@@ -335,6 +345,13 @@ class DecoderConfig:
                      first_k_dense_replace=self.first_k_dense_replace, norm_topk_prob=self.norm_topk_prob,
                      num_experts_per_tok=self.num_experts_per_tok, moe_intermediate_size=self.moe_intermediate_size)
             for k in ('num_experts', 'shared_expert_intermediate_size', 'decoder_sparse_step', 'mlp_only_layers'):
+                d.pop(k, None)
+        elif self.model_type == 'gpt_oss':
+            d.update(architectures=['GptOssForCausalLM'], model_type='gpt_oss', num_local_experts=self.num_experts, intermediate_size=self.moe_intermediate_size,
+                     sliding_window=self.sliding_window, layer_types=list(self.layer_types or ['full_attention'] * self.num_hidden_layers),
+                     attention_bias=self.attention_bias, swiglu_limit=7.0, num_experts_per_tok=self.num_experts_per_tok,
+                     router_aux_loss_coef=self.router_aux_loss_coef)
+            for k in ('num_experts', 'moe_intermediate_size', 'norm_topk_prob', 'decoder_sparse_step', 'mlp_only_layers', 'shared_expert_intermediate_size'):
                 d.pop(k, None)
         elif self.model_type == 'glm4_moe':
             d.update(architectures=['Glm4MoeForCausalLM'], model_type='glm4_moe', use_qk_norm=self.qk_norm, n_routed_experts=self.num_experts,
@@ -448,6 +465,12 @@ PRESETS: Dict[str, Dict[str, Any]] = {
                           q_lora_rank=64, kv_lora_rank=32, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32, num_experts=8,
                           num_experts_per_tok=2, moe_intermediate_size=128, shared_expert_intermediate_size=128, shared_expert_gate=False,
                           router_scoring='sigmoid', router_bias=True, n_group=4, topk_group=2, routed_scaling_factor=2.5, first_k_dense_replace=1),
+    # GPT-OSS in small: sink logits, alternating sliding-window layers, biased projections / router / experts, top-k-then-softmax routing
+    'tiny-gpt-oss': dict(vocab_size=1024, hidden_size=256, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                         rope_theta=1.5e5, tie_word_embeddings=False, qk_norm=False, torch_dtype='float32', model_type='gpt_oss', attention_bias=True,
+                         o_proj_bias=True, attn_sinks=True, router_linear_bias=True, expert_bias=True, expert_act='clamped_glu',
+                         router_scoring='topk_softmax', num_experts=8, num_experts_per_tok=2, moe_intermediate_size=128, sliding_window=16,
+                         layer_types=['sliding_attention', 'full_attention', 'sliding_attention', 'full_attention']),
     'tiny-moe': dict(vocab_size=1024, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
                      head_dim=64, rope_theta=1e4, tie_word_embeddings=True, num_experts=8, num_experts_per_tok=2,
                      moe_intermediate_size=128, router_aux_loss_coef=1e-3, torch_dtype='float32'),

@@ -67,7 +67,9 @@ class Attention(nn.Module):
         self.qkv_proj = Linear(h, sum(n for _, n in parts), bias=cfg.attention_bias, parts=parts)
         if self.gated:
             self.qkv_proj.gate_head_dim = d
-        self.o_proj = Linear(cfg.q_size, h, bias=False, name='o_proj')
+        self.o_proj = Linear(cfg.q_size, h, bias=cfg.o_proj_bias, name='o_proj')
+        # GPT-OSS: one learned logit per head that joins the softmax without a value (an always-available place for attention mass)
+        self.sinks = nn.Parameter(torch.zeros(cfg.num_attention_heads)) if cfg.attn_sinks else None
         # the per-head norms follow the model's norm convention ("1 + w" for Qwen3.5; plain weights have offset 0)
         self.norm_offset = float(cfg.rms_norm_offset) if cfg.qk_norm else 0.0
         if cfg.qk_norm:
@@ -99,7 +101,7 @@ class Attention(nn.Module):
     def _plain(self, max_seqlen: int) -> bool:
         """Whether this layer is ordinary causal attention for rows up to ``max_seqlen`` (what the sequence-parallel
         strategies and the fused paths compute)."""
-        return not self.softcap and (self.window is None or self.window >= int(max_seqlen))
+        return not self.softcap and self.sinks is None and (self.window is None or self.window >= int(max_seqlen))
 
     @staticmethod
     def cache_entry(k: torch.Tensor, v: torch.Tensor):
@@ -132,14 +134,15 @@ class Attention(nn.Module):
         if kv_sink is not None:  # sampler prefill: keep K/V for the paged cache
             kv_sink(self.layer_idx, k, v)
         if ap is not None and not self._plain(batch.max_seqlen):
-            raise NotImplementedError('sliding-window / soft-capped attention layers are not wired to the sequence-parallel attention '
+            raise NotImplementedError('sliding-window / soft-capped / sink attention layers are not wired to the sequence-parallel attention '
                                       'strategies; use data, sharded-data or pipeline parallelism, or rows no longer than the window')
         if ap is not None and hasattr(ap, 'attention'):  # context parallel: zig-zag local chunks against gathered keys
             o = ap.attention(q, k, v, batch.seq_lens, self.scale)
             return self.project_out(o, gate)
         if ap is not None:
             q, k, v = ap.scatter_heads(q, k, v)  # [T_local,H,D] → [T_full,H/sp,D]
-        o = ops.flash_attn_varlen(q, k, v, batch.cu_seqlens, batch.max_seqlen, True, self.scale, window=self.window, softcap=self.softcap)
+        o = ops.flash_attn_varlen(q, k, v, batch.cu_seqlens, batch.max_seqlen, True, self.scale, window=self.window, softcap=self.softcap,
+                                  sinks=self.sinks)
         if ap is not None:
             o = ap.gather_heads(o)  # back to [T_local, Hq, D]
         return self.project_out(o, gate)   # the gate is per token of this rank: applied after the heads are back
@@ -235,6 +238,12 @@ class Experts(nn.Module):
         self.num_local, self.first_expert = e, 0
         self.gate_up_proj = nn.Parameter(torch.empty(e, 2 * cfg.moe_intermediate_size, cfg.hidden_size))
         self.down_proj = nn.Parameter(torch.empty(e, cfg.hidden_size, cfg.moe_intermediate_size))
+        if cfg.expert_bias:
+            self.gate_up_bias = nn.Parameter(torch.zeros(e, 2 * cfg.moe_intermediate_size))
+            self.down_bias = nn.Parameter(torch.zeros(e, cfg.hidden_size))
+        else:
+            self.gate_up_bias = self.down_bias = None
+        self.act = ops.ref.clamped_glu if cfg.expert_act == 'clamped_glu' else ops.swiglu
         self.lora = nn.ParameterDict()
         self.max_loras = 0
 
@@ -278,9 +287,16 @@ class Experts(nn.Module):
         """``x_sorted`` rows grouped by local expert; ``offsets [E_local+1]``."""
         lo = self._expert_lora('gate_up')
         gu = ops.expert_linear(x_sorted, self.gate_up_proj, offsets, *(lo or ()))
-        act = ops.swiglu(gu)
+        row_expert = None
+        if self.gate_up_bias is not None:
+            # expert of every row of the grouped layout (rows that pad a segment get their segment's bias and are never read)
+            row_expert = torch.bucketize(torch.arange(x_sorted.shape[0], device=x_sorted.device), offsets[1:].to(torch.long), right=True)
+            row_expert = row_expert.clamp_(max=self.gate_up_proj.shape[0] - 1)
+            gu = gu + self.gate_up_bias[row_expert].to(gu.dtype)
+        act = self.act(gu)
         lo = self._expert_lora('down')
-        return ops.expert_linear(act, self.down_proj, offsets, *(lo or ()))
+        y = ops.expert_linear(act, self.down_proj, offsets, *(lo or ()))
+        return y if row_expert is None else y + self.down_bias[row_expert].to(y.dtype)
 
 
 class MoEBlock(nn.Module):
@@ -289,7 +305,7 @@ class MoEBlock(nn.Module):
     def __init__(self, cfg: DecoderConfig, layer_idx: int):
         super().__init__()
         self.cfg, self.layer_idx = cfg, layer_idx
-        self.gate = Linear(cfg.hidden_size, cfg.num_experts, name='gate')
+        self.gate = Linear(cfg.hidden_size, cfg.num_experts, bias=cfg.router_linear_bias, name='gate')
         self.experts = Experts(cfg)
         # an always-on expert beside the routed ones, scaled per token by a sigmoid gate (Qwen2-MoE / Qwen3-Next style);
         # replicated under expert parallelism (reference ``moe/expert_parallel.py:329-382``)
@@ -307,6 +323,14 @@ class MoEBlock(nn.Module):
         self.record_routing = False
 
     def route(self, x: torch.Tensor, forced: Optional[torch.Tensor]):
+        if self.cfg.router_scoring == 'topk_softmax':      # GPT-OSS: the k largest logits, then a softmax over just those
+            logits = self.gate(x).float()
+            top, idx = logits.topk(self.cfg.num_experts_per_tok, dim=-1)
+            if forced is not None:
+                idx = torch.where(forced[:, :1] < 0, idx, forced.long())
+                top = logits.gather(1, idx)
+            self._hist = None
+            return torch.softmax(top, -1), idx, torch.softmax(logits, -1)
         if self.cfg.router_scoring != 'softmax':
             return self._route_sigmoid(x, forced)
         w, idx, probs, self._hist = ops.moe_router(self.gate(x), self.cfg.num_experts_per_tok, self.cfg.norm_topk_prob, forced)
@@ -482,6 +506,9 @@ class DecoderModel(nn.Module):
         from ..utils.seed import stable_seed
         for name, p in self.named_parameters():
             if 'lora_' in name or name.startswith('lora'):
+                continue
+            if name.endswith(('bias', 'sinks')):       # also the per-expert bias matrices
+                p.zero_()
                 continue
             if p.dim() == 1:
                 if name.endswith('bias'):

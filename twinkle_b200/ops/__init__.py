@@ -366,16 +366,15 @@ class AttentionStash:
 
 def flash_attn_varlen(q, k, v, cu_seqlens, max_seqlen: int, causal: bool = True, scale: Optional[float] = None,
                       cu_seqlens_k=None, max_seqlen_k: int = 0, return_lse: bool = False, window: Optional[int] = None,
-                      softcap: Optional[float] = None):
+                      softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None):
     """Packed causal attention with GQA.  ``q [T,Hq,D]``, ``k,v [Tk,Hkv,D]``.  ``cu_seqlens_k``: the keys of every
     sequence are a (longer) range of their own; the causal diagonal is aligned bottom-right.  A sliding ``window`` shorter
-    than the longest row, or a score ``softcap``, selects the PyTorch form (the kernels compute plain causal attention)."""
+    than the longest row, a score ``softcap`` or per-head ``sinks`` select the PyTorch form (the kernels compute plain causal attention)."""
     scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
     if window is not None and window >= max(int(max_seqlen), int(max_seqlen_k)):
         window = None           # no row reaches past the window: plain causal attention
-    if window is not None or softcap:
-        res = ref.attention_varlen(q, k, v, cu_seqlens, causal, scale, return_lse, cu_seqlens_k, window, softcap)
-        return res
+    if window is not None or softcap or sinks is not None:
+        return ref.attention_varlen(q, k, v, cu_seqlens, causal, scale, return_lse, cu_seqlens_k, window, softcap, sinks)
     if cu_seqlens_k is not None or return_lse:
         if _cuda(q) and q.dtype == torch.bfloat16 and _head_dim_ok(q.shape[-1]):
             out, lse = _FlashAttnVarlen.apply(q.contiguous(), k.contiguous(), v.contiguous(), cu_seqlens.to(torch.int32), int(max_seqlen), causal,
@@ -400,10 +399,10 @@ def flash_attn_varlen(q, k, v, cu_seqlens, max_seqlen: int, causal: bool = True,
 
 
 def paged_attention_decode(q, k_cache, v_cache, block_tables, seq_lens, scale: Optional[float] = None, window: Optional[int] = None,
-                           softcap: Optional[float] = None):
+                           softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None):
     scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
-    if window is not None or softcap:
-        return ref.paged_attention_decode(q, k_cache, v_cache, block_tables, seq_lens, scale, window, softcap)
+    if window is not None or softcap or sinks is not None:
+        return ref.paged_attention_decode(q, k_cache, v_cache, block_tables, seq_lens, scale, window, softcap, sinks)
     if _cuda(q) and q.dtype == torch.bfloat16 and _head_dim_ok(q.shape[-1]):
         return ext().paged_attn_decode(q.contiguous(), k_cache, v_cache, block_tables.to(torch.int32),
                                        seq_lens.to(torch.int32), scale)

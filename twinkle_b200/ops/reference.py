@@ -152,16 +152,26 @@ def geglu(gate_up: torch.Tensor) -> torch.Tensor:
     return (F.gelu(g, approximate='tanh') * u).to(gate_up.dtype)
 
 
+def clamped_glu(gate_up: torch.Tensor, limit: float = 7.0, alpha: float = 1.702) -> torch.Tensor:
+    """GPT-OSS expert activation on ``[gate | up]``: ``(up + 1) · gate · σ(α · gate)`` with ``gate ≤ limit`` and
+    ``|up| ≤ limit``."""
+    g, u = gate_up.float().chunk(2, dim=-1)
+    g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+    return ((u + 1.0) * g * torch.sigmoid(alpha * g)).to(gate_up.dtype)
+
+
 # ----------------------------------------------------------------- attention
 def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor, causal: bool = True,
                      scale: Optional[float] = None, return_lse: bool = False, cu_seqlens_k: Optional[torch.Tensor] = None,
-                     window: Optional[int] = None, softcap: Optional[float] = None):
+                     window: Optional[int] = None, softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None):
     """Packed attention.  ``q [T,Hq,D]``, ``k,v [Tk,Hkv,D]``, ``cu_seqlens`` int
     ``[n+1]``; tokens of different segments never attend to each other; GQA by
     repeating each kv head ``Hq/Hkv`` times.  With ``cu_seqlens_k`` the keys of a segment may be longer than its
     queries; the causal diagonal is then aligned bottom-right (query row r sees keys 0 … r + Lk − Lq).
     ``window``: a query sees only the last ``window`` keys up to and including its own position (sliding-window
-    checkpoints); ``softcap``: scores pass through ``cap · tanh(s / cap)`` before the softmax (Gemma-2)."""
+    checkpoints); ``softcap``: scores pass through ``cap · tanh(s / cap)`` before the softmax (Gemma-2); ``sinks [Hq]``: a
+    learned logit per head that takes part in the softmax and carries no value (GPT-OSS), i.e. it only enlarges the
+    denominator."""
     T, Hq, D = q.shape
     Hkv = k.shape[1]
     rep = Hq // Hkv
@@ -185,6 +195,8 @@ def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
             if window and Lk > window:
                 s = s.masked_fill(torch.ones(L, Lk, dtype=torch.bool, device=q.device).tril(Lk - L - window), float('-inf'))
         l = torch.logsumexp(s, -1)
+        if sinks is not None:
+            l = torch.logaddexp(l, sinks.float()[:, None])
         p = torch.exp(s - l[..., None])
         out[a:b] = (p @ vs).transpose(0, 1).to(q.dtype)
         lse[:, a:b] = l
@@ -193,7 +205,7 @@ def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
 
 def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
                            seq_lens: torch.Tensor, scale: Optional[float] = None, window: Optional[int] = None,
-                           softcap: Optional[float] = None) -> torch.Tensor:
+                           softcap: Optional[float] = None, sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One query token per sequence against a paged KV cache.
     ``q [B,Hq,D]``; caches ``[num_blocks, block_size, Hkv, D]``; ``block_tables
     [B, max_blocks]`` int; ``seq_lens [B]`` (including the current token)."""
@@ -213,6 +225,10 @@ def paged_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
             s = torch.tanh(s / softcap) * softcap
         if window and n > window:
             s[:, :n - window] = float('-inf')
+        if sinks is not None:
+            l = torch.logaddexp(torch.logsumexp(s, -1), sinks.float())
+            out[b] = torch.einsum('hn,nhd->hd', torch.exp(s - l[:, None]), vv).to(q.dtype)
+            continue
         out[b] = torch.einsum('hn,nhd->hd', torch.softmax(s, -1), vv).to(q.dtype)
     return out
 

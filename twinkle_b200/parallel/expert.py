@@ -149,9 +149,12 @@ def shard_experts(model, strat, ep_rank: int, rep_comm: Optional[Communicator]) 
             ex.down_proj = torch.nn.Parameter(ex.down_proj.data[lo:lo + El].clone(), requires_grad=ex.down_proj.requires_grad)
             for key in list(ex.lora.keys()):
                 ex.lora[key] = torch.nn.Parameter(ex.lora[key].data[:, lo:lo + El].clone())
+            if getattr(ex, 'gate_up_bias', None) is not None:
+                ex.gate_up_bias = torch.nn.Parameter(ex.gate_up_bias.data[lo:lo + El].clone(), requires_grad=ex.gate_up_bias.requires_grad)
+                ex.down_bias = torch.nn.Parameter(ex.down_bias.data[lo:lo + El].clone(), requires_grad=ex.down_bias.requires_grad)
         # expert tensors differ per EP rank: their gradients are summed only over the ranks that hold the same
         # experts, and their squared norms are summed over the EP group when the global norm is taken
-        for p in [ex.gate_up_proj, ex.down_proj] + list(ex.lora.values()):
+        for p in [ex.gate_up_proj, ex.down_proj] + list(ex.lora.values()) + [b for b in (getattr(ex, 'gate_up_bias', None), getattr(ex, 'down_bias', None)) if b is not None]:
             p._ep_local = True
             p._ep_replica_comm = rep_comm
         ex.num_local, ex.first_expert = El, lo

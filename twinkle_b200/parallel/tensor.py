@@ -272,6 +272,9 @@ def apply_tensor_parallel(model, cfg, comm: Communicator, sequence_parallel: boo
     tensor) and switch the modules to their TP forward."""
     if comm.world_size <= 1:
         return None
+    if getattr(cfg, 'attn_sinks', False) or getattr(cfg, 'expert_bias', False):
+        raise NotImplementedError('attention sinks and biased experts / output projections (GPT-OSS) have no tensor-parallel split here; '
+                                  'use tp_size=1 (data, sharded-data, expert and pipeline parallelism apply)')
     if getattr(cfg, 'is_mla', False):
         raise NotImplementedError('multi-head latent attention has no tensor-parallel split here; use tp_size=1 '
                                   '(data, sharded-data, expert and pipeline parallelism apply)')

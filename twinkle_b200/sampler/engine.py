@@ -192,7 +192,7 @@ class NativeEngine:
                 q, k, v, gate = at.heads_from(h, *(local if (local is not None and getattr(at, 'local_rope', False)) else (cos, sin)))
                 self.cache.k[li, blk, off], self.cache.v[li, blk, off] = at.cache_entry(k, v)
                 o = ops.paged_attention_decode(q, self.cache.k[li], self.cache.v[li], table, seq_lens, at.scale,
-                                               window=getattr(at, 'window', None), softcap=getattr(at, 'softcap', None))
+                                               window=getattr(at, 'window', None), softcap=getattr(at, 'softcap', None), sinks=getattr(at, 'sinks', None))
                 n, x = layer.after_attention(x, at.project_out(o, gate))
                 x = x + layer.feed_forward(n)
             x = self.model.norm(x)
@@ -234,7 +234,7 @@ class NativeEngine:
         use_graph = (self.use_cuda_graphs and self.device.type == 'cuda' and lora is None and not self.capture_routing and not self.cfg.is_moe
                      and not any(getattr(l, 'is_linear', False) for l in self.model.layers) and not any(s.rope_delta for s in seqs)
                      # windows, score caps and latent attention decode through the PyTorch form, which reads lengths on the host
-                     and not self.cfg.sliding_window and not self.cfg.attn_logit_softcapping and not self.cfg.is_mla)
+                     and not self.cfg.sliding_window and not self.cfg.attn_logit_softcapping and not self.cfg.is_mla and not self.cfg.attn_sinks)
         if use_graph:
             Bb = 1 << max(B - 1, 0).bit_length()
             Mb = 1 << max(max_blocks - 1, 0).bit_length()
