@@ -72,6 +72,9 @@ def _cases():
                                               rope_parameters={'full_attention': {'rope_type': 'linear', 'factor': 8.0, 'rope_theta': 1000000.0},
                                                                'sliding_attention': {'rope_type': 'default', 'rope_theta': 10000.0}}), 'Gemma3ForCausalLM'),
         'mistral_window': (lambda: T.MistralConfig(sliding_window=16, **COMMON), 'MistralForCausalLM'),
+        # Granite: Llama with four constants (embeddings ×, softmax scale, residual ×, logits ÷)
+        'granite': (lambda: T.GraniteConfig(tie_word_embeddings=True, embedding_multiplier=12.0, attention_multiplier=0.0078125 * 4, residual_multiplier=0.22,
+                                            logits_scaling=8.0, **COMMON), 'GraniteForCausalLM'),
         'llama_dynamic_ntk': (lambda: T.LlamaConfig(tie_word_embeddings=False, **{**COMMON, 'max_position_embeddings': 64},
                                                     rope_scaling={'rope_type': 'dynamic', 'factor': 2.0}), 'LlamaForCausalLM'),
         # DeepSeek-V3: latent attention (query bottleneck, shared rotary key head, 48-wide scores / 24-wide values), a dense first
@@ -156,7 +159,7 @@ def test_hf_checkpoint_gives_the_same_logits_here(name, tmp_path):
 
 
 @pytest.mark.parametrize('name', ['qwen3', 'qwen3_moe', 'mixtral', 'qwen2_moe_shared', 'qwen3_5', 'qwen3_5_moe', 'qwen3_next', 'glm', 'glm4', 'phi3',
-                                  'phi3_longrope', 'gemma', 'deepseek_v2', 'deepseek_v3', 'deepseek_v3_yarn', 'glm4_moe', 'gemma2', 'gemma3', 'gpt_oss'])
+                                  'phi3_longrope', 'gemma', 'deepseek_v2', 'deepseek_v3', 'deepseek_v3_yarn', 'glm4_moe', 'gemma2', 'gemma3', 'gpt_oss', 'granite'])
 def test_checkpoint_saved_here_loads_in_transformers(name, tmp_path):
     hf = _hf_model(name)
     hf.save_pretrained(str(tmp_path / 'hf'), safe_serialization=True)
@@ -325,3 +328,19 @@ def test_internlm2_checkpoint_layout(tmp_path):
     assert sorted(back) == sorted(out)
     for k in out:
         assert torch.equal(back[k], out[k]), k
+
+
+def test_granite_log_probs_carry_the_logit_divisor(tmp_path):
+    """The fused head + log-softmax path never forms the scaled logits: it folds Granite's divisor into the temperature."""
+    from twinkle_b200.models.decoder import PackedBatch
+    hf = _hf_model('granite')
+    hf.save_pretrained(str(tmp_path / 'hf'), safe_serialization=True)
+    ids = torch.randint(0, 512, (1, 33), generator=torch.Generator().manual_seed(5))
+    with torch.no_grad():
+        want = torch.log_softmax(hf(ids).logits[0, :-1].float() / 0.7, -1).gather(-1, ids[0, 1:, None])[:, 0]
+    m, _ = _ours(str(tmp_path / 'hf'), ids[0])
+    n = ids.shape[1]
+    with torch.no_grad():
+        hidden = m.model(PackedBatch(ids[0], torch.arange(n), torch.tensor([0, n], dtype=torch.int32), n))
+        got, _ = m.model.token_logprobs(hidden[:-1], ids[0, 1:], temperature=0.7)
+    assert torch.allclose(got, want, atol=3e-5), float((got - want).abs().max())

@@ -18,7 +18,7 @@ from typing import List, Any, Dict, Optional
 SUPPORTED_MODEL_TYPES = frozenset({'llama', 'mistral', 'mixtral', 'qwen2', 'qwen2_moe', 'qwen3', 'qwen3_moe', 'seed_oss', 'qwen2_vl', 'qwen2_vl_text',
                                    'qwen2_5_vl', 'qwen2_5_vl_text', 'qwen3_vl', 'qwen3_vl_text', 'qwen3_vl_moe', 'qwen3_vl_moe_text',
                                    'qwen3_5', 'qwen3_5_text', 'qwen3_5_moe', 'qwen3_5_moe_text', 'qwen3_next', 'glm', 'glm4',
-                                   'phi3', 'internlm2', 'internlm3', 'gemma', 'deepseek_v2', 'deepseek_v3', 'kimi_k2', 'glm4_moe', 'gemma2', 'gemma3_text', 'gemma3', 'gpt_oss'})
+                                   'phi3', 'internlm2', 'internlm3', 'gemma', 'deepseek_v2', 'deepseek_v3', 'kimi_k2', 'glm4_moe', 'gemma2', 'gemma3_text', 'gemma3', 'gpt_oss', 'granite'})
 
 
 def _rope_scaling_of(cfg: Dict[str, Any]) -> Optional[Dict[str, Any]]:
@@ -76,6 +76,10 @@ class DecoderConfig:
     # base of their own, without the long-context scaling of the global layers
     # GPT-OSS: a learned per-head sink logit in the attention softmax, biases on the output projection, the router and the expert
     # tensors, routing = softmax over the top-k router logits, experts with the clamped ``(up + 1) · gate · σ(1.702 · gate)`` unit
+    # Granite: what each sub-layer adds to the residual stream is multiplied by ``residual_multiplier``, output logits are divided by
+    # ``logits_scaling``, the softmax scale is ``attention_multiplier`` (kept in ``query_pre_attn_scalar`` as its inverse square)
+    residual_multiplier: float = 1.0
+    logits_scaling: float = 1.0
     attn_sinks: bool = False
     o_proj_bias: bool = False
     router_linear_bias: bool = False
@@ -246,6 +250,7 @@ class DecoderConfig:
             window = None                    # the Qwen configs carry a window size that is switched off by default
         gemma23 = mt in ('gemma2', 'gemma3_text', 'gemma3')
         oss = mt == 'gpt_oss'
+        granite = mt == 'granite'
         rope_local = cfg.get('rope_local_base_freq')
         rp = cfg.get('rope_parameters')
         if isinstance(rp, dict) and isinstance(rp.get('full_attention'), dict):      # per-layer-type rotary settings (Gemma-3)
@@ -273,12 +278,14 @@ class DecoderConfig:
             q_lora_rank=cfg.get('q_lora_rank') if mla else None, kv_lora_rank=int(cfg.get('kv_lora_rank', 0)) if mla else 0,
             qk_nope_head_dim=int(cfg.get('qk_nope_head_dim', 128)), qk_rope_head_dim=int(cfg.get('qk_rope_head_dim', 64)),
             v_head_dim=int(cfg.get('v_head_dim', 128)), mla_rope_interleave=bool(cfg.get('rope_interleave', True)),
-            hidden_act=act, embed_scale=float(cfg.get('embed_scale', cfg.get('hidden_size', 4096)**0.5 if mt.startswith('gemma') else 1.0)),
+            hidden_act=act, embed_scale=float(cfg.get('embed_scale', cfg.get('hidden_size', 4096)**0.5 if mt.startswith('gemma') else (cfg.get('embedding_multiplier', 1.0) if granite else 1.0))),
             attn_sinks=oss, o_proj_bias=oss and bool(cfg.get('attention_bias', True)), router_linear_bias=oss, expert_bias=oss,
             expert_act='clamped_glu' if oss else 'swiglu',
             attn_logit_softcapping=cfg.get('attn_logit_softcapping') if gemma23 else None,
             final_logit_softcapping=cfg.get('final_logit_softcapping') if gemma23 else None,
-            query_pre_attn_scalar=cfg.get('query_pre_attn_scalar') if gemma23 else None,
+            query_pre_attn_scalar=cfg.get('query_pre_attn_scalar') if gemma23 else (float(cfg['attention_multiplier'])**-2 if (granite and cfg.get('attention_multiplier')) else None),
+            residual_multiplier=float(cfg.get('residual_multiplier', 1.0)) if granite else 1.0,
+            logits_scaling=float(cfg.get('logits_scaling', 1.0)) if granite else 1.0,
             rope_local_theta=float(rope_local) if (rope_local and mt.startswith('gemma3')) else None,
             sliding_window=int(window) if window else None,
             num_experts=cfg.get('num_experts', cfg.get('num_local_experts', cfg.get('n_routed_experts', 0))) or 0,
@@ -346,6 +353,9 @@ class DecoderConfig:
                      num_experts_per_tok=self.num_experts_per_tok, moe_intermediate_size=self.moe_intermediate_size)
             for k in ('num_experts', 'shared_expert_intermediate_size', 'decoder_sparse_step', 'mlp_only_layers'):
                 d.pop(k, None)
+        elif self.model_type == 'granite':
+            d.update(architectures=['GraniteForCausalLM'], embedding_multiplier=self.embed_scale, residual_multiplier=self.residual_multiplier,
+                     logits_scaling=self.logits_scaling, attention_multiplier=self.attn_scale, mlp_bias=False)
         elif self.model_type == 'gpt_oss':
             d.update(architectures=['GptOssForCausalLM'], model_type='gpt_oss', num_local_experts=self.num_experts, intermediate_size=self.moe_intermediate_size,
                      sliding_window=self.sliding_window, layer_types=list(self.layer_types or ['full_attention'] * self.num_hidden_layers),

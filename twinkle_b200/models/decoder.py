@@ -430,6 +430,7 @@ class DecoderLayer(nn.Module):
             self.self_attn = MLAttention(cfg, layer_idx) if cfg.is_mla else Attention(cfg, layer_idx)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.rms_norm_offset)
         self.is_moe = cfg.layer_is_moe(layer_idx)          # DeepSeek keeps a dense block in its first layers
+        self.residual_multiplier = float(cfg.residual_multiplier)
         self.first_moe_layer = cfg.first_k_dense_replace      # recorded routing lists have one entry per mixture-of-experts layer
         self.mlp = MoEBlock(cfg, layer_idx) if self.is_moe else MLP(cfg)
         # GLM-4: each sub-layer's output is normalised before it joins the residual stream
@@ -456,6 +457,8 @@ class DecoderLayer(nn.Module):
         """Token-mixer output ``a`` joins the residual stream ``x``: ``(input of the feed-forward block, new residual)``."""
         if self.post_self_attn_layernorm is not None:
             a = self.post_self_attn_layernorm(a)
+        if self.residual_multiplier != 1.0:
+            a = a * self.residual_multiplier
         return self.post_attention_layernorm.forward_add(a, x)
 
     def feed_forward(self, n: torch.Tensor, forced=None) -> torch.Tensor:
@@ -463,8 +466,9 @@ class DecoderLayer(nn.Module):
         if self.is_moe:
             m = self.mlp(n, forced)
         else:
-            m = self.mlp(n, value_unused=self.post_mlp_layernorm is None)   # a following norm reads the value
-        return self.post_mlp_layernorm(m) if self.post_mlp_layernorm is not None else m
+            m = self.mlp(n, value_unused=self.post_mlp_layernorm is None and self.residual_multiplier == 1.0)   # a following norm or factor reads the value
+        m = self.post_mlp_layernorm(m) if self.post_mlp_layernorm is not None else m
+        return m * self.residual_multiplier if self.residual_multiplier != 1.0 else m
 
 
 class DecoderModel(nn.Module):
@@ -587,6 +591,8 @@ class DecoderModel(nn.Module):
 
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
         z = ops.linear(hidden, self.head_weight())
+        if self.cfg.logits_scaling != 1.0:
+            z = z / self.cfg.logits_scaling
         cap = self.cfg.final_logit_softcapping
         return torch.tanh(z / cap) * cap if cap else z
 
@@ -602,6 +608,7 @@ class DecoderModel(nn.Module):
                 lps.append(lp)
                 ents.append(en)
             return torch.cat(lps), (torch.cat(ents) if with_entropy else None)
+        temperature = temperature * self.cfg.logits_scaling      # Granite divides its logits by a constant: the same thing as a temperature
         if self.tp is not None:
             from ..parallel.tensor import CopyToTP, GatherTokens, vocab_parallel_logprob
             # backward of either op sums the per-vocabulary-shard partial gradients of the hidden states
