@@ -72,6 +72,9 @@ def _cases():
                                               rope_parameters={'full_attention': {'rope_type': 'linear', 'factor': 8.0, 'rope_theta': 1000000.0},
                                                                'sliding_attention': {'rope_type': 'default', 'rope_theta': 10000.0}}), 'Gemma3ForCausalLM'),
         'mistral_window': (lambda: T.MistralConfig(sliding_window=16, **COMMON), 'MistralForCausalLM'),
+        # OLMo-2: norms on the sub-layer outputs only, q / k norms over the whole projection
+        'olmo2': (lambda: T.Olmo2Config(tie_word_embeddings=False, **COMMON), 'Olmo2ForCausalLM'),
+        'olmo3': (lambda: T.Olmo3Config(tie_word_embeddings=False, sliding_window=16, **{**COMMON, 'num_hidden_layers': 4}), 'Olmo3ForCausalLM'),
         # Granite: Llama with four constants (embeddings ×, softmax scale, residual ×, logits ÷)
         'granite': (lambda: T.GraniteConfig(tie_word_embeddings=True, embedding_multiplier=12.0, attention_multiplier=0.0078125 * 4, residual_multiplier=0.22,
                                             logits_scaling=8.0, **COMMON), 'GraniteForCausalLM'),
@@ -159,7 +162,7 @@ def test_hf_checkpoint_gives_the_same_logits_here(name, tmp_path):
 
 
 @pytest.mark.parametrize('name', ['qwen3', 'qwen3_moe', 'mixtral', 'qwen2_moe_shared', 'qwen3_5', 'qwen3_5_moe', 'qwen3_next', 'glm', 'glm4', 'phi3',
-                                  'phi3_longrope', 'gemma', 'deepseek_v2', 'deepseek_v3', 'deepseek_v3_yarn', 'glm4_moe', 'gemma2', 'gemma3', 'gpt_oss', 'granite'])
+                                  'phi3_longrope', 'gemma', 'deepseek_v2', 'deepseek_v3', 'deepseek_v3_yarn', 'glm4_moe', 'gemma2', 'gemma3', 'gpt_oss', 'granite', 'olmo2', 'olmo3'])
 def test_checkpoint_saved_here_loads_in_transformers(name, tmp_path):
     hf = _hf_model(name)
     hf.save_pretrained(str(tmp_path / 'hf'), safe_serialization=True)

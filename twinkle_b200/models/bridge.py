@@ -54,6 +54,8 @@ def _family(name: str, cfg: DecoderConfig) -> str:
             name = pat.sub(rep, name)
     elif cfg.model_type in ('deepseek_v2', 'deepseek_v3', 'kimi_k2', 'glm4_moe'):
         name = name.replace('.mlp.shared_expert.', '.mlp.shared_experts.').replace('.mlp.e_score_correction_bias', '.mlp.gate.e_score_correction_bias')
+    elif cfg.model_type in ('olmo2', 'olmo3'):       # only the norms on the sub-layer outputs exist there
+        name = name.replace('.post_self_attn_layernorm.', '.post_attention_layernorm.').replace('.post_mlp_layernorm.', '.post_feedforward_layernorm.')
     elif cfg.model_type == 'gpt_oss':
         name = (name.replace('.mlp.gate.', '.mlp.router.').replace('.mlp.experts.gate_up_bias', '.mlp.experts.gate_up_proj_bias')
                 .replace('.mlp.experts.down_bias', '.mlp.experts.down_proj_bias'))

@@ -18,7 +18,7 @@ from typing import List, Any, Dict, Optional
 SUPPORTED_MODEL_TYPES = frozenset({'llama', 'mistral', 'mixtral', 'qwen2', 'qwen2_moe', 'qwen3', 'qwen3_moe', 'seed_oss', 'qwen2_vl', 'qwen2_vl_text',
                                    'qwen2_5_vl', 'qwen2_5_vl_text', 'qwen3_vl', 'qwen3_vl_text', 'qwen3_vl_moe', 'qwen3_vl_moe_text',
                                    'qwen3_5', 'qwen3_5_text', 'qwen3_5_moe', 'qwen3_5_moe_text', 'qwen3_next', 'glm', 'glm4',
-                                   'phi3', 'internlm2', 'internlm3', 'gemma', 'deepseek_v2', 'deepseek_v3', 'kimi_k2', 'glm4_moe', 'gemma2', 'gemma3_text', 'gemma3', 'gpt_oss', 'granite'})
+                                   'phi3', 'internlm2', 'internlm3', 'gemma', 'deepseek_v2', 'deepseek_v3', 'kimi_k2', 'glm4_moe', 'gemma2', 'gemma3_text', 'gemma3', 'gpt_oss', 'granite', 'olmo2', 'olmo3'})
 
 
 def _rope_scaling_of(cfg: Dict[str, Any]) -> Optional[Dict[str, Any]]:
@@ -80,6 +80,10 @@ class DecoderConfig:
     # ``logits_scaling``, the softmax scale is ``attention_multiplier`` (kept in ``query_pre_attn_scalar`` as its inverse square)
     residual_multiplier: float = 1.0
     logits_scaling: float = 1.0
+    # OLMo-2 / OLMo-3: no norm in front of a sub-layer, only the one on its output (``sandwich_norm`` without ``pre_norm``), and
+    # q / k norms over the whole projection instead of per head
+    pre_norm: bool = True
+    qk_norm_full: bool = False
     attn_sinks: bool = False
     o_proj_bias: bool = False
     router_linear_bias: bool = False
@@ -251,6 +255,7 @@ class DecoderConfig:
         gemma23 = mt in ('gemma2', 'gemma3_text', 'gemma3')
         oss = mt == 'gpt_oss'
         granite = mt == 'granite'
+        olmo = mt in ('olmo2', 'olmo3')
         rope_local = cfg.get('rope_local_base_freq')
         rp = cfg.get('rope_parameters')
         if isinstance(rp, dict) and isinstance(rp.get('full_attention'), dict):      # per-layer-type rotary settings (Gemma-3)
@@ -269,7 +274,8 @@ class DecoderConfig:
             else int(cfg.get('qk_nope_head_dim', 128)) + int(cfg.get('qk_rope_head_dim', 64)), rms_norm_eps=cfg.get('rms_norm_eps', 1e-6),
             rope_theta=float(cfg.get('rope_theta', (cfg.get('rope_parameters') or {}).get('rope_theta', 1e6))),
             rope_scaling=_rope_scaling_of(cfg), tie_word_embeddings=bool(cfg.get('tie_word_embeddings', False)),
-            qk_norm=mt.startswith('qwen3') or mt.startswith('gemma3') or (mt == 'glm4_moe' and bool(cfg.get('use_qk_norm'))),
+            pre_norm=not olmo, qk_norm_full=olmo,
+            qk_norm=olmo or mt.startswith('qwen3') or mt.startswith('gemma3') or (mt == 'glm4_moe' and bool(cfg.get('use_qk_norm'))),
             attention_bias=bool(cfg.get('attention_bias', cfg.get('qkv_bias', cfg.get('bias', False)) if mt.startswith('internlm') else mt.startswith('qwen2'))),
             router_scoring=('softmax_grouped' if v2 else 'sigmoid') if dsv3 else ('topk_softmax' if oss else 'softmax'), router_bias=dsv3 and not v2,
             n_group=int(cfg.get('n_group') or 1) if (dsv3 and not (v2 and cfg.get('topk_method', 'greedy') == 'greedy')) else 1,
@@ -297,7 +303,7 @@ class DecoderConfig:
             rms_norm_offset=float(cfg.get('rms_norm_offset', 1.0 if (mt.startswith('gemma') or q35) else 0.0)),
             partial_rotary_factor=float(cfg.get('partial_rotary_factor', (cfg.get('rope_parameters') or {}).get('partial_rotary_factor', 1.0)) or 1.0),
             attn_output_gate=bool(cfg.get('attn_output_gate', q35)),
-            rope_interleaved=bool(cfg.get('rope_interleaved', mt in ('glm', 'glm4'))), sandwich_norm=bool(cfg.get('sandwich_norm', mt == 'glm4' or gemma23)),
+            rope_interleaved=bool(cfg.get('rope_interleaved', mt in ('glm', 'glm4'))), sandwich_norm=bool(cfg.get('sandwich_norm', mt == 'glm4' or gemma23 or olmo)),
             layer_types=list(cfg['layer_types']) if cfg.get('layer_types') and ('linear_attention' in cfg['layer_types'] or ('sliding_attention' in cfg['layer_types'] and window)) else None,
             linear_num_key_heads=cfg.get('linear_num_key_heads', 16), linear_num_value_heads=cfg.get('linear_num_value_heads', 32),
             linear_key_head_dim=cfg.get('linear_key_head_dim', 128), linear_value_head_dim=cfg.get('linear_value_head_dim', 128),
@@ -353,6 +359,10 @@ class DecoderConfig:
                      num_experts_per_tok=self.num_experts_per_tok, moe_intermediate_size=self.moe_intermediate_size)
             for k in ('num_experts', 'shared_expert_intermediate_size', 'decoder_sparse_step', 'mlp_only_layers'):
                 d.pop(k, None)
+        elif self.model_type in ('olmo2', 'olmo3'):
+            d.update(architectures=['Olmo3ForCausalLM' if self.model_type == 'olmo3' else 'Olmo2ForCausalLM'], model_type=self.model_type)
+            if self.model_type == 'olmo3':
+                d.update(sliding_window=self.sliding_window, layer_types=list(self.layer_types or ['full_attention'] * self.num_hidden_layers))
         elif self.model_type == 'granite':
             d.update(architectures=['GraniteForCausalLM'], embedding_multiplier=self.embed_scale, residual_multiplier=self.residual_multiplier,
                      logits_scaling=self.logits_scaling, attention_multiplier=self.attn_scale, mlp_bias=False)

@@ -72,7 +72,11 @@ class Attention(nn.Module):
         self.sinks = nn.Parameter(torch.zeros(cfg.num_attention_heads)) if cfg.attn_sinks else None
         # the per-head norms follow the model's norm convention ("1 + w" for Qwen3.5; plain weights have offset 0)
         self.norm_offset = float(cfg.rms_norm_offset) if cfg.qk_norm else 0.0
-        if cfg.qk_norm:
+        self.qk_norm_full = bool(cfg.qk_norm and cfg.qk_norm_full)       # OLMo-2: one norm over all heads of the projection
+        if self.qk_norm_full:
+            self.q_norm = RMSNorm(cfg.q_size, cfg.rms_norm_eps, self.norm_offset)
+            self.k_norm = RMSNorm(cfg.kv_size, cfg.rms_norm_eps, self.norm_offset)
+        elif cfg.qk_norm:
             self.q_norm = RMSNorm(d, cfg.rms_norm_eps, self.norm_offset)
             self.k_norm = RMSNorm(d, cfg.rms_norm_eps, self.norm_offset)
         else:
@@ -92,6 +96,9 @@ class Attention(nn.Module):
         if self.gated:
             w = (self.hq + 2 * self.hkv) * self.d
             qkv, gate = qkv[:, :w], qkv[:, w:]
+        if self.qk_norm_full:
+            q, k, v = qkv.split([self.hq * self.d, self.hkv * self.d, self.hkv * self.d], dim=-1)
+            qkv, qw, kw = torch.cat([self.q_norm(q.contiguous()), self.k_norm(k.contiguous()), v], -1), None, None
         q, k, v = ops.qkv_norm_rope(qkv, qw, kw, cos, sin, self.hq, self.hkv, self.d, self.cfg.rms_norm_eps, self.norm_offset)
         return q, k, v, gate
 
@@ -119,7 +126,7 @@ class Attention(nn.Module):
         kw = self.k_norm.weight if self.k_norm is not None else None
         ap = self.attn_parallel
         if (ap is not None and getattr(batch, 'rope_full', None) is not None and kv_sink is None and hasattr(ap, 'project_scatter')
-                and not self.gated and self.norm_offset == 0.0 and self._plain(batch.max_seqlen) and not self.local_rope):
+                and not self.gated and self.norm_offset == 0.0 and self._plain(batch.max_seqlen) and not self.local_rope and not self.qk_norm_full):
             # projection whose epilogue already delivers [T_full, (Hq + 2 Hkv)/sp · D] to every peer
             qkv_full = ap.project_scatter(x, self.qkv_proj, self.hq, self.hkv, self.d)
             if qkv_full is not None:
@@ -420,7 +427,7 @@ class DecoderLayer(nn.Module):
     def __init__(self, cfg: DecoderConfig, layer_idx: int):
         super().__init__()
         self.layer_idx = layer_idx
-        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.rms_norm_offset)
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.rms_norm_offset) if cfg.pre_norm else None
         self.is_linear = bool(cfg.layer_types) and cfg.layer_types[layer_idx] == 'linear_attention'
         if self.is_linear:
             from .linear_attention import GatedDeltaNet
@@ -428,7 +435,7 @@ class DecoderLayer(nn.Module):
                                            cfg.linear_value_head_dim, cfg.linear_conv_kernel_dim, cfg.rms_norm_eps)
         else:
             self.self_attn = MLAttention(cfg, layer_idx) if cfg.is_mla else Attention(cfg, layer_idx)
-        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.rms_norm_offset)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.rms_norm_offset) if cfg.pre_norm else None
         self.is_moe = cfg.layer_is_moe(layer_idx)          # DeepSeek keeps a dense block in its first layers
         self.residual_multiplier = float(cfg.residual_multiplier)
         self.first_moe_layer = cfg.first_k_dense_replace      # recorded routing lists have one entry per mixture-of-experts layer
@@ -446,12 +453,16 @@ class DecoderLayer(nn.Module):
             if kv_sink is not None and lin is None:
                 raise NotImplementedError('this kv_sink does not take linear-attention state (give it a linear_state attribute)')
             sink = (lambda conv, st: lin(self.layer_idx, conv, st)) if lin is not None else None
-            a = self.self_attn(self.input_layernorm(x), batch.cu_seqlens, state_sink=sink)
+            a = self.self_attn(self.pre(x), batch.cu_seqlens, state_sink=sink)
         else:
-            a = self.self_attn(self.input_layernorm(x), cos, sin, batch, kv_sink)
+            a = self.self_attn(self.pre(x), cos, sin, batch, kv_sink)
         n, h = self.after_attention(x, a)
         forced = batch.routed_experts[self.layer_idx - self.first_moe_layer] if (self.is_moe and batch.routed_experts is not None) else None
         return ops.add(h, self.feed_forward(n, forced), value_unused=True)
+
+    def pre(self, x: torch.Tensor) -> torch.Tensor:
+        """Input of the token mixer: the normalised stream, or the stream itself in stacks that only norm sub-layer outputs."""
+        return self.input_layernorm(x) if self.input_layernorm is not None else x
 
     def after_attention(self, x: torch.Tensor, a: torch.Tensor):
         """Token-mixer output ``a`` joins the residual stream ``x``: ``(input of the feed-forward block, new residual)``."""
@@ -459,6 +470,9 @@ class DecoderLayer(nn.Module):
             a = self.post_self_attn_layernorm(a)
         if self.residual_multiplier != 1.0:
             a = a * self.residual_multiplier
+        if self.post_attention_layernorm is None:       # no norm in front of the feed-forward block either
+            h = ops.add(x, a)
+            return h, h
         return self.post_attention_layernorm.forward_add(a, x)
 
     def feed_forward(self, n: torch.Tensor, forced=None) -> torch.Tensor:

@@ -275,6 +275,8 @@ def apply_tensor_parallel(model, cfg, comm: Communicator, sequence_parallel: boo
     if getattr(cfg, 'attn_sinks', False) or getattr(cfg, 'expert_bias', False):
         raise NotImplementedError('attention sinks and biased experts / output projections (GPT-OSS) have no tensor-parallel split here; '
                                   'use tp_size=1 (data, sharded-data, expert and pipeline parallelism apply)')
+    if getattr(cfg, 'qk_norm_full', False):
+        raise NotImplementedError('q / k norms over the whole projection (OLMo-2) need statistics of all heads: no tensor-parallel split here; use tp_size=1')
     if getattr(cfg, 'is_mla', False):
         raise NotImplementedError('multi-head latent attention has no tensor-parallel split here; use tp_size=1 '
                                   '(data, sharded-data, expert and pipeline parallelism apply)')

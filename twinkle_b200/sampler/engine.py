@@ -179,7 +179,7 @@ class NativeEngine:
         with lora_batch(lora):
             for li, layer in enumerate(self.model.layers):
                 at = layer.self_attn
-                h = layer.input_layernorm(x)
+                h = layer.pre(x)
                 if getattr(layer, 'is_linear', False):
                     conv = torch.stack([s.linear[li][0] for s in seqs])
                     st = torch.stack([s.linear[li][1] for s in seqs])
