@@ -226,11 +226,12 @@ def test_adapter_saved_in_peft_layout_merges_into_the_hf_model(name, tmp_path):
 
 
 def test_unknown_architectures_are_refused_not_guessed(tmp_path, monkeypatch):
-    """Granite shares every config field with Llama but scales embeddings, residuals, attention and logits: loading it as a
-    Llama would run and be wrong. Unknown ``model_type`` values are refused unless explicitly allowed."""
+    """Cohere's Command models share their config fields with Llama but run attention and feed-forward block in parallel from
+    one LayerNorm and scale their logits: loading one as a Llama would run and be wrong.  Unknown ``model_type`` values are
+    refused unless explicitly allowed."""
     from twinkle_b200.models.config import DecoderConfig
-    cfg = {'model_type': 'granite', 'hidden_size': 128, 'num_attention_heads': 4, 'num_hidden_layers': 2, 'vocab_size': 512}
-    with pytest.raises(NotImplementedError, match='granite'):
+    cfg = {'model_type': 'cohere', 'hidden_size': 128, 'num_attention_heads': 4, 'num_hidden_layers': 2, 'vocab_size': 512}
+    with pytest.raises(NotImplementedError, match='cohere'):
         DecoderConfig.from_hf(cfg)
     monkeypatch.setenv('TWINKLE_ALLOW_UNKNOWN_ARCH', '1')
     assert DecoderConfig.from_hf(cfg).hidden_size == 128
