@@ -75,6 +75,9 @@ def _cases():
         # OLMo-2: norms on the sub-layer outputs only, q / k norms over the whole projection
         'olmo2': (lambda: T.Olmo2Config(tie_word_embeddings=False, **COMMON), 'Olmo2ForCausalLM'),
         'olmo3': (lambda: T.Olmo3Config(tie_word_embeddings=False, sliding_window=16, **{**COMMON, 'num_hidden_layers': 4}), 'Olmo3ForCausalLM'),
+        # ERNIE-4.5: rotary pairs (2i, 2i+1) over the whole head; SmolLM3: every fourth layer without position information
+        'ernie4_5': (lambda: T.Ernie4_5Config(head_dim=32, tie_word_embeddings=False, use_bias=False, **COMMON), 'Ernie4_5ForCausalLM'),
+        'smollm3': (lambda: T.SmolLM3Config(tie_word_embeddings=True, pad_token_id=0, **{**COMMON, 'num_hidden_layers': 4}), 'SmolLM3ForCausalLM'),
         # Granite: Llama with four constants (embeddings ×, softmax scale, residual ×, logits ÷)
         'granite': (lambda: T.GraniteConfig(tie_word_embeddings=True, embedding_multiplier=12.0, attention_multiplier=0.0078125 * 4, residual_multiplier=0.22,
                                             logits_scaling=8.0, **COMMON), 'GraniteForCausalLM'),
@@ -162,7 +165,7 @@ def test_hf_checkpoint_gives_the_same_logits_here(name, tmp_path):
 
 
 @pytest.mark.parametrize('name', ['qwen3', 'qwen3_moe', 'mixtral', 'qwen2_moe_shared', 'qwen3_5', 'qwen3_5_moe', 'qwen3_next', 'glm', 'glm4', 'phi3',
-                                  'phi3_longrope', 'gemma', 'deepseek_v2', 'deepseek_v3', 'deepseek_v3_yarn', 'glm4_moe', 'gemma2', 'gemma3', 'gpt_oss', 'granite', 'olmo2', 'olmo3'])
+                                  'phi3_longrope', 'gemma', 'deepseek_v2', 'deepseek_v3', 'deepseek_v3_yarn', 'glm4_moe', 'gemma2', 'gemma3', 'gpt_oss', 'granite', 'olmo2', 'olmo3', 'ernie4_5', 'smollm3'])
 def test_checkpoint_saved_here_loads_in_transformers(name, tmp_path):
     hf = _hf_model(name)
     hf.save_pretrained(str(tmp_path / 'hf'), safe_serialization=True)

@@ -18,7 +18,7 @@ from typing import List, Any, Dict, Optional
 SUPPORTED_MODEL_TYPES = frozenset({'llama', 'mistral', 'mixtral', 'qwen2', 'qwen2_moe', 'qwen3', 'qwen3_moe', 'seed_oss', 'qwen2_vl', 'qwen2_vl_text',
                                    'qwen2_5_vl', 'qwen2_5_vl_text', 'qwen3_vl', 'qwen3_vl_text', 'qwen3_vl_moe', 'qwen3_vl_moe_text',
                                    'qwen3_5', 'qwen3_5_text', 'qwen3_5_moe', 'qwen3_5_moe_text', 'qwen3_next', 'glm', 'glm4',
-                                   'phi3', 'internlm2', 'internlm3', 'gemma', 'deepseek_v2', 'deepseek_v3', 'kimi_k2', 'glm4_moe', 'gemma2', 'gemma3_text', 'gemma3', 'gpt_oss', 'granite', 'olmo2', 'olmo3'})
+                                   'phi3', 'internlm2', 'internlm3', 'gemma', 'deepseek_v2', 'deepseek_v3', 'kimi_k2', 'glm4_moe', 'gemma2', 'gemma3_text', 'gemma3', 'gpt_oss', 'granite', 'olmo2', 'olmo3', 'ernie4_5', 'smollm3'})
 
 
 def _rope_scaling_of(cfg: Dict[str, Any]) -> Optional[Dict[str, Any]]:
@@ -84,6 +84,8 @@ class DecoderConfig:
     # q / k norms over the whole projection instead of per head
     pre_norm: bool = True
     qk_norm_full: bool = False
+    # SmolLM3: per layer, 1 = rotary embedding as usual, 0 = no position information in that layer's attention
+    no_rope_layers: Optional[List[int]] = None
     attn_sinks: bool = False
     o_proj_bias: bool = False
     router_linear_bias: bool = False
@@ -303,7 +305,8 @@ class DecoderConfig:
             rms_norm_offset=float(cfg.get('rms_norm_offset', 1.0 if (mt.startswith('gemma') or q35) else 0.0)),
             partial_rotary_factor=float(cfg.get('partial_rotary_factor', (cfg.get('rope_parameters') or {}).get('partial_rotary_factor', 1.0)) or 1.0),
             attn_output_gate=bool(cfg.get('attn_output_gate', q35)),
-            rope_interleaved=bool(cfg.get('rope_interleaved', mt in ('glm', 'glm4'))), sandwich_norm=bool(cfg.get('sandwich_norm', mt == 'glm4' or gemma23 or olmo)),
+            rope_interleaved=bool(cfg.get('rope_interleaved', mt in ('glm', 'glm4', 'ernie4_5'))),
+            no_rope_layers=[int(v) for v in cfg['no_rope_layers']] if (mt == 'smollm3' and cfg.get('no_rope_layers')) else None, sandwich_norm=bool(cfg.get('sandwich_norm', mt == 'glm4' or gemma23 or olmo)),
             layer_types=list(cfg['layer_types']) if cfg.get('layer_types') and ('linear_attention' in cfg['layer_types'] or ('sliding_attention' in cfg['layer_types'] and window)) else None,
             linear_num_key_heads=cfg.get('linear_num_key_heads', 16), linear_num_value_heads=cfg.get('linear_num_value_heads', 32),
             linear_key_head_dim=cfg.get('linear_key_head_dim', 128), linear_value_head_dim=cfg.get('linear_value_head_dim', 128),
@@ -359,6 +362,11 @@ class DecoderConfig:
                      num_experts_per_tok=self.num_experts_per_tok, moe_intermediate_size=self.moe_intermediate_size)
             for k in ('num_experts', 'shared_expert_intermediate_size', 'decoder_sparse_step', 'mlp_only_layers'):
                 d.pop(k, None)
+        elif self.model_type == 'ernie4_5':
+            d.update(architectures=['Ernie4_5ForCausalLM'], use_bias=self.attention_bias)
+        elif self.model_type == 'smollm3':
+            d.update(architectures=['SmolLM3ForCausalLM'], no_rope_layers=list(self.no_rope_layers or [1] * self.num_hidden_layers), use_sliding_window=False,
+                     pad_token_id=self.pad_token_id if self.pad_token_id is not None else 0)
         elif self.model_type in ('olmo2', 'olmo3'):
             d.update(architectures=['Olmo3ForCausalLM' if self.model_type == 'olmo3' else 'Olmo2ForCausalLM'], model_type=self.model_type)
             if self.model_type == 'olmo3':

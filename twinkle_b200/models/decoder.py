@@ -86,12 +86,15 @@ class Attention(nn.Module):
         self.window = cfg.layer_window(layer_idx)          # sliding-window layers see the last ``window`` keys only
         self.softcap = cfg.attn_logit_softcapping
         self.local_rope = bool(cfg.rope_local_theta) and self.window is not None     # Gemma-3: these layers rotate with their own base
+        self.use_rope = not (cfg.no_rope_layers and not cfg.no_rope_layers[layer_idx])   # SmolLM3 leaves position out of some layers
 
     def heads(self, qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor):
         """Fused projection output → ``(q [T,Hq,D], k [T,Hkv,D], v [T,Hkv,D], gate [T,Hq·D] | None)`` after the per-head
         norms and the rotary embedding (head counts are this rank's under tensor parallelism)."""
         qw = self.q_norm.weight if self.q_norm is not None else None
         kw = self.k_norm.weight if self.k_norm is not None else None
+        if not self.use_rope:          # the identity rotation
+            cos, sin = torch.ones_like(cos), torch.zeros_like(sin)
         gate = None
         if self.gated:
             w = (self.hq + 2 * self.hkv) * self.d
@@ -126,7 +129,7 @@ class Attention(nn.Module):
         kw = self.k_norm.weight if self.k_norm is not None else None
         ap = self.attn_parallel
         if (ap is not None and getattr(batch, 'rope_full', None) is not None and kv_sink is None and hasattr(ap, 'project_scatter')
-                and not self.gated and self.norm_offset == 0.0 and self._plain(batch.max_seqlen) and not self.local_rope and not self.qk_norm_full):
+                and not self.gated and self.norm_offset == 0.0 and self._plain(batch.max_seqlen) and not self.local_rope and not self.qk_norm_full and self.use_rope):
             # projection whose epilogue already delivers [T_full, (Hq + 2 Hkv)/sp · D] to every peer
             qkv_full = ap.project_scatter(x, self.qkv_proj, self.hq, self.hkv, self.d)
             if qkv_full is not None:
