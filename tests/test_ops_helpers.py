@@ -26,3 +26,21 @@ def test_rank_mask_scales_the_leading_rank_columns_and_repeats_per_stacked_pool(
 def test_segment_starts_name_the_first_token_of_every_packed_sequence():
     cu = torch.tensor([0, 3, 3, 7], dtype=torch.int32)
     assert ops._segment_starts(cu, 7).tolist() == [0, 0, 0, 3, 3, 3, 3]
+
+
+def test_adapter_options_that_are_not_implemented_are_refused_not_dropped(caplog):
+    import logging
+
+    import pytest
+
+    from twinkle_b200.model.multi_lora import LoraConfig
+    ok = LoraConfig.from_any({'r': 4, 'lora_alpha': 8, 'modules_to_save': None, 'use_dora': False, 'rank_pattern': {}, 'init_lora_weights': True, 'bias': 'none',
+                              'exclude_modules': ('o_proj', ), 'target_modules': {'q_proj', 'v_proj'}})
+    assert ok.r == 4 and ok.exclude_modules == ['o_proj'] and ok.target_modules == ['q_proj', 'v_proj']
+    for bad in ({'use_dora': True}, {'rank_pattern': {'q_proj': 4}}, {'modules_to_save': ['lm_head']}, {'layers_to_transform': [0, 1]}):
+        with pytest.raises(NotImplementedError):
+            LoraConfig.from_any({'r': 4, **bad})
+    assert LoraConfig.from_any(LoraConfig(r=4).to_peft_dict()).r == 4          # what this package writes, it reads
+    with caplog.at_level(logging.WARNING, logger='twinkle_b200'):
+        LoraConfig.from_any({'r': 4, 'lora_dropout': 0.05})
+    assert any('not applied' in r.getMessage() for r in caplog.records)

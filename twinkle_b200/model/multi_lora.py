@@ -37,6 +37,9 @@ class LoraConfig:
     exclude_modules: Union[str, List[str], None] = None  # PEFT: module-name suffixes (or a full-match regex) kept out of ``target_modules``
     base_model_name_or_path: Optional[str] = None
 
+    _UNSUPPORTED = ('use_dora', 'rank_pattern', 'alpha_pattern', 'modules_to_save', 'layers_to_transform', 'layers_pattern', 'use_qalora',
+                    'trainable_token_indices', 'layer_replication', 'megatron_config')
+
     @property
     def scaling(self) -> float:
         return self.lora_alpha / math.sqrt(self.r) if self.use_rslora else self.lora_alpha / self.r
@@ -49,8 +52,19 @@ class LoraConfig:
             with open(os.path.join(obj, 'adapter_config.json')) as f:
                 obj = json.load(f)
         if not isinstance(obj, dict):
-            obj = {k: getattr(obj, k) for k in cls.__dataclass_fields__ if hasattr(obj, k)}
+            obj = {k: getattr(obj, k) for k in tuple(cls.__dataclass_fields__) + cls._UNSUPPORTED if hasattr(obj, k)}
+        # PEFT options that change the adapter's arithmetic or its set of trained tensors and are not implemented here: refused
+        # rather than dropped (a run that silently trained something else is worse than one that does not start)
+        for k in cls._UNSUPPORTED:
+            v = obj.get(k)
+            if v not in (None, False, 0, 0.0, '', [], {}, (), 'none') and not (k == 'init_lora_weights' and v is True) and not (k == 'bias' and v == 'none'):
+                raise NotImplementedError(f'LoRA option {k}={v!r} is not supported (plain LoRA / rsLoRA with target_modules, exclude_modules and '
+                                          'target_parameters are)')
         known = {k: obj[k] for k in cls.__dataclass_fields__ if k in obj and obj[k] is not None}
+        if float(known.get('lora_dropout') or 0.0) > 0.0:
+            import logging
+            logging.getLogger('twinkle_b200').warning('lora_dropout=%s is recorded in the adapter config but not applied: the slot pools serve several '
+                                                      'tenants from one deterministic kernel path', known['lora_dropout'])
         for k in ('target_modules', 'exclude_modules'):
             if isinstance(known.get(k), (set, tuple)):
                 known[k] = sorted(known[k])
