@@ -211,3 +211,24 @@ def test_graded_math_and_multimodal_rewards():
     assert {'OlympiadBenchAccuracyReward', 'MultiModalAccuracyReward'} <= set(reward_mapping)
     row = CompetitionMathGRPOProcessor()([{'problem': '1+1?', 'solution': 'It is \\boxed{2}.'}])[0]
     assert [m['role'] for m in row['messages']] == ['system', 'user'] and row['user_data'] == {'solution': 'It is \\boxed{2}.', 'ground_truth': '2'}
+
+
+def test_torch_schedulers_resolve_by_name():
+    """``set_lr_scheduler`` takes the names of this package's schedulers and of ``torch.optim.lr_scheduler`` classes."""
+    import pytest
+
+    from twinkle_b200.model import TransformersModel
+    from twinkle_b200.module.scheduler import resolve_scheduler
+    assert resolve_scheduler('cosine').__name__ == 'CosineWarmupScheduler' and resolve_scheduler('StepLR').__name__ == 'StepLR'
+    with pytest.raises(KeyError):
+        resolve_scheduler('NoSuchScheduler')
+    m = TransformersModel(model_id='tiny-dense', seed=0, device='cpu')
+    m.set_optimizer('AdamW', lr=1e-2)
+    m.set_lr_scheduler('StepLR', step_size=1, gamma=0.5)
+    ids = list(range(3, 40))
+    lrs = []
+    for _ in range(3):
+        m.forward_backward(inputs=[{'input_ids': ids[:-1], 'labels': ids[1:]}])
+        m.clip_grad_and_step(max_grad_norm=1.0)
+        lrs.append(m._group(None).optimizer.param_groups[0]['lr'])
+    assert lrs == pytest.approx([5e-3, 2.5e-3, 1.25e-3])

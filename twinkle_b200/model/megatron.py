@@ -577,7 +577,8 @@ class MegatronModel(TwinkleModel):
         if og.optimizer is None:
             self.set_optimizer('AdamW')
         if isinstance(scheduler_cls, str):
-            scheduler_cls = scheduler_mapping[scheduler_cls]
+            from ..module.scheduler import resolve_scheduler
+            scheduler_cls = resolve_scheduler(scheduler_cls)
         og.lr_scheduler = scheduler_cls(og.optimizer, **kwargs) if isinstance(scheduler_cls, type) else scheduler_cls
 
     @remote_function()
@@ -1118,7 +1119,8 @@ class MultiLoraMegatronModel(MegatronModel):
         if og.optimizer is None:
             self.set_optimizer('AdamW', adapter_name=og.adapter_name)
         if isinstance(scheduler_cls, str):
-            scheduler_cls = scheduler_mapping[scheduler_cls]
+            from ..module.scheduler import resolve_scheduler
+            scheduler_cls = resolve_scheduler(scheduler_cls)
         og.lr_scheduler = scheduler_cls(og.optimizer, **kwargs) if isinstance(scheduler_cls, type) else scheduler_cls
 
     def calculate_metric(self, is_training: bool = True, adapter_name: Optional[str] = None, **kwargs) -> Dict[str, Any]:

@@ -796,7 +796,8 @@ class TransformersModel(TwinkleModel, CheckpointEngineMixin):
         if og.optimizer is None:
             self.set_optimizer('AdamW', adapter_name=adapter_name)
         if isinstance(scheduler_cls, str):
-            scheduler_cls = scheduler_mapping[scheduler_cls]
+            from ..module.scheduler import resolve_scheduler
+            scheduler_cls = resolve_scheduler(scheduler_cls)
         og.lr_scheduler = scheduler_cls(og.optimizer, **kwargs) if isinstance(scheduler_cls, type) else scheduler_cls
 
     @remote_function()

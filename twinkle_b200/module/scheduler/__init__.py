@@ -48,3 +48,15 @@ scheduler_mapping = {
     'CosineWarmupScheduler': CosineWarmupScheduler, 'LinearWarmupScheduler': LinearWarmupScheduler,
     'ConstantWarmupScheduler': ConstantWarmupScheduler,
 }
+
+
+def resolve_scheduler(name: str):
+    """A scheduler class by name: the ones of this module first, then any class of ``torch.optim.lr_scheduler`` (reference
+    ``model/transformers/transformers.py:975-992`` looks names up in both places)."""
+    if name in scheduler_mapping:
+        return scheduler_mapping[name]
+    import torch.optim.lr_scheduler as tls
+    cls = getattr(tls, name, None)
+    if isinstance(cls, type) and issubclass(cls, tls.LRScheduler):
+        return cls
+    raise KeyError(f'unknown lr scheduler {name!r}; known: {sorted(scheduler_mapping)} and the classes of torch.optim.lr_scheduler')
