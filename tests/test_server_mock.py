@@ -125,6 +125,10 @@ def test_twinkle_client_and_processor(server):
     with pytest.raises(TwinkleClientError):
         c.get_training_run('no-such-run')
     c.close()
+    from twinkle_b200.client import init_twinkle_client
+    c2 = init_twinkle_client(api_key='alice', session_heartbeat_interval=30, app=server.root)      # the reference's argument names
+    assert c2.t.token == 'alice' and c2.list_training_runs(limit=1)
+    c2.close()
 
 
 def test_admission_control_and_state(server, tmp_path):

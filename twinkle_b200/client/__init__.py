@@ -166,8 +166,14 @@ class TwinkleClient:
 TwinkleClientError = HttpError
 
 
-def init_twinkle_client(base_url: Optional[str] = None, token: Optional[str] = None, **kw) -> TwinkleClient:
-    c = TwinkleClient(base_url, token, **kw)
+def init_twinkle_client(base_url: Optional[str] = None, token: Optional[str] = None, *, api_key: Optional[str] = None,
+                        session_heartbeat_interval: Optional[float] = None, **kw) -> TwinkleClient:
+    """The client that later ``MultiLoraTransformersModel`` / sampler / dataset twins use by default.  ``api_key`` and
+    ``session_heartbeat_interval`` are the reference's names for ``token`` and ``heartbeat_interval`` (reference
+    ``twinkle_client/__init__.py:37-75``); URL and token fall back to ``TWINKLE_SERVER_URL`` / ``TWINKLE_SERVER_TOKEN``."""
+    if session_heartbeat_interval is not None:
+        kw.setdefault('heartbeat_interval', float(session_heartbeat_interval))
+    c = TwinkleClient(base_url, token or api_key, **kw)
     _DEFAULT['client'] = c
     return c
 
