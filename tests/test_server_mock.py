@@ -95,6 +95,9 @@ def test_twinkle_client_and_processor(server):
     out = m.forward_backward(inputs=[{'input_ids': [1, 2, 3], 'labels': [2, 3, -100]}], adapter_name='a')
     assert 'loss' in out
     assert m.clip_grad_and_step(adapter_name='a') == 1.0
+    assert 'loss' in m.forward_backward([{'input_ids': [1, 2, 3], 'labels': [2, 3, -100]}], adapter_name='a')       # inputs by position, as against a local model
+    assert m.clip_grad_and_step(1.0, 2, adapter_name='a') == 1.0
+    assert MultiLoraTransformersModel('ms://mock-base', client=c).model_id == 'mock-base'                          # hub prefixes name the same served model
     s = TorchSampler('mock-base', client=c)
     s.set_template('Template')
     r = s.sample([{'messages': [{'role': 'user', 'content': 'hi'}]}], {'max_tokens': 3})

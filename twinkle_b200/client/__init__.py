@@ -189,6 +189,8 @@ class MultiLoraTransformersModel:
     """HTTP twin: every method posts to ``<model_prefix>/<base_model>/twinkle/<method>``."""
 
     def __init__(self, model_id: str, client: Optional[TwinkleClient] = None, **kwargs):
+        if '://' in model_id:          # 'ms://org/name' and 'hf://org/name' address the same served model as 'org/name'
+            model_id = model_id.split('://', 1)[1]
         self.c, self.model_id = _client(client), model_id
         self.prefix = f'{self.c.model_prefix}/{model_id}'
         self.c.t.post(self.prefix + '/twinkle/create', {'model_id': model_id, 'session_id': self.c.session_id, **kwargs})
@@ -212,7 +214,9 @@ class MultiLoraTransformersModel:
     _POSITIONAL = {'set_loss': ('loss_cls', ), 'set_optimizer': ('optimizer_cls', ), 'set_lr_scheduler': ('scheduler_cls', ),
                    'set_template': ('template_cls', ), 'set_processor': ('processor_cls', ), 'add_metric': ('metric_cls', 'is_training'),
                    'apply_patch': ('patch_cls', ), 'calculate_metric': ('is_training', ), 'save': ('name', 'output_dir'),
-                   'load': ('name', 'output_dir'), 'resume_from_checkpoint': ('name', )}
+                   'load': ('name', 'output_dir'), 'resume_from_checkpoint': ('name', ), 'forward': ('inputs', ), 'forward_only': ('inputs', ),
+                   'forward_backward': ('inputs', ), 'clip_grad_norm': ('max_grad_norm', 'norm_type'), 'clip_grad_and_step': ('max_grad_norm', 'norm_type'),
+                   'upload_to_hub': ('checkpoint_dir', 'hub_model_id', 'hub_token', 'async_upload')}
 
     def __getattr__(self, name: str):
         if name.startswith('_'):
