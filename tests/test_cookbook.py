@@ -71,8 +71,10 @@ def test_http_twin_positional_arguments():
         twin.set_optimizer('AdamW', 'extra')
     with pytest.raises(TypeError):
         twin.set_loss('GRPOLoss', loss_cls='DPOLoss')
+    twin.forward_backward([{'input_ids': [1]}], adapter_name='a')          # the reference's HTTP twin takes the batch by position
+    assert seen['method'] == 'forward_backward' and seen['kw'] == dict(inputs=[{'input_ids': [1]}])
     with pytest.raises(TypeError):
-        twin.forward_backward([{'input_ids': [1]}])          # inputs are keyword-only, as on the local model
+        twin.forward_backward([{'input_ids': [1]}], [{'input_ids': [2]}])
 
 
 def test_sft_pipeline_cli_trains_saves_resumes_and_evaluates(tmp_path):
