@@ -98,7 +98,8 @@ def test_twinkle_client_and_processor(server):
     assert 'loss' in m.forward_backward([{'input_ids': [1, 2, 3], 'labels': [2, 3, -100]}], adapter_name='a')       # inputs by position, as against a local model
     assert m.clip_grad_and_step(1.0, 2, adapter_name='a') == 1.0
     assert MultiLoraTransformersModel('ms://mock-base', client=c).model_id == 'mock-base'                          # hub prefixes name the same served model
-    s = TorchSampler('mock-base', client=c)
+    s = TorchSampler('ms://mock-base', client=c)
+    assert s.model_id == 'mock-base' and s.apply_patch('Qwen3ChatTemplate') == {'status': 'ok'}
     s.set_template('Template')
     r = s.sample([{'messages': [{'role': 'user', 'content': 'hi'}]}], {'max_tokens': 3})
     assert len(r[0]['sequences'][0]['tokens']) == 3 and r[0]['sequences'][0]['new_input_feature']['labels'][-2] != -100

@@ -238,6 +238,8 @@ class MultiLoraTransformersModel:
 class TorchSampler:
 
     def __init__(self, model_id: str, client: Optional[TwinkleClient] = None, **kwargs):
+        if '://' in model_id:
+            model_id = model_id.split('://', 1)[1]
         self.c, self.model_id = _client(client), model_id
         self.prefix = f'{self.c.sampler_prefix}/{model_id}'
         self.c.t.post(self.prefix + '/twinkle/create', {'model_id': model_id, 'session_id': self.c.session_id})
@@ -248,6 +250,9 @@ class TorchSampler:
     def add_adapter_to_sampler(self, adapter_name: str, config_or_dir):
         key = 'adapter_path' if isinstance(config_or_dir, str) else 'config'
         return self.c.t.post(self.prefix + '/twinkle/add_adapter_to_sampler', {'adapter_name': adapter_name, key: config_or_dir})
+
+    def apply_patch(self, patch_cls: str, **kwargs):
+        return self.c.t.post(self.prefix + '/twinkle/apply_patch', {'patch_cls': patch_cls, 'kwargs': kwargs})
 
     def sample(self, inputs, sampling_params=None, adapter_name=None, adapter_path=None, **kw):
         sp = sampling_params.to_dict() if hasattr(sampling_params, 'to_dict') else sampling_params
