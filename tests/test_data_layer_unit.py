@@ -209,3 +209,16 @@ def test_arrow_and_feather_files_load_like_the_other_formats(tmp_path):
     os.makedirs(tmp_path / 'set.lance')
     with pytest.raises(ImportError):          # the Lance reader is an optional package; the error says which
         Dataset(DatasetMeta(str(tmp_path / 'set.lance')))
+
+
+def test_dataloader_collates_with_a_processor_when_one_is_set():
+    from twinkle_b200.dataloader import DataLoader
+    from twinkle_b200.dataset import Dataset, DatasetMeta
+    rows = [{'input_ids': list(range(3, 3 + n)), 'labels': list(range(4, 4 + n))} for n in (5, 7, 6, 4)]
+    dl = DataLoader(Dataset(DatasetMeta(data=rows)), batch_size=2, shuffle=False)
+    assert isinstance(next(iter(dl)), list)                              # rows as they are: the model collates
+    dl.set_processor('InputProcessor')
+    batch = next(iter(dl))
+    assert len(batch) == 1 and batch[0].cu_seqlens.tolist() == [0, 5, 12] and batch[0].max_seqlen == 7        # the two rows packed into one micro-batch
+    dl.set_processor(lambda rows: len(rows))
+    assert next(iter(dl)) == 2

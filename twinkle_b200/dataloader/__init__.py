@@ -133,6 +133,18 @@ class DataLoader:
 
     resume_from_checkpoint = skip_consumed_samples
 
+    @remote_function()
+    def set_processor(self, processor_cls, **kwargs) -> None:
+        """Collate every batch with an ``InputProcessor`` (a class, its name, an instance, or any callable on a list of rows);
+        by default batches stay lists of rows and the model collates (reference ``dataloader/dataloader.py:95-104``)."""
+        from .. import processor as processors
+        from ..utils.loader import construct_class
+        if callable(processor_cls) and not isinstance(processor_cls, (str, type)):
+            self.collate_fn = processor_cls
+            return
+        kwargs.setdefault('device_mesh', self.device_mesh)
+        self.collate_fn = construct_class(processor_cls, processors.InputProcessor, processors, **kwargs)
+
     @remote_function(collect='first')
     def get_state(self) -> Dict[str, Any]:
         return {'consumed_train_samples': self.consumed_train_samples, 'epoch': self.epoch}
