@@ -222,3 +222,21 @@ def test_dataloader_collates_with_a_processor_when_one_is_set():
     assert len(batch) == 1 and batch[0].cu_seqlens.tolist() == [0, 5, 12] and batch[0].max_seqlen == 7        # the two rows packed into one micro-batch
     dl.set_processor(lambda rows: len(rows))
     assert next(iter(dl)) == 2
+
+
+def test_image_columns_switch_between_bytes_and_decoded_images(tmp_path):
+    from PIL import Image
+
+    from twinkle_b200.dataset import Dataset, DatasetMeta
+    rows = [{'images': [Image.new('RGB', (4, 3), (255, 0, 0))], 'text': 'a'}, {'images': Image.new('RGB', (2, 2), (0, 255, 0)), 'text': 'b'}]
+    ds = Dataset(DatasetMeta(data=rows))
+    ds.cast_column('images', decode=False)
+    assert isinstance(ds[0]['images'][0]['bytes'], bytes) and isinstance(ds[1]['images']['bytes'], bytes) and ds[0]['text'] == 'a'
+    ds.cast_column('images', decode=True)
+    assert ds[0]['images'][0].size == (4, 3) and ds[1]['images'].getpixel((0, 0)) == (0, 255, 0)
+    ds.save_as(str(tmp_path / 'seen.jsonl'), mode='training')
+    ds.cast_column('images', decode=False)
+    _ = ds[1]
+    ds.flush_save()
+    _ = ds[0]                                                        # read after the writer was closed: not recorded
+    assert len(open(tmp_path / 'seen.jsonl').read().strip().splitlines()) == 1

@@ -272,6 +272,35 @@ class Dataset(TorchDataset):
             import pyarrow.parquet as pq
             pq.write_table(pa.Table.from_pylist(rows), path)
 
+    def flush_save(self) -> None:
+        """End the write-through started by ``save_as(mode='training')`` (every row was appended and flushed as it was read,
+        so nothing is pending; reference ``dataset/base.py:389-394``)."""
+        self._writer = None
+
+    def cast_column(self, column: str, decode: bool = True) -> None:
+        """Keep an image column as raw bytes (``decode=False``: ``{'bytes': …}`` per image, cheap to carry through ``map``) or
+        as decoded images (``decode=True``) — reference ``dataset/base.py:231-241``."""
+        import io
+
+        def one(v):
+            if isinstance(v, (list, tuple)):
+                return [one(x) for x in v]
+            if decode:
+                raw = v.get('bytes') if isinstance(v, dict) else (v if isinstance(v, (bytes, bytearray)) else None)
+                if raw is None:
+                    return v
+                from PIL import Image
+                return Image.open(io.BytesIO(raw)).convert('RGB')
+            if hasattr(v, 'save') and hasattr(v, 'mode'):        # a PIL image
+                buf = io.BytesIO()
+                v.save(buf, format='PNG')
+                return {'bytes': buf.getvalue(), 'path': None}
+            return v
+
+        for row in self._rows():
+            if column in row:
+                row[column] = one(row[column])
+
     def __getitem__(self, idx):
         row = self._rows()[idx]
         if self._writer is not None:
