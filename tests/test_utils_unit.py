@@ -350,3 +350,18 @@ def test_device_placement_of_explicit_groups():
     assert "group 'training_cluster'" in text and "('pp', 'dp', 'tp')" in text and 'inference' in text
     assert 'rank 13: coord (1, 1, 1) data_rank 1' in text          # pp 1, dp 1, tp 1
     assert get_device_placement([]) == 'No device group provided.'
+
+
+def test_tensor_helpers_of_the_utils_namespace():
+    import twinkle_b200.utils as u
+    moved = u.to_device({'a': torch.ones(2), 'b': [torch.zeros(1), 'text'], 'c': 3}, 'cpu')
+    assert moved['b'][1] == 'text' and moved['c'] == 3 and moved['a'].device.type == 'cpu'
+    sd = u.clone_state_dict_to_cpu({'w': torch.ones(2, requires_grad=True), 'step': 4})
+    assert not sd['w'].requires_grad and sd['step'] == 4
+    assert u.pad_sequence_to_length(torch.ones(2, 3), 5, -1.0).tolist()[0] == [1, 1, 1, -1, -1]
+    assert u.pad_sequence_to_length(torch.ones(2, 3), 5, -1.0, left_pad=True).tolist()[0] == [-1, -1, 1, 1, 1]
+    cat = u.pad_and_stack_tensors([torch.ones(2, 3), torch.ones(1, 5)])
+    assert cat.shape == (3, 5) and cat[0, 3:].tolist() == [-200, -200] and cat[2].tolist() == [1] * 5
+    assert u.pad_and_stack_tensors([torch.ones(2, 3), torch.ones(1, 5)], pad_value=0, concat=False).shape == (2, 2, 5)
+    for name in ('SafetensorLazyLoader', 'StreamingSafetensorSaver', 'selective_log_softmax', 'framework_util', 'torch_util', 'processing_lock', 'Dequantizer'):
+        assert hasattr(u, name), name

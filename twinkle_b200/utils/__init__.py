@@ -8,3 +8,9 @@ from .misc import (align_logps_to_mask, call_with_supported_kwargs, copy_files_b
 from .network import find_free_port, find_node_ip
 from .platform import GPU, Platform
 from .seed import stable_seed
+from . import framework as framework_util
+from . import torch_utils as torch_util
+from .dequantizer import Dequantizer, dequant_fp8_block, dequant_mxfp4
+from .parallel import file_lock as processing_lock
+from .safetensors_io import SafetensorLazyLoader, StreamingSafetensorSaver
+from .torch_utils import (clone_state_dict_to_cpu, pad_and_stack_tensors, pad_sequence_to_length, selective_log_softmax, to_device)

@@ -63,3 +63,45 @@ def pad_and_stack(tensors, pad_value=0, side: str = 'right') -> torch.Tensor:
             t = torch.cat([t, filler] if side == 'right' else [filler, t], 0)
         out.append(t)
     return torch.stack(out, 0)
+
+
+# ---------------------------------------------------------------- small helpers (reference ``utils/torch_utils.py:11-60, 235-260``)
+def to_device(data, device, non_blocking: bool = False):
+    """Tensors inside (nested) mappings, lists and tuples moved to ``device``; everything else returned as it is."""
+    if isinstance(data, dict):
+        return type(data)((k, to_device(v, device, non_blocking)) for k, v in data.items())
+    if isinstance(data, (list, tuple)):
+        return type(data)(to_device(v, device, non_blocking) for v in data)
+    return data.to(device, non_blocking=non_blocking) if isinstance(data, torch.Tensor) else data
+
+
+def clone_state_dict_to_cpu(state_dict) -> dict:
+    """Detached host copies of every tensor of a state dict (other values pass through)."""
+    return {k: (v.detach().to('cpu', copy=True) if isinstance(v, torch.Tensor) else v) for k, v in state_dict.items()}
+
+
+def pad_sequence_to_length(tensor: torch.Tensor, max_seq_len: int, pad_value: float = 0.0, left_pad: bool = False) -> torch.Tensor:
+    """The last dimension padded with ``pad_value`` up to ``max_seq_len`` (unchanged when it is already that long)."""
+    n = max_seq_len - tensor.shape[-1]
+    if n <= 0:
+        return tensor
+    return torch.nn.functional.pad(tensor, (n, 0) if left_pad else (0, n), value=pad_value)
+
+
+def pad_and_stack_tensors(tensors, pad_value: float = -200, concat: bool = True) -> torch.Tensor:
+    """Tensors of equal rank and differing sizes padded (at the end of every dimension) to their common largest shape, then
+    concatenated along the first dimension (``concat=True``: rows of all tensors in one batch) or stacked on a new one."""
+    if not tensors:
+        raise ValueError('no tensors to pad')
+    rank = tensors[0].dim()
+    if any(t.dim() != rank for t in tensors):
+        raise ValueError('tensors must have the same number of dimensions')
+    dims = range(1, rank) if concat else range(rank)
+    target = {d: max(t.shape[d] for t in tensors) for d in dims}
+    out = []
+    for t in tensors:
+        pad = []
+        for d in reversed(range(rank)):
+            pad += [0, (target[d] - t.shape[d]) if d in target else 0]
+        out.append(torch.nn.functional.pad(t, pad, value=pad_value))
+    return torch.cat(out, 0) if concat else torch.stack(out, 0)
